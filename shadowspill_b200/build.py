@@ -1,0 +1,123 @@
+"""In-tree native build: CUDA kernels for sm_100a and the C++ core libraries.
+
+Everything is compiled with explicit ``nvcc`` / ``g++`` commands into shared
+objects that sit next to their sources, so a source snapshot that carries the
+built ``.so`` files runs without a JIT cache. ``python -m shadowspill_b200.build``
+rebuilds what is stale.
+
+The reference builds its C11 core with CMake and no ``nvcc`` at all
+(packages/engine/csrc/backends/CMakeLists.txt:74-119); this build has CUDA
+sources, so the kernel library is compiled for ``sm_100a`` only.
+"""
+from __future__ import annotations
+
+import concurrent.futures
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+KERNEL_DIR = ROOT / "ops" / "csrc"
+KERNEL_LIB = ROOT / "ops" / "libss_kernels.so"
+CORE_DIR = ROOT / "csrc"
+CORE_LIB = CORE_DIR / "libss_core.so"
+CUDA_BACKEND_LIB = CORE_DIR / "libss_backend_cuda.so"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall",
+]
+CXX_FLAGS = ["-O2", "-g", "-std=c++17", "-fPIC", "-Wall", "-Wextra", "-pthread"]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and Path(cand).exists():
+            return cand
+    raise RuntimeError("nvcc not found; set NVCC or install the CUDA toolkit")
+
+
+def _stale(target: Path, sources: list[Path]) -> bool:
+    if not target.exists():
+        return True
+    t = target.stat().st_mtime
+    return any(s.stat().st_mtime > t for s in sources)
+
+
+def _run(cmd: list[str], verbose: bool) -> None:
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError(f"command failed: {' '.join(cmd)}\n{proc.stdout}\n{proc.stderr}")
+    if verbose and proc.stderr.strip():
+        print(proc.stderr, file=sys.stderr)
+
+
+def build_kernels(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> Path:
+    """Compile every ``ops/csrc/*.cu`` for sm_100a and link ``libss_kernels.so``."""
+    sources = sorted(KERNEL_DIR.glob("*.cu"))
+    headers = sorted(KERNEL_DIR.glob("*.cuh")) + sorted(KERNEL_DIR.glob("*.h"))
+    if not sources:
+        raise RuntimeError(f"no CUDA sources under {KERNEL_DIR}")
+    if not force and not _stale(KERNEL_LIB, sources + headers):
+        return KERNEL_LIB
+    nvcc = _nvcc()
+    objdir = KERNEL_DIR / "build"
+    objdir.mkdir(exist_ok=True)
+    extra = ["-Xptxas", "-v"] if ptxas_info else []
+
+    def compile_one(src: Path) -> Path:
+        obj = objdir / (src.stem + ".o")
+        if force or _stale(obj, [src] + headers):
+            _run([nvcc, *NVCC_FLAGS, *extra, "-c", str(src), "-o", str(obj)], verbose)
+        return obj
+
+    with concurrent.futures.ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as pool:
+        objs = list(pool.map(compile_one, sources))
+    tmp = KERNEL_LIB.with_suffix(".so.tmp")
+    _run([nvcc, "-shared", "-o", str(tmp), *map(str, objs), "-lcudart"], verbose)
+    os.replace(tmp, KERNEL_LIB)
+    return KERNEL_LIB
+
+
+def _cuda_home() -> Path | None:
+    for cand in (os.environ.get("CUDA_HOME"), "/usr/local/cuda"):
+        if cand and (Path(cand) / "include" / "cuda_runtime.h").exists():
+            return Path(cand)
+    return None
+
+
+def build_core(force: bool = False, verbose: bool = False) -> Path:
+    """Compile the C++17 core (simulator, planner, runtime, mock backend)."""
+    sources = sorted(p for p in CORE_DIR.rglob("*.cpp") if "backend_cuda" not in p.name
+                     and "canary" not in p.name)
+    headers = sorted(CORE_DIR.rglob("*.h")) + sorted(CORE_DIR.rglob("*.hpp"))
+    if not sources:
+        return CORE_LIB
+    if force or _stale(CORE_LIB, sources + headers):
+        tmp = CORE_LIB.with_suffix(".so.tmp")
+        _run(["g++", *CXX_FLAGS, "-shared", "-I", str(CORE_DIR / "include"), "-o", str(tmp),
+              *map(str, sources), "-ldl"], verbose)
+        os.replace(tmp, CORE_LIB)
+    cuda_src = sorted(CORE_DIR.rglob("backend_cuda*.cpp"))
+    cuda = _cuda_home()
+    if cuda_src and cuda is not None and (force or _stale(CUDA_BACKEND_LIB, cuda_src + headers)):
+        tmp = CUDA_BACKEND_LIB.with_suffix(".so.tmp")
+        _run(["g++", *CXX_FLAGS, "-shared", "-I", str(CORE_DIR / "include"),
+              "-I", str(cuda / "include"), "-o", str(tmp), *map(str, cuda_src),
+              "-L", str(cuda / "lib64"), "-lcudart", "-ldl"], verbose)
+        os.replace(tmp, CUDA_BACKEND_LIB)
+    return CORE_LIB
+
+
+def build_all(force: bool = False, verbose: bool = False) -> None:
+    build_kernels(force=force, verbose=verbose)
+    build_core(force=force, verbose=verbose)
+
+
+if __name__ == "__main__":
+    build_all(force="--force" in sys.argv, verbose="-v" in sys.argv or "--verbose" in sys.argv)
+    print("built:", KERNEL_LIB, CORE_LIB)

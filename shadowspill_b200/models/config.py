@@ -1,0 +1,149 @@
+"""Model family configurations and the named presets (``<family>-<size>``).
+
+The catalog mirrors the reference's preset table
+(packages/workloads/src/shadowspill_workloads/MODELS.md:38-59): same layer counts,
+widths, head geometry, expert counts and vocabularies, so a preset name means
+the same architecture in both systems.
+"""
+from __future__ import annotations
+
+from dataclasses import asdict, dataclass, field, replace
+from typing import Any
+
+
+@dataclass(frozen=True)
+class DecoderConfig:
+    family: str
+    n_layers: int
+    d_model: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    d_ff: int
+    vocab_size: int
+    rope_base: float = 500_000.0
+    rotary_fraction: float = 1.0          # Qwen 3.5 rotates a quarter of each head
+    norm_epsilon: float = 1e-5
+    zero_centered_norm: bool = False      # Qwen 3.5: weight stored as offset from one
+    qk_norm: bool = False                 # Qwen 3 family: RMSNorm on each q/k head
+    gated_attention: bool = False         # Qwen 3.5: sigmoid output gate on attention
+    tied_embeddings: bool = False
+    initializer_range: float = 0.02
+    # hybrid linear attention (Gated DeltaNet)
+    full_attention_interval: int = 0      # every k-th layer is full attention; 0 = all layers
+    dn_qk_heads: int = 0
+    dn_v_heads: int = 0
+    dn_head_dim: int = 128
+    dn_conv_width: int = 4
+    dn_chunk: int = 64
+    # mixture of experts
+    n_experts: int = 0
+    top_k: int = 0
+    d_expert: int = 0
+    d_shared_expert: int = 0              # 0 = no shared expert
+    gated_shared_expert: bool = False
+    router_renormalize: bool = True
+    router_aux_coef: float = 0.0
+
+    def __post_init__(self) -> None:
+        if self.n_heads % self.n_kv_heads:
+            raise ValueError("n_heads must be divisible by n_kv_heads")
+        if self.n_experts and not (0 < self.top_k <= self.n_experts):
+            raise ValueError("top_k must be in [1, n_experts]")
+        if self.full_attention_interval and not self.dn_v_heads:
+            raise ValueError("hybrid models need DeltaNet head counts")
+
+    @property
+    def is_moe(self) -> bool:
+        return self.n_experts > 0
+
+    @property
+    def rotary_width(self) -> int:
+        w = int(self.head_dim * self.rotary_fraction)
+        return w - (w % 4)
+
+    def layer_kind(self, index: int) -> str:
+        """``attention`` or ``deltanet`` for layer ``index``."""
+        k = self.full_attention_interval
+        if k and (index + 1) % k != 0:
+            return "deltanet"
+        return "attention"
+
+    def to_json(self) -> dict[str, Any]:
+        return asdict(self)
+
+    @staticmethod
+    def from_json(d: dict[str, Any]) -> "DecoderConfig":
+        return DecoderConfig(**d)
+
+    def parameter_count(self) -> int:
+        from .decoder import build_stages
+        return sum(s.parameter_count() for s in build_stages(self))
+
+
+def _llama(n_layers, d, h, kv, ff, vocab=128_256, hd=None, **kw):
+    return DecoderConfig("llama3", n_layers, d, h, kv, hd or d // h, ff, vocab, **kw)
+
+
+def _qwen3(n_layers, d, h, kv, hd, ff, vocab=151_936, **kw):
+    return DecoderConfig("qwen3", n_layers, d, h, kv, hd, ff, vocab, rope_base=1_000_000.0,
+                         norm_epsilon=1e-6, qk_norm=True, **kw)
+
+
+def _qwen35(n_layers, d, h, kv, hd, ff, dnk, dnv, vocab=248_320, interval=4, dnhd=128, **kw):
+    return DecoderConfig("qwen35", n_layers, d, h, kv, hd, ff, vocab, rope_base=10_000_000.0,
+                         rotary_fraction=0.25, norm_epsilon=1e-6, zero_centered_norm=True,
+                         qk_norm=True, gated_attention=True, full_attention_interval=interval,
+                         dn_qk_heads=dnk, dn_v_heads=dnv, dn_head_dim=dnhd, **kw)
+
+
+PRESETS: dict[str, DecoderConfig] = {
+    # ---- Llama 3: GQA + dense SwiGLU
+    "llama3-tiny": _llama(2, 128, 4, 2, 256, vocab=512),
+    "llama3-plumbing": _llama(4, 256, 4, 2, 688, vocab=4096, rope_base=10_000.0),
+    "llama3-numerical": _llama(12, 2048, 16, 4, 7168),
+    "llama3-1b": _llama(16, 2048, 32, 8, 8192),
+    "llama3-8b": _llama(32, 4096, 32, 8, 14336),
+    # ---- Qwen 3: GQA with q/k norms + dense SwiGLU
+    "qwen3-tiny": _qwen3(2, 128, 4, 2, 64, 256, vocab=512),
+    "qwen3-1.7b": _qwen3(28, 2048, 16, 8, 128, 6144),
+    "qwen3-8b": _qwen3(36, 4096, 32, 8, 128, 12288),
+    "qwen3-32b": _qwen3(64, 5120, 64, 8, 128, 25600),
+    # ---- Qwen 3.5: 3 Gated DeltaNet : 1 gated full attention
+    "qwen35-tiny": _qwen35(2, 128, 4, 2, 32, 256, 2, 4, vocab=512, interval=2, dnhd=32),
+    "qwen35-numerical": _qwen35(8, 1536, 12, 4, 128, 4608, 6, 12),
+    "qwen35-2b": _qwen35(24, 2048, 8, 2, 256, 6144, 16, 16),
+    "qwen35-9b": _qwen35(32, 4096, 16, 4, 256, 12288, 16, 32),
+    "qwen35-27b": _qwen35(64, 5120, 24, 4, 256, 17408, 16, 48),
+    # ---- OLMoE: GQA + routed SwiGLU experts
+    "olmoe-tiny": DecoderConfig("olmoe", 2, 128, 4, 2, 32, 0, 512, rope_base=10_000.0,
+                                qk_norm=True, n_experts=8, top_k=2, d_expert=128,
+                                router_renormalize=False),
+    "olmoe-numerical": DecoderConfig("olmoe", 16, 1024, 8, 8, 128, 0, 50_304, rope_base=10_000.0,
+                                     qk_norm=True, n_experts=16, top_k=4, d_expert=1024,
+                                     router_renormalize=False),
+    "olmoe-7b-a1b": DecoderConfig("olmoe", 16, 2048, 16, 16, 128, 0, 50_304, rope_base=10_000.0,
+                                  qk_norm=True, n_experts=64, top_k=8, d_expert=1024,
+                                  router_renormalize=False),
+    # ---- Qwen 3 MoE
+    "qwen3moe-tiny": DecoderConfig("qwen3moe", 2, 128, 4, 2, 32, 0, 1024, rope_base=1_000_000.0,
+                                   norm_epsilon=1e-6, qk_norm=True, n_experts=8, top_k=2,
+                                   d_expert=128),
+    "qwen3moe-30b-a3b": DecoderConfig("qwen3moe", 48, 2048, 32, 4, 128, 0, 151_936,
+                                      rope_base=1_000_000.0, norm_epsilon=1e-6, qk_norm=True,
+                                      n_experts=128, top_k=8, d_expert=768),
+    # ---- Qwen 3.5 MoE: hybrid attention, routed + gated shared expert
+    "qwen35moe-tiny": replace(_qwen35(2, 128, 4, 2, 32, 0, 2, 4, vocab=1024, interval=2, dnhd=32),
+                              family="qwen35moe", n_experts=8, top_k=2, d_expert=128,
+                              d_shared_expert=128, gated_shared_expert=True),
+    "qwen35moe-35b-a3b": replace(_qwen35(40, 2048, 16, 2, 256, 0, 16, 32), family="qwen35moe",
+                                 n_experts=256, top_k=8, d_expert=512, d_shared_expert=512,
+                                 gated_shared_expert=True),
+}
+
+
+def preset(name: str) -> DecoderConfig:
+    try:
+        return PRESETS[name]
+    except KeyError:
+        raise KeyError(f"unknown model preset {name!r}; known: {sorted(PRESETS)}") from None

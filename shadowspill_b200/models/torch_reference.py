@@ -1,0 +1,89 @@
+"""Autograd twin of the dense decoder: the same parameters, plain PyTorch ops,
+gradients by ``torch.autograd``. It is the independent oracle for the
+hand-written stage backward passes (the role the reference gives its
+pure-PyTorch implementations, e.g.
+packages/workloads/src/shadowspill_workloads/models/llama3/implementations/pytorch.py).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as TF
+
+from .config import DecoderConfig
+from .decoder import BatchMeta
+
+
+def _rms(x, w, eps, zero_centered):
+    xf = x.float()
+    r = torch.rsqrt(xf.square().mean(-1, keepdim=True) + eps)
+    scale = (1 + w.float()) if zero_centered else w.float()
+    return (xf * r * scale).to(x.dtype)
+
+
+def _rope(x, positions, rot, theta):
+    # x [T, H, dh]
+    half = rot // 2
+    inv = theta ** (-torch.arange(0, half, dtype=torch.float32, device=x.device) * 2.0 / rot)
+    ang = positions.float()[:, None] * inv[None]
+    cos, sin = ang.cos()[:, None], ang.sin()[:, None]
+    a, b, rest = x[..., :half].float(), x[..., half:rot].float(), x[..., rot:]
+    return torch.cat([(a * cos - b * sin).to(x.dtype), (b * cos + a * sin).to(x.dtype), rest], -1)
+
+
+def _attention(q, k, v, cu):
+    T, Hq, dh = q.shape
+    rep = Hq // k.shape[1]
+    outs = []
+    b = cu.tolist()
+    for s, e in zip(b[:-1], b[1:]):
+        if e <= s:
+            continue
+        qs = q[s:e].transpose(0, 1)[None]
+        ks = k[s:e].transpose(0, 1).repeat_interleave(rep, 0)[None]
+        vs = v[s:e].transpose(0, 1).repeat_interleave(rep, 0)[None]
+        o = TF.scaled_dot_product_attention(qs.float(), ks.float(), vs.float(), is_causal=True)
+        outs.append(o[0].transpose(0, 1).to(q.dtype))
+    return torch.cat(outs, 0)
+
+
+def dense_layer(cfg: DecoderConfig, P: dict, x, meta: BatchMeta):
+    T = x.shape[0]
+    dh, Hq, Hkv = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
+    h = _rms(x, P["attn_norm"], cfg.norm_epsilon, cfg.zero_centered_norm)
+    qkv = h @ P["wqkv"].t()
+    q = qkv[:, :Hq * dh].reshape(T, Hq, dh)
+    k = qkv[:, Hq * dh:(Hq + Hkv) * dh].reshape(T, Hkv, dh)
+    v = qkv[:, (Hq + Hkv) * dh:].reshape(T, Hkv, dh)
+    if cfg.qk_norm:
+        q = _rms(q, P["q_norm"], cfg.norm_epsilon, cfg.zero_centered_norm)
+        k = _rms(k, P["k_norm"], cfg.norm_epsilon, cfg.zero_centered_norm)
+    q = _rope(q, meta.positions, cfg.rotary_width, cfg.rope_base)
+    k = _rope(k, meta.positions, cfg.rotary_width, cfg.rope_base)
+    a = _attention(q, k, v, meta.cu_seqlens).reshape(T, Hq * dh)
+    x = x + a @ P["wo"].t()
+    h = _rms(x, P["mlp_norm"], cfg.norm_epsilon, cfg.zero_centered_norm)
+    gu = h @ P["w13"].t()
+    F_ = cfg.d_ff
+    hm = TF.silu(gu[:, :F_].float()).to(x.dtype) * gu[:, F_:]
+    return x + hm @ P["w2"].t()
+
+
+def loss(cfg: DecoderConfig, params: dict[str, torch.Tensor], meta: BatchMeta) -> torch.Tensor:
+    """Weighted-sum next-token loss of the dense decoder; ``params`` maps
+    ``"<stage>.<param>"`` to tensors (possibly requiring grad)."""
+    def stage(name):
+        pre = name + "."
+        return {k[len(pre):]: v for k, v in params.items() if k.startswith(pre)}
+    x = stage("embed")["embed"][meta.tokens]
+    for i in range(cfg.n_layers):
+        x = dense_layer(cfg, stage(f"layer{i}"), x, meta)
+    hp = stage("head")
+    h = _rms(x, hp["final_norm"], cfg.norm_epsilon, cfg.zero_centered_norm)
+    logits = (h @ hp["head"].t()).float()
+    lse = torch.logsumexp(logits, -1)
+    tgt = meta.targets.clamp(min=0)
+    picked = logits.gather(1, tgt[:, None])[:, 0]
+    w = torch.where(meta.targets >= 0, meta.weights.float(), torch.zeros_like(lse))
+    return (w * (lse - picked)).sum()

@@ -1,0 +1,361 @@
+// Persistent bf16 GEMM for sm_100a: TMA -> 128B-swizzled shared memory ->
+// tcgen05.mma (accumulators in TMEM) -> tcgen05.ld epilogue.
+//
+//   C[M,N] (=|+=) op(A) * op(B)      fp32 accumulation, C in bf16 or fp32
+//
+// Operand storage (row-major, element pitch lda/ldb):
+//   a_mn = 0 : A stored [M,K]  (contraction contiguous, "K-major")
+//   a_mn = 1 : A stored [K,M]  (M contiguous, "MN-major")      -> C = A^T * ...
+//   b_mn = 0 : B stored [N,K]  (K-major)                       -> C = A * B^T
+//   b_mn = 1 : B stored [K,N]  (MN-major)                      -> C = A * B
+// which covers forward (0,0), data-gradient (0,1) and weight-gradient (1,1)
+// without materialising a transpose. `accumulate` folds the existing C into the
+// result in the epilogue; this is the in-place weight-gradient accumulation the
+// reference expresses as shadowspill::accumulate_matmul_
+// (packages/engine/src/shadowspill/pytorch/operations.py:15).
+//
+// One CTA per SM, 192 threads:
+//   warp 0      TMA producer (one elected lane)
+//   warp 1      TMEM allocator + MMA issuer (one elected lane)
+//   warps 2..5  epilogue; warp w owns TMEM lanes 32*(w%4)..+31
+// Two 128x256 fp32 accumulators (2 x 256 TMEM columns) let the epilogue of tile
+// i overlap the main loop of tile i+1.
+#include "sm100_ptx.cuh"
+
+#include <cudaTypedefs.h>
+#include <stdio.h>
+
+namespace ss {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int TMEM_COLS = 2 * BN;  // 512 or 256
+};
+
+struct GemmParams {
+  void* C;
+  int M, N, K;
+  long long ldc;
+  int c_f32;
+  int accumulate;
+  int a_mn, b_mn;
+  int* status;
+  float alpha;
+};
+
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& mb, int& nb) {
+  constexpr int GROUP_M = 16;
+  const int per_group = GROUP_M * num_n;
+  const int g = t / per_group;
+  const int first_m = g * GROUP_M;
+  const int gm = min(GROUP_M, num_m - first_m);
+  const int r = t - g * per_group;
+  mb = first_m + (r % gm);
+  nb = r / gm;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: the 128B swizzle pattern repeats every 8 rows = 1024 B.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + Cfg::STAGES;
+  uint64_t* tfull = bars + 2 * Cfg::STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_m = (p.M + BM - 1) / BM;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 4);  // one arrival per epilogue warp
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int mb, nb;
+        tile_coords(t, num_m, num_n, mb, nb);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, p.status, KS_TIMEOUT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
+          uint8_t* sb = sa + Cfg::A_BYTES;
+          mbar_expect_tx(&full[stage], Cfg::STAGE_BYTES);
+          if (!A_MN) {
+            tma_load_2d(sa, &tmA, &full[stage], kb * BK, mb * BM);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_2d(sa + j * (BK * 128), &tmA, &full[stage], mb * BM + j * 64, kb * BK);
+          }
+          if (!B_MN) {
+            tma_load_2d(sb, &tmB, &full[stage], kb * BK, nb * BN);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * (BK * 128), &tmB, &full[stage], nb * BN + j * 64, kb * BK);
+          }
+          if (++stage == Cfg::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1, p.status, KS_TIMEOUT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, p.status, KS_TIMEOUT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+          const uint32_t sb = sa + Cfg::A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t adesc = A_MN ? umma_smem_desc(sa + kk * (UMMA_K * 128), BK * 128, 1024)
+                                        : umma_smem_desc(sa + kk * (UMMA_K * 2), 16, 1024);
+            const uint64_t bdesc = B_MN ? umma_smem_desc(sb + kk * (UMMA_K * 128), BK * 128, 1024)
+                                        : umma_smem_desc(sb + kk * (UMMA_K * 2), 16, 1024);
+            umma_bf16(d_tmem, adesc, bdesc, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);  // stage reusable once these MMAs retire
+          if (++stage == Cfg::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&tfull[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may touch
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      int mb, nb;
+      tile_coords(t, num_m, num_n, mb, nb);
+      if (!mbar_wait(&tfull[acc], acc_phase, p.status, KS_TIMEOUT_TMEM_FULL)) break;
+      tc_fence_after();
+      const int row = mb * BM + q * 32 + lane;
+      const uint32_t taddr =
+          tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = nb * BN + c * 32;
+        if (row < p.M && col0 < p.N) {
+          const int ncols = min(32, p.N - col0);
+          if (p.c_f32) {
+            float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+            for (int j = 0; j < ncols; j += 4) {
+              float4 v = make_float4(__uint_as_float(r[j]) * p.alpha,
+                                     __uint_as_float(r[j + 1]) * p.alpha,
+                                     __uint_as_float(r[j + 2]) * p.alpha,
+                                     __uint_as_float(r[j + 3]) * p.alpha);
+              if (p.accumulate) {
+                const float4 o = *reinterpret_cast<const float4*>(dst + j);
+                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+              }
+              *reinterpret_cast<float4*>(dst + j) = v;
+            }
+          } else {
+            __nv_bfloat16* dst =
+                reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+            for (int j = 0; j < ncols; j += 8) {
+              float f[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[j + e]) * p.alpha;
+              if (p.accumulate) {
+                const uint4 o = *reinterpret_cast<const uint4*>(dst + j);
+                const float2 o0 = unpack_bf16(o.x), o1 = unpack_bf16(o.y), o2 = unpack_bf16(o.z),
+                             o3 = unpack_bf16(o.w);
+                f[0] += o0.x; f[1] += o0.y; f[2] += o1.x; f[3] += o1.y;
+                f[4] += o2.x; f[5] += o2.y; f[6] += o3.x; f[7] += o3.y;
+              }
+              uint4 v;
+              v.x = pack_bf16(f[0], f[1]);
+              v.y = pack_bf16(f[2], f[3]);
+              v.z = pack_bf16(f[4], f[5]);
+              v.w = pack_bf16(f[6], f[7]);
+              *reinterpret_cast<uint4*>(dst + j) = v;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  }
+  return fn;
+}
+
+// 2-D bf16 row-major [rows, cols] with element pitch ld; box = [box_rows, 64 cols], 128B swizzle.
+int make_tmap_bf16(CUtensorMap* map, const void* base, long long rows, long long cols,
+                   long long ld, int box_rows) {
+  auto fn = encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int num_sms,
+                  cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  static bool configured = false;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int grid = tiles < num_sms ? tiles : num_sms;
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM, stream>>>(ta, tb, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace ss
+
+extern "C" {
+
+// Returns 0 on success, a CUDA/driver error code otherwise, -2 for bad arguments.
+// `status` is an int32 in device (or mapped pinned) memory that receives a
+// ss::KernelStatus if a bounded wait inside the kernel gave up; it may be null.
+int ss_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                 long long ldb, long long ldc, int a_mn, int b_mn, int c_f32, int accumulate,
+                 float alpha, int bn, int num_sms, int* status, void* stream) {
+  using namespace ss;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (ldc % (c_f32 ? 4 : 8)) || (N % 8) ||
+      (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
+      (reinterpret_cast<uintptr_t>(C) & 15))
+    return -2;
+  if (bn != 128 && bn != 256) bn = (N <= 128) ? 128 : 256;
+  if (num_sms <= 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  CUtensorMap ta, tb;
+  int r;
+  if (!a_mn) r = make_tmap_bf16(&ta, A, M, K, lda, BM);
+  else       r = make_tmap_bf16(&ta, A, K, M, lda, BK);
+  if (r) return r;
+  if (!b_mn) r = make_tmap_bf16(&tb, B, N, K, ldb, bn);
+  else       r = make_tmap_bf16(&tb, B, K, N, ldb, BK);
+  if (r) return r;
+  GemmParams p;
+  p.C = C; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.c_f32 = c_f32; p.accumulate = accumulate;
+  p.a_mn = a_mn; p.b_mn = b_mn; p.status = status; p.alpha = alpha;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+#define SS_DISPATCH(BN_)                                                              \
+  do {                                                                                \
+    if (!a_mn && !b_mn) return launch<BN_, false, false>(ta, tb, p, num_sms, s);      \
+    if (!a_mn && b_mn) return launch<BN_, false, true>(ta, tb, p, num_sms, s);        \
+    if (a_mn && b_mn) return launch<BN_, true, true>(ta, tb, p, num_sms, s);          \
+    return launch<BN_, true, false>(ta, tb, p, num_sms, s);                           \
+  } while (0)
+  if (bn == 256) SS_DISPATCH(256);
+  SS_DISPATCH(128);
+#undef SS_DISPATCH
+}
+
+}  // extern "C"

@@ -1,0 +1,250 @@
+"""Tensor-level entry points of the op library.
+
+CUDA tensors go to the hand-written sm_100a kernels in ``libss_kernels.so``;
+CPU tensors go to the plain-PyTorch definitions in :mod:`.reference`, which are
+also the numerical oracles of the kernel tests. There is no third path: a CUDA
+tensor with the library missing raises.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib, reference
+
+_BF16 = torch.bfloat16
+
+
+def _cuda(t: torch.Tensor) -> bool:
+    return t.is_cuda
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+# ------------------------------------------------------------------------ GEMM
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         out: torch.Tensor | None = None, accumulate: bool = False, alpha: float = 1.0,
+         out_dtype: torch.dtype | None = None, bn: int = 0) -> torch.Tensor:
+    """``C[M,N] (+)= alpha * op(A) @ op(B)`` with bf16 operands, fp32 accumulation.
+
+    ``a_mn``: A is stored ``[K, M]`` (else ``[M, K]``); ``b_mn``: B is stored
+    ``[K, N]`` (else ``[N, K]``). ``accumulate`` adds the existing ``out``.
+    """
+    M = a.shape[1] if a_mn else a.shape[0]
+    K = a.shape[0] if a_mn else a.shape[1]
+    N = b.shape[1] if b_mn else b.shape[0]
+    Kb = b.shape[0] if b_mn else b.shape[1]
+    if K != Kb:
+        raise ValueError(f"contraction mismatch: {tuple(a.shape)} vs {tuple(b.shape)}")
+    if out is None:
+        if accumulate:
+            raise ValueError("accumulate needs an existing output")
+        out_dtype = out_dtype or a.dtype
+    elif out.shape != (M, N):
+        raise ValueError(f"output shape {tuple(out.shape)} != {(M, N)}")
+    if not _cuda(a):
+        return reference.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out, accumulate=accumulate,
+                              alpha=alpha, out_dtype=out_dtype or a.dtype)
+    if a.dtype != _BF16 or b.dtype != _BF16:
+        raise TypeError("gemm operands must be bfloat16 on CUDA")
+    if a.stride(-1) != 1 or b.stride(-1) != 1:
+        raise ValueError("gemm operands must have unit inner stride")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    if out.stride(-1) != 1 or out.dtype not in (_BF16, torch.float32):
+        raise ValueError("gemm output must be bf16/fp32 with unit inner stride")
+    rc = _lib.lib().ss_gemm_bf16(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
+        out.stride(0), int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate),
+        float(alpha), int(bn), 0, _lib.status_word(a.device).data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "ss_gemm_bf16")
+    return out
+
+
+def linear_fwd(x, w, out=None, accumulate=False):
+    """``y[T,N] (+)= x[T,K] @ w[N,K]^T``"""
+    return gemm(x, w, out=out, accumulate=accumulate)
+
+
+def linear_dgrad(dy, w, out=None, accumulate=False):
+    """``dx[T,K] (+)= dy[T,N] @ w[N,K]``"""
+    return gemm(dy, w, b_mn=True, out=out, accumulate=accumulate)
+
+
+def linear_wgrad(dy, x, out=None, accumulate=False, out_dtype=None):
+    """``dw[N,K] (+)= dy[T,N]^T @ x[T,K]`` -- the in-place gradient accumulation
+    (reference: shadowspill::accumulate_matmul_)."""
+    return gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=accumulate, out_dtype=out_dtype)
+
+
+# ------------------------------------------------------------------------ norms
+def rmsnorm_fwd(x, w, eps=1e-5, zero_centered=False, delta=None, out=None, rstd=None):
+    """``x += delta`` (optional, in place) then RMSNorm. Returns ``(y, rstd)``."""
+    if not _cuda(x):
+        return reference.rmsnorm_fwd(x, w, eps, zero_centered, delta)
+    T, D = x.shape
+    y = torch.empty_like(x) if out is None else out
+    rs = torch.empty(T, dtype=torch.float32, device=x.device) if rstd is None else rstd
+    rc = _lib.lib().ss_rmsnorm_fwd(x.data_ptr(), _ptr(delta), w.data_ptr(), y.data_ptr(),
+                                   rs.data_ptr(), T, D, float(eps), int(zero_centered),
+                                   _lib.stream_ptr())
+    _lib.check(rc, "ss_rmsnorm_fwd")
+    return y, rs
+
+
+def rmsnorm_bwd(x, w, gy, rstd, dw, zero_centered=False, dx=None, accumulate=False):
+    """Returns ``dx`` (added into ``dx`` when ``accumulate``); ``dw`` (fp32) is
+    accumulated in place."""
+    if not _cuda(x):
+        dxr, dwr = reference.rmsnorm_bwd(x, w, gy, rstd, zero_centered)
+        if dw is not None:
+            dw.add_(dwr.to(dw.dtype))
+        if dx is None:
+            return dxr.to(x.dtype)
+        dx.copy_(((dx.float() if accumulate else 0) + dxr).to(dx.dtype))
+        return dx
+    T, D = x.shape
+    if dx is None:
+        if accumulate:
+            raise ValueError("accumulate needs dx")
+        dx = torch.empty_like(x)
+    if dw is not None and dw.dtype != torch.float32:
+        raise TypeError("rmsnorm dw accumulator must be fp32")
+    rc = _lib.lib().ss_rmsnorm_bwd(x.data_ptr(), w.data_ptr(), gy.data_ptr(), rstd.data_ptr(),
+                                   dx.data_ptr(), _ptr(dw), T, D, int(zero_centered),
+                                   int(accumulate), _lib.stream_ptr())
+    _lib.check(rc, "ss_rmsnorm_bwd")
+    return dx
+
+
+# ------------------------------------------------------------------------ rotary
+def rope_(buf, positions, *, col0, heads, dh, rot=None, theta=10000.0, inverse=False):
+    """In-place rotary on ``heads`` heads of width ``dh`` starting at column ``col0``
+    of the 2-D buffer ``buf``; ``inverse`` applies the backward rotation."""
+    rot = dh if rot is None else rot
+    if not _cuda(buf):
+        return reference.rope_(buf, positions, col0, heads, dh, rot, theta, inverse)
+    if positions.dtype != torch.int32:
+        raise TypeError("positions must be int32")
+    rc = _lib.lib().ss_rope(buf.data_ptr(), positions.data_ptr(), buf.shape[0], buf.stride(0),
+                            col0, heads, dh, rot, float(theta), int(inverse), _lib.stream_ptr())
+    _lib.check(rc, "ss_rope")
+    return buf
+
+
+# ------------------------------------------------------------------------ SwiGLU
+def swiglu_fwd(gu, out=None):
+    if not _cuda(gu):
+        return reference.swiglu_fwd(gu)
+    T, F2 = gu.shape
+    h = torch.empty((T, F2 // 2), dtype=gu.dtype, device=gu.device) if out is None else out
+    _lib.check(_lib.lib().ss_swiglu_fwd(gu.data_ptr(), h.data_ptr(), T, F2 // 2,
+                                        _lib.stream_ptr()), "ss_swiglu_fwd")
+    return h
+
+
+def swiglu_bwd(gu, dh, out=None):
+    if not _cuda(gu):
+        return reference.swiglu_bwd(gu, dh)
+    T, F2 = gu.shape
+    dgu = torch.empty_like(gu) if out is None else out
+    _lib.check(_lib.lib().ss_swiglu_bwd(gu.data_ptr(), dh.data_ptr(), dgu.data_ptr(), T, F2 // 2,
+                                        _lib.stream_ptr()), "ss_swiglu_bwd")
+    return dgu
+
+
+# ------------------------------------------------------------------------ embedding
+def embedding_fwd(ids, W, out=None):
+    if not _cuda(W):
+        return reference.embedding_fwd(ids, W)
+    T = ids.numel()
+    V, D = W.shape
+    o = torch.empty((T, D), dtype=W.dtype, device=W.device) if out is None else out
+    _lib.check(_lib.lib().ss_embedding_fwd(ids.data_ptr(), W.data_ptr(), o.data_ptr(), T, D, V,
+                                           _lib.stream_ptr()), "ss_embedding_fwd")
+    return o
+
+
+def embedding_bwd(ids, g, dW):
+    """``dW[ids[t]] += g[t]`` (dW fp32 or bf16)."""
+    if not _cuda(g):
+        return reference.embedding_bwd(ids, g, dW)
+    T = ids.numel()
+    V, D = dW.shape
+    _lib.check(_lib.lib().ss_embedding_bwd(ids.data_ptr(), g.data_ptr(), dW.data_ptr(), T, D, V,
+                                           int(dW.dtype == torch.float32), _lib.stream_ptr()),
+               "ss_embedding_bwd")
+    return dW
+
+
+# ------------------------------------------------------------------------ cross-entropy block
+def cross_entropy_(logits, targets, weights, loss_sum, *, grad_scale=1.0, write_grad=True,
+                   lse=None):
+    """Adds the weighted loss of a logits block into ``loss_sum`` (fp32[1]) and
+    rewrites ``logits`` with its gradient. Masked rows carry weight 0."""
+    if not _cuda(logits):
+        loss, _ = reference.cross_entropy_(logits, targets, weights, grad_scale, write_grad)
+        loss_sum.add_(loss)
+        return loss_sum
+    R, V = logits.shape
+    _lib.check(_lib.lib().ss_cross_entropy(logits.data_ptr(), targets.data_ptr(), _ptr(weights),
+                                           loss_sum.data_ptr(), _ptr(lse), R, V, logits.stride(0),
+                                           float(grad_scale), int(write_grad), _lib.stream_ptr()),
+               "ss_cross_entropy")
+    return loss_sum
+
+
+# ------------------------------------------------------------------------ AdamW
+def adamw_(p, g, m, v, *, lr, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0, step=1,
+           grad_scale=1.0, seed=0, offset=0, stochastic_param=True, stochastic_state=True):
+    """Fused AdamW on flat tensors. bf16 parameters/moments use stochastic
+    rounding driven by a counter RNG keyed on (seed, step, global element index),
+    so a shard updated alone produces the same bits as the whole tensor."""
+    if not _cuda(p):
+        return reference.adamw_(p, g, m, v, lr=lr, beta1=beta1, beta2=beta2, eps=eps,
+                                weight_decay=weight_decay, step=step, grad_scale=grad_scale)
+    n = p.numel()
+    L = _lib.lib()
+    if p.dtype == torch.float32:
+        _lib.check(L.ss_adamw_f32(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), n,
+                                  lr, beta1, beta2, eps, weight_decay, step, grad_scale,
+                                  _lib.stream_ptr()), "ss_adamw_f32")
+        return
+    _lib.check(L.ss_adamw_sr(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), n,
+                             int(g.dtype == torch.float32), lr, beta1, beta2, eps, weight_decay,
+                             step, grad_scale, seed, offset, int(stochastic_param),
+                             int(stochastic_state), _lib.stream_ptr()), "ss_adamw_sr")
+
+
+def sumsq(x, partials, out, accumulate=False):
+    """Sum of squares into ``out`` (fp32[1]) using caller-owned ``partials`` (fp32[256])."""
+    if not _cuda(x):
+        val = x.float().square().sum()
+        out.copy_(out + val if accumulate else val.reshape(1))
+        return out
+    _lib.check(_lib.lib().ss_sumsq(x.data_ptr(), x.numel(), partials.data_ptr(), out.data_ptr(),
+                                   int(accumulate), _lib.stream_ptr()), "ss_sumsq")
+    return out
+
+
+# ------------------------------------------------------------------------ attention
+def attention_varlen(q, k, v, cu_seqlens, max_seqlen, scale=None):
+    """Packed causal GQA forward. Returns ``(out, lse)``; ``lse`` is fp32 ``[Hq, T]``."""
+    if not _cuda(q):
+        return reference.attention_varlen(q, k, v, cu_seqlens, scale)
+    from . import attention
+    return attention.forward(q, k, v, cu_seqlens, max_seqlen, scale)
+
+
+def attention_varlen_bwd(q, k, v, out, lse, dout, cu_seqlens, max_seqlen, scale=None):
+    if not _cuda(q):
+        return reference.attention_varlen_bwd(q, k, v, out, lse, dout, cu_seqlens, scale)
+    from . import attention
+    return attention.backward(q, k, v, out, lse, dout, cu_seqlens, max_seqlen, scale)
+
+
+def default_scale(dh: int) -> float:
+    return 1.0 / math.sqrt(dh)
