@@ -58,6 +58,8 @@ def lib() -> ctypes.CDLL:
                     f"{_LIB_PATH} is not built; run `python -m shadowspill_b200.build`")
             handle = ctypes.CDLL(str(_LIB_PATH))
             for name, argtypes in _SIGNATURES.items():
+                if not hasattr(handle, name):
+                    continue   # optional kernels are probed by their users
                 fn = getattr(handle, name)
                 fn.argtypes = argtypes
                 fn.restype = c_int
@@ -68,7 +70,7 @@ def lib() -> ctypes.CDLL:
 def register(name: str, argtypes: list) -> None:
     """Declare the signature of another exported launcher (used by sibling modules)."""
     _SIGNATURES[name] = argtypes
-    if _lib is not None:
+    if _lib is not None and hasattr(_lib, name):
         fn = getattr(_lib, name)
         fn.argtypes = argtypes
         fn.restype = c_int

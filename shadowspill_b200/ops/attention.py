@@ -30,20 +30,20 @@ _lib.register("ss_attn_bwd", [_c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_p, _c
                               _c.c_p])
 
 
-def _native_available() -> bool:
+def _native_available(symbol: str) -> bool:
     try:
         handle = _lib.lib()
     except _lib.KernelLibraryMissing:
         return False
-    return hasattr(handle, "ss_attn_fwd") and hasattr(handle, "ss_attn_bwd")
+    return hasattr(handle, symbol)
 
 
-def implementation() -> str:
+def implementation(symbol: str = "ss_attn_fwd") -> str:
     want = os.environ.get("SS_ATTENTION", "native")
     if want == "native":
-        if not _native_available():
-            raise RuntimeError("native attention kernels are not in libss_kernels.so; rebuild, "
-                               "or set SS_ATTENTION=library for the baseline arm")
+        if not _native_available(symbol):
+            raise RuntimeError(f"{symbol} is not in libss_kernels.so; rebuild, or set "
+                               "SS_ATTENTION=library for the baseline arm")
         return "native"
     return "library"
 
@@ -87,7 +87,7 @@ def backward(q, k, v, out, lse, dout, cu_seqlens, max_seqlen, scale=None, dq=Non
     dq = torch.empty_like(q) if dq is None else dq
     dk = torch.empty_like(k) if dk is None else dk
     dv = torch.empty_like(v) if dv is None else dv
-    if implementation() == "library":
+    if implementation("ss_attn_bwd") == "library":
         from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
         dqc = dq if dq.is_contiguous() else torch.empty_like(q)
         dkc = dk if dk.is_contiguous() else torch.empty_like(k)
@@ -100,9 +100,13 @@ def backward(q, k, v, out, lse, dout, cu_seqlens, max_seqlen, scale=None, dq=Non
                 dst.copy_(src)
         return dq, dk, dv
     nseq = cu_seqlens.numel() - 1
+    if not out.is_contiguous():
+        raise ValueError("attention output must be contiguous [T, Hq, dh]")
+    delta = torch.empty((Hq, T), dtype=torch.float32, device=q.device)   # kernel scratch
     rc = _lib.lib().ss_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                                 lse.data_ptr(), dout.data_ptr(), dq.data_ptr(), dk.data_ptr(),
-                                dv.data_ptr(), cu_seqlens.data_ptr(), None, nseq, T, Hq, Hkv, dh,
+                                dv.data_ptr(), cu_seqlens.data_ptr(), delta.data_ptr(), nseq, T,
+                                Hq, Hkv, dh,
                                 _row_stride(q), _row_stride(k), _row_stride(v), _row_stride(dout),
                                 float(scale), _lib.status_word(q.device).data_ptr(),
                                 _lib.stream_ptr())
