@@ -1,0 +1,667 @@
+// Execution runtime: device and spill pools, admitted plans with fixed-offset
+// device stays, a fetch lane and an evict lane (one backend stream each), and a
+// worker thread that turns the action batches published at task boundaries into
+// stream work while honouring the layout's reuse dependencies.
+//
+// Division of labour (mirrors the reference's dispatcher / worker split,
+// packages/engine/csrc/src/runtime/tasks/task_boundaries.c:778 and
+// runtime/worker/worker.c:151):
+//   dispatcher thread  ss_before_task: make the compute stream wait for the
+//                      task's inputs and for the previous occupants of every
+//                      range the task creates. ss_after_task: record the task
+//                      fence and publish the actions the task triggers.
+//   worker thread      issues published actions lane by lane in plan order. A
+//                      fetch is held back (on the host) until the release of
+//                      every predecessor of its destination range has been
+//                      recorded, because a stream cannot wait for an event that
+//                      has not been recorded yet.
+// Every host-side wait is bounded; on expiry the first-writer-wins failure
+// latch is set and all entry points return SS_FAILED from then on.
+#include "common.hpp"
+
+#include <atomic>
+#include <chrono>
+#include <condition_variable>
+#include <cstdio>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <thread>
+
+namespace {
+
+constexpr int64_t HOST_WAIT_NS = 60ll * 1000000000ll;
+
+struct IntervalState {
+  ss_interval iv;
+  void* ready_event = nullptr;     // fetch completion (fetched stays)
+  void* release_event = nullptr;   // what a successor must wait for
+  std::atomic<int> ready_issued{0};
+  std::atomic<int> released{0};
+  bool release_on_compute = false; // release event is a compute-stream fence
+};
+
+struct PlanState {
+  int32_t id = 0;
+  int32_t n_tasks = 0, n_objects = 0;
+  std::vector<int64_t> object_bytes, spill_offset;
+  std::vector<ss_action> actions;
+  std::vector<std::unique_ptr<IntervalState>> intervals;
+  std::vector<int32_t> pred_begin, pred_index;
+  std::vector<ssc::Use> uses;
+  std::vector<int32_t> task_use_begin;
+  std::vector<int32_t> action_interval;        // fetch -> stay it opens; evict/release -> stay it ends
+  std::vector<std::vector<int32_t>> task_creates;   // stays opened by each task
+  std::vector<void*> task_fence;               // one event per task
+  std::vector<void*> action_event;             // one event per transfer action
+  std::vector<int32_t> action_prev_evict;      // fetch -> earlier evict of the same object, or -1
+  std::vector<std::atomic<int>> action_issued;
+  // per step
+  std::vector<int32_t> object_current;         // open stay per object, -1 if none
+  std::vector<int32_t> fetch_order, evict_order, release_order;   // action indices by lane
+  size_t next_fetch = 0, next_evict = 0, next_release = 0;
+  std::atomic<int32_t> published_task{-2};     // highest task whose actions are published
+  void* compute_stream = nullptr;
+  bool active = false;
+  void* step_event = nullptr;
+};
+
+}  // namespace
+
+struct ss_runtime {
+  ss_backend* be = nullptr;
+  ss_runtime_config cfg{};
+  void* device_base = nullptr;
+  void* spill_base = nullptr;
+  void* fetch_stream = nullptr;
+  void* evict_stream = nullptr;
+  std::mutex mu;                      // guards plans map and worker handoff
+  std::condition_variable cv;
+  std::map<int32_t, std::unique_ptr<PlanState>> plans;
+  int32_t next_plan = 1;
+  std::thread worker;
+  std::atomic<bool> stop{false};
+  std::atomic<bool> closed{false};
+  // failure latch
+  std::atomic<int> failed{0};
+  std::mutex fail_mu;
+  ss_failure failure{};
+  // trace
+  std::mutex trace_mu;
+  std::vector<ss_trace_event> ring;
+  size_t ring_head = 0, ring_count = 0;
+  std::atomic<bool> tracing{false};
+  // stats
+  std::atomic<int64_t> st_steps{0}, st_tasks{0}, st_fetches{0}, st_fetch_bytes{0}, st_evicts{0},
+      st_evict_bytes{0}, st_releases{0}, st_reuse_waits{0}, st_events{0}, st_host_allocs{0},
+      st_wakeups{0};
+
+  void trace(int kind, int a, int64_t bytes) {
+    if (!tracing.load(std::memory_order_relaxed) || ring.empty()) return;
+    std::lock_guard<std::mutex> lk(trace_mu);
+    ss_trace_event& e = ring[(ring_head + ring_count) % ring.size()];
+    e.kind = kind; e.a = a; e.host_ns = ss_monotonic_ns(); e.bytes = bytes;
+    if (ring_count < ring.size()) ++ring_count; else ring_head = (ring_head + 1) % ring.size();
+  }
+  int latch(int reason, int status, int task, int object, int action, int pool, const char* msg) {
+    int expected = 0;
+    if (failed.compare_exchange_strong(expected, 1)) {
+      std::lock_guard<std::mutex> lk(fail_mu);
+      failure.status = status; failure.reason = reason; failure.task = task;
+      failure.object = object; failure.action = action; failure.pool = pool;
+      std::snprintf(failure.message, sizeof failure.message, "%s", msg ? msg : "");
+      trace(SS_TRACE_FAILURE, action, 0);
+    }
+    cv.notify_all();
+    return SS_FAILED;
+  }
+  char* dev(int64_t off) { return static_cast<char*>(device_base) + off; }
+  char* spill(int64_t off) { return static_cast<char*>(spill_base) + off; }
+};
+
+namespace {
+
+int new_event(ss_runtime* rt, void** out) {
+  int rc = rt->be->event_create(rt->be->self, 0, out);
+  if (rc == SS_OK) rt->st_events++;
+  return rc;
+}
+
+// Issues every published action it can, lane by lane. Returns true if anything moved.
+bool pump_plan(ss_runtime* rt, PlanState& P) {
+  bool moved = false;
+  const int32_t pub = P.published_task.load(std::memory_order_acquire);
+  ss_backend* be = rt->be;
+  // ---- releases: the stay ends at the trigger task's fence
+  while (P.next_release < P.release_order.size()) {
+    const int32_t a = P.release_order[P.next_release];
+    const ss_action& A = P.actions[a];
+    if (A.trigger_task > pub) break;
+    IntervalState& I = *P.intervals[P.action_interval[a]];
+    I.release_event = A.trigger_task >= 0 ? P.task_fence[A.trigger_task] : nullptr;
+    I.release_on_compute = true;
+    I.released.store(1, std::memory_order_release);
+    P.action_issued[a].store(1, std::memory_order_release);
+    rt->st_releases++;
+    rt->trace(SS_TRACE_RELEASE, a, I.iv.bytes);
+    ++P.next_release; moved = true;
+  }
+  // ---- evicts
+  while (P.next_evict < P.evict_order.size()) {
+    const int32_t a = P.evict_order[P.next_evict];
+    const ss_action& A = P.actions[a];
+    if (A.trigger_task > pub) break;
+    IntervalState& I = *P.intervals[P.action_interval[a]];
+    int rc = SS_OK;
+    if (A.trigger_task >= 0) rc = be->stream_wait_event(be->self, rt->evict_stream, P.task_fence[A.trigger_task]);
+    if (rc == SS_OK && I.ready_event && I.iv.begin_action >= 0)
+      rc = be->stream_wait_event(be->self, rt->evict_stream, I.ready_event);
+    if (rc == SS_OK)
+      rc = be->copy_async(be->self, rt->spill(P.spill_offset[A.object]), rt->dev(I.iv.offset),
+                          static_cast<size_t>(P.object_bytes[A.object]), SS_COPY_D2H, rt->evict_stream);
+    if (rc == SS_OK) rc = be->event_record(be->self, P.action_event[a], rt->evict_stream);
+    if (rc != SS_OK) {
+      rt->latch(SS_FAIL_BACKEND_COPY, rc, A.trigger_task, A.object, a, 1, "evict failed to enqueue");
+      return false;
+    }
+    I.release_event = P.action_event[a];
+    I.release_on_compute = false;
+    I.released.store(1, std::memory_order_release);
+    P.action_issued[a].store(1, std::memory_order_release);
+    rt->st_evicts++; rt->st_evict_bytes += P.object_bytes[A.object];
+    rt->trace(SS_TRACE_EVICT_ISSUE, a, P.object_bytes[A.object]);
+    ++P.next_evict; moved = true;
+  }
+  // ---- fetches: FIFO; the head may have to wait for predecessors of its range
+  while (P.next_fetch < P.fetch_order.size()) {
+    const int32_t a = P.fetch_order[P.next_fetch];
+    const ss_action& A = P.actions[a];
+    if (A.trigger_task > pub) break;
+    const int32_t ii = P.action_interval[a];
+    IntervalState& I = *P.intervals[ii];
+    bool blocked = false;
+    for (int32_t k = P.pred_begin[ii]; k < P.pred_begin[ii + 1]; ++k)
+      if (!P.intervals[P.pred_index[k]]->released.load(std::memory_order_acquire)) { blocked = true; break; }
+    const int32_t pe = P.action_prev_evict[a];
+    if (!blocked && pe >= 0 && !P.action_issued[pe].load(std::memory_order_acquire)) blocked = true;
+    if (blocked) { rt->st_reuse_waits++; break; }
+    int rc = SS_OK;
+    if (A.trigger_task >= 0) rc = be->stream_wait_event(be->self, rt->fetch_stream, P.task_fence[A.trigger_task]);
+    for (int32_t k = P.pred_begin[ii]; rc == SS_OK && k < P.pred_begin[ii + 1]; ++k) {
+      IntervalState& J = *P.intervals[P.pred_index[k]];
+      if (J.release_event) rc = be->stream_wait_event(be->self, rt->fetch_stream, J.release_event);
+    }
+    if (rc == SS_OK && pe >= 0) rc = be->stream_wait_event(be->self, rt->fetch_stream, P.action_event[pe]);
+    if (rc == SS_OK)
+      rc = be->copy_async(be->self, rt->dev(I.iv.offset), rt->spill(P.spill_offset[A.object]),
+                          static_cast<size_t>(P.object_bytes[A.object]), SS_COPY_H2D, rt->fetch_stream);
+    if (rc == SS_OK) rc = be->event_record(be->self, P.action_event[a], rt->fetch_stream);
+    if (rc != SS_OK) {
+      rt->latch(SS_FAIL_BACKEND_COPY, rc, A.trigger_task, A.object, a, 0, "fetch failed to enqueue");
+      return false;
+    }
+    I.ready_event = P.action_event[a];
+    I.ready_issued.store(1, std::memory_order_release);
+    P.action_issued[a].store(1, std::memory_order_release);
+    rt->st_fetches++; rt->st_fetch_bytes += P.object_bytes[A.object];
+    rt->trace(SS_TRACE_FETCH_ISSUE, a, P.object_bytes[A.object]);
+    ++P.next_fetch; moved = true;
+  }
+  return moved;
+}
+
+void worker_main(ss_runtime* rt) {
+#ifdef __linux__
+  pthread_setname_np(pthread_self(), "ss.wkr");
+#endif
+  std::unique_lock<std::mutex> lk(rt->mu);
+  while (!rt->stop.load()) {
+    bool moved = false;
+    if (!rt->failed.load()) {
+      for (auto& kv : rt->plans)
+        if (kv.second->active) moved |= pump_plan(rt, *kv.second);
+    }
+    if (moved) { rt->cv.notify_all(); continue; }
+    rt->st_wakeups++;
+    rt->cv.wait_for(lk, std::chrono::nanoseconds(std::max<int64_t>(rt->cfg.worker_poll_ns, 1000) * 200));
+  }
+}
+
+PlanState* find_plan(ss_runtime* rt, int32_t id) {
+  auto it = rt->plans.find(id);
+  return it == rt->plans.end() ? nullptr : it->second.get();
+}
+
+// Bounded host wait for a flag the worker sets.
+bool wait_flag(ss_runtime* rt, std::atomic<int>& flag) {
+  if (flag.load(std::memory_order_acquire)) return true;
+  const int64_t t0 = ss_monotonic_ns();
+  rt->cv.notify_all();
+  int spins = 0;
+  while (!flag.load(std::memory_order_acquire)) {
+    if (rt->failed.load()) return false;
+    if (++spins < 2000) { std::this_thread::yield(); continue; }
+    std::this_thread::sleep_for(std::chrono::microseconds(20));
+    if (ss_monotonic_ns() - t0 > HOST_WAIT_NS) return false;
+  }
+  return true;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ss_runtime_create(ss_backend* backend, const ss_runtime_config* config, ss_runtime** out) {
+  if (!backend || !config || !out || config->device_bytes < 0 || config->spill_bytes < 0)
+    return SS_INVALID_ARGUMENT;
+  auto* rt = new ss_runtime();
+  rt->be = backend;
+  rt->cfg = *config;
+  if (rt->cfg.worker_poll_ns <= 0) rt->cfg.worker_poll_ns = 1000;
+  int rc = SS_OK;
+  if (config->device_bytes > 0)
+    rc = backend->device_alloc(backend->self, static_cast<size_t>(config->device_bytes), &rt->device_base);
+  if (rc == SS_OK && config->spill_bytes > 0) {
+    rc = backend->host_alloc(backend->self, static_cast<size_t>(config->spill_bytes),
+                             config->numa_node, &rt->spill_base);
+    rt->st_host_allocs++;
+  }
+  if (rc == SS_OK) rc = backend->stream_create(backend->self, &rt->fetch_stream);
+  if (rc == SS_OK) rc = backend->stream_create(backend->self, &rt->evict_stream);
+  if (rc != SS_OK) {
+    if (rt->fetch_stream) backend->stream_destroy(backend->self, rt->fetch_stream);
+    if (rt->device_base) backend->device_free(backend->self, rt->device_base);
+    if (rt->spill_base) backend->host_free(backend->self, rt->spill_base, static_cast<size_t>(config->spill_bytes));
+    delete rt;
+    return rc;
+  }
+  if (config->trace_capacity > 0) rt->ring.resize(static_cast<size_t>(config->trace_capacity));
+  rt->worker = std::thread(worker_main, rt);
+  *out = rt;
+  return SS_OK;
+}
+
+static void release_plan(ss_runtime* rt, PlanState& P) {
+  for (void* e : P.task_fence) if (e) rt->be->event_destroy(rt->be->self, e);
+  for (void* e : P.action_event) if (e) rt->be->event_destroy(rt->be->self, e);
+  if (P.step_event) rt->be->event_destroy(rt->be->self, P.step_event);
+  P.task_fence.clear(); P.action_event.clear(); P.step_event = nullptr;
+}
+
+int ss_runtime_close(ss_runtime* rt) {
+  if (!rt) return SS_INVALID_ARGUMENT;
+  if (rt->closed.exchange(true)) return SS_CLOSED;
+  rt->stop = true;
+  rt->cv.notify_all();
+  if (rt->worker.joinable()) rt->worker.join();
+  ss_backend* be = rt->be;
+  be->stream_synchronize(be->self, rt->fetch_stream);
+  be->stream_synchronize(be->self, rt->evict_stream);
+  for (auto& kv : rt->plans) release_plan(rt, *kv.second);
+  rt->plans.clear();
+  be->stream_destroy(be->self, rt->fetch_stream);
+  be->stream_destroy(be->self, rt->evict_stream);
+  if (rt->device_base) be->device_free(be->self, rt->device_base);
+  if (rt->spill_base) be->host_free(be->self, rt->spill_base, static_cast<size_t>(rt->cfg.spill_bytes));
+  rt->device_base = rt->spill_base = nullptr;
+  return rt->failed.load() ? SS_FAILED : SS_OK;
+}
+
+void ss_runtime_abandon(ss_runtime* rt) {
+  if (!rt || rt->closed.exchange(true)) return;
+  rt->stop = true;
+  rt->cv.notify_all();
+  if (rt->worker.joinable()) rt->worker.detach();
+  size_t open_plans = rt->plans.size();
+  std::fprintf(stderr, "ss runtime abandoned: %zu plan(s) open, no drain\n", open_plans);
+}
+
+void ss_runtime_destroy(ss_runtime* rt) {
+  if (!rt) return;
+  if (!rt->closed.load()) ss_runtime_close(rt);
+  delete rt;
+}
+
+void* ss_runtime_device_base(ss_runtime* rt) { return rt ? rt->device_base : nullptr; }
+void* ss_runtime_spill_base(ss_runtime* rt) { return rt ? rt->spill_base : nullptr; }
+
+int ss_runtime_failure(ss_runtime* rt, ss_failure* out) {
+  if (!rt || !out) return SS_INVALID_ARGUMENT;
+  if (!rt->failed.load()) { std::memset(out, 0, sizeof *out); return SS_TIMEOUT; }
+  std::lock_guard<std::mutex> lk(rt->fail_mu);
+  *out = rt->failure;
+  return SS_OK;
+}
+
+int ss_runtime_latch_failure(ss_runtime* rt, int reason, int status, const char* message) {
+  if (!rt) return SS_INVALID_ARGUMENT;
+  rt->latch(reason, status, -1, -1, -1, -1, message);
+  return SS_OK;
+}
+
+int ss_runtime_stats_read(ss_runtime* rt, ss_runtime_stats* out) {
+  if (!rt || !out) return SS_INVALID_ARGUMENT;
+  out->steps = rt->st_steps; out->tasks = rt->st_tasks; out->fetches = rt->st_fetches;
+  out->fetch_bytes = rt->st_fetch_bytes; out->evicts = rt->st_evicts;
+  out->evict_bytes = rt->st_evict_bytes; out->releases = rt->st_releases;
+  out->reuse_waits = rt->st_reuse_waits; out->events_created = rt->st_events;
+  out->host_allocations = rt->st_host_allocs; out->worker_wakeups = rt->st_wakeups;
+  return SS_OK;
+}
+
+int ss_trace_begin(ss_runtime* rt) {
+  if (!rt) return SS_INVALID_ARGUMENT;
+  if (rt->ring.empty()) return SS_INVALID_ARGUMENT;
+  { std::lock_guard<std::mutex> lk(rt->trace_mu); rt->ring_head = rt->ring_count = 0; }
+  rt->tracing = true;
+  return SS_OK;
+}
+int ss_trace_end(ss_runtime* rt) {
+  if (!rt) return SS_INVALID_ARGUMENT;
+  rt->tracing = false;
+  return SS_OK;
+}
+int32_t ss_trace_read(ss_runtime* rt, ss_trace_event* out, int32_t capacity) {
+  if (!rt || !out) return 0;
+  std::lock_guard<std::mutex> lk(rt->trace_mu);
+  const int32_t n = static_cast<int32_t>(std::min<size_t>(rt->ring_count, static_cast<size_t>(capacity)));
+  for (int32_t i = 0; i < n; ++i) out[i] = rt->ring[(rt->ring_head + i) % rt->ring.size()];
+  return n;
+}
+
+int ss_plan_admit(ss_runtime* rt, const ss_plan_desc* d, int32_t* plan_id) {
+  if (!rt || !d || !plan_id) return SS_INVALID_ARGUMENT;
+  if (rt->closed.load()) return SS_CLOSED;
+  if (rt->failed.load()) return SS_FAILED;
+  auto P = std::make_unique<PlanState>();
+  P->n_tasks = d->n_tasks; P->n_objects = d->n_objects;
+  P->object_bytes.assign(d->object_bytes, d->object_bytes + d->n_objects);
+  P->spill_offset.assign(d->spill_offset, d->spill_offset + d->n_objects);
+  P->actions.assign(d->actions, d->actions + d->n_actions);
+  for (int32_t i = 0; i < d->n_intervals; ++i) {
+    auto s = std::make_unique<IntervalState>();
+    s->iv = d->intervals[i];
+    const ss_interval& iv = s->iv;
+    if (iv.object < 0 || iv.object >= d->n_objects || iv.offset < 0 ||
+        iv.offset + d->object_bytes[iv.object] > rt->cfg.device_bytes) {
+      return rt->latch(SS_FAIL_PLAN, SS_INVALID_ARGUMENT, -1, iv.object, -1, 0,
+                       "stay outside the device pool"), SS_INVALID_ARGUMENT;
+    }
+    P->intervals.push_back(std::move(s));
+  }
+  P->pred_begin.assign(d->reuse_pred_begin, d->reuse_pred_begin + d->n_intervals + 1);
+  P->pred_index.assign(d->reuse_pred_index, d->reuse_pred_index + P->pred_begin[d->n_intervals]);
+  P->uses.resize(d->n_uses);
+  P->task_use_begin.assign(d->n_tasks + 1, 0);
+  for (int32_t i = 0; i < d->n_uses; ++i) {
+    P->uses[i] = ssc::Use{d->use_task[i], d->use_object[i], d->use_mode[i]};
+    if (d->use_task[i] < 0 || d->use_task[i] >= d->n_tasks) return SS_INVALID_ARGUMENT;
+    P->task_use_begin[d->use_task[i] + 1]++;
+  }
+  for (int32_t t = 0; t < d->n_tasks; ++t) P->task_use_begin[t + 1] += P->task_use_begin[t];
+  for (int32_t o = 0; o < d->n_objects; ++o) {
+    if (d->spill_offset[o] >= 0 && d->spill_offset[o] + d->object_bytes[o] > rt->cfg.spill_bytes)
+      return SS_OUT_OF_MEMORY;
+  }
+  // action <-> stay links
+  P->action_interval.assign(d->n_actions, -1);
+  P->task_creates.assign(d->n_tasks, {});
+  for (int32_t i = 0; i < d->n_intervals; ++i) {
+    const ss_interval& iv = P->intervals[i]->iv;
+    if (iv.begin_action >= 0) {
+      if (iv.begin_action >= d->n_actions) return SS_INVALID_ARGUMENT;
+      P->action_interval[iv.begin_action] = i;
+    } else if (iv.begin_task >= 0 && iv.begin_task < d->n_tasks) {
+      P->task_creates[iv.begin_task].push_back(i);
+    } else {
+      return SS_INVALID_ARGUMENT;
+    }
+    if (iv.end_action >= 0) {
+      if (iv.end_action >= d->n_actions) return SS_INVALID_ARGUMENT;
+      P->action_interval[iv.end_action] = i;
+    }
+  }
+  P->action_prev_evict.assign(d->n_actions, -1);
+  {
+    std::vector<int32_t> last_evict(d->n_objects, -1);
+    for (int32_t a = 0; a < d->n_actions; ++a) {
+      const ss_action& A = P->actions[a];
+      if (P->action_interval[a] < 0) return SS_INVALID_ARGUMENT;   // every action touches a stay
+      if (A.kind == SS_ACT_EVICT) {
+        if (P->spill_offset[A.object] < 0) return SS_INVALID_ARGUMENT;
+        last_evict[A.object] = a; P->evict_order.push_back(a);
+      } else if (A.kind == SS_ACT_FETCH) {
+        if (P->spill_offset[A.object] < 0) return SS_INVALID_ARGUMENT;
+        P->action_prev_evict[a] = last_evict[A.object]; P->fetch_order.push_back(a);
+      } else {
+        P->release_order.push_back(a);
+      }
+    }
+  }
+  // events are created once here; steady-state steps create none
+  P->task_fence.assign(d->n_tasks, nullptr);
+  P->action_event.assign(d->n_actions, nullptr);
+  for (int32_t t = 0; t < d->n_tasks; ++t)
+    if (int rc = new_event(rt, &P->task_fence[t])) { release_plan(rt, *P); return rc; }
+  for (int32_t a = 0; a < d->n_actions; ++a)
+    if (P->actions[a].kind != SS_ACT_RELEASE)
+      if (int rc = new_event(rt, &P->action_event[a])) { release_plan(rt, *P); return rc; }
+  if (int rc = new_event(rt, &P->step_event)) { release_plan(rt, *P); return rc; }
+  P->action_issued = std::vector<std::atomic<int>>(d->n_actions);
+  P->object_current.assign(d->n_objects, -1);
+  std::lock_guard<std::mutex> lk(rt->mu);
+  P->id = rt->next_plan++;
+  *plan_id = P->id;
+  rt->plans[P->id] = std::move(P);
+  return SS_OK;
+}
+
+int ss_plan_close(ss_runtime* rt, int32_t plan_id) {
+  if (!rt) return SS_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lk(rt->mu);
+  PlanState* P = find_plan(rt, plan_id);
+  if (!P) return SS_INVALID_ARGUMENT;
+  if (P->active) return SS_INVALID_ARGUMENT;
+  release_plan(rt, *P);
+  rt->plans.erase(plan_id);
+  return SS_OK;
+}
+
+int ss_step_begin(ss_runtime* rt, int32_t plan_id, void* compute_stream) {
+  if (!rt) return SS_INVALID_ARGUMENT;
+  if (rt->closed.load()) return SS_CLOSED;
+  if (rt->failed.load()) return SS_FAILED;
+  {
+    std::lock_guard<std::mutex> lk(rt->mu);
+    PlanState* P = find_plan(rt, plan_id);
+    if (!P || P->active) return SS_INVALID_ARGUMENT;
+    for (auto& I : P->intervals) {
+      I->ready_event = nullptr; I->release_event = nullptr;
+      I->ready_issued = 0; I->released = 0; I->release_on_compute = false;
+    }
+    for (auto& f : P->action_issued) f = 0;
+    std::fill(P->object_current.begin(), P->object_current.end(), -1);
+    P->next_fetch = P->next_evict = P->next_release = 0;
+    P->compute_stream = compute_stream;
+    P->published_task.store(-1, std::memory_order_release);
+    P->active = true;
+  }
+  rt->st_steps++;
+  rt->trace(SS_TRACE_STEP_BEGIN, plan_id, 0);
+  rt->cv.notify_all();
+  return SS_OK;
+}
+
+int ss_before_task(ss_runtime* rt, int32_t plan_id, int32_t task, void** ptrs, int32_t max_ptrs) {
+  if (!rt) return SS_INVALID_ARGUMENT;
+  if (rt->failed.load()) return SS_FAILED;
+  PlanState* P;
+  { std::lock_guard<std::mutex> lk(rt->mu); P = find_plan(rt, plan_id); }
+  if (!P || !P->active || task < 0 || task >= P->n_tasks) return SS_INVALID_ARGUMENT;
+  ss_backend* be = rt->be;
+  // stays this task opens: wait for the previous occupants of their ranges
+  for (int32_t ii : P->task_creates[task]) {
+    IntervalState& I = *P->intervals[ii];
+    for (int32_t k = P->pred_begin[ii]; k < P->pred_begin[ii + 1]; ++k) {
+      IntervalState& J = *P->intervals[P->pred_index[k]];
+      if (!wait_flag(rt, J.released))
+        return rt->latch(SS_FAIL_CAPACITY, SS_NO_PROGRESS, task, I.iv.object, -1, 0,
+                         "range predecessor never released");
+      if (J.release_event && !J.release_on_compute) {
+        int rc = be->stream_wait_event(be->self, P->compute_stream, J.release_event);
+        if (rc != SS_OK) return rt->latch(SS_FAIL_BACKEND_EVENT, rc, task, I.iv.object, -1, 0, "stream wait failed");
+        rt->trace(SS_TRACE_REUSE_WAIT, task, I.iv.bytes);
+      }
+    }
+    P->object_current[I.iv.object] = ii;
+  }
+  int32_t n = 0;
+  for (int32_t i = P->task_use_begin[task]; i < P->task_use_begin[task + 1]; ++i, ++n) {
+    const ssc::Use& u = P->uses[i];
+    int32_t ii = P->object_current[u.object];
+    if (u.mode != SS_USE_CREATE) {
+      // the stay may be one a fetch opens: find it through the worker's issue flag
+      if (ii < 0 || P->intervals[ii]->released.load(std::memory_order_acquire)) {
+        ii = -1;
+        for (int32_t f = 0; f < static_cast<int32_t>(P->fetch_order.size()); ++f) {
+          const int32_t a = P->fetch_order[f];
+          const int32_t cand = P->action_interval[a];
+          if (P->actions[a].object == u.object && P->actions[a].trigger_task < task &&
+              !(P->intervals[cand]->iv.end_action >= 0 &&
+                P->actions[P->intervals[cand]->iv.end_action].trigger_task < task))
+            ii = cand;
+        }
+        if (ii < 0)
+          return rt->latch(SS_FAIL_OBJECT_STATE, SS_INVALID_ARGUMENT, task, u.object, -1, 0,
+                           "task input has no device stay");
+        P->object_current[u.object] = ii;
+      }
+      IntervalState& I = *P->intervals[ii];
+      if (I.iv.begin_action >= 0) {
+        if (!wait_flag(rt, I.ready_issued))
+          return rt->latch(SS_FAIL_CAPACITY, SS_NO_PROGRESS, task, u.object, I.iv.begin_action, 0,
+                           "fetch was never issued");
+        int rc = be->stream_wait_event(be->self, P->compute_stream, I.ready_event);
+        if (rc != SS_OK) return rt->latch(SS_FAIL_BACKEND_EVENT, rc, task, u.object, -1, 0, "stream wait failed");
+        rt->trace(SS_TRACE_INPUT_WAIT, task, I.iv.bytes);
+      }
+    }
+    if (ptrs && n < max_ptrs) ptrs[n] = rt->dev(P->intervals[ii]->iv.offset);
+  }
+  rt->trace(SS_TRACE_TASK_BEGIN, task, 0);
+  return SS_OK;
+}
+
+int ss_after_task(ss_runtime* rt, int32_t plan_id, int32_t task) {
+  if (!rt) return SS_INVALID_ARGUMENT;
+  if (rt->failed.load()) return SS_FAILED;
+  PlanState* P;
+  { std::lock_guard<std::mutex> lk(rt->mu); P = find_plan(rt, plan_id); }
+  if (!P || !P->active || task < 0 || task >= P->n_tasks) return SS_INVALID_ARGUMENT;
+  int rc = rt->be->event_record(rt->be->self, P->task_fence[task], P->compute_stream);
+  if (rc != SS_OK) return rt->latch(SS_FAIL_BACKEND_EVENT, rc, task, -1, -1, 0, "fence record failed");
+  rt->st_tasks++;
+  rt->trace(SS_TRACE_TASK_END, task, 0);
+  P->published_task.store(task, std::memory_order_release);
+  rt->cv.notify_all();
+  return SS_OK;
+}
+
+int ss_step_end(ss_runtime* rt, int32_t plan_id) {
+  if (!rt) return SS_INVALID_ARGUMENT;
+  PlanState* P;
+  { std::lock_guard<std::mutex> lk(rt->mu); P = find_plan(rt, plan_id); }
+  if (!P || !P->active) return SS_INVALID_ARGUMENT;
+  const int64_t t0 = ss_monotonic_ns();
+  int result = SS_OK;
+  for (;;) {
+    bool done;
+    {
+      std::lock_guard<std::mutex> lk(rt->mu);
+      done = P->next_fetch == P->fetch_order.size() && P->next_evict == P->evict_order.size() &&
+             P->next_release == P->release_order.size();
+    }
+    if (done) break;
+    if (rt->failed.load()) { result = SS_FAILED; break; }
+    if (ss_monotonic_ns() - t0 > HOST_WAIT_NS) {
+      result = rt->latch(SS_FAIL_PLAN, SS_NO_PROGRESS, -1, -1, -1, 0, "step never drained");
+      break;
+    }
+    rt->cv.notify_all();
+    std::this_thread::sleep_for(std::chrono::microseconds(50));
+  }
+  ss_backend* be = rt->be;
+  if (result == SS_OK) {
+    int rc = be->stream_synchronize(be->self, rt->fetch_stream);
+    if (rc == SS_OK) rc = be->stream_synchronize(be->self, rt->evict_stream);
+    if (rc == SS_OK && P->compute_stream) rc = be->stream_synchronize(be->self, P->compute_stream);
+    if (rc != SS_OK) result = rt->latch(SS_FAIL_BACKEND_EVENT, rc, -1, -1, -1, 0, "drain failed");
+  }
+  {
+    std::lock_guard<std::mutex> lk(rt->mu);
+    P->active = false;
+  }
+  rt->trace(SS_TRACE_STEP_END, plan_id, 0);
+  if (rt->failed.load()) return SS_FAILED;
+  return result;
+}
+
+int ss_runtime_wait_idle(ss_runtime* rt) {
+  if (!rt) return SS_INVALID_ARGUMENT;
+  ss_backend* be = rt->be;
+  int rc = be->stream_synchronize(be->self, rt->fetch_stream);
+  if (rc == SS_OK) rc = be->stream_synchronize(be->self, rt->evict_stream);
+  return rc;
+}
+
+int ss_spill_write(ss_runtime* rt, int64_t off, const void* src, int64_t bytes) {
+  if (!rt || off < 0 || bytes < 0 || off + bytes > rt->cfg.spill_bytes) return SS_INVALID_ARGUMENT;
+  std::memcpy(rt->spill(off), src, static_cast<size_t>(bytes));
+  return SS_OK;
+}
+int ss_spill_read(ss_runtime* rt, int64_t off, void* dst, int64_t bytes) {
+  if (!rt || off < 0 || bytes < 0 || off + bytes > rt->cfg.spill_bytes) return SS_INVALID_ARGUMENT;
+  std::memcpy(dst, rt->spill(off), static_cast<size_t>(bytes));
+  return SS_OK;
+}
+
+int ss_calibrate_transfers(ss_runtime* rt, int64_t bytes, int32_t repeats, ss_transfer_profile* out) {
+  if (!rt || !out || bytes <= 0 || bytes > rt->cfg.device_bytes / 2 || bytes > rt->cfg.spill_bytes / 2)
+    return SS_INVALID_ARGUMENT;
+  if (repeats <= 0) repeats = 3;
+  ss_backend* be = rt->be;
+  auto time_copy = [&](bool fetch, bool with_other, int64_t n) -> double {
+    double best = 1e30;
+    for (int r = 0; r < repeats; ++r) {
+      be->stream_synchronize(be->self, rt->fetch_stream);
+      be->stream_synchronize(be->self, rt->evict_stream);
+      if (with_other) {
+        if (fetch) be->copy_async(be->self, rt->spill(bytes), rt->dev(bytes), static_cast<size_t>(bytes), SS_COPY_D2H, rt->evict_stream);
+        else be->copy_async(be->self, rt->dev(bytes), rt->spill(bytes), static_cast<size_t>(bytes), SS_COPY_H2D, rt->fetch_stream);
+      }
+      const int64_t t0 = ss_monotonic_ns();
+      if (fetch) {
+        be->copy_async(be->self, rt->dev(0), rt->spill(0), static_cast<size_t>(n), SS_COPY_H2D, rt->fetch_stream);
+        be->stream_synchronize(be->self, rt->fetch_stream);
+      } else {
+        be->copy_async(be->self, rt->spill(0), rt->dev(0), static_cast<size_t>(n), SS_COPY_D2H, rt->evict_stream);
+        be->stream_synchronize(be->self, rt->evict_stream);
+      }
+      best = std::min(best, static_cast<double>(ss_monotonic_ns() - t0));
+    }
+    return best;
+  };
+  const double lat_f = time_copy(true, false, 64), lat_e = time_copy(false, false, 64);
+  const double f_solo = time_copy(true, false, bytes), e_solo = time_copy(false, false, bytes);
+  const double f_conc = time_copy(true, true, bytes), e_conc = time_copy(false, true, bytes);
+  auto rate = [&](double ns, double lat) { return static_cast<double>(bytes) / std::max(ns - lat, 1.0) * 1e9; };
+  out->fetch_latency_ns = static_cast<int64_t>(lat_f);
+  out->evict_latency_ns = static_cast<int64_t>(lat_e);
+  out->fetch_solo_bps = rate(f_solo, lat_f);
+  out->evict_solo_bps = rate(e_solo, lat_e);
+  out->fetch_concurrent_bps = std::min(rate(f_conc, lat_f), out->fetch_solo_bps);
+  out->evict_concurrent_bps = std::min(rate(e_conc, lat_e), out->evict_solo_bps);
+  return SS_OK;
+}
+
+}  // extern "C"

@@ -148,8 +148,15 @@ int simulate(const ProgramView& pv, const ss_device_config& cfg, const ss_action
     if (fetch.current < 0 && !fetch.queue.empty()) {
       const int32_t a = fetch.queue.front();
       const int32_t o = actions[a].object;
-      if (st[o].resident) return SS_INVALID_ARGUMENT;   // fetched twice
-      if (used + pv.bytes[o] <= cap) {
+      bool blocked = false;
+      if (st[o].resident) {
+        // the previous stay is still draining to spill: the fetch waits behind that evict
+        bool draining = st[o].evicting;
+        for (int32_t e : evict.queue) if (actions[e].object == o) { draining = true; break; }
+        if (!draining) return SS_INVALID_ARGUMENT;   // fetched twice
+        blocked = true;
+      }
+      if (!blocked && used + pv.bytes[o] <= cap) {
         fetch.queue.pop_front();
         fetch.current = a;
         fetch.latency_left = cfg.fetch_latency_ns;
@@ -342,10 +349,8 @@ int ss_check_schedule(const ss_program* program, const ss_action* actions, int32
     for (int32_t a : by_trigger[slot]) {
       const int32_t o = actions[a].object;
       if (actions[a].kind == SS_ACT_FETCH) {
-        if (resident[o] || !pv.persistent(o) && !dirty[o]) {
-          // transient objects may only be fetched after an evict made a spill copy
-          if (resident[o] || !pv.persistent(o)) return a;
-        }
+        // a transient object can only come back after an evict gave it a spill copy
+        if (resident[o] || (!pv.persistent(o) && dirty[o] != 2)) return a;
         resident[o] = 1;
       } else if (actions[a].kind == SS_ACT_EVICT) {
         if (!resident[o]) return a;
@@ -358,9 +363,6 @@ int ss_check_schedule(const ss_program* program, const ss_action* actions, int32
     }
     return -1;
   };
-  // transient objects fetched back must have been evicted before: track via dirty==2
-  auto fetch_ok = [&](int32_t o) { return pv.persistent(o) || dirty[o] == 2; };
-  (void)fetch_ok;
   int32_t bad = apply(0);
   if (bad >= 0) { if (bad_action) *bad_action = bad; return SS_INVALID_ARGUMENT; }
   for (int32_t t = 0; t < pv.n_tasks; ++t) {

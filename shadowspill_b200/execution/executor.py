@@ -1,0 +1,341 @@
+"""Plan execution: the per-step hot path.
+
+``Executor`` admits a ``Plan`` into a native ``Runtime``, keeps every persistent
+tensor in the pinned spill pool between invocations, and on ``run`` stages the
+batch, then walks the plan's tasks: ``before_task`` (native: stream waits for
+fetched inputs and for the previous occupants of created ranges) -> the stage
+function on the compute stream -> ``after_task`` (native: fence + publication
+of the triggered fetch / evict / release batch to the worker thread). All
+device tensors are views at the plan's fixed offsets; nothing is allocated for
+planned objects while stepping.
+
+Reference: packages/engine/src/shadowspill/execution/executor.py:35 (``Executor``),
+``run`` :369, hot loop :507-516, dispatch.py:32.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from ..data.synthetic import HostMicrobatch
+from ..frontend.capture import TrainingDescription, batch_layout, saved_layout
+from ..ir.plan import Plan
+from ..models.decoder import BatchMeta, build_stages
+from ..ops import functional as F
+from ..runtime.core import Runtime
+
+_TORCH_DT = {"int64": torch.int64, "int32": torch.int32, "float32": torch.float32}
+
+
+@dataclass
+class Hyperparameters:
+    lr: float = 1e-4
+    beta1: float = 0.9
+    beta2: float = 0.95
+    eps: float = 1e-8
+    weight_decay: float = 0.0
+    grad_scale: float = 1.0
+
+
+@dataclass
+class InvocationResult:
+    loss: float
+    tokens: int
+    execution_seconds: float
+    device_seconds: float = 0.0
+    h2d_bytes: int = 0
+    d2h_bytes: int = 0
+    task_seconds: list[float] = field(default_factory=list)
+    trace: list[dict] = field(default_factory=list)
+    metrics: dict[str, float] = field(default_factory=dict)
+
+
+class Executor:
+    def __init__(self, plan: Plan, desc: TrainingDescription, *, device: str = "cuda",
+                 device_index: int = 0, seed: int = 0, hyper: Hyperparameters | None = None,
+                 stochastic_rounding: bool = True, trace_capacity: int = 0,
+                 mock_bps: float = 0.0):
+        self.plan, self.desc = plan, desc
+        self.program = plan.program
+        self.cuda = device == "cuda"
+        self.device_index = device_index
+        self.torch_device = torch.device(f"cuda:{device_index}") if self.cuda else torch.device("cpu")
+        self.hyper = hyper or Hyperparameters()
+        self.seed = seed
+        self.sr = stochastic_rounding and desc.dtype == torch.bfloat16
+        self.stages = build_stages(desc.cfg)
+        self.completed_updates = 0
+        self.accumulated = 0
+        if self.cuda:
+            torch.cuda.set_device(device_index)
+            from ..ops import _lib
+            _lib.lib()   # fail loudly if the kernel library is missing
+        self.rt = Runtime(plan.device_bytes, plan.spill_bytes, "cuda" if self.cuda else "mock",
+                          device_index, trace_capacity=trace_capacity, mock_bps=mock_bps)
+        self.plan_id = self.rt.admit(plan)
+        self.stream = torch.cuda.Stream(device=self.torch_device) if self.cuda else None
+        self._views: dict[tuple[int, int], object] = {}
+        self._uses = [self.program.sorted_uses(t) for t in range(len(self.program.tasks))]
+        meta = self.program.metadata
+        self.T, self.n_mb, self.slots = meta["microbatch_tokens"], meta["n_microbatches"], meta["slots"]
+        self._batch_layout, _ = batch_layout(self.T, self.slots)
+        self._max_seqlen = [2] * self.n_mb
+        self._obj = {o.name: i for i, o in enumerate(self.program.objects)}
+        self._loss_obj = self._obj["loss"]
+        self._param_offsets = self._global_param_offsets()
+        self._timing_events = None
+        self.closed = False
+
+    # ------------------------------------------------------------------ state in the spill pool
+    def spill_view(self, obj: int) -> torch.Tensor:
+        off = self.plan.spill_offsets[obj]
+        if off < 0:
+            raise KeyError(f"{self.program.objects[obj].name} has no spill home")
+        return self.rt.spill[off:off + self.program.objects[obj].bytes]
+
+    def _global_param_offsets(self) -> dict[tuple[int, str], int]:
+        out, off = {}, 0
+        for si, st in enumerate(self.stages):
+            for p in st.params:
+                out[(si, p.name)] = off
+                off += (p.numel + 7) // 8 * 8
+        return out
+
+    def initialize(self, seed: int | None = None) -> None:
+        """Random initialisation straight into the spill homes (seed-only, so the
+        result does not depend on plan, budget or sharding); moments start at zero."""
+        gen = torch.Generator().manual_seed(self.seed if seed is None else seed)
+        for si, st in enumerate(self.stages):
+            w = self.spill_view(self._obj[f"{st.name}.weights"])
+            w.zero_()
+            st.init_(st.views(w, self.desc.dtype), gen)
+            for suffix in ("exp_avg", "exp_avg_sq", "gradients"):
+                name = f"{st.name}.{suffix}"
+                if name in self._obj and self.plan.spill_offsets[self._obj[name]] >= 0:
+                    self.spill_view(self._obj[name]).zero_()
+        self.completed_updates = 0
+        self.accumulated = 0
+
+    def named_tensors(self):
+        """Yields ``(name, tensor view in the spill pool)`` for every persistent
+        model tensor: parameters, then ``exp_avg.*`` / ``exp_avg_sq.*``."""
+        for si, st in enumerate(self.stages):
+            for kind, prefix in (("weights", ""), ("exp_avg", "exp_avg."), ("exp_avg_sq", "exp_avg_sq.")):
+                name = f"{st.name}.{kind}"
+                if name not in self._obj:
+                    continue
+                views = st.views(self.spill_view(self._obj[name]), self.desc.dtype)
+                for p in st.params:
+                    yield f"{prefix}{st.name}.{p.name}", views[p.name]
+
+    def state_dict(self) -> dict[str, torch.Tensor]:
+        return {k: v.clone() for k, v in self.named_tensors()}
+
+    def load_state_dict(self, state: dict[str, torch.Tensor], strict: bool = True) -> None:
+        seen = set()
+        for k, v in self.named_tensors():
+            if k in state:
+                v.copy_(state[k].to(v.dtype).reshape(v.shape))
+                seen.add(k)
+            elif strict:
+                raise KeyError(f"missing tensor {k}")
+        extra = set(state) - seen
+        if strict and extra:
+            raise KeyError(f"unexpected tensors {sorted(extra)[:4]}")
+
+    # ------------------------------------------------------------------ inputs
+    def stage_inputs(self, batch: list[HostMicrobatch]) -> int:
+        """Writes the packed microbatches into their spill homes; returns bytes staged."""
+        if len(batch) != self.n_mb:
+            raise ValueError(f"plan expects {self.n_mb} microbatches, got {len(batch)}")
+        total = 0
+        for m, mb in enumerate(batch):
+            if mb.tokens.shape[0] != self.T:
+                raise ValueError(f"microbatch {m}: {mb.tokens.shape[0]} tokens, plan expects {self.T}")
+            if mb.cu_seqlens.shape[0] > self.slots + 1:
+                raise ValueError(f"microbatch {m}: too many sequences for {self.slots} slots")
+            dst = self.spill_view(self._obj[f"batch.{m}"]).numpy()
+            for name, (off, count, dt) in self._batch_layout.items():
+                src = getattr(mb, name)
+                view = dst[off:off + count * np.dtype(dt).itemsize].view(dt)
+                if name == "cu_seqlens":
+                    view[:src.shape[0]] = src
+                    view[src.shape[0]:] = src[-1]
+                else:
+                    view[:] = src
+                total += view.nbytes
+            self._max_seqlen[m] = int(mb.max_seqlen)
+        self.spill_view(self._loss_obj).zero_()
+        return total
+
+    # ------------------------------------------------------------------ views
+    def _device_view(self, ptr: int, nbytes: int) -> torch.Tensor:
+        off = ptr - self.rt.device_base
+        return self.rt.device[off:off + nbytes]
+
+    def _batch_meta(self, flat: torch.Tensor, m: int) -> BatchMeta:
+        parts = {}
+        for name, (off, count, dt) in self._batch_layout.items():
+            tdt = _TORCH_DT[dt]
+            parts[name] = flat[off:off + count * tdt.itemsize].view(tdt)
+        return BatchMeta(parts["tokens"], parts["targets"], parts["weights"], parts["positions"],
+                         parts["cu_seqlens"], self._max_seqlen[m])
+
+    def _bind(self, task: int, ptrs: list[int]) -> dict[str, object]:
+        """Role -> tensor views for one task (cached: offsets are fixed by the plan)."""
+        key = (task, hash(tuple(ptrs)))
+        hit = self._views.get(key)
+        if hit is not None:
+            return hit
+        t = self.program.tasks[task]
+        st = self.stages[t.stage]
+        out: dict[str, object] = {}
+        for u, ptr in zip(self._uses[task], ptrs):
+            obj = self.program.objects[u.object]
+            flat = self._device_view(ptr, obj.bytes)
+            if u.role in ("params", "m", "v"):
+                out[u.role] = st.views(flat, self.desc.dtype)
+            elif u.role == "grads":
+                out[u.role] = st.views(flat, self.desc.grad_dtype, torch.float32)
+            elif u.role in ("x", "y", "dx"):
+                out[u.role] = flat.view(self.desc.dtype).view(self.T, self.desc.cfg.d_model)
+            elif u.role == "batch":
+                out["batch_flat"] = flat
+            elif u.role == "loss":
+                out[u.role] = flat[:4].view(torch.float32)
+            elif u.role == "saved":
+                lay, _ = saved_layout(st, self.T, t.variant, self.desc.dtype)
+                sv = {}
+                for name, shape, dt, off in lay:
+                    n = int(np.prod(shape)) * dt.itemsize
+                    sv[name] = flat[off:off + n].view(dt).view(shape)
+                out[u.role] = sv
+            out[f"{u.role}.mode"] = u.mode
+        self._views[key] = out
+        return out
+
+    # ------------------------------------------------------------------ task bodies
+    def _run_task(self, task: int, B: dict[str, object]) -> None:
+        t = self.program.tasks[task]
+        st = self.stages[t.stage]
+        meta = self._batch_meta(B["batch_flat"], t.microbatch) if "batch_flat" in B else None
+        if t.kind == "forward":
+            keep = st.SAVE_SETS.get(t.variant, ()) if "saved" in B else ()
+            _, saved = st.forward(B["params"], B.get("x"), meta, keep, out=B["y"])
+            if "saved" in B:
+                for name, dst in B["saved"].items():
+                    dst.copy_(saved[name].reshape(dst.shape))
+        elif t.kind == "head":
+            train = t.variant == "train"
+            first = self._first(t.stage, B)
+            st.loss_and_backward(B["params"], B.get("grads"), B["x"], meta, B["loss"], first,
+                                 dx=B.get("dx"), train=train, grad_scale=1.0)
+        elif t.kind == "backward":
+            first = self._first(t.stage, B)
+            saved = dict(B["saved"]) if "saved" in B else {}
+            if "attn" in saved:
+                saved["attn"] = saved["attn"]
+            st.backward(B["params"], B["grads"], B.get("x"), B["dx"], meta, saved, first)
+        elif t.kind == "optimizer":
+            self._optimizer(t.stage, B)
+        else:
+            raise RuntimeError(f"task kind {t.kind!r} has no executor")
+
+    def _first(self, stage: int, B) -> bool:
+        if self.desc.mode == "step":
+            return B.get("grads.mode") == "create"
+        fresh = self.accumulated == 0 and stage not in self._grad_seen
+        self._grad_seen.add(stage)
+        return fresh
+
+    def _optimizer(self, stage: int, B) -> None:
+        st, h = self.stages[stage], self.hyper
+        for p in st.params:
+            if not p.trainable:
+                continue
+            F.adamw_(B["params"][p.name].view(-1), B["grads"][p.name].view(-1),
+                     B["m"][p.name].view(-1), B["v"][p.name].view(-1), lr=h.lr, beta1=h.beta1,
+                     beta2=h.beta2, eps=h.eps, weight_decay=h.weight_decay,
+                     step=self.completed_updates + 1, grad_scale=h.grad_scale, seed=self.seed,
+                     offset=self._param_offsets[(stage, p.name)], stochastic_param=self.sr,
+                     stochastic_state=self.sr)
+
+    # ------------------------------------------------------------------ run
+    def run(self, batch: list[HostMicrobatch], *, trace: bool = False,
+            time_tasks: bool = False) -> InvocationResult:
+        if self.closed:
+            raise RuntimeError("executor is closed")
+        t0 = time.perf_counter()
+        h2d = self.stage_inputs(batch)
+        self._grad_seen: set[int] = set()
+        if trace:
+            self.rt.trace_begin()
+        n_tasks = len(self.program.tasks)
+        events = None
+        if self.cuda:
+            start_ev, end_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if time_tasks:
+                events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                          for _ in range(n_tasks)]
+            ctx = torch.cuda.stream(self.stream)
+            ctx.__enter__()
+            start_ev.record(self.stream)
+        task_seconds = [0.0] * n_tasks
+        try:
+            self.rt.step_begin(self.plan_id, self.stream.cuda_stream if self.cuda else None)
+            for task in range(n_tasks):
+                ptrs = self.rt.before_task(self.plan_id, task, len(self._uses[task]))
+                B = self._bind(task, ptrs)
+                if events:
+                    events[task][0].record(self.stream)
+                elif not self.cuda and time_tasks:
+                    tt = time.perf_counter()
+                self._run_task(task, B)
+                if events:
+                    events[task][1].record(self.stream)
+                elif not self.cuda and time_tasks:
+                    task_seconds[task] = time.perf_counter() - tt
+                self.rt.after_task(self.plan_id, task)
+            if self.cuda:
+                end_ev.record(self.stream)
+            self.rt.step_end(self.plan_id)
+        finally:
+            if self.cuda:
+                ctx.__exit__(None, None, None)
+        loss = float(self.spill_view(self._loss_obj)[:4].view(torch.float32)[0])   # device -> host result
+        device_seconds = 0.0
+        if self.cuda:
+            device_seconds = start_ev.elapsed_time(end_ev) * 1e-3
+            if events:
+                task_seconds = [a.elapsed_time(b) * 1e-3 for a, b in events]
+        if self.desc.mode == "step":
+            self.completed_updates += 1
+        elif self.desc.mode == "forward_backward":
+            self.accumulated += 1
+        tr = self.rt.trace_end() if trace else []
+        return InvocationResult(loss, self.T * self.n_mb, time.perf_counter() - t0, device_seconds,
+                                h2d, 4, task_seconds if time_tasks else [], tr)
+
+    def discard_gradients(self) -> None:
+        self.accumulated = 0
+
+    def close(self) -> None:
+        if self.closed:
+            return
+        self.closed = True
+        if self.cuda:
+            torch.cuda.synchronize(self.torch_device)
+        self._views.clear()
+        try:
+            self.rt.close_plan(self.plan_id)
+        finally:
+            self.rt.close()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()

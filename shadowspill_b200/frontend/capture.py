@@ -1,0 +1,280 @@
+"""Build phase: model configuration + batch geometry -> ``Program``.
+
+The step is unrolled over stages and microbatches in a chosen walk
+(``StepDataOrdering``): *breadth* runs one stage across all microbatches before
+the next stage, so a stage's weights are fetched once per pass; *depth* runs
+each microbatch through the whole model. The last stage runs its forward
+together with its backward (``pair_loss``), backward passes visit microbatches
+in reverse (``reverse_breadth``), and each stage's optimizer task follows its
+last backward (``stage_interleaved``) or all of them run at the end (``tail``).
+These are the reference's walk and ordering knobs
+(packages/engine/src/shadowspill/step/ordering.py:11,
+docs/architecture/planning-pipeline.md:56-76).
+
+Every stage execution is a task; every tensor that outlives a task is an
+object: stage weights and AdamW moments (persistent: their home is the spill
+pool), gradients, stage-boundary activations, saved sets of ``save`` variants,
+the per-microbatch activation gradient, the packed batch and the loss.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..ir.program import ObjectSpec, Program, TaskSpec, UseSpec
+from ..models.config import DecoderConfig
+from ..models.decoder import ALIGN, Stage, build_stages
+
+_DT = {torch.bfloat16: "bfloat16", torch.float32: "float32", torch.float16: "float16"}
+
+
+@dataclass(frozen=True)
+class StepDataOrdering:
+    walk: str = "breadth"            # breadth | depth
+    reverse_breadth: bool = True
+    pair_loss: bool = True
+    optimizer: str = "stage_interleaved"   # stage_interleaved | tail
+
+    def label(self) -> str:
+        return f"{self.walk}/{self.optimizer}"
+
+
+@dataclass
+class BatchGeometry:
+    microbatch_tokens: int
+    n_microbatches: int
+    slots: int = 64                  # sequence slots per microbatch (cu_seqlens has slots+1)
+    mean_seqlen: float = 2048.0
+
+    @property
+    def tokens(self) -> int:
+        return self.microbatch_tokens * self.n_microbatches
+
+
+def batch_layout(T: int, slots: int) -> tuple[dict[str, tuple[int, int, str]], int]:
+    """Byte layout of one packed microbatch object: name -> (offset, count, dtype)."""
+    out, off = {}, 0
+    for name, count, dt, size in (("tokens", T, "int64", 8), ("targets", T, "int64", 8),
+                                  ("weights", T, "float32", 4), ("positions", T, "int32", 4),
+                                  ("cu_seqlens", slots + 1, "int32", 4)):
+        out[name] = (off, count, dt)
+        off = (off + count * size + ALIGN - 1) // ALIGN * ALIGN
+    return out, off
+
+
+def saved_layout(stage: Stage, T: int, variant: str, dtype: torch.dtype = torch.bfloat16):
+    """[(name, shape, dtype, offset)], total bytes of a stage's saved set."""
+    if not hasattr(stage, "saved_shapes"):
+        return [], 0
+    out, off = [], 0
+    for name, shape, dt in stage.saved_shapes(T, variant, dtype):
+        nbytes = int(torch.tensor([], dtype=dt).element_size())
+        for d in shape:
+            nbytes *= d
+        out.append((name, shape, dt, off))
+        off = (off + nbytes + ALIGN - 1) // ALIGN * ALIGN
+    return out, off
+
+
+@dataclass
+class TrainingDescription:
+    """Everything the executor needs to turn tasks back into stage calls."""
+    cfg: DecoderConfig
+    geometry: BatchGeometry
+    ordering: StepDataOrdering
+    dtype: torch.dtype = torch.bfloat16
+    grad_dtype: torch.dtype = torch.bfloat16
+    selection: dict[int, str] = field(default_factory=dict)   # stage index -> variant
+    mode: str = "step"                # step | forward_backward | forward
+
+    def variant(self, stage_index: int) -> str:
+        return self.selection.get(stage_index, "recompute")
+
+
+def estimate_duration_ns(flops: float, nbytes: float, tflops: float = 1100.0,
+                         gbps: float = 5000.0) -> int:
+    return int(max(flops / (tflops * 1e12), nbytes / (gbps * 1e9)) * 1e9) + 20_000
+
+
+def _build(desc: TrainingDescription) -> Program:
+    cfg, geo, order = desc.cfg, desc.geometry, desc.ordering
+    stages = build_stages(cfg)
+    S, n_mb, T = len(stages), geo.n_microbatches, geo.microbatch_tokens
+    train = desc.mode != "forward"
+    step = desc.mode == "step"
+    isz = desc.dtype.itemsize
+    prog = Program(metadata={"model": cfg.to_json(), "tokens": geo.tokens, "mode": desc.mode,
+                             "microbatch_tokens": T, "n_microbatches": n_mb, "slots": geo.slots,
+                             "ordering": order.label(), "dtype": _DT[desc.dtype],
+                             "grad_dtype": _DT[desc.grad_dtype],
+                             "selection": ",".join(f"{k}:{v}" for k, v in sorted(desc.selection.items()))
+                             or "recompute",
+                             "walk": order.walk, "optimizer_order": order.optimizer})
+    W, M, V, G = [], [], [], []
+    for si, st in enumerate(stages):
+        _, pbytes = st.layout(desc.dtype)
+        _, gbytes = st.layout(desc.grad_dtype, torch.float32)
+        W.append(prog.add_object(ObjectSpec(f"{st.name}.weights", pbytes, "weight", True, stage=si)))
+        if train:
+            # gradients persist across calls when accumulation is driven from outside
+            G.append(prog.add_object(ObjectSpec(f"{st.name}.gradients", gbytes, "gradient",
+                                                persistent=not step, stage=si)))
+        if step:
+            M.append(prog.add_object(ObjectSpec(f"{st.name}.exp_avg", pbytes, "optimizer_state", True, stage=si)))
+            V.append(prog.add_object(ObjectSpec(f"{st.name}.exp_avg_sq", pbytes, "optimizer_state", True, stage=si)))
+    _, in_bytes = batch_layout(T, geo.slots)
+    IN = [prog.add_object(ObjectSpec(f"batch.{m}", in_bytes, "input", True, pinned_resident=True,
+                                     microbatch=m)) for m in range(n_mb)]
+    LOSS = prog.add_object(ObjectSpec("loss", 512, "output", True, pinned_resident=True))
+    act_bytes = T * cfg.d_model * isz
+    A = [[prog.add_object(ObjectSpec(f"{stages[si].name}.out.{m}", act_bytes, "activation",
+                                     stage=si, microbatch=m)) for m in range(n_mb)]
+         for si in range(S - 1)]
+    DX = [prog.add_object(ObjectSpec(f"dx.{m}", act_bytes, "activation_gradient", microbatch=m))
+          for m in range(n_mb)] if train else []
+    SAVED: dict[tuple[int, int], int] = {}
+    for si in range(1, S - 1):
+        var = desc.variant(si)
+        if train and var != "recompute":
+            _, sbytes = saved_layout(stages[si], T, var, desc.dtype)
+            for m in range(n_mb):
+                SAVED[(si, m)] = prog.add_object(ObjectSpec(f"{stages[si].name}.saved.{m}", sbytes,
+                                                            "saved", stage=si, microbatch=m))
+    grad_created = [False] * S
+
+    def key(st: Stage, what: str, var: str = "") -> str:
+        return f"{cfg.family}:{st.kind}:{type(st).__name__}:{what}:{var}:T{T}"
+
+    def fwd(si: int, m: int) -> None:
+        st = stages[si]
+        var = desc.variant(si) if train else "recompute"
+        uses = [UseSpec(W[si], "read", "params"), UseSpec(IN[m], "read", "batch"),
+                UseSpec(A[si][m], "create", "y")]
+        if si > 0:
+            uses.append(UseSpec(A[si - 1][m], "read", "x"))
+        if (si, m) in SAVED:
+            uses.append(UseSpec(SAVED[(si, m)], "create", "saved"))
+        fl = st.flops(T, geo.mean_seqlen)
+        prog.add_task(TaskSpec(f"F.{st.name}.{m}", "forward", si, m, uses,
+                               estimate_duration_ns(fl, 8.0 * act_bytes),
+                               st.workspace_bytes(T, isz) // 2, var, flops=fl, tokens=T,
+                               profile_key=key(st, "fwd", var)))
+
+    def head(m: int) -> None:
+        si, st = S - 1, stages[S - 1]
+        uses = [UseSpec(W[si], "read", "params"), UseSpec(IN[m], "read", "batch"),
+                UseSpec(A[si - 1][m], "read", "x"), UseSpec(LOSS, "mutate", "loss")]
+        if train:
+            uses.append(UseSpec(DX[m], "create", "dx"))
+            if step and not grad_created[si]:
+                uses.append(UseSpec(G[si], "create", "grads")); grad_created[si] = True
+            else:
+                uses.append(UseSpec(G[si], "mutate", "grads"))
+        fl = st.flops(T, geo.mean_seqlen) * (3.0 if train else 1.0)
+        prog.add_task(TaskSpec(f"H.{st.name}.{m}", "head", si, m, uses,
+                               estimate_duration_ns(fl, 8.0 * act_bytes),
+                               st.workspace_bytes(T, isz), "train" if train else "eval",
+                               flops=fl, tokens=T, profile_key=key(st, "head", "train" if train else "eval")))
+
+    def bwd(si: int, m: int) -> None:
+        st = stages[si]
+        var = desc.variant(si)
+        uses = [UseSpec(W[si], "read", "params"), UseSpec(IN[m], "read", "batch"),
+                UseSpec(DX[m], "mutate" if si > 0 else "read", "dx")]
+        if si > 0:
+            uses.append(UseSpec(A[si - 1][m], "read", "x"))
+        if (si, m) in SAVED:
+            uses.append(UseSpec(SAVED[(si, m)], "read", "saved"))
+        if step and not grad_created[si]:
+            uses.append(UseSpec(G[si], "create", "grads")); grad_created[si] = True
+        else:
+            uses.append(UseSpec(G[si], "mutate", "grads"))
+        fl = st.flops(T, geo.mean_seqlen) * (3.0 if var == "recompute" else 2.0)
+        prog.add_task(TaskSpec(f"B.{st.name}.{m}", "backward", si, m, uses,
+                               estimate_duration_ns(fl, 16.0 * act_bytes),
+                               st.workspace_bytes(T, isz), var, flops=fl, tokens=T,
+                               profile_key=key(st, "bwd", var)))
+
+    def opt(si: int) -> None:
+        st = stages[si]
+        pbytes = prog.objects[W[si]].bytes
+        prog.add_task(TaskSpec(f"O.{st.name}", "optimizer", si, -1,
+                               [UseSpec(W[si], "mutate", "params"), UseSpec(G[si], "read", "grads"),
+                                UseSpec(M[si], "mutate", "m"), UseSpec(V[si], "mutate", "v")],
+                               estimate_duration_ns(0.0, 8.0 * pbytes), 0, "adamw",
+                               profile_key=f"opt:{pbytes}"))
+
+    body = list(range(S - 1))
+    mbs = list(range(n_mb))
+    back_mbs = list(reversed(mbs)) if order.reverse_breadth else mbs
+    if order.walk == "breadth":
+        for si in body:
+            for m in mbs:
+                fwd(si, m)
+        for m in mbs:
+            head(m)
+        if step and order.optimizer == "stage_interleaved":
+            opt(S - 1)
+        if train:
+            for si in reversed(body):
+                for m in back_mbs:
+                    bwd(si, m)
+                if step and order.optimizer == "stage_interleaved":
+                    opt(si)
+    elif order.walk == "depth":
+        for m in mbs:
+            for si in body:
+                fwd(si, m)
+            head(m)
+            if train:
+                for si in reversed(body):
+                    bwd(si, m)
+        if step and order.optimizer == "stage_interleaved":
+            for si in reversed(range(S)):
+                opt(si)
+    else:
+        raise ValueError(f"unknown walk {order.walk!r}")
+    if step and order.optimizer == "tail":
+        for si in reversed(range(S)):
+            opt(si)
+    prog.validate()
+    return prog
+
+
+def build_step(cfg: DecoderConfig, geometry: BatchGeometry,
+               ordering: StepDataOrdering | None = None, *, dtype=torch.bfloat16,
+               grad_dtype=None, selection: dict[int, str] | None = None):
+    """Forward + backward + optimizer of one global batch. Returns ``(Program, description)``."""
+    desc = TrainingDescription(cfg, geometry, ordering or StepDataOrdering(), dtype,
+                               grad_dtype or dtype, dict(selection or {}), "step")
+    return _build(desc), desc
+
+
+def build_forward_backward(cfg, geometry, ordering=None, *, dtype=torch.bfloat16, grad_dtype=None,
+                           selection=None):
+    """Gradient accumulation without the update (gradients are persistent state)."""
+    desc = TrainingDescription(cfg, geometry, ordering or StepDataOrdering(), dtype,
+                               grad_dtype or dtype, dict(selection or {}), "forward_backward")
+    return _build(desc), desc
+
+
+def build_forward(cfg, geometry, ordering=None, *, dtype=torch.bfloat16):
+    """Evaluation: forward passes and the loss only."""
+    desc = TrainingDescription(cfg, geometry, ordering or StepDataOrdering(), dtype, dtype, {},
+                               "forward")
+    return _build(desc), desc
+
+
+def recompute_share_selections(cfg: DecoderConfig, shares=(100, 75, 50, 25, 0),
+                               saved_variant: str = "save") -> list[dict[int, str]]:
+    """One selection per recompute share: the recomputed layers sit at centred,
+    evenly spaced positions in layer order (the reference's resolution rule,
+    docs/architecture/graph-pair-selection.md:162-171,198)."""
+    n = cfg.n_layers
+    out = []
+    for share in shares:
+        k = round(n * share / 100)
+        rec = {int((i + 0.5) * n / k) for i in range(k)} if k else set()
+        out.append({li + 1: saved_variant for li in range(n) if li not in rec})
+    return out

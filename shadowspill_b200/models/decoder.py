@@ -185,6 +185,26 @@ class DenseLayerStage(Stage):
                 total += T * 4
         return total
 
+    def saved_shapes(self, T, variant, dtype=torch.bfloat16):
+        """[(name, shape, dtype)] of the tensors a ``variant`` forward keeps."""
+        c = self.cfg
+        shapes = {"h1": (T, c.d_model), "qkv": (T, self.qkv_width),
+                  "attn": (T, c.n_heads * c.head_dim), "x_mid": (T, c.d_model),
+                  "h2": (T, c.d_model), "gu": (T, 2 * c.d_ff), "hmlp": (T, c.d_ff)}
+        out = []
+        for n in self.SAVE_SETS[variant]:
+            if n in shapes:
+                out.append((n, shapes[n], dtype))
+            elif n == "lse":
+                out.append((n, (c.n_heads, T), torch.float32))
+            else:
+                out.append((n, (T,), torch.float32))
+        if c.qk_norm and "qkv" in self.SAVE_SETS[variant]:
+            out += [("qk_raw", (T, (c.n_heads + c.n_kv_heads) * c.head_dim), dtype),
+                    ("q_rstd", (T * c.n_heads,), torch.float32),
+                    ("k_rstd", (T * c.n_kv_heads,), torch.float32)]
+        return out
+
     def workspace_bytes(self, T, itemsize=2):
         c = self.cfg
         # backward peak: every intermediate of the forward plus dgu and dqkv

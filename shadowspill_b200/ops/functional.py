@@ -84,7 +84,12 @@ def linear_wgrad(dy, x, out=None, accumulate=False, out_dtype=None):
 def rmsnorm_fwd(x, w, eps=1e-5, zero_centered=False, delta=None, out=None, rstd=None):
     """``x += delta`` (optional, in place) then RMSNorm. Returns ``(y, rstd)``."""
     if not _cuda(x):
-        return reference.rmsnorm_fwd(x, w, eps, zero_centered, delta)
+        y, rs = reference.rmsnorm_fwd(x, w, eps, zero_centered, delta)
+        if out is not None:
+            y = out.copy_(y)
+        if rstd is not None:
+            rs = rstd.copy_(rs)
+        return y, rs
     T, D = x.shape
     y = torch.empty_like(x) if out is None else out
     rs = torch.empty(T, dtype=torch.float32, device=x.device) if rstd is None else rstd
@@ -138,7 +143,8 @@ def rope_(buf, positions, *, col0, heads, dh, rot=None, theta=10000.0, inverse=F
 # ------------------------------------------------------------------------ SwiGLU
 def swiglu_fwd(gu, out=None):
     if not _cuda(gu):
-        return reference.swiglu_fwd(gu)
+        res = reference.swiglu_fwd(gu)
+        return res if out is None else out.copy_(res)
     T, F2 = gu.shape
     h = torch.empty((T, F2 // 2), dtype=gu.dtype, device=gu.device) if out is None else out
     _lib.check(_lib.lib().ss_swiglu_fwd(gu.data_ptr(), h.data_ptr(), T, F2 // 2,
@@ -148,7 +154,8 @@ def swiglu_fwd(gu, out=None):
 
 def swiglu_bwd(gu, dh, out=None):
     if not _cuda(gu):
-        return reference.swiglu_bwd(gu, dh)
+        res = reference.swiglu_bwd(gu, dh)
+        return res if out is None else out.copy_(res)
     T, F2 = gu.shape
     dgu = torch.empty_like(gu) if out is None else out
     _lib.check(_lib.lib().ss_swiglu_bwd(gu.data_ptr(), dh.data_ptr(), dgu.data_ptr(), T, F2 // 2,
@@ -159,7 +166,8 @@ def swiglu_bwd(gu, dh, out=None):
 # ------------------------------------------------------------------------ embedding
 def embedding_fwd(ids, W, out=None):
     if not _cuda(W):
-        return reference.embedding_fwd(ids, W)
+        res = reference.embedding_fwd(ids, W)
+        return res if out is None else out.copy_(res)
     T = ids.numel()
     V, D = W.shape
     o = torch.empty((T, D), dtype=W.dtype, device=W.device) if out is None else out

@@ -1,0 +1,208 @@
+"""``plan_program``: program + budgets + link facts -> executable ``Plan``.
+
+Runs the native search (reduce / emit / simulate / repair / place), then gives
+every object that touches the spill pool a home there, recovers the reuse
+dependencies of the fixed device layout, and fills the plan summary the reports
+show. ``sweep_programs`` plans a family of candidate programs (orderings,
+save/recompute selections, microbatch geometries) and keeps the fastest.
+
+Reference: packages/engine/src/shadowspill/planning/plan.py:26 (``plan_program``),
+planning/sweep.py:21, planning/memory_search/algorithm.py:284 (``SearchOptions``).
+"""
+from __future__ import annotations
+
+import concurrent.futures
+import ctypes as C
+from dataclasses import dataclass, field
+
+from .. import native
+from ..communication.info import CommunicationInfo
+from ..ir.plan import MemoryAction, MemorySchedule, Plan, PlanSummary
+from ..ir.program import Program
+from ..simulator.api import (SimulationConfig, place_lifetimes, recover_layout_reuse,
+                             stays_from_native)
+
+GIB = 1 << 30
+EXTERNAL_HEADROOM = 512 << 20   # bytes of the device budget left to the driver and libraries
+
+
+class PlanningError(RuntimeError):
+    pass
+
+
+@dataclass
+class SearchOptions:
+    workers: int = 0
+    strategies: tuple[str, ...] = native.STRATEGIES
+    fetch_rules: tuple[str, ...] = native.FETCH_RULES
+    max_repairs: int = 16
+    minimum_object_bytes_evict_eligible: int = 1 << 20
+    capacity_refinement_step: int = 256 << 20
+    deterministic: bool = False
+    trace: bool = False
+    alignment: int = 512
+
+    def to_native(self) -> native.SearchOptions:
+        sm = sum(1 << native.STRATEGIES.index(s) for s in self.strategies)
+        rm = sum(1 << native.FETCH_RULES.index(r) for r in self.fetch_rules)
+        return native.SearchOptions(self.workers, sm, rm, self.max_repairs,
+                                    self.minimum_object_bytes_evict_eligible,
+                                    self.capacity_refinement_step, int(self.deterministic),
+                                    int(self.trace))
+
+
+@dataclass
+class MemoryBudgets:
+    device_bytes: int
+    spill_bytes: int
+    headroom_bytes: int = EXTERNAL_HEADROOM
+    fixed_device_bytes: int = 0     # resident allocations outside the plan (status words, streams)
+
+    @property
+    def capacity(self) -> int:
+        return self.device_bytes - self.headroom_bytes - self.fixed_device_bytes
+
+    @staticmethod
+    def from_gib(device_gib: float, spill_gib: float) -> "MemoryBudgets":
+        return MemoryBudgets(int(device_gib * GIB), int(spill_gib * GIB))
+
+
+def plan_program(program: Program, budgets: MemoryBudgets,
+                 communication: CommunicationInfo | None = None,
+                 options: SearchOptions | None = None) -> Plan:
+    communication = communication or CommunicationInfo()
+    options = options or SearchOptions()
+    program.validate()
+    if budgets.capacity <= 0:
+        raise PlanningError("device budget does not cover the external headroom")
+    lib = native.core()
+    prog, keep = program.to_native()
+    cfg = SimulationConfig(budgets.capacity, communication, options.alignment).to_native()
+    opt = options.to_native()
+    handle = native.vp()
+    native.check(lib.ss_plan_search(C.byref(prog), C.byref(cfg), C.byref(opt), C.byref(handle)),
+                 "ss_plan_search")
+    try:
+        s = lib.ss_search_summary_of(handle).contents
+        trace = lib.ss_search_trace(handle).decode() if options.trace else ""
+        if s.status != native.OK:
+            need = max((t.workspace_bytes for t in program.tasks), default=0)
+            raise PlanningError(
+                f"no schedule fits {budgets.capacity / GIB:.2f} GiB of plan capacity "
+                f"({s.candidates_evaluated} candidates; largest task workspace "
+                f"{need / GIB:.2f} GiB)\n{trace}")
+        na, ni, nt = s.n_actions, s.n_intervals, len(program.tasks)
+        acts = lib.ss_search_actions(handle)
+        actions = [MemoryAction(("fetch", "evict", "release")[acts[i].kind], acts[i].object,
+                                acts[i].trigger_task) for i in range(na)]
+        stays = stays_from_native(lib.ss_search_intervals(handle), ni)
+        ts = [lib.ss_search_task_start(handle)[i] for i in range(nt)]
+        te = [lib.ss_search_task_end(handle)[i] for i in range(nt)]
+        as_ = [lib.ss_search_action_start(handle)[i] for i in range(na)]
+        ae = [lib.ss_search_action_end(handle)[i] for i in range(na)]
+        summary = PlanSummary(
+            duration_seconds=s.sim.makespan_ns * 1e-9, compute_seconds=s.sim.compute_ns * 1e-9,
+            input_wait_seconds=s.sim.input_wait_ns * 1e-9,
+            capacity_wait_seconds=s.sim.capacity_wait_ns * 1e-9,
+            execution_peak_bytes=s.sim.peak_bytes, layout_span_bytes=s.layout_span,
+            fetch_bytes=s.sim.fetch_bytes, evict_bytes=s.sim.evict_bytes,
+            strategy=native.STRATEGIES[s.best_strategy],
+            fetch_rule=native.FETCH_RULES[s.best_fetch_rule],
+            candidates_evaluated=s.candidates_evaluated,
+            candidates_feasible=s.candidates_feasible, repairs_applied=s.repairs_applied,
+            logical_capacity_bytes=s.logical_capacity)
+    finally:
+        lib.ss_search_result_destroy(handle)
+        del keep
+    # ---- reuse dependencies of the device layout
+    sb = [-(-st.bytes // options.alignment) * options.alignment for st in stays]
+    pb, pi = recover_layout_reuse(sb, [st.start_ns for st in stays], [st.end_ns for st in stays],
+                                  [st.offset for st in stays])
+    # ---- spill homes: persistent objects first, then evicted transients by lifetime
+    spill_offsets = [-1] * len(program.objects)
+    cursor = 0
+    for i, o in enumerate(program.objects):
+        if o.persistent:
+            spill_offsets[i] = cursor
+            cursor += -(-o.bytes // 4096) * 4096
+    persistent_end = cursor
+    first_evict, last_fetch = {}, {}
+    for ai, a in enumerate(actions):
+        if program.objects[a.object].persistent:
+            continue
+        if a.kind == "evict":
+            first_evict.setdefault(a.object, as_[ai])
+        elif a.kind == "fetch":
+            last_fetch[a.object] = ae[ai]
+    spilled = sorted(first_evict)
+    if spilled:
+        horizon = max(te) if te else 0
+        offs, span = place_lifetimes(
+            [-(-program.objects[o].bytes // 4096) * 4096 for o in spilled],
+            [first_evict[o] for o in spilled],
+            [max(last_fetch.get(o, horizon), first_evict[o] + 1) for o in spilled], 4096)
+        for o, off in zip(spilled, offs):
+            spill_offsets[o] = persistent_end + off
+        cursor = persistent_end + span
+    if cursor > budgets.spill_bytes:
+        raise PlanningError(f"spill pool needs {cursor / GIB:.2f} GiB, budget is "
+                            f"{budgets.spill_bytes / GIB:.2f} GiB")
+    summary.spill_peak_bytes = cursor
+    summary.workspace_bytes = max((t.workspace_bytes for t in program.tasks), default=0)
+    summary.fixed_device_bytes = budgets.fixed_device_bytes
+    summary.tokens = int(program.metadata.get("tokens", 0))
+    summary.ordering = str(program.metadata.get("ordering", ""))
+    summary.selection = str(program.metadata.get("selection", ""))
+    if summary.duration_seconds > 0:
+        summary.tokens_per_second = summary.tokens / summary.duration_seconds
+    plan = Plan(program, MemorySchedule(actions), stays, spill_offsets, pb, pi, ts, te, as_, ae,
+                device_bytes=max(summary.layout_span_bytes, options.alignment),
+                spill_bytes=max(cursor, 4096),
+                budgets={"device_bytes": budgets.device_bytes, "spill_bytes": budgets.spill_bytes,
+                         "headroom_bytes": budgets.headroom_bytes,
+                         "capacity_bytes": budgets.capacity},
+                summary=summary, communication=communication.to_json())
+    if options.trace:
+        plan.communication["search_trace"] = trace
+    return plan
+
+
+@dataclass
+class SweepResult:
+    best: Plan
+    plans: list[Plan | None]
+    errors: list[str]
+
+    def table(self) -> list[dict]:
+        rows = []
+        for p, e in zip(self.plans, self.errors):
+            if p is None:
+                rows.append({"feasible": False, "error": e.splitlines()[0] if e else ""})
+            else:
+                s = p.summary
+                rows.append({"feasible": True, "ordering": s.ordering, "selection": s.selection,
+                             "seconds": s.duration_seconds, "tokens_per_second": s.tokens_per_second,
+                             "fetch_bytes": s.fetch_bytes, "evict_bytes": s.evict_bytes})
+        return rows
+
+
+def sweep_programs(programs: list[Program], budgets: MemoryBudgets,
+                   communication: CommunicationInfo | None = None,
+                   options: SearchOptions | None = None, threads: int = 4) -> SweepResult:
+    """Plan every candidate program and keep the one with the shortest simulated step."""
+    plans: list[Plan | None] = [None] * len(programs)
+    errors = [""] * len(programs)
+
+    def one(i: int) -> None:
+        try:
+            plans[i] = plan_program(programs[i], budgets, communication, options)
+        except PlanningError as exc:
+            errors[i] = str(exc)
+
+    with concurrent.futures.ThreadPoolExecutor(max_workers=max(1, threads)) as pool:
+        list(pool.map(one, range(len(programs))))
+    feasible = [p for p in plans if p is not None]
+    if not feasible:
+        raise PlanningError("no candidate program fits the budgets:\n" + "\n".join(errors))
+    best = min(feasible, key=lambda p: p.summary.duration_seconds)
+    return SweepResult(best, plans, errors)

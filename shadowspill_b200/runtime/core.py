@@ -1,0 +1,195 @@
+"""Python handle of the native execution runtime.
+
+One ``Runtime`` owns one device pool and one pinned spill pool on one backend
+(``cuda`` through the dlopened CUDA backend, or ``mock`` = host memory with
+real stream threads). It exposes both pools as zero-copy ``torch`` byte tensors,
+admits plans, and drives the step protocol. Reference counterparts:
+packages/engine/src/shadowspill/runtime/core.py:86 (``Runtime``) and
+runtime/bootstrap.py:122 (``install_runtime``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from .. import native
+from ..ir.plan import Plan
+
+
+class RuntimeFailure(RuntimeError):
+    """The runtime's failure latch is set; carries the first recorded failure."""
+
+    def __init__(self, info: dict):
+        self.info = info
+        super().__init__(f"runtime failure: {info.get('message', '')} "
+                         f"(status={native.status_string(info.get('status', 0))}, "
+                         f"task={info.get('task')}, object={info.get('object')}, "
+                         f"action={info.get('action')})")
+
+
+class _CudaBuffer:
+    """Zero-copy bridge from a raw device pointer to ``torch.as_tensor``."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1",
+                                         "data": (ptr, False), "version": 2}
+
+
+@dataclass
+class TransferRates:
+    fetch_solo_bps: float
+    fetch_concurrent_bps: float
+    evict_solo_bps: float
+    evict_concurrent_bps: float
+    fetch_latency_ns: int
+    evict_latency_ns: int
+
+
+class Runtime:
+    def __init__(self, device_bytes: int, spill_bytes: int, backend: str = "cuda",
+                 device_index: int = 0, trace_capacity: int = 0, mock_bps: float = 0.0,
+                 mock_latency_ns: int = 0, numa_node: int = -1):
+        self.lib = native.core()
+        self.backend_name = backend
+        self.device_index = device_index
+        if backend == "mock":
+            self.backend = self.lib.ss_mock_backend_create(float(mock_bps), int(mock_latency_ns))
+        elif backend == "cuda":
+            if not native.CUDA_BACKEND_PATH.exists():
+                from .. import build
+                build.build_core()
+            err = C.create_string_buffer(256)
+            self.backend = self.lib.ss_backend_dlopen(str(native.CUDA_BACKEND_PATH).encode(),
+                                                      device_index, err, 256)
+            if not self.backend:
+                raise RuntimeError(f"cannot open CUDA backend: {err.value.decode()}")
+        else:
+            raise ValueError(f"unknown backend {backend!r}")
+        cfg = native.RuntimeConfig(int(device_bytes), int(spill_bytes), numa_node,
+                                   int(trace_capacity), 1000, 0, 0)
+        handle = native.vp()
+        native.check(self.lib.ss_runtime_create(self.backend, C.byref(cfg), C.byref(handle)),
+                     "ss_runtime_create")
+        self.handle = handle
+        self.device_bytes, self.spill_bytes = int(device_bytes), int(spill_bytes)
+        self._closed = False
+        dbase = self.lib.ss_runtime_device_base(handle) or 0
+        sbase = self.lib.ss_runtime_spill_base(handle) or 0
+        self.device_base, self.spill_base = dbase, sbase
+        if spill_bytes > 0:
+            arr = np.ctypeslib.as_array((C.c_uint8 * int(spill_bytes)).from_address(sbase))
+            self.spill = torch.from_numpy(arr)
+        else:
+            self.spill = torch.empty(0, dtype=torch.uint8)
+        if device_bytes == 0:
+            self.device = torch.empty(0, dtype=torch.uint8)
+        elif backend == "cuda":
+            with torch.cuda.device(device_index):
+                self.device = torch.as_tensor(_CudaBuffer(dbase, int(device_bytes)),
+                                              device=f"cuda:{device_index}")
+        else:
+            arr = np.ctypeslib.as_array((C.c_uint8 * int(device_bytes)).from_address(dbase))
+            self.device = torch.from_numpy(arr)
+        self._plan_keep: dict[int, object] = {}
+
+    # ------------------------------------------------------------------ plans
+    def admit(self, plan: Plan) -> int:
+        desc, keep = plan.to_native_desc()
+        pid = native.i32(0)
+        rc = self.lib.ss_plan_admit(self.handle, C.byref(desc), C.byref(pid))
+        self._raise(rc, "ss_plan_admit")
+        self._plan_keep[pid.value] = keep
+        return pid.value
+
+    def close_plan(self, plan_id: int) -> None:
+        self._raise(self.lib.ss_plan_close(self.handle, plan_id), "ss_plan_close")
+        self._plan_keep.pop(plan_id, None)
+
+    # ------------------------------------------------------------------ step protocol
+    def step_begin(self, plan_id: int, compute_stream: int | None) -> None:
+        self._raise(self.lib.ss_step_begin(self.handle, plan_id, compute_stream), "ss_step_begin")
+
+    def before_task(self, plan_id: int, task: int, n_uses: int) -> list[int]:
+        buf = (native.vp * max(1, n_uses))()
+        self._raise(self.lib.ss_before_task(self.handle, plan_id, task, buf, n_uses),
+                    "ss_before_task")
+        return [int(buf[i] or 0) for i in range(n_uses)]
+
+    def after_task(self, plan_id: int, task: int) -> None:
+        self._raise(self.lib.ss_after_task(self.handle, plan_id, task), "ss_after_task")
+
+    def step_end(self, plan_id: int) -> None:
+        self._raise(self.lib.ss_step_end(self.handle, plan_id), "ss_step_end")
+
+    # ------------------------------------------------------------------ diagnostics
+    def failure(self) -> dict | None:
+        f = native.Failure()
+        if self.lib.ss_runtime_failure(self.handle, C.byref(f)) != native.OK:
+            return None
+        return {"status": f.status, "reason": f.reason, "task": f.task, "object": f.object,
+                "action": f.action, "pool": f.pool, "message": f.message.decode(errors="replace")}
+
+    def latch_failure(self, message: str, status: int = native.FAILED, reason: int = 7) -> None:
+        self.lib.ss_runtime_latch_failure(self.handle, reason, status, message.encode())
+
+    def stats(self) -> dict[str, int]:
+        s = native.RuntimeStats()
+        self.lib.ss_runtime_stats_read(self.handle, C.byref(s))
+        return {n: getattr(s, n) for n, _ in native.RuntimeStats._fields_}
+
+    def trace_begin(self) -> None:
+        native.check(self.lib.ss_trace_begin(self.handle), "ss_trace_begin")
+
+    def trace_end(self) -> list[dict]:
+        self.lib.ss_trace_end(self.handle)
+        cap = 1 << 16
+        buf = (native.TraceEvent * cap)()
+        n = self.lib.ss_trace_read(self.handle, buf, cap)
+        return [{"kind": native.TRACE_KINDS[buf[i].kind], "id": buf[i].a,
+                 "host_ns": buf[i].host_ns, "bytes": buf[i].bytes} for i in range(n)]
+
+    def calibrate(self, nbytes: int = 256 << 20, repeats: int = 3) -> TransferRates:
+        p = native.TransferProfile()
+        native.check(self.lib.ss_calibrate_transfers(self.handle, int(nbytes), repeats, C.byref(p)),
+                     "ss_calibrate_transfers")
+        return TransferRates(p.fetch_solo_bps, p.fetch_concurrent_bps, p.evict_solo_bps,
+                             p.evict_concurrent_bps, p.fetch_latency_ns, p.evict_latency_ns)
+
+    def mock_fail(self, op: str, nth: int) -> None:
+        native.check(self.lib.ss_mock_fail_operation(self.backend, native.OP_KINDS.index(op), nth),
+                     "ss_mock_fail_operation")
+
+    def mock_count(self, op: str) -> int:
+        return self.lib.ss_mock_operation_count(self.backend, native.OP_KINDS.index(op))
+
+    # ------------------------------------------------------------------ lifecycle
+    def close(self) -> None:
+        if self._closed:
+            return
+        self._closed = True
+        self.device = self.spill = None
+        self.lib.ss_runtime_close(self.handle)
+        self.lib.ss_runtime_destroy(self.handle)
+
+    def abandon(self) -> None:
+        """Process-exit path: no drain, no synchronisation."""
+        if not self._closed:
+            self._closed = True
+            self.lib.ss_runtime_abandon(self.handle)
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def _raise(self, rc: int, what: str) -> None:
+        if rc == native.OK:
+            return
+        info = self.failure()
+        if info is not None:
+            raise RuntimeFailure(info)
+        raise native.NativeError(rc, what)

@@ -1,0 +1,83 @@
+"""Planned execution on the mock backend must reproduce the resident trainer."""
+import torch
+
+from shadowspill_b200.communication.info import CommunicationInfo
+from shadowspill_b200.data.synthetic import make_batch, to_device
+from shadowspill_b200.execution.executor import Executor, Hyperparameters
+from shadowspill_b200.execution.resident import ResidentTrainer
+from shadowspill_b200.frontend.capture import BatchGeometry, StepDataOrdering, build_step
+from shadowspill_b200.models.config import preset
+from shadowspill_b200.planning.plan import (MemoryBudgets, PlanningError, SearchOptions,
+                                            plan_program)
+
+
+def _setup(walk="breadth", selection=None, capacity=None, optimizer="stage_interleaved"):
+    cfg = preset("llama3-tiny")
+    geo = BatchGeometry(microbatch_tokens=256, n_microbatches=2, slots=16, mean_seqlen=64)
+    prog, desc = build_step(cfg, geo, StepDataOrdering(walk=walk, optimizer=optimizer),
+                            dtype=torch.float32, selection=selection)
+    total = sum(o.bytes for o in prog.objects)
+    ws = max(t.workspace_bytes for t in prog.tasks)
+    opts = SearchOptions(minimum_object_bytes_evict_eligible=1024, workers=2)
+    if capacity is not None:
+        return cfg, plan_program(prog, MemoryBudgets(capacity, 64 << 20, headroom_bytes=0),
+                                 CommunicationInfo(), opts), desc
+    # the smallest budget (in steps of 5 % of all state) that still plans
+    for pct in range(30, 101, 5):
+        try:
+            plan = plan_program(prog, MemoryBudgets(ws + total * pct // 100, 64 << 20,
+                                                    headroom_bytes=0), CommunicationInfo(), opts)
+            return cfg, plan, desc
+        except PlanningError:
+            continue
+    raise AssertionError("no budget planned")
+
+
+def _batches(cfg, seed=0):
+    return make_batch(seed, vocab=cfg.vocab_size, tokens_per_step=512, microbatch_tokens=256,
+                      median=60, min_len=8, max_len=128, slots=16)
+
+
+def _check_against_resident(walk, selection=None, optimizer="stage_interleaved"):
+    cfg, plan, desc = _setup(walk, selection, optimizer=optimizer)
+    assert plan.summary.fetch_bytes > 0
+    hyper = Hyperparameters(lr=3e-3)
+    ex = Executor(plan, desc, device="cpu", seed=5, hyper=hyper)
+    ex.initialize()
+    ref = ResidentTrainer(cfg, device="cpu", dtype=torch.float32, seed=5, lr=3e-3)
+    for step in range(3):
+        host = _batches(cfg, step)
+        res = ex.run(host)
+        want = ref.step([to_device(m, "cpu") for m in host])
+        assert abs(res.loss - want) < 1e-5 * max(1.0, abs(want)), (step, res.loss, want)
+    got = ex.state_dict()
+    for k, v in ref.state_dict().items():
+        assert torch.allclose(got[k], v, rtol=1e-5, atol=1e-6), k
+    stats = ex.rt.stats()
+    assert stats["steps"] == 3 and stats["fetches"] > 0
+    ex.close()
+
+
+def test_breadth_recompute_matches_resident():
+    _check_against_resident("breadth")
+
+
+def test_depth_tail_matches_resident():
+    _check_against_resident("depth", optimizer="tail")
+
+
+def test_saved_variants_match_resident():
+    _check_against_resident("breadth", selection={1: "save", 2: "save_attention"})
+
+
+def test_steady_state_creates_no_events():
+    cfg, plan, desc = _setup()
+    ex = Executor(plan, desc, device="cpu", seed=1)
+    ex.initialize()
+    ex.run(_batches(cfg))
+    before = ex.rt.stats()
+    ex.run(_batches(cfg, 1))
+    after = ex.rt.stats()
+    assert after["events_created"] == before["events_created"]
+    assert after["host_allocations"] == before["host_allocations"]
+    ex.close()
