@@ -53,6 +53,112 @@ class InvocationResult:
     metrics: dict[str, float] = field(default_factory=dict)
 
 
+class TaskRunner:
+    """Turns a program task plus the byte ranges of its objects into the stage
+    call it stands for. Shared by the executor (ranges inside the device pool)
+    and the profiler (ranges allocated ad hoc)."""
+
+    def __init__(self, program, desc: TrainingDescription, hyper: Hyperparameters, seed: int,
+                 stochastic_rounding: bool):
+        self.program, self.desc, self.hyper, self.seed = program, desc, hyper, seed
+        self.sr = stochastic_rounding and desc.dtype == torch.bfloat16
+        self.stages = build_stages(desc.cfg)
+        meta = program.metadata
+        self.T, self.n_mb, self.slots = meta["microbatch_tokens"], meta["n_microbatches"], meta["slots"]
+        self.batch_layout_, _ = batch_layout(self.T, self.slots)
+        self.max_seqlen = [2] * self.n_mb
+        self.uses = [program.sorted_uses(t) for t in range(len(program.tasks))]
+        self.completed_updates = 0
+        self.accumulated = 0
+        self.grad_seen: set[int] = set()
+        self.param_offsets, off = {}, 0
+        for si, st in enumerate(self.stages):
+            for p in st.params:
+                self.param_offsets[(si, p.name)] = off
+                off += (p.numel + 7) // 8 * 8
+
+    def _batch_meta(self, flat: torch.Tensor, m: int) -> BatchMeta:
+        parts = {}
+        for name, (off, count, dt) in self.batch_layout_.items():
+            tdt = _TORCH_DT[dt]
+            parts[name] = flat[off:off + count * tdt.itemsize].view(tdt)
+        return BatchMeta(parts["tokens"], parts["targets"], parts["weights"], parts["positions"],
+                         parts["cu_seqlens"], self.max_seqlen[m])
+
+    def bind(self, task: int, flats: list[torch.Tensor]) -> dict[str, object]:
+        """Role -> tensor views for one task over the flat byte tensors of its uses
+        (in ``Program.sorted_uses`` order)."""
+        t = self.program.tasks[task]
+        st = self.stages[t.stage]
+        out: dict[str, object] = {}
+        for u, flat in zip(self.uses[task], flats):
+            if u.role in ("params", "m", "v"):
+                out[u.role] = st.views(flat, self.desc.dtype)
+            elif u.role == "grads":
+                out[u.role] = st.views(flat, self.desc.grad_dtype, torch.float32)
+            elif u.role in ("x", "y", "dx"):
+                out[u.role] = flat.view(self.desc.dtype).view(self.T, self.desc.cfg.d_model)
+            elif u.role == "batch":
+                out["batch_flat"] = flat
+            elif u.role == "loss":
+                out[u.role] = flat[:4].view(torch.float32)
+            elif u.role == "saved":
+                lay, _ = saved_layout(st, self.T, t.variant, self.desc.dtype)
+                sv = {}
+                for name, shape, dt, off in lay:
+                    n = int(np.prod(shape)) * dt.itemsize
+                    sv[name] = flat[off:off + n].view(dt).view(shape)
+                out[u.role] = sv
+            out[f"{u.role}.mode"] = u.mode
+        return out
+
+    # ------------------------------------------------------------------ task bodies
+    def run_task(self, task: int, B: dict[str, object]) -> None:
+        t = self.program.tasks[task]
+        st = self.stages[t.stage]
+        meta = self._batch_meta(B["batch_flat"], t.microbatch) if "batch_flat" in B else None
+        if t.kind == "forward":
+            keep = st.SAVE_SETS.get(t.variant, ()) if "saved" in B else ()
+            _, saved = st.forward(B["params"], B.get("x"), meta, keep, out=B["y"])
+            if "saved" in B:
+                for name, dst in B["saved"].items():
+                    dst.copy_(saved[name].reshape(dst.shape))
+        elif t.kind == "head":
+            train = t.variant == "train"
+            first = self._first(t.stage, B)
+            st.loss_and_backward(B["params"], B.get("grads"), B["x"], meta, B["loss"], first,
+                                 dx=B.get("dx"), train=train, grad_scale=1.0)
+        elif t.kind == "backward":
+            first = self._first(t.stage, B)
+            saved = dict(B["saved"]) if "saved" in B else {}
+            if "attn" in saved:
+                saved["attn"] = saved["attn"]
+            st.backward(B["params"], B["grads"], B.get("x"), B["dx"], meta, saved, first)
+        elif t.kind == "optimizer":
+            self._optimizer(t.stage, B)
+        else:
+            raise RuntimeError(f"task kind {t.kind!r} has no executor")
+
+    def _first(self, stage: int, B) -> bool:
+        if self.desc.mode == "step":
+            return B.get("grads.mode") == "create"
+        fresh = self.accumulated == 0 and stage not in self.grad_seen
+        self.grad_seen.add(stage)
+        return fresh
+
+    def _optimizer(self, stage: int, B) -> None:
+        st, h = self.stages[stage], self.hyper
+        for p in st.params:
+            if not p.trainable:
+                continue
+            F.adamw_(B["params"][p.name].view(-1), B["grads"][p.name].view(-1),
+                     B["m"][p.name].view(-1), B["v"][p.name].view(-1), lr=h.lr, beta1=h.beta1,
+                     beta2=h.beta2, eps=h.eps, weight_decay=h.weight_decay,
+                     step=self.completed_updates + 1, grad_scale=h.grad_scale, seed=self.seed,
+                     offset=self.param_offsets[(stage, p.name)], stochastic_param=self.sr,
+                     stochastic_state=self.sr)
+
+
 class Executor:
     def __init__(self, plan: Plan, desc: TrainingDescription, *, device: str = "cuda",
                  device_index: int = 0, seed: int = 0, hyper: Hyperparameters | None = None,
@@ -65,10 +171,8 @@ class Executor:
         self.torch_device = torch.device(f"cuda:{device_index}") if self.cuda else torch.device("cpu")
         self.hyper = hyper or Hyperparameters()
         self.seed = seed
-        self.sr = stochastic_rounding and desc.dtype == torch.bfloat16
-        self.stages = build_stages(desc.cfg)
-        self.completed_updates = 0
-        self.accumulated = 0
+        self.runner = TaskRunner(plan.program, desc, self.hyper, seed, stochastic_rounding)
+        self.stages = self.runner.stages
         if self.cuda:
             torch.cuda.set_device(device_index)
             from ..ops import _lib
@@ -78,15 +182,11 @@ class Executor:
         self.plan_id = self.rt.admit(plan)
         self.stream = torch.cuda.Stream(device=self.torch_device) if self.cuda else None
         self._views: dict[tuple[int, int], object] = {}
-        self._uses = [self.program.sorted_uses(t) for t in range(len(self.program.tasks))]
-        meta = self.program.metadata
-        self.T, self.n_mb, self.slots = meta["microbatch_tokens"], meta["n_microbatches"], meta["slots"]
-        self._batch_layout, _ = batch_layout(self.T, self.slots)
-        self._max_seqlen = [2] * self.n_mb
+        self._uses = self.runner.uses
+        self.T, self.n_mb, self.slots = self.runner.T, self.runner.n_mb, self.runner.slots
+        self._batch_layout = self.runner.batch_layout_
         self._obj = {o.name: i for i, o in enumerate(self.program.objects)}
         self._loss_obj = self._obj["loss"]
-        self._param_offsets = self._global_param_offsets()
-        self._timing_events = None
         self.closed = False
 
     # ------------------------------------------------------------------ state in the spill pool
@@ -96,28 +196,32 @@ class Executor:
             raise KeyError(f"{self.program.objects[obj].name} has no spill home")
         return self.rt.spill[off:off + self.program.objects[obj].bytes]
 
-    def _global_param_offsets(self) -> dict[tuple[int, str], int]:
-        out, off = {}, 0
-        for si, st in enumerate(self.stages):
-            for p in st.params:
-                out[(si, p.name)] = off
-                off += (p.numel + 7) // 8 * 8
-        return out
-
-    def initialize(self, seed: int | None = None) -> None:
-        """Random initialisation straight into the spill homes (seed-only, so the
-        result does not depend on plan, budget or sharding); moments start at zero."""
-        gen = torch.Generator().manual_seed(self.seed if seed is None else seed)
+    def initialize(self, seed: int | None = None, on_device: bool | None = None) -> None:
+        """Random initialisation of the spill homes (seed-only, so the result does
+        not depend on plan, budget or sharding); moments start at zero.
+        ``on_device`` draws each stage on the GPU and copies it down, which is what
+        makes multi-billion-parameter models initialise in seconds; the CPU
+        generator is the default off-GPU and gives the same values everywhere."""
+        on_device = self.cuda if on_device is None else on_device
+        seed = self.seed if seed is None else seed
+        gen = (torch.Generator(device=self.torch_device) if on_device else torch.Generator())
+        gen.manual_seed(seed)
         for si, st in enumerate(self.stages):
             w = self.spill_view(self._obj[f"{st.name}.weights"])
-            w.zero_()
-            st.init_(st.views(w, self.desc.dtype), gen)
+            if on_device:
+                flat = torch.zeros(w.numel(), dtype=torch.uint8, device=self.torch_device)
+                st.init_(st.views(flat, self.desc.dtype), gen)
+                w.copy_(flat)
+                del flat
+            else:
+                w.zero_()
+                st.init_(st.views(w, self.desc.dtype), gen)
             for suffix in ("exp_avg", "exp_avg_sq", "gradients"):
                 name = f"{st.name}.{suffix}"
                 if name in self._obj and self.plan.spill_offsets[self._obj[name]] >= 0:
                     self.spill_view(self._obj[name]).zero_()
-        self.completed_updates = 0
-        self.accumulated = 0
+        self.runner.completed_updates = 0
+        self.runner.accumulated = 0
 
     def named_tensors(self):
         """Yields ``(name, tensor view in the spill pool)`` for every persistent
@@ -167,7 +271,7 @@ class Executor:
                 else:
                     view[:] = src
                 total += view.nbytes
-            self._max_seqlen[m] = int(mb.max_seqlen)
+            self.runner.max_seqlen[m] = int(mb.max_seqlen)
         self.spill_view(self._loss_obj).zero_()
         return total
 
@@ -176,92 +280,27 @@ class Executor:
         off = ptr - self.rt.device_base
         return self.rt.device[off:off + nbytes]
 
-    def _batch_meta(self, flat: torch.Tensor, m: int) -> BatchMeta:
-        parts = {}
-        for name, (off, count, dt) in self._batch_layout.items():
-            tdt = _TORCH_DT[dt]
-            parts[name] = flat[off:off + count * tdt.itemsize].view(tdt)
-        return BatchMeta(parts["tokens"], parts["targets"], parts["weights"], parts["positions"],
-                         parts["cu_seqlens"], self._max_seqlen[m])
-
     def _bind(self, task: int, ptrs: list[int]) -> dict[str, object]:
-        """Role -> tensor views for one task (cached: offsets are fixed by the plan)."""
+        """Views for one task, cached: the plan fixes every offset."""
         key = (task, hash(tuple(ptrs)))
         hit = self._views.get(key)
-        if hit is not None:
-            return hit
-        t = self.program.tasks[task]
-        st = self.stages[t.stage]
-        out: dict[str, object] = {}
-        for u, ptr in zip(self._uses[task], ptrs):
-            obj = self.program.objects[u.object]
-            flat = self._device_view(ptr, obj.bytes)
-            if u.role in ("params", "m", "v"):
-                out[u.role] = st.views(flat, self.desc.dtype)
-            elif u.role == "grads":
-                out[u.role] = st.views(flat, self.desc.grad_dtype, torch.float32)
-            elif u.role in ("x", "y", "dx"):
-                out[u.role] = flat.view(self.desc.dtype).view(self.T, self.desc.cfg.d_model)
-            elif u.role == "batch":
-                out["batch_flat"] = flat
-            elif u.role == "loss":
-                out[u.role] = flat[:4].view(torch.float32)
-            elif u.role == "saved":
-                lay, _ = saved_layout(st, self.T, t.variant, self.desc.dtype)
-                sv = {}
-                for name, shape, dt, off in lay:
-                    n = int(np.prod(shape)) * dt.itemsize
-                    sv[name] = flat[off:off + n].view(dt).view(shape)
-                out[u.role] = sv
-            out[f"{u.role}.mode"] = u.mode
-        self._views[key] = out
-        return out
+        if hit is None:
+            flats = [self._device_view(ptr, self.program.objects[u.object].bytes)
+                     for u, ptr in zip(self._uses[task], ptrs)]
+            hit = self._views[key] = self.runner.bind(task, flats)
+        return hit
 
-    # ------------------------------------------------------------------ task bodies
-    def _run_task(self, task: int, B: dict[str, object]) -> None:
-        t = self.program.tasks[task]
-        st = self.stages[t.stage]
-        meta = self._batch_meta(B["batch_flat"], t.microbatch) if "batch_flat" in B else None
-        if t.kind == "forward":
-            keep = st.SAVE_SETS.get(t.variant, ()) if "saved" in B else ()
-            _, saved = st.forward(B["params"], B.get("x"), meta, keep, out=B["y"])
-            if "saved" in B:
-                for name, dst in B["saved"].items():
-                    dst.copy_(saved[name].reshape(dst.shape))
-        elif t.kind == "head":
-            train = t.variant == "train"
-            first = self._first(t.stage, B)
-            st.loss_and_backward(B["params"], B.get("grads"), B["x"], meta, B["loss"], first,
-                                 dx=B.get("dx"), train=train, grad_scale=1.0)
-        elif t.kind == "backward":
-            first = self._first(t.stage, B)
-            saved = dict(B["saved"]) if "saved" in B else {}
-            if "attn" in saved:
-                saved["attn"] = saved["attn"]
-            st.backward(B["params"], B["grads"], B.get("x"), B["dx"], meta, saved, first)
-        elif t.kind == "optimizer":
-            self._optimizer(t.stage, B)
-        else:
-            raise RuntimeError(f"task kind {t.kind!r} has no executor")
+    @property
+    def completed_updates(self) -> int:
+        return self.runner.completed_updates
 
-    def _first(self, stage: int, B) -> bool:
-        if self.desc.mode == "step":
-            return B.get("grads.mode") == "create"
-        fresh = self.accumulated == 0 and stage not in self._grad_seen
-        self._grad_seen.add(stage)
-        return fresh
+    @completed_updates.setter
+    def completed_updates(self, value: int) -> None:
+        self.runner.completed_updates = value
 
-    def _optimizer(self, stage: int, B) -> None:
-        st, h = self.stages[stage], self.hyper
-        for p in st.params:
-            if not p.trainable:
-                continue
-            F.adamw_(B["params"][p.name].view(-1), B["grads"][p.name].view(-1),
-                     B["m"][p.name].view(-1), B["v"][p.name].view(-1), lr=h.lr, beta1=h.beta1,
-                     beta2=h.beta2, eps=h.eps, weight_decay=h.weight_decay,
-                     step=self.completed_updates + 1, grad_scale=h.grad_scale, seed=self.seed,
-                     offset=self._param_offsets[(stage, p.name)], stochastic_param=self.sr,
-                     stochastic_state=self.sr)
+    @property
+    def accumulated(self) -> int:
+        return self.runner.accumulated
 
     # ------------------------------------------------------------------ run
     def run(self, batch: list[HostMicrobatch], *, trace: bool = False,
@@ -270,7 +309,7 @@ class Executor:
             raise RuntimeError("executor is closed")
         t0 = time.perf_counter()
         h2d = self.stage_inputs(batch)
-        self._grad_seen: set[int] = set()
+        self.runner.grad_seen = set()
         if trace:
             self.rt.trace_begin()
         n_tasks = len(self.program.tasks)
@@ -293,7 +332,7 @@ class Executor:
                     events[task][0].record(self.stream)
                 elif not self.cuda and time_tasks:
                     tt = time.perf_counter()
-                self._run_task(task, B)
+                self.runner.run_task(task, B)
                 if events:
                     events[task][1].record(self.stream)
                 elif not self.cuda and time_tasks:
@@ -312,15 +351,15 @@ class Executor:
             if events:
                 task_seconds = [a.elapsed_time(b) * 1e-3 for a, b in events]
         if self.desc.mode == "step":
-            self.completed_updates += 1
+            self.runner.completed_updates += 1
         elif self.desc.mode == "forward_backward":
-            self.accumulated += 1
+            self.runner.accumulated += 1
         tr = self.rt.trace_end() if trace else []
         return InvocationResult(loss, self.T * self.n_mb, time.perf_counter() - t0, device_seconds,
                                 h2d, 4, task_seconds if time_tasks else [], tr)
 
     def discard_gradients(self) -> None:
-        self.accumulated = 0
+        self.runner.accumulated = 0
 
     def close(self) -> None:
         if self.closed:

@@ -102,6 +102,8 @@ class Stage:
                 t.fill_(1.0)
             elif p.init == "zeros":
                 t.zero_()
+            elif t.is_cuda:
+                t.normal_(0.0, p.std, generator=generator)   # device generator, large models
             else:
                 tmp = torch.empty(p.shape, dtype=torch.float32)
                 tmp.normal_(0.0, p.std, generator=generator)

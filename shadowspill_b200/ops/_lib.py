@@ -110,6 +110,15 @@ def check_status(device: torch.device | int | None = None) -> None:
         raise RuntimeError(f"kernel reported: {STATUS_NAMES.get(code, code)} (code {code})")
 
 
+# kernels launched by one successful call of each launcher (attention backward:
+# delta + dQ + dKV; sum of squares: partials + final)
+_KERNELS_PER_CALL = {"ss_attn_bwd": 3, "ss_sumsq": 2}
+launch_count = 0
+
+
 def check(rc: int, what: str) -> None:
+    """Raises on a failed launcher; counts the kernels a successful one enqueued."""
+    global launch_count
     if rc != 0:
         raise RuntimeError(f"{what} failed with code {rc}")
+    launch_count += _KERNELS_PER_CALL.get(what, 1)

@@ -1,0 +1,165 @@
+"""In-process training composition: build -> profile -> calibrate -> plan -> execute.
+
+``TrainingSession`` is what one worker process runs for one rank: it resolves a
+``TrainingSetup`` into a model configuration and batch geometry, builds the
+candidate programs (walk orders x save/recompute selections), profiles their
+distinct tasks on the device, calibrates the host link, plans every candidate
+under the memory budget and keeps the fastest, then admits that plan into an
+``Executor``. ``step`` takes the global batch as host arrays and returns the
+host-side result. The service layer wraps exactly this object per worker.
+
+Reference: packages/engine/src/shadowspill/training/preparation/phases/operations.py
+(build :39, profile :92, communicate :129, plan :199) and
+training/worker/runtime.py:195 (``PreparedWorker.open``).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+
+import torch
+
+from ..communication.info import CommunicationInfo
+from ..data.synthetic import HostMicrobatch
+from ..execution.executor import Executor, Hyperparameters, InvocationResult
+from ..frontend.capture import (BatchGeometry, StepDataOrdering, build_forward, build_step,
+                                recompute_share_selections)
+from ..models.config import DecoderConfig, preset
+from ..planning.plan import (MemoryBudgets, PlanningError, SearchOptions, plan_program,
+                             sweep_programs)
+from ..profiling.measure import Profiles, apply_profiles, measure_program
+from ..runtime.core import Runtime
+
+GIB = 1 << 30
+
+
+@dataclass
+class TrainingSetup:
+    model: str | DecoderConfig = "llama3-8b"
+    device_gib: float = 24.0
+    spill_gib: float = 128.0
+    tokens_per_step: int = 65536          # per worker
+    microbatch_tokens: int = 8192
+    slots: int = 0                        # 0 = derived from the microbatch size
+    mean_seqlen: float = 2048.0
+    lr: float = 1e-4
+    beta1: float = 0.9
+    beta2: float = 0.95
+    eps: float = 1e-8
+    weight_decay: float = 0.0
+    seed: int = 0
+    dtype: str = "bfloat16"
+    stochastic_rounding: bool = True
+    device: str = "cuda"
+    device_index: int = 0
+    rank: int = 0
+    world_size: int = 1
+    walks: tuple[str, ...] = ("breadth",)
+    recompute_shares: tuple[int, ...] = (100,)
+    saved_variant: str = "save_attention"
+    profile: bool = True
+    calibrate: bool = True
+    search: SearchOptions = field(default_factory=SearchOptions)
+    trace_capacity: int = 0
+
+
+_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+class TrainingSession:
+    def __init__(self, setup: TrainingSetup, log=None):
+        self.setup = setup
+        self.log = log or (lambda msg: None)
+        self.cfg = setup.model if isinstance(setup.model, DecoderConfig) else preset(setup.model)
+        self.dtype = _DTYPES[setup.dtype]
+        cuda = setup.device == "cuda"
+        if setup.tokens_per_step % setup.microbatch_tokens:
+            raise ValueError("tokens_per_step must be a multiple of microbatch_tokens")
+        self.slots = setup.slots or max(16, setup.microbatch_tokens // 32 + 1)
+        self.geometry = BatchGeometry(setup.microbatch_tokens,
+                                      setup.tokens_per_step // setup.microbatch_tokens,
+                                      self.slots, setup.mean_seqlen)
+        self.budgets = MemoryBudgets.from_gib(setup.device_gib, setup.spill_gib)
+        self.timings: dict[str, float] = {}
+        # ---- build candidates
+        t0 = time.perf_counter()
+        selections = recompute_share_selections(self.cfg, setup.recompute_shares, setup.saved_variant)
+        candidates = []
+        for walk in setup.walks:
+            for sel in selections:
+                order = StepDataOrdering(walk=walk, optimizer="stage_interleaved" if walk == "breadth" else "tail")
+                candidates.append(build_step(self.cfg, self.geometry, order, dtype=self.dtype,
+                                             selection=sel))
+        self.timings["build"] = time.perf_counter() - t0
+        # ---- profile distinct tasks once
+        t0 = time.perf_counter()
+        self.profiles = Profiles()
+        if setup.profile:
+            dev = f"cuda:{setup.device_index}" if cuda else "cpu"
+            for prog, desc in candidates:
+                missing = {t.profile_key for t in prog.tasks} - set(self.profiles.tasks)
+                if missing:
+                    got = measure_program(prog, desc, dev, keys=missing)
+                    self.profiles.tasks.update(got.tasks)
+                    self.profiles.device = got.device
+                apply_profiles(prog, self.profiles)
+            if cuda:
+                torch.cuda.empty_cache()
+        self.timings["profile"] = time.perf_counter() - t0
+        # ---- host link calibration
+        t0 = time.perf_counter()
+        self.communication = CommunicationInfo(world_size=setup.world_size)
+        if setup.calibrate and cuda:
+            probe = 256 << 20
+            with Runtime(2 * probe, 2 * probe, "cuda", setup.device_index) as rt:
+                r = rt.calibrate(probe, 3)
+            self.communication = CommunicationInfo(
+                r.fetch_solo_bps, r.fetch_concurrent_bps, r.evict_solo_bps, r.evict_concurrent_bps,
+                r.fetch_latency_ns, r.evict_latency_ns, world_size=setup.world_size,
+                source="calibrated")
+        self.timings["communication"] = time.perf_counter() - t0
+        # ---- plan
+        t0 = time.perf_counter()
+        sweep = sweep_programs([p for p, _ in candidates], self.budgets, self.communication,
+                               setup.search)
+        self.sweep = sweep
+        self.plan = sweep.best
+        self.desc = next(d for p, d in candidates if p is self.plan.program)
+        self.timings["plan"] = time.perf_counter() - t0
+        self.log(f"plan: {self.plan.summary.ordering} {self.plan.summary.selection} "
+                 f"simulated {self.plan.summary.duration_seconds * 1e3:.1f} ms")
+        # ---- executor (caps the torch allocator to the planned workspace)
+        t0 = time.perf_counter()
+        if cuda:
+            total = torch.cuda.get_device_properties(setup.device_index).total_memory
+            cap = self.plan.summary.workspace_bytes + (256 << 20)
+            torch.cuda.set_per_process_memory_fraction(min(1.0, cap / total), setup.device_index)
+        hyper = Hyperparameters(setup.lr, setup.beta1, setup.beta2, setup.eps, setup.weight_decay)
+        self.executor = Executor(self.plan, self.desc, device=setup.device,
+                                 device_index=setup.device_index, seed=setup.seed, hyper=hyper,
+                                 stochastic_rounding=setup.stochastic_rounding,
+                                 trace_capacity=setup.trace_capacity)
+        self.executor.initialize()
+        self.timings["open"] = time.perf_counter() - t0
+        if cuda:
+            torch.cuda.reset_peak_memory_stats(setup.device_index)
+
+    # ------------------------------------------------------------------ operations
+    def step(self, batch: list[HostMicrobatch], **kw) -> InvocationResult:
+        return self.executor.run(batch, **kw)
+
+    def peak_device_bytes(self) -> int:
+        """Device pool plus the torch allocator's peak reservation since opening."""
+        extra = 0
+        if self.setup.device == "cuda":
+            extra = torch.cuda.max_memory_reserved(self.setup.device_index)
+        return self.plan.device_bytes + extra
+
+    def write_plan_report(self, directory: str) -> None:
+        from ..reporting.write import write_report
+        write_report(self.plan, directory)
+
+    def close(self) -> None:
+        self.executor.close()
+        if self.setup.device == "cuda":
+            torch.cuda.set_per_process_memory_fraction(1.0, self.setup.device_index)
