@@ -232,6 +232,7 @@ typedef struct ss_runtime_config {
   int64_t worker_poll_ns;
   int32_t max_objects;
   int32_t event_pool;          /* dependency events reserved at creation */
+  void* external_device_base;  /* caller-owned device pool (e.g. symmetric memory); NULL = allocate */
 } ss_runtime_config;
 
 typedef struct ss_failure {

@@ -72,6 +72,7 @@ struct ss_runtime {
   ss_backend* be = nullptr;
   ss_runtime_config cfg{};
   void* device_base = nullptr;
+  bool device_external = false;
   void* spill_base = nullptr;
   void* fetch_stream = nullptr;
   void* evict_stream = nullptr;
@@ -259,8 +260,12 @@ int ss_runtime_create(ss_backend* backend, const ss_runtime_config* config, ss_r
   rt->cfg = *config;
   if (rt->cfg.worker_poll_ns <= 0) rt->cfg.worker_poll_ns = 1000;
   int rc = SS_OK;
-  if (config->device_bytes > 0)
+  if (config->external_device_base != nullptr) {
+    rt->device_base = config->external_device_base;
+    rt->device_external = true;
+  } else if (config->device_bytes > 0) {
     rc = backend->device_alloc(backend->self, static_cast<size_t>(config->device_bytes), &rt->device_base);
+  }
   if (rc == SS_OK && config->spill_bytes > 0) {
     rc = backend->host_alloc(backend->self, static_cast<size_t>(config->spill_bytes),
                              config->numa_node, &rt->spill_base);
@@ -270,7 +275,7 @@ int ss_runtime_create(ss_backend* backend, const ss_runtime_config* config, ss_r
   if (rc == SS_OK) rc = backend->stream_create(backend->self, &rt->evict_stream);
   if (rc != SS_OK) {
     if (rt->fetch_stream) backend->stream_destroy(backend->self, rt->fetch_stream);
-    if (rt->device_base) backend->device_free(backend->self, rt->device_base);
+    if (rt->device_base && !rt->device_external) backend->device_free(backend->self, rt->device_base);
     if (rt->spill_base) backend->host_free(backend->self, rt->spill_base, static_cast<size_t>(config->spill_bytes));
     delete rt;
     return rc;
@@ -301,7 +306,7 @@ int ss_runtime_close(ss_runtime* rt) {
   rt->plans.clear();
   be->stream_destroy(be->self, rt->fetch_stream);
   be->stream_destroy(be->self, rt->evict_stream);
-  if (rt->device_base) be->device_free(be->self, rt->device_base);
+  if (rt->device_base && !rt->device_external) be->device_free(be->self, rt->device_base);
   if (rt->spill_base) be->host_free(be->self, rt->spill_base, static_cast<size_t>(rt->cfg.spill_bytes));
   rt->device_base = rt->spill_base = nullptr;
   return rt->failed.load() ? SS_FAILED : SS_OK;

@@ -59,8 +59,10 @@ class TaskRunner:
     and the profiler (ranges allocated ad hoc)."""
 
     def __init__(self, program, desc: TrainingDescription, hyper: Hyperparameters, seed: int,
-                 stochastic_rounding: bool):
+                 stochastic_rounding: bool, collectives=None):
         self.program, self.desc, self.hyper, self.seed = program, desc, hyper, seed
+        self.collectives = collectives
+        self.world = desc.world_size
         self.sr = stochastic_rounding and desc.dtype == torch.bfloat16
         self.stages = build_stages(desc.cfg)
         meta = program.metadata
@@ -92,8 +94,12 @@ class TaskRunner:
         st = self.stages[t.stage]
         out: dict[str, object] = {}
         for u, flat in zip(self.uses[task], flats):
-            if u.role in ("params", "m", "v"):
-                out[u.role] = st.views(flat, self.desc.dtype)
+            obj = self.program.objects[u.object]
+            if u.role in ("params", "m", "v", "shard"):
+                if obj.sharding == "sharded":
+                    out[u.role] = st.shard_views(flat, self.desc.dtype, self.world)
+                else:
+                    out[u.role] = st.views(flat, self.desc.dtype)
             elif u.role == "grads":
                 out[u.role] = st.views(flat, self.desc.grad_dtype, torch.float32)
             elif u.role in ("x", "y", "dx"):
@@ -133,9 +139,18 @@ class TaskRunner:
             saved = dict(B["saved"]) if "saved" in B else {}
             if "attn" in saved:
                 saved["attn"] = saved["attn"]
-            st.backward(B["params"], B["grads"], B.get("x"), B["dx"], meta, saved, first)
+            st.backward(B.get("params"), B["grads"], B.get("x"), B["dx"], meta, saved, first)
         elif t.kind == "optimizer":
-            self._optimizer(t.stage, B)
+            if t.variant == "adamw_dp":
+                self._optimizer_sharded(t.stage, B)
+            else:
+                self._optimizer(t.stage, B)
+        elif t.kind == "collective" and t.variant == "allgather":
+            coll = self.collectives
+            coll.barrier_begin()          # every rank's shard has landed
+            for p in st.params:
+                coll.all_gather(B["shard"][p.name], B["params"][p.name].view(-1))
+            coll.barrier_end()            # every rank is done reading this rank's shard
         else:
             raise RuntimeError(f"task kind {t.kind!r} has no executor")
 
@@ -145,6 +160,21 @@ class TaskRunner:
         fresh = self.accumulated == 0 and stage not in self.grad_seen
         self.grad_seen.add(stage)
         return fresh
+
+    def _optimizer_sharded(self, stage: int, B) -> None:
+        """Gradient reduce-scatter fused with the AdamW update of the owned shards."""
+        st, h, coll = self.stages[stage], self.hyper, self.collectives
+        coll.barrier_begin()              # every rank's gradients for this stage are complete
+        for p in st.params:
+            if not p.trainable:
+                continue
+            coll.reduce_scatter_adamw(
+                B["grads"][p.name].view(-1), B["params"][p.name], B["m"][p.name], B["v"][p.name],
+                offset=self.param_offsets[(stage, p.name)], lr=h.lr, beta1=h.beta1, beta2=h.beta2,
+                eps=h.eps, weight_decay=h.weight_decay, step=self.completed_updates + 1,
+                grad_scale=h.grad_scale, seed=self.seed, stochastic_param=self.sr,
+                stochastic_state=self.sr)
+        coll.barrier_end()                # peers finished reading this rank's gradients
 
     def _optimizer(self, stage: int, B) -> None:
         st, h = self.stages[stage], self.hyper
@@ -163,7 +193,9 @@ class Executor:
     def __init__(self, plan: Plan, desc: TrainingDescription, *, device: str = "cuda",
                  device_index: int = 0, seed: int = 0, hyper: Hyperparameters | None = None,
                  stochastic_rounding: bool = True, trace_capacity: int = 0,
-                 mock_bps: float = 0.0):
+                 mock_bps: float = 0.0, collectives: str = "auto"):
+        """``collectives``: ``peer`` (own kernels over a symmetric device pool),
+        ``dist`` (torch.distributed: NCCL or gloo) or ``auto`` (peer on GPUs)."""
         self.plan, self.desc = plan, desc
         self.program = plan.program
         self.cuda = device == "cuda"
@@ -171,14 +203,27 @@ class Executor:
         self.torch_device = torch.device(f"cuda:{device_index}") if self.cuda else torch.device("cpu")
         self.hyper = hyper or Hyperparameters()
         self.seed = seed
-        self.runner = TaskRunner(plan.program, desc, self.hyper, seed, stochastic_rounding)
+        self.world, self.rank = desc.world_size, desc.rank
+        pool = coll = None
+        if self.world > 1:
+            from ..parallel import collectives as pc
+            mode = ("peer" if device == "cuda" else "dist") if collectives == "auto" else collectives
+            if mode == "peer":
+                torch.cuda.set_device(device_index)
+                pool = pc.allocate_symmetric_pool(plan.device_bytes, self.torch_device)
+                coll = pc.PeerCollectives(pool)
+            else:
+                coll = pc.DistCollectives()
+        self.collectives = coll
+        self.runner = TaskRunner(plan.program, desc, self.hyper, seed, stochastic_rounding, coll)
         self.stages = self.runner.stages
         if self.cuda:
             torch.cuda.set_device(device_index)
             from ..ops import _lib
             _lib.lib()   # fail loudly if the kernel library is missing
         self.rt = Runtime(plan.device_bytes, plan.spill_bytes, "cuda" if self.cuda else "mock",
-                          device_index, trace_capacity=trace_capacity, mock_bps=mock_bps)
+                          device_index, trace_capacity=trace_capacity, mock_bps=mock_bps,
+                          device_pool=pool)
         self.plan_id = self.rt.admit(plan)
         self.stream = torch.cuda.Stream(device=self.torch_device) if self.cuda else None
         self._views: dict[tuple[int, int], object] = {}
@@ -208,14 +253,28 @@ class Executor:
         gen.manual_seed(seed)
         for si, st in enumerate(self.stages):
             w = self.spill_view(self._obj[f"{st.name}.weights"])
-            if on_device:
-                flat = torch.zeros(w.numel(), dtype=torch.uint8, device=self.torch_device)
-                st.init_(st.views(flat, self.desc.dtype), gen)
-                w.copy_(flat)
-                del flat
-            else:
+            _, full_bytes = st.layout(self.desc.dtype)
+            dev = self.torch_device if on_device else torch.device("cpu")
+            if self.world == 1 and not on_device:
                 w.zero_()
                 st.init_(st.views(w, self.desc.dtype), gen)
+            else:
+                # every rank draws the whole stage from the same seed, then keeps its slices
+                flat = torch.zeros(full_bytes, dtype=torch.uint8, device=dev)
+                full = st.views(flat, self.desc.dtype)
+                st.init_(full, gen)
+                if self.world == 1:
+                    w.copy_(flat)
+                else:
+                    w.zero_()
+                    shards = st.shard_views(w, self.desc.dtype, self.world)
+                    for p in st.params:
+                        src, dst = full[p.name].reshape(-1), shards[p.name]
+                        lo = self.rank * dst.numel()
+                        hi = min(src.numel(), lo + dst.numel())
+                        if hi > lo:
+                            dst[:hi - lo].copy_(src[lo:hi])
+                del flat
             for suffix in ("exp_avg", "exp_avg_sq", "gradients"):
                 name = f"{st.name}.{suffix}"
                 if name in self._obj and self.plan.spill_offsets[self._obj[name]] >= 0:
@@ -231,7 +290,11 @@ class Executor:
                 name = f"{st.name}.{kind}"
                 if name not in self._obj:
                     continue
-                views = st.views(self.spill_view(self._obj[name]), self.desc.dtype)
+                flat = self.spill_view(self._obj[name])
+                if self.world > 1:
+                    views = st.shard_views(flat, self.desc.dtype, self.world)
+                else:
+                    views = st.views(flat, self.desc.dtype)
                 for p in st.params:
                     yield f"{prefix}{st.name}.{p.name}", views[p.name]
 

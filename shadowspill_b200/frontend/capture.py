@@ -87,6 +87,8 @@ class TrainingDescription:
     grad_dtype: torch.dtype = torch.bfloat16
     selection: dict[int, str] = field(default_factory=dict)   # stage index -> variant
     mode: str = "step"                # step | forward_backward | forward
+    world_size: int = 1               # data-parallel ranks with sharded weights/optimizer state
+    rank: int = 0
 
     def variant(self, stage_index: int) -> str:
         return self.selection.get(stage_index, "recompute")
@@ -112,17 +114,27 @@ def _build(desc: TrainingDescription) -> Program:
                              or "recompute",
                              "walk": order.walk, "optimizer_order": order.optimizer})
     W, M, V, G = [], [], [], []
+    world = desc.world_size
+    sharded = world > 1
+    prog.metadata["world_size"] = world
+    FULL: dict[tuple[int, str], int] = {}     # (stage, pass) -> gathered full-weight object
+    full_bytes = []
     for si, st in enumerate(stages):
         _, pbytes = st.layout(desc.dtype)
+        full_bytes.append(pbytes)
+        if sharded:
+            _, pbytes = st.shard_layout(desc.dtype, world)
         _, gbytes = st.layout(desc.grad_dtype, torch.float32)
-        W.append(prog.add_object(ObjectSpec(f"{st.name}.weights", pbytes, "weight", True, stage=si)))
+        W.append(prog.add_object(ObjectSpec(f"{st.name}.weights", pbytes, "weight", True, stage=si,
+                                            sharding="sharded" if sharded else "whole")))
         if train:
             # gradients persist across calls when accumulation is driven from outside
             G.append(prog.add_object(ObjectSpec(f"{st.name}.gradients", gbytes, "gradient",
                                                 persistent=not step, stage=si)))
         if step:
-            M.append(prog.add_object(ObjectSpec(f"{st.name}.exp_avg", pbytes, "optimizer_state", True, stage=si)))
-            V.append(prog.add_object(ObjectSpec(f"{st.name}.exp_avg_sq", pbytes, "optimizer_state", True, stage=si)))
+            sh = "sharded" if sharded else "whole"
+            M.append(prog.add_object(ObjectSpec(f"{st.name}.exp_avg", pbytes, "optimizer_state", True, stage=si, sharding=sh)))
+            V.append(prog.add_object(ObjectSpec(f"{st.name}.exp_avg_sq", pbytes, "optimizer_state", True, stage=si, sharding=sh)))
     _, in_bytes = batch_layout(T, geo.slots)
     IN = [prog.add_object(ObjectSpec(f"batch.{m}", in_bytes, "input", True, pinned_resident=True,
                                      microbatch=m)) for m in range(n_mb)]
@@ -146,10 +158,28 @@ def _build(desc: TrainingDescription) -> Program:
     def key(st: Stage, what: str, var: str = "") -> str:
         return f"{cfg.family}:{st.kind}:{type(st).__name__}:{what}:{var}:T{T}"
 
+    def params_of(si: int, which: str) -> int:
+        """The object a compute task reads its weights from; under sharded storage
+        the first user in a pass is preceded by the all-gather task that builds it."""
+        if not sharded:
+            return W[si]
+        tag = which if order.walk == "breadth" else "all"
+        if (si, tag) not in FULL:
+            st = stages[si]
+            obj = prog.add_object(ObjectSpec(f"{st.name}.weights.full.{tag}", full_bytes[si],
+                                             "weight", stage=si))
+            FULL[(si, tag)] = obj
+            nbytes = full_bytes[si]
+            prog.add_task(TaskSpec(f"AG.{st.name}.{tag}", "collective", si, -1,
+                                   [UseSpec(W[si], "read", "shard"), UseSpec(obj, "create", "params")],
+                                   estimate_duration_ns(0.0, 2.0 * nbytes, gbps=600.0), 0,
+                                   "allgather", profile_key=f"allgather:{nbytes}:{world}"))
+        return FULL[(si, tag)]
+
     def fwd(si: int, m: int) -> None:
         st = stages[si]
         var = desc.variant(si) if train else "recompute"
-        uses = [UseSpec(W[si], "read", "params"), UseSpec(IN[m], "read", "batch"),
+        uses = [UseSpec(params_of(si, "fwd"), "read", "params"), UseSpec(IN[m], "read", "batch"),
                 UseSpec(A[si][m], "create", "y")]
         if si > 0:
             uses.append(UseSpec(A[si - 1][m], "read", "x"))
@@ -163,7 +193,7 @@ def _build(desc: TrainingDescription) -> Program:
 
     def head(m: int) -> None:
         si, st = S - 1, stages[S - 1]
-        uses = [UseSpec(W[si], "read", "params"), UseSpec(IN[m], "read", "batch"),
+        uses = [UseSpec(params_of(si, "fwd"), "read", "params"), UseSpec(IN[m], "read", "batch"),
                 UseSpec(A[si - 1][m], "read", "x"), UseSpec(LOSS, "mutate", "loss")]
         if train:
             uses.append(UseSpec(DX[m], "create", "dx"))
@@ -180,8 +210,10 @@ def _build(desc: TrainingDescription) -> Program:
     def bwd(si: int, m: int) -> None:
         st = stages[si]
         var = desc.variant(si)
-        uses = [UseSpec(W[si], "read", "params"), UseSpec(IN[m], "read", "batch"),
+        uses = [UseSpec(IN[m], "read", "batch"),
                 UseSpec(DX[m], "mutate" if si > 0 else "read", "dx")]
+        if st.kind != "embedding":      # the embedding's backward is a scatter-add: no weights
+            uses.append(UseSpec(params_of(si, "bwd"), "read", "params"))
         if si > 0:
             uses.append(UseSpec(A[si - 1][m], "read", "x"))
         if (si, m) in SAVED:
@@ -202,8 +234,9 @@ def _build(desc: TrainingDescription) -> Program:
         prog.add_task(TaskSpec(f"O.{st.name}", "optimizer", si, -1,
                                [UseSpec(W[si], "mutate", "params"), UseSpec(G[si], "read", "grads"),
                                 UseSpec(M[si], "mutate", "m"), UseSpec(V[si], "mutate", "v")],
-                               estimate_duration_ns(0.0, 8.0 * pbytes), 0, "adamw",
-                               profile_key=f"opt:{pbytes}"))
+                               estimate_duration_ns(0.0, 8.0 * pbytes), 0,
+                               "adamw_dp" if sharded else "adamw",
+                               profile_key=f"opt:{pbytes}:{world}"))
 
     body = list(range(S - 1))
     mbs = list(range(n_mb))
@@ -244,10 +277,14 @@ def _build(desc: TrainingDescription) -> Program:
 
 def build_step(cfg: DecoderConfig, geometry: BatchGeometry,
                ordering: StepDataOrdering | None = None, *, dtype=torch.bfloat16,
-               grad_dtype=None, selection: dict[int, str] | None = None):
-    """Forward + backward + optimizer of one global batch. Returns ``(Program, description)``."""
+               grad_dtype=None, selection: dict[int, str] | None = None, world_size: int = 1,
+               rank: int = 0):
+    """Forward + backward + optimizer of one global batch. Returns ``(Program, description)``.
+    ``world_size > 1`` builds the data-parallel form: weights and AdamW moments are
+    stored as 1/N shards, gathered before use and updated shard-locally."""
     desc = TrainingDescription(cfg, geometry, ordering or StepDataOrdering(), dtype,
-                               grad_dtype or dtype, dict(selection or {}), "step")
+                               grad_dtype or dtype, dict(selection or {}), "step", world_size,
+                               rank)
     return _build(desc), desc
 
 

@@ -94,6 +94,24 @@ class Stage:
             res[p.name] = flat[off:off + p.numel * dt.itemsize].view(dt).view(p.shape)
         return res
 
+    # ---- data-parallel sharded storage: every tensor is cut into `world` equal
+    # padded slices (a multiple of 8 elements each); a rank stores slice `rank`.
+    def shard_layout(self, dtype: torch.dtype, world: int):
+        """[(spec, byte offset, dtype, elements per shard)], total bytes of one shard."""
+        out, off = [], 0
+        for p in self.params:
+            dt = p.dtype or dtype
+            per = -(-(-(-p.numel // world)) // 8) * 8
+            out.append((p, off, dt, per))
+            off = _round_up(off + per * dt.itemsize, ALIGN)
+        return out, off
+
+    def shard_views(self, flat: torch.Tensor, dtype: torch.dtype, world: int) -> dict[str, torch.Tensor]:
+        lay, total = self.shard_layout(dtype, world)
+        if flat.numel() < total:
+            raise ValueError(f"{self.name}: buffer of {flat.numel()} B < shard layout {total} B")
+        return {p.name: flat[off:off + per * dt.itemsize].view(dt) for p, off, dt, per in lay}
+
     def init_(self, P: dict[str, torch.Tensor], generator: torch.Generator) -> None:
         """Deterministic seed-only initialisation, independent of any sharding."""
         for p in self.params:

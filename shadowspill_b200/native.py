@@ -74,7 +74,7 @@ class SearchSummary(C.Structure):
 class RuntimeConfig(C.Structure):
     _fields_ = [("device_bytes", i64), ("spill_bytes", i64), ("numa_node", i32),
                 ("trace_capacity", i32), ("worker_poll_ns", i64), ("max_objects", i32),
-                ("event_pool", i32)]
+                ("event_pool", i32), ("external_device_base", vp)]
 
 
 class Failure(C.Structure):

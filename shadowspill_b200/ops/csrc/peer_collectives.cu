@@ -1,0 +1,291 @@
+// Data-parallel collectives over peer-mapped (symmetric) memory, issued from
+// inside the kernels with plain P2P loads and stores across NVLink / NVSwitch.
+//
+//   ss_peer_barrier      every rank signals every peer's flag word and waits for
+//                        all of theirs (bounded spin -> status word, never a hang)
+//   ss_peer_allgather    pull all-gather: each rank copies every peer's owned
+//                        slice of a tensor straight into its own full buffer
+//   ss_rs_adamw          gradient reduce-scatter FUSED with the sharded AdamW
+//                        update: for its owned slice, a rank loads the slice of
+//                        every rank's gradient buffer over NVLink, sums in fp32,
+//                        and applies AdamW with bf16 stochastic rounding to its
+//                        parameter / moment shards in the same pass -- the summed
+//                        gradient never exists in memory
+//   ss_peer_allreduce    one-shot all-reduce for small fp32 tensors (norm weights)
+//
+// These replace the NCCL calls the reference makes for sharded storage
+// (packages/engine/csrc/adapter/pytorch/storage/sharded.cpp:87,94,118) and for its
+// optimizer-step collective tasks (packages/engine/src/shadowspill/communication/task.py:22-71).
+// No TMA is involved; peers are reached with ordinary ld/st.global.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ss {
+
+constexpr int MAX_RANKS = 16;
+constexpr unsigned long long PEER_WAIT_NS = 2000000000ull;   // 2 s
+
+struct PeerPtrs {
+  void* p[MAX_RANKS];
+};
+
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Flag layout per rank: uint32 flags[MAX_RANKS]; flags[j] on rank r is written by rank j.
+// `epoch` increases by one per barrier; a rank waits until every peer's word >= epoch.
+__global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int world, uint32_t epoch,
+                                    int* status) {
+  const int j = threadIdx.x;
+  if (j >= world) return;
+  __threadfence_system();
+  uint32_t* theirs = reinterpret_cast<uint32_t*>(flags.p[j]) + rank;
+  st_release_sys(theirs, epoch);
+  const uint32_t* mine = reinterpret_cast<const uint32_t*>(flags.p[rank]) + j;
+  const unsigned long long t0 = gtime();
+  for (uint32_t it = 0;; ++it) {
+    const uint32_t v = ld_acquire_sys(mine);
+    if (static_cast<int32_t>(v - epoch) >= 0) break;
+    if ((it & 0x3ff) == 0x3ff && gtime() - t0 > PEER_WAIT_NS) {
+      if (status) atomicCAS(status, 0, 5);   // KS_TIMEOUT_PEER
+      break;
+    }
+  }
+}
+
+// full[r] layout: the whole tensor of `numel` elements; slice k = [k*shard, min(numel,(k+1)*shard)).
+// shards.p[k] points at rank k's owned slice (shard elements). 16-byte vectors.
+__global__ void peer_allgather_kernel(PeerPtrs shards, uint8_t* __restrict__ full,
+                                      long long shard_bytes, long long total_bytes, int rank,
+                                      int world) {
+  const long long vec_per_shard = shard_bytes >> 4;
+  const long long nvec = vec_per_shard * world;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    // rotate the starting peer by rank so that the ranks do not all hit one peer at once
+    const int k0 = static_cast<int>(i / vec_per_shard);
+    const int k = (k0 + rank) % world;
+    const long long v = i - static_cast<long long>(k0) * vec_per_shard;
+    const long long off = static_cast<long long>(k) * shard_bytes + (v << 4);
+    if (off + 16 <= total_bytes) {
+      const uint4 val = reinterpret_cast<const uint4*>(shards.p[k])[v];
+      *reinterpret_cast<uint4*>(full + off) = val;
+    } else if (off < total_bytes) {
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(shards.p[k]) + (v << 4);
+      for (long long b = 0; off + b < total_bytes; ++b) full[off + b] = src[b];
+    }
+  }
+}
+
+// ---- AdamW pieces (same arithmetic and RNG as adamw_sr_kernel in elementwise.cu)
+__device__ __forceinline__ uint4 philox(uint4 ctr, uint2 key) {
+  const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(M0, ctr.x), lo0 = M0 * ctr.x;
+    const uint32_t hi1 = __umulhi(M1, ctr.z), lo1 = M1 * ctr.z;
+    ctr = make_uint4(hi1 ^ ctr.y ^ key.x, lo1, hi0 ^ ctr.w ^ key.y, lo0);
+    key.x += W0; key.y += W1;
+  }
+  return ctr;
+}
+__device__ __forceinline__ uint16_t sr16(float f, uint32_t rnd) {
+  uint32_t u = __float_as_uint(f);
+  if ((u & 0x7f800000u) == 0x7f800000u) return static_cast<uint16_t>(u >> 16);
+  u += (rnd & 0xffffu);
+  return static_cast<uint16_t>(u >> 16);
+}
+__device__ __forceinline__ uint16_t rn16(float f) {
+  return __bfloat16_as_ushort(__float2bfloat16_rn(f));
+}
+__device__ __forceinline__ void up8(const uint4& u, float (&f)[8]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+struct RsAdamArgs {
+  float lr, beta1, beta2, eps, weight_decay, bias1, bias2, grad_scale;
+  unsigned long long seed, offset;   // offset: global element index of the tensor's element 0
+  int sr_param, sr_state, g_f32;
+};
+
+// grads.p[j]: rank j's FULL gradient tensor (numel elements). This rank owns elements
+// [lo, hi). p/m/v point at the owned shard (element 0 of the shard = element lo).
+// full_param, when non-null, is the local full parameter buffer that also receives
+// the updated owned slice (so the next all-gather source is already in place).
+__global__ void rs_adamw_kernel(PeerPtrs grads, __nv_bfloat16* __restrict__ p,
+                                __nv_bfloat16* __restrict__ m, __nv_bfloat16* __restrict__ v,
+                                long long lo, long long hi, int world, RsAdamArgs a) {
+  const long long n = hi - lo;
+  const long long nvec = (n + 7) >> 3;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long e0 = i << 3;
+    const int cnt = static_cast<int>(min(8LL, n - e0));
+    float g[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int j = 0; j < world; ++j) {
+      if (a.g_f32) {
+        const float* src = reinterpret_cast<const float*>(grads.p[j]) + lo + e0;
+        if (cnt == 8) {
+          const float4 x = *reinterpret_cast<const float4*>(src);
+          const float4 y = *reinterpret_cast<const float4*>(src + 4);
+          g[0] += x.x; g[1] += x.y; g[2] += x.z; g[3] += x.w;
+          g[4] += y.x; g[5] += y.y; g[6] += y.z; g[7] += y.w;
+        } else {
+          for (int e = 0; e < cnt; ++e) g[e] += src[e];
+        }
+      } else {
+        const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(grads.p[j]) + lo + e0;
+        if (cnt == 8) {
+          float f[8];
+          up8(*reinterpret_cast<const uint4*>(src), f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) g[e] += f[e];
+        } else {
+          for (int e = 0; e < cnt; ++e) g[e] += __bfloat162float(src[e]);
+        }
+      }
+    }
+    float pf[8], mf[8], vf[8];
+    if (cnt == 8) {
+      up8(*reinterpret_cast<const uint4*>(p + e0), pf);
+      up8(*reinterpret_cast<const uint4*>(m + e0), mf);
+      up8(*reinterpret_cast<const uint4*>(v + e0), vf);
+    } else {
+      for (int e = 0; e < 8; ++e) {
+        const bool in = e < cnt;
+        pf[e] = in ? __bfloat162float(p[e0 + e]) : 0.f;
+        mf[e] = in ? __bfloat162float(m[e0 + e]) : 0.f;
+        vf[e] = in ? __bfloat162float(v[e0 + e]) : 0.f;
+      }
+    }
+    const unsigned long long gidx = a.offset + static_cast<unsigned long long>(lo + e0);
+    const uint2 key = make_uint2(static_cast<uint32_t>(a.seed), static_cast<uint32_t>(a.seed >> 32));
+    uint4 r[3];
+#pragma unroll
+    for (int k = 0; k < 3; ++k)
+      r[k] = philox(make_uint4(static_cast<uint32_t>(gidx >> 3), static_cast<uint32_t>(gidx >> 35),
+                               static_cast<uint32_t>(k), 0x5353u), key);
+    const uint32_t rw[12] = {r[0].x, r[0].y, r[0].z, r[0].w, r[1].x, r[1].y,
+                             r[1].z, r[1].w, r[2].x, r[2].y, r[2].z, r[2].w};
+    uint16_t po[8], mo[8], vo[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float gg = g[e] * a.grad_scale;
+      const float mn = a.beta1 * mf[e] + (1.f - a.beta1) * gg;
+      const float vn = a.beta2 * vf[e] + (1.f - a.beta2) * gg * gg;
+      float pn = pf[e] * (1.f - a.lr * a.weight_decay);
+      pn -= a.lr * (mn / a.bias1) / (sqrtf(vn / a.bias2) + a.eps);
+      const uint32_t w0 = rw[e >> 1], w1 = rw[4 + (e >> 1)], w2 = rw[8 + (e >> 1)];
+      const int sh = (e & 1) * 16;
+      po[e] = a.sr_param ? sr16(pn, w0 >> sh) : rn16(pn);
+      mo[e] = a.sr_state ? sr16(mn, w1 >> sh) : rn16(mn);
+      vo[e] = a.sr_state ? sr16(vn, w2 >> sh) : rn16(vn);
+    }
+    if (cnt == 8) {
+      auto pack = [](const uint16_t (&x)[8]) {
+        uint4 u;
+        u.x = x[0] | (uint32_t(x[1]) << 16); u.y = x[2] | (uint32_t(x[3]) << 16);
+        u.z = x[4] | (uint32_t(x[5]) << 16); u.w = x[6] | (uint32_t(x[7]) << 16);
+        return u;
+      };
+      *reinterpret_cast<uint4*>(p + e0) = pack(po);
+      *reinterpret_cast<uint4*>(m + e0) = pack(mo);
+      *reinterpret_cast<uint4*>(v + e0) = pack(vo);
+    } else {
+      for (int e = 0; e < cnt; ++e) {
+        p[e0 + e] = __ushort_as_bfloat16(po[e]);
+        m[e0 + e] = __ushort_as_bfloat16(mo[e]);
+        v[e0 + e] = __ushort_as_bfloat16(vo[e]);
+      }
+    }
+  }
+}
+
+// One-shot all-reduce (sum) of a small fp32 tensor: every rank reads every rank.
+__global__ void peer_allreduce_f32_kernel(PeerPtrs src, float* __restrict__ dst, long long n,
+                                          int world) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < world; ++j) acc += reinterpret_cast<const float*>(src.p[j])[i];
+    dst[i] = acc;
+  }
+}
+
+static inline int grid_of(long long work, int threads, int cap) {
+  long long g = (work + threads - 1) / threads;
+  return static_cast<int>(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+}  // namespace ss
+
+extern "C" {
+using namespace ss;
+
+int ss_peer_barrier(void* const* flag_ptrs, int rank, int world, unsigned int epoch, int* status,
+                    void* stream) {
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) return -2;
+  PeerPtrs f;
+  for (int j = 0; j < world; ++j) f.p[j] = flag_ptrs[j];
+  peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f, rank, world, epoch, status);
+  return (int)cudaGetLastError();
+}
+
+int ss_peer_allgather(void* const* shard_ptrs, void* full, long long shard_bytes,
+                      long long total_bytes, int rank, int world, void* stream) {
+  if (world < 1 || world > MAX_RANKS || (shard_bytes & 15)) return -2;
+  PeerPtrs s;
+  for (int j = 0; j < world; ++j) s.p[j] = shard_ptrs[j];
+  const long long nvec = (shard_bytes >> 4) * world;
+  if (nvec == 0) return 0;
+  peer_allgather_kernel<<<grid_of(nvec, 256, 148 * 8), 256, 0, (cudaStream_t)stream>>>(
+      s, (uint8_t*)full, shard_bytes, total_bytes, rank, world);
+  return (int)cudaGetLastError();
+}
+
+int ss_rs_adamw(void* const* grad_ptrs, void* p, void* m, void* v, long long lo, long long hi,
+                int world, int g_f32, float lr, float beta1, float beta2, float eps,
+                float weight_decay, int step, float grad_scale, unsigned long long seed,
+                unsigned long long offset, int sr_param, int sr_state, void* stream) {
+  if (world < 1 || world > MAX_RANKS || (lo & 7) || ((offset) & 7)) return -2;
+  if (hi <= lo) return 0;
+  PeerPtrs g;
+  for (int j = 0; j < world; ++j) g.p[j] = grad_ptrs[j];
+  RsAdamArgs a;
+  a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.weight_decay = weight_decay;
+  a.bias1 = 1.f - powf(beta1, (float)step); a.bias2 = 1.f - powf(beta2, (float)step);
+  a.grad_scale = grad_scale;
+  a.seed = seed ^ (0x9E3779B97F4A7C15ull * (unsigned long long)(step + 1));
+  a.offset = offset; a.sr_param = sr_param; a.sr_state = sr_state; a.g_f32 = g_f32;
+  const long long nvec = (hi - lo + 7) >> 3;
+  rs_adamw_kernel<<<grid_of(nvec, 256, 148 * 8), 256, 0, (cudaStream_t)stream>>>(
+      g, (__nv_bfloat16*)p, (__nv_bfloat16*)m, (__nv_bfloat16*)v, lo, hi, world, a);
+  return (int)cudaGetLastError();
+}
+
+int ss_peer_allreduce_f32(void* const* src_ptrs, float* dst, long long n, int world, void* stream) {
+  if (world < 1 || world > MAX_RANKS) return -2;
+  if (n <= 0) return 0;
+  PeerPtrs s;
+  for (int j = 0; j < world; ++j) s.p[j] = src_ptrs[j];
+  peer_allreduce_f32_kernel<<<grid_of(n, 256, 148 * 4), 256, 0, (cudaStream_t)stream>>>(s, dst, n, world);
+  return (int)cudaGetLastError();
+}
+}  // extern "C"

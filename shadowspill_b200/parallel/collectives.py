@@ -1,0 +1,150 @@
+"""Data-parallel collectives behind one interface, two arms.
+
+``PeerCollectives``  the product path on NVLink/NVSwitch: the executor's device
+                     pool is one symmetric allocation mapped into every rank, so
+                     an object at pool offset X on this rank is at ``base[r] + X``
+                     on rank r, and the hand-written kernels in
+                     ``peer_collectives.cu`` reach it with plain loads/stores:
+                     pull all-gather, reduce-scatter fused with sharded AdamW,
+                     flag barriers with bounded waits.
+``DistCollectives``  the library arm (``torch.distributed``: NCCL on GPUs, gloo on
+                     CPU). It is the baseline the fused path is measured against
+                     and the functional stand-in for multi-rank tests on CPU.
+
+Both run on the compute stream as plan tasks, in the same order on every rank.
+Reference for what is being replaced: the NCCL calls in
+packages/engine/csrc/adapter/pytorch/storage/sharded.cpp:87,94,118 and
+packages/engine/src/shadowspill/communication/operations.py:9-26.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+from ..ops import functional as F
+
+_c = _lib
+_lib.register("ss_peer_barrier", [_c.c_p, _c.c_int, _c.c_int, C.c_uint, _c.c_p, _c.c_p])
+_lib.register("ss_peer_allgather", [_c.c_p, _c.c_p, _c.c_ll, _c.c_ll, _c.c_int, _c.c_int, _c.c_p])
+_lib.register("ss_rs_adamw", [_c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_ll, _c.c_ll, _c.c_int, _c.c_int,
+                              _c.c_f, _c.c_f, _c.c_f, _c.c_f, _c.c_f, _c.c_int, _c.c_f, _c.c_ull,
+                              _c.c_ull, _c.c_int, _c.c_int, _c.c_p])
+_lib.register("ss_peer_allreduce_f32", [_c.c_p, _c.c_p, _c.c_ll, _c.c_int, _c.c_p])
+
+
+def shard_numel(numel: int, world: int) -> int:
+    """Elements per rank: equal padded shards, a multiple of 8 elements so that
+    every shard starts on a 16-byte boundary for 2-byte types."""
+    per = -(-numel // world)
+    return -(-per // 8) * 8
+
+
+class DistCollectives:
+    """torch.distributed arm (NCCL / gloo)."""
+    name = "dist"
+
+    def __init__(self, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+
+    def barrier_begin(self) -> None:
+        pass
+
+    def barrier_end(self) -> None:
+        pass
+
+    def all_gather(self, shard: torch.Tensor, full: torch.Tensor) -> None:
+        """``full`` (numel elements) <- concatenation of every rank's ``shard``."""
+        n, per = full.numel(), shard.numel()
+        if self.world == 1:
+            full.view(-1)[:n].copy_(shard.view(-1)[:n])
+            return
+        parts = [torch.empty_like(shard.view(-1)) for _ in range(self.world)]
+        dist.all_gather(parts, shard.view(-1).contiguous(), group=self.group)
+        flat = full.view(-1)
+        for k, part in enumerate(parts):
+            lo = k * per
+            if lo < n:
+                flat[lo:min(n, lo + per)].copy_(part[:min(n, lo + per) - lo])
+
+    def reduce_scatter_adamw(self, grad: torch.Tensor, p, m, v, *, offset: int, **adam) -> None:
+        """Sum ``grad`` over ranks; update this rank's owned slice of (p, m, v)."""
+        n, per = grad.numel(), p.numel()
+        g = grad.view(-1).clone()
+        if self.world > 1:
+            dist.all_reduce(g, group=self.group)
+        lo = self.rank * per
+        hi = min(n, lo + per)
+        if hi <= lo:
+            return
+        cnt = hi - lo
+        F.adamw_(p.view(-1)[:cnt], g[lo:hi], m.view(-1)[:cnt], v.view(-1)[:cnt],
+                 offset=offset + lo, **adam)
+
+
+class PeerCollectives:
+    """Own kernels over the symmetric device pool."""
+    name = "peer"
+
+    def __init__(self, pool: torch.Tensor, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group or dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.pool = pool
+        self.handle = symm_mem.rendezvous(pool, self.group.group_name)
+        self.bases = [int(p) for p in self.handle.buffer_ptrs]
+        self.local_base = pool.data_ptr()
+        if self.bases[self.rank] != self.local_base:
+            raise RuntimeError("symmetric pool base does not match the local tensor")
+        self.flags = symm_mem.empty(64, dtype=torch.int32, device=pool.device)
+        self.flags.zero_()
+        self.flag_handle = symm_mem.rendezvous(self.flags, self.group.group_name)
+        self.flag_ptrs = (C.c_void_p * self.world)(*[int(p) for p in self.flag_handle.buffer_ptrs])
+        self.epoch = 0
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+
+    def _peers(self, t: torch.Tensor):
+        off = t.data_ptr() - self.local_base
+        if off < 0 or off + t.numel() * t.element_size() > self.pool.numel():
+            raise ValueError("tensor is not inside the symmetric pool")
+        return (C.c_void_p * self.world)(*[b + off for b in self.bases])
+
+    def _barrier(self) -> None:
+        self.epoch += 1
+        _lib.check(_lib.lib().ss_peer_barrier(self.flag_ptrs, self.rank, self.world, self.epoch,
+                                              _lib.status_word(self.pool.device).data_ptr(),
+                                              _lib.stream_ptr()), "ss_peer_barrier")
+
+    barrier_begin = _barrier
+    barrier_end = _barrier
+
+    def all_gather(self, shard: torch.Tensor, full: torch.Tensor) -> None:
+        _lib.check(_lib.lib().ss_peer_allgather(
+            self._peers(shard), full.data_ptr(), shard.numel() * shard.element_size(),
+            full.numel() * full.element_size(), self.rank, self.world, _lib.stream_ptr()),
+            "ss_peer_allgather")
+
+    def reduce_scatter_adamw(self, grad: torch.Tensor, p, m, v, *, offset: int, lr, beta1, beta2,
+                             eps, weight_decay, step, grad_scale, seed, stochastic_param,
+                             stochastic_state) -> None:
+        n, per = grad.numel(), p.numel()
+        lo = self.rank * per
+        hi = min(n, lo + per)
+        if hi <= lo:
+            return
+        _lib.check(_lib.lib().ss_rs_adamw(
+            self._peers(grad), p.data_ptr(), m.data_ptr(), v.data_ptr(), lo, hi, self.world,
+            int(grad.dtype == torch.float32), lr, beta1, beta2, eps, weight_decay, step,
+            grad_scale, seed, offset, int(stochastic_param), int(stochastic_state),
+            _lib.stream_ptr()), "ss_rs_adamw")
+
+
+def allocate_symmetric_pool(nbytes: int, device: torch.device) -> torch.Tensor:
+    import torch.distributed._symmetric_memory as symm_mem
+    return symm_mem.empty(int(nbytes), dtype=torch.uint8, device=device)

@@ -51,7 +51,10 @@ class TransferRates:
 class Runtime:
     def __init__(self, device_bytes: int, spill_bytes: int, backend: str = "cuda",
                  device_index: int = 0, trace_capacity: int = 0, mock_bps: float = 0.0,
-                 mock_latency_ns: int = 0, numa_node: int = -1):
+                 mock_latency_ns: int = 0, numa_node: int = -1,
+                 device_pool: torch.Tensor | None = None):
+        """``device_pool``: a caller-owned uint8 tensor to use as the device pool
+        (a symmetric-memory allocation for multi-GPU plans); it must outlive the runtime."""
         self.lib = native.core()
         self.backend_name = backend
         self.device_index = device_index
@@ -68,8 +71,14 @@ class Runtime:
                 raise RuntimeError(f"cannot open CUDA backend: {err.value.decode()}")
         else:
             raise ValueError(f"unknown backend {backend!r}")
+        external = None
+        if device_pool is not None:
+            if device_pool.numel() < device_bytes:
+                raise ValueError("device_pool is smaller than the plan's device bytes")
+            external = device_pool.data_ptr()
+            self._external_pool = device_pool
         cfg = native.RuntimeConfig(int(device_bytes), int(spill_bytes), numa_node,
-                                   int(trace_capacity), 1000, 0, 0)
+                                   int(trace_capacity), 1000, 0, 0, external)
         handle = native.vp()
         native.check(self.lib.ss_runtime_create(self.backend, C.byref(cfg), C.byref(handle)),
                      "ss_runtime_create")
@@ -84,7 +93,9 @@ class Runtime:
             self.spill = torch.from_numpy(arr)
         else:
             self.spill = torch.empty(0, dtype=torch.uint8)
-        if device_bytes == 0:
+        if device_pool is not None:
+            self.device = device_pool
+        elif device_bytes == 0:
             self.device = torch.empty(0, dtype=torch.uint8)
         elif backend == "cuda":
             with torch.cuda.device(device_index):

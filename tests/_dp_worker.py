@@ -1,0 +1,87 @@
+"""Child process of the data-parallel tests: one rank of a 2+-rank job."""
+import os
+import sys
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+
+import torch
+import torch.distributed as dist
+
+from shadowspill_b200.communication.info import CommunicationInfo
+from shadowspill_b200.data.synthetic import make_batch, to_device
+from shadowspill_b200.execution.executor import Executor, Hyperparameters
+from shadowspill_b200.execution.resident import ResidentTrainer
+from shadowspill_b200.frontend.capture import BatchGeometry, StepDataOrdering, build_step
+from shadowspill_b200.models.config import preset
+from shadowspill_b200.planning.plan import MemoryBudgets, SearchOptions, plan_program
+
+
+def main():
+    device = sys.argv[1]                      # cpu | cuda
+    arm = sys.argv[2] if len(sys.argv) > 2 else "auto"
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    cuda = device == "cuda"
+    if cuda:
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{rank}"))
+    else:
+        dist.init_process_group("gloo")
+    dtype = torch.bfloat16 if cuda else torch.float32
+    cfg = preset("llama3-tiny")
+    T, n_mb = 256, 2
+    geo = BatchGeometry(T, n_mb, slots=16, mean_seqlen=64)
+    prog, desc = build_step(cfg, geo, StepDataOrdering(), dtype=dtype, world_size=world, rank=rank)
+    total = sum(o.bytes for o in prog.objects)
+    plan = plan_program(prog, MemoryBudgets(total, 64 << 20, headroom_bytes=0), CommunicationInfo(),
+                        SearchOptions(minimum_object_bytes_evict_eligible=1024, workers=1,
+                                      deterministic=True))
+    ex = Executor(plan, desc, device=device, device_index=rank if cuda else 0, seed=5,
+                  hyper=Hyperparameters(lr=3e-3), stochastic_rounding=False, collectives=arm)
+    ex.initialize(on_device=False)
+    ref = ResidentTrainer(cfg, device=f"cuda:{rank}" if cuda else "cpu", dtype=dtype, seed=5,
+                          lr=3e-3, stochastic_rounding=False)
+    ok = True
+    for step in range(2):
+        # the global batch: every rank's microbatches, weights normalised over all of them
+        parts = [make_batch(100 * step + r, vocab=cfg.vocab_size, tokens_per_step=T * n_mb,
+                            microbatch_tokens=T, median=60, min_len=8, max_len=128, slots=16)
+                 for r in range(world)]
+        for part in parts:
+            for mb in part:
+                mb.weights /= world
+        res = ex.run(parts[rank])
+        loss = torch.tensor([res.loss], dtype=torch.float64, device="cuda" if cuda else "cpu")
+        dist.all_reduce(loss)
+        want = ref.step([to_device(m, ref.device) for part in parts for m in part])
+        tol = 2e-2 if cuda else 1e-5
+        if abs(float(loss) - want) > tol * max(1.0, abs(want)):
+            print(f"rank {rank} step {step}: loss {float(loss)} != {want}", flush=True)
+            ok = False
+    # owned slices must equal the matching slices of the resident model
+    refs = ref.state_dict()
+    # gradient summation order differs (per-rank partial sums), hence a few ulps in fp32
+    rtol, atol = (5e-2, 2e-3) if cuda else (1e-4, 5e-5)
+    for name, shard in ex.named_tensors():
+        if name.startswith("exp_avg"):
+            continue
+        full = refs[name].reshape(-1).cpu()
+        lo = rank * shard.numel()
+        hi = min(full.numel(), lo + shard.numel())
+        if hi > lo and not torch.allclose(shard[:hi - lo].float(), full[lo:hi].float(), rtol=rtol,
+                                          atol=atol):
+            err = (shard[:hi - lo].float() - full[lo:hi].float()).abs().max()
+            print(f"rank {rank}: {name} differs by {float(err)}", flush=True)
+            ok = False
+    if cuda:
+        from shadowspill_b200.ops import _lib
+        _lib.check_status()
+    ex.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    print(f"rank {rank} {'OK' if ok else 'FAILED'} arm={ex.collectives.name}", flush=True)
+    sys.exit(0 if ok else 1)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,30 @@
+"""Sharded data-parallel execution against the resident single-process trainer."""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+WORKER = Path(__file__).with_name("_dp_worker.py")
+
+
+def _launch(world, device, arm, port):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), str(WORKER), device, arm]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    assert out.stdout.count(" OK ") == world, out.stdout[-2000:]
+
+
+def test_two_ranks_gloo_match_resident():
+    _launch(2, "cpu", "dist", 29611)
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.parametrize("arm", ["peer", "dist"])
+def test_two_gpus_match_resident(arm):
+    _launch(2, "cuda", arm, 29613 if arm == "peer" else 29615)
