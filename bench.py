@@ -103,6 +103,8 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=65536, help="tokens per worker per step")
     ap.add_argument("--microbatch", type=int, default=8192)
     ap.add_argument("--report", default="", help="directory for the plan report")
+    ap.add_argument("--collectives", default="auto", choices=["auto", "peer", "dist"],
+                    help="peer = own kernels over NVLink peer memory; dist = NCCL baseline arm")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm()
@@ -125,13 +127,17 @@ def main() -> None:
 
     setup = TrainingSetup(model=args.model, device_gib=args.device_gib, spill_gib=args.spill_gib,
                           tokens_per_step=args.tokens, microbatch_tokens=args.microbatch,
-                          lr=1e-5, seed=1234, rank=rank, world_size=world, device_index=local)
+                          lr=1e-5, seed=1234, rank=rank, world_size=world, device_index=local,
+                          collectives=args.collectives)
     session = TrainingSession(setup)          # build -> profile -> calibrate -> plan -> executor
     cfg = session.cfg
     n_batches = args.warmup + args.steps
     batches = [make_batch(1000 * rank + i, vocab=cfg.vocab_size, tokens_per_step=args.tokens,
                           microbatch_tokens=args.microbatch, max_len=8192, median=1200.0,
                           slots=session.slots) for i in range(n_batches)]
+    for b in batches:                 # loss weights are 1/N over the GLOBAL batch
+        for mb in b:
+            mb.weights /= world
     losses = []
     for i in range(args.warmup):
         losses.append(session.step(batches[i]).loss)
@@ -188,7 +194,9 @@ def main() -> None:
                                 "device_pool_gib": round(session.plan.device_bytes / GIB, 2),
                                 "workspace_gib": round(plan.workspace_bytes / GIB, 2),
                                 "spill_gib": round(session.plan.spill_bytes / GIB, 2)},
-                       "attention": os.environ.get("SS_ATTENTION", "native")},
+                       "attention": os.environ.get("SS_ATTENTION", "native"),
+                       "collectives": (session.executor.collectives.name
+                                       if session.executor.collectives else "none")},
             "e2e": {"value": round(total_tokens / wall, 1), "unit": "tokens/s",
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                     "api": "TrainingSession.step(host numpy batch) -> host loss"},

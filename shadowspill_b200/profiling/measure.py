@@ -94,6 +94,8 @@ def measure_program(program: Program, desc: TrainingDescription, device: str = "
     profiles = Profiles(device=torch.cuda.get_device_name(dev) if cuda else "cpu")
     seen: dict[str, int] = {}
     for ti, t in enumerate(program.tasks):
+        if t.kind == "collective" or t.variant == "adamw_dp":
+            continue      # needs every rank; keeps its modelled cost until calibrated
         if t.profile_key and t.profile_key not in seen and (keys is None or t.profile_key in keys):
             seen[t.profile_key] = ti
     for key, ti in seen.items():
@@ -148,7 +150,8 @@ def apply_profiles(program: Program, profiles: Profiles, workspace_margin: float
     for t in program.tasks:
         p = profiles.tasks.get(t.profile_key)
         if p is None:
-            missing.append(t.profile_key)
+            if not (t.kind == "collective" or t.variant == "adamw_dp"):
+                missing.append(t.profile_key)
             continue
         t.duration_ns = max(1, int(p.seconds * duration_scale * 1e9))
         t.workspace_bytes = int(p.workspace_bytes * workspace_margin)

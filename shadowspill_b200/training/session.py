@@ -61,6 +61,7 @@ class TrainingSetup:
     calibrate: bool = True
     search: SearchOptions = field(default_factory=SearchOptions)
     trace_capacity: int = 0
+    collectives: str = "auto"             # peer | dist | auto
 
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
@@ -81,51 +82,70 @@ class TrainingSession:
                                       self.slots, setup.mean_seqlen)
         self.budgets = MemoryBudgets.from_gib(setup.device_gib, setup.spill_gib)
         self.timings: dict[str, float] = {}
-        # ---- build candidates
-        t0 = time.perf_counter()
+        world, rank = setup.world_size, setup.rank
         selections = recompute_share_selections(self.cfg, setup.recompute_shares, setup.saved_variant)
-        candidates = []
-        for walk in setup.walks:
-            for sel in selections:
-                order = StepDataOrdering(walk=walk, optimizer="stage_interleaved" if walk == "breadth" else "tail")
-                candidates.append(build_step(self.cfg, self.geometry, order, dtype=self.dtype,
-                                             selection=sel))
-        self.timings["build"] = time.perf_counter() - t0
-        # ---- profile distinct tasks once
-        t0 = time.perf_counter()
+        variants = [(walk, sel) for walk in setup.walks for sel in selections]
+
+        def build(index: int):
+            walk, sel = variants[index]
+            order = StepDataOrdering(walk=walk, optimizer="stage_interleaved" if walk == "breadth" else "tail")
+            return build_step(self.cfg, self.geometry, order, dtype=self.dtype, selection=sel,
+                              world_size=world, rank=rank)
+
         self.profiles = Profiles()
-        if setup.profile:
-            dev = f"cuda:{setup.device_index}" if cuda else "cpu"
-            for prog, desc in candidates:
-                missing = {t.profile_key for t in prog.tasks} - set(self.profiles.tasks)
-                if missing:
-                    got = measure_program(prog, desc, dev, keys=missing)
-                    self.profiles.tasks.update(got.tasks)
-                    self.profiles.device = got.device
-                apply_profiles(prog, self.profiles)
-            if cuda:
-                torch.cuda.empty_cache()
-        self.timings["profile"] = time.perf_counter() - t0
-        # ---- host link calibration
-        t0 = time.perf_counter()
-        self.communication = CommunicationInfo(world_size=setup.world_size)
-        if setup.calibrate and cuda:
-            probe = 256 << 20
-            with Runtime(2 * probe, 2 * probe, "cuda", setup.device_index) as rt:
-                r = rt.calibrate(probe, 3)
-            self.communication = CommunicationInfo(
-                r.fetch_solo_bps, r.fetch_concurrent_bps, r.evict_solo_bps, r.evict_concurrent_bps,
-                r.fetch_latency_ns, r.evict_latency_ns, world_size=setup.world_size,
-                source="calibrated")
-        self.timings["communication"] = time.perf_counter() - t0
-        # ---- plan
-        t0 = time.perf_counter()
-        sweep = sweep_programs([p for p, _ in candidates], self.budgets, self.communication,
-                               setup.search)
-        self.sweep = sweep
-        self.plan = sweep.best
-        self.desc = next(d for p, d in candidates if p is self.plan.program)
-        self.timings["plan"] = time.perf_counter() - t0
+        self.communication = CommunicationInfo(world_size=world)
+        chosen, plan_json = 0, None
+        if rank == 0:
+            # ---- build candidates
+            t0 = time.perf_counter()
+            candidates = [build(i) for i in range(len(variants))]
+            self.timings["build"] = time.perf_counter() - t0
+            # ---- profile distinct tasks once
+            t0 = time.perf_counter()
+            if setup.profile:
+                dev = f"cuda:{setup.device_index}" if cuda else "cpu"
+                for prog, desc in candidates:
+                    missing = {t.profile_key for t in prog.tasks} - set(self.profiles.tasks)
+                    if missing:
+                        got = measure_program(prog, desc, dev, keys=missing)
+                        self.profiles.tasks.update(got.tasks)
+                        self.profiles.device = got.device
+                    apply_profiles(prog, self.profiles)
+                if cuda:
+                    torch.cuda.empty_cache()
+            self.timings["profile"] = time.perf_counter() - t0
+            # ---- host link calibration
+            t0 = time.perf_counter()
+            if setup.calibrate and cuda:
+                probe = 256 << 20
+                with Runtime(2 * probe, 2 * probe, "cuda", setup.device_index) as rt:
+                    r = rt.calibrate(probe, 3)
+                self.communication = CommunicationInfo(
+                    r.fetch_solo_bps, r.fetch_concurrent_bps, r.evict_solo_bps,
+                    r.evict_concurrent_bps, r.fetch_latency_ns, r.evict_latency_ns,
+                    world_size=world, source="calibrated")
+            self.timings["communication"] = time.perf_counter() - t0
+            # ---- plan every candidate, keep the fastest
+            t0 = time.perf_counter()
+            sweep = sweep_programs([p for p, _ in candidates], self.budgets, self.communication,
+                                   setup.search)
+            self.sweep = sweep
+            self.plan = sweep.best
+            chosen = next(i for i, (p, _) in enumerate(candidates) if p is self.plan.program)
+            self.desc = candidates[chosen][1]
+            self.timings["plan"] = time.perf_counter() - t0
+            plan_json = self.plan.to_json()
+        if world > 1:
+            # one plan for the whole job: identical offsets on every rank are what makes the
+            # device pool symmetric, and identical task order keeps collectives matched
+            import torch.distributed as dist
+            box = [chosen, plan_json]
+            dist.broadcast_object_list(box, src=0)
+            if rank != 0:
+                from ..ir.plan import Plan
+                chosen, plan_json = box
+                self.plan = Plan.from_json(plan_json)
+                self.desc = build(chosen)[1]
         self.log(f"plan: {self.plan.summary.ordering} {self.plan.summary.selection} "
                  f"simulated {self.plan.summary.duration_seconds * 1e3:.1f} ms")
         # ---- executor (caps the torch allocator to the planned workspace)
@@ -138,7 +158,8 @@ class TrainingSession:
         self.executor = Executor(self.plan, self.desc, device=setup.device,
                                  device_index=setup.device_index, seed=setup.seed, hyper=hyper,
                                  stochastic_rounding=setup.stochastic_rounding,
-                                 trace_capacity=setup.trace_capacity)
+                                 trace_capacity=setup.trace_capacity,
+                                 collectives=setup.collectives)
         self.executor.initialize()
         self.timings["open"] = time.perf_counter() - t0
         if cuda:
