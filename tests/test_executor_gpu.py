@@ -47,8 +47,14 @@ def test_planned_step_matches_resident(selection):
     _lib.check_status()
     mine = ex.state_dict()
     for k, v in ref.state_dict().items():
-        # identical kernels in identical order: bitwise equal without stochastic rounding
-        assert torch.equal(mine[k].cpu(), v.cpu()), k
+        # same kernels, but bf16 gradients accumulate over microbatches in a different order
+        # (reverse-breadth walk) and embedding gradients use atomics: a few bf16 ulps apart
+        # (Adam turns a sign flip of a near-zero gradient into a 2*lr difference, so the
+        # comparison is the relative L2 / cosine one of a numerical gate, not elementwise)
+        a, b = mine[k].float().cpu().reshape(-1), v.float().cpu().reshape(-1)
+        rel = float((a - b).norm() / (b.norm() + 1e-12))
+        cos = float(torch.dot(a, b) / (a.norm() * b.norm() + 1e-12))
+        assert rel < 2.5e-2 and cos > 0.999, (k, rel, cos)
     assert len(got.task_seconds) == len(plan.program.tasks)
     stats = ex.rt.stats()
     assert stats["fetch_bytes"] > 0 and stats["evict_bytes"] > 0
