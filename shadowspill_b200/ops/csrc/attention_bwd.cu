@@ -627,3 +627,57 @@ extern "C" int ss_attn_bwd(const void* q, const void* k, const void* v, const vo
   }
   return -2;
 }
+
+// ============================================================================ no-allocation entry
+// See attention_noalloc.h. The scratch that ss_attn_bwd takes from its caller
+// (delta, fp32 [Hq, T]) lives here in a fixed device array instead, so the call
+// performs no allocation of any kind.
+#include "attention_noalloc.h"
+
+#include <mutex>
+
+namespace ss {
+
+// Every GPU that loads this library holds this array until the process exits.
+static __device__ __align__(256) float g_attn_delta_scratch[SS_ATTN_NOALLOC_MAX_ELEMENTS];
+
+constexpr int kMaxDevices = 64;
+static float* g_scratch_address[kMaxDevices];   // device address of the array, per device
+static std::mutex g_scratch_mutex;
+
+// In host code `g_attn_delta_scratch` is only a stand-in symbol, not an address a
+// kernel can use; the device address has to be asked for, once per device, with
+// that device current.
+static int scratch_for_current_device(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kMaxDevices) return SS_ATTN_NOALLOC_BAD_DEVICE;
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_address[dev] == nullptr) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_attn_delta_scratch);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    g_scratch_address[dev] = ptr;
+  }
+  *out = g_scratch_address[dev];
+  return 0;
+}
+
+}  // namespace ss
+
+extern "C" long long ss_attn_bwd_noalloc_max_elements(void) { return SS_ATTN_NOALLOC_MAX_ELEMENTS; }
+
+extern "C" int ss_attn_bwd_noalloc(const void* q, const void* k, const void* v, const void* out,
+                                   const float* lse, const void* dout, void* dq, void* dk, void* dv,
+                                   const int* cu_seqlens, int nseq, int T, int Hq, int Hkv, int dh,
+                                   long long ldq, long long ldk, long long ldv, long long ldo,
+                                   float scale, int* status, void* stream) {
+  if (T <= 0 || nseq <= 0) return 0;
+  if (Hq <= 0 || static_cast<long long>(Hq) * T > SS_ATTN_NOALLOC_MAX_ELEMENTS)
+    return SS_ATTN_NOALLOC_TOO_LARGE;
+  float* scratch = nullptr;
+  if (int rc = ss::scratch_for_current_device(&scratch)) return rc;
+  return ss_attn_bwd(q, k, v, out, lse, dout, dq, dk, dv, cu_seqlens, scratch, nseq, T, Hq, Hkv,
+                     dh, ldq, ldk, ldv, ldo, scale, status, stream);
+}
