@@ -333,6 +333,12 @@ typedef struct ss_transfer_profile {
 int ss_calibrate_transfers(ss_runtime* rt, int64_t bytes, int32_t repeats,
                            ss_transfer_profile* out);
 
+/* ------------------------------------------------------------------ BLAKE3 */
+void* ss_blake3_new(void);
+void ss_blake3_update(void* hasher, const void* data, size_t len);
+void ss_blake3_finalize(void* hasher, uint8_t* out32);   /* may be called mid-stream */
+void ss_blake3_free(void* hasher);
+
 #ifdef __cplusplus
 }
 #endif

@@ -202,6 +202,13 @@ def _declare(lib: C.CDLL) -> None:
     lib.ss_spill_write.argtypes = [vp, i64, vp, i64]
     lib.ss_spill_read.argtypes = [vp, i64, vp, i64]
     lib.ss_calibrate_transfers.argtypes = [vp, i64, i32, C.POINTER(TransferProfile)]
+    lib.ss_blake3_new.restype = vp
+    lib.ss_blake3_update.argtypes = [vp, vp, C.c_size_t]
+    lib.ss_blake3_update.restype = None
+    lib.ss_blake3_finalize.argtypes = [vp, C.c_char_p]
+    lib.ss_blake3_finalize.restype = None
+    lib.ss_blake3_free.argtypes = [vp]
+    lib.ss_blake3_free.restype = None
 
 
 def status_string(status: int) -> str:
@@ -236,3 +243,38 @@ def ptr64(a: np.ndarray):
 
 def ptr32(a: np.ndarray):
     return a.ctypes.data_as(P32)
+
+
+class Blake3:
+    """Streaming BLAKE3 (32-byte digest) backed by the native core."""
+
+    def __init__(self, data: bytes | None = None):
+        self._lib = core()
+        self._h = self._lib.ss_blake3_new()
+        if data:
+            self.update(data)
+
+    def update(self, data) -> "Blake3":
+        mv = memoryview(data).cast("B")
+        if len(mv):
+            if mv.readonly:
+                buf = bytes(mv)
+                self._lib.ss_blake3_update(self._h, C.cast(C.c_char_p(buf), vp), len(buf))
+            else:
+                arr = (C.c_char * len(mv)).from_buffer(mv)
+                self._lib.ss_blake3_update(self._h, C.addressof(arr), len(mv))
+        return self
+
+    def digest(self) -> bytes:
+        out = C.create_string_buffer(32)
+        self._lib.ss_blake3_finalize(self._h, out)
+        return out.raw
+
+    def hexdigest(self) -> str:
+        return self.digest().hex()
+
+    def __del__(self):
+        try:
+            self._lib.ss_blake3_free(self._h)
+        except Exception:  # noqa: BLE001 - interpreter shutdown
+            pass

@@ -1,0 +1,80 @@
+"""Checkpoint archive format, round trip and resume equivalence (CPU, mock backend)."""
+import json
+import sys
+import tarfile
+
+import pytest
+import torch
+
+sys.path.insert(0, __file__.rsplit("/", 1)[0])
+from test_executor_cpu import _batches, _setup  # noqa: E402
+
+from shadowspill_b200.checkpoint import (CheckpointError, export_weights, load_checkpoint,
+                                         read_manifest, save_checkpoint)
+from shadowspill_b200.execution.executor import Executor, Hyperparameters
+from shadowspill_b200.native import Blake3
+
+
+def test_blake3_known_vectors():
+    assert Blake3(b"").hexdigest() == \
+        "af1349b9f5f9a1a6a0404dea36dcc9499bcb25c9adc112b7cc9a93cae41f3262"
+    assert Blake3(bytes([0])).hexdigest() == \
+        "2d3adedff11b61f14c886e35afa036736dcd87a74d27b5c1510225d0f592e213"
+    data = bytes(i % 251 for i in range(70000))
+    h = Blake3()
+    for i in range(0, len(data), 1000):
+        h.update(data[i:i + 1000])
+    assert h.hexdigest() == Blake3(data).hexdigest()
+    try:
+        import blake3
+    except ImportError:
+        return
+    for n in (1023, 1024, 1025, 4097, 70000):
+        assert blake3.blake3(data[:n]).hexdigest() == Blake3(data[:n]).hexdigest()
+
+
+def test_archive_layout_and_resume(tmp_path):
+    cfg, plan, desc = _setup()
+    hyper = Hyperparameters(lr=3e-3)
+    a = Executor(plan, desc, device="cpu", seed=5, hyper=hyper)
+    a.initialize()
+    for s in range(2):
+        a.run(_batches(cfg, s))
+    path = save_checkpoint(a, tmp_path / "ckpt", metadata={"note": "after two updates"})
+    # ---- the TAR layout
+    with tarfile.open(path, "r:") as tar:
+        names = tar.getnames()
+    assert names[-2:] == ["manifest.json", "manifest.blake3"]
+    assert names[0] == "tensors/0" and all(n.startswith("tensors/") for n in names[:-2])
+    m = read_manifest(path)
+    assert m["format"] == "shadowspill.checkpoint" and m["version"] == 1
+    assert m["metadata"]["completed_updates"] == 2 and m["weights"] == "compute"
+    e = m["tensors"][0]
+    assert {"name", "shape", "dtype", "stride", "storage_offset", "storage_elements", "region",
+            "member", "bytes", "blake3"} <= set(e)
+    assert path.stat().st_size % 512 == 0
+    # ---- resume: a fresh executor continues exactly where the first one goes next
+    b = Executor(plan, desc, device="cpu", seed=99, hyper=hyper)
+    b.initialize()
+    meta = load_checkpoint(b, tmp_path / "ckpt")
+    assert meta["note"] == "after two updates" and b.completed_updates == 2
+    la, lb = a.run(_batches(cfg, 2)).loss, b.run(_batches(cfg, 2)).loss
+    assert la == lb
+    sa, sb = a.state_dict(), b.state_dict()
+    assert all(torch.equal(sa[k], sb[k]) for k in sa)
+    w = export_weights(tmp_path / "ckpt")
+    assert set(w) == {k for k in sa if not k.startswith("exp_avg")}
+    a.close(); b.close()
+
+
+def test_corruption_is_detected(tmp_path):
+    cfg, plan, desc = _setup()
+    ex = Executor(plan, desc, device="cpu", seed=1)
+    ex.initialize()
+    path = save_checkpoint(ex, tmp_path / "c")
+    raw = bytearray(path.read_bytes())
+    raw[512 + 100] ^= 0xFF                      # inside the first tensor member
+    path.write_bytes(bytes(raw))
+    with pytest.raises(CheckpointError):
+        load_checkpoint(ex, tmp_path / "c")
+    ex.close()
