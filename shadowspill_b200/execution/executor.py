@@ -193,9 +193,13 @@ class Executor:
     def __init__(self, plan: Plan, desc: TrainingDescription, *, device: str = "cuda",
                  device_index: int = 0, seed: int = 0, hyper: Hyperparameters | None = None,
                  stochastic_rounding: bool = True, trace_capacity: int = 0,
-                 mock_bps: float = 0.0, collectives: str = "auto"):
+                 mock_bps: float = 0.0, collectives: str = "auto",
+                 extra_plans: dict[str, tuple[Plan, TrainingDescription]] | None = None):
         """``collectives``: ``peer`` (own kernels over a symmetric device pool),
-        ``dist`` (torch.distributed: NCCL or gloo) or ``auto`` (peer on GPUs)."""
+        ``dist`` (torch.distributed: NCCL or gloo) or ``auto`` (peer on GPUs).
+        ``extra_plans``: further operations (``forward_backward``, ``optim_step``,
+        ``forward``) admitted into the same runtime; they must have been planned
+        with the same ``StateLayout`` so that persistent tensors share their homes."""
         self.plan, self.desc = plan, desc
         self.program = plan.program
         self.cuda = device == "cuda"
@@ -204,13 +208,16 @@ class Executor:
         self.hyper = hyper or Hyperparameters()
         self.seed = seed
         self.world, self.rank = desc.world_size, desc.rank
+        extra_plans = dict(extra_plans or {})
+        device_bytes = max([plan.device_bytes] + [p.device_bytes for p, _ in extra_plans.values()])
+        spill_bytes = max([plan.spill_bytes] + [p.spill_bytes for p, _ in extra_plans.values()])
         pool = coll = None
         if self.world > 1:
             from ..parallel import collectives as pc
             mode = ("peer" if device == "cuda" else "dist") if collectives == "auto" else collectives
             if mode == "peer":
                 torch.cuda.set_device(device_index)
-                pool = pc.allocate_symmetric_pool(plan.device_bytes, self.torch_device)
+                pool = pc.allocate_symmetric_pool(device_bytes, self.torch_device)
                 coll = pc.PeerCollectives(pool)
             else:
                 coll = pc.DistCollectives()
@@ -221,7 +228,7 @@ class Executor:
             torch.cuda.set_device(device_index)
             from ..ops import _lib
             _lib.lib()   # fail loudly if the kernel library is missing
-        self.rt = Runtime(plan.device_bytes, plan.spill_bytes, "cuda" if self.cuda else "mock",
+        self.rt = Runtime(device_bytes, spill_bytes, "cuda" if self.cuda else "mock",
                           device_index, trace_capacity=trace_capacity, mock_bps=mock_bps,
                           device_pool=pool)
         self.plan_id = self.rt.admit(plan)
@@ -231,8 +238,50 @@ class Executor:
         self.T, self.n_mb, self.slots = self.runner.T, self.runner.n_mb, self.runner.slots
         self._batch_layout = self.runner.batch_layout_
         self._obj = {o.name: i for i, o in enumerate(self.program.objects)}
-        self._loss_obj = self._obj["loss"]
+        self._loss_obj = self._obj.get("loss", -1)
         self.closed = False
+        self.operation = {"step": "step", "forward_backward": "forward_backward",
+                          "forward": "forward", "optimizer": "optim_step"}.get(desc.mode, desc.mode)
+        self._primary = self._snapshot()
+        self._bound = {self.operation: self._primary}
+        for name, (xplan, xdesc) in extra_plans.items():
+            self._bound[name] = self._bind_extra(xplan, xdesc, stochastic_rounding)
+
+    # ------------------------------------------------------------------ several plans, one state
+    _PLAN_FIELDS = ("plan", "desc", "program", "runner", "plan_id", "_views", "_uses", "T", "n_mb",
+                    "slots", "_batch_layout", "_obj", "_loss_obj")
+
+    def _snapshot(self) -> dict:
+        return {k: getattr(self, k) for k in self._PLAN_FIELDS}
+
+    def _bind_extra(self, plan: Plan, desc: TrainingDescription, sr: bool) -> dict:
+        runner = TaskRunner(plan.program, desc, self.hyper, self.seed, sr, self.collectives)
+        obj = {o.name: i for i, o in enumerate(plan.program.objects)}
+        # persistent tensors of the same name must live at the same spill offset
+        for name, i in obj.items():
+            j = self._obj.get(name)
+            if (j is not None and plan.program.objects[i].persistent
+                    and self.program.objects[j].persistent
+                    and plan.spill_offsets[i] != self.plan.spill_offsets[j]):
+                raise ValueError(f"plans disagree on the spill home of {name}")
+        return {"plan": plan, "desc": desc, "program": plan.program, "runner": runner,
+                "plan_id": self.rt.admit(plan), "_views": {}, "_uses": runner.uses, "T": runner.T,
+                "n_mb": runner.n_mb, "slots": runner.slots, "_batch_layout": runner.batch_layout_,
+                "_obj": obj, "_loss_obj": obj.get("loss", -1)}
+
+    def _select(self, operation: str) -> None:
+        """Makes ``operation``'s plan the current one (counters travel with the executor)."""
+        if operation not in self._bound:
+            raise KeyError(f"no plan admitted for operation {operation!r}; "
+                           f"have {sorted(self._bound)}")
+        done, acc = self.runner.completed_updates, self.runner.accumulated
+        for k, v in self._bound[operation].items():
+            setattr(self, k, v)
+        self.runner.completed_updates, self.runner.accumulated = done, acc
+        self.runner.hyper = self.hyper
+
+    def operations(self) -> list[str]:
+        return sorted(self._bound)
 
     # ------------------------------------------------------------------ state in the spill pool
     def spill_view(self, obj: int) -> torch.Tensor:
@@ -335,7 +384,6 @@ class Executor:
                     view[:] = src
                 total += view.nbytes
             self.runner.max_seqlen[m] = int(mb.max_seqlen)
-        self.spill_view(self._loss_obj).zero_()
         return total
 
     # ------------------------------------------------------------------ views
@@ -366,12 +414,27 @@ class Executor:
         return self.runner.accumulated
 
     # ------------------------------------------------------------------ run
-    def run(self, batch: list[HostMicrobatch], *, trace: bool = False,
-            time_tasks: bool = False) -> InvocationResult:
+    def run(self, batch: list[HostMicrobatch] | None = None, *, operation: str | None = None,
+            trace: bool = False, time_tasks: bool = False) -> InvocationResult:
         if self.closed:
             raise RuntimeError("executor is closed")
         t0 = time.perf_counter()
-        h2d = self.stage_inputs(batch)
+        self._select(operation or self.operation)
+        try:
+            return self._run(batch, trace, time_tasks, t0)
+        finally:
+            self._select_primary()
+
+    def _select_primary(self) -> None:
+        done, acc = self.runner.completed_updates, self.runner.accumulated
+        for k, v in self._primary.items():
+            setattr(self, k, v)
+        self.runner.completed_updates, self.runner.accumulated = done, acc
+
+    def _run(self, batch, trace: bool, time_tasks: bool, t0: float) -> InvocationResult:
+        h2d = self.stage_inputs(batch) if self.n_mb and batch is not None else 0
+        if self._loss_obj >= 0:
+            self.spill_view(self._loss_obj).zero_()
         self.runner.grad_seen = set()
         if trace:
             self.rt.trace_begin()
@@ -407,14 +470,16 @@ class Executor:
         finally:
             if self.cuda:
                 ctx.__exit__(None, None, None)
-        loss = float(self.spill_view(self._loss_obj)[:4].view(torch.float32)[0])   # device -> host result
+        loss = (float(self.spill_view(self._loss_obj)[:4].view(torch.float32)[0])   # device -> host
+                if self._loss_obj >= 0 else 0.0)
         device_seconds = 0.0
         if self.cuda:
             device_seconds = start_ev.elapsed_time(end_ev) * 1e-3
             if events:
                 task_seconds = [a.elapsed_time(b) * 1e-3 for a, b in events]
-        if self.desc.mode == "step":
+        if self.desc.mode in ("step", "optimizer"):
             self.runner.completed_updates += 1
+            self.runner.accumulated = 0
         elif self.desc.mode == "forward_backward":
             self.runner.accumulated += 1
         tr = self.rt.trace_end() if trace else []
@@ -430,9 +495,10 @@ class Executor:
         self.closed = True
         if self.cuda:
             torch.cuda.synchronize(self.torch_device)
-        self._views.clear()
         try:
-            self.rt.close_plan(self.plan_id)
+            for b in self._bound.values():
+                b["_views"].clear()
+                self.rt.close_plan(b["plan_id"])
         finally:
             self.rt.close()
 

@@ -104,7 +104,8 @@ def _build(desc: TrainingDescription) -> Program:
     stages = build_stages(cfg)
     S, n_mb, T = len(stages), geo.n_microbatches, geo.microbatch_tokens
     train = desc.mode != "forward"
-    step = desc.mode == "step"
+    step = desc.mode in ("step", "optimizer")
+    only_optimizer = desc.mode == "optimizer"
     isz = desc.dtype.itemsize
     prog = Program(metadata={"model": cfg.to_json(), "tokens": geo.tokens, "mode": desc.mode,
                              "microbatch_tokens": T, "n_microbatches": n_mb, "slots": geo.slots,
@@ -130,11 +131,25 @@ def _build(desc: TrainingDescription) -> Program:
         if train:
             # gradients persist across calls when accumulation is driven from outside
             G.append(prog.add_object(ObjectSpec(f"{st.name}.gradients", gbytes, "gradient",
-                                                persistent=not step, stage=si)))
+                                                persistent=desc.mode != "step", stage=si)))
         if step:
             sh = "sharded" if sharded else "whole"
             M.append(prog.add_object(ObjectSpec(f"{st.name}.exp_avg", pbytes, "optimizer_state", True, stage=si, sharding=sh)))
             V.append(prog.add_object(ObjectSpec(f"{st.name}.exp_avg_sq", pbytes, "optimizer_state", True, stage=si, sharding=sh)))
+    if only_optimizer:
+        # the update alone: gradients accumulated by earlier forward_backward calls are state
+        prog.metadata["n_microbatches"] = 0
+        for si in reversed(range(S)):
+            st = stages[si]
+            pbytes = prog.objects[W[si]].bytes
+            prog.add_task(TaskSpec(f"O.{st.name}", "optimizer", si, -1,
+                                   [UseSpec(W[si], "mutate", "params"), UseSpec(G[si], "read", "grads"),
+                                    UseSpec(M[si], "mutate", "m"), UseSpec(V[si], "mutate", "v")],
+                                   estimate_duration_ns(0.0, 8.0 * pbytes), 0,
+                                   "adamw_dp" if sharded else "adamw",
+                                   profile_key=f"opt:{pbytes}:{world}"))
+        prog.validate()
+        return prog
     _, in_bytes = batch_layout(T, geo.slots)
     IN = [prog.add_object(ObjectSpec(f"batch.{m}", in_bytes, "input", True, pinned_resident=True,
                                      microbatch=m)) for m in range(n_mb)]
@@ -197,7 +212,7 @@ def _build(desc: TrainingDescription) -> Program:
                 UseSpec(A[si - 1][m], "read", "x"), UseSpec(LOSS, "mutate", "loss")]
         if train:
             uses.append(UseSpec(DX[m], "create", "dx"))
-            if step and not grad_created[si]:
+            if desc.mode == "step" and not grad_created[si]:
                 uses.append(UseSpec(G[si], "create", "grads")); grad_created[si] = True
             else:
                 uses.append(UseSpec(G[si], "mutate", "grads"))
@@ -218,7 +233,7 @@ def _build(desc: TrainingDescription) -> Program:
             uses.append(UseSpec(A[si - 1][m], "read", "x"))
         if (si, m) in SAVED:
             uses.append(UseSpec(SAVED[(si, m)], "read", "saved"))
-        if step and not grad_created[si]:
+        if desc.mode == "step" and not grad_created[si]:
             uses.append(UseSpec(G[si], "create", "grads")); grad_created[si] = True
         else:
             uses.append(UseSpec(G[si], "mutate", "grads"))
@@ -241,6 +256,7 @@ def _build(desc: TrainingDescription) -> Program:
     body = list(range(S - 1))
     mbs = list(range(n_mb))
     back_mbs = list(reversed(mbs)) if order.reverse_breadth else mbs
+    step = desc.mode == "step"      # from here on: does this program contain the update?
     if order.walk == "breadth":
         for si in body:
             for m in mbs:
@@ -289,17 +305,26 @@ def build_step(cfg: DecoderConfig, geometry: BatchGeometry,
 
 
 def build_forward_backward(cfg, geometry, ordering=None, *, dtype=torch.bfloat16, grad_dtype=None,
-                           selection=None):
+                           selection=None, world_size=1, rank=0):
     """Gradient accumulation without the update (gradients are persistent state)."""
     desc = TrainingDescription(cfg, geometry, ordering or StepDataOrdering(), dtype,
-                               grad_dtype or dtype, dict(selection or {}), "forward_backward")
+                               grad_dtype or dtype, dict(selection or {}), "forward_backward",
+                               world_size, rank)
     return _build(desc), desc
 
 
-def build_forward(cfg, geometry, ordering=None, *, dtype=torch.bfloat16):
+def build_forward(cfg, geometry, ordering=None, *, dtype=torch.bfloat16, world_size=1, rank=0):
     """Evaluation: forward passes and the loss only."""
     desc = TrainingDescription(cfg, geometry, ordering or StepDataOrdering(), dtype, dtype, {},
-                               "forward")
+                               "forward", world_size, rank)
+    return _build(desc), desc
+
+
+def build_optimizer(cfg, geometry, *, dtype=torch.bfloat16, grad_dtype=None, world_size=1, rank=0):
+    """The optimizer update alone, over gradients that earlier ``forward_backward``
+    invocations left in the spill pool (the ``optim_step`` operation)."""
+    desc = TrainingDescription(cfg, geometry, StepDataOrdering(), dtype, grad_dtype or dtype, {},
+                               "optimizer", world_size, rank)
     return _build(desc), desc
 
 

@@ -67,9 +67,29 @@ class MemoryBudgets:
         return MemoryBudgets(int(device_gib * GIB), int(spill_gib * GIB))
 
 
+@dataclass
+class StateLayout:
+    """Spill homes shared by every plan of one run: persistent tensors keep the
+    same offset whichever operation's plan is executing."""
+    offsets: dict[str, int] = field(default_factory=dict)
+    reserved: int = 0
+
+    @staticmethod
+    def build(programs: list[Program]) -> "StateLayout":
+        lay = StateLayout()
+        for prog in programs:
+            for o in prog.objects:
+                if o.persistent and o.kind in ("weight", "optimizer_state", "gradient") \
+                        and o.name not in lay.offsets:
+                    lay.offsets[o.name] = lay.reserved
+                    lay.reserved += -(-o.bytes // 4096) * 4096
+        return lay
+
+
 def plan_program(program: Program, budgets: MemoryBudgets,
                  communication: CommunicationInfo | None = None,
-                 options: SearchOptions | None = None) -> Plan:
+                 options: SearchOptions | None = None,
+                 state_layout: StateLayout | None = None) -> Plan:
     communication = communication or CommunicationInfo()
     options = options or SearchOptions()
     program.validate()
@@ -120,9 +140,12 @@ def plan_program(program: Program, budgets: MemoryBudgets,
                                   [st.offset for st in stays])
     # ---- spill homes: persistent objects first, then evicted transients by lifetime
     spill_offsets = [-1] * len(program.objects)
-    cursor = 0
+    cursor = state_layout.reserved if state_layout else 0
     for i, o in enumerate(program.objects):
         if o.persistent:
+            if state_layout and o.name in state_layout.offsets:
+                spill_offsets[i] = state_layout.offsets[o.name]
+                continue
             spill_offsets[i] = cursor
             cursor += -(-o.bytes // 4096) * 4096
     persistent_end = cursor
@@ -188,14 +211,15 @@ class SweepResult:
 
 def sweep_programs(programs: list[Program], budgets: MemoryBudgets,
                    communication: CommunicationInfo | None = None,
-                   options: SearchOptions | None = None, threads: int = 4) -> SweepResult:
+                   options: SearchOptions | None = None, threads: int = 4,
+                   state_layout: StateLayout | None = None) -> SweepResult:
     """Plan every candidate program and keep the one with the shortest simulated step."""
     plans: list[Plan | None] = [None] * len(programs)
     errors = [""] * len(programs)
 
     def one(i: int) -> None:
         try:
-            plans[i] = plan_program(programs[i], budgets, communication, options)
+            plans[i] = plan_program(programs[i], budgets, communication, options, state_layout)
         except PlanningError as exc:
             errors[i] = str(exc)
 

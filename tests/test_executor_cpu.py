@@ -81,3 +81,49 @@ def test_steady_state_creates_no_events():
     assert after["events_created"] == before["events_created"]
     assert after["host_allocations"] == before["host_allocations"]
     ex.close()
+
+
+def test_operations_share_state_across_plans():
+    """forward_backward twice + optim_step, then forward, through four plans over one
+    spill-resident state, against the resident trainer doing the same calls."""
+    from shadowspill_b200.frontend.capture import (build_forward, build_forward_backward,
+                                                   build_optimizer)
+    from shadowspill_b200.planning.plan import StateLayout
+    cfg = preset("llama3-tiny")
+    geo = BatchGeometry(microbatch_tokens=256, n_microbatches=2, slots=16, mean_seqlen=64)
+    built = {"step": build_step(cfg, geo, dtype=torch.float32),
+             "forward_backward": build_forward_backward(cfg, geo, dtype=torch.float32),
+             "optim_step": build_optimizer(cfg, geo, dtype=torch.float32),
+             "forward": build_forward(cfg, geo, dtype=torch.float32)}
+    layout = StateLayout.build([p for p, _ in built.values()])
+    budgets = MemoryBudgets(24 << 20, 64 << 20, headroom_bytes=0)
+    opts = SearchOptions(minimum_object_bytes_evict_eligible=1024, workers=1)
+    plans = {k: (plan_program(p, budgets, CommunicationInfo(), opts, layout), d)
+             for k, (p, d) in built.items()}
+    hyper = Hyperparameters(lr=3e-3)
+    step_plan, step_desc = plans.pop("step")
+    ex = Executor(step_plan, step_desc, device="cpu", seed=5, hyper=hyper, extra_plans=plans)
+    ex.initialize()
+    assert ex.operations() == ["forward", "forward_backward", "optim_step", "step"]
+    ref = ResidentTrainer(cfg, device="cpu", dtype=torch.float32, seed=5, lr=3e-3)
+    for round_ in range(2):
+        for call in range(2):
+            host = _batches(cfg, 10 * round_ + call)
+            got = ex.run(host, operation="forward_backward").loss
+            ref.loss_sum.zero_()
+            for m in host:
+                ref.forward_backward(to_device(m, "cpu"))
+            assert abs(got - float(ref.loss_sum)) < 1e-5 * max(1.0, abs(got))
+        ex.run(operation="optim_step")
+        ref.optim_step()
+        assert ex.completed_updates == round_ + 1 and ex.accumulated == 0
+    host = _batches(cfg, 99)
+    assert abs(ex.run(host, operation="forward").loss -
+               ref.evaluate([to_device(m, "cpu") for m in host])) < 1e-5
+    want = ref.step([to_device(m, "cpu") for m in host])
+    assert abs(ex.run(host, operation="step").loss - want) < 1e-5 * abs(want)
+    got = ex.state_dict()
+    for k, v in ref.state_dict().items():
+        # microbatches accumulate in another order (reverse walk), hence a few fp32 ulps
+        assert torch.allclose(got[k], v, rtol=1e-4, atol=2e-5), (k, float((got[k] - v).abs().max()))
+    ex.close()
