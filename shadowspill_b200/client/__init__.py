@@ -1,0 +1,18 @@
+"""Client package: NumPy-only API to a training service.
+
+    from shadowspill_b200.client import ServiceClient, Model, Optimizer, Memory, BatchConfig
+    with ServiceClient("http://127.0.0.1:8765") as svc:
+        trainer = svc.create_training_client(Model("llama3-8b"), Optimizer(lr=1e-4),
+                                             memory=Memory(24, 128)).result()
+        result = trainer.step(text_batch(sequences)).result()
+"""
+from .config import (BatchConfig, BuildOptions, Execution, LoRA, Memory, Model, Objective,  # noqa: F401
+                     Operation, Optimizer, PlanningOptions, Policy, Preparation, ProfilingOptions,
+                     Resources, Weights)
+from .display import CommandTable  # noqa: F401
+from .packing import BatchError, BatchValidator, pack_batch  # noqa: F401
+from .parallelism import MIN_SHARD_BYTES, data_parallel, expert_parallel  # noqa: F401
+from .schedules import Constant, WarmupCosine  # noqa: F401
+from .service import ServiceClient  # noqa: F401
+from .text import Datum, build_candidates, text_batch, text_datum  # noqa: F401
+from .training import OperationFailed, TrainingClient, TrainingResult  # noqa: F401

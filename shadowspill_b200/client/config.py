@@ -1,0 +1,204 @@
+"""Training settings: ``Model``, ``Weights``, ``LoRA``, ``Objective``, ``Optimizer``,
+``BatchConfig``, ``Memory``, ``Execution``, ``Preparation`` and friends.
+
+The names and meanings follow the reference client
+(packages/client/src/shadowspill_client/config/{model,batch,execution,preparation,
+resources,operations}.py); every record is frozen, validated and serialises to
+plain JSON.
+"""
+from __future__ import annotations
+
+from typing import Any
+
+from ._records import record, require
+
+
+@record
+class Weights:
+    source: str = "random"          # random | checkpoint | artifact
+    seed: int = 0
+    location: str = ""              # checkpoint directory or artifact id
+
+    @staticmethod
+    def random(seed: int = 0) -> "Weights":
+        return Weights("random", seed)
+
+    @staticmethod
+    def checkpoint(location: str) -> "Weights":
+        return Weights("checkpoint", 0, location)
+
+    @staticmethod
+    def artifact(artifact_id: str) -> "Weights":
+        return Weights("artifact", 0, artifact_id)
+
+    def validate(self):
+        require(self.source in ("random", "checkpoint", "artifact"), f"unknown weights source {self.source!r}")
+        require(self.source == "random" or bool(self.location), "weights location is required")
+
+
+@record
+class LoRA:
+    rank: int = 16
+    alpha: float = 32.0
+    targets: tuple = ("attention", "experts")
+
+    def validate(self):
+        require(self.rank > 0, "LoRA rank must be positive")
+
+
+@record
+class Model:
+    name: str = "llama3-8b"                   # catalog name <family>-<size>
+    config: dict | None = None                # explicit architecture (overrides the catalog)
+    weights: Weights = Weights()
+    lora: LoRA | None = None
+    dtype: str = "bfloat16"
+
+    @staticmethod
+    def from_pretrained(location: str, name: str) -> "Model":
+        return Model(name=name, weights=Weights.checkpoint(location))
+
+    def validate(self):
+        require(bool(self.name) or self.config is not None, "a model needs a name or a config")
+        require(self.dtype in ("bfloat16", "float32"), f"unsupported dtype {self.dtype!r}")
+
+
+@record
+class Objective:
+    id: str = "shadowspill/cross_entropy@1"
+    config: dict | None = None
+    terms: tuple = ()
+
+    @staticmethod
+    def sum(*terms: "Objective") -> "Objective":
+        return Objective("shadowspill/sum@1", None, tuple(terms))
+
+    def validate(self):
+        require("@" in self.id, "objective ids are versioned: name@version")
+
+
+@record
+class Optimizer:
+    id: str = "adamw@1"
+    lr: float = 1e-4
+    beta1: float = 0.9
+    beta2: float = 0.95
+    eps: float = 1e-8
+    weight_decay: float = 0.0
+    gradient_dtype: str = "bfloat16"
+    opt_state_dtype: str = "bfloat16"
+    master_dtype: str = "bfloat16"
+    parameter_rounding: str = "stochastic"    # nearest | stochastic
+    opt_state_rounding: str = "stochastic"
+
+    def validate(self):
+        require(self.lr >= 0 and 0 <= self.beta1 < 1 and 0 <= self.beta2 < 1, "bad AdamW hyperparameters")
+        require(self.parameter_rounding in ("nearest", "stochastic"), "bad parameter_rounding")
+        require(self.opt_state_rounding in ("nearest", "stochastic"), "bad opt_state_rounding")
+
+
+@record
+class BatchConfig:
+    tokens_per_step: int = 65536              # per worker
+    microbatch_tokens: int = 8192
+    max_datums: int = 0                       # 0 = derived from the microbatch size
+    packing: str = "best_fit"                 # best_fit | balanced
+
+    def validate(self):
+        require(self.microbatch_tokens > 0 and self.tokens_per_step % self.microbatch_tokens == 0,
+                "tokens_per_step must be a positive multiple of microbatch_tokens")
+        require(self.packing in ("best_fit", "balanced"), "unknown packing policy")
+
+    @property
+    def microbatches(self) -> int:
+        return self.tokens_per_step // self.microbatch_tokens
+
+
+@record
+class Memory:
+    device_gib: float = 0.0                   # 0 = automatic: 90 % of the device
+    spill_gib: float = 0.0                    # 0 = automatic: 90 % of free host memory
+
+    def validate(self):
+        require(self.device_gib >= 0 and self.spill_gib >= 0, "memory budgets are non-negative")
+
+
+@record
+class Execution:
+    seed: int = 0
+    max_staging_bytes: int = 1 << 30
+    max_pending_requests: int = 8
+    idle_timeout_seconds: float = 0.0         # 0 = never
+    runtime_trace: bool = False
+    profiler_annotations: bool = False
+    reject_overbudget: bool = True
+    nsys: dict | None = None                  # accepted for parity; capture is unavailable here
+    collectives: str = "auto"                 # peer | dist | auto
+
+
+@record
+class Policy:
+    id: str
+    config: dict | None = None
+
+
+@record
+class BuildOptions:
+    walks: tuple = ("breadth",)
+    recompute_shares: tuple = (100,)
+    saved_variant: str = "save_attention"
+    projection_chunks: tuple = ()
+    moe_chunks: tuple = ()
+
+
+@record
+class ProfilingOptions:
+    enabled: bool = True
+    min_samples: int = 3
+    max_samples: int = 8
+    tolerance: float = 0.03
+
+
+@record
+class PlanningOptions:
+    strategies: tuple = ("stall", "traffic")
+    fetch_rules: tuple = ("demand", "latest-safe", "packed-fifo", "packed-fit")
+    workers: int = 0
+    max_repairs: int = 16
+    minimum_object_bytes_evict_eligible: int = 1 << 20
+    deterministic: bool = False
+
+
+@record
+class Preparation:
+    build: BuildOptions = BuildOptions()
+    profiling: ProfilingOptions = ProfilingOptions()
+    planning: PlanningOptions = PlanningOptions()
+    policies: tuple = ()
+    calibrate: bool = True
+
+
+@record
+class Resources:
+    gpus: int = 1
+    node: str = ""                            # "" = the service's own node
+    backend: str = "cuda"                     # cuda | cpu (mock backend, functional runs)
+
+
+@record
+class Operation:
+    name: str                                 # step | forward_backward | forward | optim_step
+    enabled: bool = True
+
+
+def training_setup(model: Model, optimizer: Optimizer = Optimizer(), objective: Objective = Objective(),
+                   batch: BatchConfig = BatchConfig(), memory: Memory = Memory(),
+                   execution: Execution = Execution(), preparation: Preparation = Preparation(),
+                   resources: Resources = Resources(), parallelism: dict | None = None,
+                   operations: tuple = ("step",)) -> dict[str, Any]:
+    """The JSON body of a run-creation request."""
+    return {"model": model.to_json(), "optimizer": optimizer.to_json(),
+            "objective": objective.to_json(), "batch": batch.to_json(), "memory": memory.to_json(),
+            "execution": execution.to_json(), "preparation": preparation.to_json(),
+            "resources": resources.to_json(), "parallelism": parallelism or {},
+            "operations": list(operations)}

@@ -1,0 +1,114 @@
+"""``ServiceClient``: connection to a training service.
+
+Connecting is blocking; every later call returns a future run by a bounded
+thread pool; nothing is retried automatically. Reference:
+packages/client/src/shadowspill_client/service.py:49-611.
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import time
+import uuid
+from typing import Any
+
+from .config import (BatchConfig, Execution, Memory, Model, Objective, Optimizer, Preparation,
+                     Resources, training_setup)
+from .training import TrainingClient
+from .transport import HTTPTransport, TransportError
+
+
+class ServiceClient:
+    def __init__(self, url: str, token: str = "", timeout: float = 600.0, max_workers: int = 8):
+        self.transport = HTTPTransport(url, token, timeout)
+        _, self.info = self.transport.request("GET", "/v1/info")     # blocking connect
+        self.pool = cf.ThreadPoolExecutor(max_workers=max_workers)
+        self.session = uuid.uuid4().hex[:12]
+
+    # ------------------------------------------------------------------ discovery
+    def list_hardware(self) -> cf.Future:
+        return self.pool.submit(lambda: self.transport.request("GET", "/v1/hardware")[1])
+
+    def describe_training(self, **setup) -> cf.Future:
+        """Resolves settings and previews workers and memory without reserving anything."""
+        body = training_setup(**setup)
+        return self.pool.submit(lambda: self.transport.request("POST", "/v1/training/describe", body)[1])
+
+    # ------------------------------------------------------------------ runs
+    def _create(self, body: dict[str, Any], wait: bool, timeout: float) -> dict[str, Any]:
+        _, info = self.transport.request("POST", f"/v1/runs/{self.session}", body)
+        run = info["run"]
+        deadline = time.monotonic() + timeout
+        while wait and info["state"] == "preparing":
+            if time.monotonic() > deadline:
+                raise TimeoutError("run did not become ready in time")
+            time.sleep(0.2)
+            _, info = self.transport.request("GET", f"/v1/runs/{self.session}/{run}")
+        if info["state"] == "failed":
+            raise RuntimeError(f"run creation failed: {info.get('error', '')}")
+        return info
+
+    def create_training_client(self, model: Model, optimizer: Optimizer = Optimizer(),
+                               objective: Objective = Objective(), batch: BatchConfig = BatchConfig(),
+                               memory: Memory = Memory(), execution: Execution = Execution(),
+                               preparation: Preparation = Preparation(),
+                               resources: Resources = Resources(), parallelism: dict | None = None,
+                               operations: tuple = ("step",), plans: str | None = None,
+                               checkpoint: str | None = None, timeout: float = 3600.0) -> cf.Future:
+        body = training_setup(model, optimizer, objective, batch, memory, execution, preparation,
+                              resources, parallelism, operations)
+        body["plans"], body["checkpoint"] = plans, checkpoint
+
+        def work() -> TrainingClient:
+            info = self._create(body, True, timeout)
+            return TrainingClient(self.transport, self.session, info["run"], info,
+                                  execution.max_staging_bytes, execution.max_pending_requests)
+        return self.pool.submit(work)
+
+    def prepare_training(self, **setup) -> cf.Future:
+        """Runs build/profile/plan only and stores the plans under the run."""
+        body = training_setup(**setup)
+        body["prepare_only"] = True
+        return self.pool.submit(lambda: self._create(body, True, 3600.0))
+
+    def plan_training(self, **setup) -> cf.Future:
+        """Plans against modelled task costs without touching a GPU (simulation only)."""
+        body = training_setup(**setup)
+        body["prepare_only"], body["simulation_only"] = True, True
+        return self.pool.submit(lambda: self._create(body, True, 3600.0))
+
+    def get_training_client(self, run: str) -> cf.Future:
+        """Attaches to a running run as its writer; any earlier writer is fenced."""
+        def work():
+            _, info = self.transport.request("GET", f"/v1/runs/{self.session}/{run}")
+            return TrainingClient(self.transport, self.session, run, info)
+        return self.pool.submit(work)
+
+    # ------------------------------------------------------------------ observations
+    def get_metrics(self, run: str, after: int = 0, limit: int = 1000) -> cf.Future:
+        return self.pool.submit(lambda: self.transport.request(
+            "GET", f"/v1/runs/{self.session}/{run}/metrics", query={"after": after, "limit": limit})[1])
+
+    def get_plans(self, run: str, page: int = 0) -> cf.Future:
+        return self.pool.submit(lambda: self.transport.request(
+            "GET", f"/v1/runs/{self.session}/{run}/plans", query={"page": page})[1])
+
+    def get_plan_report(self, run: str, directory: str | None = None) -> cf.Future:
+        return self.pool.submit(lambda: self.transport.request(
+            "POST", f"/v1/runs/{self.session}/{run}/plans/report", {"directory": directory})[1])
+
+    def get_progress(self, run: str, after: int = 0) -> cf.Future:
+        return self.pool.submit(lambda: self.transport.request(
+            "GET", f"/v1/runs/{self.session}/{run}/progress", query={"after": after})[1])
+
+    def get_nsys(self, run: str, rank: int = 0) -> cf.Future:
+        return self.pool.submit(lambda: self.transport.request(
+            "GET", f"/v1/runs/{self.session}/{run}/nsys", query={"rank": rank})[1])
+
+    def close(self) -> None:
+        self.pool.shutdown(wait=False)
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()

@@ -1,0 +1,172 @@
+"""``TrainingClient``: ordered, dependency-chained asynchronous training operations.
+
+Every call validates and packs its batch locally, registers an operation request
+with the run (earlier pending requests become explicit dependencies), uploads
+the input with back-pressure, and returns a future whose ``result()`` is a
+``TrainingResult``. Staging is bounded by ``max_staging_bytes`` and
+``max_pending_requests``. Reference: packages/client/src/shadowspill_client/training.py:117-1043.
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import threading
+import time
+import uuid
+from dataclasses import dataclass, field
+from typing import Any
+
+from .packing import BatchError, BatchValidator, pack_batch
+from .protocol import OperationRequest, OperationResult, encode_microbatches
+from .text import Datum
+from .transport import HTTPTransport, TransportError
+
+
+@dataclass
+class TrainingResult:
+    loss: float | None
+    metrics: dict[str, float]
+    completed_updates: int
+    execution_seconds: float
+    request_id: str
+    outputs: dict[str, Any] = field(default_factory=dict)
+
+
+class OperationFailed(RuntimeError):
+    def __init__(self, result: OperationResult):
+        self.result = result
+        super().__init__(f"{result.state}: {result.error} (effect: {result.effect})")
+
+
+class TrainingClient:
+    def __init__(self, transport: HTTPTransport, session: str, run: str, info: dict[str, Any],
+                 max_staging_bytes: int = 1 << 30, max_pending_requests: int = 8):
+        self.transport, self.session, self.run = transport, session, run
+        self.route = f"/v1/runs/{session}/{run}"
+        self.info = info
+        geo = info["geometry"]
+        self.microbatch_tokens, self.microbatches = geo["microbatch_tokens"], geo["microbatches"]
+        self.slots, self.vocab, self.workers = geo["slots"], geo["vocab_size"], geo["workers"]
+        self.packing = geo.get("packing", "best_fit")
+        self.validator = BatchValidator(self.vocab, self.microbatch_tokens,
+                                        self.microbatches * self.workers, self.slots)
+        self.writer_id = uuid.uuid4().hex
+        self.transport.request("POST", f"{self.route}/writers/{self.writer_id}", {})
+        self.pool = cf.ThreadPoolExecutor(max_workers=max(2, max_pending_requests))
+        self.max_staging_bytes, self.max_pending = max_staging_bytes, max_pending_requests
+        self._lock = threading.Condition()
+        self._pending: dict[str, cf.Future] = {}
+        self._staged = 0
+        self._closed = False
+        self._local_metrics: list[dict[str, Any]] = []
+
+    # ------------------------------------------------------------------ batches
+    def validate_batch(self, datums: list[Datum]) -> None:
+        self.validator.validate(datums)
+
+    def _pack(self, datums: list[Datum]) -> bytes:
+        self.validate_batch(datums)
+        mbs = pack_batch(datums, microbatch_tokens=self.microbatch_tokens,
+                         microbatches=self.microbatches * self.workers, slots=self.slots,
+                         policy=self.packing)
+        return encode_microbatches(mbs)
+
+    # ------------------------------------------------------------------ submission
+    def _submit(self, operation: str, payload: bytes | None = None, **arguments) -> cf.Future:
+        if self._closed:
+            raise RuntimeError("training client is closed")
+        size = len(payload) if payload else 0
+        with self._lock:
+            while (len(self._pending) >= self.max_pending or
+                   (self._staged and self._staged + size > self.max_staging_bytes)):
+                self._lock.wait(0.05)
+            deps = list(self._pending)
+            req = OperationRequest(operation, dependencies=deps, arguments=arguments,
+                                   has_input=payload is not None, writer_id=self.writer_id)
+            self._staged += size
+            fut = self.pool.submit(self._drive, req, payload)
+            self._pending[req.request_id] = fut
+
+        def done(_f, rid=req.request_id, n=size):
+            with self._lock:
+                self._pending.pop(rid, None)
+                self._staged -= n
+                self._lock.notify_all()
+        fut.add_done_callback(done)
+        return fut
+
+    def _drive(self, req: OperationRequest, payload: bytes | None) -> TrainingResult:
+        body = {"operation": req.operation, "request_id": req.request_id,
+                "dependencies": req.dependencies, "arguments": req.arguments,
+                "has_input": req.has_input, "writer_id": req.writer_id, "digest": req.digest()}
+        self.transport.request("POST", f"{self.route}/requests", body)
+        if payload is not None:
+            delay = 0.05
+            while True:
+                try:
+                    self.transport.request("PUT", f"{self.route}/requests/{req.request_id}/input", payload)
+                    break
+                except TransportError as exc:
+                    if exc.status != 429:      # back-pressure: the server asks to retry later
+                        raise
+                    time.sleep(delay)
+                    delay = min(1.0, delay * 2)
+        while True:
+            _, data = self.transport.request("GET", f"{self.route}/requests/{req.request_id}",
+                                             query={"wait": "completed", "timeout": 30})
+            res = OperationResult(**data)
+            if res.done:
+                break
+        if res.state != "completed":
+            raise OperationFailed(res)
+        return TrainingResult(res.loss, res.metrics, res.completed_updates, res.execution_seconds,
+                              res.request_id, res.outputs)
+
+    # ------------------------------------------------------------------ operations
+    def step(self, datums: list[Datum], *, lr: float | None = None) -> cf.Future:
+        """Forward, backward and one optimizer update on one global batch."""
+        return self._submit("step", self._pack(datums), lr=lr)
+
+    def forward_backward(self, datums: list[Datum]) -> cf.Future:
+        """Accumulates gradients; the first contribution after an update writes them fresh."""
+        return self._submit("forward_backward", self._pack(datums))
+
+    def optim_step(self, *, grad_scale: float = 1.0, lr: float | None = None) -> cf.Future:
+        return self._submit("optim_step", None, grad_scale=grad_scale, lr=lr)
+
+    def forward(self, datums: list[Datum], mode: str = "evaluation") -> cf.Future:
+        return self._submit("forward", self._pack(datums), mode=mode)
+
+    def discard_gradients(self) -> cf.Future:
+        return self._submit("discard", None)
+
+    def save_checkpoint(self, name: str, metadata: dict | None = None) -> cf.Future:
+        return self._submit("save", None, name=name, metadata=metadata or {})
+
+    def load_checkpoint(self, checkpoint_id: str) -> cf.Future:
+        return self._submit("restore", None, name=checkpoint_id)
+
+    def export_weights(self, name: str) -> cf.Future:
+        return self._submit("export", None, name=name)
+
+    # ------------------------------------------------------------------ observations
+    def log_metrics(self, step: int, **values: float) -> None:
+        self.transport.request("POST", f"{self.route}/metrics", {"step": step, "values": values})
+
+    def report(self, directory: str | None = None) -> dict:
+        _, data = self.transport.request("POST", f"{self.route}/report", {"directory": directory})
+        return data
+
+    def close(self) -> None:
+        if self._closed:
+            return
+        try:
+            self._submit("close", None).result()
+        finally:
+            self._closed = True
+            self.pool.shutdown(wait=False)
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()

@@ -1,0 +1,258 @@
+"""Training service: HTTP endpoint, run creation, live runs, durable records.
+
+``Server(service_root).serve()`` listens on loopback (or a given address),
+authenticates with a bearer token when one is configured, creates runs in
+background threads (resolve settings -> admission lease -> worker group ->
+controller), and answers the REST surface a ``ServiceClient`` speaks. All heavy
+work happens in worker processes; this process never touches a GPU beyond
+inventory. Reference: packages/engine/src/shadowspill/server/{service.py:33,334,
+http.py:179,373-520, jobs.py, live.py, routes/*.py}.
+"""
+from __future__ import annotations
+
+import json
+import os
+import threading
+import time
+import traceback
+import urllib.parse
+import uuid
+from dataclasses import asdict
+from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+from pathlib import Path
+from typing import Any
+
+from ..client.protocol import OperationResult, decode_microbatches, encode_microbatches
+from ..orchestration.nodes import AdmissionError, Membership, NodeAdmission, device_inventory
+from ..training.components import default_registry, resolve_training
+from ..training.controller import Rejected, RunController
+from ..training.group import WorkerFailure, WorkerGroup
+from .journal import Journal
+
+GIB = 1 << 30
+
+
+class LiveRun:
+    """One run: its workers, controller, journal and observations."""
+
+    def __init__(self, server: "Server", session: str, run: str, body: dict[str, Any]):
+        self.server, self.session, self.run, self.body = server, session, run, body
+        self.dir = server.root / "runs" / session / run
+        self.dir.mkdir(parents=True, exist_ok=True)
+        self.journal = Journal(self.dir / "journal")
+        self.state, self.error = "preparing", ""
+        self.progress: list[str] = []
+        self.metrics: list[dict[str, Any]] = []
+        self.group: WorkerGroup | None = None
+        self.controller: RunController | None = None
+        self.resolved = None
+        self.lease: str | None = None
+        self.plan_summary: dict[str, Any] = {}
+        self.plan_names: dict[str, str] = {}
+        self.checkpoints: dict[str, str] = {}
+        self.thread = threading.Thread(target=self._create, name=f"create-{run}", daemon=True)
+        self.thread.start()
+
+    def log(self, msg: str) -> None:
+        stamp = time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime())
+        self.progress.append(f"{stamp} [run={self.run} +{time.monotonic() - self.server.t0:.1f}s] {msg}")
+
+    def _create(self) -> None:
+        try:
+            self.journal.append("created", {"session": self.session, "run": self.run})
+            self.log("resolving settings")
+            self.resolved = resolve_training(self.body, self.server.registry, self.server.hardware)
+            r = self.resolved
+            host_bytes = int(r.budgets["spill_gib"] * GIB) * r.workers
+            gpus = r.workers if r.setups[0]["device"] == "cuda" else 0
+            self.lease, devices = self.server.admission.lease(gpus, host_bytes)
+            for setup, dev in zip(r.setups, devices or [0] * r.workers):
+                setup["device_index"] = dev
+            ckpt = self.body.get("checkpoint")
+            if ckpt:
+                ckpt = self.server.resolve_checkpoint(self.session, ckpt)
+            self.log(f"starting {r.workers} worker(s): build, profile, plan")
+            self.group = WorkerGroup(r.setups, self.dir / "logs", checkpoint=ckpt,
+                                     on_progress=self.log)
+            self.plan_summary = self.group.ready_info[0].get("plan_summary", {})
+            self.journal.append("ready", {"workers": r.workers, "plan": self.plan_summary})
+            if self.body.get("prepare_only"):
+                self.group.stop()
+                self.group = None
+                self.server.admission.release(self.lease)
+                self.state = "prepared"
+                return
+            self.controller = RunController(self._execute, self.journal,
+                                            idle_timeout=float(self.body.get("execution", {})
+                                                               .get("idle_timeout_seconds", 0) or 0))
+            # a run restored from a checkpoint continues that checkpoint's update count
+            self.controller.state.b.completed_updates = int(
+                self.group.ready_info[0].get("completed_updates", 0))
+            self.state = "ready"
+            self.log("ready")
+        except Exception as exc:  # noqa: BLE001
+            self.error = f"{type(exc).__name__}: {exc}"
+            self.state = "failed"
+            self.log("failed: " + self.error)
+            self.journal.append("failed", {"error": self.error, "traceback": traceback.format_exc()[-2000:]})
+            self.release()
+
+    def _execute(self, req: dict[str, Any], payload: bytes | None) -> dict[str, Any]:
+        op, args = req["operation"], dict(req.get("arguments", {}))
+        payloads = None
+        if payload is not None:
+            mbs = decode_microbatches(payload)
+            w, per = self.resolved.workers, self.resolved.geometry["microbatches"]
+            if len(mbs) != w * per:
+                raise WorkerFailure(f"expected {w * per} microbatches, got {len(mbs)}", "not_started")
+            payloads = [encode_microbatches(mbs[r * per:(r + 1) * per]) for r in range(w)]   # route
+        if op in ("save", "export"):
+            name = args.get("name") or uuid.uuid4().hex[:8]
+            args["directory"] = str(self.server.root / "checkpoints" / self.session / name)
+            self.checkpoints[name] = args["directory"]
+            op_worker = "save"
+        elif op == "restore":
+            args["directory"] = self.server.resolve_checkpoint(self.session, args["name"])
+            op_worker = "restore"
+        else:
+            op_worker = op
+        t0 = time.perf_counter()
+        replies = self.group.execute(req["request_id"], op_worker, args, payloads)
+        out: dict[str, Any] = {"execution_seconds": max(r.get("execution_seconds", 0.0) for r in replies)}
+        losses = [r["loss"] for r in replies if r.get("loss") is not None]
+        if losses:
+            out["loss"] = float(sum(losses))          # objectives sum; weights already carry 1/N
+        out["metrics"] = {"wall_seconds": time.perf_counter() - t0,
+                          **{k: v for k, v in (replies[0].get("metrics") or {}).items()}}
+        out["outputs"] = replies[0].get("outputs", {})
+        if op in ("save", "export"):
+            out["outputs"] = {"checkpoint": args.get("name"), "directory": args["directory"]}
+        if op in ("step", "optim_step") and out.get("loss") is not None:
+            self.metrics.append({"update": replies[0].get("completed_updates"), "loss": out["loss"],
+                                 "execution_seconds": out["execution_seconds"]})
+        if op == "close":
+            self.state = "closed"
+            threading.Thread(target=self.release, daemon=True).start()
+        return out
+
+    def release(self) -> None:
+        if self.group is not None:
+            try:
+                self.group.stop()
+            except Exception:  # noqa: BLE001
+                pass
+            self.group = None
+        if self.lease:
+            self.server.admission.release(self.lease)
+            self.lease = None
+
+    def info(self) -> dict[str, Any]:
+        geo = self.resolved.geometry if self.resolved else {}
+        return {"session": self.session, "run": self.run, "state": self.state, "error": self.error,
+                "workers": self.resolved.workers if self.resolved else 0, "geometry": geo,
+                "plan_summary": self.plan_summary,
+                "provenance": self.resolved.provenance if self.resolved else {},
+                "budgets": self.resolved.budgets if self.resolved else {},
+                "state_valid": (self.controller.boundary()["valid"] if self.controller else True),
+                "boundary": self.controller.boundary() if self.controller else {}}
+
+
+class Server:
+    def __init__(self, service_root: str | Path, model_root: str | Path | None = None,
+                 host: str = "127.0.0.1", port: int = 0, token: str | None = None):
+        self.root = Path(service_root)
+        self.root.mkdir(parents=True, exist_ok=True)
+        self.model_root = Path(model_root) if model_root else None
+        self.host, self.port = host, port
+        self.token = token if token is not None else os.environ.get("SHADOWSPILL_TOKEN", "")
+        self.node_token = os.environ.get("SHADOWSPILL_NODE_TOKEN", self.token)
+        self.registry = default_registry()
+        self.hardware = device_inventory()
+        self.admission = NodeAdmission(self.hardware["gpus"], int(self.hardware["host_total_gib"] * GIB))
+        self.membership = Membership()
+        self.journal = Journal(self.root / "journal")
+        self.runs: dict[tuple[str, str], LiveRun] = {}
+        self.artifacts: dict[str, dict[str, Any]] = {}
+        self.incarnation = uuid.uuid4().hex
+        self.t0 = time.monotonic()
+        self.httpd: ThreadingHTTPServer | None = None
+        self._thread: threading.Thread | None = None
+        # recovery: runs that were live when the previous incarnation stopped are marked stopped
+        for rec in self.journal.records("run"):
+            if not any(r["data"].get("run") == rec["data"]["run"] for r in self.journal.records("run_closed")):
+                self.journal.append("run_closed", {"run": rec["data"]["run"], "reason": "service restart"})
+        self.journal.append("started", {"incarnation": self.incarnation})
+
+    # ------------------------------------------------------------------ lifecycle
+    def start(self) -> "Server":
+        from .http import make_handler
+        self.httpd = ThreadingHTTPServer((self.host, self.port), make_handler(self))
+        self.httpd.daemon_threads = True
+        self.port = self.httpd.server_address[1]
+        self._thread = threading.Thread(target=self.httpd.serve_forever, name="http", daemon=True)
+        self._thread.start()
+        return self
+
+    def serve(self) -> None:
+        self.start()
+        try:
+            while True:
+                time.sleep(3600)
+        except KeyboardInterrupt:
+            pass
+        finally:
+            self.close()
+
+    @property
+    def url(self) -> str:
+        return f"http://{self.host}:{self.port}"
+
+    def close(self) -> None:
+        for run in list(self.runs.values()):
+            if run.controller:
+                run.controller.stop()
+            run.release()
+        if self.httpd:
+            self.httpd.shutdown()
+            self.httpd.server_close()
+            self.httpd = None
+
+    def __enter__(self):
+        return self.start()
+
+    def __exit__(self, *exc):
+        self.close()
+
+    # ------------------------------------------------------------------ helpers used by routes
+    def create_run(self, session: str, body: dict[str, Any]) -> LiveRun:
+        run = uuid.uuid4().hex[:10]
+        live = LiveRun(self, session, run, body)
+        self.runs[(session, run)] = live
+        self.journal.append("run", {"session": session, "run": run})
+        return live
+
+    def get_run(self, session: str, run: str) -> LiveRun:
+        try:
+            return self.runs[(session, run)]
+        except KeyError:
+            raise KeyError(f"no run {session}/{run}") from None
+
+    def resolve_checkpoint(self, session: str, name: str) -> str:
+        p = Path(name)
+        if p.is_absolute() and p.exists():
+            return str(p)
+        for cand in (self.root / "checkpoints" / session / name,):
+            if cand.exists():
+                return str(cand)
+        found = list((self.root / "checkpoints").glob(f"*/{name}"))
+        if found:
+            return str(found[0])
+        raise FileNotFoundError(f"no checkpoint {name!r}")
+
+    def describe(self, body: dict[str, Any]) -> dict[str, Any]:
+        r = resolve_training(body, self.registry, self.hardware)
+        params = r.cfg.parameter_count()
+        return {"workers": r.workers, "geometry": r.geometry, "budgets": r.budgets,
+                "provenance": r.provenance, "parameters": params,
+                "state_bytes_per_worker": params * 2 * 3 // r.workers,
+                "components": self.registry.list()}

@@ -1,0 +1,177 @@
+"""Component registry: models, objectives, optimizers, preparations and policies
+under versioned ids, plus the built-in components and the resolution of a
+client's settings into per-rank worker setups.
+
+Reference: packages/engine/src/shadowspill/training/components/{registry.py,
+contracts.py:48-199} and training/preparation/setup.py (``resolve_training``).
+"""
+from __future__ import annotations
+
+import dataclasses
+import hashlib
+import inspect
+from dataclasses import dataclass, field
+from typing import Any, Callable
+
+from ..models.config import PRESETS, DecoderConfig, preset
+
+GIB = 1 << 30
+
+
+@dataclass(frozen=True)
+class ComponentSource:
+    distribution: str
+    version: str
+    sha256: str
+
+    @staticmethod
+    def of(obj) -> "ComponentSource":
+        try:
+            src = inspect.getsource(obj)
+        except (OSError, TypeError):
+            src = repr(obj)
+        from .. import __version__
+        return ComponentSource("shadowspill_b200", __version__, hashlib.sha256(src.encode()).hexdigest())
+
+
+@dataclass
+class Component:
+    id: str
+    kind: str
+    create: Callable[..., Any]
+    source: ComponentSource
+    config_schema: dict[str, Any] = field(default_factory=dict)
+    capabilities: tuple[str, ...] = ()
+
+
+class Registry:
+    KINDS = ("model", "objective", "optimizer", "preparation", "policy")
+
+    def __init__(self):
+        self._items: dict[tuple[str, str], Component] = {}
+
+    def _add(self, kind: str, id_: str, create, **kw) -> Component:
+        if "@" not in id_:
+            raise ValueError("component ids are versioned: name@version")
+        if (kind, id_) in self._items:
+            raise ValueError(f"{kind} {id_!r} is already registered")
+        c = Component(id_, kind, create, ComponentSource.of(create), **kw)
+        self._items[(kind, id_)] = c
+        return c
+
+    def add_model(self, id_, create, **kw): return self._add("model", id_, create, **kw)
+    def add_objective(self, id_, create, **kw): return self._add("objective", id_, create, **kw)
+    def add_optimizer(self, id_, create, **kw): return self._add("optimizer", id_, create, **kw)
+    def add_preparation(self, id_, create, **kw): return self._add("preparation", id_, create, **kw)
+    def add_policy(self, id_, create, **kw): return self._add("policy", id_, create, **kw)
+
+    def get(self, kind: str, id_: str) -> Component:
+        try:
+            return self._items[(kind, id_)]
+        except KeyError:
+            known = sorted(i for k, i in self._items if k == kind)
+            raise KeyError(f"no {kind} component {id_!r}; known: {known}") from None
+
+    def list(self, kind: str | None = None) -> list[dict[str, Any]]:
+        return [{"id": c.id, "kind": c.kind, "source": dataclasses.asdict(c.source),
+                 "capabilities": list(c.capabilities)}
+                for (k, _), c in sorted(self._items.items()) if kind in (None, k)]
+
+
+def default_registry() -> Registry:
+    r = Registry()
+    for name in PRESETS:
+        r.add_model(f"{name}@1", (lambda n=name: preset(n)), capabilities=("text", "packed"))
+    r.add_objective("shadowspill/cross_entropy@1", lambda **kw: {"kind": "cross_entropy", **kw},
+                    capabilities=("text",))
+    r.add_objective("shadowspill/sum@1", lambda terms=(): {"kind": "sum", "terms": list(terms)})
+    r.add_optimizer("adamw@1", lambda **kw: {"kind": "adamw", **kw})
+    r.add_optimizer("mlops/adamw@1", lambda **kw: {"kind": "adamw", **kw})    # the reference's id
+    r.add_preparation("shadowspill/default@1", lambda **kw: kw)
+    r.add_policy("shadowspill/text_chunks@1", lambda projection=0, moe=0: {"projection": projection, "moe": moe})
+    r.add_policy("shadowspill/text_retention@1", lambda rule="cost-input": {"rule": rule})
+    return r
+
+
+_RETENTION_VARIANT = {"cost-input": "recompute", "cost-attention": "save_attention",
+                      "attention-input": "save_attention"}
+
+
+@dataclass
+class ResolvedTraining:
+    cfg: DecoderConfig
+    workers: int
+    setups: list[dict[str, Any]]              # one TrainingSetup (as JSON) per rank
+    geometry: dict[str, Any]
+    provenance: dict[str, str]
+    budgets: dict[str, float]
+
+
+def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[str, Any]) -> ResolvedTraining:
+    """Client settings -> per-rank worker setups, with the provenance of every default."""
+    prov: dict[str, str] = {}
+    m = body["model"]
+    if m.get("config"):
+        cfg = DecoderConfig.from_json(m["config"]); prov["model"] = "explicit config"
+    else:
+        name = m["name"] if "@" in m["name"] else m["name"] + "@1"
+        cfg = registry.get("model", name).create(); prov["model"] = f"catalog {name}"
+    registry.get("objective", body["objective"]["id"])
+    opt = body["optimizer"]
+    registry.get("optimizer", opt["id"])
+    res = body.get("resources", {})
+    par = body.get("parallelism") or {}
+    workers = int(par.get("ranks_per_replica", res.get("gpus", 1))) * int(par.get("num_replicas", 1))
+    backend = res.get("backend", "cuda")
+    device = "cuda" if backend == "cuda" else "cpu"
+    if device == "cuda" and workers > max(1, hardware.get("gpus", 0)):
+        raise ValueError(f"{workers} workers requested, {hardware.get('gpus', 0)} GPUs present")
+    mem = body.get("memory", {})
+    device_gib, spill_gib = float(mem.get("device_gib", 0)), float(mem.get("spill_gib", 0))
+    if device_gib <= 0:
+        device_gib = 0.9 * hardware.get("device_gib", 180.0); prov["device_gib"] = "automatic 90 %"
+    if spill_gib <= 0:
+        spill_gib = 0.9 * hardware.get("host_free_gib", 64.0) / max(1, workers)
+        prov["spill_gib"] = "automatic 90 % of free host memory"
+    b = body.get("batch", {})
+    T, tokens = int(b.get("microbatch_tokens", 8192)), int(b.get("tokens_per_step", 65536))
+    slots = int(b.get("max_datums", 0)) or max(16, T // 32 + 1)
+    prep = body.get("preparation", {})
+    build, planning = prep.get("build", {}), prep.get("planning", {})
+    saved_variant = build.get("saved_variant", "save_attention")
+    for pol in prep.get("policies", []):
+        if pol.get("id") == "shadowspill/text_retention@1":
+            saved_variant = _RETENTION_VARIANT.get((pol.get("config") or {}).get("rule", ""), saved_variant)
+    ex = body.get("execution", {})
+    sr = opt.get("parameter_rounding", "stochastic") == "stochastic"
+    search = {"workers": planning.get("workers", 0),
+              "strategies": list(planning.get("strategies", ("stall", "traffic"))),
+              "fetch_rules": list(planning.get("fetch_rules",
+                                               ("demand", "latest-safe", "packed-fifo", "packed-fit"))),
+              "max_repairs": planning.get("max_repairs", 16),
+              "minimum_object_bytes_evict_eligible":
+                  planning.get("minimum_object_bytes_evict_eligible", 1 << 20),
+              "deterministic": planning.get("deterministic", False)}
+    setups = []
+    for rank in range(workers):
+        setups.append({
+            "model": cfg.to_json(), "device_gib": device_gib, "spill_gib": spill_gib,
+            "tokens_per_step": tokens, "microbatch_tokens": T, "slots": slots,
+            "lr": opt.get("lr", 1e-4), "beta1": opt.get("beta1", 0.9), "beta2": opt.get("beta2", 0.95),
+            "eps": opt.get("eps", 1e-8), "weight_decay": opt.get("weight_decay", 0.0),
+            "seed": int(m.get("weights", {}).get("seed", ex.get("seed", 0))),
+            "dtype": m.get("dtype", "bfloat16"), "stochastic_rounding": sr, "device": device,
+            "device_index": rank if device == "cuda" else 0, "rank": rank, "world_size": workers,
+            "walks": list(build.get("walks", ("breadth",))),
+            "recompute_shares": list(build.get("recompute_shares", (100,))),
+            "saved_variant": saved_variant,
+            "profile": bool(prep.get("profiling", {}).get("enabled", True)) and not body.get("simulation_only"),
+            "calibrate": bool(prep.get("calibrate", True)) and not body.get("simulation_only"),
+            "search": search, "collectives": ex.get("collectives", "auto"),
+            "operations": list(body.get("operations", ("step",))),
+            "trace_capacity": 65536 if ex.get("runtime_trace") else 0})
+    geometry = {"microbatch_tokens": T, "microbatches": tokens // T, "slots": slots,
+                "vocab_size": cfg.vocab_size, "workers": workers, "packing": b.get("packing", "best_fit"),
+                "tokens_per_step": tokens * workers}
+    return ResolvedTraining(cfg, workers, setups, geometry, prov,
+                            {"device_gib": device_gib, "spill_gib": spill_gib})

@@ -1,0 +1,122 @@
+"""Worker group: launches one worker process per rank and runs two-phase commands.
+
+``execute`` sends the call to every rank, waits until all are ``ready`` (inputs
+staged and validated), then tells all to ``execute``; if any rank fails to stage,
+every rank is told to ``abort`` and training state is untouched. A failure after
+execution began marks the whole group's state invalid.
+Reference: packages/engine/src/shadowspill/training/worker/{group.py:54-99,launch.py:28,startup.py:71}.
+"""
+from __future__ import annotations
+
+import os
+import socket
+import subprocess
+import sys
+import threading
+from pathlib import Path
+
+from .channel import Channel, ChannelClosed
+
+
+class WorkerFailure(RuntimeError):
+    def __init__(self, message: str, effect: str = "unknown"):
+        self.effect = effect
+        super().__init__(message)
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+class WorkerGroup:
+    def __init__(self, setups: list[dict], log_dir: str | Path, checkpoint: str | None = None,
+                 startup_seconds: float = 1800.0, on_progress=None):
+        self.world = len(setups)
+        self.log_dir = Path(log_dir)
+        self.log_dir.mkdir(parents=True, exist_ok=True)
+        self.procs: list[subprocess.Popen] = []
+        self.chans: list[Channel] = []
+        self.valid = True
+        self.ready_info: list[dict] = []
+        self.on_progress = on_progress or (lambda msg: None)
+        port = _free_port()
+        root = str(Path(__file__).resolve().parents[2])
+        for rank, setup in enumerate(setups):
+            to_child_r, to_child_w = os.pipe()
+            from_child_r, from_child_w = os.pipe()
+            env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+            log = open(self.log_dir / f"worker{rank}.log", "ab")
+            proc = subprocess.Popen(
+                [sys.executable, "-m", "shadowspill_b200.training.worker", "--control-fd",
+                 f"{to_child_r},{from_child_w}"], pass_fds=(to_child_r, from_child_w), env=env,
+                stdout=log, stderr=subprocess.STDOUT, cwd=root)
+            os.close(to_child_r); os.close(from_child_w)
+            chan = Channel(from_child_r, to_child_w)
+            chan.send({"type": "launch", "rank": rank, "world_size": self.world, "setup": setup,
+                       "master_addr": "127.0.0.1", "master_port": port, "checkpoint": checkpoint})
+            self.procs.append(proc)
+            self.chans.append(chan)
+        try:
+            for rank, chan in enumerate(self.chans):
+                self.ready_info.append(self._await(rank, chan, "ready", startup_seconds))
+        except BaseException:
+            self.stop()
+            raise
+
+    def _await(self, rank: int, chan: Channel, want: str, timeout: float | None) -> dict:
+        while True:
+            try:
+                header, _ = chan.recv(timeout)
+            except (ChannelClosed, TimeoutError) as exc:
+                self.valid = False
+                raise WorkerFailure(f"worker {rank} lost: {exc}") from None
+            kind = header.get("type")
+            if kind == "progress":
+                self.on_progress(f"[rank={rank}] {header.get('message', '')}")
+                continue
+            if kind == "failed":
+                raise WorkerFailure(f"worker {rank} failed to start: {header.get('error')}\n"
+                                    f"{header.get('traceback', '')}", "not_started")
+            if kind == want or kind == "reply":
+                return header
+
+    def execute(self, request_id: str, operation: str, arguments: dict,
+                payloads: list[bytes] | None = None, timeout: float | None = None) -> list[dict]:
+        if not self.valid:
+            raise WorkerFailure("training state is invalid after an earlier failure; only close "
+                                "is accepted", "not_started")
+        for rank, chan in enumerate(self.chans):
+            chan.send({"type": "call", "request_id": request_id, "operation": operation,
+                       "arguments": arguments}, payloads[rank] if payloads else b"")
+        staged = [self._await(r, c, "reply", timeout) for r, c in enumerate(self.chans)]
+        bad = [s for s in staged if s.get("state") != "ready"]
+        action = "abort" if bad else "execute"
+        for chan in self.chans:
+            chan.send({"type": "control", "request_id": request_id, "action": action})
+        replies = [self._await(r, c, "reply", timeout) for r, c in enumerate(self.chans)]
+        if bad:
+            raise WorkerFailure(f"staging failed: {bad[0].get('error')}", "not_started")
+        failed = [r for r in replies if r.get("state") != "completed"]
+        if failed:
+            effect = "unknown" if any(r.get("effect") == "unknown" for r in failed) else "not_started"
+            if effect == "unknown":
+                self.valid = False
+            raise WorkerFailure(f"{failed[0].get('error')}\n{failed[0].get('traceback', '')}", effect)
+        return replies
+
+    def stop(self) -> None:
+        for chan in self.chans:
+            try:
+                chan.send({"type": "shutdown"})
+            except ChannelClosed:
+                pass
+        for proc in self.procs:
+            try:
+                proc.wait(timeout=30)
+            except subprocess.TimeoutExpired:
+                proc.kill()
+        for chan in self.chans:
+            chan.close()
+        self.procs, self.chans = [], []

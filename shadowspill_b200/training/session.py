@@ -22,11 +22,12 @@ import torch
 from ..communication.info import CommunicationInfo
 from ..data.synthetic import HostMicrobatch
 from ..execution.executor import Executor, Hyperparameters, InvocationResult
-from ..frontend.capture import (BatchGeometry, StepDataOrdering, build_forward, build_step,
+from ..frontend.capture import (BatchGeometry, StepDataOrdering, build_forward,
+                                build_forward_backward, build_optimizer, build_step,
                                 recompute_share_selections)
 from ..models.config import DecoderConfig, preset
-from ..planning.plan import (MemoryBudgets, PlanningError, SearchOptions, plan_program,
-                             sweep_programs)
+from ..planning.plan import (MemoryBudgets, PlanningError, SearchOptions, StateLayout,
+                             plan_program, sweep_programs)
 from ..profiling.measure import Profiles, apply_profiles, measure_program
 from ..runtime.core import Runtime
 
@@ -62,6 +63,7 @@ class TrainingSetup:
     search: SearchOptions = field(default_factory=SearchOptions)
     trace_capacity: int = 0
     collectives: str = "auto"             # peer | dist | auto
+    operations: tuple[str, ...] = ("step",)   # also: forward_backward, optim_step, forward
 
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
@@ -92,19 +94,32 @@ class TrainingSession:
             return build_step(self.cfg, self.geometry, order, dtype=self.dtype, selection=sel,
                               world_size=world, rank=rank)
 
+        def build_extra(op: str):
+            kw = dict(dtype=self.dtype, world_size=world, rank=rank)
+            if op == "forward_backward":
+                return build_forward_backward(self.cfg, self.geometry, StepDataOrdering(), **kw)
+            if op == "optim_step":
+                return build_optimizer(self.cfg, self.geometry, **kw)
+            if op == "forward":
+                return build_forward(self.cfg, self.geometry, StepDataOrdering(), **kw)
+            raise ValueError(f"unknown operation {op!r}")
+
+        extra_ops = [op for op in setup.operations if op != "step"]
         self.profiles = Profiles()
         self.communication = CommunicationInfo(world_size=world)
-        chosen, plan_json = 0, None
+        chosen, plan_json, extra_json = 0, None, {}
         if rank == 0:
             # ---- build candidates
             t0 = time.perf_counter()
             candidates = [build(i) for i in range(len(variants))]
+            extras = {op: build_extra(op) for op in extra_ops}
+            layout = StateLayout.build([p for p, _ in candidates] + [p for p, _ in extras.values()])
             self.timings["build"] = time.perf_counter() - t0
             # ---- profile distinct tasks once
             t0 = time.perf_counter()
             if setup.profile:
                 dev = f"cuda:{setup.device_index}" if cuda else "cpu"
-                for prog, desc in candidates:
+                for prog, desc in candidates + list(extras.values()):
                     missing = {t.profile_key for t in prog.tasks} - set(self.profiles.tasks)
                     if missing:
                         got = measure_program(prog, desc, dev, keys=missing)
@@ -128,7 +143,11 @@ class TrainingSession:
             # ---- plan every candidate, keep the fastest
             t0 = time.perf_counter()
             sweep = sweep_programs([p for p, _ in candidates], self.budgets, self.communication,
-                                   setup.search)
+                                   setup.search, state_layout=layout)
+            self.extra_plans = {op: (plan_program(p, self.budgets, self.communication,
+                                                  setup.search, layout), d)
+                                for op, (p, d) in extras.items()}
+            extra_json = {op: pl.to_json() for op, (pl, _) in self.extra_plans.items()}
             self.sweep = sweep
             self.plan = sweep.best
             chosen = next(i for i, (p, _) in enumerate(candidates) if p is self.plan.program)
@@ -139,27 +158,30 @@ class TrainingSession:
             # one plan for the whole job: identical offsets on every rank are what makes the
             # device pool symmetric, and identical task order keeps collectives matched
             import torch.distributed as dist
-            box = [chosen, plan_json]
+            box = [chosen, plan_json, extra_json]
             dist.broadcast_object_list(box, src=0)
             if rank != 0:
                 from ..ir.plan import Plan
-                chosen, plan_json = box
+                chosen, plan_json, extra_json = box
                 self.plan = Plan.from_json(plan_json)
                 self.desc = build(chosen)[1]
+                self.extra_plans = {op: (Plan.from_json(j), build_extra(op)[1])
+                                    for op, j in extra_json.items()}
         self.log(f"plan: {self.plan.summary.ordering} {self.plan.summary.selection} "
                  f"simulated {self.plan.summary.duration_seconds * 1e3:.1f} ms")
         # ---- executor (caps the torch allocator to the planned workspace)
         t0 = time.perf_counter()
         if cuda:
             total = torch.cuda.get_device_properties(setup.device_index).total_memory
-            cap = self.plan.summary.workspace_bytes + (256 << 20)
+            cap = max([self.plan.summary.workspace_bytes] +
+                      [p.summary.workspace_bytes for p, _ in self.extra_plans.values()]) + (256 << 20)
             torch.cuda.set_per_process_memory_fraction(min(1.0, cap / total), setup.device_index)
         hyper = Hyperparameters(setup.lr, setup.beta1, setup.beta2, setup.eps, setup.weight_decay)
         self.executor = Executor(self.plan, self.desc, device=setup.device,
                                  device_index=setup.device_index, seed=setup.seed, hyper=hyper,
                                  stochastic_rounding=setup.stochastic_rounding,
                                  trace_capacity=setup.trace_capacity,
-                                 collectives=setup.collectives)
+                                 collectives=setup.collectives, extra_plans=self.extra_plans)
         self.executor.initialize()
         self.timings["open"] = time.perf_counter() - t0
         if cuda:
@@ -168,6 +190,17 @@ class TrainingSession:
     # ------------------------------------------------------------------ operations
     def step(self, batch: list[HostMicrobatch], **kw) -> InvocationResult:
         return self.executor.run(batch, **kw)
+
+    def run(self, operation: str, batch: list[HostMicrobatch] | None = None, **kw) -> InvocationResult:
+        return self.executor.run(batch, operation=operation, **kw)
+
+    def save(self, directory: str, metadata: dict | None = None):
+        from ..checkpoint import save_checkpoint
+        return save_checkpoint(self.executor, directory, metadata=metadata)
+
+    def restore(self, directory: str) -> dict:
+        from ..checkpoint import load_checkpoint
+        return load_checkpoint(self.executor, directory)
 
     def peak_device_bytes(self) -> int:
         """Device pool plus the torch allocator's peak reservation since opening."""

@@ -1,0 +1,106 @@
+"""Public client -> HTTP service -> worker process -> planned execution, on CPU.
+
+A real ``Server`` listens on loopback, the run's worker is a real subprocess with
+the mock backend, and the client is the NumPy-only package a user imports.
+"""
+import numpy as np
+import pytest
+
+from shadowspill_b200.client import (BatchConfig, BatchError, Memory, Model, Optimizer,
+                                     OperationFailed, Preparation, ProfilingOptions, Resources,
+                                     ServiceClient, text_batch)
+from shadowspill_b200.client.config import PlanningOptions
+from shadowspill_b200.server.service import Server
+
+
+def _sequences(seed, n=8, vocab=512):
+    rng = np.random.default_rng(seed)
+    return [rng.integers(0, vocab, size=int(rng.integers(16, 60))) for _ in range(n)]
+
+
+@pytest.fixture(scope="module")
+def service(tmp_path_factory):
+    with Server(tmp_path_factory.mktemp("service"), token="secret") as srv:
+        yield srv
+
+
+def _trainer(svc, operations=("step",)):
+    return svc.create_training_client(
+        Model("llama3-tiny", dtype="float32"), Optimizer(lr=3e-3, parameter_rounding="nearest"),
+        batch=BatchConfig(tokens_per_step=512, microbatch_tokens=256),
+        memory=Memory(device_gib=0.53, spill_gib=0.25), resources=Resources(gpus=1, backend="cpu"),
+        preparation=Preparation(profiling=ProfilingOptions(enabled=False), calibrate=False,
+                                planning=PlanningOptions(minimum_object_bytes_evict_eligible=1024,
+                                                         workers=1)),
+        operations=operations, timeout=300).result()
+
+
+def test_auth_is_enforced(service):
+    from shadowspill_b200.client.transport import TransportError
+    with pytest.raises(TransportError) as e:
+        ServiceClient(service.url, token="wrong")
+    assert e.value.status == 401
+
+
+def test_train_checkpoint_resume_through_the_public_api(service):
+    with ServiceClient(service.url, token="secret") as svc:
+        hw = svc.list_hardware().result()
+        assert hw["nodes"][0]["cpus"] >= 1
+        desc = svc.describe_training(model=Model("llama3-tiny"),
+                                     resources=Resources(backend="cpu")).result()
+        assert desc["workers"] == 1 and desc["parameters"] == 426_624
+        trainer = _trainer(svc, ("step", "forward_backward", "optim_step", "forward"))
+        assert trainer.info["plan_summary"]["fetch_bytes"] > 0
+        losses = [trainer.step(text_batch(_sequences(0))).result().loss for _ in range(4)]
+        assert losses[-1] < losses[0]
+        # accumulation: two contributions then one update
+        f1 = trainer.forward_backward(text_batch(_sequences(1)))
+        f2 = trainer.forward_backward(text_batch(_sequences(2)))
+        up = trainer.optim_step()
+        assert f1.result().loss > 0 and f2.result().loss > 0
+        assert up.result().completed_updates == 5
+        ev = trainer.forward(text_batch(_sequences(0))).result().loss
+        assert 0 < ev < losses[0]
+        # a step while gradients are open is rejected, and says why
+        trainer.forward_backward(text_batch(_sequences(3))).result()
+        with pytest.raises(OperationFailed) as e:
+            trainer.step(text_batch(_sequences(0))).result()
+        assert "accumulation" in str(e.value)
+        trainer.discard_gradients().result()
+        saved = trainer.save_checkpoint("after5").result()
+        assert saved.outputs["checkpoint"] == "after5"
+        next_loss = trainer.step(text_batch(_sequences(7))).result().loss
+        # local validation never reaches the server
+        with pytest.raises(BatchError):
+            trainer.step(text_batch([np.arange(0, 600) % 512]))
+        trainer.log_metrics(6, accuracy=0.5)
+        metrics = svc.get_metrics(trainer.run).result()["metrics"]
+        assert any(m.get("source") == "caller" for m in metrics) and len(metrics) >= 6
+        progress = svc.get_progress(trainer.run).result()["lines"]
+        assert any("ready" in line for line in progress)
+        trainer.close()
+        # ---- resume from the checkpoint in a fresh run: the same next step
+        resumed = svc.create_training_client(
+            Model("llama3-tiny", dtype="float32"), Optimizer(lr=3e-3, parameter_rounding="nearest"),
+            batch=BatchConfig(tokens_per_step=512, microbatch_tokens=256),
+            memory=Memory(device_gib=0.53, spill_gib=0.25), resources=Resources(gpus=1, backend="cpu"),
+            preparation=Preparation(profiling=ProfilingOptions(enabled=False), calibrate=False,
+                                    planning=PlanningOptions(minimum_object_bytes_evict_eligible=1024,
+                                                             workers=1)),
+            checkpoint="after5", timeout=300).result()
+        r = resumed.step(text_batch(_sequences(7))).result()
+        assert abs(r.loss - next_loss) < 1e-6 and r.completed_updates == 6
+        resumed.close()
+
+
+def test_newer_writer_fences_the_older_one(service):
+    with ServiceClient(service.url, token="secret") as svc:
+        first = _trainer(svc)
+        first.step(text_batch(_sequences(0))).result()
+        second = svc.get_training_client(first.run).result()
+        second.step(text_batch(_sequences(1))).result()
+        from shadowspill_b200.client.transport import TransportError
+        with pytest.raises(TransportError) as e:
+            first.step(text_batch(_sequences(2))).result()
+        assert e.value.status == 409 and "fenced" in str(e.value)
+        second.close()
