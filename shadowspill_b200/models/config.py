@@ -26,6 +26,7 @@ class DecoderConfig:
     norm_epsilon: float = 1e-5
     zero_centered_norm: bool = False      # Qwen 3.5: weight stored as offset from one
     qk_norm: bool = False                 # Qwen 3 family: RMSNorm on each q/k head
+    qk_norm_full_width: bool = False      # OLMoE: one RMSNorm over the whole q (and k) projection
     gated_attention: bool = False         # Qwen 3.5: sigmoid output gate on attention
     tied_embeddings: bool = False
     initializer_range: float = 0.02
@@ -112,19 +113,18 @@ PRESETS: dict[str, DecoderConfig] = {
     # ---- Qwen 3.5: 3 Gated DeltaNet : 1 gated full attention
     "qwen35-tiny": _qwen35(2, 128, 4, 2, 32, 256, 2, 4, vocab=512, interval=2, dnhd=32),
     "qwen35-numerical": _qwen35(8, 1536, 12, 4, 128, 4608, 6, 12),
-    "qwen35-2b": _qwen35(24, 2048, 8, 2, 256, 6144, 16, 16),
     "qwen35-9b": _qwen35(32, 4096, 16, 4, 256, 12288, 16, 32),
     "qwen35-27b": _qwen35(64, 5120, 24, 4, 256, 17408, 16, 48),
     # ---- OLMoE: GQA + routed SwiGLU experts
     "olmoe-tiny": DecoderConfig("olmoe", 2, 128, 4, 2, 32, 0, 512, rope_base=10_000.0,
-                                qk_norm=True, n_experts=8, top_k=2, d_expert=128,
-                                router_renormalize=False),
+                                qk_norm=True, qk_norm_full_width=True, n_experts=8, top_k=2,
+                                d_expert=128, router_renormalize=False),
     "olmoe-numerical": DecoderConfig("olmoe", 16, 1024, 8, 8, 128, 0, 50_304, rope_base=10_000.0,
-                                     qk_norm=True, n_experts=16, top_k=4, d_expert=1024,
-                                     router_renormalize=False),
+                                     qk_norm=True, qk_norm_full_width=True, n_experts=16, top_k=4,
+                                     d_expert=1024, router_renormalize=False),
     "olmoe-7b-a1b": DecoderConfig("olmoe", 16, 2048, 16, 16, 128, 0, 50_304, rope_base=10_000.0,
-                                  qk_norm=True, n_experts=64, top_k=8, d_expert=1024,
-                                  router_renormalize=False),
+                                  qk_norm=True, qk_norm_full_width=True, n_experts=64, top_k=8,
+                                  d_expert=1024, router_renormalize=False),
     # ---- Qwen 3 MoE
     "qwen3moe-tiny": DecoderConfig("qwen3moe", 2, 128, 4, 2, 32, 0, 1024, rope_base=1_000_000.0,
                                    norm_epsilon=1e-6, qk_norm=True, n_experts=8, top_k=2,

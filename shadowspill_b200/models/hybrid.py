@@ -1,0 +1,223 @@
+"""Hybrid and mixture decoder layers: Gated DeltaNet or (gated) GQA attention as the
+sequence mixer, a dense SwiGLU MLP or routed experts (plus an optional shared
+expert) as the channel mixer.
+
+The forward pass is written once with differentiable ops; ``torch.autograd``
+derives the backward pass per stage execution (recompute form: the backward task
+re-runs the forward under autograd from the stage input). Matrix weight
+gradients are written by the ``linear`` op directly into the stage's gradient
+buffer; the few remaining parameters (convolution taps, ``A_log``, ``dt_bias``,
+router-free gates) are leaf tensors whose ``.grad`` is folded in afterwards.
+
+Architecture references:
+  Gated DeltaNet   packages/workloads/src/shadowspill_workloads/models/shared/delta_net.py:13-89
+  gated attention  models/qwen35/implementations/mlops.py:30-100
+  routed experts   models/shared/qwen_moe/experts.py:31-72 (router -> top-k -> grouped
+                   up/SwiGLU/down -> weighted combine)
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as TF
+
+from ..ops import sequence as seq_ops
+from . import autograd_ops as A
+from .config import DecoderConfig
+from .decoder import BatchMeta, ParamSpec, Stage
+
+
+class HybridLayerStage(Stage):
+    kind = "layer"
+    SAVE_SETS = {"recompute": ()}
+
+    def __init__(self, name: str, cfg: DecoderConfig, index: int):
+        super().__init__(name, cfg)
+        self.index = index
+        self.mixer = cfg.layer_kind(index)
+        c, std = cfg, cfg.initializer_range
+        D, dh, Hq, Hkv = c.d_model, c.head_dim, c.n_heads, c.n_kv_heads
+        norm_init = "zeros" if c.zero_centered_norm else "ones"
+        P = [ParamSpec("attn_norm", (D,), init=norm_init)]
+        if self.mixer == "attention":
+            qw = Hq * dh * (2 if c.gated_attention else 1)
+            P += [ParamSpec("wq", (qw, D), std=std), ParamSpec("wk", (Hkv * dh, D), std=std),
+                  ParamSpec("wv", (Hkv * dh, D), std=std), ParamSpec("wo", (D, Hq * dh), std=std)]
+            if c.qk_norm:
+                qn, kn = (Hq * dh, Hkv * dh) if c.qk_norm_full_width else (dh, dh)
+                P += [ParamSpec("q_norm", (qn,), init=norm_init), ParamSpec("k_norm", (kn,), init=norm_init)]
+        else:
+            self.key_width = c.dn_qk_heads * c.dn_head_dim
+            self.value_width = c.dn_v_heads * c.dn_head_dim
+            self.conv_width = 2 * self.key_width + self.value_width
+            P += [ParamSpec("w_qkvz", (self.conv_width + self.value_width, D), std=std),
+                  ParamSpec("w_ba", (2 * c.dn_v_heads, D), std=std),
+                  ParamSpec("conv_w", (self.conv_width, c.dn_conv_width), std=0.3),
+                  ParamSpec("A_log", (c.dn_v_heads,), init="zeros", dtype=torch.float32),
+                  ParamSpec("dt_bias", (c.dn_v_heads,), init="zeros", dtype=torch.float32),
+                  ParamSpec("lin_norm", (c.dn_head_dim,), init=norm_init),
+                  ParamSpec("w_out", (D, self.value_width), std=std)]
+        P.append(ParamSpec("mlp_norm", (D,), init=norm_init))
+        if c.is_moe:
+            P += [ParamSpec("router", (c.n_experts, D), std=std),
+                  ParamSpec("w13", (c.n_experts, 2 * c.d_expert, D), std=std),
+                  ParamSpec("w2", (c.n_experts, D, c.d_expert), std=std)]
+            if c.d_shared_expert:
+                P += [ParamSpec("sw13", (2 * c.d_shared_expert, D), std=std),
+                      ParamSpec("sw2", (D, c.d_shared_expert), std=std)]
+                if c.gated_shared_expert:
+                    P.append(ParamSpec("shared_gate", (D,), std=std))
+        else:
+            P += [ParamSpec("w13", (2 * c.d_ff, D), std=std), ParamSpec("w2", (D, c.d_ff), std=std)]
+        self.params = P
+        self._leaf = [p.name for p in P if p.name in ("conv_w", "A_log", "dt_bias", "shared_gate")]
+        self._banks = ["w13", "w2"] if c.is_moe else []
+
+    # ---- sizes (used for modelled costs until profiled)
+    def workspace_bytes(self, T, itemsize=2):
+        c = self.cfg
+        width = (c.d_ff or c.top_k * c.d_expert + c.d_shared_expert)
+        return T * (8 * c.d_model + 6 * width + 4 * c.n_heads * c.head_dim) * itemsize * 2
+
+    def flops(self, T, mean_seqlen):
+        c = self.cfg
+        if self.mixer == "attention":
+            mix = 2.0 * T * c.d_model * (c.n_heads * c.head_dim * (3 if c.gated_attention else 2)
+                                         + 2 * c.n_kv_heads * c.head_dim)
+            mix += 4.0 * T * (mean_seqlen / 2.0) * c.n_heads * c.head_dim
+        else:
+            mix = 2.0 * T * c.d_model * (self.conv_width + 2 * self.value_width)
+            mix += 6.0 * T * c.dn_v_heads * c.dn_head_dim * c.dn_head_dim
+        ff = 3 * (c.d_ff if not c.is_moe else c.top_k * c.d_expert + c.d_shared_expert)
+        return mix + 2.0 * T * c.d_model * ff
+
+    # ---- the layer
+    def _attention(self, P, h, meta: BatchMeta, sink):
+        c = self.cfg
+        T = h.shape[0]
+        dh, Hq, Hkv = c.head_dim, c.n_heads, c.n_kv_heads
+        qg = A.linear(h, P["wq"], sink, "wq")
+        q, gate = (qg[:, :Hq * dh], qg[:, Hq * dh:]) if c.gated_attention else (qg, None)
+        k = A.linear(h, P["wk"], sink, "wk")
+        v = A.linear(h, P["wv"], sink, "wv")
+        if c.qk_norm and c.qk_norm_full_width:
+            q = A.rmsnorm(q.contiguous(), P["q_norm"], c.norm_epsilon, c.zero_centered_norm, sink, "q_norm")
+            k = A.rmsnorm(k.contiguous(), P["k_norm"], c.norm_epsilon, c.zero_centered_norm, sink, "k_norm")
+        elif c.qk_norm:
+            q = A.rmsnorm(q.reshape(T * Hq, dh), P["q_norm"], c.norm_epsilon, c.zero_centered_norm,
+                          sink, "q_norm").reshape(T, Hq * dh)
+            k = A.rmsnorm(k.reshape(T * Hkv, dh), P["k_norm"], c.norm_epsilon, c.zero_centered_norm,
+                          sink, "k_norm").reshape(T, Hkv * dh)
+        q = A.rope(q.contiguous(), meta.positions, Hq, dh, c.rotary_width, c.rope_base)
+        k = A.rope(k.contiguous(), meta.positions, Hkv, dh, c.rotary_width, c.rope_base)
+        att = A.attention(q.view(T, Hq, dh), k.view(T, Hkv, dh), v.view(T, Hkv, dh),
+                          meta.cu_seqlens, meta.max_seqlen).reshape(T, Hq * dh)
+        if gate is not None:
+            att = att * torch.sigmoid(gate.float()).to(att.dtype)
+        return A.linear(att.contiguous(), P["wo"], sink, "wo")
+
+    def _deltanet(self, P, L, h, meta: BatchMeta, sink, bounds):
+        c = self.cfg
+        T = h.shape[0]
+        Hk, Hv, dk = c.dn_qk_heads, c.dn_v_heads, c.dn_head_dim
+        qkvz = A.linear(h, P["w_qkvz"], sink, "w_qkvz")
+        ba = A.linear(h, P["w_ba"], sink, "w_ba")
+        conv = seq_ops.causal_conv_silu(qkvz[:, :self.conv_width], L["conv_w"], bounds)
+        q = seq_ops.l2_normalize(conv[:, :self.key_width].reshape(T, Hk, dk))
+        k = seq_ops.l2_normalize(conv[:, self.key_width:2 * self.key_width].reshape(T, Hk, dk))
+        v = conv[:, 2 * self.key_width:].reshape(T, Hv, dk)
+        beta = torch.sigmoid(ba[:, :Hv].float())
+        g = -torch.exp(L["A_log"].float()) * TF.softplus(ba[:, Hv:].float() + L["dt_bias"].float())
+        mixed = seq_ops.gated_delta_rule_chunked(q, k, v, beta, g, bounds, c.dn_chunk)
+        gate = qkvz[:, self.conv_width:].reshape(T, Hv, dk)
+        normed = seq_ops.gated_rmsnorm(mixed, gate, P["lin_norm_leaf"], c.norm_epsilon,
+                                       c.zero_centered_norm)
+        return A.linear(normed.reshape(T, Hv * dk).contiguous(), P["w_out"], sink, "w_out")
+
+    def _experts(self, P, L, h, sink):
+        c = self.cfg
+        T = h.shape[0]
+        logits = A.linear(h, P["router"], sink, "router").float()
+        if c.router_renormalize:
+            vals, ids = torch.topk(logits, c.top_k, dim=-1)
+            wts = torch.softmax(vals, dim=-1)
+        else:
+            probs = torch.softmax(logits, dim=-1)
+            wts, ids = torch.topk(probs, c.top_k, dim=-1)
+        flat_e = ids.reshape(-1)
+        order = torch.argsort(flat_e, stable=True)
+        counts = torch.bincount(flat_e, minlength=c.n_experts).tolist()
+        tok = (order // c.top_k)
+        w_sorted = wts.reshape(-1)[order].to(h.dtype)
+        out = torch.zeros_like(h)
+        pos = 0
+        for e, n in enumerate(counts):
+            if n == 0:
+                continue
+            rows = tok[pos:pos + n]
+            xe = h.index_select(0, rows)
+            gu = A.linear(xe, P["w13"][e], sink, "w13", e)
+            ye = A.linear(A.swiglu(gu), P["w2"][e], sink, "w2", e)
+            out = out.index_add(0, rows, ye * w_sorted[pos:pos + n, None])
+            pos += n
+        if c.d_shared_expert:
+            sh = A.linear(A.swiglu(A.linear(h, P["sw13"], sink, "sw13")), P["sw2"], sink, "sw2")
+            if c.gated_shared_expert:
+                sh = sh * torch.sigmoid(h.float() @ L["shared_gate"].float()).to(h.dtype)[:, None]
+            out = out + sh
+        return out
+
+    def _layer(self, P, L, x, meta: BatchMeta, sink, bounds):
+        c = self.cfg
+        h = A.rmsnorm(x, P["attn_norm"], c.norm_epsilon, c.zero_centered_norm, sink, "attn_norm")
+        mix = (self._attention(P, h, meta, sink) if self.mixer == "attention"
+               else self._deltanet(P, L, h, meta, sink, bounds))
+        x = x + mix
+        h = A.rmsnorm(x, P["mlp_norm"], c.norm_epsilon, c.zero_centered_norm, sink, "mlp_norm")
+        if c.is_moe:
+            ff = self._experts(P, L, h, sink)
+        else:
+            ff = A.linear(A.swiglu(A.linear(h, P["w13"], sink, "w13")), P["w2"], sink, "w2")
+        return x + ff
+
+    def _leaves(self, P, grad: bool):
+        """Parameters whose gradient comes from autograd's ``.grad``."""
+        L = {n: (P[n].detach().requires_grad_(True) if grad else P[n]) for n in self._leaf}
+        P = dict(P)
+        if "lin_norm" in P:       # the gated norm is plain differentiable math
+            leaf = P["lin_norm"].detach().requires_grad_(True) if grad else P["lin_norm"]
+            P["lin_norm_leaf"] = leaf
+            L["lin_norm"] = leaf
+        return P, L
+
+    # ---- stage interface
+    def forward(self, P, x, meta: BatchMeta, keep=(), out=None):
+        bounds = meta.cu_seqlens.tolist() if self.mixer == "deltanet" else None
+        with torch.no_grad():
+            P2, L = self._leaves(P, False)
+            y = self._layer(P2, L, x, meta, None, bounds)
+        if out is not None:
+            out.copy_(y)
+            y = out
+        return y, {}
+
+    def backward(self, P, G, x, dy, meta: BatchMeta, saved, first: bool):
+        bounds = meta.cu_seqlens.tolist() if self.mixer == "deltanet" else None
+        sink = A.GradSink(G, first)
+        if first:
+            for name in self._banks:          # experts without tokens still need defined gradients
+                G[name].zero_()
+                for e in range(self.cfg.n_experts):
+                    sink.written.add(f"{name}[{e}]")
+        P2, L = self._leaves(P, True)
+        xin = x.detach().requires_grad_(True)
+        with torch.enable_grad():
+            y = self._layer(P2, L, xin, meta, sink, bounds)
+        torch.autograd.backward(y, dy)
+        for name, leaf in L.items():
+            sink.add_vector(name, leaf.grad if leaf.grad is not None else torch.zeros_like(leaf))
+        dy.copy_(xin.grad)
+        return dy
+
+
+def make_layer(name: str, cfg: DecoderConfig, index: int) -> Stage:
+    return HybridLayerStage(name, cfg, index)
