@@ -281,8 +281,20 @@ static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 }
 
 // 2-D bf16 row-major [rows, cols] with element pitch ld; box = [box_rows, 64 cols], 128B swizzle.
+// The tensor-map encoder is a driver entry point and needs this thread to have a
+// current context. Framework worker threads (for example an autograd engine thread)
+// may not have touched the runtime yet, so bind the device that owns the operand.
+static void bind_device_of(const void* ptr) {
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, ptr) == cudaSuccess && attr.type == cudaMemoryTypeDevice)
+    cudaSetDevice(attr.device);
+  else
+    cudaGetLastError();   // clear the sticky "invalid value" of a non-CUDA pointer
+}
+
 int make_tmap_bf16(CUtensorMap* map, const void* base, long long rows, long long cols,
                    long long ld, int box_rows) {
+  bind_device_of(base);
   auto fn = encode_fn();
   if (fn == nullptr) return -1;
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
