@@ -137,6 +137,10 @@ class HybridLayerStage(Stage):
         c = self.cfg
         T = h.shape[0]
         logits = A.linear(h, P["router"], sink, "router").float()
+        if h.is_cuda:
+            from ..ops import moe as moe_ops
+            out = moe_ops.experts(h, logits, P["w13"], P["w2"], c.top_k, c.router_renormalize, sink)
+            return self._shared(P, L, h, sink, out)
         if c.router_renormalize:
             vals, ids = torch.topk(logits, c.top_k, dim=-1)
             wts = torch.softmax(vals, dim=-1)
@@ -159,6 +163,10 @@ class HybridLayerStage(Stage):
             ye = A.linear(A.swiglu(gu), P["w2"][e], sink, "w2", e)
             out = out.index_add(0, rows, ye * w_sorted[pos:pos + n, None])
             pos += n
+        return self._shared(P, L, h, sink, out)
+
+    def _shared(self, P, L, h, sink, out):
+        c = self.cfg
         if c.d_shared_expert:
             sh = A.linear(A.swiglu(A.linear(h, P["sw13"], sink, "sw13")), P["sw2"], sink, "sw2")
             if c.gated_shared_expert:
@@ -203,7 +211,7 @@ class HybridLayerStage(Stage):
     def backward(self, P, G, x, dy, meta: BatchMeta, saved, first: bool):
         bounds = meta.cu_seqlens.tolist() if self.mixer == "deltanet" else None
         sink = A.GradSink(G, first)
-        if first:
+        if first and not x.is_cuda:
             for name in self._banks:          # experts without tokens still need defined gradients
                 G[name].zero_()
                 for e in range(self.cfg.n_experts):

@@ -42,6 +42,20 @@ struct GemmCfg {
   static constexpr int TMEM_COLS = 2 * BN;  // 512 or 256
 };
 
+// Grouped (mixture-of-experts) forms share the kernel:
+//   mode 1  rows of A/C are grouped by expert in 128-row-aligned segments; the B
+//           operand of a tile is expert tile_expert[m-block] of a [E, ., .] bank
+//           (forward and data-gradient of an expert bank).
+//   mode 2  one output matrix per expert, contracted over that expert's padded row
+//           segment [expert_offset[e], expert_offset[e+1]) (weight gradient of a bank).
+struct GroupInfo {
+  int mode;
+  const int* tile_expert;     // mode 1: [ceil(M/128)], -1 = tile past the used rows
+  const int* expert_offset;   // mode 2: [E+1], multiples of 128
+  int n_experts;
+  long long c_expert_stride;  // mode 2: elements between experts' outputs
+};
+
 struct GemmParams {
   void* C;
   int M, N, K;
@@ -51,6 +65,13 @@ struct GemmParams {
   int a_mn, b_mn;
   int* status;
   float alpha;
+  GroupInfo g;
+};
+
+struct TileWork {
+  int mb, nb, expert, kb0, nkb;
+  long long c_off;
+  bool skip;
 };
 
 __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& mb, int& nb) {
@@ -62,6 +83,28 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& mb
   const int r = t - g * per_group;
   mb = first_m + (r % gm);
   nb = r / gm;
+}
+
+__device__ __forceinline__ TileWork decode_tile(const GemmParams& p, int t, int num_m, int num_n,
+                                                int num_kb) {
+  TileWork w;
+  w.expert = 0; w.kb0 = 0; w.nkb = num_kb; w.c_off = 0; w.skip = false;
+  if (p.g.mode == 2) {
+    const int per = num_m * num_n;
+    w.expert = t / per;
+    tile_coords(t - w.expert * per, num_m, num_n, w.mb, w.nb);
+    const int lo = p.g.expert_offset[w.expert], hi = p.g.expert_offset[w.expert + 1];
+    w.kb0 = lo / BK;
+    w.nkb = (hi - lo) / BK;
+    w.c_off = static_cast<long long>(w.expert) * p.g.c_expert_stride;
+  } else {
+    tile_coords(t, num_m, num_n, w.mb, w.nb);
+    if (p.g.mode == 1) {
+      w.expert = p.g.tile_expert[w.mb];
+      w.skip = w.expert < 0;
+    }
+  }
+  return w;
 }
 
 template <int BN, bool A_MN, bool B_MN>
@@ -84,7 +127,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int lane = threadIdx.x & 31;
   const int num_m = (p.M + BM - 1) / BM;
   const int num_n = (p.N + BN - 1) / BN;
-  const int num_tiles = num_m * num_n;
+  const int num_tiles = num_m * num_n * (p.g.mode == 2 ? p.g.n_experts : 1);
   const int num_kb = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -116,9 +159,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        int mb, nb;
-        tile_coords(t, num_m, num_n, mb, nb);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const TileWork w = decode_tile(p, t, num_m, num_n, num_kb);
+        if (w.skip) continue;
+        const int mb = w.mb, nb = w.nb;
+        for (int kr = 0; kr < w.nkb; ++kr) {
+          const int kb = w.kb0 + kr;
           if (!mbar_wait(&empty[stage], phase ^ 1, p.status, KS_TIMEOUT_EMPTY)) {
             ok = false;
             break;
@@ -133,12 +178,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int j = 0; j < BM / 64; ++j)
               tma_load_2d(sa + j * (BK * 128), &tmA, &full[stage], mb * BM + j * 64, kb * BK);
           }
+          // B is always described by a 3-D map [expert, rows, cols]; plain GEMMs have one expert
+          const int bz = p.g.mode == 1 ? w.expert : 0;
           if (!B_MN) {
-            tma_load_2d(sb, &tmB, &full[stage], kb * BK, nb * BN);
+            tma_load_3d(sb, &tmB, &full[stage], kb * BK, nb * BN, bz);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(sb + j * (BK * 128), &tmB, &full[stage], nb * BN + j * 64, kb * BK);
+              tma_load_3d(sb + j * (BK * 128), &tmB, &full[stage], nb * BN + j * 64, kb * BK, bz);
           }
           if (++stage == Cfg::STAGES) {
             stage = 0;
@@ -157,10 +204,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const TileWork w = decode_tile(p, t, num_m, num_n, num_kb);
+        if (w.skip || w.nkb == 0) continue;
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1, p.status, KS_TIMEOUT_TMEM_EMPTY)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = 0; kb < w.nkb; ++kb) {
           if (!mbar_wait(&full[stage], phase, p.status, KS_TIMEOUT_FULL)) {
             ok = false;
             break;
@@ -196,8 +245,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-      int mb, nb;
-      tile_coords(t, num_m, num_n, mb, nb);
+      const TileWork w = decode_tile(p, t, num_m, num_n, num_kb);
+      if (w.skip) continue;
+      const int mb = w.mb, nb = w.nb;
+      if (w.nkb == 0) {
+        // an expert without rows: its gradient tile is zero (nothing to add when accumulating)
+        if (!p.accumulate) {
+          const int zr = mb * BM + q * 32 + lane;
+          for (int c = nb * BN; zr < p.M && c < min(p.N, (nb + 1) * BN); c += 8) {
+            if (p.c_f32) {
+              float* d = reinterpret_cast<float*>(p.C) + w.c_off + static_cast<long long>(zr) * p.ldc + c;
+              *reinterpret_cast<float4*>(d) = make_float4(0, 0, 0, 0);
+              *reinterpret_cast<float4*>(d + 4) = make_float4(0, 0, 0, 0);
+            } else {
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + w.c_off +
+                                        static_cast<long long>(zr) * p.ldc + c) = make_uint4(0, 0, 0, 0);
+            }
+          }
+        }
+        continue;
+      }
       if (!mbar_wait(&tfull[acc], acc_phase, p.status, KS_TIMEOUT_TMEM_FULL)) break;
       tc_fence_after();
       const int row = mb * BM + q * 32 + lane;
@@ -212,7 +279,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (row < p.M && col0 < p.N) {
           const int ncols = min(32, p.N - col0);
           if (p.c_f32) {
-            float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+            float* dst = reinterpret_cast<float*>(p.C) + w.c_off + static_cast<long long>(row) * p.ldc + col0;
             for (int j = 0; j < ncols; j += 4) {
               float4 v = make_float4(__uint_as_float(r[j]) * p.alpha,
                                      __uint_as_float(r[j + 1]) * p.alpha,
@@ -226,7 +293,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
           } else {
             __nv_bfloat16* dst =
-                reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+                reinterpret_cast<__nv_bfloat16*>(p.C) + w.c_off + static_cast<long long>(row) * p.ldc + col0;
             for (int j = 0; j < ncols; j += 8) {
               float f[8];
 #pragma unroll
@@ -307,6 +374,24 @@ int make_tmap_bf16(CUtensorMap* map, const void* base, long long rows, long long
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
+// 3-D bf16 [experts, rows, cols] with row pitch ld and expert pitch `expert_rows * ld`.
+int make_tmap3_bf16(CUtensorMap* map, const void* base, long long experts, long long rows,
+                    long long cols, long long ld, long long expert_pitch_elems, int box_rows) {
+  bind_device_of(base);
+  auto fn = encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows),
+                        static_cast<cuuint64_t>(experts)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * 2,
+                           static_cast<cuuint64_t>(expert_pitch_elems) * 2};
+  cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
 template <int BN, bool A_MN, bool B_MN>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int num_sms,
                   cudaStream_t stream) {
@@ -318,10 +403,33 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
-  const int grid = tiles < num_sms ? tiles : num_sms;
+  const long long tiles = static_cast<long long>((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) *
+                          (p.g.mode == 2 ? p.g.n_experts : 1);
+  const int grid = tiles < num_sms ? static_cast<int>(tiles) : num_sms;
   kern<<<grid, GEMM_THREADS, Cfg::SMEM, stream>>>(ta, tb, p);
   return static_cast<int>(cudaGetLastError());
+}
+
+static int dispatch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int bn,
+                    int num_sms, cudaStream_t s) {
+  const bool a_mn = p.a_mn, b_mn = p.b_mn;
+#define SS_DISPATCH(BN_)                                                              \
+  do {                                                                                \
+    if (!a_mn && !b_mn) return launch<BN_, false, false>(ta, tb, p, num_sms, s);      \
+    if (!a_mn && b_mn) return launch<BN_, false, true>(ta, tb, p, num_sms, s);        \
+    if (a_mn && b_mn) return launch<BN_, true, true>(ta, tb, p, num_sms, s);          \
+    return launch<BN_, true, false>(ta, tb, p, num_sms, s);                           \
+  } while (0)
+  if (bn == 256) SS_DISPATCH(256);
+  SS_DISPATCH(128);
+#undef SS_DISPATCH
+}
+
+static int sm_count() {
+  int dev = 0, n = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  return n;
 }
 
 }  // namespace ss
@@ -341,33 +449,59 @@ int ss_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lon
       (reinterpret_cast<uintptr_t>(C) & 15))
     return -2;
   if (bn != 128 && bn != 256) bn = (N <= 128) ? 128 : 256;
-  if (num_sms <= 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-  }
+  if (num_sms <= 0) num_sms = sm_count();
   CUtensorMap ta, tb;
   int r;
   if (!a_mn) r = make_tmap_bf16(&ta, A, M, K, lda, BM);
   else       r = make_tmap_bf16(&ta, A, K, M, lda, BK);
   if (r) return r;
-  if (!b_mn) r = make_tmap_bf16(&tb, B, N, K, ldb, bn);
-  else       r = make_tmap_bf16(&tb, B, K, N, ldb, BK);
+  if (!b_mn) r = make_tmap3_bf16(&tb, B, 1, N, K, ldb, static_cast<long long>(N) * ldb, bn);
+  else       r = make_tmap3_bf16(&tb, B, 1, K, N, ldb, static_cast<long long>(K) * ldb, BK);
   if (r) return r;
-  GemmParams p;
+  GemmParams p{};
   p.C = C; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.c_f32 = c_f32; p.accumulate = accumulate;
   p.a_mn = a_mn; p.b_mn = b_mn; p.status = status; p.alpha = alpha;
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-#define SS_DISPATCH(BN_)                                                              \
-  do {                                                                                \
-    if (!a_mn && !b_mn) return launch<BN_, false, false>(ta, tb, p, num_sms, s);      \
-    if (!a_mn && b_mn) return launch<BN_, false, true>(ta, tb, p, num_sms, s);        \
-    if (a_mn && b_mn) return launch<BN_, true, true>(ta, tb, p, num_sms, s);          \
-    return launch<BN_, true, false>(ta, tb, p, num_sms, s);                           \
-  } while (0)
-  if (bn == 256) SS_DISPATCH(256);
-  SS_DISPATCH(128);
-#undef SS_DISPATCH
+  p.g.mode = 0;
+  return dispatch(ta, tb, p, bn, num_sms, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// Expert-bank GEMMs over token rows sorted by expert into 128-row-aligned segments.
+//   mode 1, b_mn = 0: C[R,N]  = A[R,K] @ bank[e][N,K]^T     (forward through the bank)
+//   mode 1, b_mn = 1: C[R,N]  = A[R,K] @ bank[e][K,N]        (data gradient)
+//   mode 2          : C[e][M,N] (+)= A[rows_e, M]^T @ B[rows_e, N]   (weight gradient)
+// R = padded row count; `tile_expert` (mode 1) and `expert_offset` (mode 2) are device arrays.
+int ss_gemm_grouped_bf16(const void* A, const void* B, void* C, int mode, int rows, int M, int N,
+                         int K, int n_experts, long long lda, long long ldb, long long ldc,
+                         int b_mn, int c_f32, int accumulate, const int* tile_expert,
+                         const int* expert_offset, int bn, int* status, void* stream) {
+  using namespace ss;
+  if (rows <= 0 || n_experts <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (ldc % (c_f32 ? 4 : 8)) || (N % 8) || (rows % BM)) return -2;
+  if (bn != 128 && bn != 256) bn = (N <= 128) ? 128 : 256;
+  CUtensorMap ta, tb;
+  GemmParams p{};
+  int r;
+  if (mode == 1) {
+    if (tile_expert == nullptr) return -2;
+    if ((r = make_tmap_bf16(&ta, A, rows, K, lda, BM))) return r;
+    if (!b_mn) r = make_tmap3_bf16(&tb, B, n_experts, N, K, ldb, static_cast<long long>(N) * ldb, bn);
+    else       r = make_tmap3_bf16(&tb, B, n_experts, K, N, ldb, static_cast<long long>(K) * ldb, BK);
+    if (r) return r;
+    p.M = rows; p.N = N; p.K = K; p.a_mn = 0; p.b_mn = b_mn;
+  } else if (mode == 2) {
+    if (expert_offset == nullptr) return -2;
+    // A stored [rows, M] and B stored [rows, N]: both contraction-major over the sorted rows
+    if ((r = make_tmap_bf16(&ta, A, rows, M, lda, BK))) return r;
+    if ((r = make_tmap3_bf16(&tb, B, 1, rows, N, ldb, static_cast<long long>(rows) * ldb, BK))) return r;
+    p.M = M; p.N = N; p.K = rows; p.a_mn = 1; p.b_mn = 1;
+    p.g.c_expert_stride = static_cast<long long>(M) * ldc;
+  } else {
+    return -2;
+  }
+  p.C = C; p.ldc = ldc; p.c_f32 = c_f32; p.accumulate = accumulate; p.status = status; p.alpha = 1.f;
+  p.g.mode = mode; p.g.tile_expert = tile_expert; p.g.expert_offset = expert_offset;
+  p.g.n_experts = n_experts;
+  return dispatch(ta, tb, p, bn, sm_count(), reinterpret_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"
