@@ -1,0 +1,147 @@
+"""Failure detection without touching a GPU: the mock backend fails the n-th
+operation, host-side waits run out, and the first failure is latched."""
+import sys
+
+import pytest
+import torch
+
+sys.path.insert(0, __file__.rsplit("/", 1)[0])
+from test_executor_cpu import _batches, _setup  # noqa: E402
+
+from shadowspill_b200 import native
+from shadowspill_b200.execution.executor import Executor
+from shadowspill_b200.orchestration.nodes import AdmissionError, Membership, NodeAdmission
+from shadowspill_b200.runtime.core import Runtime, RuntimeFailure
+from shadowspill_b200.server.journal import Journal, JournalCorrupt
+from shadowspill_b200.training.controller import OperationState, Rejected, RunController
+
+
+def test_failed_copy_latches_and_refuses_further_work():
+    cfg, plan, desc = _setup()
+    ex = Executor(plan, desc, device="cpu", seed=1)
+    ex.initialize()
+    ex.run(_batches(cfg))                                   # a clean step first
+    ex.rt.mock_fail("copy", 5)                              # the 5th copy from now fails
+    with pytest.raises(RuntimeFailure) as e:
+        ex.run(_batches(cfg, 1))
+    info = e.value.info
+    assert info["status"] == native.BACKEND_FAILURE and info["action"] >= 0 and info["object"] >= 0
+    assert "failed to enqueue" in info["message"]
+    # first writer wins: a later failure does not overwrite the record
+    ex.rt.latch_failure("second failure")
+    assert ex.rt.failure()["message"] == info["message"]
+    with pytest.raises(RuntimeFailure):
+        ex.run(_batches(cfg, 2))                            # latched: nothing starts
+    ex.closed = True
+    ex.rt.close()
+
+
+def test_failed_event_record_is_attributed_to_the_task():
+    cfg, plan, desc = _setup()
+    ex = Executor(plan, desc, device="cpu", seed=1)
+    ex.initialize()
+    ex.rt.mock_fail("event_record", 3)
+    with pytest.raises(RuntimeFailure) as e:
+        ex.run(_batches(cfg))
+    assert e.value.info["status"] == native.BACKEND_FAILURE
+    ex.closed = True
+    ex.rt.close()
+
+
+def test_pool_allocation_failure_is_reported_at_creation():
+    lib = native.core()
+    backend = lib.ss_mock_backend_create(0.0, 0)
+    lib.ss_mock_fail_operation(backend, native.OP_KINDS.index("device_alloc"), 1)
+    import ctypes as C
+    cfg = native.RuntimeConfig(1 << 20, 1 << 20, -1, 0, 1000, 0, 0, None)
+    handle = native.vp()
+    assert lib.ss_runtime_create(backend, C.byref(cfg), C.byref(handle)) == native.OOM
+
+
+def test_trace_ring_records_the_step():
+    cfg, plan, desc = _setup()
+    ex = Executor(plan, desc, device="cpu", seed=1, trace_capacity=4096)
+    ex.initialize()
+    res = ex.run(_batches(cfg), trace=True, time_tasks=True)
+    kinds = {e["kind"] for e in res.trace}
+    assert {"step_begin", "task_begin", "task_end", "fetch_issue", "step_end"} <= kinds
+    assert sum(e["kind"] == "task_end" for e in res.trace) == len(plan.program.tasks)
+    assert len(res.task_seconds) == len(plan.program.tasks)
+    ex.close()
+
+
+def test_membership_lease_expiry_fences_permanently():
+    now = [0.0]
+    m = Membership(lease_seconds=10.0, clock=lambda: now[0])
+    inc = m.join("node-a")
+    now[0] = 5.0
+    assert m.heartbeat("node-a", inc) and m.live() == ["node-a"]
+    now[0] = 30.0
+    assert m.reconcile() == ["node-a"] and m.live() == []
+    assert not m.heartbeat("node-a", inc)                    # a late heartbeat is refused
+    inc2 = m.join("node-a")
+    assert inc2 != inc and m.heartbeat("node-a", inc2)
+    assert not m.heartbeat("node-a", inc)                    # the old incarnation stays fenced
+
+
+def test_node_admission_never_oversubscribes():
+    adm = NodeAdmission(gpus=4, host_bytes=100)
+    a, devs = adm.lease(3, 60)
+    assert devs == (0, 1, 2)
+    with pytest.raises(AdmissionError):
+        adm.lease(2, 10)
+    with pytest.raises(AdmissionError):
+        adm.lease(1, 50)
+    adm.release(a)
+    assert adm.lease(4, 100)[1] == (0, 1, 2, 3)
+
+
+def test_journal_chain_detects_tampering(tmp_path):
+    j = Journal(tmp_path)
+    for i in range(5):
+        j.append("receipt", {"i": i})
+    assert [r["data"]["i"] for r in Journal(tmp_path).records("receipt")] == list(range(5))
+    victim = tmp_path / "000000000002.json"
+    victim.write_text(victim.read_text().replace('"i": 2', '"i": 9'))
+    with pytest.raises(JournalCorrupt):
+        Journal(tmp_path)
+
+
+def test_operation_state_machine():
+    s = OperationState()
+    s.admit("forward_backward"); s.complete("forward_backward")
+    for op in ("step", "save", "restore"):
+        with pytest.raises(Rejected):
+            s.admit(op)
+    s.admit("optim_step"); s.complete("optim_step")
+    assert s.b.completed_updates == 1 and s.b.accumulation == 0
+    with pytest.raises(Rejected):
+        s.admit("optim_step")                                # nothing accumulated
+    s.fail("unknown")
+    with pytest.raises(Rejected):
+        s.admit("step")
+    s.admit("close")                                         # the only thing still accepted
+
+
+def test_controller_never_replays_and_propagates_failed_dependencies():
+    calls = []
+
+    def execute(req, payload):
+        calls.append(req["request_id"])
+        if req["operation"] == "forward_backward":
+            err = RuntimeError("worker lost"); err.effect = "unknown"
+            raise err
+        return {"loss": 1.0}
+    c = RunController(execute)
+    a = {"request_id": "a", "operation": "step", "dependencies": [], "digest": "d1"}
+    c.register(a)
+    assert c.wait("a", 5).state == "completed"
+    assert c.register(a).state == "completed" and calls == ["a"]          # idempotent, not replayed
+    with pytest.raises(Rejected):
+        c.register(dict(a, digest="other"))
+    c.register({"request_id": "b", "operation": "forward_backward", "dependencies": ["a"], "digest": "d2"})
+    rb = c.wait("b", 5)
+    assert rb.state == "failed" and rb.effect == "unknown"
+    c.register({"request_id": "c", "operation": "step", "dependencies": ["b"], "digest": "d3"})
+    assert c.wait("c", 5).state == "rejected" and calls == ["a", "b"]
+    c.stop()
