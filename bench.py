@@ -102,6 +102,9 @@ def main() -> None:
     ap.add_argument("--spill-gib", type=float, default=128.0)
     ap.add_argument("--tokens", type=int, default=65536, help="tokens per worker per step")
     ap.add_argument("--microbatch", type=int, default=8192)
+    ap.add_argument("--candidates", default="100,75:save,50:save,0:save_attention",
+                    help="comma list of <recompute share %%>[:<saved variant>] programs the planner sweeps")
+    ap.add_argument("--walks", default="breadth")
     ap.add_argument("--report", default="", help="directory for the plan report")
     ap.add_argument("--collectives", default="auto", choices=["auto", "peer", "dist"],
                     help="peer = own kernels over NVLink peer memory; dist = NCCL baseline arm")
@@ -128,8 +131,21 @@ def main() -> None:
     setup = TrainingSetup(model=args.model, device_gib=args.device_gib, spill_gib=args.spill_gib,
                           tokens_per_step=args.tokens, microbatch_tokens=args.microbatch,
                           lr=1e-5, seed=1234, rank=rank, world_size=world, device_index=local,
-                          collectives=args.collectives)
-    session = TrainingSession(setup)          # build -> profile -> calibrate -> plan -> executor
+                          collectives=args.collectives,
+                          candidate_selections=tuple(c for c in args.candidates.split(",") if c),
+                          walks=tuple(args.walks.split(",")),
+                          trace_capacity=(1 << 16) if args.report else 0)
+    log = (lambda m: print(f"[bench] {m}", file=sys.stderr, flush=True)) if rank == 0 else None
+    session = TrainingSession(setup, log=log)  # build -> profile -> calibrate -> plan -> executor
+    if rank == 0:
+        for pl, err in zip(session.sweep.plans, session.sweep.errors):
+            if pl is None:
+                log(f"candidate infeasible: {err.splitlines()[0] if err else '?'}")
+            else:
+                sm = pl.summary
+                log(f"candidate {sm.ordering} [{sm.selection[:60]}]: simulated "
+                    f"{sm.duration_seconds * 1e3:.0f} ms, fetch {sm.fetch_bytes / 1e9:.0f} GB, "
+                    f"evict {sm.evict_bytes / 1e9:.0f} GB")
     cfg = session.cfg
     n_batches = args.warmup + args.steps
     batches = [make_batch(1000 * rank + i, vocab=cfg.vocab_size, tokens_per_step=args.tokens,
@@ -205,8 +221,22 @@ def main() -> None:
             "peak_device_gib": round(session.peak_device_bytes() / GIB, 2),
         }
         print(json.dumps(out), flush=True)
-    if args.report and rank == 0:
-        session.write_plan_report(args.report)
+    if args.report:
+        # one more (untimed) step with per-task clocks and the runtime trace on
+        extra = make_batch(1000 * rank + n_batches, vocab=cfg.vocab_size, tokens_per_step=args.tokens,
+                           microbatch_tokens=args.microbatch, max_len=8192, median=1200.0,
+                           slots=session.slots)
+        for mb in extra:
+            mb.weights /= world
+        _, diag = session.traced_step(extra, args.report if rank == 0 else None)
+        if rank == 0:
+            session.write_plan_report(args.report)
+            log(f"traced step: real {diag.makespan_s * 1e3:.0f} ms vs simulated "
+                f"{diag.simulated_makespan_s * 1e3:.0f} ms; tasks real {diag.task_seconds_real * 1e3:.0f} "
+                f"/ profiled {diag.task_seconds_profiled * 1e3:.0f} ms; idle {diag.idle_seconds_real * 1e3:.0f} ms "
+                f"(inputs {diag.input_readiness_wait_seconds * 1e3:.0f}, reuse "
+                f"{diag.allocation_reuse_wait_seconds * 1e3:.0f}, frontend "
+                f"{diag.frontend_overhead_seconds * 1e3:.0f})")
     session.close()
     if world > 1:
         dist.destroy_process_group()

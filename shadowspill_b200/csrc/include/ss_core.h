@@ -284,6 +284,11 @@ int ss_runtime_stats_read(ss_runtime* rt, ss_runtime_stats* out);
 int ss_trace_begin(ss_runtime* rt);
 int ss_trace_end(ss_runtime* rt);
 int32_t ss_trace_read(ss_runtime* rt, ss_trace_event* out, int32_t capacity);
+/* Device-clock start and end of every transfer of the plan's last step, relative to the
+ * step's first event; -1 where an action moved nothing. Only on runtimes created with
+ * trace_capacity > 0 (their events carry timestamps). Returns the action count or -1. */
+int32_t ss_plan_transfer_times(ss_runtime* rt, int32_t plan_id, int64_t* begin_ns, int64_t* end_ns,
+                               int32_t capacity);
 
 /* Plan admission: objects get spill homes, intervals fixed device offsets.
  * spill_offset[o] < 0 means the object never touches the spill pool. */

@@ -54,6 +54,8 @@ struct PlanState {
   std::vector<std::vector<int32_t>> task_creates;   // stays opened by each task
   std::vector<void*> task_fence;               // one event per task
   std::vector<void*> action_event;             // one event per transfer action
+  std::vector<void*> action_begin_event;       // only with tracing configured: copy start
+  void* step_begin_event = nullptr;            // only with tracing configured
   std::vector<int32_t> action_prev_evict;      // fetch -> earlier evict of the same object, or -1
   std::vector<std::atomic<int>> action_issued;
   // per step
@@ -122,8 +124,8 @@ struct ss_runtime {
 
 namespace {
 
-int new_event(ss_runtime* rt, void** out) {
-  int rc = rt->be->event_create(rt->be->self, 0, out);
+int new_event(ss_runtime* rt, void** out, int timing = 0) {
+  int rc = rt->be->event_create(rt->be->self, timing, out);
   if (rc == SS_OK) rt->st_events++;
   return rc;
 }
@@ -157,6 +159,8 @@ bool pump_plan(ss_runtime* rt, PlanState& P) {
     if (A.trigger_task >= 0) rc = be->stream_wait_event(be->self, rt->evict_stream, P.task_fence[A.trigger_task]);
     if (rc == SS_OK && I.ready_event && I.iv.begin_action >= 0)
       rc = be->stream_wait_event(be->self, rt->evict_stream, I.ready_event);
+    if (rc == SS_OK && !P.action_begin_event.empty())
+      rc = be->event_record(be->self, P.action_begin_event[a], rt->evict_stream);
     if (rc == SS_OK)
       rc = be->copy_async(be->self, rt->spill(P.spill_offset[A.object]), rt->dev(I.iv.offset),
                           static_cast<size_t>(P.object_bytes[A.object]), SS_COPY_D2H, rt->evict_stream);
@@ -193,6 +197,8 @@ bool pump_plan(ss_runtime* rt, PlanState& P) {
       if (J.release_event) rc = be->stream_wait_event(be->self, rt->fetch_stream, J.release_event);
     }
     if (rc == SS_OK && pe >= 0) rc = be->stream_wait_event(be->self, rt->fetch_stream, P.action_event[pe]);
+    if (rc == SS_OK && !P.action_begin_event.empty())
+      rc = be->event_record(be->self, P.action_begin_event[a], rt->fetch_stream);
     if (rc == SS_OK)
       rc = be->copy_async(be->self, rt->dev(I.iv.offset), rt->spill(P.spill_offset[A.object]),
                           static_cast<size_t>(P.object_bytes[A.object]), SS_COPY_H2D, rt->fetch_stream);
@@ -289,8 +295,11 @@ int ss_runtime_create(ss_backend* backend, const ss_runtime_config* config, ss_r
 static void release_plan(ss_runtime* rt, PlanState& P) {
   for (void* e : P.task_fence) if (e) rt->be->event_destroy(rt->be->self, e);
   for (void* e : P.action_event) if (e) rt->be->event_destroy(rt->be->self, e);
+  for (void* e : P.action_begin_event) if (e) rt->be->event_destroy(rt->be->self, e);
   if (P.step_event) rt->be->event_destroy(rt->be->self, P.step_event);
-  P.task_fence.clear(); P.action_event.clear(); P.step_event = nullptr;
+  if (P.step_begin_event) rt->be->event_destroy(rt->be->self, P.step_begin_event);
+  P.task_fence.clear(); P.action_event.clear(); P.action_begin_event.clear();
+  P.step_event = P.step_begin_event = nullptr;
 }
 
 int ss_runtime_close(ss_runtime* rt) {
@@ -448,10 +457,17 @@ int ss_plan_admit(ss_runtime* rt, const ss_plan_desc* d, int32_t* plan_id) {
   P->action_event.assign(d->n_actions, nullptr);
   for (int32_t t = 0; t < d->n_tasks; ++t)
     if (int rc = new_event(rt, &P->task_fence[t])) { release_plan(rt, *P); return rc; }
+  const int timed = rt->ring.empty() ? 0 : 1;   // tracing configured: events carry timestamps
+  if (timed) P->action_begin_event.assign(d->n_actions, nullptr);
   for (int32_t a = 0; a < d->n_actions; ++a)
-    if (P->actions[a].kind != SS_ACT_RELEASE)
-      if (int rc = new_event(rt, &P->action_event[a])) { release_plan(rt, *P); return rc; }
+    if (P->actions[a].kind != SS_ACT_RELEASE) {
+      if (int rc = new_event(rt, &P->action_event[a], timed)) { release_plan(rt, *P); return rc; }
+      if (timed)
+        if (int rc = new_event(rt, &P->action_begin_event[a], 1)) { release_plan(rt, *P); return rc; }
+    }
   if (int rc = new_event(rt, &P->step_event)) { release_plan(rt, *P); return rc; }
+  if (timed)
+    if (int rc = new_event(rt, &P->step_begin_event, 1)) { release_plan(rt, *P); return rc; }
   P->action_issued = std::vector<std::atomic<int>>(d->n_actions);
   P->object_current.assign(d->n_objects, -1);
   std::lock_guard<std::mutex> lk(rt->mu);
@@ -489,6 +505,8 @@ int ss_step_begin(ss_runtime* rt, int32_t plan_id, void* compute_stream) {
     P->next_fetch = P->next_evict = P->next_release = 0;
     P->compute_stream = compute_stream;
     P->published_task.store(-1, std::memory_order_release);
+    if (P->step_begin_event)
+      rt->be->event_record(rt->be->self, P->step_begin_event, compute_stream);
     P->active = true;
   }
   rt->st_steps++;
@@ -609,6 +627,28 @@ int ss_step_end(ss_runtime* rt, int32_t plan_id) {
   rt->trace(SS_TRACE_STEP_END, plan_id, 0);
   if (rt->failed.load()) return SS_FAILED;
   return result;
+}
+
+int32_t ss_plan_transfer_times(ss_runtime* rt, int32_t plan_id, int64_t* begin_ns, int64_t* end_ns,
+                               int32_t capacity) {
+  if (!rt || !begin_ns || !end_ns) return -1;
+  PlanState* P;
+  { std::lock_guard<std::mutex> lk(rt->mu); P = find_plan(rt, plan_id); }
+  if (!P || P->active || !P->step_begin_event) return -1;
+  ss_backend* be = rt->be;
+  be->stream_synchronize(be->self, rt->fetch_stream);
+  be->stream_synchronize(be->self, rt->evict_stream);
+  const int32_t n = std::min<int32_t>(capacity, static_cast<int32_t>(P->actions.size()));
+  for (int32_t a = 0; a < n; ++a) {
+    begin_ns[a] = end_ns[a] = -1;
+    if (!P->action_event[a] || !P->action_issued[a].load(std::memory_order_acquire)) continue;
+    int64_t b = 0, e = 0;
+    if (be->event_elapsed_ns(be->self, P->step_begin_event, P->action_begin_event[a], &b) == SS_OK &&
+        be->event_elapsed_ns(be->self, P->step_begin_event, P->action_event[a], &e) == SS_OK) {
+      begin_ns[a] = b; end_ns[a] = e;
+    }
+  }
+  return static_cast<int32_t>(P->actions.size());
 }
 
 int ss_runtime_wait_idle(ss_runtime* rt) {

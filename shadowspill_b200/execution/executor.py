@@ -49,7 +49,10 @@ class InvocationResult:
     h2d_bytes: int = 0
     d2h_bytes: int = 0
     task_seconds: list[float] = field(default_factory=list)
+    task_start_seconds: list[float] = field(default_factory=list)   # from the step's first event
     trace: list[dict] = field(default_factory=list)
+    transfer_begin_ns: list[int] = field(default_factory=list)      # device clock, per action
+    transfer_end_ns: list[int] = field(default_factory=list)
     metrics: dict[str, float] = field(default_factory=dict)
 
 
@@ -124,11 +127,16 @@ class TaskRunner:
         st = self.stages[t.stage]
         meta = self._batch_meta(B["batch_flat"], t.microbatch) if "batch_flat" in B else None
         if t.kind == "forward":
-            keep = st.SAVE_SETS.get(t.variant, ()) if "saved" in B else ()
-            _, saved = st.forward(B["params"], B.get("x"), meta, keep, out=B["y"])
             if "saved" in B:
-                for name, dst in B["saved"].items():
-                    dst.copy_(saved[name].reshape(dst.shape))
+                keep = st.SAVE_SETS.get(t.variant, ())
+                _, saved = st.forward(B["params"], B.get("x"), meta, keep, out=B["y"],
+                                      saved_out=B["saved"])
+                for name, dst in B["saved"].items():     # anything not produced in place
+                    src = saved[name]
+                    if src.data_ptr() != dst.data_ptr():
+                        dst.copy_(src.reshape(dst.shape))
+            else:
+                st.forward(B["params"], B.get("x"), meta, (), out=B["y"])
         elif t.kind == "head":
             train = t.variant == "train"
             first = self._first(t.stage, B)
@@ -309,7 +317,12 @@ class Executor:
                 st.init_(st.views(w, self.desc.dtype), gen)
             else:
                 # every rank draws the whole stage from the same seed, then keeps its slices
-                flat = torch.zeros(full_bytes, dtype=torch.uint8, device=dev)
+                if on_device and self.rt.device.numel() >= full_bytes:
+                    # between steps the planned device pool holds nothing: stage in it
+                    # instead of asking the (capped) torch allocator for a whole stage
+                    flat = self.rt.device[:full_bytes].zero_()
+                else:
+                    flat = torch.zeros(full_bytes, dtype=torch.uint8, device=dev)
                 full = st.views(flat, self.desc.dtype)
                 st.init_(full, gen)
                 if self.world == 1:
@@ -323,6 +336,8 @@ class Executor:
                         hi = min(src.numel(), lo + dst.numel())
                         if hi > lo:
                             dst[:hi - lo].copy_(src[lo:hi])
+                if on_device:
+                    torch.cuda.synchronize(self.torch_device)
                 del flat
             for suffix in ("exp_avg", "exp_avg_sq", "gradients"):
                 name = f"{st.name}.{suffix}"
@@ -473,18 +488,22 @@ class Executor:
         loss = (float(self.spill_view(self._loss_obj)[:4].view(torch.float32)[0])   # device -> host
                 if self._loss_obj >= 0 else 0.0)
         device_seconds = 0.0
+        task_starts: list[float] = []
         if self.cuda:
             device_seconds = start_ev.elapsed_time(end_ev) * 1e-3
             if events:
                 task_seconds = [a.elapsed_time(b) * 1e-3 for a, b in events]
+                task_starts = [start_ev.elapsed_time(a) * 1e-3 for a, _ in events]
         if self.desc.mode in ("step", "optimizer"):
             self.runner.completed_updates += 1
             self.runner.accumulated = 0
         elif self.desc.mode == "forward_backward":
             self.runner.accumulated += 1
         tr = self.rt.trace_end() if trace else []
+        tb, te = (self.rt.transfer_times(self.plan_id, len(self.plan.schedule.actions))
+                  if trace else ([], []))
         return InvocationResult(loss, self.T * self.n_mb, time.perf_counter() - t0, device_seconds,
-                                h2d, 4, task_seconds if time_tasks else [], tr)
+                                h2d, 4, task_seconds if time_tasks else [], task_starts, tr, tb, te)
 
     def discard_gradients(self) -> None:
         self.runner.accumulated = 0

@@ -239,23 +239,26 @@ class DenseLayerStage(Stage):
         return gemm + attn
 
     # ---- forward
-    def _compute(self, P, x, meta: BatchMeta, have: dict, upto: str = "end", out=None):
-        """Fill in every intermediate missing from ``have`` (recompute path) and,
-        when ``upto == 'end'``, return the layer output as well."""
+    def _compute(self, P, x, meta: BatchMeta, have: dict, upto: str = "end", out=None, bufs=None):
+        """Fill in every intermediate missing from ``have`` (recompute path). ``bufs``
+        names preallocated destinations (the views of a saved-set object), so that a
+        saving forward writes what it keeps exactly once, in place."""
         c = self.cfg
         T = x.shape[0]
         dh, Hq, Hkv = c.head_dim, c.n_heads, c.n_kv_heads
         I = dict(have)
+        bufs = bufs or {}
+        b = bufs.get
         if "qkv" not in I or "h1" not in I:
-            h1, rstd1 = F.rmsnorm_fwd(x, P["attn_norm"], c.norm_epsilon, c.zero_centered_norm)
+            h1, rstd1 = F.rmsnorm_fwd(x, P["attn_norm"], c.norm_epsilon, c.zero_centered_norm,
+                                      out=b("h1"), rstd=b("rstd1"))
             I["h1"], I["rstd1"] = h1, rstd1
         if "qkv" not in I:
-            qkv = F.linear_fwd(I["h1"], P["wqkv"])
+            qkv = F.linear_fwd(I["h1"], P["wqkv"], out=b("qkv"))
             if c.qk_norm:
                 self._qk_norm_fwd(P, qkv, I)
-            rot = c.rotary_width
-            F.rope_(qkv, meta.positions, col0=0, heads=Hq, dh=dh, rot=rot, theta=c.rope_base)
-            F.rope_(qkv, meta.positions, col0=Hq * dh, heads=Hkv, dh=dh, rot=rot,
+            # q and k heads are adjacent in the fused projection: one rotary launch covers both
+            F.rope_(qkv, meta.positions, col0=0, heads=Hq + Hkv, dh=dh, rot=c.rotary_width,
                     theta=c.rope_base)
             I["qkv"] = qkv
         qkv = I["qkv"]
@@ -263,8 +266,10 @@ class DenseLayerStage(Stage):
         k = qkv[:, Hq * dh:(Hq + Hkv) * dh].view(T, Hkv, dh)
         v = qkv[:, (Hq + Hkv) * dh:].view(T, Hkv, dh)
         if "attn" not in I:
-            attn, lse = F.attention_varlen(_heads(q), _heads(k), _heads(v), meta.cu_seqlens,
-                                           meta.max_seqlen)
+            ao = b("attn")
+            attn, lse = F.attention_varlen(q, k, v, meta.cu_seqlens, meta.max_seqlen,
+                                           out=None if ao is None else ao.view(T, Hq, dh),
+                                           lse=b("lse"))
             I["attn"], I["lse"] = attn.view(T, Hq * dh), lse
         if "x_mid" not in I:
             x_mid = out if out is not None else torch.empty_like(x)
@@ -273,11 +278,11 @@ class DenseLayerStage(Stage):
             I["x_mid"] = x_mid
         if "h2" not in I or "gu" not in I:
             I["h2"], I["rstd2"] = F.rmsnorm_fwd(I["x_mid"], P["mlp_norm"], c.norm_epsilon,
-                                                c.zero_centered_norm)
+                                                c.zero_centered_norm, out=b("h2"), rstd=b("rstd2"))
         if "gu" not in I:
-            I["gu"] = F.linear_fwd(I["h2"], P["w13"])
+            I["gu"] = F.linear_fwd(I["h2"], P["w13"], out=b("gu"))
         if "hmlp" not in I:
-            I["hmlp"] = F.swiglu_fwd(I["gu"])
+            I["hmlp"] = F.swiglu_fwd(I["gu"], out=b("hmlp"))
         return I
 
     def _qk_norm_fwd(self, P, qkv, I):
@@ -293,14 +298,18 @@ class DenseLayerStage(Stage):
         qkv[:, :Hq * dh] = qn.view(T, Hq * dh)
         qkv[:, Hq * dh:(Hq + Hkv) * dh] = kn.view(T, Hkv * dh)
 
-    def forward(self, P, x, meta: BatchMeta, keep: tuple[str, ...] = (), out=None):
-        """Returns ``(y, saved)`` where ``saved`` holds the intermediates named in ``keep``."""
-        I = self._compute(P, x, meta, {}, out=out)
+    def forward(self, P, x, meta: BatchMeta, keep: tuple[str, ...] = (), out=None, saved_out=None):
+        """Returns ``(y, saved)`` where ``saved`` holds the intermediates named in ``keep``.
+        With ``saved_out`` (name -> preallocated tensor) they are produced in place."""
+        I = self._compute(P, x, meta, {}, out=out, bufs=saved_out)
         y = I["x_mid"]
         saved = {}
         if "x_mid" in keep:
             # the output buffer is about to absorb the MLP branch; keep a copy
-            saved["x_mid"] = y.clone()
+            if saved_out is not None and "x_mid" in saved_out:
+                saved["x_mid"] = saved_out["x_mid"].copy_(y)
+            else:
+                saved["x_mid"] = y.clone()
         F.linear_fwd(I["hmlp"], P["w2"], out=y, accumulate=True)
         for n in keep:
             if n != "x_mid":
@@ -348,11 +357,8 @@ class DenseLayerStage(Stage):
         _attention_bwd(q, k, v, I["attn"].view(T, Hq, dh), I["lse"], dattn.view(T, Hq, dh),
                        meta, dq, dk, dv)
         del dattn
-        rot = c.rotary_width
-        F.rope_(dqkv, meta.positions, col0=0, heads=Hq, dh=dh, rot=rot, theta=c.rope_base,
-                inverse=True)
-        F.rope_(dqkv, meta.positions, col0=Hq * dh, heads=Hkv, dh=dh, rot=rot, theta=c.rope_base,
-                inverse=True)
+        F.rope_(dqkv, meta.positions, col0=0, heads=Hq + Hkv, dh=dh, rot=c.rotary_width,
+                theta=c.rope_base, inverse=True)
         if c.qk_norm:
             self._qk_norm_bwd(P, G, dqkv, I)
         F.linear_wgrad(dqkv, I["h1"], out=G["wqkv"], accumulate=acc)

@@ -192,6 +192,8 @@ def _declare(lib: C.CDLL) -> None:
     lib.ss_trace_begin.argtypes = [vp]
     lib.ss_trace_end.argtypes = [vp]
     lib.ss_trace_read.argtypes = [vp, C.POINTER(TraceEvent), i32]
+    lib.ss_plan_transfer_times.argtypes = [vp, i32, C.POINTER(i64), C.POINTER(i64), i32]
+    lib.ss_plan_transfer_times.restype = i32
     lib.ss_plan_admit.argtypes = [vp, C.POINTER(PlanDesc), P32]
     lib.ss_plan_close.argtypes = [vp, i32]
     lib.ss_step_begin.argtypes = [vp, i32, vp]

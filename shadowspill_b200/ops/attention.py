@@ -54,7 +54,7 @@ def _row_stride(t: torch.Tensor) -> int:
     return t.stride(0)
 
 
-def forward(q, k, v, cu_seqlens, max_seqlen, scale=None, out=None):
+def forward(q, k, v, cu_seqlens, max_seqlen, scale=None, out=None, lse=None):
     T, Hq, dh = q.shape
     Hkv = k.shape[1]
     scale = scale if scale is not None else 1.0 / math.sqrt(dh)
@@ -62,13 +62,16 @@ def forward(q, k, v, cu_seqlens, max_seqlen, scale=None, out=None):
         from flash_attn.flash_attn_interface import _flash_attn_varlen_forward
         res = _flash_attn_varlen_forward(q, k, v, cu_seqlens, cu_seqlens, max_seqlen, max_seqlen,
                                          0.0, scale, causal=True)
-        o, lse = res[0], res[1]
+        o, l = res[0], res[1]
         if out is not None:
             out.copy_(o)
             o = out
-        return o, lse
+        if lse is not None:
+            l = lse.copy_(l)
+        return o, l
     o = torch.empty((T, Hq, dh), dtype=q.dtype, device=q.device) if out is None else out
-    lse = torch.empty((Hq, T), dtype=torch.float32, device=q.device)
+    if lse is None:
+        lse = torch.empty((Hq, T), dtype=torch.float32, device=q.device)
     nseq = cu_seqlens.numel() - 1
     rc = _lib.lib().ss_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
                                 lse.data_ptr(), cu_seqlens.data_ptr(), nseq, T, Hq, Hkv, dh,

@@ -239,6 +239,55 @@ __global__ void rope_kernel(bf16* __restrict__ buf, const int* __restrict__ posi
   }
 }
 
+// Vector form: a thread owns eight adjacent frequencies of one token (its sines and
+// cosines are computed once) and walks `heads_per_thread` heads with 16-byte loads, so
+// the transcendental work is amortised over the heads and the kernel runs at memory
+// speed. Needs rot % 16 == 0 and 16-byte aligned heads.
+__global__ void rope_vec_kernel(bf16* __restrict__ buf, const int* __restrict__ positions, int T,
+                                long long row_stride, int col0, int heads, int dh, int rot,
+                                float log2_theta, int inverse, int slots) {
+  const int half = rot >> 1;
+  const int vph = half >> 3;
+  const int per_token = vph * slots;
+  const long long total = static_cast<long long>(T) * per_token;
+  for (long long gid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; gid < total;
+       gid += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(gid / per_token);
+    const int r = static_cast<int>(gid % per_token);
+    const int slot = r / vph;
+    const int i0 = (r % vph) * 8;
+    const float pos = static_cast<float>(positions[t]);
+    float sn[8], cs[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float f = exp2f(-log2_theta * (2.f * (i0 + e)) / rot);
+      sincosf(pos * f, &sn[e], &cs[e]);
+      if (inverse) sn[e] = -sn[e];
+    }
+    bf16* row = buf + static_cast<long long>(t) * row_stride + col0 + i0;
+    for (int h = slot; h < heads; h += slots) {
+      bf16* base = row + h * dh;
+      uint4 av = *reinterpret_cast<const uint4*>(base);
+      uint4 bv = *reinterpret_cast<const uint4*>(base + half);
+      __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&av);
+      __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&bv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 a = __bfloat1622float2(a2[e]), b = __bfloat1622float2(b2[e]);
+        float2 oa, ob;
+        oa.x = a.x * cs[2 * e] - b.x * sn[2 * e];
+        ob.x = b.x * cs[2 * e] + a.x * sn[2 * e];
+        oa.y = a.y * cs[2 * e + 1] - b.y * sn[2 * e + 1];
+        ob.y = b.y * cs[2 * e + 1] + a.y * sn[2 * e + 1];
+        a2[e] = __float22bfloat162_rn(oa);
+        b2[e] = __float22bfloat162_rn(ob);
+      }
+      *reinterpret_cast<uint4*>(base) = av;
+      *reinterpret_cast<uint4*>(base + half) = bv;
+    }
+  }
+}
+
 // =============================================================== SwiGLU
 // gu is [T, 2F] with gate in columns [0,F) and up in [F,2F) (one fused GEMM
 // output). h = bf16(silu(float(gate))) * up.
@@ -586,6 +635,15 @@ int ss_rope(void* buf, const int* positions, int T, long long row_stride, int co
             int dh, int rot, float theta, int inverse, void* stream) {
   if (rot % 4 || rot > dh || row_stride % 2 || col0 % 2) return -2;
   if (T <= 0) return 0;
+  if (rot % 16 == 0 && dh % 8 == 0 && col0 % 8 == 0 && row_stride % 8 == 0 &&
+      (reinterpret_cast<uintptr_t>(buf) & 15) == 0) {
+    const int hpt = heads >= 8 ? 4 : 1;              // heads walked by one thread
+    const int slots = (heads + hpt - 1) / hpt;
+    const long long threads = (long long)T * (rot >> 4) * slots;
+    rope_vec_kernel<<<grid_for(threads, 256), 256, 0, (cudaStream_t)stream>>>(
+        (bf16*)buf, positions, T, row_stride, col0, heads, dh, rot, log2f(theta), inverse, slots);
+    return (int)cudaGetLastError();
+  }
   const long long total = (long long)T * heads * (rot >> 2);
   rope_kernel<<<grid_for(total, 256), 256, 0, (cudaStream_t)stream>>>(
       (bf16*)buf, positions, T, row_stride, col0, heads, dh, rot, log2f(theta), inverse);

@@ -239,12 +239,17 @@ def sumsq(x, partials, out, accumulate=False):
 
 
 # ------------------------------------------------------------------------ attention
-def attention_varlen(q, k, v, cu_seqlens, max_seqlen, scale=None):
+def attention_varlen(q, k, v, cu_seqlens, max_seqlen, scale=None, out=None, lse=None):
     """Packed causal GQA forward. Returns ``(out, lse)``; ``lse`` is fp32 ``[Hq, T]``."""
     if not _cuda(q):
-        return reference.attention_varlen(q, k, v, cu_seqlens, scale)
+        o, l = reference.attention_varlen(q, k, v, cu_seqlens, scale)
+        if out is not None:
+            o = out.copy_(o)
+        if lse is not None:
+            l = lse.copy_(l)
+        return o, l
     from . import attention
-    return attention.forward(q, k, v, cu_seqlens, max_seqlen, scale)
+    return attention.forward(q, k, v, cu_seqlens, max_seqlen, scale, out=out, lse=lse)
 
 
 def attention_varlen_bwd(q, k, v, out, lse, dout, cu_seqlens, max_seqlen, scale=None):

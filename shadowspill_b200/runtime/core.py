@@ -162,6 +162,16 @@ class Runtime:
         return [{"kind": native.TRACE_KINDS[buf[i].kind], "id": buf[i].a,
                  "host_ns": buf[i].host_ns, "bytes": buf[i].bytes} for i in range(n)]
 
+    def transfer_times(self, plan_id: int, n_actions: int) -> tuple[list[int], list[int]]:
+        """Device-clock ``(begin_ns, end_ns)`` of each action's copy in the plan's last
+        step, relative to the step's start; -1 for releases. Needs ``trace_capacity > 0``."""
+        b = (native.i64 * max(n_actions, 1))()
+        e = (native.i64 * max(n_actions, 1))()
+        n = self.lib.ss_plan_transfer_times(self.handle, plan_id, b, e, n_actions)
+        if n < 0:
+            return [], []
+        return list(b[:n_actions]), list(e[:n_actions])
+
     def calibrate(self, nbytes: int = 256 << 20, repeats: int = 3) -> TransferRates:
         p = native.TransferProfile()
         native.check(self.lib.ss_calibrate_transfers(self.handle, int(nbytes), repeats, C.byref(p)),

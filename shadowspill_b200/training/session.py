@@ -58,6 +58,9 @@ class TrainingSetup:
     walks: tuple[str, ...] = ("breadth",)
     recompute_shares: tuple[int, ...] = (100,)
     saved_variant: str = "save_attention"
+    # explicit "<recompute share>:<saved variant>" candidates (e.g. "50:save"); when given
+    # they replace the recompute_shares x saved_variant grid
+    candidate_selections: tuple[str, ...] = ()
     profile: bool = True
     calibrate: bool = True
     search: SearchOptions = field(default_factory=SearchOptions)
@@ -85,7 +88,15 @@ class TrainingSession:
         self.budgets = MemoryBudgets.from_gib(setup.device_gib, setup.spill_gib)
         self.timings: dict[str, float] = {}
         world, rank = setup.world_size, setup.rank
-        selections = recompute_share_selections(self.cfg, setup.recompute_shares, setup.saved_variant)
+        if setup.candidate_selections:
+            selections = []
+            for item in setup.candidate_selections:
+                share, _, variant = item.partition(":")
+                selections += recompute_share_selections(self.cfg, (int(share),),
+                                                         variant or setup.saved_variant)
+        else:
+            selections = recompute_share_selections(self.cfg, setup.recompute_shares,
+                                                    setup.saved_variant)
         variants = [(walk, sel) for walk in setup.walks for sel in selections]
 
         def build(index: int):
@@ -212,6 +223,20 @@ class TrainingSession:
     def write_plan_report(self, directory: str) -> None:
         from ..reporting.write import write_report
         write_report(self.plan, directory)
+
+    def traced_step(self, batch: list[HostMicrobatch], directory: str | None = None):
+        """Runs one real training step with per-task device timing and the runtime trace
+        on, and returns ``(result, StepDiagnostics)``; with ``directory`` also writes the
+        runtime report there. Needs ``TrainingSetup.trace_capacity > 0``."""
+        from ..diagnostics.step import diagnose_step
+        if self.setup.trace_capacity <= 0:
+            raise ValueError("traced_step needs TrainingSetup.trace_capacity > 0")
+        result = self.executor.run(batch, trace=True, time_tasks=True)
+        diag = diagnose_step(self.plan, result, runtime_stats=self.executor.rt.stats())
+        if directory:
+            from ..reporting.runtime import write_runtime_report
+            write_runtime_report(self.plan, diag, directory)
+        return result, diag
 
     def close(self) -> None:
         self.executor.close()

@@ -127,3 +127,33 @@ def test_operations_share_state_across_plans():
         # microbatches accumulate in another order (reverse walk), hence a few fp32 ulps
         assert torch.allclose(got[k], v, rtol=1e-4, atol=2e-5), (k, float((got[k] - v).abs().max()))
     ex.close()
+
+
+def test_traced_step_diagnostics_and_runtime_report(tmp_path):
+    from shadowspill_b200.diagnostics.step import diagnose_step
+    from shadowspill_b200.reporting.runtime import write_runtime_report
+    cfg, plan, desc = _setup("breadth")
+    ex = Executor(plan, desc, device="cpu", seed=5, hyper=Hyperparameters(lr=1e-3),
+                  trace_capacity=1 << 14)
+    ex.initialize()
+    ex.run(_batches(cfg, 0))
+    res = ex.run(_batches(cfg, 1), trace=True, time_tasks=True)
+    n_moves = sum(a.kind != "release" for a in plan.schedule.actions)
+    assert len(res.task_seconds) == len(plan.program.tasks)
+    assert len(res.transfer_begin_ns) == len(plan.schedule.actions)
+    diag = diagnose_step(plan, res, runtime_stats=ex.rt.stats())
+    assert diag.trace_complete
+    assert len(diag.tasks) == len(plan.program.tasks)
+    assert len(diag.transfers) == n_moves          # every planned copy was seen issued
+    assert all(t.real_s >= 0 for t in diag.transfers)
+    assert diag.task_seconds_real > 0 and diag.makespan_s > 0
+    total_idle = (diag.input_readiness_wait_seconds + diag.allocation_reuse_wait_seconds
+                  + diag.frontend_overhead_seconds)
+    assert abs(total_idle - diag.idle_seconds_real) < 1e-9
+    assert set(diag.phases) >= {"forward", "backward", "optimizer"}
+    page = write_runtime_report(plan, diag, tmp_path)
+    text = page.read_text()
+    assert "Runtime report" in text and "exposed frontend overhead" in text
+    assert (tmp_path / "runtime_tasks.csv").read_text().count("\n") == len(plan.program.tasks) + 1
+    assert (tmp_path / "runtime.json").exists() and (tmp_path / "runtime_transfers.csv").exists()
+    ex.close()
