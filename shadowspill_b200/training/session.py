@@ -63,6 +63,8 @@ class TrainingSetup:
     candidate_selections: tuple[str, ...] = ()
     profile: bool = True
     calibrate: bool = True
+    # scale burst-measured task profiles to sustained clocks with both lanes streaming
+    calibrate_overlap: bool = True
     search: SearchOptions = field(default_factory=SearchOptions)
     trace_capacity: int = 0
     collectives: str = "auto"             # peer | dist | auto
@@ -128,6 +130,14 @@ class TrainingSession:
             self.timings["build"] = time.perf_counter() - t0
             # ---- profile distinct tasks once
             t0 = time.perf_counter()
+            scale = 1.0
+            if setup.profile and setup.calibrate_overlap and cuda:
+                from ..communication.measure import measure_overlap
+                ov = measure_overlap(setup.device_index)
+                scale = min(1.3, max(1.0, ov.duration_scale))
+                self.overlap = ov
+                self.log(f"overlap: burst {ov.burst_tflops:.0f}, sustained {ov.sustained_tflops:.0f}, "
+                         f"streaming {ov.streaming_tflops:.0f} TFLOP/s -> task times x{scale:.3f}")
             if setup.profile:
                 dev = f"cuda:{setup.device_index}" if cuda else "cpu"
                 for prog, desc in candidates + list(extras.values()):
@@ -136,7 +146,7 @@ class TrainingSession:
                         got = measure_program(prog, desc, dev, keys=missing)
                         self.profiles.tasks.update(got.tasks)
                         self.profiles.device = got.device
-                    apply_profiles(prog, self.profiles)
+                    apply_profiles(prog, self.profiles, duration_scale=scale)
                 if cuda:
                     torch.cuda.empty_cache()
             self.timings["profile"] = time.perf_counter() - t0
