@@ -48,12 +48,18 @@ struct GemmCfg {
 //           (forward and data-gradient of an expert bank).
 //   mode 2  one output matrix per expert, contracted over that expert's padded row
 //           segment [expert_offset[e], expert_offset[e+1]) (weight gradient of a bank).
+// With row_dst (mode 1, bf16 output) the epilogue writes output row r to the address
+// row_dst[r] instead of C + r*ldc; 0 drops the row. Addresses may point into another
+// GPU's memory (plain peer stores), which is how an expert bank's output rows go
+// straight back to the ranks that own their tokens: the combine transfer of expert
+// parallelism rides in this kernel's epilogue, overlapped with the next tile's MMAs.
 struct GroupInfo {
   int mode;
   const int* tile_expert;     // mode 1: [ceil(M/128)], -1 = tile past the used rows
   const int* expert_offset;   // mode 2: [E+1], multiples of 128
   int n_experts;
   long long c_expert_stride;  // mode 2: elements between experts' outputs
+  const long long* row_dst;   // mode 1, optional: per-row destination addresses (bytes)
 };
 
 struct GemmParams {
@@ -294,6 +300,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           } else {
             __nv_bfloat16* dst =
                 reinterpret_cast<__nv_bfloat16*>(p.C) + w.c_off + static_cast<long long>(row) * p.ldc + col0;
+            if (p.g.row_dst != nullptr) {
+              const long long where = p.g.row_dst[row];
+              if (where == 0) continue;
+              dst = reinterpret_cast<__nv_bfloat16*>(where) + col0;
+            }
             for (int j = 0; j < ncols; j += 8) {
               float f[8];
 #pragma unroll
@@ -501,6 +512,29 @@ int ss_gemm_grouped_bf16(const void* A, const void* B, void* C, int mode, int ro
   p.C = C; p.ldc = ldc; p.c_f32 = c_f32; p.accumulate = accumulate; p.status = status; p.alpha = 1.f;
   p.g.mode = mode; p.g.tile_expert = tile_expert; p.g.expert_offset = expert_offset;
   p.g.n_experts = n_experts;
+  return dispatch(ta, tb, p, bn, sm_count(), reinterpret_cast<cudaStream_t>(stream));
+}
+
+// Row-grouped expert GEMM whose output rows are scattered: row r of A x B[expert]^T
+// (bf16) is written to the byte address row_dst[r] (16-byte aligned; 0 = dropped),
+// which may lie in a peer GPU's mapped memory.
+int ss_gemm_grouped_scatter_bf16(const void* A, const void* B, const long long* row_dst, int rows,
+                                 int N, int K, int n_experts, long long lda, long long ldb, int b_mn,
+                                 const int* tile_expert, int bn, int* status, void* stream) {
+  using namespace ss;
+  if (rows <= 0 || n_experts <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (N % 8) || (rows % BM) || !tile_expert || !row_dst) return -2;
+  if (bn != 128 && bn != 256) bn = (N <= 128) ? 128 : 256;
+  CUtensorMap ta, tb;
+  GemmParams p{};
+  int r;
+  if ((r = make_tmap_bf16(&ta, A, rows, K, lda, BM))) return r;
+  if (!b_mn) r = make_tmap3_bf16(&tb, B, n_experts, N, K, ldb, static_cast<long long>(N) * ldb, bn);
+  else       r = make_tmap3_bf16(&tb, B, n_experts, K, N, ldb, static_cast<long long>(K) * ldb, BK);
+  if (r) return r;
+  p.M = rows; p.N = N; p.K = K; p.a_mn = 0; p.b_mn = b_mn;
+  p.C = nullptr; p.ldc = 0; p.c_f32 = 0; p.accumulate = 0; p.status = status; p.alpha = 1.f;
+  p.g.mode = 1; p.g.tile_expert = tile_expert; p.g.n_experts = n_experts; p.g.row_dst = row_dst;
   return dispatch(ta, tb, p, bn, sm_count(), reinterpret_cast<cudaStream_t>(stream));
 }
 
