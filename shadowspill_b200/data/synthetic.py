@@ -12,7 +12,7 @@ reference's ``text_batch`` convention, packages/client/src/shadowspill_client/te
 from __future__ import annotations
 
 import math
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 
 import numpy as np
 
@@ -26,11 +26,13 @@ class HostMicrobatch:
     positions: np.ndarray    # int32 [T]
     cu_seqlens: np.ndarray   # int32 [slots+1]
     max_seqlen: int
+    extras: dict = field(default_factory=dict)   # objective inputs: float32 [T] each
 
     @property
     def nbytes(self) -> int:
         return (self.tokens.nbytes + self.targets.nbytes + self.weights.nbytes
-                + self.positions.nbytes + self.cu_seqlens.nbytes)
+                + self.positions.nbytes + self.cu_seqlens.nbytes
+                + sum(v.nbytes for v in self.extras.values()))
 
 
 def sample_lengths(rng: np.random.Generator, total_tokens: int, *, median: float = 1200.0,
@@ -124,4 +126,4 @@ def to_device(mb: HostMicrobatch, device):
     from ..models.decoder import BatchMeta
     t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)
     return BatchMeta(t(mb.tokens), t(mb.targets), t(mb.weights), t(mb.positions),
-                     t(mb.cu_seqlens), mb.max_seqlen)
+                     t(mb.cu_seqlens), mb.max_seqlen, {k: t(v) for k, v in mb.extras.items()})

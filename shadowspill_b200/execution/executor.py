@@ -67,10 +67,11 @@ class TaskRunner:
         self.collectives = collectives
         self.world = desc.world_size
         self.sr = stochastic_rounding and desc.dtype == torch.bfloat16
-        self.stages = build_stages(desc.cfg)
+        self.stages = desc.stages()
         meta = program.metadata
         self.T, self.n_mb, self.slots = meta["microbatch_tokens"], meta["n_microbatches"], meta["slots"]
-        self.batch_layout_, _ = batch_layout(self.T, self.slots)
+        self.extra_fields = tuple(desc.geometry.extra_fields)
+        self.batch_layout_, _ = batch_layout(self.T, self.slots, self.extra_fields)
         self.max_seqlen = [2] * self.n_mb
         self.uses = [program.sorted_uses(t) for t in range(len(program.tasks))]
         self.completed_updates = 0
@@ -88,7 +89,8 @@ class TaskRunner:
             tdt = _TORCH_DT[dt]
             parts[name] = flat[off:off + count * tdt.itemsize].view(tdt)
         return BatchMeta(parts["tokens"], parts["targets"], parts["weights"], parts["positions"],
-                         parts["cu_seqlens"], self.max_seqlen[m])
+                         parts["cu_seqlens"], self.max_seqlen[m],
+                         {n: parts[n] for n in self.extra_fields})
 
     def bind(self, task: int, flats: list[torch.Tensor]) -> dict[str, object]:
         """Role -> tensor views for one task over the flat byte tensors of its uses
@@ -99,12 +101,13 @@ class TaskRunner:
         for u, flat in zip(self.uses[task], flats):
             obj = self.program.objects[u.object]
             if u.role in ("params", "m", "v", "shard"):
+                only = u.role in ("m", "v")       # moments exist for trainable parameters only
                 if obj.sharding == "sharded":
-                    out[u.role] = st.shard_views(flat, self.desc.dtype, self.world)
+                    out[u.role] = st.shard_views(flat, self.desc.dtype, self.world, only)
                 else:
-                    out[u.role] = st.views(flat, self.desc.dtype)
+                    out[u.role] = st.views(flat, self.desc.dtype, trainable_only=only)
             elif u.role == "grads":
-                out[u.role] = st.views(flat, self.desc.grad_dtype, torch.float32)
+                out[u.role] = st.views(flat, self.desc.grad_dtype, torch.float32, True)
             elif u.role in ("x", "y", "dx"):
                 out[u.role] = flat.view(self.desc.dtype).view(self.T, self.desc.cfg.d_model)
             elif u.role == "batch":
@@ -147,7 +150,7 @@ class TaskRunner:
             saved = dict(B["saved"]) if "saved" in B else {}
             if "attn" in saved:
                 saved["attn"] = saved["attn"]
-            st.backward(B.get("params"), B["grads"], B.get("x"), B["dx"], meta, saved, first)
+            st.backward(B.get("params"), B.get("grads") or {}, B.get("x"), B["dx"], meta, saved, first)
         elif t.kind == "optimizer":
             if t.variant == "adamw_dp":
                 self._optimizer_sharded(t.stage, B)
@@ -355,12 +358,14 @@ class Executor:
                 if name not in self._obj:
                     continue
                 flat = self.spill_view(self._obj[name])
+                only = kind != "weights"      # moments exist for trainable parameters only
                 if self.world > 1:
-                    views = st.shard_views(flat, self.desc.dtype, self.world)
+                    views = st.shard_views(flat, self.desc.dtype, self.world, only)
                 else:
-                    views = st.views(flat, self.desc.dtype)
+                    views = st.views(flat, self.desc.dtype, trainable_only=only)
                 for p in st.params:
-                    yield f"{prefix}{st.name}.{p.name}", views[p.name]
+                    if p.name in views:
+                        yield f"{prefix}{st.name}.{p.name}", views[p.name]
 
     def state_dict(self) -> dict[str, torch.Tensor]:
         return {k: v.clone() for k, v in self.named_tensors()}
@@ -390,7 +395,7 @@ class Executor:
                 raise ValueError(f"microbatch {m}: too many sequences for {self.slots} slots")
             dst = self.spill_view(self._obj[f"batch.{m}"]).numpy()
             for name, (off, count, dt) in self._batch_layout.items():
-                src = getattr(mb, name)
+                src = getattr(mb, name) if hasattr(mb, name) else mb.extras[name]
                 view = dst[off:off + count * np.dtype(dt).itemsize].view(dt)
                 if name == "cu_seqlens":
                     view[:src.shape[0]] = src
@@ -403,8 +408,13 @@ class Executor:
 
     # ------------------------------------------------------------------ views
     def _device_view(self, ptr: int, nbytes: int) -> torch.Tensor:
+        # An alias with its own autograd version counter (not a view of the pool tensor):
+        # in-place writes to one object must not invalidate tensors autograd saved from
+        # another object that merely lives in the same pool.
         off = ptr - self.rt.device_base
-        return self.rt.device[off:off + nbytes]
+        pool = self.rt.device
+        return torch.empty(0, dtype=torch.uint8, device=pool.device).set_(
+            pool.untyped_storage(), pool.storage_offset() + off, (nbytes,))
 
     def _bind(self, task: int, ptrs: list[int]) -> dict[str, object]:
         """Views for one task, cached: the plan fixes every offset."""
@@ -499,11 +509,18 @@ class Executor:
             self.runner.accumulated = 0
         elif self.desc.mode == "forward_backward":
             self.runner.accumulated += 1
+        metrics = {}
+        aux = [st.aux_sum for st in self.stages if getattr(st, "aux_sum", None) is not None]
+        if aux:
+            metrics["moe_balance"] = float(sum(float(a.item()) for a in aux))
+            for a in aux:
+                a.zero_()
         tr = self.rt.trace_end() if trace else []
         tb, te = (self.rt.transfer_times(self.plan_id, len(self.plan.schedule.actions))
                   if trace else ([], []))
         return InvocationResult(loss, self.T * self.n_mb, time.perf_counter() - t0, device_seconds,
-                                h2d, 4, task_seconds if time_tasks else [], task_starts, tr, tb, te)
+                                h2d, 4, task_seconds if time_tasks else [], task_starts, tr, tb, te,
+                                metrics)
 
     def discard_gradients(self) -> None:
         self.runner.accumulated = 0

@@ -20,7 +20,7 @@ class ResidentTrainer:
                  dtype: torch.dtype = torch.bfloat16, seed: int = 0,
                  grad_dtype: torch.dtype | None = None, lr: float = 1e-3, beta1: float = 0.9,
                  beta2: float = 0.95, eps: float = 1e-8, weight_decay: float = 0.0,
-                 stochastic_rounding: bool = True):
+                 stochastic_rounding: bool = True, objective=None, lora=None):
         self.cfg = cfg
         self.device = torch.device(device)
         self.dtype = dtype
@@ -28,25 +28,26 @@ class ResidentTrainer:
         self.hyper = dict(lr=lr, beta1=beta1, beta2=beta2, eps=eps, weight_decay=weight_decay)
         self.sr = stochastic_rounding and dtype == torch.bfloat16
         self.seed = seed
-        self.stages = build_stages(cfg)
+        self.stages = build_stages(cfg, objective, lora)
         self.step_count = 0
         self.P, self.G, self.M, self.V = [], [], [], []
         self._flat = []
         gen = torch.Generator().manual_seed(seed)
         for st in self.stages:
             _, pbytes = st.layout(dtype)
-            _, gbytes = st.layout(self.grad_dtype, torch.float32)
+            _, gbytes = st.layout(self.grad_dtype, torch.float32, trainable_only=True)
+            _, obytes = st.layout(dtype, trainable_only=True)
             host = torch.zeros(pbytes, dtype=torch.uint8)
             st.init_(st.views(host, dtype), gen)
             pf = host.to(self.device)
             gf = torch.zeros(gbytes, dtype=torch.uint8, device=self.device)
-            mf = torch.zeros(pbytes, dtype=torch.uint8, device=self.device)
-            vf = torch.zeros(pbytes, dtype=torch.uint8, device=self.device)
+            mf = torch.zeros(obytes, dtype=torch.uint8, device=self.device)
+            vf = torch.zeros(obytes, dtype=torch.uint8, device=self.device)
             self._flat.append((pf, gf, mf, vf))
             self.P.append(st.views(pf, dtype))
-            self.G.append(st.views(gf, self.grad_dtype, torch.float32))
-            self.M.append(st.views(mf, dtype))
-            self.V.append(st.views(vf, dtype))
+            self.G.append(st.views(gf, self.grad_dtype, torch.float32, True))
+            self.M.append(st.views(mf, dtype, trainable_only=True))
+            self.V.append(st.views(vf, dtype, trainable_only=True))
         self.loss_sum = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._accum = 0
 
@@ -68,6 +69,8 @@ class ResidentTrainer:
             return
         for i in range(len(body) - 1, -1, -1):
             st = body[i]
+            if i == 0 and not st.has_trainable:
+                break
             dx = st.backward(self.P[i], self.G[i], xs[i], dx, meta, {}, first)
         self._accum += 1
 
@@ -76,6 +79,9 @@ class ResidentTrainer:
         offset = 0
         for si, st in enumerate(self.stages):
             for p in st.params:
+                if not p.trainable:
+                    offset += (p.numel + 7) // 8 * 8
+                    continue
                 pt, gt = self.P[si][p.name], self.G[si][p.name]
                 F.adamw_(pt.view(-1), gt.view(-1), self.M[si][p.name].view(-1),
                          self.V[si][p.name].view(-1), step=self.step_count,

@@ -46,18 +46,21 @@ class BatchGeometry:
     n_microbatches: int
     slots: int = 64                  # sequence slots per microbatch (cu_seqlens has slots+1)
     mean_seqlen: float = 2048.0
+    extra_fields: tuple[str, ...] = ()   # per-token fp32 fields an objective reads
 
     @property
     def tokens(self) -> int:
         return self.microbatch_tokens * self.n_microbatches
 
 
-def batch_layout(T: int, slots: int) -> tuple[dict[str, tuple[int, int, str]], int]:
+def batch_layout(T: int, slots: int, extras: tuple[str, ...] = ()
+                 ) -> tuple[dict[str, tuple[int, int, str]], int]:
     """Byte layout of one packed microbatch object: name -> (offset, count, dtype)."""
     out, off = {}, 0
-    for name, count, dt, size in (("tokens", T, "int64", 8), ("targets", T, "int64", 8),
-                                  ("weights", T, "float32", 4), ("positions", T, "int32", 4),
-                                  ("cu_seqlens", slots + 1, "int32", 4)):
+    fields = [("tokens", T, "int64", 8), ("targets", T, "int64", 8), ("weights", T, "float32", 4),
+              ("positions", T, "int32", 4), ("cu_seqlens", slots + 1, "int32", 4)]
+    fields += [(name, T, "float32", 4) for name in extras]
+    for name, count, dt, size in fields:
         out[name] = (off, count, dt)
         off = (off + count * size + ALIGN - 1) // ALIGN * ALIGN
     return out, off
@@ -89,6 +92,17 @@ class TrainingDescription:
     mode: str = "step"                # step | forward_backward | forward
     world_size: int = 1               # data-parallel ranks with sharded weights/optimizer state
     rank: int = 0
+    objective: "Objective | None" = None
+    lora: "LoRAConfig | None" = None
+
+    def __post_init__(self) -> None:
+        extras = self.objective.extra_fields if self.objective is not None else ()
+        if tuple(self.geometry.extra_fields) != tuple(extras):
+            from dataclasses import replace as _replace
+            self.geometry = _replace(self.geometry, extra_fields=tuple(extras))
+
+    def stages(self):
+        return build_stages(self.cfg, self.objective, self.lora)
 
     def variant(self, stage_index: int) -> str:
         return self.selection.get(stage_index, "recompute")
@@ -101,7 +115,7 @@ def estimate_duration_ns(flops: float, nbytes: float, tflops: float = 1100.0,
 
 def _build(desc: TrainingDescription) -> Program:
     cfg, geo, order = desc.cfg, desc.geometry, desc.ordering
-    stages = build_stages(cfg)
+    stages = desc.stages()
     S, n_mb, T = len(stages), geo.n_microbatches, geo.microbatch_tokens
     train = desc.mode != "forward"
     step = desc.mode in ("step", "optimizer")
@@ -113,7 +127,9 @@ def _build(desc: TrainingDescription) -> Program:
                              "grad_dtype": _DT[desc.grad_dtype],
                              "selection": ",".join(f"{k}:{v}" for k, v in sorted(desc.selection.items()))
                              or "recompute",
-                             "walk": order.walk, "optimizer_order": order.optimizer})
+                             "walk": order.walk, "optimizer_order": order.optimizer,
+                             "objective": desc.objective.to_json() if desc.objective else None,
+                             "lora": desc.lora.to_json() if desc.lora else None})
     W, M, V, G = [], [], [], []
     world = desc.world_size
     sharded = world > 1
@@ -125,22 +141,31 @@ def _build(desc: TrainingDescription) -> Program:
         full_bytes.append(pbytes)
         if sharded:
             _, pbytes = st.shard_layout(desc.dtype, world)
-        _, gbytes = st.layout(desc.grad_dtype, torch.float32)
+        _, gbytes = st.layout(desc.grad_dtype, torch.float32, trainable_only=True)
+        if sharded:
+            _, sbytes_opt = st.shard_layout(desc.dtype, world, trainable_only=True)
+        else:
+            _, sbytes_opt = st.layout(desc.dtype, trainable_only=True)
         W.append(prog.add_object(ObjectSpec(f"{st.name}.weights", pbytes, "weight", True, stage=si,
                                             sharding="sharded" if sharded else "whole")))
+        if not st.has_trainable:          # a frozen stage owns no gradients and no moments
+            G.append(-1); M.append(-1); V.append(-1)
+            continue
         if train:
             # gradients persist across calls when accumulation is driven from outside
             G.append(prog.add_object(ObjectSpec(f"{st.name}.gradients", gbytes, "gradient",
                                                 persistent=desc.mode != "step", stage=si)))
         if step:
             sh = "sharded" if sharded else "whole"
-            M.append(prog.add_object(ObjectSpec(f"{st.name}.exp_avg", pbytes, "optimizer_state", True, stage=si, sharding=sh)))
-            V.append(prog.add_object(ObjectSpec(f"{st.name}.exp_avg_sq", pbytes, "optimizer_state", True, stage=si, sharding=sh)))
+            M.append(prog.add_object(ObjectSpec(f"{st.name}.exp_avg", sbytes_opt, "optimizer_state", True, stage=si, sharding=sh)))
+            V.append(prog.add_object(ObjectSpec(f"{st.name}.exp_avg_sq", sbytes_opt, "optimizer_state", True, stage=si, sharding=sh)))
     if only_optimizer:
         # the update alone: gradients accumulated by earlier forward_backward calls are state
         prog.metadata["n_microbatches"] = 0
         for si in reversed(range(S)):
             st = stages[si]
+            if not st.has_trainable:
+                continue
             pbytes = prog.objects[W[si]].bytes
             prog.add_task(TaskSpec(f"O.{st.name}", "optimizer", si, -1,
                                    [UseSpec(W[si], "mutate", "params"), UseSpec(G[si], "read", "grads"),
@@ -150,7 +175,7 @@ def _build(desc: TrainingDescription) -> Program:
                                    profile_key=f"opt:{pbytes}:{world}"))
         prog.validate()
         return prog
-    _, in_bytes = batch_layout(T, geo.slots)
+    _, in_bytes = batch_layout(T, geo.slots, geo.extra_fields)
     IN = [prog.add_object(ObjectSpec(f"batch.{m}", in_bytes, "input", True, pinned_resident=True,
                                      microbatch=m)) for m in range(n_mb)]
     LOSS = prog.add_object(ObjectSpec("loss", 512, "output", True, pinned_resident=True))
@@ -170,8 +195,14 @@ def _build(desc: TrainingDescription) -> Program:
                                                             "saved", stage=si, microbatch=m))
     grad_created = [False] * S
 
+    tag = ""
+    if desc.lora is not None:
+        tag += f":lora{desc.lora.rank}{'b' if desc.lora.train_base else ''}"
+    if desc.objective is not None and desc.objective.kind != "cross_entropy":
+        tag += f":{desc.objective.kind}"
+
     def key(st: Stage, what: str, var: str = "") -> str:
-        return f"{cfg.family}:{st.kind}:{type(st).__name__}:{what}:{var}:T{T}"
+        return f"{cfg.family}:{st.kind}:{type(st).__name__}:{what}:{var}:T{T}{tag}"
 
     def params_of(si: int, which: str) -> int:
         """The object a compute task reads its weights from; under sharded storage
@@ -212,7 +243,9 @@ def _build(desc: TrainingDescription) -> Program:
                 UseSpec(A[si - 1][m], "read", "x"), UseSpec(LOSS, "mutate", "loss")]
         if train:
             uses.append(UseSpec(DX[m], "create", "dx"))
-            if desc.mode == "step" and not grad_created[si]:
+            if not st.has_trainable:
+                pass
+            elif desc.mode == "step" and not grad_created[si]:
                 uses.append(UseSpec(G[si], "create", "grads")); grad_created[si] = True
             else:
                 uses.append(UseSpec(G[si], "mutate", "grads"))
@@ -224,6 +257,8 @@ def _build(desc: TrainingDescription) -> Program:
 
     def bwd(si: int, m: int) -> None:
         st = stages[si]
+        if not st.has_trainable and si == 0:
+            return                      # a frozen embedding has nothing to compute backward
         var = desc.variant(si)
         uses = [UseSpec(IN[m], "read", "batch"),
                 UseSpec(DX[m], "mutate" if si > 0 else "read", "dx")]
@@ -233,7 +268,9 @@ def _build(desc: TrainingDescription) -> Program:
             uses.append(UseSpec(A[si - 1][m], "read", "x"))
         if (si, m) in SAVED:
             uses.append(UseSpec(SAVED[(si, m)], "read", "saved"))
-        if desc.mode == "step" and not grad_created[si]:
+        if not st.has_trainable:
+            pass
+        elif desc.mode == "step" and not grad_created[si]:
             uses.append(UseSpec(G[si], "create", "grads")); grad_created[si] = True
         else:
             uses.append(UseSpec(G[si], "mutate", "grads"))
@@ -245,6 +282,8 @@ def _build(desc: TrainingDescription) -> Program:
 
     def opt(si: int) -> None:
         st = stages[si]
+        if not st.has_trainable:
+            return
         pbytes = prog.objects[W[si]].bytes
         prog.add_task(TaskSpec(f"O.{st.name}", "optimizer", si, -1,
                                [UseSpec(W[si], "mutate", "params"), UseSpec(G[si], "read", "grads"),
@@ -294,37 +333,39 @@ def _build(desc: TrainingDescription) -> Program:
 def build_step(cfg: DecoderConfig, geometry: BatchGeometry,
                ordering: StepDataOrdering | None = None, *, dtype=torch.bfloat16,
                grad_dtype=None, selection: dict[int, str] | None = None, world_size: int = 1,
-               rank: int = 0):
+               rank: int = 0, objective=None, lora=None):
     """Forward + backward + optimizer of one global batch. Returns ``(Program, description)``.
     ``world_size > 1`` builds the data-parallel form: weights and AdamW moments are
     stored as 1/N shards, gathered before use and updated shard-locally."""
     desc = TrainingDescription(cfg, geometry, ordering or StepDataOrdering(), dtype,
                                grad_dtype or dtype, dict(selection or {}), "step", world_size,
-                               rank)
+                               rank, objective, lora)
     return _build(desc), desc
 
 
 def build_forward_backward(cfg, geometry, ordering=None, *, dtype=torch.bfloat16, grad_dtype=None,
-                           selection=None, world_size=1, rank=0):
+                           selection=None, world_size=1, rank=0, objective=None, lora=None):
     """Gradient accumulation without the update (gradients are persistent state)."""
     desc = TrainingDescription(cfg, geometry, ordering or StepDataOrdering(), dtype,
                                grad_dtype or dtype, dict(selection or {}), "forward_backward",
-                               world_size, rank)
+                               world_size, rank, objective, lora)
     return _build(desc), desc
 
 
-def build_forward(cfg, geometry, ordering=None, *, dtype=torch.bfloat16, world_size=1, rank=0):
+def build_forward(cfg, geometry, ordering=None, *, dtype=torch.bfloat16, world_size=1, rank=0,
+                  objective=None, lora=None):
     """Evaluation: forward passes and the loss only."""
     desc = TrainingDescription(cfg, geometry, ordering or StepDataOrdering(), dtype, dtype, {},
-                               "forward", world_size, rank)
+                               "forward", world_size, rank, objective, lora)
     return _build(desc), desc
 
 
-def build_optimizer(cfg, geometry, *, dtype=torch.bfloat16, grad_dtype=None, world_size=1, rank=0):
+def build_optimizer(cfg, geometry, *, dtype=torch.bfloat16, grad_dtype=None, world_size=1, rank=0,
+                    objective=None, lora=None):
     """The optimizer update alone, over gradients that earlier ``forward_backward``
     invocations left in the spill pool (the ``optim_step`` operation)."""
     desc = TrainingDescription(cfg, geometry, StepDataOrdering(), dtype, grad_dtype or dtype, {},
-                               "optimizer", world_size, rank)
+                               "optimizer", world_size, rank, objective, lora)
     return _build(desc), desc
 
 

@@ -29,7 +29,13 @@ class GradSink:
         self.written.add(name)
         return acc
 
+    def wants(self, name: str) -> bool:
+        """False for frozen parameters: their gradient buffer does not exist."""
+        return self.G is not None and name in self.G
+
     def add_vector(self, name: str, g: torch.Tensor) -> None:
+        if not self.wants(name):
+            return
         dst = self.G[name]
         if self.accumulate(name):
             dst.add_(g.to(dst.dtype).reshape(dst.shape))
@@ -49,7 +55,7 @@ class _Linear(torch.autograd.Function):
         x, w = ctx.saved_tensors
         dy = dy.contiguous()
         sink = ctx.sink
-        if sink is not None and sink.G is not None:
+        if sink is not None and sink.wants(ctx.name):
             dst = sink.G[ctx.name]
             key = ctx.name
             if ctx.index is not None:
@@ -146,3 +152,75 @@ class _SwiGLU(torch.autograd.Function):
 def swiglu(gu):
     """``silu(gate) * up`` for ``gu = [gate | up]`` along the last dimension."""
     return _SwiGLU.apply(gu)
+
+
+def lora_linear(x, w, a, b, scale: float, sink: GradSink | None, name: str):
+    """``x w^T + scale * (x a^T) b^T`` with factor gradients under ``<name>_lora_a/_b``;
+    the base gradient is skipped when ``sink`` has no buffer for ``name`` (frozen base)."""
+    y = linear(x, w, sink, name)
+    low = linear(linear(x, a, sink, f"{name}_lora_a"), b, sink, f"{name}_lora_b")
+    return y + low * scale
+
+
+# ---------------------------------------------------------------------------- grouped (expert) ops
+class _GroupedLinear(torch.autograd.Function):
+    """Rows sorted by expert times that expert's matrix, differentiable on both sides."""
+
+    @staticmethod
+    def forward(ctx, xs, bank, lay, sink, name):
+        from ..ops import moe as moe_ops
+        ctx.save_for_backward(xs, bank)
+        ctx.lay, ctx.sink, ctx.name = lay, sink, name
+        return moe_ops.grouped_linear(xs, bank, lay)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops import moe as moe_ops
+        xs, bank = ctx.saved_tensors
+        dy = dy.contiguous()
+        sink = ctx.sink
+        if sink is not None and sink.wants(ctx.name):
+            moe_ops.grouped_wgrad(dy, xs, ctx.lay, sink.G[ctx.name], sink.accumulate(ctx.name))
+        dx = moe_ops.grouped_linear(dy, bank, ctx.lay, transpose=True) if ctx.needs_input_grad[0] else None
+        return dx, None, None, None, None
+
+
+def grouped_linear(xs, bank, lay, sink, name):
+    return _GroupedLinear.apply(xs, bank, lay, sink, name)
+
+
+class _Gather(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, lay):
+        ctx.lay = lay
+        return lay.gather(x)
+
+    @staticmethod
+    def backward(ctx, dxs):
+        return ctx.lay.combine(dxs.contiguous(), None), None
+
+
+class _Combine(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ys, wts, lay):
+        ctx.save_for_backward(ys, wts)
+        ctx.lay = lay
+        return lay.combine(ys, wts)
+
+    @staticmethod
+    def backward(ctx, dout):
+        ys, wts = ctx.saved_tensors
+        dout = dout.contiguous()
+        _, dwts = ctx.lay.combine(ys, None, dots_with=dout, only_dots=True)
+        return ctx.lay.gather(dout, wts), dwts, None
+
+
+def expert_gather(x, lay):
+    """Token rows -> expert-sorted padded rows."""
+    return _Gather.apply(x, lay)
+
+
+def expert_combine(ys, wts, lay):
+    """Expert-sorted rows -> token rows, weighted by the routing weights (differentiable
+    in both)."""
+    return _Combine.apply(ys, wts, lay)

@@ -50,6 +50,7 @@ class BatchMeta:
     positions: torch.Tensor     # int32 [T]
     cu_seqlens: torch.Tensor    # int32 [S+1]
     max_seqlen: int
+    extras: dict = field(default_factory=dict)   # objective inputs: fp32 [T] each
 
     @property
     def T(self) -> int:
@@ -73,20 +74,30 @@ class Stage:
     def parameter_count(self) -> int:
         return sum(p.numel for p in self.params)
 
-    def layout(self, dtype: torch.dtype, vector_dtype: torch.dtype | None = None):
+    @property
+    def has_trainable(self) -> bool:
+        return any(p.trainable for p in self.params)
+
+    def layout(self, dtype: torch.dtype, vector_dtype: torch.dtype | None = None,
+               trainable_only: bool = False):
         """[(spec, byte offset, dtype)], total bytes. ``vector_dtype`` overrides
-        the dtype of 1-D parameters (gradient buffers keep those in fp32)."""
+        the dtype of 1-D parameters (gradient buffers keep those in fp32);
+        ``trainable_only`` lays out gradient and optimizer-state buffers, which hold
+        nothing for frozen parameters."""
         out, off = [], 0
         for p in self.params:
+            if trainable_only and not p.trainable:
+                continue
             dt = p.dtype or (vector_dtype if (vector_dtype and len(p.shape) == 1) else dtype)
             out.append((p, off, dt))
             off = _round_up(off + p.numel * dt.itemsize, ALIGN)
         return out, off
 
     def views(self, flat: torch.Tensor, dtype: torch.dtype,
-              vector_dtype: torch.dtype | None = None) -> dict[str, torch.Tensor]:
+              vector_dtype: torch.dtype | None = None,
+              trainable_only: bool = False) -> dict[str, torch.Tensor]:
         """Named tensor views over a flat uint8 buffer."""
-        lay, total = self.layout(dtype, vector_dtype)
+        lay, total = self.layout(dtype, vector_dtype, trainable_only)
         if flat.numel() < total:
             raise ValueError(f"{self.name}: buffer of {flat.numel()} B < layout {total} B")
         res = {}
@@ -96,18 +107,21 @@ class Stage:
 
     # ---- data-parallel sharded storage: every tensor is cut into `world` equal
     # padded slices (a multiple of 8 elements each); a rank stores slice `rank`.
-    def shard_layout(self, dtype: torch.dtype, world: int):
+    def shard_layout(self, dtype: torch.dtype, world: int, trainable_only: bool = False):
         """[(spec, byte offset, dtype, elements per shard)], total bytes of one shard."""
         out, off = [], 0
         for p in self.params:
+            if trainable_only and not p.trainable:
+                continue
             dt = p.dtype or dtype
             per = -(-(-(-p.numel // world)) // 8) * 8
             out.append((p, off, dt, per))
             off = _round_up(off + per * dt.itemsize, ALIGN)
         return out, off
 
-    def shard_views(self, flat: torch.Tensor, dtype: torch.dtype, world: int) -> dict[str, torch.Tensor]:
-        lay, total = self.shard_layout(dtype, world)
+    def shard_views(self, flat: torch.Tensor, dtype: torch.dtype, world: int,
+                    trainable_only: bool = False) -> dict[str, torch.Tensor]:
+        lay, total = self.shard_layout(dtype, world, trainable_only)
         if flat.numel() < total:
             raise ValueError(f"{self.name}: buffer of {flat.numel()} B < shard layout {total} B")
         return {p.name: flat[off:off + per * dt.itemsize].view(dt) for p, off, dt, per in lay}
@@ -144,9 +158,10 @@ class Stage:
 class EmbeddingStage(Stage):
     kind = "embedding"
 
-    def __init__(self, name, cfg):
+    def __init__(self, name, cfg, trainable: bool = True):
         super().__init__(name, cfg)
-        self.params = [ParamSpec("embed", (cfg.vocab_size, cfg.d_model), std=cfg.initializer_range)]
+        self.params = [ParamSpec("embed", (cfg.vocab_size, cfg.d_model), std=cfg.initializer_range,
+                                 trainable=trainable)]
 
     def forward(self, P, x, meta: BatchMeta, keep=None, out=None):
         return F.embedding_fwd(meta.tokens, P["embed"], out=out), {}
@@ -408,14 +423,16 @@ class HeadLossStage(Stage):
     hidden-state gradient by two GEMMs."""
     kind = "head"
 
-    def __init__(self, name, cfg, block_rows: int = 2048):
+    def __init__(self, name, cfg, block_rows: int = 2048, objective=None, trainable: bool = True):
         super().__init__(name, cfg)
+        from .objectives import Objective
         self.block_rows = block_rows
+        self.objective = objective or Objective()
         norm_init = "zeros" if cfg.zero_centered_norm else "ones"
-        self.params = [ParamSpec("final_norm", (cfg.d_model,), init=norm_init)]
+        self.params = [ParamSpec("final_norm", (cfg.d_model,), init=norm_init, trainable=trainable)]
         if not cfg.tied_embeddings:
             self.params.append(ParamSpec("head", (cfg.vocab_size, cfg.d_model),
-                                         std=cfg.initializer_range))
+                                         std=cfg.initializer_range, trainable=trainable))
 
     def workspace_bytes(self, T, itemsize=2):
         c = self.cfg
@@ -434,35 +451,63 @@ class HeadLossStage(Stage):
         W = P["head"]
         h, rstd = F.rmsnorm_fwd(x, P["final_norm"], c.norm_epsilon, c.zero_centered_norm)
         dh = torch.empty_like(h) if train else None
-        if train and first:
+        frozen = not G or "head" not in G
+        if train and first and not frozen:
             G["final_norm"].zero_()
         B = self.block_rows
         acc = not first
+        ob, X = self.objective, meta.extras
         for r0 in range(0, T, B):
             r1 = min(T, r0 + B)
             logits = F.linear_fwd(h[r0:r1], W)
-            F.cross_entropy_(logits, meta.targets[r0:r1], meta.weights[r0:r1], loss_sum,
-                             grad_scale=grad_scale, write_grad=train)
+            if ob.kind == "clipped_policy":
+                ref = X["reference_logprobs"][r0:r1] if ob.reference_beta > 0 else None
+                F.clipped_policy_(logits, meta.targets[r0:r1], meta.weights[r0:r1],
+                                  X["old_logprobs"][r0:r1], X["advantages"][r0:r1], loss_sum,
+                                  clip=ob.clip_ratio, ref_logp=ref, ref_beta=ob.reference_beta,
+                                  grad_scale=grad_scale, write_grad=train)
+            else:
+                F.cross_entropy_(logits, meta.targets[r0:r1], meta.weights[r0:r1], loss_sum,
+                                 grad_scale=grad_scale, write_grad=train)
             if train:
-                F.linear_wgrad(logits, h[r0:r1], out=G["head"], accumulate=acc)
+                if not frozen:
+                    F.linear_wgrad(logits, h[r0:r1], out=G["head"], accumulate=acc)
                 F.linear_dgrad(logits, W, out=dh[r0:r1])
                 acc = True
             del logits
         if not train:
             return None
-        return F.rmsnorm_bwd(x, P["final_norm"], dh, rstd, G["final_norm"], c.zero_centered_norm,
+        dw = G["final_norm"] if not frozen else torch.zeros(c.d_model, dtype=torch.float32,
+                                                            device=x.device)
+        return F.rmsnorm_bwd(x, P["final_norm"], dh, rstd, dw, c.zero_centered_norm,
                              dx=dx, accumulate=False)
+
+    def target_logprobs(self, P, x, meta: BatchMeta) -> torch.Tensor:
+        """log p(target) for every token (fp32 [T]), in the same row blocks."""
+        c = self.cfg
+        T = x.shape[0]
+        h, _ = F.rmsnorm_fwd(x, P["final_norm"], c.norm_epsilon, c.zero_centered_norm)
+        out = torch.empty(T, dtype=torch.float32, device=x.device)
+        for r0 in range(0, T, self.block_rows):
+            r1 = min(T, r0 + self.block_rows)
+            F.target_logprobs_(F.linear_fwd(h[r0:r1], P["head"]), meta.targets[r0:r1], out[r0:r1])
+        return out
 
 
 # ============================================================================ assembly
-def build_stages(cfg: DecoderConfig) -> list[Stage]:
-    stages: list[Stage] = [EmbeddingStage("embed", cfg)]
+def build_stages(cfg: DecoderConfig, objective=None, lora=None) -> list[Stage]:
+    """``objective`` selects what the head evaluates; ``lora`` adds low-rank adapters to
+    every layer (which then run through the autograd-derived layer stage) and freezes
+    the embedding, the head and the base matrices unless ``lora.train_base``."""
+    base_trainable = lora is None or lora.train_base
+    stages: list[Stage] = [EmbeddingStage("embed", cfg, trainable=base_trainable)]
     for i in range(cfg.n_layers):
         kind = cfg.layer_kind(i)
-        if kind == "deltanet" or cfg.is_moe or cfg.gated_attention:
+        if kind == "deltanet" or cfg.is_moe or cfg.gated_attention or lora is not None:
             from .hybrid import make_layer
-            stages.append(make_layer(f"layer{i}", cfg, i))
+            coef = objective.moe_balance_coef if objective is not None and objective.moe_balance_coef > 0 else None
+            stages.append(make_layer(f"layer{i}", cfg, i, lora, coef))
         else:
             stages.append(DenseLayerStage(f"layer{i}", cfg))
-    stages.append(HeadLossStage("head", cfg))
+    stages.append(HeadLossStage("head", cfg, objective=objective, trainable=base_trainable))
     return stages

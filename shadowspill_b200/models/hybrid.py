@@ -30,9 +30,13 @@ class HybridLayerStage(Stage):
     kind = "layer"
     SAVE_SETS = {"recompute": ()}
 
-    def __init__(self, name: str, cfg: DecoderConfig, index: int):
+    def __init__(self, name: str, cfg: DecoderConfig, index: int, lora=None):
         super().__init__(name, cfg)
         self.index = index
+        self.lora = lora
+        self.aux_coef = float(cfg.router_aux_coef)   # router balance term; 0 = off
+        self._aux: list[torch.Tensor] = []           # this execution's balance term (autograd)
+        self.aux_sum: torch.Tensor | None = None     # running sum of applied balance losses
         self.mixer = cfg.layer_kind(index)
         c, std = cfg, cfg.initializer_range
         D, dh, Hq, Hkv = c.d_model, c.head_dim, c.n_heads, c.n_kv_heads
@@ -68,9 +72,27 @@ class HybridLayerStage(Stage):
                     P.append(ParamSpec("shared_gate", (D,), std=std))
         else:
             P += [ParamSpec("w13", (2 * c.d_ff, D), std=std), ParamSpec("w2", (D, c.d_ff), std=std)]
+        self._banks = ["w13", "w2"] if c.is_moe else []
+        self._adapted: set[str] = set()
+        if lora is not None:
+            from dataclasses import replace as _replace
+            from .lora import factor_names
+            extra = []
+            for p in P:
+                is_bank = p.name in self._banks
+                if p.name not in lora.targets or len(p.shape) < 2 or (is_bank and not lora.routed_experts):
+                    continue
+                a, b = factor_names(p.name)
+                lead = p.shape[:-2]
+                extra += [ParamSpec(a, lead + (lora.rank, p.shape[-1]), std=std),
+                          ParamSpec(b, lead + (p.shape[-2], lora.rank), init="zeros")]
+                self._adapted.add(p.name)
+            if not lora.train_base:
+                P = [_replace(p, trainable=False) for p in P]
+            P += extra
+            self._banks += [n for e in extra for n in [e.name] if len(e.shape) == 3]
         self.params = P
         self._leaf = [p.name for p in P if p.name in ("conv_w", "A_log", "dt_bias", "shared_gate")]
-        self._banks = ["w13", "w2"] if c.is_moe else []
 
     # ---- sizes (used for modelled costs until profiled)
     def workspace_bytes(self, T, itemsize=2):
@@ -91,14 +113,21 @@ class HybridLayerStage(Stage):
         return mix + 2.0 * T * c.d_model * ff
 
     # ---- the layer
+    def _lin(self, P, x, name: str, sink):
+        """Projection ``name``, with its low-rank adapter when it has one."""
+        if name in self._adapted:
+            return A.lora_linear(x, P[name], P[f"{name}_lora_a"], P[f"{name}_lora_b"],
+                                 self.lora.scale, sink, name)
+        return A.linear(x, P[name], sink, name)
+
     def _attention(self, P, h, meta: BatchMeta, sink):
         c = self.cfg
         T = h.shape[0]
         dh, Hq, Hkv = c.head_dim, c.n_heads, c.n_kv_heads
-        qg = A.linear(h, P["wq"], sink, "wq")
+        qg = self._lin(P, h, "wq", sink)
         q, gate = (qg[:, :Hq * dh], qg[:, Hq * dh:]) if c.gated_attention else (qg, None)
-        k = A.linear(h, P["wk"], sink, "wk")
-        v = A.linear(h, P["wv"], sink, "wv")
+        k = self._lin(P, h, "wk", sink)
+        v = self._lin(P, h, "wv", sink)
         if c.qk_norm and c.qk_norm_full_width:
             q = A.rmsnorm(q.contiguous(), P["q_norm"], c.norm_epsilon, c.zero_centered_norm, sink, "q_norm")
             k = A.rmsnorm(k.contiguous(), P["k_norm"], c.norm_epsilon, c.zero_centered_norm, sink, "k_norm")
@@ -113,13 +142,13 @@ class HybridLayerStage(Stage):
                           meta.cu_seqlens, meta.max_seqlen).reshape(T, Hq * dh)
         if gate is not None:
             att = att * torch.sigmoid(gate.float()).to(att.dtype)
-        return A.linear(att.contiguous(), P["wo"], sink, "wo")
+        return self._lin(P, att.contiguous(), "wo", sink)
 
     def _deltanet(self, P, L, h, meta: BatchMeta, sink, bounds):
         c = self.cfg
         T = h.shape[0]
         Hk, Hv, dk = c.dn_qk_heads, c.dn_v_heads, c.dn_head_dim
-        qkvz = A.linear(h, P["w_qkvz"], sink, "w_qkvz")
+        qkvz = self._lin(P, h, "w_qkvz", sink)
         ba = A.linear(h, P["w_ba"], sink, "w_ba")
         conv = seq_ops.causal_conv_silu(qkvz[:, :self.conv_width], L["conv_w"], bounds)
         q = seq_ops.l2_normalize(conv[:, :self.key_width].reshape(T, Hk, dk))
@@ -131,16 +160,26 @@ class HybridLayerStage(Stage):
         gate = qkvz[:, self.conv_width:].reshape(T, Hv, dk)
         normed = seq_ops.gated_rmsnorm(mixed, gate, P["lin_norm_leaf"], c.norm_epsilon,
                                        c.zero_centered_norm)
-        return A.linear(normed.reshape(T, Hv * dk).contiguous(), P["w_out"], sink, "w_out")
+        return self._lin(P, normed.reshape(T, Hv * dk).contiguous(), "w_out", sink)
 
     def _experts(self, P, L, h, sink):
         c = self.cfg
         T = h.shape[0]
         logits = A.linear(h, P["router"], sink, "router").float()
-        if h.is_cuda:
+        if self.aux_coef > 0 and sink is not None:
+            from .objectives import router_balance
+            with torch.no_grad():
+                top = torch.topk(logits if c.router_renormalize else torch.softmax(logits, -1),
+                                 c.top_k, dim=-1).indices
+                counts = torch.bincount(top.reshape(-1), minlength=c.n_experts)
+            self._aux.append(router_balance(torch.softmax(logits, -1).sum(0), counts, T, c.top_k))
+        routed_lora = bool(self._adapted & {"w13", "w2"})
+        if h.is_cuda and not routed_lora:
             from ..ops import moe as moe_ops
             out = moe_ops.experts(h, logits, P["w13"], P["w2"], c.top_k, c.router_renormalize, sink)
             return self._shared(P, L, h, sink, out)
+        if h.is_cuda:
+            return self._shared(P, L, h, sink, self._experts_lora_cuda(P, h, logits, sink))
         if c.router_renormalize:
             vals, ids = torch.topk(logits, c.top_k, dim=-1)
             wts = torch.softmax(vals, dim=-1)
@@ -159,16 +198,44 @@ class HybridLayerStage(Stage):
                 continue
             rows = tok[pos:pos + n]
             xe = h.index_select(0, rows)
-            gu = A.linear(xe, P["w13"][e], sink, "w13", e)
-            ye = A.linear(A.swiglu(gu), P["w2"][e], sink, "w2", e)
+            gu = self._expert_lin(P, xe, "w13", e, sink)
+            ye = self._expert_lin(P, A.swiglu(gu), "w2", e, sink)
             out = out.index_add(0, rows, ye * w_sorted[pos:pos + n, None])
             pos += n
         return self._shared(P, L, h, sink, out)
 
+    def _expert_lin(self, P, x, name: str, e: int, sink):
+        y = A.linear(x, P[name][e], sink, name, e)
+        if name in self._adapted:
+            a, b = f"{name}_lora_a", f"{name}_lora_b"
+            y = y + A.linear(A.linear(x, P[a][e], sink, a, e), P[b][e], sink, b, e) * self.lora.scale
+        return y
+
+    def _experts_lora_cuda(self, P, h, logits, sink):
+        """Routed experts with per-expert adapters: the same grouped tcgen05 GEMMs, composed
+        from differentiable pieces (gather, grouped linear, combine) so that the adapter
+        factors train while the banks stay frozen."""
+        from ..ops import moe as moe_ops
+        c = self.cfg
+        ids, _, counts = moe_ops.route(logits.detach(), c.top_k, c.router_renormalize)
+        wts = moe_ops._weights_from_logits(logits, ids.long(), c.router_renormalize)
+        lay = moe_ops.Layout(ids, counts)
+        xs = A.expert_gather(h, lay)
+
+        def bank(x, name):
+            y = A.grouped_linear(x, P[name], lay, sink, name)
+            if name in self._adapted:
+                a, b = f"{name}_lora_a", f"{name}_lora_b"
+                low = A.grouped_linear(A.grouped_linear(x, P[a], lay, sink, a), P[b], lay, sink, b)
+                y = y + low * self.lora.scale
+            return y
+        ys = bank(A.swiglu(bank(xs, "w13")), "w2")
+        return A.expert_combine(ys, wts.float().contiguous(), lay)
+
     def _shared(self, P, L, h, sink, out):
         c = self.cfg
         if c.d_shared_expert:
-            sh = A.linear(A.swiglu(A.linear(h, P["sw13"], sink, "sw13")), P["sw2"], sink, "sw2")
+            sh = self._lin(P, A.swiglu(self._lin(P, h, "sw13", sink)), "sw2", sink)
             if c.gated_shared_expert:
                 sh = sh * torch.sigmoid(h.float() @ L["shared_gate"].float()).to(h.dtype)[:, None]
             out = out + sh
@@ -184,7 +251,7 @@ class HybridLayerStage(Stage):
         if c.is_moe:
             ff = self._experts(P, L, h, sink)
         else:
-            ff = A.linear(A.swiglu(A.linear(h, P["w13"], sink, "w13")), P["w2"], sink, "w2")
+            ff = self._lin(P, A.swiglu(self._lin(P, h, "w13", sink)), "w2", sink)
         return x + ff
 
     def _leaves(self, P, grad: bool):
@@ -213,19 +280,35 @@ class HybridLayerStage(Stage):
         sink = A.GradSink(G, first)
         if first and not x.is_cuda:
             for name in self._banks:          # experts without tokens still need defined gradients
+                if name not in G:
+                    continue
                 G[name].zero_()
                 for e in range(self.cfg.n_experts):
                     sink.written.add(f"{name}[{e}]")
         P2, L = self._leaves(P, True)
         xin = x.detach().requires_grad_(True)
+        self._aux = []
         with torch.enable_grad():
             y = self._layer(P2, L, xin, meta, sink, bounds)
-        torch.autograd.backward(y, dy)
+        if self._aux:
+            # the balance term joins the loss with this microbatch's share of the loss weight
+            share = meta.weights.sum() * self.aux_coef
+            aux = self._aux[0] * share
+            if self.aux_sum is None:
+                self.aux_sum = torch.zeros(1, dtype=torch.float32, device=x.device)
+            self.aux_sum += aux.detach().float()
+            torch.autograd.backward([y, aux], [dy, torch.ones_like(aux)])
+            self._aux = []
+        else:
+            torch.autograd.backward(y, dy)
         for name, leaf in L.items():
             sink.add_vector(name, leaf.grad if leaf.grad is not None else torch.zeros_like(leaf))
         dy.copy_(xin.grad)
         return dy
 
 
-def make_layer(name: str, cfg: DecoderConfig, index: int) -> Stage:
-    return HybridLayerStage(name, cfg, index)
+def make_layer(name: str, cfg: DecoderConfig, index: int, lora=None, aux_coef: float | None = None) -> Stage:
+    st = HybridLayerStage(name, cfg, index, lora)
+    if aux_coef is not None and cfg.is_moe:
+        st.aux_coef = float(aux_coef)
+    return st

@@ -165,14 +165,16 @@ def hybrid_layer(cfg: DecoderConfig, P: dict, x, meta: BatchMeta, index: int):
     return x + ff
 
 
-def model_loss(cfg: DecoderConfig, params: dict[str, torch.Tensor], meta: BatchMeta) -> torch.Tensor:
-    """Weighted-sum loss of any catalog family (dense layers use ``dense_layer``)."""
+def model_loss(cfg: DecoderConfig, params: dict[str, torch.Tensor], meta: BatchMeta,
+               stages=None) -> torch.Tensor:
+    """Weighted-sum loss of any catalog family (dense layers use ``dense_layer``).
+    ``stages`` overrides the stage list whose layer classes pick the layer form."""
     from .decoder import DenseLayerStage, build_stages
 
     def stage(name):
         pre = name + "."
         return {k[len(pre):]: v for k, v in params.items() if k.startswith(pre)}
-    stages = build_stages(cfg)
+    stages = stages or build_stages(cfg)
     x = stage("embed")["embed"][meta.tokens]
     for i in range(cfg.n_layers):
         P = stage(f"layer{i}")

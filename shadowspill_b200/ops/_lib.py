@@ -30,6 +30,8 @@ _SIGNATURES = {
     "ss_embedding_fwd": [c_p, c_p, c_p, c_int, c_int, c_int, c_p],
     "ss_embedding_bwd": [c_p, c_p, c_p, c_int, c_int, c_int, c_int, c_p],
     "ss_cross_entropy": [c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_ll, c_f, c_int, c_p],
+    "ss_token_objective": [c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_ll, c_f, c_int, c_int, c_p, c_p,
+                           c_f, c_p, c_f, c_p],
     "ss_adamw_sr": [c_p, c_p, c_p, c_p, c_ll, c_int, c_f, c_f, c_f, c_f, c_f, c_int, c_f, c_ull,
                     c_ull, c_int, c_int, c_p],
     "ss_adamw_f32": [c_p, c_p, c_p, c_p, c_ll, c_f, c_f, c_f, c_f, c_f, c_int, c_f, c_p],

@@ -378,12 +378,25 @@ __global__ void embedding_bwd_bf16_kernel(const long long* __restrict__ ids,
 // weight * (lse - logit[target]); then the row is REWRITTEN IN PLACE with its
 // gradient weight * grad_scale * (softmax - onehot). Rows with weight 0 (masked)
 // produce a zero gradient row. loss_sum / weight_sum accumulate with atomics.
+//
+// mode 1 is the clipped policy objective on the same block: with
+// logp = logit[target] - lse, r = exp(logp - old_logp), A = advantage,
+//   L = -min(r A, clamp(r, 1-clip, 1+clip) A)  [+ beta * (exp(ref-logp) - (ref-logp) - 1)]
+// and the row becomes weight * grad_scale * dL/dlogp * (onehot - softmax).
+struct PolicyArgs {
+  int mode;                 // 0 cross-entropy, 1 clipped policy
+  const float* old_logp;
+  const float* advantage;
+  const float* ref_logp;    // optional
+  float clip, ref_beta;
+  float* logp_out;          // optional: per-row log-probability of the target
+};
 constexpr int CE_THREADS = 512;
 __global__ void __launch_bounds__(CE_THREADS)
 cross_entropy_kernel(bf16* __restrict__ logits, const long long* __restrict__ targets,
                      const float* __restrict__ weights, float* __restrict__ loss_sum,
                      float* __restrict__ lse_out, int R, int V, long long ld, float grad_scale,
-                     int write_grad) {
+                     int write_grad, PolicyArgs pa) {
   __shared__ float red[33];
   const int row = blockIdx.x;
   if (row >= R) return;
@@ -415,14 +428,31 @@ cross_entropy_kernel(bf16* __restrict__ logits, const long long* __restrict__ ta
   const float gs = block_sum(s, red);
   const float lse = gm + __logf(gs);
   long long tgt = targets[row];
-  const bool valid = (tgt >= 0 && tgt < V) && wgt != 0.f;
+  const bool in_vocab = tgt >= 0 && tgt < V;
+  const bool valid = in_vocab && wgt != 0.f;
+  const float logp = in_vocab ? __bfloat162float(lr[tgt]) - lse : 0.f;
+  float row_loss = -logp, dl_dlogp = -1.f;
+  if (pa.mode == 1 && valid) {
+    const float r = __expf(logp - pa.old_logp[row]);
+    const float A = pa.advantage[row];
+    const float unclipped = r * A;
+    const float clipped = fminf(fmaxf(r, 1.f - pa.clip), 1.f + pa.clip) * A;
+    row_loss = -fminf(unclipped, clipped);
+    dl_dlogp = (unclipped <= clipped) ? -unclipped : 0.f;
+    if (pa.ref_logp != nullptr) {
+      const float d = pa.ref_logp[row] - logp;
+      row_loss += pa.ref_beta * (__expf(d) - d - 1.f);
+      dl_dlogp += pa.ref_beta * (1.f - __expf(d));
+    }
+  }
   if (threadIdx.x == 0) {
     if (lse_out) lse_out[row] = lse;
-    if (valid) atomicAdd(loss_sum, wgt * (lse - __bfloat162float(lr[tgt])));
+    if (pa.logp_out) pa.logp_out[row] = logp;
+    if (valid) atomicAdd(loss_sum, wgt * row_loss);
   }
   if (!write_grad) return;
   __syncthreads();
-  const float scale = valid ? wgt * grad_scale : 0.f;
+  const float scale = valid ? -wgt * grad_scale * dl_dlogp : 0.f;
   uint4* gv = reinterpret_cast<uint4*>(lr);
   for (int c = threadIdx.x; c < nv; c += CE_THREADS) {
     float f[8];
@@ -689,7 +719,22 @@ int ss_cross_entropy(void* logits, const long long* targets, const float* weight
   if (ld % 8) return -2;
   if (R <= 0) return 0;
   cross_entropy_kernel<<<R, CE_THREADS, 0, (cudaStream_t)stream>>>(
-      (bf16*)logits, targets, weights, loss_sum, lse, R, V, ld, grad_scale, write_grad);
+      (bf16*)logits, targets, weights, loss_sum, lse, R, V, ld, grad_scale, write_grad, PolicyArgs{});
+  return (int)cudaGetLastError();
+}
+// Token objectives on a logits block: mode 0 cross-entropy, mode 1 clipped policy
+// (old_logp and advantage required; ref_logp optional). logp_out, when given,
+// receives log p(target) per row.
+int ss_token_objective(void* logits, const long long* targets, const float* weights, float* loss_sum,
+                       float* logp_out, int R, int V, long long ld, float grad_scale, int write_grad,
+                       int mode, const float* old_logp, const float* advantage, float clip,
+                       const float* ref_logp, float ref_beta, void* stream) {
+  if (ld % 8 || mode < 0 || mode > 1) return -2;
+  if (mode == 1 && (!old_logp || !advantage)) return -2;
+  if (R <= 0) return 0;
+  PolicyArgs pa{mode, old_logp, advantage, ref_logp, clip, ref_beta, logp_out};
+  cross_entropy_kernel<<<R, CE_THREADS, 0, (cudaStream_t)stream>>>(
+      (bf16*)logits, targets, weights, loss_sum, nullptr, R, V, ld, grad_scale, write_grad, pa);
   return (int)cudaGetLastError();
 }
 int ss_adamw_sr(void* p, const void* g, void* m, void* v, long long n, int g_f32, float lr,

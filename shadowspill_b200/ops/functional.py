@@ -205,6 +205,44 @@ def cross_entropy_(logits, targets, weights, loss_sum, *, grad_scale=1.0, write_
     return loss_sum
 
 
+def clipped_policy_(logits, targets, weights, old_logp, advantage, loss_sum, *, clip=0.2,
+                    ref_logp=None, ref_beta=0.0, grad_scale=1.0, write_grad=True, logp=None):
+    """Clipped policy objective on a logits block: adds the weighted loss into
+    ``loss_sum`` and rewrites ``logits`` with its gradient; ``logp`` (fp32[R]) receives
+    the target log-probabilities."""
+    if not _cuda(logits):
+        loss, lp = reference.clipped_policy_(logits, targets, weights, old_logp, advantage, clip,
+                                             ref_logp, ref_beta, grad_scale, write_grad)
+        loss_sum.add_(loss)
+        if logp is not None:
+            logp.copy_(lp)
+        return loss_sum
+    R, V = logits.shape
+    _lib.check(_lib.lib().ss_token_objective(
+        logits.data_ptr(), targets.data_ptr(), _ptr(weights), loss_sum.data_ptr(), _ptr(logp), R, V,
+        logits.stride(0), float(grad_scale), int(write_grad), 1, old_logp.data_ptr(),
+        advantage.data_ptr(), float(clip), _ptr(ref_logp), float(ref_beta), _lib.stream_ptr()),
+        "ss_token_objective")
+    return loss_sum
+
+
+def target_logprobs_(logits, targets, logp):
+    """log p(target) per row of a logits block into ``logp`` (fp32[R]); logits unchanged."""
+    if not _cuda(logits):
+        lf = logits.float()
+        V = logits.shape[-1]
+        picked = lf.gather(1, targets.clamp(0, V - 1)[:, None])[:, 0]
+        logp.copy_(picked - torch.logsumexp(lf, dim=-1))
+        return logp
+    R, V = logits.shape
+    scratch = torch.zeros(1, dtype=torch.float32, device=logits.device)
+    _lib.check(_lib.lib().ss_token_objective(
+        logits.data_ptr(), targets.data_ptr(), None, scratch.data_ptr(), logp.data_ptr(), R, V,
+        logits.stride(0), 1.0, 0, 0, None, None, 0.0, None, 0.0, _lib.stream_ptr()),
+        "ss_token_objective")
+    return logp
+
+
 # ------------------------------------------------------------------------ AdamW
 def adamw_(p, g, m, v, *, lr, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0, step=1,
            grad_scale=1.0, seed=0, offset=0, stochastic_param=True, stochastic_state=True):

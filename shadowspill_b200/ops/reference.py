@@ -114,6 +114,30 @@ def cross_entropy_(logits, targets, weights, grad_scale=1.0, write_grad=True):
     return loss, lse
 
 
+def clipped_policy_(logits, targets, weights, old_logp, advantage, clip, ref_logp=None,
+                    ref_beta=0.0, grad_scale=1.0, write_grad=True):
+    """Weighted-sum clipped policy objective over a logits block (autograd-derived
+    gradient written in place). Returns (loss_sum, logp[R])."""
+    lf = logits.float().detach().requires_grad_(write_grad)
+    V = logits.shape[-1]
+    valid = (targets >= 0) & (targets < V)
+    w = torch.ones(logits.shape[0], device=logits.device) if weights is None else weights.float()
+    w = torch.where(valid, w, torch.zeros_like(w))
+    tgt = targets.clamp(0, V - 1)
+    logp = lf.gather(1, tgt[:, None])[:, 0] - torch.logsumexp(lf, dim=-1)
+    r = torch.exp(logp - old_logp.float())
+    A = advantage.float()
+    per = -torch.minimum(r * A, r.clamp(1 - clip, 1 + clip) * A)
+    if ref_logp is not None:
+        d = ref_logp.float() - logp
+        per = per + ref_beta * (torch.exp(d) - d - 1)
+    loss = (w * per).sum()
+    if write_grad:
+        (g,) = torch.autograd.grad(loss * grad_scale, lf)
+        logits.copy_(g.to(logits.dtype))
+    return loss.detach(), logp.detach()
+
+
 def adamw_(p, g, m, v, *, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0):
     """Round-to-nearest AdamW in fp32 math on tensors of any dtype (in place)."""
     gf = g.float() * grad_scale

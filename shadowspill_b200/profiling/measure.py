@@ -57,7 +57,10 @@ def _fill_inputs(runner: TaskRunner, task: int, flats: list[torch.Tensor], host_
             mb = host_batch[max(t.microbatch, 0)]
             buf = np.zeros(obj.bytes, dtype=np.uint8)
             for name, (off, count, dt) in runner.batch_layout_.items():
-                src = getattr(mb, name)
+                if hasattr(mb, name):
+                    src = getattr(mb, name)
+                else:      # objective inputs: zeros keep ratios at one and every branch finite
+                    src = mb.extras.get(name, np.zeros(count, dtype=dt))
                 view = buf[off:off + count * np.dtype(dt).itemsize].view(dt)
                 view[:src.shape[0]] = src
                 if name == "cu_seqlens":
