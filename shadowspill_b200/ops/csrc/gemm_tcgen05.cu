@@ -39,6 +39,9 @@ struct GemmCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  // scatter epilogue only: per epilogue warp a 32-row x 128-column bf16 staging tile, so that
+  // rows leave the SM as whole 256-byte runs (peer stores want full lines, not 16-byte pieces)
+  static constexpr int SCATTER_STAGE = 4 * 32 * 256;
   static constexpr int TMEM_COLS = 2 * BN;  // 512 or 256
 };
 
@@ -276,6 +279,45 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int row = mb * BM + q * 32 + lane;
       const uint32_t taddr =
           tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
+      if (p.g.row_dst != nullptr) {
+        // Scatter epilogue. Each thread owns one accumulator row; the rows are transposed
+        // through an XOR-swizzled staging tile so that 16 lanes store one row's 256
+        // contiguous bytes at its destination address.
+        uint8_t* stg = smem + Cfg::STAGES * Cfg::STAGE_BYTES + 256 + q * (32 * 256);
+        const long long my_dst = (row < p.M) ? p.g.row_dst[row] : 0;
+#pragma unroll 1
+        for (int half = 0; half < BN / 128; ++half) {
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + half * 128 + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 v;
+              v.x = pack_bf16(__uint_as_float(r[8 * i + 0]) * p.alpha, __uint_as_float(r[8 * i + 1]) * p.alpha);
+              v.y = pack_bf16(__uint_as_float(r[8 * i + 2]) * p.alpha, __uint_as_float(r[8 * i + 3]) * p.alpha);
+              v.z = pack_bf16(__uint_as_float(r[8 * i + 4]) * p.alpha, __uint_as_float(r[8 * i + 5]) * p.alpha);
+              v.w = pack_bf16(__uint_as_float(r[8 * i + 6]) * p.alpha, __uint_as_float(r[8 * i + 7]) * p.alpha);
+              const int chunk = c * 4 + i;
+              *reinterpret_cast<uint4*>(stg + lane * 256 + ((chunk ^ (lane & 15)) << 4)) = v;
+            }
+          }
+          __syncwarp();
+#pragma unroll 1
+          for (int rr = 0; rr < 16; ++rr) {
+            const int srow = rr * 2 + (lane >> 4);
+            const int chunk = lane & 15;
+            const long long where = __shfl_sync(0xffffffffu, my_dst, srow);
+            const int col = nb * BN + half * 128 + chunk * 8;
+            if (where != 0 && col < p.N) {
+              const uint4 v = *reinterpret_cast<const uint4*>(stg + srow * 256 + ((chunk ^ (srow & 15)) << 4));
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(where) + col) = v;
+            }
+          }
+          __syncwarp();
+        }
+      } else
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -300,11 +342,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           } else {
             __nv_bfloat16* dst =
                 reinterpret_cast<__nv_bfloat16*>(p.C) + w.c_off + static_cast<long long>(row) * p.ldc + col0;
-            if (p.g.row_dst != nullptr) {
-              const long long where = p.g.row_dst[row];
-              if (where == 0) continue;
-              dst = reinterpret_cast<__nv_bfloat16*>(where) + col0;
-            }
             for (int j = 0; j < ncols; j += 8) {
               float f[8];
 #pragma unroll
@@ -410,14 +447,16 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
   static bool configured = false;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::SMEM + Cfg::SCATTER_STAGE);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
+  const int smem_bytes = Cfg::SMEM + (p.g.row_dst != nullptr ? Cfg::SCATTER_STAGE : 0);
   const long long tiles = static_cast<long long>((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) *
                           (p.g.mode == 2 ? p.g.n_experts : 1);
   const int grid = tiles < num_sms ? static_cast<int>(tiles) : num_sms;
-  kern<<<grid, GEMM_THREADS, Cfg::SMEM, stream>>>(ta, tb, p);
+  kern<<<grid, GEMM_THREADS, smem_bytes, stream>>>(ta, tb, p);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -179,7 +179,6 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, long lon
                                    __nv_bfloat16* __restrict__ out, long long ldo, int T, int k, int D,
                                    int accumulate, const __nv_bfloat16* __restrict__ g, long long ldg,
                                    float* __restrict__ dots) {
-  __shared__ float red[32];
   const int nv = D >> 3;
   for (int t = blockIdx.x; t < T; t += gridDim.x) {
     if (out != nullptr) {
@@ -207,22 +206,25 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, long lon
       }
     }
     if (dots != nullptr) {
-      for (int j = 0; j < k; ++j) {
+      // one warp per slot: 16-byte loads, a shuffle reduction, no block barrier
+      const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+      const uint4* gv = reinterpret_cast<const uint4*>(g + static_cast<long long>(t) * ldg);
+      for (int j = warp; j < k; j += nwarps) {
         const long long a = static_cast<long long>(t) * k + j;
-        const __nv_bfloat16* yr = y + static_cast<long long>(dest[a]) * ldy;
-        const __nv_bfloat16* gr = g + static_cast<long long>(t) * ldg;
+        const uint4* yv = reinterpret_cast<const uint4*>(y + static_cast<long long>(dest[a]) * ldy);
         float part = 0.f;
-        for (int c = threadIdx.x; c < D; c += blockDim.x)
-          part += __bfloat162float(yr[c]) * __bfloat162float(gr[c]);
-        part = wsum(part);
-        __syncthreads();
-        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = part;
-        __syncthreads();
-        if (threadIdx.x == 0) {
-          float s = 0.f;
-          for (int w = 0; w < (blockDim.x + 31) / 32; ++w) s += red[w];
-          dots[a] = s;
+        for (int c = lane; c < nv; c += 32) {
+          const uint4 u = yv[c], w = gv[c];
+          const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&u);
+          const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&w);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 fu = __bfloat1622float2(uh[e]), fw = __bfloat1622float2(wh[e]);
+            part += fu.x * fw.x + fu.y * fw.y;
+          }
         }
+        part = wsum(part);
+        if (lane == 0) dots[a] = part;
       }
     }
   }
@@ -269,7 +271,7 @@ int ss_moe_gather(const void* x, long long ldx, const int* dest, const float* we
 int ss_moe_combine(const void* y, long long ldy, const int* dest, const float* weights, void* out,
                    long long ldo, int T, int k, int D, int accumulate, const void* g, long long ldg,
                    float* dots, void* stream) {
-  if (D % 8 || ldy % 8 || (out && ldo % 8)) return -2;
+  if (D % 8 || ldy % 8 || (out && ldo % 8) || (dots && ldg % 8)) return -2;
   if (T <= 0) return 0;
   moe_combine_kernel<<<T > 148 * 8 ? 148 * 8 : T, 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)y, ldy, dest, weights, (__nv_bfloat16*)out, ldo, T, k, D, accumulate,

@@ -93,12 +93,14 @@ class Layout:
         return (res, dots) if dots_with is not None else res
 
 
-def grouped_linear(x_sorted: torch.Tensor, bank: torch.Tensor, lay: Layout, transpose: bool = False):
+def grouped_linear(x_sorted: torch.Tensor, bank: torch.Tensor, lay: Layout, transpose: bool = False,
+                   out: torch.Tensor | None = None):
     """``y[r] = x[r] @ bank[e(r)]^T`` (or ``@ bank[e(r)]`` when ``transpose``) over sorted rows."""
     E = bank.shape[0]
     K = x_sorted.shape[1]
     N = bank.shape[2] if transpose else bank.shape[1]
-    out = torch.empty((lay.rows, N), dtype=x_sorted.dtype, device=x_sorted.device)
+    if out is None:
+        out = torch.empty((lay.rows, N), dtype=x_sorted.dtype, device=x_sorted.device)
     _lib.check(_lib.lib().ss_gemm_grouped_bf16(
         x_sorted.data_ptr(), bank.data_ptr(), out.data_ptr(), 1, lay.rows, 0, N, K, E,
         x_sorted.stride(0), bank.stride(1), out.stride(0), int(transpose), 0, 0,
