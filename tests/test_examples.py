@@ -1,0 +1,23 @@
+"""The example scripts run as written (CPU paths)."""
+import importlib.util
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _load(name):
+    spec = importlib.util.spec_from_file_location(name, ROOT / "examples" / f"{name}.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_train_budgeted_example(tmp_path):
+    loss = _load("train_budgeted").main(["--steps", "2", "--out", str(tmp_path)])
+    assert loss > 0
+    assert (tmp_path / "index.html").exists() and (tmp_path / "runtime.html").exists()
+
+
+def test_service_quickstart_example():
+    losses = _load("service_quickstart").main()
+    assert len(losses) == 4 and losses[-1] < losses[0]
