@@ -381,3 +381,14 @@ def recompute_share_selections(cfg: DecoderConfig, shares=(100, 75, 50, 25, 0),
         rec = {int((i + 0.5) * n / k) for i in range(k)} if k else set()
         out.append({li + 1: saved_variant for li in range(n) if li not in rec})
     return out
+
+
+def mixed_selection(cfg: DecoderConfig, full_save_layers: int, base_variant: str = "save_attention",
+                    full_variant: str = "save") -> dict[int, str]:
+    """Every layer keeps ``base_variant``; ``full_save_layers`` of them, evenly spaced, keep the
+    whole ``full_variant`` set instead. A finer resolution between "attention saved
+    everywhere" and "everything saved everywhere" for budgets that afford a little more."""
+    n = cfg.n_layers
+    k = max(0, min(n, full_save_layers))
+    full = {int((i + 0.5) * n / k) for i in range(k)} if k else set()
+    return {li + 1: (full_variant if li in full else base_variant) for li in range(n)}

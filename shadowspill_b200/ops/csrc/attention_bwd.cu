@@ -17,7 +17,9 @@
 // delta[h,t] = sum_d dO*O comes from a small preprocess kernel into caller
 // scratch (fp32 [Hq, T]).
 //
-// warps 0..3 softmax (one TMEM lane per thread), warp 4 TMA producer, warp 5 MMA.
+// warps 0..7 softmax: warp w owns TMEM lanes 32*(w%4)..+31 and the 32-column half w/4 of
+// every score tile, so two warps per scheduler hide each other's TMEM-load and exp latency;
+// warp 8 TMA producer, warp 9 MMA.
 #include "sm100_ptx.cuh"
 
 #include <cudaTypedefs.h>
@@ -28,7 +30,8 @@ namespace ss {
 int make_tmap_bf16(CUtensorMap* map, const void* base, long long rows, long long cols,
                    long long ld, int box_rows);
 
-constexpr int BW_THREADS = 192;
+constexpr int BW_THREADS = 320;
+constexpr int BW_TMA_WARP = 8, BW_MMA_WARP = 9;
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct AttnBwdParams {
@@ -70,8 +73,8 @@ __device__ __forceinline__ void store_swizzled_32(uint8_t* tile, int box_bytes, 
   }
 }
 
-__device__ __forceinline__ void named_barrier_128() {
-  asm volatile("bar.sync 1, 128;" ::: "memory");
+__device__ __forceinline__ void named_barrier_softmax() {
+  asm volatile("bar.sync 1, 256;" ::: "memory");
 }
 
 // ============================================================================ preprocess
@@ -142,19 +145,19 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(qdo_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1);
-      mbar_init(&sdp_full[i], 1); mbar_init(&sdp_free[i], 4);
+      mbar_init(&sdp_full[i], 1); mbar_init(&sdp_free[i], 8);
     }
-    mbar_init(ds_full, 4);
+    mbar_init(ds_full, 8);
     mbar_init(dq_done, 1);
     mbar_fence_init();
   }
-  if (warp == 5) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  if (warp == BW_MMA_WARP) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4) {
+  if (warp == BW_TMA_WARP) {
     if (elect_one()) {
       mbar_expect_tx(qdo_full, 2 * Cfg::Q_BYTES);
 #pragma unroll
@@ -177,7 +180,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == BW_MMA_WARP) {
     if (elect_one()) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, BKV, false, false);
       constexpr uint32_t idesc_dq = umma_idesc_bf16(128, DH, false, true);
@@ -233,9 +236,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
     }
   } else {
-    const int row = warp * 32 + lane;
+    const int quarter = warp & 3, hsel = warp >> 2;
+    const int row = quarter * 32 + lane;
     const int gq = q0 + row;
-    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const long long li = static_cast<long long>(head) * p.T + min(gq, p.T - 1);
     const float lse2 = p.lse[li] * LOG2E;
     const float dl = p.delta[li];
@@ -249,7 +253,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc_fence_after();
       const int k0 = seq_start + j * BKV;
 #pragma unroll 1
-      for (int c = 0; c < BKV / 32; ++c) {
+      for (int c = hsel; c < BKV / 32; c += 2) {
         uint32_t s[32], d[32];
         tmem_ld_32x32(lane_addr + Cfg::TM_S + b * BKV + c * 32, s);
         tmem_ld_32x32(lane_addr + Cfg::TM_DP + b * BKV + c * 32, d);
@@ -278,7 +282,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.dq) +
                             static_cast<long long>(gq) * p.ldq + head * DH;
 #pragma unroll 1
-      for (int c = 0; c < DH / 32; ++c) {
+      for (int c = hsel; c < DH / 32; c += 2) {
         uint32_t r[32];
         tmem_ld_32x32(lane_addr + Cfg::TM_DQ + c * 32, r);
         tmem_ld_wait();
@@ -298,7 +302,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+  if (warp == BW_MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
 // ============================================================================ dKV kernel
@@ -360,19 +364,19 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(kv_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1);
-      mbar_init(&sp_full[i], 1); mbar_init(&sp_free[i], 4);
+      mbar_init(&sp_full[i], 1); mbar_init(&sp_free[i], 8);
     }
-    mbar_init(pds_full, 4);
+    mbar_init(pds_full, 8);
     mbar_init(acc_done, 1);
     mbar_fence_init();
   }
-  if (warp == 5) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  if (warp == BW_MMA_WARP) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4) {
+  if (warp == BW_TMA_WARP) {
     if (elect_one()) {
       mbar_expect_tx(kv_full, Cfg::NEED_DP ? 2 * Cfg::K_BYTES : Cfg::K_BYTES);
 #pragma unroll
@@ -397,7 +401,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == BW_MMA_WARP) {
     if (elect_one()) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, BQ, false, false);
       constexpr uint32_t idesc_acc = umma_idesc_bf16(128, DH, false, true);
@@ -465,9 +469,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
     }
   } else {
-    const int row = warp * 32 + lane;        // key row within the tile
+    const int quarter = warp & 3, hsel = warp >> 2;
+    const int row = quarter * 32 + lane;     // key row within the tile
     const int gk = k0 + row;
-    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const float c2 = p.scale * LOG2E;
     bool ok = true;
     for (int it = 0; it < n_it; ++it) {
@@ -479,14 +484,14 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int col = threadIdx.x & (BQ - 1);
         const long long li = static_cast<long long>(head) * p.T + min(qt0 + col, p.T - 1);
         if (threadIdx.x < BQ) sl[col] = p.lse[li] * LOG2E;
-        else sl[BQ + col] = p.delta[li];
+        else if (threadIdx.x < 2 * BQ) sl[BQ + col] = p.delta[li];
       }
-      named_barrier_128();
+      named_barrier_softmax();
       if (!mbar_wait(&sp_full[b], (it >> 1) & 1, p.status, KS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       if (it > 0 && !mbar_wait(acc_done, (it - 1) & 1, p.status, KS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < BQ / 32; ++c) {
+      for (int c = hsel; c < BQ / 32; c += 2) {
         uint32_t s[32], d[32];
         tmem_ld_32x32(lane_addr + Cfg::TM_ST + b * BQ + c * 32, s);
         if (Cfg::NEED_DP) tmem_ld_32x32(lane_addr + Cfg::TM_DPT + b * BQ + c * 32, d);
@@ -522,7 +527,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(base) +
                               static_cast<long long>(gk) * ld + kv_head * DH;
 #pragma unroll 1
-        for (int c = 0; c < DH / 32; ++c) {
+        for (int c = hsel; c < DH / 32; c += 2) {
           uint32_t r[32];
           tmem_ld_32x32(lane_addr + tm_col + c * 32, r);
           tmem_ld_wait();
@@ -545,7 +550,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+  if (warp == BW_MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
 template <typename K>

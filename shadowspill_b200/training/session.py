@@ -58,8 +58,9 @@ class TrainingSetup:
     walks: tuple[str, ...] = ("breadth",)
     recompute_shares: tuple[int, ...] = (100,)
     saved_variant: str = "save_attention"
-    # explicit "<recompute share>:<saved variant>" candidates (e.g. "50:save"); when given
-    # they replace the recompute_shares x saved_variant grid
+    # explicit "<recompute share>:<saved variant>" candidates (e.g. "50:save") or "mix:<K>"
+    # (attention saved on every layer, K layers saved whole); when given they replace the
+    # recompute_shares x saved_variant grid
     candidate_selections: tuple[str, ...] = ()
     profile: bool = True
     calibrate: bool = True
@@ -94,6 +95,10 @@ class TrainingSession:
             selections = []
             for item in setup.candidate_selections:
                 share, _, variant = item.partition(":")
+                if share == "mix":        # "mix:K": save_attention everywhere, K layers fully saved
+                    from ..frontend.capture import mixed_selection
+                    selections.append(mixed_selection(self.cfg, int(variant)))
+                    continue
                 selections += recompute_share_selections(self.cfg, (int(share),),
                                                          variant or setup.saved_variant)
         else:
