@@ -108,7 +108,7 @@ struct DqCfg {
   static constexpr int OFF_K = 2 * Q_BYTES;
   static constexpr int OFF_V = OFF_K + KVS * KV_BYTES;
   static constexpr int OFF_DS = OFF_V + KVS * KV_BYTES;
-  static constexpr int OFF_BAR = OFF_DS + DS_BYTES;
+  static constexpr int OFF_BAR = OFF_DS + 2 * DS_BYTES;   // dS is double-buffered
   static constexpr int SMEM = OFF_BAR + 256 + 1024;
   static constexpr int TM_S = 0, TM_DP = 2 * BKV, TM_DQ = 4 * BKV;
   static_assert(TM_DQ + DH <= 512, "TMEM budget");
@@ -129,9 +129,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* kv_empty = bars + 3;        // 2
   uint64_t* sdp_full = bars + 5;        // 2
   uint64_t* sdp_free = bars + 7;        // 2
-  uint64_t* ds_full = bars + 9;         // 1
-  uint64_t* dq_done = bars + 10;        // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* ds_full = bars + 9;         // 2
+  uint64_t* dq_done = bars + 11;        // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.y;
@@ -146,9 +146,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int i = 0; i < 2; ++i) {
       mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1);
       mbar_init(&sdp_full[i], 1); mbar_init(&sdp_free[i], 8);
+      mbar_init(&ds_full[i], 8); mbar_init(&dq_done[i], 1);
     }
-    mbar_init(ds_full, 8);
-    mbar_init(dq_done, 1);
     mbar_fence_init();
   }
   if (warp == BW_MMA_WARP) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
@@ -220,18 +219,19 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (ok) { tc_fence_after(); issue_sdp(0); }
       for (int j = 0; j < n_kv && ok; ++j) {
         if (KVS >= 2 && j + 1 < n_kv) { ok = prefetch_next(j); if (!ok) break; }
-        ok = mbar_wait(ds_full, j & 1, p.status, KS_TIMEOUT_FULL);
+        ok = mbar_wait(&ds_full[j & 1], (j >> 1) & 1, p.status, KS_TIMEOUT_FULL);
         if (!ok) break;
         tc_fence_after();
         const uint32_t sk = smem_u32(smem + Cfg::OFF_K + (j % KVS) * Cfg::KV_BYTES);
+        const uint32_t sdsj = sds + (j & 1) * Cfg::DS_BYTES;
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk) {
-          const uint64_t ad = umma_smem_desc(sds + (kk >> 2) * (128 * 128) + (kk & 3) * 32, 16, 1024);
+          const uint64_t ad = umma_smem_desc(sdsj + (kk >> 2) * (128 * 128) + (kk & 3) * 32, 16, 1024);
           const uint64_t bd = umma_smem_desc(sk + kk * (16 * 128), BKV * 128, 1024);
           umma_bf16(tmem_base + Cfg::TM_DQ, ad, bd, idesc_dq, (j | kk) != 0);
         }
         umma_commit(&kv_empty[j % KVS]);
-        umma_commit(dq_done);
+        umma_commit(&dq_done[j & 1]);
         if (KVS < 2 && j + 1 < n_kv) { ok = prefetch_next(j); }
       }
     }
@@ -244,14 +244,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const float lse2 = p.lse[li] * LOG2E;
     const float dl = p.delta[li];
     const float c2 = p.scale * LOG2E;
-    uint8_t* sds = smem + Cfg::OFF_DS;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
       const int b = j & 1;
+      uint8_t* sds = smem + Cfg::OFF_DS + b * Cfg::DS_BYTES;
       if (!mbar_wait(&sdp_full[b], (j >> 1) & 1, p.status, KS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
-      if (j > 0 && !mbar_wait(dq_done, (j - 1) & 1, p.status, KS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      // this dS buffer was last read by the dQ MMAs of tile j-2
+      if (j > 1 && !mbar_wait(&dq_done[b], ((j >> 1) - 1) & 1, p.status, KS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
       const int k0 = seq_start + j * BKV;
+      const bool below_diagonal = k0 + BKV - 1 <= q0;   // every key of the tile is visible to every row
 #pragma unroll 1
       for (int c = hsel; c < BKV / 32; c += 2) {
         uint32_t s[32], d[32];
@@ -259,25 +261,36 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tmem_ld_32x32(lane_addr + Cfg::TM_DP + b * BKV + c * 32, d);
         tmem_ld_wait();
         uint32_t pk[16];
+        if (below_diagonal) {
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float v[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int gk = k0 + c * 32 + e + u;
-            const float pr = (gk > gq) ? 0.f : exp2f(__uint_as_float(s[e + u]) * c2 - lse2);
-            v[u] = pr * (__uint_as_float(d[e + u]) - dl) * p.scale;
+          for (int e = 0; e < 32; e += 2) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(s[e]), c2, -lse2));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(s[e + 1]), c2, -lse2));
+            pk[e >> 1] = pack_bf16(p0 * (__uint_as_float(d[e]) - dl),
+                                   p1 * (__uint_as_float(d[e + 1]) - dl));
           }
-          pk[e >> 1] = pack_bf16(v[0], v[1]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            float v[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int gk = k0 + c * 32 + e + u;
+              const float pr = (gk > gq) ? 0.f : fast_exp2(fmaf(__uint_as_float(s[e + u]), c2, -lse2));
+              v[u] = pr * (__uint_as_float(d[e + u]) - dl);   // the softmax scale is applied to dQ once
+            }
+            pk[e >> 1] = pack_bf16(v[0], v[1]);
+          }
         }
         store_swizzled_32(sds, 128 * 128, row, c * 32, pk);
       }
       tc_fence_before();
       fence_async_proxy();
       __syncwarp();
-      if (lane == 0) { mbar_arrive(&sdp_free[b]); mbar_arrive(ds_full); }
+      if (lane == 0) { mbar_arrive(&sdp_free[b]); mbar_arrive(&ds_full[b]); }
     }
-    if (ok && n_kv > 0 && mbar_wait(dq_done, (n_kv - 1) & 1, p.status, KS_TIMEOUT_TMEM_FULL)) {
+    if (ok && n_kv > 0 && mbar_wait(&dq_done[(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1, p.status,
+                                    KS_TIMEOUT_TMEM_FULL)) {
       tc_fence_after();
       __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.dq) +
                             static_cast<long long>(gq) * p.ldq + head * DH;
@@ -287,13 +300,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tmem_ld_32x32(lane_addr + Cfg::TM_DQ + c * 32, r);
         tmem_ld_wait();
         if (gq < q_hi) {
+          const float sc = p.scale;
 #pragma unroll
           for (int e = 0; e < 32; e += 8) {
             uint4 v;
-            v.x = pack_bf16(__uint_as_float(r[e]), __uint_as_float(r[e + 1]));
-            v.y = pack_bf16(__uint_as_float(r[e + 2]), __uint_as_float(r[e + 3]));
-            v.z = pack_bf16(__uint_as_float(r[e + 4]), __uint_as_float(r[e + 5]));
-            v.w = pack_bf16(__uint_as_float(r[e + 6]), __uint_as_float(r[e + 7]));
+            v.x = pack_bf16(__uint_as_float(r[e]) * sc, __uint_as_float(r[e + 1]) * sc);
+            v.y = pack_bf16(__uint_as_float(r[e + 2]) * sc, __uint_as_float(r[e + 3]) * sc);
+            v.z = pack_bf16(__uint_as_float(r[e + 4]) * sc, __uint_as_float(r[e + 5]) * sc);
+            v.w = pack_bf16(__uint_as_float(r[e + 6]) * sc, __uint_as_float(r[e + 7]) * sc);
             *reinterpret_cast<uint4*>(orow + c * 32 + e) = v;
           }
         }
@@ -321,8 +335,8 @@ struct DkvCfg {
   static constexpr int OFF_Q = OFF_V + (NEED_DP ? K_BYTES : 0);
   static constexpr int OFF_DO = OFF_Q + QS * QT_BYTES;
   static constexpr int OFF_PT = OFF_DO + QS * QT_BYTES;
-  static constexpr int OFF_DST = OFF_PT + (DO_DV ? PT_BYTES : 0);
-  static constexpr int OFF_LSE = OFF_DST + (DO_DK ? PT_BYTES : 0);
+  static constexpr int OFF_DST = OFF_PT + (DO_DV ? 2 * PT_BYTES : 0);   // P^T, dS^T double-buffered
+  static constexpr int OFF_LSE = OFF_DST + (DO_DK ? 2 * PT_BYTES : 0);
   static constexpr int OFF_BAR = OFF_LSE + 2 * 2 * BQ * 4;
   static constexpr int SMEM = OFF_BAR + 256 + 1024;
   static constexpr int TM_ST = 0, TM_DPT = 2 * BQ;
@@ -347,9 +361,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* q_empty = bars + 3;         // 2
   uint64_t* sp_full = bars + 5;         // 2
   uint64_t* sp_free = bars + 7;         // 2
-  uint64_t* pds_full = bars + 9;        // 1
-  uint64_t* acc_done = bars + 10;       // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* pds_full = bars + 9;        // 2
+  uint64_t* acc_done = bars + 11;       // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   float* s_lse = reinterpret_cast<float*>(smem + Cfg::OFF_LSE);   // [2][2][BQ]: lse2, delta
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -365,9 +379,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     for (int i = 0; i < 2; ++i) {
       mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1);
       mbar_init(&sp_full[i], 1); mbar_init(&sp_free[i], 8);
+      mbar_init(&pds_full[i], 8); mbar_init(&acc_done[i], 1);
     }
-    mbar_init(pds_full, 8);
-    mbar_init(acc_done, 1);
     mbar_fence_init();
   }
   if (warp == BW_MMA_WARP) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
@@ -443,28 +456,29 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (ok) { tc_fence_after(); issue_sp(0); }
       for (int it = 0; it < n_it && ok; ++it) {
         if (QS >= 2 && it + 1 < n_it) { ok = prefetch_next(it); if (!ok) break; }
-        ok = mbar_wait(pds_full, it & 1, p.status, KS_TIMEOUT_FULL);
+        ok = mbar_wait(&pds_full[it & 1], (it >> 1) & 1, p.status, KS_TIMEOUT_FULL);
         if (!ok) break;
         tc_fence_after();
         const int st = it % QS;
+        const uint32_t spt_i = spt + (it & 1) * Cfg::PT_BYTES, sdst_i = sdst + (it & 1) * Cfg::PT_BYTES;
         const uint32_t sq = smem_u32(smem + Cfg::OFF_Q + st * Cfg::QT_BYTES);
         const uint32_t sdo = smem_u32(smem + Cfg::OFF_DO + st * Cfg::QT_BYTES);
 #pragma unroll
         for (int kk = 0; kk < BQ / 16; ++kk) {
           if (Cfg::DO_DV) {
             const uint32_t acc = tmem_base + (MODE == MODE_BOTH ? Cfg::TM_ACC1 : Cfg::TM_ACC0);
-            umma_bf16(acc, umma_smem_desc(spt + kk * 32, 16, 1024),
+            umma_bf16(acc, umma_smem_desc(spt_i + kk * 32, 16, 1024),
                       umma_smem_desc(sdo + kk * (16 * 128), BQ * 128, 1024), idesc_acc,
                       (it | kk) != 0);
           }
           if (Cfg::DO_DK) {
-            umma_bf16(tmem_base + Cfg::TM_ACC0, umma_smem_desc(sdst + kk * 32, 16, 1024),
+            umma_bf16(tmem_base + Cfg::TM_ACC0, umma_smem_desc(sdst_i + kk * 32, 16, 1024),
                       umma_smem_desc(sq + kk * (16 * 128), BQ * 128, 1024), idesc_acc,
                       (it | kk) != 0);
           }
         }
         umma_commit(&q_empty[st]);
-        umma_commit(acc_done);
+        umma_commit(&acc_done[it & 1]);
         if (QS < 2 && it + 1 < n_it) { ok = prefetch_next(it); }
       }
     }
@@ -488,7 +502,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       named_barrier_softmax();
       if (!mbar_wait(&sp_full[b], (it >> 1) & 1, p.status, KS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
-      if (it > 0 && !mbar_wait(acc_done, (it - 1) & 1, p.status, KS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      // the P^T / dS^T buffers of this parity were last read by the MMAs of iteration it-2
+      if (it > 1 && !mbar_wait(&acc_done[b], ((it >> 1) - 1) & 1, p.status, KS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
 #pragma unroll 1
       for (int c = hsel; c < BQ / 32; c += 2) {
@@ -497,6 +512,21 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (Cfg::NEED_DP) tmem_ld_32x32(lane_addr + Cfg::TM_DPT + b * BQ + c * 32, d);
         tmem_ld_wait();
         uint32_t pkp[16], pkd[16];
+        // whole tile visible: every query of the tile is at or after every key, none past the end
+        const bool all_valid = (qt0 >= k0 + 127) && (qt0 + BQ <= seq_end);
+        if (all_valid) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const int col = c * 32 + e;
+            const float p0 = fast_exp2(fmaf(__uint_as_float(s[e]), c2, -sl[col]));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(s[e + 1]), c2, -sl[col + 1]));
+            pkp[e >> 1] = pack_bf16(p0, p1);
+            pkd[e >> 1] = Cfg::NEED_DP
+                ? pack_bf16(p0 * (__uint_as_float(d[e]) - sl[BQ + col]),
+                            p1 * (__uint_as_float(d[e + 1]) - sl[BQ + col + 1]))
+                : 0u;
+          }
+        } else
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
           float pv[2], dv[2];
@@ -505,25 +535,26 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             const int col = c * 32 + e + u;
             const int gqc = qt0 + col;
             const bool valid = (gqc < seq_end) && (gk <= gqc);
-            const float pr = valid ? exp2f(__uint_as_float(s[e + u]) * c2 - sl[col]) : 0.f;
+            const float pr = valid ? fast_exp2(fmaf(__uint_as_float(s[e + u]), c2, -sl[col])) : 0.f;
             pv[u] = pr;
-            dv[u] = Cfg::NEED_DP ? pr * (__uint_as_float(d[e + u]) - sl[BQ + col]) * p.scale : 0.f;
+            dv[u] = Cfg::NEED_DP ? pr * (__uint_as_float(d[e + u]) - sl[BQ + col]) : 0.f;   // dK scaled once at the end
           }
           pkp[e >> 1] = pack_bf16(pv[0], pv[1]);
           pkd[e >> 1] = pack_bf16(dv[0], dv[1]);
         }
-        if (Cfg::DO_DV) store_swizzled_32(smem + Cfg::OFF_PT, 128 * 128, row, c * 32, pkp);
-        if (Cfg::DO_DK) store_swizzled_32(smem + Cfg::OFF_DST, 128 * 128, row, c * 32, pkd);
+        if (Cfg::DO_DV) store_swizzled_32(smem + Cfg::OFF_PT + b * Cfg::PT_BYTES, 128 * 128, row, c * 32, pkp);
+        if (Cfg::DO_DK) store_swizzled_32(smem + Cfg::OFF_DST + b * Cfg::PT_BYTES, 128 * 128, row, c * 32, pkd);
       }
       tc_fence_before();
       fence_async_proxy();
       __syncwarp();
-      if (lane == 0) { mbar_arrive(&sp_free[b]); mbar_arrive(pds_full); }
+      if (lane == 0) { mbar_arrive(&sp_free[b]); mbar_arrive(&pds_full[b]); }
     }
-    if (ok && n_it > 0 && mbar_wait(acc_done, (n_it - 1) & 1, p.status, KS_TIMEOUT_TMEM_FULL)) {
+    if (ok && n_it > 0 && mbar_wait(&acc_done[(n_it - 1) & 1], ((n_it - 1) >> 1) & 1, p.status,
+                                    KS_TIMEOUT_TMEM_FULL)) {
       tc_fence_after();
       const bool valid = gk < seq_end;
-      auto store_acc = [&](uint32_t tm_col, void* base, long long ld) {
+      auto store_acc = [&](uint32_t tm_col, void* base, long long ld, float sc) {
         __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(base) +
                               static_cast<long long>(gk) * ld + kv_head * DH;
 #pragma unroll 1
@@ -535,17 +566,17 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
             for (int e = 0; e < 32; e += 8) {
               uint4 v;
-              v.x = pack_bf16(__uint_as_float(r[e]), __uint_as_float(r[e + 1]));
-              v.y = pack_bf16(__uint_as_float(r[e + 2]), __uint_as_float(r[e + 3]));
-              v.z = pack_bf16(__uint_as_float(r[e + 4]), __uint_as_float(r[e + 5]));
-              v.w = pack_bf16(__uint_as_float(r[e + 6]), __uint_as_float(r[e + 7]));
+              v.x = pack_bf16(__uint_as_float(r[e]) * sc, __uint_as_float(r[e + 1]) * sc);
+              v.y = pack_bf16(__uint_as_float(r[e + 2]) * sc, __uint_as_float(r[e + 3]) * sc);
+              v.z = pack_bf16(__uint_as_float(r[e + 4]) * sc, __uint_as_float(r[e + 5]) * sc);
+              v.w = pack_bf16(__uint_as_float(r[e + 6]) * sc, __uint_as_float(r[e + 7]) * sc);
               *reinterpret_cast<uint4*>(orow + c * 32 + e) = v;
             }
           }
         }
       };
-      if (Cfg::DO_DK) store_acc(Cfg::TM_ACC0, p.dk, p.ldk);
-      if (Cfg::DO_DV) store_acc(MODE == MODE_BOTH ? Cfg::TM_ACC1 : Cfg::TM_ACC0, p.dv, p.ldv);
+      if (Cfg::DO_DK) store_acc(Cfg::TM_ACC0, p.dk, p.ldk, p.scale);
+      if (Cfg::DO_DV) store_acc(MODE == MODE_BOTH ? Cfg::TM_ACC1 : Cfg::TM_ACC0, p.dv, p.ldv, 1.f);
     }
   }
   tc_fence_before();

@@ -232,7 +232,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       float alpha = 1.f;
       if (warp_rescale) {
         const float m_new = fmaxf(m_used, m_t);
-        alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_new);
+        alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new);
         m_used = m_new;
         l *= alpha;
       }
@@ -268,8 +268,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if ((k0 + c * 32 + e) > gq) s0 = -INFINITY;
             if ((k0 + c * 32 + e + 1) > gq) s1 = -INFINITY;
           }
-          const float p0 = exp2f(s0 - m_used);
-          const float p1 = exp2f(s1 - m_used);
+          const float p0 = fast_exp2(s0 - m_used);
+          const float p1 = fast_exp2(s1 - m_used);
           lsum += p0 + p1;
           pk[e >> 1] = pack_bf16(p0, p1);
         }

@@ -276,4 +276,13 @@ __device__ __forceinline__ float2 unpack_bf16(uint32_t u) {
   return __bfloat1622float2(v);
 }
 
+// 2^x on the special-function unit, flush-to-zero: one instruction, no range fix-up
+// (softmax probabilities never need denormals).
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+
 }  // namespace ss
