@@ -22,6 +22,8 @@ c_int, c_ll, c_ull, c_f, c_p = (ctypes.c_int, ctypes.c_longlong, ctypes.c_ulongl
 _SIGNATURES = {
     "ss_gemm_bf16": [c_p, c_p, c_p, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int, c_int, c_int,
                      c_int, c_f, c_int, c_int, c_p, c_p],
+    "ss_gemm2_bf16": [c_p, c_p, c_p, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int, c_int, c_int,
+                      c_int, c_f, c_int, c_p, c_p],
     "ss_rmsnorm_fwd": [c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_f, c_int, c_p],
     "ss_rmsnorm_bwd": [c_p, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_int, c_p],
     "ss_rope": [c_p, c_p, c_int, c_ll, c_int, c_int, c_int, c_int, c_f, c_int, c_p],

@@ -9,6 +9,8 @@ from __future__ import annotations
 
 import math
 
+import os
+
 import torch
 
 from . import _lib, reference
@@ -25,6 +27,10 @@ def _ptr(t: torch.Tensor | None) -> int | None:
 
 
 # ------------------------------------------------------------------------ GEMM
+# plain GEMMs run on the CTA-pair kernel; SS_GEMM_PAIR=0 selects the single-CTA kernel
+_PAIR_GEMM = os.environ.get("SS_GEMM_PAIR", "1") == "1"
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          out: torch.Tensor | None = None, accumulate: bool = False, alpha: float = 1.0,
          out_dtype: torch.dtype | None = None, bn: int = 0) -> torch.Tensor:
@@ -56,6 +62,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     if out.stride(-1) != 1 or out.dtype not in (_BF16, torch.float32):
         raise ValueError("gemm output must be bf16/fp32 with unit inner stride")
+    if _PAIR_GEMM and bn == 0 and M >= 256 and N >= 128:
+        # CTA-pair kernel (tcgen05 cta_group::2): 256x256 tiles, half the shared-memory
+        # traffic per FLOP of the single-CTA kernel
+        rc = _lib.lib().ss_gemm2_bf16(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
+            out.stride(0), int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate),
+            float(alpha), 0, _lib.status_word(a.device).data_ptr(), _lib.stream_ptr())
+        _lib.check(rc, "ss_gemm2_bf16")
+        return out
     rc = _lib.lib().ss_gemm_bf16(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
         out.stride(0), int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate),
