@@ -133,69 +133,69 @@ rmsnorm_fwd_kernel(bf16* __restrict__ x, const bf16* __restrict__ delta,
 // =============================================================== RMSNorm backward
 // dx = rstd * (g*w - xhat * mean(g*w*xhat)),  dw += sum_t g * xhat   (fp32 atomics)
 // dx is ADDED into dx_acc when accumulate != 0 (residual-stream gradient).
-__global__ void __launch_bounds__(NORM_THREADS)
+//
+// One warp per row, two passes over the row (the second hits L1/L2): no block barrier
+// per row and few live registers, so many rows are in flight per SM. The weight
+// gradient is accumulated with shared-memory atomics (one fp32 per column per block)
+// and flushed to global memory once per block.
+constexpr int NORM_BWD_WARPS = 8;
+__global__ void __launch_bounds__(NORM_BWD_WARPS * 32)
 rmsnorm_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
                    const bf16* __restrict__ gy, const float* __restrict__ rstd,
                    bf16* __restrict__ dx, float* __restrict__ dw, int T, int D, int zero_centered,
                    int accumulate) {
-  __shared__ float red[33];
+  extern __shared__ float s_dw[];          // [8][D/8]: element e of vector c at e*nv + c (conflict-free lanes)
   const int nv = D >> 3;
-  float dwacc[NORM_MAXV][8];
-#pragma unroll
-  for (int i = 0; i < NORM_MAXV; ++i)
-#pragma unroll
-    for (int e = 0; e < 8; ++e) dwacc[i][e] = 0.f;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (dw) {
+    for (int c = threadIdx.x; c < D; c += blockDim.x) s_dw[c] = 0.f;
+    __syncthreads();
+  }
   const uint4* wr = reinterpret_cast<const uint4*>(w);
-  for (int row = blockIdx.x; row < T; row += gridDim.x) {
+  for (int row = blockIdx.x * NORM_BWD_WARPS + warp; row < T; row += gridDim.x * NORM_BWD_WARPS) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * D);
     const uint4* gr = reinterpret_cast<const uint4*>(gy + static_cast<size_t>(row) * D);
     const float r = rstd[row];
-    float xh[NORM_MAXV][8], gw[NORM_MAXV][8];
     float dot = 0.f;
+#pragma unroll 4
+    for (int c = lane; c < nv; c += 32) {
+      float xv[8], gv[8], ww[8];
+      unpack8(xr[c], xv);
+      unpack8(gr[c], gv);
+      unpack8(wr[c], ww);
 #pragma unroll
-    for (int i = 0; i < NORM_MAXV; ++i) {
-      const int c = threadIdx.x + i * NORM_THREADS;
-      if (c < nv) {
-        float xv[8], gv[8], ww[8];
-        unpack8(xr[c], xv);
-        unpack8(gr[c], gv);
-        unpack8(wr[c], ww);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          xh[i][e] = xv[e] * r;
-          gw[i][e] = gv[e] * (zero_centered ? 1.f + ww[e] : ww[e]);
-          dot += gw[i][e] * xh[i][e];
-          dwacc[i][e] += gv[e] * xh[i][e];
-        }
+      for (int e = 0; e < 8; ++e) {
+        const float xh = xv[e] * r;
+        dot += gv[e] * (zero_centered ? 1.f + ww[e] : ww[e]) * xh;
+        if (dw) atomicAdd(&s_dw[e * nv + c], gv[e] * xh);
       }
     }
-    const float mean = block_sum(dot, red) / static_cast<float>(D);
+    const float mean = warp_sum(dot) / static_cast<float>(D);
     uint4* dr = reinterpret_cast<uint4*>(dx + static_cast<size_t>(row) * D);
+#pragma unroll 4
+    for (int c = lane; c < nv; c += 32) {
+      float xv[8], gv[8], ww[8], o[8];
+      unpack8(xr[c], xv);
+      unpack8(gr[c], gv);
+      unpack8(wr[c], ww);
 #pragma unroll
-    for (int i = 0; i < NORM_MAXV; ++i) {
-      const int c = threadIdx.x + i * NORM_THREADS;
-      if (c < nv) {
-        float o[8];
+      for (int e = 0; e < 8; ++e)
+        o[e] = r * (gv[e] * (zero_centered ? 1.f + ww[e] : ww[e]) - xv[e] * r * mean);
+      if (accumulate) {
+        float prev[8];
+        unpack8(dr[c], prev);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) o[e] = r * (gw[i][e] - xh[i][e] * mean);
-        if (accumulate) {
-          float prev[8];
-          unpack8(dr[c], prev);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) o[e] += prev[e];
-        }
-        dr[c] = pack8(o);
+        for (int e = 0; e < 8; ++e) o[e] += prev[e];
       }
+      dr[c] = pack8(o);
     }
   }
   if (dw) {
-#pragma unroll
-    for (int i = 0; i < NORM_MAXV; ++i) {
-      const int c = threadIdx.x + i * NORM_THREADS;
-      if (c < nv) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) atomicAdd(dw + c * 8 + e, dwacc[i][e]);
-      }
+    __syncthreads();
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+      const float v = s_dw[i];
+      const int e = i / nv, c = i - e * nv;
+      if (v != 0.f) atomicAdd(dw + c * 8 + e, v);
     }
   }
 }
@@ -654,9 +654,11 @@ int ss_rmsnorm_fwd(void* x, const void* delta, const void* w, void* y, float* rs
 }
 int ss_rmsnorm_bwd(const void* x, const void* w, const void* gy, const float* rstd, void* dx,
                    float* dw, int T, int D, int zero_centered, int accumulate, void* stream) {
-  if (D % 8 || D > NORM_THREADS * NORM_MAXV * 8) return -2;
+  if (D % 8 || D > 12288) return -2;       // the block's fp32 column sums live in 48 KB of shared memory
   if (T <= 0) return 0;
-  rmsnorm_bwd_kernel<<<T < 148 * 4 ? T : 148 * 4, NORM_THREADS, 0, (cudaStream_t)stream>>>(
+  const int row_blocks = (T + NORM_BWD_WARPS - 1) / NORM_BWD_WARPS;
+  rmsnorm_bwd_kernel<<<row_blocks < 148 * 4 ? row_blocks : 148 * 4, NORM_BWD_WARPS * 32,
+                       sizeof(float) * D, (cudaStream_t)stream>>>(
       (const bf16*)x, (const bf16*)w, (const bf16*)gy, rstd, (bf16*)dx, dw, T, D, zero_centered,
       accumulate);
   return (int)cudaGetLastError();
