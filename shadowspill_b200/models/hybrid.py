@@ -150,7 +150,7 @@ class HybridLayerStage(Stage):
         Hk, Hv, dk = c.dn_qk_heads, c.dn_v_heads, c.dn_head_dim
         qkvz = self._lin(P, h, "w_qkvz", sink)
         ba = A.linear(h, P["w_ba"], sink, "w_ba")
-        conv = seq_ops.causal_conv_silu(qkvz[:, :self.conv_width], L["conv_w"], bounds)
+        conv = seq_ops.causal_conv_silu(qkvz[:, :self.conv_width], L["conv_w"], bounds, meta.positions)
         q = seq_ops.l2_normalize(conv[:, :self.key_width].reshape(T, Hk, dk))
         k = seq_ops.l2_normalize(conv[:, self.key_width:2 * self.key_width].reshape(T, Hk, dk))
         v = conv[:, 2 * self.key_width:].reshape(T, Hv, dk)

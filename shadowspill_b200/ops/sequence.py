@@ -1,5 +1,9 @@
-"""Sequence-mixer ops of the hybrid (Gated DeltaNet) layers, written as
-differentiable PyTorch so that ``torch.autograd`` supplies their backward pass.
+"""Sequence-mixer ops of the hybrid (Gated DeltaNet) layers.
+
+The memory-bound pieces (causal convolution + SiLU, L2 normalisation, gated RMSNorm)
+run as hand-written sm_100a kernels with explicit backward kernels on bf16 CUDA
+tensors (``ops/csrc/deltanet.cu``) and as the plain PyTorch definitions below
+otherwise; the chunked delta rule itself is differentiable PyTorch.
 
 ``gated_delta_rule_chunked`` evaluates the gated delta rule in chunks of 64 tokens
 (the WY / UT-transform form): inside a chunk everything is dense matrix algebra,
@@ -22,16 +26,120 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as TF
 
+from . import _lib
+
+_c = _lib
+_lib.register("ss_conv_silu_fwd", [_c.c_p, _c.c_ll, _c.c_p, _c.c_p, _c.c_int, _c.c_int, _c.c_int, _c.c_p,
+                                   _c.c_ll, _c.c_p])
+_lib.register("ss_conv_silu_bwd", [_c.c_p, _c.c_ll, _c.c_p, _c.c_p, _c.c_int, _c.c_int, _c.c_int, _c.c_p,
+                                   _c.c_ll, _c.c_p, _c.c_p, _c.c_ll, _c.c_p, _c.c_p])
+_lib.register("ss_l2norm_fwd", [_c.c_p, _c.c_p, _c.c_ll, _c.c_int, _c.c_f, _c.c_p])
+_lib.register("ss_l2norm_bwd", [_c.c_p, _c.c_p, _c.c_p, _c.c_ll, _c.c_int, _c.c_f, _c.c_p])
+_lib.register("ss_gated_rmsnorm_fwd", [_c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_ll, _c.c_int, _c.c_f, _c.c_int,
+                                       _c.c_p])
+_lib.register("ss_gated_rmsnorm_bwd", [_c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_ll,
+                                       _c.c_int, _c.c_f, _c.c_int, _c.c_p])
+
+
+def _native(x: torch.Tensor) -> bool:
+    return x.is_cuda and x.dtype == torch.bfloat16
+
+
+class _L2Norm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, eps):
+        x = x.contiguous()
+        y = torch.empty_like(x)
+        W = x.shape[-1]
+        _lib.check(_lib.lib().ss_l2norm_fwd(x.data_ptr(), y.data_ptr(), x.numel() // W, W, eps,
+                                            _lib.stream_ptr()), "ss_l2norm_fwd")
+        ctx.save_for_backward(x)
+        ctx.eps = eps
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = torch.empty_like(x)
+        W = x.shape[-1]
+        _lib.check(_lib.lib().ss_l2norm_bwd(x.data_ptr(), dy.data_ptr(), dx.data_ptr(), x.numel() // W, W,
+                                            ctx.eps, _lib.stream_ptr()), "ss_l2norm_bwd")
+        return dx, None
+
+
+class _ConvSiLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, positions):
+        T, C = x.shape
+        w = w.contiguous()
+        y = torch.empty((T, C), dtype=x.dtype, device=x.device)
+        _lib.check(_lib.lib().ss_conv_silu_fwd(x.data_ptr(), x.stride(0), w.data_ptr(),
+                                               positions.data_ptr(), T, C, w.shape[1], y.data_ptr(),
+                                               y.stride(0), _lib.stream_ptr()), "ss_conv_silu_fwd")
+        ctx.save_for_backward(x, w, positions)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, positions = ctx.saved_tensors
+        T, C = x.shape
+        dy = dy.contiguous()
+        dpre = torch.empty((T, C), dtype=torch.float32, device=x.device)
+        dx = torch.empty((T, C), dtype=x.dtype, device=x.device)
+        dw = torch.zeros(w.shape, dtype=torch.float32, device=x.device)
+        _lib.check(_lib.lib().ss_conv_silu_bwd(x.data_ptr(), x.stride(0), w.data_ptr(),
+                                               positions.data_ptr(), T, C, w.shape[1], dy.data_ptr(),
+                                               dy.stride(0), dpre.data_ptr(), dx.data_ptr(), dx.stride(0),
+                                               dw.data_ptr(), _lib.stream_ptr()), "ss_conv_silu_bwd")
+        return dx, dw.to(w.dtype), None
+
+
+class _GatedRMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gate, w, eps, zero_centered):
+        x, gate, w = x.contiguous(), gate.contiguous(), w.contiguous()
+        y = torch.empty_like(x)
+        W = x.shape[-1]
+        _lib.check(_lib.lib().ss_gated_rmsnorm_fwd(x.data_ptr(), gate.data_ptr(), w.data_ptr(),
+                                                   y.data_ptr(), x.numel() // W, W, eps,
+                                                   int(zero_centered), _lib.stream_ptr()),
+                   "ss_gated_rmsnorm_fwd")
+        ctx.save_for_backward(x, gate, w)
+        ctx.args = (eps, zero_centered)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, gate, w = ctx.saved_tensors
+        eps, zc = ctx.args
+        dy = dy.contiguous()
+        dx, dgate = torch.empty_like(x), torch.empty_like(gate)
+        dw = torch.zeros(w.shape, dtype=torch.float32, device=x.device)
+        W = x.shape[-1]
+        _lib.check(_lib.lib().ss_gated_rmsnorm_bwd(x.data_ptr(), gate.data_ptr(), w.data_ptr(),
+                                                   dy.data_ptr(), dx.data_ptr(), dgate.data_ptr(),
+                                                   dw.data_ptr(), x.numel() // W, W, eps, int(zc),
+                                                   _lib.stream_ptr()), "ss_gated_rmsnorm_bwd")
+        return dx, dgate, dw.to(w.dtype), None, None
+
 
 def l2_normalize(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    if _native(x) and x.shape[-1] % 2 == 0:
+        return _L2Norm.apply(x, eps)
     xf = x.float()
     return (xf * torch.rsqrt(xf.square().sum(-1, keepdim=True) + eps)).to(x.dtype)
 
 
-def causal_conv_silu(x: torch.Tensor, w: torch.Tensor, bounds: list[int]) -> torch.Tensor:
+def causal_conv_silu(x: torch.Tensor, w: torch.Tensor, bounds: list[int],
+                     positions: torch.Tensor | None = None) -> torch.Tensor:
     """Depthwise causal conv1d (kernel ``w.shape[1]``) + SiLU; ``x`` [T,C], ``w`` [C,K].
-    The window never crosses a sequence boundary (``bounds`` = cu_seqlens as a list)."""
+    The window never crosses a sequence boundary (``bounds`` = cu_seqlens as a list;
+    ``positions`` = index of each token in its sequence, which the CUDA kernel uses)."""
     T, C = x.shape
+    if (_native(x) and positions is not None and C % 8 == 0 and x.stride(0) % 8 == 0
+            and x.stride(1) == 1 and w.shape[1] <= 8 and w.dtype == x.dtype):
+        return _ConvSiLU.apply(x, w, positions)
     K = w.shape[1]
     xf = x.float()
     # shifted copies: y[t] = sum_j w[:, K-1-j] * x[t-j], with x[t-j] zero before the sequence start
@@ -106,6 +214,8 @@ def gated_rmsnorm(x: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, eps: flo
                   zero_centered: bool = False) -> torch.Tensor:
     """RMSNorm over the last dimension followed by a SiLU gate (reference:
     models/shared/decoder.py GatedRMSNorm)."""
+    if _native(x) and gate.dtype == x.dtype and w.dtype == x.dtype and x.shape[-1] % 2 == 0:
+        return _GatedRMSNorm.apply(x, gate, w, eps, zero_centered)
     xf = x.float()
     r = torch.rsqrt(xf.square().mean(-1, keepdim=True) + eps)
     scale = (1.0 + w.float()) if zero_centered else w.float()
