@@ -78,3 +78,27 @@ def test_corruption_is_detected(tmp_path):
     with pytest.raises(CheckpointError):
         load_checkpoint(ex, tmp_path / "c")
     ex.close()
+
+
+def test_hugging_face_names_round_trip(tmp_path):
+    import torch
+    from shadowspill_b200.checkpoint import hf
+    from shadowspill_b200.execution.resident import ResidentTrainer
+    from shadowspill_b200.models.config import preset
+    for name in ("llama3-tiny", "qwen3-tiny", "olmoe-tiny"):
+        cfg = preset(name)
+        tr = ResidentTrainer(cfg, device="cpu", dtype=torch.float32, seed=1)
+        state = tr.state_dict()
+        named = hf.to_hf(cfg, state)
+        assert "model.layers.0.self_attn.q_proj.weight" in named
+        assert named["model.layers.0.self_attn.q_proj.weight"].shape == (cfg.n_heads * cfg.head_dim, cfg.d_model)
+        if cfg.is_moe:
+            assert f"model.layers.1.mlp.experts.{cfg.n_experts - 1}.down_proj.weight" in named
+        else:
+            assert named["model.layers.1.mlp.up_proj.weight"].shape == (cfg.d_ff, cfg.d_model)
+        hf.save_hf(cfg, state, tmp_path / name)
+        back = hf.load_hf(cfg, tmp_path / name)
+        assert set(back) == set(state)
+        for k, v in state.items():
+            assert torch.equal(back[k], v), k
+    assert not hf.supported(preset("qwen35-tiny"))
