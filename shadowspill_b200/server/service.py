@@ -68,6 +68,11 @@ class LiveRun:
             self.lease, devices = self.server.admission.lease(gpus, host_bytes)
             for setup, dev in zip(r.setups, devices or [0] * r.workers):
                 setup["device_index"] = dev
+            # prepared bundle: written by this run's rank 0, or reused from the run named in
+            # "plans" (same session) when its identity matches these settings
+            source = self.body.get("plans")
+            bundle_dir = (self.server.root / "runs" / self.session / str(source)) if source else self.dir
+            r.setups[0]["bundle"] = str(bundle_dir / "training.ssp")
             ckpt = self.body.get("checkpoint")
             if ckpt:
                 ckpt = self.server.resolve_checkpoint(self.session, ckpt)

@@ -69,6 +69,8 @@ class TrainingSetup:
     search: SearchOptions = field(default_factory=SearchOptions)
     trace_capacity: int = 0
     collectives: str = "auto"             # peer | dist | auto
+    # prepared bundle (training.ssp): read when it matches this setup, written after planning
+    bundle: str = ""
     operations: tuple[str, ...] = ("step",)   # also: forward_backward, optim_step, forward
 
 
@@ -126,7 +128,24 @@ class TrainingSession:
         self.profiles = Profiles()
         self.communication = CommunicationInfo(world_size=world)
         chosen, plan_json, extra_json = 0, None, {}
-        if rank == 0:
+        from .preparation import load_bundle, save_bundle, setup_identity
+        identity = setup_identity(setup, self.cfg)
+        loaded = load_bundle(setup.bundle, identity) if (rank == 0 and setup.bundle) else None
+        self.prepared_from_bundle = loaded is not None
+        self.sweep = None
+        if loaded is not None:
+            from ..ir.plan import Plan
+            chosen, plan_json, extra_json = loaded["chosen"], loaded["plan"], loaded["extra_plans"]
+            self.plan = Plan.from_json(plan_json)
+            self.desc = build(chosen)[1]
+            self.extra_plans = {op: (Plan.from_json(j), build_extra(op)[1])
+                                for op, j in extra_json.items()}
+            if loaded.get("communication"):
+                self.communication = CommunicationInfo.from_json(loaded["communication"])
+            if loaded.get("profiles"):
+                self.profiles = Profiles.from_json(loaded["profiles"])
+            self.log(f"prepared bundle {setup.bundle}: build, profile and plan skipped")
+        elif rank == 0:
             # ---- build candidates
             t0 = time.perf_counter()
             candidates = [build(i) for i in range(len(variants))]
@@ -180,6 +199,10 @@ class TrainingSession:
             self.desc = candidates[chosen][1]
             self.timings["plan"] = time.perf_counter() - t0
             plan_json = self.plan.to_json()
+            if setup.bundle:
+                save_bundle(setup.bundle, identity, chosen, plan_json, extra_json,
+                            self.profiles.to_json(), self.communication.to_json(), self.timings)
+                self.log(f"prepared bundle written to {setup.bundle}")
         if world > 1:
             # one plan for the whole job: identical offsets on every rank are what makes the
             # device pool symmetric, and identical task order keeps collectives matched
