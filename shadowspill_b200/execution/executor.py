@@ -14,6 +14,7 @@ Reference: packages/engine/src/shadowspill/execution/executor.py:35 (``Executor`
 """
 from __future__ import annotations
 
+import math
 import time
 from dataclasses import dataclass, field
 
@@ -81,7 +82,8 @@ class TaskRunner:
         for si, st in enumerate(self.stages):
             for p in st.params:
                 self.param_offsets[(si, p.name)] = off
-                off += (p.numel + 7) // 8 * 8
+                n = math.prod(p.global_shape) if p.expert_sharded else p.numel
+                off += (n + 7) // 8 * 8
 
     def _batch_meta(self, flat: torch.Tensor, m: int) -> BatchMeta:
         parts = {}
@@ -160,7 +162,10 @@ class TaskRunner:
             coll = self.collectives
             coll.barrier_begin()          # every rank's shard has landed
             for p in st.params:
-                coll.all_gather(B["shard"][p.name], B["params"][p.name].view(-1))
+                if p.expert_sharded:      # this rank's own experts: nothing to gather
+                    B["params"][p.name].view(-1).copy_(B["shard"][p.name][:p.numel])
+                else:
+                    coll.all_gather(B["shard"][p.name], B["params"][p.name].view(-1))
             coll.barrier_end()            # every rank is done reading this rank's shard
         else:
             raise RuntimeError(f"task kind {t.kind!r} has no executor")
@@ -178,6 +183,16 @@ class TaskRunner:
         coll.barrier_begin()              # every rank's gradients for this stage are complete
         for p in st.params:
             if not p.trainable:
+                continue
+            if p.expert_sharded:
+                # the local bank's gradient is already the sum over every rank's tokens
+                # (expert parallelism routes all of them here): a plain local update
+                F.adamw_(B["params"][p.name][:p.numel], B["grads"][p.name].view(-1),
+                         B["m"][p.name][:p.numel], B["v"][p.name][:p.numel], lr=h.lr, beta1=h.beta1,
+                         beta2=h.beta2, eps=h.eps, weight_decay=h.weight_decay,
+                         step=self.completed_updates + 1, grad_scale=h.grad_scale, seed=self.seed,
+                         offset=self.param_offsets[(stage, p.name)] + p.expert_lo * (p.numel // p.shape[0]),
+                         stochastic_param=self.sr, stochastic_state=self.sr)
                 continue
             coll.reduce_scatter_adamw(
                 B["grads"][p.name].view(-1), B["params"][p.name], B["m"][p.name], B["v"][p.name],
@@ -235,6 +250,17 @@ class Executor:
         self.collectives = coll
         self.runner = TaskRunner(plan.program, desc, self.hyper, seed, stochastic_rounding, coll)
         self.stages = self.runner.stages
+        self.ep_group = None
+        if desc.expert_parallel and self.world > 1:
+            if not self.cuda:
+                raise NotImplementedError("expert parallelism needs CUDA devices")
+            from ..parallel.expert_parallel import ExpertParallelGroup
+            c = desc.cfg
+            torch.cuda.set_device(device_index)
+            # one symmetric workspace for every routed layer of the model (outside the plan's pool)
+            self.ep_group = ExpertParallelGroup(self.runner.T, c.top_k, c.d_model, c.n_experts,
+                                                device=self.torch_device)
+            self._bind_expert_group(self.runner)
         if self.cuda:
             torch.cuda.set_device(device_index)
             from ..ops import _lib
@@ -265,8 +291,15 @@ class Executor:
     def _snapshot(self) -> dict:
         return {k: getattr(self, k) for k in self._PLAN_FIELDS}
 
+    def _bind_expert_group(self, runner: "TaskRunner") -> None:
+        for st in runner.stages:
+            if getattr(st, "ep_world", 1) > 1:
+                st.ep_group = self.ep_group
+
     def _bind_extra(self, plan: Plan, desc: TrainingDescription, sr: bool) -> dict:
         runner = TaskRunner(plan.program, desc, self.hyper, self.seed, sr, self.collectives)
+        if self.ep_group is not None:
+            self._bind_expert_group(runner)
         obj = {o.name: i for i, o in enumerate(plan.program.objects)}
         # persistent tensors of the same name must live at the same spill offset
         for name, i in obj.items():
@@ -335,6 +368,9 @@ class Executor:
                     shards = st.shard_views(w, self.desc.dtype, self.world)
                     for p in st.params:
                         src, dst = full[p.name].reshape(-1), shards[p.name]
+                        if p.expert_sharded:
+                            dst[:src.numel()].copy_(src)
+                            continue
                         lo = self.rank * dst.numel()
                         hi = min(src.numel(), lo + dst.numel())
                         if hi > lo:

@@ -94,6 +94,7 @@ class TrainingDescription:
     rank: int = 0
     objective: "Objective | None" = None
     lora: "LoRAConfig | None" = None
+    expert_parallel: bool = False     # routed layers keep 1/world of the experts per rank
 
     def __post_init__(self) -> None:
         extras = self.objective.extra_fields if self.objective is not None else ()
@@ -102,7 +103,8 @@ class TrainingDescription:
             self.geometry = _replace(self.geometry, extra_fields=tuple(extras))
 
     def stages(self):
-        return build_stages(self.cfg, self.objective, self.lora)
+        ep = (self.world_size, self.rank) if (self.expert_parallel and self.world_size > 1) else None
+        return build_stages(self.cfg, self.objective, self.lora, ep)
 
     def variant(self, stage_index: int) -> str:
         return self.selection.get(stage_index, "recompute")
@@ -198,6 +200,8 @@ def _build(desc: TrainingDescription) -> Program:
     tag = ""
     if desc.lora is not None:
         tag += f":lora{desc.lora.rank}{'b' if desc.lora.train_base else ''}"
+    if desc.expert_parallel and world > 1:
+        tag += f":ep{world}"
     if desc.objective is not None and desc.objective.kind != "cross_entropy":
         tag += f":{desc.objective.kind}"
 
@@ -333,13 +337,13 @@ def _build(desc: TrainingDescription) -> Program:
 def build_step(cfg: DecoderConfig, geometry: BatchGeometry,
                ordering: StepDataOrdering | None = None, *, dtype=torch.bfloat16,
                grad_dtype=None, selection: dict[int, str] | None = None, world_size: int = 1,
-               rank: int = 0, objective=None, lora=None):
+               rank: int = 0, objective=None, lora=None, expert_parallel: bool = False):
     """Forward + backward + optimizer of one global batch. Returns ``(Program, description)``.
     ``world_size > 1`` builds the data-parallel form: weights and AdamW moments are
     stored as 1/N shards, gathered before use and updated shard-locally."""
     desc = TrainingDescription(cfg, geometry, ordering or StepDataOrdering(), dtype,
                                grad_dtype or dtype, dict(selection or {}), "step", world_size,
-                               rank, objective, lora)
+                               rank, objective, lora, expert_parallel)
     return _build(desc), desc
 
 

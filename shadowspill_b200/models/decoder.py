@@ -35,6 +35,14 @@ class ParamSpec:
     std: float = 0.02
     dtype: torch.dtype | None = None   # None = the model dtype; fp32 exceptions set this
     trainable: bool = True
+    # expert parallelism: this rank holds experts [lo, lo + shape[0]) of a bank whose whole
+    # shape is ``global_shape``; such a tensor is never cut into flat 1/N shards or gathered
+    global_shape: tuple[int, ...] | None = None
+    expert_lo: int = 0
+
+    @property
+    def expert_sharded(self) -> bool:
+        return self.global_shape is not None
 
     @property
     def numel(self) -> int:
@@ -114,7 +122,10 @@ class Stage:
             if trainable_only and not p.trainable:
                 continue
             dt = p.dtype or dtype
-            per = -(-(-(-p.numel // world)) // 8) * 8
+            if p.expert_sharded:          # the local bank is this rank's own: stored whole
+                per = -(-p.numel // 8) * 8
+            else:
+                per = -(-(-(-p.numel // world)) // 8) * 8
             out.append((p, off, dt, per))
             off = _round_up(off + per * dt.itemsize, ALIGN)
         return out, off
@@ -134,6 +145,13 @@ class Stage:
                 t.fill_(1.0)
             elif p.init == "zeros":
                 t.zero_()
+            elif p.expert_sharded:
+                # draw the whole bank so that every rank consumes the same random stream
+                # and the union of the ranks' slices equals the single-rank model
+                full = torch.empty(p.global_shape, dtype=t.dtype if t.is_cuda else torch.float32,
+                                   device=t.device)
+                full.normal_(0.0, p.std, generator=generator)
+                t.copy_(full[p.expert_lo:p.expert_lo + p.shape[0]])
             elif t.is_cuda:
                 t.normal_(0.0, p.std, generator=generator)   # device generator, large models
             else:
@@ -495,10 +513,13 @@ class HeadLossStage(Stage):
 
 
 # ============================================================================ assembly
-def build_stages(cfg: DecoderConfig, objective=None, lora=None) -> list[Stage]:
+def build_stages(cfg: DecoderConfig, objective=None, lora=None,
+                 expert_parallel: tuple[int, int] | None = None) -> list[Stage]:
     """``objective`` selects what the head evaluates; ``lora`` adds low-rank adapters to
     every layer (which then run through the autograd-derived layer stage) and freezes
-    the embedding, the head and the base matrices unless ``lora.train_base``."""
+    the embedding, the head and the base matrices unless ``lora.train_base``.
+    ``expert_parallel = (ranks, rank)`` gives routed layers this rank's slice of the
+    expert banks."""
     base_trainable = lora is None or lora.train_base
     stages: list[Stage] = [EmbeddingStage("embed", cfg, trainable=base_trainable)]
     for i in range(cfg.n_layers):
@@ -506,7 +527,7 @@ def build_stages(cfg: DecoderConfig, objective=None, lora=None) -> list[Stage]:
         if kind == "deltanet" or cfg.is_moe or cfg.gated_attention or lora is not None:
             from .hybrid import make_layer
             coef = objective.moe_balance_coef if objective is not None and objective.moe_balance_coef > 0 else None
-            stages.append(make_layer(f"layer{i}", cfg, i, lora, coef))
+            stages.append(make_layer(f"layer{i}", cfg, i, lora, coef, expert_parallel))
         else:
             stages.append(DenseLayerStage(f"layer{i}", cfg))
     stages.append(HeadLossStage("head", cfg, objective=objective, trainable=base_trainable))

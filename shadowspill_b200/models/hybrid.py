@@ -30,10 +30,15 @@ class HybridLayerStage(Stage):
     kind = "layer"
     SAVE_SETS = {"recompute": ()}
 
-    def __init__(self, name: str, cfg: DecoderConfig, index: int, lora=None):
+    def __init__(self, name: str, cfg: DecoderConfig, index: int, lora=None,
+                 expert_parallel: tuple[int, int] | None = None):
         super().__init__(name, cfg)
         self.index = index
         self.lora = lora
+        self.ep_world, self.ep_rank = expert_parallel if (expert_parallel and cfg.is_moe) else (1, 0)
+        if cfg.is_moe and cfg.n_experts % self.ep_world:
+            raise ValueError("n_experts must be divisible by the expert-parallel ranks")
+        self.ep_group = None      # bound by the executor: symmetric workspace + barriers
         self.aux_coef = float(cfg.router_aux_coef)   # router balance term; 0 = off
         self._aux: list[torch.Tensor] = []           # this execution's balance term (autograd)
         self.aux_sum: torch.Tensor | None = None     # running sum of applied balance losses
@@ -62,9 +67,13 @@ class HybridLayerStage(Stage):
                   ParamSpec("w_out", (D, self.value_width), std=std)]
         P.append(ParamSpec("mlp_norm", (D,), init=norm_init))
         if c.is_moe:
+            el = c.n_experts // self.ep_world
+            ep = ({} if self.ep_world == 1 else {"expert_lo": self.ep_rank * el})
+            g13 = (c.n_experts, 2 * c.d_expert, D) if self.ep_world > 1 else None
+            g2 = (c.n_experts, D, c.d_expert) if self.ep_world > 1 else None
             P += [ParamSpec("router", (c.n_experts, D), std=std),
-                  ParamSpec("w13", (c.n_experts, 2 * c.d_expert, D), std=std),
-                  ParamSpec("w2", (c.n_experts, D, c.d_expert), std=std)]
+                  ParamSpec("w13", (el, 2 * c.d_expert, D), std=std, global_shape=g13, **ep),
+                  ParamSpec("w2", (el, D, c.d_expert), std=std, global_shape=g2, **ep)]
             if c.d_shared_expert:
                 P += [ParamSpec("sw13", (2 * c.d_shared_expert, D), std=std),
                       ParamSpec("sw2", (D, c.d_shared_expert), std=std)]
@@ -174,6 +183,21 @@ class HybridLayerStage(Stage):
                 counts = torch.bincount(top.reshape(-1), minlength=c.n_experts)
             self._aux.append(router_balance(torch.softmax(logits, -1).sum(0), counts, T, c.top_k))
         routed_lora = bool(self._adapted & {"w13", "w2"})
+        if self.ep_world > 1:
+            if not h.is_cuda or routed_lora:
+                raise NotImplementedError("expert parallelism runs on CUDA without routed adapters")
+            if self.ep_group is not None:
+                from ..parallel import expert_parallel as ep_ops
+                out = ep_ops.experts(h, logits, P["w13"], P["w2"], self.ep_group,
+                                     c.router_renormalize, sink)
+            else:
+                # unbound (task profiling on one rank): the local experts alone, same row count
+                from ..ops import moe as moe_ops
+                el = c.n_experts // self.ep_world
+                lo = self.ep_rank * el
+                out = moe_ops.experts(h, logits[:, lo:lo + el].contiguous(), P["w13"], P["w2"],
+                                      c.top_k, c.router_renormalize, sink)
+            return self._shared(P, L, h, sink, out)
         if h.is_cuda and not routed_lora:
             from ..ops import moe as moe_ops
             out = moe_ops.experts(h, logits, P["w13"], P["w2"], c.top_k, c.router_renormalize, sink)
@@ -307,8 +331,9 @@ class HybridLayerStage(Stage):
         return dy
 
 
-def make_layer(name: str, cfg: DecoderConfig, index: int, lora=None, aux_coef: float | None = None) -> Stage:
-    st = HybridLayerStage(name, cfg, index, lora)
+def make_layer(name: str, cfg: DecoderConfig, index: int, lora=None, aux_coef: float | None = None,
+               expert_parallel: tuple[int, int] | None = None) -> Stage:
+    st = HybridLayerStage(name, cfg, index, lora, expert_parallel)
     if aux_coef is not None and cfg.is_moe:
         st.aux_coef = float(aux_coef)
     return st

@@ -1,5 +1,5 @@
 """Plan report: ``index.html``, ``summary.json``, ``tasks.csv``, ``transfers.csv``,
-``timeline.json`` and an SVG timeline, all static files readable offline.
+``timeline.json``, ``occupancy.html`` and an SVG timeline, all static files readable offline.
 
 The file set and the summary fields follow the reference's ``write_report``
 (packages/engine/src/shadowspill/reporting/write.py:54,
@@ -58,6 +58,42 @@ def occupancy_series(plan: Plan) -> list[tuple[int, int]]:
     return out
 
 
+def _occupancy_page(plan: Plan, width: int = 1400, height: int = 360) -> str:
+    """Static page: device bytes held by planned stays over simulated time, against the
+    pool size and the budget, with the ten largest stays alive at the peak."""
+    series = occupancy_series(plan)
+    total_ns = max([t for t, _ in series] + [1])
+    cap = max([plan.device_bytes, plan.summary.logical_capacity_bytes or 0] + [v for _, v in series] + [1])
+    sx, sy = (width - 80) / total_ns, (height - 40) / cap
+    pts, level = [f"60,{height - 20}"], 0
+    for t, v in series:
+        x = 60 + t * sx
+        pts.append(f"{x:.1f},{height - 20 - level * sy:.1f}")
+        pts.append(f"{x:.1f},{height - 20 - v * sy:.1f}")
+        level = v
+    peak_t, peak = max(series, key=lambda p: p[1]) if series else (0, 0)
+    alive = sorted((s for s in plan.stays if s.start_ns <= peak_t < s.end_ns), key=lambda s: -s.bytes)[:10]
+    rows = "".join(f"<tr><td>{html.escape(plan.program.objects[s.object].name)}</td>"
+                   f"<td>{s.bytes / (1 << 20):.1f} MiB</td><td>{s.offset}</td>"
+                   f"<td>{s.start_ns / 1e6:.2f} - {s.end_ns / 1e6:.2f} ms</td></tr>" for s in alive)
+    line = lambda v, color, label: (
+        f'<line x1="60" x2="{width - 20}" y1="{height - 20 - v * sy:.1f}" y2="{height - 20 - v * sy:.1f}" '
+        f'stroke="{color}" stroke-dasharray="6 4"/><text x="64" y="{height - 24 - v * sy:.1f}" '
+        f'fill="{color}">{label} {v / GIB:.2f} GiB</text>')
+    svg = (f'<svg xmlns="http://www.w3.org/2000/svg" width="{width}" height="{height}" '
+           'font-family="monospace" font-size="11">'
+           f'<polyline fill="none" stroke="#4c78a8" stroke-width="1.5" points="{" ".join(pts)}"/>'
+           + line(plan.device_bytes, "#e45756", "device pool")
+           + f'<text x="60" y="{height - 4}">0 ms</text>'
+           f'<text x="{width - 90}" y="{height - 4}">{total_ns / 1e6:.0f} ms</text></svg>')
+    return ("<!doctype html><meta charset=utf-8><title>occupancy</title>"
+            "<style>body{font-family:sans-serif;margin:2em}td,th{padding:2px 12px;text-align:left}</style>"
+            f"<h1>Device occupancy</h1><p>peak {peak / GIB:.2f} GiB at {peak_t / 1e6:.1f} ms; "
+            f"pool {plan.device_bytes / GIB:.2f} GiB</p>{svg}"
+            "<h2>Largest stays alive at the peak</h2><table><tr><th>object</th><th>size</th>"
+            f"<th>offset</th><th>interval</th></tr>{rows}</table>")
+
+
 def write_report(plan: Plan, directory: str | Path) -> Path:
     d = Path(directory)
     d.mkdir(parents=True, exist_ok=True)
@@ -92,6 +128,7 @@ def write_report(plan: Plan, directory: str | Path) -> Path:
         "occupancy": occupancy_series(plan)}))
     svg = _timeline_svg(plan)
     (d / "timeline.svg").write_text(svg)
+    (d / "occupancy.html").write_text(_occupancy_page(plan))
     s = plan.summary
     rows = [("simulated step", f"{s.duration_seconds * 1e3:.1f} ms"),
             ("tokens / s (scheduled tokens)", f"{s.tokens_per_second:,.0f}"),
@@ -110,5 +147,6 @@ def write_report(plan: Plan, directory: str | Path) -> Path:
         "<!doctype html><meta charset=utf-8><title>plan report</title>"
         "<style>body{font-family:sans-serif;margin:2em}td,th{padding:2px 12px}</style>"
         f"<h1>Plan report</h1><table>{body}</table><h2>Timeline</h2>{svg}"
-        "<p>Files: summary.json, tasks.csv, transfers.csv, timeline.json, timeline.svg</p>")
+        "<p>Files: summary.json, tasks.csv, transfers.csv, timeline.json, timeline.svg, "
+        "<a href=occupancy.html>occupancy.html</a></p>")
     return d / "index.html"

@@ -28,3 +28,12 @@ def test_two_ranks_gloo_match_resident():
 @pytest.mark.parametrize("arm", ["peer", "dist"])
 def test_two_gpus_match_resident(arm):
     _launch(2, "cuda", arm, 29613 if arm == "peer" else 29615)
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_two_gpus_expert_parallel_planned_execution():
+    """A routed model trains through the planned executor with its experts split over two
+    GPUs (peer-memory dispatch/combine inside the layer tasks) and matches the resident
+    single-process model that holds every expert."""
+    _launch(2, "cuda", "ep", 29617)
