@@ -206,7 +206,9 @@ def _build(desc: TrainingDescription) -> Program:
         tag += f":{desc.objective.kind}"
 
     def key(st: Stage, what: str, var: str = "") -> str:
-        return f"{cfg.family}:{st.kind}:{type(st).__name__}:{what}:{var}:T{T}{tag}"
+        # layers of one class can differ in kind (DeltaNet or attention mixer): keep them apart
+        kind = getattr(st, "mixer", "")
+        return f"{cfg.family}:{st.kind}:{type(st).__name__}{':' + kind if kind else ''}:{what}:{var}:T{T}{tag}"
 
     def params_of(si: int, which: str) -> int:
         """The object a compute task reads its weights from; under sharded storage

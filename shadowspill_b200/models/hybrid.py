@@ -165,7 +165,7 @@ class HybridLayerStage(Stage):
         v = conv[:, 2 * self.key_width:].reshape(T, Hv, dk)
         beta = torch.sigmoid(ba[:, :Hv].float())
         g = -torch.exp(L["A_log"].float()) * TF.softplus(ba[:, Hv:].float() + L["dt_bias"].float())
-        mixed = seq_ops.gated_delta_rule_chunked(q, k, v, beta, g, bounds, c.dn_chunk)
+        mixed = seq_ops.gated_delta_rule_chunked(q, k, v, beta, g, bounds, c.dn_chunk, meta.cu_seqlens)
         gate = qkvz[:, self.conv_width:].reshape(T, Hv, dk)
         normed = seq_ops.gated_rmsnorm(mixed, gate, P["lin_norm_leaf"], c.norm_epsilon,
                                        c.zero_centered_norm)
@@ -290,7 +290,7 @@ class HybridLayerStage(Stage):
 
     # ---- stage interface
     def forward(self, P, x, meta: BatchMeta, keep=(), out=None):
-        bounds = meta.cu_seqlens.tolist() if self.mixer == "deltanet" else None
+        bounds = meta.cu_seqlens.tolist() if (self.mixer == "deltanet" and not x.is_cuda) else None
         with torch.no_grad():
             P2, L = self._leaves(P, False)
             y = self._layer(P2, L, x, meta, None, bounds)
@@ -300,7 +300,7 @@ class HybridLayerStage(Stage):
         return y, {}
 
     def backward(self, P, G, x, dy, meta: BatchMeta, saved, first: bool):
-        bounds = meta.cu_seqlens.tolist() if self.mixer == "deltanet" else None
+        bounds = meta.cu_seqlens.tolist() if (self.mixer == "deltanet" and not x.is_cuda) else None
         sink = A.GradSink(G, first)
         if first and not x.is_cuda:
             for name in self._banks:          # experts without tokens still need defined gradients

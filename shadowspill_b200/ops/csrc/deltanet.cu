@@ -333,3 +333,84 @@ int ss_gated_rmsnorm_bwd(const void* x, const void* gate, const void* w, const v
   return (int)cudaGetLastError();
 }
 }  // extern "C"
+
+// ============================================================================ chunk-state scan
+// The only sequential part of the chunked gated delta rule: a linear recurrence over the
+// chunk index for every head,
+//     X_{c+1} = op(A_c) X_c + B_c,        X_0 = 0,        out[c] = X_c   (the state ENTERING c)
+// with A_c [dk, dk], B_c / X [dk, dv] fp32. Columns of X evolve independently, so a block owns
+// one head and 32 columns. `reverse` walks c = n-1 .. 0 and `transpose` uses A_c^T, which is the
+// adjoint recurrence of the backward pass (out[c] = gradient reaching the state LEAVING c).
+// Everything that is parallel over chunks (building A and B, outputs, their gradients) is batched
+// matrix algebra outside this kernel.
+namespace ss_dn {
+
+constexpr int SCAN_COLS = 32;
+constexpr int SCAN_THREADS = 256;
+
+__global__ void __launch_bounds__(SCAN_THREADS)
+linear_scan_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ out,
+                   int n, int H, int dk, int dv, int reverse, int transpose) {
+  extern __shared__ float sm[];
+  const int lda = dk + 4;                       // padded rows: no bank conflicts on row reads
+  float* As = sm;                               // [dk][lda]
+  float* X = As + dk * lda;                     // [dk][SCAN_COLS]
+  float* Xn = X + dk * SCAN_COLS;
+  const int slices = dv / SCAN_COLS;
+  const int h = blockIdx.x / slices, col0 = (blockIdx.x % slices) * SCAN_COLS;
+  const int tid = threadIdx.x;
+  const int tx = tid & 7, ty = tid >> 3;        // 4 columns each, rows ty + 32*r
+  for (int i = tid; i < dk * SCAN_COLS; i += SCAN_THREADS) X[i] = 0.f;
+  __syncthreads();
+  for (int s = 0; s < n; ++s) {
+    const int c = reverse ? n - 1 - s : s;
+    const long long mat = (static_cast<long long>(c) * H + h);
+    const float* Ac = A + mat * dk * dk;
+    const float* Bc = B + mat * dk * dv;
+    float* oc = out + mat * dk * dv;
+    for (int i = tid * 4; i < dk * dk; i += SCAN_THREADS * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(Ac + i);
+      const int r = i / dk, cc = i - r * dk;
+      *reinterpret_cast<float4*>(As + r * lda + cc) = v;
+    }
+    // the state entering this step is an output
+    for (int i = tid; i < dk * SCAN_COLS; i += SCAN_THREADS) {
+      const int r = i / SCAN_COLS, cc = i - r * SCAN_COLS;
+      oc[static_cast<long long>(r) * dv + col0 + cc] = X[i];
+    }
+    __syncthreads();
+    for (int r0 = ty; r0 < dk; r0 += 32) {
+      const float4 b = *reinterpret_cast<const float4*>(Bc + static_cast<long long>(r0) * dv + col0 + tx * 4);
+      float a0 = b.x, a1 = b.y, a2 = b.z, a3 = b.w;
+#pragma unroll 4
+      for (int m = 0; m < dk; ++m) {
+        const float a = transpose ? As[m * lda + r0] : As[r0 * lda + m];
+        const float4 x = *reinterpret_cast<const float4*>(X + m * SCAN_COLS + tx * 4);
+        a0 += a * x.x; a1 += a * x.y; a2 += a * x.z; a3 += a * x.w;
+      }
+      *reinterpret_cast<float4*>(Xn + r0 * SCAN_COLS + tx * 4) = make_float4(a0, a1, a2, a3);
+    }
+    __syncthreads();
+    float* t = X; X = Xn; Xn = t;
+  }
+}
+
+}  // namespace ss_dn
+
+extern "C" int ss_linear_scan(const float* A, const float* B, float* out, int n, int H, int dk, int dv,
+                              int reverse, int transpose, void* stream) {
+  using namespace ss_dn;
+  if (dk % 4 || dk > 128 || dv % SCAN_COLS || n < 0) return -2;
+  if (n == 0 || H == 0) return 0;
+  const int smem = sizeof(float) * (dk * (dk + 4) + 2 * dk * SCAN_COLS);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(linear_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)sizeof(float) * (128 * 132 + 2 * 128 * SCAN_COLS));
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  linear_scan_kernel<<<H * (dv / SCAN_COLS), SCAN_THREADS, smem, (cudaStream_t)stream>>>(
+      A, B, out, n, H, dk, dv, reverse, transpose);
+  return (int)cudaGetLastError();
+}

@@ -156,58 +156,112 @@ def causal_conv_silu(x: torch.Tensor, w: torch.Tensor, bounds: list[int],
     return TF.silu(y).to(x.dtype)
 
 
-def _chunk_sequence(q, k, v, beta, g, C):
-    """One sequence, heads batched. q,k [L,H,dk] fp32 (q pre-scaled), v [L,H,dv], beta,g [L,H]."""
-    L, H, dk = q.shape
-    dv = v.shape[-1]
-    n = -(-L // C)
-    pad = n * C - L
-    if pad:
-        zp = lambda t: TF.pad(t, (0, 0) * (t.dim() - 1) + (0, pad))
-        q, k, v, beta, g = zp(q), zp(k), zp(v), zp(beta), zp(g)
-    # [n, H, C, ...]
-    rs = lambda t: t.reshape(n, C, H, -1).permute(0, 2, 1, 3)
-    q, k, v = rs(q), rs(k), rs(v)
-    beta = beta.reshape(n, C, H).permute(0, 2, 1)
-    gam = g.reshape(n, C, H).permute(0, 2, 1).cumsum(-1)            # log G_t
-    ratio = torch.exp((gam[..., :, None] - gam[..., None, :]).clamp(max=0.0))   # G_t/G_i, i<=t
-    lower = torch.ones(C, C, device=q.device, dtype=torch.bool).tril()
-    strict = lower & ~torch.eye(C, device=q.device, dtype=torch.bool)
-    kk = k @ k.transpose(-1, -2)
-    A = (beta[..., :, None] * ratio * kk).masked_fill(~strict, 0.0)
-    eye = torch.eye(C, device=q.device, dtype=q.dtype).expand(n, H, C, C)
-    Tm = torch.linalg.solve_triangular(eye + A, eye, upper=False)
-    Gt = torch.exp(gam)[..., None]                                   # G_t
-    W = Tm @ (beta[..., None] * Gt * k)                              # [n,H,C,dk]
-    U0 = Tm @ (beta[..., None] * v)                                  # [n,H,C,dv]
-    M = (ratio * (q @ k.transpose(-1, -2))).masked_fill(~lower, 0.0)
-    Qg = Gt * q
-    Gc = torch.exp(gam[..., -1])[..., None, None]                    # G_C
-    Kd = torch.exp(gam[..., -1:] - gam)[..., None] * k               # (G_C/G_i) k_i
-    S = q.new_zeros(H, dk, dv)
-    outs = []
-    for c in range(n):
-        U = U0[c] - W[c] @ S
-        outs.append(Qg[c] @ S + M[c] @ U)
-        S = Gc[c] * S + Kd[c].transpose(-1, -2) @ U
-    out = torch.stack(outs, 0).permute(0, 2, 1, 3).reshape(n * C, H, dv)
-    return out[:L]
+class _LinearScan(torch.autograd.Function):
+    """``S_{c+1} = A_c S_c + B_c`` over the chunk axis, ``S_0 = 0``; returns the state entering
+    every chunk. ``A`` [n,H,dk,dk], ``B`` [n,H,dk,dv] fp32. The backward pass is the adjoint
+    recurrence (same kernel, transposed and reversed) plus two batched products."""
+
+    @staticmethod
+    def run(A, B, reverse: bool, transpose: bool):
+        n, H, dk, dv = B.shape
+        out = torch.empty_like(B)
+        if A.is_cuda and dv % 32 == 0 and dk % 4 == 0 and dk <= 128:
+            _lib.check(_lib.lib().ss_linear_scan(A.data_ptr(), B.data_ptr(), out.data_ptr(), n, H, dk, dv,
+                                                 int(reverse), int(transpose), _lib.stream_ptr()),
+                       "ss_linear_scan")
+            return out
+        X = B.new_zeros(H, dk, dv)
+        for s in range(n):
+            c = n - 1 - s if reverse else s
+            out[c] = X
+            Ac = A[c].transpose(-1, -2) if transpose else A[c]
+            X = Ac @ X + B[c]
+        return out
+
+    @staticmethod
+    def forward(ctx, A, B):
+        A, B = A.contiguous(), B.contiguous()
+        S = _LinearScan.run(A, B, False, False)
+        ctx.save_for_backward(A, S)
+        return S
+
+    @staticmethod
+    def backward(ctx, dS):
+        A, S = ctx.saved_tensors
+        lam = _LinearScan.run(A, dS.contiguous(), True, True)     # gradient reaching S_{c+1}
+        return lam @ S.transpose(-1, -2), lam
 
 
-def gated_delta_rule_chunked(q, k, v, beta, g, bounds: list[int], chunk: int = 64) -> torch.Tensor:
+_lib.register("ss_linear_scan", [_c.c_p, _c.c_p, _c.c_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                                 _c.c_int, _c.c_p])
+
+
+def gated_delta_rule_chunked(q, k, v, beta, g, bounds: list[int] | None, chunk: int = 64,
+                             cu_seqlens: torch.Tensor | None = None) -> torch.Tensor:
     """q,k [T,Hk,dk] (L2-normalised), v [T,Hv,dv], beta,g [T,Hv] (g = log decay <= 0).
-    QK heads are repeat-interleaved to the V heads. Returns [T,Hv,dv] in ``v.dtype``."""
-    Hk, dk = q.shape[1], q.shape[2]
-    Hv = v.shape[1]
-    rep = Hv // Hk
+    QK heads are repeat-interleaved to the V heads. Returns [T,Hv,dv] in ``v.dtype``.
+
+    The packed stream is cut into chunks of ``chunk`` tokens regardless of where sequences
+    begin; sequence boundaries act through masks (no decay path and no state carry across a
+    boundary), so the work and the memory are the same for every packing and there is no
+    loop over sequences. Sequence ids come from ``cu_seqlens`` on the device (no host read)
+    or from ``bounds``."""
+    T, Hk, dk = q.shape
+    H, dv = v.shape[1], v.shape[2]
+    rep = H // Hk
+    C = chunk
+    n = -(-T // C)
+    pad = n * C - T
+    dev = q.device
+    pos = torch.arange(T, device=dev)
+    if cu_seqlens is not None:
+        sid = torch.bucketize(pos, cu_seqlens[1:].to(torch.long), right=True)
+    else:
+        sid = torch.bucketize(pos, torch.tensor(list(bounds[1:]), device=dev, dtype=torch.long), right=True)
     qf = q.float().repeat_interleave(rep, dim=1) * dk ** -0.5
     kf = k.float().repeat_interleave(rep, dim=1)
     vf, bf, gf = v.float(), beta.float(), g.float()
-    pieces = []
-    for s, e in zip(bounds[:-1], bounds[1:]):
-        if e > s:
-            pieces.append(_chunk_sequence(qf[s:e], kf[s:e], vf[s:e], bf[s:e], gf[s:e], chunk))
-    return torch.cat(pieces, 0).to(v.dtype)
+    if pad:
+        zp = lambda t: TF.pad(t, (0, 0) * (t.dim() - 1) + (0, pad))
+        qf, kf, vf, bf, gf = zp(qf), zp(kf), zp(vf), zp(bf), zp(gf)
+        sid = torch.cat([sid, sid.new_full((pad,), int(2 ** 31 - 1))])    # padding is its own sequence
+    rs = lambda t: t.reshape(n, C, H, -1).permute(0, 2, 1, 3)            # [n,H,C,*]
+    qc, kc, vc = rs(qf), rs(kf), rs(vf)
+    bc = bf.reshape(n, C, H).permute(0, 2, 1)                           # [n,H,C]
+    gam = gf.reshape(n, C, H).permute(0, 2, 1).cumsum(-1)               # log of the running decay
+    sidc = sid.reshape(n, C)
+    same = sidc[:, :, None] == sidc[:, None, :]                         # [n,C,C]
+    prev_last = torch.cat([sidc.new_full((1,), -1), sidc[:-1, -1]])
+    first_seg = (sidc == prev_last[:, None])                            # continues the previous chunk
+    last_seg = (sidc == sidc[:, -1:])                                   # same sequence as the chunk's end
+    lower = torch.ones(C, C, device=dev, dtype=torch.bool).tril()
+    valid = (same & lower)[:, None]                                     # [n,1,C,C]
+    diff = gam[..., :, None] - gam[..., None, :]
+    ratio = torch.exp(diff.masked_fill(~valid, float("-inf")))          # G_t/G_i inside one sequence
+    strict = ~torch.eye(C, device=dev, dtype=torch.bool)
+    tf32 = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False                       # the triangular system is fp32
+    try:
+        A = bc[..., :, None] * ratio * (kc @ kc.transpose(-1, -2)) * strict
+        eye = torch.eye(C, device=dev, dtype=qf.dtype).expand(n, H, C, C)
+        Tm = torch.linalg.solve_triangular(eye + A, eye, upper=False)
+        Gt = torch.exp(gam) * first_seg[:, None, :]                     # decay from the carried state
+        W = Tm @ (bc[..., None] * Gt[..., None] * kc)                   # [n,H,C,dk]
+        U0 = Tm @ (bc[..., None] * vc)                                  # [n,H,C,dv]
+        M = ratio * (qc @ kc.transpose(-1, -2))
+        Qg = Gt[..., None] * qc
+        Gc = torch.exp(gam[..., -1]) * first_seg[:, -1][:, None]        # [n,H]
+        Kd = (torch.exp(gam[..., -1:] - gam) * last_seg[:, None, :])[..., None] * kc
+        KdT = Kd.transpose(-1, -2)
+        Amat = Gc[..., None, None] * torch.eye(dk, device=dev, dtype=qf.dtype) - KdT @ W
+        Bmat = KdT @ U0
+        S = _LinearScan.apply(Amat, Bmat)                               # state entering each chunk
+        U = U0 - W @ S
+        out = Qg @ S + M @ U
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = tf32
+    out = out.permute(0, 2, 1, 3).reshape(n * C, H, dv)
+    return out[:T].to(v.dtype)
 
 
 def gated_rmsnorm(x: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, eps: float,

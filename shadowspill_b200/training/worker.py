@@ -13,6 +13,12 @@ loop.py:71-181, protocol.py}.
 """
 from __future__ import annotations
 
+import os as _os
+
+# task workspaces come from the caching allocator under a hard cap: expandable segments keep
+# fragmentation from turning a fitting plan into an allocation failure
+_os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+
 import argparse
 import os
 import sys

@@ -76,3 +76,37 @@ def test_gated_rmsnorm_forward_backward(zero_centered):
     assert _rel(y, want) < 6e-3
     assert _rel(xk.grad, xr.grad) < 1.5e-2 and _rel(gk.grad, gr.grad) < 1.5e-2
     assert _rel(wk.grad, wr.grad) < 1.5e-2
+
+
+def test_linear_scan_kernel_matches_loop():
+    torch.manual_seed(0)
+    n, H, dk, dv = 9, 5, 64, 64
+    A = torch.randn(n, H, dk, dk, device="cuda") * 0.1
+    B = torch.randn(n, H, dk, dv, device="cuda")
+    for reverse, transpose in ((False, False), (True, True)):
+        got = seq._LinearScan.run(A, B, reverse, transpose)
+        want = seq._LinearScan.run(A.cpu(), B.cpu(), reverse, transpose)
+        assert _rel(got.cpu(), want) < 1e-5
+
+
+def test_gated_delta_rule_on_gpu_matches_token_recurrence():
+    from shadowspill_b200.ops import reference as ref
+    torch.manual_seed(1)
+    T, Hk, Hv, dk = 704, 2, 4, 64
+    bounds = [0, 5, 300, 301, 640, 704]
+    q = seq.l2_normalize(torch.randn(T, Hk, dk))
+    k = seq.l2_normalize(torch.randn(T, Hk, dk))
+    v = torch.randn(T, Hv, dk)
+    beta = torch.sigmoid(torch.randn(T, Hv))
+    g = -torch.nn.functional.softplus(torch.randn(T, Hv)) * 0.3
+    cu = torch.tensor(bounds + [T] * 4, dtype=torch.int32)
+    dout = torch.randn(T, Hv, dk)
+    cpu = [t.clone().requires_grad_(True) for t in (q, k, v, beta, g)]
+    want = ref.gated_delta_rule(*cpu, torch.tensor(bounds))
+    want.backward(dout)
+    dev = [t.clone().cuda().requires_grad_(True) for t in (q, k, v, beta, g)]
+    got = seq.gated_delta_rule_chunked(*dev, None, 64, cu_seqlens=cu.cuda())
+    got.backward(dout.cuda())
+    assert _rel(got.cpu(), want) < 2e-4
+    for name, a, b in zip("q k v beta g".split(), dev, cpu):
+        assert _rel(a.grad.cpu(), b.grad) < 2e-3, name
