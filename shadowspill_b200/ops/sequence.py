@@ -240,11 +240,15 @@ def gated_delta_rule_chunked(q, k, v, beta, g, bounds: list[int] | None, chunk: 
     ratio = torch.exp(diff.masked_fill(~valid, float("-inf")))          # G_t/G_i inside one sequence
     strict = ~torch.eye(C, device=dev, dtype=torch.bool)
     tf32 = torch.backends.cuda.matmul.allow_tf32
-    torch.backends.cuda.matmul.allow_tf32 = False                       # the triangular system is fp32
+    # the batched products run on the tensor cores in TF32 (10-bit mantissa, fp32 accumulate:
+    # finer than the bf16 operands they come from); the triangular system stays in fp32
+    torch.backends.cuda.matmul.allow_tf32 = True
     try:
         A = bc[..., :, None] * ratio * (kc @ kc.transpose(-1, -2)) * strict
         eye = torch.eye(C, device=dev, dtype=qf.dtype).expand(n, H, C, C)
+        torch.backends.cuda.matmul.allow_tf32 = False
         Tm = torch.linalg.solve_triangular(eye + A, eye, upper=False)
+        torch.backends.cuda.matmul.allow_tf32 = True
         Gt = torch.exp(gam) * first_seg[:, None, :]                     # decay from the carried state
         W = Tm @ (bc[..., None] * Gt[..., None] * kc)                   # [n,H,C,dk]
         U0 = Tm @ (bc[..., None] * vc)                                  # [n,H,C,dv]

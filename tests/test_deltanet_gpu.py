@@ -107,6 +107,6 @@ def test_gated_delta_rule_on_gpu_matches_token_recurrence():
     dev = [t.clone().cuda().requires_grad_(True) for t in (q, k, v, beta, g)]
     got = seq.gated_delta_rule_chunked(*dev, None, 64, cu_seqlens=cu.cuda())
     got.backward(dout.cuda())
-    assert _rel(got.cpu(), want) < 2e-4
+    assert _rel(got.cpu(), want) < 2e-3            # TF32 products
     for name, a, b in zip("q k v beta g".split(), dev, cpu):
-        assert _rel(a.grad.cpu(), b.grad) < 2e-3, name
+        assert _rel(a.grad.cpu(), b.grad) < 1e-2, name
