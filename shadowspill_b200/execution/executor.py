@@ -102,7 +102,11 @@ class TaskRunner:
         out: dict[str, object] = {}
         for u, flat in zip(self.uses[task], flats):
             obj = self.program.objects[u.object]
-            if u.role in ("params", "m", "v", "shard"):
+            if u.role == "tied_params":
+                out[u.role] = self.stages[0].views(flat, self.desc.dtype)
+            elif u.role == "tied_grads":
+                out[u.role] = self.stages[0].views(flat, self.desc.grad_dtype, torch.float32, True)
+            elif u.role in ("params", "m", "v", "shard"):
                 only = u.role in ("m", "v")       # moments exist for trainable parameters only
                 if obj.sharding == "sharded":
                     out[u.role] = st.shard_views(flat, self.desc.dtype, self.world, only)
@@ -145,8 +149,16 @@ class TaskRunner:
         elif t.kind == "head":
             train = t.variant == "train"
             first = self._first(t.stage, B)
+            tied = None
+            if "tied_params" in B:
+                if self.desc.mode == "step":
+                    tied_first = B.get("tied_grads.mode") == "create"
+                else:   # accumulation driven from outside: fresh on the first contribution
+                    tied_first = self.accumulated == 0 and 0 not in self.grad_seen
+                    self.grad_seen.add(0)
+                tied = {"params": B["tied_params"], "grads": B.get("tied_grads"), "first": tied_first}
             st.loss_and_backward(B["params"], B.get("grads"), B["x"], meta, B["loss"], first,
-                                 dx=B.get("dx"), train=train, grad_scale=1.0)
+                                 dx=B.get("dx"), train=train, grad_scale=1.0, tied=tied)
         elif t.kind == "backward":
             first = self._first(t.stage, B)
             saved = dict(B["saved"]) if "saved" in B else {}

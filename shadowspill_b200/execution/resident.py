@@ -63,15 +63,19 @@ class ResidentTrainer:
             x, _ = st.forward(self.P[i], x, meta, ())
             xs.append(x)
         head: HeadLossStage = self.stages[-1]
+        tied = ({"params": self.P[0], "grads": self.G[0] if train else None, "first": first}
+                if self.cfg.tied_embeddings else None)
         dx = head.loss_and_backward(self.P[-1], self.G[-1], x, meta, self.loss_sum, first,
-                                    train=train)
+                                    train=train, tied=tied)
         if not train:
             return
         for i in range(len(body) - 1, -1, -1):
             st = body[i]
             if i == 0 and not st.has_trainable:
                 break
-            dx = st.backward(self.P[i], self.G[i], xs[i], dx, meta, {}, first)
+            # with tied embeddings the head has already started the embedding's gradient
+            create = first and not (i == 0 and self.cfg.tied_embeddings)
+            dx = st.backward(self.P[i], self.G[i], xs[i], dx, meta, {}, create)
         self._accum += 1
 
     def optim_step(self, grad_scale: float = 1.0) -> None:

@@ -247,6 +247,14 @@ def _build(desc: TrainingDescription) -> Program:
         si, st = S - 1, stages[S - 1]
         uses = [UseSpec(params_of(si, "fwd"), "read", "params"), UseSpec(IN[m], "read", "batch"),
                 UseSpec(A[si - 1][m], "read", "x"), UseSpec(LOSS, "mutate", "loss")]
+        if cfg.tied_embeddings:
+            # the output matrix is the embedding: read it here, and start (or add to) its gradient
+            uses.append(UseSpec(params_of(0, "fwd"), "read", "tied_params"))
+            if train and stages[0].has_trainable:
+                if desc.mode == "step" and not grad_created[0]:
+                    uses.append(UseSpec(G[0], "create", "tied_grads")); grad_created[0] = True
+                else:
+                    uses.append(UseSpec(G[0], "mutate", "tied_grads"))
         if train:
             uses.append(UseSpec(DX[m], "create", "dx"))
             if not st.has_trainable:

@@ -113,6 +113,7 @@ PRESETS: dict[str, DecoderConfig] = {
     # ---- Qwen 3.5: 3 Gated DeltaNet : 1 gated full attention
     "qwen35-tiny": _qwen35(2, 128, 4, 2, 32, 256, 2, 4, vocab=512, interval=2, dnhd=32),
     "qwen35-numerical": _qwen35(8, 1536, 12, 4, 128, 4608, 6, 12),
+    "qwen35-2b": _qwen35(24, 2048, 8, 2, 256, 6144, 16, 16, tied_embeddings=True),
     "qwen35-9b": _qwen35(32, 4096, 16, 4, 256, 12288, 16, 32),
     "qwen35-27b": _qwen35(64, 5120, 24, 4, 256, 17408, 16, 48),
     # ---- OLMoE: GQA + routed SwiGLU experts

@@ -461,19 +461,30 @@ class HeadLossStage(Stage):
 
     def loss_and_backward(self, P, G, x, meta: BatchMeta, loss_sum: torch.Tensor, first: bool,
                           dx: torch.Tensor | None = None, train: bool = True,
-                          grad_scale: float = 1.0):
+                          grad_scale: float = 1.0, tied: dict | None = None):
         """Adds this microbatch's weighted loss into ``loss_sum`` (fp32[1]); when
-        ``train``, accumulates parameter gradients and returns ``dx``."""
+        ``train``, accumulates parameter gradients and returns ``dx``. With tied
+        embeddings the output matrix is the embedding: ``tied = {"params": embedding
+        views, "grads": embedding gradient views or None, "first": bool}`` and the
+        head's weight gradient is accumulated into the embedding's."""
         c = self.cfg
         T = x.shape[0]
-        W = P["head"]
+        if c.tied_embeddings:
+            W = tied["params"]["embed"]
+            Gw = tied.get("grads")
+            Gw = Gw["embed"] if Gw else None
+            w_first = bool(tied.get("first", False))
+        else:
+            W = P["head"]
+            Gw = G["head"] if (G and "head" in G) else None
+            w_first = first
         h, rstd = F.rmsnorm_fwd(x, P["final_norm"], c.norm_epsilon, c.zero_centered_norm)
         dh = torch.empty_like(h) if train else None
-        frozen = not G or "head" not in G
+        frozen = not G or "final_norm" not in G
         if train and first and not frozen:
             G["final_norm"].zero_()
         B = self.block_rows
-        acc = not first
+        acc = not w_first
         ob, X = self.objective, meta.extras
         for r0 in range(0, T, B):
             r1 = min(T, r0 + B)
@@ -488,8 +499,8 @@ class HeadLossStage(Stage):
                 F.cross_entropy_(logits, meta.targets[r0:r1], meta.weights[r0:r1], loss_sum,
                                  grad_scale=grad_scale, write_grad=train)
             if train:
-                if not frozen:
-                    F.linear_wgrad(logits, h[r0:r1], out=G["head"], accumulate=acc)
+                if Gw is not None:
+                    F.linear_wgrad(logits, h[r0:r1], out=Gw, accumulate=acc)
                 F.linear_dgrad(logits, W, out=dh[r0:r1])
                 acc = True
             del logits
@@ -500,10 +511,12 @@ class HeadLossStage(Stage):
         return F.rmsnorm_bwd(x, P["final_norm"], dh, rstd, dw, c.zero_centered_norm,
                              dx=dx, accumulate=False)
 
-    def target_logprobs(self, P, x, meta: BatchMeta) -> torch.Tensor:
+    def target_logprobs(self, P, x, meta: BatchMeta, tied: dict | None = None) -> torch.Tensor:
         """log p(target) for every token (fp32 [T]), in the same row blocks."""
         c = self.cfg
         T = x.shape[0]
+        if c.tied_embeddings:
+            P = dict(P, head=tied["params"]["embed"])
         h, _ = F.rmsnorm_fwd(x, P["final_norm"], c.norm_epsilon, c.zero_centered_norm)
         out = torch.empty(T, dtype=torch.float32, device=x.device)
         for r0 in range(0, T, self.block_rows):

@@ -81,7 +81,8 @@ def loss(cfg: DecoderConfig, params: dict[str, torch.Tensor], meta: BatchMeta) -
         x = dense_layer(cfg, stage(f"layer{i}"), x, meta)
     hp = stage("head")
     h = _rms(x, hp["final_norm"], cfg.norm_epsilon, cfg.zero_centered_norm)
-    logits = (h @ hp["head"].t()).float()
+    out_w = stage("embed")["embed"] if cfg.tied_embeddings else hp["head"]
+    logits = (h @ out_w.t()).float()
     lse = torch.logsumexp(logits, -1)
     tgt = meta.targets.clamp(min=0)
     picked = logits.gather(1, tgt[:, None])[:, 0]
@@ -182,7 +183,8 @@ def model_loss(cfg: DecoderConfig, params: dict[str, torch.Tensor], meta: BatchM
             else hybrid_layer(cfg, P, x, meta, i)
     hp = stage("head")
     h = _rms(x, hp["final_norm"], cfg.norm_epsilon, cfg.zero_centered_norm)
-    logits = (h @ hp["head"].t()).float()
+    out_w = stage("embed")["embed"] if cfg.tied_embeddings else hp["head"]
+    logits = (h @ out_w.t()).float()
     lse = torch.logsumexp(logits, -1)
     tgt = meta.targets.clamp(min=0)
     picked = logits.gather(1, tgt[:, None])[:, 0]
