@@ -260,6 +260,10 @@ class Executor:
             else:
                 coll = pc.DistCollectives()
         self.collectives = coll
+        if self.world > 1:
+            # refuse to start if the ranks would not issue the same collectives in the same order
+            pc.check_collective_order({"main": plan.program,
+                                       **{op: p.program for op, (p, _) in extra_plans.items()}})
         self.runner = TaskRunner(plan.program, desc, self.hyper, seed, stochastic_rounding, coll)
         self.stages = self.runner.stages
         self.ep_group = None

@@ -148,3 +148,43 @@ class PeerCollectives:
 def allocate_symmetric_pool(nbytes: int, device: torch.device) -> torch.Tensor:
     import torch.distributed._symmetric_memory as symm_mem
     return symm_mem.empty(int(nbytes), dtype=torch.uint8, device=device)
+
+
+def collective_sequence_digest(program) -> str:
+    """SHA-256 over the ordered collective work of a program: every task that runs a
+    collective (gathers, sharded optimizer updates, expert-parallel layers) with the sizes
+    of the objects it touches. Ranks whose digests differ would deadlock or corrupt data."""
+    import hashlib
+    h = hashlib.sha256()
+    for t in program.tasks:
+        if t.kind == "collective" or t.variant == "adamw_dp" or ":ep" in (t.profile_key or ""):
+            sizes = ",".join(str(program.objects[u.object].bytes) for u in t.uses)
+            h.update(f"{t.name}|{t.kind}|{t.variant}|{sizes};".encode())
+    return h.hexdigest()
+
+
+def check_collective_order(programs: dict[str, object], group=None) -> None:
+    """Every rank must be about to run the same collectives in the same order for each
+    operation's plan: compared before any collective is issued (reference:
+    packages/engine/src/shadowspill/execution/distributed/sequence.py:42-78)."""
+    world = dist.get_world_size(group)
+    mine = {op: collective_sequence_digest(p) for op, p in sorted(programs.items())}
+    everyone: list = [None] * world
+    dist.all_gather_object(everyone, mine, group=group)
+    for r, other in enumerate(everyone):
+        if other != mine:
+            bad = sorted(op for op in set(mine) | set(other) if mine.get(op) != other.get(op))
+            raise RuntimeError(f"collective sequence of {bad} differs between rank "
+                               f"{dist.get_rank(group)} and rank {r}; refusing to execute")
+
+
+def backend_identity() -> dict:
+    """What the collective calibration is valid for: library versions and the NCCL_* environment."""
+    import os
+    out = {"torch": torch.__version__, "backend": dist.get_backend() if dist.is_initialized() else "",
+           "env": {k: v for k, v in sorted(os.environ.items()) if k.startswith("NCCL_")}}
+    try:
+        out["nccl"] = ".".join(str(x) for x in torch.cuda.nccl.version())
+    except Exception:  # noqa: BLE001
+        out["nccl"] = ""
+    return out

@@ -75,3 +75,21 @@ def test_client_records_convert():
     assert p.world_size == 8 and p.default_parameter_storage.optimizer == "sharded"
     e = from_client_record(client_par.expert_parallel(4, n_experts=32, top_k=4))
     assert e.resolve("layer0.experts.w2", 1, 1 << 30).compute_shards == 4
+
+
+def test_collective_sequence_digest_is_rank_invariant_and_order_sensitive():
+    import torch
+    from dataclasses import replace
+    from shadowspill_b200.frontend.capture import BatchGeometry, StepDataOrdering, build_step
+    from shadowspill_b200.models.config import preset
+    from shadowspill_b200.parallel.collectives import collective_sequence_digest
+    cfg = preset("llama3-tiny")
+    geo = BatchGeometry(microbatch_tokens=256, n_microbatches=2, slots=16, mean_seqlen=64)
+    build = lambda c, rank, order=StepDataOrdering(): build_step(c, geo, order, dtype=torch.float32,
+                                                                  world_size=2, rank=rank)[0]
+    a, b = collective_sequence_digest(build(cfg, 0)), collective_sequence_digest(build(cfg, 1))
+    assert a == b                                             # every rank of one job agrees
+    deeper = replace(cfg, n_layers=3)
+    assert collective_sequence_digest(build(deeper, 0)) != a  # another model: another sequence
+    depth = StepDataOrdering(walk="depth", optimizer="tail")
+    assert collective_sequence_digest(build(cfg, 0, depth)) != a
