@@ -1,0 +1,152 @@
+"""Qualification gates: ``python -m shadowspill_b200.qualification.gates [numerical] [performance]``.
+
+numerical    planned bf16 execution on the GPU (fp32 on CPU) against an independent resident
+             trainer on the same data: 5 updates of 2 heterogeneous microbatches, a checkpoint
+             saved at update 3 and replayed, tolerances weights rel-L2 <= 2.5 %, cosine >= 0.999,
+             sign agreement >= 99 %, near-zero weights within 2*lr; moments rel-L2 <= 5 %.
+performance  build -> profile -> plan -> execute; median measured step against the simulated step
+             (within 10 %) and, when a floor is recorded for this hardware and configuration,
+             at least 95 % of it.
+
+Each gate prints one JSON record and the process exits non-zero if a gate fails. The gate
+definitions follow the reference's (qualification/numerical/README.md:199-213,
+qualification/performance/README.md:69-100).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import sys
+import tempfile
+
+import torch
+
+from ..data.synthetic import make_batch, to_device
+from ..execution.resident import ResidentTrainer
+from ..planning.plan import SearchOptions
+from ..training.session import TrainingSession, TrainingSetup
+
+
+def compare_tensors(a: torch.Tensor, b: torch.Tensor, lr: float) -> dict[str, float]:
+    a, b = a.detach().float().reshape(-1).cpu(), b.detach().float().reshape(-1).cpu()
+    rel = float((a - b).norm() / (b.norm() + 1e-12))
+    cos = float(torch.dot(a, b) / (a.norm() * b.norm() + 1e-12))
+    big = b.abs() > 2 * lr
+    sign = float((torch.sign(a[big]) == torch.sign(b[big])).float().mean()) if big.any() else 1.0
+    near = float((a[~big] - b[~big]).abs().max()) if (~big).any() else 0.0
+    return {"rel_l2": rel, "cosine": cos, "sign_agreement": sign, "near_zero_abs": near}
+
+
+def numerical_gate(model: str = "llama3-tiny", device: str = "cpu", updates: int = 5,
+                   lr: float = 1e-3) -> dict:
+    cpu = device == "cpu"
+    T, n_mb = (256, 2) if cpu else (2048, 2)
+    setup = TrainingSetup(model=model, device_gib=0.53 if cpu else 8.0, spill_gib=0.25 if cpu else 16.0,
+                          tokens_per_step=T * n_mb, microbatch_tokens=T, lr=lr, seed=7, device=device,
+                          dtype="float32" if cpu else "bfloat16", stochastic_rounding=False,
+                          profile=not cpu, calibrate=not cpu,
+                          search=SearchOptions(minimum_object_bytes_evict_eligible=1024, workers=2))
+    session = TrainingSession(setup)
+    cfg = session.cfg
+    ref = ResidentTrainer(cfg, device=device if cpu else "cuda", dtype=session.dtype, seed=7, lr=lr,
+                          stochastic_rounding=False)
+    batches = [make_batch(i, vocab=cfg.vocab_size, tokens_per_step=T * n_mb, microbatch_tokens=T,
+                          median=60 if cpu else 300, min_len=8, max_len=T // 2, slots=session.slots)
+               for i in range(updates)]
+    losses, failures = [], []
+    with tempfile.TemporaryDirectory() as ckpt:
+        for i, b in enumerate(batches):
+            got = session.step(b).loss
+            want = ref.step([to_device(m, ref.device) for m in b])
+            losses.append((got, want))
+            if abs(got - want) > (1e-5 if cpu else 2e-2) * max(1.0, abs(want)):
+                failures.append(f"loss at update {i + 1}: {got} vs {want}")
+            if i == 2:
+                session.save(ckpt)
+        final = session.executor.state_dict()
+        # replay from the checkpoint: updates 4.. must reproduce the same state
+        session.restore(ckpt)
+        for b in batches[3:]:
+            session.step(b)
+        replay = session.executor.state_dict()
+    worst = {"rel_l2": 0.0, "cosine": 1.0, "sign_agreement": 1.0, "near_zero_abs": 0.0}
+    moments = 0.0
+    for k, v in ref.state_dict().items():
+        m = compare_tensors(final[k], v, lr)
+        worst = {"rel_l2": max(worst["rel_l2"], m["rel_l2"]), "cosine": min(worst["cosine"], m["cosine"]),
+                 "sign_agreement": min(worst["sign_agreement"], m["sign_agreement"]),
+                 "near_zero_abs": max(worst["near_zero_abs"], m["near_zero_abs"])}
+    for si, st in enumerate(ref.stages):
+        for p in st.params:
+            if p.trainable:
+                key = f"exp_avg.{st.name}.{p.name}"
+                if key in final:
+                    moments = max(moments, compare_tensors(final[key], ref.M[si][p.name], lr)["rel_l2"])
+    replay_diff = max(float((replay[k].float() - final[k].float()).abs().max()) for k in final)
+    if worst["rel_l2"] > 0.025 or worst["cosine"] < 0.999 or worst["sign_agreement"] < 0.99:
+        failures.append(f"weights outside tolerance: {worst}")
+    if worst["near_zero_abs"] > 2 * lr + 1e-7:
+        failures.append(f"near-zero weights differ by {worst['near_zero_abs']}")
+    if moments > 0.05:
+        failures.append(f"first moments rel-L2 {moments}")
+    if replay_diff > (0.0 if cpu else 1e-6):
+        failures.append(f"checkpoint replay differs by {replay_diff}")
+    session.close()
+    return {"gate": "numerical", "model": model, "device": device, "updates": updates,
+            "weights": worst, "moments_rel_l2": moments, "replay_max_abs": replay_diff,
+            "losses": losses, "passed": not failures, "failures": failures}
+
+
+def performance_gate(model: str = "llama3-8b", device_gib: float = 24.0, spill_gib: float = 128.0,
+                     tokens: int = 65536, microbatch: int = 8192, groups: int = 3, updates: int = 4,
+                     floor: float | None = None) -> dict:
+    setup = TrainingSetup(model=model, device_gib=device_gib, spill_gib=spill_gib, tokens_per_step=tokens,
+                          microbatch_tokens=microbatch, lr=1e-5, seed=1,
+                          candidate_selections=("100", "0:save_attention"))
+    session = TrainingSession(setup)
+    cfg = session.cfg
+    cycles = []
+    for gidx in range(groups):
+        times = []
+        for u in range(updates):
+            b = make_batch(100 * gidx + u, vocab=cfg.vocab_size, tokens_per_step=tokens,
+                           microbatch_tokens=microbatch, max_len=min(8192, microbatch), median=1200.0,
+                           slots=session.slots)
+            times.append(session.step(b).device_seconds)
+        cycles.append(statistics.median(times[1:]))      # the first update of a group warms up
+    measured = statistics.median(cycles)
+    simulated = session.plan.summary.duration_seconds
+    tps = tokens / measured
+    failures = []
+    if abs(measured - simulated) > 0.10 * simulated:
+        failures.append(f"measured {measured:.3f} s vs simulated {simulated:.3f} s: outside 10 %")
+    if floor is not None and tps < 0.95 * floor:
+        failures.append(f"{tps:.0f} tokens/s is under 95 % of the floor {floor:.0f}")
+    session.close()
+    return {"gate": "performance", "model": model, "measured_seconds": measured,
+            "simulated_seconds": simulated, "tokens_per_second": tps, "floor": floor,
+            "group_cycles": cycles, "passed": not failures, "failures": failures}
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="python -m shadowspill_b200.qualification.gates")
+    ap.add_argument("gates", nargs="*", default=["numerical"], choices=["numerical", "performance"])
+    ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
+    ap.add_argument("--model", default=None)
+    ap.add_argument("--floor", type=float, default=None, help="recorded tokens/s floor for this box")
+    a = ap.parse_args(argv)
+    ok = True
+    for gate in a.gates:
+        if gate == "numerical":
+            default = "llama3-tiny" if a.device == "cpu" else "llama3-1b"
+            rec = numerical_gate(a.model or default, a.device)
+        else:
+            rec = performance_gate(a.model or "llama3-8b", floor=a.floor)
+        print(json.dumps(rec), flush=True)
+        ok &= rec["passed"]
+    return 0 if ok else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())
