@@ -49,8 +49,17 @@ def numerical_gate(model: str = "llama3-tiny", device: str = "cpu", updates: int
                           search=SearchOptions(minimum_object_bytes_evict_eligible=1024, workers=2))
     session = TrainingSession(setup)
     cfg = session.cfg
+    if not cpu:
+        # the independent trainer shares this process: lift the session's allocator cap
+        torch.cuda.set_per_process_memory_fraction(1.0, setup.device_index)
     ref = ResidentTrainer(cfg, device=device if cpu else "cuda", dtype=session.dtype, seed=7, lr=lr,
                           stochastic_rounding=False)
+    # same starting point: the planned run's initial weights (its on-device initialisation
+    # draws from another generator than the resident trainer's)
+    start = session.executor.state_dict()
+    for k, v in ref.state_dict().items():
+        v.copy_(start[k].to(v.device))
+    del start
     batches = [make_batch(i, vocab=cfg.vocab_size, tokens_per_step=T * n_mb, microbatch_tokens=T,
                           median=60 if cpu else 300, min_len=8, max_len=T // 2, slots=session.slots)
                for i in range(updates)]
