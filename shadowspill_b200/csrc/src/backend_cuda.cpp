@@ -11,8 +11,13 @@
 
 #include <cuda_runtime.h>
 
+#include <sched.h>
+
+#include <cctype>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
+#include <string>
 
 namespace {
 
@@ -32,9 +37,62 @@ int device_alloc(void* self, size_t bytes, void** out) {
   return rc_of(cudaMalloc(out, bytes));
 }
 int device_free(void* self, void* p) { bind(self); return rc_of(cudaFree(p)); }
-int host_alloc(void* self, size_t bytes, int, void** out) {
+// NUMA node of a GPU from sysfs (-1 when unknown).
+int numa_node_of_device(int device) {
+  char bus[32] = {0};
+  if (cudaDeviceGetPCIBusId(bus, sizeof bus, device) != cudaSuccess) return -1;
+  for (char* c = bus; *c; ++c) *c = static_cast<char>(std::tolower(*c));
+  const std::string path = std::string("/sys/bus/pci/devices/") + bus + "/numa_node";
+  FILE* f = std::fopen(path.c_str(), "r");
+  if (!f) return -1;
+  int node = -1;
+  if (std::fscanf(f, "%d", &node) != 1) node = -1;
+  std::fclose(f);
+  return node;
+}
+
+// CPUs of a NUMA node ("0-31,64-95") into a mask; false when the list cannot be read.
+bool cpus_of_node(int node, cpu_set_t* set) {
+  char path[96];
+  std::snprintf(path, sizeof path, "/sys/devices/system/node/node%d/cpulist", node);
+  FILE* f = std::fopen(path, "r");
+  if (!f) return false;
+  char buf[4096] = {0};
+  const bool got = std::fgets(buf, sizeof buf, f) != nullptr;
+  std::fclose(f);
+  if (!got) return false;
+  CPU_ZERO(set);
+  int n = 0;
+  for (char* p = buf; *p;) {
+    char* end;
+    long lo = std::strtol(p, &end, 10);
+    if (end == p) break;
+    long hi = lo;
+    if (*end == '-') { p = end + 1; hi = std::strtol(p, &end, 10); }
+    for (long c = lo; c <= hi && c < CPU_SETSIZE; ++c) { CPU_SET(static_cast<int>(c), set); ++n; }
+    p = (*end == ',') ? end + 1 : end;
+    if (*end != ',' ) break;
+  }
+  return n > 0;
+}
+
+// Pinned host memory lands on the node of the CPU that allocates it: run the allocation on
+// the GPU's own node (numa_node < 0: look it up), then put the thread's affinity back. With
+// eight ranks on a two-socket host this keeps every rank's spill traffic off the inter-socket link.
+int host_alloc(void* self, size_t bytes, int numa_node, void** out) {
   if (int rc = bind(self)) return rc;
-  return rc_of(cudaHostAlloc(out, bytes, cudaHostAllocPortable));
+  if (numa_node < 0) numa_node = numa_node_of_device(static_cast<Cuda*>(self)->device);
+  cpu_set_t old_set, node_set;
+  bool moved = false;
+  if (numa_node >= 0 && cpus_of_node(numa_node, &node_set) &&
+      sched_getaffinity(0, sizeof old_set, &old_set) == 0) {
+    cpu_set_t both;
+    CPU_AND(&both, &node_set, &old_set);          // stay inside the cpuset we were given
+    if (CPU_COUNT(&both) > 0) moved = sched_setaffinity(0, sizeof both, &both) == 0;
+  }
+  const cudaError_t e = cudaHostAlloc(out, bytes, cudaHostAllocPortable);
+  if (moved) sched_setaffinity(0, sizeof old_set, &old_set);
+  return rc_of(e);
 }
 int host_free(void* self, void* p, size_t) { bind(self); return rc_of(cudaFreeHost(p)); }
 int stream_create(void* self, void** out) {

@@ -133,6 +133,35 @@ class TrainingSession:
         loaded = load_bundle(setup.bundle, identity) if (rank == 0 and setup.bundle) else None
         self.prepared_from_bundle = loaded is not None
         self.sweep = None
+        # ---- host link calibration: every rank of the job measures its lanes at the same time,
+        # because they share the host's memory system; the plan is made for the slowest rank
+        from_bundle = loaded is not None
+        if world > 1:
+            import torch.distributed as dist
+            flag = [from_bundle]
+            dist.broadcast_object_list(flag, src=0)
+            from_bundle = flag[0]
+        calibrated = None
+        if setup.calibrate and cuda and not from_bundle:
+            t0 = time.perf_counter()
+            probe = 256 << 20
+            if world > 1:
+                dist.barrier()
+            with Runtime(2 * probe, 2 * probe, "cuda", setup.device_index) as rt:
+                r = rt.calibrate(probe, 3)
+            rates = torch.tensor([r.fetch_solo_bps, r.fetch_concurrent_bps, r.evict_solo_bps,
+                                  r.evict_concurrent_bps], dtype=torch.float64, device="cuda")
+            lat = torch.tensor([r.fetch_latency_ns, r.evict_latency_ns], dtype=torch.float64, device="cuda")
+            if world > 1:
+                dist.all_reduce(rates, op=dist.ReduceOp.MIN)
+                dist.all_reduce(lat, op=dist.ReduceOp.MAX)
+            rates, lat = rates.tolist(), lat.tolist()
+            calibrated = CommunicationInfo(rates[0], rates[1], rates[2], rates[3], int(lat[0]), int(lat[1]),
+                                           world_size=world,
+                                           source="calibrated" if world == 1 else f"calibrated with {world} ranks streaming")
+            self.timings["communication"] = time.perf_counter() - t0
+            self.log(f"host link: fetch {rates[0] / 1e9:.1f} ({rates[1] / 1e9:.1f} two-way) GB/s, "
+                     f"evict {rates[2] / 1e9:.1f} ({rates[3] / 1e9:.1f}) GB/s")
         if loaded is not None:
             from ..ir.plan import Plan
             chosen, plan_json, extra_json = loaded["chosen"], loaded["plan"], loaded["extra_plans"]
@@ -174,17 +203,9 @@ class TrainingSession:
                 if cuda:
                     torch.cuda.empty_cache()
             self.timings["profile"] = time.perf_counter() - t0
-            # ---- host link calibration
-            t0 = time.perf_counter()
-            if setup.calibrate and cuda:
-                probe = 256 << 20
-                with Runtime(2 * probe, 2 * probe, "cuda", setup.device_index) as rt:
-                    r = rt.calibrate(probe, 3)
-                self.communication = CommunicationInfo(
-                    r.fetch_solo_bps, r.fetch_concurrent_bps, r.evict_solo_bps,
-                    r.evict_concurrent_bps, r.fetch_latency_ns, r.evict_latency_ns,
-                    world_size=world, source="calibrated")
-            self.timings["communication"] = time.perf_counter() - t0
+            # ---- host link calibration (done by every rank at once, see below)
+            if calibrated is not None:
+                self.communication = calibrated
             # ---- plan every candidate, keep the fastest
             t0 = time.perf_counter()
             sweep = sweep_programs([p for p, _ in candidates], self.budgets, self.communication,
