@@ -109,7 +109,7 @@ def main() -> None:
     ap.add_argument("--spill-gib", type=float, default=128.0)
     ap.add_argument("--tokens", type=int, default=65536, help="tokens per worker per step")
     ap.add_argument("--microbatch", type=int, default=8192)
-    ap.add_argument("--candidates", default="100,0:save_attention,mix:3,mix:6,mix:9",
+    ap.add_argument("--candidates", default="100,75:save_attention,50:save_attention,25:save_attention,0:save_attention,mix:3",
                     help="comma list of programs the planner sweeps: <recompute share %%>[:<saved variant>] "
                          "or mix:<K> (attention saved everywhere, K layers saved whole)")
     ap.add_argument("--walks", default="breadth")

@@ -71,6 +71,9 @@ class TrainingSetup:
     collectives: str = "auto"             # peer | dist | auto
     # prepared bundle (training.ssp): read when it matches this setup, written after planning
     bundle: str = ""
+    # content-addressed store of task profiles shared between runs ("" = none)
+    store: str = ""
+    store_mode: str = "read_write"
     operations: tuple[str, ...] = ("step",)   # also: forward_backward, optim_step, forward
 
 
@@ -193,16 +196,35 @@ class TrainingSession:
                          f"streaming {ov.streaming_tflops:.0f} TFLOP/s -> task times x{scale:.3f}")
             if setup.profile:
                 dev = f"cuda:{setup.device_index}" if cuda else "cpu"
+                store = ident = None
+                if setup.store:
+                    from ..store import ContentStore, kernel_library_digest
+                    store = ContentStore(setup.store, setup.store_mode)
+                    ident = {"device": torch.cuda.get_device_name(setup.device_index) if cuda else "cpu",
+                             "kernels": kernel_library_digest(), "dtype": setup.dtype}
                 for prog, desc in candidates + list(extras.values()):
                     missing = {t.profile_key for t in prog.tasks} - set(self.profiles.tasks)
+                    if store is not None:
+                        from ..profiling.measure import TaskProfile
+                        for key in sorted(missing):
+                            hit = store.get("task_profile", {**ident, "task": key})
+                            if hit is not None:
+                                self.profiles.tasks[key] = TaskProfile(**hit)
+                        missing -= set(self.profiles.tasks)
                     if missing:
                         got = measure_program(prog, desc, dev, keys=missing)
                         self.profiles.tasks.update(got.tasks)
                         self.profiles.device = got.device
+                        if store is not None:
+                            from dataclasses import asdict as _asdict
+                            for key, prof in got.tasks.items():
+                                store.put("task_profile", {**ident, "task": key}, _asdict(prof))
                     apply_profiles(prog, self.profiles, duration_scale=scale)
                 if cuda:
                     torch.cuda.empty_cache()
             self.timings["profile"] = time.perf_counter() - t0
+            if setup.profile and setup.store:
+                self.log(f"profile store: {store.hits} hits, {store.writes} new entries")
             # ---- host link calibration (done by every rank at once, see below)
             if calibrated is not None:
                 self.communication = calibrated
