@@ -43,7 +43,7 @@ constexpr int THREADS = 192;
 constexpr int A_BYTES = BM * BK * 2;
 constexpr int B_BYTES = (BN / 2) * BK * 2;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;       // 32 KB per CTA per stage
-constexpr int STAGES = 6;
+constexpr int STAGES = 7;
 constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
 constexpr int TMEM_COLS = 2 * BN;
 
