@@ -291,7 +291,7 @@ class HybridLayerStage(Stage):
     # ---- stage interface
     def forward(self, P, x, meta: BatchMeta, keep=(), out=None):
         bounds = meta.cu_seqlens.tolist() if (self.mixer == "deltanet" and not x.is_cuda) else None
-        with torch.no_grad():
+        with torch.no_grad(), seq_ops.tf32_matmul():
             P2, L = self._leaves(P, False)
             y = self._layer(P2, L, x, meta, None, bounds)
         if out is not None:
@@ -312,6 +312,8 @@ class HybridLayerStage(Stage):
         P2, L = self._leaves(P, True)
         xin = x.detach().requires_grad_(True)
         self._aux = []
+        tf32 = seq_ops.tf32_matmul()
+        tf32.__enter__()                  # also covers the autograd backward below
         with torch.enable_grad():
             y = self._layer(P2, L, xin, meta, sink, bounds)
         if self._aux:
@@ -325,6 +327,7 @@ class HybridLayerStage(Stage):
             self._aux = []
         else:
             torch.autograd.backward(y, dy)
+        tf32.__exit__()
         for name, leaf in L.items():
             sink.add_vector(name, leaf.grad if leaf.grad is not None else torch.zeros_like(leaf))
         dy.copy_(xin.grad)

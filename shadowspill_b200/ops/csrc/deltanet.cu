@@ -337,10 +337,12 @@ int ss_gated_rmsnorm_bwd(const void* x, const void* gate, const void* w, const v
 // ============================================================================ chunk-state scan
 // The only sequential part of the chunked gated delta rule: a linear recurrence over the
 // chunk index for every head,
-//     X_{c+1} = op(A_c) X_c + B_c,        X_0 = 0,        out[c] = X_c   (the state ENTERING c)
-// with A_c [dk, dk], B_c / X [dk, dv] fp32. Columns of X evolve independently, so a block owns
-// one head and 32 columns. `reverse` walks c = n-1 .. 0 and `transpose` uses A_c^T, which is the
-// adjoint recurrence of the backward pass (out[c] = gradient reaching the state LEAVING c).
+//     X_{c+1} = M_c^T X_c + B_c,        X_0 = 0,        out[c] = X_c   (the state ENTERING c)
+// with M_c [dk, dk], B_c / X [dk, dv] fp32. The caller passes M = A^T for the forward
+// recurrence X_{c+1} = A_c X_c + B_c and M = A itself (walking c = n-1 .. 0) for its adjoint,
+// so the tile is always copied into shared memory as stored. Columns of X evolve independently:
+// a block owns one head and 32 columns; each thread keeps a 4 x 4 register tile; the next
+// step's matrix streams in with cp.async while the current one is multiplied.
 // Everything that is parallel over chunks (building A and B, outputs, their gradients) is batched
 // matrix algebra outside this kernel.
 namespace ss_dn {
@@ -348,69 +350,96 @@ namespace ss_dn {
 constexpr int SCAN_COLS = 32;
 constexpr int SCAN_THREADS = 256;
 
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 __global__ void __launch_bounds__(SCAN_THREADS)
-linear_scan_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ out,
-                   int n, int H, int dk, int dv, int reverse, int transpose) {
-  extern __shared__ float sm[];
-  const int lda = dk + 4;                       // padded rows: no bank conflicts on row reads
-  float* As = sm;                               // [dk][lda]
-  float* X = As + dk * lda;                     // [dk][SCAN_COLS]
+linear_scan_kernel(const float* __restrict__ M, const float* __restrict__ B, float* __restrict__ out,
+                   int n, int H, int dk, int dv, int reverse) {
+  extern __shared__ __align__(16) float sm[];
+  const int lda = dk + 4;                       // padded rows keep 16-byte alignment, spread banks
+  float* Ms[2] = {sm, sm + dk * lda};           // [dk][lda] x 2 (double buffer)
+  float* X = sm + 2 * dk * lda;                 // [dk][SCAN_COLS]
   float* Xn = X + dk * SCAN_COLS;
   const int slices = dv / SCAN_COLS;
   const int h = blockIdx.x / slices, col0 = (blockIdx.x % slices) * SCAN_COLS;
   const int tid = threadIdx.x;
-  const int tx = tid & 7, ty = tid >> 3;        // 4 columns each, rows ty + 32*r
+  const int tx = tid & 7, ty = tid >> 3;        // output tile: rows 4*ty.., columns 4*tx..
+  auto matrix = [&](int s) { return static_cast<long long>(reverse ? n - 1 - s : s) * H + h; };
+  auto prefetch = [&](int s, float* dst) {
+    const float* src = M + matrix(s) * dk * dk;
+    for (int i = tid * 4; i < dk * dk; i += SCAN_THREADS * 4) {
+      const int r = i / dk, cc = i - r * dk;
+      cp_async16(dst + r * lda + cc, src + i);
+    }
+    cp_async_commit();
+  };
   for (int i = tid; i < dk * SCAN_COLS; i += SCAN_THREADS) X[i] = 0.f;
-  __syncthreads();
+  if (n > 0) prefetch(0, Ms[0]);
   for (int s = 0; s < n; ++s) {
-    const int c = reverse ? n - 1 - s : s;
-    const long long mat = (static_cast<long long>(c) * H + h);
-    const float* Ac = A + mat * dk * dk;
+    const long long mat = matrix(s);
     const float* Bc = B + mat * dk * dv;
     float* oc = out + mat * dk * dv;
-    for (int i = tid * 4; i < dk * dk; i += SCAN_THREADS * 4) {
-      const float4 v = *reinterpret_cast<const float4*>(Ac + i);
-      const int r = i / dk, cc = i - r * dk;
-      *reinterpret_cast<float4*>(As + r * lda + cc) = v;
-    }
+    if (s + 1 < n) { prefetch(s + 1, Ms[(s + 1) & 1]); cp_async_wait<1>(); }
+    else cp_async_wait<0>();
+    __syncthreads();                             // this step's matrix and the current X are visible
+    const float* As = Ms[s & 1];
     // the state entering this step is an output
-    for (int i = tid; i < dk * SCAN_COLS; i += SCAN_THREADS) {
-      const int r = i / SCAN_COLS, cc = i - r * SCAN_COLS;
-      oc[static_cast<long long>(r) * dv + col0 + cc] = X[i];
+    for (int i = tid; i < dk * SCAN_COLS / 4; i += SCAN_THREADS) {
+      const int r = (i * 4) / SCAN_COLS, cc = (i * 4) - r * SCAN_COLS;
+      *reinterpret_cast<float4*>(oc + static_cast<long long>(r) * dv + col0 + cc) =
+          *reinterpret_cast<const float4*>(X + r * SCAN_COLS + cc);
     }
-    __syncthreads();
-    for (int r0 = ty; r0 < dk; r0 += 32) {
-      const float4 b = *reinterpret_cast<const float4*>(Bc + static_cast<long long>(r0) * dv + col0 + tx * 4);
-      float a0 = b.x, a1 = b.y, a2 = b.z, a3 = b.w;
-#pragma unroll 4
-      for (int m = 0; m < dk; ++m) {
-        const float a = transpose ? As[m * lda + r0] : As[r0 * lda + m];
-        const float4 x = *reinterpret_cast<const float4*>(X + m * SCAN_COLS + tx * 4);
-        a0 += a * x.x; a1 += a * x.y; a2 += a * x.z; a3 += a * x.w;
+    if (ty * 4 < dk) {
+      float acc[4][4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const float4 b = *reinterpret_cast<const float4*>(Bc + static_cast<long long>(ty * 4 + r) * dv + col0 + tx * 4);
+        acc[r][0] = b.x; acc[r][1] = b.y; acc[r][2] = b.z; acc[r][3] = b.w;
       }
-      *reinterpret_cast<float4*>(Xn + r0 * SCAN_COLS + tx * 4) = make_float4(a0, a1, a2, a3);
+#pragma unroll 8
+      for (int m = 0; m < dk; ++m) {
+        const float4 a = *reinterpret_cast<const float4*>(As + m * lda + ty * 4);      // M[m][4ty..]
+        const float4 x = *reinterpret_cast<const float4*>(X + m * SCAN_COLS + tx * 4);
+        const float av[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          acc[r][0] += av[r] * x.x; acc[r][1] += av[r] * x.y;
+          acc[r][2] += av[r] * x.z; acc[r][3] += av[r] * x.w;
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+        *reinterpret_cast<float4*>(Xn + (ty * 4 + r) * SCAN_COLS + tx * 4) =
+            make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
     }
-    __syncthreads();
+    __syncthreads();                             // everyone is done with X and with Ms[s & 1]
     float* t = X; X = Xn; Xn = t;
   }
 }
 
 }  // namespace ss_dn
 
-extern "C" int ss_linear_scan(const float* A, const float* B, float* out, int n, int H, int dk, int dv,
-                              int reverse, int transpose, void* stream) {
+// X_{c+1} = M_c^T X_c + B_c (see above). dk a multiple of 4 up to 128, dv a multiple of 32.
+extern "C" int ss_linear_scan(const float* M, const float* B, float* out, int n, int H, int dk, int dv,
+                              int reverse, void* stream) {
   using namespace ss_dn;
   if (dk % 4 || dk > 128 || dv % SCAN_COLS || n < 0) return -2;
   if (n == 0 || H == 0) return 0;
-  const int smem = sizeof(float) * (dk * (dk + 4) + 2 * dk * SCAN_COLS);
+  const int smem = sizeof(float) * (2 * dk * (dk + 4) + 2 * dk * SCAN_COLS);
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(linear_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)sizeof(float) * (128 * 132 + 2 * 128 * SCAN_COLS));
+                                         (int)sizeof(float) * (2 * 128 * 132 + 2 * 128 * SCAN_COLS));
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   linear_scan_kernel<<<H * (dv / SCAN_COLS), SCAN_THREADS, smem, (cudaStream_t)stream>>>(
-      A, B, out, n, H, dk, dv, reverse, transpose);
+      M, B, out, n, H, dk, dv, reverse);
   return (int)cudaGetLastError();
 }

@@ -41,6 +41,19 @@ _lib.register("ss_gated_rmsnorm_bwd", [_c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_p, _
                                        _c.c_int, _c.c_f, _c.c_int, _c.c_p])
 
 
+class tf32_matmul:
+    """Context: fp32 matrix products on the tensor cores in TF32 (10-bit mantissa, fp32
+    accumulate). The chunked delta rule's batched products, and their autograd backward,
+    run under it; its operands come from bf16 activations, so nothing finer is lost."""
+
+    def __enter__(self):
+        self.prev = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = True
+
+    def __exit__(self, *exc):
+        torch.backends.cuda.matmul.allow_tf32 = self.prev
+
+
 def _native(x: torch.Tensor) -> bool:
     return x.is_cuda and x.dtype == torch.bfloat16
 
@@ -158,42 +171,44 @@ def causal_conv_silu(x: torch.Tensor, w: torch.Tensor, bounds: list[int],
 
 class _LinearScan(torch.autograd.Function):
     """``S_{c+1} = A_c S_c + B_c`` over the chunk axis, ``S_0 = 0``; returns the state entering
-    every chunk. ``A`` [n,H,dk,dk], ``B`` [n,H,dk,dv] fp32. The backward pass is the adjoint
-    recurrence (same kernel, transposed and reversed) plus two batched products."""
+    every chunk. The matrices are given TRANSPOSED (``At[c] = A_c^T``, [n,H,dk,dk]), ``B``
+    [n,H,dk,dv], fp32: the kernel multiplies by the transpose of what it is handed, so the
+    forward pass reads ``At`` as stored and the adjoint recurrence reads ``A`` as stored.
+    Backward: ``lam_c = dS_c + A_c^T lam_{c+1}``, ``dB_c = lam_{c+1}``, ``dA_c = lam_{c+1} S_c^T``."""
 
     @staticmethod
-    def run(A, B, reverse: bool, transpose: bool):
+    def run(M, B, reverse: bool):
+        """``X_{c+1} = M_c^T X_c + B_c``; out[c] = X entering step c (walking down when reverse)."""
         n, H, dk, dv = B.shape
         out = torch.empty_like(B)
-        if A.is_cuda and dv % 32 == 0 and dk % 4 == 0 and dk <= 128:
-            _lib.check(_lib.lib().ss_linear_scan(A.data_ptr(), B.data_ptr(), out.data_ptr(), n, H, dk, dv,
-                                                 int(reverse), int(transpose), _lib.stream_ptr()),
-                       "ss_linear_scan")
+        if M.is_cuda and dv % 32 == 0 and dk % 4 == 0 and dk <= 128:
+            _lib.check(_lib.lib().ss_linear_scan(M.data_ptr(), B.data_ptr(), out.data_ptr(), n, H, dk, dv,
+                                                 int(reverse), _lib.stream_ptr()), "ss_linear_scan")
             return out
         X = B.new_zeros(H, dk, dv)
         for s in range(n):
             c = n - 1 - s if reverse else s
             out[c] = X
-            Ac = A[c].transpose(-1, -2) if transpose else A[c]
-            X = Ac @ X + B[c]
+            X = M[c].transpose(-1, -2) @ X + B[c]
         return out
 
     @staticmethod
-    def forward(ctx, A, B):
-        A, B = A.contiguous(), B.contiguous()
-        S = _LinearScan.run(A, B, False, False)
-        ctx.save_for_backward(A, S)
+    def forward(ctx, At, B):
+        At, B = At.contiguous(), B.contiguous()
+        S = _LinearScan.run(At, B, False)
+        ctx.save_for_backward(At, S)
         return S
 
     @staticmethod
     def backward(ctx, dS):
-        A, S = ctx.saved_tensors
-        lam = _LinearScan.run(A, dS.contiguous(), True, True)     # gradient reaching S_{c+1}
-        return lam @ S.transpose(-1, -2), lam
+        At, S = ctx.saved_tensors
+        A = At.transpose(-1, -2).contiguous()
+        lam = _LinearScan.run(A, dS.contiguous(), True)           # gradient reaching S_{c+1}
+        return S @ lam.transpose(-1, -2), lam                      # d(A^T) = (lam S^T)^T
 
 
 _lib.register("ss_linear_scan", [_c.c_p, _c.c_p, _c.c_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
-                                 _c.c_int, _c.c_p])
+                                 _c.c_p])
 
 
 def gated_delta_rule_chunked(q, k, v, beta, g, bounds: list[int] | None, chunk: int = 64,
@@ -218,14 +233,15 @@ def gated_delta_rule_chunked(q, k, v, beta, g, bounds: list[int] | None, chunk: 
         sid = torch.bucketize(pos, cu_seqlens[1:].to(torch.long), right=True)
     else:
         sid = torch.bucketize(pos, torch.tensor(list(bounds[1:]), device=dev, dtype=torch.long), right=True)
-    qf = q.float().repeat_interleave(rep, dim=1) * dk ** -0.5
-    kf = k.float().repeat_interleave(rep, dim=1)
+    scale = dk ** -0.5                              # folded into the query-side products below
+    grow = lambda t: (t if rep == 1 else t[:, :, None, :].expand(T, Hk, rep, dk).reshape(T, H, dk))
+    qf, kf = grow(q).float(), grow(k).float()
     vf, bf, gf = v.float(), beta.float(), g.float()
     if pad:
         zp = lambda t: TF.pad(t, (0, 0) * (t.dim() - 1) + (0, pad))
         qf, kf, vf, bf, gf = zp(qf), zp(kf), zp(vf), zp(bf), zp(gf)
         sid = torch.cat([sid, sid.new_full((pad,), int(2 ** 31 - 1))])    # padding is its own sequence
-    rs = lambda t: t.reshape(n, C, H, -1).permute(0, 2, 1, 3)            # [n,H,C,*]
+    rs = lambda t: t.reshape(n, C, H, -1).permute(0, 2, 1, 3).contiguous()   # [n,H,C,*], one copy each
     qc, kc, vc = rs(qf), rs(kf), rs(vf)
     bc = bf.reshape(n, C, H).permute(0, 2, 1)                           # [n,H,C]
     gam = gf.reshape(n, C, H).permute(0, 2, 1).cumsum(-1)               # log of the running decay
@@ -252,14 +268,15 @@ def gated_delta_rule_chunked(q, k, v, beta, g, bounds: list[int] | None, chunk: 
         Gt = torch.exp(gam) * first_seg[:, None, :]                     # decay from the carried state
         W = Tm @ (bc[..., None] * Gt[..., None] * kc)                   # [n,H,C,dk]
         U0 = Tm @ (bc[..., None] * vc)                                  # [n,H,C,dv]
-        M = ratio * (qc @ kc.transpose(-1, -2))
-        Qg = Gt[..., None] * qc
+        M = (ratio * scale) * (qc @ kc.transpose(-1, -2))
+        Qg = (Gt * scale)[..., None] * qc
         Gc = torch.exp(gam[..., -1]) * first_seg[:, -1][:, None]        # [n,H]
         Kd = (torch.exp(gam[..., -1:] - gam) * last_seg[:, None, :])[..., None] * kc
         KdT = Kd.transpose(-1, -2)
-        Amat = Gc[..., None, None] * torch.eye(dk, device=dev, dtype=qf.dtype) - KdT @ W
+        # S_next = (Gc I - Kd^T W) S + Kd^T U0; the scan takes the matrix transposed
+        AmatT = Gc[..., None, None] * torch.eye(dk, device=dev, dtype=qf.dtype) - W.transpose(-1, -2) @ Kd
         Bmat = KdT @ U0
-        S = _LinearScan.apply(Amat, Bmat)                               # state entering each chunk
+        S = _LinearScan.apply(AmatT, Bmat)                              # state entering each chunk
         U = U0 - W @ S
         out = Qg @ S + M @ U
     finally:

@@ -49,7 +49,7 @@ def test_linear_scan_adjoint():
     n, H, dk, dv = 5, 3, 8, 32
     A = (torch.randn(n, H, dk, dk) * 0.3).requires_grad_(True)
     B = torch.randn(n, H, dk, dv).requires_grad_(True)
-    S = seq._LinearScan.apply(A, B)
+    S = seq._LinearScan.apply(A.transpose(-1, -2), B)
     X = torch.zeros(H, dk, dv)
     want = []
     for c in range(n):
