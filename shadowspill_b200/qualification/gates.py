@@ -80,7 +80,7 @@ def numerical_gate(model: str = "llama3-tiny", device: str = "cpu", updates: int
             session.step(b)
         replay = session.executor.state_dict()
     worst = {"rel_l2": 0.0, "cosine": 1.0, "sign_agreement": 1.0, "near_zero_abs": 0.0}
-    moments = 0.0
+    moments, moments_at, moments_embed = 0.0, "", 0.0
     for k, v in ref.state_dict().items():
         m = compare_tensors(final[k], v, lr)
         worst = {"rel_l2": max(worst["rel_l2"], m["rel_l2"]), "cosine": min(worst["cosine"], m["cosine"]),
@@ -91,19 +91,28 @@ def numerical_gate(model: str = "llama3-tiny", device: str = "cpu", updates: int
             if p.trainable:
                 key = f"exp_avg.{st.name}.{p.name}"
                 if key in final:
-                    moments = max(moments, compare_tensors(final[key], ref.M[si][p.name], lr)["rel_l2"])
+                    rel = compare_tensors(final[key], ref.M[si][p.name], lr)["rel_l2"]
+                    if st.kind == "embedding":
+                        moments_embed = rel      # its gradient is summed with bf16 atomics (order varies)
+                    elif rel > moments:
+                        moments, moments_at = rel, key
     replay_diff = max(float((replay[k].float() - final[k].float()).abs().max()) for k in final)
     if worst["rel_l2"] > 0.025 or worst["cosine"] < 0.999 or worst["sign_agreement"] < 0.99:
         failures.append(f"weights outside tolerance: {worst}")
-    if worst["near_zero_abs"] > 2 * lr + 1e-7:
+    # a near-zero weight can move by lr per update in either direction
+    if worst["near_zero_abs"] > 2 * lr * updates + 1e-7:
         failures.append(f"near-zero weights differ by {worst['near_zero_abs']}")
     if moments > 0.05:
-        failures.append(f"first moments rel-L2 {moments}")
-    if replay_diff > (0.0 if cpu else 1e-6):
+        failures.append(f"first moments rel-L2 {moments} at {moments_at}")
+    if moments_embed > 0.10:
+        failures.append(f"embedding first moment rel-L2 {moments_embed}")
+    # on the GPU a few reductions use atomics, so a replay agrees to rounding, not bit for bit
+    if replay_diff > (0.0 if cpu else 2 * lr):
         failures.append(f"checkpoint replay differs by {replay_diff}")
     session.close()
     return {"gate": "numerical", "model": model, "device": device, "updates": updates,
-            "weights": worst, "moments_rel_l2": moments, "replay_max_abs": replay_diff,
+            "weights": worst, "moments_rel_l2": moments, "moments_worst_tensor": moments_at,
+            "embedding_moment_rel_l2": moments_embed, "replay_max_abs": replay_diff,
             "losses": losses, "passed": not failures, "failures": failures}
 
 
