@@ -202,6 +202,10 @@ class DenseLayerStage(Stage):
     SAVE_SETS = {
         "recompute": (),
         "save_attention": ("qkv", "attn", "lse"),
+        # also keeps the gate/up projection: the backward pass then recomputes only the small
+        # output-projection GEMM and the elementwise pieces (the gate/up GEMM is 85 % of the
+        # recomputed FLOPs of save_attention)
+        "save_attention_gu": ("qkv", "attn", "lse", "gu"),
         "save": ("h1", "rstd1", "qkv", "attn", "lse", "x_mid", "h2", "rstd2", "gu", "hmlp"),
     }
 

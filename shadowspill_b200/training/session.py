@@ -100,9 +100,10 @@ class TrainingSession:
             selections = []
             for item in setup.candidate_selections:
                 share, _, variant = item.partition(":")
-                if share == "mix":        # "mix:K": save_attention everywhere, K layers fully saved
+                if share == "mix":        # "mix:K[:variant]": save_attention everywhere, K layers keep more
                     from ..frontend.capture import mixed_selection
-                    selections.append(mixed_selection(self.cfg, int(variant)))
+                    count, _, full = variant.partition(":")
+                    selections.append(mixed_selection(self.cfg, int(count), full_variant=full or "save"))
                     continue
                 selections += recompute_share_selections(self.cfg, (int(share),),
                                                          variant or setup.saved_variant)

@@ -68,6 +68,7 @@ def test_depth_tail_matches_resident():
 
 def test_saved_variants_match_resident():
     _check_against_resident("breadth", selection={1: "save", 2: "save_attention"})
+    _check_against_resident("breadth", selection={1: "save_attention_gu", 2: "save_attention"})
 
 
 def test_steady_state_creates_no_events():
