@@ -110,7 +110,7 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=65536, help="tokens per worker per step")
     ap.add_argument("--microbatch", type=int, default=8192)
     ap.add_argument("--candidates", default="100,75:save_attention,50:save_attention,25:save_attention,0:save_attention,"
-                            "mix:8:save_attention_gu,mix:16:save_attention_gu,mix:32:save_attention_gu",
+                            "mix:8:save_attention_gu",
                     help="comma list of programs the planner sweeps: <recompute share %%>[:<saved variant>] "
                          "or mix:<K>[:<variant>] (attention saved everywhere, K layers keep <variant>, default save)")
     ap.add_argument("--walks", default="breadth")
