@@ -63,23 +63,25 @@ def _layer_to_hf(cfg: DecoderConfig, i: int, dense: bool, P: dict[str, torch.Ten
     return out
 
 
-def to_hf(cfg: DecoderConfig, state: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+def to_hf(cfg: DecoderConfig, state: dict[str, torch.Tensor], stages=None) -> dict[str, torch.Tensor]:
+    """``stages``: the run's own stage list when it differs from the default build (adapters
+    switch dense layers to separate q/k/v projections); adapter factors are not exported."""
     if not supported(cfg):
         raise ValueError(f"no Hugging Face mapping for family {cfg.family!r}")
-    stages = build_stages(cfg)
+    stages = stages or build_stages(cfg)
     out = {"model.embed_tokens.weight": state["embed.embed"],
            "model.norm.weight": state["head.final_norm"], "lm_head.weight": state["head.head"]}
     for i in range(cfg.n_layers):
         st = stages[i + 1]
-        P = {p.name: state[f"{st.name}.{p.name}"] for p in st.params}
+        P = {p.name: state[f"{st.name}.{p.name}"] for p in st.params if "_lora_" not in p.name}
         out.update(_layer_to_hf(cfg, i, isinstance(st, DenseLayerStage), P))
     return {k: v.contiguous() for k, v in out.items()}
 
 
-def from_hf(cfg: DecoderConfig, hf: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+def from_hf(cfg: DecoderConfig, hf: dict[str, torch.Tensor], stages=None) -> dict[str, torch.Tensor]:
     if not supported(cfg):
         raise ValueError(f"no Hugging Face mapping for family {cfg.family!r}")
-    stages = build_stages(cfg)
+    stages = stages or build_stages(cfg)
     head = hf.get("lm_head.weight", hf["model.embed_tokens.weight"])
     out = {"embed.embed": hf["model.embed_tokens.weight"], "head.final_norm": hf["model.norm.weight"],
            "head.head": head}
@@ -106,6 +108,8 @@ def from_hf(cfg: DecoderConfig, hf: dict[str, torch.Tensor]) -> dict[str, torch.
             P["w13"] = torch.cat([g("mlp.gate_proj.weight"), g("mlp.up_proj.weight")], 0)
             P["w2"] = g("mlp.down_proj.weight")
         for p in st.params:
+            if "_lora_" in p.name:
+                continue                  # adapters are not part of a base checkpoint
             if p.name not in P:
                 raise KeyError(f"{st.name}.{p.name} has no Hugging Face source")
             if tuple(P[p.name].shape) != tuple(p.shape):
@@ -127,17 +131,17 @@ def hf_config(cfg: DecoderConfig) -> dict:
     return d
 
 
-def save_hf(cfg: DecoderConfig, state: dict[str, torch.Tensor], directory: str | Path) -> Path:
+def save_hf(cfg: DecoderConfig, state: dict[str, torch.Tensor], directory: str | Path, stages=None) -> Path:
     from safetensors.torch import save_file
     d = Path(directory)
     d.mkdir(parents=True, exist_ok=True)
-    save_file({k: v.detach().cpu().contiguous() for k, v in to_hf(cfg, state).items()},
+    save_file({k: v.detach().cpu().contiguous() for k, v in to_hf(cfg, state, stages).items()},
               str(d / "model.safetensors"), metadata={"format": "pt"})
     (d / "config.json").write_text(json.dumps(hf_config(cfg), indent=1))
     return d
 
 
-def load_hf(cfg: DecoderConfig, directory: str | Path) -> dict[str, torch.Tensor]:
+def load_hf(cfg: DecoderConfig, directory: str | Path, stages=None) -> dict[str, torch.Tensor]:
     from safetensors.torch import load_file
     d = Path(directory)
     files = sorted(d.glob("*.safetensors"))
@@ -146,4 +150,4 @@ def load_hf(cfg: DecoderConfig, directory: str | Path) -> dict[str, torch.Tensor
     hf: dict[str, torch.Tensor] = {}
     for f in files:
         hf.update(load_file(str(f)))
-    return from_hf(cfg, hf)
+    return from_hf(cfg, hf, stages)

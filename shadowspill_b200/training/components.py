@@ -107,6 +107,40 @@ class ResolvedTraining:
     budgets: dict[str, float]
 
 
+def _lora_record(rec: dict | None) -> dict | None:
+    """Client ``LoRA`` record -> ``models.lora.LoRAConfig`` JSON."""
+    if not rec:
+        return None
+    from ..models.lora import DENSE_TARGETS, LoRAConfig
+    groups = {"attention": ("wq", "wk", "wv", "wo", "w_qkvz", "w_out"), "mlp": ("w13", "w2", "sw13", "sw2"),
+              "experts": ("w13", "w2")}
+    wanted = rec.get("targets", ("attention", "experts"))
+    targets: list[str] = []
+    for t in wanted:                        # group names of the client record, or matrix names
+        for name in groups.get(t, (t,)):
+            if name in DENSE_TARGETS and name not in targets:
+                targets.append(name)
+    return LoRAConfig(int(rec.get("rank", 16)), float(rec.get("alpha", 32.0)), tuple(targets),
+                      "experts" in wanted, bool(rec.get("train_base", False))).to_json()
+
+
+def _objective_record(rec: dict | None) -> dict | None:
+    """Client ``Objective`` record (component id, config, summed terms) -> ``Objective`` JSON."""
+    if not rec or rec.get("id", "shadowspill/cross_entropy@1") == "shadowspill/cross_entropy@1":
+        return None
+    from ..models.objectives import Objective
+    if rec["id"] == "shadowspill/sum@1":
+        head, head_cfg, balance = "shadowspill/cross_entropy@1", {}, 0.0
+        for term in rec.get("terms", ()):
+            if term.get("id") == "shadowspill/moe_balance@1":
+                balance = float((term.get("config") or {}).get("coefficient", 0.01))
+            else:
+                head, head_cfg = term["id"], dict(term.get("config") or {})
+        return Objective.from_component("shadowspill/sum@1", head=head, head_config=head_cfg,
+                                        moe_balance=balance).to_json()
+    return Objective.from_component(rec["id"], **dict(rec.get("config") or {})).to_json()
+
+
 def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[str, Any]) -> ResolvedTraining:
     """Client settings -> per-rank worker setups, with the provenance of every default."""
     prov: dict[str, str] = {}
@@ -169,7 +203,11 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
             "calibrate": bool(prep.get("calibrate", True)) and not body.get("simulation_only"),
             "search": search, "collectives": ex.get("collectives", "auto"),
             "operations": list(body.get("operations", ("step",))),
-            "trace_capacity": 65536 if ex.get("runtime_trace") else 0})
+            "trace_capacity": 65536 if ex.get("runtime_trace") else 0,
+            "lora": _lora_record(m.get("lora")), "objective": _objective_record(body.get("objective")),
+            "expert_parallel": (body.get("parallelism") or {}).get("kind") == "expert_parallel",
+            "pretrained": (m.get("weights", {}).get("location", "")
+                           if m.get("weights", {}).get("source") == "checkpoint" else "")})
     geometry = {"microbatch_tokens": T, "microbatches": tokens // T, "slots": slots,
                 "vocab_size": cfg.vocab_size, "workers": workers, "packing": b.get("packing", "best_fit"),
                 "tokens_per_step": tokens * workers}

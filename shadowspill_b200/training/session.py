@@ -71,6 +71,11 @@ class TrainingSetup:
     collectives: str = "auto"             # peer | dist | auto
     # prepared bundle (training.ssp): read when it matches this setup, written after planning
     bundle: str = ""
+    # training choices beyond the architecture (JSON records, see models/lora.py, models/objectives.py)
+    lora: dict | None = None
+    objective: dict | None = None
+    expert_parallel: bool = False        # routed layers keep 1/world of the experts per rank
+    pretrained: str = ""                 # directory of Hugging Face safetensors to start from
     # content-addressed store of task profiles shared between runs ("" = none)
     store: str = ""
     store_mode: str = "read_write"
@@ -112,14 +117,25 @@ class TrainingSession:
                                                     setup.saved_variant)
         variants = [(walk, sel) for walk in setup.walks for sel in selections]
 
+        from ..models.lora import LoRAConfig
+        from ..models.objectives import Objective
+        self.lora = LoRAConfig.from_json(setup.lora)
+        self.objective = Objective.from_json(setup.objective) if setup.objective else None
+        if self.lora is not None or setup.expert_parallel:
+            # these layers run through the autograd-derived stage, which only recomputes
+            selections = [{}]
+            variants = [(walk, {}) for walk in setup.walks]
+        choices = dict(objective=self.objective, lora=self.lora)
+
         def build(index: int):
             walk, sel = variants[index]
             order = StepDataOrdering(walk=walk, optimizer="stage_interleaved" if walk == "breadth" else "tail")
             return build_step(self.cfg, self.geometry, order, dtype=self.dtype, selection=sel,
-                              world_size=world, rank=rank)
+                              world_size=world, rank=rank, expert_parallel=setup.expert_parallel,
+                              **choices)
 
         def build_extra(op: str):
-            kw = dict(dtype=self.dtype, world_size=world, rank=rank)
+            kw = dict(dtype=self.dtype, world_size=world, rank=rank, **choices)
             if op == "forward_backward":
                 return build_forward_backward(self.cfg, self.geometry, StepDataOrdering(), **kw)
             if op == "optim_step":
@@ -276,6 +292,15 @@ class TrainingSession:
                                  trace_capacity=setup.trace_capacity,
                                  collectives=setup.collectives, extra_plans=self.extra_plans)
         self.executor.initialize()
+        if setup.pretrained:
+            from ..checkpoint.hf import load_hf
+            state = load_hf(self.cfg, setup.pretrained, self.executor.stages)
+            if world > 1:
+                raise NotImplementedError("pretrained weights load into single-rank runs; "
+                                          "restore a checkpoint to continue on several ranks")
+            # adapters and anything else the checkpoint does not name keep their initial values
+            self.executor.load_state_dict(state, strict=False)
+            self.log(f"weights from {setup.pretrained}")
         self.timings["open"] = time.perf_counter() - t0
         if cuda:
             torch.cuda.reset_peak_memory_stats(setup.device_index)

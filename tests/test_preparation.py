@@ -43,3 +43,35 @@ def test_bundle_round_trip_and_identity(tmp_path):
     assert not other.prepared_from_bundle
     other.close()
     assert load_bundle(path)["identity"] != meta["identity"]
+
+
+def test_pretrained_weights_and_adapters_through_the_session(tmp_path):
+    """A base model exported with Hugging Face names is the starting point of a LoRA run:
+    base tensors come from the file, adapters start fresh, only adapters train."""
+    import torch
+    from shadowspill_b200.checkpoint import hf
+    from shadowspill_b200.execution.resident import ResidentTrainer
+    from shadowspill_b200.models.config import preset
+    from shadowspill_b200.models.lora import LoRAConfig
+    cfg = preset("llama3-tiny")
+    base = ResidentTrainer(cfg, device="cpu", dtype=torch.float32, seed=123).state_dict()
+    hf.save_hf(cfg, base, tmp_path / "base")
+    setup = replace(_setup(tmp_path / "lora.ssp"), pretrained=str(tmp_path / "base"), operations=("step",),
+                    lora=LoRAConfig(rank=8, alpha=16.0).to_json(), lr=1e-2)
+    session = TrainingSession(setup)
+    state = session.executor.state_dict()
+    q = state["layer0.wq"]
+    Hq = cfg.n_heads * cfg.head_dim
+    assert torch.equal(q, base["layer0.wqkv"][:Hq])           # fused projection cut back into wq
+    assert torch.equal(state["embed.embed"], base["embed.embed"])
+    assert float(state["layer0.wq_lora_b"].abs().max()) == 0.0
+    losses = []
+    for i in range(3):
+        batch = make_batch(0, vocab=cfg.vocab_size, tokens_per_step=512, microbatch_tokens=256,
+                           median=60, min_len=8, max_len=128, slots=session.slots)
+        losses.append(session.step(batch).loss)
+    after = session.executor.state_dict()
+    assert losses[-1] < losses[0]
+    assert torch.equal(after["layer0.wq"], q)                  # the base stayed frozen
+    assert float(after["layer0.wq_lora_b"].abs().max()) > 0.0  # the adapter moved
+    session.close()

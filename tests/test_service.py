@@ -104,3 +104,20 @@ def test_newer_writer_fences_the_older_one(service):
             first.step(text_batch(_sequences(2))).result()
         assert e.value.status == 409 and "fenced" in str(e.value)
         second.close()
+
+
+def test_lora_run_through_the_service(service):
+    from shadowspill_b200.client import LoRA
+    with ServiceClient(service.url, token="secret") as svc:
+        trainer = svc.create_training_client(
+            Model("llama3-tiny", dtype="float32", lora=LoRA(rank=8, alpha=16.0)),
+            Optimizer(lr=1e-2, parameter_rounding="nearest"),
+            batch=BatchConfig(tokens_per_step=512, microbatch_tokens=256),
+            memory=Memory(device_gib=0.53, spill_gib=0.25), resources=Resources(gpus=1, backend="cpu"),
+            preparation=Preparation(profiling=ProfilingOptions(enabled=False), calibrate=False,
+                                    planning=PlanningOptions(minimum_object_bytes_evict_eligible=1024,
+                                                             workers=1)),
+            timeout=300).result()
+        losses = [trainer.step(text_batch(_sequences(0))).result().loss for _ in range(4)]
+        assert losses[-1] < losses[0]
+        trainer.close()
