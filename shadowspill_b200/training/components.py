@@ -107,7 +107,7 @@ class ResolvedTraining:
     budgets: dict[str, float]
 
 
-def _lora_record(rec: dict | None) -> dict | None:
+def _lora_record(rec: dict | None, is_moe: bool = False) -> dict | None:
     """Client ``LoRA`` record -> ``models.lora.LoRAConfig`` JSON."""
     if not rec:
         return None
@@ -117,6 +117,8 @@ def _lora_record(rec: dict | None) -> dict | None:
     wanted = rec.get("targets", ("attention", "experts"))
     targets: list[str] = []
     for t in wanted:                        # group names of the client record, or matrix names
+        if t == "experts" and not is_moe:
+            continue                        # a dense model has no routed banks to adapt
         for name in groups.get(t, (t,)):
             if name in DENSE_TARGETS and name not in targets:
                 targets.append(name)
@@ -204,7 +206,7 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
             "search": search, "collectives": ex.get("collectives", "auto"),
             "operations": list(body.get("operations", ("step",))),
             "trace_capacity": 65536 if ex.get("runtime_trace") else 0,
-            "lora": _lora_record(m.get("lora")), "objective": _objective_record(body.get("objective")),
+            "lora": _lora_record(m.get("lora"), cfg.is_moe), "objective": _objective_record(body.get("objective")),
             "expert_parallel": (body.get("parallelism") or {}).get("kind") == "expert_parallel",
             "pretrained": (m.get("weights", {}).get("location", "")
                            if m.get("weights", {}).get("source") == "checkpoint" else "")})
