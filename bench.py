@@ -114,6 +114,9 @@ def main() -> None:
                     help="comma list of programs the planner sweeps: <recompute share %%>[:<saved variant>] "
                          "or mix:<K>[:<variant>] (attention saved everywhere, K layers keep <variant>, default save)")
     ap.add_argument("--walks", default="breadth")
+    ap.add_argument("--lora-rank", type=int, default=0, help="train rank-r adapters on a frozen base")
+    ap.add_argument("--expert-parallel", action="store_true",
+                    help="multi-GPU runs of routed models: split the experts over the ranks")
     ap.add_argument("--report", default="", help="directory for the plan report")
     ap.add_argument("--collectives", default="auto", choices=["auto", "peer", "dist"],
                     help="peer = own kernels over NVLink peer memory; dist = NCCL baseline arm")
@@ -143,7 +146,11 @@ def main() -> None:
                           collectives=args.collectives,
                           candidate_selections=tuple(c for c in args.candidates.split(",") if c),
                           walks=tuple(args.walks.split(",")),
-                          trace_capacity=(1 << 16) if args.report else 0)
+                          trace_capacity=(1 << 16) if args.report else 0,
+                          lora=({"rank": args.lora_rank, "alpha": 2.0 * args.lora_rank,
+                                 "targets": ["wq", "wk", "wv", "wo", "w13", "w2"], "routed_experts": True,
+                                 "train_base": False} if args.lora_rank else None),
+                          expert_parallel=args.expert_parallel)
     log = (lambda m: print(f"[bench] {m}", file=sys.stderr, flush=True)) if rank == 0 else None
     session = TrainingSession(setup, log=log)  # build -> profile -> calibrate -> plan -> executor
     if rank == 0:

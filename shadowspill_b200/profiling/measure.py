@@ -160,6 +160,10 @@ def apply_profiles(program: Program, profiles: Profiles, workspace_margin: float
         # stages whose backward is derived by autograd allocate many large temporaries in
         # data-dependent order: leave the caching allocator room for fragmentation
         margin = max(workspace_margin, 1.25) if "HybridLayerStage" in t.profile_key else workspace_margin
+        if ":ep" in t.profile_key:
+            # profiled on one rank with its local experts; in the job the rows a rank receives
+            # depend on every rank's routing
+            margin = max(margin, 1.75)
         t.workspace_bytes = int(p.workspace_bytes * margin)
     if missing:
         raise KeyError(f"no profile for {sorted(set(missing))[:4]}")
