@@ -28,16 +28,23 @@ class PackedMicrobatch:
     positions: np.ndarray
     cu_seqlens: np.ndarray
     max_seqlen: int
+    extras: dict = None       # objective inputs, float32 [T] each
+
+    def __post_init__(self):
+        if self.extras is None:
+            self.extras = {}
 
     @property
     def nbytes(self) -> int:
         return sum(a.nbytes for a in (self.tokens, self.targets, self.weights, self.positions,
-                                      self.cu_seqlens))
+                                      self.cu_seqlens, *self.extras.values()))
 
 
 class BatchValidator:
-    def __init__(self, vocab_size: int, microbatch_tokens: int, microbatches: int, slots: int):
+    def __init__(self, vocab_size: int, microbatch_tokens: int, microbatches: int, slots: int,
+                 extra_fields: tuple = ()):
         self.vocab, self.capacity, self.bins, self.slots = vocab_size, microbatch_tokens, microbatches, slots
+        self.extra_fields = tuple(extra_fields)     # per-token inputs the run's objective reads
 
     def validate(self, datums: list[Datum]) -> None:
         if not datums:
@@ -50,6 +57,12 @@ class BatchValidator:
                 raise BatchError(f"datum {i} has token ids outside [0, {self.vocab})")
             if not np.isfinite(d.weights).all() or (d.weights < 0).any():
                 raise BatchError(f"datum {i} has negative or non-finite weights")
+            for name in self.extra_fields:
+                values = getattr(d, "extras", {}).get(name)
+                if values is None:
+                    raise BatchError(f"datum {i} lacks {name!r}, which this run's objective reads")
+                if len(values) != len(d) or not np.isfinite(values).all():
+                    raise BatchError(f"datum {i}: {name!r} must be finite with one entry per token")
             participating += float(d.weights.sum())
         if participating <= 0:
             raise BatchError("no position of the batch participates in the loss")
@@ -88,11 +101,17 @@ def pack_batch(datums: list[Datum], *, microbatch_tokens: int, microbatches: int
         targets = np.full(T, -1, np.int64)
         weights = np.zeros(T, np.float32)
         positions = np.zeros(T, np.int32)
+        names = sorted({k for d in datums for k in getattr(d, "extras", {})})
+        extras = {k: np.zeros(T, np.float32) for k in names}
         cu, pos = [0], 0
         for i in sorted(members):
             d = datums[i]
             n = len(d)
             tokens[pos:pos + n], targets[pos:pos + n], weights[pos:pos + n] = d.tokens, d.targets, d.weights
+            for k in names:
+                if k not in d.extras:
+                    raise BatchError(f"datum {i} lacks the objective input {k!r}")
+                extras[k][pos:pos + n] = d.extras[k]
             positions[pos:pos + n] = np.arange(n, dtype=np.int32)
             pos += n
             cu.append(pos)
@@ -102,5 +121,5 @@ def pack_batch(datums: list[Datum], *, microbatch_tokens: int, microbatches: int
         cu += [T] * (slots + 1 - len(cu))
         lens = np.diff(np.asarray(cu))
         out.append(PackedMicrobatch(tokens, targets, weights, positions,
-                                    np.asarray(cu, np.int32), int(max(2, lens.max()))))
+                                    np.asarray(cu, np.int32), int(max(2, lens.max())), extras))
     return out

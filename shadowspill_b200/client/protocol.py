@@ -105,7 +105,10 @@ def encode_microbatches(mbs) -> bytes:
     for i, mb in enumerate(mbs):
         for name in ("tokens", "targets", "weights", "positions", "cu_seqlens"):
             arrays[f"{i}.{name}"] = getattr(mb, name)
-    return encode_arrays({"kind": "microbatches", "count": len(mbs),
+        for name, values in (getattr(mb, "extras", None) or {}).items():
+            arrays[f"{i}.extra.{name}"] = values
+    extras = sorted((getattr(mbs[0], "extras", None) or {})) if mbs else []
+    return encode_arrays({"kind": "microbatches", "count": len(mbs), "extras": extras,
                           "max_seqlen": [int(mb.max_seqlen) for mb in mbs]}, arrays)
 
 
@@ -118,5 +121,7 @@ def decode_microbatches(blob: bytes):
     for i in range(header["count"]):
         out.append(PackedMicrobatch(*(np.array(arrays[f"{i}.{n}"]) for n in
                                       ("tokens", "targets", "weights", "positions", "cu_seqlens")),
-                                    max_seqlen=header["max_seqlen"][i]))
+                                    max_seqlen=header["max_seqlen"][i],
+                                    extras={n: np.array(arrays[f"{i}.extra.{n}"])
+                                            for n in header.get("extras", [])}))
     return out

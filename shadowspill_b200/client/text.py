@@ -7,7 +7,7 @@ batch the weight ``1/N`` so that the objective's plain sum is the batch mean
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 
 import numpy as np
 
@@ -17,6 +17,7 @@ class Datum:
     tokens: np.ndarray        # int64 [n]   model inputs
     targets: np.ndarray       # int64 [n]   next token, -1 where there is none
     weights: np.ndarray       # float32 [n] loss weight per position
+    extras: dict = field(default_factory=dict)   # objective inputs, float32 [n] each, indexed like targets
 
     def __len__(self) -> int:
         return int(self.tokens.shape[0])
@@ -42,10 +43,32 @@ def text_datum(tokens, loss_mask=None) -> Datum:
     return Datum(tok, targets, w)
 
 
+def policy_datum(tokens, response_mask, old_logprobs, advantages, reference_logprobs=None) -> Datum:
+    """A datum for the clipped policy objective. The per-token arrays are given per TOKEN
+    (``old_logprobs[i]`` is the behaviour policy's log-probability of token ``i``); they are
+    shifted here to the position that predicts that token, like the targets."""
+    d = text_datum(tokens, response_mask)
+    n = len(d)
+
+    def shifted(values, name):
+        a = np.asarray(values, dtype=np.float32).reshape(-1)
+        if a.shape[0] != n:
+            raise ValueError(f"{name} must have one entry per token")
+        out = np.zeros(n, dtype=np.float32)
+        out[:-1] = a[1:]
+        return out
+    d.extras["old_logprobs"] = shifted(old_logprobs, "old_logprobs")
+    d.extras["advantages"] = shifted(advantages, "advantages")
+    if reference_logprobs is not None:
+        d.extras["reference_logprobs"] = shifted(reference_logprobs, "reference_logprobs")
+    return d
+
+
 def text_batch(sequences, loss_masks=None) -> list[Datum]:
-    """Datums whose weights sum to one over the whole batch."""
+    """Datums whose weights sum to one over the whole batch. ``sequences`` may also hold
+    ready ``Datum`` objects (for example from ``policy_datum``), which are only re-weighted."""
     masks = loss_masks if loss_masks is not None else [None] * len(sequences)
-    datums = [text_datum(s, m) for s, m in zip(sequences, masks)]
+    datums = [s if isinstance(s, Datum) else text_datum(s, m) for s, m in zip(sequences, masks)]
     total = sum(float(d.weights.sum()) for d in datums)
     if total <= 0:
         raise ValueError("the batch has no position that participates in the loss")

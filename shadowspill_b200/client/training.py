@@ -48,7 +48,8 @@ class TrainingClient:
         self.slots, self.vocab, self.workers = geo["slots"], geo["vocab_size"], geo["workers"]
         self.packing = geo.get("packing", "best_fit")
         self.validator = BatchValidator(self.vocab, self.microbatch_tokens,
-                                        self.microbatches * self.workers, self.slots)
+                                        self.microbatches * self.workers, self.slots,
+                                        tuple(geo.get("extra_fields", ())))
         self.writer_id = uuid.uuid4().hex
         self.transport.request("POST", f"{self.route}/writers/{self.writer_id}", {})
         self.pool = cf.ThreadPoolExecutor(max_workers=max(2, max_pending_requests))

@@ -84,6 +84,13 @@ def default_registry() -> Registry:
         r.add_model(f"{name}@1", (lambda n=name: preset(n)), capabilities=("text", "packed"))
     r.add_objective("shadowspill/cross_entropy@1", lambda **kw: {"kind": "cross_entropy", **kw},
                     capabilities=("text",))
+    r.add_objective("shadowspill/clipped_policy@1",
+                    lambda clip_ratio=0.2, reference_beta=0.0: {"kind": "clipped_policy",
+                                                                "clip_ratio": clip_ratio,
+                                                                "reference_beta": reference_beta},
+                    capabilities=("text",))
+    r.add_objective("shadowspill/moe_balance@1", lambda coefficient=0.01: {"kind": "moe_balance",
+                                                                           "coefficient": coefficient})
     r.add_objective("shadowspill/sum@1", lambda terms=(): {"kind": "sum", "terms": list(terms)})
     r.add_optimizer("adamw@1", lambda **kw: {"kind": "adamw", **kw})
     r.add_optimizer("mlops/adamw@1", lambda **kw: {"kind": "adamw", **kw})    # the reference's id
@@ -210,7 +217,14 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
             "expert_parallel": (body.get("parallelism") or {}).get("kind") == "expert_parallel",
             "pretrained": (m.get("weights", {}).get("location", "")
                            if m.get("weights", {}).get("source") == "checkpoint" else "")})
-    geometry = {"microbatch_tokens": T, "microbatches": tokens // T, "slots": slots,
+    ob = _objective_record(body.get("objective"))
+    if ob:
+        from ..models.objectives import Objective as _Ob
+        extra_fields = list(_Ob.from_json(ob).extra_fields)
+    else:
+        extra_fields = []
+    geometry = {"extra_fields": extra_fields,
+                "microbatch_tokens": T, "microbatches": tokens // T, "slots": slots,
                 "vocab_size": cfg.vocab_size, "workers": workers, "packing": b.get("packing", "best_fit"),
                 "tokens_per_step": tokens * workers}
     return ResolvedTraining(cfg, workers, setups, geometry, prov,

@@ -31,7 +31,8 @@ from .channel import Channel, ChannelClosed
 def _to_host_batches(payload: bytes):
     from ..client.protocol import decode_microbatches
     from ..data.synthetic import HostMicrobatch
-    return [HostMicrobatch(m.tokens, m.targets, m.weights, m.positions, m.cu_seqlens, m.max_seqlen)
+    return [HostMicrobatch(m.tokens, m.targets, m.weights, m.positions, m.cu_seqlens, m.max_seqlen,
+                           dict(getattr(m, "extras", None) or {}))
             for m in decode_microbatches(payload)]
 
 

@@ -121,3 +121,35 @@ def test_lora_run_through_the_service(service):
         losses = [trainer.step(text_batch(_sequences(0))).result().loss for _ in range(4)]
         assert losses[-1] < losses[0]
         trainer.close()
+
+
+def test_policy_objective_through_the_service(service):
+    """Clipped-policy training end to end: per-token old log-probabilities and advantages travel
+    from client datums through packing and the wire to the head kernel."""
+    from shadowspill_b200.client import Objective, policy_datum
+    rng = np.random.default_rng(5)
+
+    def datums(seed):
+        out = []
+        for seq in _sequences(seed):
+            n = len(seq)
+            out.append(policy_datum(seq, np.ones(n), rng.normal(-6.0, 0.1, n), rng.normal(0.0, 1.0, n)))
+        return text_batch(out)
+    with ServiceClient(service.url, token="secret") as svc:
+        trainer = svc.create_training_client(
+            Model("llama3-tiny", dtype="float32"), Optimizer(lr=1e-3, parameter_rounding="nearest"),
+            objective=Objective("shadowspill/clipped_policy@1", {"clip_ratio": 0.2}),
+            batch=BatchConfig(tokens_per_step=512, microbatch_tokens=256),
+            memory=Memory(device_gib=0.53, spill_gib=0.25), resources=Resources(gpus=1, backend="cpu"),
+            preparation=Preparation(profiling=ProfilingOptions(enabled=False), calibrate=False,
+                                    planning=PlanningOptions(minimum_object_bytes_evict_eligible=1024,
+                                                             workers=1)),
+            timeout=300).result()
+        first = trainer.step(datums(0)).result().loss
+        second = trainer.step(datums(0)).result().loss
+        assert np.isfinite(first) and np.isfinite(second) and first != second
+        # a batch without the objective's inputs is refused locally, before anything is sent
+        with pytest.raises(BatchError):
+            trainer.step(text_batch(_sequences(1)))
+        assert np.isfinite(trainer.step(datums(1)).result().loss)
+        trainer.close()
