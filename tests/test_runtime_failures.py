@@ -145,3 +145,13 @@ def test_controller_never_replays_and_propagates_failed_dependencies():
     c.register({"request_id": "c", "operation": "step", "dependencies": ["b"], "digest": "d3"})
     assert c.wait("c", 5).state == "rejected" and calls == ["a", "b"]
     c.stop()
+
+
+def test_invalid_worker_group_still_accepts_close():
+    from shadowspill_b200.training.group import WorkerFailure, WorkerGroup
+    import pytest
+    g = WorkerGroup.__new__(WorkerGroup)
+    g.valid, g.chans, g.procs = False, [object()], []
+    with pytest.raises(WorkerFailure):
+        g.execute("r1", "step", {})
+    assert g.execute("r2", "close", {})[0]["state"] == "completed"
