@@ -129,7 +129,12 @@ struct RsAdamArgs {
 // [lo, hi). p/m/v point at the owned shard (element 0 of the shard = element lo).
 // full_param, when non-null, is the local full parameter buffer that also receives
 // the updated owned slice (so the next all-gather source is already in place).
-__global__ void rs_adamw_kernel(PeerPtrs grads, __nv_bfloat16* __restrict__ p,
+//
+// mc_grad, when non-null, is the NVSwitch multicast address of the same bf16 gradient tensor:
+// one multimem.ld_reduce returns the sum over every rank's copy, reduced inside the switch
+// (fp32 accumulation, bf16 result), instead of `world` separate peer loads.
+__global__ void rs_adamw_kernel(PeerPtrs grads, const __nv_bfloat16* __restrict__ mc_grad,
+                                __nv_bfloat16* __restrict__ p,
                                 __nv_bfloat16* __restrict__ m, __nv_bfloat16* __restrict__ v,
                                 long long lo, long long hi, int world, RsAdamArgs a) {
   const long long n = hi - lo;
@@ -139,6 +144,14 @@ __global__ void rs_adamw_kernel(PeerPtrs grads, __nv_bfloat16* __restrict__ p,
     const long long e0 = i << 3;
     const int cnt = static_cast<int>(min(8LL, n - e0));
     float g[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (mc_grad != nullptr && cnt == 8) {
+      uint4 u;
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w)
+                   : "l"(mc_grad + lo + e0)
+                   : "memory");
+      up8(u, g);
+    } else
     for (int j = 0; j < world; ++j) {
       if (a.g_f32) {
         const float* src = reinterpret_cast<const float*>(grads.p[j]) + lo + e0;
@@ -276,7 +289,34 @@ int ss_rs_adamw(void* const* grad_ptrs, void* p, void* m, void* v, long long lo,
   a.offset = offset; a.sr_param = sr_param; a.sr_state = sr_state; a.g_f32 = g_f32;
   const long long nvec = (hi - lo + 7) >> 3;
   rs_adamw_kernel<<<grid_of(nvec, 256, 148 * 8), 256, 0, (cudaStream_t)stream>>>(
-      g, (__nv_bfloat16*)p, (__nv_bfloat16*)m, (__nv_bfloat16*)v, lo, hi, world, a);
+      g, nullptr, (__nv_bfloat16*)p, (__nv_bfloat16*)m, (__nv_bfloat16*)v, lo, hi, world, a);
+  return (int)cudaGetLastError();
+}
+
+// Same update with the gradient sum taken inside the NVSwitch: mc_grad is the multicast
+// address of the bf16 gradient tensor (every rank's copy bound to one multicast object).
+// grad_ptrs still serves the ragged tail (fewer than eight elements).
+int ss_rs_adamw_nvls(void* const* grad_ptrs, const void* mc_grad, void* p, void* m, void* v,
+                     long long lo, long long hi, int world, float lr, float beta1, float beta2,
+                     float eps, float weight_decay, int step, float grad_scale,
+                     unsigned long long seed, unsigned long long offset, int sr_param, int sr_state,
+                     void* stream) {
+  if (world < 1 || world > MAX_RANKS || (lo & 7) || ((offset) & 7) || mc_grad == nullptr ||
+      (reinterpret_cast<uintptr_t>(mc_grad) & 15))
+    return -2;
+  if (hi <= lo) return 0;
+  PeerPtrs g;
+  for (int j = 0; j < world; ++j) g.p[j] = grad_ptrs[j];
+  RsAdamArgs a;
+  a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.weight_decay = weight_decay;
+  a.bias1 = 1.f - powf(beta1, (float)step); a.bias2 = 1.f - powf(beta2, (float)step);
+  a.grad_scale = grad_scale;
+  a.seed = seed ^ (0x9E3779B97F4A7C15ull * (unsigned long long)(step + 1));
+  a.offset = offset; a.sr_param = sr_param; a.sr_state = sr_state; a.g_f32 = 0;
+  const long long nvec = (hi - lo + 7) >> 3;
+  rs_adamw_kernel<<<grid_of(nvec, 256, 148 * 8), 256, 0, (cudaStream_t)stream>>>(
+      g, (const __nv_bfloat16*)mc_grad, (__nv_bfloat16*)p, (__nv_bfloat16*)m, (__nv_bfloat16*)v, lo, hi,
+      world, a);
   return (int)cudaGetLastError();
 }
 

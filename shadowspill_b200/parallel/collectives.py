@@ -32,6 +32,9 @@ _lib.register("ss_peer_allgather", [_c.c_p, _c.c_p, _c.c_ll, _c.c_ll, _c.c_int, 
 _lib.register("ss_rs_adamw", [_c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_ll, _c.c_ll, _c.c_int, _c.c_int,
                               _c.c_f, _c.c_f, _c.c_f, _c.c_f, _c.c_f, _c.c_int, _c.c_f, _c.c_ull,
                               _c.c_ull, _c.c_int, _c.c_int, _c.c_p])
+_lib.register("ss_rs_adamw_nvls", [_c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_ll, _c.c_ll, _c.c_int,
+                                   _c.c_f, _c.c_f, _c.c_f, _c.c_f, _c.c_f, _c.c_int, _c.c_f, _c.c_ull,
+                                   _c.c_ull, _c.c_int, _c.c_int, _c.c_p])
 _lib.register("ss_peer_allreduce_f32", [_c.c_p, _c.c_p, _c.c_ll, _c.c_int, _c.c_p])
 
 
@@ -99,6 +102,12 @@ class PeerCollectives:
         self.handle = symm_mem.rendezvous(pool, self.group.group_name)
         self.bases = [int(p) for p in self.handle.buffer_ptrs]
         self.local_base = pool.data_ptr()
+        # NVSwitch multicast view of the pool (0 when the fabric or the driver has none). Off unless
+        # SS_NVLS=1: a rank that dies while bound to a multicast object can fault its peers, so
+        # the in-switch reduction is opted into by jobs that do not expect rank loss.
+        import os
+        mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        self.mc_base = mc if os.environ.get("SS_NVLS", "0") == "1" else 0
         if self.bases[self.rank] != self.local_base:
             raise RuntimeError("symmetric pool base does not match the local tensor")
         self.flags = symm_mem.empty(64, dtype=torch.int32, device=pool.device)
@@ -137,6 +146,13 @@ class PeerCollectives:
         lo = self.rank * per
         hi = min(n, lo + per)
         if hi <= lo:
+            return
+        if self.mc_base and grad.dtype == torch.bfloat16:
+            off = grad.data_ptr() - self.local_base
+            _lib.check(_lib.lib().ss_rs_adamw_nvls(
+                self._peers(grad), self.mc_base + off, p.data_ptr(), m.data_ptr(), v.data_ptr(), lo, hi,
+                self.world, lr, beta1, beta2, eps, weight_decay, step, grad_scale, seed, offset,
+                int(stochastic_param), int(stochastic_state), _lib.stream_ptr()), "ss_rs_adamw_nvls")
             return
         _lib.check(_lib.lib().ss_rs_adamw(
             self._peers(grad), p.data_ptr(), m.data_ptr(), v.data_ptr(), lo, hi, self.world,

@@ -5,7 +5,8 @@
 
 Per rank, for a tensor of the given size (default: one Llama-3-8B layer, 416 MiB of bf16):
   all-gather        own pull kernel (`ss_peer_allgather`) vs `dist.all_gather_into_tensor`
-  reduce-scatter+AdamW  own fused kernel (`ss_rs_adamw`: peers' gradient slices are read over
+  reduce-scatter+AdamW  (with SS_NVLS=1 and a multicast-capable fabric the gradient sum is one
+                    multimem.ld_reduce inside the NVSwitch)  own fused kernel (`ss_rs_adamw`: peers' gradient slices are read over
                     NVLink, summed and applied to this rank's shard of weights and moments
                     in one pass) vs `dist.reduce_scatter_tensor` followed by the local AdamW kernel
 CUDA-event times, max over ranks, 3 warm-ups; roofline = bytes that must cross NVLink per rank
@@ -91,8 +92,9 @@ def main(argv=None) -> None:
 
     rows = []
     link_bytes = (world - 1) * per * 2                                    # what each rank must receive
+    rs_name = "rs_adamw_own_nvls" if peer.mc_base else "rs_adamw_own"     # SS_NVLS=1: in-switch sum
     for name, fn, hbm_bytes in (("allgather_own", ag_own, n * 2), ("allgather_nccl", ag_lib, n * 2),
-                                ("rs_adamw_own", rs_own, per * 2 * (world + 6)),
+                                (rs_name, rs_own, per * 2 * (world + 6)),
                                 ("rs_nccl_then_adamw", rs_lib, per * 2 * (world + 8))):
         ms = _timed(fn, dev)
         floor_ms = max(link_bytes / (LINK_GBS * 1e9), hbm_bytes / (a.hbm_gbs * 1e9)) * 1e3

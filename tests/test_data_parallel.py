@@ -10,8 +10,8 @@ import torch
 WORKER = Path(__file__).with_name("_dp_worker.py")
 
 
-def _launch(world, device, arm, port):
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
+def _launch(world, device, arm, port, **extra_env):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0", **extra_env)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), str(WORKER), device, arm]
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
@@ -37,3 +37,11 @@ def test_two_gpus_expert_parallel_planned_execution():
     GPUs (peer-memory dispatch/combine inside the layer tasks) and matches the resident
     single-process model that holds every expert."""
     _launch(2, "cuda", "ep", 29617)
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_two_gpus_in_switch_gradient_sum():
+    """The sharded optimizer update with its gradient sum taken by multimem.ld_reduce inside the
+    NVSwitch (SS_NVLS=1; falls back to peer loads where the fabric has no multicast)."""
+    _launch(2, "cuda", "peer", 29619, SS_NVLS="1")
