@@ -41,7 +41,7 @@ GIB = 1 << 30
 def reference_arm() -> None:
     reason = ("reference not installable offline: its engine needs torch>=2.13,<2.14 and the "
               "external mlops kernel library cloned from GitHub; neither is on this image "
-              "(pip install of /root/reference fails at metadata generation)")
+              "(its pip install fails at metadata generation)")
     ref = ROOT / "baseline" / "_ref"
     if ref.exists() and any(ref.iterdir()):
         try:
