@@ -106,11 +106,14 @@ class LiveRun:
         op, args = req["operation"], dict(req.get("arguments", {}))
         payloads = None
         if payload is not None:
+            from ..training.inputs import InputError, route, validate_microbatches
             mbs = decode_microbatches(payload)
             w, per = self.resolved.workers, self.resolved.geometry["microbatches"]
-            if len(mbs) != w * per:
-                raise WorkerFailure(f"expected {w * per} microbatches, got {len(mbs)}", "not_started")
-            payloads = [encode_microbatches(mbs[r * per:(r + 1) * per]) for r in range(w)]   # route
+            try:
+                validate_microbatches(mbs, self.resolved.geometry)      # authoritative, before any worker
+            except InputError as exc:
+                raise WorkerFailure(f"batch rejected: {exc}", "not_started") from None
+            payloads = [encode_microbatches(part) for part in route(mbs, w, per)]
         if op in ("save", "export"):
             name = args.get("name") or uuid.uuid4().hex[:8]
             args["directory"] = str(self.server.root / "checkpoints" / self.session / name)
