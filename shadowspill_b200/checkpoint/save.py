@@ -70,6 +70,9 @@ def save_checkpoint(executor, directory: str | Path, *, metadata: dict[str, Any]
     if metadata is not None and len(json.dumps(metadata)) > (16 << 20):
         raise ValueError("checkpoint metadata is limited to 16 MiB of JSON")
     directory = Path(directory)
+    if getattr(executor, "replicas", 1) > 1 and executor.global_rank >= executor.world:
+        # replicas hold identical state: the first replica's ranks write the checkpoint
+        return directory / f"rank{executor.rank}.tar"
     entries = state_entries(executor)
     writer = ArchiveWriter(directory / f"rank{executor.rank}.tar")
     try:

@@ -245,7 +245,14 @@ class Executor:
         self.torch_device = torch.device(f"cuda:{device_index}") if self.cuda else torch.device("cpu")
         self.hyper = hyper or Hyperparameters()
         self.seed = seed
-        self.world, self.rank = desc.world_size, desc.rank
+        # `world` / `rank`: the shard group this rank stores state with; with replicas the job has
+        # world * replicas ranks and `global_rank` is this rank's index among all of them
+        self.world, self.rank = desc.world_size, desc.shard_rank
+        self.global_rank, self.total_ranks, self.replicas = desc.rank, desc.total_ranks, desc.replicas
+        if desc.replicas > 1 and desc.world_size == 1:
+            raise NotImplementedError("replicas need a shard group of at least two ranks")
+        if desc.replicas > 1 and desc.expert_parallel:
+            raise NotImplementedError("expert parallelism runs on one replica")
         extra_plans = dict(extra_plans or {})
         device_bytes = max([plan.device_bytes] + [p.device_bytes for p, _ in extra_plans.values()])
         spill_bytes = max([plan.spill_bytes] + [p.spill_bytes for p, _ in extra_plans.values()])
@@ -256,9 +263,9 @@ class Executor:
             if mode == "peer":
                 torch.cuda.set_device(device_index)
                 pool = pc.allocate_symmetric_pool(device_bytes, self.torch_device)
-                coll = pc.PeerCollectives(pool)
+                coll = pc.PeerCollectives(pool, ranks_per_replica=self.world)
             else:
-                coll = pc.DistCollectives()
+                coll = pc.DistCollectives(ranks_per_replica=self.world)
         self.collectives = coll
         if self.world > 1:
             # refuse to start if the ranks would not issue the same collectives in the same order

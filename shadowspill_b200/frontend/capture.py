@@ -95,12 +95,24 @@ class TrainingDescription:
     objective: "Objective | None" = None
     lora: "LoRAConfig | None" = None
     expert_parallel: bool = False     # routed layers keep 1/world of the experts per rank
+    # hierarchical data parallelism: ``world_size`` ranks share one sharded copy of the state and
+    # ``replicas`` such groups run side by side (rank = replica * world_size + shard index);
+    # gradients are summed over every rank, weights are gathered inside a replica
+    replicas: int = 1
 
     def __post_init__(self) -> None:
         extras = self.objective.extra_fields if self.objective is not None else ()
         if tuple(self.geometry.extra_fields) != tuple(extras):
             from dataclasses import replace as _replace
             self.geometry = _replace(self.geometry, extra_fields=tuple(extras))
+
+    @property
+    def shard_rank(self) -> int:
+        return self.rank % self.world_size
+
+    @property
+    def total_ranks(self) -> int:
+        return self.world_size * self.replicas
 
     def stages(self):
         ep = (self.world_size, self.rank) if (self.expert_parallel and self.world_size > 1) else None
@@ -347,13 +359,14 @@ def _build(desc: TrainingDescription) -> Program:
 def build_step(cfg: DecoderConfig, geometry: BatchGeometry,
                ordering: StepDataOrdering | None = None, *, dtype=torch.bfloat16,
                grad_dtype=None, selection: dict[int, str] | None = None, world_size: int = 1,
-               rank: int = 0, objective=None, lora=None, expert_parallel: bool = False):
+               rank: int = 0, objective=None, lora=None, expert_parallel: bool = False,
+               replicas: int = 1):
     """Forward + backward + optimizer of one global batch. Returns ``(Program, description)``.
     ``world_size > 1`` builds the data-parallel form: weights and AdamW moments are
     stored as 1/N shards, gathered before use and updated shard-locally."""
     desc = TrainingDescription(cfg, geometry, ordering or StepDataOrdering(), dtype,
                                grad_dtype or dtype, dict(selection or {}), "step", world_size,
-                               rank, objective, lora, expert_parallel)
+                               rank, objective, lora, expert_parallel, replicas)
     return _build(desc), desc
 
 

@@ -49,10 +49,20 @@ class DistCollectives:
     """torch.distributed arm (NCCL / gloo)."""
     name = "dist"
 
-    def __init__(self, group=None):
+    def __init__(self, group=None, ranks_per_replica: int | None = None):
+        """With ``ranks_per_replica`` smaller than the job, weights are gathered inside this
+        rank's replica group and gradients are summed over every rank of the job."""
         self.group = group
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        total = dist.get_world_size(group) if dist.is_initialized() else 1
+        global_rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = ranks_per_replica or total
+        self.rank = global_rank % self.world
+        self.shard_group = group
+        if self.world != total:
+            for r in range(total // self.world):       # every rank creates every subgroup, same order
+                g = dist.new_group(list(range(r * self.world, (r + 1) * self.world)))
+                if r == global_rank // self.world:
+                    self.shard_group = g
 
     def barrier_begin(self) -> None:
         pass
@@ -67,7 +77,7 @@ class DistCollectives:
             full.view(-1)[:n].copy_(shard.view(-1)[:n])
             return
         parts = [torch.empty_like(shard.view(-1)) for _ in range(self.world)]
-        dist.all_gather(parts, shard.view(-1).contiguous(), group=self.group)
+        dist.all_gather(parts, shard.view(-1).contiguous(), group=self.shard_group)
         flat = full.view(-1)
         for k, part in enumerate(parts):
             lo = k * per
@@ -78,8 +88,8 @@ class DistCollectives:
         """Sum ``grad`` over ranks; update this rank's owned slice of (p, m, v)."""
         n, per = grad.numel(), p.numel()
         g = grad.view(-1).clone()
-        if self.world > 1:
-            dist.all_reduce(g, group=self.group)
+        if dist.is_initialized() and dist.get_world_size(self.group) > 1:
+            dist.all_reduce(g, group=self.group)          # over every rank, replicas included
         lo = self.rank * per
         hi = min(n, lo + per)
         if hi <= lo:
@@ -93,11 +103,18 @@ class PeerCollectives:
     """Own kernels over the symmetric device pool."""
     name = "peer"
 
-    def __init__(self, pool: torch.Tensor, group=None):
+    def __init__(self, pool: torch.Tensor, group=None, ranks_per_replica: int | None = None):
+        """``ranks_per_replica``: size of the shard group (default: every rank). With replicas
+        the pool is still symmetric over the whole job: gathers read the ranks of this replica,
+        the fused update reads every rank's gradient."""
         import torch.distributed._symmetric_memory as symm_mem
         self.group = group or dist.group.WORLD
-        self.world = dist.get_world_size(self.group)
-        self.rank = dist.get_rank(self.group)
+        self.total = dist.get_world_size(self.group)
+        self.global_rank = dist.get_rank(self.group)
+        self.shard_world = ranks_per_replica or self.total
+        self.shard_rank = self.global_rank % self.shard_world
+        self.replica_base = self.global_rank - self.shard_rank
+        self.world, self.rank = self.total, self.global_rank      # barrier and peer tables span the job
         self.pool = pool
         self.handle = symm_mem.rendezvous(pool, self.group.group_name)
         self.bases = [int(p) for p in self.handle.buffer_ptrs]
@@ -134,16 +151,20 @@ class PeerCollectives:
     barrier_end = _barrier
 
     def all_gather(self, shard: torch.Tensor, full: torch.Tensor) -> None:
+        peers = self._peers(shard)
+        if self.shard_world != self.total:       # this replica's ranks only
+            peers = (C.c_void_p * self.shard_world)(
+                *[peers[self.replica_base + j] for j in range(self.shard_world)])
         _lib.check(_lib.lib().ss_peer_allgather(
-            self._peers(shard), full.data_ptr(), shard.numel() * shard.element_size(),
-            full.numel() * full.element_size(), self.rank, self.world, _lib.stream_ptr()),
+            peers, full.data_ptr(), shard.numel() * shard.element_size(),
+            full.numel() * full.element_size(), self.shard_rank, self.shard_world, _lib.stream_ptr()),
             "ss_peer_allgather")
 
     def reduce_scatter_adamw(self, grad: torch.Tensor, p, m, v, *, offset: int, lr, beta1, beta2,
                              eps, weight_decay, step, grad_scale, seed, stochastic_param,
                              stochastic_state) -> None:
         n, per = grad.numel(), p.numel()
-        lo = self.rank * per
+        lo = self.shard_rank * per           # the slice this rank owns inside its replica
         hi = min(n, lo + per)
         if hi <= lo:
             return

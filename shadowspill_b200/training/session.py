@@ -75,6 +75,7 @@ class TrainingSetup:
     lora: dict | None = None
     objective: dict | None = None
     expert_parallel: bool = False        # routed layers keep 1/world of the experts per rank
+    ranks_per_replica: int = 0           # 0 = one replica; else state is sharded inside groups of this size
     pretrained: str = ""                 # directory of Hugging Face safetensors to start from
     # content-addressed store of task profiles shared between runs ("" = none)
     store: str = ""
@@ -126,22 +127,30 @@ class TrainingSession:
             selections = [{}]
             variants = [(walk, {}) for walk in setup.walks]
         choices = dict(objective=self.objective, lora=self.lora)
+        shard_world = setup.ranks_per_replica or world
+        if world % shard_world:
+            raise ValueError("world_size must be a multiple of ranks_per_replica")
+        replicas = world // shard_world
+
+        def with_replicas(built):
+            built[1].replicas = replicas          # programs depend on the shard count only
+            return built
 
         def build(index: int):
             walk, sel = variants[index]
             order = StepDataOrdering(walk=walk, optimizer="stage_interleaved" if walk == "breadth" else "tail")
-            return build_step(self.cfg, self.geometry, order, dtype=self.dtype, selection=sel,
-                              world_size=world, rank=rank, expert_parallel=setup.expert_parallel,
-                              **choices)
+            return with_replicas(build_step(self.cfg, self.geometry, order, dtype=self.dtype,
+                                            selection=sel, world_size=shard_world, rank=rank,
+                                            expert_parallel=setup.expert_parallel, **choices))
 
         def build_extra(op: str):
-            kw = dict(dtype=self.dtype, world_size=world, rank=rank, **choices)
+            kw = dict(dtype=self.dtype, world_size=shard_world, rank=rank, **choices)
             if op == "forward_backward":
-                return build_forward_backward(self.cfg, self.geometry, StepDataOrdering(), **kw)
+                return with_replicas(build_forward_backward(self.cfg, self.geometry, StepDataOrdering(), **kw))
             if op == "optim_step":
-                return build_optimizer(self.cfg, self.geometry, **kw)
+                return with_replicas(build_optimizer(self.cfg, self.geometry, **kw))
             if op == "forward":
-                return build_forward(self.cfg, self.geometry, StepDataOrdering(), **kw)
+                return with_replicas(build_forward(self.cfg, self.geometry, StepDataOrdering(), **kw))
             raise ValueError(f"unknown operation {op!r}")
 
         extra_ops = [op for op in setup.operations if op != "step"]

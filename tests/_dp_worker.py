@@ -23,6 +23,9 @@ def main():
     expert_parallel = arm == "ep"         # routed model, experts split over the ranks
     if expert_parallel:
         arm = "peer"
+    replicas = 1
+    if arm.startswith("replicas-"):       # e.g. replicas-dist / replicas-peer on 4 ranks: 2 x 2
+        replicas, arm = 2, arm.split("-", 1)[1]
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     cuda = device == "cuda"
     if cuda:
@@ -38,8 +41,9 @@ def main():
         cfg = replace(preset("olmoe-tiny"), d_model=256, head_dim=64, vocab_size=1024)
     T, n_mb = 256, 2
     geo = BatchGeometry(T, n_mb, slots=16, mean_seqlen=64)
-    prog, desc = build_step(cfg, geo, StepDataOrdering(), dtype=dtype, world_size=world, rank=rank,
-                            expert_parallel=expert_parallel)
+    shard_world = world // replicas
+    prog, desc = build_step(cfg, geo, StepDataOrdering(), dtype=dtype, world_size=shard_world, rank=rank,
+                            expert_parallel=expert_parallel, replicas=replicas)
     total = sum(o.bytes for o in prog.objects)
     plan = plan_program(prog, MemoryBudgets(total, 64 << 20, headroom_bytes=0), CommunicationInfo(),
                         SearchOptions(minimum_object_bytes_evict_eligible=1024, workers=1,
@@ -81,7 +85,7 @@ def main():
             per = p.numel // p.shape[0]
             lo, hi = p.expert_lo * per, (p.expert_lo + p.shape[0]) * per
         else:
-            lo = rank * shard.numel()
+            lo = (rank % shard_world) * shard.numel()
             hi = min(full.numel(), lo + shard.numel())
         if hi <= lo:
             continue

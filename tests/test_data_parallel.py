@@ -23,6 +23,12 @@ def test_two_ranks_gloo_match_resident():
     _launch(2, "cpu", "dist", 29611)
 
 
+def test_two_replicas_of_two_shards_gloo_match_resident():
+    """Hierarchical data parallelism: state sharded inside groups of two ranks, two such groups;
+    gradients are summed over all four ranks, weights are gathered inside a group."""
+    _launch(4, "cpu", "replicas-dist", 29621)
+
+
 @pytest.mark.gpu
 @pytest.mark.multigpu
 @pytest.mark.parametrize("arm", ["peer", "dist"])
@@ -45,3 +51,12 @@ def test_two_gpus_in_switch_gradient_sum():
     """The sharded optimizer update with its gradient sum taken by multimem.ld_reduce inside the
     NVSwitch (SS_NVLS=1; falls back to peer loads where the fabric has no multicast)."""
     _launch(2, "cuda", "peer", 29619, SS_NVLS="1")
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_four_gpus_two_replicas_peer_kernels():
+    import torch
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs four GPUs")
+    _launch(4, "cuda", "replicas-peer", 29623)
