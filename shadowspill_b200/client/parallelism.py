@@ -18,10 +18,12 @@ def data_parallel(ranks: int, *, weights: str = "sharded", gradients: str = "sha
             raise ValueError(f"{name} must be 'sharded' or 'replicated'")
     if ranks < 1 or replicas < 1:
         raise ValueError("ranks and replicas must be positive")
+    if replicas > 1 and ranks < 2:
+        raise ValueError("replicas repeat a shard group of at least two ranks")
     if "sharded" in (weights, gradients) and optimizer != "sharded":
         raise ValueError("optimizer state must shard over the same group as sharded weights/gradients")
     return {"kind": "data_parallel", "ranks_per_replica": ranks, "num_replicas": replicas,
-            "groups": {"all_ranks": list(range(ranks * replicas))},
+            "groups": {"all_ranks": list(range(ranks))},      # ranks of one replica
             "storage": {"weights": weights, "gradients": gradients, "optimizer": optimizer},
             "min_shard_bytes": min_shard_bytes, "inputs": {"placement": "split_microbatches"}}
 

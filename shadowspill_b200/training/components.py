@@ -164,7 +164,11 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
     registry.get("optimizer", opt["id"])
     res = body.get("resources", {})
     par = body.get("parallelism") or {}
-    workers = int(par.get("ranks_per_replica", res.get("gpus", 1))) * int(par.get("num_replicas", 1))
+    per_replica = int(par.get("ranks_per_replica", res.get("gpus", 1)))
+    replicas = int(par.get("num_replicas", 1))
+    if replicas > 1 and par.get("kind") == "expert_parallel":
+        raise ValueError("expert parallelism runs as one replica")
+    workers = per_replica * replicas
     backend = res.get("backend", "cuda")
     device = "cuda" if backend == "cuda" else "cpu"
     if device == "cuda" and workers > max(1, hardware.get("gpus", 0)):
@@ -205,6 +209,7 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
             "seed": int(m.get("weights", {}).get("seed", ex.get("seed", 0))),
             "dtype": m.get("dtype", "bfloat16"), "stochastic_rounding": sr, "device": device,
             "device_index": rank if device == "cuda" else 0, "rank": rank, "world_size": workers,
+            "ranks_per_replica": per_replica if replicas > 1 else 0,
             "walks": list(build.get("walks", ("breadth",))),
             "recompute_shares": list(build.get("recompute_shares", (100,))),
             "saved_variant": saved_variant,

@@ -131,6 +131,8 @@ class TrainingSession:
         if world % shard_world:
             raise ValueError("world_size must be a multiple of ranks_per_replica")
         replicas = world // shard_world
+        if replicas > 1 and shard_world < 2:
+            raise ValueError("replicas repeat a shard group of at least two ranks")
 
         def with_replicas(built):
             built[1].replicas = replicas          # programs depend on the shard count only

@@ -153,3 +153,23 @@ def test_policy_objective_through_the_service(service):
             trainer.step(text_batch(_sequences(1)))
         assert np.isfinite(trainer.step(datums(1)).result().loss)
         trainer.close()
+
+
+def test_two_replicas_of_two_ranks_through_the_service(service):
+    """``data_parallel(2, replicas=2)``: four gloo workers, state sharded inside each pair."""
+    from shadowspill_b200.client import data_parallel
+    with ServiceClient(service.url, token="secret") as svc:
+        trainer = svc.create_training_client(
+            Model("llama3-tiny", dtype="float32"), Optimizer(lr=3e-3, parameter_rounding="nearest"),
+            batch=BatchConfig(tokens_per_step=512, microbatch_tokens=256),
+            memory=Memory(device_gib=0.53, spill_gib=0.25), resources=Resources(gpus=4, backend="cpu"),
+            parallelism=data_parallel(2, replicas=2),
+            preparation=Preparation(profiling=ProfilingOptions(enabled=False), calibrate=False,
+                                    planning=PlanningOptions(minimum_object_bytes_evict_eligible=1024,
+                                                             workers=1)),
+            timeout=600).result()
+        assert trainer.info["workers"] == 4
+        batches = [text_batch(_sequences(s, n=32)) for s in (0, 0, 0, 0)]
+        losses = [trainer.step(b).result().loss for b in batches]
+        assert losses[-1] < losses[0]
+        trainer.close()
