@@ -1,22 +1,33 @@
 """Hugging Face weight names <-> this framework's stage parameters.
 
 ``to_hf(cfg, state)`` turns ``{"<stage>.<param>": tensor}`` into a Hugging Face style
-state dict (fused projections are cut back into ``q_proj / k_proj / v_proj`` and
-``gate_proj / up_proj``; expert banks into per-expert matrices); ``from_hf`` is the
-inverse and is how pretrained weights enter a run. ``save_hf`` / ``load_hf`` read and
-write ``model.safetensors`` plus a ``config.json`` with the architecture fields.
-Rotary tables are computed, not stored, and the rotate-half convention matches, so no
-projection is permuted (as in the reference's per-family ``checkpoint.py``, e.g.
-packages/workloads/src/shadowspill_workloads/models/llama3/checkpoint.py:20-55).
+state dict and ``from_hf`` is the inverse; that is how pretrained weights enter a run.
+``save_hf`` / ``load_hf`` read and write ``model.safetensors`` plus a ``config.json``
+with the architecture fields. Rotary tables are computed, not stored, and the
+rotate-half convention matches, so no projection is permuted.
 
-Covered: llama3, qwen3 (dense layers), olmoe / qwen3moe (routed layers). The Gated
-DeltaNet families keep this framework's own names on export (their Hugging Face
-layout interleaves projections per head group; not mapped yet).
+Every parameter has one *source*: a checkpoint tensor as it is, several tensors joined
+on dimension 0 (fused ``qkv`` / ``gate|up`` projections), per-expert matrices stacked
+into a bank, or a per-head de-interleave. The Qwen 3.5 families differ in four ways
+(reference: packages/workloads/src/shadowspill_workloads/models/qwen35/checkpoint.py:1-80,
+models/qwen35moe/checkpoint.py:1-60, models/llama3/checkpoint.py:20-55):
+
+* their text decoder's keys begin ``model.language_model.`` (the checkpoint is the
+  vision-language model; vision tower and multi-token-prediction head are skipped);
+* a full-attention block's ``q_proj`` carries the attention gate interleaved per head
+  (``[q_h, gate_h]`` for each head); this framework keeps all queries, then all gates;
+* a linear-attention block's ``w_qkvz`` is ``in_proj_qkv`` then ``in_proj_z``, ``w_ba``
+  is ``in_proj_b`` then ``in_proj_a``; ``conv1d.weight`` has a singleton middle axis;
+* the mixture family stores routed experts as fused banks ``mlp.experts.gate_up_proj``
+  ``[E, 2I, H]`` / ``mlp.experts.down_proj`` ``[E, H, I]`` and a shared expert with its
+  own sigmoid gate.
 """
 from __future__ import annotations
 
 import json
+from dataclasses import dataclass
 from pathlib import Path
+from typing import Callable
 
 import torch
 
@@ -24,97 +35,175 @@ from ..models.config import DecoderConfig
 from ..models.decoder import DenseLayerStage, build_stages
 
 _ARCH = {"llama3": "LlamaForCausalLM", "qwen3": "Qwen3ForCausalLM", "olmoe": "OlmoeForCausalLM",
-         "qwen3moe": "Qwen3MoeForCausalLM"}
+         "qwen3moe": "Qwen3MoeForCausalLM", "qwen35": "Qwen3_5ForConditionalGeneration",
+         "qwen35moe": "Qwen3_5MoeForConditionalGeneration"}
+_IGNORED_PREFIXES = ("model.visual.", "mtp.")
 
 
 def supported(cfg: DecoderConfig) -> bool:
-    return cfg.family in _ARCH and not cfg.tied_embeddings
+    return cfg.family in _ARCH
 
 
-def _layer_to_hf(cfg: DecoderConfig, i: int, dense: bool, P: dict[str, torch.Tensor]) -> dict:
-    pre = f"model.layers.{i}."
-    dh, Hq, Hkv = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
-    out = {pre + "input_layernorm.weight": P["attn_norm"],
-           pre + "post_attention_layernorm.weight": P["mlp_norm"],
-           pre + "self_attn.o_proj.weight": P["wo"]}
-    if dense:
-        q, k, v = P["wqkv"].split([Hq * dh, Hkv * dh, Hkv * dh], dim=0)
+def _prefix(cfg: DecoderConfig) -> str:
+    return "model.language_model." if cfg.family in ("qwen35", "qwen35moe") else "model."
+
+
+@dataclass
+class Source:
+    """Where one framework parameter comes from: ``names`` in the checkpoint, ``load`` joins
+    them into the parameter, ``store`` cuts the parameter back into those tensors."""
+    names: tuple[str, ...]
+    load: Callable[[list[torch.Tensor]], torch.Tensor]
+    store: Callable[[torch.Tensor], list[torch.Tensor]]
+
+
+def _tensor(name: str) -> Source:
+    return Source((name,), lambda ts: ts[0], lambda p: [p])
+
+
+def _reshaped(name: str, stored: tuple[int, ...], ours: tuple[int, ...]) -> Source:
+    return Source((name,), lambda ts: ts[0].reshape(ours), lambda p: [p.reshape(stored)])
+
+
+def _joined(names: tuple[str, ...], rows: tuple[int, ...]) -> Source:
+    return Source(names, lambda ts: torch.cat(ts, 0), lambda p: list(p.split(list(rows), dim=0)))
+
+
+def _deinterleaved(name: str, heads: int, head_dim: int) -> Source:
+    """Checkpoint rows ``[q_0, g_0, q_1, g_1, ...]`` (blocks of ``head_dim``) <-> all q, all g."""
+    def load(ts):
+        w = ts[0]
+        w = w.reshape(heads, 2, head_dim, w.shape[-1])
+        return torch.cat([w[:, 0].reshape(heads * head_dim, -1), w[:, 1].reshape(heads * head_dim, -1)], 0)
+
+    def store(p):
+        q, g = p.split(heads * head_dim, dim=0)
+        w = torch.stack([q.reshape(heads, head_dim, -1), g.reshape(heads, head_dim, -1)], 1)
+        return [w.reshape(2 * heads * head_dim, -1)]
+    return Source((name,), load, store)
+
+
+def _expert_bank(fmt: tuple[str, ...], n_experts: int, rows: tuple[int, ...]) -> Source:
+    """Per-expert matrices (``fmt`` formatted with the expert index, joined on dim 0) stacked."""
+    names = tuple(f.format(e=e) for e in range(n_experts) for f in fmt)
+    k = len(fmt)
+
+    def load(ts):
+        return torch.stack([torch.cat(ts[e * k:(e + 1) * k], 0) for e in range(n_experts)])
+
+    def store(p):
+        out = []
+        for e in range(n_experts):
+            out += list(p[e].split(list(rows), dim=0))
+        return out
+    return Source(names, load, store)
+
+
+def _layer_sources(cfg: DecoderConfig, i: int, stage) -> dict[str, Source]:
+    pre = f"{_prefix(cfg)}layers.{i}."
+    dh, Hq, Hkv, D = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads, cfg.d_model
+    S = {"attn_norm": _tensor(pre + "input_layernorm.weight"),
+         "mlp_norm": _tensor(pre + "post_attention_layernorm.weight")}
+    if cfg.layer_kind(i) == "attention":
+        a = pre + "self_attn."
+        S["wo"] = _tensor(a + "o_proj.weight")
+        if isinstance(stage, DenseLayerStage):
+            S["wqkv"] = _joined((a + "q_proj.weight", a + "k_proj.weight", a + "v_proj.weight"),
+                                (Hq * dh, Hkv * dh, Hkv * dh))
+        else:
+            S["wq"] = (_deinterleaved(a + "q_proj.weight", Hq, dh) if cfg.gated_attention
+                       else _tensor(a + "q_proj.weight"))
+            S["wk"], S["wv"] = _tensor(a + "k_proj.weight"), _tensor(a + "v_proj.weight")
+        if cfg.qk_norm:
+            S["q_norm"], S["k_norm"] = _tensor(a + "q_norm.weight"), _tensor(a + "k_norm.weight")
     else:
-        q, k, v = P["wq"], P["wk"], P["wv"]
-    out[pre + "self_attn.q_proj.weight"] = q
-    out[pre + "self_attn.k_proj.weight"] = k
-    out[pre + "self_attn.v_proj.weight"] = v
-    if cfg.qk_norm:
-        out[pre + "self_attn.q_norm.weight"] = P["q_norm"]
-        out[pre + "self_attn.k_norm.weight"] = P["k_norm"]
+        la = pre + "linear_attn."
+        kw = cfg.dn_qk_heads * cfg.dn_head_dim
+        vw = cfg.dn_v_heads * cfg.dn_head_dim
+        conv = 2 * kw + vw
+        S["w_qkvz"] = _joined((la + "in_proj_qkv.weight", la + "in_proj_z.weight"), (conv, vw))
+        S["w_ba"] = _joined((la + "in_proj_b.weight", la + "in_proj_a.weight"),
+                            (cfg.dn_v_heads, cfg.dn_v_heads))
+        S["conv_w"] = _reshaped(la + "conv1d.weight", (conv, 1, cfg.dn_conv_width),
+                                (conv, cfg.dn_conv_width))
+        S["A_log"], S["dt_bias"] = _tensor(la + "A_log"), _tensor(la + "dt_bias")
+        S["lin_norm"] = _tensor(la + "norm.weight")
+        S["w_out"] = _tensor(la + "out_proj.weight")
+    m = pre + "mlp."
     if cfg.is_moe:
-        out[pre + "mlp.gate.weight"] = P["router"]
+        S["router"] = _tensor(m + "gate.weight")
         F = cfg.d_expert
-        for e in range(cfg.n_experts):
-            ep = f"{pre}mlp.experts.{e}."
-            out[ep + "gate_proj.weight"] = P["w13"][e, :F]
-            out[ep + "up_proj.weight"] = P["w13"][e, F:]
-            out[ep + "down_proj.weight"] = P["w2"][e]
+        if cfg.family == "qwen35moe":
+            S["w13"], S["w2"] = _tensor(m + "experts.gate_up_proj"), _tensor(m + "experts.down_proj")
+        else:
+            S["w13"] = _expert_bank((m + "experts.{e}.gate_proj.weight", m + "experts.{e}.up_proj.weight"),
+                                    cfg.n_experts, (F, F))
+            S["w2"] = _expert_bank((m + "experts.{e}.down_proj.weight",), cfg.n_experts, (D,))
+        if cfg.d_shared_expert:
+            Fs = cfg.d_shared_expert
+            S["sw13"] = _joined((m + "shared_expert.gate_proj.weight", m + "shared_expert.up_proj.weight"),
+                                (Fs, Fs))
+            S["sw2"] = _tensor(m + "shared_expert.down_proj.weight")
+            S["shared_gate"] = _reshaped(m + "shared_expert_gate.weight", (1, D), (D,))
     else:
-        F = cfg.d_ff
-        out[pre + "mlp.gate_proj.weight"] = P["w13"][:F]
-        out[pre + "mlp.up_proj.weight"] = P["w13"][F:]
-        out[pre + "mlp.down_proj.weight"] = P["w2"]
+        S["w13"] = _joined((m + "gate_proj.weight", m + "up_proj.weight"), (cfg.d_ff, cfg.d_ff))
+        S["w2"] = _tensor(m + "down_proj.weight")
+    return S
+
+
+def parameter_sources(cfg: DecoderConfig, stages=None) -> dict[str, Source]:
+    """``{"<stage>.<param>": Source}`` for every base (non-adapter) parameter of the model."""
+    if not supported(cfg):
+        raise ValueError(f"no Hugging Face mapping for family {cfg.family!r}")
+    stages = stages or build_stages(cfg)
+    pre = _prefix(cfg)
+    out = {"embed.embed": _tensor(pre + "embed_tokens.weight"),
+           "head.final_norm": _tensor(pre + "norm.weight")}
+    if not cfg.tied_embeddings:
+        out["head.head"] = _tensor("lm_head.weight")
+    for i in range(cfg.n_layers):
+        st = stages[i + 1]
+        S = _layer_sources(cfg, i, st)
+        for p in st.params:
+            if "_lora_" in p.name:
+                continue                  # adapters are not part of a base checkpoint
+            if p.name not in S:
+                raise KeyError(f"{st.name}.{p.name} has no Hugging Face source")
+            out[f"{st.name}.{p.name}"] = S[p.name]
     return out
 
 
 def to_hf(cfg: DecoderConfig, state: dict[str, torch.Tensor], stages=None) -> dict[str, torch.Tensor]:
     """``stages``: the run's own stage list when it differs from the default build (adapters
     switch dense layers to separate q/k/v projections); adapter factors are not exported."""
-    if not supported(cfg):
-        raise ValueError(f"no Hugging Face mapping for family {cfg.family!r}")
-    stages = stages or build_stages(cfg)
-    out = {"model.embed_tokens.weight": state["embed.embed"],
-           "model.norm.weight": state["head.final_norm"], "lm_head.weight": state["head.head"]}
-    for i in range(cfg.n_layers):
-        st = stages[i + 1]
-        P = {p.name: state[f"{st.name}.{p.name}"] for p in st.params if "_lora_" not in p.name}
-        out.update(_layer_to_hf(cfg, i, isinstance(st, DenseLayerStage), P))
-    return {k: v.contiguous() for k, v in out.items()}
+    out: dict[str, torch.Tensor] = {}
+    for name, src in parameter_sources(cfg, stages).items():
+        for hf_name, t in zip(src.names, src.store(state[name])):
+            out[hf_name] = t.contiguous()
+    return out
 
 
 def from_hf(cfg: DecoderConfig, hf: dict[str, torch.Tensor], stages=None) -> dict[str, torch.Tensor]:
-    if not supported(cfg):
-        raise ValueError(f"no Hugging Face mapping for family {cfg.family!r}")
     stages = stages or build_stages(cfg)
-    head = hf.get("lm_head.weight", hf["model.embed_tokens.weight"])
-    out = {"embed.embed": hf["model.embed_tokens.weight"], "head.final_norm": hf["model.norm.weight"],
-           "head.head": head}
-    for i in range(cfg.n_layers):
-        st = stages[i + 1]
-        pre = f"model.layers.{i}."
-        g = lambda name: hf[pre + name]
-        P = {"attn_norm": g("input_layernorm.weight"), "mlp_norm": g("post_attention_layernorm.weight"),
-             "wo": g("self_attn.o_proj.weight")}
-        q, k, v = (g(f"self_attn.{n}_proj.weight") for n in "qkv")
-        if isinstance(st, DenseLayerStage):
-            P["wqkv"] = torch.cat([q, k, v], 0)
-        else:
-            P["wq"], P["wk"], P["wv"] = q, k, v
-        if cfg.qk_norm:
-            P["q_norm"], P["k_norm"] = g("self_attn.q_norm.weight"), g("self_attn.k_norm.weight")
-        if cfg.is_moe:
-            P["router"] = g("mlp.gate.weight")
-            P["w13"] = torch.stack([torch.cat([g(f"mlp.experts.{e}.gate_proj.weight"),
-                                               g(f"mlp.experts.{e}.up_proj.weight")], 0)
-                                    for e in range(cfg.n_experts)])
-            P["w2"] = torch.stack([g(f"mlp.experts.{e}.down_proj.weight") for e in range(cfg.n_experts)])
-        else:
-            P["w13"] = torch.cat([g("mlp.gate_proj.weight"), g("mlp.up_proj.weight")], 0)
-            P["w2"] = g("mlp.down_proj.weight")
-        for p in st.params:
-            if "_lora_" in p.name:
-                continue                  # adapters are not part of a base checkpoint
-            if p.name not in P:
-                raise KeyError(f"{st.name}.{p.name} has no Hugging Face source")
-            if tuple(P[p.name].shape) != tuple(p.shape):
-                raise ValueError(f"{st.name}.{p.name}: checkpoint shape {tuple(P[p.name].shape)} != {p.shape}")
-            out[f"{st.name}.{p.name}"] = P[p.name]
+    shapes = {f"{st.name}.{p.name}": tuple(p.shape) for st in stages for p in st.params}
+    out: dict[str, torch.Tensor] = {}
+    used: set[str] = set()
+    for name, src in parameter_sources(cfg, stages).items():
+        names = src.names
+        if name == "head.head" and "lm_head.weight" not in hf:
+            names = (_prefix(cfg) + "embed_tokens.weight",)      # exported with shared matrices
+        missing = [n for n in names if n not in hf]
+        if missing:
+            raise KeyError(f"{name}: checkpoint has no {missing[0]!r}")
+        t = src.load([hf[n] for n in names])
+        if tuple(t.shape) != shapes[name]:
+            raise ValueError(f"{name}: checkpoint shape {tuple(t.shape)} != {shapes[name]}")
+        out[name] = t
+        used.update(names)
+    extra = [k for k in hf if k not in used and not k.startswith(_IGNORED_PREFIXES)
+             and not (cfg.tied_embeddings and k == "lm_head.weight")]
+    if extra:
+        raise ValueError(f"checkpoint tensors with no destination: {sorted(extra)[:4]}")
     return out
 
 
@@ -128,6 +217,15 @@ def hf_config(cfg: DecoderConfig) -> dict:
     if cfg.is_moe:
         d.update(num_experts=cfg.n_experts, num_experts_per_tok=cfg.top_k,
                  moe_intermediate_size=cfg.d_expert, norm_topk_prob=cfg.router_renormalize)
+        if cfg.d_shared_expert:
+            d["shared_expert_intermediate_size"] = cfg.d_shared_expert
+    if cfg.full_attention_interval:
+        d.update(full_attention_interval=cfg.full_attention_interval,
+                 layer_types=["full_attention" if cfg.layer_kind(i) == "attention" else "linear_attention"
+                              for i in range(cfg.n_layers)],
+                 linear_num_key_heads=cfg.dn_qk_heads, linear_num_value_heads=cfg.dn_v_heads,
+                 linear_key_head_dim=cfg.dn_head_dim, linear_value_head_dim=cfg.dn_head_dim,
+                 linear_conv_kernel_dim=cfg.dn_conv_width)
     return d
 
 

@@ -85,20 +85,56 @@ def test_hugging_face_names_round_trip(tmp_path):
     from shadowspill_b200.checkpoint import hf
     from shadowspill_b200.execution.resident import ResidentTrainer
     from shadowspill_b200.models.config import preset
-    for name in ("llama3-tiny", "qwen3-tiny", "olmoe-tiny"):
+    for name in ("llama3-tiny", "qwen3-tiny", "olmoe-tiny", "qwen3moe-tiny", "qwen35-tiny",
+                 "qwen35moe-tiny"):
         cfg = preset(name)
+        assert hf.supported(cfg)
         tr = ResidentTrainer(cfg, device="cpu", dtype=torch.float32, seed=1)
         state = tr.state_dict()
         named = hf.to_hf(cfg, state)
-        assert "model.layers.0.self_attn.q_proj.weight" in named
-        assert named["model.layers.0.self_attn.q_proj.weight"].shape == (cfg.n_heads * cfg.head_dim, cfg.d_model)
-        if cfg.is_moe:
-            assert f"model.layers.1.mlp.experts.{cfg.n_experts - 1}.down_proj.weight" in named
+        pre = "model.language_model." if name.startswith("qwen35") else "model."
+        attn = next(i for i in range(cfg.n_layers) if cfg.layer_kind(i) == "attention")
+        q = named[f"{pre}layers.{attn}.self_attn.q_proj.weight"]
+        gated = 2 if cfg.gated_attention else 1
+        assert q.shape == (gated * cfg.n_heads * cfg.head_dim, cfg.d_model)
+        if cfg.gated_attention:
+            # per-head interleave: rows [q_0, gate_0, q_1, ...]; ours keeps all q, then all gates
+            ours = state[f"layer{attn}.wq"]
+            dh = cfg.head_dim
+            assert torch.equal(q[:dh], ours[:dh])
+            assert torch.equal(q[dh:2 * dh], ours[cfg.n_heads * dh:cfg.n_heads * dh + dh])
+            assert torch.equal(q[2 * dh:3 * dh], ours[dh:2 * dh])
+        if cfg.full_attention_interval:
+            la = f"{pre}layers.0.linear_attn."
+            kw, vw = cfg.dn_qk_heads * cfg.dn_head_dim, cfg.dn_v_heads * cfg.dn_head_dim
+            assert named[la + "in_proj_qkv.weight"].shape == (2 * kw + vw, cfg.d_model)
+            assert named[la + "in_proj_z.weight"].shape == (vw, cfg.d_model)
+            assert named[la + "in_proj_a.weight"].shape == (cfg.dn_v_heads, cfg.d_model)
+            assert named[la + "conv1d.weight"].shape == (2 * kw + vw, 1, cfg.dn_conv_width)
+        if cfg.family == "qwen35moe":
+            assert named[f"{pre}layers.1.mlp.experts.gate_up_proj"].shape == \
+                (cfg.n_experts, 2 * cfg.d_expert, cfg.d_model)
+            if cfg.d_shared_expert:
+                assert named[f"{pre}layers.1.mlp.shared_expert_gate.weight"].shape == (1, cfg.d_model)
+        elif cfg.is_moe:
+            assert f"{pre}layers.1.mlp.experts.{cfg.n_experts - 1}.down_proj.weight" in named
         else:
-            assert named["model.layers.1.mlp.up_proj.weight"].shape == (cfg.d_ff, cfg.d_model)
+            assert named[f"{pre}layers.1.mlp.up_proj.weight"].shape == (cfg.d_ff, cfg.d_model)
+        assert ("lm_head.weight" in named) == (not cfg.tied_embeddings)
         hf.save_hf(cfg, state, tmp_path / name)
         back = hf.load_hf(cfg, tmp_path / name)
         assert set(back) == set(state)
         for k, v in state.items():
             assert torch.equal(back[k], v), k
-    assert not hf.supported(preset("qwen35-tiny"))
+    # the vision tower and the extra prediction head of a full checkpoint are skipped;
+    # anything else without a destination is an error
+    cfg = preset("qwen35-tiny")
+    state = ResidentTrainer(cfg, device="cpu", dtype=torch.float32, seed=1).state_dict()
+    named = hf.to_hf(cfg, state)
+    named["model.visual.patch_embed.weight"] = torch.zeros(2)
+    named["mtp.fc.weight"] = torch.zeros(2)
+    assert set(hf.from_hf(cfg, named)) == set(state)
+    named["model.language_model.unknown"] = torch.zeros(2)
+    import pytest
+    with pytest.raises(ValueError):
+        hf.from_hf(cfg, named)
