@@ -76,7 +76,7 @@ def save_checkpoint(executor, directory: str | Path, *, metadata: dict[str, Any]
     entries = state_entries(executor)
     writer = ArchiveWriter(directory / f"rank{executor.rank}.tar")
     try:
-        views = dict(executor.named_tensors())
+        views = dict(executor.named_tensors(writable=False))
         for e in entries:
             t = views[e["name"]]
             lo, n = e["region"]

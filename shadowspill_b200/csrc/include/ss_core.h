@@ -28,7 +28,8 @@ typedef enum ss_status {
   SS_FAILED = 6,            /* the runtime failure latch is set */
   SS_TIMEOUT = 7,
   SS_INFEASIBLE = 8,        /* no schedule fits the capacity */
-  SS_INTERNAL = 9
+  SS_INTERNAL = 9,
+  SS_IO_ERROR = 10          /* the file-backed spill pool could not be read or written */
 } ss_status;
 
 const char* ss_status_string(int status);
@@ -233,6 +234,17 @@ typedef struct ss_runtime_config {
   int32_t max_objects;
   int32_t event_pool;          /* dependency events reserved at creation */
   void* external_device_base;  /* caller-owned device pool (e.g. symmetric memory); NULL = allocate */
+  /* File-backed spill pool (optional third pool, on a local drive). Objects whose home is in
+   * it move through staged lanes: bounded rings of pinned host memory, `file_queue_depth`
+   * chunks of `file_chunk_bytes` per direction, filled and drained by disk threads. */
+  int64_t file_bytes;          /* 0 = no file pool */
+  const char* file_directory;  /* existing directory for the unlinked scratch file */
+  const char* file_image;      /* optional named file that is the whole pool and is kept */
+  int32_t file_create_image;   /* create file_image (must not exist) instead of opening it */
+  int32_t file_queue_depth;    /* slots per direction; 0 = 16 */
+  int64_t file_chunk_bytes;    /* multiple of 4096; 0 = 2 MiB */
+  int32_t file_io_threads;     /* disk threads per direction; 0 = 2 */
+  int32_t reserved0;
 } ss_runtime_config;
 
 typedef struct ss_failure {
@@ -241,7 +253,7 @@ typedef struct ss_failure {
   int32_t task;
   int32_t object;
   int32_t action;
-  int32_t pool;                /* 0 device, 1 spill */
+  int32_t pool;                /* 0 device, 1 spill, 2 file */
   char message[192];
 } ss_failure;
 
@@ -307,6 +319,8 @@ typedef struct ss_plan_desc {
   const int32_t* use_task;
   const int32_t* use_object;
   const int32_t* use_mode;
+  const int64_t* file_offset;         /* home in the file pool per object, -1 = not there; may be
+                                         NULL. An object has at most one home. */
 } ss_plan_desc;
 
 int ss_plan_admit(ss_runtime* rt, const ss_plan_desc* desc, int32_t* plan_id);
@@ -329,6 +343,12 @@ int ss_runtime_wait_idle(ss_runtime* rt);
 int ss_spill_write(ss_runtime* rt, int64_t spill_offset, const void* src, int64_t bytes);
 int ss_spill_read(ss_runtime* rt, int64_t spill_offset, void* dst, int64_t bytes);
 
+/* The same for objects whose home is the file pool. */
+int ss_file_write(ss_runtime* rt, int64_t file_offset, const void* src, int64_t bytes);
+int ss_file_read(ss_runtime* rt, int64_t file_offset, void* dst, int64_t bytes);
+/* direct: 1 if the pool file accepted O_DIRECT. ring_bytes: pinned staging per direction. */
+int ss_runtime_file_info(ss_runtime* rt, int32_t* direct, int64_t* ring_bytes);
+
 /* Route calibration: times copies of `bytes` alone and with the opposite
  * direction in flight. Rates in bytes/second. */
 typedef struct ss_transfer_profile {
@@ -337,6 +357,10 @@ typedef struct ss_transfer_profile {
 } ss_transfer_profile;
 int ss_calibrate_transfers(ss_runtime* rt, int64_t bytes, int32_t repeats,
                            ss_transfer_profile* out);
+/* The same through the staged lanes of the file pool (device <-> file). Call with no step
+ * in flight; it overwrites the first 2*bytes of the device pool and of the file. */
+int ss_calibrate_file_transfers(ss_runtime* rt, int64_t bytes, int32_t repeats,
+                                ss_transfer_profile* out);
 
 /* ------------------------------------------------------------------ BLAKE3 */
 void* ss_blake3_new(void);

@@ -15,9 +15,14 @@
 //                      every predecessor of its destination range has been
 //                      recorded, because a stream cannot wait for an event that
 //                      has not been recorded yet.
+// Objects whose home is the optional file pool move through staged lanes
+// (staged_lane.hpp): the worker submits a job when the action's trigger is
+// published and pumps the lanes; completion events are recorded when the last
+// chunk's copy is enqueued, an evict is durable when its last chunk is written.
 // Every host-side wait is bounded; on expiry the first-writer-wins failure
 // latch is set and all entry points return SS_FAILED from then on.
 #include "common.hpp"
+#include "staged_lane.hpp"
 
 #include <atomic>
 #include <chrono>
@@ -44,7 +49,10 @@ struct IntervalState {
 struct PlanState {
   int32_t id = 0;
   int32_t n_tasks = 0, n_objects = 0;
-  std::vector<int64_t> object_bytes, spill_offset;
+  std::vector<int64_t> object_bytes, spill_offset, file_offset;
+  std::vector<std::unique_ptr<ssc::StagedJob>> jobs;      // per action; null unless file-homed
+  std::vector<std::atomic<int>> action_durable;           // evict to file: every chunk written
+  std::atomic<int> staged_pending{0};                     // submitted staged jobs not yet complete
   std::vector<ss_action> actions;
   std::vector<std::unique_ptr<IntervalState>> intervals;
   std::vector<int32_t> pred_begin, pred_index;
@@ -78,6 +86,8 @@ struct ss_runtime {
   void* spill_base = nullptr;
   void* fetch_stream = nullptr;
   void* evict_stream = nullptr;
+  ssc::FilePool file;
+  std::unique_ptr<ssc::StagedLane> fetch_lane, evict_lane;
   std::mutex mu;                      // guards plans map and worker handoff
   std::condition_variable cv;
   std::map<int32_t, std::unique_ptr<PlanState>> plans;
@@ -130,6 +140,99 @@ int new_event(ss_runtime* rt, void** out, int timing = 0) {
   return rc;
 }
 
+// ---- staged transfers of objects whose home is the file pool
+bool file_homed(const PlanState& P, int32_t object) {
+  return !P.file_offset.empty() && P.file_offset[object] >= 0;
+}
+
+void submit_staged_evict(ss_runtime* rt, PlanState& P, int32_t a) {
+  const ss_action& A = P.actions[a];
+  IntervalState* I = P.intervals[P.action_interval[a]].get();
+  ssc::StagedJob& J = *P.jobs[a];
+  J.to_device = false;
+  J.file_off = P.file_offset[A.object];
+  J.dev = rt->dev(I->iv.offset);
+  J.bytes = P.object_bytes[A.object];
+  J.tag = a;
+  PlanState* Pp = &P;
+  J.before_first_copy = [rt, Pp, I, a](ssc::StagedJob&) -> int {
+    ss_backend* be = rt->be;
+    const ss_action& A = Pp->actions[a];
+    int rc = SS_OK;
+    if (A.trigger_task >= 0) rc = be->stream_wait_event(be->self, rt->evict_stream, Pp->task_fence[A.trigger_task]);
+    if (rc == SS_OK && I->ready_event && I->iv.begin_action >= 0)
+      rc = be->stream_wait_event(be->self, rt->evict_stream, I->ready_event);
+    if (rc == SS_OK && !Pp->action_begin_event.empty())
+      rc = be->event_record(be->self, Pp->action_begin_event[a], rt->evict_stream);
+    return rc == SS_OK ? 0 : -1;
+  };
+  J.after_last_copy = [rt, Pp, I, a](ssc::StagedJob& j) -> int {
+    ss_backend* be = rt->be;
+    if (be->event_record(be->self, Pp->action_event[a], rt->evict_stream) != SS_OK) return -1;
+    I->release_event = Pp->action_event[a];      // the range is free once the last chunk left it
+    I->release_on_compute = false;
+    I->released.store(1, std::memory_order_release);
+    Pp->action_issued[a].store(1, std::memory_order_release);
+    rt->st_evicts++; rt->st_evict_bytes += j.bytes;
+    rt->trace(SS_TRACE_EVICT_ISSUE, a, j.bytes);
+    return 0;
+  };
+  J.on_durable = [rt, Pp, a](ssc::StagedJob& j) {
+    Pp->action_durable[a].store(1, std::memory_order_release);
+    Pp->staged_pending.fetch_sub(1, std::memory_order_acq_rel);
+    rt->trace(SS_TRACE_EVICT_DONE, a, j.bytes);
+  };
+  P.staged_pending.fetch_add(1, std::memory_order_acq_rel);
+  rt->evict_lane->submit(&J);
+}
+
+void submit_staged_fetch(ss_runtime* rt, PlanState& P, int32_t a) {
+  const ss_action& A = P.actions[a];
+  const int32_t ii = P.action_interval[a];
+  IntervalState* I = P.intervals[ii].get();
+  ssc::StagedJob& J = *P.jobs[a];
+  J.to_device = true;
+  J.file_off = P.file_offset[A.object];
+  J.dev = rt->dev(I->iv.offset);
+  J.bytes = P.object_bytes[A.object];
+  J.tag = a;
+  PlanState* Pp = &P;
+  // reading ahead into the ring starts at once; the copies wait until every previous
+  // occupant of the destination range has been released
+  J.before_first_copy = [rt, Pp, ii, a](ssc::StagedJob&) -> int {
+    ss_backend* be = rt->be;
+    for (int32_t k = Pp->pred_begin[ii]; k < Pp->pred_begin[ii + 1]; ++k)
+      if (!Pp->intervals[Pp->pred_index[k]]->released.load(std::memory_order_acquire)) {
+        rt->st_reuse_waits++;
+        return 1;
+      }
+    const ss_action& A = Pp->actions[a];
+    int rc = SS_OK;
+    if (A.trigger_task >= 0) rc = be->stream_wait_event(be->self, rt->fetch_stream, Pp->task_fence[A.trigger_task]);
+    for (int32_t k = Pp->pred_begin[ii]; rc == SS_OK && k < Pp->pred_begin[ii + 1]; ++k) {
+      IntervalState& Jv = *Pp->intervals[Pp->pred_index[k]];
+      if (Jv.release_event) rc = be->stream_wait_event(be->self, rt->fetch_stream, Jv.release_event);
+    }
+    if (rc == SS_OK && !Pp->action_begin_event.empty())
+      rc = be->event_record(be->self, Pp->action_begin_event[a], rt->fetch_stream);
+    return rc == SS_OK ? 0 : -1;
+  };
+  J.after_last_copy = [rt, Pp, I, a](ssc::StagedJob& j) -> int {
+    ss_backend* be = rt->be;
+    if (be->event_record(be->self, Pp->action_event[a], rt->fetch_stream) != SS_OK) return -1;
+    I->ready_event = Pp->action_event[a];
+    I->ready_issued.store(1, std::memory_order_release);
+    Pp->action_issued[a].store(1, std::memory_order_release);
+    rt->st_fetches++; rt->st_fetch_bytes += j.bytes;
+    rt->trace(SS_TRACE_FETCH_ISSUE, a, j.bytes);
+    Pp->staged_pending.fetch_sub(1, std::memory_order_acq_rel);
+    return 0;
+  };
+  J.on_durable = nullptr;
+  P.staged_pending.fetch_add(1, std::memory_order_acq_rel);
+  rt->fetch_lane->submit(&J);
+}
+
 // Issues every published action it can, lane by lane. Returns true if anything moved.
 bool pump_plan(ss_runtime* rt, PlanState& P) {
   bool moved = false;
@@ -154,6 +257,15 @@ bool pump_plan(ss_runtime* rt, PlanState& P) {
     const int32_t a = P.evict_order[P.next_evict];
     const ss_action& A = P.actions[a];
     if (A.trigger_task > pub) break;
+    if (file_homed(P, A.object)) {
+      // a stay opened by a staged fetch has its ready event only once that fetch is complete
+      const int32_t ii = P.action_interval[a];
+      if (P.intervals[ii]->iv.begin_action >= 0 &&
+          !P.intervals[ii]->ready_issued.load(std::memory_order_acquire)) break;
+      submit_staged_evict(rt, P, a);
+      ++P.next_evict; moved = true;
+      continue;
+    }
     IntervalState& I = *P.intervals[P.action_interval[a]];
     int rc = SS_OK;
     if (A.trigger_task >= 0) rc = be->stream_wait_event(be->self, rt->evict_stream, P.task_fence[A.trigger_task]);
@@ -183,6 +295,13 @@ bool pump_plan(ss_runtime* rt, PlanState& P) {
     const ss_action& A = P.actions[a];
     if (A.trigger_task > pub) break;
     const int32_t ii = P.action_interval[a];
+    if (file_homed(P, A.object)) {
+      const int32_t prev = P.action_prev_evict[a];
+      if (prev >= 0 && !P.action_durable[prev].load(std::memory_order_acquire)) break;
+      submit_staged_fetch(rt, P, a);
+      ++P.next_fetch; moved = true;
+      continue;
+    }
     IntervalState& I = *P.intervals[ii];
     bool blocked = false;
     for (int32_t k = P.pred_begin[ii]; k < P.pred_begin[ii + 1]; ++k)
@@ -227,10 +346,23 @@ void worker_main(ss_runtime* rt) {
     if (!rt->failed.load()) {
       for (auto& kv : rt->plans)
         if (kv.second->active) moved |= pump_plan(rt, *kv.second);
+      for (ssc::StagedLane* lane : {rt->evict_lane.get(), rt->fetch_lane.get()}) {
+        if (!lane) continue;
+        const int r = lane->pump();
+        if (r < 0) {
+          rt->latch(SS_FAIL_BACKEND_COPY, SS_IO_ERROR, -1, -1, -1, 2, lane->message().c_str());
+          break;
+        }
+        moved |= r > 0;
+      }
     }
     if (moved) { rt->cv.notify_all(); continue; }
     rt->st_wakeups++;
-    rt->cv.wait_for(lk, std::chrono::nanoseconds(std::max<int64_t>(rt->cfg.worker_poll_ns, 1000) * 200));
+    // chunks in flight complete without anybody signalling this thread: poll them closely
+    const bool staging = !rt->failed.load() && ((rt->fetch_lane && rt->fetch_lane->busy()) ||
+                                                (rt->evict_lane && rt->evict_lane->busy()));
+    const int64_t poll = std::max<int64_t>(rt->cfg.worker_poll_ns, 1000);
+    rt->cv.wait_for(lk, std::chrono::nanoseconds(staging ? poll * 10 : poll * 200));
   }
 }
 
@@ -279,7 +411,28 @@ int ss_runtime_create(ss_backend* backend, const ss_runtime_config* config, ss_r
   }
   if (rc == SS_OK) rc = backend->stream_create(backend->self, &rt->fetch_stream);
   if (rc == SS_OK) rc = backend->stream_create(backend->self, &rt->evict_stream);
+  if (rc == SS_OK && config->file_bytes > 0) {
+    std::string error;
+    rc = rt->file.open(config->file_directory, config->file_image, config->file_create_image != 0,
+                       config->file_bytes, error);
+    if (rc != SS_OK) std::fprintf(stderr, "ss runtime: %s\n", error.c_str());
+    const int64_t chunk = config->file_chunk_bytes > 0 ? config->file_chunk_bytes : (2ll << 20);
+    const int32_t depth = config->file_queue_depth > 0 ? config->file_queue_depth : 16;
+    const int32_t io = config->file_io_threads > 0 ? config->file_io_threads : 2;
+    if (rc == SS_OK) {
+      rt->fetch_lane = std::make_unique<ssc::StagedLane>(backend, rt->fetch_stream, &rt->file, true, chunk, depth, io);
+      rt->evict_lane = std::make_unique<ssc::StagedLane>(backend, rt->evict_stream, &rt->file, false, chunk, depth, io);
+      rc = rt->fetch_lane->init(config->numa_node);
+      if (rc == SS_OK) rc = rt->evict_lane->init(config->numa_node);
+      rt->st_host_allocs += 2;
+    }
+    // the strings belong to the caller
+    rt->cfg.file_directory = rt->cfg.file_image = nullptr;
+  }
   if (rc != SS_OK) {
+    rt->fetch_lane.reset(); rt->evict_lane.reset();
+    rt->file.close();
+    if (rt->evict_stream) backend->stream_destroy(backend->self, rt->evict_stream);
     if (rt->fetch_stream) backend->stream_destroy(backend->self, rt->fetch_stream);
     if (rt->device_base && !rt->device_external) backend->device_free(backend->self, rt->device_base);
     if (rt->spill_base) backend->host_free(backend->self, rt->spill_base, static_cast<size_t>(config->spill_bytes));
@@ -311,6 +464,9 @@ int ss_runtime_close(ss_runtime* rt) {
   ss_backend* be = rt->be;
   be->stream_synchronize(be->self, rt->fetch_stream);
   be->stream_synchronize(be->self, rt->evict_stream);
+  rt->fetch_lane.reset();            // joins the disk threads, frees the rings
+  rt->evict_lane.reset();
+  rt->file.close();
   for (auto& kv : rt->plans) release_plan(rt, *kv.second);
   rt->plans.clear();
   be->stream_destroy(be->self, rt->fetch_stream);
@@ -391,6 +547,15 @@ int ss_plan_admit(ss_runtime* rt, const ss_plan_desc* d, int32_t* plan_id) {
   P->n_tasks = d->n_tasks; P->n_objects = d->n_objects;
   P->object_bytes.assign(d->object_bytes, d->object_bytes + d->n_objects);
   P->spill_offset.assign(d->spill_offset, d->spill_offset + d->n_objects);
+  if (d->file_offset) {
+    P->file_offset.assign(d->file_offset, d->file_offset + d->n_objects);
+    for (int32_t o = 0; o < d->n_objects; ++o) {
+      if (P->file_offset[o] < 0) continue;
+      if (!rt->file.is_open() || P->spill_offset[o] >= 0 || d->object_bytes[o] <= 0 ||
+          P->file_offset[o] + d->object_bytes[o] > rt->file.bytes())
+        return SS_INVALID_ARGUMENT;      // no file pool, two homes, or outside the file
+    }
+  }
   P->actions.assign(d->actions, d->actions + d->n_actions);
   for (int32_t i = 0; i < d->n_intervals; ++i) {
     auto s = std::make_unique<IntervalState>();
@@ -442,10 +607,10 @@ int ss_plan_admit(ss_runtime* rt, const ss_plan_desc* d, int32_t* plan_id) {
       const ss_action& A = P->actions[a];
       if (P->action_interval[a] < 0) return SS_INVALID_ARGUMENT;   // every action touches a stay
       if (A.kind == SS_ACT_EVICT) {
-        if (P->spill_offset[A.object] < 0) return SS_INVALID_ARGUMENT;
+        if (P->spill_offset[A.object] < 0 && !file_homed(*P, A.object)) return SS_INVALID_ARGUMENT;
         last_evict[A.object] = a; P->evict_order.push_back(a);
       } else if (A.kind == SS_ACT_FETCH) {
-        if (P->spill_offset[A.object] < 0) return SS_INVALID_ARGUMENT;
+        if (P->spill_offset[A.object] < 0 && !file_homed(*P, A.object)) return SS_INVALID_ARGUMENT;
         P->action_prev_evict[a] = last_evict[A.object]; P->fetch_order.push_back(a);
       } else {
         P->release_order.push_back(a);
@@ -469,6 +634,11 @@ int ss_plan_admit(ss_runtime* rt, const ss_plan_desc* d, int32_t* plan_id) {
   if (timed)
     if (int rc = new_event(rt, &P->step_begin_event, 1)) { release_plan(rt, *P); return rc; }
   P->action_issued = std::vector<std::atomic<int>>(d->n_actions);
+  P->action_durable = std::vector<std::atomic<int>>(d->n_actions);
+  P->jobs.resize(d->n_actions);
+  for (int32_t a = 0; a < d->n_actions; ++a)
+    if (P->actions[a].kind != SS_ACT_RELEASE && file_homed(*P, P->actions[a].object))
+      P->jobs[a] = std::make_unique<ssc::StagedJob>();
   P->object_current.assign(d->n_objects, -1);
   std::lock_guard<std::mutex> lk(rt->mu);
   P->id = rt->next_plan++;
@@ -501,6 +671,8 @@ int ss_step_begin(ss_runtime* rt, int32_t plan_id, void* compute_stream) {
       I->ready_issued = 0; I->released = 0; I->release_on_compute = false;
     }
     for (auto& f : P->action_issued) f = 0;
+    for (auto& f : P->action_durable) f = 0;
+    P->staged_pending.store(0);
     std::fill(P->object_current.begin(), P->object_current.end(), -1);
     P->next_fetch = P->next_evict = P->next_release = 0;
     P->compute_stream = compute_stream;
@@ -602,7 +774,7 @@ int ss_step_end(ss_runtime* rt, int32_t plan_id) {
     {
       std::lock_guard<std::mutex> lk(rt->mu);
       done = P->next_fetch == P->fetch_order.size() && P->next_evict == P->evict_order.size() &&
-             P->next_release == P->release_order.size();
+             P->next_release == P->release_order.size() && P->staged_pending.load() == 0;
     }
     if (done) break;
     if (rt->failed.load()) { result = SS_FAILED; break; }
@@ -699,6 +871,79 @@ int ss_calibrate_transfers(ss_runtime* rt, int64_t bytes, int32_t repeats, ss_tr
   const double lat_f = time_copy(true, false, 64), lat_e = time_copy(false, false, 64);
   const double f_solo = time_copy(true, false, bytes), e_solo = time_copy(false, false, bytes);
   const double f_conc = time_copy(true, true, bytes), e_conc = time_copy(false, true, bytes);
+  auto rate = [&](double ns, double lat) { return static_cast<double>(bytes) / std::max(ns - lat, 1.0) * 1e9; };
+  out->fetch_latency_ns = static_cast<int64_t>(lat_f);
+  out->evict_latency_ns = static_cast<int64_t>(lat_e);
+  out->fetch_solo_bps = rate(f_solo, lat_f);
+  out->evict_solo_bps = rate(e_solo, lat_e);
+  out->fetch_concurrent_bps = std::min(rate(f_conc, lat_f), out->fetch_solo_bps);
+  out->evict_concurrent_bps = std::min(rate(e_conc, lat_e), out->evict_solo_bps);
+  return SS_OK;
+}
+
+int ss_file_write(ss_runtime* rt, int64_t off, const void* src, int64_t bytes) {
+  if (!rt || !rt->file.is_open()) return SS_INVALID_ARGUMENT;
+  return rt->file.write(off, src, bytes);
+}
+int ss_file_read(ss_runtime* rt, int64_t off, void* dst, int64_t bytes) {
+  if (!rt || !rt->file.is_open()) return SS_INVALID_ARGUMENT;
+  return rt->file.read(off, dst, bytes);
+}
+int ss_runtime_file_info(ss_runtime* rt, int32_t* direct, int64_t* ring_bytes) {
+  if (!rt || !rt->file.is_open()) return SS_INVALID_ARGUMENT;
+  if (direct) *direct = rt->file.direct() ? 1 : 0;
+  if (ring_bytes) *ring_bytes = rt->fetch_lane ? rt->fetch_lane->ring_bytes() : 0;
+  return SS_OK;
+}
+
+int ss_calibrate_file_transfers(ss_runtime* rt, int64_t bytes, int32_t repeats, ss_transfer_profile* out) {
+  if (!rt || !out || !rt->file.is_open() || bytes <= 0 || bytes > rt->cfg.device_bytes / 2 ||
+      bytes > rt->file.bytes() / 2)
+    return SS_INVALID_ARGUMENT;
+  if (repeats <= 0) repeats = 3;
+  ss_backend* be = rt->be;
+  // the worker only pumps the lanes while it holds this mutex: keep it out for the duration
+  std::lock_guard<std::mutex> lk(rt->mu);
+  for (auto& kv : rt->plans) if (kv.second->active) return SS_INVALID_ARGUMENT;
+  bool failed = false;
+  auto time_job = [&](bool fetch, bool with_other, int64_t n) -> double {
+    double best = 1e30;
+    for (int r = 0; r < repeats && !failed; ++r) {
+      be->stream_synchronize(be->self, rt->fetch_stream);
+      be->stream_synchronize(be->self, rt->evict_stream);
+      ssc::StagedJob main_job, other_job;
+      main_job.to_device = fetch; main_job.file_off = 0; main_job.dev = rt->dev(0); main_job.bytes = n;
+      other_job.to_device = !fetch; other_job.file_off = bytes; other_job.dev = rt->dev(bytes); other_job.bytes = bytes;
+      ssc::StagedLane* main_lane = fetch ? rt->fetch_lane.get() : rt->evict_lane.get();
+      ssc::StagedLane* other_lane = fetch ? rt->evict_lane.get() : rt->fetch_lane.get();
+      if (with_other) other_lane->submit(&other_job);
+      const int64_t t0 = ss_monotonic_ns();
+      main_lane->submit(&main_job);
+      int64_t t_done = 0;
+      while (main_lane->busy() || (with_other && other_lane->busy())) {
+        if (main_lane->pump() < 0 || (with_other && other_lane->pump() < 0)) { failed = true; break; }
+        if (!t_done && !main_lane->busy()) {
+          if (fetch) be->stream_synchronize(be->self, rt->fetch_stream);
+          t_done = ss_monotonic_ns();
+        }
+        if (ss_monotonic_ns() - t0 > HOST_WAIT_NS) { failed = true; break; }
+        std::this_thread::yield();
+      }
+      if (!t_done) {
+        if (fetch) be->stream_synchronize(be->self, rt->fetch_stream);
+        t_done = ss_monotonic_ns();
+      }
+      best = std::min(best, static_cast<double>(t_done - t0));
+    }
+    return best;
+  };
+  const int64_t small = ssc::DIRECT_ALIGN;
+  const double lat_f = time_job(true, false, small), lat_e = time_job(false, false, small);
+  const double e_solo = time_job(false, false, bytes), f_solo = time_job(true, false, bytes);
+  const double f_conc = time_job(true, true, bytes), e_conc = time_job(false, true, bytes);
+  be->stream_synchronize(be->self, rt->fetch_stream);
+  be->stream_synchronize(be->self, rt->evict_stream);
+  if (failed) return SS_IO_ERROR;
   auto rate = [&](double ns, double lat) { return static_cast<double>(bytes) / std::max(ns - lat, 1.0) * 1e9; };
   out->fetch_latency_ns = static_cast<int64_t>(lat_f);
   out->evict_latency_ns = static_cast<int64_t>(lat_e);

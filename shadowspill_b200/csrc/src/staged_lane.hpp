@@ -1,0 +1,119 @@
+// File-backed spill pool and the staged lanes that move bytes between it and the
+// device pool.
+//
+// A transfer is cut into chunks. Each chunk passes through one slot of a bounded ring
+// of pinned host memory: for a fetch a disk thread reads the chunk from the file into
+// the slot and the runtime's worker then enqueues the host-to-device copy; for an
+// evict the worker enqueues the device-to-host copy and, once its event has completed,
+// a disk thread writes the slot to the file. Disk threads only read and write the file
+// and flip slot states; every backend call (copies, events, stream waits) is made by
+// the runtime's worker thread inside pump(). The same division is used by the
+// reference's SSD extension (packages/engine/csrc/ssd/{pool,lane,lane_io}.c).
+//
+// The file is opened twice, with and without O_DIRECT. A chunk whose file offset,
+// length and buffer are all multiples of 4096 goes through the direct descriptor; any
+// other chunk (the ragged tail of an object) and whole-object host I/O use the buffered
+// one. Where the filesystem refuses O_DIRECT everything is buffered.
+#pragma once
+#include "common.hpp"
+
+#include <atomic>
+#include <condition_variable>
+#include <deque>
+#include <functional>
+#include <mutex>
+#include <thread>
+
+namespace ssc {
+
+constexpr int64_t DIRECT_ALIGN = 4096;
+
+class FilePool {
+ public:
+  ~FilePool() { close(); }
+  // directory: where the unlinked scratch file lives. image: optional named file that is
+  // the whole pool and is kept (created when create_image, else opened read-write).
+  int open(const char* directory, const char* image, bool create_image, int64_t bytes,
+           std::string& error);
+  void close();
+  bool is_open() const { return fd_buffered_ >= 0; }
+  bool direct() const { return fd_direct_ >= 0; }
+  int64_t bytes() const { return bytes_; }
+  // Whole-range host I/O (initialisation, checkpoints): buffered, durable on return.
+  int write(int64_t off, const void* src, int64_t n);
+  int read(int64_t off, void* dst, int64_t n);
+  // One chunk for a lane; picks the direct descriptor when everything is aligned.
+  int chunk_io(bool write, void* buf, int64_t off, int64_t n);
+
+ private:
+  int fd_direct_ = -1, fd_buffered_ = -1;
+  int64_t bytes_ = 0;
+};
+
+struct StagedJob {
+  // filled by the submitter
+  bool to_device = true;
+  int64_t file_off = 0;
+  char* dev = nullptr;
+  int64_t bytes = 0;
+  int32_t tag = -1;                                  // the submitter's action index
+  // 0 = waits enqueued, go on; 1 = not yet (the lane retries later); <0 = error
+  std::function<int(StagedJob&)> before_first_copy;
+  std::function<int(StagedJob&)> after_last_copy;    // record completion events
+  std::function<void(StagedJob&)> on_durable;        // evict: every chunk is in the file
+  // lane state
+  int64_t posted = 0;     // fetch: bytes handed to disk threads; evict: bytes whose copy is enqueued
+  int64_t copied = 0;     // fetch: bytes whose copy is enqueued
+  std::atomic<int64_t> written{0};                   // evict: bytes written to the file
+  bool finished = false;
+  void reset() { posted = copied = 0; written.store(0); finished = false; }
+};
+
+class StagedLane {
+ public:
+  StagedLane(ss_backend* be, void* stream, FilePool* pool, bool to_device, int64_t chunk_bytes,
+             int32_t queue_depth, int32_t io_threads);
+  ~StagedLane();
+  int init(int numa_node);                 // allocates the ring and starts the disk threads
+  void submit(StagedJob* job);             // worker thread only
+  // Advances every state machine once. Returns >0 if anything moved, 0 if not, <0 on error
+  // (message() says what failed).
+  int pump();
+  bool busy() const { return !jobs_.empty(); }
+  const std::string& message() const { return message_; }
+  int64_t ring_bytes() const { return chunk_ * depth_; }
+
+ private:
+  enum SlotState : int { FREE = 0, READING, FILLED, COPYING, COPIED, WRITING, WRITTEN, FAILED };
+  struct Slot {
+    char* buf = nullptr;
+    void* event = nullptr;
+    std::atomic<int> state{FREE};
+    StagedJob* job = nullptr;
+    int64_t off = 0, n = 0;                 // offset inside the job
+  };
+  void disk_main();
+  int take_free();
+  int fail(const char* what);
+
+  ss_backend* be_;
+  void* stream_;
+  FilePool* pool_;
+  bool to_device_;
+  int64_t chunk_;
+  int32_t depth_, io_threads_;
+  char* ring_ = nullptr;
+  std::vector<Slot> slots_;
+  std::deque<StagedJob*> jobs_;             // submitted, not finished; FIFO
+  size_t read_cursor_ = 0;                  // fetch: index into jobs_ of the job being read ahead
+  std::deque<int> order_;                   // fetch: slots in posting order; evict: slots copying
+  std::deque<int> copying_;                 // fetch: slots whose copy is in flight
+  std::mutex mu_;
+  std::condition_variable cv_;
+  std::deque<int> disk_queue_;
+  std::vector<std::thread> threads_;
+  bool stop_ = false;
+  std::string message_;
+};
+
+}  // namespace ssc

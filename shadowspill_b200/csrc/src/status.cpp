@@ -19,6 +19,7 @@ const char* ss_status_string(int status) {
     case SS_TIMEOUT: return "timeout";
     case SS_INFEASIBLE: return "infeasible";
     case SS_INTERNAL: return "internal error";
+    case SS_IO_ERROR: return "file pool i/o error";
     default: return "unknown status";
   }
 }

@@ -232,8 +232,12 @@ class Executor:
                  device_index: int = 0, seed: int = 0, hyper: Hyperparameters | None = None,
                  stochastic_rounding: bool = True, trace_capacity: int = 0,
                  mock_bps: float = 0.0, collectives: str = "auto",
-                 extra_plans: dict[str, tuple[Plan, TrainingDescription]] | None = None):
-        """``collectives``: ``peer`` (own kernels over a symmetric device pool),
+                 extra_plans: dict[str, tuple[Plan, TrainingDescription]] | None = None,
+                 file_pool: dict | None = None):
+        """``file_pool``: settings of the file-backed spill pool for plans whose homes were
+        moved there (``planning.plan.move_homes_to_file``): ``directory`` or ``image``
+        (+ ``create_image``), optional ``chunk_bytes`` / ``queue_depth`` / ``io_threads``.
+        ``collectives``: ``peer`` (own kernels over a symmetric device pool),
         ``dist`` (torch.distributed: NCCL or gloo) or ``auto`` (peer on GPUs).
         ``extra_plans``: further operations (``forward_backward``, ``optim_step``,
         ``forward``) admitted into the same runtime; they must have been planned
@@ -288,9 +292,21 @@ class Executor:
             torch.cuda.set_device(device_index)
             from ..ops import _lib
             _lib.lib()   # fail loudly if the kernel library is missing
+        file_bytes = max([plan.file_bytes] + [p.file_bytes for p, _ in extra_plans.values()])
+        fp = dict(file_pool or {})
+        if file_bytes > 0 and not (fp.get("directory") or fp.get("image")):
+            raise ValueError("the plan homes objects in a file pool: pass file_pool={'directory': ...}")
         self.rt = Runtime(device_bytes, spill_bytes, "cuda" if self.cuda else "mock",
                           device_index, trace_capacity=trace_capacity, mock_bps=mock_bps,
-                          device_pool=pool)
+                          device_pool=pool, file_bytes=file_bytes,
+                          file_directory=str(fp.get("directory", "")), file_image=str(fp.get("image", "")),
+                          file_create_image=bool(fp.get("create_image", False)),
+                          file_chunk_bytes=int(fp.get("chunk_bytes", 0)),
+                          file_queue_depth=int(fp.get("queue_depth", 0)),
+                          file_io_threads=int(fp.get("io_threads", 0)))
+        # host mirrors of file-homed objects handed out by spill_view, written back before
+        # the next step: {file offset: (tensor, writable)}
+        self._mirrors: dict[int, tuple[torch.Tensor, bool]] = {}
         self.plan_id = self.rt.admit(plan)
         self.stream = torch.cuda.Stream(device=self.torch_device) if self.cuda else None
         self._views: dict[tuple[int, int], object] = {}
@@ -329,7 +345,10 @@ class Executor:
             j = self._obj.get(name)
             if (j is not None and plan.program.objects[i].persistent
                     and self.program.objects[j].persistent
-                    and plan.spill_offsets[i] != self.plan.spill_offsets[j]):
+                    and (plan.spill_offsets[i] != self.plan.spill_offsets[j]
+                         or plan.home_pool(i) != self.plan.home_pool(j)
+                         or (plan.home_pool(i) == "file"
+                             and plan.file_offsets[i] != self.plan.file_offsets[j]))):
                 raise ValueError(f"plans disagree on the spill home of {name}")
         return {"plan": plan, "desc": desc, "program": plan.program, "runner": runner,
                 "plan_id": self.rt.admit(plan), "_views": {}, "_uses": runner.uses, "T": runner.T,
@@ -351,11 +370,37 @@ class Executor:
         return sorted(self._bound)
 
     # ------------------------------------------------------------------ state in the spill pool
-    def spill_view(self, obj: int) -> torch.Tensor:
+    def spill_view(self, obj: int, writable: bool = True) -> torch.Tensor:
+        """The object's home as host bytes. In the pinned pool this is a view. For an object
+        homed in the file pool it is a host mirror read from the file; a writable mirror is
+        written back by ``flush_homes`` (which every step calls first), so changes made
+        through it reach the file before any fetch can read them."""
+        nbytes = self.program.objects[obj].bytes
+        if self.plan.home_pool(obj) == "file":
+            off = self.plan.file_offsets[obj]
+            hit = self._mirrors.get(off)
+            if hit is not None and hit[0].numel() == nbytes:
+                if writable and not hit[1]:
+                    self._mirrors[off] = (hit[0], True)
+                return hit[0]
+            mirror = self.rt.file_read(off, nbytes)
+            self._mirrors[off] = (mirror, writable)
+            return mirror
         off = self.plan.spill_offsets[obj]
         if off < 0:
             raise KeyError(f"{self.program.objects[obj].name} has no spill home")
-        return self.rt.spill[off:off + self.program.objects[obj].bytes]
+        return self.rt.spill[off:off + nbytes]
+
+    def flush_homes(self) -> int:
+        """Writes every writable mirror back to the file pool and drops all mirrors;
+        returns the bytes written."""
+        total = 0
+        for off, (mirror, writable) in sorted(self._mirrors.items()):
+            if writable:
+                self.rt.file_write(off, mirror)
+                total += mirror.numel()
+        self._mirrors.clear()
+        return total
 
     def initialize(self, seed: int | None = None, on_device: bool | None = None) -> None:
         """Random initialisation of the spill homes (seed-only, so the result does
@@ -408,7 +453,7 @@ class Executor:
         self.runner.completed_updates = 0
         self.runner.accumulated = 0
 
-    def named_tensors(self):
+    def named_tensors(self, writable: bool = True):
         """Yields ``(name, tensor view in the spill pool)`` for every persistent
         model tensor: parameters, then ``exp_avg.*`` / ``exp_avg_sq.*``."""
         for si, st in enumerate(self.stages):
@@ -416,7 +461,7 @@ class Executor:
                 name = f"{st.name}.{kind}"
                 if name not in self._obj:
                     continue
-                flat = self.spill_view(self._obj[name])
+                flat = self.spill_view(self._obj[name], writable)
                 only = kind != "weights"      # moments exist for trainable parameters only
                 if self.world > 1:
                     views = st.shard_views(flat, self.desc.dtype, self.world, only)
@@ -427,7 +472,7 @@ class Executor:
                         yield f"{prefix}{st.name}.{p.name}", views[p.name]
 
     def state_dict(self) -> dict[str, torch.Tensor]:
-        return {k: v.clone() for k, v in self.named_tensors()}
+        return {k: v.clone() for k, v in self.named_tensors(writable=False)}
 
     def load_state_dict(self, state: dict[str, torch.Tensor], strict: bool = True) -> None:
         seen = set()
@@ -534,6 +579,8 @@ class Executor:
             start_ev.record(self.stream)
         task_seconds = [0.0] * n_tasks
         try:
+            if self._mirrors:
+                self.flush_homes()
             self.rt.step_begin(self.plan_id, self.stream.cuda_stream if self.cuda else None)
             for task in range(n_tasks):
                 ptrs = self.rt.before_task(self.plan_id, task, len(self._uses[task]))
@@ -591,6 +638,8 @@ class Executor:
         if self.cuda:
             torch.cuda.synchronize(self.torch_device)
         try:
+            if self._mirrors and self.rt.failure() is None:
+                self.flush_homes()          # a kept pool image must hold the latest state
             for b in self._bound.values():
                 b["_views"].clear()
                 self.rt.close_plan(b["plan_id"])

@@ -102,6 +102,16 @@ class Plan:
     budgets: dict[str, int] = field(default_factory=dict)
     summary: PlanSummary = field(default_factory=PlanSummary)
     communication: dict[str, Any] = field(default_factory=dict)
+    # homes in the file-backed pool (per object, -1 = not there); empty = no file pool.
+    # An object has one home: a non-negative entry here means spill_offsets[o] == -1.
+    file_offsets: list[int] = field(default_factory=list)
+    file_bytes: int = 0
+
+    def home_pool(self, obj: int) -> str:
+        """``"file"``, ``"host"`` or ``""`` (the object never leaves the device)."""
+        if self.file_offsets and self.file_offsets[obj] >= 0:
+            return "file"
+        return "host" if self.spill_offsets[obj] >= 0 else ""
 
     def to_json(self) -> dict[str, Any]:
         return {"format": "ss-b200.plan", "version": 1, "program": self.program.to_json(),
@@ -113,7 +123,8 @@ class Plan:
                 "action_start_ns": self.action_start_ns, "action_end_ns": self.action_end_ns,
                 "device_bytes": self.device_bytes, "spill_bytes": self.spill_bytes,
                 "budgets": self.budgets, "summary": asdict(self.summary),
-                "communication": self.communication}
+                "communication": self.communication, "file_offsets": self.file_offsets,
+                "file_bytes": self.file_bytes}
 
     @staticmethod
     def from_json(d: dict[str, Any]) -> "Plan":
@@ -126,7 +137,8 @@ class Plan:
                     list(d["task_start_ns"]), list(d["task_end_ns"]),
                     list(d["action_start_ns"]), list(d["action_end_ns"]),
                     int(d["device_bytes"]), int(d["spill_bytes"]), dict(d.get("budgets", {})),
-                    PlanSummary(**d.get("summary", {})), dict(d.get("communication", {})))
+                    PlanSummary(**d.get("summary", {})), dict(d.get("communication", {})),
+                    list(d.get("file_offsets", [])), int(d.get("file_bytes", 0)))
 
     def to_native_desc(self):
         """``(native.PlanDesc, keepalive)`` for ``ss_plan_admit``."""
@@ -139,8 +151,10 @@ class Plan:
         ob = native.as_i64([o.bytes for o in self.program.objects])
         so = native.as_i64(self.spill_offsets)
         pb, pi = native.as_i32(self.reuse_pred_begin), native.as_i32(self.reuse_pred_index or [0])
+        fo = native.as_i64(self.file_offsets) if self.file_offsets else None
         desc = native.PlanDesc(prog.n_tasks, prog.n_objects, native.ptr64(ob), native.ptr64(so),
                                len(self.schedule.actions), acts, len(self.stays), ivs,
                                native.ptr32(pb), native.ptr32(pi), prog.n_uses, prog.use_task,
-                               prog.use_object, prog.use_mode)
-        return desc, (keep, acts, ivs, ob, so, pb, pi)
+                               prog.use_object, prog.use_mode,
+                               native.ptr64(fo) if fo is not None else None)
+        return desc, (keep, acts, ivs, ob, so, pb, pi, fo)

@@ -74,7 +74,10 @@ class SearchSummary(C.Structure):
 class RuntimeConfig(C.Structure):
     _fields_ = [("device_bytes", i64), ("spill_bytes", i64), ("numa_node", i32),
                 ("trace_capacity", i32), ("worker_poll_ns", i64), ("max_objects", i32),
-                ("event_pool", i32), ("external_device_base", vp)]
+                ("event_pool", i32), ("external_device_base", vp),
+                ("file_bytes", i64), ("file_directory", C.c_char_p), ("file_image", C.c_char_p),
+                ("file_create_image", i32), ("file_queue_depth", i32), ("file_chunk_bytes", i64),
+                ("file_io_threads", i32), ("reserved0", i32)]
 
 
 class Failure(C.Structure):
@@ -97,7 +100,7 @@ class PlanDesc(C.Structure):
                 ("n_actions", i32), ("actions", C.POINTER(Action)), ("n_intervals", i32),
                 ("intervals", C.POINTER(Interval)), ("reuse_pred_begin", P32),
                 ("reuse_pred_index", P32), ("n_uses", i32), ("use_task", P32),
-                ("use_object", P32), ("use_mode", P32)]
+                ("use_object", P32), ("use_mode", P32), ("file_offset", P64)]
 
 
 class TransferProfile(C.Structure):
@@ -204,6 +207,10 @@ def _declare(lib: C.CDLL) -> None:
     lib.ss_spill_write.argtypes = [vp, i64, vp, i64]
     lib.ss_spill_read.argtypes = [vp, i64, vp, i64]
     lib.ss_calibrate_transfers.argtypes = [vp, i64, i32, C.POINTER(TransferProfile)]
+    lib.ss_calibrate_file_transfers.argtypes = [vp, i64, i32, C.POINTER(TransferProfile)]
+    lib.ss_file_write.argtypes = [vp, i64, vp, i64]
+    lib.ss_file_read.argtypes = [vp, i64, vp, i64]
+    lib.ss_runtime_file_info.argtypes = [vp, C.POINTER(i32), P64]
     lib.ss_blake3_new.restype = vp
     lib.ss_blake3_update.argtypes = [vp, vp, C.c_size_t]
     lib.ss_blake3_update.restype = None

@@ -190,6 +190,46 @@ def plan_program(program: Program, budgets: MemoryBudgets,
     return plan
 
 
+def host_kept(name: str, nbytes: int) -> bool:
+    """Objects the host reads or writes every step stay in pinned memory when the spill pool
+    is a file: packed batches, the loss word and anything too small to be worth a disk I/O."""
+    return name.startswith("batch.") or name == "loss" or nbytes < 4096
+
+
+def move_homes_to_file(plan: Plan, keep_host=host_kept) -> Plan:
+    """Re-homes a plan for a file-backed spill pool (in place; returns the plan).
+
+    Every spilled object keeps its offset but in the file; the few objects ``keep_host``
+    names are packed into a small pinned pool instead (sorted by persistence and name, so
+    that plans of several operations over the same state agree on them). The schedule is
+    untouched: which pool an object's home is in only changes the lanes its transfers use
+    (reference: packages/engine/src/shadowspill/ssd.py:38-110, where the SSD pool takes the
+    place of the pinned spill pool)."""
+    objs = plan.program.objects
+    file_offsets = [-1] * len(objs)
+    kept = []
+    for i, o in enumerate(objs):
+        off = plan.spill_offsets[i]
+        if off < 0:
+            continue
+        if keep_host(o.name, o.bytes):
+            kept.append(i)
+        else:
+            file_offsets[i] = off
+    plan.file_bytes = max(plan.spill_bytes, 4096)
+    cursor = 0
+    for i in sorted(kept, key=lambda i: (not objs[i].persistent, objs[i].name)):
+        plan.spill_offsets[i] = cursor
+        cursor += -(-objs[i].bytes // 4096) * 4096
+    for i, off in enumerate(file_offsets):
+        if off >= 0:
+            plan.spill_offsets[i] = -1
+    plan.file_offsets = file_offsets
+    plan.spill_bytes = max(cursor, 4096)
+    plan.budgets["file_bytes"] = plan.file_bytes
+    return plan
+
+
 @dataclass
 class SweepResult:
     best: Plan

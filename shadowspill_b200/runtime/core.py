@@ -52,9 +52,14 @@ class Runtime:
     def __init__(self, device_bytes: int, spill_bytes: int, backend: str = "cuda",
                  device_index: int = 0, trace_capacity: int = 0, mock_bps: float = 0.0,
                  mock_latency_ns: int = 0, numa_node: int = -1,
-                 device_pool: torch.Tensor | None = None):
+                 device_pool: torch.Tensor | None = None, file_bytes: int = 0,
+                 file_directory: str = "", file_image: str = "", file_create_image: bool = False,
+                 file_chunk_bytes: int = 0, file_queue_depth: int = 0, file_io_threads: int = 0):
         """``device_pool``: a caller-owned uint8 tensor to use as the device pool
-        (a symmetric-memory allocation for multi-GPU plans); it must outlive the runtime."""
+        (a symmetric-memory allocation for multi-GPU plans); it must outlive the runtime.
+        ``file_bytes > 0`` adds a file-backed spill pool in ``file_directory`` (an unlinked
+        scratch file) or in the kept file ``file_image``; objects homed there move through
+        pinned staging rings of ``file_queue_depth`` chunks of ``file_chunk_bytes``."""
         self.lib = native.core()
         self.backend_name = backend
         self.device_index = device_index
@@ -77,8 +82,17 @@ class Runtime:
                 raise ValueError("device_pool is smaller than the plan's device bytes")
             external = device_pool.data_ptr()
             self._external_pool = device_pool
+        if file_bytes > 0 and not (file_directory or file_image):
+            raise ValueError("a file pool needs a directory or an image path")
+        if file_chunk_bytes % 4096:
+            raise ValueError("file_chunk_bytes must be a multiple of 4096")
         cfg = native.RuntimeConfig(int(device_bytes), int(spill_bytes), numa_node,
-                                   int(trace_capacity), 1000, 0, 0, external)
+                                   int(trace_capacity), 1000, 0, 0, external,
+                                   int(file_bytes), str(file_directory).encode() or None,
+                                   str(file_image).encode() or None, int(bool(file_create_image)),
+                                   int(file_queue_depth), int(file_chunk_bytes),
+                                   int(file_io_threads), 0)
+        self.file_bytes = int(file_bytes)
         handle = native.vp()
         native.check(self.lib.ss_runtime_create(self.backend, C.byref(cfg), C.byref(handle)),
                      "ss_runtime_create")
@@ -178,6 +192,32 @@ class Runtime:
                      "ss_calibrate_transfers")
         return TransferRates(p.fetch_solo_bps, p.fetch_concurrent_bps, p.evict_solo_bps,
                              p.evict_concurrent_bps, p.fetch_latency_ns, p.evict_latency_ns)
+
+    def calibrate_file(self, nbytes: int = 256 << 20, repeats: int = 3) -> TransferRates:
+        """Rates of the staged lanes between the device pool and the file pool."""
+        p = native.TransferProfile()
+        self._raise(self.lib.ss_calibrate_file_transfers(self.handle, int(nbytes), repeats, C.byref(p)),
+                    "ss_calibrate_file_transfers")
+        return TransferRates(p.fetch_solo_bps, p.fetch_concurrent_bps, p.evict_solo_bps,
+                             p.evict_concurrent_bps, p.fetch_latency_ns, p.evict_latency_ns)
+
+    def file_write(self, offset: int, data: torch.Tensor) -> None:
+        """Writes a contiguous CPU tensor at ``offset`` of the file pool (durable on return)."""
+        data = data.contiguous()
+        n = data.numel() * data.element_size()
+        self._raise(self.lib.ss_file_write(self.handle, int(offset), data.data_ptr(), n), "ss_file_write")
+
+    def file_read(self, offset: int, nbytes: int) -> torch.Tensor:
+        out = torch.empty(int(nbytes), dtype=torch.uint8)
+        self._raise(self.lib.ss_file_read(self.handle, int(offset), out.data_ptr(), int(nbytes)),
+                    "ss_file_read")
+        return out
+
+    def file_info(self) -> dict:
+        direct, ring = native.i32(0), native.i64(0)
+        native.check(self.lib.ss_runtime_file_info(self.handle, C.byref(direct), C.byref(ring)),
+                     "ss_runtime_file_info")
+        return {"direct_io": bool(direct.value), "ring_bytes": int(ring.value), "bytes": self.file_bytes}
 
     def mock_fail(self, op: str, nth: int) -> None:
         native.check(self.lib.ss_mock_fail_operation(self.backend, native.OP_KINDS.index(op), nth),

@@ -1,0 +1,121 @@
+"""File-backed spill pool and its staged lanes, on the mock backend.
+
+The file lives in a temporary directory; copies are host memcpys on ordered stream
+threads, so the whole path (disk threads, pinned rings, slot events, durable evicts,
+reuse dependencies) runs as it does with a GPU.
+"""
+import copy
+import sys
+
+import pytest
+import torch
+
+sys.path.insert(0, __file__.rsplit("/", 1)[0])
+from test_executor_cpu import _batches, _setup  # noqa: E402
+
+from shadowspill_b200 import native
+from shadowspill_b200.execution.executor import Executor
+from shadowspill_b200.ir.plan import Plan
+from shadowspill_b200.planning.plan import move_homes_to_file
+from shadowspill_b200.runtime.core import Runtime, RuntimeFailure
+
+
+def test_whole_object_io_and_lane_calibration(tmp_path):
+    rt = Runtime(8 << 20, 1 << 20, backend="mock", file_bytes=8 << 20, file_directory=str(tmp_path),
+                 file_chunk_bytes=64 << 10, file_queue_depth=3)
+    info = rt.file_info()
+    assert info["ring_bytes"] == 3 * (64 << 10) and info["bytes"] == 8 << 20
+    data = torch.arange(100_000, dtype=torch.int32)
+    rt.file_write(4096 + 12, data)                       # unaligned offset and length
+    back = rt.file_read(4096 + 12, data.numel() * 4).view(torch.int32)
+    assert torch.equal(back, data)
+    rates = rt.calibrate_file(2 << 20, repeats=2)
+    assert rates.fetch_solo_bps > 0 and rates.evict_solo_bps > 0
+    assert rates.fetch_concurrent_bps <= rates.fetch_solo_bps
+    with pytest.raises(native.NativeError):
+        rt.file_read(8 << 20, 16)                        # outside the pool
+    rt.close()
+    assert list(tmp_path.iterdir()) == []                # the scratch file was never linked
+
+
+def test_runtime_refuses_a_file_home_without_a_file_pool():
+    cfg, plan, desc = _setup()
+    move_homes_to_file(plan)
+    with pytest.raises(ValueError):
+        Executor(plan, desc, device="cpu", seed=1)
+
+
+def _train(plan, desc, cfg, steps=4, **kw):
+    ex = Executor(plan, desc, device="cpu", seed=1, **kw)
+    ex.initialize()
+    losses = [ex.run(_batches(cfg, s)).loss for s in range(steps)]
+    state = ex.state_dict()
+    stats = ex.rt.stats()
+    ex.close()
+    return losses, state, stats
+
+
+@pytest.mark.parametrize("chunk,depth", [(4096, 2), (16 << 10, 3), (1 << 20, 16)])
+def test_training_through_the_file_pool_is_bit_identical(tmp_path, chunk, depth):
+    cfg, plan, desc = _setup()
+    host_losses, host_state, host_stats = _train(copy.deepcopy(plan), desc, cfg)
+    filed = move_homes_to_file(copy.deepcopy(plan))
+    assert filed.file_bytes >= plan.spill_bytes and filed.spill_bytes < plan.spill_bytes
+    n_file = sum(o >= 0 for o in filed.file_offsets)
+    assert n_file > 0 and all(filed.spill_offsets[i] < 0 for i, o in enumerate(filed.file_offsets) if o >= 0)
+    assert filed.home_pool(filed.program.objects.index(
+        next(o for o in filed.program.objects if o.name == "batch.0"))) == "host"
+    # the record survives its JSON form
+    again = Plan.from_json(filed.to_json())
+    assert again.file_offsets == filed.file_offsets and again.file_bytes == filed.file_bytes
+    losses, state, stats = _train(again, desc, cfg, file_pool={
+        "directory": str(tmp_path), "chunk_bytes": chunk, "queue_depth": depth})
+    assert losses == host_losses
+    assert set(state) == set(host_state)
+    for k in state:
+        assert torch.equal(state[k], host_state[k]), k
+    assert stats["fetch_bytes"] == host_stats["fetch_bytes"]
+    assert stats["evict_bytes"] == host_stats["evict_bytes"]
+
+
+def test_a_kept_image_carries_state_to_the_next_run(tmp_path):
+    cfg, plan, desc = _setup()
+    filed = move_homes_to_file(plan)
+    image = tmp_path / "pool.img"
+    ex = Executor(copy.deepcopy(filed), desc, device="cpu", seed=1,
+                  file_pool={"image": str(image), "create_image": True})
+    ex.initialize()
+    first = [ex.run(_batches(cfg, s)).loss for s in range(2)]
+    state = ex.state_dict()
+    done = ex.runner.completed_updates
+    ex.close()
+    assert image.stat().st_size >= filed.file_bytes
+    with pytest.raises(native.NativeError):                 # creating over an existing image is refused
+        Executor(copy.deepcopy(filed), desc, device="cpu", seed=1,
+                 file_pool={"image": str(image), "create_image": True})
+    ex = Executor(copy.deepcopy(filed), desc, device="cpu", seed=1, file_pool={"image": str(image)})
+    ex.runner.completed_updates = done
+    for k, v in ex.state_dict().items():
+        assert torch.equal(v, state[k]), k
+    more = ex.run(_batches(cfg, 2)).loss
+    ex.close()
+    # the same three steps in one run
+    ref = Executor(copy.deepcopy(plan), desc, device="cpu", seed=1, file_pool={"directory": str(tmp_path)})
+    ref.initialize()
+    ref_losses = [ref.run(_batches(cfg, s)).loss for s in range(3)]
+    ref.close()
+    assert first + [more] == ref_losses
+
+
+def test_a_failed_host_copy_in_a_staged_lane_latches(tmp_path):
+    cfg, plan, desc = _setup()
+    ex = Executor(move_homes_to_file(plan), desc, device="cpu", seed=1,
+                  file_pool={"directory": str(tmp_path), "chunk_bytes": 16 << 10, "queue_depth": 2})
+    ex.initialize()
+    ex.run(_batches(cfg))
+    ex.rt.mock_fail("copy", 7)
+    with pytest.raises(RuntimeFailure) as e:
+        ex.run(_batches(cfg, 1))
+    assert e.value.info["pool"] == 2 and "staged" in e.value.info["message"]
+    ex.closed = True
+    ex.rt.close()
