@@ -15,8 +15,7 @@ class ConfigError(ValueError):
 
 def record(cls):
     """Frozen dataclass with ``to_json`` / ``from_json`` and ``validate`` on construction."""
-    cls = dataclasses.dataclass(frozen=True)(cls)
-    orig_post = getattr(cls, "__post_init__", None)
+    orig_post = cls.__dict__.get("__post_init__")
 
     def __post_init__(self):
         if orig_post:
@@ -25,7 +24,9 @@ def record(cls):
         if v:
             v()
 
+    # the generated __init__ only calls a __post_init__ that exists when the class is decorated
     cls.__post_init__ = __post_init__
+    cls = dataclasses.dataclass(frozen=True)(cls)
 
     def to_json(self) -> dict[str, Any]:
         out = {}

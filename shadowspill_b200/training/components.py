@@ -177,6 +177,11 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
     device_gib, spill_gib = float(mem.get("device_gib", 0)), float(mem.get("spill_gib", 0))
     if device_gib <= 0:
         device_gib = 0.9 * hardware.get("device_gib", 180.0); prov["device_gib"] = "automatic 90 %"
+    if mem.get("spill_pool", "host") == "file":
+        import os
+        if spill_gib <= 0 or not os.path.isdir(mem.get("spill_directory", "")):
+            raise ValueError("a file spill pool needs spill_gib and an existing spill_directory on the node")
+        prov["spill_pool"] = f"file in {mem['spill_directory']}"
     if spill_gib <= 0:
         spill_gib = 0.9 * hardware.get("host_free_gib", 64.0) / max(1, workers)
         prov["spill_gib"] = "automatic 90 % of free host memory"
@@ -218,6 +223,9 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
             "search": search, "collectives": ex.get("collectives", "auto"),
             "operations": list(body.get("operations", ("step",))),
             "trace_capacity": 65536 if ex.get("runtime_trace") else 0,
+            "spill_pool": mem.get("spill_pool", "host"), "spill_directory": mem.get("spill_directory", ""),
+            "spill_chunk_bytes": int(mem.get("spill_chunk_bytes", 2 << 20)),
+            "spill_queue_depth": int(mem.get("spill_queue_depth", 16)),
             "lora": _lora_record(m.get("lora"), cfg.is_moe), "objective": _objective_record(body.get("objective")),
             "expert_parallel": (body.get("parallelism") or {}).get("kind") == "expert_parallel",
             "pretrained": (m.get("weights", {}).get("location", "")

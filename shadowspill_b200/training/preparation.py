@@ -29,7 +29,8 @@ def setup_identity(setup, cfg: DecoderConfig) -> str:
     s = asdict(setup) if hasattr(setup, "__dataclass_fields__") else dict(setup)
     keep = {k: s[k] for k in ("device_gib", "spill_gib", "tokens_per_step", "microbatch_tokens", "slots",
                               "mean_seqlen", "dtype", "world_size", "walks", "recompute_shares",
-                              "saved_variant", "candidate_selections", "operations", "device")
+                              "saved_variant", "candidate_selections", "operations", "device",
+                              "spill_pool", "spill_chunk_bytes", "spill_queue_depth")
             if k in s}
     keep["model"] = cfg.to_json()
     keep["search"] = s.get("search")

@@ -81,6 +81,14 @@ class TrainingSetup:
     store: str = ""
     store_mode: str = "read_write"
     operations: tuple[str, ...] = ("step",)   # also: forward_backward, optim_step, forward
+    # spilled state in pinned host memory ("host") or in a direct-I/O file ("file"): then
+    # spill_gib is the file's size and only batches and the loss word stay pinned
+    spill_pool: str = "host"
+    spill_directory: str = ""             # existing directory for the unlinked scratch file
+    spill_image: str = ""                 # or a named file that is kept when the run closes
+    spill_create_image: bool = False
+    spill_chunk_bytes: int = 2 << 20
+    spill_queue_depth: int = 16
 
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
@@ -173,13 +181,27 @@ class TrainingSession:
             dist.broadcast_object_list(flag, src=0)
             from_bundle = flag[0]
         calibrated = None
+        file_spill = setup.spill_pool == "file"
+        if setup.spill_pool not in ("host", "file"):
+            raise ValueError("spill_pool is 'host' or 'file'")
+        if file_spill and not (setup.spill_directory or setup.spill_image):
+            raise ValueError("a file spill pool needs spill_directory or spill_image")
         if setup.calibrate and cuda and not from_bundle:
             t0 = time.perf_counter()
             probe = 256 << 20
             if world > 1:
                 dist.barrier()
-            with Runtime(2 * probe, 2 * probe, "cuda", setup.device_index) as rt:
-                r = rt.calibrate(probe, 3)
+            if file_spill:
+                # rates of the staged lanes (device <-> file), every rank's file on the drive at once
+                import os
+                scratch = setup.spill_directory or os.path.dirname(os.path.abspath(setup.spill_image))
+                with Runtime(2 * probe, 4096, "cuda", setup.device_index, file_bytes=2 * probe,
+                             file_directory=scratch, file_chunk_bytes=setup.spill_chunk_bytes,
+                             file_queue_depth=setup.spill_queue_depth) as rt:
+                    r = rt.calibrate_file(probe, 2)
+            else:
+                with Runtime(2 * probe, 2 * probe, "cuda", setup.device_index) as rt:
+                    r = rt.calibrate(probe, 3)
             rates = torch.tensor([r.fetch_solo_bps, r.fetch_concurrent_bps, r.evict_solo_bps,
                                   r.evict_concurrent_bps], dtype=torch.float64, device="cuda")
             lat = torch.tensor([r.fetch_latency_ns, r.evict_latency_ns], dtype=torch.float64, device="cuda")
@@ -191,7 +213,7 @@ class TrainingSession:
                                            world_size=world,
                                            source="calibrated" if world == 1 else f"calibrated with {world} ranks streaming")
             self.timings["communication"] = time.perf_counter() - t0
-            self.log(f"host link: fetch {rates[0] / 1e9:.1f} ({rates[1] / 1e9:.1f} two-way) GB/s, "
+            self.log(f"{'file pool lanes' if file_spill else 'host link'}: fetch {rates[0] / 1e9:.1f} ({rates[1] / 1e9:.1f} two-way) GB/s, "
                      f"evict {rates[2] / 1e9:.1f} ({rates[3] / 1e9:.1f}) GB/s")
         if loaded is not None:
             from ..ir.plan import Plan
@@ -287,6 +309,20 @@ class TrainingSession:
                 self.desc = build(chosen)[1]
                 self.extra_plans = {op: (Plan.from_json(j), build_extra(op)[1])
                                     for op, j in extra_json.items()}
+        file_pool = None
+        if file_spill:
+            from ..planning.plan import move_homes_to_file
+            move_homes_to_file(self.plan)
+            for xplan, _ in self.extra_plans.values():
+                move_homes_to_file(xplan)
+            image = setup.spill_image
+            if image and world > 1:
+                image = f"{image}.rank{rank}"
+            file_pool = {"directory": setup.spill_directory, "image": image,
+                         "create_image": setup.spill_create_image,
+                         "chunk_bytes": setup.spill_chunk_bytes, "queue_depth": setup.spill_queue_depth}
+            self.log(f"spill pool: {self.plan.file_bytes / 2**30:.2f} GiB file, "
+                     f"{self.plan.spill_bytes / 2**20:.1f} MiB pinned")
         self.log(f"plan: {self.plan.summary.ordering} {self.plan.summary.selection} "
                  f"simulated {self.plan.summary.duration_seconds * 1e3:.1f} ms")
         # ---- executor (caps the torch allocator to the planned workspace)
@@ -301,8 +337,10 @@ class TrainingSession:
                                  device_index=setup.device_index, seed=setup.seed, hyper=hyper,
                                  stochastic_rounding=setup.stochastic_rounding,
                                  trace_capacity=setup.trace_capacity,
-                                 collectives=setup.collectives, extra_plans=self.extra_plans)
-        self.executor.initialize()
+                                 collectives=setup.collectives, extra_plans=self.extra_plans,
+                                 file_pool=file_pool)
+        if not (file_spill and setup.spill_image and not setup.spill_create_image):
+            self.executor.initialize()      # an opened image already holds the state
         if setup.pretrained:
             from ..checkpoint.hf import load_hf
             state = load_hf(self.cfg, setup.pretrained, self.executor.stages)

@@ -119,3 +119,38 @@ def test_a_failed_host_copy_in_a_staged_lane_latches(tmp_path):
     assert e.value.info["pool"] == 2 and "staged" in e.value.info["message"]
     ex.closed = True
     ex.rt.close()
+
+
+def test_session_with_a_file_spill_pool_matches_the_pinned_one(tmp_path):
+    from shadowspill_b200.planning.plan import SearchOptions
+    from shadowspill_b200.training.session import TrainingSession, TrainingSetup
+    common = dict(model="llama3-tiny", device_gib=0.53, spill_gib=0.25, tokens_per_step=512,
+                  microbatch_tokens=256, dtype="float32", stochastic_rounding=False, device="cpu",
+                  profile=False, calibrate=False, seed=3, lr=3e-3,
+                  search=SearchOptions(minimum_object_bytes_evict_eligible=1024, workers=1))
+    losses = {}
+    for pool in ("host", "file"):
+        extra = dict(spill_pool="file", spill_directory=str(tmp_path), spill_chunk_bytes=8192,
+                     spill_queue_depth=4) if pool == "file" else {}
+        s = TrainingSession(TrainingSetup(**common, **extra))
+        cfg = s.cfg
+        losses[pool] = [s.step(_batches(cfg, i)).loss for i in range(3)]
+        if pool == "file":
+            assert s.plan.file_bytes > 0 and s.plan.spill_bytes < 1 << 20
+            s.save(tmp_path / "ckpt")
+            more = s.step(_batches(cfg, 3)).loss
+            s.restore(tmp_path / "ckpt")
+            assert s.step(_batches(cfg, 3)).loss == more
+        s.close()
+    assert losses["file"] == losses["host"]
+    with pytest.raises(ValueError):
+        TrainingSession(TrainingSetup(**common, spill_pool="file"))
+
+
+def test_client_memory_record_validates_the_file_pool(tmp_path):
+    from shadowspill_b200.client import Memory
+    Memory(device_gib=1, spill_gib=2, spill_pool="file", spill_directory=str(tmp_path))
+    for bad in (dict(spill_pool="tape"), dict(spill_pool="file", spill_gib=1),
+                dict(spill_pool="file", spill_gib=1, spill_directory="x", spill_chunk_bytes=1000)):
+        with pytest.raises(ValueError):
+            Memory(**bad)
