@@ -14,5 +14,6 @@ from .packing import BatchError, BatchValidator, pack_batch  # noqa: F401
 from .parallelism import MIN_SHARD_BYTES, data_parallel, expert_parallel  # noqa: F401
 from .schedules import Constant, WarmupCosine  # noqa: F401
 from .service import ServiceClient  # noqa: F401
-from .text import Datum, build_candidates, policy_datum, text_batch, text_datum  # noqa: F401
+from .text import (Datum, build_candidates, policy_datum, tensor_datum, text_batch,  # noqa: F401
+                   text_datum)
 from .training import OperationFailed, TrainingClient, TrainingResult  # noqa: F401

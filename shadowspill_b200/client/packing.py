@@ -57,12 +57,15 @@ class BatchValidator:
                 raise BatchError(f"datum {i} has token ids outside [0, {self.vocab})")
             if not np.isfinite(d.weights).all() or (d.weights < 0).any():
                 raise BatchError(f"datum {i} has negative or non-finite weights")
-            for name in self.extra_fields:
+            for spec in self.extra_fields:
+                name, _, width = spec.partition(":")
                 values = getattr(d, "extras", {}).get(name)
                 if values is None:
-                    raise BatchError(f"datum {i} lacks {name!r}, which this run's objective reads")
-                if len(values) != len(d) or not np.isfinite(values).all():
-                    raise BatchError(f"datum {i}: {name!r} must be finite with one entry per token")
+                    raise BatchError(f"datum {i} lacks {name!r}, which this run reads")
+                values = np.asarray(values)
+                shape = (len(d), int(width)) if width else (len(d),)
+                if values.shape != shape or not np.isfinite(values).all():
+                    raise BatchError(f"datum {i}: {name!r} must be finite with shape {shape}")
             participating += float(d.weights.sum())
         if participating <= 0:
             raise BatchError("no position of the batch participates in the loss")
@@ -102,7 +105,8 @@ def pack_batch(datums: list[Datum], *, microbatch_tokens: int, microbatches: int
         weights = np.zeros(T, np.float32)
         positions = np.zeros(T, np.int32)
         names = sorted({k for d in datums for k in getattr(d, "extras", {})})
-        extras = {k: np.zeros(T, np.float32) for k in names}
+        widths = {k: np.asarray(next(d.extras[k] for d in datums if k in d.extras)).shape[1:] for k in names}
+        extras = {k: np.zeros((T,) + widths[k], np.float32) for k in names}
         cu, pos = [0], 0
         for i in sorted(members):
             d = datums[i]

@@ -64,6 +64,17 @@ def policy_datum(tokens, response_mask, old_logprobs, advantages, reference_logp
     return d
 
 
+def tensor_datum(fields: dict, weight: float = 1.0) -> Datum:
+    """One row of a non-text model (the ``regression`` family): ``fields`` are its named
+    float vectors, e.g. ``{"value": x, "target_values": y}``; ``weight`` scales its loss term.
+    It occupies one row of a microbatch (reference: the ``Datum(inputs, loss_inputs)`` form of
+    packages/client/src/shadowspill_client/protocol/inputs.py used by examples/training/regression)."""
+    if not np.isfinite(weight) or weight < 0:
+        raise ValueError("weight must be finite and non-negative")
+    extras = {k: np.asarray(v, dtype=np.float32).reshape(1, -1) for k, v in fields.items()}
+    return Datum(np.zeros(1, np.int64), np.zeros(1, np.int64), np.full(1, weight, np.float32), extras)
+
+
 def text_batch(sequences, loss_masks=None) -> list[Datum]:
     """Datums whose weights sum to one over the whole batch. ``sequences`` may also hold
     ready ``Datum`` objects (for example from ``policy_datum``), which are only re-weighted."""

@@ -22,7 +22,7 @@ import numpy as np
 import torch
 
 from ..data.synthetic import HostMicrobatch
-from ..frontend.capture import TrainingDescription, batch_layout, saved_layout
+from ..frontend.capture import TrainingDescription, batch_layout, field_spec, saved_layout
 from ..ir.plan import Plan
 from ..models.decoder import BatchMeta, build_stages
 from ..ops import functional as F
@@ -90,9 +90,12 @@ class TaskRunner:
         for name, (off, count, dt) in self.batch_layout_.items():
             tdt = _TORCH_DT[dt]
             parts[name] = flat[off:off + count * tdt.itemsize].view(tdt)
+        extras = {}
+        for spec in self.extra_fields:
+            name, width = field_spec(spec)
+            extras[name] = parts[name] if width == 1 else parts[name].view(self.T, width)
         return BatchMeta(parts["tokens"], parts["targets"], parts["weights"], parts["positions"],
-                         parts["cu_seqlens"], self.max_seqlen[m],
-                         {n: parts[n] for n in self.extra_fields})
+                         parts["cu_seqlens"], self.max_seqlen[m], extras)
 
     def bind(self, task: int, flats: list[torch.Tensor]) -> dict[str, object]:
         """Role -> tensor views for one task over the flat byte tensors of its uses
@@ -505,7 +508,7 @@ class Executor:
                     view[:src.shape[0]] = src
                     view[src.shape[0]:] = src[-1]
                 else:
-                    view[:] = src
+                    view[:] = np.asarray(src).reshape(-1)
                 total += view.nbytes
             self.runner.max_seqlen[m] = int(mb.max_seqlen)
         return total

@@ -46,11 +46,27 @@ class BatchGeometry:
     n_microbatches: int
     slots: int = 64                  # sequence slots per microbatch (cu_seqlens has slots+1)
     mean_seqlen: float = 2048.0
-    extra_fields: tuple[str, ...] = ()   # per-token fp32 fields an objective reads
+    # further per-row fp32 fields the objective or the model reads: "name" or "name:width"
+    extra_fields: tuple[str, ...] = ()
 
     @property
     def tokens(self) -> int:
         return self.microbatch_tokens * self.n_microbatches
+
+
+def field_spec(field_name: str) -> tuple[str, int]:
+    """``"name"`` -> ``(name, 1)``; ``"name:width"`` -> ``(name, width)``."""
+    name, _, width = field_name.partition(":")
+    return name, int(width) if width else 1
+
+
+def extra_fields_for(cfg, objective) -> tuple[str, ...]:
+    """Batch fields beyond tokens/targets/weights/positions for this model and objective."""
+    fields = tuple(objective.extra_fields) if objective is not None else ()
+    if cfg.family == "regression":
+        from ..models.regression import batch_fields
+        fields = batch_fields(cfg) + fields
+    return fields
 
 
 def batch_layout(T: int, slots: int, extras: tuple[str, ...] = ()
@@ -59,7 +75,9 @@ def batch_layout(T: int, slots: int, extras: tuple[str, ...] = ()
     out, off = {}, 0
     fields = [("tokens", T, "int64", 8), ("targets", T, "int64", 8), ("weights", T, "float32", 4),
               ("positions", T, "int32", 4), ("cu_seqlens", slots + 1, "int32", 4)]
-    fields += [(name, T, "float32", 4) for name in extras]
+    for spec in extras:
+        name, width = field_spec(spec)
+        fields.append((name, T * width, "float32", 4))
     for name, count, dt, size in fields:
         out[name] = (off, count, dt)
         off = (off + count * size + ALIGN - 1) // ALIGN * ALIGN
@@ -101,7 +119,7 @@ class TrainingDescription:
     replicas: int = 1
 
     def __post_init__(self) -> None:
-        extras = self.objective.extra_fields if self.objective is not None else ()
+        extras = extra_fields_for(self.cfg, self.objective)
         if tuple(self.geometry.extra_fields) != tuple(extras):
             from dataclasses import replace as _replace
             self.geometry = _replace(self.geometry, extra_fields=tuple(extras))

@@ -140,6 +140,9 @@ PRESETS: dict[str, DecoderConfig] = {
     "qwen35moe-35b-a3b": replace(_qwen35(40, 2048, 16, 2, 256, 0, 16, 32), family="qwen35moe",
                                  n_experts=256, top_k=8, d_expert=512, d_shared_expert=512,
                                  gated_shared_expert=True),
+    # ---- the small non-text model: Linear(16, 32) -> SiLU -> Linear(32, 8), fp32
+    # (d_ff = input width, d_model = hidden width, vocab_size = output width; models/regression.py)
+    "regression": DecoderConfig("regression", 0, 32, 1, 1, 1, 16, 8, initializer_range=0.25),
 }
 
 

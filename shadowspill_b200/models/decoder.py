@@ -58,7 +58,7 @@ class BatchMeta:
     positions: torch.Tensor     # int32 [T]
     cu_seqlens: torch.Tensor    # int32 [S+1]
     max_seqlen: int
-    extras: dict = field(default_factory=dict)   # objective inputs: fp32 [T] each
+    extras: dict = field(default_factory=dict)   # further inputs: fp32 [T] or [T, width] each
 
     @property
     def T(self) -> int:
@@ -537,6 +537,11 @@ def build_stages(cfg: DecoderConfig, objective=None, lora=None,
     the embedding, the head and the base matrices unless ``lora.train_base``.
     ``expert_parallel = (ranks, rank)`` gives routed layers this rank's slice of the
     expert banks."""
+    if cfg.family == "regression":
+        from .regression import build_regression_stages
+        if lora is not None or expert_parallel is not None:
+            raise ValueError("the regression family has no adapters and no experts")
+        return build_regression_stages(cfg)
     base_trainable = lora is None or lora.train_base
     stages: list[Stage] = [EmbeddingStage("embed", cfg, trainable=base_trainable)]
     for i in range(cfg.n_layers):

@@ -81,7 +81,9 @@ class Registry:
 def default_registry() -> Registry:
     r = Registry()
     for name in PRESETS:
-        r.add_model(f"{name}@1", (lambda n=name: preset(n)), capabilities=("text", "packed"))
+        caps = ("tensor",) if PRESETS[name].family == "regression" else ("text", "packed")
+        r.add_model(f"{name}@1", (lambda n=name: preset(n)), capabilities=caps)
+    r.add_model("shadowspill/regression@1", lambda: preset("regression"), capabilities=("tensor",))
     r.add_objective("shadowspill/cross_entropy@1", lambda **kw: {"kind": "cross_entropy", **kw},
                     capabilities=("text",))
     r.add_objective("shadowspill/clipped_policy@1",
@@ -89,6 +91,8 @@ def default_registry() -> Registry:
                                                                 "clip_ratio": clip_ratio,
                                                                 "reference_beta": reference_beta},
                     capabilities=("text",))
+    r.add_objective("shadowspill/weighted_squared_error@1",
+                    lambda **kw: {"kind": "weighted_squared_error", **kw}, capabilities=("tensor",))
     r.add_objective("shadowspill/moe_balance@1", lambda coefficient=0.01: {"kind": "moe_balance",
                                                                            "coefficient": coefficient})
     r.add_objective("shadowspill/sum@1", lambda terms=(): {"kind": "sum", "terms": list(terms)})
@@ -188,6 +192,10 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
     b = body.get("batch", {})
     T, tokens = int(b.get("microbatch_tokens", 8192)), int(b.get("tokens_per_step", 65536))
     slots = int(b.get("max_datums", 0)) or max(16, T // 32 + 1)
+    if cfg.family == "regression":
+        slots = max(slots, T + 1)             # every row is its own datum
+        if m.get("dtype", "bfloat16") != "float32":
+            raise ValueError("the regression family trains in float32: Model(..., dtype='float32')")
     prep = body.get("preparation", {})
     build, planning = prep.get("build", {}), prep.get("planning", {})
     saved_variant = build.get("saved_variant", "save_attention")
@@ -231,11 +239,9 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
             "pretrained": (m.get("weights", {}).get("location", "")
                            if m.get("weights", {}).get("source") == "checkpoint" else "")})
     ob = _objective_record(body.get("objective"))
-    if ob:
-        from ..models.objectives import Objective as _Ob
-        extra_fields = list(_Ob.from_json(ob).extra_fields)
-    else:
-        extra_fields = []
+    from ..frontend.capture import extra_fields_for
+    from ..models.objectives import Objective as _Ob
+    extra_fields = list(extra_fields_for(cfg, _Ob.from_json(ob) if ob else None))
     geometry = {"extra_fields": extra_fields,
                 "microbatch_tokens": T, "microbatches": tokens // T, "slots": slots,
                 "vocab_size": cfg.vocab_size, "workers": workers, "packing": b.get("packing", "best_fit"),

@@ -48,10 +48,13 @@ def validate_microbatches(mbs, geometry: dict) -> None:
             raise InputError(f"microbatch {i}: max_seqlen {mb.max_seqlen} outside [1, {T}]")
         if int(np.diff(cu).max()) > int(mb.max_seqlen):
             raise InputError(f"microbatch {i}: a sequence is longer than the declared max_seqlen")
-        for name in geometry.get("extra_fields", ()):
+        for spec in geometry.get("extra_fields", ()):
+            name, _, width = spec.partition(":")
+            shape = (T, int(width)) if width else (T,)
             a = (getattr(mb, "extras", None) or {}).get(name)
-            if a is None or a.shape != (T,) or not np.isfinite(a).all():
-                raise InputError(f"microbatch {i}: objective input {name!r} missing or malformed")
+            if a is None or a.shape != shape or not np.isfinite(a).all():
+                raise InputError(f"microbatch {i}: input {name!r} missing or malformed "
+                                 f"(expected float32 {shape})")
         participating += float(mb.weights[mb.targets >= 0].sum())
     if participating <= 0:
         raise InputError("no position of the batch participates in the loss")

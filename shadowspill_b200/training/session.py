@@ -104,6 +104,10 @@ class TrainingSession:
         if setup.tokens_per_step % setup.microbatch_tokens:
             raise ValueError("tokens_per_step must be a multiple of microbatch_tokens")
         self.slots = setup.slots or max(16, setup.microbatch_tokens // 32 + 1)
+        if self.cfg.family == "regression":
+            if self.dtype != torch.float32:
+                raise ValueError("the regression family trains in float32")
+            self.slots = max(self.slots, setup.microbatch_tokens + 1)   # every row is its own datum
         self.geometry = BatchGeometry(setup.microbatch_tokens,
                                       setup.tokens_per_step // setup.microbatch_tokens,
                                       self.slots, setup.mean_seqlen)

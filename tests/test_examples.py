@@ -21,3 +21,13 @@ def test_train_budgeted_example(tmp_path):
 def test_service_quickstart_example():
     losses = _load("service_quickstart").main()
     assert len(losses) == 4 and losses[-1] < losses[0]
+
+
+def test_regression_example():
+    losses = _load("regression_training").main(["--steps", "8"])
+    assert len(losses) == 8 and losses[-1] < losses[0]
+
+
+def test_regression_example_on_two_ranks():
+    losses = _load("regression_training").main(["--steps", "6", "--ranks", "2"])
+    assert len(losses) == 6 and losses[-1] < losses[0]

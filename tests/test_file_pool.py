@@ -154,3 +154,59 @@ def test_client_memory_record_validates_the_file_pool(tmp_path):
                 dict(spill_pool="file", spill_gib=1, spill_directory="x", spill_chunk_bytes=1000)):
         with pytest.raises(ValueError):
             Memory(**bad)
+
+
+@pytest.mark.gpu
+def test_file_pool_with_the_cuda_backend_matches_the_pinned_pool(tmp_path):
+    """Real pinned rings, CUDA events on the slots and copies on the lane streams: the same
+    plan run from a file and from pinned memory gives the same losses and state."""
+    from shadowspill_b200.communication.info import CommunicationInfo
+    from shadowspill_b200.data.synthetic import make_batch
+    from shadowspill_b200.execution.executor import Hyperparameters
+    from shadowspill_b200.frontend.capture import BatchGeometry, StepDataOrdering, build_step
+    from shadowspill_b200.models.config import DecoderConfig
+    from shadowspill_b200.planning.plan import MemoryBudgets, PlanningError, SearchOptions, plan_program
+    cfg = DecoderConfig("llama3", 3, 512, 4, 2, 128, 1024, 4096)
+    geo = BatchGeometry(1024, 3, slots=32, mean_seqlen=200)
+    prog, desc = build_step(cfg, geo, StepDataOrdering())
+    total = sum(o.bytes for o in prog.objects)
+    ws = max(t.workspace_bytes for t in prog.tasks)
+    plan = None
+    for pct in range(25, 101, 5):
+        try:
+            plan = plan_program(prog, MemoryBudgets(2 * ws + total * pct // 100, 1 << 30, headroom_bytes=0),
+                                CommunicationInfo(), SearchOptions(minimum_object_bytes_evict_eligible=4096))
+            break
+        except PlanningError:
+            continue
+    assert plan is not None and plan.summary.fetch_bytes > 0
+
+    def run(p, **kw):
+        ex = Executor(p, desc, device="cuda", seed=3, hyper=Hyperparameters(lr=1e-3),
+                      stochastic_rounding=False, **kw)
+        ex.initialize(on_device=False)
+        losses = []
+        for step in range(3):
+            host = make_batch(step, vocab=cfg.vocab_size, tokens_per_step=3072, microbatch_tokens=1024,
+                              median=200, min_len=16, max_len=512, slots=32)
+            losses.append(ex.run(host).loss)
+        state = ex.state_dict()
+        info = ex.rt.file_info() if p.file_bytes else None
+        ex.close()
+        return losses, state, info
+
+    host_losses, host_state, _ = run(copy.deepcopy(plan))
+    filed = move_homes_to_file(copy.deepcopy(plan))
+    losses, state, info = run(filed, file_pool={"directory": str(tmp_path), "chunk_bytes": 256 << 10,
+                                                "queue_depth": 4})
+    assert info["ring_bytes"] == 1 << 20
+    # the only run-to-run difference is the atomic order of embedding gradients
+    for a, b in zip(losses, host_losses):
+        assert abs(a - b) < 1e-3 * abs(b)
+    for k, v in host_state.items():
+        a, b = state[k].float().reshape(-1), v.float().reshape(-1)
+        assert float((a - b).norm() / (b.norm() + 1e-12)) < 2.5e-2, k
+    rt = Runtime(64 << 20, 4096, backend="cuda", file_bytes=64 << 20, file_directory=str(tmp_path))
+    rates = rt.calibrate_file(16 << 20, repeats=2)
+    assert rates.fetch_solo_bps > 0 and rates.evict_solo_bps > 0
+    rt.close()
