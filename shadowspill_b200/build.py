@@ -24,6 +24,7 @@ KERNEL_LIB = ROOT / "ops" / "libss_kernels.so"
 CORE_DIR = ROOT / "csrc"
 CORE_LIB = CORE_DIR / "libss_core.so"
 CUDA_BACKEND_LIB = CORE_DIR / "libss_backend_cuda.so"
+MEMORY_DAEMON = CORE_DIR / "ss_memory_daemon"     # far side of the remote spill pool
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -93,7 +94,7 @@ def _cuda_home() -> Path | None:
 def build_core(force: bool = False, verbose: bool = False) -> Path:
     """Compile the C++17 core (simulator, planner, runtime, mock backend)."""
     sources = sorted(p for p in CORE_DIR.rglob("*.cpp") if "backend_cuda" not in p.name
-                     and "canary" not in p.name)
+                     and "canary" not in p.name and p.parent.name != "daemon")
     headers = sorted(CORE_DIR.rglob("*.h")) + sorted(CORE_DIR.rglob("*.hpp"))
     if not sources:
         return CORE_LIB
@@ -102,6 +103,12 @@ def build_core(force: bool = False, verbose: bool = False) -> Path:
         _run(["g++", *CXX_FLAGS, "-shared", "-I", str(CORE_DIR / "include"), "-o", str(tmp),
               *map(str, sources), "-ldl"], verbose)
         os.replace(tmp, CORE_LIB)
+    daemon_src = sorted((CORE_DIR / "daemon").glob("*.cpp"))
+    if daemon_src and (force or _stale(MEMORY_DAEMON, daemon_src)):
+        tmp = MEMORY_DAEMON.with_suffix(".tmp")
+        _run(["g++", "-O2", "-g", "-std=c++17", "-Wall", "-Wextra", "-pthread", "-o", str(tmp),
+              *map(str, daemon_src)], verbose)
+        os.replace(tmp, MEMORY_DAEMON)
     cuda_src = sorted(CORE_DIR.rglob("backend_cuda*.cpp"))
     cuda = _cuda_home()
     if cuda_src and cuda is not None and (force or _stale(CUDA_BACKEND_LIB, cuda_src + headers)):

@@ -118,19 +118,24 @@ class BatchConfig:
 class Memory:
     device_gib: float = 0.0                   # 0 = automatic: 90 % of the device
     spill_gib: float = 0.0                    # 0 = automatic: 90 % of free host memory
-    # where spilled state lives: "host" (pinned memory) or "file" (a direct-I/O file on a local
-    # drive of the worker's node, staged through small pinned rings)
+    # where spilled state lives: "host" (pinned memory), "file" (a direct-I/O file on a local
+    # drive of the worker's node) or "remote" (memory of an ss_memory_daemon); the last two are
+    # staged through small pinned rings
     spill_pool: str = "host"
+    spill_address: str = ""                   # "remote": host:port of the memory daemon
     spill_directory: str = ""                 # "file": existing directory for the scratch file
     spill_chunk_bytes: int = 2 << 20          # "file": staged piece of a transfer, multiple of 4096
     spill_queue_depth: int = 16               # "file": chunks staged at once per direction
 
     def validate(self):
         require(self.device_gib >= 0 and self.spill_gib >= 0, "memory budgets are non-negative")
-        require(self.spill_pool in ("host", "file"), "spill_pool is 'host' or 'file'")
+        require(self.spill_pool in ("host", "file", "remote"), "spill_pool is 'host', 'file' or 'remote'")
+        if self.spill_pool == "remote":
+            require(":" in self.spill_address, "a remote spill pool needs spill_address = host:port")
         if self.spill_pool == "file":
             require(bool(self.spill_directory), "a file spill pool needs spill_directory")
-            require(self.spill_gib > 0, "a file spill pool needs an explicit spill_gib")
+        if self.spill_pool != "host":
+            require(self.spill_gib > 0, "a file or remote spill pool needs an explicit spill_gib")
             require(self.spill_chunk_bytes > 0 and self.spill_chunk_bytes % 4096 == 0
                     and self.spill_chunk_bytes <= 1 << 30, "spill_chunk_bytes: multiple of 4096, at most 1 GiB")
             require(1 <= self.spill_queue_depth <= 1024, "spill_queue_depth is between 1 and 1024")

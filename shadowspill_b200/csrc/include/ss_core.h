@@ -245,6 +245,9 @@ typedef struct ss_runtime_config {
   int64_t file_chunk_bytes;    /* multiple of 4096; 0 = 2 MiB */
   int32_t file_io_threads;     /* disk threads per direction; 0 = 2 */
   int32_t reserved0;
+  /* "host:port" of a memory daemon: the pool's file_bytes are then held by that daemon
+   * instead of a local file (same staged lanes, chunks travel over TCP). */
+  const char* remote_address;
 } ss_runtime_config;
 
 typedef struct ss_failure {
@@ -346,7 +349,8 @@ int ss_spill_read(ss_runtime* rt, int64_t spill_offset, void* dst, int64_t bytes
 /* The same for objects whose home is the file pool. */
 int ss_file_write(ss_runtime* rt, int64_t file_offset, const void* src, int64_t bytes);
 int ss_file_read(ss_runtime* rt, int64_t file_offset, void* dst, int64_t bytes);
-/* direct: 1 if the pool file accepted O_DIRECT. ring_bytes: pinned staging per direction. */
+/* direct: 1 if the pool file accepted O_DIRECT (0 for a remote pool). ring_bytes: pinned
+ * staging per direction. */
 int ss_runtime_file_info(ss_runtime* rt, int32_t* direct, int64_t* ring_bytes);
 
 /* Route calibration: times copies of `bytes` alone and with the opposite

@@ -86,7 +86,9 @@ struct ss_runtime {
   void* spill_base = nullptr;
   void* fetch_stream = nullptr;
   void* evict_stream = nullptr;
-  ssc::FilePool file;
+  ssc::FilePool local_file;
+  ssc::RemotePool remote;
+  ssc::ChunkStore* store = nullptr;        // whichever of the two is open
   std::unique_ptr<ssc::StagedLane> fetch_lane, evict_lane;
   std::mutex mu;                      // guards plans map and worker handoff
   std::condition_variable cv;
@@ -413,25 +415,31 @@ int ss_runtime_create(ss_backend* backend, const ss_runtime_config* config, ss_r
   if (rc == SS_OK) rc = backend->stream_create(backend->self, &rt->evict_stream);
   if (rc == SS_OK && config->file_bytes > 0) {
     std::string error;
-    rc = rt->file.open(config->file_directory, config->file_image, config->file_create_image != 0,
-                       config->file_bytes, error);
+    if (config->remote_address && *config->remote_address) {
+      rc = rt->remote.open(config->remote_address, config->file_bytes, error);
+      rt->store = &rt->remote;
+    } else {
+      rc = rt->local_file.open(config->file_directory, config->file_image, config->file_create_image != 0,
+                               config->file_bytes, error);
+      rt->store = &rt->local_file;
+    }
     if (rc != SS_OK) std::fprintf(stderr, "ss runtime: %s\n", error.c_str());
     const int64_t chunk = config->file_chunk_bytes > 0 ? config->file_chunk_bytes : (2ll << 20);
     const int32_t depth = config->file_queue_depth > 0 ? config->file_queue_depth : 16;
     const int32_t io = config->file_io_threads > 0 ? config->file_io_threads : 2;
     if (rc == SS_OK) {
-      rt->fetch_lane = std::make_unique<ssc::StagedLane>(backend, rt->fetch_stream, &rt->file, true, chunk, depth, io);
-      rt->evict_lane = std::make_unique<ssc::StagedLane>(backend, rt->evict_stream, &rt->file, false, chunk, depth, io);
+      rt->fetch_lane = std::make_unique<ssc::StagedLane>(backend, rt->fetch_stream, rt->store, true, chunk, depth, io);
+      rt->evict_lane = std::make_unique<ssc::StagedLane>(backend, rt->evict_stream, rt->store, false, chunk, depth, io);
       rc = rt->fetch_lane->init(config->numa_node);
       if (rc == SS_OK) rc = rt->evict_lane->init(config->numa_node);
       rt->st_host_allocs += 2;
     }
     // the strings belong to the caller
-    rt->cfg.file_directory = rt->cfg.file_image = nullptr;
+    rt->cfg.file_directory = rt->cfg.file_image = rt->cfg.remote_address = nullptr;
   }
   if (rc != SS_OK) {
     rt->fetch_lane.reset(); rt->evict_lane.reset();
-    rt->file.close();
+    rt->local_file.close(); rt->remote.close(); rt->store = nullptr;
     if (rt->evict_stream) backend->stream_destroy(backend->self, rt->evict_stream);
     if (rt->fetch_stream) backend->stream_destroy(backend->self, rt->fetch_stream);
     if (rt->device_base && !rt->device_external) backend->device_free(backend->self, rt->device_base);
@@ -466,7 +474,7 @@ int ss_runtime_close(ss_runtime* rt) {
   be->stream_synchronize(be->self, rt->evict_stream);
   rt->fetch_lane.reset();            // joins the disk threads, frees the rings
   rt->evict_lane.reset();
-  rt->file.close();
+  rt->local_file.close(); rt->remote.close(); rt->store = nullptr;
   for (auto& kv : rt->plans) release_plan(rt, *kv.second);
   rt->plans.clear();
   be->stream_destroy(be->self, rt->fetch_stream);
@@ -551,8 +559,8 @@ int ss_plan_admit(ss_runtime* rt, const ss_plan_desc* d, int32_t* plan_id) {
     P->file_offset.assign(d->file_offset, d->file_offset + d->n_objects);
     for (int32_t o = 0; o < d->n_objects; ++o) {
       if (P->file_offset[o] < 0) continue;
-      if (!rt->file.is_open() || P->spill_offset[o] >= 0 || d->object_bytes[o] <= 0 ||
-          P->file_offset[o] + d->object_bytes[o] > rt->file.bytes())
+      if (!rt->store || P->spill_offset[o] >= 0 || d->object_bytes[o] <= 0 ||
+          P->file_offset[o] + d->object_bytes[o] > rt->store->bytes())
         return SS_INVALID_ARGUMENT;      // no file pool, two homes, or outside the file
     }
   }
@@ -882,23 +890,23 @@ int ss_calibrate_transfers(ss_runtime* rt, int64_t bytes, int32_t repeats, ss_tr
 }
 
 int ss_file_write(ss_runtime* rt, int64_t off, const void* src, int64_t bytes) {
-  if (!rt || !rt->file.is_open()) return SS_INVALID_ARGUMENT;
-  return rt->file.write(off, src, bytes);
+  if (!rt || !rt->store) return SS_INVALID_ARGUMENT;
+  return rt->store->write(off, src, bytes);
 }
 int ss_file_read(ss_runtime* rt, int64_t off, void* dst, int64_t bytes) {
-  if (!rt || !rt->file.is_open()) return SS_INVALID_ARGUMENT;
-  return rt->file.read(off, dst, bytes);
+  if (!rt || !rt->store) return SS_INVALID_ARGUMENT;
+  return rt->store->read(off, dst, bytes);
 }
 int ss_runtime_file_info(ss_runtime* rt, int32_t* direct, int64_t* ring_bytes) {
-  if (!rt || !rt->file.is_open()) return SS_INVALID_ARGUMENT;
-  if (direct) *direct = rt->file.direct() ? 1 : 0;
+  if (!rt || !rt->store) return SS_INVALID_ARGUMENT;
+  if (direct) *direct = rt->local_file.direct() ? 1 : 0;
   if (ring_bytes) *ring_bytes = rt->fetch_lane ? rt->fetch_lane->ring_bytes() : 0;
   return SS_OK;
 }
 
 int ss_calibrate_file_transfers(ss_runtime* rt, int64_t bytes, int32_t repeats, ss_transfer_profile* out) {
-  if (!rt || !out || !rt->file.is_open() || bytes <= 0 || bytes > rt->cfg.device_bytes / 2 ||
-      bytes > rt->file.bytes() / 2)
+  if (!rt || !out || !rt->store || bytes <= 0 || bytes > rt->cfg.device_bytes / 2 ||
+      bytes > rt->store->bytes() / 2)
     return SS_INVALID_ARGUMENT;
   if (repeats <= 0) repeats = 3;
   ss_backend* be = rt->be;

@@ -112,7 +112,7 @@ int FilePool::chunk_io(bool write, void* buf, int64_t off, int64_t n) {
 }
 
 // ------------------------------------------------------------------ StagedLane
-StagedLane::StagedLane(ss_backend* be, void* stream, FilePool* pool, bool to_device,
+StagedLane::StagedLane(ss_backend* be, void* stream, ChunkStore* pool, bool to_device,
                        int64_t chunk_bytes, int32_t queue_depth, int32_t io_threads)
     : be_(be), stream_(stream), pool_(pool), to_device_(to_device), chunk_(chunk_bytes),
       depth_(queue_depth), io_threads_(std::max(1, io_threads)), slots_(static_cast<size_t>(queue_depth)) {}

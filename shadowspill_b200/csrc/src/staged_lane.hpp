@@ -28,26 +28,75 @@ namespace ssc {
 
 constexpr int64_t DIRECT_ALIGN = 4096;
 
-class FilePool {
+// Where a staged lane's chunks live: a local file or memory held by a remote daemon.
+class ChunkStore {
  public:
-  ~FilePool() { close(); }
+  virtual ~ChunkStore() = default;
+  virtual bool is_open() const = 0;
+  virtual int64_t bytes() const = 0;
+  // Whole-range host I/O (initialisation, checkpoints); complete on return.
+  virtual int write(int64_t off, const void* src, int64_t n) = 0;
+  virtual int read(int64_t off, void* dst, int64_t n) = 0;
+  // One chunk for a lane; called from several disk threads at once.
+  virtual int chunk_io(bool write, void* buf, int64_t off, int64_t n) = 0;
+};
+
+class FilePool : public ChunkStore {
+ public:
+  ~FilePool() override { close(); }
   // directory: where the unlinked scratch file lives. image: optional named file that is
   // the whole pool and is kept (created when create_image, else opened read-write).
   int open(const char* directory, const char* image, bool create_image, int64_t bytes,
            std::string& error);
   void close();
-  bool is_open() const { return fd_buffered_ >= 0; }
+  bool is_open() const override { return fd_buffered_ >= 0; }
   bool direct() const { return fd_direct_ >= 0; }
-  int64_t bytes() const { return bytes_; }
-  // Whole-range host I/O (initialisation, checkpoints): buffered, durable on return.
-  int write(int64_t off, const void* src, int64_t n);
-  int read(int64_t off, void* dst, int64_t n);
-  // One chunk for a lane; picks the direct descriptor when everything is aligned.
-  int chunk_io(bool write, void* buf, int64_t off, int64_t n);
+  int64_t bytes() const override { return bytes_; }
+  // buffered, durable on return
+  int write(int64_t off, const void* src, int64_t n) override;
+  int read(int64_t off, void* dst, int64_t n) override;
+  // picks the direct descriptor when everything is aligned
+  int chunk_io(bool write, void* buf, int64_t off, int64_t n) override;
 
  private:
   int fd_direct_ = -1, fd_buffered_ = -1;
   int64_t bytes_ = 0;
+};
+
+// A region of host memory held by a memory daemon on another machine (or this one),
+// reached over TCP. Control and data use one line-oriented protocol:
+//   ALLOCATE <bytes>          -> OK <region>        the region lives while this connection does
+//   CONNECT <region>          -> OK <bytes>         further data connections of the same client
+//   WRITE <offset> <n> + n B  -> OK
+//   READ <offset> <n>         -> OK <n> + n B
+//   FREE <region>             -> OK
+//   STAT                      -> OK <regions> <bytes held>
+// Every calling thread borrows a connection from a small pool, so disk threads of both
+// lanes stream concurrently. The reference's network extension moves the same chunks with
+// one-sided RDMA where a NIC allows and through a staged host ring otherwise
+// (packages/engine/csrc/network/src/{remote_memory,remote_lane_staging,control}.c); this is
+// the staged form over sockets.
+class RemotePool : public ChunkStore {
+ public:
+  ~RemotePool() override { close(); }
+  int open(const char* address, int64_t bytes, std::string& error);   // "host:port"
+  void close();
+  bool is_open() const override { return control_fd_ >= 0; }
+  int64_t bytes() const override { return bytes_; }
+  int write(int64_t off, const void* src, int64_t n) override { return chunk_io(true, const_cast<void*>(src), off, n); }
+  int read(int64_t off, void* dst, int64_t n) override { return chunk_io(false, dst, off, n); }
+  int chunk_io(bool write, void* buf, int64_t off, int64_t n) override;
+
+ private:
+  int connect_data();
+  int borrow();
+  void give_back(int fd);
+  std::string host_;
+  int port_ = 0;
+  int control_fd_ = -1;
+  int64_t region_ = -1, bytes_ = 0;
+  std::mutex mu_;
+  std::vector<int> idle_;
 };
 
 struct StagedJob {
@@ -71,7 +120,7 @@ struct StagedJob {
 
 class StagedLane {
  public:
-  StagedLane(ss_backend* be, void* stream, FilePool* pool, bool to_device, int64_t chunk_bytes,
+  StagedLane(ss_backend* be, void* stream, ChunkStore* pool, bool to_device, int64_t chunk_bytes,
              int32_t queue_depth, int32_t io_threads);
   ~StagedLane();
   int init(int numa_node);                 // allocates the ring and starts the disk threads
@@ -98,7 +147,7 @@ class StagedLane {
 
   ss_backend* be_;
   void* stream_;
-  FilePool* pool_;
+  ChunkStore* pool_;
   bool to_device_;
   int64_t chunk_;
   int32_t depth_, io_threads_;

@@ -239,7 +239,8 @@ class Executor:
                  file_pool: dict | None = None):
         """``file_pool``: settings of the file-backed spill pool for plans whose homes were
         moved there (``planning.plan.move_homes_to_file``): ``directory`` or ``image``
-        (+ ``create_image``), optional ``chunk_bytes`` / ``queue_depth`` / ``io_threads``.
+        (+ ``create_image``) or ``remote`` ("host:port" of a memory daemon), optional
+        ``chunk_bytes`` / ``queue_depth`` / ``io_threads``.
         ``collectives``: ``peer`` (own kernels over a symmetric device pool),
         ``dist`` (torch.distributed: NCCL or gloo) or ``auto`` (peer on GPUs).
         ``extra_plans``: further operations (``forward_backward``, ``optim_step``,
@@ -297,8 +298,9 @@ class Executor:
             _lib.lib()   # fail loudly if the kernel library is missing
         file_bytes = max([plan.file_bytes] + [p.file_bytes for p, _ in extra_plans.values()])
         fp = dict(file_pool or {})
-        if file_bytes > 0 and not (fp.get("directory") or fp.get("image")):
-            raise ValueError("the plan homes objects in a file pool: pass file_pool={'directory': ...}")
+        if file_bytes > 0 and not (fp.get("directory") or fp.get("image") or fp.get("remote")):
+            raise ValueError("the plan homes objects in a file pool: pass file_pool={'directory': ...} "
+                             "(or 'image', or 'remote': 'host:port' of a memory daemon)")
         self.rt = Runtime(device_bytes, spill_bytes, "cuda" if self.cuda else "mock",
                           device_index, trace_capacity=trace_capacity, mock_bps=mock_bps,
                           device_pool=pool, file_bytes=file_bytes,
@@ -306,7 +308,8 @@ class Executor:
                           file_create_image=bool(fp.get("create_image", False)),
                           file_chunk_bytes=int(fp.get("chunk_bytes", 0)),
                           file_queue_depth=int(fp.get("queue_depth", 0)),
-                          file_io_threads=int(fp.get("io_threads", 0)))
+                          file_io_threads=int(fp.get("io_threads", 0)),
+                          remote_address=str(fp.get("remote", "")))
         # host mirrors of file-homed objects handed out by spill_view, written back before
         # the next step: {file offset: (tensor, writable)}
         self._mirrors: dict[int, tuple[torch.Tensor, bool]] = {}

@@ -77,7 +77,7 @@ class RuntimeConfig(C.Structure):
                 ("event_pool", i32), ("external_device_base", vp),
                 ("file_bytes", i64), ("file_directory", C.c_char_p), ("file_image", C.c_char_p),
                 ("file_create_image", i32), ("file_queue_depth", i32), ("file_chunk_bytes", i64),
-                ("file_io_threads", i32), ("reserved0", i32)]
+                ("file_io_threads", i32), ("reserved0", i32), ("remote_address", C.c_char_p)]
 
 
 class Failure(C.Structure):

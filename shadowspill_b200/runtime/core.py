@@ -54,12 +54,15 @@ class Runtime:
                  mock_latency_ns: int = 0, numa_node: int = -1,
                  device_pool: torch.Tensor | None = None, file_bytes: int = 0,
                  file_directory: str = "", file_image: str = "", file_create_image: bool = False,
-                 file_chunk_bytes: int = 0, file_queue_depth: int = 0, file_io_threads: int = 0):
+                 file_chunk_bytes: int = 0, file_queue_depth: int = 0, file_io_threads: int = 0,
+                 remote_address: str = ""):
         """``device_pool``: a caller-owned uint8 tensor to use as the device pool
         (a symmetric-memory allocation for multi-GPU plans); it must outlive the runtime.
         ``file_bytes > 0`` adds a file-backed spill pool in ``file_directory`` (an unlinked
         scratch file) or in the kept file ``file_image``; objects homed there move through
-        pinned staging rings of ``file_queue_depth`` chunks of ``file_chunk_bytes``."""
+        pinned staging rings of ``file_queue_depth`` chunks of ``file_chunk_bytes``.
+        ``remote_address`` ("host:port" of an ``ss_memory_daemon``) keeps those bytes in the
+        daemon's memory instead of a local file."""
         self.lib = native.core()
         self.backend_name = backend
         self.device_index = device_index
@@ -82,8 +85,8 @@ class Runtime:
                 raise ValueError("device_pool is smaller than the plan's device bytes")
             external = device_pool.data_ptr()
             self._external_pool = device_pool
-        if file_bytes > 0 and not (file_directory or file_image):
-            raise ValueError("a file pool needs a directory or an image path")
+        if file_bytes > 0 and not (file_directory or file_image or remote_address):
+            raise ValueError("a file pool needs a directory, an image path or a daemon address")
         if file_chunk_bytes % 4096:
             raise ValueError("file_chunk_bytes must be a multiple of 4096")
         cfg = native.RuntimeConfig(int(device_bytes), int(spill_bytes), numa_node,
@@ -91,7 +94,7 @@ class Runtime:
                                    int(file_bytes), str(file_directory).encode() or None,
                                    str(file_image).encode() or None, int(bool(file_create_image)),
                                    int(file_queue_depth), int(file_chunk_bytes),
-                                   int(file_io_threads), 0)
+                                   int(file_io_threads), 0, str(remote_address).encode() or None)
         self.file_bytes = int(file_bytes)
         handle = native.vp()
         native.check(self.lib.ss_runtime_create(self.backend, C.byref(cfg), C.byref(handle)),

@@ -186,6 +186,10 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
         if spill_gib <= 0 or not os.path.isdir(mem.get("spill_directory", "")):
             raise ValueError("a file spill pool needs spill_gib and an existing spill_directory on the node")
         prov["spill_pool"] = f"file in {mem['spill_directory']}"
+    if mem.get("spill_pool") == "remote":
+        if spill_gib <= 0 or ":" not in mem.get("spill_address", ""):
+            raise ValueError("a remote spill pool needs spill_gib and spill_address = host:port")
+        prov["spill_pool"] = f"memory daemon at {mem['spill_address']}"
     if spill_gib <= 0:
         spill_gib = 0.9 * hardware.get("host_free_gib", 64.0) / max(1, workers)
         prov["spill_gib"] = "automatic 90 % of free host memory"
@@ -232,6 +236,7 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
             "operations": list(body.get("operations", ("step",))),
             "trace_capacity": 65536 if ex.get("runtime_trace") else 0,
             "spill_pool": mem.get("spill_pool", "host"), "spill_directory": mem.get("spill_directory", ""),
+            "spill_address": mem.get("spill_address", ""),
             "spill_chunk_bytes": int(mem.get("spill_chunk_bytes", 2 << 20)),
             "spill_queue_depth": int(mem.get("spill_queue_depth", 16)),
             "lora": _lora_record(m.get("lora"), cfg.is_moe), "objective": _objective_record(body.get("objective")),

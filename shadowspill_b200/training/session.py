@@ -83,7 +83,9 @@ class TrainingSetup:
     operations: tuple[str, ...] = ("step",)   # also: forward_backward, optim_step, forward
     # spilled state in pinned host memory ("host") or in a direct-I/O file ("file"): then
     # spill_gib is the file's size and only batches and the loss word stay pinned
+    # ... or in the memory of an ss_memory_daemon on another machine ("remote", spill_address)
     spill_pool: str = "host"
+    spill_address: str = ""               # "remote": host:port of the daemon
     spill_directory: str = ""             # existing directory for the unlinked scratch file
     spill_image: str = ""                 # or a named file that is kept when the run closes
     spill_create_image: bool = False
@@ -185,11 +187,14 @@ class TrainingSession:
             dist.broadcast_object_list(flag, src=0)
             from_bundle = flag[0]
         calibrated = None
-        file_spill = setup.spill_pool == "file"
-        if setup.spill_pool not in ("host", "file"):
-            raise ValueError("spill_pool is 'host' or 'file'")
-        if file_spill and not (setup.spill_directory or setup.spill_image):
+        file_spill = setup.spill_pool in ("file", "remote")
+        remote = setup.spill_address if setup.spill_pool == "remote" else ""
+        if setup.spill_pool not in ("host", "file", "remote"):
+            raise ValueError("spill_pool is 'host', 'file' or 'remote'")
+        if setup.spill_pool == "file" and not (setup.spill_directory or setup.spill_image):
             raise ValueError("a file spill pool needs spill_directory or spill_image")
+        if setup.spill_pool == "remote" and not remote:
+            raise ValueError("a remote spill pool needs spill_address (host:port of a memory daemon)")
         if setup.calibrate and cuda and not from_bundle:
             t0 = time.perf_counter()
             probe = 256 << 20
@@ -198,9 +203,11 @@ class TrainingSession:
             if file_spill:
                 # rates of the staged lanes (device <-> file), every rank's file on the drive at once
                 import os
-                scratch = setup.spill_directory or os.path.dirname(os.path.abspath(setup.spill_image))
+                scratch = "" if remote else (setup.spill_directory
+                                             or os.path.dirname(os.path.abspath(setup.spill_image)))
                 with Runtime(2 * probe, 4096, "cuda", setup.device_index, file_bytes=2 * probe,
-                             file_directory=scratch, file_chunk_bytes=setup.spill_chunk_bytes,
+                             file_directory=scratch, remote_address=remote,
+                             file_chunk_bytes=setup.spill_chunk_bytes,
                              file_queue_depth=setup.spill_queue_depth) as rt:
                     r = rt.calibrate_file(probe, 2)
             else:
@@ -217,7 +224,7 @@ class TrainingSession:
                                            world_size=world,
                                            source="calibrated" if world == 1 else f"calibrated with {world} ranks streaming")
             self.timings["communication"] = time.perf_counter() - t0
-            self.log(f"{'file pool lanes' if file_spill else 'host link'}: fetch {rates[0] / 1e9:.1f} ({rates[1] / 1e9:.1f} two-way) GB/s, "
+            self.log(f"{'staged lanes' if file_spill else 'host link'}: fetch {rates[0] / 1e9:.1f} ({rates[1] / 1e9:.1f} two-way) GB/s, "
                      f"evict {rates[2] / 1e9:.1f} ({rates[3] / 1e9:.1f}) GB/s")
         if loaded is not None:
             from ..ir.plan import Plan
@@ -322,10 +329,11 @@ class TrainingSession:
             image = setup.spill_image
             if image and world > 1:
                 image = f"{image}.rank{rank}"
-            file_pool = {"directory": setup.spill_directory, "image": image,
+            file_pool = {"directory": setup.spill_directory, "image": image, "remote": remote,
                          "create_image": setup.spill_create_image,
                          "chunk_bytes": setup.spill_chunk_bytes, "queue_depth": setup.spill_queue_depth}
-            self.log(f"spill pool: {self.plan.file_bytes / 2**30:.2f} GiB file, "
+            self.log(f"spill pool: {self.plan.file_bytes / 2**30:.2f} GiB "
+                     f"{'at ' + remote if remote else 'file'}, "
                      f"{self.plan.spill_bytes / 2**20:.1f} MiB pinned")
         self.log(f"plan: {self.plan.summary.ordering} {self.plan.summary.selection} "
                  f"simulated {self.plan.summary.duration_seconds * 1e3:.1f} ms")

@@ -210,3 +210,93 @@ def test_file_pool_with_the_cuda_backend_matches_the_pinned_pool(tmp_path):
     rates = rt.calibrate_file(16 << 20, repeats=2)
     assert rates.fetch_solo_bps > 0 and rates.evict_solo_bps > 0
     rt.close()
+
+
+# ---------------------------------------------------------------------------- remote pool
+@pytest.fixture()
+def memory_daemon():
+    """A real ``ss_memory_daemon`` on a free loopback port."""
+    import subprocess
+    from shadowspill_b200 import build
+    build.build_core()
+    proc = subprocess.Popen([str(build.MEMORY_DAEMON), "--port", "0", "--capacity-gib", "0.25"],
+                            stdout=subprocess.PIPE, text=True)
+    line = proc.stdout.readline().split()
+    assert line[0] == "listening"
+    yield f"127.0.0.1:{line[1]}"
+    proc.kill()
+    proc.wait()
+
+
+def _daemon_stat(address):
+    import socket
+    host, port = address.rsplit(":", 1)
+    with socket.create_connection((host, int(port)), timeout=5) as s:
+        s.sendall(b"STAT\n")
+        reply = s.makefile().readline().split()
+    assert reply[0] == "OK"
+    return int(reply[1]), int(reply[2])
+
+
+def test_training_from_a_memory_daemon_is_bit_identical(memory_daemon):
+    cfg, plan, desc = _setup()
+    host_losses, host_state, _ = _train(copy.deepcopy(plan), desc, cfg)
+    filed = move_homes_to_file(copy.deepcopy(plan))
+    ex = Executor(filed, desc, device="cpu", seed=1,
+                  file_pool={"remote": memory_daemon, "chunk_bytes": 32 << 10, "queue_depth": 4})
+    assert _daemon_stat(memory_daemon) == (1, filed.file_bytes)
+    ex.initialize()
+    losses = [ex.run(_batches(cfg, s)).loss for s in range(4)]
+    state = ex.state_dict()
+    ex.close()
+    assert losses == host_losses
+    for k in state:
+        assert torch.equal(state[k], host_state[k]), k
+    assert _daemon_stat(memory_daemon) == (0, 0)            # closing the run freed its region
+
+
+def test_the_daemon_enforces_its_capacity_and_leases(memory_daemon):
+    with pytest.raises(native.NativeError):
+        Runtime(1 << 20, 4096, backend="mock", file_bytes=1 << 30, remote_address=memory_daemon)
+    rt = Runtime(1 << 20, 4096, backend="mock", file_bytes=64 << 20, remote_address=memory_daemon)
+    data = torch.arange(50_000, dtype=torch.int64)
+    rt.file_write(12345, data)
+    assert torch.equal(rt.file_read(12345, data.numel() * 8).view(torch.int64), data)
+    assert rt.file_info()["direct_io"] is False
+    rt.close()
+    assert _daemon_stat(memory_daemon) == (0, 0)
+    # a client that dies without FREE: the region's lease ends with its connection
+    import socket
+    import time
+    host, port = memory_daemon.rsplit(":", 1)
+    s = socket.create_connection((host, int(port)), timeout=5)
+    s.sendall(b"ALLOCATE 1048576\n")
+    assert s.makefile().readline().split()[0] == "OK"
+    assert _daemon_stat(memory_daemon) == (1, 1 << 20)
+    s.close()
+    deadline = time.time() + 5
+    while time.time() < deadline and _daemon_stat(memory_daemon)[0]:
+        time.sleep(0.05)
+    assert _daemon_stat(memory_daemon) == (0, 0)
+
+
+def test_an_unreachable_daemon_is_an_error_not_a_hang():
+    with pytest.raises(native.NativeError):
+        Runtime(1 << 20, 4096, backend="mock", file_bytes=1 << 20, remote_address="127.0.0.1:1")
+
+
+def test_session_with_a_remote_spill_pool(memory_daemon):
+    from shadowspill_b200.planning.plan import SearchOptions
+    from shadowspill_b200.training.session import TrainingSession, TrainingSetup
+    common = dict(model="llama3-tiny", device_gib=0.53, spill_gib=0.1, tokens_per_step=512,
+                  microbatch_tokens=256, dtype="float32", stochastic_rounding=False, device="cpu",
+                  profile=False, calibrate=False, seed=3, lr=3e-3,
+                  search=SearchOptions(minimum_object_bytes_evict_eligible=1024, workers=1))
+    host = TrainingSession(TrainingSetup(**common))
+    want = [host.step(_batches(host.cfg, i)).loss for i in range(3)]
+    host.close()
+    s = TrainingSession(TrainingSetup(**common, spill_pool="remote", spill_address=memory_daemon))
+    assert [s.step(_batches(s.cfg, i)).loss for i in range(3)] == want
+    s.close()
+    with pytest.raises(ValueError):
+        TrainingSession(TrainingSetup(**common, spill_pool="remote"))
