@@ -150,7 +150,8 @@ class Execution:
     runtime_trace: bool = False
     profiler_annotations: bool = False
     reject_overbudget: bool = True
-    nsys: dict | None = None                  # accepted for parity; capture is unavailable here
+    nsys: dict | None = None                  # {start_step, steps, gpu_metrics}: Nsight capture of a few
+                                              # steps where the node has nsys (orchestration/capture.py)
     collectives: str = "auto"                 # peer | dist | auto
 
 

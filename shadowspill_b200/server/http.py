@@ -11,7 +11,7 @@
     GET  /v1/runs/{session}/{run}              run info
     GET  .../progress?after=N                  preparation / startup log lines
     GET|POST .../plans , POST .../plans/report plan names, summaries, HTML plan report
-    GET  .../nsys                              Nsight capture status (unavailable on this image)
+    GET  .../nsys?rank=                        Nsight capture status and report path
     POST .../writers/{writer_id}               attach as writer (fences earlier writers)
     POST .../requests                          register an operation request (idempotent by digest)
     PUT  .../requests/{id}/input               input payload (429 = back-pressure, retry)
@@ -214,8 +214,9 @@ def make_handler(server):
                 return self._send(200, {"summary": live.plan_summary,
                                         "note": "workers write full HTML reports with write_report"})
             if rest == ["nsys"]:
-                return self._send(200, {"available": False,
-                                        "reason": "Nsight Systems is not installed on this image"})
+                from ..orchestration import capture
+                wanted = capture.NsysOptions.from_json((live.body.get("execution") or {}).get("nsys"))
+                return self._send(200, capture.status(live.dir / "logs", int(q.get("rank", 0)), wanted))
             if len(rest) == 2 and rest[0] == "writers" and method == "POST":
                 self._require_ready(live)
                 live.controller.attach_writer(rest[1])

@@ -234,7 +234,7 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
             "calibrate": bool(prep.get("calibrate", True)) and not body.get("simulation_only"),
             "search": search, "collectives": ex.get("collectives", "auto"),
             "operations": list(body.get("operations", ("step",))),
-            "trace_capacity": 65536 if ex.get("runtime_trace") else 0,
+            "trace_capacity": 65536 if ex.get("runtime_trace") else 0, "nsys": ex.get("nsys"),
             "spill_pool": mem.get("spill_pool", "host"), "spill_directory": mem.get("spill_directory", ""),
             "spill_address": mem.get("spill_address", ""),
             "spill_chunk_bytes": int(mem.get("spill_chunk_bytes", 2 << 20)),

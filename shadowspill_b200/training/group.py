@@ -48,10 +48,17 @@ class WorkerGroup:
             from_child_r, from_child_w = os.pipe()
             env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
             log = open(self.log_dir / f"worker{rank}.log", "ab")
-            proc = subprocess.Popen(
-                [sys.executable, "-m", "shadowspill_b200.training.worker", "--control-fd",
-                 f"{to_child_r},{from_child_w}"], pass_fds=(to_child_r, from_child_w), env=env,
-                stdout=log, stderr=subprocess.STDOUT, cwd=root)
+            command = [sys.executable, "-m", "shadowspill_b200.training.worker", "--control-fd",
+                       f"{to_child_r},{from_child_w}"]
+            from ..orchestration import capture
+            nsys = capture.NsysOptions.from_json(setup.get("nsys"))
+            if nsys is not None and capture.available(nsys):
+                command = capture.wrap_command(command, rank, self.log_dir, nsys)
+            elif nsys is not None:
+                self.on_progress(f"[rank={rank}] nsys capture requested but {nsys.executable} is not "
+                                 f"installed; running unprofiled")
+            proc = subprocess.Popen(command, pass_fds=(to_child_r, from_child_w), env=env,
+                                    stdout=log, stderr=subprocess.STDOUT, cwd=root)
             os.close(to_child_r); os.close(from_child_w)
             chan = Channel(from_child_r, to_child_w)
             chan.send({"type": "launch", "rank": rank, "world_size": self.world, "setup": setup,

@@ -44,6 +44,7 @@ def serve(chan: Channel) -> int:
     rank, world = int(header["rank"]), int(header["world_size"])
     log = lambda msg: chan.send({"type": "progress", "rank": rank, "message": msg})
     session = None
+    window = None
     try:
         import torch
         setup_json = header["setup"]
@@ -59,6 +60,11 @@ def serve(chan: Channel) -> int:
         from ..planning.plan import SearchOptions
         from .session import TrainingSession, TrainingSetup
         kw = dict(setup_json)
+        from ..orchestration import capture
+        nsys = capture.NsysOptions.from_json(kw.pop("nsys", None))
+        if nsys is not None and capture.available(nsys):
+            barrier = (lambda: dist.barrier()) if world > 1 else None
+            window = capture.StepWindow(nsys, barrier=barrier)
         if isinstance(kw.get("model"), dict):
             kw["model"] = DecoderConfig.from_json(kw["model"])
         kw["search"] = SearchOptions(**kw.get("search", {}))
@@ -120,7 +126,11 @@ def serve(chan: Channel) -> int:
                     if op == "optim_step":
                         session.executor.hyper.grad_scale = float(args.get("grad_scale", 1.0))
                     started = True
+                    if window is not None and op != "optim_step":
+                        window.before_step()
                     res = session.run(op, batch, trace=bool(args.get("runtime_trace")))
+                    if window is not None and op != "optim_step":
+                        window.after_step()
                     out["loss"] = res.loss if op != "optim_step" else None
                     out["metrics"] = {"tokens": res.tokens, "device_seconds": res.device_seconds}
                 elif op == "discard":

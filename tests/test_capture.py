@@ -1,0 +1,82 @@
+"""Nsight capture plumbing, with a stand-in ``nsys`` executable (none is installed here)."""
+import os
+import stat
+import sys
+
+import numpy as np
+import pytest
+
+from shadowspill_b200.orchestration import capture
+
+
+def _fake_nsys(directory):
+    """A script that behaves like ``nsys profile <options> <command>``: writes the report file
+    named by --output and runs the command."""
+    path = directory / "nsys"
+    path.write_text("#!/bin/sh\nshift\nout=\nwhile [ $# -gt 0 ]; do case \"$1\" in\n"
+                    "  --output=*) out=\"${1#--output=}\"; shift;;\n  --*) shift;;\n  *) break;;\nesac; done\n"
+                    "echo report > \"$out.nsys-rep\"\nexec \"$@\"\n")
+    path.chmod(path.stat().st_mode | stat.S_IEXEC)
+    return path
+
+
+def test_step_window_opens_and_closes_once_with_barriers():
+    calls = []
+    w = capture.StepWindow(capture.NsysOptions(start_step=3, steps=2), start=lambda: calls.append("start"),
+                           stop=lambda: calls.append("stop"), barrier=lambda: calls.append("barrier"))
+    for step in range(1, 8):
+        w.before_step()
+        calls.append(f"step{step}")
+        w.after_step()
+    assert calls == ["step1", "step2", "barrier", "start", "step3", "step4", "barrier", "stop",
+                     "step5", "step6", "step7"]
+    assert w.state == "done"
+    with pytest.raises(ValueError):
+        capture.NsysOptions.from_json({"start_step": 0})
+
+
+def test_wrap_command_and_status(tmp_path, monkeypatch):
+    opts = capture.NsysOptions(start_step=2, steps=1, gpu_metrics=True)
+    monkeypatch.setenv("PATH", str(tmp_path / "empty"))
+    assert capture.available(opts) is None
+    assert capture.status(tmp_path, 0, opts) == {"requested": True, "available": False,
+                                                 "reason": "nsys is not installed on this node"}
+    with pytest.raises(FileNotFoundError):
+        capture.wrap_command(["python", "x.py"], 0, tmp_path, opts)
+    fake = _fake_nsys(tmp_path)
+    monkeypatch.setenv("PATH", f"{tmp_path}{os.pathsep}/usr/bin{os.pathsep}/bin")
+    cmd = capture.wrap_command(["python", "x.py"], 1, tmp_path, opts)
+    assert cmd[0] == str(fake) and cmd[1] == "profile" and cmd[-2:] == ["python", "x.py"]
+    assert "--capture-range=cudaProfilerApi" in cmd and "--gpu-metrics-devices=cuda-visible" in cmd
+    assert f"--output={tmp_path / 'worker1'}" in cmd
+    assert capture.status(tmp_path, 1, opts)["complete"] is False
+    assert capture.status(tmp_path, 1, None) == {"requested": False, "available": True}
+
+
+def test_workers_run_under_the_wrapper_and_the_service_reports_it(tmp_path, monkeypatch):
+    from shadowspill_b200.client import (BatchConfig, Memory, Model, Optimizer, Preparation,
+                                         ProfilingOptions, Resources, ServiceClient, text_batch)
+    from shadowspill_b200.client.config import Execution, PlanningOptions
+    from shadowspill_b200.server.service import Server
+    bin_dir = tmp_path / "bin"
+    bin_dir.mkdir()
+    _fake_nsys(bin_dir)
+    monkeypatch.setenv("PATH", f"{bin_dir}{os.pathsep}{os.path.dirname(sys.executable)}{os.pathsep}/usr/bin{os.pathsep}/bin")
+    rng = np.random.default_rng(0)
+    seqs = [rng.integers(0, 512, size=40) for _ in range(8)]
+    with Server(tmp_path / "svc", token="t") as srv, ServiceClient(srv.url, token="t") as svc:
+        trainer = svc.create_training_client(
+            Model("llama3-tiny", dtype="float32"), Optimizer(lr=3e-3, parameter_rounding="nearest"),
+            batch=BatchConfig(tokens_per_step=512, microbatch_tokens=256),
+            memory=Memory(device_gib=0.53, spill_gib=0.25), resources=Resources(gpus=1, backend="cpu"),
+            execution=Execution(nsys={"start_step": 1, "steps": 1}),
+            preparation=Preparation(profiling=ProfilingOptions(enabled=False), calibrate=False,
+                                    planning=PlanningOptions(minimum_object_bytes_evict_eligible=1024, workers=1)),
+            timeout=300).result()
+        assert trainer.step(text_batch(seqs)).result().loss > 0
+        info = svc.get_nsys(trainer.run).result() if hasattr(trainer, "run") else None
+        trainer.close()
+    reports = list((tmp_path / "svc").rglob("worker0.nsys-rep"))
+    assert len(reports) == 1
+    if info is not None:
+        assert info["requested"] and info["available"] and info["report"].endswith("worker0.nsys-rep")
