@@ -38,9 +38,14 @@ def device_inventory() -> dict[str, Any]:
         host_total, host_free = info["MemTotal"] / (1 << 20), info.get("MemAvailable", 0) / (1 << 20)
     except OSError:
         pass
-    return {"gpus": gpus, "gpu_names": names, "device_gib": device_gib, "host_total_gib": host_total,
-            "host_free_gib": host_free, "cpus": os.cpu_count() or 1,
-            "slurm_job": os.environ.get("SLURM_JOB_ID")}
+    inventory = {"gpus": gpus, "gpu_names": names, "device_gib": device_gib, "host_total_gib": host_total,
+                 "host_free_gib": host_free, "cpus": os.cpu_count() or 1, "slurm_job": None}
+    from . import slurm
+    try:
+        job = slurm.detect()
+    except ValueError:
+        job = None                       # a malformed Slurm environment offers the plain inventory
+    return slurm.clamp_inventory(inventory, job, os.environ.get("SLURMD_NODENAME"))
 
 
 class AdmissionError(RuntimeError):
