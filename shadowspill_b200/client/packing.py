@@ -92,9 +92,13 @@ def _bins(lengths: list[int], capacity: int, n_bins: int, policy: str) -> list[l
 
 
 def pack_batch(datums: list[Datum], *, microbatch_tokens: int, microbatches: int, slots: int,
-               policy: str = "best_fit") -> list[PackedMicrobatch]:
+               policy: str = "best_fit", placement: list | None = None) -> list[PackedMicrobatch]:
+    """``placement`` (a list, filled in place): for every datum ``(microbatch, first row, rows)``,
+    which is what maps per-row outputs of a forward call back to the datums."""
     bins = _bins([len(d) for d in datums], microbatch_tokens, microbatches, policy)
     out = []
+    if placement is not None:
+        placement[:] = [None] * len(datums)
     T = microbatch_tokens
     for members in bins:
         if len(members) + 1 > slots:
@@ -117,6 +121,8 @@ def pack_batch(datums: list[Datum], *, microbatch_tokens: int, microbatches: int
                     raise BatchError(f"datum {i} lacks the objective input {k!r}")
                 extras[k][pos:pos + n] = d.extras[k]
             positions[pos:pos + n] = np.arange(n, dtype=np.int32)
+            if placement is not None:
+                placement[i] = (len(out), pos, n)
             pos += n
             cu.append(pos)
         if pos < T:

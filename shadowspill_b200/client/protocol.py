@@ -100,6 +100,18 @@ def decode_arrays(blob: bytes) -> tuple[dict[str, Any], dict[str, np.ndarray]]:
     return header, arrays
 
 
+def encode_array(a: np.ndarray) -> dict[str, Any]:
+    """A small array inside a JSON reply (per-row outputs of a forward call)."""
+    import base64
+    a = np.ascontiguousarray(a)
+    return {"dtype": a.dtype.str, "shape": list(a.shape), "b64": base64.b64encode(a.tobytes()).decode()}
+
+
+def decode_array(d: dict[str, Any]) -> np.ndarray:
+    import base64
+    return np.frombuffer(base64.b64decode(d["b64"]), dtype=np.dtype(d["dtype"])).reshape(d["shape"]).copy()
+
+
 def encode_microbatches(mbs) -> bytes:
     arrays = {}
     for i, mb in enumerate(mbs):

@@ -16,7 +16,7 @@ from dataclasses import dataclass, field
 from typing import Any
 
 from .packing import BatchError, BatchValidator, pack_batch
-from .protocol import OperationRequest, OperationResult, encode_microbatches
+from .protocol import OperationRequest, OperationResult, decode_array, encode_microbatches
 from .text import Datum
 from .transport import HTTPTransport, TransportError
 
@@ -64,11 +64,11 @@ class TrainingClient:
     def validate_batch(self, datums: list[Datum]) -> None:
         self.validator.validate(datums)
 
-    def _pack(self, datums: list[Datum]) -> bytes:
+    def _pack(self, datums: list[Datum], placement: list | None = None) -> bytes:
         self.validate_batch(datums)
         mbs = pack_batch(datums, microbatch_tokens=self.microbatch_tokens,
                          microbatches=self.microbatches * self.workers, slots=self.slots,
-                         policy=self.packing)
+                         policy=self.packing, placement=placement)
         return encode_microbatches(mbs)
 
     # ------------------------------------------------------------------ submission
@@ -135,7 +135,27 @@ class TrainingClient:
         return self._submit("optim_step", None, grad_scale=grad_scale, lr=lr)
 
     def forward(self, datums: list[Datum], mode: str = "evaluation") -> cf.Future:
-        return self._submit("forward", self._pack(datums), mode=mode)
+        """Evaluates the batch without touching state. The result's ``loss`` is the objective;
+        ``outputs["per_datum"]`` holds one float32 array per datum, row for row: for language
+        models ``[n, 1]`` with the log-probability of each position's target (0 where there is
+        none), for the regression family the ``[1, outputs]`` prediction."""
+        placement: list = []
+        inner = self._submit("forward", self._pack(datums, placement), mode=mode)
+
+        outer: cf.Future = cf.Future()
+
+        def unpack(done: cf.Future) -> None:      # runs on the thread that completed `inner`
+            try:
+                res = done.result()
+                per_mb = [decode_array(a) for a in res.outputs.get("per_microbatch", [])]
+                if per_mb:
+                    res.outputs = {k: v for k, v in res.outputs.items() if k != "per_microbatch"}
+                    res.outputs["per_datum"] = [per_mb[m][lo:lo + n] for m, lo, n in placement]
+                outer.set_result(res)
+            except BaseException as exc:  # noqa: BLE001
+                outer.set_exception(exc)
+        inner.add_done_callback(unpack)
+        return outer
 
     def discard_gradients(self) -> cf.Future:
         return self._submit("discard", None)

@@ -55,6 +55,9 @@ class InvocationResult:
     transfer_begin_ns: list[int] = field(default_factory=list)      # device clock, per action
     transfer_end_ns: list[int] = field(default_factory=list)
     metrics: dict[str, float] = field(default_factory=dict)
+    # forward-only programs: one float32 [T, width] array per microbatch (log p(target) per
+    # position for language models, the prediction rows of a regression head)
+    outputs: list = field(default_factory=list)
 
 
 class TaskRunner:
@@ -123,6 +126,9 @@ class TaskRunner:
                 out["batch_flat"] = flat
             elif u.role == "loss":
                 out[u.role] = flat[:4].view(torch.float32)
+            elif u.role == "outputs":
+                w = st.output_width
+                out[u.role] = flat[:self.T * w * 4].view(torch.float32).view(self.T, w)
             elif u.role == "saved":
                 lay, _ = saved_layout(st, self.T, t.variant, self.desc.dtype)
                 sv = {}
@@ -162,6 +168,8 @@ class TaskRunner:
                 tied = {"params": B["tied_params"], "grads": B.get("tied_grads"), "first": tied_first}
             st.loss_and_backward(B["params"], B.get("grads"), B["x"], meta, B["loss"], first,
                                  dx=B.get("dx"), train=train, grad_scale=1.0, tied=tied)
+            if "outputs" in B:
+                B["outputs"].copy_(st.outputs(B["params"], B["x"], meta, tied))
         elif t.kind == "backward":
             first = self._first(t.stage, B)
             saved = dict(B["saved"]) if "saved" in B else {}
@@ -630,9 +638,18 @@ class Executor:
         tr = self.rt.trace_end() if trace else []
         tb, te = (self.rt.transfer_times(self.plan_id, len(self.plan.schedule.actions))
                   if trace else ([], []))
+        outputs, d2h = [], 4
+        for m in range(self.n_mb):
+            o = self._obj.get(f"outputs.{m}")
+            if o is None:
+                break
+            w = self.stages[-1].output_width
+            outputs.append(self.spill_view(o, False)[:self.T * w * 4].view(torch.float32)
+                           .view(self.T, w).numpy().copy())
+            d2h += outputs[-1].nbytes
         return InvocationResult(loss, self.T * self.n_mb, time.perf_counter() - t0, device_seconds,
-                                h2d, 4, task_seconds if time_tasks else [], task_starts, tr, tb, te,
-                                metrics)
+                                h2d, d2h, task_seconds if time_tasks else [], task_starts, tr, tb, te,
+                                metrics, outputs)
 
     def discard_gradients(self) -> None:
         self.runner.accumulated = 0

@@ -211,6 +211,12 @@ def _build(desc: TrainingDescription) -> Program:
     IN = [prog.add_object(ObjectSpec(f"batch.{m}", in_bytes, "input", True, pinned_resident=True,
                                      microbatch=m)) for m in range(n_mb)]
     LOSS = prog.add_object(ObjectSpec("loss", 512, "output", True, pinned_resident=True))
+    # a forward-only program also returns what the head computes per row (the log-probability
+    # of each target token; the prediction vector of a regression head)
+    ow = getattr(stages[-1], "output_width", 0)
+    OUT = ([prog.add_object(ObjectSpec(f"outputs.{m}", -(-T * ow * 4 // ALIGN) * ALIGN, "output", True,
+                                       pinned_resident=True, microbatch=m)) for m in range(n_mb)]
+           if (not train and ow) else [])
     act_bytes = T * cfg.d_model * isz
     A = [[prog.add_object(ObjectSpec(f"{stages[si].name}.out.{m}", act_bytes, "activation",
                                      stage=si, microbatch=m)) for m in range(n_mb)]
@@ -285,6 +291,8 @@ def _build(desc: TrainingDescription) -> Program:
                     uses.append(UseSpec(G[0], "create", "tied_grads")); grad_created[0] = True
                 else:
                     uses.append(UseSpec(G[0], "mutate", "tied_grads"))
+        if OUT:
+            uses.append(UseSpec(OUT[m], "mutate", "outputs"))
         if train:
             uses.append(UseSpec(DX[m], "create", "dx"))
             if not st.has_trainable:

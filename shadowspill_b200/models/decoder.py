@@ -515,6 +515,12 @@ class HeadLossStage(Stage):
         return F.rmsnorm_bwd(x, P["final_norm"], dh, rstd, dw, c.zero_centered_norm,
                              dx=dx, accumulate=False)
 
+    output_width = 1          # per-row outputs of a forward-only program: log p(target)
+
+    def outputs(self, P, x, meta: BatchMeta, tied: dict | None = None) -> torch.Tensor:
+        logp = self.target_logprobs(P, x, meta, tied)
+        return logp.masked_fill_(meta.targets < 0, 0.0).reshape(-1, 1)   # no target: reported as 0
+
     def target_logprobs(self, P, x, meta: BatchMeta, tied: dict | None = None) -> torch.Tensor:
         """log p(target) for every token (fp32 [T]), in the same row blocks."""
         c = self.cfg

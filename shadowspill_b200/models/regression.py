@@ -84,8 +84,15 @@ class RegressionHeadStage(Stage):
         self.params = [ParamSpec("w2", (cfg.vocab_size, cfg.d_model), std=std),
                        ParamSpec("b2", (cfg.vocab_size,), init="zeros")]
 
+    @property
+    def output_width(self) -> int:
+        return self.cfg.vocab_size        # a forward-only program returns every row's prediction
+
     def predict(self, P, x) -> torch.Tensor:
         return torch.addmm(P["b2"], x.to(P["w2"].dtype), P["w2"].t())
+
+    def outputs(self, P, x, meta: BatchMeta, tied=None) -> torch.Tensor:
+        return self.predict(P, x)
 
     def loss_and_backward(self, P, G, x, meta: BatchMeta, loss_sum: torch.Tensor, first: bool,
                           dx=None, train: bool = True, grad_scale: float = 1.0, tied=None):

@@ -133,6 +133,11 @@ class LiveRun:
         out["metrics"] = {"wall_seconds": time.perf_counter() - t0,
                           **{k: v for k, v in (replies[0].get("metrics") or {}).items()}}
         out["outputs"] = replies[0].get("outputs", {})
+        if op == "forward":
+            # microbatches were routed to the workers in order: their outputs concatenate the same way
+            per = [a for r in replies for a in (r.get("outputs") or {}).get("per_microbatch", [])]
+            if per:
+                out["outputs"] = {"per_microbatch": per}
         if op in ("save", "export"):
             out["outputs"] = {"checkpoint": args.get("name"), "directory": args["directory"]}
         if op in ("step", "optim_step") and out.get("loss") is not None:

@@ -132,6 +132,9 @@ def serve(chan: Channel) -> int:
                     if window is not None and op != "optim_step":
                         window.after_step()
                     out["loss"] = res.loss if op != "optim_step" else None
+                    if op == "forward" and res.outputs:
+                        from ..client.protocol import encode_array
+                        out["outputs"] = {"per_microbatch": [encode_array(a) for a in res.outputs]}
                     out["metrics"] = {"tokens": res.tokens, "device_seconds": res.device_seconds}
                 elif op == "discard":
                     session.executor.discard_gradients()

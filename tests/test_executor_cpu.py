@@ -119,10 +119,16 @@ def test_operations_share_state_across_plans():
         ref.optim_step()
         assert ex.completed_updates == round_ + 1 and ex.accumulated == 0
     host = _batches(cfg, 99)
-    assert abs(ex.run(host, operation="forward").loss -
-               ref.evaluate([to_device(m, "cpu") for m in host])) < 1e-5
+    fwd = ex.run(host, operation="forward")
+    assert abs(fwd.loss - ref.evaluate([to_device(m, "cpu") for m in host])) < 1e-5
+    # a forward-only program also returns log p(target) of every position, per microbatch
+    assert len(fwd.outputs) == len(host) and fwd.outputs[0].shape == (256, 1)
+    rebuilt = sum(float(-(o[:, 0] * m.weights)[m.targets >= 0].sum()) for o, m in zip(fwd.outputs, host))
+    assert abs(rebuilt - fwd.loss) < 1e-4
+    assert all((o[:, 0][m.targets < 0] == 0).all() and (o <= 0).all() for o, m in zip(fwd.outputs, host))
     want = ref.step([to_device(m, "cpu") for m in host])
-    assert abs(ex.run(host, operation="step").loss - want) < 1e-5 * abs(want)
+    stepped = ex.run(host, operation="step")
+    assert abs(stepped.loss - want) < 1e-5 * abs(want) and stepped.outputs == []
     got = ex.state_dict()
     for k, v in ref.state_dict().items():
         # microbatches accumulate in another order (reverse walk), hence a few fp32 ulps

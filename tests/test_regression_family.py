@@ -97,9 +97,14 @@ def test_regression_through_the_service(tmp_path):
             memory=Memory(device_gib=0.53, spill_gib=0.05), resources=Resources(gpus=1, backend="cpu"),
             preparation=Preparation(profiling=ProfilingOptions(enabled=False), calibrate=False,
                                     planning=PlanningOptions(minimum_object_bytes_evict_eligible=64, workers=1)),
-            timeout=300).result()
+            operations=("step", "forward"), timeout=300).result()
         losses = [trainer.step(batch(0)).result().loss for _ in range(12)]
         assert losses[-1] < 0.8 * losses[0]
+        pred = trainer.forward(batch(0)).result().outputs["per_datum"]
+        assert len(pred) == ROWS * MBS and pred[0].shape == (1, 8)
+        targets = _rows(0)[1]
+        err = float(np.mean([(p[0] - t) ** 2 for p, t in zip(pred, targets)]))
+        assert abs(err - trainer.forward(batch(0)).result().loss) < 1e-5       # weights make the sum a mean
         with pytest.raises(BatchError):          # a row without its regression target
             trainer.step([tensor_datum({"value": np.zeros(16)})])
         with pytest.raises(BatchError):          # a row of the wrong width

@@ -53,6 +53,13 @@ def test_train_checkpoint_resume_through_the_public_api(service):
         assert trainer.info["plan_summary"]["fetch_bytes"] > 0
         losses = [trainer.step(text_batch(_sequences(0))).result().loss for _ in range(4)]
         assert losses[-1] < losses[0]
+        # forward: the loss and, per datum, log p(target) of every position
+        probe = text_batch(_sequences(7))
+        fwd = trainer.forward(probe).result()
+        per = fwd.outputs["per_datum"]
+        assert len(per) == len(probe) and all(p.shape == (len(d), 1) for p, d in zip(per, probe))
+        rebuilt = sum(float(-(p[:, 0] * d.weights)[d.targets >= 0].sum()) for p, d in zip(per, probe))
+        assert abs(rebuilt - fwd.loss) < 1e-4
         # accumulation: two contributions then one update
         f1 = trainer.forward_backward(text_batch(_sequences(1)))
         f2 = trainer.forward_backward(text_batch(_sequences(2)))
