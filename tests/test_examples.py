@@ -31,3 +31,12 @@ def test_regression_example():
 def test_regression_example_on_two_ranks():
     losses = _load("regression_training").main(["--steps", "6", "--ranks", "2"])
     assert len(losses) == 6 and losses[-1] < losses[0]
+
+
+def test_policy_example():
+    history = _load("policy_training").main(["--iterations", "2"])
+    assert len(history) == 4
+    # with old log-probabilities taken from the current weights the first surrogate of every
+    # iteration is -mean(advantage) over response tokens = 0 up to rounding; steps lower it
+    assert abs(history[0]) < 1e-4 and abs(history[2]) < 1e-4
+    assert history[1] < history[0] and history[3] < history[2]
