@@ -100,6 +100,23 @@ class ServiceClient:
         return self.pool.submit(lambda: self.transport.request(
             "GET", f"/v1/runs/{self.session}/{run}/progress", query={"after": after})[1])
 
+    def list_components(self, kind: str | None = None) -> cf.Future:
+        return self.pool.submit(lambda: self.transport.request(
+            "GET", "/v1/components", query={"kind": kind} if kind else None)[1]["components"])
+
+    def upload_artifact(self, path, **kw) -> cf.Future:
+        """Resumable upload of a file (weights, a prepared bundle); returns an ``ArtifactHandle``."""
+        from .handles import upload_artifact
+        return self.pool.submit(lambda: upload_artifact(self.transport, path, **kw))
+
+    def download_artifact(self, artifact, path, **kw) -> cf.Future:
+        from .handles import download_artifact
+        return self.pool.submit(lambda: download_artifact(self.transport, artifact, path, **kw))
+
+    def delete_artifact(self, artifact) -> cf.Future:
+        aid = getattr(artifact, "artifact", artifact)
+        return self.pool.submit(lambda: self.transport.request("DELETE", f"/v1/artifacts/{aid}")[1])
+
     def get_nsys(self, run: str, rank: int = 0) -> cf.Future:
         return self.pool.submit(lambda: self.transport.request(
             "GET", f"/v1/runs/{self.session}/{run}/nsys", query={"rank": rank})[1])

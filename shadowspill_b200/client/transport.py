@@ -31,8 +31,9 @@ class HTTPTransport:
         return cls(self.host, self.port, timeout=self.timeout)
 
     def request(self, method: str, path: str, body: bytes | dict | None = None,
-                query: dict[str, Any] | None = None, raw: bool = False):
-        headers = {}
+                query: dict[str, Any] | None = None, raw: bool = False,
+                headers: dict[str, str] | None = None):
+        headers = dict(headers or {})
         if self.token:
             headers["Authorization"] = f"Bearer {self.token}"
         if isinstance(body, dict):

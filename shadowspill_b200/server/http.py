@@ -3,6 +3,7 @@
     GET  /v1/info                              service identity
     GET  /v1/hardware                          node inventory + admission state
     POST /v1/training/describe                 resolve settings, preview workers (no reservation)
+    GET  /v1/components?kind=                  registered model / objective / optimizer / policy components
     POST /v1/artifacts                         begin a resumable upload
     PUT  /v1/artifacts/{id}/chunks/{offset}    upload a chunk
     POST /v1/artifacts/{id}/complete           seal (sha256 checked)
@@ -121,6 +122,8 @@ def make_handler(server):
                                         "members": server.membership.live()})
             if head == "training" and p[1:] == ["describe"] and method == "POST":
                 return self._send(200, server.describe(self._json()))
+            if head == "components" and method == "GET":
+                return self._send(200, {"components": server.registry.list(q.get("kind"))})
             if head == "artifacts":
                 return self._artifacts(method, p[1:], q)
             if head == "nodes" and method == "POST":
@@ -174,13 +177,23 @@ def make_handler(server):
                 meta["complete"] = True
                 return self._send(200, {"artifact": aid, "sha256": digest})
             if method == "GET":
-                data = (store / aid).read_bytes()
+                target = store / aid
+                size = target.stat().st_size
                 rng = self.headers.get("Range")
                 if rng:
                     m = re.match(r"bytes=(\d+)-(\d*)", rng)
-                    lo = int(m.group(1)); hi = int(m.group(2)) if m.group(2) else len(data) - 1
-                    return self._send(206, data[lo:hi + 1], "application/octet-stream",
-                                      {"Content-Range": f"bytes {lo}-{hi}/{len(data)}"})
+                    if not m:
+                        raise HTTPError(400, "bad Range header")
+                    lo = int(m.group(1))
+                    hi = min(int(m.group(2)) if m.group(2) else size - 1, size - 1)
+                    if lo >= size:
+                        return self._send(416, {"error": "range starts past the end", "size": size})
+                    with open(target, "rb") as f:      # only the requested window is read
+                        f.seek(lo)
+                        data = f.read(hi - lo + 1)
+                    return self._send(206, data, "application/octet-stream",
+                                      {"Content-Range": f"bytes {lo}-{hi}/{size}"})
+                data = target.read_bytes()
                 return self._send(200, data, "application/octet-stream",
                                   {"ETag": hashlib.sha256(data).hexdigest()})
             if method == "DELETE":

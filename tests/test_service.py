@@ -180,3 +180,38 @@ def test_two_replicas_of_two_ranks_through_the_service(service):
         losses = [trainer.step(b).result().loss for b in batches]
         assert losses[-1] < losses[0]
         trainer.close()
+
+
+def test_resumable_artifact_transfer_and_component_listing(service, tmp_path):
+    import hashlib
+    from shadowspill_b200.client.handles import upload_artifact
+    src = tmp_path / "weights.bin"
+    payload = np.random.default_rng(0).integers(0, 256, size=300_000, dtype=np.uint8).tobytes()
+    src.write_bytes(payload)
+    with ServiceClient(service.url, token="secret") as svc:
+        ids = {c["id"] for c in svc.list_components("model").result()}
+        assert {"llama3-8b@1", "shadowspill/regression@1"} <= ids
+        assert all(c["kind"] == "objective" for c in svc.list_components("objective").result())
+        # an upload that stopped after the first chunk resumes where the service stands
+        _, begun = svc.transport.request("POST", "/v1/artifacts", {
+            "name": "weights.bin", "size": len(payload), "sha256": hashlib.sha256(payload).hexdigest()})
+        svc.transport.request("PUT", f"/v1/artifacts/{begun['artifact']}/chunks/0", payload[:65536])
+        seen = []
+        handle = upload_artifact(svc.transport, src, chunk_bytes=100_000,
+                                 on_progress=lambda done, total: seen.append(done))
+        assert handle.artifact == begun["artifact"] and seen[0] == 165_536 and seen[-1] == len(payload)
+        # a download that already has a part file only fetches the rest
+        dst = tmp_path / "copy.bin"
+        (tmp_path / "copy.bin.part").write_bytes(payload[:120_000])
+        got = []
+        svc.download_artifact(handle, dst, chunk_bytes=64_000,
+                              on_progress=lambda have, total: got.append(have)).result()
+        assert dst.read_bytes() == payload and got[0] == 184_000
+        # a corrupted part file is caught by the digest
+        (tmp_path / "bad.bin.part").write_bytes(b"x" * 1000)
+        with pytest.raises(IOError):
+            svc.download_artifact(handle, tmp_path / "bad.bin").result()
+        svc.delete_artifact(handle).result()
+        from shadowspill_b200.client.transport import TransportError
+        with pytest.raises(TransportError):
+            svc.download_artifact(handle.artifact, tmp_path / "gone.bin").result()
