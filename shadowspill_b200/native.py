@@ -21,6 +21,7 @@ i32, i64, f64, vp = C.c_int32, C.c_int64, C.c_double, C.c_void_p
 P64, P32 = C.POINTER(i64), C.POINTER(i32)
 
 OK, INVALID, OOM, NO_PROGRESS, BACKEND_FAILURE, CLOSED, FAILED, TIMEOUT, INFEASIBLE = range(9)
+INTERNAL, IO_ERROR = 9, 10
 USE_READ, USE_CREATE, USE_MUTATE = 0, 1, 2
 OBJ_PERSISTENT, OBJ_PINNED_RESIDENT = 1, 2
 ACT_FETCH, ACT_EVICT, ACT_RELEASE = 0, 1, 2

@@ -300,3 +300,31 @@ def test_session_with_a_remote_spill_pool(memory_daemon):
     s.close()
     with pytest.raises(ValueError):
         TrainingSession(TrainingSetup(**common, spill_pool="remote"))
+
+
+def test_a_daemon_that_dies_between_steps_latches_an_io_failure():
+    """The far side of the remote pool goes away: the next step ends with the runtime's failure
+    latch set (pool 2, an I/O status), never with a hang, and the run refuses further steps."""
+    import subprocess
+    import time
+    from shadowspill_b200 import build
+    build.build_core()
+    proc = subprocess.Popen([str(build.MEMORY_DAEMON), "--port", "0"], stdout=subprocess.PIPE, text=True)
+    address = f"127.0.0.1:{proc.stdout.readline().split()[1]}"
+    cfg, plan, desc = _setup()
+    ex = Executor(move_homes_to_file(plan), desc, device="cpu", seed=1,
+                  file_pool={"remote": address, "chunk_bytes": 32 << 10, "queue_depth": 2})
+    ex.initialize()
+    assert ex.run(_batches(cfg)).loss > 0
+    proc.kill()
+    proc.wait()
+    t0 = time.time()
+    with pytest.raises((RuntimeFailure, native.NativeError)) as e:
+        ex.run(_batches(cfg, 1))
+    assert time.time() - t0 < 20
+    info = ex.rt.failure()
+    assert info is not None and info["pool"] == 2 and info["status"] == native.IO_ERROR
+    with pytest.raises((RuntimeFailure, native.NativeError)):
+        ex.run(_batches(cfg, 2))
+    ex.closed = True
+    ex.rt.close()
