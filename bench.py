@@ -118,6 +118,10 @@ def main() -> None:
     ap.add_argument("--expert-parallel", action="store_true",
                     help="multi-GPU runs of routed models: split the experts over the ranks")
     ap.add_argument("--report", default="", help="directory for the plan report")
+    ap.add_argument("--spill-pool", default="host", choices=["host", "file", "remote"],
+                    help="where spilled state lives: pinned memory, a direct-I/O file, or a memory daemon")
+    ap.add_argument("--spill-dir", default="/tmp", help="directory of the file spill pool")
+    ap.add_argument("--spill-address", default="", help="host:port of the memory daemon")
     ap.add_argument("--collectives", default="auto", choices=["auto", "peer", "dist"],
                     help="peer = own kernels over NVLink peer memory; dist = NCCL baseline arm")
     args = ap.parse_args()
@@ -150,7 +154,9 @@ def main() -> None:
                           lora=({"rank": args.lora_rank, "alpha": 2.0 * args.lora_rank,
                                  "targets": ["wq", "wk", "wv", "wo", "w13", "w2"], "routed_experts": True,
                                  "train_base": False} if args.lora_rank else None),
-                          expert_parallel=args.expert_parallel)
+                          expert_parallel=args.expert_parallel, spill_pool=args.spill_pool,
+                          spill_directory=args.spill_dir if args.spill_pool == "file" else "",
+                          spill_address=args.spill_address)
     log = (lambda m: print(f"[bench] {m}", file=sys.stderr, flush=True)) if rank == 0 else None
     session = TrainingSession(setup, log=log)  # build -> profile -> calibrate -> plan -> executor
     if rank == 0:
@@ -218,7 +224,8 @@ def main() -> None:
                        "seq_len": 8192, "tokens_per_worker_step": args.tokens,
                        "microbatch_tokens": args.microbatch,
                        "parallelism": f"dp{world}" if world > 1 else "single",
-                       "memory": {"device_gib": args.device_gib, "spill_gib": args.spill_gib},
+                       "memory": {"device_gib": args.device_gib, "spill_gib": args.spill_gib,
+                                  "spill_pool": args.spill_pool},
                        "optimizer": "adamw bf16 state, stochastic rounding",
                        "l2": "inputs per step (16+ GB of weights streamed from host) exceed L2",
                        "plan": {"ordering": plan.ordering, "selection": plan.selection,
