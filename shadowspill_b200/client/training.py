@@ -169,6 +169,29 @@ class TrainingClient:
     def export_weights(self, name: str) -> cf.Future:
         return self._submit("export", None, name=name)
 
+    def list_checkpoints(self) -> list[str]:
+        return self.transport.request("GET", f"{self.route}/checkpoints")[1]["checkpoints"]
+
+    def download_checkpoint(self, name: str, directory, **kw) -> cf.Future:
+        """Fetches a checkpoint saved by ``save_checkpoint`` (or ``export_weights``) from the
+        service and unpacks it under ``directory``; the future gives the unpacked path. The
+        transfer resumes if ``<name>.tar.part`` from an earlier attempt is still there."""
+        from pathlib import Path
+        from .handles import ArtifactHandle, download_artifact
+
+        def work():
+            import tarfile
+            _, h = self.transport.request("POST", f"{self.route}/checkpoints/{name}/artifact", {})
+            handle = ArtifactHandle(h["artifact"], int(h["size"]), h["sha256"])
+            root = Path(directory)
+            root.mkdir(parents=True, exist_ok=True)
+            archive = download_artifact(self.transport, handle, root / f"{name}.tar", **kw)
+            with tarfile.open(archive) as tar:
+                tar.extractall(root, filter="data")
+            archive.unlink()
+            return root / name
+        return self.pool.submit(work)
+
     # ------------------------------------------------------------------ observations
     def log_metrics(self, step: int, **values: float) -> None:
         self.transport.request("POST", f"{self.route}/metrics", {"step": step, "values": values})

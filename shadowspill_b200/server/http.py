@@ -11,6 +11,8 @@
     POST /v1/runs/{session}                    create a run (202 while preparing)
     GET  /v1/runs/{session}/{run}              run info
     GET  .../progress?after=N                  preparation / startup log lines
+    GET  .../checkpoints                       names saved by this run
+    POST .../checkpoints/{name}/artifact       pack a checkpoint into a downloadable artifact
     GET|POST .../plans , POST .../plans/report plan names, summaries, HTML plan report
     GET  .../nsys?rank=                        Nsight capture status and report path
     POST .../writers/{writer_id}               attach as writer (fences earlier writers)
@@ -212,6 +214,13 @@ def make_handler(server):
             rest = p[2:]
             if not rest and method == "GET":
                 return self._send(200 if live.state != "preparing" else 202, live.info())
+            if len(rest) == 3 and rest[0] == "checkpoints" and rest[2] == "artifact" and method == "POST":
+                try:
+                    return self._send(200, server.checkpoint_artifact(p[0], rest[1]))
+                except FileNotFoundError as exc:
+                    raise HTTPError(404, str(exc)) from None
+            if rest == ["checkpoints"] and method == "GET":
+                return self._send(200, {"checkpoints": sorted(live.checkpoints)})
             if rest == ["progress"]:
                 after = int(q.get("after", 0))
                 return self._send(200, {"lines": live.progress[after:], "next": len(live.progress)})

@@ -262,6 +262,34 @@ class Server:
             return str(found[0])
         raise FileNotFoundError(f"no checkpoint {name!r}")
 
+    def checkpoint_artifact(self, session: str, name: str) -> dict[str, Any]:
+        """Packs a saved checkpoint (or exported weights) directory into one artifact that the
+        client can download with byte ranges; returns its handle. The archive is an
+        uncompressed TAR with members in sorted order, so the same checkpoint always gives
+        the same bytes and digest."""
+        import hashlib
+        import tarfile
+        directory = Path(self.resolve_checkpoint(session, name))
+        store = self.root / "artifacts"
+        store.mkdir(exist_ok=True)
+        tmp = store / f".pack-{uuid.uuid4().hex}"
+        with tarfile.open(tmp, "w", format=tarfile.PAX_FORMAT) as tar:
+            for f in sorted(p for p in directory.rglob("*") if p.is_file()):
+                info = tar.gettarinfo(str(f), arcname=str(Path(name) / f.relative_to(directory)))
+                info.mtime, info.uid, info.gid, info.uname, info.gname = 0, 0, 0, "", ""
+                with open(f, "rb") as fh:
+                    tar.addfile(info, fh)
+        h = hashlib.sha256()
+        with open(tmp, "rb") as fh:
+            for block in iter(lambda: fh.read(1 << 20), b""):
+                h.update(block)
+        digest = h.hexdigest()
+        aid = digest[:16]
+        tmp.replace(store / aid)
+        size = (store / aid).stat().st_size
+        self.artifacts[aid] = {"size": size, "sha256": digest, "complete": True}
+        return {"artifact": aid, "size": size, "sha256": digest, "checkpoint": name}
+
     def describe(self, body: dict[str, Any]) -> dict[str, Any]:
         r = resolve_training(body, self.registry, self.hardware)
         params = r.cfg.parameter_count()

@@ -42,7 +42,7 @@ def test_auth_is_enforced(service):
     assert e.value.status == 401
 
 
-def test_train_checkpoint_resume_through_the_public_api(service):
+def test_train_checkpoint_resume_through_the_public_api(service, tmp_path_factory):
     with ServiceClient(service.url, token="secret") as svc:
         hw = svc.list_hardware().result()
         assert hw["nodes"][0]["cpus"] >= 1
@@ -76,6 +76,13 @@ def test_train_checkpoint_resume_through_the_public_api(service):
         trainer.discard_gradients().result()
         saved = trainer.save_checkpoint("after5").result()
         assert saved.outputs["checkpoint"] == "after5"
+        # the checkpoint can be fetched: packed on the service, downloaded with ranges, unpacked
+        assert trainer.list_checkpoints() == ["after5"]
+        local = trainer.download_checkpoint("after5", tmp_path_factory.mktemp("dl"), chunk_bytes=200_000).result()
+        from shadowspill_b200.checkpoint.load import checkpoint_files, export_weights
+        assert len(checkpoint_files(local)) == 1
+        weights = export_weights(local)
+        assert weights["embed.embed"].shape == (512, 128) and "exp_avg.embed.embed" not in weights
         next_loss = trainer.step(text_batch(_sequences(7))).result().loss
         # local validation never reaches the server
         with pytest.raises(BatchError):
