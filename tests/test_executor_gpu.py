@@ -59,3 +59,28 @@ def test_planned_step_matches_resident(selection):
     stats = ex.rt.stats()
     assert stats["fetch_bytes"] > 0 and stats["evict_bytes"] > 0
     ex.close()
+
+
+def test_forward_program_returns_target_logprobs():
+    """A forward-only plan on the device: the per-position log-probabilities it returns add up
+    (with the batch weights) to the loss it reports, and positions without a target read 0."""
+    from shadowspill_b200.frontend.capture import build_forward
+    cfg = DecoderConfig("llama3", 2, 512, 4, 2, 128, 1024, 4096)
+    geo = BatchGeometry(1024, 2, slots=32, mean_seqlen=200)
+    prog, desc = build_forward(cfg, geo, StepDataOrdering())
+    total = sum(o.bytes for o in prog.objects)
+    ws = max(t.workspace_bytes for t in prog.tasks)
+    plan = plan_program(prog, MemoryBudgets(2 * ws + total, 1 << 30, headroom_bytes=0), CommunicationInfo(),
+                        SearchOptions(minimum_object_bytes_evict_eligible=4096))
+    ex = Executor(plan, desc, device="cuda", seed=3, stochastic_rounding=False)
+    ex.initialize(on_device=False)
+    host = make_batch(0, vocab=cfg.vocab_size, tokens_per_step=2048, microbatch_tokens=1024,
+                      median=200, min_len=16, max_len=512, slots=32)
+    res = ex.run(host)
+    _lib.check_status()
+    assert len(res.outputs) == 2 and res.outputs[0].shape == (1024, 1)
+    rebuilt = sum(float(-(o[:, 0] * m.weights)[m.targets >= 0].sum()) for o, m in zip(res.outputs, host))
+    assert abs(rebuilt - res.loss) < 2e-3 * abs(res.loss)
+    for o, m in zip(res.outputs, host):
+        assert (o[:, 0][m.targets < 0] == 0).all() and (o <= 0).all()
+    ex.close()
