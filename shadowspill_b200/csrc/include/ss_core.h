@@ -243,7 +243,7 @@ typedef struct ss_runtime_config {
   int32_t file_create_image;   /* create file_image (must not exist) instead of opening it */
   int32_t file_queue_depth;    /* slots per direction; 0 = 16 */
   int64_t file_chunk_bytes;    /* multiple of 4096; 0 = 2 MiB */
-  int32_t file_io_threads;     /* disk threads per direction; 0 = 2 */
+  int32_t file_io_threads;     /* disk threads per direction; 0 = 4 */
   int32_t reserved0;
   /* "host:port" of a memory daemon: the pool's file_bytes are then held by that daemon
    * instead of a local file (same staged lanes, chunks travel over TCP). */

@@ -426,7 +426,7 @@ int ss_runtime_create(ss_backend* backend, const ss_runtime_config* config, ss_r
     if (rc != SS_OK) std::fprintf(stderr, "ss runtime: %s\n", error.c_str());
     const int64_t chunk = config->file_chunk_bytes > 0 ? config->file_chunk_bytes : (2ll << 20);
     const int32_t depth = config->file_queue_depth > 0 ? config->file_queue_depth : 16;
-    const int32_t io = config->file_io_threads > 0 ? config->file_io_threads : 2;
+    const int32_t io = config->file_io_threads > 0 ? config->file_io_threads : 4;
     if (rc == SS_OK) {
       rt->fetch_lane = std::make_unique<ssc::StagedLane>(backend, rt->fetch_stream, rt->store, true, chunk, depth, io);
       rt->evict_lane = std::make_unique<ssc::StagedLane>(backend, rt->evict_stream, rt->store, false, chunk, depth, io);
