@@ -124,7 +124,11 @@ int event_record(void* self, void* e, void* s) {
 int event_query(void* self, void* e) {
   bind(self);
   cudaError_t r = cudaEventQuery(static_cast<cudaEvent_t>(e));
-  if (r == cudaErrorNotReady) return SS_TIMEOUT;
+  if (r == cudaErrorNotReady) {
+    (void)cudaGetLastError();   // "not ready" is recorded as this thread's last error: clear it, or
+                                // the next launch check on this thread would report it
+    return SS_TIMEOUT;
+  }
   return rc_of(r);
 }
 int event_synchronize(void* self, void* e) {
