@@ -35,7 +35,8 @@ def _microbatches(seed, valid=ROWS):
     return out
 
 
-def test_planned_regression_matches_torch_autograd_and_adamw():
+@pytest.mark.parametrize("device", ["cpu", pytest.param("cuda", marks=pytest.mark.gpu)])
+def test_planned_regression_matches_torch_autograd_and_adamw(device):
     cfg = preset("regression")
     assert cfg.parameter_count() == 16 * 32 + 32 + 32 * 8 + 8
     geo = BatchGeometry(ROWS, MBS, slots=ROWS + 1, mean_seqlen=1)
@@ -46,8 +47,8 @@ def test_planned_regression_matches_torch_autograd_and_adamw():
     plan = plan_program(prog, MemoryBudgets(ws + total, 16 << 20, headroom_bytes=0), CommunicationInfo(),
                         SearchOptions(minimum_object_bytes_evict_eligible=64, workers=1))
     hyper = Hyperparameters(lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0)
-    ex = Executor(plan, desc, device="cpu", seed=5, hyper=hyper, stochastic_rounding=False)
-    ex.initialize()
+    ex = Executor(plan, desc, device=device, seed=5, hyper=hyper, stochastic_rounding=False)
+    ex.initialize(on_device=False)
     state = ex.state_dict()
     ref = reference_module(cfg)
     with torch.no_grad():
