@@ -201,7 +201,9 @@ class TrainingSession:
             if world > 1:
                 dist.barrier()
             if file_spill:
-                # rates of the staged lanes (device <-> file), every rank's file on the drive at once
+                # rates of the staged lanes (device <-> file), every rank's file on the drive at once;
+                # a probe well beyond a drive's write cache, or the plan is built on its burst rate
+                probe = 1 << 30
                 import os
                 scratch = "" if remote else (setup.spill_directory
                                              or os.path.dirname(os.path.abspath(setup.spill_image)))
