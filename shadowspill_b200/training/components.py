@@ -166,6 +166,13 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
     registry.get("objective", body["objective"]["id"])
     opt = body["optimizer"]
     registry.get("optimizer", opt["id"])
+    # gradients, moments and parameters are all kept in the model dtype (no master copies):
+    # say so instead of silently ignoring a request for anything else
+    model_dtype = m.get("dtype", "bfloat16")
+    for key in ("gradient_dtype", "opt_state_dtype", "master_dtype"):
+        if opt.get(key, "bfloat16") not in ("bfloat16", model_dtype):
+            raise ValueError(f"optimizer {key}={opt[key]!r} is not supported: state is kept in the "
+                             f"model dtype ({model_dtype})")
     res = body.get("resources", {})
     par = body.get("parallelism") or {}
     per_replica = int(par.get("ranks_per_replica", res.get("gpus", 1)))

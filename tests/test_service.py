@@ -222,3 +222,15 @@ def test_resumable_artifact_transfer_and_component_listing(service, tmp_path):
         from shadowspill_b200.client.transport import TransportError
         with pytest.raises(TransportError):
             svc.download_artifact(handle.artifact, tmp_path / "gone.bin").result()
+
+
+def test_unsupported_optimizer_state_dtypes_are_refused(service):
+    with ServiceClient(service.url, token="secret") as svc:
+        with pytest.raises(Exception) as e:
+            svc.describe_training(model=Model("llama3-tiny"), optimizer=Optimizer(master_dtype="float32"),
+                                  resources=Resources(backend="cpu")).result()
+        assert "master_dtype" in str(e.value)
+        ok = svc.describe_training(model=Model("llama3-tiny", dtype="float32"),
+                                   optimizer=Optimizer(master_dtype="float32", opt_state_dtype="float32"),
+                                   resources=Resources(backend="cpu")).result()
+        assert ok["workers"] == 1
