@@ -8,13 +8,15 @@ points release the GIL, so several searches can run from Python threads.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import threading
 from pathlib import Path
 
 import numpy as np
 
 _DIR = Path(__file__).resolve().parent / "csrc"
-CORE_PATH = _DIR / "libss_core.so"
+# SS_CORE_LIB selects another build of the core (an instrumented one for race detection)
+CORE_PATH = Path(os.environ["SS_CORE_LIB"]) if os.environ.get("SS_CORE_LIB") else _DIR / "libss_core.so"
 CUDA_BACKEND_PATH = _DIR / "libss_backend_cuda.so"
 
 i32, i64, f64, vp = C.c_int32, C.c_int64, C.c_double, C.c_void_p
