@@ -5,7 +5,7 @@
 The C++ core is rebuilt with ``-fsanitize=thread`` into a scratch directory and a workload
 that exercises every thread the runtime owns is run against it in a child process: planned
 training steps on the mock backend (dispatcher + worker thread + two stream threads), the
-same through the file pool (plus disk threads and staged lanes), lane calibration from the
+same through the file pool and the remote pool (plus disk threads and staged lanes), lane calibration from the
 calling thread, and a step that ends in an injected copy failure (latch + drain). The child
 runs with ``libtsan`` preloaded because the interpreter itself is not instrumented.
 
@@ -79,6 +79,22 @@ with tempfile.TemporaryDirectory() as d:
                  file_chunk_bytes=64 << 10, file_queue_depth=3)
     rt.calibrate_file(1 << 20, repeats=1)
     rt.close()
+# the remote pool: chunks over sockets borrowed by several disk threads at once
+import subprocess
+from shadowspill_b200 import build
+build.build_core()
+daemon = subprocess.Popen([str(build.MEMORY_DAEMON), "--port", "0"], stdout=subprocess.PIPE, text=True)
+try:
+    address = "127.0.0.1:" + daemon.stdout.readline().split()[1]
+    ex = Executor(move_homes_to_file(copy.deepcopy(plan)), desc, device="cpu", seed=1,
+                  file_pool={"remote": address, "chunk_bytes": 16 << 10, "queue_depth": 3})
+    ex.initialize()
+    got = [ex.run(batch(s)).loss for s in range(2)]
+    ex.close()
+    assert got == want, (got, want)
+finally:
+    daemon.kill()
+    daemon.wait()
 print("workload ok")
 """
 
