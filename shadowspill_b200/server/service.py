@@ -61,6 +61,12 @@ class LiveRun:
         try:
             self.journal.append("created", {"session": self.session, "run": self.run})
             self.log("resolving settings")
+            weights = (self.body.get("model") or {}).get("weights") or {}
+            if weights.get("source") == "artifact":
+                # an uploaded TAR of a Hugging Face directory: unpack once, then it is a checkpoint path
+                where = self.server.unpack_artifact(weights["location"])
+                self.body["model"]["weights"] = dict(weights, source="checkpoint", location=str(where))
+                self.log(f"weights artifact {weights['location']} unpacked")
             self.resolved = resolve_training(self.body, self.server.registry, self.server.hardware)
             r = self.resolved
             host_bytes = int(r.budgets["spill_gib"] * GIB) * r.workers
@@ -261,6 +267,24 @@ class Server:
         if found:
             return str(found[0])
         raise FileNotFoundError(f"no checkpoint {name!r}")
+
+    def unpack_artifact(self, artifact: str) -> Path:
+        """Extracts an uploaded, sealed TAR artifact under the artifact store and returns the
+        directory that holds its ``*.safetensors`` files."""
+        import tarfile
+        src = self.root / "artifacts" / artifact
+        if not src.exists():
+            raise FileNotFoundError(f"no sealed artifact {artifact!r}")
+        dst = self.root / "artifacts" / f"{artifact}.d"
+        if not dst.exists():
+            tmp = self.root / "artifacts" / f".unpack-{uuid.uuid4().hex}"
+            with tarfile.open(src) as tar:
+                tar.extractall(tmp, filter="data")        # refuses links and paths outside tmp
+            tmp.replace(dst)
+        found = sorted(dst.rglob("*.safetensors"))
+        if not found:
+            raise FileNotFoundError(f"artifact {artifact!r} holds no .safetensors file")
+        return found[0].parent
 
     def checkpoint_artifact(self, session: str, name: str) -> dict[str, Any]:
         """Packs a saved checkpoint (or exported weights) directory into one artifact that the

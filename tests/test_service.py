@@ -234,3 +234,39 @@ def test_unsupported_optimizer_state_dtypes_are_refused(service):
                                    optimizer=Optimizer(master_dtype="float32", opt_state_dtype="float32"),
                                    resources=Resources(backend="cpu")).result()
         assert ok["workers"] == 1
+
+
+def test_pretrained_weights_arrive_as_an_uploaded_artifact(service, tmp_path):
+    """Hugging Face weights packed into a TAR, uploaded, and named by ``Weights.artifact``: the
+    run starts from them (its first loss equals a local model's loss on the same weights)."""
+    import tarfile
+    import torch
+    from shadowspill_b200.checkpoint import hf
+    from shadowspill_b200.client.config import Weights
+    from shadowspill_b200.client.packing import pack_batch
+    from shadowspill_b200.data.synthetic import HostMicrobatch, to_device
+    from shadowspill_b200.execution.resident import ResidentTrainer
+    from shadowspill_b200.models.config import preset
+    cfg = preset("llama3-tiny")
+    local = ResidentTrainer(cfg, device="cpu", dtype=torch.float32, seed=77)
+    hf.save_hf(cfg, local.state_dict(), tmp_path / "weights")
+    with tarfile.open(tmp_path / "weights.tar", "w") as tar:
+        tar.add(tmp_path / "weights", arcname="weights")
+    batch = text_batch(_sequences(4))
+    mbs = pack_batch(batch, microbatch_tokens=256, microbatches=2, slots=16)
+    want = local.evaluate([to_device(HostMicrobatch(m.tokens, m.targets, m.weights, m.positions, m.cu_seqlens,
+                                                    m.max_seqlen), "cpu") for m in mbs])
+    with ServiceClient(service.url, token="secret") as svc:
+        handle = svc.upload_artifact(tmp_path / "weights.tar").result()
+        trainer = svc.create_training_client(
+            Model("llama3-tiny", dtype="float32", weights=Weights.artifact(handle.artifact)),
+            Optimizer(lr=1e-3, parameter_rounding="nearest"),
+            batch=BatchConfig(tokens_per_step=512, microbatch_tokens=256),
+            memory=Memory(device_gib=0.53, spill_gib=0.25), resources=Resources(gpus=1, backend="cpu"),
+            preparation=Preparation(profiling=ProfilingOptions(enabled=False), calibrate=False,
+                                    planning=PlanningOptions(minimum_object_bytes_evict_eligible=1024,
+                                                             workers=1)),
+            operations=("step", "forward"), timeout=300).result()
+        got = trainer.forward(batch).result().loss
+        trainer.close()
+    assert abs(got - want) < 1e-5 * max(1.0, abs(want))
