@@ -500,6 +500,48 @@ class Executor:
         if strict and extra:
             raise KeyError(f"unexpected tensors {sorted(extra)[:4]}")
 
+    def load_full_state_dict(self, state: dict[str, torch.Tensor], strict: bool = True) -> None:
+        """Loads WHOLE parameters (``{"<stage>.<param>": tensor}``, for example a converted
+        Hugging Face checkpoint) into this rank's homes: with sharded storage every rank keeps
+        its 1/N slice of each tensor, with expert parallelism its own rows of each bank.
+        Moments are left as they are. Parameters the state does not name keep their values
+        unless ``strict``."""
+        if self.world == 1:
+            if strict:
+                for st in self.stages:
+                    for p in st.params:
+                        if f"{st.name}.{p.name}" not in state:
+                            raise KeyError(f"missing tensor {st.name}.{p.name}")
+            self.load_state_dict(state, strict=False)
+            return
+        for st in self.stages:
+            name = f"{st.name}.weights"
+            if name not in self._obj:
+                continue
+            shards = st.shard_views(self.spill_view(self._obj[name]), self.desc.dtype, self.world)
+            for p in st.params:
+                key = f"{st.name}.{p.name}"
+                if key not in state:
+                    if strict:
+                        raise KeyError(f"missing tensor {key}")
+                    continue
+                src, dst = state[key], shards[p.name]
+                if p.expert_sharded:
+                    want = tuple(p.global_shape)
+                    if tuple(src.shape) != want:
+                        raise ValueError(f"{key}: shape {tuple(src.shape)} != {want}")
+                    rows = src[p.expert_lo:p.expert_lo + p.shape[0]].reshape(-1)
+                    dst[:rows.numel()].copy_(rows.to(dst.dtype))
+                    continue
+                if src.numel() != p.numel:
+                    raise ValueError(f"{key}: {src.numel()} elements, expected {p.numel}")
+                flat = src.reshape(-1)
+                lo = self.rank * dst.numel()
+                hi = min(flat.numel(), lo + dst.numel())
+                dst.zero_()
+                if hi > lo:
+                    dst[:hi - lo].copy_(flat[lo:hi].to(dst.dtype))
+
     # ------------------------------------------------------------------ inputs
     def stage_inputs(self, batch: list[HostMicrobatch]) -> int:
         """Writes the packed microbatches into their spill homes; returns bytes staged."""

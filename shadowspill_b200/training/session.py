@@ -357,12 +357,14 @@ class TrainingSession:
             self.executor.initialize()      # an opened image already holds the state
         if setup.pretrained:
             from ..checkpoint.hf import load_hf
-            state = load_hf(self.cfg, setup.pretrained, self.executor.stages)
-            if world > 1:
-                raise NotImplementedError("pretrained weights load into single-rank runs; "
-                                          "restore a checkpoint to continue on several ranks")
-            # adapters and anything else the checkpoint does not name keep their initial values
-            self.executor.load_state_dict(state, strict=False)
+            # expert-parallel stages hold local banks: name the whole banks from a plain build
+            from ..models.decoder import build_stages as _plain
+            naming = (_plain(self.cfg, self.objective, self.lora) if setup.expert_parallel
+                      else self.executor.stages)
+            state = load_hf(self.cfg, setup.pretrained, naming)
+            # adapters and anything else the checkpoint does not name keep their initial values;
+            # with several ranks each keeps its slice of every tensor
+            self.executor.load_full_state_dict(state, strict=False)
             self.log(f"weights from {setup.pretrained}")
         self.timings["open"] = time.perf_counter() - t0
         if cuda:

@@ -23,6 +23,9 @@ def main():
     expert_parallel = arm == "ep"         # routed model, experts split over the ranks
     if expert_parallel:
         arm = "peer"
+    pretrained = arm.startswith("pretrained-")   # start from whole-parameter weights of another seed
+    if pretrained:
+        arm = arm.split("-", 1)[1]
     replicas = 1
     if arm.startswith("replicas-"):       # e.g. replicas-dist / replicas-peer on 4 ranks: 2 x 2
         replicas, arm = 2, arm.split("-", 1)[1]
@@ -52,8 +55,12 @@ def main():
     ex = Executor(plan, desc, device=device, device_index=rank if cuda else 0, seed=5,
                   hyper=Hyperparameters(lr=lr), stochastic_rounding=False, collectives=arm)
     ex.initialize(on_device=False)
-    ref = ResidentTrainer(cfg, device=f"cuda:{rank}" if cuda else "cpu", dtype=dtype, seed=5,
-                          lr=lr, stochastic_rounding=False)
+    ref = ResidentTrainer(cfg, device=f"cuda:{rank}" if cuda else "cpu", dtype=dtype,
+                          seed=9 if pretrained else 5, lr=lr, stochastic_rounding=False)
+    if pretrained:
+        # every rank keeps its slice of each whole tensor; moments stay at zero on both sides
+        whole = {k: v.cpu() for k, v in ref.state_dict().items() if not k.startswith("exp_avg")}
+        ex.load_full_state_dict(whole)
     ok = True
     for step in range(2):
         # the global batch: every rank's microbatches, weights normalised over all of them

@@ -23,6 +23,12 @@ def test_two_ranks_gloo_match_resident():
     _launch(2, "cpu", "dist", 29611)
 
 
+def test_whole_parameter_weights_load_into_sharded_ranks():
+    """Weights of another seed given as whole tensors: every rank keeps its slice, and the
+    sharded job then trains exactly like a single-process model started from those weights."""
+    _launch(2, "cpu", "pretrained-dist", 29631)
+
+
 def test_two_replicas_of_two_shards_gloo_match_resident():
     """Hierarchical data parallelism: state sharded inside groups of two ranks, two such groups;
     gradients are summed over all four ranks, weights are gathered inside a group."""
