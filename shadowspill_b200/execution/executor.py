@@ -244,8 +244,10 @@ class Executor:
                  stochastic_rounding: bool = True, trace_capacity: int = 0,
                  mock_bps: float = 0.0, collectives: str = "auto",
                  extra_plans: dict[str, tuple[Plan, TrainingDescription]] | None = None,
-                 file_pool: dict | None = None):
-        """``file_pool``: settings of the file-backed spill pool for plans whose homes were
+                 file_pool: dict | None = None, annotate: bool = False):
+        """``annotate``: wrap every task in an NVTX range named after it (visible in Nsight
+        Systems captures; no effect off the GPU).
+        ``file_pool``: settings of the file-backed spill pool for plans whose homes were
         moved there (``planning.plan.move_homes_to_file``): ``directory`` or ``image``
         (+ ``create_image``) or ``remote`` ("host:port" of a memory daemon), optional
         ``chunk_bytes`` / ``queue_depth`` / ``io_threads``.
@@ -257,6 +259,7 @@ class Executor:
         self.plan, self.desc = plan, desc
         self.program = plan.program
         self.cuda = device == "cuda"
+        self.annotate = bool(annotate) and self.cuda
         self.device_index = device_index
         self.torch_device = torch.device(f"cuda:{device_index}") if self.cuda else torch.device("cpu")
         self.hyper = hyper or Hyperparameters()
@@ -645,7 +648,11 @@ class Executor:
                     events[task][0].record(self.stream)
                 elif not self.cuda and time_tasks:
                     tt = time.perf_counter()
+                if self.annotate:
+                    torch.cuda.nvtx.range_push(self.program.tasks[task].name)
                 self.runner.run_task(task, B)
+                if self.annotate:
+                    torch.cuda.nvtx.range_pop()
                 if events:
                     events[task][1].record(self.stream)
                 elif not self.cuda and time_tasks:

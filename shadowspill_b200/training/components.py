@@ -242,6 +242,7 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
             "search": search, "collectives": ex.get("collectives", "auto"),
             "operations": list(body.get("operations", ("step",))),
             "trace_capacity": 65536 if ex.get("runtime_trace") else 0, "nsys": ex.get("nsys"),
+            "profiler_annotations": bool(ex.get("profiler_annotations", False)),
             "spill_pool": mem.get("spill_pool", "host"), "spill_directory": mem.get("spill_directory", ""),
             "spill_address": mem.get("spill_address", ""),
             "spill_chunk_bytes": int(mem.get("spill_chunk_bytes", 2 << 20)),

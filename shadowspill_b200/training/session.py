@@ -84,6 +84,7 @@ class TrainingSetup:
     # spilled state in pinned host memory ("host") or in a direct-I/O file ("file"): then
     # spill_gib is the file's size and only batches and the loss word stay pinned
     # ... or in the memory of an ss_memory_daemon on another machine ("remote", spill_address)
+    profiler_annotations: bool = False    # NVTX range per task
     spill_pool: str = "host"
     spill_address: str = ""               # "remote": host:port of the daemon
     spill_directory: str = ""             # existing directory for the unlinked scratch file
@@ -352,7 +353,7 @@ class TrainingSession:
                                  stochastic_rounding=setup.stochastic_rounding,
                                  trace_capacity=setup.trace_capacity,
                                  collectives=setup.collectives, extra_plans=self.extra_plans,
-                                 file_pool=file_pool)
+                                 file_pool=file_pool, annotate=setup.profiler_annotations)
         if not (file_spill and setup.spill_image and not setup.spill_create_image):
             self.executor.initialize()      # an opened image already holds the state
         if setup.pretrained:
