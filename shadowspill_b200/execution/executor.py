@@ -465,8 +465,10 @@ class Executor:
                 del flat
             for suffix in ("exp_avg", "exp_avg_sq", "gradients"):
                 name = f"{st.name}.{suffix}"
-                if name in self._obj and self.plan.spill_offsets[self._obj[name]] >= 0:
+                if name in self._obj and self.plan.home_pool(self._obj[name]):
                     self.spill_view(self._obj[name]).zero_()
+            if self._mirrors:
+                self.flush_homes()      # file-homed state: one stage in host memory at a time
         self.runner.completed_updates = 0
         self.runner.accumulated = 0
 
