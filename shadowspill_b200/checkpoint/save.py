@@ -76,13 +76,22 @@ def save_checkpoint(executor, directory: str | Path, *, metadata: dict[str, Any]
     entries = state_entries(executor)
     writer = ArchiveWriter(directory / f"rank{executor.rank}.tar")
     try:
-        views = dict(executor.named_tensors(writable=False))
-        for e in entries:
-            t = views[e["name"]]
+        # streamed: with state homed in a file pool each object is read from the file when its
+        # first tensor comes up and dropped again, so one object is in host memory at a time
+        by_name = {e["name"]: e for e in entries}
+        for name, t in executor.named_tensors(writable=False):
+            e = by_name.pop(name, None)
+            if e is None:
+                continue
             lo, n = e["region"]
             flat = t.reshape(-1)[:n] if executor.world > 1 else t.reshape(-1)
             arr = flat.view(torch.uint8).numpy() if flat.numel() else np.zeros(0, np.uint8)
             writer.add_tensor(e, arr)
+            release = getattr(executor, "release_mirrors", None)
+            if release is not None:
+                release()
+        if by_name:
+            raise KeyError(f"state tensors without a home: {sorted(by_name)[:3]}")
         manifest = {
             "format": FORMAT, "version": VERSION, "byteorder": sys.byteorder,
             "state": state_identity(entries, executor.world),

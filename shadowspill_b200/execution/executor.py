@@ -408,6 +408,11 @@ class Executor:
             raise KeyError(f"{self.program.objects[obj].name} has no spill home")
         return self.rt.spill[off:off + nbytes]
 
+    def release_mirrors(self) -> None:
+        """Forgets read-only mirrors (their memory goes once the caller lets go of its views)."""
+        for off in [o for o, (_, writable) in self._mirrors.items() if not writable]:
+            del self._mirrors[off]
+
     def flush_homes(self) -> int:
         """Writes every writable mirror back to the file pool and drops all mirrors;
         returns the bytes written."""
