@@ -951,7 +951,11 @@ int ss_calibrate_file_transfers(ss_runtime* rt, int64_t bytes, int32_t repeats, 
   const double f_conc = time_job(true, true, bytes), e_conc = time_job(false, true, bytes);
   be->stream_synchronize(be->self, rt->fetch_stream);
   be->stream_synchronize(be->self, rt->evict_stream);
-  if (failed) return SS_IO_ERROR;
+  if (failed) {
+    // the lanes may still hold this call's jobs: make sure nobody pumps them again
+    rt->latch(SS_FAIL_BACKEND_COPY, SS_IO_ERROR, -1, -1, -1, 2, "calibration of the staged lanes failed");
+    return SS_IO_ERROR;
+  }
   auto rate = [&](double ns, double lat) { return static_cast<double>(bytes) / std::max(ns - lat, 1.0) * 1e9; };
   out->fetch_latency_ns = static_cast<int64_t>(lat_f);
   out->evict_latency_ns = static_cast<int64_t>(lat_e);
