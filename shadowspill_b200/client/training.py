@@ -123,9 +123,10 @@ class TrainingClient:
                               res.request_id, res.outputs)
 
     # ------------------------------------------------------------------ operations
-    def step(self, datums: list[Datum], *, lr: float | None = None) -> cf.Future:
-        """Forward, backward and one optimizer update on one global batch."""
-        return self._submit("step", self._pack(datums), lr=lr)
+    def step(self, datums: list[Datum], *, lr: float | None = None, grad_scale: float = 1.0) -> cf.Future:
+        """Forward, backward and one optimizer update on one global batch. ``grad_scale``
+        multiplies the gradients inside the update (loss-scale compensation, caller-side clipping)."""
+        return self._submit("step", self._pack(datums), lr=lr, grad_scale=grad_scale)
 
     def forward_backward(self, datums: list[Datum]) -> cf.Future:
         """Accumulates gradients; the first contribution after an update writes them fresh."""

@@ -123,8 +123,8 @@ def serve(chan: Channel) -> int:
                 if args.get("lr") is not None:
                     session.executor.hyper.lr = float(args["lr"])
                 if op in ("step", "forward_backward", "forward", "optim_step"):
-                    if op == "optim_step":
-                        session.executor.hyper.grad_scale = float(args.get("grad_scale", 1.0))
+                    if op in ("optim_step", "step"):
+                        session.executor.hyper.grad_scale = float(args.get("grad_scale") or 1.0)
                     started = True
                     if window is not None and op != "optim_step":
                         window.before_step()
