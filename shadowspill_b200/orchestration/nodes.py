@@ -99,6 +99,8 @@ class Membership:
         self.lease_seconds, self.clock = lease_seconds, clock
         self._lock = threading.Lock()
         self.members: dict[str, Member] = {}
+        # commands for node daemons: delivered on poll until the daemon sends a receipt
+        self._commands: dict[str, list[dict[str, Any]]] = {}
 
     def join(self, node_id: str, info: dict[str, Any] | None = None) -> str:
         with self._lock:
@@ -125,6 +127,38 @@ class Membership:
                 return False
             del self.members[node_id]
             return True
+
+    def enqueue(self, node_id: str, command: dict[str, Any]) -> str:
+        """Queues ``command`` for a live node's daemon; returns the command id."""
+        with self._lock:
+            m = self.members.get(node_id)
+            if m is None or m.fenced or self.clock() > m.expires:
+                raise KeyError(f"node {node_id!r} is not a live member")
+            cid = uuid.uuid4().hex[:12]
+            self._commands.setdefault(node_id, []).append(dict(command, id=cid, incarnation=m.incarnation))
+            return cid
+
+    def poll(self, node_id: str, incarnation: str) -> list[dict[str, Any]] | None:
+        """A daemon's poll renews its lease and returns every command it has not acknowledged
+        (at-least-once delivery); ``None`` for a fenced or unknown incarnation."""
+        if not self.heartbeat(node_id, incarnation):
+            return None
+        with self._lock:
+            return [c for c in self._commands.get(node_id, []) if c["incarnation"] == incarnation]
+
+    def receipt(self, node_id: str, incarnation: str, command_id: str, outcome: dict[str, Any] | None = None) -> bool:
+        """Acknowledges one command; it is not delivered again. False if unknown."""
+        with self._lock:
+            m = self.members.get(node_id)
+            if m is None or m.incarnation != incarnation:
+                return False
+            queue = self._commands.get(node_id, [])
+            for i, c in enumerate(queue):
+                if c["id"] == command_id:
+                    del queue[i]
+                    m.info.setdefault("receipts", []).append({"id": command_id, **(outcome or {})})
+                    return True
+            return False
 
     def reconcile(self) -> list[str]:
         """Fences every member whose lease ran out; returns their ids."""

@@ -20,7 +20,7 @@
     PUT  .../requests/{id}/input               input payload (429 = back-pressure, retry)
     GET  .../requests/{id}?wait=completed&timeout=S   status / long poll
     GET|POST .../metrics , POST .../report     metric pages, caller metrics, run report
-    POST /v1/nodes/{join,heartbeat,leave,reconcile}   node-daemon membership (node credential)
+    POST /v1/nodes/{join,heartbeat,poll,receipt,leave,reconcile}   node-daemon membership (node credential)
 
 Reference: packages/engine/src/shadowspill/server/http.py:448-520 and routes/*.py.
 """
@@ -143,6 +143,13 @@ def make_handler(server):
                 return self._send(200 if ok else 410, {"ok": ok})
             if action == "leave":
                 return self._send(200, {"ok": m.leave(body["node_id"], body["incarnation"])})
+            if action == "poll":
+                cmds = m.poll(body["node_id"], body["incarnation"])
+                return self._send(200 if cmds is not None else 410,
+                                  {"commands": cmds or [], "ok": cmds is not None})
+            if action == "receipt":
+                ok = m.receipt(body["node_id"], body["incarnation"], body["command"], body.get("outcome"))
+                return self._send(200 if ok else 404, {"ok": ok})
             if action == "reconcile":
                 return self._send(200, {"fenced": m.reconcile(), "live": m.live()})
             raise HTTPError(404, "unknown node action")

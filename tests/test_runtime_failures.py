@@ -84,6 +84,27 @@ def test_membership_lease_expiry_fences_permanently():
     assert not m.heartbeat("node-a", inc)                    # the old incarnation stays fenced
 
 
+def test_node_commands_are_delivered_until_acknowledged():
+    now = [0.0]
+    m = Membership(lease_seconds=10.0, clock=lambda: now[0])
+    inc = m.join("node-a")
+    cid = m.enqueue("node-a", {"kind": "drain"})
+    assert [c["id"] for c in m.poll("node-a", inc)] == [cid]
+    assert [c["id"] for c in m.poll("node-a", inc)] == [cid]          # not acknowledged: again
+    assert m.receipt("node-a", inc, cid, {"state": "done"}) and m.poll("node-a", inc) == []
+    assert not m.receipt("node-a", inc, cid)                          # only once
+    now[0] = 8.0
+    assert m.poll("node-a", inc) == []                                # a poll renews the lease
+    now[0] = 17.0
+    assert m.live() == ["node-a"]
+    now[0] = 40.0
+    assert m.poll("node-a", inc) is None                              # expired: fenced
+    with pytest.raises(KeyError):
+        m.enqueue("node-a", {"kind": "drain"})
+    new = m.join("node-a")
+    assert m.poll("node-a", inc) is None and m.poll("node-a", new) == []
+
+
 def test_node_admission_never_oversubscribes():
     adm = NodeAdmission(gpus=4, host_bytes=100)
     a, devs = adm.lease(3, 60)
