@@ -36,15 +36,17 @@ def state_entries(executor) -> list[dict[str, Any]]:
                 continue
             for p in st.params:
                 dt = p.dtype or executor.desc.dtype
-                numel = p.numel
-                if world > 1:
-                    per = -(-(-(-numel // world)) // 8) * 8
-                    lo = min(numel, rank * per)
-                    hi = min(numel, lo + per)
+                numel, shape = p.numel, p.shape
+                if p.expert_sharded:
+                    # this rank's experts are rows [expert_lo, expert_lo + local) of the whole bank
+                    shape = tuple(p.global_shape)
+                    row = p.numel // p.shape[0]
+                    numel = row * shape[0]
+                    lo, hi = p.expert_lo * row, p.expert_lo * row + p.numel
                 else:
-                    lo, hi = 0, numel
-                out.append({"name": f"{prefix}{st.name}.{p.name}", "shape": list(p.shape),
-                            "dtype": _NP[dt][0], "stride": _contiguous_stride(p.shape),
+                    lo, hi = st.owned_span(p, executor.desc.dtype, world, rank)
+                out.append({"name": f"{prefix}{st.name}.{p.name}", "shape": list(shape),
+                            "dtype": _NP[dt][0], "stride": _contiguous_stride(shape),
                             "storage_offset": 0, "storage_elements": numel,
                             "region": [lo, hi - lo]})
     return out

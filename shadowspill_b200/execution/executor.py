@@ -185,7 +185,8 @@ class TaskRunner:
             coll = self.collectives
             coll.barrier_begin()          # every rank's shard has landed
             for p in st.params:
-                if p.expert_sharded:      # this rank's own experts: nothing to gather
+                if p.expert_sharded or st.kept_whole(p, self.desc.dtype):
+                    # this rank's own experts, or a small tensor every rank stores whole: no gather
                     B["params"][p.name].view(-1).copy_(B["shard"][p.name][:p.numel])
                 else:
                     coll.all_gather(B["shard"][p.name], B["params"][p.name].view(-1))
@@ -222,7 +223,7 @@ class TaskRunner:
                 offset=self.param_offsets[(stage, p.name)], lr=h.lr, beta1=h.beta1, beta2=h.beta2,
                 eps=h.eps, weight_decay=h.weight_decay, step=self.completed_updates + 1,
                 grad_scale=h.grad_scale, seed=self.seed, stochastic_param=self.sr,
-                stochastic_state=self.sr)
+                stochastic_state=self.sr, whole=st.kept_whole(p, self.desc.dtype))
         coll.barrier_end()                # peers finished reading this rank's gradients
 
     def _optimizer(self, stage: int, B) -> None:
@@ -458,7 +459,7 @@ class Executor:
                     shards = st.shard_views(w, self.desc.dtype, self.world)
                     for p in st.params:
                         src, dst = full[p.name].reshape(-1), shards[p.name]
-                        if p.expert_sharded:
+                        if p.expert_sharded or st.kept_whole(p, self.desc.dtype):
                             dst[:src.numel()].copy_(src)
                             continue
                         lo = self.rank * dst.numel()
@@ -546,7 +547,7 @@ class Executor:
                 if src.numel() != p.numel:
                     raise ValueError(f"{key}: {src.numel()} elements, expected {p.numel}")
                 flat = src.reshape(-1)
-                lo = self.rank * dst.numel()
+                lo = 0 if st.kept_whole(p, self.desc.dtype) else self.rank * dst.numel()
                 hi = min(flat.numel(), lo + dst.numel())
                 dst.zero_()
                 if hi > lo:

@@ -77,6 +77,8 @@ class Stage:
         self.name = name
         self.cfg = cfg
         self.params: list[ParamSpec] = []
+        # sharded storage keeps tensors smaller than this whole on every rank (0 = shard all)
+        self.min_shard_bytes = 0
 
     # ---- layout
     def parameter_count(self) -> int:
@@ -122,13 +124,28 @@ class Stage:
             if trainable_only and not p.trainable:
                 continue
             dt = p.dtype or dtype
-            if p.expert_sharded:          # the local bank is this rank's own: stored whole
+            if p.expert_sharded or self.kept_whole(p, dtype):
+                # the local bank is this rank's own; a small tensor is not worth cutting
                 per = -(-p.numel // 8) * 8
             else:
                 per = -(-(-(-p.numel // world)) // 8) * 8
             out.append((p, off, dt, per))
             off = _round_up(off + per * dt.itemsize, ALIGN)
         return out, off
+
+    def kept_whole(self, p: ParamSpec, dtype: torch.dtype) -> bool:
+        """Under sharded storage: is ``p`` stored whole on every rank (replicated, updated by
+        every rank from the summed gradient) because it is smaller than ``min_shard_bytes``?"""
+        return (not p.expert_sharded and self.min_shard_bytes > 0
+                and p.numel * (p.dtype or dtype).itemsize < self.min_shard_bytes)
+
+    def owned_span(self, p: ParamSpec, dtype: torch.dtype, world: int, rank: int) -> tuple[int, int]:
+        """``[lo, hi)`` of ``p``'s flat elements that ``rank`` stores under sharded storage."""
+        if world <= 1 or self.kept_whole(p, dtype):
+            return 0, p.numel
+        per = -(-(-(-p.numel // world)) // 8) * 8
+        lo = min(p.numel, rank * per)
+        return lo, min(p.numel, lo + per)
 
     def shard_views(self, flat: torch.Tensor, dtype: torch.dtype, world: int,
                     trainable_only: bool = False) -> dict[str, torch.Tensor]:

@@ -84,13 +84,15 @@ class DistCollectives:
             if lo < n:
                 flat[lo:min(n, lo + per)].copy_(part[:min(n, lo + per) - lo])
 
-    def reduce_scatter_adamw(self, grad: torch.Tensor, p, m, v, *, offset: int, **adam) -> None:
-        """Sum ``grad`` over ranks; update this rank's owned slice of (p, m, v)."""
+    def reduce_scatter_adamw(self, grad: torch.Tensor, p, m, v, *, offset: int, whole: bool = False,
+                             **adam) -> None:
+        """Sum ``grad`` over ranks; update this rank's owned slice of (p, m, v). ``whole``: the
+        tensor is stored whole on every rank, which all apply the same update to all of it."""
         n, per = grad.numel(), p.numel()
         g = grad.view(-1).clone()
         if dist.is_initialized() and dist.get_world_size(self.group) > 1:
             dist.all_reduce(g, group=self.group)          # over every rank, replicas included
-        lo = self.rank * per
+        lo = 0 if whole else self.rank * per
         hi = min(n, lo + per)
         if hi <= lo:
             return
@@ -162,9 +164,11 @@ class PeerCollectives:
 
     def reduce_scatter_adamw(self, grad: torch.Tensor, p, m, v, *, offset: int, lr, beta1, beta2,
                              eps, weight_decay, step, grad_scale, seed, stochastic_param,
-                             stochastic_state) -> None:
+                             stochastic_state, whole: bool = False) -> None:
         n, per = grad.numel(), p.numel()
-        lo = self.shard_rank * per           # the slice this rank owns inside its replica
+        # the slice this rank owns inside its replica; a tensor stored whole is updated whole by
+        # every rank (same summed gradient, same counter-based rounding: identical results)
+        lo = 0 if whole else self.shard_rank * per
         hi = min(n, lo + per)
         if hi <= lo:
             return

@@ -234,6 +234,7 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
             "dtype": m.get("dtype", "bfloat16"), "stochastic_rounding": sr, "device": device,
             "device_index": rank if device == "cuda" else 0, "rank": rank, "world_size": workers,
             "ranks_per_replica": per_replica if replicas > 1 else 0,
+            "min_shard_bytes": int(par.get("min_shard_bytes", 0)) if workers > 1 else 0,
             "walks": list(build.get("walks", ("breadth",))),
             "recompute_shares": list(build.get("recompute_shares", (100,))),
             "saved_variant": saved_variant,

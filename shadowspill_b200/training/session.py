@@ -76,6 +76,7 @@ class TrainingSetup:
     objective: dict | None = None
     expert_parallel: bool = False        # routed layers keep 1/world of the experts per rank
     ranks_per_replica: int = 0           # 0 = one replica; else state is sharded inside groups of this size
+    min_shard_bytes: int = 0             # sharded storage keeps smaller tensors whole on every rank
     pretrained: str = ""                 # directory of Hugging Face safetensors to start from
     # content-addressed store of task profiles shared between runs ("" = none)
     store: str = ""
@@ -158,10 +159,12 @@ class TrainingSession:
             order = StepDataOrdering(walk=walk, optimizer="stage_interleaved" if walk == "breadth" else "tail")
             return with_replicas(build_step(self.cfg, self.geometry, order, dtype=self.dtype,
                                             selection=sel, world_size=shard_world, rank=rank,
-                                            expert_parallel=setup.expert_parallel, **choices))
+                                            expert_parallel=setup.expert_parallel,
+                                            min_shard_bytes=setup.min_shard_bytes, **choices))
 
         def build_extra(op: str):
-            kw = dict(dtype=self.dtype, world_size=shard_world, rank=rank, **choices)
+            kw = dict(dtype=self.dtype, world_size=shard_world, rank=rank,
+                      min_shard_bytes=setup.min_shard_bytes, **choices)
             if op == "forward_backward":
                 return with_replicas(build_forward_backward(self.cfg, self.geometry, StepDataOrdering(), **kw))
             if op == "optim_step":

@@ -26,6 +26,11 @@ def main():
     pretrained = arm.startswith("pretrained-")   # start from whole-parameter weights of another seed
     if pretrained:
         arm = arm.split("-", 1)[1]
+    # "small-<arm>": tensors under 64 KiB stay whole on every rank (the norm vectors and, in the
+    # tiny model, the attention projections), everything larger is cut into shards
+    min_shard = 0
+    if arm.startswith("small-"):
+        min_shard, arm = 64 << 10, arm.split("-", 1)[1]
     replicas = 1
     if arm.startswith("replicas-"):       # e.g. replicas-dist / replicas-peer on 4 ranks: 2 x 2
         replicas, arm = 2, arm.split("-", 1)[1]
@@ -46,7 +51,8 @@ def main():
     geo = BatchGeometry(T, n_mb, slots=16, mean_seqlen=64)
     shard_world = world // replicas
     prog, desc = build_step(cfg, geo, StepDataOrdering(), dtype=dtype, world_size=shard_world, rank=rank,
-                            expert_parallel=expert_parallel, replicas=replicas)
+                            expert_parallel=expert_parallel, replicas=replicas,
+                            min_shard_bytes=min_shard)
     total = sum(o.bytes for o in prog.objects)
     plan = plan_program(prog, MemoryBudgets(total, 64 << 20, headroom_bytes=0), CommunicationInfo(),
                         SearchOptions(minimum_object_bytes_evict_eligible=1024, workers=1,

@@ -23,6 +23,12 @@ def test_two_ranks_gloo_match_resident():
     _launch(2, "cpu", "dist", 29611)
 
 
+def test_small_tensors_stay_whole_under_sharded_storage():
+    """``min_shard_bytes``: small tensors are replicated and updated identically by every rank
+    from the summed gradient; the job still matches the single-process model."""
+    _launch(2, "cpu", "small-dist", 29641)
+
+
 def test_whole_parameter_weights_load_into_sharded_ranks():
     """Weights of another seed given as whole tensors: every rank keeps its slice, and the
     sharded job then trains exactly like a single-process model started from those weights."""
@@ -37,7 +43,7 @@ def test_two_replicas_of_two_shards_gloo_match_resident():
 
 @pytest.mark.gpu
 @pytest.mark.multigpu
-@pytest.mark.parametrize("arm", ["peer", "dist"])
+@pytest.mark.parametrize("arm", ["peer", "dist", "small-peer"])
 def test_two_gpus_match_resident(arm):
     _launch(2, "cuda", arm, 29613 if arm == "peer" else 29615)
 

@@ -181,12 +181,28 @@ def test_two_replicas_of_two_ranks_through_the_service(service):
             preparation=Preparation(profiling=ProfilingOptions(enabled=False), calibrate=False,
                                     planning=PlanningOptions(minimum_object_bytes_evict_eligible=1024,
                                                              workers=1)),
-            timeout=600).result()
+            operations=("step", "forward"), timeout=600).result()
         assert trainer.info["workers"] == 4
         batches = [text_batch(_sequences(s, n=32)) for s in (0, 0, 0, 0)]
         losses = [trainer.step(b).result().loss for b in batches]
         assert losses[-1] < losses[0]
+        # the client's declaration carries min_shard_bytes = 2 MiB: every tensor of this tiny model
+        # is kept whole on each rank. A checkpoint of that job restores into a single worker.
+        probe = text_batch(_sequences(9, n=8))
+        before = trainer.forward(probe).result().loss
+        trainer.save_checkpoint("from4").result()
         trainer.close()
+        single = svc.create_training_client(
+            Model("llama3-tiny", dtype="float32"), Optimizer(lr=3e-3, parameter_rounding="nearest"),
+            batch=BatchConfig(tokens_per_step=512, microbatch_tokens=256),
+            memory=Memory(device_gib=0.53, spill_gib=0.25), resources=Resources(gpus=1, backend="cpu"),
+            preparation=Preparation(profiling=ProfilingOptions(enabled=False), calibrate=False,
+                                    planning=PlanningOptions(minimum_object_bytes_evict_eligible=1024,
+                                                             workers=1)),
+            operations=("step", "forward"), checkpoint="from4", timeout=300).result()
+        after = single.forward(probe).result().loss
+        assert abs(after - before) < 1e-5 * max(1.0, abs(before))
+        single.close()
 
 
 def test_resumable_artifact_transfer_and_component_listing(service, tmp_path):
