@@ -138,3 +138,32 @@ def test_hugging_face_names_round_trip(tmp_path):
     import pytest
     with pytest.raises(ValueError):
         hf.from_hf(cfg, named)
+
+
+def test_expert_banks_are_recorded_in_global_coordinates():
+    """Under expert parallelism every rank holds its own rows of each bank; the checkpoint entries
+    of all ranks must tile the whole bank so that a run with another rank count can load it."""
+    import math
+    import types
+    import torch
+    from shadowspill_b200.checkpoint.save import state_entries
+    from shadowspill_b200.models.config import preset
+    from shadowspill_b200.models.decoder import build_stages
+    cfg = preset("olmoe-tiny")
+    per_rank = []
+    for rank in range(2):
+        stages = build_stages(cfg, expert_parallel=(2, rank))
+        obj = {f"{st.name}.{k}": 1 for st in stages for k in ("weights", "exp_avg", "exp_avg_sq")}
+        fake = types.SimpleNamespace(world=2, rank=rank, stages=stages, _obj=obj,
+                                     desc=types.SimpleNamespace(dtype=torch.float32))
+        per_rank.append({e["name"]: e for e in state_entries(fake)})
+    name = "layer0.w13"
+    a, b = per_rank[0][name], per_rank[1][name]
+    assert a["shape"] == b["shape"] == [cfg.n_experts, 2 * cfg.d_expert, cfg.d_model]
+    total = math.prod(a["shape"])
+    assert a["storage_elements"] == total
+    assert a["region"] == [0, total // 2] and b["region"] == [total // 2, total // 2]
+    # dense tensors of the same stage are still cut into flat shards
+    d0, d1 = per_rank[0]["layer0.wq"], per_rank[1]["layer0.wq"]
+    assert d0["region"][0] == 0 and d1["region"][0] == d0["region"][1]
+    assert d0["region"][1] + d1["region"][1] == d0["storage_elements"]
