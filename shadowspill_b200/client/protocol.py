@@ -17,7 +17,7 @@ from typing import Any
 import numpy as np
 
 OPERATIONS = ("step", "forward_backward", "forward", "optim_step", "discard", "save", "restore",
-              "export", "close")
+              "export", "plan_report", "close")
 
 
 @dataclass

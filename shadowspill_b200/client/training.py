@@ -53,6 +53,8 @@ class TrainingClient:
         self.writer_id = uuid.uuid4().hex
         self.transport.request("POST", f"{self.route}/writers/{self.writer_id}", {})
         self.pool = cf.ThreadPoolExecutor(max_workers=max(2, max_pending_requests))
+        # transfers wait on operations: they get threads of their own so they can never starve them
+        self._downloads = cf.ThreadPoolExecutor(max_workers=2)
         self.max_staging_bytes, self.max_pending = max_staging_bytes, max_pending_requests
         self._lock = threading.Condition()
         self._pending: dict[str, cf.Future] = {}
@@ -170,6 +172,27 @@ class TrainingClient:
     def export_weights(self, name: str) -> cf.Future:
         return self._submit("export", None, name=name)
 
+    def download_plan_report(self, directory) -> cf.Future:
+        """Renders the run's plan report on the service (``index.html``, ``occupancy.html``,
+        ``tasks.csv``, ``transfers.csv``, ``timeline.json/.svg``, ``summary.json``) and unpacks it
+        under ``directory``; the future gives the report's path."""
+        from pathlib import Path
+        from .handles import ArtifactHandle, download_artifact
+        inner = self._submit("plan_report", None)
+
+        def work():
+            import tarfile
+            h = inner.result().outputs
+            handle = ArtifactHandle(h["artifact"], int(h["size"]), h["sha256"])
+            root = Path(directory)
+            root.mkdir(parents=True, exist_ok=True)
+            archive = download_artifact(self.transport, handle, root / "plan_report.tar")
+            with tarfile.open(archive) as tar:
+                tar.extractall(root, filter="data")
+            archive.unlink()
+            return root / "plan_report"
+        return self._downloads.submit(work)
+
     def list_checkpoints(self) -> list[str]:
         return self.transport.request("GET", f"{self.route}/checkpoints")[1]["checkpoints"]
 
@@ -209,6 +232,7 @@ class TrainingClient:
         finally:
             self._closed = True
             self.pool.shutdown(wait=False)
+            self._downloads.shutdown(wait=False)
 
     def __enter__(self):
         return self

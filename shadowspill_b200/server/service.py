@@ -128,6 +128,9 @@ class LiveRun:
         elif op == "restore":
             args["directory"] = self.server.resolve_checkpoint(self.session, args["name"])
             op_worker = "restore"
+        elif op == "plan_report":
+            args["directory"] = str(self.dir / "plan_report")
+            op_worker = op
         else:
             op_worker = op
         t0 = time.perf_counter()
@@ -146,6 +149,9 @@ class LiveRun:
                 out["outputs"] = {"per_microbatch": per}
         if op in ("save", "export"):
             out["outputs"] = {"checkpoint": args.get("name"), "directory": args["directory"]}
+        if op == "plan_report":
+            # index.html, occupancy.html, tasks.csv, transfers.csv, timeline.*: one downloadable archive
+            out["outputs"] = self.server.pack_directory(Path(args["directory"]), "plan_report")
         if op in ("step", "optim_step") and out.get("loss") is not None:
             self.metrics.append({"update": replies[0].get("completed_updates"), "loss": out["loss"],
                                  "execution_seconds": out["execution_seconds"]})
@@ -291,9 +297,12 @@ class Server:
         client can download with byte ranges; returns its handle. The archive is an
         uncompressed TAR with members in sorted order, so the same checkpoint always gives
         the same bytes and digest."""
+        return dict(self.pack_directory(Path(self.resolve_checkpoint(session, name)), name), checkpoint=name)
+
+    def pack_directory(self, directory: Path, name: str) -> dict[str, Any]:
+        """``directory`` as one sealed artifact (deterministic TAR under ``name/``); its handle."""
         import hashlib
         import tarfile
-        directory = Path(self.resolve_checkpoint(session, name))
         store = self.root / "artifacts"
         store.mkdir(exist_ok=True)
         tmp = store / f".pack-{uuid.uuid4().hex}"
@@ -312,7 +321,7 @@ class Server:
         tmp.replace(store / aid)
         size = (store / aid).stat().st_size
         self.artifacts[aid] = {"size": size, "sha256": digest, "complete": True}
-        return {"artifact": aid, "size": size, "sha256": digest, "checkpoint": name}
+        return {"artifact": aid, "size": size, "sha256": digest}
 
     def describe(self, body: dict[str, Any]) -> dict[str, Any]:
         r = resolve_training(body, self.registry, self.hardware)

@@ -142,6 +142,10 @@ def serve(chan: Channel) -> int:
                     started = True
                     path = session.save(args["directory"], args.get("metadata"))
                     out["outputs"] = {"path": str(path)}
+                elif op == "plan_report":
+                    if rank == 0:          # one plan for the whole job: rank 0 renders it
+                        session.write_plan_report(args["directory"])
+                    out["outputs"] = {"path": args["directory"]}
                 elif op == "restore":
                     started = True
                     out["outputs"] = {"metadata": session.restore(args["directory"])}

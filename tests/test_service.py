@@ -83,6 +83,8 @@ def test_train_checkpoint_resume_through_the_public_api(service, tmp_path_factor
         assert len(checkpoint_files(local)) == 1
         weights = export_weights(local)
         assert weights["embed.embed"].shape == (512, 128) and "exp_avg.embed.embed" not in weights
+        report = trainer.download_plan_report(tmp_path_factory.mktemp("report")).result()
+        assert (report / "index.html").exists() and (report / "tasks.csv").exists()
         next_loss = trainer.step(text_batch(_sequences(7))).result().loss
         # local validation never reaches the server
         with pytest.raises(BatchError):
