@@ -172,6 +172,29 @@ class TrainingClient:
     def export_weights(self, name: str) -> cf.Future:
         return self._submit("export", None, name=name)
 
+    def traced_step(self, datums: list[Datum], directory, *, lr: float | None = None) -> cf.Future:
+        """One real training step with the runtime trace on (the run must have been created with
+        ``Execution(runtime_trace=True)``). The future gives ``(TrainingResult, path)`` where
+        ``path/rank<r>/`` holds ``runtime.html``, ``runtime.json`` and the per-task tables of
+        each worker: measured against simulated times, transfers, idle attribution."""
+        from pathlib import Path
+        from .handles import ArtifactHandle, download_artifact
+        inner = self._submit("step", self._pack(datums), lr=lr, runtime_trace=True)
+
+        def work():
+            import tarfile
+            res = inner.result()
+            h = res.outputs["trace"]
+            root = Path(directory)
+            root.mkdir(parents=True, exist_ok=True)
+            archive = download_artifact(self.transport, ArtifactHandle(h["artifact"], int(h["size"]), h["sha256"]),
+                                        root / "trace.tar")
+            with tarfile.open(archive) as tar:
+                tar.extractall(root, filter="data")
+            archive.unlink()
+            return res, root / "trace"
+        return self._downloads.submit(work)
+
     def download_plan_report(self, directory) -> cf.Future:
         """Renders the run's plan report on the service (``index.html``, ``occupancy.html``,
         ``tasks.csv``, ``transfers.csv``, ``timeline.json/.svg``, ``summary.json``) and unpacks it

@@ -131,6 +131,11 @@ class LiveRun:
         elif op == "plan_report":
             args["directory"] = str(self.dir / "plan_report")
             op_worker = op
+        elif op == "step" and args.get("runtime_trace"):
+            if not (self.body.get("execution") or {}).get("runtime_trace"):
+                raise WorkerFailure("a traced step needs Execution(runtime_trace=True) at creation", "not_started")
+            args["trace_directory"] = str(self.dir / f"trace_{req['request_id']}")
+            op_worker = op
         else:
             op_worker = op
         t0 = time.perf_counter()
@@ -149,6 +154,9 @@ class LiveRun:
                 out["outputs"] = {"per_microbatch": per}
         if op in ("save", "export"):
             out["outputs"] = {"checkpoint": args.get("name"), "directory": args["directory"]}
+        if op == "step" and args.get("trace_directory"):
+            out["outputs"] = dict(out.get("outputs") or {},
+                                  trace=self.server.pack_directory(Path(args["trace_directory"]), "trace"))
         if op == "plan_report":
             # index.html, occupancy.html, tasks.csv, transfers.csv, timeline.*: one downloadable archive
             out["outputs"] = self.server.pack_directory(Path(args["directory"]), "plan_report")

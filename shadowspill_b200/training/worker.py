@@ -128,7 +128,11 @@ def serve(chan: Channel) -> int:
                     started = True
                     if window is not None and op != "optim_step":
                         window.before_step()
-                    res = session.run(op, batch, trace=bool(args.get("runtime_trace")))
+                    if op == "step" and args.get("runtime_trace") and args.get("trace_directory"):
+                        # per-task device clocks + the runtime's trace ring -> runtime.html etc.
+                        res, _ = session.traced_step(batch, f"{args['trace_directory']}/rank{rank}")
+                    else:
+                        res = session.run(op, batch)
                     if window is not None and op != "optim_step":
                         window.after_step()
                     out["loss"] = res.loss if op != "optim_step" else None

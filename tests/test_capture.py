@@ -69,12 +69,16 @@ def test_workers_run_under_the_wrapper_and_the_service_reports_it(tmp_path, monk
             Model("llama3-tiny", dtype="float32"), Optimizer(lr=3e-3, parameter_rounding="nearest"),
             batch=BatchConfig(tokens_per_step=512, microbatch_tokens=256),
             memory=Memory(device_gib=0.53, spill_gib=0.25), resources=Resources(gpus=1, backend="cpu"),
-            execution=Execution(nsys={"start_step": 1, "steps": 1}),
+            execution=Execution(nsys={"start_step": 1, "steps": 1}, runtime_trace=True),
             preparation=Preparation(profiling=ProfilingOptions(enabled=False), calibrate=False,
                                     planning=PlanningOptions(minimum_object_bytes_evict_eligible=1024, workers=1)),
             timeout=300).result()
         assert trainer.step(text_batch(seqs)).result().loss > 0
         info = svc.get_nsys(trainer.run).result() if hasattr(trainer, "run") else None
+        # a traced step: the runtime report of the worker comes back with the result
+        res, where = trainer.traced_step(text_batch(seqs), tmp_path / "trace_dl").result()
+        assert res.loss > 0 and (where / "rank0" / "runtime.html").exists()
+        assert (where / "rank0" / "runtime.json").exists()
         trainer.close()
     reports = list((tmp_path / "svc").rglob("worker0.nsys-rep"))
     assert len(reports) == 1
