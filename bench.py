@@ -138,6 +138,9 @@ def main() -> None:
     torch.cuda.set_device(local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # whatever NCCL logs (a version banner with NCCL_DEBUG=VERSION, more with INFO) goes to
+        # stderr: stdout carries the one JSON line and nothing else
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
 
     from shadowspill_b200.training.session import TrainingSession, TrainingSetup
