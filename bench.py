@@ -140,6 +140,9 @@ def main() -> None:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         # whatever NCCL logs (a version banner with NCCL_DEBUG=VERSION, more with INFO) goes to
         # stderr: stdout carries the one JSON line and nothing else
+        # (NCCL honours NCCL_DEBUG_FILE only above the VERSION level, so VERSION becomes WARN)
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
 
