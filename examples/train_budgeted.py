@@ -3,6 +3,7 @@
     python examples/train_budgeted.py                 # tiny model on CPU (mock device backend)
     python examples/train_budgeted.py --device cuda --model llama3-1b --device-gib 8 --spill-gib 32 \
         --tokens 32768 --microbatch 8192
+    python examples/train_budgeted.py --spill-pool file --spill-dir /tmp     # spill to a direct-I/O file
 """
 import argparse
 import sys
@@ -25,12 +26,16 @@ def main(argv=None) -> float:
     ap.add_argument("--microbatch", type=int, default=256)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--out", default="")
+    ap.add_argument("--spill-pool", default="host", choices=["host", "file", "remote"])
+    ap.add_argument("--spill-dir", default="", help="directory of the file spill pool")
+    ap.add_argument("--spill-address", default="", help="host:port of an ss_memory_daemon")
     a = ap.parse_args(argv)
     cpu = a.device == "cpu"
     setup = TrainingSetup(model=a.model, device_gib=a.device_gib, spill_gib=a.spill_gib,
                           tokens_per_step=a.tokens, microbatch_tokens=a.microbatch, lr=3e-3,
                           device=a.device, dtype="float32" if cpu else "bfloat16",
                           profile=not cpu, calibrate=not cpu, trace_capacity=1 << 14,
+                          spill_pool=a.spill_pool, spill_directory=a.spill_dir, spill_address=a.spill_address,
                           search=SearchOptions(minimum_object_bytes_evict_eligible=1024, workers=2))
     session = TrainingSession(setup, log=print)
     s = session.plan.summary

@@ -18,6 +18,12 @@ def test_train_budgeted_example(tmp_path):
     assert (tmp_path / "index.html").exists() and (tmp_path / "runtime.html").exists()
 
 
+def test_train_budgeted_example_with_a_file_spill_pool(tmp_path):
+    plain = _load("train_budgeted").main(["--steps", "2"])
+    filed = _load("train_budgeted").main(["--steps", "2", "--spill-pool", "file", "--spill-dir", str(tmp_path)])
+    assert filed == plain
+
+
 def test_service_quickstart_example():
     losses = _load("service_quickstart").main()
     assert len(losses) == 4 and losses[-1] < losses[0]
