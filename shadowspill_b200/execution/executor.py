@@ -39,6 +39,10 @@ class Hyperparameters:
     eps: float = 1e-8
     weight_decay: float = 0.0
     grad_scale: float = 1.0
+    # "adamw" runs the fused kernels (bf16 state with stochastic rounding, fused with the gradient
+    # reduce-scatter under data parallelism); "sgd" (momentum beta1) and "lion" run as plain
+    # tensor operations with round-to-nearest stores
+    rule: str = "adamw"
 
 
 @dataclass
@@ -208,6 +212,18 @@ class TaskRunner:
         for p in st.params:
             if not p.trainable:
                 continue
+            if h.rule != "adamw":
+                from ..ops import reference
+                hyper = dict(lr=h.lr, beta1=h.beta1, beta2=h.beta2, eps=h.eps, weight_decay=h.weight_decay,
+                             step=self.completed_updates + 1, grad_scale=h.grad_scale)
+                if p.expert_sharded:
+                    reference.update_rule_(h.rule, B["params"][p.name][:p.numel], B["grads"][p.name].view(-1),
+                                           B["m"][p.name][:p.numel], B["v"][p.name][:p.numel], **hyper)
+                else:
+                    coll.reduce_scatter_update(h.rule, B["grads"][p.name].view(-1), B["params"][p.name],
+                                               B["m"][p.name], B["v"][p.name],
+                                               whole=st.kept_whole(p, self.desc.dtype), **hyper)
+                continue
             if p.expert_sharded:
                 # the local bank's gradient is already the sum over every rank's tokens
                 # (expert parallelism routes all of them here): a plain local update
@@ -230,6 +246,13 @@ class TaskRunner:
         st, h = self.stages[stage], self.hyper
         for p in st.params:
             if not p.trainable:
+                continue
+            if h.rule != "adamw":
+                from ..ops import reference
+                reference.update_rule_(h.rule, B["params"][p.name].view(-1), B["grads"][p.name].view(-1),
+                                       B["m"][p.name].view(-1), B["v"][p.name].view(-1), lr=h.lr,
+                                       beta1=h.beta1, beta2=h.beta2, eps=h.eps, weight_decay=h.weight_decay,
+                                       step=self.completed_updates + 1, grad_scale=h.grad_scale)
                 continue
             F.adamw_(B["params"][p.name].view(-1), B["grads"][p.name].view(-1),
                      B["m"][p.name].view(-1), B["v"][p.name].view(-1), lr=h.lr, beta1=h.beta1,

@@ -20,8 +20,9 @@ class ResidentTrainer:
                  dtype: torch.dtype = torch.bfloat16, seed: int = 0,
                  grad_dtype: torch.dtype | None = None, lr: float = 1e-3, beta1: float = 0.9,
                  beta2: float = 0.95, eps: float = 1e-8, weight_decay: float = 0.0,
-                 stochastic_rounding: bool = True, objective=None, lora=None):
+                 stochastic_rounding: bool = True, objective=None, lora=None, rule: str = "adamw"):
         self.cfg = cfg
+        self.rule = rule
         self.device = torch.device(device)
         self.dtype = dtype
         self.grad_dtype = grad_dtype or dtype
@@ -87,6 +88,13 @@ class ResidentTrainer:
                     offset += (p.numel + 7) // 8 * 8
                     continue
                 pt, gt = self.P[si][p.name], self.G[si][p.name]
+                if self.rule != "adamw":
+                    from ..ops import reference
+                    reference.update_rule_(self.rule, pt.view(-1), gt.view(-1), self.M[si][p.name].view(-1),
+                                           self.V[si][p.name].view(-1), step=self.step_count,
+                                           grad_scale=grad_scale, **self.hyper)
+                    offset += (p.numel + 7) // 8 * 8
+                    continue
                 F.adamw_(pt.view(-1), gt.view(-1), self.M[si][p.name].view(-1),
                          self.V[si][p.name].view(-1), step=self.step_count,
                          grad_scale=grad_scale, seed=self.seed, offset=offset,

@@ -150,6 +150,34 @@ def adamw_(p, g, m, v, *, lr, beta1, beta2, eps, weight_decay, step, grad_scale=
     p.copy_(pf.to(p.dtype)); m.copy_(mf.to(m.dtype)); v.copy_(vf.to(v.dtype))
 
 
+RULES = ("adamw", "sgd", "lion")
+
+
+def update_rule_(rule, p, g, m, v, *, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0):
+    """The update rules other than AdamW, in fp32 math with round-to-nearest stores, on tensors of
+    any dtype and device (plain tensor operations: these are not hot paths).
+
+    ``sgd``: momentum ``m <- beta1 m + g``, ``p <- p - lr (m + wd p)`` (``torch.optim.SGD`` with
+    momentum ``beta1``, no dampening; the decay is added to the step, not to the gradient).
+    ``lion``: ``u = sign(beta1 m + (1 - beta1) g)``, ``p <- p - lr (u + wd p)``,
+    ``m <- beta2 m + (1 - beta2) g`` (Chen et al. 2023). ``v`` is not used by either."""
+    if rule == "adamw":
+        return adamw_(p, g, m, v, lr=lr, beta1=beta1, beta2=beta2, eps=eps, weight_decay=weight_decay,
+                      step=step, grad_scale=grad_scale)
+    gf = g.float() * grad_scale
+    pf, mf = p.float(), m.float()
+    if rule == "sgd":
+        mf = beta1 * mf + gf
+        pf = pf - lr * (mf + weight_decay * pf)
+    elif rule == "lion":
+        u = torch.sign(beta1 * mf + (1 - beta1) * gf)
+        pf = pf - lr * (u + weight_decay * pf)
+        mf = beta2 * mf + (1 - beta2) * gf
+    else:
+        raise ValueError(f"unknown update rule {rule!r}; known: {RULES}")
+    p.copy_(pf.to(p.dtype)); m.copy_(mf.to(m.dtype))
+
+
 def attention_varlen(q, k, v, cu_seqlens, scale=None):
     """Packed causal GQA: q [T,Hq,dh], k/v [T,Hkv,dh]; each [cu[i],cu[i+1]) is its
     own causal sequence. Returns (out [T,Hq,dh], lse fp32 [Hq,T])."""

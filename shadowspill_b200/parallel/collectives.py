@@ -84,6 +84,26 @@ class DistCollectives:
             if lo < n:
                 flat[lo:min(n, lo + per)].copy_(part[:min(n, lo + per) - lo])
 
+    def reduce_scatter_update(self, rule: str, grad: torch.Tensor, p, m, v, *, whole: bool = False,
+                              **hyper) -> None:
+        """The unfused form for update rules other than AdamW: sum ``grad`` over every rank with
+        the library all-reduce (on a copy: this rank's gradient buffer stays as peers expect it),
+        then apply ``rule`` to the slice of (p, m, v) this rank owns."""
+        from ..ops import reference
+        n, per = grad.numel(), p.numel()
+        g = grad.view(-1).clone()
+        if dist.is_initialized() and dist.get_world_size(self.group) > 1:
+            dist.all_reduce(g, group=self.group)
+        lo = 0 if whole else self._owned_rank() * per
+        hi = min(n, lo + per)
+        if hi <= lo:
+            return
+        cnt = hi - lo
+        reference.update_rule_(rule, p.view(-1)[:cnt], g[lo:hi], m.view(-1)[:cnt], v.view(-1)[:cnt], **hyper)
+
+    def _owned_rank(self) -> int:
+        return self.rank
+
     def reduce_scatter_adamw(self, grad: torch.Tensor, p, m, v, *, offset: int, whole: bool = False,
                              **adam) -> None:
         """Sum ``grad`` over ranks; update this rank's owned slice of (p, m, v). ``whole``: the
@@ -161,6 +181,26 @@ class PeerCollectives:
             peers, full.data_ptr(), shard.numel() * shard.element_size(),
             full.numel() * full.element_size(), self.shard_rank, self.shard_world, _lib.stream_ptr()),
             "ss_peer_allgather")
+
+    def reduce_scatter_update(self, rule: str, grad: torch.Tensor, p, m, v, *, whole: bool = False,
+                              **hyper) -> None:
+        """The unfused form for update rules other than AdamW: sum ``grad`` over every rank with
+        the library all-reduce (on a copy: this rank's gradient buffer stays as peers expect it),
+        then apply ``rule`` to the slice of (p, m, v) this rank owns."""
+        from ..ops import reference
+        n, per = grad.numel(), p.numel()
+        g = grad.view(-1).clone()
+        if dist.is_initialized() and dist.get_world_size(self.group) > 1:
+            dist.all_reduce(g, group=self.group)
+        lo = 0 if whole else self._owned_rank() * per
+        hi = min(n, lo + per)
+        if hi <= lo:
+            return
+        cnt = hi - lo
+        reference.update_rule_(rule, p.view(-1)[:cnt], g[lo:hi], m.view(-1)[:cnt], v.view(-1)[:cnt], **hyper)
+
+    def _owned_rank(self) -> int:
+        return self.shard_rank
 
     def reduce_scatter_adamw(self, grad: torch.Tensor, p, m, v, *, offset: int, lr, beta1, beta2,
                              eps, weight_decay, step, grad_scale, seed, stochastic_param,

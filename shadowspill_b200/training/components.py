@@ -98,6 +98,8 @@ def default_registry() -> Registry:
     r.add_objective("shadowspill/sum@1", lambda terms=(): {"kind": "sum", "terms": list(terms)})
     r.add_optimizer("adamw@1", lambda **kw: {"kind": "adamw", **kw})
     r.add_optimizer("mlops/adamw@1", lambda **kw: {"kind": "adamw", **kw})    # the reference's id
+    r.add_optimizer("sgd@1", lambda **kw: {"kind": "sgd", **kw})              # momentum = beta1
+    r.add_optimizer("lion@1", lambda **kw: {"kind": "lion", **kw})
     r.add_preparation("shadowspill/default@1", lambda **kw: kw)
     r.add_policy("shadowspill/text_chunks@1", lambda projection=0, moe=0: {"projection": projection, "moe": moe})
     r.add_policy("shadowspill/text_retention@1", lambda rule="cost-input": {"rule": rule})
@@ -230,6 +232,7 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
             "tokens_per_step": tokens, "microbatch_tokens": T, "slots": slots,
             "lr": opt.get("lr", 1e-4), "beta1": opt.get("beta1", 0.9), "beta2": opt.get("beta2", 0.95),
             "eps": opt.get("eps", 1e-8), "weight_decay": opt.get("weight_decay", 0.0),
+            "optimizer_rule": registry.get("optimizer", opt["id"]).create()["kind"],
             "seed": int(m.get("weights", {}).get("seed", ex.get("seed", 0))),
             "dtype": m.get("dtype", "bfloat16"), "stochastic_rounding": sr, "device": device,
             "device_index": rank if device == "cuda" else 0, "rank": rank, "world_size": workers,

@@ -48,6 +48,7 @@ class TrainingSetup:
     beta2: float = 0.95
     eps: float = 1e-8
     weight_decay: float = 0.0
+    optimizer_rule: str = "adamw"         # adamw | sgd (momentum beta1) | lion
     seed: int = 0
     dtype: str = "bfloat16"
     stochastic_rounding: bool = True
@@ -350,7 +351,11 @@ class TrainingSession:
             cap = max([self.plan.summary.workspace_bytes] +
                       [p.summary.workspace_bytes for p, _ in self.extra_plans.values()]) + (256 << 20)
             torch.cuda.set_per_process_memory_fraction(min(1.0, cap / total), setup.device_index)
-        hyper = Hyperparameters(setup.lr, setup.beta1, setup.beta2, setup.eps, setup.weight_decay)
+        from ..ops.reference import RULES
+        if setup.optimizer_rule not in RULES:
+            raise ValueError(f"unknown optimizer rule {setup.optimizer_rule!r}; known: {RULES}")
+        hyper = Hyperparameters(setup.lr, setup.beta1, setup.beta2, setup.eps, setup.weight_decay,
+                                rule=setup.optimizer_rule)
         self.executor = Executor(self.plan, self.desc, device=setup.device,
                                  device_index=setup.device_index, seed=setup.seed, hyper=hyper,
                                  stochastic_rounding=setup.stochastic_rounding,

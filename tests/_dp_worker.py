@@ -26,6 +26,9 @@ def main():
     pretrained = arm.startswith("pretrained-")   # start from whole-parameter weights of another seed
     if pretrained:
         arm = arm.split("-", 1)[1]
+    rule = "adamw"
+    if arm.startswith("lion-"):           # the unfused update path: all-reduce, then the rule
+        rule, arm = "lion", arm.split("-", 1)[1]
     # "small-<arm>": tensors under 64 KiB stay whole on every rank (the norm vectors and, in the
     # tiny model, the attention projections), everything larger is cut into shards
     min_shard = 0
@@ -59,10 +62,10 @@ def main():
                                       deterministic=True))
     lr = 3e-4 if cuda else 3e-3
     ex = Executor(plan, desc, device=device, device_index=rank if cuda else 0, seed=5,
-                  hyper=Hyperparameters(lr=lr), stochastic_rounding=False, collectives=arm)
+                  hyper=Hyperparameters(lr=lr, rule=rule), stochastic_rounding=False, collectives=arm)
     ex.initialize(on_device=False)
     ref = ResidentTrainer(cfg, device=f"cuda:{rank}" if cuda else "cpu", dtype=dtype,
-                          seed=9 if pretrained else 5, lr=lr, stochastic_rounding=False)
+                          seed=9 if pretrained else 5, lr=lr, stochastic_rounding=False, rule=rule)
     if pretrained:
         # every rank keeps its slice of each whole tensor; moments stay at zero on both sides
         whole = {k: v.cpu() for k, v in ref.state_dict().items() if not k.startswith("exp_avg")}

@@ -29,6 +29,12 @@ def test_small_tensors_stay_whole_under_sharded_storage():
     _launch(2, "cpu", "small-dist", 29641)
 
 
+def test_lion_update_under_sharded_storage():
+    """An update rule other than AdamW: gradients are summed with the library all-reduce and the
+    rule is applied to the owned slices (small tensors whole); matches the single-process model."""
+    _launch(2, "cpu", "lion-small-dist", 29651)
+
+
 def test_whole_parameter_weights_load_into_sharded_ranks():
     """Weights of another seed given as whole tensors: every rank keeps its slice, and the
     sharded job then trains exactly like a single-process model started from those weights."""
@@ -43,7 +49,7 @@ def test_two_replicas_of_two_shards_gloo_match_resident():
 
 @pytest.mark.gpu
 @pytest.mark.multigpu
-@pytest.mark.parametrize("arm", ["peer", "dist", "small-peer"])
+@pytest.mark.parametrize("arm", ["peer", "dist", "small-peer", "lion-peer"])
 def test_two_gpus_match_resident(arm):
     _launch(2, "cuda", arm, 29613 if arm == "peer" else 29615)
 

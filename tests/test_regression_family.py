@@ -111,3 +111,54 @@ def test_regression_through_the_service(tmp_path):
         with pytest.raises(BatchError):          # a row of the wrong width
             trainer.step([tensor_datum({"value": np.zeros(4), "target_values": np.zeros(8)})])
         trainer.close()
+
+
+@pytest.mark.parametrize("rule", ["sgd", "lion"])
+def test_other_update_rules_match_their_textbook_forms(rule):
+    """``sgd`` against ``torch.optim.SGD(momentum)``; ``lion`` against the published update."""
+    cfg = preset("regression")
+    geo = BatchGeometry(ROWS, MBS, slots=ROWS + 1, mean_seqlen=1)
+    prog, desc = build_step(cfg, geo, StepDataOrdering(), dtype=torch.float32)
+    total = sum(o.bytes for o in prog.objects)
+    ws = max(t.workspace_bytes for t in prog.tasks)
+    plan = plan_program(prog, MemoryBudgets(ws + total, 16 << 20, headroom_bytes=0), CommunicationInfo(),
+                        SearchOptions(minimum_object_bytes_evict_eligible=64, workers=1))
+    lr, b1, b2, wd = 2e-2, 0.9, 0.99, 0.01
+    ex = Executor(plan, desc, device="cpu", seed=5, stochastic_rounding=False,
+                  hyper=Hyperparameters(lr=lr, beta1=b1, beta2=b2, weight_decay=wd, rule=rule))
+    ex.initialize()
+    state = ex.state_dict()
+    ref = reference_module(cfg)
+    with torch.no_grad():
+        ref[0].weight.copy_(state["input.w1"]); ref[0].bias.copy_(state["input.b1"])
+        ref[2].weight.copy_(state["head.w2"]); ref[2].bias.copy_(state["head.b2"])
+    params = list(ref.parameters())
+    opt = torch.optim.SGD(params, lr=lr, momentum=b1) if rule == "sgd" else None
+    moment = [torch.zeros_like(p) for p in params]
+    for step in range(4):
+        mbs = _microbatches(step)
+        got = ex.run(mbs).loss
+        for p in params:
+            p.grad = None
+        want = 0.0
+        for mb in mbs:
+            pred = ref(torch.from_numpy(mb.extras["value"]))
+            loss = ((pred - torch.from_numpy(mb.extras["target_values"])).square().sum(1)
+                    * torch.from_numpy(mb.weights)).sum()
+            loss.backward()
+            want += float(loss.detach())
+        with torch.no_grad():
+            if rule == "sgd":
+                for p in params:
+                    p.mul_(1 - lr * wd)          # decay on the weights, not folded into the gradient
+                opt.step()
+            else:
+                for p, m in zip(params, moment):
+                    u = torch.sign(b1 * m + (1 - b1) * p.grad)
+                    p.sub_(lr * (u + wd * p))
+                    m.mul_(b2).add_((1 - b2) * p.grad)
+        assert got == pytest.approx(want, rel=2e-5), (rule, step)
+    mine = ex.state_dict()
+    for name, t in (("input.w1", ref[0].weight), ("head.b2", ref[2].bias)):
+        assert torch.allclose(mine[name], t.detach(), rtol=2e-4, atol=2e-6), (rule, name)
+    ex.close()
