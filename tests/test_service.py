@@ -288,3 +288,24 @@ def test_pretrained_weights_arrive_as_an_uploaded_artifact(service, tmp_path):
         got = trainer.forward(batch).result().loss
         trainer.close()
     assert abs(got - want) < 1e-5 * max(1.0, abs(want))
+
+
+def test_other_optimizer_components_through_the_service(service):
+    with ServiceClient(service.url, token="secret") as svc:
+        assert {"adamw@1", "sgd@1", "lion@1"} <= {c["id"] for c in svc.list_components("optimizer").result()}
+        trainer = svc.create_training_client(
+            Model("llama3-tiny", dtype="float32"),
+            Optimizer(id="lion@1", lr=3e-4, beta1=0.9, beta2=0.99, parameter_rounding="nearest"),
+            batch=BatchConfig(tokens_per_step=512, microbatch_tokens=256),
+            memory=Memory(device_gib=0.53, spill_gib=0.25), resources=Resources(gpus=1, backend="cpu"),
+            preparation=Preparation(profiling=ProfilingOptions(enabled=False), calibrate=False,
+                                    planning=PlanningOptions(minimum_object_bytes_evict_eligible=1024,
+                                                             workers=1)),
+            timeout=300).result()
+        losses = [trainer.step(text_batch(_sequences(0))).result().loss for _ in range(5)]
+        assert losses[-1] < losses[0]
+        trainer.close()
+        with pytest.raises(Exception) as e:
+            svc.describe_training(model=Model("llama3-tiny"), optimizer=Optimizer(id="adagrad@1"),
+                                  resources=Resources(backend="cpu")).result()
+        assert "adagrad@1" in str(e.value)
