@@ -119,6 +119,9 @@ class TrainingDescription:
     replicas: int = 1
     # sharded storage keeps tensors smaller than this whole on every rank (0 = cut everything)
     min_shard_bytes: int = 0
+    # rows of the output projection evaluated at once (the head never materialises all logits);
+    # 0 = the stage's default. Fewer rows = less workspace, more launches.
+    head_block_rows: int = 0
 
     def __post_init__(self) -> None:
         extras = extra_fields_for(self.cfg, self.objective)
@@ -139,6 +142,8 @@ class TrainingDescription:
         stages = build_stages(self.cfg, self.objective, self.lora, ep)
         for st in stages:
             st.min_shard_bytes = int(self.min_shard_bytes)
+        if self.head_block_rows > 0 and hasattr(stages[-1], "block_rows"):
+            stages[-1].block_rows = int(self.head_block_rows)
         return stages
 
     def variant(self, stage_index: int) -> str:
@@ -391,42 +396,44 @@ def build_step(cfg: DecoderConfig, geometry: BatchGeometry,
                ordering: StepDataOrdering | None = None, *, dtype=torch.bfloat16,
                grad_dtype=None, selection: dict[int, str] | None = None, world_size: int = 1,
                rank: int = 0, objective=None, lora=None, expert_parallel: bool = False,
-               replicas: int = 1, min_shard_bytes: int = 0):
+               replicas: int = 1, min_shard_bytes: int = 0, head_block_rows: int = 0):
     """Forward + backward + optimizer of one global batch. Returns ``(Program, description)``.
     ``world_size > 1`` builds the data-parallel form: weights and AdamW moments are
     stored as 1/N shards, gathered before use and updated shard-locally."""
     desc = TrainingDescription(cfg, geometry, ordering or StepDataOrdering(), dtype,
                                grad_dtype or dtype, dict(selection or {}), "step", world_size,
-                               rank, objective, lora, expert_parallel, replicas, min_shard_bytes)
+                               rank, objective, lora, expert_parallel, replicas, min_shard_bytes,
+                               head_block_rows)
     return _build(desc), desc
 
 
 def build_forward_backward(cfg, geometry, ordering=None, *, dtype=torch.bfloat16, grad_dtype=None,
                            selection=None, world_size=1, rank=0, objective=None, lora=None,
-                           min_shard_bytes=0):
+                           min_shard_bytes=0, head_block_rows=0):
     """Gradient accumulation without the update (gradients are persistent state)."""
     desc = TrainingDescription(cfg, geometry, ordering or StepDataOrdering(), dtype,
                                grad_dtype or dtype, dict(selection or {}), "forward_backward",
-                               world_size, rank, objective, lora, min_shard_bytes=min_shard_bytes)
+                               world_size, rank, objective, lora, min_shard_bytes=min_shard_bytes,
+                               head_block_rows=head_block_rows)
     return _build(desc), desc
 
 
 def build_forward(cfg, geometry, ordering=None, *, dtype=torch.bfloat16, world_size=1, rank=0,
-                  objective=None, lora=None, min_shard_bytes=0):
+                  objective=None, lora=None, min_shard_bytes=0, head_block_rows=0):
     """Evaluation: forward passes and the loss only."""
     desc = TrainingDescription(cfg, geometry, ordering or StepDataOrdering(), dtype, dtype, {},
                                "forward", world_size, rank, objective, lora,
-                               min_shard_bytes=min_shard_bytes)
+                               min_shard_bytes=min_shard_bytes, head_block_rows=head_block_rows)
     return _build(desc), desc
 
 
 def build_optimizer(cfg, geometry, *, dtype=torch.bfloat16, grad_dtype=None, world_size=1, rank=0,
-                    objective=None, lora=None, min_shard_bytes=0):
+                    objective=None, lora=None, min_shard_bytes=0, head_block_rows=0):
     """The optimizer update alone, over gradients that earlier ``forward_backward``
     invocations left in the spill pool (the ``optim_step`` operation)."""
     desc = TrainingDescription(cfg, geometry, StepDataOrdering(), dtype, grad_dtype or dtype, {},
                                "optimizer", world_size, rank, objective, lora,
-                               min_shard_bytes=min_shard_bytes)
+                               min_shard_bytes=min_shard_bytes, head_block_rows=head_block_rows)
     return _build(desc), desc
 
 

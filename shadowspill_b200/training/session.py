@@ -78,6 +78,7 @@ class TrainingSetup:
     expert_parallel: bool = False        # routed layers keep 1/world of the experts per rank
     ranks_per_replica: int = 0           # 0 = one replica; else state is sharded inside groups of this size
     min_shard_bytes: int = 0             # sharded storage keeps smaller tensors whole on every rank
+    head_chunks: int = 0                 # evaluate the output projection in this many row chunks (0 = default)
     pretrained: str = ""                 # directory of Hugging Face safetensors to start from
     # content-addressed store of task profiles shared between runs ("" = none)
     store: str = ""
@@ -151,6 +152,8 @@ class TrainingSession:
         if replicas > 1 and shard_world < 2:
             raise ValueError("replicas repeat a shard group of at least two ranks")
 
+        head_rows = -(-setup.microbatch_tokens // setup.head_chunks) if setup.head_chunks > 0 else 0
+
         def with_replicas(built):
             built[1].replicas = replicas          # programs depend on the shard count only
             return built
@@ -161,11 +164,12 @@ class TrainingSession:
             return with_replicas(build_step(self.cfg, self.geometry, order, dtype=self.dtype,
                                             selection=sel, world_size=shard_world, rank=rank,
                                             expert_parallel=setup.expert_parallel,
-                                            min_shard_bytes=setup.min_shard_bytes, **choices))
+                                            min_shard_bytes=setup.min_shard_bytes,
+                                            head_block_rows=head_rows, **choices))
 
         def build_extra(op: str):
             kw = dict(dtype=self.dtype, world_size=shard_world, rank=rank,
-                      min_shard_bytes=setup.min_shard_bytes, **choices)
+                      min_shard_bytes=setup.min_shard_bytes, head_block_rows=head_rows, **choices)
             if op == "forward_backward":
                 return with_replicas(build_forward_backward(self.cfg, self.geometry, StepDataOrdering(), **kw))
             if op == "optim_step":

@@ -1,4 +1,5 @@
 """Planned execution on the mock backend must reproduce the resident trainer."""
+import pytest
 import torch
 
 from shadowspill_b200.communication.info import CommunicationInfo
@@ -164,3 +165,21 @@ def test_traced_step_diagnostics_and_runtime_report(tmp_path):
     assert (tmp_path / "runtime_tasks.csv").read_text().count("\n") == len(plan.program.tasks) + 1
     assert (tmp_path / "runtime.json").exists() and (tmp_path / "runtime_transfers.csv").exists()
     ex.close()
+
+
+def test_head_row_chunks_change_workspace_not_results():
+    """The output projection evaluated in smaller row blocks: less task workspace, same numbers."""
+    cfg = preset("llama3-tiny")
+    geo = BatchGeometry(microbatch_tokens=256, n_microbatches=2, slots=16, mean_seqlen=64)
+    losses, work = [], []
+    for rows in (0, 64):
+        prog, desc = build_step(cfg, geo, StepDataOrdering(), dtype=torch.float32, head_block_rows=rows)
+        work.append(max(t.workspace_bytes for t in prog.tasks if t.kind == "head"))
+        plan = plan_program(prog, MemoryBudgets(32 << 20, 64 << 20, headroom_bytes=0), CommunicationInfo(),
+                            SearchOptions(minimum_object_bytes_evict_eligible=1024, workers=1))
+        ex = Executor(plan, desc, device="cpu", seed=1)
+        ex.initialize()
+        losses.append([ex.run(_batches(cfg, s)).loss for s in range(2)])
+        ex.close()
+    assert work[1] < work[0]
+    assert losses[1] == pytest.approx(losses[0], rel=1e-6)
