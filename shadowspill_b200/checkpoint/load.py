@@ -79,7 +79,7 @@ def export_weights(directory: str | Path) -> dict[str, torch.Tensor]:
     out: dict[str, torch.Tensor] = {}
     for path in checkpoint_files(directory):
         for entry, data in iter_members(path):
-            if entry["name"].startswith("exp_avg"):
+            if entry["name"].startswith(("exp_avg", "master.")):
                 continue
             dt = _TORCH[entry["dtype"]]
             full = out.get(entry["name"])

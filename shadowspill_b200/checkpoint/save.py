@@ -31,11 +31,14 @@ def state_entries(executor) -> list[dict[str, Any]]:
     world, rank = executor.world, executor.rank
     out = []
     for si, st in enumerate(executor.stages):
-        for kind, prefix in (("weights", ""), ("exp_avg", "exp_avg."), ("exp_avg_sq", "exp_avg_sq.")):
+        for kind, prefix in (("weights", ""), ("exp_avg", "exp_avg."), ("exp_avg_sq", "exp_avg_sq."),
+                             ("master", "master.")):
             if f"{st.name}.{kind}" not in executor._obj:
                 continue
             for p in st.params:
-                dt = p.dtype or executor.desc.dtype
+                if kind != "weights" and not p.trainable:
+                    continue          # frozen parameters own no moments and no master copy
+                dt = p.dtype or (torch.float32 if kind == "master" else executor.desc.dtype)
                 numel, shape = p.numel, p.shape
                 if p.expert_sharded:
                     # this rank's experts are rows [expert_lo, expert_lo + local) of the whole bank

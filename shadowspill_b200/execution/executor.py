@@ -122,6 +122,11 @@ class TaskRunner:
                     out[u.role] = st.shard_views(flat, self.desc.dtype, self.world, only)
                 else:
                     out[u.role] = st.views(flat, self.desc.dtype, trainable_only=only)
+            elif u.role == "master":
+                if obj.sharding == "sharded":
+                    out[u.role] = st.shard_views(flat, torch.float32, self.world, True)
+                else:
+                    out[u.role] = st.views(flat, torch.float32, trainable_only=True)
             elif u.role == "grads":
                 out[u.role] = st.views(flat, self.desc.grad_dtype, torch.float32, True)
             elif u.role in ("x", "y", "dx"):
@@ -212,17 +217,22 @@ class TaskRunner:
         for p in st.params:
             if not p.trainable:
                 continue
-            if h.rule != "adamw":
+            if h.rule != "adamw" or "master" in B:
                 from ..ops import reference
                 hyper = dict(lr=h.lr, beta1=h.beta1, beta2=h.beta2, eps=h.eps, weight_decay=h.weight_decay,
                              step=self.completed_updates + 1, grad_scale=h.grad_scale)
+                # with master copies the rule runs on the fp32 shard, which is then rounded into
+                # the model-dtype shard (both laid out alike)
+                target = B["master"][p.name] if "master" in B else B["params"][p.name]
                 if p.expert_sharded:
-                    reference.update_rule_(h.rule, B["params"][p.name][:p.numel], B["grads"][p.name].view(-1),
+                    reference.update_rule_(h.rule, target[:p.numel], B["grads"][p.name].view(-1),
                                            B["m"][p.name][:p.numel], B["v"][p.name][:p.numel], **hyper)
                 else:
-                    coll.reduce_scatter_update(h.rule, B["grads"][p.name].view(-1), B["params"][p.name],
+                    coll.reduce_scatter_update(h.rule, B["grads"][p.name].view(-1), target,
                                                B["m"][p.name], B["v"][p.name],
                                                whole=st.kept_whole(p, self.desc.dtype), **hyper)
+                if "master" in B:
+                    B["params"][p.name].copy_(target)
                 continue
             if p.expert_sharded:
                 # the local bank's gradient is already the sum over every rank's tokens
@@ -246,6 +256,16 @@ class TaskRunner:
         st, h = self.stages[stage], self.hyper
         for p in st.params:
             if not p.trainable:
+                continue
+            if "master" in B:
+                # fp32 master copy: update it (unfused), then round it into the model-dtype weights
+                from ..ops import reference
+                master = B["master"][p.name].view(-1)
+                reference.update_rule_(h.rule, master, B["grads"][p.name].view(-1),
+                                       B["m"][p.name].view(-1), B["v"][p.name].view(-1), lr=h.lr,
+                                       beta1=h.beta1, beta2=h.beta2, eps=h.eps, weight_decay=h.weight_decay,
+                                       step=self.completed_updates + 1, grad_scale=h.grad_scale)
+                B["params"][p.name].view(-1).copy_(master)
                 continue
             if h.rule != "adamw":
                 from ..ops import reference
@@ -496,25 +516,44 @@ class Executor:
                 name = f"{st.name}.{suffix}"
                 if name in self._obj and self.plan.home_pool(self._obj[name]):
                     self.spill_view(self._obj[name]).zero_()
+            self._sync_master(st)
             if self._mirrors:
                 self.flush_homes()      # file-homed state: one stage in host memory at a time
         self.runner.completed_updates = 0
         self.runner.accumulated = 0
 
+    def _sync_master(self, st) -> None:
+        """fp32 master copy of a stage := its current weights (after initialisation or a load)."""
+        name = f"{st.name}.master"
+        if name not in self._obj:
+            return
+        w = self.spill_view(self._obj[f"{st.name}.weights"], False)
+        mflat = self.spill_view(self._obj[name])
+        if self.world > 1:
+            src = st.shard_views(w, self.desc.dtype, self.world)
+            dst = st.shard_views(mflat, torch.float32, self.world, True)
+        else:
+            src = st.views(w, self.desc.dtype)
+            dst = st.views(mflat, torch.float32, trainable_only=True)
+        for k, d in dst.items():
+            d.copy_(src[k].reshape(d.shape))
+
     def named_tensors(self, writable: bool = True):
         """Yields ``(name, tensor view in the spill pool)`` for every persistent
         model tensor: parameters, then ``exp_avg.*`` / ``exp_avg_sq.*``."""
         for si, st in enumerate(self.stages):
-            for kind, prefix in (("weights", ""), ("exp_avg", "exp_avg."), ("exp_avg_sq", "exp_avg_sq.")):
+            for kind, prefix in (("weights", ""), ("exp_avg", "exp_avg."), ("exp_avg_sq", "exp_avg_sq."),
+                                 ("master", "master.")):
                 name = f"{st.name}.{kind}"
                 if name not in self._obj:
                     continue
                 flat = self.spill_view(self._obj[name], writable)
-                only = kind != "weights"      # moments exist for trainable parameters only
+                only = kind != "weights"      # moments and masters exist for trainable parameters only
+                dt = torch.float32 if kind == "master" else self.desc.dtype
                 if self.world > 1:
-                    views = st.shard_views(flat, self.desc.dtype, self.world, only)
+                    views = st.shard_views(flat, dt, self.world, only)
                 else:
-                    views = st.views(flat, self.desc.dtype, trainable_only=only)
+                    views = st.views(flat, dt, trainable_only=only)
                 for p in st.params:
                     if p.name in views:
                         yield f"{prefix}{st.name}.{p.name}", views[p.name]
@@ -533,6 +572,9 @@ class Executor:
         extra = set(state) - seen
         if strict and extra:
             raise KeyError(f"unexpected tensors {sorted(extra)[:4]}")
+        if not any(k.startswith("master.") for k in state):
+            for st in self.stages:          # weights came without masters: derive them
+                self._sync_master(st)
 
     def load_full_state_dict(self, state: dict[str, torch.Tensor], strict: bool = True) -> None:
         """Loads WHOLE parameters (``{"<stage>.<param>": tensor}``, for example a converted
@@ -575,6 +617,7 @@ class Executor:
                 dst.zero_()
                 if hi > lo:
                     dst[:hi - lo].copy_(flat[lo:hi].to(dst.dtype))
+            self._sync_master(st)
 
     # ------------------------------------------------------------------ inputs
     def stage_inputs(self, batch: list[HostMicrobatch]) -> int:

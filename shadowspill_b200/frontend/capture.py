@@ -122,6 +122,9 @@ class TrainingDescription:
     # rows of the output projection evaluated at once (the head never materialises all logits);
     # 0 = the stage's default. Fewer rows = less workspace, more launches.
     head_block_rows: int = 0
+    # fp32 master copies of the trainable parameters: the optimizer updates them and rounds the
+    # result into the model-dtype weights (unfused update path)
+    master_weights: bool = False
 
     def __post_init__(self) -> None:
         extras = extra_fields_for(self.cfg, self.objective)
@@ -177,6 +180,7 @@ def _build(desc: TrainingDescription) -> Program:
     sharded = world > 1
     prog.metadata["world_size"] = world
     FULL: dict[tuple[int, str], int] = {}     # (stage, pass) -> gathered full-weight object
+    MASTER: dict[int, int] = {}               # stage -> fp32 master copy (optional)
     full_bytes = []
     for si, st in enumerate(stages):
         _, pbytes = st.layout(desc.dtype)
@@ -197,6 +201,13 @@ def _build(desc: TrainingDescription) -> Program:
             # gradients persist across calls when accumulation is driven from outside
             G.append(prog.add_object(ObjectSpec(f"{st.name}.gradients", gbytes, "gradient",
                                                 persistent=desc.mode != "step", stage=si)))
+        if step and desc.master_weights:
+            if sharded:
+                _, mbytes = st.shard_layout(torch.float32, world, trainable_only=True)
+            else:
+                _, mbytes = st.layout(torch.float32, trainable_only=True)
+            MASTER[si] = prog.add_object(ObjectSpec(f"{st.name}.master", mbytes, "optimizer_state", True,
+                                                    stage=si, sharding="sharded" if sharded else "whole"))
         if step:
             sh = "sharded" if sharded else "whole"
             M.append(prog.add_object(ObjectSpec(f"{st.name}.exp_avg", sbytes_opt, "optimizer_state", True, stage=si, sharding=sh)))
@@ -211,7 +222,8 @@ def _build(desc: TrainingDescription) -> Program:
             pbytes = prog.objects[W[si]].bytes
             prog.add_task(TaskSpec(f"O.{st.name}", "optimizer", si, -1,
                                    [UseSpec(W[si], "mutate", "params"), UseSpec(G[si], "read", "grads"),
-                                    UseSpec(M[si], "mutate", "m"), UseSpec(V[si], "mutate", "v")],
+                                    UseSpec(M[si], "mutate", "m"), UseSpec(V[si], "mutate", "v")]
+                                   + ([UseSpec(MASTER[si], "mutate", "master")] if si in MASTER else []),
                                    estimate_duration_ns(0.0, 8.0 * pbytes), 0,
                                    "adamw_dp" if sharded else "adamw",
                                    profile_key=f"opt:{pbytes}:{world}"))
@@ -349,7 +361,8 @@ def _build(desc: TrainingDescription) -> Program:
         pbytes = prog.objects[W[si]].bytes
         prog.add_task(TaskSpec(f"O.{st.name}", "optimizer", si, -1,
                                [UseSpec(W[si], "mutate", "params"), UseSpec(G[si], "read", "grads"),
-                                UseSpec(M[si], "mutate", "m"), UseSpec(V[si], "mutate", "v")],
+                                UseSpec(M[si], "mutate", "m"), UseSpec(V[si], "mutate", "v")]
+                               + ([UseSpec(MASTER[si], "mutate", "master")] if si in MASTER else []),
                                estimate_duration_ns(0.0, 8.0 * pbytes), 0,
                                "adamw_dp" if sharded else "adamw",
                                profile_key=f"opt:{pbytes}:{world}"))
@@ -396,14 +409,15 @@ def build_step(cfg: DecoderConfig, geometry: BatchGeometry,
                ordering: StepDataOrdering | None = None, *, dtype=torch.bfloat16,
                grad_dtype=None, selection: dict[int, str] | None = None, world_size: int = 1,
                rank: int = 0, objective=None, lora=None, expert_parallel: bool = False,
-               replicas: int = 1, min_shard_bytes: int = 0, head_block_rows: int = 0):
+               replicas: int = 1, min_shard_bytes: int = 0, head_block_rows: int = 0,
+               master_weights: bool = False):
     """Forward + backward + optimizer of one global batch. Returns ``(Program, description)``.
     ``world_size > 1`` builds the data-parallel form: weights and AdamW moments are
     stored as 1/N shards, gathered before use and updated shard-locally."""
     desc = TrainingDescription(cfg, geometry, ordering or StepDataOrdering(), dtype,
                                grad_dtype or dtype, dict(selection or {}), "step", world_size,
                                rank, objective, lora, expert_parallel, replicas, min_shard_bytes,
-                               head_block_rows)
+                               head_block_rows, master_weights)
     return _build(desc), desc
 
 
@@ -428,12 +442,13 @@ def build_forward(cfg, geometry, ordering=None, *, dtype=torch.bfloat16, world_s
 
 
 def build_optimizer(cfg, geometry, *, dtype=torch.bfloat16, grad_dtype=None, world_size=1, rank=0,
-                    objective=None, lora=None, min_shard_bytes=0, head_block_rows=0):
+                    objective=None, lora=None, min_shard_bytes=0, head_block_rows=0, master_weights=False):
     """The optimizer update alone, over gradients that earlier ``forward_backward``
     invocations left in the spill pool (the ``optim_step`` operation)."""
     desc = TrainingDescription(cfg, geometry, StepDataOrdering(), dtype, grad_dtype or dtype, {},
                                "optimizer", world_size, rank, objective, lora,
-                               min_shard_bytes=min_shard_bytes, head_block_rows=head_block_rows)
+                               min_shard_bytes=min_shard_bytes, head_block_rows=head_block_rows,
+                               master_weights=master_weights)
     return _build(desc), desc
 
 

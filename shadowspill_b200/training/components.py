@@ -171,10 +171,13 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
     # gradients, moments and parameters are all kept in the model dtype (no master copies):
     # say so instead of silently ignoring a request for anything else
     model_dtype = m.get("dtype", "bfloat16")
-    for key in ("gradient_dtype", "opt_state_dtype", "master_dtype"):
+    for key in ("gradient_dtype", "opt_state_dtype"):
         if opt.get(key, "bfloat16") not in ("bfloat16", model_dtype):
-            raise ValueError(f"optimizer {key}={opt[key]!r} is not supported: state is kept in the "
-                             f"model dtype ({model_dtype})")
+            raise ValueError(f"optimizer {key}={opt[key]!r} is not supported: gradients and moments are "
+                             f"kept in the model dtype ({model_dtype})")
+    if opt.get("master_dtype", "bfloat16") not in ("bfloat16", "float32", model_dtype):
+        raise ValueError(f"optimizer master_dtype={opt['master_dtype']!r} is not supported")
+    master_weights = opt.get("master_dtype", "bfloat16") == "float32" and model_dtype != "float32"
     res = body.get("resources", {})
     par = body.get("parallelism") or {}
     per_replica = int(par.get("ranks_per_replica", res.get("gpus", 1)))
@@ -242,7 +245,7 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
             "device_index": rank if device == "cuda" else 0, "rank": rank, "world_size": workers,
             "ranks_per_replica": per_replica if replicas > 1 else 0,
             "min_shard_bytes": int(par.get("min_shard_bytes", 0)) if workers > 1 else 0,
-            "head_chunks": head_chunks,
+            "head_chunks": head_chunks, "master_weights": master_weights,
             "walks": list(build.get("walks", ("breadth",))),
             "recompute_shares": list(build.get("recompute_shares", (100,))),
             "saved_variant": saved_variant,

@@ -79,6 +79,7 @@ class TrainingSetup:
     ranks_per_replica: int = 0           # 0 = one replica; else state is sharded inside groups of this size
     min_shard_bytes: int = 0             # sharded storage keeps smaller tensors whole on every rank
     head_chunks: int = 0                 # evaluate the output projection in this many row chunks (0 = default)
+    master_weights: bool = False         # fp32 master copies of trainable parameters (unfused update path)
     pretrained: str = ""                 # directory of Hugging Face safetensors to start from
     # content-addressed store of task profiles shared between runs ("" = none)
     store: str = ""
@@ -165,7 +166,8 @@ class TrainingSession:
                                             selection=sel, world_size=shard_world, rank=rank,
                                             expert_parallel=setup.expert_parallel,
                                             min_shard_bytes=setup.min_shard_bytes,
-                                            head_block_rows=head_rows, **choices))
+                                            head_block_rows=head_rows,
+                                            master_weights=setup.master_weights, **choices))
 
         def build_extra(op: str):
             kw = dict(dtype=self.dtype, world_size=shard_world, rank=rank,
@@ -173,7 +175,8 @@ class TrainingSession:
             if op == "forward_backward":
                 return with_replicas(build_forward_backward(self.cfg, self.geometry, StepDataOrdering(), **kw))
             if op == "optim_step":
-                return with_replicas(build_optimizer(self.cfg, self.geometry, **kw))
+                return with_replicas(build_optimizer(self.cfg, self.geometry,
+                                                     master_weights=setup.master_weights, **kw))
             if op == "forward":
                 return with_replicas(build_forward(self.cfg, self.geometry, StepDataOrdering(), **kw))
             raise ValueError(f"unknown operation {op!r}")

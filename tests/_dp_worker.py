@@ -26,6 +26,9 @@ def main():
     pretrained = arm.startswith("pretrained-")   # start from whole-parameter weights of another seed
     if pretrained:
         arm = arm.split("-", 1)[1]
+    master = arm.startswith("master-")    # fp32 master shards beside the model-dtype shards
+    if master:
+        arm = arm.split("-", 1)[1]
     rule = "adamw"
     if arm.startswith("lion-"):           # the unfused update path: all-reduce, then the rule
         rule, arm = "lion", arm.split("-", 1)[1]
@@ -55,7 +58,7 @@ def main():
     shard_world = world // replicas
     prog, desc = build_step(cfg, geo, StepDataOrdering(), dtype=dtype, world_size=shard_world, rank=rank,
                             expert_parallel=expert_parallel, replicas=replicas,
-                            min_shard_bytes=min_shard)
+                            min_shard_bytes=min_shard, master_weights=master)
     total = sum(o.bytes for o in prog.objects)
     plan = plan_program(prog, MemoryBudgets(total, 64 << 20, headroom_bytes=0), CommunicationInfo(),
                         SearchOptions(minimum_object_bytes_evict_eligible=1024, workers=1,
@@ -95,9 +98,10 @@ def main():
     for name, shard in ex.named_tensors():
         if name.startswith("exp_avg"):
             continue
-        full = refs[name].reshape(-1).cpu()
-        if name in banks:                 # this rank's experts, stored whole
-            p = banks[name]
+        key = name[len("master."):] if name.startswith("master.") else name   # masters mirror the weights
+        full = refs[key].reshape(-1).cpu()
+        if key in banks:                  # this rank's experts, stored whole
+            p = banks[key]
             per = p.numel // p.shape[0]
             lo, hi = p.expert_lo * per, (p.expert_lo + p.shape[0]) * per
         else:

@@ -167,3 +167,38 @@ def test_expert_banks_are_recorded_in_global_coordinates():
     d0, d1 = per_rank[0]["layer0.wq"], per_rank[1]["layer0.wq"]
     assert d0["region"][0] == 0 and d1["region"][0] == d0["region"][1]
     assert d0["region"][1] + d1["region"][1] == d0["storage_elements"]
+
+
+def test_master_copies_travel_with_the_checkpoint(tmp_path):
+    """A bf16 run with fp32 master copies resumes bit for bit: the masters are state."""
+    from shadowspill_b200.communication.info import CommunicationInfo
+    from shadowspill_b200.frontend.capture import BatchGeometry, StepDataOrdering, build_step
+    from shadowspill_b200.models.config import preset
+    from shadowspill_b200.planning.plan import MemoryBudgets, SearchOptions, plan_program
+    cfg = preset("llama3-tiny")
+    geo = BatchGeometry(microbatch_tokens=256, n_microbatches=2, slots=16, mean_seqlen=64)
+
+    def make():
+        prog, desc = build_step(cfg, geo, StepDataOrdering(), dtype=torch.bfloat16, master_weights=True)
+        plan = plan_program(prog, MemoryBudgets(32 << 20, 64 << 20, headroom_bytes=0), CommunicationInfo(),
+                            SearchOptions(minimum_object_bytes_evict_eligible=1024, workers=1))
+        return Executor(plan, desc, device="cpu", seed=5, hyper=Hyperparameters(lr=1e-4),
+                        stochastic_rounding=False)
+    a = make()
+    a.initialize()
+    for s in range(3):
+        a.run(_batches(cfg, s))
+    save_checkpoint(a, tmp_path / "ck")
+    names = {e["name"] for e in read_manifest(tmp_path / "ck" / "rank0.tar")["tensors"]}
+    assert "master.layer0.wqkv" in names and "exp_avg.layer0.wqkv" in names
+    want = [a.run(_batches(cfg, s)).loss for s in (3, 4)]
+    state = a.state_dict()
+    a.close()
+    b = make()
+    b.initialize(seed=99)
+    load_checkpoint(b, tmp_path / "ck")
+    assert [b.run(_batches(cfg, s)).loss for s in (3, 4)] == want
+    for k, v in b.state_dict().items():
+        assert torch.equal(v, state[k]), k
+    b.close()
+    assert not any(k.startswith("master.") for k in export_weights(tmp_path / "ck"))

@@ -35,6 +35,12 @@ def test_lion_update_under_sharded_storage():
     _launch(2, "cpu", "lion-small-dist", 29651)
 
 
+def test_master_copies_under_sharded_storage():
+    """fp32 master shards: the update runs on them (unfused, after a library all-reduce) and is
+    rounded into the weight shards; small tensors whole. Matches the single-process model."""
+    _launch(2, "cpu", "master-small-dist", 29661)
+
+
 def test_whole_parameter_weights_load_into_sharded_ranks():
     """Weights of another seed given as whole tensors: every rank keeps its slice, and the
     sharded job then trains exactly like a single-process model started from those weights."""

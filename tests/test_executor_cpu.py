@@ -183,3 +183,32 @@ def test_head_row_chunks_change_workspace_not_results():
         ex.close()
     assert work[1] < work[0]
     assert losses[1] == pytest.approx(losses[0], rel=1e-6)
+
+
+def test_fp32_master_copies_keep_progress_that_bf16_rounding_loses():
+    """bf16 weights with round-to-nearest and a small learning rate: for all but the smallest
+    weights every single update is below half an ulp and is rounded away. With fp32 master copies
+    the same updates accumulate in the master and surface in the weights after a few steps."""
+    cfg = preset("llama3-tiny")
+    geo = BatchGeometry(microbatch_tokens=256, n_microbatches=2, slots=16, mean_seqlen=64)
+    moved = {}
+    for master in (False, True):
+        prog, desc = build_step(cfg, geo, StepDataOrdering(), dtype=torch.bfloat16, master_weights=master)
+        assert any(o.name.endswith(".master") for o in prog.objects) == master
+        plan = plan_program(prog, MemoryBudgets(32 << 20, 64 << 20, headroom_bytes=0), CommunicationInfo(),
+                            SearchOptions(minimum_object_bytes_evict_eligible=1024, workers=1))
+        ex = Executor(plan, desc, device="cpu", seed=1, stochastic_rounding=False,
+                      hyper=Hyperparameters(lr=1e-5))
+        ex.initialize()
+        before = ex.state_dict()
+        for s in range(12):
+            ex.run(_batches(cfg, s))
+        after = ex.state_dict()
+        w = "layer0.wqkv"
+        moved[master] = float((after[w] != before[w]).float().mean())
+        if master:
+            m = after["master." + w]
+            assert m.dtype == torch.float32 and torch.equal(m.to(torch.bfloat16), after[w])
+            assert float((m - after[w].float()).abs().max()) > 0      # the master holds what bf16 cannot
+        ex.close()
+    assert moved[False] < 0.25 and moved[True] > 0.3 and moved[True] > 2 * moved[False], moved

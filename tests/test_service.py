@@ -245,9 +245,12 @@ def test_resumable_artifact_transfer_and_component_listing(service, tmp_path):
 def test_unsupported_optimizer_state_dtypes_are_refused(service):
     with ServiceClient(service.url, token="secret") as svc:
         with pytest.raises(Exception) as e:
-            svc.describe_training(model=Model("llama3-tiny"), optimizer=Optimizer(master_dtype="float32"),
+            svc.describe_training(model=Model("llama3-tiny"), optimizer=Optimizer(opt_state_dtype="float32"),
                                   resources=Resources(backend="cpu")).result()
-        assert "master_dtype" in str(e.value)
+        assert "opt_state_dtype" in str(e.value)
+        # fp32 master copies on a bf16 model are a supported request
+        assert svc.describe_training(model=Model("llama3-tiny"), optimizer=Optimizer(master_dtype="float32"),
+                                     resources=Resources(backend="cpu")).result()["workers"] == 1
         ok = svc.describe_training(model=Model("llama3-tiny", dtype="float32"),
                                    optimizer=Optimizer(master_dtype="float32", opt_state_dtype="float32"),
                                    resources=Resources(backend="cpu")).result()
