@@ -226,7 +226,7 @@ def _build(desc: TrainingDescription) -> Program:
                                    + ([UseSpec(MASTER[si], "mutate", "master")] if si in MASTER else []),
                                    estimate_duration_ns(0.0, 8.0 * pbytes), 0,
                                    "adamw_dp" if sharded else "adamw",
-                                   profile_key=f"opt:{pbytes}:{world}"))
+                                   profile_key=f"opt:{pbytes}:{world}" + (":master" if si in MASTER else "")))
         prog.validate()
         return prog
     _, in_bytes = batch_layout(T, geo.slots, geo.extra_fields)
@@ -363,9 +363,11 @@ def _build(desc: TrainingDescription) -> Program:
                                [UseSpec(W[si], "mutate", "params"), UseSpec(G[si], "read", "grads"),
                                 UseSpec(M[si], "mutate", "m"), UseSpec(V[si], "mutate", "v")]
                                + ([UseSpec(MASTER[si], "mutate", "master")] if si in MASTER else []),
-                               estimate_duration_ns(0.0, 8.0 * pbytes), 0,
+                               estimate_duration_ns(0.0, 8.0 * pbytes),
+                               # the unfused update holds a handful of fp32 temporaries per parameter
+                               (6 * prog.objects[MASTER[si]].bytes) if si in MASTER else 0,
                                "adamw_dp" if sharded else "adamw",
-                               profile_key=f"opt:{pbytes}:{world}"))
+                               profile_key=f"opt:{pbytes}:{world}" + (":master" if si in MASTER else "")))
 
     body = list(range(S - 1))
     mbs = list(range(n_mb))

@@ -83,11 +83,12 @@ def _fill_inputs(runner: TaskRunner, task: int, flats: list[torch.Tensor], host_
 
 def measure_program(program: Program, desc: TrainingDescription, device: str = "cuda",
                     min_samples: int = 3, max_samples: int = 8, tolerance: float = 0.03,
-                    keys: set[str] | None = None) -> Profiles:
-    """Times one representative task per ``profile_key`` with the ordinary torch allocator."""
+                    keys: set[str] | None = None, rule: str = "adamw") -> Profiles:
+    """Times one representative task per ``profile_key`` with the ordinary torch allocator.
+    ``rule``: the run's update rule (the unfused rules allocate temporaries the fused one does not)."""
     dev = torch.device(device)
     cuda = dev.type == "cuda"
-    runner = TaskRunner(program, desc, Hyperparameters(lr=0.0), seed=0, stochastic_rounding=True)
+    runner = TaskRunner(program, desc, Hyperparameters(lr=0.0, rule=rule), seed=0, stochastic_rounding=True)
     meta = program.metadata
     cfg = desc.cfg
     host_batch = make_batch(0, vocab=cfg.vocab_size, tokens_per_step=runner.T * runner.n_mb,

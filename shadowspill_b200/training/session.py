@@ -287,7 +287,7 @@ class TrainingSession:
                                 self.profiles.tasks[key] = TaskProfile(**hit)
                         missing -= set(self.profiles.tasks)
                     if missing:
-                        got = measure_program(prog, desc, dev, keys=missing)
+                        got = measure_program(prog, desc, dev, keys=missing, rule=setup.optimizer_rule)
                         self.profiles.tasks.update(got.tasks)
                         self.profiles.device = got.device
                         if store is not None:
