@@ -84,3 +84,31 @@ def test_forward_program_returns_target_logprobs():
     for o, m in zip(res.outputs, host):
         assert (o[:, 0][m.targets < 0] == 0).all() and (o <= 0).all()
     ex.close()
+
+
+@pytest.mark.parametrize("rule,master", [("adamw", True), ("lion", False), ("sgd", True)])
+def test_unfused_update_paths_on_the_device(rule, master):
+    """fp32 master copies and the update rules beyond AdamW run as tensor operations on the
+    planned device ranges: the loss falls, masters round exactly into the weights."""
+    cfg = DecoderConfig("llama3", 2, 512, 4, 2, 128, 1024, 4096)
+    geo = BatchGeometry(1024, 2, slots=32, mean_seqlen=200)
+    prog, desc = build_step(cfg, geo, StepDataOrdering(), master_weights=master)
+    total = sum(o.bytes for o in prog.objects)
+    ws = max(t.workspace_bytes for t in prog.tasks)
+    plan = plan_program(prog, MemoryBudgets(2 * ws + total, 1 << 30, headroom_bytes=0), CommunicationInfo(),
+                        SearchOptions(minimum_object_bytes_evict_eligible=4096))
+    lr = {"adamw": 1e-3, "lion": 1e-4, "sgd": 3e-2}[rule]
+    ex = Executor(plan, desc, device="cuda", seed=3, stochastic_rounding=False,
+                  hyper=Hyperparameters(lr=lr, beta2=0.99 if rule == "lion" else 0.95, rule=rule))
+    ex.initialize(on_device=False)
+    host = make_batch(0, vocab=cfg.vocab_size, tokens_per_step=2048, microbatch_tokens=1024,
+                      median=200, min_len=16, max_len=512, slots=32)
+    losses = [ex.run(host).loss for _ in range(4)]
+    _lib.check_status()
+    assert all(l == l for l in losses) and losses[-1] < losses[0], losses
+    state = ex.state_dict()
+    if master:
+        for k, v in state.items():
+            if k.startswith("master."):
+                assert v.dtype == torch.float32 and torch.equal(v.to(torch.bfloat16), state[k[7:]]), k
+    ex.close()
