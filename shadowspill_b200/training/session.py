@@ -157,6 +157,11 @@ class TrainingSession:
 
         def with_replicas(built):
             built[1].replicas = replicas          # programs depend on the shard count only
+            if setup.optimizer_rule != "adamw":
+                # the unfused rules cost (and allocate) differently: keep their profiles apart
+                for t in built[0].tasks:
+                    if t.kind == "optimizer" and t.profile_key:
+                        t.profile_key += f":{setup.optimizer_rule}"
             return built
 
         def build(index: int):
