@@ -99,7 +99,8 @@ def write_report(plan: Plan, directory: str | Path) -> Path:
     d.mkdir(parents=True, exist_ok=True)
     summary = asdict(plan.summary)
     summary["device_pool_bytes"] = plan.device_bytes
-    summary["spill_pool_bytes"] = plan.spill_bytes
+    summary["spill_pool_bytes"] = plan.spill_bytes       # pinned host memory
+    summary["file_pool_bytes"] = plan.file_bytes         # file-backed (or remote) pool, 0 = none
     summary["budgets"] = plan.budgets
     (d / "summary.json").write_text(json.dumps(summary, indent=1))
     with open(d / "tasks.csv", "w", newline="") as f:
@@ -113,11 +114,12 @@ def write_report(plan: Plan, directory: str | Path) -> Path:
             prev_end = e
     with open(d / "transfers.csv", "w", newline="") as f:
         w = csv.writer(f)
-        w.writerow(["index", "kind", "object", "bytes", "trigger_task", "start_ms", "end_ms"])
+        w.writerow(["index", "kind", "object", "bytes", "trigger_task", "start_ms", "end_ms", "home_pool"])
         for i, (a, s, e) in enumerate(zip(plan.schedule.actions, plan.action_start_ns,
                                           plan.action_end_ns)):
             o = plan.program.objects[a.object]
-            w.writerow([i, a.kind, o.name, o.bytes, a.trigger_task, s / 1e6, e / 1e6])
+            w.writerow([i, a.kind, o.name, o.bytes, a.trigger_task, s / 1e6, e / 1e6,
+                        plan.home_pool(a.object)])
     (d / "timeline.json").write_text(json.dumps({
         "tasks": [{"name": t.name, "kind": t.kind, "start_ns": s, "end_ns": e}
                   for t, s, e in zip(plan.program.tasks, plan.task_start_ns, plan.task_end_ns)],
