@@ -288,8 +288,10 @@ class Executor:
                  stochastic_rounding: bool = True, trace_capacity: int = 0,
                  mock_bps: float = 0.0, collectives: str = "auto",
                  extra_plans: dict[str, tuple[Plan, TrainingDescription]] | None = None,
-                 file_pool: dict | None = None, annotate: bool = False):
-        """``annotate``: wrap every task in an NVTX range named after it (visible in Nsight
+                 file_pool: dict | None = None, annotate: bool = False, moe_chunks: int = 0):
+        """``moe_chunks``: under expert parallelism, cut each routed layer's local experts into this
+        many groups whose dispatch, GEMMs and combine are pipelined (0 or 1 = one group).
+        ``annotate``: wrap every task in an NVTX range named after it (visible in Nsight
         Systems captures; no effect off the GPU).
         ``file_pool``: settings of the file-backed spill pool for plans whose homes were
         moved there (``planning.plan.move_homes_to_file``): ``directory`` or ``image``
@@ -346,6 +348,8 @@ class Executor:
             # one symmetric workspace for every routed layer of the model (outside the plan's pool)
             self.ep_group = ExpertParallelGroup(self.runner.T, c.top_k, c.d_model, c.n_experts,
                                                 device=self.torch_device)
+            if moe_chunks > 1:
+                self.ep_group.pipeline_chunks = int(moe_chunks)
             self._bind_expert_group(self.runner)
         if self.cuda:
             torch.cuda.set_device(device_index)

@@ -215,11 +215,13 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
     prep = body.get("preparation", {})
     build, planning = prep.get("build", {}), prep.get("planning", {})
     saved_variant = build.get("saved_variant", "save_attention")
-    head_chunks = 0
+    head_chunks = moe_chunks = 0
     for pol in prep.get("policies", []):
         if pol.get("id") == "shadowspill/text_chunks@1":
-            # "projection": row chunks of the output projection; "moe" chunks are not applied
+            # "projection": row chunks of the output projection; "moe": expert groups a routed layer
+            # is pipelined in under expert parallelism
             head_chunks = int((pol.get("config") or {}).get("projection", 0) or 0)
+            moe_chunks = int((pol.get("config") or {}).get("moe", 0) or 0)
         if pol.get("id") == "shadowspill/text_retention@1":
             saved_variant = _RETENTION_VARIANT.get((pol.get("config") or {}).get("rule", ""), saved_variant)
     ex = body.get("execution", {})
@@ -245,7 +247,7 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
             "device_index": rank if device == "cuda" else 0, "rank": rank, "world_size": workers,
             "ranks_per_replica": per_replica if replicas > 1 else 0,
             "min_shard_bytes": int(par.get("min_shard_bytes", 0)) if workers > 1 else 0,
-            "head_chunks": head_chunks, "master_weights": master_weights,
+            "head_chunks": head_chunks, "moe_chunks": moe_chunks, "master_weights": master_weights,
             "walks": list(build.get("walks", ("breadth",))),
             "recompute_shares": list(build.get("recompute_shares", (100,))),
             "saved_variant": saved_variant,

@@ -79,6 +79,7 @@ class TrainingSetup:
     ranks_per_replica: int = 0           # 0 = one replica; else state is sharded inside groups of this size
     min_shard_bytes: int = 0             # sharded storage keeps smaller tensors whole on every rank
     head_chunks: int = 0                 # evaluate the output projection in this many row chunks (0 = default)
+    moe_chunks: int = 0                  # expert parallelism: pipeline each routed layer in this many expert groups
     master_weights: bool = False         # fp32 master copies of trainable parameters (unfused update path)
     pretrained: str = ""                 # directory of Hugging Face safetensors to start from
     # content-addressed store of task profiles shared between runs ("" = none)
@@ -373,7 +374,8 @@ class TrainingSession:
                                  stochastic_rounding=setup.stochastic_rounding,
                                  trace_capacity=setup.trace_capacity,
                                  collectives=setup.collectives, extra_plans=self.extra_plans,
-                                 file_pool=file_pool, annotate=setup.profiler_annotations)
+                                 file_pool=file_pool, annotate=setup.profiler_annotations,
+                                 moe_chunks=setup.moe_chunks)
         if not (file_spill and setup.spill_image and not setup.spill_create_image):
             self.executor.initialize()      # an opened image already holds the state
         if setup.pretrained:
