@@ -43,8 +43,9 @@ int FilePool::open(const char* directory, const char* image, bool create_image, 
       return SS_IO_ERROR;
     }
     // reserve the blocks now so that a full disk shows at open, not in the middle of a step;
-    // filesystems without preallocation keep the sparse file
-    int rc = ::posix_fallocate(fd, 0, bytes);
+    // filesystems without preallocation keep the sparse file (the raw call, not the library
+    // emulation that would write every block of a multi-GiB pool)
+    int rc = ::fallocate(fd, 0, 0, bytes) == 0 ? 0 : errno;
     if (rc == ENOSPC) {
       error = "not enough space for the pool file";
       ::close(fd);
