@@ -238,6 +238,7 @@ def make_handler(server):
                     return self._send(200, {"plans": live.plan_names})
                 page = int(q.get("page", 0))
                 rows = [{"operation": "step", **live.plan_summary}]
+                rows += [{"operation": op, **summary} for op, summary in sorted(live.operation_plans.items())]
                 return self._send(200, {"plans": rows[page * 32:(page + 1) * 32], "names": live.plan_names})
             if rest == ["plans", "report"] and method == "POST":
                 return self._send(200, {"summary": live.plan_summary,

@@ -48,6 +48,7 @@ class LiveRun:
         self.resolved = None
         self.lease: str | None = None
         self.plan_summary: dict[str, Any] = {}
+        self.operation_plans: dict[str, dict[str, Any]] = {}     # further operations' plans
         self.plan_names: dict[str, str] = {}
         self.checkpoints: dict[str, str] = {}
         self.thread = threading.Thread(target=self._create, name=f"create-{run}", daemon=True)
@@ -86,6 +87,7 @@ class LiveRun:
             self.group = WorkerGroup(r.setups, self.dir / "logs", checkpoint=ckpt,
                                      on_progress=self.log)
             self.plan_summary = self.group.ready_info[0].get("plan_summary", {})
+            self.operation_plans = self.group.ready_info[0].get("operation_plans", {})
             self.journal.append("ready", {"workers": r.workers, "plan": self.plan_summary})
             if self.body.get("prepare_only"):
                 self.group.stop()

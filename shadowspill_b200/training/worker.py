@@ -78,6 +78,8 @@ def serve(chan: Channel) -> int:
             session.restore(header["checkpoint"])
         from dataclasses import asdict
         chan.send({"type": "ready", "rank": rank, "plan_summary": asdict(session.plan.summary),
+                   "operation_plans": {op: asdict(pl.summary)
+                                       for op, (pl, _) in getattr(session, "extra_plans", {}).items()},
                    "slots": session.slots, "timings": session.timings,
                    "completed_updates": session.executor.completed_updates,
                    "operations": session.executor.operations()})

@@ -51,6 +51,9 @@ def test_train_checkpoint_resume_through_the_public_api(service, tmp_path_factor
         assert desc["workers"] == 1 and desc["parameters"] == 426_624
         trainer = _trainer(svc, ("step", "forward_backward", "optim_step", "forward"))
         assert trainer.info["plan_summary"]["fetch_bytes"] > 0
+        plans = svc.get_plans(trainer.run).result()["plans"]
+        assert [p["operation"] for p in plans] == ["step", "forward", "forward_backward", "optim_step"]
+        assert all(p["duration_seconds"] > 0 for p in plans)
         losses = [trainer.step(text_batch(_sequences(0))).result().loss for _ in range(4)]
         assert losses[-1] < losses[0]
         # forward: the loss and, per datum, log p(target) of every position
