@@ -285,6 +285,8 @@ typedef struct ss_runtime_stats {
   int64_t events_created;      /* stays constant in steady state */
   int64_t host_allocations;    /* stays constant in steady state */
   int64_t worker_wakeups;
+  int64_t staged_read_chunks, staged_read_bytes;     /* file / remote pool -> pinned ring */
+  int64_t staged_write_chunks, staged_write_bytes;   /* pinned ring -> file / remote pool */
 } ss_runtime_stats;
 
 int ss_runtime_create(ss_backend* backend, const ss_runtime_config* config, ss_runtime** out);

@@ -524,6 +524,10 @@ int ss_runtime_stats_read(ss_runtime* rt, ss_runtime_stats* out) {
   out->evict_bytes = rt->st_evict_bytes; out->releases = rt->st_releases;
   out->reuse_waits = rt->st_reuse_waits; out->events_created = rt->st_events;
   out->host_allocations = rt->st_host_allocs; out->worker_wakeups = rt->st_wakeups;
+  out->staged_read_chunks = rt->fetch_lane ? rt->fetch_lane->chunks_done() : 0;
+  out->staged_read_bytes = rt->fetch_lane ? rt->fetch_lane->bytes_done() : 0;
+  out->staged_write_chunks = rt->evict_lane ? rt->evict_lane->chunks_done() : 0;
+  out->staged_write_bytes = rt->evict_lane ? rt->evict_lane->bytes_done() : 0;
   return SS_OK;
 }
 

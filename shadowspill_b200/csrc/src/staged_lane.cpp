@@ -158,6 +158,8 @@ void StagedLane::disk_main() {
     Slot& s = slots_[si];
     const int rc = pool_->chunk_io(!to_device_, s.buf, s.job->file_off + s.off, s.n);
     if (rc != SS_OK) { s.state.store(FAILED, std::memory_order_release); continue; }
+    chunks_done_.fetch_add(1, std::memory_order_relaxed);
+    bytes_done_.fetch_add(s.n, std::memory_order_relaxed);
     if (to_device_) {
       s.state.store(FILLED, std::memory_order_release);
     } else {

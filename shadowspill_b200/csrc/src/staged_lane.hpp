@@ -131,6 +131,8 @@ class StagedLane {
   bool busy() const { return !jobs_.empty(); }
   const std::string& message() const { return message_; }
   int64_t ring_bytes() const { return chunk_ * depth_; }
+  int64_t chunks_done() const { return chunks_done_.load(std::memory_order_relaxed); }
+  int64_t bytes_done() const { return bytes_done_.load(std::memory_order_relaxed); }
 
  private:
   enum SlotState : int { FREE = 0, READING, FILLED, COPYING, COPIED, WRITING, WRITTEN, FAILED };
@@ -163,6 +165,7 @@ class StagedLane {
   std::vector<std::thread> threads_;
   bool stop_ = false;
   std::string message_;
+  std::atomic<int64_t> chunks_done_{0}, bytes_done_{0};     // chunks the disk threads completed
 };
 
 }  // namespace ssc

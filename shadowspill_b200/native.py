@@ -95,7 +95,8 @@ class TraceEvent(C.Structure):
 class RuntimeStats(C.Structure):
     _fields_ = [(n, i64) for n in ("steps", "tasks", "fetches", "fetch_bytes", "evicts",
                                    "evict_bytes", "releases", "reuse_waits", "events_created",
-                                   "host_allocations", "worker_wakeups")]
+                                   "host_allocations", "worker_wakeups", "staged_read_chunks",
+                                   "staged_read_bytes", "staged_write_chunks", "staged_write_bytes")]
 
 
 class PlanDesc(C.Structure):

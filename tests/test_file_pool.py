@@ -76,6 +76,11 @@ def test_training_through_the_file_pool_is_bit_identical(tmp_path, chunk, depth)
         assert torch.equal(state[k], host_state[k]), k
     assert stats["fetch_bytes"] == host_stats["fetch_bytes"]
     assert stats["evict_bytes"] == host_stats["evict_bytes"]
+    # everything except the pinned batches and the loss word went through the rings, chunk by chunk
+    assert 0 < stats["staged_read_bytes"] <= stats["fetch_bytes"]
+    assert 0 < stats["staged_write_bytes"] <= stats["evict_bytes"]
+    assert stats["staged_read_chunks"] >= stats["staged_read_bytes"] // chunk
+    assert host_stats["staged_read_bytes"] == 0 and host_stats["staged_write_chunks"] == 0
 
 
 def test_a_kept_image_carries_state_to_the_next_run(tmp_path):
