@@ -315,3 +315,23 @@ def test_other_optimizer_components_through_the_service(service):
             svc.describe_training(model=Model("llama3-tiny"), optimizer=Optimizer(id="adagrad@1"),
                                   resources=Resources(backend="cpu")).result()
         assert "adagrad@1" in str(e.value)
+
+
+def test_node_daemon_routes(service):
+    """join -> heartbeat -> queued command delivered on poll until its receipt -> leave."""
+    from shadowspill_b200.client.transport import HTTPTransport, TransportError
+    t = HTTPTransport(service.url, token=service.node_token)
+    inc = t.request("POST", "/v1/nodes/join", {"node_id": "node-x", "info": {"gpus": 8}})[1]["incarnation"]
+    assert t.request("POST", "/v1/nodes/heartbeat", {"node_id": "node-x", "incarnation": inc})[1]["ok"]
+    cid = service.membership.enqueue("node-x", {"kind": "drain"})
+    got = t.request("POST", "/v1/nodes/poll", {"node_id": "node-x", "incarnation": inc})[1]["commands"]
+    assert [c["id"] for c in got] == [cid] and got[0]["kind"] == "drain"
+    assert t.request("POST", "/v1/nodes/receipt", {"node_id": "node-x", "incarnation": inc, "command": cid,
+                                                   "outcome": {"state": "done"}})[1]["ok"]
+    assert t.request("POST", "/v1/nodes/poll", {"node_id": "node-x", "incarnation": inc})[1]["commands"] == []
+    with pytest.raises(TransportError) as e:          # a stale incarnation is fenced
+        t.request("POST", "/v1/nodes/poll", {"node_id": "node-x", "incarnation": "0" * 32})
+    assert e.value.status == 410
+    with ServiceClient(service.url, token="secret") as svc:
+        assert "node-x" in svc.list_hardware().result()["members"]
+    assert t.request("POST", "/v1/nodes/leave", {"node_id": "node-x", "incarnation": inc})[1]["ok"]
