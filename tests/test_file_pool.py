@@ -55,8 +55,9 @@ def _train(plan, desc, cfg, steps=4, **kw):
     return losses, state, stats
 
 
-@pytest.mark.parametrize("chunk,depth", [(4096, 2), (16 << 10, 3), (1 << 20, 16)])
-def test_training_through_the_file_pool_is_bit_identical(tmp_path, chunk, depth):
+@pytest.mark.parametrize("chunk,depth,io", [(4096, 2, 0), (16 << 10, 3, 0), (1 << 20, 16, 0),
+                                            (8192, 1, 1), (64 << 10, 5, 8)])
+def test_training_through_the_file_pool_is_bit_identical(tmp_path, chunk, depth, io):
     cfg, plan, desc = _setup()
     host_losses, host_state, host_stats = _train(copy.deepcopy(plan), desc, cfg)
     filed = move_homes_to_file(copy.deepcopy(plan))
@@ -69,7 +70,7 @@ def test_training_through_the_file_pool_is_bit_identical(tmp_path, chunk, depth)
     again = Plan.from_json(filed.to_json())
     assert again.file_offsets == filed.file_offsets and again.file_bytes == filed.file_bytes
     losses, state, stats = _train(again, desc, cfg, file_pool={
-        "directory": str(tmp_path), "chunk_bytes": chunk, "queue_depth": depth})
+        "directory": str(tmp_path), "chunk_bytes": chunk, "queue_depth": depth, "io_threads": io})
     assert losses == host_losses
     assert set(state) == set(host_state)
     for k in state:
