@@ -240,7 +240,8 @@ typedef struct ss_runtime_config {
   int64_t file_bytes;          /* 0 = no file pool */
   const char* file_directory;  /* existing directory for the unlinked scratch file */
   const char* file_image;      /* optional named file that is the whole pool and is kept */
-  int32_t file_create_image;   /* create file_image (must not exist) instead of opening it */
+  int32_t file_create_image;   /* 0 open file_image read-write; 1 create it (must not exist); 2 adopt it:
+                                  read-only first bytes of the pool, the rest a scratch file in file_directory */
   int32_t file_queue_depth;    /* slots per direction; 0 = 16 */
   int64_t file_chunk_bytes;    /* multiple of 4096; 0 = 2 MiB */
   int32_t file_io_threads;     /* disk threads per direction; 0 = 4 */

@@ -419,7 +419,7 @@ int ss_runtime_create(ss_backend* backend, const ss_runtime_config* config, ss_r
       rc = rt->remote.open(config->remote_address, config->file_bytes, error);
       rt->store = &rt->remote;
     } else {
-      rc = rt->local_file.open(config->file_directory, config->file_image, config->file_create_image != 0,
+      rc = rt->local_file.open(config->file_directory, config->file_image, config->file_create_image,
                                config->file_bytes, error);
       rt->store = &rt->local_file;
     }

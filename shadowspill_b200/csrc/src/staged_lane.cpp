@@ -11,17 +11,31 @@
 namespace ssc {
 
 // ------------------------------------------------------------------ FilePool
-int FilePool::open(const char* directory, const char* image, bool create_image, int64_t bytes,
+int FilePool::open(const char* directory, const char* image, int image_mode, int64_t bytes,
                    std::string& error) {
   close();
   if (bytes <= 0) { error = "file pool needs a positive size"; return SS_INVALID_ARGUMENT; }
   const bool named = image && *image;
+  const bool adopt = named && image_mode == 2;
+  int64_t scratch_bytes = bytes;
+  if (adopt) {
+    fd_image_ = ::open(image, O_RDONLY | O_CLOEXEC);
+    if (fd_image_ < 0) { error = std::string("cannot open pool image ") + image + ": " + std::strerror(errno); return SS_IO_ERROR; }
+    struct stat ist{};
+    if (::fstat(fd_image_, &ist) != 0 || ist.st_size <= 0 || ist.st_size % DIRECT_ALIGN != 0 || ist.st_size > bytes) {
+      error = "an adopted image is a positive multiple of 4096 bytes, no larger than the pool";
+      close();
+      return SS_INVALID_ARGUMENT;
+    }
+    image_bytes_ = ist.st_size;
+    scratch_bytes = std::max<int64_t>(bytes - image_bytes_, DIRECT_ALIGN);
+  }
   int fd = -1;
-  if (named) {
-    fd = ::open(image, O_RDWR | O_CLOEXEC | (create_image ? (O_CREAT | O_EXCL) : 0), 0600);
+  if (named && !adopt) {
+    fd = ::open(image, O_RDWR | O_CLOEXEC | (image_mode == 1 ? (O_CREAT | O_EXCL) : 0), 0600);
     if (fd < 0) { error = std::string("cannot open pool image ") + image + ": " + std::strerror(errno); return SS_IO_ERROR; }
   } else {
-    if (!directory || !*directory) { error = "file pool needs a directory"; return SS_INVALID_ARGUMENT; }
+    if (!directory || !*directory) { error = "file pool needs a directory"; close(); return SS_INVALID_ARGUMENT; }
 #ifdef O_TMPFILE
     fd = ::open(directory, O_TMPFILE | O_RDWR | O_CLOEXEC, 0600);
 #endif
@@ -32,23 +46,25 @@ int FilePool::open(const char* directory, const char* image, bool create_image, 
       fd = ::mkstemp(path.data());
       if (fd >= 0) ::unlink(path.data());
     }
-    if (fd < 0) { error = std::string("cannot create a pool file in ") + directory + ": " + std::strerror(errno); return SS_IO_ERROR; }
+    if (fd < 0) { error = std::string("cannot create a pool file in ") + directory + ": " + std::strerror(errno); close(); return SS_IO_ERROR; }
   }
   struct stat st{};
-  if (::fstat(fd, &st) != 0) { error = "fstat failed"; ::close(fd); return SS_IO_ERROR; }
-  if (st.st_size < bytes) {
-    if (::ftruncate(fd, bytes) != 0) {
+  if (::fstat(fd, &st) != 0) { error = "fstat failed"; ::close(fd); close(); return SS_IO_ERROR; }
+  if (st.st_size < scratch_bytes) {
+    if (::ftruncate(fd, scratch_bytes) != 0) {
       error = std::string("cannot size the pool file: ") + std::strerror(errno);
       ::close(fd);
+      close();
       return SS_IO_ERROR;
     }
     // reserve the blocks now so that a full disk shows at open, not in the middle of a step;
     // filesystems without preallocation keep the sparse file (the raw call, not the library
     // emulation that would write every block of a multi-GiB pool)
-    int rc = ::fallocate(fd, 0, 0, bytes) == 0 ? 0 : errno;
+    int rc = ::fallocate(fd, 0, 0, scratch_bytes) == 0 ? 0 : errno;
     if (rc == ENOSPC) {
       error = "not enough space for the pool file";
       ::close(fd);
+      close();
       return SS_OUT_OF_MEMORY;
     }
   }
@@ -63,8 +79,9 @@ int FilePool::open(const char* directory, const char* image, bool create_image, 
 void FilePool::close() {
   if (fd_direct_ >= 0) ::close(fd_direct_);
   if (fd_buffered_ >= 0) ::close(fd_buffered_);
-  fd_direct_ = fd_buffered_ = -1;
-  bytes_ = 0;
+  if (fd_image_ >= 0) ::close(fd_image_);
+  fd_direct_ = fd_buffered_ = fd_image_ = -1;
+  bytes_ = image_bytes_ = 0;
 }
 
 static int full_io(int fd, bool write, char* buf, int64_t off, int64_t n) {
@@ -81,35 +98,43 @@ static int full_io(int fd, bool write, char* buf, int64_t off, int64_t n) {
   return 0;
 }
 
-int FilePool::write(int64_t off, const void* src, int64_t n) {
+// One range of the pool: the adopted image serves [0, image_bytes_) read-only, the scratch (or
+// whole-pool) file the rest, at offsets counted from the end of the image.
+int FilePool::region_io(bool write, bool chunk, char* buf, int64_t off, int64_t n) {
   if (fd_buffered_ < 0 || off < 0 || n < 0 || off + n > bytes_) return SS_INVALID_ARGUMENT;
-  if (full_io(fd_buffered_, true, static_cast<char*>(const_cast<void*>(src)), off, n) != 0) return SS_IO_ERROR;
-  if (::fdatasync(fd_buffered_) != 0) return SS_IO_ERROR;
-  // leave no stale cached pages behind for the direct descriptor to disagree with
-  ::posix_fadvise(fd_buffered_, off, n, POSIX_FADV_DONTNEED);
-  return SS_OK;
-}
-
-int FilePool::read(int64_t off, void* dst, int64_t n) {
-  if (fd_buffered_ < 0 || off < 0 || n < 0 || off + n > bytes_) return SS_INVALID_ARGUMENT;
-  if (full_io(fd_buffered_, false, static_cast<char*>(dst), off, n) != 0) return SS_IO_ERROR;
-  ::posix_fadvise(fd_buffered_, off, n, POSIX_FADV_DONTNEED);
-  return SS_OK;
-}
-
-int FilePool::chunk_io(bool write, void* buf, int64_t off, int64_t n) {
-  if (fd_buffered_ < 0 || off < 0 || n < 0 || off + n > bytes_) return SS_INVALID_ARGUMENT;
-  const bool aligned = fd_direct_ >= 0 && off % DIRECT_ALIGN == 0 && n % DIRECT_ALIGN == 0 &&
+  if (off < image_bytes_) {
+    if (write) return SS_IO_ERROR;                 // the image is never written
+    const int64_t k = std::min(n, image_bytes_ - off);
+    if (full_io(fd_image_, false, buf, off, k) != 0) return SS_IO_ERROR;
+    buf += k; off += k; n -= k;
+    if (n == 0) return SS_OK;
+  }
+  off -= image_bytes_;
+  const bool aligned = chunk && fd_direct_ >= 0 && off % DIRECT_ALIGN == 0 && n % DIRECT_ALIGN == 0 &&
                        reinterpret_cast<uintptr_t>(buf) % DIRECT_ALIGN == 0;
   if (aligned) {
-    int rc = full_io(fd_direct_, write, static_cast<char*>(buf), off, n);
+    int rc = full_io(fd_direct_, write, buf, off, n);
     if (rc == 0) return SS_OK;
     if (rc != -EINVAL) return SS_IO_ERROR;      // EINVAL: this filesystem wants a coarser alignment
   }
-  if (full_io(fd_buffered_, write, static_cast<char*>(buf), off, n) != 0) return SS_IO_ERROR;
-  // keep the page cache from growing by the whole pool
+  if (full_io(fd_buffered_, write, buf, off, n) != 0) return SS_IO_ERROR;
+  if (write && !chunk && ::fdatasync(fd_buffered_) != 0) return SS_IO_ERROR;
+  // leave no cached pages behind: they would grow by the whole pool, and the direct descriptor
+  // must not disagree with them
   ::posix_fadvise(fd_buffered_, off, n, POSIX_FADV_DONTNEED);
   return SS_OK;
+}
+
+int FilePool::write(int64_t off, const void* src, int64_t n) {
+  return region_io(true, false, static_cast<char*>(const_cast<void*>(src)), off, n);
+}
+
+int FilePool::read(int64_t off, void* dst, int64_t n) {
+  return region_io(false, false, static_cast<char*>(dst), off, n);
+}
+
+int FilePool::chunk_io(bool write, void* buf, int64_t off, int64_t n) {
+  return region_io(write, true, static_cast<char*>(buf), off, n);
 }
 
 // ------------------------------------------------------------------ StagedLane

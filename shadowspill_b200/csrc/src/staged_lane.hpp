@@ -44,10 +44,14 @@ class ChunkStore {
 class FilePool : public ChunkStore {
  public:
   ~FilePool() override { close(); }
-  // directory: where the unlinked scratch file lives. image: optional named file that is
-  // the whole pool and is kept (created when create_image, else opened read-write).
-  int open(const char* directory, const char* image, bool create_image, int64_t bytes,
+  // directory: where the unlinked scratch file lives. image: optional named file.
+  // image_mode 0: the image is the whole pool, opened read-write and kept. 1: the same, created
+  // here (it must not exist). 2 (adopt): the existing image is opened read-only as the pool's
+  // first bytes, the rest of the pool is a scratch file in `directory`; writing into the image
+  // part fails.
+  int open(const char* directory, const char* image, int image_mode, int64_t bytes,
            std::string& error);
+  int64_t image_bytes() const { return image_bytes_; }
   void close();
   bool is_open() const override { return fd_buffered_ >= 0; }
   bool direct() const { return fd_direct_ >= 0; }
@@ -59,7 +63,10 @@ class FilePool : public ChunkStore {
   int chunk_io(bool write, void* buf, int64_t off, int64_t n) override;
 
  private:
+  int region_io(bool write, bool chunk, char* buf, int64_t off, int64_t n);
   int fd_direct_ = -1, fd_buffered_ = -1;
+  int fd_image_ = -1;            // adopt mode: read-only image holding [0, image_bytes_)
+  int64_t image_bytes_ = 0;
   int64_t bytes_ = 0;
 };
 

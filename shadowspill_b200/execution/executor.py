@@ -295,7 +295,8 @@ class Executor:
         Systems captures; no effect off the GPU).
         ``file_pool``: settings of the file-backed spill pool for plans whose homes were
         moved there (``planning.plan.move_homes_to_file``): ``directory`` or ``image``
-        (+ ``create_image``) or ``remote`` ("host:port" of a memory daemon), optional
+        (+ ``create_image``, or ``adopt_image`` with a ``directory``: the image is read-only and
+        holds the pool's first bytes) or ``remote`` ("host:port" of a memory daemon), optional
         ``chunk_bytes`` / ``queue_depth`` / ``io_threads``.
         ``collectives``: ``peer`` (own kernels over a symmetric device pool),
         ``dist`` (torch.distributed: NCCL or gloo) or ``auto`` (peer on GPUs).
@@ -365,6 +366,7 @@ class Executor:
                           device_pool=pool, file_bytes=file_bytes,
                           file_directory=str(fp.get("directory", "")), file_image=str(fp.get("image", "")),
                           file_create_image=bool(fp.get("create_image", False)),
+                          file_adopt_image=bool(fp.get("adopt_image", False)),
                           file_chunk_bytes=int(fp.get("chunk_bytes", 0)),
                           file_queue_depth=int(fp.get("queue_depth", 0)),
                           file_io_threads=int(fp.get("io_threads", 0)),

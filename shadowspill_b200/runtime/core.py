@@ -55,14 +55,17 @@ class Runtime:
                  device_pool: torch.Tensor | None = None, file_bytes: int = 0,
                  file_directory: str = "", file_image: str = "", file_create_image: bool = False,
                  file_chunk_bytes: int = 0, file_queue_depth: int = 0, file_io_threads: int = 0,
-                 remote_address: str = ""):
+                 remote_address: str = "", file_adopt_image: bool = False):
         """``device_pool``: a caller-owned uint8 tensor to use as the device pool
         (a symmetric-memory allocation for multi-GPU plans); it must outlive the runtime.
         ``file_bytes > 0`` adds a file-backed spill pool in ``file_directory`` (an unlinked
         scratch file) or in the kept file ``file_image``; objects homed there move through
         pinned staging rings of ``file_queue_depth`` chunks of ``file_chunk_bytes``.
         ``remote_address`` ("host:port" of an ``ss_memory_daemon``) keeps those bytes in the
-        daemon's memory instead of a local file."""
+        daemon's memory instead of a local file. ``file_adopt_image`` opens an existing
+        ``file_image`` read-only as the pool's first bytes (the rest is a scratch file in
+        ``file_directory``): state imported into the image can be read by many runs, and any
+        transfer that would write into it fails."""
         self.lib = native.core()
         self.backend_name = backend
         self.device_index = device_index
@@ -87,12 +90,15 @@ class Runtime:
             self._external_pool = device_pool
         if file_bytes > 0 and not (file_directory or file_image or remote_address):
             raise ValueError("a file pool needs a directory, an image path or a daemon address")
+        if file_adopt_image and not (file_image and file_directory):
+            raise ValueError("adopting an image needs the image and a directory for the scratch part")
         if file_chunk_bytes % 4096:
             raise ValueError("file_chunk_bytes must be a multiple of 4096")
         cfg = native.RuntimeConfig(int(device_bytes), int(spill_bytes), numa_node,
                                    int(trace_capacity), 1000, 0, 0, external,
                                    int(file_bytes), str(file_directory).encode() or None,
-                                   str(file_image).encode() or None, int(bool(file_create_image)),
+                                   str(file_image).encode() or None,
+                                   2 if file_adopt_image else int(bool(file_create_image)),
                                    int(file_queue_depth), int(file_chunk_bytes),
                                    int(file_io_threads), 0, str(remote_address).encode() or None)
         self.file_bytes = int(file_bytes)

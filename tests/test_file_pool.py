@@ -113,6 +113,46 @@ def test_a_kept_image_carries_state_to_the_next_run(tmp_path):
     assert first + [more] == ref_losses
 
 
+def test_an_adopted_image_is_read_in_place_and_never_written(tmp_path):
+    cfg, plan, desc = _setup()
+    filed = move_homes_to_file(plan)
+    image = tmp_path / "pool.img"
+    ex = Executor(copy.deepcopy(filed), desc, device="cpu", seed=1,
+                  file_pool={"image": str(image), "create_image": True})
+    ex.initialize()
+    ex.run(_batches(cfg))
+    state = ex.state_dict()
+    ex.close()
+    size = image.stat().st_size
+    digest = __import__("hashlib").sha256(image.read_bytes()).hexdigest()
+    scratch = tmp_path / "scratch"
+    scratch.mkdir()
+    ex = Executor(copy.deepcopy(filed), desc, device="cpu", seed=1,
+                  file_pool={"image": str(image), "adopt_image": True, "directory": str(scratch)})
+    for k, v in ex.state_dict().items():            # the imported state is readable in place
+        assert torch.equal(v, state[k]), k
+    with pytest.raises((RuntimeFailure, native.NativeError)):
+        ex.run(_batches(cfg, 1))                    # training writes its state back: refused
+    info = ex.rt.failure()
+    assert info is not None and info["pool"] == 2
+    ex.closed = True
+    ex.rt.close()
+    assert image.stat().st_size == size and __import__("hashlib").sha256(image.read_bytes()).hexdigest() == digest
+    # a pool larger than the image: the part beyond it is scratch and writable
+    rt = Runtime(1 << 20, 4096, backend="mock", file_bytes=size + (1 << 20), file_image=str(image),
+                 file_adopt_image=True, file_directory=str(scratch))
+    blob = torch.arange(5000, dtype=torch.int32)
+    rt.file_write(size + 4096, blob)
+    assert torch.equal(rt.file_read(size + 4096, 20000).view(torch.int32), blob)
+    straddle = rt.file_read(size - 8, 16)           # a read across the boundary comes from both files
+    assert straddle.numel() == 16
+    with pytest.raises(native.NativeError):
+        rt.file_write(size - 8, blob)               # touches the image: refused
+    rt.close()
+    with pytest.raises(ValueError):
+        Runtime(1 << 20, 4096, backend="mock", file_bytes=size, file_image=str(image), file_adopt_image=True)
+
+
 def test_a_failed_host_copy_in_a_staged_lane_latches(tmp_path):
     cfg, plan, desc = _setup()
     ex = Executor(move_homes_to_file(plan), desc, device="cpu", seed=1,
