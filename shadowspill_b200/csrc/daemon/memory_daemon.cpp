@@ -119,11 +119,11 @@ void serve(int fd) {
       }
       if (!reply(fd, region ? "OK " + std::to_string(region->bytes) + "\n" : "ERR no such region\n")) break;
     } else if (!std::strcmp(verb, "WRITE") && fields >= 3) {
-      if (!region || a < 0 || b < 0 || a + b > region->bytes) { reply(fd, "ERR range\n"); break; }
+      if (!region || a < 0 || b < 0 || b > region->bytes || a > region->bytes - b) { reply(fd, "ERR range\n"); break; }
       if (!recv_all(fd, region->base + a, b)) break;
       if (!reply(fd, "OK\n")) break;
     } else if (!std::strcmp(verb, "READ") && fields >= 3) {
-      if (!region || a < 0 || b < 0 || a + b > region->bytes) { reply(fd, "ERR range\n"); break; }
+      if (!region || a < 0 || b < 0 || b > region->bytes || a > region->bytes - b) { reply(fd, "ERR range\n"); break; }
       if (!reply(fd, "OK " + std::to_string(b) + "\n")) break;
       if (!send_all(fd, region->base + a, b)) break;
     } else if (!std::strcmp(verb, "FREE") && fields >= 2) {

@@ -138,15 +138,18 @@ class PeerCollectives:
         self.replica_base = self.global_rank - self.shard_rank
         self.world, self.rank = self.total, self.global_rank      # barrier and peer tables span the job
         self.pool = pool
+        _keep_multicast_unbound()
         self.handle = symm_mem.rendezvous(pool, self.group.group_name)
         self.bases = [int(p) for p in self.handle.buffer_ptrs]
         self.local_base = pool.data_ptr()
-        # NVSwitch multicast view of the pool (0 when the fabric or the driver has none). Off unless
-        # SS_NVLS=1: a rank that dies while bound to a multicast object can fault its peers, so
-        # the in-switch reduction is opted into by jobs that do not expect rank loss.
-        import os
+        # NVSwitch multicast view of the pool (0 when the fabric or the driver has none). Without
+        # SS_NVLS=1 no multicast object may exist at all (see _keep_multicast_unbound): the
+        # in-switch reduction is opted into by jobs that do not expect rank loss.
         mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
-        self.mc_base = mc if os.environ.get("SS_NVLS", "0") == "1" else 0
+        if not nvls_requested() and mc != 0:
+            raise RuntimeError("the symmetric pool was bound to an NVSwitch multicast object although "
+                               "SS_NVLS is not set; refusing to run with rank-loss handling invalid")
+        self.mc_base = mc if nvls_requested() else 0
         if self.bases[self.rank] != self.local_base:
             raise RuntimeError("symmetric pool base does not match the local tensor")
         self.flags = symm_mem.empty(64, dtype=torch.int32, device=pool.device)
@@ -226,8 +229,25 @@ class PeerCollectives:
             _lib.stream_ptr()), "ss_rs_adamw")
 
 
+def nvls_requested() -> bool:
+    """``SS_NVLS=1`` opts a job into NVSwitch multicast (in-switch gradient sums)."""
+    import os
+    return os.environ.get("SS_NVLS", "0") == "1"
+
+
+def _keep_multicast_unbound() -> None:
+    """Unless the job asked for NVSwitch multicast, tell the symmetric-memory allocator not to
+    create a multicast object at rendezvous. A rank that dies while its memory is bound to one
+    can raise NVLink faults on its peers' GPUs, so rank-loss handling (a worker that crashes or
+    is killed) is only valid with the binding off. Must run before the first rendezvous."""
+    import os
+    if not nvls_requested():
+        os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"
+
+
 def allocate_symmetric_pool(nbytes: int, device: torch.device) -> torch.Tensor:
     import torch.distributed._symmetric_memory as symm_mem
+    _keep_multicast_unbound()
     return symm_mem.empty(int(nbytes), dtype=torch.uint8, device=device)
 
 

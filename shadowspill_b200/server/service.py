@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import json
 import os
+import re
 import threading
 import time
 import traceback
@@ -30,6 +31,14 @@ from ..training.group import WorkerFailure, WorkerGroup
 from .journal import Journal
 
 GIB = 1 << 30
+_NAME = re.compile(r"^[A-Za-z0-9._-]+$")
+
+
+def safe_name(name: Any, what: str) -> str:
+    """A client-supplied name that becomes one path component under the service root."""
+    if not isinstance(name, str) or not _NAME.match(name) or name in (".", ".."):
+        raise ValueError(f"{what} name {name!r} is not allowed: use letters, digits, '.', '_' and '-'")
+    return name
 
 
 class LiveRun:
@@ -124,11 +133,17 @@ class LiveRun:
             payloads = [encode_microbatches(part) for part in route(mbs, w, per)]
         if op in ("save", "export"):
             name = args.get("name") or uuid.uuid4().hex[:8]
-            args["directory"] = str(self.server.root / "checkpoints" / self.session / name)
+            try:
+                args["directory"] = str(self.server.checkpoint_directory(self.session, name))
+            except ValueError as exc:           # refused before any worker hears of it
+                raise WorkerFailure(str(exc), "not_started") from None
             self.checkpoints[name] = args["directory"]
             op_worker = "save"
         elif op == "restore":
-            args["directory"] = self.server.resolve_checkpoint(self.session, args["name"])
+            try:
+                args["directory"] = self.server.resolve_checkpoint(self.session, args["name"])
+            except (ValueError, FileNotFoundError) as exc:
+                raise WorkerFailure(str(exc), "not_started") from None
             op_worker = "restore"
         elif op == "plan_report":
             args["directory"] = str(self.dir / "plan_report")
@@ -221,6 +236,9 @@ class Server:
     # ------------------------------------------------------------------ lifecycle
     def start(self) -> "Server":
         from .http import make_handler
+        if not self.token and self.host not in ("127.0.0.1", "localhost", "::1"):
+            raise ValueError("a service that listens beyond loopback needs a bearer token "
+                             "(token=... or SHADOWSPILL_TOKEN)")
         self.httpd = ThreadingHTTPServer((self.host, self.port), make_handler(self))
         self.httpd.daemon_threads = True
         self.port = self.httpd.server_address[1]
@@ -260,6 +278,7 @@ class Server:
 
     # ------------------------------------------------------------------ helpers used by routes
     def create_run(self, session: str, body: dict[str, Any]) -> LiveRun:
+        safe_name(session, "session")
         run = uuid.uuid4().hex[:10]
         live = LiveRun(self, session, run, body)
         self.runs[(session, run)] = live
@@ -272,23 +291,27 @@ class Server:
         except KeyError:
             raise KeyError(f"no run {session}/{run}") from None
 
+    def checkpoint_directory(self, session: str, name: str) -> Path:
+        """``<root>/checkpoints/<session>/<name>`` for names made of letters, digits, ``.``,
+        ``_`` and ``-`` only. Anything else (a separator, ``..``, an absolute path) is refused,
+        so a client can neither write nor read outside its own session's checkpoints."""
+        base = (self.root / "checkpoints" / safe_name(session, "session")).resolve()
+        path = (base / safe_name(name, "checkpoint")).resolve()
+        if not path.is_relative_to(base):
+            raise ValueError(f"checkpoint name {name!r} leaves the session's directory")
+        return path
+
     def resolve_checkpoint(self, session: str, name: str) -> str:
-        p = Path(name)
-        if p.is_absolute() and p.exists():
-            return str(p)
-        for cand in (self.root / "checkpoints" / session / name,):
-            if cand.exists():
-                return str(cand)
-        found = list((self.root / "checkpoints").glob(f"*/{name}"))
-        if found:
-            return str(found[0])
-        raise FileNotFoundError(f"no checkpoint {name!r}")
+        path = self.checkpoint_directory(session, name)
+        if not path.exists():
+            raise FileNotFoundError(f"no checkpoint {name!r} in session {session!r}")
+        return str(path)
 
     def unpack_artifact(self, artifact: str) -> Path:
         """Extracts an uploaded, sealed TAR artifact under the artifact store and returns the
         directory that holds its ``*.safetensors`` files."""
         import tarfile
-        src = self.root / "artifacts" / artifact
+        src = self.root / "artifacts" / safe_name(artifact, "artifact")
         if not src.exists():
             raise FileNotFoundError(f"no sealed artifact {artifact!r}")
         dst = self.root / "artifacts" / f"{artifact}.d"

@@ -122,11 +122,17 @@ class WorkerGroup:
                 chan.send({"type": "shutdown"})
             except ChannelClosed:
                 pass
+        from ..parallel.collectives import nvls_requested
         for proc in self.procs:
             try:
                 proc.wait(timeout=30)
             except subprocess.TimeoutExpired:
-                proc.kill()
+                if nvls_requested():
+                    # memory bound to an NVSwitch multicast object: a killed rank can fault its
+                    # peers' GPUs, so wait for the rank to leave between steps on its own
+                    proc.wait()
+                else:
+                    proc.kill()
         for chan in self.chans:
             chan.close()
         self.procs, self.chans = [], []

@@ -48,10 +48,15 @@ def test_archive_layout_and_resume(tmp_path):
     assert names[0] == "tensors/0" and all(n.startswith("tensors/") for n in names[:-2])
     m = read_manifest(path)
     assert m["format"] == "shadowspill.checkpoint" and m["version"] == 1
-    assert m["metadata"]["completed_updates"] == 2 and m["weights"] == "compute"
+    assert m["metadata"]["completed_updates"] == 2 and m["weights"] == "master"
     e = m["tensors"][0]
-    assert {"name", "shape", "dtype", "stride", "storage_offset", "storage_elements", "region",
-            "member", "bytes", "blake3"} <= set(e)
+    # the reference's entry schema: str(torch.dtype), no region keys for a whole storage
+    assert set(e) == {"name", "shape", "dtype", "stride", "storage_offset", "storage_elements",
+                      "member", "bytes", "blake3"}
+    assert e["dtype"] == "torch.float32" and m["additional_programs"] == {}
+    assert "logical_ranks" not in m
+    streams = m["metadata"]["random_streams"]
+    assert {s["identity"]["component_path"][2] for s in streams} == {"python", "numpy", "torch"}
     assert path.stat().st_size % 512 == 0
     # ---- resume: a fresh executor continues exactly where the first one goes next
     b = Executor(plan, desc, device="cpu", seed=99, hyper=hyper)
@@ -162,11 +167,13 @@ def test_expert_banks_are_recorded_in_global_coordinates():
     assert a["shape"] == b["shape"] == [cfg.n_experts, 2 * cfg.d_expert, cfg.d_model]
     total = math.prod(a["shape"])
     assert a["storage_elements"] == total
-    assert a["region"] == [0, total // 2] and b["region"] == [total // 2, total // 2]
+    from shadowspill_b200.checkpoint.save import entry_region
+    assert entry_region(a) == (0, total // 2) and entry_region(b) == (total // 2, total // 2)
+    assert (b["region_offset"], b["region_elements"]) == (total // 2, total // 2)
     # dense tensors of the same stage are still cut into flat shards
-    d0, d1 = per_rank[0]["layer0.wq"], per_rank[1]["layer0.wq"]
-    assert d0["region"][0] == 0 and d1["region"][0] == d0["region"][1]
-    assert d0["region"][1] + d1["region"][1] == d0["storage_elements"]
+    d0, d1 = (entry_region(per_rank[r]["layer0.wq"]) for r in range(2))
+    assert d0[0] == 0 and d1[0] == d0[1]
+    assert d0[1] + d1[1] == per_rank[0]["layer0.wq"]["storage_elements"]
 
 
 def test_master_copies_travel_with_the_checkpoint(tmp_path):
@@ -190,7 +197,10 @@ def test_master_copies_travel_with_the_checkpoint(tmp_path):
         a.run(_batches(cfg, s))
     save_checkpoint(a, tmp_path / "ck")
     names = {e["name"] for e in read_manifest(tmp_path / "ck" / "rank0.tar")["tensors"]}
+    # the masters are saved, the bf16 copies are derived from them on load
     assert "master.layer0.wqkv" in names and "exp_avg.layer0.wqkv" in names
+    assert "layer0.wqkv" not in names
+    assert "layer0.wqkv" in read_manifest(tmp_path / "ck" / "rank0.tar")["derived_tensors"]
     want = [a.run(_batches(cfg, s)).loss for s in (3, 4)]
     state = a.state_dict()
     a.close()
@@ -202,3 +212,79 @@ def test_master_copies_travel_with_the_checkpoint(tmp_path):
         assert torch.equal(v, state[k]), k
     b.close()
     assert not any(k.startswith("master.") for k in export_weights(tmp_path / "ck"))
+
+
+def test_reference_geometry_entries_load(tmp_path):
+    """An archive whose entries carry exactly the reference's geometry keys (``torch.``-prefixed
+    dtype, optional region_offset / region_elements, no ``region``, no ``logical_ranks``) loads."""
+    from shadowspill_b200.checkpoint.archive import FORMAT, VERSION, ArchiveWriter
+    from shadowspill_b200.checkpoint.save import state_entries, state_identity
+    cfg, plan, desc = _setup()
+    a = Executor(plan, desc, device="cpu", seed=5)
+    a.initialize()
+    a.run(_batches(cfg, 0))
+    want = a.state_dict()
+    views = dict(a.named_tensors(writable=False))
+    w = ArchiveWriter(tmp_path / "ref" / "rank0.tar")
+    entries = []
+    for e in state_entries(a):
+        flat = views[e["name"]].reshape(-1)
+        entry = {"name": e["name"], "shape": e["shape"], "dtype": str(flat.dtype),
+                 "stride": e["stride"], "storage_offset": 0, "storage_elements": flat.numel()}
+        entries.append(entry)
+        w.add_tensor(entry, flat.view(torch.uint8).numpy())
+    w.finish({"format": FORMAT, "version": VERSION, "byteorder": sys.byteorder,
+              "state": state_identity(entries, 1), "program": "0" * 64, "logical_rank": 0,
+              "additional_programs": {"forward": "1" * 64}, "metadata": {"completed_updates": 1},
+              "frozen_state_id": None, "omitted_parameters": [], "weights": "master",
+              "derived_tensors": [], "gathered_tensors": [], "retained_weight_copies": []})
+    b = Executor(plan, desc, device="cpu", seed=77)
+    b.initialize()
+    load_checkpoint(b, tmp_path / "ref")
+    assert b.completed_updates == 1
+    for k, v in b.state_dict().items():
+        assert torch.equal(v, want[k]), k
+    a.close(); b.close()
+
+
+def test_frozen_base_is_omitted_and_generators_resume(tmp_path):
+    """With a ``frozen_state_id`` a LoRA checkpoint holds only the adapters and their moments; it
+    loads only under the same id, and the default generators continue where they were saved."""
+    import random
+
+    import numpy as np
+    from shadowspill_b200.communication.info import CommunicationInfo
+    from shadowspill_b200.frontend.capture import BatchGeometry, StepDataOrdering, build_step
+    from shadowspill_b200.models.config import preset
+    from shadowspill_b200.models.lora import LoRAConfig
+    from shadowspill_b200.planning.plan import MemoryBudgets, SearchOptions, plan_program
+    cfg = preset("llama3-tiny")
+    geo = BatchGeometry(microbatch_tokens=256, n_microbatches=2, slots=16, mean_seqlen=64)
+
+    def make(seed):
+        prog, desc = build_step(cfg, geo, StepDataOrdering(), dtype=torch.float32, lora=LoRAConfig(rank=8))
+        plan = plan_program(prog, MemoryBudgets(64 << 20, 128 << 20, headroom_bytes=0), CommunicationInfo(),
+                            SearchOptions(minimum_object_bytes_evict_eligible=1024, workers=1))
+        ex = Executor(plan, desc, device="cpu", seed=seed, hyper=Hyperparameters(lr=1e-3))
+        ex.initialize()
+        return ex
+    a = make(5)
+    a.run(_batches(cfg, 0))
+    full = save_checkpoint(a, tmp_path / "full")
+    slim = save_checkpoint(a, tmp_path / "slim", frozen_state_id="base-v1")
+    m = read_manifest(slim)
+    names = {e["name"] for e in m["tensors"]}
+    assert m["frozen_state_id"] == "base-v1" and "embed.embed" in m["omitted_parameters"]
+    assert not names & set(m["omitted_parameters"]) and any("lora" in n for n in names)
+    assert slim.stat().st_size < full.stat().st_size / 4
+    draws = (random.random(), float(np.random.rand()), float(torch.rand(1)))
+    b = make(5)                      # same seed = same frozen base
+    with pytest.raises(CheckpointError):
+        load_checkpoint(b, tmp_path / "slim")
+    with pytest.raises(CheckpointError):
+        load_checkpoint(b, tmp_path / "slim", frozen_state_id="another")
+    load_checkpoint(b, tmp_path / "slim", frozen_state_id="base-v1")
+    assert (random.random(), float(np.random.rand()), float(torch.rand(1))) == draws
+    sa, sb = a.state_dict(), b.state_dict()
+    assert all(torch.equal(sa[k], sb[k]) for k in sa)
+    a.close(); b.close()

@@ -335,3 +335,27 @@ def test_node_daemon_routes(service):
     with ServiceClient(service.url, token="secret") as svc:
         assert "node-x" in svc.list_hardware().result()["members"]
     assert t.request("POST", "/v1/nodes/leave", {"node_id": "node-x", "incarnation": inc})[1]["ok"]
+
+
+def test_checkpoint_and_artifact_names_stay_inside_the_service_root(tmp_path):
+    """Client-supplied names become single path components: separators, ``..`` and absolute
+    paths are refused for checkpoints, sessions and artifacts, and a restore looks only inside
+    its own session's directory."""
+    from shadowspill_b200.server.service import Server, safe_name
+    srv = Server(tmp_path / "root")
+    good = srv.checkpoint_directory("sess-1", "after_5.v2")
+    assert good == (tmp_path / "root" / "checkpoints" / "sess-1" / "after_5.v2").resolve()
+    for bad in ("../../x", "..", ".", "/etc/passwd", "a/b", "", "x y", "a\\b", None):
+        with pytest.raises(ValueError):
+            srv.checkpoint_directory("sess-1", bad)
+        with pytest.raises(ValueError):
+            srv.checkpoint_directory(bad, "ok")
+        with pytest.raises(ValueError):
+            safe_name(bad, "artifact")
+    other = tmp_path / "root" / "checkpoints" / "other" / "ck"
+    other.mkdir(parents=True)
+    with pytest.raises(FileNotFoundError):
+        srv.resolve_checkpoint("sess-1", "ck")          # another session's checkpoint
+    assert srv.resolve_checkpoint("other", "ck") == str(other.resolve())
+    with pytest.raises(ValueError):
+        srv.unpack_artifact("../checkpoints")
