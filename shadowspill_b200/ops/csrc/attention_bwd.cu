@@ -584,19 +584,13 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (warp == BW_MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
-template <typename K>
-static int set_smem(K kern, int bytes) {
-  return static_cast<int>(
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-}
-
 template <int DH, int BKV, int KVS>
 static int launch_dq(const CUtensorMap& tq, const CUtensorMap& tdo, const CUtensorMap& tk,
                      const CUtensorMap& tv, const AttnBwdParams& p, int tiles, cudaStream_t s) {
   using Cfg = DqCfg<DH, BKV, KVS>;
   auto kern = attn_bwd_dq_kernel<DH, BKV, KVS>;
-  static bool done = false;
-  if (!done) { if (int e = set_smem(kern, Cfg::SMEM)) return e; done = true; }
+  static SmemOptIn opt_in;
+  if (int e = opt_in.ensure(kern, Cfg::SMEM)) return e;
   kern<<<dim3(tiles, p.Hq), BW_THREADS, Cfg::SMEM, s>>>(tq, tdo, tk, tv, p);
   return static_cast<int>(cudaGetLastError());
 }
@@ -606,8 +600,8 @@ static int launch_dkv(const CUtensorMap& tq, const CUtensorMap& tdo, const CUten
                       const CUtensorMap& tv, const AttnBwdParams& p, int tiles, cudaStream_t s) {
   using Cfg = DkvCfg<DH, QS, MODE>;
   auto kern = attn_bwd_dkv_kernel<DH, QS, MODE>;
-  static bool done = false;
-  if (!done) { if (int e = set_smem(kern, Cfg::SMEM)) return e; done = true; }
+  static SmemOptIn opt_in;
+  if (int e = opt_in.ensure(kern, Cfg::SMEM)) return e;
   kern<<<dim3(tiles, p.Hkv), BW_THREADS, Cfg::SMEM, s>>>(tq, tdo, tk, tv, p);
   return static_cast<int>(cudaGetLastError());
 }
@@ -710,8 +704,23 @@ extern "C" int ss_attn_bwd_noalloc(const void* q, const void* k, const void* v, 
                                    long long ldq, long long ldk, long long ldv, long long ldo,
                                    float scale, int* status, void* stream) {
   if (T <= 0 || nseq <= 0) return 0;
-  if (Hq <= 0 || static_cast<long long>(Hq) * T > SS_ATTN_NOALLOC_MAX_ELEMENTS)
+  if (Hq <= 0 || Hkv <= 0) return -2;          // the same answer ss_attn_bwd gives
+  if (static_cast<long long>(Hq) * T > SS_ATTN_NOALLOC_MAX_ELEMENTS)
     return SS_ATTN_NOALLOC_TOO_LARGE;
+  // The scratch array handed to the kernels is the CURRENT device's copy. If the operands
+  // live on another GPU the kernels would run there (the tensor-map set-up binds the
+  // operands' device) with this GPU's array: refuse instead.
+  {
+    int current = -1;
+    if (cudaGetDevice(&current) != cudaSuccess) return SS_ATTN_NOALLOC_BAD_DEVICE;
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, dq) != cudaSuccess) {
+      cudaGetLastError();
+      return SS_ATTN_NOALLOC_BAD_DEVICE;
+    }
+    if (attr.type != cudaMemoryTypeDevice || attr.device != current)
+      return SS_ATTN_NOALLOC_BAD_DEVICE;
+  }
   float* scratch = nullptr;
   if (int rc = ss::scratch_for_current_device(&scratch)) return rc;
   return ss_attn_bwd(q, k, v, out, lse, dout, dq, dk, dv, cu_seqlens, scratch, nseq, T, Hq, Hkv,

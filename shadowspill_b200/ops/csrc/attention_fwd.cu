@@ -340,12 +340,8 @@ static int launch_fwd(const void* q, const void* k, const void* v, AttnParams p,
   if ((r = make_tmap_bf16(&tk, k, p.T, static_cast<long long>(p.Hkv) * DH, ldk, BKV))) return r;
   if ((r = make_tmap_bf16(&tv, v, p.T, static_cast<long long>(p.Hkv) * DH, ldv, BKV))) return r;
   auto kern = attn_fwd_kernel<DH, BKV>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  static SmemOptIn opt_in;
+  if (int e = opt_in.ensure(kern, Cfg::SMEM)) return e;
   dim3 grid(max_tiles, p.Hq);
   kern<<<grid, ATT_THREADS, Cfg::SMEM, stream>>>(tq, tk, tv, p);
   return static_cast<int>(cudaGetLastError());

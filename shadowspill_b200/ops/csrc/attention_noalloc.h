@@ -20,16 +20,20 @@
  *  - Hq * T must not exceed SS_ATTN_NOALLOC_MAX_ELEMENTS; larger problems are
  *    refused with SS_ATTN_NOALLOC_TOO_LARGE and nothing is launched. Use
  *    ss_attn_bwd with your own scratch for those.
+ *  - Every call must be made with the operands' device current: the scratch
+ *    used is the current device's copy of the array, and a call whose `dq` lives
+ *    on another GPU (or is not device memory) is refused with
+ *    SS_ATTN_NOALLOC_BAD_DEVICE before anything is launched.
  *  - The first call on each device looks up the array's device address (a
  *    one-time host-side query, no allocation). Make that first call outside any
- *    stream capture, with the target device current.
+ *    stream capture.
  *  - All calls on a device share the one array, and it keeps whatever the last
  *    call left in it. Each call rewrites every element it later reads, so
  *    nothing needs clearing, but two calls whose kernels may overlap on the GPU
  *    (different streams without ordering between them) race on it: keep calls
  *    on one stream, or order them with events.
  *  - Inputs, outputs, strides, status word and return codes are exactly those
- *    of ss_attn_bwd; the function calls no cudaMalloc, cudaFree or any
+ *    of ss_attn_bwd (bad head counts give -2 here too); the function calls no cudaMalloc, cudaFree or any
  *    allocating library routine.
  */
 #ifndef SS_ATTENTION_NOALLOC_H

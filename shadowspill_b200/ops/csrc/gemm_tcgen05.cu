@@ -444,14 +444,9 @@ template <int BN, bool A_MN, bool B_MN>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int num_sms,
                   cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
-  static bool configured = false;
+  static SmemOptIn opt_in;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::SMEM + Cfg::SCATTER_STAGE);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  if (int e = opt_in.ensure(kern, Cfg::SMEM + Cfg::SCATTER_STAGE)) return e;
   const int smem_bytes = Cfg::SMEM + (p.g.row_dst != nullptr ? Cfg::SCATTER_STAGE : 0);
   const long long tiles = static_cast<long long>((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) *
                           (p.g.mode == 2 ? p.g.n_experts : 1);

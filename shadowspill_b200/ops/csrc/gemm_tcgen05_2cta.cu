@@ -321,13 +321,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 template <bool A_MN, bool B_MN>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int num_sms,
                   cudaStream_t stream) {
-  static bool configured = false;
+  static SmemOptIn opt_in;
   auto kern = gemm2_bf16_kernel<A_MN, B_MN>;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  if (int e = opt_in.ensure(kern, SMEM)) return e;
   const long long tiles = static_cast<long long>((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN);
   long long pairs = num_sms / 2;
   if (tiles < pairs) pairs = tiles;

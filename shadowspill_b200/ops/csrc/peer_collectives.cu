@@ -24,7 +24,7 @@
 namespace ss {
 
 constexpr int MAX_RANKS = 16;
-constexpr unsigned long long PEER_WAIT_NS = 2000000000ull;   // 2 s
+constexpr unsigned long long PEER_WAIT_NS = 2000000000ull;   // default budget of a peer wait: 2 s
 
 struct PeerPtrs {
   void* p[MAX_RANKS];
@@ -46,8 +46,9 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 
 // Flag layout per rank: uint32 flags[MAX_RANKS]; flags[j] on rank r is written by rank j.
 // `epoch` increases by one per barrier; a rank waits until every peer's word >= epoch.
+// A wait that outlasts `wait_ns` writes KS_TIMEOUT_PEER (5) into the status word and returns.
 __global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int world, uint32_t epoch,
-                                    int* status) {
+                                    unsigned long long wait_ns, int* status) {
   const int j = threadIdx.x;
   if (j >= world) return;
   __threadfence_system();
@@ -58,7 +59,7 @@ __global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int world, uint32_
   for (uint32_t it = 0;; ++it) {
     const uint32_t v = ld_acquire_sys(mine);
     if (static_cast<int32_t>(v - epoch) >= 0) break;
-    if ((it & 0x3ff) == 0x3ff && gtime() - t0 > PEER_WAIT_NS) {
+    if ((it & 0x3f) == 0x3f && gtime() - t0 > wait_ns) {
       if (status) atomicCAS(status, 0, 5);   // KS_TIMEOUT_PEER
       break;
     }
@@ -252,13 +253,20 @@ static inline int grid_of(long long work, int threads, int cap) {
 extern "C" {
 using namespace ss;
 
-int ss_peer_barrier(void* const* flag_ptrs, int rank, int world, unsigned int epoch, int* status,
-                    void* stream) {
+// wait_ns: how long a rank waits for each peer's flag before it gives up (0 = the default, 2 s).
+int ss_peer_barrier_timed(void* const* flag_ptrs, int rank, int world, unsigned int epoch,
+                          unsigned long long wait_ns, int* status, void* stream) {
   if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) return -2;
   PeerPtrs f;
   for (int j = 0; j < world; ++j) f.p[j] = flag_ptrs[j];
-  peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f, rank, world, epoch, status);
+  peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f, rank, world, epoch,
+                                                          wait_ns ? wait_ns : PEER_WAIT_NS, status);
   return (int)cudaGetLastError();
+}
+
+int ss_peer_barrier(void* const* flag_ptrs, int rank, int world, unsigned int epoch, int* status,
+                    void* stream) {
+  return ss_peer_barrier_timed(flag_ptrs, rank, world, epoch, 0, status, stream);
 }
 
 int ss_peer_allgather(void* const* shard_ptrs, void* full, long long shard_bytes,

@@ -28,6 +28,26 @@ __device__ __forceinline__ void report(int* status, int code) {
   if (status != nullptr) atomicCAS(status, 0, code);
 }
 
+// ------------------------------------------------------------------ launch set-up
+// cudaFuncAttributeMaxDynamicSharedMemorySize belongs to a (function, device) pair, so a
+// process that drives several GPUs has to raise it once on each of them. One object of this
+// type per kernel instantiation remembers which devices are done.
+struct SmemOptIn {
+  static constexpr int kMaxDevices = 64;
+  bool done[kMaxDevices] = {};
+  template <typename K>
+  int ensure(K kern, int bytes) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev >= 0 && dev < kMaxDevices && done[dev]) return 0;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev >= 0 && dev < kMaxDevices) done[dev] = true;   // benign race: the call is idempotent
+    return 0;
+  }
+};
+
 // ------------------------------------------------------------------ small helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -216,6 +216,19 @@ def gated_delta_rule_chunked(q, k, v, beta, g, bounds: list[int] | None, chunk: 
     """q,k [T,Hk,dk] (L2-normalised), v [T,Hv,dv], beta,g [T,Hv] (g = log decay <= 0).
     QK heads are repeat-interleaved to the V heads. Returns [T,Hv,dv] in ``v.dtype``.
 
+    bf16 CUDA tensors with 128-wide heads and 64-token chunks run on the hand-written tcgen05
+    kernels of ``ops/csrc/deltanet_chunk.cu`` (forward and backward); everything else (CPU, fp32,
+    other head widths) evaluates the same algebra with PyTorch tensor operations."""
+    from . import delta_rule
+    if delta_rule.supported(q, k, v, chunk) and cu_seqlens is not None:
+        return delta_rule.gated_delta_rule(q, k, v, beta, g, cu_seqlens)
+    return _gated_delta_rule_torch(q, k, v, beta, g, bounds, chunk, cu_seqlens)
+
+
+def _gated_delta_rule_torch(q, k, v, beta, g, bounds: list[int] | None, chunk: int = 64,
+                            cu_seqlens: torch.Tensor | None = None) -> torch.Tensor:
+    """The chunked gated delta rule as PyTorch tensor operations (CPU path and oracle).
+
     The packed stream is cut into chunks of ``chunk`` tokens regardless of where sequences
     begin; sequence boundaries act through masks (no decay path and no state carry across a
     boundary), so the work and the memory are the same for every packing and there is no

@@ -28,6 +28,7 @@ from ..ops import functional as F
 
 _c = _lib
 _lib.register("ss_peer_barrier", [_c.c_p, _c.c_int, _c.c_int, C.c_uint, _c.c_p, _c.c_p])
+_lib.register("ss_peer_barrier_timed", [_c.c_p, _c.c_int, _c.c_int, C.c_uint, _c.c_ull, _c.c_p, _c.c_p])
 _lib.register("ss_peer_allgather", [_c.c_p, _c.c_p, _c.c_ll, _c.c_ll, _c.c_int, _c.c_int, _c.c_p])
 _lib.register("ss_rs_adamw", [_c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_ll, _c.c_ll, _c.c_int, _c.c_int,
                               _c.c_f, _c.c_f, _c.c_f, _c.c_f, _c.c_f, _c.c_int, _c.c_f, _c.c_ull,
@@ -157,6 +158,10 @@ class PeerCollectives:
         self.flag_handle = symm_mem.rendezvous(self.flags, self.group.group_name)
         self.flag_ptrs = (C.c_void_p * self.world)(*[int(p) for p in self.flag_handle.buffer_ptrs])
         self.epoch = 0
+        # how long a flag wait lasts before the kernel gives up with status 5 (0 = 2 s); a job
+        # that wants to notice a lost rank quickly sets SS_PEER_WAIT_MS
+        import os
+        self.wait_ns = int(float(os.environ.get("SS_PEER_WAIT_MS", "0")) * 1e6)
         torch.cuda.synchronize()
         dist.barrier(self.group)
 
@@ -168,9 +173,10 @@ class PeerCollectives:
 
     def _barrier(self) -> None:
         self.epoch += 1
-        _lib.check(_lib.lib().ss_peer_barrier(self.flag_ptrs, self.rank, self.world, self.epoch,
-                                              _lib.status_word(self.pool.device).data_ptr(),
-                                              _lib.stream_ptr()), "ss_peer_barrier")
+        _lib.check(_lib.lib().ss_peer_barrier_timed(self.flag_ptrs, self.rank, self.world, self.epoch,
+                                                    int(self.wait_ns),
+                                                    _lib.status_word(self.pool.device).data_ptr(),
+                                                    _lib.stream_ptr()), "ss_peer_barrier")
 
     barrier_begin = _barrier
     barrier_end = _barrier

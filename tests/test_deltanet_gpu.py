@@ -110,3 +110,58 @@ def test_gated_delta_rule_on_gpu_matches_token_recurrence():
     assert _rel(got.cpu(), want) < 2e-3            # TF32 products
     for name, a, b in zip("q k v beta g".split(), dev, cpu):
         assert _rel(a.grad.cpu(), b.grad) < 1e-2, name
+
+
+def _delta_case(T, Hk, Hv, bounds, seed):
+    g = torch.Generator().manual_seed(seed)
+    nrm = lambda x: x / x.norm(dim=-1, keepdim=True)
+    q = nrm(torch.randn(T, Hk, 128, generator=g)).bfloat16()
+    k = nrm(torch.randn(T, Hk, 128, generator=g)).bfloat16()
+    v = torch.randn(T, Hv, 128, generator=g).bfloat16()
+    beta = torch.sigmoid(torch.randn(T, Hv, generator=g))
+    gl = -torch.nn.functional.softplus(torch.randn(T, Hv, generator=g)) * 0.3
+    dout = (torch.randn(T, Hv, 128, generator=g) * 0.5).bfloat16()
+    cu = torch.tensor(bounds + [T] * 3, dtype=torch.int32)
+    return q, k, v, beta, gl, dout, cu
+
+
+@pytest.mark.parametrize("T,Hk,Hv,bounds", [
+    (333, 2, 4, [0, 5, 130, 131, 300, 333]),        # T not a multiple of 64, boundaries at odd offsets
+    (200, 1, 3, [0, 77, 200]),                      # three V heads per QK head: a pair and a single
+    (256, 2, 2, [0, 64, 191, 256]),                 # one V head per QK head, a boundary on a chunk edge
+])
+def test_delta_rule_kernels_match_the_token_recurrence(T, Hk, Hv, bounds):
+    """The tcgen05 chunk kernels (forward and every gradient) against the token-by-token
+    recurrence evaluated in fp32 on the CPU from the same bf16 inputs."""
+    from shadowspill_b200.ops import _lib, delta_rule, reference as ref
+    q, k, v, beta, gl, dout, cu = _delta_case(T, Hk, Hv, bounds, seed=T)
+    cpu = [t.float().clone().requires_grad_(True) for t in (q, k, v, beta, gl)]
+    want = ref.gated_delta_rule(*cpu, torch.tensor(bounds))
+    want.backward(dout.float())
+    dev = [t.clone().cuda().requires_grad_(True) for t in (q, k, v, beta, gl)]
+    assert delta_rule.supported(dev[0], dev[1], dev[2])
+    got = seq.gated_delta_rule_chunked(*dev, None, 64, cu_seqlens=cu.cuda())
+    got.backward(dout.cuda())
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert _rel(got.cpu(), want) < 1.5e-2                      # bf16 operands, fp32 accumulation
+    for name, a, b in zip("q k v beta g".split(), dev, cpu):
+        assert _rel(a.grad.cpu(), b.grad) < 3e-2, name
+
+
+def test_delta_rule_kernels_at_the_model_head_counts():
+    """16 QK heads, 32 V heads (the 9B configuration), against the PyTorch chunked form on the GPU."""
+    from shadowspill_b200.ops import _lib
+    T, bounds = 640, [0, 1, 250, 577, 640]
+    q, k, v, beta, gl, dout, cu = _delta_case(T, 16, 32, bounds, seed=3)
+    a = [t.clone().cuda().requires_grad_(True) for t in (q, k, v, beta, gl)]
+    b = [t.clone().cuda().float().requires_grad_(True) for t in (q, k, v, beta, gl)]
+    got = seq.gated_delta_rule_chunked(*a, None, 64, cu_seqlens=cu.cuda())
+    want = seq._gated_delta_rule_torch(*b, None, 64, cu_seqlens=cu.cuda())
+    got.backward(dout.cuda())
+    want.backward(dout.cuda().float())
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert _rel(got, want) < 1.5e-2
+    for name, x, y in zip("q k v beta g".split(), a, b):
+        assert _rel(x.grad, y.grad) < 3e-2, name

@@ -57,7 +57,9 @@ def test_noalloc_matches_allocating_entry_point_on_two_calls():
         want = attention.backward(q, k, v, out, lse, dout, cu, max(lens), scale)
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         torch.cuda.synchronize()
-        before = torch.cuda.memory_allocated()
+        # the driver's own count of free device bytes sees a cudaMalloc made inside the
+        # library, which torch's allocator statistics would not
+        before, free_before = torch.cuda.memory_allocated(), torch.cuda.mem_get_info()[0]
         rc = fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
                 dout.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), cu.data_ptr(),
                 cu.numel() - 1, T, Hq, Hkv, dh, Hq * dh, Hkv * dh, Hkv * dh, Hq * dh,
@@ -65,6 +67,8 @@ def test_noalloc_matches_allocating_entry_point_on_two_calls():
         assert rc == 0
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
+        if seed > 0:      # the first call may still load the kernels' code onto the device
+            assert torch.cuda.mem_get_info()[0] == free_before
         _lib.check_status()
         for got, ref in zip((dq, dk, dv), want):
             rel = float((got.float() - ref.float()).norm() / (ref.float().norm() + 1e-12))
@@ -78,3 +82,16 @@ def test_noalloc_refuses_problems_beyond_its_array():
     rc = fn(None, None, None, None, None, None, None, None, None, None, 1, T, Hq, 1, 128,
             Hq * 128, 128, 128, Hq * 128, C.c_float(1.0), None, None)
     assert rc == -3     # SS_ATTN_NOALLOC_TOO_LARGE: nothing was launched
+    # bad head counts: the allocating entry point's own answer
+    rc = fn(None, None, None, None, None, None, None, None, None, None, 1, 128, 0, 1, 128,
+            0, 128, 128, 0, C.c_float(1.0), None, None)
+    assert rc == -2
+
+
+def test_noalloc_refuses_operands_that_are_not_on_the_current_device():
+    lib, fn = _symbol()
+    host = torch.zeros(128 * 128, dtype=torch.bfloat16)          # not device memory at all
+    rc = fn(host.data_ptr(), host.data_ptr(), host.data_ptr(), host.data_ptr(), None,
+            host.data_ptr(), host.data_ptr(), host.data_ptr(), host.data_ptr(), None, 1, 128, 1, 1,
+            128, 128, 128, 128, 128, C.c_float(1.0), None, None)
+    assert rc == -4     # SS_ATTN_NOALLOC_BAD_DEVICE: refused before any launch
