@@ -125,6 +125,9 @@ class TrainingDescription:
     # fp32 master copies of the trainable parameters: the optimizer updates them and rounds the
     # result into the model-dtype weights (unfused update path)
     master_weights: bool = False
+    # "stages": the hand-written stage classes; "graph": torch.export -> partition -> AOT graph
+    # pairs (frontend/graph_stage.py) for the models it covers, the stage classes otherwise
+    frontend: str = "stages"
 
     def __post_init__(self) -> None:
         extras = extra_fields_for(self.cfg, self.objective)
@@ -142,6 +145,16 @@ class TrainingDescription:
 
     def stages(self):
         ep = (self.world_size, self.rank) if (self.expert_parallel and self.world_size > 1) else None
+        if self.frontend == "graph":
+            from .graph_stage import build_graph_stages, supports
+            if supports(self.cfg, self.lora, ep, self.objective):
+                stages = build_graph_stages(self.cfg, self.geometry.microbatch_tokens, self.geometry.slots,
+                                            self.dtype, self.grad_dtype, self.head_block_rows)
+                for st in stages:
+                    st.min_shard_bytes = int(self.min_shard_bytes)
+                return stages
+        elif self.frontend != "stages":
+            raise ValueError(f"unknown frontend {self.frontend!r}")
         stages = build_stages(self.cfg, self.objective, self.lora, ep)
         for st in stages:
             st.min_shard_bytes = int(self.min_shard_bytes)
@@ -412,45 +425,47 @@ def build_step(cfg: DecoderConfig, geometry: BatchGeometry,
                grad_dtype=None, selection: dict[int, str] | None = None, world_size: int = 1,
                rank: int = 0, objective=None, lora=None, expert_parallel: bool = False,
                replicas: int = 1, min_shard_bytes: int = 0, head_block_rows: int = 0,
-               master_weights: bool = False):
+               master_weights: bool = False, frontend: str = "stages"):
     """Forward + backward + optimizer of one global batch. Returns ``(Program, description)``.
     ``world_size > 1`` builds the data-parallel form: weights and AdamW moments are
     stored as 1/N shards, gathered before use and updated shard-locally."""
     desc = TrainingDescription(cfg, geometry, ordering or StepDataOrdering(), dtype,
                                grad_dtype or dtype, dict(selection or {}), "step", world_size,
                                rank, objective, lora, expert_parallel, replicas, min_shard_bytes,
-                               head_block_rows, master_weights)
+                               head_block_rows, master_weights, frontend)
     return _build(desc), desc
 
 
 def build_forward_backward(cfg, geometry, ordering=None, *, dtype=torch.bfloat16, grad_dtype=None,
                            selection=None, world_size=1, rank=0, objective=None, lora=None,
-                           min_shard_bytes=0, head_block_rows=0):
+                           min_shard_bytes=0, head_block_rows=0, frontend="stages"):
     """Gradient accumulation without the update (gradients are persistent state)."""
     desc = TrainingDescription(cfg, geometry, ordering or StepDataOrdering(), dtype,
                                grad_dtype or dtype, dict(selection or {}), "forward_backward",
                                world_size, rank, objective, lora, min_shard_bytes=min_shard_bytes,
-                               head_block_rows=head_block_rows)
+                               head_block_rows=head_block_rows, frontend=frontend)
     return _build(desc), desc
 
 
 def build_forward(cfg, geometry, ordering=None, *, dtype=torch.bfloat16, world_size=1, rank=0,
-                  objective=None, lora=None, min_shard_bytes=0, head_block_rows=0):
+                  objective=None, lora=None, min_shard_bytes=0, head_block_rows=0, frontend="stages"):
     """Evaluation: forward passes and the loss only."""
     desc = TrainingDescription(cfg, geometry, ordering or StepDataOrdering(), dtype, dtype, {},
                                "forward", world_size, rank, objective, lora,
-                               min_shard_bytes=min_shard_bytes, head_block_rows=head_block_rows)
+                               min_shard_bytes=min_shard_bytes, head_block_rows=head_block_rows,
+                               frontend=frontend)
     return _build(desc), desc
 
 
 def build_optimizer(cfg, geometry, *, dtype=torch.bfloat16, grad_dtype=None, world_size=1, rank=0,
-                    objective=None, lora=None, min_shard_bytes=0, head_block_rows=0, master_weights=False):
+                    objective=None, lora=None, min_shard_bytes=0, head_block_rows=0, master_weights=False,
+                    frontend="stages"):
     """The optimizer update alone, over gradients that earlier ``forward_backward``
     invocations left in the spill pool (the ``optim_step`` operation)."""
     desc = TrainingDescription(cfg, geometry, StepDataOrdering(), dtype, grad_dtype or dtype, {},
                                "optimizer", world_size, rank, objective, lora,
                                min_shard_bytes=min_shard_bytes, head_block_rows=head_block_rows,
-                               master_weights=master_weights)
+                               master_weights=master_weights, frontend=frontend)
     return _build(desc), desc
 
 

@@ -1,0 +1,224 @@
+"""Model families as plain ``nn.Module`` trees over the ``ss`` operators.
+
+These are what the graph frontend exports: a ``DecoderLM`` is an embedding, a
+``ModuleList`` of layers (the repeated child that the partitioner turns into stages)
+and a head that returns the weighted-sum loss. Parameter names and shapes are those
+of the stage classes in :mod:`shadowspill_b200.models` (``wqkv``, ``w13``, ...), so a
+state dict, a checkpoint or a Hugging Face conversion fits either form.
+
+Reference models: packages/workloads/src/shadowspill_workloads/models/llama3/
+implementations/mlops.py:29-161 (dense), models/shared/delta_net.py:13-89 (Gated
+DeltaNet), models/qwen35/implementations/mlops.py:30-100 (gated attention).
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from ..models.config import DecoderConfig
+from . import ops as _ops  # noqa: F401  (registers torch.ops.ss)
+
+S = torch.ops.ss
+
+
+def _param(shape, init: str = "normal", std: float = 0.02, dtype=None, trainable: bool = True) -> nn.Parameter:
+    p = nn.Parameter(torch.empty(shape, dtype=dtype), requires_grad=trainable)
+    p.ss_init, p.ss_std = init, std
+    return p
+
+
+class Embedding(nn.Module):
+    def __init__(self, cfg: DecoderConfig, dtype):
+        super().__init__()
+        self.embed = _param((cfg.vocab_size, cfg.d_model), std=cfg.initializer_range, dtype=dtype)
+
+    def forward(self, tokens):
+        return S.embedding(tokens, self.embed)
+
+
+class _Norms:
+    """Shared helpers of the layer modules."""
+
+    def _norm(self, x, w):
+        c = self.cfg
+        return S.rmsnorm(x, w, c.norm_epsilon, c.zero_centered_norm)[0]
+
+    def _mlp(self, x):
+        h = self._norm(x, self.mlp_norm)
+        return x + S.linear(S.swiglu(S.linear(h, self.w13)), self.w2)
+
+
+class DenseLayer(nn.Module, _Norms):
+    """Pre-norm GQA attention + SwiGLU; q/k/v and gate/up are fused projections."""
+
+    def __init__(self, cfg: DecoderConfig, dtype):
+        super().__init__()
+        self.cfg = cfg
+        D, dh, Hq, Hkv, Ff = cfg.d_model, cfg.head_dim, cfg.n_heads, cfg.n_kv_heads, cfg.d_ff
+        std = cfg.initializer_range
+        ninit = "zeros" if cfg.zero_centered_norm else "ones"
+        self.attn_norm = _param((D,), ninit, dtype=dtype)
+        self.wqkv = _param(((Hq + 2 * Hkv) * dh, D), std=std, dtype=dtype)
+        self.wo = _param((D, Hq * dh), std=std, dtype=dtype)
+        self.mlp_norm = _param((D,), ninit, dtype=dtype)
+        self.w13 = _param((2 * Ff, D), std=std, dtype=dtype)
+        self.w2 = _param((D, Ff), std=std, dtype=dtype)
+        if cfg.qk_norm:
+            self.q_norm = _param((dh,), ninit, dtype=dtype)
+            self.k_norm = _param((dh,), ninit, dtype=dtype)
+
+    def forward(self, x, positions, cu_seqlens):
+        c = self.cfg
+        T = x.shape[0]
+        dh, Hq, Hkv = c.head_dim, c.n_heads, c.n_kv_heads
+        h = self._norm(x, self.attn_norm)
+        qkv = S.linear(h, self.wqkv)
+        if c.qk_norm:
+            qn = self._norm(qkv[:, :Hq * dh].reshape(T * Hq, dh), self.q_norm).reshape(T, Hq * dh)
+            kn = self._norm(qkv[:, Hq * dh:(Hq + Hkv) * dh].reshape(T * Hkv, dh), self.k_norm).reshape(T, Hkv * dh)
+            qkv = torch.cat([qn, kn, qkv[:, (Hq + Hkv) * dh:]], dim=1)
+        # q and k heads are adjacent in the fused projection: one rotary launch covers both
+        qkv = S.rope(qkv, positions, Hq + Hkv, dh, c.rotary_width, c.rope_base, False)
+        q = qkv[:, :Hq * dh].view(T, Hq, dh)
+        k = qkv[:, Hq * dh:(Hq + Hkv) * dh].view(T, Hkv, dh)
+        v = qkv[:, (Hq + Hkv) * dh:].view(T, Hkv, dh)
+        att, _ = S.attention(q, k, v, cu_seqlens, T)
+        x = x + S.linear(att.view(T, Hq * dh), self.wo)
+        return self._mlp(x)
+
+
+class HybridLayer(nn.Module, _Norms):
+    """Gated DeltaNet or (gated) full attention mixer + dense SwiGLU feed-forward."""
+
+    def __init__(self, cfg: DecoderConfig, index: int, dtype):
+        super().__init__()
+        self.cfg, self.index = cfg, index
+        self.mixer = cfg.layer_kind(index)
+        c, std = cfg, cfg.initializer_range
+        D, dh, Hq, Hkv = c.d_model, c.head_dim, c.n_heads, c.n_kv_heads
+        ninit = "zeros" if c.zero_centered_norm else "ones"
+        self.attn_norm = _param((D,), ninit, dtype=dtype)
+        if self.mixer == "attention":
+            self.wq = _param((Hq * dh * (2 if c.gated_attention else 1), D), std=std, dtype=dtype)
+            self.wk = _param((Hkv * dh, D), std=std, dtype=dtype)
+            self.wv = _param((Hkv * dh, D), std=std, dtype=dtype)
+            self.wo = _param((D, Hq * dh), std=std, dtype=dtype)
+            if c.qk_norm:
+                qn, kn = (Hq * dh, Hkv * dh) if c.qk_norm_full_width else (dh, dh)
+                self.q_norm = _param((qn,), ninit, dtype=dtype)
+                self.k_norm = _param((kn,), ninit, dtype=dtype)
+        else:
+            self.key_width = c.dn_qk_heads * c.dn_head_dim
+            self.value_width = c.dn_v_heads * c.dn_head_dim
+            self.conv_width = 2 * self.key_width + self.value_width
+            self.w_qkvz = _param((self.conv_width + self.value_width, D), std=std, dtype=dtype)
+            self.w_ba = _param((2 * c.dn_v_heads, D), std=std, dtype=dtype)
+            self.conv_w = _param((self.conv_width, c.dn_conv_width), std=0.3, dtype=dtype)
+            self.A_log = _param((c.dn_v_heads,), "zeros", dtype=torch.float32)
+            self.dt_bias = _param((c.dn_v_heads,), "zeros", dtype=torch.float32)
+            self.lin_norm = _param((c.dn_head_dim,), ninit, dtype=dtype)
+            self.w_out = _param((D, self.value_width), std=std, dtype=dtype)
+        self.mlp_norm = _param((D,), ninit, dtype=dtype)
+        self.w13 = _param((2 * c.d_ff, D), std=std, dtype=dtype)
+        self.w2 = _param((D, c.d_ff), std=std, dtype=dtype)
+
+    def _attention(self, h, positions, cu_seqlens):
+        c = self.cfg
+        T = h.shape[0]
+        dh, Hq, Hkv = c.head_dim, c.n_heads, c.n_kv_heads
+        qg = S.linear(h, self.wq)
+        q, gate = (qg[:, :Hq * dh], qg[:, Hq * dh:]) if c.gated_attention else (qg, None)
+        k, v = S.linear(h, self.wk), S.linear(h, self.wv)
+        if c.qk_norm and c.qk_norm_full_width:
+            q, k = self._norm(q, self.q_norm), self._norm(k, self.k_norm)
+        elif c.qk_norm:
+            q = self._norm(q.reshape(T * Hq, dh), self.q_norm).reshape(T, Hq * dh)
+            k = self._norm(k.reshape(T * Hkv, dh), self.k_norm).reshape(T, Hkv * dh)
+        q = S.rope(q, positions, Hq, dh, c.rotary_width, c.rope_base, False)
+        k = S.rope(k, positions, Hkv, dh, c.rotary_width, c.rope_base, False)
+        att, _ = S.attention(q.view(T, Hq, dh), k.view(T, Hkv, dh), v.view(T, Hkv, dh), cu_seqlens, T)
+        att = att.reshape(T, Hq * dh)
+        if gate is not None:
+            att = att * torch.sigmoid(gate.float()).to(att.dtype)
+        return S.linear(att, self.wo)
+
+    def _deltanet(self, h, positions, cu_seqlens):
+        c = self.cfg
+        T = h.shape[0]
+        Hk, Hv, dk = c.dn_qk_heads, c.dn_v_heads, c.dn_head_dim
+        kw, cw = self.key_width, self.conv_width
+        qkvz = S.linear(h, self.w_qkvz)
+        ba = S.linear(h, self.w_ba)
+        conv = S.conv_silu(qkvz[:, :cw], self.conv_w, positions, cu_seqlens)
+        q = S.l2norm(conv[:, :kw].reshape(T, Hk, dk), 1e-6)
+        k = S.l2norm(conv[:, kw:2 * kw].reshape(T, Hk, dk), 1e-6)
+        v = conv[:, 2 * kw:].reshape(T, Hv, dk)
+        beta = torch.sigmoid(ba[:, :Hv].float())
+        g = -torch.exp(self.A_log.float()) * torch.nn.functional.softplus(ba[:, Hv:].float() + self.dt_bias.float())
+        mixed = S.gated_delta_rule(q, k, v, beta, g, cu_seqlens, c.dn_chunk)
+        gate = qkvz[:, cw:].reshape(T, Hv, dk)
+        normed = S.gated_rmsnorm(mixed, gate, self.lin_norm, c.norm_epsilon, c.zero_centered_norm)
+        return S.linear(normed.reshape(T, Hv * dk), self.w_out)
+
+    def forward(self, x, positions, cu_seqlens):
+        h = self._norm(x, self.attn_norm)
+        mix = (self._attention if self.mixer == "attention" else self._deltanet)(h, positions, cu_seqlens)
+        return self._mlp(x + mix)
+
+
+class Head(nn.Module):
+    """Final norm + output projection + masked weighted-sum cross entropy in row blocks."""
+
+    def __init__(self, cfg: DecoderConfig, dtype, block_rows: int = 2048):
+        super().__init__()
+        self.cfg, self.block_rows = cfg, block_rows
+        ninit = "zeros" if cfg.zero_centered_norm else "ones"
+        self.final_norm = _param((cfg.d_model,), ninit, dtype=dtype)
+        if not cfg.tied_embeddings:
+            self.head = _param((cfg.vocab_size, cfg.d_model), std=cfg.initializer_range, dtype=dtype)
+
+    def forward(self, x, targets, weights, tied=None):
+        c = self.cfg
+        h = S.rmsnorm(x, self.final_norm, c.norm_epsilon, c.zero_centered_norm)[0]
+        W = tied if c.tied_embeddings else self.head
+        return S.head_loss(h, W, targets, weights, self.block_rows)[0]
+
+
+class DecoderLM(nn.Module):
+    """``forward(tokens, targets, weights, positions, cu_seqlens) -> loss[1]``."""
+
+    def __init__(self, cfg: DecoderConfig, dtype=torch.bfloat16, head_block_rows: int = 2048):
+        super().__init__()
+        if cfg.is_moe:
+            raise NotImplementedError("routed-expert layers run through the stage classes")
+        self.cfg = cfg
+        self.embed = Embedding(cfg, dtype)
+        layers = []
+        for i in range(cfg.n_layers):
+            plain = cfg.layer_kind(i) == "attention" and not cfg.gated_attention
+            layers.append(DenseLayer(cfg, dtype) if plain else HybridLayer(cfg, i, dtype))
+        self.layers = nn.ModuleList(layers)
+        self.head = Head(cfg, dtype, head_block_rows)
+
+    def forward(self, tokens, targets, weights, positions, cu_seqlens):
+        x = self.embed(tokens)
+        for layer in self.layers:
+            x = layer(x, positions, cu_seqlens)
+        tied = self.embed.embed if self.cfg.tied_embeddings else None
+        return self.head(x, targets, weights, tied)
+
+
+def init_(module: nn.Module, seed: int = 0) -> None:
+    """Seed-only initialisation following each parameter's ``ss_init`` / ``ss_std`` tags."""
+    gen = torch.Generator().manual_seed(seed)
+    with torch.no_grad():
+        for p in module.parameters():
+            kind = getattr(p, "ss_init", "normal")
+            if kind == "ones":
+                p.fill_(1.0)
+            elif kind == "zeros":
+                p.zero_()
+            else:
+                tmp = torch.empty(p.shape, dtype=torch.float32)
+                tmp.normal_(0.0, getattr(p, "ss_std", 0.02), generator=gen)
+                p.copy_(tmp)

@@ -1,0 +1,475 @@
+"""The op library as ``torch.library`` custom operators (namespace ``ss``).
+
+Every operator here is a functional wrapper over :mod:`shadowspill_b200.ops.functional`
+(hand-written sm_100a kernels on CUDA tensors, the plain-PyTorch definitions on CPU)
+with a fake (shape) implementation and an autograd rule, so that ``torch.export`` and
+AOTAutograd see the model as a graph of opaque stage operators whose backward pass is
+again made of ``ss`` operators. That is how the reference treats its provider
+operators (docs/integrations/mlops.md:1-21; packages/engine/src/shadowspill/pytorch/
+capture/export.py:126): the graph frontend never looks inside them.
+
+Backward operators that produce a parameter gradient (``ss::gemm`` in its
+weight-gradient form, ``ss::rmsnorm_bwd``, ``ss::embedding_bwd``, ``ss::head_loss``) have
+an ``*_into`` twin in :mod:`.graph_pairs` that writes into the stage's gradient buffer
+in place; the gradient-destination pass swaps them in
+(packages/engine/src/shadowspill/pytorch/capture/gradients/destinations.py).
+"""
+from __future__ import annotations
+
+import torch
+from torch.library import custom_op
+
+from ..ops import functional as F
+
+Tensor = torch.Tensor
+
+
+def _c(t: Tensor) -> Tensor:
+    return t if t.stride(-1) == 1 else t.contiguous()
+
+
+# ------------------------------------------------------------------------ GEMM / linear
+@custom_op("ss::gemm", mutates_args=())
+def gemm(a: Tensor, b: Tensor, a_mn: bool, b_mn: bool) -> Tensor:
+    return F.gemm(_c(a), _c(b), a_mn=a_mn, b_mn=b_mn)
+
+
+@gemm.register_fake
+def _(a, b, a_mn, b_mn):
+    M = a.shape[1] if a_mn else a.shape[0]
+    N = b.shape[1] if b_mn else b.shape[0]
+    return a.new_empty((M, N))
+
+
+@custom_op("ss::linear", mutates_args=())
+def linear(x: Tensor, w: Tensor) -> Tensor:
+    return F.linear_fwd(_c(x), w)
+
+
+@linear.register_fake
+def _(x, w):
+    return x.new_empty((x.shape[0], w.shape[0]))
+
+
+def _linear_setup(ctx, inputs, output):
+    ctx.save_for_backward(*inputs)
+
+
+def _linear_bwd(ctx, gy):
+    x, w = ctx.saved_tensors
+    dx = torch.ops.ss.gemm(gy, w, False, True) if ctx.needs_input_grad[0] else None
+    dw = torch.ops.ss.gemm(gy, x, True, True) if ctx.needs_input_grad[1] else None
+    return dx, dw
+
+
+linear.register_autograd(_linear_bwd, setup_context=_linear_setup)
+
+
+# ------------------------------------------------------------------------ RMSNorm
+@custom_op("ss::rmsnorm", mutates_args=())
+def rmsnorm(x: Tensor, w: Tensor, eps: float, zero_centered: bool) -> tuple[Tensor, Tensor]:
+    y, rstd = F.rmsnorm_fwd(x.contiguous(), w, eps, zero_centered)
+    return y, rstd
+
+
+@rmsnorm.register_fake
+def _(x, w, eps, zero_centered):
+    return torch.empty_like(x, memory_format=torch.contiguous_format), x.new_empty((x.shape[0],),
+                                                                                 dtype=torch.float32)
+
+
+@custom_op("ss::rmsnorm_bwd", mutates_args=())
+def rmsnorm_bwd(x: Tensor, w: Tensor, gy: Tensor, rstd: Tensor, zero_centered: bool) -> tuple[Tensor, Tensor]:
+    dw = torch.zeros(w.shape, dtype=torch.float32, device=x.device)
+    dx = F.rmsnorm_bwd(x.contiguous(), w, gy.contiguous(), rstd, dw, zero_centered)
+    return dx, dw
+
+
+@rmsnorm_bwd.register_fake
+def _(x, w, gy, rstd, zero_centered):
+    return torch.empty_like(x, memory_format=torch.contiguous_format), w.new_empty(w.shape, dtype=torch.float32)
+
+
+def _rmsnorm_setup(ctx, inputs, output):
+    x, w, _, zc = inputs
+    ctx.save_for_backward(x, w, output[1])
+    ctx.zc = zc
+
+
+def _rmsnorm_bwd(ctx, gy, _grstd):
+    x, w, rstd = ctx.saved_tensors
+    dx, dw = torch.ops.ss.rmsnorm_bwd(x, w, gy, rstd, ctx.zc)
+    return dx, dw, None, None
+
+
+rmsnorm.register_autograd(_rmsnorm_bwd, setup_context=_rmsnorm_setup)
+
+
+# ------------------------------------------------------------------------ rotary
+@custom_op("ss::rope", mutates_args=())
+def rope(x: Tensor, positions: Tensor, heads: int, dh: int, rot: int, theta: float,
+         inverse: bool) -> Tensor:
+    out = x.contiguous().clone()
+    F.rope_(out, positions, col0=0, heads=heads, dh=dh, rot=rot, theta=theta, inverse=inverse)
+    return out
+
+
+@rope.register_fake
+def _(x, positions, heads, dh, rot, theta, inverse):
+    return torch.empty_like(x, memory_format=torch.contiguous_format)
+
+
+def _rope_setup(ctx, inputs, output):
+    ctx.save_for_backward(inputs[1])
+    ctx.args = inputs[2:]
+
+
+def _rope_bwd(ctx, g):
+    heads, dh, rot, theta, inverse = ctx.args
+    (positions,) = ctx.saved_tensors
+    return torch.ops.ss.rope(g, positions, heads, dh, rot, theta, not inverse), None, None, None, None, None, None
+
+
+rope.register_autograd(_rope_bwd, setup_context=_rope_setup)
+
+
+# ------------------------------------------------------------------------ SwiGLU
+@custom_op("ss::swiglu", mutates_args=())
+def swiglu(gu: Tensor) -> Tensor:
+    return F.swiglu_fwd(gu.contiguous())
+
+
+@swiglu.register_fake
+def _(gu):
+    return gu.new_empty((gu.shape[0], gu.shape[1] // 2))
+
+
+@custom_op("ss::swiglu_bwd", mutates_args=())
+def swiglu_bwd(gu: Tensor, gh: Tensor) -> Tensor:
+    return F.swiglu_bwd(gu.contiguous(), gh.contiguous())
+
+
+@swiglu_bwd.register_fake
+def _(gu, gh):
+    return torch.empty_like(gu, memory_format=torch.contiguous_format)
+
+
+def _swiglu_setup(ctx, inputs, output):
+    ctx.save_for_backward(inputs[0])
+
+
+def _swiglu_bwd(ctx, gh):
+    return torch.ops.ss.swiglu_bwd(ctx.saved_tensors[0], gh)
+
+
+swiglu.register_autograd(_swiglu_bwd, setup_context=_swiglu_setup)
+
+
+# ------------------------------------------------------------------------ attention
+@custom_op("ss::attention", mutates_args=())
+def attention(q: Tensor, k: Tensor, v: Tensor, cu_seqlens: Tensor, max_seqlen: int) -> tuple[Tensor, Tensor]:
+    out, lse = F.attention_varlen(q, k, v, cu_seqlens, max_seqlen)
+    return out, lse
+
+
+@attention.register_fake
+def _(q, k, v, cu_seqlens, max_seqlen):
+    return q.new_empty(q.shape), q.new_empty((q.shape[1], q.shape[0]), dtype=torch.float32)
+
+
+@custom_op("ss::attention_bwd", mutates_args=())
+def attention_bwd(q: Tensor, k: Tensor, v: Tensor, out: Tensor, lse: Tensor, dout: Tensor,
+                  cu_seqlens: Tensor, max_seqlen: int) -> tuple[Tensor, Tensor, Tensor]:
+    dq, dk, dv = F.attention_varlen_bwd(q, k, v, out, lse, dout.contiguous(), cu_seqlens, max_seqlen)
+    return dq, dk, dv
+
+
+@attention_bwd.register_fake
+def _(q, k, v, out, lse, dout, cu_seqlens, max_seqlen):
+    return q.new_empty(q.shape), k.new_empty(k.shape), v.new_empty(v.shape)
+
+
+def _attention_setup(ctx, inputs, output):
+    q, k, v, cu, ms = inputs
+    ctx.save_for_backward(q, k, v, output[0], output[1], cu)
+    ctx.max_seqlen = ms
+
+
+def _attention_bwd(ctx, dout, _dlse):
+    q, k, v, out, lse, cu = ctx.saved_tensors
+    dq, dk, dv = torch.ops.ss.attention_bwd(q, k, v, out, lse, dout, cu, ctx.max_seqlen)
+    return dq, dk, dv, None, None
+
+
+attention.register_autograd(_attention_bwd, setup_context=_attention_setup)
+
+
+# ------------------------------------------------------------------------ embedding
+@custom_op("ss::embedding", mutates_args=())
+def embedding(ids: Tensor, W: Tensor) -> Tensor:
+    return F.embedding_fwd(ids, W)
+
+
+@embedding.register_fake
+def _(ids, W):
+    return W.new_empty((ids.numel(), W.shape[1]))
+
+
+@custom_op("ss::embedding_bwd", mutates_args=())
+def embedding_bwd(ids: Tensor, g: Tensor, rows: int) -> Tensor:
+    dW = torch.zeros((rows, g.shape[1]), dtype=g.dtype, device=g.device)
+    F.embedding_bwd(ids, g.contiguous(), dW)
+    return dW
+
+
+@embedding_bwd.register_fake
+def _(ids, g, rows):
+    return g.new_empty((rows, g.shape[1]))
+
+
+def _embedding_setup(ctx, inputs, output):
+    ctx.save_for_backward(inputs[0])
+    ctx.rows = inputs[1].shape[0]
+
+
+def _embedding_bwd(ctx, g):
+    return None, torch.ops.ss.embedding_bwd(ctx.saved_tensors[0], g, ctx.rows)
+
+
+embedding.register_autograd(_embedding_bwd, setup_context=_embedding_setup)
+
+
+# ------------------------------------------------------------------------ head + loss
+def head_loss_run(h: Tensor, W: Tensor, targets: Tensor, weights: Tensor, block_rows: int,
+                  dW: Tensor | None, accumulate: bool, train: bool = True):
+    """Masked weighted cross entropy of ``h @ W^T`` in row blocks: the ``[T, V]`` logits never
+    exist at once. Returns ``(loss fp32[1], dh)``; the head-weight gradient is written (or added)
+    into ``dW`` block by block. Shared by the operator below and its in-place twin."""
+    T = h.shape[0]
+    loss = torch.zeros(1, dtype=torch.float32, device=h.device)
+    dh = torch.empty_like(h) if train else None
+    acc = accumulate
+    for r0 in range(0, T, block_rows):
+        r1 = min(T, r0 + block_rows)
+        logits = F.linear_fwd(h[r0:r1], W)
+        F.cross_entropy_(logits, targets[r0:r1], weights[r0:r1], loss, write_grad=train)
+        if train:
+            if dW is not None:
+                F.linear_wgrad(logits, h[r0:r1], out=dW, accumulate=acc)
+                acc = True
+            F.linear_dgrad(logits, W, out=dh[r0:r1])
+        del logits
+    return loss, dh
+
+
+@custom_op("ss::head_loss", mutates_args=())
+def head_loss(h: Tensor, W: Tensor, targets: Tensor, weights: Tensor, block_rows: int) -> tuple[Tensor, Tensor, Tensor]:
+    dW = torch.empty_like(W)
+    loss, dh = head_loss_run(h.contiguous(), W, targets, weights, block_rows, dW, False)
+    return loss, dh, dW
+
+
+@head_loss.register_fake
+def _(h, W, targets, weights, block_rows):
+    return h.new_empty((1,), dtype=torch.float32), torch.empty_like(h), torch.empty_like(W)
+
+
+@custom_op("ss::head_eval", mutates_args=())
+def head_eval(h: Tensor, W: Tensor, targets: Tensor, weights: Tensor, block_rows: int) -> Tensor:
+    return head_loss_run(h.contiguous(), W, targets, weights, block_rows, None, False, train=False)[0]
+
+
+@head_eval.register_fake
+def _(h, W, targets, weights, block_rows):
+    return h.new_empty((1,), dtype=torch.float32)
+
+
+def _head_setup(ctx, inputs, output):
+    ctx.save_for_backward(output[1], output[2])
+
+
+def _head_bwd(ctx, gl, _gdh, _gdw):
+    dh, dW = ctx.saved_tensors
+    # the loss is a weighted SUM: its upstream gradient is a scalar (1 in a training step)
+    return dh * gl.to(dh.dtype), dW * gl.to(dW.dtype), None, None, None
+
+
+head_loss.register_autograd(_head_bwd, setup_context=_head_setup)
+
+
+# ------------------------------------------------------------------------ DeltaNet pieces
+@custom_op("ss::conv_silu", mutates_args=())
+def conv_silu(x: Tensor, w: Tensor, positions: Tensor, cu_seqlens: Tensor) -> Tensor:
+    from ..ops import sequence as seq
+    with torch.no_grad():
+        bounds = None if x.is_cuda else cu_seqlens.tolist()
+        return seq.causal_conv_silu(x, w, bounds, positions).contiguous()
+
+
+@conv_silu.register_fake
+def _(x, w, positions, cu_seqlens):
+    return x.new_empty(x.shape)
+
+
+@custom_op("ss::conv_silu_bwd", mutates_args=())
+def conv_silu_bwd(x: Tensor, w: Tensor, positions: Tensor, cu_seqlens: Tensor, gy: Tensor) -> tuple[Tensor, Tensor]:
+    from ..ops import sequence as seq
+    with torch.enable_grad():
+        xg, wg = x.detach().requires_grad_(True), w.detach().requires_grad_(True)
+        bounds = None if x.is_cuda else cu_seqlens.tolist()
+        y = seq.causal_conv_silu(xg, wg, bounds, positions)
+        dx, dw = torch.autograd.grad(y, (xg, wg), gy.to(y.dtype))
+    return dx.contiguous(), dw.contiguous()
+
+
+@conv_silu_bwd.register_fake
+def _(x, w, positions, cu_seqlens, gy):
+    return x.new_empty(x.shape), w.new_empty(w.shape)
+
+
+def _conv_setup(ctx, inputs, output):
+    ctx.save_for_backward(*inputs)
+
+
+def _conv_bwd(ctx, gy):
+    x, w, pos, cu = ctx.saved_tensors
+    dx, dw = torch.ops.ss.conv_silu_bwd(x, w, pos, cu, gy)
+    return dx, dw, None, None
+
+
+conv_silu.register_autograd(_conv_bwd, setup_context=_conv_setup)
+
+
+@custom_op("ss::l2norm", mutates_args=())
+def l2norm(x: Tensor, eps: float) -> Tensor:
+    from ..ops import sequence as seq
+    with torch.no_grad():
+        return seq.l2_normalize(x.contiguous(), eps)
+
+
+@l2norm.register_fake
+def _(x, eps):
+    return torch.empty_like(x, memory_format=torch.contiguous_format)
+
+
+@custom_op("ss::l2norm_bwd", mutates_args=())
+def l2norm_bwd(x: Tensor, gy: Tensor, eps: float) -> Tensor:
+    from ..ops import sequence as seq
+    with torch.enable_grad():
+        xg = x.detach().contiguous().requires_grad_(True)
+        (dx,) = torch.autograd.grad(seq.l2_normalize(xg, eps), (xg,), gy.contiguous())
+    return dx
+
+
+@l2norm_bwd.register_fake
+def _(x, gy, eps):
+    return torch.empty_like(x, memory_format=torch.contiguous_format)
+
+
+def _l2_setup(ctx, inputs, output):
+    ctx.save_for_backward(inputs[0])
+    ctx.eps = inputs[1]
+
+
+def _l2_bwd(ctx, gy):
+    return torch.ops.ss.l2norm_bwd(ctx.saved_tensors[0], gy, ctx.eps), None
+
+
+l2norm.register_autograd(_l2_bwd, setup_context=_l2_setup)
+
+
+@custom_op("ss::gated_rmsnorm", mutates_args=())
+def gated_rmsnorm(x: Tensor, gate: Tensor, w: Tensor, eps: float, zero_centered: bool) -> Tensor:
+    from ..ops import sequence as seq
+    with torch.no_grad():
+        return seq.gated_rmsnorm(x.contiguous(), gate.contiguous(), w, eps, zero_centered)
+
+
+@gated_rmsnorm.register_fake
+def _(x, gate, w, eps, zero_centered):
+    return torch.empty_like(x, memory_format=torch.contiguous_format)
+
+
+@custom_op("ss::gated_rmsnorm_bwd", mutates_args=())
+def gated_rmsnorm_bwd(x: Tensor, gate: Tensor, w: Tensor, gy: Tensor, eps: float,
+                      zero_centered: bool) -> tuple[Tensor, Tensor, Tensor]:
+    from ..ops import sequence as seq
+    with torch.enable_grad():
+        xg, gg, wg = (t.detach().contiguous().requires_grad_(True) for t in (x, gate, w))
+        y = seq.gated_rmsnorm(xg, gg, wg, eps, zero_centered)
+        dx, dg, dw = torch.autograd.grad(y, (xg, gg, wg), gy.contiguous())
+    return dx, dg, dw
+
+
+@gated_rmsnorm_bwd.register_fake
+def _(x, gate, w, gy, eps, zero_centered):
+    return (torch.empty_like(x, memory_format=torch.contiguous_format),
+            torch.empty_like(gate, memory_format=torch.contiguous_format), torch.empty_like(w))
+
+
+def _grms_setup(ctx, inputs, output):
+    ctx.save_for_backward(*inputs[:3])
+    ctx.args = inputs[3:]
+
+
+def _grms_bwd(ctx, gy):
+    x, gate, w = ctx.saved_tensors
+    dx, dg, dw = torch.ops.ss.gated_rmsnorm_bwd(x, gate, w, gy, *ctx.args)
+    return dx, dg, dw, None, None
+
+
+gated_rmsnorm.register_autograd(_grms_bwd, setup_context=_grms_setup)
+
+
+@custom_op("ss::gated_delta_rule", mutates_args=())
+def gated_delta_rule(q: Tensor, k: Tensor, v: Tensor, beta: Tensor, g: Tensor, cu_seqlens: Tensor,
+                     chunk: int) -> Tensor:
+    from ..ops import sequence as seq
+    with torch.no_grad():
+        bounds = None if q.is_cuda else cu_seqlens.tolist()
+        return seq.gated_delta_rule_chunked(q, k, v, beta, g, bounds, chunk, cu_seqlens).contiguous()
+
+
+@gated_delta_rule.register_fake
+def _(q, k, v, beta, g, cu_seqlens, chunk):
+    return v.new_empty(v.shape)
+
+
+@custom_op("ss::gated_delta_rule_bwd", mutates_args=())
+def gated_delta_rule_bwd(q: Tensor, k: Tensor, v: Tensor, beta: Tensor, g: Tensor, cu_seqlens: Tensor,
+                         chunk: int, dout: Tensor) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
+    from ..ops import delta_rule, sequence as seq
+    if delta_rule.supported(q, k, v, chunk):
+        dq, dk, dv, db, dg = delta_rule.backward(q, k, v, beta, g, cu_seqlens, dout)
+        return dq, dk, dv, db.to(beta.dtype), dg.to(g.dtype)
+    with torch.enable_grad():
+        leaves = [t.detach().requires_grad_(True) for t in (q, k, v, beta, g)]
+        bounds = None if q.is_cuda else cu_seqlens.tolist()
+        y = seq.gated_delta_rule_chunked(*leaves, bounds, chunk, cu_seqlens)
+        grads = torch.autograd.grad(y, leaves, dout.to(y.dtype))
+    return tuple(t.contiguous() for t in grads)
+
+
+@gated_delta_rule_bwd.register_fake
+def _(q, k, v, beta, g, cu_seqlens, chunk, dout):
+    return tuple(t.new_empty(t.shape) for t in (q, k, v, beta, g))
+
+
+def _gdr_setup(ctx, inputs, output):
+    ctx.save_for_backward(*inputs[:6])
+    ctx.chunk = inputs[6]
+
+
+def _gdr_bwd(ctx, dout):
+    q, k, v, beta, g, cu = ctx.saved_tensors
+    return (*torch.ops.ss.gated_delta_rule_bwd(q, k, v, beta, g, cu, ctx.chunk, dout), None, None)
+
+
+gated_delta_rule.register_autograd(_gdr_bwd, setup_context=_gdr_setup)
+
+# Operators whose outputs are cheap to recompute from their inputs relative to reading them back:
+# the retention policy never keeps these unless a rule names them.
+MEMORY_BOUND = ("ss.rmsnorm", "ss.rope", "ss.swiglu", "ss.l2norm", "ss.conv_silu", "ss.gated_rmsnorm",
+                "ss.embedding")
+# Operators dominated by tensor-core work: keeping their outputs saves real time.
+COMPUTE_BOUND = ("ss.linear", "ss.gemm", "ss.attention", "ss.gated_delta_rule", "ss.head_loss")

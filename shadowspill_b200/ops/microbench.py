@@ -2,6 +2,7 @@
 
     python -m shadowspill_b200.ops.microbench gemm --m 8192 --n 8192 --k 8192
     python -m shadowspill_b200.ops.microbench attention --tokens 16384 --seqlen 4096
+    python -m shadowspill_b200.ops.microbench deltanet --tokens 8192 --seqlen 2048 --compare
     python -m shadowspill_b200.ops.microbench all --json out.json
 
 Each case is timed with CUDA events on the launching stream after warm-up, with
@@ -150,9 +151,63 @@ def bench_elementwise(a) -> list[dict]:
     return out
 
 
+def bench_deltanet(a) -> list[dict]:
+    """Gated delta rule, 16 QK / 32 V heads of width 128: forward and forward+backward of the
+    chunk kernels, each kernel on its own, and the PyTorch tensor-operation form beside them."""
+    from . import delta_rule as dr, sequence as seq
+    T, L, Hk, H = a.tokens, a.seqlen, 16, 32
+    nrm = lambda x: (x / x.norm(dim=-1, keepdim=True)).bfloat16()
+    q, k = nrm(torch.randn(T, Hk, 128, device="cuda")), nrm(torch.randn(T, Hk, 128, device="cuda"))
+    v = torch.randn(T, H, 128, device="cuda", dtype=torch.bfloat16)
+    beta = torch.sigmoid(torch.randn(T, H, device="cuda"))
+    g = -torch.nn.functional.softplus(torch.randn(T, H, device="cuda")) * 0.3
+    cu = torch.arange(0, T + 1, L, dtype=torch.int32, device="cuda")
+    dout = torch.randn_like(v)
+    n = -(-T // 64)
+    # products per chunk and V head (multiply-adds x 2): see the kernel file's header
+    fwd_fl = n * H * 2.0 * (2 * 64 * 64 * 128 / 2 + 2 * 64 * 64 * 128 + 3 * 64 * 128 * 128 + 64 * 64 * 128)
+    out = []
+    s = timed(lambda: dr._forward(q, k, v, beta, g, cu, False), a.iters, a.warmup)
+    out.append(report(f"deltanet_fwd_T{T}_L{L}", s, fwd_fl))
+    s = timed(lambda: dr.backward(q, k, v, beta, g, cu, dout), a.iters, a.warmup)
+    out.append(report(f"deltanet_recompute+bwd_T{T}_L{L}", s, 3.5 * fwd_fl))
+    _, B, geo = dr._forward(q, k, v, beta, g, cu, True)
+    L_, st, status = _lib.lib(), _lib.stream_ptr(), _lib.status_word().data_ptr()
+    o = torch.empty_like(v)
+    cases = {
+        "prep": lambda: L_.ss_dn_prep(q.data_ptr(), k.data_ptr(), v.data_ptr(), beta.data_ptr(), g.data_ptr(),
+                                      B.sid.data_ptr(), B.WTp.data_ptr(), B.U0Tp.data_ptr(), B.QG.data_ptr(),
+                                      B.KD.data_ptr(), B.MQ.data_ptr(), B.TMT.data_ptr(), B.XW.data_ptr(),
+                                      B.XU.data_ptr(), B.gam.data_ptr(), B.gc.data_ptr(), T, H, Hk,
+                                      128 ** -0.5, status, st),
+        "state_walk": lambda: L_.ss_dn_fwd(B.WTp.data_ptr(), B.U0Tp.data_ptr(), B.QG.data_ptr(), B.KD.data_ptr(),
+                                           B.MQ.data_ptr(), B.gc.data_ptr(), o.data_ptr(), B.ST.data_ptr(),
+                                           B.UTp.data_ptr(), T, H, Hk, status, st),
+        "bwd_state_walk": lambda: L_.ss_dn_bwd_state(dout.data_ptr(), B.MQ.data_ptr(), B.KD.data_ptr(),
+                                                     B.QG.data_ptr(), B.WTp.data_ptr(), B.gc.data_ptr(),
+                                                     B.dSpT.data_ptr(), B.dUTp.data_ptr(), T, H, Hk, status, st),
+        "bwd_chunk": lambda: L_.ss_dn_bwd_chunk(B.dSpT.data_ptr(), B.ST.data_ptr(), B.UTp.data_ptr(),
+                                                B.dUTp.data_ptr(), dout.data_ptr(), B.dKdTp.data_ptr(),
+                                                B.dQgTp.data_ptr(), B.dWTp.data_ptr(), B.dMQ.data_ptr(),
+                                                B.dgc.data_ptr(), T, H, Hk, status, st),
+    }
+    for name, fn in cases.items():
+        out.append(report(f"deltanet_{name}_T{T}", timed(fn, a.iters, a.warmup)))
+    if a.compare:
+        qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+
+        def torch_form():
+            with seq.tf32_matmul():
+                y = seq._gated_delta_rule_torch(qf, kf, vf, beta, g, None, 64, cu)
+                y.backward(dout.float())
+        out.append(report(f"deltanet_torch_form_fwd+bwd_T{T}_L{L}", timed(torch_form, max(1, a.iters // 3), 1)))
+    return out
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
-    ap.add_argument("what", choices=["gemm", "attention", "elementwise", "all"])
+    ap.add_argument("what", choices=["gemm", "attention", "elementwise", "deltanet", "all"])
+    ap.add_argument("--compare", action="store_true", help="also time the PyTorch tensor-operation form")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -178,6 +233,8 @@ def main(argv=None) -> None:
         rows += bench_attention(a)
     if a.what in ("elementwise", "all"):
         rows += bench_elementwise(a)
+    if a.what in ("deltanet", "all"):
+        rows += bench_deltanet(a)
     _lib.check_status()
     if a.json:
         Path(a.json).parent.mkdir(parents=True, exist_ok=True)

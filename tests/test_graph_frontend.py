@@ -1,0 +1,137 @@
+"""The PyTorch graph frontend: strict export, stage partition, save / recompute graph pairs from
+the AOTAutograd joint graph, gradient destinations, and planned execution of the result."""
+import sys
+
+import pytest
+import torch
+
+sys.path.insert(0, __file__.rsplit("/", 1)[0])
+from test_executor_cpu import _batches  # noqa: E402
+
+from shadowspill_b200.communication.info import CommunicationInfo
+from shadowspill_b200.data.synthetic import to_device
+from shadowspill_b200.execution.executor import Executor, Hyperparameters
+from shadowspill_b200.execution.resident import ResidentTrainer
+from shadowspill_b200.frontend import graph_pairs as gp
+from shadowspill_b200.frontend.capture import BatchGeometry, StepDataOrdering, build_step
+from shadowspill_b200.frontend.export import export_step, op_name, partition_export
+from shadowspill_b200.frontend.graph_stage import _example_batch, capture_module
+from shadowspill_b200.frontend.modules import DecoderLM
+from shadowspill_b200.models.config import preset
+from shadowspill_b200.planning.plan import MemoryBudgets, PlanningError, SearchOptions, plan_program
+
+GEO = BatchGeometry(microbatch_tokens=256, n_microbatches=2, slots=16, mean_seqlen=64)
+
+
+def _plan(prog, pct_from=30):
+    total = sum(o.bytes for o in prog.objects)
+    ws = max(t.workspace_bytes for t in prog.tasks)
+    opts = SearchOptions(minimum_object_bytes_evict_eligible=1024, workers=2)
+    for pct in range(pct_from, 101, 5):
+        try:
+            return plan_program(prog, MemoryBudgets(ws + total * pct // 100, 64 << 20, headroom_bytes=0),
+                                CommunicationInfo(), opts)
+        except PlanningError:
+            continue
+    raise AssertionError("no budget planned")
+
+
+def test_export_partition_and_pairs_of_a_dense_model():
+    cfg = preset("llama3-plumbing")
+    with torch.device("meta"):
+        model = DecoderLM(cfg, torch.float32)
+    ep = export_step(model, _example_batch(256, 16))
+    ops = {op_name(n) for n in ep.graph_module.graph.nodes}
+    assert {"ss.linear", "ss.rmsnorm", "ss.rope", "ss.attention", "ss.swiglu", "ss.embedding",
+            "ss.head_loss"} <= ops
+    exported = partition_export(ep)
+    assert [s.name for s in exported.stages] == ["embed"] + [f"layer{i}" for i in range(cfg.n_layers)] + ["head"]
+    keys = {s.key for s in exported.stages[1:-1]}
+    assert len(keys) == 1                               # every layer is one structural contract
+    layer = exported.stages[1]
+    assert layer.param_names == ["attn_norm", "wqkv", "wo", "mlp_norm", "w13", "w2"]
+    assert layer.boundary_in == "x" and layer.batch_fields == ["positions", "cu_seqlens"]
+    whole = partition_export(ep, "whole")
+    assert len(whole.stages) == 1 and whole.stages[0].boundary_in is None
+    # ---- graph pairs of the layer contract
+    pairs = gp.build_stage_pairs(layer, [True] * 6, grad_dtypes={"attn_norm": torch.float32,
+                                                                "mlp_norm": torch.float32})
+    assert set(pairs.pairs) == {"recompute", "save_attention", "save"}
+    rec, att, sav = (pairs.pairs[v] for v in ("recompute", "save_attention", "save"))
+    assert rec.saved == []
+    fwd_ops = lambda pair: [op_name(n) for n in pair.backward.graph.nodes if op_name(n).startswith("ss.")]
+    assert "ss.attention" in fwd_ops(rec) and "ss.attention" not in fwd_ops(att)      # kept, not redone
+    assert fwd_ops(att).count("ss.linear") == 2 and "ss.linear" not in fwd_ops(sav)    # save redoes no GEMM
+    assert fwd_ops(sav).count("ss.swiglu") == 1                                         # but the cheap SwiGLU
+    assert len(att.saved) == 3 and len(att.saved) < len(sav.saved)
+    # one fused q/k/v projection is kept once, through its base
+    assert sum(s.shape == (256, (cfg.n_heads + 2 * cfg.n_kv_heads) * cfg.head_dim) for s in att.saved) == 1
+    # every matrix gradient is written by the graph itself
+    assert {"wqkv", "wo", "w13", "w2", "attn_norm", "mlp_norm"} <= rec.in_place
+    assert any(n.target is gp.gemm_into for n in rec.backward.graph.nodes)
+
+
+@pytest.mark.parametrize("name", ["llama3-tiny", "qwen3-tiny"])
+def test_planned_graph_frontend_matches_the_resident_trainer(name):
+    """The same 3 updates through export -> partition -> pairs -> plan (forced to spill) -> execute
+    and through the resident hand-written stages; the planner mixes the variants."""
+    cfg = preset(name)
+    prog, desc = build_step(cfg, GEO, StepDataOrdering(), dtype=torch.float32,
+                            selection={1: "save", 2: "save_attention"}, frontend="graph")
+    hand, _ = build_step(cfg, GEO, StepDataOrdering(), dtype=torch.float32,
+                         selection={1: "save", 2: "save_attention"})
+    assert len(prog.tasks) == len(hand.tasks) and len(prog.objects) == len(hand.objects)
+    assert [t.name for t in prog.tasks] == [t.name for t in hand.tasks]
+    plan = _plan(prog)
+    assert plan.summary.fetch_bytes > 0
+    ex = Executor(plan, desc, device="cpu", seed=5, hyper=Hyperparameters(lr=3e-3))
+    ex.initialize()
+    ref = ResidentTrainer(cfg, device="cpu", dtype=torch.float32, seed=5, lr=3e-3)
+    for step in range(3):
+        host = _batches(cfg, step)
+        res = ex.run(host)
+        want = ref.step([to_device(m, "cpu") for m in host])
+        assert abs(res.loss - want) < 1e-5 * max(1.0, abs(want)), (step, res.loss, want)
+    got = ex.state_dict()
+    for k, v in ref.state_dict().items():
+        assert torch.allclose(got[k], v, rtol=1e-5, atol=1e-6), k
+    ex.close()
+
+
+def test_plumbing_config_twenty_steps_match_eager_pytorch():
+    """BASELINE configuration 0: the tiny Llama through export, partition, profile-free planning with
+    half of the state spilled, execution and the plan report, against plain eager PyTorch + AdamW."""
+    from shadowspill_b200.data.synthetic import make_batch
+    from shadowspill_b200.models import torch_reference as tr
+    cfg = preset("llama3-plumbing")
+    geo = BatchGeometry(microbatch_tokens=1024, n_microbatches=2, slots=16, mean_seqlen=256)
+    prog, desc = build_step(cfg, geo, StepDataOrdering(), dtype=torch.float32,
+                            selection={i: ("save" if i % 2 else "recompute") for i in range(1, cfg.n_layers + 1)},
+                            frontend="graph")
+    plan = _plan(prog, pct_from=50)
+    assert plan.summary.fetch_bytes > 0 and plan.summary.evict_bytes > 0
+    hyper = Hyperparameters(lr=1e-3, beta2=0.999, weight_decay=0.0)
+    ex = Executor(plan, desc, device="cpu", seed=7, hyper=hyper)
+    ex.initialize()
+    params = {k: v.clone().requires_grad_(True) for k, v in ex.state_dict().items() if not k.startswith("exp_avg")}
+    opt = torch.optim.AdamW(list(params.values()), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
+    for step in range(20):
+        host = make_batch(step, vocab=cfg.vocab_size, tokens_per_step=2048, microbatch_tokens=1024,
+                          median=200, min_len=64, max_len=512, slots=16)
+        got = ex.run(host).loss
+        opt.zero_grad()
+        want = 0.0
+        for m in host:
+            loss = tr.loss(cfg, params, to_device(m, "cpu"))
+            loss.backward()
+            want += float(loss)
+        opt.step()
+        assert abs(got - want) < 1e-5 * max(1.0, abs(want)), (step, got, want)
+    state = ex.state_dict()
+    # weights: relative L2 error, and no element further off than two Adam steps (a gradient that
+    # is zero up to rounding may take either sign)
+    for k, v in params.items():
+        diff = (state[k] - v.detach()).float()
+        assert float(diff.norm() / v.detach().float().norm()) < 1e-3, k
+        assert float(diff.abs().max()) <= 2 * 1e-3 + 1e-6, k
+    ex.close()
