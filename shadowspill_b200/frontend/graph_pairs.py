@@ -419,7 +419,7 @@ def build_stage_pairs(stage: StageGraph, trainable: list[bool], policies=DEFAULT
             else:
                 grad_outputs.append("x" if nm == "x" else None)
         in_place = rewrite_destinations(bwd, param_grads, grad_dtypes or {})
-        b_inputs = [n.name for n in bwd.graph.nodes if n.op == "placeholder"]
+        b_inputs = [str(n.target) for n in bwd.graph.nodes if n.op == "placeholder"]
         pairs[pol.name] = GraphPair(pol.name, fwd, bwd, saved, b_inputs, grad_outputs, in_place)
     flops, inter = 0.0, 0
     for n in stage.gm.graph.nodes:

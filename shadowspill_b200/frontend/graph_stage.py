@@ -242,7 +242,6 @@ def _head_training_graph(pairs: gp.StagePairs, stage: StageGraph):
     names = list(pairs.placeholders)
     primals, tangents = phs[:len(names)], phs[len(names):]
     for p, nm in zip(primals, names):
-        p.name = nm
         p.target = nm
     out_node = next(n for n in g.nodes if n.op == "output")
     outs = list(out_node.args[0])
@@ -256,7 +255,7 @@ def _head_training_graph(pairs: gp.StagePairs, stage: StageGraph):
         if op_name(n) != "ss.head_loss":
             continue
         h, W, targets, weights, block = n.args
-        w_name = W.name if W.op == "placeholder" else None
+        w_name = str(W.target) if W.op == "placeholder" else None
         trainable = w_name is not None and grads_of[names.index(w_name)] is not None
         d = f = None
         if trainable:
@@ -265,7 +264,7 @@ def _head_training_graph(pairs: gp.StagePairs, stage: StageGraph):
             with g.inserting_after(d):
                 f = g.placeholder(f"first_{w_name}")
             last = f
-            extra_inputs += [d.name, f.name]
+            extra_inputs += [str(d.target), str(f.target)]
         with g.inserting_before(n):
             new = g.call_function(gp.head_loss_into, (d, h, W, targets, weights, block, f if f is not None else True))
         pending.append((n, new, d))
@@ -311,7 +310,7 @@ def _head_training_graph(pairs: gp.StagePairs, stage: StageGraph):
     g._codegen = fx.graph.CodeGen()          # plain positional inputs instead of (primals, tangents)
     g.lint()
     joint = fx.GraphModule(torch.nn.Module(), g)
-    inputs = [n.name for n in joint.graph.nodes if n.op == "placeholder"]
+    inputs = [str(n.target) for n in joint.graph.nodes if n.op == "placeholder"]
     return joint, inputs, grads_of
 
 

@@ -28,6 +28,34 @@ def _c(t: Tensor) -> Tensor:
     return t if t.stride(-1) == 1 else t.contiguous()
 
 
+_pool = None
+
+
+def _autograd_elsewhere(fn, inputs: tuple[Tensor, ...], grad_out: Tensor) -> tuple[Tensor, ...]:
+    """Gradients of ``fn(*inputs)`` by ``torch.autograd``, for operators whose backward pass has no
+    kernel of its own on this device (the CPU forms of the sequence-mixer pieces). The body of a
+    custom operator runs below the autograd dispatch keys, where nothing records a graph; that
+    exclusion is thread-local, so the differentiation runs on a helper thread."""
+    global _pool
+    if _pool is None:
+        from concurrent.futures import ThreadPoolExecutor
+        _pool = ThreadPoolExecutor(max_workers=1, thread_name_prefix="ss-autograd")
+    stream = torch.cuda.current_stream() if grad_out.is_cuda else None
+
+    def work():
+        # device and stream are thread-local too: carry the caller's over
+        import contextlib
+        ctx = contextlib.ExitStack()
+        if stream is not None:
+            ctx.enter_context(torch.cuda.device(grad_out.device))
+            ctx.enter_context(torch.cuda.stream(stream))
+        with ctx, torch.enable_grad():
+            leaves = [t.detach().requires_grad_(True) for t in inputs]
+            y = fn(*leaves)
+            return tuple(g.contiguous() for g in torch.autograd.grad(y, leaves, grad_out.to(y.dtype)))
+    return _pool.submit(work).result()
+
+
 # ------------------------------------------------------------------------ GEMM / linear
 @custom_op("ss::gemm", mutates_args=())
 def gemm(a: Tensor, b: Tensor, a_mn: bool, b_mn: bool) -> Tensor:
@@ -314,12 +342,8 @@ def _(x, w, positions, cu_seqlens):
 @custom_op("ss::conv_silu_bwd", mutates_args=())
 def conv_silu_bwd(x: Tensor, w: Tensor, positions: Tensor, cu_seqlens: Tensor, gy: Tensor) -> tuple[Tensor, Tensor]:
     from ..ops import sequence as seq
-    with torch.enable_grad():
-        xg, wg = x.detach().requires_grad_(True), w.detach().requires_grad_(True)
-        bounds = None if x.is_cuda else cu_seqlens.tolist()
-        y = seq.causal_conv_silu(xg, wg, bounds, positions)
-        dx, dw = torch.autograd.grad(y, (xg, wg), gy.to(y.dtype))
-    return dx.contiguous(), dw.contiguous()
+    bounds = None if x.is_cuda else cu_seqlens.tolist()
+    return _autograd_elsewhere(lambda a, b: seq.causal_conv_silu(a, b, bounds, positions), (x, w), gy)
 
 
 @conv_silu_bwd.register_fake
@@ -355,10 +379,7 @@ def _(x, eps):
 @custom_op("ss::l2norm_bwd", mutates_args=())
 def l2norm_bwd(x: Tensor, gy: Tensor, eps: float) -> Tensor:
     from ..ops import sequence as seq
-    with torch.enable_grad():
-        xg = x.detach().contiguous().requires_grad_(True)
-        (dx,) = torch.autograd.grad(seq.l2_normalize(xg, eps), (xg,), gy.contiguous())
-    return dx
+    return _autograd_elsewhere(lambda a: seq.l2_normalize(a, eps), (x.contiguous(),), gy.contiguous())[0]
 
 
 @l2norm_bwd.register_fake
@@ -394,11 +415,8 @@ def _(x, gate, w, eps, zero_centered):
 def gated_rmsnorm_bwd(x: Tensor, gate: Tensor, w: Tensor, gy: Tensor, eps: float,
                       zero_centered: bool) -> tuple[Tensor, Tensor, Tensor]:
     from ..ops import sequence as seq
-    with torch.enable_grad():
-        xg, gg, wg = (t.detach().contiguous().requires_grad_(True) for t in (x, gate, w))
-        y = seq.gated_rmsnorm(xg, gg, wg, eps, zero_centered)
-        dx, dg, dw = torch.autograd.grad(y, (xg, gg, wg), gy.contiguous())
-    return dx, dg, dw
+    return _autograd_elsewhere(lambda a, b, c: seq.gated_rmsnorm(a, b, c, eps, zero_centered),
+                               (x.contiguous(), gate.contiguous(), w), gy.contiguous())
 
 
 @gated_rmsnorm_bwd.register_fake
@@ -442,12 +460,9 @@ def gated_delta_rule_bwd(q: Tensor, k: Tensor, v: Tensor, beta: Tensor, g: Tenso
     if delta_rule.supported(q, k, v, chunk):
         dq, dk, dv, db, dg = delta_rule.backward(q, k, v, beta, g, cu_seqlens, dout)
         return dq, dk, dv, db.to(beta.dtype), dg.to(g.dtype)
-    with torch.enable_grad():
-        leaves = [t.detach().requires_grad_(True) for t in (q, k, v, beta, g)]
-        bounds = None if q.is_cuda else cu_seqlens.tolist()
-        y = seq.gated_delta_rule_chunked(*leaves, bounds, chunk, cu_seqlens)
-        grads = torch.autograd.grad(y, leaves, dout.to(y.dtype))
-    return tuple(t.contiguous() for t in grads)
+    bounds = None if q.is_cuda else cu_seqlens.tolist()
+    return _autograd_elsewhere(lambda *a: seq._gated_delta_rule_torch(*a, bounds, chunk, cu_seqlens),
+                               (q, k, v, beta, g), dout)
 
 
 @gated_delta_rule_bwd.register_fake

@@ -160,7 +160,8 @@ def apply_profiles(program: Program, profiles: Profiles, workspace_margin: float
         t.duration_ns = max(1, int(p.seconds * duration_scale * 1e9))
         # stages whose backward is derived by autograd allocate many large temporaries in
         # data-dependent order: leave the caching allocator room for fragmentation
-        margin = max(workspace_margin, 1.25) if "HybridLayerStage" in t.profile_key else workspace_margin
+        margin = (max(workspace_margin, 1.25) if ("HybridLayerStage" in t.profile_key or "Graph" in t.profile_key)
+                  else workspace_margin)
         if ":ep" in t.profile_key:
             # profiled on one rank with its local experts; in the job the rows a rank receives
             # depend on every rank's routing

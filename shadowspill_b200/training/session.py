@@ -81,6 +81,9 @@ class TrainingSetup:
     head_chunks: int = 0                 # evaluate the output projection in this many row chunks (0 = default)
     moe_chunks: int = 0                  # expert parallelism: pipeline each routed layer in this many expert groups
     master_weights: bool = False         # fp32 master copies of trainable parameters (unfused update path)
+    # "graph": torch.export -> stage partition -> AOT save/recompute graph pairs for the models the
+    # graph frontend covers (frontend/graph_stage.py); "stages": the hand-written stage classes
+    frontend: str = "stages"
     pretrained: str = ""                 # directory of Hugging Face safetensors to start from
     # content-addressed store of task profiles shared between runs ("" = none)
     store: str = ""
@@ -146,7 +149,7 @@ class TrainingSession:
             # these layers run through the autograd-derived stage, which only recomputes
             selections = [{}]
             variants = [(walk, {}) for walk in setup.walks]
-        choices = dict(objective=self.objective, lora=self.lora)
+        choices = dict(objective=self.objective, lora=self.lora, frontend=setup.frontend)
         shard_world = setup.ranks_per_replica or world
         if world % shard_world:
             raise ValueError("world_size must be a multiple of ranks_per_replica")
