@@ -341,6 +341,12 @@ int ss_step_begin(ss_runtime* rt, int32_t plan_id, void* compute_stream);
 int ss_before_task(ss_runtime* rt, int32_t plan_id, int32_t task, void** ptrs, int32_t max_ptrs);
 /* Records the task fence on compute_stream and publishes the actions it triggers. */
 int ss_after_task(ss_runtime* rt, int32_t plan_id, int32_t task);
+/* The same boundaries for a task that runs on another stream than the step's compute stream
+ * (a collective on a communication stream): waits are enqueued on, and the fence is recorded on,
+ * `stream`. Null means the compute stream. */
+int ss_before_task_on(ss_runtime* rt, int32_t plan_id, int32_t task, void** ptrs, int32_t max_ptrs,
+                      void* stream);
+int ss_after_task_on(ss_runtime* rt, int32_t plan_id, int32_t task, void* stream);
 /* Waits until every action of the step has completed; returns the failure latch state. */
 int ss_step_end(ss_runtime* rt, int32_t plan_id);
 int ss_runtime_wait_idle(ss_runtime* rt);

@@ -61,6 +61,7 @@ struct PlanState {
   std::vector<int32_t> action_interval;        // fetch -> stay it opens; evict/release -> stay it ends
   std::vector<std::vector<int32_t>> task_creates;   // stays opened by each task
   std::vector<void*> task_fence;               // one event per task
+  std::vector<uint8_t> task_side_stream;       // 1: the task's fence was recorded on a stream other than compute
   std::vector<void*> action_event;             // one event per transfer action
   std::vector<void*> action_begin_event;       // only with tracing configured: copy start
   void* step_begin_event = nullptr;            // only with tracing configured
@@ -247,7 +248,9 @@ bool pump_plan(ss_runtime* rt, PlanState& P) {
     if (A.trigger_task > pub) break;
     IntervalState& I = *P.intervals[P.action_interval[a]];
     I.release_event = A.trigger_task >= 0 ? P.task_fence[A.trigger_task] : nullptr;
-    I.release_on_compute = true;
+    // a fence on the compute stream orders later compute work by itself; a fence of a task that
+    // ran on a side stream (a collective) has to be waited for
+    I.release_on_compute = !(A.trigger_task >= 0 && P.task_side_stream[A.trigger_task]);
     I.released.store(1, std::memory_order_release);
     P.action_issued[a].store(1, std::memory_order_release);
     rt->st_releases++;
@@ -631,6 +634,7 @@ int ss_plan_admit(ss_runtime* rt, const ss_plan_desc* d, int32_t* plan_id) {
   }
   // events are created once here; steady-state steps create none
   P->task_fence.assign(d->n_tasks, nullptr);
+  P->task_side_stream.assign(d->n_tasks, 0);
   P->action_event.assign(d->n_actions, nullptr);
   for (int32_t t = 0; t < d->n_tasks; ++t)
     if (int rc = new_event(rt, &P->task_fence[t])) { release_plan(rt, *P); return rc; }
@@ -684,6 +688,7 @@ int ss_step_begin(ss_runtime* rt, int32_t plan_id, void* compute_stream) {
     }
     for (auto& f : P->action_issued) f = 0;
     for (auto& f : P->action_durable) f = 0;
+    std::fill(P->task_side_stream.begin(), P->task_side_stream.end(), 0);
     P->staged_pending.store(0);
     std::fill(P->object_current.begin(), P->object_current.end(), -1);
     P->next_fetch = P->next_evict = P->next_release = 0;
@@ -700,12 +705,23 @@ int ss_step_begin(ss_runtime* rt, int32_t plan_id, void* compute_stream) {
 }
 
 int ss_before_task(ss_runtime* rt, int32_t plan_id, int32_t task, void** ptrs, int32_t max_ptrs) {
+  return ss_before_task_on(rt, plan_id, task, ptrs, max_ptrs, nullptr);
+}
+
+// `stream`: the stream the task's kernels will run on (null = the step's compute stream). The waits
+// for fetched inputs and for the previous occupants of created ranges are enqueued there. A task on
+// a side stream is ordered against compute work by its caller; the runtime orders it against
+// transfers and range reuse.
+int ss_before_task_on(ss_runtime* rt, int32_t plan_id, int32_t task, void** ptrs, int32_t max_ptrs,
+                      void* stream) {
   if (!rt) return SS_INVALID_ARGUMENT;
   if (rt->failed.load()) return SS_FAILED;
   PlanState* P;
   { std::lock_guard<std::mutex> lk(rt->mu); P = find_plan(rt, plan_id); }
   if (!P || !P->active || task < 0 || task >= P->n_tasks) return SS_INVALID_ARGUMENT;
   ss_backend* be = rt->be;
+  void* const task_stream = stream ? stream : P->compute_stream;
+  const bool side = task_stream != P->compute_stream;
   // stays this task opens: wait for the previous occupants of their ranges
   for (int32_t ii : P->task_creates[task]) {
     IntervalState& I = *P->intervals[ii];
@@ -714,8 +730,8 @@ int ss_before_task(ss_runtime* rt, int32_t plan_id, int32_t task, void** ptrs, i
       if (!wait_flag(rt, J.released))
         return rt->latch(SS_FAIL_CAPACITY, SS_NO_PROGRESS, task, I.iv.object, -1, 0,
                          "range predecessor never released");
-      if (J.release_event && !J.release_on_compute) {
-        int rc = be->stream_wait_event(be->self, P->compute_stream, J.release_event);
+      if (J.release_event && (side || !J.release_on_compute)) {
+        int rc = be->stream_wait_event(be->self, task_stream, J.release_event);
         if (rc != SS_OK) return rt->latch(SS_FAIL_BACKEND_EVENT, rc, task, I.iv.object, -1, 0, "stream wait failed");
         rt->trace(SS_TRACE_REUSE_WAIT, task, I.iv.bytes);
       }
@@ -748,7 +764,7 @@ int ss_before_task(ss_runtime* rt, int32_t plan_id, int32_t task, void** ptrs, i
         if (!wait_flag(rt, I.ready_issued))
           return rt->latch(SS_FAIL_CAPACITY, SS_NO_PROGRESS, task, u.object, I.iv.begin_action, 0,
                            "fetch was never issued");
-        int rc = be->stream_wait_event(be->self, P->compute_stream, I.ready_event);
+        int rc = be->stream_wait_event(be->self, task_stream, I.ready_event);
         if (rc != SS_OK) return rt->latch(SS_FAIL_BACKEND_EVENT, rc, task, u.object, -1, 0, "stream wait failed");
         rt->trace(SS_TRACE_INPUT_WAIT, task, I.iv.bytes);
       }
@@ -760,12 +776,18 @@ int ss_before_task(ss_runtime* rt, int32_t plan_id, int32_t task, void** ptrs, i
 }
 
 int ss_after_task(ss_runtime* rt, int32_t plan_id, int32_t task) {
+  return ss_after_task_on(rt, plan_id, task, nullptr);
+}
+
+int ss_after_task_on(ss_runtime* rt, int32_t plan_id, int32_t task, void* stream) {
   if (!rt) return SS_INVALID_ARGUMENT;
   if (rt->failed.load()) return SS_FAILED;
   PlanState* P;
   { std::lock_guard<std::mutex> lk(rt->mu); P = find_plan(rt, plan_id); }
   if (!P || !P->active || task < 0 || task >= P->n_tasks) return SS_INVALID_ARGUMENT;
-  int rc = rt->be->event_record(rt->be->self, P->task_fence[task], P->compute_stream);
+  void* const task_stream = stream ? stream : P->compute_stream;
+  P->task_side_stream[task] = task_stream != P->compute_stream;
+  int rc = rt->be->event_record(rt->be->self, P->task_fence[task], task_stream);
   if (rc != SS_OK) return rt->latch(SS_FAIL_BACKEND_EVENT, rc, task, -1, -1, 0, "fence record failed");
   rt->st_tasks++;
   rt->trace(SS_TRACE_TASK_END, task, 0);

@@ -376,6 +376,14 @@ class Executor:
         self._mirrors: dict[int, tuple[torch.Tensor, bool]] = {}
         self.plan_id = self.rt.admit(plan)
         self.stream = torch.cuda.Stream(device=self.torch_device) if self.cuda else None
+        # Collective tasks (weight all-gathers, the fused reduce-scatter + update) run on a stream of
+        # their own, as the reference issues them on the transfer lane's route stream
+        # (packages/engine/csrc/adapter/pytorch/storage/sharded.cpp:87-122), so they overlap the
+        # compute tasks around them. SS_COMM_STREAM=0 keeps them on the compute stream.
+        import os
+        self.comm_stream = (torch.cuda.Stream(device=self.torch_device)
+                            if (self.cuda and self.world > 1 and os.environ.get("SS_COMM_STREAM", "1") == "1")
+                            else None)
         self._views: dict[tuple[int, int], object] = {}
         self._uses = self.runner.uses
         self.T, self.n_mb, self.slots = self.runner.T, self.runner.n_mb, self.runner.slots
@@ -721,23 +729,56 @@ class Executor:
             if self._mirrors:
                 self.flush_homes()
             self.rt.step_begin(self.plan_id, self.stream.cuda_stream if self.cuda else None)
+            pending: dict[int, torch.cuda.Event] = {}     # object -> end of the side-stream task using it
+            tasks = self.program.tasks
             for task in range(n_tasks):
-                ptrs = self.rt.before_task(self.plan_id, task, len(self._uses[task]))
+                t = tasks[task]
+                side = self.comm_stream is not None and (t.kind == "collective" or t.variant == "adamw_dp")
+                run_stream = self.comm_stream if side else self.stream
+                if side:
+                    if t.kind != "collective":
+                        # reads what compute tasks produced (gradients): order after them. A weight
+                        # gather depends on fetches and freed ranges only, which the runtime orders.
+                        ready = torch.cuda.Event()
+                        ready.record(self.stream)
+                        self.comm_stream.wait_event(ready)
+                    ptrs = self.rt.before_task(self.plan_id, task, len(self._uses[task]),
+                                               stream=self.comm_stream.cuda_stream)
+                else:
+                    if pending:
+                        for u in self._uses[task]:
+                            ev = pending.pop(u.object, None)
+                            if ev is not None:
+                                self.stream.wait_event(ev)
+                    ptrs = self.rt.before_task(self.plan_id, task, len(self._uses[task]))
                 B = self._bind(task, ptrs)
                 if events:
-                    events[task][0].record(self.stream)
+                    events[task][0].record(run_stream)
                 elif not self.cuda and time_tasks:
                     tt = time.perf_counter()
                 if self.annotate:
-                    torch.cuda.nvtx.range_push(self.program.tasks[task].name)
-                self.runner.run_task(task, B)
+                    torch.cuda.nvtx.range_push(t.name)
+                if side:
+                    with torch.cuda.stream(self.comm_stream):
+                        self.runner.run_task(task, B)
+                else:
+                    self.runner.run_task(task, B)
                 if self.annotate:
                     torch.cuda.nvtx.range_pop()
                 if events:
-                    events[task][1].record(self.stream)
+                    events[task][1].record(run_stream)
                 elif not self.cuda and time_tasks:
                     task_seconds[task] = time.perf_counter() - tt
-                self.rt.after_task(self.plan_id, task)
+                if side:
+                    self.rt.after_task(self.plan_id, task, stream=self.comm_stream.cuda_stream)
+                    done = torch.cuda.Event()
+                    done.record(self.comm_stream)
+                    for u in self._uses[task]:
+                        pending[u.object] = done
+                else:
+                    self.rt.after_task(self.plan_id, task)
+            for ev in set(pending.values()):          # the step ends when the side stream has ended
+                self.stream.wait_event(ev)
             if self.cuda:
                 end_ev.record(self.stream)
             self.rt.step_end(self.plan_id)

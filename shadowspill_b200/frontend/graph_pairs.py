@@ -55,7 +55,11 @@ SAVE = RetentionPolicy("save", "all")
 SAVE_ATTENTION = RetentionPolicy("save_attention", "rules", (
     RetentionRule("ss.attention", "outputs"), RetentionRule("ss.attention", "inputs"),
     RetentionRule("ss.gated_delta_rule", "outputs"), RetentionRule("ss.gated_delta_rule", "inputs")))
-DEFAULT_POLICIES = (RECOMPUTE, SAVE_ATTENTION, SAVE)
+# also keeps the gate/up projection: the backward pass then redoes only the small output
+# projection and the elementwise pieces
+SAVE_ATTENTION_GU = RetentionPolicy("save_attention_gu", "rules",
+                                    SAVE_ATTENTION.rules + (RetentionRule("ss.swiglu", "inputs"),))
+DEFAULT_POLICIES = (RECOMPUTE, SAVE_ATTENTION, SAVE_ATTENTION_GU, SAVE)
 
 
 @dataclass
@@ -114,6 +118,11 @@ def joint_graph(stage: StageGraph, trainable: list[bool]) -> fx.GraphModule:
     for node in list(joint.graph.nodes):
         if node.op == "call_function" and "_assert_tensor_metadata" in str(node.target):
             joint.graph.erase_node(node)
+        elif node.op == "call_function" and "device" in node.kwargs:
+            # the trace ran on the meta device; a cast keeps its input's device when none is named
+            if not node.all_input_nodes:
+                raise ValueError(f"{node.name}: the backward pass creates a tensor on a fixed device")
+            node.kwargs = {k: v for k, v in node.kwargs.items() if k not in ("device", "layout")}
     joint.graph.eliminate_dead_code()
     joint.recompile()
     return joint

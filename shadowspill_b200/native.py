@@ -206,6 +206,8 @@ def _declare(lib: C.CDLL) -> None:
     lib.ss_step_begin.argtypes = [vp, i32, vp]
     lib.ss_before_task.argtypes = [vp, i32, i32, C.POINTER(vp), i32]
     lib.ss_after_task.argtypes = [vp, i32, i32]
+    lib.ss_before_task_on.argtypes = [vp, i32, i32, C.POINTER(vp), i32, vp]
+    lib.ss_after_task_on.argtypes = [vp, i32, i32, vp]
     lib.ss_step_end.argtypes = [vp, i32]
     lib.ss_runtime_wait_idle.argtypes = [vp]
     lib.ss_spill_write.argtypes = [vp, i64, vp, i64]

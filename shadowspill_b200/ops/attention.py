@@ -82,14 +82,35 @@ def forward(q, k, v, cu_seqlens, max_seqlen, scale=None, out=None, lse=None):
     return o, lse
 
 
+def _gradients_like(q, k, v):
+    """Gradient buffers with the strides of q, k and v (the kernels use one row pitch for an
+    operand and its gradient). Views of one fused projection get views of one fused buffer."""
+    if q.is_contiguous() and k.is_contiguous() and v.is_contiguous():
+        return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    same = (q.untyped_storage().data_ptr() == k.untyped_storage().data_ptr() == v.untyped_storage().data_ptr()
+            and q.stride(0) == k.stride(0) == v.stride(0))
+    if same:
+        base = min(q.storage_offset(), k.storage_offset(), v.storage_offset())
+        cols = [t.storage_offset() - base + t.shape[1] * t.shape[2] for t in (q, k, v)]
+        if max(cols) <= q.stride(0):
+            buf = torch.empty((q.shape[0], q.stride(0)), dtype=q.dtype, device=q.device)
+            return tuple(buf.as_strided(t.shape, t.stride(), t.storage_offset() - base) for t in (q, k, v))
+    return tuple(torch.empty_strided(t.shape, t.stride(), dtype=t.dtype, device=t.device) for t in (q, k, v))
+
+
 def backward(q, k, v, out, lse, dout, cu_seqlens, max_seqlen, scale=None, dq=None, dk=None,
              dv=None):
     T, Hq, dh = q.shape
     Hkv = k.shape[1]
     scale = scale if scale is not None else 1.0 / math.sqrt(dh)
+    if dq is None and dk is None and dv is None:
+        dq, dk, dv = _gradients_like(q, k, v)
     dq = torch.empty_like(q) if dq is None else dq
     dk = torch.empty_like(k) if dk is None else dk
     dv = torch.empty_like(v) if dv is None else dv
+    for g, t in ((dq, q), (dk, k), (dv, v)):
+        if g.stride() != t.stride():
+            raise ValueError("attention gradients must have the strides of their operands")
     if implementation("ss_attn_bwd") == "library":
         from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
         dqc = dq if dq.is_contiguous() else torch.empty_like(q)

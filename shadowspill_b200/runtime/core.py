@@ -146,14 +146,16 @@ class Runtime:
     def step_begin(self, plan_id: int, compute_stream: int | None) -> None:
         self._raise(self.lib.ss_step_begin(self.handle, plan_id, compute_stream), "ss_step_begin")
 
-    def before_task(self, plan_id: int, task: int, n_uses: int) -> list[int]:
+    def before_task(self, plan_id: int, task: int, n_uses: int, stream: int | None = None) -> list[int]:
+        """``stream``: raw handle of the stream the task runs on when that is not the step's
+        compute stream (a collective on the communication stream)."""
         buf = (native.vp * max(1, n_uses))()
-        self._raise(self.lib.ss_before_task(self.handle, plan_id, task, buf, n_uses),
+        self._raise(self.lib.ss_before_task_on(self.handle, plan_id, task, buf, n_uses, stream),
                     "ss_before_task")
         return [int(buf[i] or 0) for i in range(n_uses)]
 
-    def after_task(self, plan_id: int, task: int) -> None:
-        self._raise(self.lib.ss_after_task(self.handle, plan_id, task), "ss_after_task")
+    def after_task(self, plan_id: int, task: int, stream: int | None = None) -> None:
+        self._raise(self.lib.ss_after_task_on(self.handle, plan_id, task, stream), "ss_after_task")
 
     def step_end(self, plan_id: int) -> None:
         self._raise(self.lib.ss_step_end(self.handle, plan_id), "ss_step_end")

@@ -62,6 +62,21 @@ def test_two_gpus_match_resident(arm):
 
 @pytest.mark.gpu
 @pytest.mark.multigpu
+@pytest.mark.parametrize("nvls", ["0", "1"])
+def test_fused_reduce_scatter_adamw_elementwise(nvls):
+    """The fused kernel on its own: p, m and v of the owned slice against AdamW on the fp32-summed
+    gradient, to one bf16 unit in the last place; ragged tails, fp32 gradients, and the in-switch
+    sum when the fabric offers it."""
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0", SS_NVLS=nvls)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29671", str(WORKER.with_name("_rs_worker.py"))]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    assert out.stdout.count(" OK ") == 2, out.stdout[-2000:]
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
 def test_two_gpus_expert_parallel_planned_execution():
     """A routed model trains through the planned executor with its experts split over two
     GPUs (peer-memory dispatch/combine inside the layer tasks) and matches the resident
