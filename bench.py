@@ -6,6 +6,7 @@ alternating loss-mask spans), synthetic data and random-init weights.
 
     python bench.py --gpus N --steps K --warmup W         # this framework
     python bench.py --impl reference ...                   # the reference, if installable
+    python bench.py --impl library ...                     # same planner/runtime on cuBLAS + flash-attn + NCCL
 
 For N > 1 launch one rank per GPU (torch.distributed.run); per-GPU work is fixed
 (weak scaling) and the reported value is the whole-job aggregate. One JSON line
@@ -103,7 +104,9 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--impl", default="native", choices=["native", "reference", "library"],
+                    help="library = this repository's planner and runtime over cuBLAS, flash-attn, eager "
+                         "elementwise ops and NCCL (the comparison arm; never labelled reference)")
     ap.add_argument("--model", default="llama3-8b")
     ap.add_argument("--device-gib", type=float, default=24.0)
     ap.add_argument("--spill-gib", type=float, default=128.0)
@@ -130,6 +133,11 @@ def main() -> None:
     if args.impl == "reference":
         reference_arm()
         return
+    if args.impl == "library":
+        # must be set before the op layer is imported
+        os.environ["SS_KERNELS"] = "library"
+        os.environ["SS_ATTENTION"] = "library"
+        args.collectives = "dist"
 
     import torch
     import torch.distributed as dist
@@ -250,7 +258,7 @@ def main() -> None:
             "e2e": {"value": round(total_tokens / wall, 1), "unit": "tokens/s",
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                     "api": "TrainingSession.step(host numpy batch) -> host loss"},
-            "gpu_launches": int(launches), "clocks": clocks,
+            "gpu_launches": int(launches), "impl": args.impl, "clocks": clocks,
             "loss_first": round(losses[0], 4), "loss_last": round(losses[-1], 4),
             "peak_device_gib": round(session.peak_device_bytes() / GIB, 2),
         }

@@ -444,6 +444,13 @@ class Executor:
     def operations(self) -> list[str]:
         return sorted(self._bound)
 
+    def operation_name(self) -> str:
+        """Name of the operation whose plan is currently selected."""
+        for name, bound in self._bound.items():
+            if bound["plan_id"] == self.plan_id:
+                return name
+        return self.operation
+
     # ------------------------------------------------------------------ state in the spill pool
     def spill_view(self, obj: int, writable: bool = True) -> torch.Tensor:
         """The object's home as host bytes. In the pinned pool this is a view. For an object
@@ -708,7 +715,17 @@ class Executor:
         self.runner.completed_updates, self.runner.accumulated = done, acc
 
     def _run(self, batch, trace: bool, time_tasks: bool, t0: float) -> InvocationResult:
-        h2d = self.stage_inputs(batch) if self.n_mb and batch is not None else 0
+        if self.total_ranks > 1:
+            # host-side work first, then agreement: a rank whose batch is bad (or which raised for
+            # any other reason) stops every rank before the first collective is enqueued
+            from ..parallel import control
+
+            def prepare():
+                control.check_invocation(self.operation_name(), self.runner.accumulated)
+                return self.stage_inputs(batch) if self.n_mb and batch is not None else 0
+            h2d = control.coordinated(prepare)
+        else:
+            h2d = self.stage_inputs(batch) if self.n_mb and batch is not None else 0
         if self._loss_obj >= 0:
             self.spill_view(self._loss_obj).zero_()
         self.runner.grad_seen = set()

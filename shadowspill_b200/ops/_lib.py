@@ -116,7 +116,7 @@ def check_status(device: torch.device | int | None = None) -> None:
 
 # kernels launched by one successful call of each launcher (attention backward:
 # delta + dQ + dKV; sum of squares: partials + final)
-_KERNELS_PER_CALL = {"ss_attn_bwd": 3, "ss_sumsq": 2}
+_KERNELS_PER_CALL = {"ss_attn_bwd": 3, "ss_attn_bwd_g": 3, "ss_sumsq": 2}
 launch_count = 0
 
 

@@ -24,6 +24,10 @@ _c = _lib
 _lib.register("ss_attn_fwd", [_c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_int, _c.c_int,
                               _c.c_int, _c.c_int, _c.c_int, _c.c_ll, _c.c_ll, _c.c_ll, _c.c_ll,
                               _c.c_f, _c.c_p, _c.c_p])
+_lib.register("ss_attn_bwd_g", [_c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_p,
+                                _c.c_p, _c.c_p, _c.c_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                                _c.c_int, _c.c_ll, _c.c_ll, _c.c_ll, _c.c_ll, _c.c_ll, _c.c_ll, _c.c_ll,
+                                _c.c_f, _c.c_p, _c.c_p])
 _lib.register("ss_attn_bwd", [_c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_p,
                               _c.c_p, _c.c_p, _c.c_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
                               _c.c_int, _c.c_ll, _c.c_ll, _c.c_ll, _c.c_ll, _c.c_f, _c.c_p,
@@ -82,35 +86,14 @@ def forward(q, k, v, cu_seqlens, max_seqlen, scale=None, out=None, lse=None):
     return o, lse
 
 
-def _gradients_like(q, k, v):
-    """Gradient buffers with the strides of q, k and v (the kernels use one row pitch for an
-    operand and its gradient). Views of one fused projection get views of one fused buffer."""
-    if q.is_contiguous() and k.is_contiguous() and v.is_contiguous():
-        return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-    same = (q.untyped_storage().data_ptr() == k.untyped_storage().data_ptr() == v.untyped_storage().data_ptr()
-            and q.stride(0) == k.stride(0) == v.stride(0))
-    if same:
-        base = min(q.storage_offset(), k.storage_offset(), v.storage_offset())
-        cols = [t.storage_offset() - base + t.shape[1] * t.shape[2] for t in (q, k, v)]
-        if max(cols) <= q.stride(0):
-            buf = torch.empty((q.shape[0], q.stride(0)), dtype=q.dtype, device=q.device)
-            return tuple(buf.as_strided(t.shape, t.stride(), t.storage_offset() - base) for t in (q, k, v))
-    return tuple(torch.empty_strided(t.shape, t.stride(), dtype=t.dtype, device=t.device) for t in (q, k, v))
-
-
 def backward(q, k, v, out, lse, dout, cu_seqlens, max_seqlen, scale=None, dq=None, dk=None,
              dv=None):
     T, Hq, dh = q.shape
     Hkv = k.shape[1]
     scale = scale if scale is not None else 1.0 / math.sqrt(dh)
-    if dq is None and dk is None and dv is None:
-        dq, dk, dv = _gradients_like(q, k, v)
-    dq = torch.empty_like(q) if dq is None else dq
-    dk = torch.empty_like(k) if dk is None else dk
-    dv = torch.empty_like(v) if dv is None else dv
-    for g, t in ((dq, q), (dk, k), (dv, v)):
-        if g.stride() != t.stride():
-            raise ValueError("attention gradients must have the strides of their operands")
+    dq = torch.empty(q.shape, dtype=q.dtype, device=q.device) if dq is None else dq
+    dk = torch.empty(k.shape, dtype=k.dtype, device=k.device) if dk is None else dk
+    dv = torch.empty(v.shape, dtype=v.dtype, device=v.device) if dv is None else dv
     if implementation("ss_attn_bwd") == "library":
         from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
         dqc = dq if dq.is_contiguous() else torch.empty_like(q)
@@ -127,12 +110,13 @@ def backward(q, k, v, out, lse, dout, cu_seqlens, max_seqlen, scale=None, dq=Non
     if not out.is_contiguous():
         raise ValueError("attention output must be contiguous [T, Hq, dh]")
     delta = torch.empty((Hq, T), dtype=torch.float32, device=q.device)   # kernel scratch
-    rc = _lib.lib().ss_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
-                                lse.data_ptr(), dout.data_ptr(), dq.data_ptr(), dk.data_ptr(),
-                                dv.data_ptr(), cu_seqlens.data_ptr(), delta.data_ptr(), nseq, T,
-                                Hq, Hkv, dh,
-                                _row_stride(q), _row_stride(k), _row_stride(v), _row_stride(dout),
-                                float(scale), _lib.status_word(q.device).data_ptr(),
-                                _lib.stream_ptr())
+    rc = _lib.lib().ss_attn_bwd_g(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                  lse.data_ptr(), dout.data_ptr(), dq.data_ptr(), dk.data_ptr(),
+                                  dv.data_ptr(), cu_seqlens.data_ptr(), delta.data_ptr(), nseq, T,
+                                  Hq, Hkv, dh,
+                                  _row_stride(q), _row_stride(k), _row_stride(v), _row_stride(dout),
+                                  _row_stride(dq), _row_stride(dk), _row_stride(dv),
+                                  float(scale), _lib.status_word(q.device).data_ptr(),
+                                  _lib.stream_ptr())
     _lib.check(rc, "ss_attn_bwd")
     return dq, dk, dv

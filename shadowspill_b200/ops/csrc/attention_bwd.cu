@@ -609,15 +609,19 @@ static int launch_dkv(const CUtensorMap& tq, const CUtensorMap& tdo, const CUten
 }  // namespace ss
 
 // delta_scratch: fp32 [Hq, T] caller-provided scratch.
-extern "C" int ss_attn_bwd(const void* q, const void* k, const void* v, const void* out,
-                           const float* lse, const void* dout, void* dq, void* dk, void* dv,
-                           const int* cu_seqlens, float* delta_scratch, int nseq, int T, int Hq,
-                           int Hkv, int dh, long long ldq, long long ldk, long long ldv,
-                           long long ldo, float scale, int* status, void* stream) {
+// lddq / lddk / lddv: row pitches of the gradient buffers, which need not be those of q, k, v
+// (a fused q/k/v projection read through views, gradients written to tensors of their own).
+extern "C" int ss_attn_bwd_g(const void* q, const void* k, const void* v, const void* out,
+                             const float* lse, const void* dout, void* dq, void* dk, void* dv,
+                             const int* cu_seqlens, float* delta_scratch, int nseq, int T, int Hq,
+                             int Hkv, int dh, long long ldq, long long ldk, long long ldv,
+                             long long ldo, long long lddq, long long lddk, long long lddv,
+                             float scale, int* status, void* stream) {
   using namespace ss;
   if (T <= 0 || nseq <= 0) return 0;
   if (delta_scratch == nullptr) return -2;
   if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (ldo % 8) || Hq % Hkv) return -2;
+  if ((lddq % 8) || (lddk % 8) || (lddv % 8)) return -2;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   {
     const long long warps = static_cast<long long>(T) * Hq;
@@ -628,7 +632,7 @@ extern "C" int ss_attn_bwd(const void* q, const void* k, const void* v, const vo
   }
   AttnBwdParams p;
   p.dq = dq; p.dk = dk; p.dv = dv; p.lse = lse; p.delta = delta_scratch; p.cu_seqlens = cu_seqlens;
-  p.nseq = nseq; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.ldq = ldq; p.ldk = ldk; p.ldv = ldv;
+  p.nseq = nseq; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.ldq = lddq; p.ldk = lddk; p.ldv = lddv;
   p.scale = scale; p.status = status;
   const int tiles = (T + 127) / 128 + nseq;
   const long long qc = static_cast<long long>(Hq) * dh, kc = static_cast<long long>(Hkv) * dh;
@@ -656,6 +660,16 @@ extern "C" int ss_attn_bwd(const void* q, const void* k, const void* v, const vo
     return launch_dkv<256, 1, MODE_DK>(tq64, tdo64, tk128, tv128, p, tiles, s);
   }
   return -2;
+}
+
+// delta_scratch: fp32 [Hq, T] caller-provided scratch. Gradients have the pitches of their operands.
+extern "C" int ss_attn_bwd(const void* q, const void* k, const void* v, const void* out,
+                           const float* lse, const void* dout, void* dq, void* dk, void* dv,
+                           const int* cu_seqlens, float* delta_scratch, int nseq, int T, int Hq,
+                           int Hkv, int dh, long long ldq, long long ldk, long long ldv,
+                           long long ldo, float scale, int* status, void* stream) {
+  return ss_attn_bwd_g(q, k, v, out, lse, dout, dq, dk, dv, cu_seqlens, delta_scratch, nseq, T, Hq, Hkv,
+                       dh, ldq, ldk, ldv, ldo, ldq, ldk, ldv, scale, status, stream);
 }
 
 // ============================================================================ no-allocation entry

@@ -36,10 +36,16 @@ struct AttnCfg {
   static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;
   static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;
   static constexpr int OFF_BAR = OFF_P + P_BYTES;
-  static constexpr int SMEM = OFF_BAR + 256 + 1024;
+  // Two CTAs share an SM when they fit (dh <= 128 with 64-key tiles): while one CTA's softmax
+  // warps work, the other CTA's MMAs keep the tensor pipe busy. Shared memory has no room for a
+  // blanket alignment slack then; the kernel checks the aligned layout against what it was given.
+  static constexpr int USED = OFF_BAR + 128;
+  // an SM has 228 KiB of shared memory and keeps 1 KiB per resident CTA for itself
+  static constexpr bool PAIR = 2 * (USED + 1024) <= 233472;
+  static constexpr int SMEM = PAIR ? USED : USED + 1024;
   static constexpr int TMEM_S0 = 0;
   static constexpr int TMEM_O = 2 * BKV;
-  static constexpr int TMEM_COLS = 512;
+  static constexpr int TMEM_COLS = (2 * BKV + DH) <= 256 ? 256 : 512;
 };
 
 struct AttnParams {
@@ -71,13 +77,18 @@ __device__ __forceinline__ bool find_tile(const int* cu, int nseq, int tile, int
 }
 
 template <int DH, int BKV>
-__global__ void __launch_bounds__(ATT_THREADS, 1)
+__global__ void __launch_bounds__(ATT_THREADS, (AttnCfg<DH, BKV>::TMEM_COLS <= 256 &&
+                                                AttnCfg<DH, BKV>::PAIR) ? 2 : 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
   using Cfg = AttnCfg<DH, BKV>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
+  if (smem + Cfg::USED > smem_raw + Cfg::SMEM) {      // the launch gave an unaligned window
+    if (threadIdx.x == 0) report(p.status, KS_BAD_ARGUMENT);
+    return;
+  }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
   uint64_t* q_full = bars;          // 1
   uint64_t* kv_full = bars + 1;     // 2
@@ -211,9 +222,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int k0 = seq_start + j * BKV;
       const bool diag = (k0 + BKV - 1) > q0;     // some key of this tile may exceed some query
       const uint32_t s_addr = lane_addr + Cfg::TMEM_S0 + b * BKV;
-      // pass 1: row maximum
-      float m_t = -INFINITY;
-#pragma unroll 1
+      // one read of S: the row stays in registers for the maximum and for the exponentials
+      float sv[BKV];
+#pragma unroll
       for (int c = 0; c < BKV / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(s_addr + c * 32, r);
@@ -222,9 +233,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int e = 0; e < 32; ++e) {
           float s = __uint_as_float(r[e]) * p.scale_log2;
           if (diag && (k0 + c * 32 + e) > gq) s = -INFINITY;
-          m_t = fmaxf(m_t, s);
+          sv[c * 32 + e] = s;
         }
       }
+      // S is in registers: the MMA warp may overwrite this buffer with the tile after next
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[b]);
+      float m_t = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < BKV; ++e) m_t = fmaxf(m_t, sv[e]);
       // lazy rescale: move the reference max only when it would grow by > 8 (2^8 headroom)
       const bool want = m_t > m_used + 8.f;
       const bool first = (j == 0);
@@ -236,6 +254,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         m_used = m_new;
         l *= alpha;
       }
+      // probabilities -> swizzled K-major P tile in shared memory. The previous P·V has to be
+      // done with the tile first (o_done also covers the rescale of O below).
       if (j > 0) {
         if (!mbar_wait(o_done, (j - 1) & 1, p.status, KS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
         tc_fence_after();
@@ -252,24 +272,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tmem_st_wait();
         }
       }
-      // pass 2: probabilities -> swizzled K-major P tile in shared memory
       float lsum = 0.f;
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < BKV / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(s_addr + c * 32, r);
-        tmem_ld_wait();
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          float s0 = __uint_as_float(r[e]) * p.scale_log2;
-          float s1 = __uint_as_float(r[e + 1]) * p.scale_log2;
-          if (diag) {
-            if ((k0 + c * 32 + e) > gq) s0 = -INFINITY;
-            if ((k0 + c * 32 + e + 1) > gq) s1 = -INFINITY;
-          }
-          const float p0 = fast_exp2(s0 - m_used);
-          const float p1 = fast_exp2(s1 - m_used);
+          const float p0 = fast_exp2(sv[c * 32 + e] - m_used);
+          const float p1 = fast_exp2(sv[c * 32 + e + 1] - m_used);
           lsum += p0 + p1;
           pk[e >> 1] = pack_bf16(p0, p1);
         }
@@ -287,10 +297,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_before();
       fence_async_proxy();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&s_free[b]);
-        mbar_arrive(p_full);
-      }
+      if (lane == 0) mbar_arrive(p_full);
     }
     // ---------------------------------------------------------------- epilogue
     if (ok && n_kv > 0 && mbar_wait(o_done, (n_kv - 1) & 1, p.status, KS_TIMEOUT_TMEM_FULL)) {
@@ -362,8 +369,8 @@ extern "C" int ss_attn_fwd(const void* q, const void* k, const void* v, void* ou
   // every sequence adds at most one partial tile
   const int max_tiles = (T + ATT_BM - 1) / ATT_BM + nseq;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (dh == 128) return launch_fwd<128, 128>(q, k, v, p, ldq, ldk, ldv, max_tiles, s);
-  if (dh == 64) return launch_fwd<64, 128>(q, k, v, p, ldq, ldk, ldv, max_tiles, s);
+  if (dh == 128) return launch_fwd<128, 64>(q, k, v, p, ldq, ldk, ldv, max_tiles, s);
+  if (dh == 64) return launch_fwd<64, 64>(q, k, v, p, ldq, ldk, ldv, max_tiles, s);
   if (dh == 256) return launch_fwd<256, 64>(q, k, v, p, ldq, ldk, ldv, max_tiles, s);
   return -2;
 }

@@ -18,8 +18,30 @@ from . import _lib, reference
 _BF16 = torch.bfloat16
 
 
+# SS_KERNELS=library is the comparison arm: the same planner, runtime and model code, but every op
+# runs on vendor libraries and eager PyTorch (cuBLAS GEMMs, flash-attn, elementwise tensor
+# operations) instead of this repository's kernels. It exists to be timed against, never as a
+# fallback: nothing selects it but the variable.
+_LIBRARY = os.environ.get("SS_KERNELS", "native") == "library"
+
+
 def _cuda(t: torch.Tensor) -> bool:
-    return t.is_cuda
+    return t.is_cuda and not _LIBRARY
+
+
+def _gemm_library(a, b, a_mn, b_mn, out, accumulate, alpha, out_dtype):
+    """cuBLAS arm of ``gemm`` (bf16 operands, fp32 accumulation inside the library)."""
+    am = a.t() if a_mn else a
+    bm = b if b_mn else b.t()
+    if out is None:
+        res = torch.mm(am, bm)
+        return (res if alpha == 1.0 else res * alpha).to(out_dtype)
+    if out.dtype == am.dtype and out.is_contiguous():
+        return torch.addmm(out, am, bm, beta=1.0 if accumulate else 0.0, alpha=alpha, out=out)
+    res = torch.mm(am, bm).to(out.dtype)
+    if alpha != 1.0:
+        res = res * alpha
+    return out.add_(res) if accumulate else out.copy_(res)
 
 
 def _ptr(t: torch.Tensor | None) -> int | None:
@@ -51,6 +73,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         out_dtype = out_dtype or a.dtype
     elif out.shape != (M, N):
         raise ValueError(f"output shape {tuple(out.shape)} != {(M, N)}")
+    if a.is_cuda and _LIBRARY:
+        return _gemm_library(a, b, a_mn, b_mn, out, accumulate, alpha, out_dtype or a.dtype)
     if not _cuda(a):
         return reference.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out, accumulate=accumulate,
                               alpha=alpha, out_dtype=out_dtype or a.dtype)
@@ -294,7 +318,7 @@ def sumsq(x, partials, out, accumulate=False):
 # ------------------------------------------------------------------------ attention
 def attention_varlen(q, k, v, cu_seqlens, max_seqlen, scale=None, out=None, lse=None):
     """Packed causal GQA forward. Returns ``(out, lse)``; ``lse`` is fp32 ``[Hq, T]``."""
-    if not _cuda(q):
+    if not q.is_cuda:
         o, l = reference.attention_varlen(q, k, v, cu_seqlens, scale)
         if out is not None:
             o = out.copy_(o)
@@ -306,7 +330,7 @@ def attention_varlen(q, k, v, cu_seqlens, max_seqlen, scale=None, out=None, lse=
 
 
 def attention_varlen_bwd(q, k, v, out, lse, dout, cu_seqlens, max_seqlen, scale=None):
-    if not _cuda(q):
+    if not q.is_cuda:
         return reference.attention_varlen_bwd(q, k, v, out, lse, dout, cu_seqlens, scale)
     from . import attention
     return attention.backward(q, k, v, out, lse, dout, cu_seqlens, max_seqlen, scale)

@@ -23,13 +23,13 @@ from shadowspill_b200.planning.plan import MemoryBudgets, PlanningError, SearchO
 GEO = BatchGeometry(microbatch_tokens=256, n_microbatches=2, slots=16, mean_seqlen=64)
 
 
-def _plan(prog, pct_from=30):
+def _plan(prog, pct_from=30, spill=64 << 20):
     total = sum(o.bytes for o in prog.objects)
     ws = max(t.workspace_bytes for t in prog.tasks)
     opts = SearchOptions(minimum_object_bytes_evict_eligible=1024, workers=2)
     for pct in range(pct_from, 101, 5):
         try:
-            return plan_program(prog, MemoryBudgets(ws + total * pct // 100, 64 << 20, headroom_bytes=0),
+            return plan_program(prog, MemoryBudgets(ws + total * pct // 100, spill, headroom_bytes=0),
                                 CommunicationInfo(), opts)
         except PlanningError:
             continue
@@ -168,7 +168,7 @@ def test_graph_frontend_on_the_gpu_matches_the_stage_classes(name):
     for frontend in ("stages", "graph"):
         prog, desc = build_step(cfg, geo, StepDataOrdering(), dtype=torch.bfloat16,
                                 selection=sel if frontend == "graph" else {}, frontend=frontend)
-        plan = _plan(prog, pct_from=60)
+        plan = _plan(prog, pct_from=60, spill=1 << 30)
         ex = Executor(plan, desc, device="cuda", seed=11, hyper=Hyperparameters(lr=1e-3),
                       stochastic_rounding=False)
         ex.initialize(on_device=False)

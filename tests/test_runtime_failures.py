@@ -176,3 +176,20 @@ def test_invalid_worker_group_still_accepts_close():
     with pytest.raises(WorkerFailure):
         g.execute("r1", "step", {})
     assert g.execute("r2", "close", {})[0]["state"] == "completed"
+
+
+@pytest.mark.parametrize("bad", [1, -1])
+def test_host_agreement_stops_every_rank_before_the_collectives(bad):
+    """Three gloo ranks; one raises while preparing the invocation. Every rank learns of it over
+    the control group and none enters the collective; with no failure they all proceed, and a
+    mismatch of the selected operation is refused too."""
+    import os
+    import subprocess
+    from pathlib import Path
+    worker = Path(__file__).with_name("_coord_worker.py")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3",
+           "--master-addr", "127.0.0.1", "--master-port", "29683" if bad >= 0 else "29685", str(worker), str(bad)]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    assert out.stdout.count(" OK refused" if bad >= 0 else " OK ran") == 3, out.stdout[-2000:]
