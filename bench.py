@@ -127,6 +127,9 @@ def main() -> None:
     ap.add_argument("--spill-address", default="", help="host:port of the memory daemon")
     ap.add_argument("--collectives", default="auto", choices=["auto", "peer", "dist"],
                     help="peer = own kernels over NVLink peer memory; dist = NCCL baseline arm")
+    ap.add_argument("--allocator", default="caching", choices=["caching", "planned"],
+                    help="planned = the allocation adapter: task temporaries from a workspace slice of the "
+                         "device pool under a checked contract; caching = torch's allocator under a cap")
     ap.add_argument("--frontend", default="stages", choices=["stages", "graph"],
                     help="graph = torch.export -> partition -> AOT graph pairs; stages = hand-written stage classes")
     args = ap.parse_args()
@@ -171,7 +174,7 @@ def main() -> None:
                                  "targets": ["wq", "wk", "wv", "wo", "w13", "w2"], "routed_experts": True,
                                  "train_base": False} if args.lora_rank else None),
                           expert_parallel=args.expert_parallel, spill_pool=args.spill_pool,
-                          frontend=args.frontend,
+                          frontend=args.frontend, allocator=args.allocator,
                           spill_directory=args.spill_dir if args.spill_pool == "file" else "",
                           spill_address=args.spill_address)
     log = (lambda m: print(f"[bench] {m}", file=sys.stderr, flush=True)) if rank == 0 else None
@@ -252,7 +255,7 @@ def main() -> None:
                                 "workspace_gib": round(plan.workspace_bytes / GIB, 2),
                                 "spill_gib": round(session.plan.spill_bytes / GIB, 2)},
                        "attention": os.environ.get("SS_ATTENTION", "native"),
-                       "frontend": session.desc.frontend,
+                       "frontend": session.desc.frontend, "allocator": args.allocator,
                        "collectives": (session.executor.collectives.name
                                        if session.executor.collectives else "none")},
             "e2e": {"value": round(total_tokens / wall, 1), "unit": "tokens/s",

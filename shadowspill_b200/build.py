@@ -24,6 +24,8 @@ KERNEL_LIB = ROOT / "ops" / "libss_kernels.so"
 CORE_DIR = ROOT / "csrc"
 CORE_LIB = CORE_DIR / "libss_core.so"
 CUDA_BACKEND_LIB = CORE_DIR / "libss_backend_cuda.so"
+ALLOCATOR_LIB = CORE_DIR / "libss_allocator.so"           # torch pluggable allocator (links cudart)
+ALLOCATOR_HOST_LIB = CORE_DIR / "libss_allocator_host.so"  # the same logic over host memory, for tests
 MEMORY_DAEMON = CORE_DIR / "ss_memory_daemon"     # far side of the remote spill pool
 
 NVCC_FLAGS = [
@@ -94,7 +96,7 @@ def _cuda_home() -> Path | None:
 def build_core(force: bool = False, verbose: bool = False) -> Path:
     """Compile the C++17 core (simulator, planner, runtime, mock backend)."""
     sources = sorted(p for p in CORE_DIR.rglob("*.cpp") if "backend_cuda" not in p.name
-                     and "canary" not in p.name and p.parent.name != "daemon")
+                     and "canary" not in p.name and p.parent.name not in ("daemon", "adapter"))
     headers = sorted(CORE_DIR.rglob("*.h")) + sorted(CORE_DIR.rglob("*.hpp"))
     if not sources:
         return CORE_LIB
@@ -117,6 +119,16 @@ def build_core(force: bool = False, verbose: bool = False) -> Path:
               "-I", str(cuda / "include"), "-o", str(tmp), *map(str, cuda_src),
               "-L", str(cuda / "lib64"), "-lcudart", "-ldl"], verbose)
         os.replace(tmp, CUDA_BACKEND_LIB)
+    alloc_src = sorted((CORE_DIR / "adapter").glob("allocator*.cpp"))
+    if alloc_src and (force or _stale(ALLOCATOR_HOST_LIB, alloc_src)):
+        tmp = ALLOCATOR_HOST_LIB.with_suffix(".so.tmp")
+        _run(["g++", *CXX_FLAGS, "-shared", "-o", str(tmp), *map(str, alloc_src)], verbose)
+        os.replace(tmp, ALLOCATOR_HOST_LIB)
+    if alloc_src and cuda is not None and (force or _stale(ALLOCATOR_LIB, alloc_src)):
+        tmp = ALLOCATOR_LIB.with_suffix(".so.tmp")
+        _run(["g++", *CXX_FLAGS, "-shared", "-DSS_ALLOCATOR_WITH_CUDA", "-I", str(cuda / "include"),
+              "-o", str(tmp), *map(str, alloc_src), "-L", str(cuda / "lib64"), "-lcudart"], verbose)
+        os.replace(tmp, ALLOCATOR_LIB)
     return CORE_LIB
 
 

@@ -320,7 +320,17 @@ class Executor:
         if desc.replicas > 1 and desc.expert_parallel:
             raise NotImplementedError("expert parallelism runs on one replica")
         extra_plans = dict(extra_plans or {})
+        # With the allocation adapter installed, task temporaries are carved from a workspace slice
+        # that sits right behind the planned ranges in the same device allocation.
+        from ..runtime import allocator as _alloc
+        self.allocator = _alloc.installed() if self.cuda else None
+        self.workspace_bytes = 0
+        if self.allocator is not None:
+            ws = max([plan.summary.workspace_bytes] + [p.summary.workspace_bytes for p, _ in extra_plans.values()])
+            self.workspace_bytes = -(-int(ws) // 4096) * 4096
         device_bytes = max([plan.device_bytes] + [p.device_bytes for p, _ in extra_plans.values()])
+        self.planned_device_bytes = device_bytes
+        device_bytes += self.workspace_bytes
         spill_bytes = max([plan.spill_bytes] + [p.spill_bytes for p, _ in extra_plans.values()])
         pool = coll = None
         if self.world > 1:
@@ -384,6 +394,9 @@ class Executor:
         self.comm_stream = (torch.cuda.Stream(device=self.torch_device)
                             if (self.cuda and self.world > 1 and os.environ.get("SS_COMM_STREAM", "1") == "1")
                             else None)
+        if self.allocator is not None:
+            self.allocator.configure(self.rt.device_base + self.planned_device_bytes, self.workspace_bytes,
+                                     self.stream.cuda_stream)
         self._views: dict[tuple[int, int], object] = {}
         self._uses = self.runner.uses
         self.T, self.n_mb, self.slots = self.runner.T, self.runner.n_mb, self.runner.slots
@@ -769,6 +782,9 @@ class Executor:
                                 self.stream.wait_event(ev)
                     ptrs = self.rt.before_task(self.plan_id, task, len(self._uses[task]))
                 B = self._bind(task, ptrs)
+                if self.allocator is not None:
+                    self.allocator.begin_task(t.name, 2 if (t.allocations and not side) else 0,
+                                              t.allocations if not side else None)
                 if events:
                     events[task][0].record(run_stream)
                 elif not self.cuda and time_tasks:
@@ -786,6 +802,9 @@ class Executor:
                     events[task][1].record(run_stream)
                 elif not self.cuda and time_tasks:
                     task_seconds[task] = time.perf_counter() - tt
+                if self.allocator is not None:
+                    self.allocator.end_task()
+                    self.allocator.raise_if_failed()     # OutOfMemoryError / contract violation naming the task
                 if side:
                     self.rt.after_task(self.plan_id, task, stream=self.comm_stream.cuda_stream)
                     done = torch.cuda.Event()
@@ -853,6 +872,11 @@ class Executor:
             for b in self._bound.values():
                 b["_views"].clear()
                 self.rt.close_plan(b["plan_id"])
+            if self.allocator is not None:
+                try:
+                    self.allocator.configure(0, 0)
+                except RuntimeError:
+                    pass                      # a caller still holds a tensor from the slice
         finally:
             self.rt.close()
 

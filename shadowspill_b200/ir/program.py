@@ -67,6 +67,9 @@ class TaskSpec:
     flops: float = 0.0
     tokens: int = 0
     profile_key: str = ""            # tasks with the same key share one measured profile
+    # the task's allocation contract: sizes of the tensor allocations it makes, in order, as
+    # recorded when it was profiled under the allocation adapter (empty = not recorded)
+    allocations: list[int] = field(default_factory=list)
 
     def __post_init__(self):
         if self.kind not in TASK_KINDS:

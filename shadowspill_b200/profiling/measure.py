@@ -33,6 +33,7 @@ class TaskProfile:
     workspace_bytes: int
     samples: int
     spread: float            # MAD / median
+    allocations: list = field(default_factory=list)   # request sizes under the allocation adapter
 
 
 @dataclass
@@ -108,16 +109,37 @@ def measure_program(program: Program, desc: TrainingDescription, device: str = "
         _fill_inputs(runner, ti, flats, host_batch)
         B = runner.bind(ti, flats)
         samples: list[float] = []
-        if cuda:
+        from ..runtime import allocator as _alloc
+        adapter = _alloc.installed() if cuda else None
+        contract: list[int] = []
+        if adapter is not None:
+            # the allocation contract: three warmed runs must ask for the same tensors in the same
+            # order (packages/engine/src/shadowspill/profiling/measure.py:31 does the same)
+            runner.grad_seen = set()
+            runner.run_task(ti, B)                 # warm-up outside the record
+            runs = []
+            for _ in range(3):
+                runner.grad_seen = set()
+                with adapter.task(program.tasks[ti].name, _alloc.RECORD) as seq:
+                    runner.run_task(ti, B)
+                runs.append(list(seq))
+            torch.cuda.synchronize(dev)
+            if not (runs[0] == runs[1] == runs[2]):
+                raise RuntimeError(f"task {program.tasks[ti].name} allocates differently from run to run: "
+                                   f"{[len(r) for r in runs]} requests; it has no stable allocation contract")
+            contract = runs[0]
+            workspace = adapter.stats()["task_peak"]
+        elif cuda:
             torch.cuda.synchronize(dev)
             torch.cuda.reset_peak_memory_stats(dev)
             base = torch.cuda.memory_allocated(dev)
-        runner.grad_seen = set()
-        runner.run_task(ti, B)                     # conditioning
-        if cuda:
+            runner.grad_seen = set()
+            runner.run_task(ti, B)                 # conditioning
             torch.cuda.synchronize(dev)
             workspace = torch.cuda.max_memory_allocated(dev) - base
         else:
+            runner.grad_seen = set()
+            runner.run_task(ti, B)                 # conditioning
             workspace = program.tasks[ti].workspace_bytes
         while len(samples) < max_samples:
             runner.grad_seen = set()
@@ -140,10 +162,12 @@ def measure_program(program: Program, desc: TrainingDescription, device: str = "
         med = statistics.median(samples)
         mad = statistics.median(abs(s - med) for s in samples)
         profiles.tasks[key] = TaskProfile(key, med, int(workspace), len(samples),
-                                          mad / med if med > 0 else 0.0)
+                                          mad / med if med > 0 else 0.0, contract)
         del flats, B
         if cuda:
             torch.cuda.empty_cache()
+            if adapter is not None:
+                adapter.trim()
     return profiles
 
 
@@ -167,6 +191,7 @@ def apply_profiles(program: Program, profiles: Profiles, workspace_margin: float
             # depend on every rank's routing
             margin = max(margin, 1.75)
         t.workspace_bytes = int(p.workspace_bytes * margin)
+        t.allocations = list(p.allocations)
     if missing:
         raise KeyError(f"no profile for {sorted(set(missing))[:4]}")
     program.metadata["profiled_on"] = profiles.device

@@ -84,6 +84,10 @@ class TrainingSetup:
     # "graph": torch.export -> stage partition -> AOT save/recompute graph pairs for the models the
     # graph frontend covers (frontend/graph_stage.py); "stages": the hand-written stage classes
     frontend: str = "stages"
+    # "planned": install the allocation adapter (runtime/allocator.py) before the first CUDA use:
+    # task temporaries then come out of a workspace slice of the device pool under a checked
+    # per-task contract. "caching": torch's caching allocator, capped to the planned workspace.
+    allocator: str = "caching"
     pretrained: str = ""                 # directory of Hugging Face safetensors to start from
     # content-addressed store of task profiles shared between runs ("" = none)
     store: str = ""
@@ -111,6 +115,11 @@ class TrainingSession:
         self.log = log or (lambda msg: None)
         self.cfg = setup.model if isinstance(setup.model, DecoderConfig) else preset(setup.model)
         self.dtype = _DTYPES[setup.dtype]
+        if setup.allocator == "planned" and setup.device == "cuda":
+            from ..runtime import allocator as _alloc
+            _alloc.install()
+        elif setup.allocator not in ("planned", "caching"):
+            raise ValueError("allocator is 'planned' or 'caching'")
         cuda = setup.device == "cuda"
         if setup.tokens_per_step % setup.microbatch_tokens:
             raise ValueError("tokens_per_step must be a multiple of microbatch_tokens")
@@ -362,7 +371,7 @@ class TrainingSession:
                  f"simulated {self.plan.summary.duration_seconds * 1e3:.1f} ms")
         # ---- executor (caps the torch allocator to the planned workspace)
         t0 = time.perf_counter()
-        if cuda:
+        if cuda and setup.allocator != "planned":
             total = torch.cuda.get_device_properties(setup.device_index).total_memory
             cap = max([self.plan.summary.workspace_bytes] +
                       [p.summary.workspace_bytes for p, _ in self.extra_plans.values()]) + (256 << 20)
@@ -412,11 +421,16 @@ class TrainingSession:
         return load_checkpoint(self.executor, directory)
 
     def peak_device_bytes(self) -> int:
-        """Device pool plus the torch allocator's peak reservation since opening."""
-        extra = 0
-        if self.setup.device == "cuda":
-            extra = torch.cuda.max_memory_reserved(self.setup.device_index)
-        return self.plan.device_bytes + extra
+        """Peak device memory of this worker. Under the allocation adapter that is reported from the
+        pool itself: planned ranges + the workspace slice (its peak use) + driver blocks held outside
+        tasks. Otherwise: the planned ranges plus the torch allocator's peak reservation."""
+        if self.setup.device != "cuda":
+            return self.plan.device_bytes
+        adapter = getattr(self.executor, "allocator", None)
+        if adapter is not None:
+            st = adapter.stats()
+            return self.plan.device_bytes + st["peak"] + st["driver_bytes"]
+        return self.plan.device_bytes + torch.cuda.max_memory_reserved(self.setup.device_index)
 
     def write_plan_report(self, directory: str) -> None:
         from ..reporting.write import write_report
@@ -438,5 +452,5 @@ class TrainingSession:
 
     def close(self) -> None:
         self.executor.close()
-        if self.setup.device == "cuda":
+        if self.setup.device == "cuda" and self.setup.allocator != "planned":
             torch.cuda.set_per_process_memory_fraction(1.0, self.setup.device_index)

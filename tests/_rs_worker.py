@@ -74,10 +74,13 @@ def main():
                                          ("v", v, want[2], v_full)):
             ref = ref_full[lo:hi]
             err = (got[:hi - lo].float() - ref).abs()
-            # one unit in the last place of the result, twice that where the in-switch sum was rounded
-            tol = ulp_bf16(ref) * (2.5 if nvls else 1.01) + 1e-12
+            # one unit in the last place of the result (twice that where the in-switch sum was rounded),
+            # plus the fp32 rounding of the terms themselves, which matters where they cancel
+            terms = old[lo:hi].float().abs() + (g_sum[lo:hi] * hyper["grad_scale"]).abs() + 1e-3
+            tol = ulp_bf16(ref) * (2.5 if nvls else 1.01) + 4e-7 * terms
             bad = int((err > tol).sum())
-            moved = float((got[:hi - lo].float() - old[lo:hi].float()).abs().max()) if hi > lo else 1.0
+            # a slice of a few elements may round back to where it was; a real slice must move
+            moved = float((got[:hi - lo].float() - old[lo:hi].float()).abs().max()) if hi - lo >= 64 else 1.0
             if bad or moved == 0.0:
                 failures.append(f"case {case} {name}: {bad} elements off, largest change {moved:.3g}")
         if per - (hi - lo) > 0 and float(p[hi - lo:].float().abs().max()) != 0.0:
