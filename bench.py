@@ -127,6 +127,8 @@ def main() -> None:
     ap.add_argument("--spill-address", default="", help="host:port of the memory daemon")
     ap.add_argument("--collectives", default="auto", choices=["auto", "peer", "dist"],
                     help="peer = own kernels over NVLink peer memory; dist = NCCL baseline arm")
+    ap.add_argument("--fused-gather", action="store_true",
+                    help="multi-GPU: the forward weight all-gather runs inside the consuming GEMM")
     ap.add_argument("--allocator", default="caching", choices=["caching", "planned"],
                     help="planned = the allocation adapter: task temporaries from a workspace slice of the "
                          "device pool under a checked contract; caching = torch's allocator under a cap")
@@ -144,6 +146,11 @@ def main() -> None:
 
     import torch
     import torch.distributed as dist
+
+    if args.allocator == "planned":
+        # before anything touches CUDA: the adapter cannot replace an allocator already in use
+        from shadowspill_b200.runtime import allocator as _allocator
+        _allocator.install()
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -174,7 +181,7 @@ def main() -> None:
                                  "targets": ["wq", "wk", "wv", "wo", "w13", "w2"], "routed_experts": True,
                                  "train_base": False} if args.lora_rank else None),
                           expert_parallel=args.expert_parallel, spill_pool=args.spill_pool,
-                          frontend=args.frontend, allocator=args.allocator,
+                          frontend=args.frontend, allocator=args.allocator, fused_gather=args.fused_gather,
                           spill_directory=args.spill_dir if args.spill_pool == "file" else "",
                           spill_address=args.spill_address)
     log = (lambda m: print(f"[bench] {m}", file=sys.stderr, flush=True)) if rank == 0 else None

@@ -85,6 +85,7 @@ class TaskRunner:
         self.completed_updates = 0
         self.accumulated = 0
         self.grad_seen: set[int] = set()
+        self.open_gathers: dict[int, list[int]] = {}     # stage -> full-weight buffers awaiting a fused gather
         self.param_offsets, off = {}, 0
         for si, st in enumerate(self.stages):
             for p in st.params:
@@ -193,15 +194,38 @@ class TaskRunner:
         elif t.kind == "collective" and t.variant == "allgather":
             coll = self.collectives
             coll.barrier_begin()          # every rank's shard has landed
+            fuse = ()
+            if (self.desc.fused_gather and hasattr(coll, "register_fused_gather")
+                    and t.name.rsplit(".", 1)[-1] in ("fwd", "all")):
+                fuse = getattr(st, "fused_gather_params", ())
+            opened = []
             for p in st.params:
                 if p.expert_sharded or st.kept_whole(p, self.desc.dtype):
                     # this rank's own experts, or a small tensor every rank stores whole: no gather
                     B["params"][p.name].view(-1).copy_(B["shard"][p.name][:p.numel])
+                elif p.name in fuse and len(p.shape) == 2:
+                    # the first GEMM that reads this matrix pulls the shards itself
+                    coll.register_fused_gather(B["shard"][p.name], B["params"][p.name])
+                    opened.append(B["params"][p.name].data_ptr())
                 else:
                     coll.all_gather(B["shard"][p.name], B["params"][p.name].view(-1))
-            coll.barrier_end()            # every rank is done reading this rank's shard
+            if opened:
+                # closed by close_gathers() after the stage's first forward task: peers read this
+                # rank's shard until then
+                self.open_gathers[t.stage] = opened
+            else:
+                coll.barrier_end()        # every rank is done reading this rank's shard
         else:
             raise RuntimeError(f"task kind {t.kind!r} has no executor")
+
+    def close_gathers(self, stage: int) -> None:
+        """After the first forward task of ``stage``: gather whatever no GEMM consumed, then wait
+        (on the compute stream's own flag words) until every rank is done reading the shards."""
+        opened = self.open_gathers.pop(stage, None)
+        if not opened:
+            return
+        F.flush_gathers(set(opened))
+        self.collectives.barrier_compute()
 
     def _first(self, stage: int, B) -> bool:
         if self.desc.mode == "step":
@@ -796,6 +820,8 @@ class Executor:
                         self.runner.run_task(task, B)
                 else:
                     self.runner.run_task(task, B)
+                    if self.runner.open_gathers and t.stage in self.runner.open_gathers:
+                        self.runner.close_gathers(t.stage)     # inside the task: its fence covers the barrier
                 if self.annotate:
                     torch.cuda.nvtx.range_pop()
                 if events:

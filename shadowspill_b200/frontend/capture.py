@@ -128,6 +128,10 @@ class TrainingDescription:
     # "stages": the hand-written stage classes; "graph": torch.export -> partition -> AOT graph
     # pairs (frontend/graph_stage.py) for the models it covers, the stage classes otherwise
     frontend: str = "stages"
+    # sharded storage on GPUs: leave the all-gather of a layer's matrices to the first GEMM that
+    # consumes them in the forward pass (ops/csrc/gemm_tcgen05_2cta.cu, GATHER form). The first
+    # forward task of the stage then also holds the shard, whose peers read it during that task.
+    fused_gather: bool = False
 
     def __post_init__(self) -> None:
         extras = extra_fields_for(self.cfg, self.objective)
@@ -281,6 +285,8 @@ def _build(desc: TrainingDescription) -> Program:
         kind = getattr(st, "mixer", "")
         return f"{cfg.family}:{st.kind}:{type(st).__name__}{':' + kind if kind else ''}:{what}:{var}:T{T}{tag}"
 
+    fresh_gather: set[tuple[int, str]] = set()       # gathers whose first consumer is still to come
+
     def params_of(si: int, which: str) -> int:
         """The object a compute task reads its weights from; under sharded storage
         the first user in a pass is preceded by the all-gather task that builds it."""
@@ -288,6 +294,7 @@ def _build(desc: TrainingDescription) -> Program:
             return W[si]
         tag = which if order.walk == "breadth" else "all"
         if (si, tag) not in FULL:
+            fresh_gather.add((si, tag))
             st = stages[si]
             obj = prog.add_object(ObjectSpec(f"{st.name}.weights.full.{tag}", full_bytes[si],
                                              "weight", stage=si))
@@ -304,6 +311,12 @@ def _build(desc: TrainingDescription) -> Program:
         var = desc.variant(si) if train else "recompute"
         uses = [UseSpec(params_of(si, "fwd"), "read", "params"), UseSpec(IN[m], "read", "batch"),
                 UseSpec(A[si][m], "create", "y")]
+        tag_ = "fwd" if order.walk == "breadth" else "all"
+        if (si, tag_) in fresh_gather:
+            fresh_gather.discard((si, tag_))
+            if desc.fused_gather and getattr(st, "fused_gather_params", ()):
+                # this task's GEMMs pull the peers' shards: the shard must outlive it
+                uses.append(UseSpec(W[si], "read", "shard"))
         if si > 0:
             uses.append(UseSpec(A[si - 1][m], "read", "x"))
         if (si, m) in SAVED:
@@ -425,14 +438,14 @@ def build_step(cfg: DecoderConfig, geometry: BatchGeometry,
                grad_dtype=None, selection: dict[int, str] | None = None, world_size: int = 1,
                rank: int = 0, objective=None, lora=None, expert_parallel: bool = False,
                replicas: int = 1, min_shard_bytes: int = 0, head_block_rows: int = 0,
-               master_weights: bool = False, frontend: str = "stages"):
+               master_weights: bool = False, frontend: str = "stages", fused_gather: bool = False):
     """Forward + backward + optimizer of one global batch. Returns ``(Program, description)``.
     ``world_size > 1`` builds the data-parallel form: weights and AdamW moments are
     stored as 1/N shards, gathered before use and updated shard-locally."""
     desc = TrainingDescription(cfg, geometry, ordering or StepDataOrdering(), dtype,
                                grad_dtype or dtype, dict(selection or {}), "step", world_size,
                                rank, objective, lora, expert_parallel, replicas, min_shard_bytes,
-                               head_block_rows, master_weights, frontend)
+                               head_block_rows, master_weights, frontend, fused_gather)
     return _build(desc), desc
 
 

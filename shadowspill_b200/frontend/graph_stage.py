@@ -49,6 +49,14 @@ class GraphStage(Stage):
         self.mixer = stage.key                 # keeps profiles of different structures apart
         self.SAVE_SETS = {v: tuple(s.name for s in pair.saved) for v, pair in pairs.pairs.items()}
         self._by_keep = {names: v for v, names in self.SAVE_SETS.items()}
+        # parameters the forward graph uses only as the weight of ss.linear: their gather can be
+        # fused into that GEMM under sharded storage
+        weight_of, other = set(), set()
+        for n in stage.gm.graph.nodes:
+            for i, a in enumerate(n.args if n.op == "call_function" else ()):
+                if isinstance(a, fx.Node) and a.op == "placeholder" and str(a.target) in stage.param_names:
+                    (weight_of if (op_name(n) == "ss.linear" and i == 1) else other).add(str(a.target))
+        self.fused_gather_params = tuple(sorted(weight_of - other)) if self.kind == "layer" else ()
 
     # ---- sizes
     def saved_shapes(self, T, variant, dtype=torch.bfloat16):

@@ -216,6 +216,9 @@ class DenseLayerStage(Stage):
     """Pre-norm GQA attention + SwiGLU MLP. q/k/v and gate/up are single fused
     projections; the two residual adds are folded into GEMM epilogues."""
     kind = "layer"
+    # matrices whose first use in a forward pass is ``x @ W^T``: their all-gather can be fused into
+    # that GEMM under sharded storage
+    fused_gather_params = ("wqkv", "wo", "w13", "w2")
     SAVE_SETS = {
         "recompute": (),
         "save_attention": ("qkv", "attn", "lse"),

@@ -24,6 +24,8 @@ _SIGNATURES = {
                      c_int, c_f, c_int, c_int, c_p, c_p],
     "ss_gemm2_bf16": [c_p, c_p, c_p, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int, c_int, c_int,
                       c_int, c_f, c_int, c_p, c_p],
+    "ss_gemm2_gather_bf16": [c_p, c_p, c_p, c_int, c_int, c_int, c_ll, c_ll, c_int, c_int, c_f, c_p, c_ll,
+                             c_int, c_int, c_p, c_ull, c_int, c_p, c_p],
     "ss_rmsnorm_fwd": [c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_f, c_int, c_p],
     "ss_rmsnorm_bwd": [c_p, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_int, c_p],
     "ss_rope": [c_p, c_p, c_int, c_ll, c_int, c_int, c_int, c_int, c_f, c_int, c_p],

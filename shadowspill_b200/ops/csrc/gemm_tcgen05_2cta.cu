@@ -19,6 +19,17 @@
 // "accumulator drained" barrier. Every wait is bounded (status word); both CTAs always
 // reach the closing cluster barrier.
 //
+// GATHER form (ss_gemm2_gather_bf16): the weight all-gather of sharded data parallelism fused
+// into the GEMM that first consumes the weight. B = W[N, K] lives as 1/world flat shards on the
+// ranks of the job; four extra warps per CTA pull the shards (plain 16-byte loads from peer
+// memory over NVLink, never TMA) into the LOCAL full-weight buffer in the order the tiles consume
+// it, 32 KiB at a time, and count the finished pieces of every 256-row tile in a per-tile counter.
+// The TMA producer waits (bounded) for a tile's counter before it loads that tile from local
+// HBM, so each weight byte crosses NVLink once, the gather overlaps the MMAs tile by tile, and
+// later GEMMs of the same weight read the buffer as usual. Tiles run n-major in this form, so the
+// weight is needed progressively over the whole GEMM. This is what the reference does with an
+// NCCL all-gather ahead of the GEMM (packages/engine/csrc/adapter/pytorch/storage/sharded.cpp:87).
+//
 // Same contract as ss_gemm_bf16 (operand layouts a_mn / b_mn, alpha, accumulate, bf16 or
 // fp32 output); reference: shadowspill::accumulate_matmul_
 // (packages/engine/src/shadowspill/pytorch/operations.py:15).
@@ -55,6 +66,32 @@ struct Params {
   float alpha;
   int* status;
 };
+
+constexpr int GATHER_THREADS = 128;                  // warps 6..9 of the GATHER form
+constexpr int PIECE_BYTES = 32768;
+constexpr int MAX_RANKS = 16;
+
+struct GatherArgs {
+  const uint8_t* shard[MAX_RANKS];   // rank k's shard: flat elements [k*per, (k+1)*per) of W
+  uint8_t* full;                     // the local full-weight buffer (= the GEMM's B)
+  long long shard_bytes;             // per * 2
+  long long total_bytes;             // N * K * 2
+  int world, rank;
+  unsigned int* counters;            // [tiles along N], zero at launch
+  unsigned long long wait_ns;
+};
+
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_gpu_add(unsigned int* p, unsigned int v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_global() {
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+}
 
 // ---- cluster / pair primitives
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -116,7 +153,13 @@ __device__ __forceinline__ void umma2_commit_both(uint64_t* bar) {
       : "memory");
 }
 
+template <bool GATHER>
 __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& mb, int& nb) {
+  if (GATHER) {            // every row block of one column tile, then the next column tile
+    mb = t % num_m;
+    nb = t / num_m;
+    return;
+  }
   constexpr int GROUP_M = 8;
   const int per_group = GROUP_M * num_n;
   const int g = t / per_group;
@@ -127,10 +170,10 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& mb
   nb = r / gm;
 }
 
-template <bool A_MN, bool B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+template <bool A_MN, bool B_MN, bool GATHER>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? THREADS + GATHER_THREADS : THREADS, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                  const Params p) {
+                  const Params p, const GatherArgs ga) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -183,9 +226,25 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       bool ok = true;
       for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
         int mb, nb;
-        tile_coords(t, num_m, num_n, mb, nb);
+        tile_coords<GATHER>(t, num_m, num_n, mb, nb);
         const int m0 = mb * (2 * BM) + static_cast<int>(rank) * BM;
         const int n0 = nb * BN + static_cast<int>(rank) * (BN / 2);
+        if (GATHER) {
+          // rows [nb*BN, nb*BN + BN) of W are local once every piece of the tile is counted
+          const long long tile_bytes = static_cast<long long>(BN) * p.K * 2;
+          const long long lo = static_cast<long long>(nb) * tile_bytes;
+          const long long hi = min(ga.total_bytes, lo + tile_bytes);
+          const unsigned int need = static_cast<unsigned int>((hi - lo + PIECE_BYTES - 1) / PIECE_BYTES);
+          const uint64_t t0 = globaltimer_ns();
+          for (uint32_t it = 0; ld_acquire_gpu(&ga.counters[nb]) < need; ++it) {
+            if ((it & 0x3f) == 0x3f) {
+              if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) { ok = false; break; }
+              if (globaltimer_ns() - t0 > ga.wait_ns) { report(p.status, KS_TIMEOUT_PEER); ok = false; break; }
+            }
+          }
+          if (!ok) break;
+          fence_proxy_async_global();      // the pieces were written by ordinary stores; TMA reads them
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, p.status, KS_TIMEOUT_EMPTY)) { ok = false; break; }
           uint8_t* sa = smem + stage * STAGE_BYTES;
@@ -244,14 +303,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ------------------------------------------------------------ epilogue (both CTAs)
     const int q = warp & 3;
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = pair_id; t < num_tiles; t += num_pairs) {
       int mb, nb;
-      tile_coords(t, num_m, num_n, mb, nb);
+      tile_coords<GATHER>(t, num_m, num_n, mb, nb);
       if (!mbar_wait(&tfull[acc], acc_phase, p.status, KS_TIMEOUT_TMEM_FULL)) break;
       tc_fence_after();
       const int row = mb * (2 * BM) + static_cast<int>(rank) * BM + q * 32 + lane;
@@ -307,6 +366,31 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
   }
 
+  else if (GATHER) {
+    // ------------------------------------------------------------ gather warps (both CTAs)
+    // Piece i of the flat weight goes to CTA i mod gridDim.x; a CTA's pieces come in increasing
+    // order, so the tiles fill in the order the GEMM consumes them.
+    const int gt = threadIdx.x - THREADS;
+    const long long n_pieces = (ga.total_bytes + PIECE_BYTES - 1) / PIECE_BYTES;
+    const long long tile_bytes = static_cast<long long>(BN) * p.K * 2;
+    for (long long piece = blockIdx.x; piece < n_pieces; piece += gridDim.x) {
+      const long long base = piece * PIECE_BYTES;
+      const long long end = min(ga.total_bytes, base + PIECE_BYTES);
+#pragma unroll 4
+      for (long long off = base + gt * 16; off < end; off += GATHER_THREADS * 16) {
+        const int k = static_cast<int>(off / ga.shard_bytes);
+        const uint4 v = *reinterpret_cast<const uint4*>(ga.shard[k] + (off - k * ga.shard_bytes));
+        *reinterpret_cast<uint4*>(ga.full + off) = v;
+      }
+      __threadfence();
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (gt == 0) {
+        fence_proxy_async_global();
+        red_release_gpu_add(&ga.counters[base / tile_bytes], 1u);
+      }
+    }
+  }
+
   // Neither CTA may leave while the other can still read its shared memory (the pair's
   // MMA reads both) or signal its barriers.
   tc_fence_before();
@@ -322,12 +406,24 @@ template <bool A_MN, bool B_MN>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int num_sms,
                   cudaStream_t stream) {
   static SmemOptIn opt_in;
-  auto kern = gemm2_bf16_kernel<A_MN, B_MN>;
+  auto kern = gemm2_bf16_kernel<A_MN, B_MN, false>;
   if (int e = opt_in.ensure(kern, SMEM)) return e;
   const long long tiles = static_cast<long long>((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN);
   long long pairs = num_sms / 2;
   if (tiles < pairs) pairs = tiles;
-  kern<<<static_cast<int>(2 * pairs), THREADS, SMEM, stream>>>(ta, tb, p);
+  kern<<<static_cast<int>(2 * pairs), THREADS, SMEM, stream>>>(ta, tb, p, GatherArgs{});
+  return static_cast<int>(cudaGetLastError());
+}
+
+static int launch_gather(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, const GatherArgs& ga,
+                         int num_sms, cudaStream_t stream) {
+  static SmemOptIn opt_in;
+  auto kern = gemm2_bf16_kernel<false, false, true>;
+  if (int e = opt_in.ensure(kern, SMEM)) return e;
+  const long long tiles = static_cast<long long>((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN);
+  long long pairs = num_sms / 2;
+  if (tiles < pairs) pairs = tiles;
+  kern<<<static_cast<int>(2 * pairs), THREADS + GATHER_THREADS, SMEM, stream>>>(ta, tb, p, ga);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -366,6 +462,47 @@ int ss_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
   if (!a_mn && b_mn) return launch<false, true>(ta, tb, p, num_sms, s);
   if (a_mn && b_mn) return launch<true, true>(ta, tb, p, num_sms, s);
   return launch<true, false>(ta, tb, p, num_sms, s);
+}
+
+// C[M, N] (+)= alpha * A[M, K] @ W[N, K]^T where W is gathered into `full` by the same kernel.
+// shard_ptrs[k]: rank k's shard (`per` elements, a multiple of 8; flat elements [k*per, (k+1)*per)
+// of W, this rank's own included); counters: `ceil(N / 256)` zeroed words; wait_ns: budget of the
+// wait for a tile (0 = 2 s). K must be a multiple of 64, M >= 256, ldb == K (W is contiguous).
+int ss_gemm2_gather_bf16(const void* A, void* full, void* C, int M, int N, int K, long long lda,
+                         long long ldc, int c_f32, int accumulate, float alpha,
+                         void* const* shard_ptrs, long long per, int world, int rank,
+                         unsigned int* counters, unsigned long long wait_ns, int num_sms, int* status,
+                         void* stream) {
+  using namespace ss;
+  using namespace ss::pair;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || (per % 8) || per <= 0) return -2;
+  if ((K % 64) || M < 2 * BM || (lda % 8) || (ldc % (c_f32 ? 4 : 8)) || (N % 8) ||
+      (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(full) & 15) ||
+      (reinterpret_cast<uintptr_t>(C) & 15) || counters == nullptr ||
+      per * world < static_cast<long long>(N) * K)
+    return -2;
+  if (num_sms <= 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  CUtensorMap ta, tb;
+  int r;
+  if ((r = make_tmap_bf16(&ta, A, M, K, lda, BM))) return r;
+  if ((r = make_tmap3_bf16(&tb, full, 1, N, K, K, static_cast<long long>(N) * K, BN / 2))) return r;
+  Params p{C, M, N, K, ldc, c_f32, accumulate, alpha, status};
+  GatherArgs ga{};
+  for (int k = 0; k < world; ++k) {
+    if (reinterpret_cast<uintptr_t>(shard_ptrs[k]) & 15) return -2;
+    ga.shard[k] = static_cast<const uint8_t*>(shard_ptrs[k]);
+  }
+  ga.full = static_cast<uint8_t*>(full);
+  ga.shard_bytes = per * 2;
+  ga.total_bytes = static_cast<long long>(N) * K * 2;
+  ga.world = world; ga.rank = rank; ga.counters = counters;
+  ga.wait_ns = wait_ns ? wait_ns : 2000000000ull;
+  return launch_gather(ta, tb, p, ga, num_sms, reinterpret_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

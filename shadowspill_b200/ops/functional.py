@@ -103,8 +103,64 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     return out
 
 
+# ------------------------------------------------------------------------ gather fused into the GEMM
+class PendingGather:
+    """A sharded weight whose all-gather has not happened yet: the first GEMM that consumes the
+    full-weight buffer pulls the shards from the peers itself (``ss_gemm2_gather_bf16``)."""
+
+    def __init__(self, full: torch.Tensor, shard_ptrs, per: int, world: int, rank: int, fallback):
+        self.full, self.shard_ptrs, self.per, self.world, self.rank = full, shard_ptrs, per, world, rank
+        self.fallback = fallback          # gathers with the stand-alone kernel instead
+
+
+_pending_gathers: dict[int, PendingGather] = {}
+fused_gather_launches = 0
+
+
+def register_gather(info: PendingGather) -> None:
+    _pending_gathers[info.full.data_ptr()] = info
+
+
+def flush_gathers(ptrs=None) -> int:
+    """Runs the stand-alone gather for every registered weight no GEMM consumed (all of them, or
+    those whose buffers start at ``ptrs``). Returns how many there were."""
+    keys = [k for k in list(_pending_gathers) if ptrs is None or k in ptrs]
+    for k in keys:
+        _pending_gathers.pop(k).fallback()
+    return len(keys)
+
+
+def _gemm_gather(x: torch.Tensor, info: PendingGather, out, accumulate: bool):
+    global fused_gather_launches
+    w = info.full
+    N, K = w.shape
+    M = x.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    counters = torch.zeros(-(-N // 256), dtype=torch.int32, device=x.device)
+    import ctypes
+    ptrs = (ctypes.c_void_p * info.world)(*info.shard_ptrs)
+    rc = _lib.lib().ss_gemm2_gather_bf16(
+        x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, x.stride(0), out.stride(0),
+        int(out.dtype == torch.float32), int(accumulate), 1.0, ptrs, info.per, info.world, info.rank,
+        counters.data_ptr(), 0, 0, _lib.status_word(x.device).data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "ss_gemm2_gather_bf16")
+    fused_gather_launches += 1
+    return out
+
+
 def linear_fwd(x, w, out=None, accumulate=False):
-    """``y[T,N] (+)= x[T,K] @ w[N,K]^T``"""
+    """``y[T,N] (+)= x[T,K] @ w[N,K]^T``. A weight registered by ``register_gather`` is gathered
+    from its shards by this GEMM itself."""
+    if _pending_gathers:
+        info = _pending_gathers.pop(w.data_ptr(), None)
+        if info is not None:
+            fits = (_cuda(x) and x.dtype == _BF16 and w.dim() == 2 and w.is_contiguous() and x.stride(-1) == 1
+                    and x.shape[0] >= 256 and w.shape[1] % 64 == 0 and w.shape[0] % 8 == 0
+                    and (out is None or out.stride(-1) == 1))
+            if fits:
+                return _gemm_gather(x, info, out, accumulate)
+            info.fallback()
     return gemm(x, w, out=out, accumulate=accumulate)
 
 

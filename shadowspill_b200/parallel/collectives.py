@@ -158,6 +158,7 @@ class PeerCollectives:
         self.flag_handle = symm_mem.rendezvous(self.flags, self.group.group_name)
         self.flag_ptrs = (C.c_void_p * self.world)(*[int(p) for p in self.flag_handle.buffer_ptrs])
         self.epoch = 0
+        self.flags2, self.flag2_ptrs, self.epoch2 = None, None, 0
         # how long a flag wait lasts before the kernel gives up with status 5 (0 = 2 s); a job
         # that wants to notice a lost rank quickly sets SS_PEER_WAIT_MS
         import os
@@ -180,6 +181,35 @@ class PeerCollectives:
 
     barrier_begin = _barrier
     barrier_end = _barrier
+
+    def barrier_compute(self) -> None:
+        """A barrier on a second set of flag words, for the compute stream: barriers on two streams
+        must not share an epoch counter, or one stream's later barrier could satisfy the other's
+        earlier one."""
+        if self.flags2 is None:
+            import torch.distributed._symmetric_memory as symm_mem
+            self.flags2 = symm_mem.empty(64, dtype=torch.int32, device=self.pool.device)
+            self.flags2.zero_()
+            handle = symm_mem.rendezvous(self.flags2, self.group.group_name)
+            self.flag2_ptrs = (C.c_void_p * self.world)(*[int(p) for p in handle.buffer_ptrs])
+            self._flag2_handle = handle
+            torch.cuda.synchronize()
+            dist.barrier(self.group)
+        self.epoch2 += 1
+        _lib.check(_lib.lib().ss_peer_barrier_timed(self.flag2_ptrs, self.rank, self.world, self.epoch2,
+                                                    int(self.wait_ns),
+                                                    _lib.status_word(self.pool.device).data_ptr(),
+                                                    _lib.stream_ptr()), "ss_peer_barrier")
+
+    def register_fused_gather(self, shard: torch.Tensor, full: torch.Tensor) -> None:
+        """Leaves the gather of ``full`` (a 2-D weight in the pool) to the first GEMM that reads it:
+        the kernel pulls every rank's ``shard`` over NVLink while it computes."""
+        base = self.replica_base
+        peers = self._peers(shard)
+        ptrs = [int(peers[base + k]) for k in range(self.shard_world)]
+        flat = full.view(-1)
+        F.register_gather(F.PendingGather(full, ptrs, shard.numel(), self.shard_world, self.shard_rank,
+                                          lambda: self.all_gather(shard, flat)))
 
     def all_gather(self, shard: torch.Tensor, full: torch.Tensor) -> None:
         peers = self._peers(shard)

@@ -164,10 +164,10 @@ def measure_program(program: Program, desc: TrainingDescription, device: str = "
         profiles.tasks[key] = TaskProfile(key, med, int(workspace), len(samples),
                                           mad / med if med > 0 else 0.0, contract)
         del flats, B
-        if cuda:
+        if cuda and adapter is not None:
+            adapter.trim()
+        elif cuda:
             torch.cuda.empty_cache()
-            if adapter is not None:
-                adapter.trim()
     return profiles
 
 

@@ -88,6 +88,9 @@ class TrainingSetup:
     # task temporaries then come out of a workspace slice of the device pool under a checked
     # per-task contract. "caching": torch's caching allocator, capped to the planned workspace.
     allocator: str = "caching"
+    # sharded data parallelism on GPUs with the peer collectives: fuse the forward weight gather
+    # into the consuming GEMM
+    fused_gather: bool = False
     pretrained: str = ""                 # directory of Hugging Face safetensors to start from
     # content-addressed store of task profiles shared between runs ("" = none)
     store: str = ""
@@ -185,7 +188,8 @@ class TrainingSession:
                                             expert_parallel=setup.expert_parallel,
                                             min_shard_bytes=setup.min_shard_bytes,
                                             head_block_rows=head_rows,
-                                            master_weights=setup.master_weights, **choices))
+                                            master_weights=setup.master_weights,
+                                            fused_gather=setup.fused_gather and world > 1, **choices))
 
         def build_extra(op: str):
             kw = dict(dtype=self.dtype, world_size=shard_world, rank=rank,
@@ -314,7 +318,11 @@ class TrainingSession:
                                 store.put("task_profile", {**ident, "task": key}, _asdict(prof))
                     apply_profiles(prog, self.profiles, duration_scale=scale)
                 if cuda:
-                    torch.cuda.empty_cache()
+                    if setup.allocator == "planned":
+                        from ..runtime import allocator as _alloc
+                        _alloc.installed().trim()
+                    else:
+                        torch.cuda.empty_cache()
             self.timings["profile"] = time.perf_counter() - t0
             if setup.profile and setup.store:
                 self.log(f"profile store: {store.hits} hits, {store.writes} new entries")
@@ -403,7 +411,10 @@ class TrainingSession:
             self.log(f"weights from {setup.pretrained}")
         self.timings["open"] = time.perf_counter() - t0
         if cuda:
-            torch.cuda.reset_peak_memory_stats(setup.device_index)
+            if setup.allocator == "planned":
+                self.executor.allocator.reset_peak()
+            else:
+                torch.cuda.reset_peak_memory_stats(setup.device_index)
 
     # ------------------------------------------------------------------ operations
     def step(self, batch: list[HostMicrobatch], **kw) -> InvocationResult:

@@ -37,6 +37,9 @@ def main():
     min_shard = 0
     if arm.startswith("small-"):
         min_shard, arm = 64 << 10, arm.split("-", 1)[1]
+    fused = arm.startswith("fused-")      # forward weight gather inside the consuming GEMM
+    if fused:
+        arm = arm.split("-", 1)[1]
     replicas = 1
     if arm.startswith("replicas-"):       # e.g. replicas-dist / replicas-peer on 4 ranks: 2 x 2
         replicas, arm = 2, arm.split("-", 1)[1]
@@ -54,11 +57,15 @@ def main():
         from dataclasses import replace
         cfg = replace(preset("olmoe-tiny"), d_model=256, head_dim=64, vocab_size=1024)
     T, n_mb = 256, 2
+    if fused:
+        # matrices large enough for several 256-row tiles and 64-multiple contraction lengths
+        cfg = DecoderConfig("llama3", 2, 512, 8, 2, 64, 1024, 1024)
+        T = 512
     geo = BatchGeometry(T, n_mb, slots=16, mean_seqlen=64)
     shard_world = world // replicas
     prog, desc = build_step(cfg, geo, StepDataOrdering(), dtype=dtype, world_size=shard_world, rank=rank,
                             expert_parallel=expert_parallel, replicas=replicas,
-                            min_shard_bytes=min_shard, master_weights=master)
+                            min_shard_bytes=min_shard, master_weights=master, fused_gather=fused)
     total = sum(o.bytes for o in prog.objects)
     plan = plan_program(prog, MemoryBudgets(total, 64 << 20, headroom_bytes=0), CommunicationInfo(),
                         SearchOptions(minimum_object_bytes_evict_eligible=1024, workers=1,
@@ -89,6 +96,12 @@ def main():
         tol = 2e-2 if cuda else 1e-5
         if abs(float(loss) - want) > tol * max(1.0, abs(want)):
             print(f"rank {rank} step {step}: loss {float(loss)} != {want}", flush=True)
+            ok = False
+    if fused:
+        from shadowspill_b200.ops import functional as F
+        # 2 layers x 4 matrices x 2 steps, each gathered by the first GEMM that read it
+        if F.fused_gather_launches != 16:
+            print(f"rank {rank}: {F.fused_gather_launches} fused gathers, expected 16", flush=True)
             ok = False
     # owned slices must equal the matching slices of the resident model
     refs = ref.state_dict()

@@ -62,6 +62,14 @@ def test_two_gpus_match_resident(arm):
 
 @pytest.mark.gpu
 @pytest.mark.multigpu
+def test_two_gpus_weight_gather_fused_into_the_gemm():
+    """Sharded storage with the forward all-gather of every layer matrix done by the GEMM that
+    first consumes it (peer loads inside the tcgen05 kernel); matches the resident model."""
+    _launch(2, "cuda", "fused-peer", 29673)
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
 @pytest.mark.parametrize("nvls", ["0", "1"])
 def test_fused_reduce_scatter_adamw_elementwise(nvls):
     """The fused kernel on its own: p, m and v of the owned slice against AdamW on the fp32-summed

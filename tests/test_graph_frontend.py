@@ -187,4 +187,5 @@ def test_graph_frontend_on_the_gpu_matches_the_stage_classes(name):
             continue
         w = states["graph"][k].float()
         rel = float((w - v.float()).norm() / v.float().norm().clamp_min(1e-9))
-        assert rel < 2.5e-2, (k, rel)
+        # norm vectors see the sum of many bf16-rounded terms in a different order
+        assert rel < (5e-2 if v.dim() == 1 else 2.5e-2), (k, rel)
