@@ -132,6 +132,10 @@ def main() -> None:
     ap.add_argument("--allocator", default="caching", choices=["caching", "planned"],
                     help="planned = the allocation adapter: task temporaries from a workspace slice of the "
                          "device pool under a checked contract; caching = torch's allocator under a cap")
+    ap.add_argument("--axis-chunk-rows", type=int, default=0,
+                    help="graph frontend: run the token-local operators of a layer in row chunks of this size")
+    ap.add_argument("--fixed-len", type=int, default=0,
+                    help="sequences of exactly this many tokens (= --microbatch: one long sequence per microbatch)")
     ap.add_argument("--frontend", default="stages", choices=["stages", "graph"],
                     help="graph = torch.export -> partition -> AOT graph pairs; stages = hand-written stage classes")
     args = ap.parse_args()
@@ -182,6 +186,7 @@ def main() -> None:
                                  "train_base": False} if args.lora_rank else None),
                           expert_parallel=args.expert_parallel, spill_pool=args.spill_pool,
                           frontend=args.frontend, allocator=args.allocator, fused_gather=args.fused_gather,
+                          axis_chunk_rows=args.axis_chunk_rows, profile_sequence_tokens=args.fixed_len,
                           spill_directory=args.spill_dir if args.spill_pool == "file" else "",
                           spill_address=args.spill_address)
     log = (lambda m: print(f"[bench] {m}", file=sys.stderr, flush=True)) if rank == 0 else None
@@ -199,7 +204,7 @@ def main() -> None:
     n_batches = args.warmup + args.steps
     batches = [make_batch(1000 * rank + i, vocab=cfg.vocab_size, tokens_per_step=args.tokens,
                           microbatch_tokens=args.microbatch, max_len=8192, median=1200.0,
-                          slots=session.slots) for i in range(n_batches)]
+                          fixed_len=args.fixed_len or None, slots=session.slots) for i in range(n_batches)]
     for b in batches:                 # loss weights are 1/N over the GLOBAL batch
         for mb in b:
             mb.weights /= world
@@ -245,10 +250,11 @@ def main() -> None:
             "higher_is_better": True, "scaling": "weak",
             "vs_baseline": (round(value / BASELINE_TOKENS_PER_S[args.model], 3)
                             if args.model in BASELINE_TOKENS_PER_S else None), "dtype": "bf16",
-            "data": "synthetic packed varlen (log-normal lengths, median 1200, <=8192), "
-                    "random-init weights",
+            "data": ((f"synthetic sequences of exactly {args.fixed_len} tokens, " if args.fixed_len else
+                      "synthetic packed varlen (log-normal lengths, median 1200, <=8192), ")
+                     + "random-init weights"),
             "config": {"model": args.model, "global_batch": args.tokens * world,
-                       "seq_len": 8192, "tokens_per_worker_step": args.tokens,
+                       "seq_len": args.fixed_len or 8192, "tokens_per_worker_step": args.tokens,
                        "microbatch_tokens": args.microbatch,
                        "parallelism": f"dp{world}" if world > 1 else "single",
                        "memory": {"device_gib": args.device_gib, "spill_gib": args.spill_gib,
@@ -263,6 +269,7 @@ def main() -> None:
                                 "spill_gib": round(session.plan.spill_bytes / GIB, 2)},
                        "attention": os.environ.get("SS_ATTENTION", "native"),
                        "frontend": session.desc.frontend, "allocator": args.allocator,
+                       "axis_chunk_rows": args.axis_chunk_rows,
                        "collectives": (session.executor.collectives.name
                                        if session.executor.collectives else "none")},
             "e2e": {"value": round(total_tokens / wall, 1), "unit": "tokens/s",
@@ -277,7 +284,7 @@ def main() -> None:
         # one more (untimed) step with per-task clocks and the runtime trace on
         extra = make_batch(1000 * rank + n_batches, vocab=cfg.vocab_size, tokens_per_step=args.tokens,
                            microbatch_tokens=args.microbatch, max_len=8192, median=1200.0,
-                           slots=session.slots)
+                           fixed_len=args.fixed_len or None, slots=session.slots)
         for mb in extra:
             mb.weights /= world
         _, diag = session.traced_step(extra, args.report if rank == 0 else None)

@@ -349,6 +349,10 @@ int ss_before_task_on(ss_runtime* rt, int32_t plan_id, int32_t task, void** ptrs
 int ss_after_task_on(ss_runtime* rt, int32_t plan_id, int32_t task, void* stream);
 /* Waits until every action of the step has completed; returns the failure latch state. */
 int ss_step_end(ss_runtime* rt, int32_t plan_id);
+/* Ends a step that the caller could not finish (a task raised): latches a caller failure, waits
+ * for the copies in flight, and marks the plan inactive so that it can be closed. The runtime is
+ * terminal afterwards, like after any other latched failure. */
+int ss_step_abandon(ss_runtime* rt, int32_t plan_id, const char* why);
 int ss_runtime_wait_idle(ss_runtime* rt);
 
 /* Direct object I/O on the spill home (initialisation, checkpoints). */

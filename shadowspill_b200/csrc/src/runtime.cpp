@@ -835,6 +835,26 @@ int ss_step_end(ss_runtime* rt, int32_t plan_id) {
   return result;
 }
 
+int ss_step_abandon(ss_runtime* rt, int32_t plan_id, const char* why) {
+  if (!rt) return SS_INVALID_ARGUMENT;
+  PlanState* P;
+  { std::lock_guard<std::mutex> lk(rt->mu); P = find_plan(rt, plan_id); }
+  if (!P) return SS_INVALID_ARGUMENT;
+  if (!P->active) return SS_OK;
+  rt->latch(SS_FAIL_EXTERNAL, SS_FAILED, -1, -1, -1, 0, why ? why : "step abandoned by the caller");
+  rt->cv.notify_all();
+  ss_backend* be = rt->be;
+  be->stream_synchronize(be->self, rt->fetch_stream);
+  be->stream_synchronize(be->self, rt->evict_stream);
+  if (P->compute_stream) be->stream_synchronize(be->self, P->compute_stream);
+  {
+    std::lock_guard<std::mutex> lk(rt->mu);
+    P->active = false;
+  }
+  rt->trace(SS_TRACE_STEP_END, plan_id, 1);
+  return SS_OK;
+}
+
 int32_t ss_plan_transfer_times(ss_runtime* rt, int32_t plan_id, int64_t* begin_ns, int64_t* end_ns,
                                int32_t capacity) {
   if (!rt || !begin_ns || !end_ns) return -1;

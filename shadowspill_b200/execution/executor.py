@@ -844,6 +844,16 @@ class Executor:
             if self.cuda:
                 end_ev.record(self.stream)
             self.rt.step_end(self.plan_id)
+        except BaseException as exc:
+            # a task raised inside the step: the pool's contents are undefined from here on, so the
+            # runtime goes terminal (as after any latched failure) and the plan becomes closable
+            if self.allocator is not None:
+                try:
+                    self.allocator.end_task()
+                except RuntimeError:
+                    pass                       # the scope was closed before the error was raised
+            self.rt.step_abandon(self.plan_id, f"{type(exc).__name__} in a task: {exc}")
+            raise
         finally:
             if self.cuda:
                 ctx.__exit__(None, None, None)

@@ -132,6 +132,9 @@ class TrainingDescription:
     # consumes them in the forward pass (ops/csrc/gemm_tcgen05_2cta.cu, GATHER form). The first
     # forward task of the stage then also holds the shard, whose peers read it during that task.
     fused_gather: bool = False
+    # graph frontend: token-local operators of a layer stage (projections, norms, MLP) run in row
+    # chunks of this many tokens (frontend/chunking.py); 0 = whole microbatch at once
+    axis_chunk_rows: int = 0
 
     def __post_init__(self) -> None:
         extras = extra_fields_for(self.cfg, self.objective)
@@ -153,7 +156,8 @@ class TrainingDescription:
             from .graph_stage import build_graph_stages, supports
             if supports(self.cfg, self.lora, ep, self.objective):
                 stages = build_graph_stages(self.cfg, self.geometry.microbatch_tokens, self.geometry.slots,
-                                            self.dtype, self.grad_dtype, self.head_block_rows)
+                                            self.dtype, self.grad_dtype, self.head_block_rows,
+                                            chunk_rows=self.axis_chunk_rows)
                 for st in stages:
                     st.min_shard_bytes = int(self.min_shard_bytes)
                 return stages
@@ -438,47 +442,51 @@ def build_step(cfg: DecoderConfig, geometry: BatchGeometry,
                grad_dtype=None, selection: dict[int, str] | None = None, world_size: int = 1,
                rank: int = 0, objective=None, lora=None, expert_parallel: bool = False,
                replicas: int = 1, min_shard_bytes: int = 0, head_block_rows: int = 0,
-               master_weights: bool = False, frontend: str = "stages", fused_gather: bool = False):
+               master_weights: bool = False, frontend: str = "stages", fused_gather: bool = False,
+               axis_chunk_rows: int = 0):
     """Forward + backward + optimizer of one global batch. Returns ``(Program, description)``.
     ``world_size > 1`` builds the data-parallel form: weights and AdamW moments are
     stored as 1/N shards, gathered before use and updated shard-locally."""
     desc = TrainingDescription(cfg, geometry, ordering or StepDataOrdering(), dtype,
                                grad_dtype or dtype, dict(selection or {}), "step", world_size,
                                rank, objective, lora, expert_parallel, replicas, min_shard_bytes,
-                               head_block_rows, master_weights, frontend, fused_gather)
+                               head_block_rows, master_weights, frontend, fused_gather, axis_chunk_rows)
     return _build(desc), desc
 
 
 def build_forward_backward(cfg, geometry, ordering=None, *, dtype=torch.bfloat16, grad_dtype=None,
                            selection=None, world_size=1, rank=0, objective=None, lora=None,
-                           min_shard_bytes=0, head_block_rows=0, frontend="stages"):
+                           min_shard_bytes=0, head_block_rows=0, frontend="stages", axis_chunk_rows=0):
     """Gradient accumulation without the update (gradients are persistent state)."""
     desc = TrainingDescription(cfg, geometry, ordering or StepDataOrdering(), dtype,
                                grad_dtype or dtype, dict(selection or {}), "forward_backward",
                                world_size, rank, objective, lora, min_shard_bytes=min_shard_bytes,
-                               head_block_rows=head_block_rows, frontend=frontend)
+                               head_block_rows=head_block_rows, frontend=frontend,
+                               axis_chunk_rows=axis_chunk_rows)
     return _build(desc), desc
 
 
 def build_forward(cfg, geometry, ordering=None, *, dtype=torch.bfloat16, world_size=1, rank=0,
-                  objective=None, lora=None, min_shard_bytes=0, head_block_rows=0, frontend="stages"):
+                  objective=None, lora=None, min_shard_bytes=0, head_block_rows=0, frontend="stages",
+                  axis_chunk_rows=0):
     """Evaluation: forward passes and the loss only."""
     desc = TrainingDescription(cfg, geometry, ordering or StepDataOrdering(), dtype, dtype, {},
                                "forward", world_size, rank, objective, lora,
                                min_shard_bytes=min_shard_bytes, head_block_rows=head_block_rows,
-                               frontend=frontend)
+                               frontend=frontend, axis_chunk_rows=axis_chunk_rows)
     return _build(desc), desc
 
 
 def build_optimizer(cfg, geometry, *, dtype=torch.bfloat16, grad_dtype=None, world_size=1, rank=0,
                     objective=None, lora=None, min_shard_bytes=0, head_block_rows=0, master_weights=False,
-                    frontend="stages"):
+                    frontend="stages", axis_chunk_rows=0):
     """The optimizer update alone, over gradients that earlier ``forward_backward``
     invocations left in the spill pool (the ``optim_step`` operation)."""
     desc = TrainingDescription(cfg, geometry, StepDataOrdering(), dtype, grad_dtype or dtype, {},
                                "optimizer", world_size, rank, objective, lora,
                                min_shard_bytes=min_shard_bytes, head_block_rows=head_block_rows,
-                               master_weights=master_weights, frontend=frontend)
+                               master_weights=master_weights, frontend=frontend,
+                               axis_chunk_rows=axis_chunk_rows)
     return _build(desc), desc
 
 

@@ -376,11 +376,13 @@ def rewrite_destinations(bwd: fx.GraphModule, param_grads: dict[int, str], dest_
             d, f = dest(name)
             with g.inserting_before(prod):
                 new = g.call_function(gemm_into, (d, a, b, a_mn, b_mn, f))
+            new.meta["val"] = d.meta["val"] = prod.meta.get("val")
         elif kind == "ss.embedding_bwd" and len(prod.users) == 1:
             ids, gy, _rows = prod.args
             d, f = dest(name)
             with g.inserting_before(prod):
                 new = g.call_function(embedding_bwd_into, (d, ids, gy, f))
+            new.meta["val"] = d.meta["val"] = prod.meta.get("val")
         elif prod.target is operator.getitem and op_name(prod.args[0]) == "ss.rmsnorm_bwd" \
                 and prod.args[1] == 1 and dest_dtypes.get(name) == torch.float32:
             call = prod.args[0]
@@ -388,6 +390,8 @@ def rewrite_destinations(bwd: fx.GraphModule, param_grads: dict[int, str], dest_
             d, f = dest(name)
             with g.inserting_before(call):
                 dx = g.call_function(rmsnorm_bwd_into, (d, x, w, gy, rstd, zc, f))
+            dx.meta["val"] = x.meta.get("val") if isinstance(x, fx.Node) else None
+            d.meta["val"] = prod.meta.get("val")
             for u in list(call.users):
                 if u.target is operator.getitem and u.args[1] == 0:
                     u.replace_all_uses_with(dx)

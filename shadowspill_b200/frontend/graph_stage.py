@@ -364,11 +364,13 @@ def supports(cfg, lora=None, expert_parallel=None, objective=None) -> bool:
 
 def build_graph_stages(cfg, T: int, slots: int, dtype: torch.dtype = torch.bfloat16,
                        grad_dtype: torch.dtype | None = None, head_block_rows: int = 0,
-                       module: nn.Module | None = None) -> list[Stage]:
-    """The stage list of ``cfg`` (or of ``module``) through the graph frontend."""
+                       module: nn.Module | None = None, chunk_rows: int = 0) -> list[Stage]:
+    """The stage list of ``cfg`` (or of ``module``) through the graph frontend. ``chunk_rows`` > 0
+    runs the token-local regions of every layer stage in row chunks of that many tokens."""
     from .modules import DecoderLM
     block = head_block_rows or 2048
-    key = (cfg.to_json() if module is None else id(module), T, slots, str(dtype), str(grad_dtype), block)
+    key = (cfg.to_json() if module is None else id(module), T, slots, str(dtype), str(grad_dtype), block,
+           chunk_rows)
     with _cache_lock:
         hit = _cache.get(str(key))
     if hit is None:
@@ -376,6 +378,15 @@ def build_graph_stages(cfg, T: int, slots: int, dtype: torch.dtype = torch.bfloa
             with torch.device("meta"):
                 module = DecoderLM(cfg, dtype, block)
         hit = capture_module(module, _example_batch(T, slots), grad_dtype=grad_dtype or dtype, model_dtype=dtype)
+        if 0 < chunk_rows < T:
+            from .chunking import chunk_pairs, peak_intermediate_bytes
+            exported, by_key = hit
+            inner = {st.key for st in exported.stages[1:-1]} if len(exported.stages) > 2 else set()
+            for k in inner:
+                if chunk_pairs(by_key[k], T, chunk_rows):
+                    by_key[k].intermediate_bytes = min(by_key[k].intermediate_bytes, max(
+                        max(peak_intermediate_bytes(p.forward), peak_intermediate_bytes(p.backward))
+                        for p in by_key[k].pairs.values()))
         with _cache_lock:
             _cache[str(key)] = hit
     exported, by_key = hit
@@ -397,4 +408,6 @@ def build_graph_stages(cfg, T: int, slots: int, dtype: torch.dtype = torch.bfloa
             stages.append(GraphHeadStage(st.name, cfg, st, pairs, specs, foreign, block))
         else:
             stages.append(GraphStage(st.name, cfg, st, pairs, specs, foreign))
+            if 0 < chunk_rows < T:
+                stages[-1].mixer += f":rows{chunk_rows}"     # chunked and whole forms profile apart
     return stages

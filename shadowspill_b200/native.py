@@ -209,6 +209,7 @@ def _declare(lib: C.CDLL) -> None:
     lib.ss_before_task_on.argtypes = [vp, i32, i32, C.POINTER(vp), i32, vp]
     lib.ss_after_task_on.argtypes = [vp, i32, i32, vp]
     lib.ss_step_end.argtypes = [vp, i32]
+    lib.ss_step_abandon.argtypes = [vp, i32, C.c_char_p]
     lib.ss_runtime_wait_idle.argtypes = [vp]
     lib.ss_spill_write.argtypes = [vp, i64, vp, i64]
     lib.ss_spill_read.argtypes = [vp, i64, vp, i64]

@@ -84,9 +84,11 @@ def _fill_inputs(runner: TaskRunner, task: int, flats: list[torch.Tensor], host_
 
 def measure_program(program: Program, desc: TrainingDescription, device: str = "cuda",
                     min_samples: int = 3, max_samples: int = 8, tolerance: float = 0.03,
-                    keys: set[str] | None = None, rule: str = "adamw") -> Profiles:
+                    keys: set[str] | None = None, rule: str = "adamw", fixed_len: int = 0) -> Profiles:
     """Times one representative task per ``profile_key`` with the ordinary torch allocator.
-    ``rule``: the run's update rule (the unfused rules allocate temporaries the fused one does not)."""
+    ``rule``: the run's update rule (the unfused rules allocate temporaries the fused one does not).
+    ``fixed_len``: profile on sequences of exactly this length (long-context runs) instead of the
+    packed log-normal mix."""
     dev = torch.device(device)
     cuda = dev.type == "cuda"
     runner = TaskRunner(program, desc, Hyperparameters(lr=0.0, rule=rule), seed=0, stochastic_rounding=True)
@@ -94,7 +96,7 @@ def measure_program(program: Program, desc: TrainingDescription, device: str = "
     cfg = desc.cfg
     host_batch = make_batch(0, vocab=cfg.vocab_size, tokens_per_step=runner.T * runner.n_mb,
                             microbatch_tokens=runner.T, slots=runner.slots,
-                            max_len=min(8192, runner.T),
+                            max_len=min(8192, runner.T), fixed_len=min(fixed_len, runner.T) or None,
                             median=min(1200.0, runner.T / 4), min_len=min(32, runner.T // 4))
     profiles = Profiles(device=torch.cuda.get_device_name(dev) if cuda else "cpu")
     seen: dict[str, int] = {}

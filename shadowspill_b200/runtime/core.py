@@ -160,6 +160,10 @@ class Runtime:
     def step_end(self, plan_id: int) -> None:
         self._raise(self.lib.ss_step_end(self.handle, plan_id), "ss_step_end")
 
+    def step_abandon(self, plan_id: int, why: str) -> None:
+        """Ends a step whose task raised: the failure is latched and the plan can be closed."""
+        self.lib.ss_step_abandon(self.handle, plan_id, why.encode()[:200])
+
     # ------------------------------------------------------------------ diagnostics
     def failure(self) -> dict | None:
         f = native.Failure()

@@ -91,6 +91,12 @@ class TrainingSetup:
     # sharded data parallelism on GPUs with the peer collectives: fuse the forward weight gather
     # into the consuming GEMM
     fused_gather: bool = False
+    # graph frontend: row chunk of the token-local operators inside a layer stage (0 = off); what
+    # lets one long sequence fit: the wide projection outputs then exist one chunk at a time
+    axis_chunk_rows: int = 0
+    # profile the tasks on sequences of exactly this many tokens (0 = the packed log-normal mix):
+    # the cost of the sequence mixers depends on it, so long-context runs set it
+    profile_sequence_tokens: int = 0
     pretrained: str = ""                 # directory of Hugging Face safetensors to start from
     # content-addressed store of task profiles shared between runs ("" = none)
     store: str = ""
@@ -161,7 +167,8 @@ class TrainingSession:
             # these layers run through the autograd-derived stage, which only recomputes
             selections = [{}]
             variants = [(walk, {}) for walk in setup.walks]
-        choices = dict(objective=self.objective, lora=self.lora, frontend=setup.frontend)
+        choices = dict(objective=self.objective, lora=self.lora, frontend=setup.frontend,
+                       axis_chunk_rows=setup.axis_chunk_rows if setup.frontend == "graph" else 0)
         shard_world = setup.ranks_per_replica or world
         if world % shard_world:
             raise ValueError("world_size must be a multiple of ranks_per_replica")
@@ -298,7 +305,8 @@ class TrainingSession:
                     from ..store import ContentStore, kernel_library_digest
                     store = ContentStore(setup.store, setup.store_mode)
                     ident = {"device": torch.cuda.get_device_name(setup.device_index) if cuda else "cpu",
-                             "kernels": kernel_library_digest(), "dtype": setup.dtype}
+                             "kernels": kernel_library_digest(), "dtype": setup.dtype,
+                             "sequence_tokens": setup.profile_sequence_tokens}
                 for prog, desc in candidates + list(extras.values()):
                     missing = {t.profile_key for t in prog.tasks} - set(self.profiles.tasks)
                     if store is not None:
@@ -309,7 +317,8 @@ class TrainingSession:
                                 self.profiles.tasks[key] = TaskProfile(**hit)
                         missing -= set(self.profiles.tasks)
                     if missing:
-                        got = measure_program(prog, desc, dev, keys=missing, rule=setup.optimizer_rule)
+                        got = measure_program(prog, desc, dev, keys=missing, rule=setup.optimizer_rule,
+                                              fixed_len=setup.profile_sequence_tokens)
                         self.profiles.tasks.update(got.tasks)
                         self.profiles.device = got.device
                         if store is not None:

@@ -212,3 +212,29 @@ def test_fp32_master_copies_keep_progress_that_bf16_rounding_loses():
             assert float((m - after[w].float()).abs().max()) > 0      # the master holds what bf16 cannot
         ex.close()
     assert moved[False] < 0.25 and moved[True] > 0.3 and moved[True] > 2 * moved[False], moved
+
+
+def test_a_task_that_raises_leaves_a_terminal_runtime_that_still_closes():
+    """An exception inside a task ends the step on the native side too: the failure is latched
+    with the exception's text, later steps are refused, and close() releases the plan."""
+    from shadowspill_b200.runtime.core import RuntimeFailure
+    cfg, plan, desc = _setup("breadth")
+    ex = Executor(plan, desc, device="cpu", seed=5, hyper=Hyperparameters(lr=1e-3))
+    ex.initialize()
+    ex.run(_batches(cfg, 0))
+    real, calls = ex.runner.run_task, [0]
+
+    def failing(task, bound):
+        calls[0] += 1
+        if calls[0] == 7:
+            raise ValueError("synthetic task failure")
+        return real(task, bound)
+    ex.runner.run_task = failing
+    with pytest.raises(ValueError, match="synthetic task failure"):
+        ex.run(_batches(cfg, 1))
+    failure = ex.rt.failure()
+    assert failure is not None and "synthetic task failure" in failure["message"]
+    ex.runner.run_task = real
+    with pytest.raises(RuntimeFailure):
+        ex.run(_batches(cfg, 2))
+    ex.close()                                      # no "plan is active" error

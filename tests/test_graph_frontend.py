@@ -109,6 +109,74 @@ def test_planned_graph_frontend_matches_the_resident_trainer(name):
     ex.close()
 
 
+@pytest.mark.parametrize("name", ["llama3-tiny", "qwen3-tiny", "qwen35-tiny"])
+def test_axis_chunked_stage_graphs_compute_the_same_step(name):
+    """Row-chunking the token-local regions of every layer graph (projections, norms, MLP; the
+    sequence mixers stay whole) changes the graphs and their live intermediates, not the numbers:
+    three planned updates agree with the unchunked graphs, and the gradients' in-place forms
+    accumulate across chunks (created by the first chunk of the first microbatch only)."""
+    from shadowspill_b200.frontend import chunking
+    cfg = preset(name)
+    sel = {1: "save", 2: "save_attention"}
+    whole, desc_w = build_step(cfg, GEO, StepDataOrdering(), dtype=torch.float32, selection=sel, frontend="graph")
+    prog, desc = build_step(cfg, GEO, StepDataOrdering(), dtype=torch.float32, selection=sel, frontend="graph",
+                            axis_chunk_rows=96)                       # 256 rows: chunks of 96, 96, 64
+    sw, sc = desc_w.stages(), desc.stages()
+    regions = 0
+    for a, b in zip(sw[1:-1], sc[1:-1]):
+        for v in a.pairs.pairs:
+            fa, fb = a.pairs.pairs[v].forward, b.pairs.pairs[v].forward
+            cats = [n for n in fb.graph.nodes if op_name(n) == "aten.cat.default"]
+            assert len(fb.graph.nodes) > len(fa.graph.nodes) and cats
+            regions += len(cats)
+            # barriers are never replicated
+            for kind in ("ss.attention", "ss.gated_delta_rule", "ss.conv_silu"):
+                assert (sum(op_name(n) == kind for n in fb.graph.nodes)
+                        == sum(op_name(n) == kind for n in fa.graph.nodes))
+            # the widest projection is evaluated once per chunk
+            assert (sum(op_name(n) == "ss.linear" for n in fb.graph.nodes)
+                    == 3 * sum(op_name(n) == "ss.linear" for n in fa.graph.nodes))
+        assert ":rows96" in b.mixer and ":rows" not in a.mixer
+    assert regions > 0
+    assert {t.profile_key for t in prog.tasks} != {t.profile_key for t in whole.tasks}
+
+    def run(program, description):
+        ex = Executor(_plan(program), description, device="cpu", seed=5, hyper=Hyperparameters(lr=3e-3))
+        ex.initialize()
+        losses = [ex.run(_batches(cfg, step)).loss for step in range(3)]
+        state = ex.state_dict()
+        ex.close()
+        return losses, state
+    lw, stw = run(whole, desc_w)
+    lc, stc = run(prog, desc)
+    for a, b in zip(lw, lc):
+        assert abs(a - b) < 1e-5 * max(1.0, abs(a)), (lw, lc)
+    for k, v in stw.items():
+        if k.startswith("exp_avg"):
+            continue
+        diff = (stc[k] - v).float()
+        assert float(diff.norm() / v.float().norm().clamp_min(1e-9)) < 1e-3, k
+    mixers = [n for st in sw[1:-1] for n in st.pairs.pairs["recompute"].forward.graph.nodes
+              if op_name(n) in ("ss.attention", "ss.gated_delta_rule", "ss.conv_silu")]
+    assert mixers and all(chunking.classify(n, 256)[0] == chunking.BARRIER for n in mixers)
+
+
+def test_axis_chunks_shrink_the_live_intermediates_of_a_wide_layer():
+    """With an MLP eight times wider than the model, the live intermediates of the chunked
+    backward graph (counted from the traced shapes) are a fraction of the whole graph's."""
+    from shadowspill_b200.frontend import chunking
+    from shadowspill_b200.frontend.graph_stage import build_graph_stages
+    from shadowspill_b200.models.config import DecoderConfig
+    cfg = DecoderConfig("llama3", 2, 256, 4, 2, 64, 2048, 512)
+    whole = build_graph_stages(cfg, 2048, 16, torch.bfloat16)
+    cut = build_graph_stages(cfg, 2048, 16, torch.bfloat16, chunk_rows=256)
+    for variant in ("recompute", "save_attention"):
+        a = chunking.peak_intermediate_bytes(whole[1].pairs.pairs[variant].backward)
+        b = chunking.peak_intermediate_bytes(cut[1].pairs.pairs[variant].backward)
+        assert b < 0.6 * a, (variant, a, b)
+    assert cut[1].workspace_bytes(2048) <= whole[1].workspace_bytes(2048)
+
+
 def test_plumbing_config_twenty_steps_match_eager_pytorch():
     """BASELINE configuration 0: the tiny Llama through export, partition, profile-free planning with
     half of the state spilled, execution and the plan report, against plain eager PyTorch + AdamW."""
