@@ -33,6 +33,7 @@ import urllib.parse
 from dataclasses import asdict
 from http.server import BaseHTTPRequestHandler
 
+from . import reference_protocol as refproto
 from ..orchestration.nodes import AdmissionError
 from ..training.controller import Rejected
 
@@ -66,6 +67,16 @@ def make_handler(server):
                 raise HTTPError(400, "body is not JSON") from None
 
         def _send(self, status: int, payload, content_type: str = "application/json", headers=None):
+            if content_type == "application/json" and refproto.wants_control(self.headers):
+                # the reference client accepts only its own envelope: errors become service.error
+                # records, routes without a translated record say so by name
+                content_type = refproto.CONTROL_MEDIA_TYPE
+                if status >= 400:
+                    payload = refproto.service_error(status, (payload or {}).get("error", ""))
+                elif not isinstance(payload, bytes):
+                    status = 501
+                    payload = refproto.service_error(501, f"{self.command} {self.path.split('?')[0]}: this server "
+                                                          "has no reference-protocol record for this route")
             data = payload if isinstance(payload, bytes) else json.dumps(payload).encode()
             self.send_response(status)
             self.send_header("Content-Type", content_type)
@@ -115,6 +126,13 @@ def make_handler(server):
         # ------------------------------------------------------------------ routes
         def _dispatch(self, method: str, p: list[str], q: dict) -> None:
             head = p[0]
+            control = refproto.wants_control(self.headers)
+            if control and head == "info" and method == "GET":
+                return self._send(200, refproto.service_info(server.incarnation, "local"),
+                                  refproto.CONTROL_MEDIA_TYPE)
+            if control and head == "hardware" and method == "GET":
+                return self._send(200, refproto.hardware_inventory(server.hardware, server.admission.snapshot()),
+                                  refproto.CONTROL_MEDIA_TYPE)
             if head == "info" and method == "GET":
                 return self._send(200, {"service": "shadowspill-b200", "incarnation": server.incarnation,
                                         "owner": "local", "api": 1})

@@ -359,3 +359,71 @@ def test_checkpoint_and_artifact_names_stay_inside_the_service_root(tmp_path):
     assert srv.resolve_checkpoint("other", "ck") == str(other.resolve())
     with pytest.raises(ValueError):
         srv.unpack_artifact("../checkpoints")
+
+
+def test_reference_control_protocol_envelopes(tmp_path):
+    """A request that asks for the reference client's control media type gets that protocol's
+    envelope: ``service.info`` and ``service.hardware`` records on the connection routes, a
+    ``service.error`` record (never a bare JSON body) on failures and on untranslated routes."""
+    import json
+    import urllib.error
+    import urllib.request
+    from shadowspill_b200.server.reference_protocol import CONTROL_MEDIA_TYPE
+    token = "t" * 40
+    with Server(tmp_path / "root", token=token) as srv:
+        def ask(path, tok=token, method="GET", body=None):
+            req = urllib.request.Request(srv.url + path, method=method, data=body,
+                                         headers={"Accept": CONTROL_MEDIA_TYPE, "Authorization": f"Bearer {tok}",
+                                                  "Content-Type": CONTROL_MEDIA_TYPE})
+            try:
+                with urllib.request.urlopen(req) as r:
+                    return r.status, r.headers["Content-Type"], json.loads(r.read())
+            except urllib.error.HTTPError as e:
+                return e.code, e.headers["Content-Type"], json.loads(e.read())
+        status, ctype, env = ask("/v1/info")
+        assert status == 200 and ctype == CONTROL_MEDIA_TYPE
+        assert set(env) == {"version", "kind", "value"} and env["version"] == 1 and env["kind"] == "service.info"
+        assert set(env["value"]) == {"server_incarnation", "owner_id"}
+        status, ctype, env = ask("/v1/hardware")
+        assert status == 200 and env["kind"] == "service.hardware"
+        node = env["value"]["nodes"][0]
+        assert node["host_available_bytes"] <= node["host_capacity_bytes"] and node["cpu_count"] >= 1
+        assert [d["index"] for d in node["devices"]] == list(range(len(node["devices"])))
+        status, ctype, env = ask("/v1/info", tok="w" * 40)
+        assert status == 401 and ctype == CONTROL_MEDIA_TYPE
+        assert env["kind"] == "service.error" and env["value"]["code"] == "unauthenticated"
+        status, ctype, env = ask("/v1/training/describe", method="POST", body=b"{}")
+        assert status >= 400 and ctype == CONTROL_MEDIA_TYPE and env["kind"] == "service.error"
+        status, ctype, env = ask("/v1/components")
+        assert status == 501 and env["value"]["code"] == "unsupported" and "/v1/components" in env["value"]["message"]
+
+
+def test_the_unmodified_reference_client_connects(tmp_path):
+    """The reference's own client package (an unmodified copy, when one is present beside the
+    baseline) opens a connection to this server, authenticates, reads the service identity and
+    lists hardware; a training request is answered with a service error it can decode."""
+    import sys
+    from pathlib import Path
+    ref = Path(__file__).resolve().parents[1] / "baseline" / "_ref"
+    if not (ref / "shadowspill_client" / "__init__.py").exists():
+        pytest.skip("no copy of the reference client in this checkout")
+    sys.path.insert(0, str(ref))
+    try:
+        import shadowspill_client as rc
+        from shadowspill_client.protocol.hardware import HardwareInventory
+        token = "k" * 48
+        with Server(tmp_path / "root", token=token) as srv:
+            client = rc.ServiceClient(srv.url, token=token, timeout=30)
+            try:
+                assert client.info.owner_id == "local" and client.info.server_incarnation
+                inventory = client.list_hardware().result(timeout=30)
+                assert isinstance(inventory, HardwareInventory) and len(inventory.nodes) == 1
+                with pytest.raises(Exception) as e:
+                    client._request("GET", "/v1/components", HardwareInventory)
+                assert "unsupported" in str(e.value) or getattr(e.value, "status", 0) == 501
+            finally:
+                client.close()
+    finally:
+        sys.path.remove(str(ref))
+        for name in [m for m in sys.modules if m == "shadowspill_client" or m.startswith("shadowspill_client.")]:
+            del sys.modules[name]
