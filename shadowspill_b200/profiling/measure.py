@@ -34,6 +34,8 @@ class TaskProfile:
     samples: int
     spread: float            # MAD / median
     allocations: list = field(default_factory=list)   # request sizes under the allocation adapter
+    # the same task when it adds to an existing gradient instead of creating it (later microbatches)
+    allocations_accumulate: list = field(default_factory=list)
 
 
 @dataclass
@@ -114,6 +116,7 @@ def measure_program(program: Program, desc: TrainingDescription, device: str = "
         from ..runtime import allocator as _alloc
         adapter = _alloc.installed() if cuda else None
         contract: list[int] = []
+        contract_acc: list[int] = []
         if adapter is not None:
             # the allocation contract: three warmed runs must ask for the same tensors in the same
             # order (packages/engine/src/shadowspill/profiling/measure.py:31 does the same)
@@ -131,6 +134,22 @@ def measure_program(program: Program, desc: TrainingDescription, device: str = "
                                    f"{[len(r) for r in runs]} requests; it has no stable allocation contract")
             contract = runs[0]
             workspace = adapter.stats()["task_peak"]
+            own = B.get("grads.mode") or B.get("tied_grads.mode")
+            if own in ("create", "mutate"):
+                # the same task runs with the gradient created (first microbatch) and added to
+                # (later ones); the two forms may allocate differently, so each has its contract
+                other = "mutate" if own == "create" else "create"
+                alt = dict(B)
+                for role in ("grads", "tied_grads"):
+                    if f"{role}.mode" in alt:
+                        alt[f"{role}.mode"] = other
+                runner.grad_seen = set(range(len(runner.stages))) if other == "mutate" else set()
+                with adapter.task(program.tasks[ti].name, _alloc.RECORD) as seq:
+                    runner.run_task(ti, alt)
+                flipped = list(seq)
+                workspace = max(workspace, adapter.stats()["task_peak"])
+                torch.cuda.synchronize(dev)
+                contract, contract_acc = (contract, flipped) if own == "create" else (flipped, contract)
         elif cuda:
             torch.cuda.synchronize(dev)
             torch.cuda.reset_peak_memory_stats(dev)
@@ -164,7 +183,7 @@ def measure_program(program: Program, desc: TrainingDescription, device: str = "
         med = statistics.median(samples)
         mad = statistics.median(abs(s - med) for s in samples)
         profiles.tasks[key] = TaskProfile(key, med, int(workspace), len(samples),
-                                          mad / med if med > 0 else 0.0, contract)
+                                          mad / med if med > 0 else 0.0, contract, contract_acc)
         del flats, B
         if cuda and adapter is not None:
             adapter.trim()
@@ -193,7 +212,9 @@ def apply_profiles(program: Program, profiles: Profiles, workspace_margin: float
             # depend on every rank's routing
             margin = max(margin, 1.75)
         t.workspace_bytes = int(p.workspace_bytes * margin)
-        t.allocations = list(p.allocations)
+        accumulates = any(u.role in ("grads", "tied_grads") and u.mode == "mutate" for u in t.uses)
+        t.allocations = list(p.allocations_accumulate if (accumulates and p.allocations_accumulate)
+                             else p.allocations)
     if missing:
         raise KeyError(f"no profile for {sorted(set(missing))[:4]}")
     program.metadata["profiled_on"] = profiles.device

@@ -116,6 +116,82 @@ def numerical_gate(model: str = "llama3-tiny", device: str = "cpu", updates: int
             "losses": losses, "passed": not failures, "failures": failures}
 
 
+def torch_twin_gate(cfg, device: str = "cuda", updates: int = 5, microbatches: int = 2, tokens: int = 1024,
+                    lr: float = 1e-3, frontend: str = "stages") -> dict:
+    """Planned execution in the model dtype (bf16 on a GPU) against an independent fp32 PyTorch
+    model (``models/torch_reference.py``: plain tensor code, no kernel of this package) trained by
+    ``torch.optim.AdamW`` on the same data from the same starting weights: ``updates`` updates of
+    ``microbatches`` heterogeneous microbatches, forced to spill. Tolerances as in the reference's
+    numerical gate (qualification/numerical/README.md:199-213): weights rel-L2 <= 2.5 %, cosine >=
+    0.999, sign agreement >= 99 %, near-zero weights within 2*lr per update."""
+    from ..communication.info import CommunicationInfo
+    from ..execution.executor import Executor, Hyperparameters
+    from ..frontend.capture import BatchGeometry, StepDataOrdering, build_step
+    from ..models import torch_reference as twin
+    from ..planning.plan import MemoryBudgets, PlanningError, plan_program
+    cpu = device == "cpu"
+    dtype = torch.float32 if cpu else torch.bfloat16
+    slots = tokens // 32 + 1
+    geo = BatchGeometry(microbatch_tokens=tokens, n_microbatches=microbatches, slots=slots, mean_seqlen=tokens / 4)
+    from ..frontend.graph_stage import supports
+    graph = frontend == "graph" and supports(cfg)
+    sel = {i: ("save" if i % 2 else "save_attention") for i in range(1, cfg.n_layers + 1)} if graph else {}
+    prog, desc = build_step(cfg, geo, StepDataOrdering(), dtype=dtype, selection=sel,
+                            frontend="graph" if graph else "stages")
+    total = sum(o.bytes for o in prog.objects)
+    ws = max(t.workspace_bytes for t in prog.tasks)
+    plan = None
+    for pct in range(50, 101, 10):
+        try:
+            plan = plan_program(prog, MemoryBudgets(4 * ws + total * pct // 100, 4 << 30, headroom_bytes=0),
+                                CommunicationInfo(), SearchOptions(minimum_object_bytes_evict_eligible=1024, workers=2))
+            break
+        except PlanningError:
+            continue
+    if plan is None:
+        raise PlanningError("no budget planned")
+    hyper = Hyperparameters(lr=lr, beta2=0.95, weight_decay=0.0)
+    ex = Executor(plan, desc, device=device, seed=11, hyper=hyper, stochastic_rounding=False)
+    ex.initialize(on_device=False)
+    dev = torch.device(device)
+    params = {k: v.to(dev, torch.float32).clone().requires_grad_(True)
+              for k, v in ex.state_dict().items() if not k.startswith("exp_avg")}
+    opt = torch.optim.AdamW(list(params.values()), lr=lr, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0)
+    losses, failures = [], []
+    for step in range(updates):
+        host = make_batch(100 + step, vocab=cfg.vocab_size, tokens_per_step=tokens * microbatches,
+                          microbatch_tokens=tokens, median=tokens / 5, min_len=16, max_len=tokens, slots=slots)
+        got = ex.run(host).loss
+        opt.zero_grad()
+        want = 0.0
+        for m in host:
+            loss = twin.model_loss(cfg, params, to_device(m, dev))
+            loss.backward()
+            want += float(loss)
+        opt.step()
+        losses.append((got, want))
+        if abs(got - want) > (1e-5 if cpu else 2e-2) * max(1.0, abs(want)):
+            failures.append(f"loss at update {step + 1}: {got} vs {want}")
+    state = ex.state_dict()
+    worst = {"rel_l2": 0.0, "cosine": 1.0, "sign_agreement": 1.0, "near_zero_abs": 0.0}
+    at = {}
+    for k, v in params.items():
+        m = compare_tensors(state[k], v, lr)
+        for name, better in (("rel_l2", max), ("cosine", min), ("sign_agreement", min), ("near_zero_abs", max)):
+            new = better(worst[name], m[name])
+            if new != worst[name]:
+                worst[name], at[name] = new, k
+    if worst["rel_l2"] > 0.025 or worst["cosine"] < 0.999 or worst["sign_agreement"] < 0.99:
+        failures.append(f"weights outside tolerance: {worst} at {at}")
+    if worst["near_zero_abs"] > 2 * lr * updates + 1e-7:
+        failures.append(f"near-zero weights differ by {worst['near_zero_abs']} at {at.get('near_zero_abs')}")
+    fetched = plan.summary.fetch_bytes
+    ex.close()
+    return {"gate": "torch_twin", "family": cfg.family, "device": device, "updates": updates,
+            "frontend": "graph" if graph else "stages", "fetch_bytes": fetched, "weights": worst,
+            "worst_at": at, "losses": losses, "passed": not failures, "failures": failures}
+
+
 def performance_gate(model: str = "llama3-8b", device_gib: float = 24.0, spill_gib: float = 128.0,
                      tokens: int = 65536, microbatch: int = 8192, groups: int = 3, updates: int = 4,
                      floor: float | None = None) -> dict:
