@@ -168,6 +168,8 @@ class BuildOptions:
     saved_variant: str = "save_attention"
     projection_chunks: tuple = ()
     moe_chunks: tuple = ()
+    # "stages": the hand-written stage classes; "graph": torch.export -> partition -> AOT graph pairs
+    frontend: str = "stages"
 
 
 @record

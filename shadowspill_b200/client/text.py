@@ -89,14 +89,15 @@ def text_batch(sequences, loss_masks=None) -> list[Datum]:
 
 
 def build_candidates(projection_chunks=(), moe_chunks=(), retention=("cost-input",),
-                     recompute_shares=(100, 50, 0)) -> dict:
+                     recompute_shares=(100, 50, 0), row_chunks=()) -> dict:
     """Preparation candidates as a cross product (policy ids follow the reference's
     ``shadowspill/text_chunks@1`` / ``shadowspill/text_retention@1``)."""
     cases = []
     for pc in (projection_chunks or (0,)):
         for mc in (moe_chunks or (0,)):
-            for r in retention:
-                cases.append({"policies": [
-                    {"id": "shadowspill/text_chunks@1", "config": {"projection": pc, "moe": mc}},
-                    {"id": "shadowspill/text_retention@1", "config": {"rule": r}}]})
+            for rows in (row_chunks or (0,)):
+                for r in retention:
+                    cases.append({"policies": [
+                        {"id": "shadowspill/text_chunks@1", "config": {"projection": pc, "moe": mc, "rows": rows}},
+                        {"id": "shadowspill/text_retention@1", "config": {"rule": r}}]})
     return {"cases": cases, "recompute_shares": list(recompute_shares)}

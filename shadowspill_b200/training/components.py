@@ -101,7 +101,8 @@ def default_registry() -> Registry:
     r.add_optimizer("sgd@1", lambda **kw: {"kind": "sgd", **kw})              # momentum = beta1
     r.add_optimizer("lion@1", lambda **kw: {"kind": "lion", **kw})
     r.add_preparation("shadowspill/default@1", lambda **kw: kw)
-    r.add_policy("shadowspill/text_chunks@1", lambda projection=0, moe=0: {"projection": projection, "moe": moe})
+    r.add_policy("shadowspill/text_chunks@1",
+                 lambda projection=0, moe=0, rows=0: {"projection": projection, "moe": moe, "rows": rows})
     r.add_policy("shadowspill/text_retention@1", lambda rule="cost-input": {"rule": rule})
     return r
 
@@ -215,13 +216,22 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
     prep = body.get("preparation", {})
     build, planning = prep.get("build", {}), prep.get("planning", {})
     saved_variant = build.get("saved_variant", "save_attention")
-    head_chunks = moe_chunks = 0
+    head_chunks = moe_chunks = axis_rows = 0
+    frontend = str(build.get("frontend", "stages"))
+    if frontend not in ("stages", "graph"):
+        raise ValueError(f"unknown build frontend {frontend!r} (stages | graph)")
     for pol in prep.get("policies", []):
         if pol.get("id") == "shadowspill/text_chunks@1":
             # "projection": row chunks of the output projection; "moe": expert groups a routed layer
-            # is pipelined in under expert parallelism
+            # is pipelined in under expert parallelism; "rows": token rows per chunk of the
+            # token-local operators inside a layer stage (graph frontend; sequence mixers stay whole)
             head_chunks = int((pol.get("config") or {}).get("projection", 0) or 0)
             moe_chunks = int((pol.get("config") or {}).get("moe", 0) or 0)
+            axis_rows = int((pol.get("config") or {}).get("rows", 0) or 0)
+            if axis_rows < 0:
+                raise ValueError("text_chunks rows must not be negative")
+            if axis_rows:
+                frontend = "graph"            # axis chunks are a transform of the exported graphs
         if pol.get("id") == "shadowspill/text_retention@1":
             saved_variant = _RETENTION_VARIANT.get((pol.get("config") or {}).get("rule", ""), saved_variant)
     ex = body.get("execution", {})
@@ -248,6 +258,7 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
             "ranks_per_replica": per_replica if replicas > 1 else 0,
             "min_shard_bytes": int(par.get("min_shard_bytes", 0)) if workers > 1 else 0,
             "head_chunks": head_chunks, "moe_chunks": moe_chunks, "master_weights": master_weights,
+            "frontend": frontend, "axis_chunk_rows": axis_rows,
             "walks": list(build.get("walks", ("breadth",))),
             "recompute_shares": list(build.get("recompute_shares", (100,))),
             "saved_variant": saved_variant,

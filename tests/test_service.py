@@ -427,3 +427,28 @@ def test_the_unmodified_reference_client_connects(tmp_path):
         sys.path.remove(str(ref))
         for name in [m for m in sys.modules if m == "shadowspill_client" or m.startswith("shadowspill_client.")]:
             del sys.modules[name]
+
+
+def test_axis_chunks_and_the_graph_frontend_through_the_service(service):
+    """``text_chunks@1`` with ``rows`` selects the graph frontend and cuts the layer graphs into row
+    chunks; the run trains, and its loss equals the unchunked stage-class run on the same data."""
+    from shadowspill_b200.client import BuildOptions
+
+    def run(preparation):
+        with ServiceClient(service.url, token="secret") as svc:
+            tr = svc.create_training_client(
+                Model("llama3-tiny", dtype="float32"), Optimizer(lr=3e-3, parameter_rounding="nearest"),
+                batch=BatchConfig(tokens_per_step=512, microbatch_tokens=256),
+                memory=Memory(device_gib=0.53, spill_gib=0.25), resources=Resources(gpus=1, backend="cpu"),
+                preparation=preparation, timeout=300).result()
+            try:
+                return [tr.step(text_batch(_sequences(s))).result().loss for s in range(2)]
+            finally:
+                tr.close()
+    common = dict(profiling=ProfilingOptions(enabled=False), calibrate=False,
+                  planning=PlanningOptions(minimum_object_bytes_evict_eligible=1024, workers=1))
+    whole = run(Preparation(**common))
+    cut = run(Preparation(policies=({"id": "shadowspill/text_chunks@1", "config": {"rows": 96}},), **common))
+    graph = run(Preparation(build=BuildOptions(frontend="graph"), **common))
+    for a, b, c in zip(whole, cut, graph):
+        assert abs(a - b) < 1e-4 * max(1.0, abs(a)) and abs(a - c) < 1e-4 * max(1.0, abs(a)), (whole, cut, graph)
