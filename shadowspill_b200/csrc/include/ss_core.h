@@ -149,6 +149,8 @@ typedef struct ss_search_options {
   int64_t capacity_refinement_step;   /* bytes given back when the layout overruns */
   int32_t deterministic;
   int32_t trace;                 /* record per-candidate trace lines */
+  int32_t linear_reduce;         /* 1 = the plain O(cuts x gaps) reducer (the indexed one's reference) */
+  int32_t no_resident_slice;     /* 1 = place small never-cut objects among the other leases */
 } ss_search_options;
 
 typedef struct ss_search_summary {
@@ -169,6 +171,15 @@ typedef struct ss_search_result ss_search_result;   /* opaque */
 
 int ss_plan_search(const ss_program* program, const ss_device_config* config,
                    const ss_search_options* options, ss_search_result** out);
+/* One Reduce + Emit pass at a given capacity, without simulation, repair or placement: the cut gaps
+ * as (object, index of the use the gap follows) pairs in the order they were cut, and the emitted
+ * actions. For differential tests against independent implementations. SS_INFEASIBLE when the
+ * capacity cannot be met; SS_OUT_OF_MEMORY when an output array is too short. */
+int ss_plan_reduce_emit(const ss_program* program, const ss_device_config* config,
+                        const ss_search_options* options, int64_t capacity, int32_t strategy,
+                        int32_t fetch_rule, int32_t tight, int32_t* cut_object, int32_t* cut_use,
+                        int32_t max_cuts, int32_t* n_cuts, ss_action* actions, int32_t max_actions,
+                        int32_t* n_actions);
 const ss_search_summary* ss_search_summary_of(const ss_search_result* r);
 const ss_action* ss_search_actions(const ss_search_result* r);
 const ss_interval* ss_search_intervals(const ss_search_result* r);

@@ -64,7 +64,8 @@ class SimResult(C.Structure):
 class SearchOptions(C.Structure):
     _fields_ = [("workers", i32), ("strategy_mask", i32), ("fetch_rule_mask", i32),
                 ("max_repairs", i32), ("minimum_object_bytes_evict_eligible", i64),
-                ("capacity_refinement_step", i64), ("deterministic", i32), ("trace", i32)]
+                ("capacity_refinement_step", i64), ("deterministic", i32), ("trace", i32),
+                ("linear_reduce", i32), ("no_resident_slice", i32)]
 
 
 class SearchSummary(C.Structure):
@@ -162,6 +163,8 @@ def _declare(lib: C.CDLL) -> None:
     lib.ss_recover_layout_reuse.argtypes = [i32, P64, P64, P64, P64, P32, P32, i32]
     lib.ss_plan_search.argtypes = [C.POINTER(Program), C.POINTER(DeviceConfig),
                                    C.POINTER(SearchOptions), C.POINTER(vp)]
+    lib.ss_plan_reduce_emit.argtypes = [C.POINTER(Program), C.POINTER(DeviceConfig), C.POINTER(SearchOptions),
+                                        i64, i32, i32, i32, P32, P32, i32, P32, C.POINTER(Action), i32, P32]
     lib.ss_search_summary_of.restype = C.POINTER(SearchSummary)
     lib.ss_search_summary_of.argtypes = [vp]
     lib.ss_search_actions.restype = C.POINTER(Action)

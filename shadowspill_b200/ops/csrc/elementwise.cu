@@ -200,6 +200,99 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
   }
 }
 
+// Block-per-row form for D <= 8192: a thread owns up to NORM_MAXV fixed vectors of eight columns,
+// so the row is read once (x and gy stay in registers across the row reduction) and the weight
+// gradient accumulates in registers over every row the block handles; one global atomic per
+// column per block at the end. Same arithmetic as the warp-per-row kernel above.
+template <int VPT>
+__global__ void __launch_bounds__(NORM_THREADS, VPT <= 2 ? 3 : 1)
+rmsnorm_bwd_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
+                        const bf16* __restrict__ gy, const float* __restrict__ rstd,
+                        bf16* __restrict__ dx, float* __restrict__ dw, int T, int D, int zero_centered,
+                        int accumulate) {
+  __shared__ float red[33];
+  const int nv = D >> 3;
+  const float wofs = zero_centered ? 1.f : 0.f;
+  uint4 wq[VPT];
+  float acc[VPT][8];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * NORM_THREADS;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
+    wq[i] = c < nv ? reinterpret_cast<const uint4*>(w)[c] : make_uint4(0, 0, 0, 0);
+  }
+  // rows are software-pipelined: the next row's x and gy are in flight while this one reduces
+  uint4 xq[VPT], gq[VPT], xn[VPT], gn[VPT];
+  auto fetch = [&](int row, uint4 (&xo)[VPT], uint4 (&go)[VPT]) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * D);
+    const uint4* gr = reinterpret_cast<const uint4*>(gy + static_cast<size_t>(row) * D);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nv) { xo[i] = xr[c]; go[i] = gr[c]; }
+    }
+  };
+  int row = blockIdx.x;
+  if (row < T) fetch(row, xq, gq);
+  for (; row < T; row += gridDim.x) {
+    const int next = row + gridDim.x;
+    if (next < T) fetch(next, xn, gn);
+    const float r = rstd[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nv) {
+        float xv[8], gv[8], ww[8];
+        unpack8(xq[i], xv);
+        unpack8(gq[i], gv);
+        unpack8(wq[i], ww);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float xh = xv[e] * r;
+          acc[i][e] += gv[e] * xh;
+          dot += gv[e] * (ww[e] + wofs) * xh;
+        }
+      }
+    }
+    const float mean = block_sum(dot, red) / static_cast<float>(D);
+    uint4* dr = reinterpret_cast<uint4*>(dx + static_cast<size_t>(row) * D);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nv) {
+        float xv[8], gv[8], ww[8], o[8];
+        unpack8(xq[i], xv);
+        unpack8(gq[i], gv);
+        unpack8(wq[i], ww);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = r * (gv[e] * (ww[e] + wofs) - xv[e] * r * mean);
+        if (accumulate) {
+          float prev[8];
+          unpack8(dr[c], prev);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] += prev[e];
+        }
+        dr[c] = pack8(o);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) { xq[i] = xn[i]; gq[i] = gn[i]; }
+  }
+  if (dw) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nv) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          if (acc[i][e] != 0.f) atomicAdd(dw + c * 8 + e, acc[i][e]);
+      }
+    }
+  }
+}
+
 // =============================================================== rotary embedding
 // In place on a [T, row_stride] buffer holding `heads` heads of width dh starting
 // at column col0; rotates the first `rot` channels of each head with the
@@ -261,30 +354,53 @@ __global__ void rope_vec_kernel(bf16* __restrict__ buf, const int* __restrict__ 
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       const float f = exp2f(-log2_theta * (2.f * (i0 + e)) / rot);
-      sincosf(pos * f, &sn[e], &cs[e]);
+      // sin/cos of pi*(angle/pi): the argument reduction of sincospif is exact and short
+      sincospif(pos * f * 0.31830988618379067f, &sn[e], &cs[e]);
       if (inverse) sn[e] = -sn[e];
     }
     bf16* row = buf + static_cast<long long>(t) * row_stride + col0 + i0;
-    for (int h = slot; h < heads; h += slots) {
-      bf16* base = row + h * dh;
-      uint4 av = *reinterpret_cast<const uint4*>(base);
-      uint4 bv = *reinterpret_cast<const uint4*>(base + half);
-      __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&av);
-      __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&bv);
+    // up to four heads per pass with every load issued before the first use
+    for (int h0 = slot; h0 < heads; h0 += 4 * slots) {
+      uint4 av[4], bv[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 a = __bfloat1622float2(a2[e]), b = __bfloat1622float2(b2[e]);
-        float2 oa, ob;
-        oa.x = a.x * cs[2 * e] - b.x * sn[2 * e];
-        ob.x = b.x * cs[2 * e] + a.x * sn[2 * e];
-        oa.y = a.y * cs[2 * e + 1] - b.y * sn[2 * e + 1];
-        ob.y = b.y * cs[2 * e + 1] + a.y * sn[2 * e + 1];
-        a2[e] = __float22bfloat162_rn(oa);
-        b2[e] = __float22bfloat162_rn(ob);
+      for (int k = 0; k < 4; ++k) {
+        const int h = h0 + k * slots;
+        if (h < heads) {
+          av[k] = *reinterpret_cast<const uint4*>(row + h * dh);
+          bv[k] = *reinterpret_cast<const uint4*>(row + h * dh + half);
+        }
       }
-      *reinterpret_cast<uint4*>(base) = av;
-      *reinterpret_cast<uint4*>(base + half) = bv;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int h = h0 + k * slots;
+        if (h >= heads) continue;
+        __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&av[k]);
+        __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&bv[k]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 a = __bfloat1622float2(a2[e]), b = __bfloat1622float2(b2[e]);
+          float2 oa, ob;
+          oa.x = a.x * cs[2 * e] - b.x * sn[2 * e];
+          ob.x = b.x * cs[2 * e] + a.x * sn[2 * e];
+          oa.y = a.y * cs[2 * e + 1] - b.y * sn[2 * e + 1];
+          ob.y = b.y * cs[2 * e + 1] + a.y * sn[2 * e + 1];
+          a2[e] = __float22bfloat162_rn(oa);
+          b2[e] = __float22bfloat162_rn(ob);
+        }
+        *reinterpret_cast<uint4*>(row + h * dh) = av[k];
+        *reinterpret_cast<uint4*>(row + h * dh + half) = bv[k];
+      }
     }
+  }
+}
+
+// idx = t * nv + c with 32-bit arithmetic whenever idx fits (a 64-bit division costs ~100 instructions)
+__device__ __forceinline__ void split_index(long long idx, int nv, long long& t, int& c) {
+  if (idx < (1LL << 31)) {
+    const unsigned i = static_cast<unsigned>(idx), q = i / static_cast<unsigned>(nv);
+    t = q; c = static_cast<int>(i - q * static_cast<unsigned>(nv));
+  } else {
+    t = idx / nv; c = static_cast<int>(idx - t * nv);
   }
 }
 
@@ -296,15 +412,15 @@ __global__ void swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict_
   const long long total = static_cast<long long>(T) * nv;
   for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
        idx += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long t = idx / nv;
-    const int c = static_cast<int>(idx % nv);
+    long long t; int c;
+    split_index(idx, nv, t, c);
     const uint4* row = reinterpret_cast<const uint4*>(gu + t * 2 * F);
     float g[8], u[8], o[8];
     unpack8(row[c], g);
     unpack8(row[nv + c], u);
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      const float s = g[e] / (1.f + __expf(-g[e]));
+      const float s = __fdividef(g[e], 1.f + __expf(-g[e]));
       o[e] = __bfloat162float(__float2bfloat16_rn(s)) * u[e];
     }
     reinterpret_cast<uint4*>(h + t * F)[c] = pack8(o);
@@ -317,8 +433,8 @@ __global__ void swiglu_bwd_kernel(const bf16* __restrict__ gu, const bf16* __res
   const long long total = static_cast<long long>(T) * nv;
   for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
        idx += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long t = idx / nv;
-    const int c = static_cast<int>(idx % nv);
+    long long t; int c;
+    split_index(idx, nv, t, c);
     const uint4* row = reinterpret_cast<const uint4*>(gu + t * 2 * F);
     float g[8], u[8], d[8], og[8], ou[8];
     unpack8(row[c], g);
@@ -326,7 +442,7 @@ __global__ void swiglu_bwd_kernel(const bf16* __restrict__ gu, const bf16* __res
     unpack8(reinterpret_cast<const uint4*>(dh + t * F)[c], d);
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      const float sig = 1.f / (1.f + __expf(-g[e]));
+      const float sig = __fdividef(1.f, 1.f + __expf(-g[e]));
       const float s = g[e] * sig;
       ou[e] = d[e] * s;
       og[e] = d[e] * u[e] * (sig * (1.f + g[e] * (1.f - sig)));
@@ -554,10 +670,11 @@ __global__ void adamw_sr_kernel(bf16* __restrict__ p, const void* __restrict__ g
       const float gg = gf[e] * a.grad_scale;
       const float mn = a.beta1 * mf[e] + (1.f - a.beta1) * gg;
       const float vn = a.beta2 * vf[e] + (1.f - a.beta2) * gg * gg;
-      const float mhat = mn / a.bias1;
-      const float vhat = vn / a.bias2;
+      // bias1/bias2 hold the reciprocals of the bias corrections (set by the launcher)
+      const float mhat = mn * a.bias1;
+      const float vhat = vn * a.bias2;
       float pn = pf[e] * (1.f - a.lr * a.weight_decay);
-      pn -= a.lr * mhat / (sqrtf(vhat) + a.eps);
+      pn -= a.lr * __fdividef(mhat, __fsqrt_rn(vhat) + a.eps);
       const uint32_t w0 = rw[e >> 1], w1 = rw[4 + (e >> 1)], w2 = rw[8 + (e >> 1)];
       const int sh = (e & 1) * 16;
       po[e] = a.sr_param ? sr_bf16(pn, w0 >> sh) : rn_bf16(pn);
@@ -576,10 +693,13 @@ __global__ void adamw_sr_kernel(bf16* __restrict__ p, const void* __restrict__ g
       u.z = vo[4] | (uint32_t(vo[5]) << 16); u.w = vo[6] | (uint32_t(vo[7]) << 16);
       *reinterpret_cast<uint4*>(v + e0) = u;
     } else {
-      for (int e = 0; e < cnt; ++e) {
-        p[e0 + e] = __ushort_as_bfloat16(po[e]);
-        m[e0 + e] = __ushort_as_bfloat16(mo[e]);
-        v[e0 + e] = __ushort_as_bfloat16(vo[e]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {            // static indices keep po/mo/vo in registers
+        if (e < cnt) {
+          p[e0 + e] = __ushort_as_bfloat16(po[e]);
+          m[e0 + e] = __ushort_as_bfloat16(mo[e]);
+          v[e0 + e] = __ushort_as_bfloat16(vo[e]);
+        }
       }
     }
   }
@@ -656,6 +776,18 @@ int ss_rmsnorm_bwd(const void* x, const void* w, const void* gy, const float* rs
                    float* dw, int T, int D, int zero_centered, int accumulate, void* stream) {
   if (D % 8 || D > 12288) return -2;       // the block's fp32 column sums live in 48 KB of shared memory
   if (T <= 0) return 0;
+  if (D <= NORM_THREADS * NORM_MAXV * 8 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    const int vpt = (D / 8 + NORM_THREADS - 1) / NORM_THREADS;
+    const int grid = T < 148 * 3 ? T : 148 * 3;
+    auto launch = [&](auto kern) {
+      kern<<<grid, NORM_THREADS, 0, (cudaStream_t)stream>>>(
+          (const bf16*)x, (const bf16*)w, (const bf16*)gy, rstd, (bf16*)dx, dw, T, D, zero_centered, accumulate);
+    };
+    if (vpt <= 1) launch(rmsnorm_bwd_rows_kernel<1>);
+    else if (vpt == 2) launch(rmsnorm_bwd_rows_kernel<2>);
+    else launch(rmsnorm_bwd_rows_kernel<4>);
+    return (int)cudaGetLastError();
+  }
   const int row_blocks = (T + NORM_BWD_WARPS - 1) / NORM_BWD_WARPS;
   rmsnorm_bwd_kernel<<<row_blocks < 148 * 4 ? row_blocks : 148 * 4, NORM_BWD_WARPS * 32,
                        sizeof(float) * D, (cudaStream_t)stream>>>(
@@ -747,8 +879,8 @@ int ss_adamw_sr(void* p, const void* g, void* m, void* v, long long n, int g_f32
   if (offset % 8) return -2;
   AdamWArgs a;
   a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.weight_decay = weight_decay;
-  a.bias1 = 1.f - powf(beta1, (float)step);
-  a.bias2 = 1.f - powf(beta2, (float)step);
+  a.bias1 = 1.f / (1.f - powf(beta1, (float)step));     // reciprocals: the kernel multiplies
+  a.bias2 = 1.f / (1.f - powf(beta2, (float)step));
   a.grad_scale = grad_scale;
   a.seed = seed ^ (0x9E3779B97F4A7C15ull * (unsigned long long)(step + 1));
   a.offset = offset; a.sr_param = sr_param; a.sr_state = sr_state;

@@ -205,7 +205,8 @@ __global__ void rs_adamw_kernel(PeerPtrs grads, const __nv_bfloat16* __restrict_
       const float mn = a.beta1 * mf[e] + (1.f - a.beta1) * gg;
       const float vn = a.beta2 * vf[e] + (1.f - a.beta2) * gg * gg;
       float pn = pf[e] * (1.f - a.lr * a.weight_decay);
-      pn -= a.lr * (mn / a.bias1) / (sqrtf(vn / a.bias2) + a.eps);
+      // bias1 / bias2 hold reciprocals; same arithmetic as the single-GPU kernel (elementwise.cu)
+      pn -= a.lr * __fdividef(mn * a.bias1, __fsqrt_rn(vn * a.bias2) + a.eps);
       const uint32_t w0 = rw[e >> 1], w1 = rw[4 + (e >> 1)], w2 = rw[8 + (e >> 1)];
       const int sh = (e & 1) * 16;
       po[e] = a.sr_param ? sr16(pn, w0 >> sh) : rn16(pn);
@@ -291,7 +292,7 @@ int ss_rs_adamw(void* const* grad_ptrs, void* p, void* m, void* v, long long lo,
   for (int j = 0; j < world; ++j) g.p[j] = grad_ptrs[j];
   RsAdamArgs a;
   a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.weight_decay = weight_decay;
-  a.bias1 = 1.f - powf(beta1, (float)step); a.bias2 = 1.f - powf(beta2, (float)step);
+  a.bias1 = 1.f / (1.f - powf(beta1, (float)step)); a.bias2 = 1.f / (1.f - powf(beta2, (float)step));
   a.grad_scale = grad_scale;
   a.seed = seed ^ (0x9E3779B97F4A7C15ull * (unsigned long long)(step + 1));
   a.offset = offset; a.sr_param = sr_param; a.sr_state = sr_state; a.g_f32 = g_f32;
@@ -317,7 +318,7 @@ int ss_rs_adamw_nvls(void* const* grad_ptrs, const void* mc_grad, void* p, void*
   for (int j = 0; j < world; ++j) g.p[j] = grad_ptrs[j];
   RsAdamArgs a;
   a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.weight_decay = weight_decay;
-  a.bias1 = 1.f - powf(beta1, (float)step); a.bias2 = 1.f - powf(beta2, (float)step);
+  a.bias1 = 1.f / (1.f - powf(beta1, (float)step)); a.bias2 = 1.f / (1.f - powf(beta2, (float)step));
   a.grad_scale = grad_scale;
   a.seed = seed ^ (0x9E3779B97F4A7C15ull * (unsigned long long)(step + 1));
   a.offset = offset; a.sr_param = sr_param; a.sr_state = sr_state; a.g_f32 = 0;

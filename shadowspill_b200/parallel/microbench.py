@@ -12,6 +12,11 @@ Per rank, for a tensor of the given size (default: one Llama-3-8B layer, 416 MiB
 CUDA-event times, max over ranks, 3 warm-ups; roofline = bytes that must cross NVLink per rank
 / 770 GB/s (measured peer-copy rate per direction) or, for the fused update, the slower of
 that and the shard's HBM traffic / measured copy bandwidth.
+
+``--case experts`` times one forward + backward of an expert-parallel routed layer (pull dispatch,
+grouped GEMMs, scatter-epilogue combine) beside the same per-rank expert work with nothing crossing
+NVLink and beside four library all-to-all exchanges of the row set, which is what a dispatch /
+combine built on a collective library moves for one forward + backward.
 """
 from __future__ import annotations
 
@@ -44,16 +49,63 @@ def _timed(fn, dev, iters=10, warmup=3):
     return float(t)
 
 
+def experts_case(a, rank: int, world: int, dev) -> dict:
+    from ..ops import moe as moe_ops
+    from .expert_parallel import ExpertParallelGroup, experts
+    T, D, Fe, E, k = a.tokens, a.d_model, a.d_expert, a.experts, a.top_k
+    group = ExpertParallelGroup(T, k, D, E)
+    local_experts = E // world
+    w13 = (torch.randn(local_experts, 2 * Fe, D, device=dev) * 0.02).bfloat16()
+    w2 = (torch.randn(local_experts, D, Fe, device=dev) * 0.02).bfloat16()
+    h = torch.randn(T, D, device=dev).bfloat16().requires_grad_(True)
+    logits = torch.randn(T, E, device=dev).requires_grad_(True)
+    logits_local = torch.randn(T, local_experts, device=dev).requires_grad_(True)
+    dout = torch.randn(T, D, device=dev).bfloat16()
+    rows_out = torch.empty(T * k, D, device=dev, dtype=torch.bfloat16)
+    rows_in = torch.empty_like(rows_out)
+
+    def parallel():
+        experts(h, logits, w13, w2, group, True, None).backward(dout)
+
+    def all_local():        # the same expert work per rank on rows that never leave the GPU
+        moe_ops.experts(h, logits_local, w13, w2, k, True, None).backward(dout)
+
+    def library_exchange():
+        for _ in range(4):
+            dist.all_to_all_single(rows_in, rows_out)
+    ms = _timed(parallel, dev, iters=5, warmup=2)
+    ms_local = _timed(all_local, dev, iters=5, warmup=2)
+    ms_a2a = _timed(library_exchange, dev, iters=5, warmup=2)
+    flops = 2 * 2 * T * k * (2 * Fe * D + D * Fe)             # per rank: forward + data gradients
+    return {"case": "experts_fwd_bwd", "ranks": world, "tokens": T, "d_model": D, "d_expert": Fe,
+            "experts": E, "top_k": k, "ms": round(ms, 3), "all_local_ms": round(ms_local, 3),
+            "nccl_all_to_all_x4_ms": round(ms_a2a, 3),
+            "gemm_floor_ms_at_1.4_pflops": round(flops / 1.4e15 * 1e3, 3)}
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default="collectives", choices=["collectives", "experts"])
     ap.add_argument("--mib", type=float, default=416.0)
     ap.add_argument("--hbm-gbs", type=float, default=6550.0)
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--d-model", type=int, default=2048)
+    ap.add_argument("--d-expert", type=int, default=1024)
+    ap.add_argument("--experts", type=int, default=64)
+    ap.add_argument("--top-k", type=int, default=8)
     a = ap.parse_args(argv)
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
+    if a.case == "experts":
+        row = experts_case(a, rank, world, dev)
+        if rank == 0:
+            print(json.dumps(row), flush=True)
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     n = int(a.mib * (1 << 20)) // 2 // (8 * world) * (8 * world)          # bf16 elements, whole shards
     per = n // world
     pool = pc.allocate_symmetric_pool(2 * n * 2 + (1 << 20), dev)

@@ -41,6 +41,10 @@ class SearchOptions:
     deterministic: bool = False
     trace: bool = False
     alignment: int = 512
+    # the plain O(cuts x gaps) reducer instead of the indexed one (same decisions; for comparison)
+    linear_reduce: bool = False
+    # small never-cut objects get static homes in a slice behind the main layout
+    resident_slice: bool = True
 
     def to_native(self) -> native.SearchOptions:
         sm = sum(1 << native.STRATEGIES.index(s) for s in self.strategies)
@@ -48,7 +52,7 @@ class SearchOptions:
         return native.SearchOptions(self.workers, sm, rm, self.max_repairs,
                                     self.minimum_object_bytes_evict_eligible,
                                     self.capacity_refinement_step, int(self.deterministic),
-                                    int(self.trace))
+                                    int(self.trace), int(self.linear_reduce), int(not self.resident_slice))
 
 
 @dataclass
@@ -188,6 +192,35 @@ def plan_program(program: Program, budgets: MemoryBudgets,
     if options.trace:
         plan.communication["search_trace"] = trace
     return plan
+
+
+def reduce_emit(program: Program, capacity: int, communication: CommunicationInfo | None = None,
+                options: SearchOptions | None = None, strategy: str = "stall",
+                fetch_rule: str = "latest-safe", tight: bool = False):
+    """One Reduce + Emit pass of the native planner at ``capacity`` (no simulation, repair or
+    placement): ``(cuts, actions)`` with cuts as ``(object, use index)`` in cut order and actions as
+    ``(kind, object, trigger task)`` with kind 0 fetch / 1 evict / 2 release, or ``None`` when the
+    capacity cannot be met. For comparison with ``qualification/pressurefit_oracle.py``."""
+    communication = communication or CommunicationInfo()
+    options = options or SearchOptions()
+    lib = native.core()
+    prog, keep = program.to_native()
+    cfg = SimulationConfig(capacity, communication, options.alignment).to_native()
+    opt = options.to_native()
+    n_uses = sum(len(t.uses) for t in program.tasks)
+    max_cuts, max_actions = n_uses + 1, 2 * n_uses + 2 * len(program.objects) + 2
+    co, cu = (C.c_int32 * max_cuts)(), (C.c_int32 * max_cuts)()
+    acts = (native.Action * max_actions)()
+    nc, na = C.c_int32(0), C.c_int32(0)
+    rc = lib.ss_plan_reduce_emit(C.byref(prog), C.byref(cfg), C.byref(opt), int(capacity),
+                                 native.STRATEGIES.index(strategy), native.FETCH_RULES.index(fetch_rule),
+                                 int(tight), co, cu, max_cuts, C.byref(nc), acts, max_actions, C.byref(na))
+    del keep
+    if rc == native.INFEASIBLE:
+        return None
+    native.check(rc, "ss_plan_reduce_emit")
+    return ([(co[i], cu[i]) for i in range(nc.value)],
+            [(acts[i].kind, acts[i].object, acts[i].trigger_task) for i in range(na.value)])
 
 
 def host_kept(name: str, nbytes: int) -> bool:

@@ -138,6 +138,7 @@ class LiveRun:
             except ValueError as exc:           # refused before any worker hears of it
                 raise WorkerFailure(str(exc), "not_started") from None
             self.checkpoints[name] = args["directory"]
+            self.journal.append("checkpoint", {"name": name, "directory": args["directory"]})
             op_worker = "save"
         elif op == "restore":
             try:
@@ -182,6 +183,7 @@ class LiveRun:
                                  "execution_seconds": out["execution_seconds"]})
         if op == "close":
             self.state = "closed"
+            self.journal.append("closed", {})
             threading.Thread(target=self.release, daemon=True).start()
         return out
 
@@ -207,6 +209,69 @@ class LiveRun:
                 "boundary": self.controller.boundary() if self.controller else {}}
 
 
+class RecoveredRun:
+    """What the journal of a run says after the service process that owned it has gone: read-only.
+
+    The run's own journal is replayed record by record (``created``, ``ready``, ``receipt``,
+    ``checkpoint``, ``failed``, ``closed``); a run that was neither closed nor failed is
+    ``interrupted``: its workers died with the old process, so it accepts no requests, but its
+    status, loss history, receipts and checkpoints stay readable, and a new run can start from its
+    last checkpoint. Reference: packages/engine/src/shadowspill/server/storage.py:178."""
+    controller = None
+    group = None
+
+    def __init__(self, server: "Server", session: str, run: str):
+        self.server, self.session, self.run = server, session, run
+        self.dir = server.root / "runs" / session / run
+        self.journal = Journal(self.dir / "journal")
+        self.body: dict[str, Any] = {}
+        self.state, self.error = "preparing", ""
+        self.progress: list[str] = []
+        self.metrics: list[dict[str, Any]] = []
+        self.checkpoints: dict[str, str] = {}
+        self.plan_summary: dict[str, Any] = {}
+        self.operation_plans: dict[str, dict[str, Any]] = {}
+        self.plan_names: dict[str, str] = {}
+        self.completed_updates = 0
+        workers = 0
+        for rec in self.journal.records():
+            kind, data = rec["kind"], rec["data"]
+            if kind == "ready":
+                self.state, workers = "ready", int(data.get("workers", 0))
+                self.plan_summary = dict(data.get("plan") or {})
+            elif kind == "receipt":
+                if data.get("completed_updates") is not None:
+                    self.completed_updates = max(self.completed_updates, int(data["completed_updates"]))
+                if data.get("operation") in ("step", "optim_step") and data.get("loss") is not None \
+                        and data.get("state") == "completed":
+                    self.metrics.append({"update": data.get("completed_updates"), "loss": data["loss"],
+                                         "execution_seconds": data.get("execution_seconds")})
+            elif kind == "checkpoint":
+                self.checkpoints[data["name"]] = data["directory"]
+            elif kind == "failed":
+                self.state, self.error = "failed", str(data.get("error", ""))
+            elif kind == "closed":
+                self.state = "closed"
+        self.workers = workers
+        if self.state in ("preparing", "ready"):
+            last = next(reversed(self.checkpoints), None)
+            self.error = ("the service restarted while this run was live; "
+                          + (f"its last checkpoint is {last!r}" if last else "it had saved no checkpoint")
+                          + f" ({self.completed_updates} completed updates)")
+            self.state = "interrupted"
+            self.journal.append("interrupted", {"reason": "service restart",
+                                                "completed_updates": self.completed_updates})
+
+    def info(self) -> dict[str, Any]:
+        return {"session": self.session, "run": self.run, "state": self.state, "error": self.error,
+                "workers": self.workers, "geometry": {}, "plan_summary": self.plan_summary, "provenance": {},
+                "budgets": {}, "state_valid": False, "recovered": True,
+                "boundary": {"completed_updates": self.completed_updates, "valid": False}}
+
+    def release(self) -> None:
+        """Nothing to release: the workers and the admission lease died with the old process."""
+
+
 class Server:
     def __init__(self, service_root: str | Path, model_root: str | Path | None = None,
                  host: str = "127.0.0.1", port: int = 0, token: str | None = None):
@@ -227,10 +292,22 @@ class Server:
         self.t0 = time.monotonic()
         self.httpd: ThreadingHTTPServer | None = None
         self._thread: threading.Thread | None = None
-        # recovery: runs that were live when the previous incarnation stopped are marked stopped
+        # recovery: every run the service journal names is rebuilt from its own journal; those
+        # that were live when the previous incarnation stopped come back as "interrupted"
+        closed = {r["data"].get("run") for r in self.journal.records("run_closed")}
         for rec in self.journal.records("run"):
-            if not any(r["data"].get("run") == rec["data"]["run"] for r in self.journal.records("run_closed")):
-                self.journal.append("run_closed", {"run": rec["data"]["run"], "reason": "service restart"})
+            session, run = rec["data"].get("session"), rec["data"]["run"]
+            if not session or not (self.root / "runs" / session / run / "journal").is_dir():
+                continue
+            try:
+                recovered = RecoveredRun(self, session, run)
+            except Exception as exc:  # noqa: BLE001  (a damaged run journal must not stop the service)
+                self.journal.append("recovery_failed", {"run": run, "error": f"{type(exc).__name__}: {exc}"})
+                continue
+            self.runs[(session, run)] = recovered
+            if run not in closed:
+                self.journal.append("run_closed", {"run": run, "reason": "service restart",
+                                                   "state": recovered.state})
         self.journal.append("started", {"incarnation": self.incarnation})
 
     # ------------------------------------------------------------------ lifecycle

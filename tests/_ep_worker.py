@@ -56,54 +56,6 @@ def main():
                 "dw13": rel(G1["w13"], G0["w13"][lo:lo + el]), "dw2": rel(G1["w2"], G0["w2"][lo:lo + el])}
         bad = {n: e for n, e in errs.items() if not e < 2e-2}
         assert not bad, (rank, step, errs)
-    # ---- timing of forward+backward against the all-local op (device events, max over ranks)
-    def timed(fn, n=5):
-        for _ in range(2):
-            fn()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        dist.barrier()
-        torch.cuda.synchronize()
-        a.record()
-        for _ in range(n):
-            fn()
-        b.record()
-        b.synchronize()
-        t = torch.tensor([a.elapsed_time(b) / n], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t)
-    if os.environ.get("SS_EP_BENCH"):
-        T2, D2, F2, E2, k2 = 8192, 2048, 1024, 64, 8
-        ep2 = ExpertParallelGroup(T2, k2, D2, E2)
-        e2 = E2 // world
-        b13 = (torch.randn(e2, 2 * F2, D2, device=dev) * 0.02).bfloat16()
-        b2 = (torch.randn(e2, D2, F2, device=dev) * 0.02).bfloat16()
-        hh = torch.randn(T2, D2, device=dev).bfloat16().requires_grad_(True)
-        lg = torch.randn(T2, E2, device=dev).requires_grad_(True)
-        dd = torch.randn(T2, D2, device=dev).bfloat16()
-
-        def run():
-            experts(hh, lg, b13, b2, ep2, True, None).backward(dd)
-        ms = timed(run)
-        # the same per-rank expert work with nothing crossing NVLink (all-local op on E/R experts)
-        lg_l = torch.randn(T2, e2, device=dev).requires_grad_(True)
-
-        def run_local():
-            moe_ops.experts(hh, lg_l, b13, b2, k2, True, None).backward(dd)
-        ms_local = timed(run_local)
-        # what a library all-to-all alone would cost for the four row exchanges of one fwd+bwd
-        rows_out = torch.empty(T2 * k2, D2, device=dev, dtype=torch.bfloat16)
-        rows_in = torch.empty_like(rows_out)
-
-        def run_a2a():
-            for _ in range(4):
-                dist.all_to_all_single(rows_in, rows_out)
-        ms_a2a = timed(run_a2a)
-        flops = 2 * 2 * T2 * k2 * (2 * F2 * D2 + D2 * F2)          # per rank: forward + data gradients
-        if rank == 0:
-            print(f"EP_BENCH world={world} T={T2} D={D2} F={F2} E={E2} k={k2}: {ms:.3f} ms fwd+bwd "
-                  f"(no wgrad sink); all-local experts on the same rows {ms_local:.3f} ms; "
-                  f"4 x NCCL all_to_all_single of the row set alone {ms_a2a:.3f} ms; "
-                  f"GEMM floor {flops / 1.4e15 * 1e3:.3f} ms at 1.4 PFLOP/s sustained")
     print(f"rank {rank} OK ", flush=True)
     dist.destroy_process_group()
 

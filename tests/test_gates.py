@@ -17,17 +17,6 @@ def test_compare_tensors_flags_sign_flips():
     assert m["sign_agreement"] < 0.99 and m["near_zero_abs"] < 1e-5
 
 
-def _twin_config(family):
-    from dataclasses import replace
-    from shadowspill_b200.models.config import preset
-    if family == "llama3":
-        return replace(preset("llama3-tiny"), n_layers=3, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, d_ff=512)
-    if family == "qwen35":
-        return replace(preset("qwen35-numerical"), n_layers=4, d_model=512, d_ff=1024, n_heads=4, n_kv_heads=2,
-                       head_dim=128, dn_qk_heads=2, dn_v_heads=4, vocab_size=2048)
-    return replace(preset("olmoe-tiny"), n_layers=3, d_model=256, n_heads=4, n_kv_heads=4, head_dim=64)
-
-
 def test_torch_twin_gate_on_cpu():
     """The same gate in fp32 on the CPU is exact to rounding: the planned program and the
     plain-PyTorch twin are two implementations of one model."""
@@ -48,8 +37,8 @@ def test_planned_bf16_training_matches_the_fp32_pytorch_twin(family, frontend):
     """Five updates of two microbatches, bf16 kernels under a spilling plan, against fp32 eager
     PyTorch + torch.optim.AdamW: weights within rel-L2 2.5 %, cosine 0.999, sign agreement 99 %."""
     from shadowspill_b200.ops import _lib
-    from shadowspill_b200.qualification.gates import torch_twin_gate
-    rec = torch_twin_gate(_twin_config(family), "cuda", updates=5, microbatches=2, tokens=1024, frontend=frontend)
+    from shadowspill_b200.qualification.gates import torch_twin_gate, twin_config
+    rec = torch_twin_gate(twin_config(family), "cuda", updates=5, microbatches=2, tokens=1024, frontend=frontend)
     _lib.check_status()
     assert rec["passed"], (rec["failures"], rec["weights"], rec["losses"])
     assert rec["frontend"] == frontend and rec["fetch_bytes"] > 0

@@ -452,3 +452,51 @@ def test_axis_chunks_and_the_graph_frontend_through_the_service(service):
     graph = run(Preparation(build=BuildOptions(frontend="graph"), **common))
     for a, b, c in zip(whole, cut, graph):
         assert abs(a - b) < 1e-4 * max(1.0, abs(a)) and abs(a - c) < 1e-4 * max(1.0, abs(a)), (whole, cut, graph)
+
+
+def test_a_restarted_service_replays_its_journals(tmp_path):
+    """A run that was live when the service process stopped comes back as a read-only record:
+    state ``interrupted``, its completed updates, loss history and checkpoint names from the
+    journal; requests to it are refused, and a new run resumes from its checkpoint."""
+    root = tmp_path / "root"
+    common = dict(batch=BatchConfig(tokens_per_step=512, microbatch_tokens=256),
+                  memory=Memory(device_gib=0.53, spill_gib=0.25), resources=Resources(gpus=1, backend="cpu"),
+                  preparation=Preparation(profiling=ProfilingOptions(enabled=False), calibrate=False,
+                                          planning=PlanningOptions(minimum_object_bytes_evict_eligible=1024,
+                                                                   workers=1)), timeout=300)
+    with Server(root, token="secret") as first:
+        with ServiceClient(first.url, token="secret") as svc:
+            tr = svc.create_training_client(Model("llama3-tiny", dtype="float32"),
+                                            Optimizer(lr=3e-3, parameter_rounding="nearest"), **common).result()
+            losses = [tr.step(text_batch(_sequences(s))).result().loss for s in range(2)]
+            tr.save_checkpoint("after_two").result()
+            session, run = svc.session, tr.run
+            # the service goes away with the run still open (no close request)
+    with Server(root, token="secret") as second:
+        old = second.get_run(session, run)
+        info = old.info()
+        assert info["state"] == "interrupted" and info["recovered"] and "after_two" in info["error"]
+        assert info["boundary"]["completed_updates"] == 2
+        assert [round(m["loss"], 5) for m in old.metrics] == [round(x, 5) for x in losses]
+        assert list(old.checkpoints) == ["after_two"]
+        assert any(r["kind"] == "run_closed" and r["data"]["reason"] == "service restart"
+                   for r in second.journal.records())
+        import json
+        import urllib.error
+        import urllib.request
+        req = urllib.request.Request(f"{second.url}/v1/runs/{session}/{run}/requests", method="POST",
+                                     data=json.dumps({"request_id": "x", "operation": "step"}).encode(),
+                                     headers={"Authorization": "Bearer secret", "Content-Type": "application/json"})
+        with pytest.raises(urllib.error.HTTPError) as e:
+            urllib.request.urlopen(req)
+        assert e.value.code == 409 and "interrupted" in e.value.read().decode()
+        with ServiceClient(second.url, token="secret") as svc:
+            svc.session = session                        # the checkpoint belongs to that session
+            again = svc.create_training_client(Model("llama3-tiny", dtype="float32"),
+                                               Optimizer(lr=3e-3, parameter_rounding="nearest"),
+                                               checkpoint="after_two", **common).result()
+            nxt = again.step(text_batch(_sequences(2))).result()
+            assert nxt.completed_updates == 3
+            again.close()
+    with Server(root, token="secret") as third:
+        assert third.get_run(session, run).info()["state"] == "interrupted"      # stable across restarts
