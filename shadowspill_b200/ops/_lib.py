@@ -120,6 +120,7 @@ def check_status(device: torch.device | int | None = None) -> None:
 # delta + dQ + dKV; sum of squares: partials + final)
 _KERNELS_PER_CALL = {"ss_attn_bwd": 3, "ss_attn_bwd_g": 3, "ss_sumsq": 2}
 launch_count = 0
+_by_entry: dict[str, int] = {}
 
 
 def check(rc: int, what: str) -> None:
@@ -127,4 +128,11 @@ def check(rc: int, what: str) -> None:
     global launch_count
     if rc != 0:
         raise RuntimeError(f"{what} failed with code {rc}")
-    launch_count += _KERNELS_PER_CALL.get(what, 1)
+    n = _KERNELS_PER_CALL.get(what, 1)
+    launch_count += n
+    _by_entry[what] = _by_entry.get(what, 0) + n
+
+
+def launch_counts() -> dict[str, int]:
+    """Kernels enqueued so far, by launcher entry point."""
+    return dict(_by_entry)

@@ -84,3 +84,20 @@ def test_workers_run_under_the_wrapper_and_the_service_reports_it(tmp_path, monk
     assert len(reports) == 1
     if info is not None:
         assert info["requested"] and info["available"] and info["report"].endswith("worker0.nsys-rep")
+
+
+def test_stage_trace_runs_one_task_in_isolation():
+    """The single-task tool builds the program, binds the named task to synthetic operands and
+    times it; an unknown task name lists the tasks of that kind."""
+    import pytest
+    from shadowspill_b200.profiling.stage_trace import parse_selection, trace_task
+    import torch
+    assert parse_selection("1:save,2:save_attention") == {1: "save", 2: "save_attention"}
+    rec = trace_task("llama3-tiny", "B.layer0.1", microbatch_tokens=256, selection={1: "save_attention"},
+                     device="cpu", warmup=1, repeats=2, dtype=torch.float32)
+    assert rec["variant"] == "save_attention" and len(rec["seconds"]) == 2 and rec["operand_bytes"] > 0
+    graph = trace_task("llama3-tiny", "F.layer1.0", microbatch_tokens=256, frontend="graph", device="cpu",
+                       warmup=1, repeats=1, dtype=torch.float32)
+    assert graph["kind"] == "forward"
+    with pytest.raises(KeyError, match="B.layer0.0"):
+        trace_task("llama3-tiny", "B.layer9.0", microbatch_tokens=256, device="cpu", dtype=torch.float32)

@@ -126,3 +126,36 @@ def test_whole_search_is_the_same_with_either_reducer_and_honours_the_resident_s
         for (lo, nb), (nxt, _) in zip(homes, homes[1:]):
             assert lo + nb <= nxt, seed
         assert all(off >= main_end for off, _ in homes), seed
+
+
+def test_search_trace_is_parsed_into_candidate_trajectories(tmp_path):
+    """The trace tool: every candidate the search evaluated appears with its reductions and its
+    placement; the planned pressure never exceeds the capacity."""
+    import torch
+    from shadowspill_b200.frontend.capture import BatchGeometry, StepDataOrdering, build_step
+    from shadowspill_b200.models.config import preset
+    from shadowspill_b200.planning import trace as tr
+    cfg = preset("llama3-tiny")
+    program, _ = build_step(cfg, BatchGeometry(256, 2, 16, 64), StepDataOrdering(), dtype=torch.float32)
+    plan = None
+    for percent in (100, 105, 110, 120):          # the tightest of these that still plans
+        budgets = MemoryBudgets(max(tr.uncut_pressure(program)) * percent // 100, 64 << 20, headroom_bytes=0)
+        try:
+            plan = plan_program(program, budgets, COMM, SearchOptions(trace=True, workers=1,
+                                                                      minimum_object_bytes_evict_eligible=1024))
+            break
+        except PlanningError:
+            continue
+    assert plan is not None
+    got = tr.parse_trace(plan.communication["search_trace"])
+    assert len(got) == 8 and {c["strategy"] for c in got} == {"stall", "traffic"}
+    assert any(c["placed"] for c in got)
+    winner = min((c for c in got if c["placed"]), key=lambda c: c["makespan_ns"])
+    assert abs(winner["makespan_ns"] * 1e-9 - plan.summary.duration_seconds) < 1e-9
+    assert all(any(e["kind"] == "reduce" for e in c["events"]) for c in got if c["placed"])
+    text = tr.explain(got)
+    assert "gaps cut" in text and "fits" in text
+    uncut, planned = tr.uncut_pressure(program), tr.planned_pressure(plan)
+    assert budgets.capacity >= max(planned) and plan.summary.fetch_bytes > 0 and len(uncut) == len(planned)
+    svg = tr.pressure_svg(uncut, planned, budgets.capacity)
+    assert svg.startswith("<svg") and "capacity" in svg

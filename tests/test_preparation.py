@@ -1,6 +1,8 @@
 """Prepared bundles: a second session opens from the archive and trains identically."""
 from dataclasses import replace
 
+import pytest
+
 from shadowspill_b200.data.synthetic import make_batch
 from shadowspill_b200.planning.plan import SearchOptions
 from shadowspill_b200.training.preparation import load_bundle
@@ -75,3 +77,23 @@ def test_pretrained_weights_and_adapters_through_the_session(tmp_path):
     assert torch.equal(after["layer0.wq"], q)                  # the base stayed frozen
     assert float(after["layer0.wq_lora_b"].abs().max()) > 0.0  # the adapter moved
     session.close()
+
+
+def test_measure_plan_runs_a_prepared_bundle_without_preparing(tmp_path):
+    """The plan-measurement tool opens an existing bundle (no build, profile or search), runs
+    updates, and writes per-update and summary figures; a bundle of another setup is refused."""
+    import json
+    from shadowspill_b200.execution.measure_plan import run
+    path = tmp_path / "training.ssp"
+    TrainingSession(_setup(path)).close()
+    out = tmp_path / "measurement"
+    report = run(_setup(path), steps=3, warmup_steps=1, output_dir=out)
+    s = report["summary"]
+    assert s["prepared_from_bundle"] and s["steps"] == 3 and s["tokens_per_second"] > 0
+    assert len(report["updates"]) == 4 and report["updates"][0]["warmup"] and not report["updates"][1]["warmup"]
+    assert all(u["loss"] > 0 for u in report["updates"])
+    assert sum(u["fetch_bytes"] for u in report["updates"]) > 0
+    assert json.loads((out / "measurement.json").read_text())["summary"]["unit"] == "tokens"
+    assert "measured / simulated" in (out / "measurement.md").read_text()
+    with pytest.raises(RuntimeError, match="does not match"):
+        run(replace(_setup(path), device_gib=0.61), steps=1, warmup_steps=0)
