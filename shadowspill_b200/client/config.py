@@ -197,6 +197,8 @@ class Preparation:
     planning: PlanningOptions = PlanningOptions()
     policies: tuple = ()
     calibrate: bool = True
+    # run build / profile / communicate / plan as four fresh processes before the workers start
+    separate_processes: bool = False
 
 
 @record

@@ -89,6 +89,15 @@ class LiveRun:
             source = self.body.get("plans")
             bundle_dir = (self.server.root / "runs" / self.session / str(source)) if source else self.dir
             r.setups[0]["bundle"] = str(bundle_dir / "training.ssp")
+            if (self.body.get("preparation") or {}).get("separate_processes") and not source \
+                    and not Path(r.setups[0]["bundle"]).exists():
+                # build, profile, communicate and plan as four fresh processes; the worker then opens
+                # the bundle and carries nothing of them (training/phases.py)
+                from ..training.phases import prepare_job, setup_from_json
+                self.log("preparing in separate processes: build, profile, communicate, plan")
+                made = prepare_job(setup_from_json(r.setups[0]), self.dir / "preparation", log=self.log)
+                import shutil
+                shutil.copyfile(made, r.setups[0]["bundle"])
             ckpt = self.body.get("checkpoint")
             if ckpt:
                 ckpt = self.server.resolve_checkpoint(self.session, ckpt)

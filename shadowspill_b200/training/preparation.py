@@ -25,7 +25,8 @@ FILE_NAME = "training.ssp"
 
 
 def setup_identity(setup, cfg: DecoderConfig) -> str:
-    """Digest of every setting that changes the programs or their plans."""
+    """Digest of every setting that changes the programs or their plans (which process runs
+    which preparation phase is not one of them)."""
     s = asdict(setup) if hasattr(setup, "__dataclass_fields__") else dict(setup)
     keep = {k: s[k] for k in ("device_gib", "spill_gib", "tokens_per_step", "microbatch_tokens", "slots",
                               "mean_seqlen", "dtype", "world_size", "walks", "recompute_shares",

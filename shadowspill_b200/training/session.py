@@ -14,7 +14,9 @@ training/worker/runtime.py:195 (``PreparedWorker.open``).
 """
 from __future__ import annotations
 
+import json
 import time
+from pathlib import Path
 from dataclasses import dataclass, field
 
 import torch
@@ -97,6 +99,11 @@ class TrainingSetup:
     # profile the tasks on sequences of exactly this many tokens (0 = the packed log-normal mix):
     # the cost of the sequence mixers depends on it, so long-context runs set it
     profile_sequence_tokens: int = 0
+    # preparation as separate processes (training/phases.py): a session stops after the named
+    # phase ("build" | "profile" | "communicate" | "plan") having written that phase's result
+    # into phase_directory; later phases read the earlier results from there instead of measuring
+    stop_after: str = ""
+    phase_directory: str = ""
     pretrained: str = ""                 # directory of Hugging Face safetensors to start from
     # content-addressed store of task profiles shared between runs ("" = none)
     store: str = ""
@@ -143,6 +150,18 @@ class TrainingSession:
         self.budgets = MemoryBudgets.from_gib(setup.device_gib, setup.spill_gib)
         self.timings: dict[str, float] = {}
         world, rank = setup.world_size, setup.rank
+        self.executor = None
+        if setup.stop_after not in ("", "build", "profile", "communicate", "plan"):
+            raise ValueError("stop_after is one of build, profile, communicate, plan")
+        phase_dir = Path(setup.phase_directory) if setup.phase_directory else None
+        if setup.stop_after and phase_dir is None:
+            raise ValueError("stop_after needs phase_directory")
+        if phase_dir is not None:
+            phase_dir.mkdir(parents=True, exist_ok=True)
+
+        def phase_result(name: str):
+            f = phase_dir / f"{name}.json" if phase_dir is not None else None
+            return json.loads(f.read_text()) if (f is not None and f.exists()) else None
         if setup.candidate_selections:
             selections = []
             for item in setup.candidate_selections:
@@ -222,7 +241,9 @@ class TrainingSession:
         # ---- host link calibration: every rank of the job measures its lanes at the same time,
         # because they share the host's memory system; the plan is made for the slowest rank
         from_bundle = loaded is not None
-        if world > 1:
+        # a preparation phase other than "communicate" is one process, whatever the job's size
+        solo = setup.stop_after in ("build", "profile", "plan")
+        if world > 1 and not solo:
             import torch.distributed as dist
             flag = [from_bundle]
             dist.broadcast_object_list(flag, src=0)
@@ -236,7 +257,13 @@ class TrainingSession:
             raise ValueError("a file spill pool needs spill_directory or spill_image")
         if setup.spill_pool == "remote" and not remote:
             raise ValueError("a remote spill pool needs spill_address (host:port of a memory daemon)")
-        if setup.calibrate and cuda and not from_bundle:
+        measured_comm = phase_result("communication") if setup.stop_after != "communicate" else None
+        if measured_comm is not None:
+            calibrated = CommunicationInfo.from_json(measured_comm["communication"])
+            self.log(f"communication: from {phase_dir / 'communication.json'}")
+        if setup.stop_after in ("build", "profile"):
+            pass                                   # these phases do not touch the lanes
+        elif setup.calibrate and cuda and not from_bundle and measured_comm is None:
             t0 = time.perf_counter()
             probe = 256 << 20
             if world > 1:
@@ -269,6 +296,16 @@ class TrainingSession:
             self.timings["communication"] = time.perf_counter() - t0
             self.log(f"{'staged lanes' if file_spill else 'host link'}: fetch {rates[0] / 1e9:.1f} ({rates[1] / 1e9:.1f} two-way) GB/s, "
                      f"evict {rates[2] / 1e9:.1f} ({rates[3] / 1e9:.1f}) GB/s")
+        if setup.stop_after == "communicate":
+            scale = 1.0
+            if setup.profile and setup.calibrate_overlap and cuda:
+                from ..communication.measure import measure_overlap
+                scale = min(1.3, max(1.0, measure_overlap(setup.device_index).duration_scale))
+            if rank == 0:
+                comm = calibrated or CommunicationInfo(world_size=world)
+                (phase_dir / "communication.json").write_text(json.dumps(
+                    {"communication": comm.to_json(), "duration_scale": scale, "timings": self.timings}))
+            return
         if loaded is not None:
             from ..ir.plan import Plan
             chosen, plan_json, extra_json = loaded["chosen"], loaded["plan"], loaded["extra_plans"]
@@ -288,10 +325,28 @@ class TrainingSession:
             extras = {op: build_extra(op) for op in extra_ops}
             layout = StateLayout.build([p for p, _ in candidates] + [p for p, _ in extras.values()])
             self.timings["build"] = time.perf_counter() - t0
+            digests = {"candidates": [p.digest() for p, _ in candidates],
+                       "operations": {op: p.digest() for op, (p, _) in extras.items()}}
+            built = phase_result("build")
+            if setup.stop_after == "build":
+                (phase_dir / "build.json").write_text(json.dumps(
+                    {**digests, "identity": identity, "timings": self.timings,
+                     "tasks": [len(p.tasks) for p, _ in candidates],
+                     "objects": [len(p.objects) for p, _ in candidates]}))
+                return
+            if built is not None and {k: built[k] for k in digests} != digests:
+                raise RuntimeError("the programs built in this process differ from the ones the build phase "
+                                   "recorded: the phases were not given the same setup")
             # ---- profile distinct tasks once
             t0 = time.perf_counter()
             scale = 1.0
-            if setup.profile and setup.calibrate_overlap and cuda:
+            measured_profiles = phase_result("profiles") if setup.stop_after != "profile" else None
+            if measured_profiles is not None:
+                self.profiles = Profiles.from_json(measured_profiles["profiles"])
+                self.log(f"profiles: {len(self.profiles.tasks)} tasks from {phase_dir / 'profiles.json'}")
+            if measured_comm is not None:
+                scale = float(measured_comm.get("duration_scale", 1.0))
+            elif setup.profile and setup.calibrate_overlap and cuda and setup.stop_after != "profile":
                 from ..communication.measure import measure_overlap
                 ov = measure_overlap(setup.device_index)
                 scale = min(1.3, max(1.0, ov.duration_scale))
@@ -301,7 +356,7 @@ class TrainingSession:
             if setup.profile:
                 dev = f"cuda:{setup.device_index}" if cuda else "cpu"
                 store = ident = None
-                if setup.store:
+                if setup.store and measured_profiles is None:
                     from ..store import ContentStore, kernel_library_digest
                     store = ContentStore(setup.store, setup.store_mode)
                     ident = {"device": torch.cuda.get_device_name(setup.device_index) if cuda else "cpu",
@@ -316,6 +371,8 @@ class TrainingSession:
                             if hit is not None:
                                 self.profiles.tasks[key] = TaskProfile(**hit)
                         missing -= set(self.profiles.tasks)
+                    if missing and measured_profiles is not None:
+                        raise KeyError(f"the profile phase did not measure {sorted(missing)[:3]}")
                     if missing:
                         got = measure_program(prog, desc, dev, keys=missing, rule=setup.optimizer_rule,
                                               fixed_len=setup.profile_sequence_tokens)
@@ -326,13 +383,17 @@ class TrainingSession:
                             for key, prof in got.tasks.items():
                                 store.put("task_profile", {**ident, "task": key}, _asdict(prof))
                     apply_profiles(prog, self.profiles, duration_scale=scale)
-                if cuda:
+                if cuda and measured_profiles is None and setup.stop_after != "profile":
                     if setup.allocator == "planned":
                         from ..runtime import allocator as _alloc
                         _alloc.installed().trim()
                     else:
                         torch.cuda.empty_cache()
             self.timings["profile"] = time.perf_counter() - t0
+            if setup.stop_after == "profile":      # with profiling off: an empty record, estimates stay
+                (phase_dir / "profiles.json").write_text(json.dumps(
+                    {"profiles": self.profiles.to_json(), "timings": self.timings}))
+                return
             if setup.profile and setup.store:
                 self.log(f"profile store: {store.hits} hits, {store.writes} new entries")
             # ---- host link calibration (done by every rank at once, see below)
@@ -356,7 +417,11 @@ class TrainingSession:
                 save_bundle(setup.bundle, identity, chosen, plan_json, extra_json,
                             self.profiles.to_json(), self.communication.to_json(), self.timings)
                 self.log(f"prepared bundle written to {setup.bundle}")
-        if world > 1:
+        if setup.stop_after == "plan":
+            if not setup.bundle:
+                raise ValueError("the plan phase writes its result into TrainingSetup.bundle")
+            return
+        if world > 1 and not solo:
             # one plan for the whole job: identical offsets on every rank are what makes the
             # device pool symmetric, and identical task order keeps collectives matched
             import torch.distributed as dist
@@ -471,6 +536,8 @@ class TrainingSession:
         return result, diag
 
     def close(self) -> None:
+        if self.executor is None:                 # a session stopped after a preparation phase
+            return
         self.executor.close()
         if self.setup.device == "cuda" and self.setup.allocator != "planned":
             torch.cuda.set_per_process_memory_fraction(1.0, self.setup.device_index)

@@ -97,3 +97,33 @@ def test_measure_plan_runs_a_prepared_bundle_without_preparing(tmp_path):
     assert "measured / simulated" in (out / "measurement.md").read_text()
     with pytest.raises(RuntimeError, match="does not match"):
         run(replace(_setup(path), device_gib=0.61), steps=1, warmup_steps=0)
+
+
+def test_preparation_as_four_fresh_processes(tmp_path):
+    """build, profile, communicate and plan each run as their own process and hand their results
+    on through files; the bundle they end in opens a session that trains exactly like one that
+    prepared in-process, and a second call finds every phase done."""
+    import json
+    from shadowspill_b200.training.phases import prepare_job, setup_from_json, setup_to_json
+    directory = tmp_path / "prep"
+    setup = replace(_setup(""), profile=True)          # profiling on the CPU: wall-clock task times
+    assert setup_from_json(json.loads(json.dumps(setup_to_json(setup), default=str))) == setup
+    bundle = prepare_job(setup, directory)
+    assert bundle.exists() and bundle.name == "training.ssp"
+    for name in ("build.json", "profiles.json", "communication.json", "job.json", "build.log", "plan.log"):
+        assert (directory / name).exists(), name
+    built = json.loads((directory / "build.json").read_text())
+    assert len(built["candidates"]) >= 1 and set(built["operations"]) == {"forward"}
+    profiles = json.loads((directory / "profiles.json").read_text())["profiles"]["tasks"]
+    assert profiles and all(p["seconds"] > 0 for p in profiles.values())
+    job = json.loads((directory / "job.json").read_text())["phases"]
+    assert [p["phase"] for p in job] == ["build", "profile", "communicate", "plan"]
+    assert all(p.get("pid_was_fresh") for p in job)
+    opened = TrainingSession(replace(setup, bundle=str(bundle)))
+    assert opened.prepared_from_bundle and set(opened.profiles.tasks) == set(profiles)
+    direct = TrainingSession(replace(setup, profile=False))
+    assert [t.name for t in opened.plan.program.tasks] == [t.name for t in direct.plan.program.tasks]
+    assert _losses(opened) == _losses(direct)
+    again = prepare_job(setup, directory)               # nothing to do: every result is there
+    assert again == bundle
+    assert all(p.get("skipped") for p in json.loads((directory / "job.json").read_text())["phases"])

@@ -500,3 +500,26 @@ def test_a_restarted_service_replays_its_journals(tmp_path):
             again.close()
     with Server(root, token="secret") as third:
         assert third.get_run(session, run).info()["state"] == "interrupted"      # stable across restarts
+
+
+def test_a_run_prepared_in_separate_processes(service):
+    """``Preparation(separate_processes=True)``: the service runs the four preparation phases as
+    fresh processes, the worker opens their bundle, and training proceeds as usual."""
+    with ServiceClient(service.url, token="secret") as svc:
+        tr = svc.create_training_client(
+            Model("llama3-tiny", dtype="float32"), Optimizer(lr=3e-3, parameter_rounding="nearest"),
+            batch=BatchConfig(tokens_per_step=512, microbatch_tokens=256),
+            memory=Memory(device_gib=0.53, spill_gib=0.25), resources=Resources(gpus=1, backend="cpu"),
+            preparation=Preparation(profiling=ProfilingOptions(enabled=False), calibrate=False,
+                                    separate_processes=True,
+                                    planning=PlanningOptions(minimum_object_bytes_evict_eligible=1024, workers=1)),
+            timeout=300).result()
+        try:
+            progress = " ".join(svc.get_progress(tr.run).result()["lines"])
+            assert "separate processes" in progress and "prepared bundle" in progress
+            losses = [tr.step(text_batch(_sequences(s))).result().loss for s in range(3)]
+            assert losses[-1] < losses[0] + 0.05
+        finally:
+            tr.close()
+    live = service.get_run(svc.session, tr.run)
+    assert (live.dir / "preparation" / "job.json").exists()
