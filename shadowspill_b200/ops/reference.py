@@ -161,6 +161,10 @@ def update_rule_(rule, p, g, m, v, *, lr, beta1, beta2, eps, weight_decay, step,
     momentum ``beta1``, no dampening; the decay is added to the step, not to the gradient).
     ``lion``: ``u = sign(beta1 m + (1 - beta1) g)``, ``p <- p - lr (u + wd p)``,
     ``m <- beta2 m + (1 - beta2) g`` (Chen et al. 2023). ``v`` is not used by either."""
+    if hasattr(rule, "apply"):
+        # the update of a torch.optim optimizer captured as a graph (frontend/optimizer_capture.py);
+        # its own hyperparameters are constants of that graph, the learning rate follows the run
+        return rule.apply(p, g, m, v, lr=lr, step=step, grad_scale=grad_scale)
     if rule == "adamw":
         return adamw_(p, g, m, v, lr=lr, beta1=beta1, beta2=beta2, eps=eps, weight_decay=weight_decay,
                       step=step, grad_scale=grad_scale)

@@ -42,6 +42,9 @@ RESULT = {"build": "build.json", "profile": "profiles.json", "communicate": "com
 
 
 def setup_to_json(setup) -> dict:
+    if hasattr(setup.optimizer_rule, "apply"):
+        raise ValueError("a captured optimizer is a graph in this process; separate preparation processes "
+                         "take the named rules (adamw, sgd, lion)")
     d = asdict(setup)
     d["model"] = setup.model if isinstance(setup.model, str) else setup.model.to_json()
     return d

@@ -27,6 +27,10 @@ FILE_NAME = "training.ssp"
 def setup_identity(setup, cfg: DecoderConfig) -> str:
     """Digest of every setting that changes the programs or their plans (which process runs
     which preparation phase is not one of them)."""
+    if hasattr(setup, "__dataclass_fields__") and hasattr(getattr(setup, "optimizer_rule", None), "apply"):
+        from dataclasses import replace
+        rule = setup.optimizer_rule        # a captured optimizer: its name and constants identify it
+        setup = replace(setup, optimizer_rule=f"{rule}:{sorted(rule.defaults.items())}")
     s = asdict(setup) if hasattr(setup, "__dataclass_fields__") else dict(setup)
     keep = {k: s[k] for k in ("device_gib", "spill_gib", "tokens_per_step", "microbatch_tokens", "slots",
                               "mean_seqlen", "dtype", "world_size", "walks", "recompute_shares",

@@ -50,7 +50,9 @@ class TrainingSetup:
     beta2: float = 0.95
     eps: float = 1e-8
     weight_decay: float = 0.0
-    optimizer_rule: str = "adamw"         # adamw | sgd (momentum beta1) | lion
+    # adamw | sgd (momentum beta1) | lion, or the captured update of any elementwise
+    # torch.optim optimizer (frontend/optimizer_capture.py: capture_optimizer_update)
+    optimizer_rule: object = "adamw"
     seed: int = 0
     dtype: str = "bfloat16"
     stochastic_rounding: bool = True
@@ -459,7 +461,7 @@ class TrainingSession:
                       [p.summary.workspace_bytes for p, _ in self.extra_plans.values()]) + (256 << 20)
             torch.cuda.set_per_process_memory_fraction(min(1.0, cap / total), setup.device_index)
         from ..ops.reference import RULES
-        if setup.optimizer_rule not in RULES:
+        if setup.optimizer_rule not in RULES and not hasattr(setup.optimizer_rule, "apply"):
             raise ValueError(f"unknown optimizer rule {setup.optimizer_rule!r}; known: {RULES}")
         hyper = Hyperparameters(setup.lr, setup.beta1, setup.beta2, setup.eps, setup.weight_decay,
                                 rule=setup.optimizer_rule)
