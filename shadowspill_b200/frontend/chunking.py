@@ -212,7 +212,7 @@ def chunk_graph(gm: fx.GraphModule, T: int, chunk_rows: int,
                 env[m] = g.call_function(torch.ops.aten.cat.default, (chunk_vals[m], 0))
                 env[m].meta = dict(m.meta)
         done += 1
-    writers = _WRITERS + (gp.head_loss_into,)
+    writers = _WRITERS + (gp.head_loss_into, gp.moe_experts_bwd_into)
     g.eliminate_dead_code(is_impure_node=lambda n: n.op in ("placeholder", "output") or n.target in writers)
     g.lint()
     return fx.GraphModule(torch.nn.Module(), g), done

@@ -332,6 +332,13 @@ def head_loss_into(dst: torch.Tensor | None, h, W, targets, weights, block_rows:
     return ss_ops.head_loss_run(h.contiguous(), W, targets, weights, block_rows, dst, not first)
 
 
+def moe_experts_bwd_into(dst13: torch.Tensor, dst2: torch.Tensor, h, logits, w13, w2, gy, k: int, renorm: bool,
+                         first: bool):
+    """``ss::moe_experts_bwd`` with both bank gradients created in or added to their destinations
+    by the grouped weight-gradient GEMMs; returns ``(dh, dlogits)``."""
+    return ss_ops.moe_bwd_run(h, logits, w13, w2, gy, k, renorm, dst13, dst2, first)
+
+
 def _strip_cast(node: fx.Node) -> fx.Node:
     """Looks through the dtype cast autograd appends to a gradient (fp32 -> parameter dtype)."""
     if node.op == "call_function" and op_name(node) == "aten._to_copy.default" and len(node.users) == 1:
@@ -400,6 +407,35 @@ def rewrite_destinations(bwd: fx.GraphModule, param_grads: dict[int, str], dest_
             continue
         outs[i] = new if new is not None else d
         done.add(name)
+    # routed experts: one call produces both bank gradients; rewrite when both are destinations
+    for call in [n for n in g.nodes if n.op == "call_function" and op_name(n) == "ss.moe_experts_bwd"]:
+        items = {u.args[1]: u for u in call.users if u.target is operator.getitem}
+        slots = {}
+        for i, name in param_grads.items():
+            v = outs[i]
+            if isinstance(v, fx.Node) and name not in done:
+                src = _strip_cast(v)
+                for which in (2, 3):
+                    if items.get(which) is src and (src is v or len(src.users) == 1):
+                        slots[which] = (i, name)
+        if set(slots) != {2, 3}:
+            continue
+        (i13, n13), (i2, n2) = slots[2], slots[3]
+        d13, f = dest(n13)
+        d2, _ = dest(n2)
+        d13.meta["val"], d2.meta["val"] = items[2].meta.get("val"), items[3].meta.get("val")
+        with g.inserting_before(call):
+            new = g.call_function(moe_experts_bwd_into, (d13, d2, *call.args, f))
+            dh = g.call_function(operator.getitem, (new, 0))
+            dl = g.call_function(operator.getitem, (new, 1))
+        dh.meta["val"] = items[0].meta.get("val") if 0 in items else None
+        dl.meta["val"] = items[1].meta.get("val") if 1 in items else None
+        if 0 in items:
+            items[0].replace_all_uses_with(dh)
+        if 1 in items:
+            items[1].replace_all_uses_with(dl)
+        outs[i13], outs[i2] = d13, d2
+        done.update((n13, n2))
     out_node.args = (tuple(outs),)
     g.eliminate_dead_code()
     bwd.recompile()

