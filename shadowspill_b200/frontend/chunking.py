@@ -24,6 +24,7 @@ import operator
 import torch
 from torch import fx
 
+from . import fusion
 from . import graph_pairs as gp
 from .export import op_name
 
@@ -62,6 +63,10 @@ def classify(node: fx.Node, T: int) -> tuple[str, tuple[int, ...]]:
 
     def lead(*pos):
         return all(isinstance(a[i], fx.Node) and _leading(a[i], T) for i in pos)
+    if t is fusion.rope_in_place:
+        return (ROWS, (0, 1)) if (lead(0, 1) and _leading(node, T)) else none
+    if t is fusion.add_rmsnorm:
+        return (ROWS, (0, 1)) if lead(0, 1) else none      # (sum, y, rstd): all with the rows of the operands
     if t is gp.gemm_into:
         return (REDUCE, (1, 2)) if (a[3] and a[4] and lead(1, 2)) else none
     if t is gp.rmsnorm_bwd_into:

@@ -25,6 +25,7 @@ the min-cut ``partition_function``), pytorch/capture/gradients/destinations.py.
 from __future__ import annotations
 
 import operator
+import os
 from dataclasses import dataclass, field
 
 import torch
@@ -468,6 +469,10 @@ def build_stage_pairs(stage: StageGraph, trainable: list[bool], policies=DEFAULT
             else:
                 grad_outputs.append("x" if nm == "x" else None)
         in_place = rewrite_destinations(bwd, param_grads, grad_dtypes or {})
+        if os.environ.get("SS_GRAPH_FUSION", "1") != "0":
+            from .fusion import fuse_graph
+            fuse_graph(fwd)
+            fuse_graph(bwd)
         b_inputs = [str(n.target) for n in bwd.graph.nodes if n.op == "placeholder"]
         pairs[pol.name] = GraphPair(pol.name, fwd, bwd, saved, b_inputs, grad_outputs, in_place)
     flops, inter = 0.0, 0

@@ -187,6 +187,26 @@ def test_routed_expert_layers_get_save_variants_and_in_place_bank_gradients():
     assert sum(op_name(n) == "ss.moe_experts" for n in cut[1].pairs.pairs["recompute"].forward.graph.nodes) == 1
 
 
+def test_fused_forms_replace_copies_adds_and_zero_filled_slice_gradients():
+    """The layer graphs run rotary in place on the fresh projection output, fold the residual add
+    into the norm kernel, and build the gradient of the fused q/k/v projection by one concatenation
+    instead of three zero-filled full-width tensors added together."""
+    from shadowspill_b200.frontend import fusion
+    from shadowspill_b200.frontend.graph_stage import build_graph_stages
+    layer = build_graph_stages(preset("llama3-tiny"), 256, 16, torch.float32)[1]
+    pair = layer.pairs.pairs["recompute"]
+    fwd = [n.target for n in pair.forward.graph.nodes if n.op == "call_function"]
+    bwd = [n for n in pair.backward.graph.nodes if n.op == "call_function"]
+    assert fusion.rope_in_place in fwd and fusion.add_rmsnorm in fwd
+    assert not any(op_name(n) == "ss.rope" for n in pair.forward.graph.nodes)
+    assert not any(op_name(n) == "aten.slice_backward.default" for n in bwd)
+    assert sum(op_name(n) == "aten.cat.default" for n in bwd) == 1
+    assert sum(n.target is fusion.rope_in_place for n in bwd) == 2        # recomputed forward + its gradient
+    # the first norm reads the stage input, which is never written: it stays a plain norm
+    first_norm = next(n for n in pair.forward.graph.nodes if n.op == "call_function")
+    assert op_name(first_norm) == "ss.rmsnorm" and first_norm.args[0].op == "placeholder"
+
+
 def test_axis_chunks_shrink_the_live_intermediates_of_a_wide_layer():
     """With an MLP eight times wider than the model, the live intermediates of the chunked
     backward graph (counted from the traced shapes) are a fraction of the whole graph's."""
