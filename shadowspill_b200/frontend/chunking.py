@@ -228,10 +228,14 @@ def chunk_pairs(pairs: gp.StagePairs, T: int, chunk_rows: int) -> int:
     total = 0
     params = set(pairs.placeholders[:len(pairs.trainable)])
     whole = params | {"grad_" + p for p in params} | {"first"}
+    done: dict[int, tuple] = {}                 # variants that keep the same set share their graphs
     for pair in pairs.pairs.values():
-        pair.forward, a = chunk_graph(pair.forward, T, chunk_rows, whole)
-        pair.backward, b = chunk_graph(pair.backward, T, chunk_rows, whole)
-        total += a + b
+        for side in ("forward", "backward"):
+            gm = getattr(pair, side)
+            if id(gm) not in done:
+                done[id(gm)] = chunk_graph(gm, T, chunk_rows, whole)
+                total += done[id(gm)][1]
+            setattr(pair, side, done[id(gm)][0])
     return total
 
 

@@ -456,7 +456,12 @@ def build_stage_pairs(stage: StageGraph, trainable: list[bool], policies=DEFAULT
         retained = choose_retained(joint, n_primals, 1, pol)
         sig = tuple(v.name for v in retained)
         if sig in seen_sets and pol.mode == "rules":
-            continue                      # the rules select nothing new for this stage kind
+            # the rules select nothing new for this stage kind: the name stays usable in a
+            # selection and means the pair that already keeps exactly this set
+            first = pairs[seen_sets[sig]]
+            pairs[pol.name] = GraphPair(pol.name, first.forward, first.backward, first.saved,
+                                        first.backward_inputs, first.grad_outputs, first.in_place)
+            continue
         seen_sets[sig] = pol.name
         fwd, bwd, saved, b_inputs = split_joint(joint, n_primals, 1, retained, names)
         grad_outputs: list[str | None] = []

@@ -514,7 +514,7 @@ def _moe_torch(h: Tensor, logits: Tensor, w13: Tensor, w2: Tensor, k: int, renor
 
 @custom_op("ss::moe_experts", mutates_args=())
 def moe_experts(h: Tensor, logits: Tensor, w13: Tensor, w2: Tensor, k: int, renorm: bool) -> Tensor:
-    if h.is_cuda and F._cuda():
+    if h.is_cuda and F._cuda(h):
         from ..ops import moe as moe_ops
         with torch.no_grad():
             return moe_ops.experts(_c(h), _c(logits), w13, w2, k, renorm, None)
@@ -536,7 +536,7 @@ def moe_bwd_run(h: Tensor, logits: Tensor, w13: Tensor, w2: Tensor, gy: Tensor, 
         dst13, dst2 = torch.zeros_like(w13), torch.zeros_like(w2)
     elif first:
         dst13.zero_(); dst2.zero_()                      # experts without rows still get a defined gradient
-    if h.is_cuda and F._cuda():
+    if h.is_cuda and F._cuda(h):
         from ..models.autograd_ops import GradSink
         from ..ops import moe as moe_ops
         sink = GradSink({"w13": dst13, "w2": dst2}, False)
