@@ -199,3 +199,34 @@ def fuse_graph(gm: fx.GraphModule) -> dict[str, int]:
         g.lint()
         gm.recompile()
     return counts
+
+
+# ------------------------------------------------------------------------ lowering for execution
+def lower_for_execution(gm: fx.GraphModule) -> fx.GraphModule:
+    """A copy of ``gm`` whose ``ss::`` operator calls go straight to the Python functions behind
+    them. The operators exist so that export, AOTAutograd and the rewrites above can see and
+    differentiate them; a finished graph runs under ``no_grad`` and is never traced again, so the
+    dispatcher round trip per call (tens of microseconds, thousands of calls per step) is only
+    host time that the step has to hide."""
+    from . import ops as ss_ops
+    raw = {}
+    for name in dir(ss_ops):
+        obj = getattr(ss_ops, name)
+        init = getattr(obj, "_init_fn", None)
+        opname = getattr(obj, "_qualname", "") or getattr(obj, "_name", "")
+        if init is not None and str(opname).startswith("ss::"):
+            raw[str(opname)[4:]] = init
+    g = fx.Graph()
+    env: dict[fx.Node, fx.Node] = {}
+    swapped = 0
+    for n in gm.graph.nodes:
+        new = g.node_copy(n, lambda a: env[a])
+        if n.op == "call_function" and isinstance(n.target, torch._ops.OpOverload) and n.target.namespace == "ss":
+            fn = raw.get(n.target._schema.name.split("::")[1])
+            if fn is not None:
+                new.target = fn
+                swapped += 1
+        env[n] = new
+    out = fx.GraphModule(gm, g)
+    out.ss_lowered_calls = swapped
+    return out

@@ -13,6 +13,8 @@ partition -> graph pairs -> lowering).
 """
 from __future__ import annotations
 
+import os
+
 import operator
 import threading
 
@@ -102,7 +104,7 @@ class GraphStage(Stage):
         variant = self._by_keep.get(tuple(keep), "recompute")
         pair = self.pairs.pairs[variant]
         with torch.no_grad():
-            res = pair.forward(*self._inputs(P, x, meta, self.pairs.placeholders))
+            res = _runnable(pair, "forward")(*self._inputs(P, x, meta, self.pairs.placeholders))
         y, kept = res[0], res[1:]
         if out is not None:
             out.copy_(y)
@@ -128,7 +130,7 @@ class GraphStage(Stage):
             elif nm.startswith("grad_"):
                 extra[nm] = G[nm[5:]]
         with torch.no_grad():
-            grads = pair.backward(*self._inputs(P, x, meta, pair.backward_inputs, extra))
+            grads = _runnable(pair, "backward")(*self._inputs(P, x, meta, pair.backward_inputs, extra))
         dx = None
         for target, g in zip(pair.grad_outputs, grads):
             if target is None or g is None:
@@ -144,6 +146,17 @@ class GraphStage(Stage):
         if dx is not None:
             dy.copy_(dx)
         return dy
+
+
+def _runnable(owner, attr: str) -> fx.GraphModule:
+    """The execution form of a graph held in ``owner.<attr>`` (made once, kept beside it)."""
+    cached = getattr(owner, "_exec_" + attr, None)
+    gm = getattr(owner, attr)
+    if cached is None or cached[0] is not gm:
+        from .fusion import lower_for_execution
+        cached = (gm, lower_for_execution(gm) if os.environ.get("SS_GRAPH_LOWER", "1") != "0" else gm)
+        setattr(owner, "_exec_" + attr, cached)
+    return cached[1]
 
 
 def _saved_index(name: str) -> int:
@@ -170,7 +183,7 @@ class GraphEmbeddingStage(GraphStage):
             if nm.startswith("grad_"):
                 extra[nm] = G[nm[5:]]
         with torch.no_grad():
-            grads = pair.backward(*self._inputs(P or {}, None, meta, pair.backward_inputs, extra))
+            grads = _runnable(pair, "backward")(*self._inputs(P or {}, None, meta, pair.backward_inputs, extra))
         for target, g in zip(pair.grad_outputs, grads):
             if target and target != "x" and target not in pair.in_place and g is not None:
                 (G[target].copy_ if first else G[target].add_)(g.reshape(G[target].shape))
@@ -192,7 +205,7 @@ class GraphHeadStage(GraphStage):
     def _train_graph(self):
         if self._train is None:
             self._train, self._train_inputs, self._train_grads = _head_training_graph(self.pairs, self.graph)
-        return self._train
+        return _runnable(self, "_train")
 
     def loss_and_backward(self, P, G, x, meta: BatchMeta, loss_sum, first: bool, dx=None, train: bool = True,
                           grad_scale: float = 1.0, tied: dict | None = None):
@@ -206,7 +219,8 @@ class GraphHeadStage(GraphStage):
                 first_of[local] = bool(tied.get("first", False))
         if not train:
             with torch.no_grad():
-                loss = self.pairs.pairs["recompute"].forward(*self._inputs(P, x, meta, self.pairs.placeholders))[0]
+                loss = _runnable(self.pairs.pairs["recompute"], "forward")(
+                    *self._inputs(P, x, meta, self.pairs.placeholders))[0]
             loss_sum.add_(loss.reshape(loss_sum.shape))
             return None
         gm = self._train_graph()
