@@ -71,7 +71,8 @@ def main():
             # result may follow either bf16 neighbour of the exact sum
             near = g_sum.bfloat16().float()
             step_ = ulp_bf16(near)
-            sums = [near, near - step_, near + step_]
+            # at a power of two the neighbour towards zero is half a step away
+            sums = [near, near - step_, near + step_, near - step_ / 2, near + step_ / 2]
             g_sum = near
 
         def ref_for(gs):
