@@ -136,7 +136,7 @@ def main() -> None:
                     help="graph frontend: run the token-local operators of a layer in row chunks of this size")
     ap.add_argument("--fixed-len", type=int, default=0,
                     help="sequences of exactly this many tokens (= --microbatch: one long sequence per microbatch)")
-    ap.add_argument("--frontend", default="stages", choices=["stages", "graph"],
+    ap.add_argument("--frontend", default="graph", choices=["stages", "graph"],
                     help="graph = torch.export -> partition -> AOT graph pairs; stages = hand-written stage classes")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -220,6 +220,9 @@ def lower_for_execution(gm: fx.GraphModule) -> fx.GraphModule:
     env: dict[fx.Node, fx.Node] = {}
     swapped = 0
     for n in gm.graph.nodes:
+        if n.op == "call_function" and op_name(n) in ("aten.detach.default", "aten.alias.default"):
+            env[n] = env[n.args[0]]              # nothing records a graph at execution: a no-op call
+            continue
         new = g.node_copy(n, lambda a: env[a])
         if n.op == "call_function" and isinstance(n.target, torch._ops.OpOverload) and n.target.namespace == "ss":
             fn = raw.get(n.target._schema.name.split("::")[1])

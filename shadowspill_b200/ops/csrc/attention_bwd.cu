@@ -489,17 +489,23 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const float c2 = p.scale * LOG2E;
     bool ok = true;
+    // log-sum-exp and delta of the tile's queries: threads 0..2*BQ-1 fetch one value each, one
+    // iteration ahead, so that the global-memory latency is not on the path of every tile
+    auto fetch_row_stat = [&](int it) -> float {
+      if (threadIdx.x >= 2 * BQ || it >= n_it) return 0.f;
+      const int head_i = kv_head * rep + it / n_q;
+      const int col = threadIdx.x & (BQ - 1);
+      const long long li = static_cast<long long>(head_i) * p.T + min(k0 + (it % n_q) * BQ + col, p.T - 1);
+      return threadIdx.x < BQ ? p.lse[li] * LOG2E : p.delta[li];
+    };
+    float row_stat = fetch_row_stat(0);
     for (int it = 0; it < n_it; ++it) {
       const int b = it & 1;
       const int head = kv_head * rep + it / n_q;
       const int qt0 = k0 + (it % n_q) * BQ;
       float* sl = s_lse + b * (2 * BQ);
-      {
-        const int col = threadIdx.x & (BQ - 1);
-        const long long li = static_cast<long long>(head) * p.T + min(qt0 + col, p.T - 1);
-        if (threadIdx.x < BQ) sl[col] = p.lse[li] * LOG2E;
-        else if (threadIdx.x < 2 * BQ) sl[BQ + col] = p.delta[li];
-      }
+      if (threadIdx.x < 2 * BQ) sl[threadIdx.x] = row_stat;     // [0,BQ): lse, [BQ,2BQ): delta
+      row_stat = fetch_row_stat(it + 1);
       named_barrier_softmax();
       if (!mbar_wait(&sp_full[b], (it >> 1) & 1, p.status, KS_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       // the P^T / dS^T buffers of this parity were last read by the MMAs of iteration it-2

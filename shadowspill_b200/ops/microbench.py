@@ -112,6 +112,23 @@ def bench_attention(a) -> list[dict]:
     s = timed(lambda: attention.backward(q, k, v, o, lse, do, cu, L, dq=dq, dk=dk, dv=dv),
               a.iters, a.warmup)
     out.append(report(f"attn_bwd_T{T}_L{L}_H{Hq}/{Hkv}_d{dh}", s, 2.5 * fl))
+    if a.compare:
+        # the library arm at the same shape (flash-attn's kernels through the same entry points)
+        import os
+        before = os.environ.get("SS_ATTENTION")
+        os.environ["SS_ATTENTION"] = "library"
+        try:
+            s = timed(lambda: attention.forward(q, k, v, cu, L), a.iters, a.warmup)
+            out.append(report(f"library_attn_fwd_T{T}_L{L}_H{Hq}/{Hkv}_d{dh}", s, fl))
+            o2, lse2 = attention.forward(q, k, v, cu, L)
+            s = timed(lambda: attention.backward(q, k, v, o2, lse2, do, cu, L, dq=dq, dk=dk, dv=dv),
+                      a.iters, a.warmup)
+            out.append(report(f"library_attn_bwd_T{T}_L{L}_H{Hq}/{Hkv}_d{dh}", s, 2.5 * fl))
+        finally:
+            if before is None:
+                os.environ.pop("SS_ATTENTION", None)
+            else:
+                os.environ["SS_ATTENTION"] = before
     return out
 
 
