@@ -245,80 +245,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const float dl = p.delta[li];
     const float c2 = p.scale * LOG2E;
     bool ok = true;
-    if (BKV == 64) {
-      // Each warp owns one 32-column half of every 128x64 score tile. The TMEM reads of tile j+1 are
-      // issued into a second register set before tile j is processed, so their latency (several
-      // hundred cycles with eight warps reading) runs under the exponentials instead of in front
-      // of them; the TMEM buffer is handed back to the MMA warp as soon as its values are in
-      // registers.
-      uint32_t sa[32], da[32], sb[32], db[32];
-      const uint32_t col = static_cast<uint32_t>(hsel * 32);
-      auto issue = [&](int j, uint32_t (&s)[32], uint32_t (&d)[32]) {
-        const uint32_t bb = static_cast<uint32_t>(j & 1) * BKV;
-        tc_fence_after();
-        tmem_ld_32x32(lane_addr + Cfg::TM_S + bb + col, s);
-        tmem_ld_32x32(lane_addr + Cfg::TM_DP + bb + col, d);
-      };
-      auto tile = [&](int j, uint32_t (&s)[32], uint32_t (&d)[32], uint32_t (&sn)[32], uint32_t (&dn)[32],
-                      bool& next_issued) -> bool {
-        const int b = j & 1;
-        uint8_t* sds = smem + Cfg::OFF_DS + b * Cfg::DS_BYTES;
-        tmem_ld_wait();                                   // tile j is in s, d
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sdp_free[b]);        // S / dP of tile j may be overwritten
-        bool early = false;
-        if (j + 1 < n_kv && mbar_try_wait(&sdp_full[(j + 1) & 1], ((j + 1) >> 1) & 1)) {
-          issue(j + 1, sn, dn);                           // in flight during the arithmetic below
-          early = true;
-        }
-        const int k0 = seq_start + j * BKV;
-        const bool below_diagonal = k0 + BKV - 1 <= q0;
-        uint32_t pk[16];
-        if (below_diagonal) {
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(s[e]), c2, -lse2));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(s[e + 1]), c2, -lse2));
-            pk[e >> 1] = pack_bf16(p0 * (__uint_as_float(d[e]) - dl), p1 * (__uint_as_float(d[e + 1]) - dl));
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            float v[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const int gk = k0 + static_cast<int>(col) + e + u;
-              const float pr = (gk > gq) ? 0.f : fast_exp2(fmaf(__uint_as_float(s[e + u]), c2, -lse2));
-              v[u] = pr * (__uint_as_float(d[e + u]) - dl);
-            }
-            pk[e >> 1] = pack_bf16(v[0], v[1]);
-          }
-        }
-        // this dS buffer was last read by the dQ MMAs of tile j-2
-        if (j > 1 && !mbar_wait(&dq_done[b], ((j >> 1) - 1) & 1, p.status, KS_TIMEOUT_TMEM_FULL)) return false;
-        store_swizzled_32(sds, 128 * 128, row, static_cast<int>(col), pk);
-        fence_async_proxy();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&ds_full[b]);
-        if (j + 1 < n_kv && !early) {
-          if (!mbar_wait(&sdp_full[(j + 1) & 1], ((j + 1) >> 1) & 1, p.status, KS_TIMEOUT_TMEM_FULL)) return false;
-          issue(j + 1, sn, dn);
-        }
-        next_issued = j + 1 < n_kv;
-        return true;
-      };
-      if (n_kv > 0) {
-        ok = mbar_wait(&sdp_full[0], 0, p.status, KS_TIMEOUT_TMEM_FULL);
-        if (ok) issue(0, sa, da);
-        bool pending = ok;
-        for (int j = 0; j < n_kv && ok; j += 2) {
-          ok = tile(j, sa, da, sb, db, pending);
-          if (ok && j + 1 < n_kv) ok = tile(j + 1, sb, db, sa, da, pending);
-        }
-        if (!ok && pending) tmem_ld_wait();               // nothing of ours stays in flight
-      }
-    } else
     for (int j = 0; j < n_kv; ++j) {
       const int b = j & 1;
       uint8_t* sds = smem + Cfg::OFF_DS + b * Cfg::DS_BYTES;
@@ -587,53 +513,41 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tc_fence_after();
 #pragma unroll 1
       for (int c = hsel; c < BQ / 32; c += 2) {
-        // two halves of sixteen columns: the TMEM reads of the second are in flight while the
-        // first is turned into P^T / dS^T
-        uint32_t s0[16], d0[16], s1[16], d1[16];
-        const uint32_t ts = lane_addr + Cfg::TM_ST + b * BQ + c * 32;
-        const uint32_t td = lane_addr + Cfg::TM_DPT + b * BQ + c * 32;
-        tmem_ld_32x16(ts, s0);
-        if (Cfg::NEED_DP) tmem_ld_32x16(td, d0);
+        uint32_t s[32], d[32];
+        tmem_ld_32x32(lane_addr + Cfg::TM_ST + b * BQ + c * 32, s);
+        if (Cfg::NEED_DP) tmem_ld_32x32(lane_addr + Cfg::TM_DPT + b * BQ + c * 32, d);
         tmem_ld_wait();
-        tmem_ld_32x16(ts + 16, s1);
-        if (Cfg::NEED_DP) tmem_ld_32x16(td + 16, d1);
         uint32_t pkp[16], pkd[16];
         // whole tile visible: every query of the tile is at or after every key, none past the end
         const bool all_valid = (qt0 >= k0 + 127) && (qt0 + BQ <= seq_end);
-        auto half = [&](const uint32_t (&s)[16], const uint32_t (&d)[16], int e0) {
-          if (all_valid) {
+        if (all_valid) {
 #pragma unroll
-            for (int e = 0; e < 16; e += 2) {
-              const int col = c * 32 + e0 + e;
-              const float p0 = fast_exp2(fmaf(__uint_as_float(s[e]), c2, -sl[col]));
-              const float p1 = fast_exp2(fmaf(__uint_as_float(s[e + 1]), c2, -sl[col + 1]));
-              pkp[(e0 + e) >> 1] = pack_bf16(p0, p1);
-              pkd[(e0 + e) >> 1] = Cfg::NEED_DP
-                  ? pack_bf16(p0 * (__uint_as_float(d[e]) - sl[BQ + col]),
-                              p1 * (__uint_as_float(d[e + 1]) - sl[BQ + col + 1]))
-                  : 0u;
-            }
-          } else {
-#pragma unroll
-            for (int e = 0; e < 16; e += 2) {
-              float pv[2], dv[2];
-#pragma unroll
-              for (int u = 0; u < 2; ++u) {
-                const int col = c * 32 + e0 + e + u;
-                const int gqc = qt0 + col;
-                const bool valid = (gqc < seq_end) && (gk <= gqc);
-                const float pr = valid ? fast_exp2(fmaf(__uint_as_float(s[e + u]), c2, -sl[col])) : 0.f;
-                pv[u] = pr;
-                dv[u] = Cfg::NEED_DP ? pr * (__uint_as_float(d[e + u]) - sl[BQ + col]) : 0.f;   // dK scaled once at the end
-              }
-              pkp[(e0 + e) >> 1] = pack_bf16(pv[0], pv[1]);
-              pkd[(e0 + e) >> 1] = pack_bf16(dv[0], dv[1]);
-            }
+          for (int e = 0; e < 32; e += 2) {
+            const int col = c * 32 + e;
+            const float p0 = fast_exp2(fmaf(__uint_as_float(s[e]), c2, -sl[col]));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(s[e + 1]), c2, -sl[col + 1]));
+            pkp[e >> 1] = pack_bf16(p0, p1);
+            pkd[e >> 1] = Cfg::NEED_DP
+                ? pack_bf16(p0 * (__uint_as_float(d[e]) - sl[BQ + col]),
+                            p1 * (__uint_as_float(d[e + 1]) - sl[BQ + col + 1]))
+                : 0u;
           }
-        };
-        half(s0, d0, 0);
-        tmem_ld_wait();
-        half(s1, d1, 16);
+        } else
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float pv[2], dv[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int col = c * 32 + e + u;
+            const int gqc = qt0 + col;
+            const bool valid = (gqc < seq_end) && (gk <= gqc);
+            const float pr = valid ? fast_exp2(fmaf(__uint_as_float(s[e + u]), c2, -sl[col])) : 0.f;
+            pv[u] = pr;
+            dv[u] = Cfg::NEED_DP ? pr * (__uint_as_float(d[e + u]) - sl[BQ + col]) : 0.f;   // dK scaled once at the end
+          }
+          pkp[e >> 1] = pack_bf16(pv[0], pv[1]);
+          pkd[e >> 1] = pack_bf16(dv[0], dv[1]);
+        }
         if (Cfg::DO_DV) store_swizzled_32(smem + Cfg::OFF_PT + b * Cfg::PT_BYTES, 128 * 128, row, c * 32, pkp);
         if (Cfg::DO_DK) store_swizzled_32(smem + Cfg::OFF_DST + b * Cfg::PT_BYTES, 128 * 128, row, c * 32, pkd);
       }
