@@ -185,7 +185,9 @@ class TaskRunner:
             saved = dict(B["saved"]) if "saved" in B else {}
             if "attn" in saved:
                 saved["attn"] = saved["attn"]
-            st.backward(B.get("params"), B.get("grads") or {}, B.get("x"), B["dx"], meta, saved, first)
+            from ..ops import delta_rule
+            with delta_rule.keeping_intermediates():     # a recomputed forward feeds its own backward
+                st.backward(B.get("params"), B.get("grads") or {}, B.get("x"), B["dx"], meta, saved, first)
         elif t.kind == "optimizer":
             if t.variant == "adamw_dp":
                 self._optimizer_sharded(t.stage, B)

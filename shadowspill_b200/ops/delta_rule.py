@@ -70,6 +70,28 @@ class _Buffers:
             self.dgc = torch.empty((n, H), **f32)
 
 
+# A backward task that recomputes its forward pass runs the rule's forward twice on the same
+# operands: once for the layer's output, once inside the rule's own backward, which needs the
+# chunk intermediates. Inside ``keeping_intermediates()`` the first run keeps them and the second
+# is skipped. The scope is one task, so nothing outlives it and a pointer reused by other data in
+# a later task can never match.
+_scope = {"on": False, "key": None, "value": None}
+
+
+class keeping_intermediates:
+    def __enter__(self):
+        _scope.update(on=True, key=None, value=None)
+        return self
+
+    def __exit__(self, *exc):
+        _scope.update(on=False, key=None, value=None)
+        return False
+
+
+def _operand_key(q, k, v, beta, g, cu_seqlens):
+    return tuple((t.data_ptr(), t._version, tuple(t.shape)) for t in (q, k, v, beta, g, cu_seqlens))
+
+
 def _forward(q, k, v, beta, g, cu_seqlens, backward: bool):
     T, Hk, _ = q.shape
     H = v.shape[1]
@@ -90,6 +112,18 @@ def _forward(q, k, v, beta, g, cu_seqlens, backward: bool):
     return out, B, geo
 
 
+def forward_keeping(q, k, v, beta, g, cu_seqlens, raw_key=None):
+    """The forward pass on prepared operands; inside ``keeping_intermediates()`` with its saves on,
+    kept for a backward pass in the same scope that names the same operands, either as the caller
+    passed them (``raw_key``) or prepared."""
+    if not _scope["on"]:
+        return _forward(q, k, v, beta, g, cu_seqlens, backward=False)[0]
+    out, B, geo = _forward(q, k, v, beta, g, cu_seqlens, backward=True)
+    _scope["key"] = {raw_key, _operand_key(q, k, v, beta, g, cu_seqlens)}
+    _scope["value"] = (B, geo, (q, k, v, beta, g))
+    return out
+
+
 def _operands(q, k, v, beta, g):
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     return q, k, v, beta.float().contiguous(), g.float().contiguous()
@@ -98,8 +132,9 @@ def _operands(q, k, v, beta, g):
 class _GatedDeltaRule(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, beta, g, cu_seqlens):
+        raw = _operand_key(q, k, v, beta, g, cu_seqlens)
         q, k, v, bf, gf = _operands(q, k, v, beta, g)
-        out, _, _ = _forward(q, k, v, bf, gf, cu_seqlens, backward=False)
+        out = forward_keeping(q, k, v, bf, gf, cu_seqlens, raw)
         ctx.save_for_backward(q, k, v, bf, gf, cu_seqlens)
         ctx.scalar_dtypes = (beta.dtype, g.dtype)
         return out
@@ -114,9 +149,13 @@ class _GatedDeltaRule(torch.autograd.Function):
 def backward(q, k, v, beta, g, cu_seqlens, dout):
     """Gradients of :func:`gated_delta_rule` for ``dout`` [T,H,128] (bf16): ``(dq, dk, dv, dbeta,
     dg)`` with dbeta, dg in fp32. The forward pass is recomputed with its saves switched on."""
-    q, k, v, beta, g = _operands(q, k, v, beta, g)
     dout = dout.to(torch.bfloat16).contiguous()
-    _, B, geo = _forward(q, k, v, beta, g, cu_seqlens, backward=True)
+    if _scope["on"] and _scope["key"] and _operand_key(q, k, v, beta, g, cu_seqlens) in _scope["key"]:
+        B, geo, (q, k, v, beta, g) = _scope["value"]     # the forward pass of this task kept them
+        _scope["key"] = _scope["value"] = None
+    else:
+        q, k, v, beta, g = _operands(q, k, v, beta, g)
+        _, B, geo = _forward(q, k, v, beta, g, cu_seqlens, backward=True)
     T, H, Hk = geo.T, geo.H, geo.Hk
     L, st, status = _lib.lib(), _lib.stream_ptr(), _lib.status_word(q.device).data_ptr()
     _lib.check(L.ss_dn_bwd_state(dout.data_ptr(), B.MQ.data_ptr(), B.KD.data_ptr(), B.QG.data_ptr(),
