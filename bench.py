@@ -134,6 +134,8 @@ def main() -> None:
                          "device pool under a checked contract; caching = torch's allocator under a cap")
     ap.add_argument("--axis-chunk-rows", type=int, default=0,
                     help="graph frontend: run the token-local operators of a layer in row chunks of this size")
+    ap.add_argument("--delta-head-groups", type=int, default=1,
+                    help="gated delta rule: run each call in this many groups of key heads")
     ap.add_argument("--fixed-len", type=int, default=0,
                     help="sequences of exactly this many tokens (= --microbatch: one long sequence per microbatch)")
     ap.add_argument("--frontend", default="graph", choices=["stages", "graph"],
@@ -187,6 +189,7 @@ def main() -> None:
                           expert_parallel=args.expert_parallel, spill_pool=args.spill_pool,
                           frontend=args.frontend, allocator=args.allocator, fused_gather=args.fused_gather,
                           axis_chunk_rows=args.axis_chunk_rows, profile_sequence_tokens=args.fixed_len,
+                          delta_head_groups=args.delta_head_groups,
                           spill_directory=args.spill_dir if args.spill_pool == "file" else "",
                           spill_address=args.spill_address)
     log = (lambda m: print(f"[bench] {m}", file=sys.stderr, flush=True)) if rank == 0 else None

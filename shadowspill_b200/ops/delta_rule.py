@@ -116,7 +116,7 @@ def forward_keeping(q, k, v, beta, g, cu_seqlens, raw_key=None):
     """The forward pass on prepared operands; inside ``keeping_intermediates()`` with its saves on,
     kept for a backward pass in the same scope that names the same operands, either as the caller
     passed them (``raw_key``) or prepared."""
-    if not _scope["on"]:
+    if not _scope["on"] or _head_groups > 1:       # head groups are about holding less, not more
         return _forward(q, k, v, beta, g, cu_seqlens, backward=False)[0]
     out, B, geo = _forward(q, k, v, beta, g, cu_seqlens, backward=True)
     _scope["key"] = {raw_key, _operand_key(q, k, v, beta, g, cu_seqlens)}
@@ -127,6 +127,30 @@ def forward_keeping(q, k, v, beta, g, cu_seqlens, raw_key=None):
 def _operands(q, k, v, beta, g):
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     return q, k, v, beta.float().contiguous(), g.float().contiguous()
+
+
+# Head-group chunks: the rule is independent per key head (and the value heads that share it), so
+# a call can run in groups of key heads one after another; the chunk intermediates (about 1 GB for
+# 8,192 tokens of 16/32 heads with the backward saves) then exist for one group at a time.
+# (packages/workloads/src/shadowspill_workloads/policies/text/chunking.py:22,
+# ``linear_attention_head_chunks``.)
+_head_groups = 1
+
+
+def set_head_groups(groups: int) -> None:
+    """Run every call in ``groups`` groups of key heads (1 = all heads at once)."""
+    global _head_groups
+    if groups < 1:
+        raise ValueError("head groups must be at least 1")
+    _head_groups = int(groups)
+
+
+def _groups(Hk: int) -> list[tuple[int, int]]:
+    g = _head_groups
+    if g <= 1 or Hk % g:
+        return [(0, Hk)]
+    per = Hk // g
+    return [(a, a + per) for a in range(0, Hk, per)]
 
 
 class _GatedDeltaRule(torch.autograd.Function):
@@ -149,6 +173,16 @@ class _GatedDeltaRule(torch.autograd.Function):
 def backward(q, k, v, beta, g, cu_seqlens, dout):
     """Gradients of :func:`gated_delta_rule` for ``dout`` [T,H,128] (bf16): ``(dq, dk, dv, dbeta,
     dg)`` with dbeta, dg in fp32. The forward pass is recomputed with its saves switched on."""
+    spans = _groups(q.shape[1])
+    if len(spans) > 1:
+        rep = v.shape[1] // q.shape[1]
+        parts = [_backward_all(q[:, a:b], k[:, a:b], v[:, a * rep:b * rep], beta[:, a * rep:b * rep],
+                               g[:, a * rep:b * rep], cu_seqlens, dout[:, a * rep:b * rep]) for a, b in spans]
+        return tuple(torch.cat([p[i] for p in parts], dim=1) for i in range(5))
+    return _backward_all(q, k, v, beta, g, cu_seqlens, dout)
+
+
+def _backward_all(q, k, v, beta, g, cu_seqlens, dout):
     dout = dout.to(torch.bfloat16).contiguous()
     if _scope["on"] and _scope["key"] and _operand_key(q, k, v, beta, g, cu_seqlens) in _scope["key"]:
         B, geo, (q, k, v, beta, g) = _scope["value"]     # the forward pass of this task kept them
@@ -186,4 +220,9 @@ def backward(q, k, v, beta, g, cu_seqlens, dout):
 def gated_delta_rule(q, k, v, beta, g, cu_seqlens):
     """q, k [T,Hk,128] bf16 (L2-normalised), v [T,H,128] bf16, beta, g [T,H] (g = log decay <= 0),
     ``cu_seqlens`` int32 on the device. Returns [T,H,128] bf16; differentiable in q, k, v, beta, g."""
+    spans = _groups(q.shape[1])
+    if len(spans) > 1:
+        rep = v.shape[1] // q.shape[1]
+        return torch.cat([_GatedDeltaRule.apply(q[:, a:b], k[:, a:b], v[:, a * rep:b * rep], beta[:, a * rep:b * rep],
+                                                g[:, a * rep:b * rep], cu_seqlens) for a, b in spans], dim=1)
     return _GatedDeltaRule.apply(q, k, v, beta, g, cu_seqlens)

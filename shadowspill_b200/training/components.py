@@ -102,7 +102,8 @@ def default_registry() -> Registry:
     r.add_optimizer("lion@1", lambda **kw: {"kind": "lion", **kw})
     r.add_preparation("shadowspill/default@1", lambda **kw: kw)
     r.add_policy("shadowspill/text_chunks@1",
-                 lambda projection=0, moe=0, rows=0: {"projection": projection, "moe": moe, "rows": rows})
+                 lambda projection=0, moe=0, rows=0, delta_heads=1: {"projection": projection, "moe": moe, "rows": rows,
+                                                                     "delta_heads": delta_heads})
     r.add_policy("shadowspill/text_retention@1", lambda rule="cost-input": {"rule": rule})
     return r
 
@@ -217,6 +218,7 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
     build, planning = prep.get("build", {}), prep.get("planning", {})
     saved_variant = build.get("saved_variant", "save_attention")
     head_chunks = moe_chunks = axis_rows = 0
+    delta_heads = 1
     frontend = str(build.get("frontend", "stages"))
     if frontend not in ("stages", "graph"):
         raise ValueError(f"unknown build frontend {frontend!r} (stages | graph)")
@@ -228,6 +230,7 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
             head_chunks = int((pol.get("config") or {}).get("projection", 0) or 0)
             moe_chunks = int((pol.get("config") or {}).get("moe", 0) or 0)
             axis_rows = int((pol.get("config") or {}).get("rows", 0) or 0)
+            delta_heads = int((pol.get("config") or {}).get("delta_heads", 1) or 1)   # key-head groups of the delta rule
             if axis_rows < 0:
                 raise ValueError("text_chunks rows must not be negative")
             if axis_rows:
@@ -258,7 +261,7 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
             "ranks_per_replica": per_replica if replicas > 1 else 0,
             "min_shard_bytes": int(par.get("min_shard_bytes", 0)) if workers > 1 else 0,
             "head_chunks": head_chunks, "moe_chunks": moe_chunks, "master_weights": master_weights,
-            "frontend": frontend, "axis_chunk_rows": axis_rows,
+            "frontend": frontend, "axis_chunk_rows": axis_rows, "delta_head_groups": delta_heads,
             "walks": list(build.get("walks", ("breadth",))),
             "recompute_shares": list(build.get("recompute_shares", (100,))),
             "saved_variant": saved_variant,

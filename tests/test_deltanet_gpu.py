@@ -165,3 +165,31 @@ def test_delta_rule_kernels_at_the_model_head_counts():
     assert _rel(got, want) < 1.5e-2
     for name, x, y in zip("q k v beta g".split(), a, b):
         assert _rel(x.grad, y.grad) < 3e-2, name
+
+
+@pytest.mark.gpu
+def test_head_groups_compute_the_same_rule_in_pieces():
+    """Running the rule in groups of key heads (less intermediate memory) gives the same output
+    and gradients as all heads at once."""
+    from shadowspill_b200.ops import delta_rule as dr
+    torch.manual_seed(3)
+    dev = torch.device("cuda")
+    T, Hk, H = 640, 4, 8
+    q = torch.nn.functional.normalize(torch.randn(T, Hk, 128, device=dev), dim=-1).bfloat16()
+    k = torch.nn.functional.normalize(torch.randn(T, Hk, 128, device=dev), dim=-1).bfloat16()
+    v = (torch.randn(T, H, 128, device=dev) * 0.5).bfloat16()
+    beta = torch.sigmoid(torch.randn(T, H, device=dev))
+    g = -torch.rand(T, H, device=dev) * 0.2
+    cu = torch.tensor([0, 201, 640] + [640] * 6, dtype=torch.int32, device=dev)
+    dout = torch.randn(T, H, 128, device=dev).bfloat16()
+    whole = dr.gated_delta_rule(q, k, v, beta, g, cu)
+    grads = dr.backward(q, k, v, beta, g, cu, dout)
+    dr.set_head_groups(2)
+    try:
+        pieces = dr.gated_delta_rule(q, k, v, beta, g, cu)
+        grads2 = dr.backward(q, k, v, beta, g, cu, dout)
+    finally:
+        dr.set_head_groups(1)
+    assert torch.equal(whole, pieces)
+    for a, b in zip(grads, grads2):
+        assert torch.equal(a, b)
