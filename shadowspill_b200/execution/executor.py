@@ -123,6 +123,8 @@ class TaskRunner:
                     out[u.role] = st.shard_views(flat, self.desc.dtype, self.world, only)
                 else:
                     out[u.role] = st.views(flat, self.desc.dtype, trainable_only=only)
+            elif u.role == "acc":
+                out[u.role] = st.shard_views(flat, torch.float32, self.world, True)
             elif u.role == "master":
                 if obj.sharding == "sharded":
                     out[u.role] = st.shard_views(flat, torch.float32, self.world, True)
@@ -193,6 +195,22 @@ class TaskRunner:
                 self._optimizer_sharded(t.stage, B)
             else:
                 self._optimizer(t.stage, B)
+        elif t.kind == "collective" and t.variant == "rs_accumulate":
+            # one group's gradients, summed over ranks, folded into this rank's fp32 shard sums
+            coll = self.collectives
+            first = B.get("acc.mode") == "create"
+            coll.barrier_begin()          # every rank's gradients of this group are complete
+            for p in st.params:
+                if not p.trainable:
+                    continue
+                g, acc = B["grads"][p.name].view(-1), B["acc"][p.name]
+                if p.expert_sharded:      # the local bank's gradient is already the sum over ranks
+                    dst = acc.view(-1)[:p.numel]
+                    dst.copy_(g) if first else dst.add_(g.float())
+                else:
+                    coll.reduce_scatter_accumulate(g, acc, first=first,
+                                                   whole=st.kept_whole(p, self.desc.dtype))
+            coll.barrier_end()            # peers finished reading this rank's gradients
         elif t.kind == "collective" and t.variant == "allgather":
             coll = self.collectives
             coll.barrier_begin()          # every rank's shard has landed
@@ -240,6 +258,7 @@ class TaskRunner:
         """Gradient reduce-scatter fused with the AdamW update of the owned shards."""
         st, h, coll = self.stages[stage], self.hyper, self.collectives
         coll.barrier_begin()              # every rank's gradients for this stage are complete
+        acc = B.get("acc")                # fp32 shard sums of the earlier microbatch groups
         for p in st.params:
             if not p.trainable:
                 continue
@@ -251,19 +270,26 @@ class TaskRunner:
                 # the model-dtype shard (both laid out alike)
                 target = B["master"][p.name] if "master" in B else B["params"][p.name]
                 if p.expert_sharded:
-                    reference.update_rule_(h.rule, target[:p.numel], B["grads"][p.name].view(-1),
+                    own = B["grads"][p.name].view(-1)
+                    if acc is not None:
+                        own = own.float() + acc[p.name].view(-1)[:p.numel]
+                    reference.update_rule_(h.rule, target[:p.numel], own,
                                            B["m"][p.name][:p.numel], B["v"][p.name][:p.numel], **hyper)
                 else:
                     coll.reduce_scatter_update(h.rule, B["grads"][p.name].view(-1), target,
                                                B["m"][p.name], B["v"][p.name],
-                                               whole=st.kept_whole(p, self.desc.dtype), **hyper)
+                                               whole=st.kept_whole(p, self.desc.dtype),
+                                               acc=None if acc is None else acc[p.name], **hyper)
                 if "master" in B:
                     B["params"][p.name].copy_(target)
                 continue
             if p.expert_sharded:
                 # the local bank's gradient is already the sum over every rank's tokens
                 # (expert parallelism routes all of them here): a plain local update
-                F.adamw_(B["params"][p.name][:p.numel], B["grads"][p.name].view(-1),
+                own = B["grads"][p.name].view(-1)
+                if acc is not None:
+                    own = own.float() + acc[p.name].view(-1)[:p.numel]
+                F.adamw_(B["params"][p.name][:p.numel], own,
                          B["m"][p.name][:p.numel], B["v"][p.name][:p.numel], lr=h.lr, beta1=h.beta1,
                          beta2=h.beta2, eps=h.eps, weight_decay=h.weight_decay,
                          step=self.completed_updates + 1, grad_scale=h.grad_scale, seed=self.seed,
@@ -275,7 +301,8 @@ class TaskRunner:
                 offset=self.param_offsets[(stage, p.name)], lr=h.lr, beta1=h.beta1, beta2=h.beta2,
                 eps=h.eps, weight_decay=h.weight_decay, step=self.completed_updates + 1,
                 grad_scale=h.grad_scale, seed=self.seed, stochastic_param=self.sr,
-                stochastic_state=self.sr, whole=st.kept_whole(p, self.desc.dtype))
+                stochastic_state=self.sr, whole=st.kept_whole(p, self.desc.dtype),
+                **({} if acc is None else {"acc": acc[p.name]}))
         coll.barrier_end()                # peers finished reading this rank's gradients
 
     def _optimizer(self, stage: int, B) -> None:
@@ -792,7 +819,7 @@ class Executor:
                 side = self.comm_stream is not None and (t.kind == "collective" or t.variant == "adamw_dp")
                 run_stream = self.comm_stream if side else self.stream
                 if side:
-                    if t.kind != "collective":
+                    if t.kind != "collective" or t.variant == "rs_accumulate":
                         # reads what compute tasks produced (gradients): order after them. A weight
                         # gather depends on fetches and freed ranges only, which the runtime orders.
                         ready = torch.cuda.Event()

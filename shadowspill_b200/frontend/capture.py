@@ -35,9 +35,15 @@ class StepDataOrdering:
     reverse_breadth: bool = True
     pair_loss: bool = True
     optimizer: str = "stage_interleaved"   # stage_interleaved | tail
+    # sharded storage, breadth walk: run the microbatches in this many groups, each a full
+    # forward + backward sweep over the layers. Live activations shrink with the group; the
+    # weights are gathered once per group and pass (NVLink, cheap) and every group's gradient is
+    # reduce-scattered into a shard-sized fp32 accumulator, which the update of the last group
+    # reads. 1 = one sweep over all microbatches.
+    microbatch_groups: int = 1
 
     def label(self) -> str:
-        return f"{self.walk}/{self.optimizer}"
+        return f"{self.walk}/{self.optimizer}" + (f"/groups{self.microbatch_groups}" if self.microbatch_groups > 1 else "")
 
 
 @dataclass
@@ -186,6 +192,7 @@ def _build(desc: TrainingDescription) -> Program:
     train = desc.mode != "forward"
     step = desc.mode in ("step", "optimizer")
     only_optimizer = desc.mode == "optimizer"
+    step_mode = desc.mode == "step"
     isz = desc.dtype.itemsize
     prog = Program(metadata={"model": cfg.to_json(), "tokens": geo.tokens, "mode": desc.mode,
                              "microbatch_tokens": T, "n_microbatches": n_mb, "slots": geo.slots,
@@ -275,6 +282,31 @@ def _build(desc: TrainingDescription) -> Program:
                 SAVED[(si, m)] = prog.add_object(ObjectSpec(f"{stages[si].name}.saved.{m}", sbytes,
                                                             "saved", stage=si, microbatch=m))
     grad_created = [False] * S
+    GG: dict[tuple[int, int], int] = {}       # (stage, group) -> that group's gradient object
+    ACC: dict[int, int] = {}                  # stage -> fp32 shard-sized sum of the earlier groups
+    acc_created: set[int] = set()
+
+    def grad_obj(si: int) -> int:
+        """The gradient object the current group of microbatches writes."""
+        if groups <= 1:
+            return G[si]
+        gi = group_now[0]
+        if (si, gi) not in GG:
+            if gi == 0:
+                GG[(si, gi)] = G[si]
+            else:
+                spec = prog.objects[G[si]]
+                GG[(si, gi)] = prog.add_object(ObjectSpec(f"{stages[si].name}.gradients.g{gi}", spec.bytes,
+                                                          "gradient", stage=si))
+        return GG[(si, gi)]
+
+    def grad_use(si: int, role: str) -> UseSpec:
+        key_ = (si, group_now[0]) if groups > 1 else si
+        if step_mode and key_ not in grads_started:
+            grads_started.add(key_)
+            return UseSpec(grad_obj(si), "create", role)
+        return UseSpec(grad_obj(si), "mutate", role)
+    grads_started: set = set()
 
     tag = ""
     if desc.lora is not None:
@@ -291,12 +323,19 @@ def _build(desc: TrainingDescription) -> Program:
 
     fresh_gather: set[tuple[int, str]] = set()       # gathers whose first consumer is still to come
 
+    groups = max(1, int(order.microbatch_groups)) if (sharded and order.walk == "breadth" and step_mode) else 1
+    if groups > 1 and n_mb % groups:
+        raise ValueError("microbatch_groups must divide the number of microbatches")
+    group_now = [0]
+
     def params_of(si: int, which: str) -> int:
         """The object a compute task reads its weights from; under sharded storage
         the first user in a pass is preceded by the all-gather task that builds it."""
         if not sharded:
             return W[si]
         tag = which if order.walk == "breadth" else "all"
+        if groups > 1:
+            tag = f"{tag}.g{group_now[0]}"
         if (si, tag) not in FULL:
             fresh_gather.add((si, tag))
             st = stages[si]
@@ -316,6 +355,8 @@ def _build(desc: TrainingDescription) -> Program:
         uses = [UseSpec(params_of(si, "fwd"), "read", "params"), UseSpec(IN[m], "read", "batch"),
                 UseSpec(A[si][m], "create", "y")]
         tag_ = "fwd" if order.walk == "breadth" else "all"
+        if groups > 1:
+            tag_ = f"{tag_}.g{group_now[0]}"
         if (si, tag_) in fresh_gather:
             fresh_gather.discard((si, tag_))
             if desc.fused_gather and getattr(st, "fused_gather_params", ()):
@@ -339,20 +380,13 @@ def _build(desc: TrainingDescription) -> Program:
             # the output matrix is the embedding: read it here, and start (or add to) its gradient
             uses.append(UseSpec(params_of(0, "fwd"), "read", "tied_params"))
             if train and stages[0].has_trainable:
-                if desc.mode == "step" and not grad_created[0]:
-                    uses.append(UseSpec(G[0], "create", "tied_grads")); grad_created[0] = True
-                else:
-                    uses.append(UseSpec(G[0], "mutate", "tied_grads"))
+                uses.append(grad_use(0, "tied_grads"))
         if OUT:
             uses.append(UseSpec(OUT[m], "mutate", "outputs"))
         if train:
             uses.append(UseSpec(DX[m], "create", "dx"))
-            if not st.has_trainable:
-                pass
-            elif desc.mode == "step" and not grad_created[si]:
-                uses.append(UseSpec(G[si], "create", "grads")); grad_created[si] = True
-            else:
-                uses.append(UseSpec(G[si], "mutate", "grads"))
+            if st.has_trainable:
+                uses.append(grad_use(si, "grads"))
         fl = st.flops(T, geo.mean_seqlen) * (3.0 if train else 1.0)
         prog.add_task(TaskSpec(f"H.{st.name}.{m}", "head", si, m, uses,
                                estimate_duration_ns(fl, 8.0 * act_bytes),
@@ -372,12 +406,8 @@ def _build(desc: TrainingDescription) -> Program:
             uses.append(UseSpec(A[si - 1][m], "read", "x"))
         if (si, m) in SAVED:
             uses.append(UseSpec(SAVED[(si, m)], "read", "saved"))
-        if not st.has_trainable:
-            pass
-        elif desc.mode == "step" and not grad_created[si]:
-            uses.append(UseSpec(G[si], "create", "grads")); grad_created[si] = True
-        else:
-            uses.append(UseSpec(G[si], "mutate", "grads"))
+        if st.has_trainable:
+            uses.append(grad_use(si, "grads"))
         fl = st.flops(T, geo.mean_seqlen) * (3.0 if var == "recompute" else 2.0)
         prog.add_task(TaskSpec(f"B.{st.name}.{m}", "backward", si, m, uses,
                                estimate_duration_ns(fl, 16.0 * act_bytes),
@@ -390,20 +420,61 @@ def _build(desc: TrainingDescription) -> Program:
             return
         pbytes = prog.objects[W[si]].bytes
         prog.add_task(TaskSpec(f"O.{st.name}", "optimizer", si, -1,
-                               [UseSpec(W[si], "mutate", "params"), UseSpec(G[si], "read", "grads"),
+                               [UseSpec(W[si], "mutate", "params"), UseSpec(grad_obj(si), "read", "grads"),
                                 UseSpec(M[si], "mutate", "m"), UseSpec(V[si], "mutate", "v")]
-                               + ([UseSpec(MASTER[si], "mutate", "master")] if si in MASTER else []),
+                               + ([UseSpec(MASTER[si], "mutate", "master")] if si in MASTER else [])
+                               + ([UseSpec(ACC[si], "read", "acc")] if si in ACC else []),
                                estimate_duration_ns(0.0, 8.0 * pbytes),
                                # the unfused update holds a handful of fp32 temporaries per parameter
                                (6 * prog.objects[MASTER[si]].bytes) if si in MASTER else 0,
                                "adamw_dp" if sharded else "adamw",
-                               profile_key=f"opt:{pbytes}:{world}" + (":master" if si in MASTER else "")))
+                               profile_key=f"opt:{pbytes}:{world}" + (":master" if si in MASTER else "")
+                               + (":acc" if si in ACC else "")))
+
+    def accumulate(si: int) -> None:
+        """Reduce-scatter this group's gradient of stage ``si`` into the fp32 shard accumulator."""
+        st = stages[si]
+        if not st.has_trainable:
+            return
+        if si not in ACC:
+            _, abytes = st.shard_layout(torch.float32, world, trainable_only=True)
+            ACC[si] = prog.add_object(ObjectSpec(f"{st.name}.gradient_sum", abytes, "gradient", stage=si,
+                                                 sharding="sharded"))
+        gbytes = prog.objects[grad_obj(si)].bytes
+        mode = "mutate" if si in acc_created else "create"
+        acc_created.add(si)
+        prog.add_task(TaskSpec(f"RS.{st.name}.g{group_now[0]}", "collective", si, -1,
+                               [UseSpec(grad_obj(si), "read", "grads"), UseSpec(ACC[si], mode, "acc")],
+                               estimate_duration_ns(0.0, 2.0 * gbytes, gbps=600.0), 0, "rs_accumulate",
+                               profile_key=f"rs_accumulate:{gbytes}:{world}"))
 
     body = list(range(S - 1))
     mbs = list(range(n_mb))
     back_mbs = list(reversed(mbs)) if order.reverse_breadth else mbs
     step = desc.mode == "step"      # from here on: does this program contain the update?
-    if order.walk == "breadth":
+    if order.walk == "breadth" and groups > 1:
+        per_group = n_mb // groups
+        for gi in range(groups):
+            group_now[0] = gi
+            gm = mbs[gi * per_group:(gi + 1) * per_group]
+            last = gi == groups - 1
+
+            def finish(si: int) -> None:
+                if not last:
+                    accumulate(si)
+                elif order.optimizer == "stage_interleaved":
+                    opt(si)
+            for si in body:
+                for m in gm:
+                    fwd(si, m)
+            for m in gm:
+                head(m)
+            finish(S - 1)
+            for si in reversed(body):
+                for m in (list(reversed(gm)) if order.reverse_breadth else gm):
+                    bwd(si, m)
+                finish(si)
+    elif order.walk == "breadth":
         for si in body:
             for m in mbs:
                 fwd(si, m)

@@ -11,6 +11,9 @@
 //                        and applies AdamW with bf16 stochastic rounding to its
 //                        parameter / moment shards in the same pass -- the summed
 //                        gradient never exists in memory
+//   ss_rs_accumulate     gradient reduce-scatter into a shard-sized fp32 sum that stays on
+//                        this rank: a step that runs its microbatches in groups folds each
+//                        group's gradient into it, and ss_rs_adamw_acc starts its own sum there
 //   ss_peer_allreduce    one-shot all-reduce for small fp32 tensors (norm weights)
 //
 // These replace the NCCL calls the reference makes for sharded storage
@@ -134,8 +137,11 @@ struct RsAdamArgs {
 // mc_grad, when non-null, is the NVSwitch multicast address of the same bf16 gradient tensor:
 // one multimem.ld_reduce returns the sum over every rank's copy, reduced inside the switch
 // (fp32 accumulation, bf16 result), instead of `world` separate peer loads.
+//
+// acc, when non-null, is this rank's fp32 sum of earlier groups' gradients over [lo, hi)
+// (element 0 = element lo): the sum starts there instead of at zero.
 __global__ void rs_adamw_kernel(PeerPtrs grads, const __nv_bfloat16* __restrict__ mc_grad,
-                                __nv_bfloat16* __restrict__ p,
+                                const float* __restrict__ acc, __nv_bfloat16* __restrict__ p,
                                 __nv_bfloat16* __restrict__ m, __nv_bfloat16* __restrict__ v,
                                 long long lo, long long hi, int world, RsAdamArgs a) {
   const long long n = hi - lo;
@@ -145,13 +151,25 @@ __global__ void rs_adamw_kernel(PeerPtrs grads, const __nv_bfloat16* __restrict_
     const long long e0 = i << 3;
     const int cnt = static_cast<int>(min(8LL, n - e0));
     float g[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (acc != nullptr) {
+      if (cnt == 8) {
+        const float4 x = *reinterpret_cast<const float4*>(acc + e0);
+        const float4 y = *reinterpret_cast<const float4*>(acc + e0 + 4);
+        g[0] = x.x; g[1] = x.y; g[2] = x.z; g[3] = x.w; g[4] = y.x; g[5] = y.y; g[6] = y.z; g[7] = y.w;
+      } else {
+        for (int e = 0; e < cnt; ++e) g[e] = acc[e0 + e];
+      }
+    }
     if (mc_grad != nullptr && cnt == 8) {
+      float f[8];
       uint4 u;
       asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
                    : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w)
                    : "l"(mc_grad + lo + e0)
                    : "memory");
-      up8(u, g);
+      up8(u, f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) g[e] += f[e];
     } else
     for (int j = 0; j < world; ++j) {
       if (a.g_f32) {
@@ -233,6 +251,58 @@ __global__ void rs_adamw_kernel(PeerPtrs grads, const __nv_bfloat16* __restrict_
   }
 }
 
+// acc[i] (fp32, this rank's owned slice [lo, hi)) = (first ? 0 : acc[i]) + the sum over ranks of
+// grads.p[j][lo + i]: the reduce-scatter of one group's gradient, kept as a running sum.
+__global__ void rs_accumulate_kernel(PeerPtrs grads, float* __restrict__ acc, long long lo,
+                                     long long hi, int world, int g_f32, int first) {
+  const long long n = hi - lo;
+  const long long nvec = (n + 7) >> 3;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long e0 = i << 3;
+    const int cnt = static_cast<int>(min(8LL, n - e0));
+    float g[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (!first) {
+      if (cnt == 8) {
+        const float4 x = *reinterpret_cast<const float4*>(acc + e0);
+        const float4 y = *reinterpret_cast<const float4*>(acc + e0 + 4);
+        g[0] = x.x; g[1] = x.y; g[2] = x.z; g[3] = x.w; g[4] = y.x; g[5] = y.y; g[6] = y.z; g[7] = y.w;
+      } else {
+        for (int e = 0; e < cnt; ++e) g[e] = acc[e0 + e];
+      }
+    }
+    for (int j = 0; j < world; ++j) {
+      if (g_f32) {
+        const float* src = reinterpret_cast<const float*>(grads.p[j]) + lo + e0;
+        if (cnt == 8) {
+          const float4 x = *reinterpret_cast<const float4*>(src);
+          const float4 y = *reinterpret_cast<const float4*>(src + 4);
+          g[0] += x.x; g[1] += x.y; g[2] += x.z; g[3] += x.w;
+          g[4] += y.x; g[5] += y.y; g[6] += y.z; g[7] += y.w;
+        } else {
+          for (int e = 0; e < cnt; ++e) g[e] += src[e];
+        }
+      } else {
+        const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(grads.p[j]) + lo + e0;
+        if (cnt == 8) {
+          float f[8];
+          up8(*reinterpret_cast<const uint4*>(src), f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) g[e] += f[e];
+        } else {
+          for (int e = 0; e < cnt; ++e) g[e] += __bfloat162float(src[e]);
+        }
+      }
+    }
+    if (cnt == 8) {
+      *reinterpret_cast<float4*>(acc + e0) = make_float4(g[0], g[1], g[2], g[3]);
+      *reinterpret_cast<float4*>(acc + e0 + 4) = make_float4(g[4], g[5], g[6], g[7]);
+    } else {
+      for (int e = 0; e < cnt; ++e) acc[e0 + e] = g[e];
+    }
+  }
+}
+
 // One-shot all-reduce (sum) of a small fp32 tensor: every rank reads every rank.
 __global__ void peer_allreduce_f32_kernel(PeerPtrs src, float* __restrict__ dst, long long n,
                                           int world) {
@@ -282,6 +352,42 @@ int ss_peer_allgather(void* const* shard_ptrs, void* full, long long shard_bytes
   return (int)cudaGetLastError();
 }
 
+int ss_rs_accumulate(void* const* grad_ptrs, void* acc, long long lo, long long hi, int world,
+                     int g_f32, int first, void* stream) {
+  if (world < 1 || world > MAX_RANKS || (lo & 7) || (reinterpret_cast<uintptr_t>(acc) & 15)) return -2;
+  if (hi <= lo) return 0;
+  PeerPtrs g;
+  for (int j = 0; j < world; ++j) g.p[j] = grad_ptrs[j];
+  const long long nvec = (hi - lo + 7) >> 3;
+  rs_accumulate_kernel<<<grid_of(nvec, 256, 148 * 8), 256, 0, (cudaStream_t)stream>>>(
+      g, (float*)acc, lo, hi, world, g_f32, first);
+  return (int)cudaGetLastError();
+}
+
+// acc: null, or this rank's fp32 sum of earlier groups' gradients over [lo, hi).
+int ss_rs_adamw_acc(void* const* grad_ptrs, const void* acc, void* p, void* m, void* v, long long lo,
+                    long long hi, int world, int g_f32, float lr, float beta1, float beta2, float eps,
+                    float weight_decay, int step, float grad_scale, unsigned long long seed,
+                    unsigned long long offset, int sr_param, int sr_state, void* stream) {
+  if (world < 1 || world > MAX_RANKS || (lo & 7) || ((offset) & 7) ||
+      (reinterpret_cast<uintptr_t>(acc) & 15))
+    return -2;
+  if (hi <= lo) return 0;
+  PeerPtrs g;
+  for (int j = 0; j < world; ++j) g.p[j] = grad_ptrs[j];
+  RsAdamArgs a;
+  a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.weight_decay = weight_decay;
+  a.bias1 = 1.f / (1.f - powf(beta1, (float)step)); a.bias2 = 1.f / (1.f - powf(beta2, (float)step));
+  a.grad_scale = grad_scale;
+  a.seed = seed ^ (0x9E3779B97F4A7C15ull * (unsigned long long)(step + 1));
+  a.offset = offset; a.sr_param = sr_param; a.sr_state = sr_state; a.g_f32 = g_f32;
+  const long long nvec = (hi - lo + 7) >> 3;
+  rs_adamw_kernel<<<grid_of(nvec, 256, 148 * 8), 256, 0, (cudaStream_t)stream>>>(
+      g, nullptr, (const float*)acc, (__nv_bfloat16*)p, (__nv_bfloat16*)m, (__nv_bfloat16*)v, lo, hi,
+      world, a);
+  return (int)cudaGetLastError();
+}
+
 int ss_rs_adamw(void* const* grad_ptrs, void* p, void* m, void* v, long long lo, long long hi,
                 int world, int g_f32, float lr, float beta1, float beta2, float eps,
                 float weight_decay, int step, float grad_scale, unsigned long long seed,
@@ -298,7 +404,7 @@ int ss_rs_adamw(void* const* grad_ptrs, void* p, void* m, void* v, long long lo,
   a.offset = offset; a.sr_param = sr_param; a.sr_state = sr_state; a.g_f32 = g_f32;
   const long long nvec = (hi - lo + 7) >> 3;
   rs_adamw_kernel<<<grid_of(nvec, 256, 148 * 8), 256, 0, (cudaStream_t)stream>>>(
-      g, nullptr, (__nv_bfloat16*)p, (__nv_bfloat16*)m, (__nv_bfloat16*)v, lo, hi, world, a);
+      g, nullptr, nullptr, (__nv_bfloat16*)p, (__nv_bfloat16*)m, (__nv_bfloat16*)v, lo, hi, world, a);
   return (int)cudaGetLastError();
 }
 
@@ -324,8 +430,8 @@ int ss_rs_adamw_nvls(void* const* grad_ptrs, const void* mc_grad, void* p, void*
   a.offset = offset; a.sr_param = sr_param; a.sr_state = sr_state; a.g_f32 = 0;
   const long long nvec = (hi - lo + 7) >> 3;
   rs_adamw_kernel<<<grid_of(nvec, 256, 148 * 8), 256, 0, (cudaStream_t)stream>>>(
-      g, (const __nv_bfloat16*)mc_grad, (__nv_bfloat16*)p, (__nv_bfloat16*)m, (__nv_bfloat16*)v, lo, hi,
-      world, a);
+      g, (const __nv_bfloat16*)mc_grad, nullptr, (__nv_bfloat16*)p, (__nv_bfloat16*)m, (__nv_bfloat16*)v,
+      lo, hi, world, a);
   return (int)cudaGetLastError();
 }
 

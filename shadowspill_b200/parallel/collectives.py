@@ -33,6 +33,10 @@ _lib.register("ss_peer_allgather", [_c.c_p, _c.c_p, _c.c_ll, _c.c_ll, _c.c_int, 
 _lib.register("ss_rs_adamw", [_c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_ll, _c.c_ll, _c.c_int, _c.c_int,
                               _c.c_f, _c.c_f, _c.c_f, _c.c_f, _c.c_f, _c.c_int, _c.c_f, _c.c_ull,
                               _c.c_ull, _c.c_int, _c.c_int, _c.c_p])
+_lib.register("ss_rs_adamw_acc", [_c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_ll, _c.c_ll, _c.c_int, _c.c_int,
+                                  _c.c_f, _c.c_f, _c.c_f, _c.c_f, _c.c_f, _c.c_int, _c.c_f, _c.c_ull,
+                                  _c.c_ull, _c.c_int, _c.c_int, _c.c_p])
+_lib.register("ss_rs_accumulate", [_c.c_p, _c.c_p, _c.c_ll, _c.c_ll, _c.c_int, _c.c_int, _c.c_int, _c.c_p])
 _lib.register("ss_rs_adamw_nvls", [_c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_p, _c.c_ll, _c.c_ll, _c.c_int,
                                    _c.c_f, _c.c_f, _c.c_f, _c.c_f, _c.c_f, _c.c_int, _c.c_f, _c.c_ull,
                                    _c.c_ull, _c.c_int, _c.c_int, _c.c_p])
@@ -86,10 +90,11 @@ class DistCollectives:
                 flat[lo:min(n, lo + per)].copy_(part[:min(n, lo + per) - lo])
 
     def reduce_scatter_update(self, rule: str, grad: torch.Tensor, p, m, v, *, whole: bool = False,
-                              **hyper) -> None:
+                              acc: torch.Tensor | None = None, **hyper) -> None:
         """The unfused form for update rules other than AdamW: sum ``grad`` over every rank with
         the library all-reduce (on a copy: this rank's gradient buffer stays as peers expect it),
-        then apply ``rule`` to the slice of (p, m, v) this rank owns."""
+        then apply ``rule`` to the slice of (p, m, v) this rank owns. ``acc``: this rank's fp32
+        sum of earlier groups' gradients over that slice, added first."""
         from ..ops import reference
         n, per = grad.numel(), p.numel()
         g = grad.view(-1).clone()
@@ -100,15 +105,17 @@ class DistCollectives:
         if hi <= lo:
             return
         cnt = hi - lo
-        reference.update_rule_(rule, p.view(-1)[:cnt], g[lo:hi], m.view(-1)[:cnt], v.view(-1)[:cnt], **hyper)
+        owned = g[lo:hi] if acc is None else g[lo:hi].float() + acc.view(-1)[:cnt]
+        reference.update_rule_(rule, p.view(-1)[:cnt], owned, m.view(-1)[:cnt], v.view(-1)[:cnt], **hyper)
 
     def _owned_rank(self) -> int:
         return self.rank
 
     def reduce_scatter_adamw(self, grad: torch.Tensor, p, m, v, *, offset: int, whole: bool = False,
-                             **adam) -> None:
+                             acc: torch.Tensor | None = None, **adam) -> None:
         """Sum ``grad`` over ranks; update this rank's owned slice of (p, m, v). ``whole``: the
-        tensor is stored whole on every rank, which all apply the same update to all of it."""
+        tensor is stored whole on every rank, which all apply the same update to all of it.
+        ``acc``: this rank's fp32 sum of earlier groups' gradients over the slice, added first."""
         n, per = grad.numel(), p.numel()
         g = grad.view(-1).clone()
         if dist.is_initialized() and dist.get_world_size(self.group) > 1:
@@ -118,8 +125,28 @@ class DistCollectives:
         if hi <= lo:
             return
         cnt = hi - lo
-        F.adamw_(p.view(-1)[:cnt], g[lo:hi], m.view(-1)[:cnt], v.view(-1)[:cnt],
+        owned = g[lo:hi] if acc is None else g[lo:hi].float() + acc.view(-1)[:cnt]
+        F.adamw_(p.view(-1)[:cnt], owned, m.view(-1)[:cnt], v.view(-1)[:cnt],
                  offset=offset + lo, **adam)
+
+    def reduce_scatter_accumulate(self, grad: torch.Tensor, acc: torch.Tensor, *, first: bool,
+                                  whole: bool = False) -> None:
+        """``acc`` (fp32, this rank's owned slice) = (0 if ``first`` else ``acc``) + the sum of
+        ``grad`` over every rank: one group's gradient folded into the running sum."""
+        n, per = grad.numel(), acc.numel()
+        g = grad.view(-1).clone()
+        if dist.is_initialized() and dist.get_world_size(self.group) > 1:
+            dist.all_reduce(g, group=self.group)
+        lo = 0 if whole else self.rank * per
+        hi = min(n, lo + per)
+        if hi <= lo:
+            return
+        cnt = hi - lo
+        dst = acc.view(-1)[:cnt]
+        if first:
+            dst.copy_(g[lo:hi])
+        else:
+            dst.add_(g[lo:hi].float())
 
 
 class PeerCollectives:
@@ -222,10 +249,11 @@ class PeerCollectives:
             "ss_peer_allgather")
 
     def reduce_scatter_update(self, rule: str, grad: torch.Tensor, p, m, v, *, whole: bool = False,
-                              **hyper) -> None:
+                              acc: torch.Tensor | None = None, **hyper) -> None:
         """The unfused form for update rules other than AdamW: sum ``grad`` over every rank with
         the library all-reduce (on a copy: this rank's gradient buffer stays as peers expect it),
-        then apply ``rule`` to the slice of (p, m, v) this rank owns."""
+        then apply ``rule`` to the slice of (p, m, v) this rank owns. ``acc``: this rank's fp32
+        sum of earlier groups' gradients over that slice, added first."""
         from ..ops import reference
         n, per = grad.numel(), p.numel()
         g = grad.view(-1).clone()
@@ -236,20 +264,28 @@ class PeerCollectives:
         if hi <= lo:
             return
         cnt = hi - lo
-        reference.update_rule_(rule, p.view(-1)[:cnt], g[lo:hi], m.view(-1)[:cnt], v.view(-1)[:cnt], **hyper)
+        owned = g[lo:hi] if acc is None else g[lo:hi].float() + acc.view(-1)[:cnt]
+        reference.update_rule_(rule, p.view(-1)[:cnt], owned, m.view(-1)[:cnt], v.view(-1)[:cnt], **hyper)
 
     def _owned_rank(self) -> int:
         return self.shard_rank
 
     def reduce_scatter_adamw(self, grad: torch.Tensor, p, m, v, *, offset: int, lr, beta1, beta2,
                              eps, weight_decay, step, grad_scale, seed, stochastic_param,
-                             stochastic_state, whole: bool = False) -> None:
+                             stochastic_state, whole: bool = False, acc: torch.Tensor | None = None) -> None:
         n, per = grad.numel(), p.numel()
         # the slice this rank owns inside its replica; a tensor stored whole is updated whole by
         # every rank (same summed gradient, same counter-based rounding: identical results)
         lo = 0 if whole else self.shard_rank * per
         hi = min(n, lo + per)
         if hi <= lo:
+            return
+        if acc is not None:
+            _lib.check(_lib.lib().ss_rs_adamw_acc(
+                self._peers(grad), acc.data_ptr(), p.data_ptr(), m.data_ptr(), v.data_ptr(), lo, hi,
+                self.world, int(grad.dtype == torch.float32), lr, beta1, beta2, eps, weight_decay, step,
+                grad_scale, seed, offset, int(stochastic_param), int(stochastic_state),
+                _lib.stream_ptr()), "ss_rs_adamw_acc")
             return
         if self.mc_base and grad.dtype == torch.bfloat16:
             off = grad.data_ptr() - self.local_base
@@ -263,6 +299,21 @@ class PeerCollectives:
             int(grad.dtype == torch.float32), lr, beta1, beta2, eps, weight_decay, step,
             grad_scale, seed, offset, int(stochastic_param), int(stochastic_state),
             _lib.stream_ptr()), "ss_rs_adamw")
+
+    def reduce_scatter_accumulate(self, grad: torch.Tensor, acc: torch.Tensor, *, first: bool,
+                                  whole: bool = False) -> None:
+        """One group's gradient, summed over every rank's buffer with peer loads, folded into this
+        rank's fp32 running sum of its owned slice."""
+        n, per = grad.numel(), acc.numel()
+        lo = 0 if whole else self.shard_rank * per
+        hi = min(n, lo + per)
+        if hi <= lo:
+            return
+        if acc.dtype != torch.float32:
+            raise ValueError("the gradient sum is kept in fp32")
+        _lib.check(_lib.lib().ss_rs_accumulate(
+            self._peers(grad), acc.data_ptr(), lo, hi, self.world, int(grad.dtype == torch.float32),
+            int(first), _lib.stream_ptr()), "ss_rs_accumulate")
 
 
 def nvls_requested() -> bool:

@@ -60,7 +60,7 @@ class TrainingSetup:
     device_index: int = 0
     rank: int = 0
     world_size: int = 1
-    walks: tuple[str, ...] = ("breadth",)
+    walks: tuple[str, ...] = ("breadth",)   # breadth | depth | breadth/<microbatch groups>
     recompute_shares: tuple[int, ...] = (100,)
     saved_variant: str = "save_attention"
     # explicit "<recompute share>:<saved variant>" candidates (e.g. "50:save") or "mix:<K>"
@@ -98,6 +98,9 @@ class TrainingSetup:
     # graph frontend: row chunk of the token-local operators inside a layer stage (0 = off); what
     # lets one long sequence fit: the wide projection outputs then exist one chunk at a time
     axis_chunk_rows: int = 0
+    # gated delta rule: run each call in this many groups of key heads (1 = all at once); the chunk
+    # intermediates then exist for one group at a time
+    delta_head_groups: int = 1
     # profile the tasks on sequences of exactly this many tokens (0 = the packed log-normal mix):
     # the cost of the sequence mixers depends on it, so long-context runs set it
     profile_sequence_tokens: int = 0
@@ -153,6 +156,9 @@ class TrainingSession:
         self.timings: dict[str, float] = {}
         world, rank = setup.world_size, setup.rank
         self.executor = None
+        if setup.delta_head_groups != 1:
+            from ..ops import delta_rule
+            delta_rule.set_head_groups(setup.delta_head_groups)
         if setup.stop_after not in ("", "build", "profile", "communicate", "plan"):
             raise ValueError("stop_after is one of build, profile, communicate, plan")
         phase_dir = Path(setup.phase_directory) if setup.phase_directory else None
@@ -210,7 +216,10 @@ class TrainingSession:
 
         def build(index: int):
             walk, sel = variants[index]
-            order = StepDataOrdering(walk=walk, optimizer="stage_interleaved" if walk == "breadth" else "tail")
+            # "breadth/4": the microbatches in four forward + backward sweeps (sharded storage)
+            walk, _, in_groups = walk.partition("/")
+            order = StepDataOrdering(walk=walk, optimizer="stage_interleaved" if walk == "breadth" else "tail",
+                                     microbatch_groups=int(in_groups or 1))
             return with_replicas(build_step(self.cfg, self.geometry, order, dtype=self.dtype,
                                             selection=sel, world_size=shard_world, rank=rank,
                                             expert_parallel=setup.expert_parallel,

@@ -29,6 +29,9 @@ def main():
     master = arm.startswith("master-")    # fp32 master shards beside the model-dtype shards
     if master:
         arm = arm.split("-", 1)[1]
+    groups = 1
+    if arm.startswith("groups-"):         # microbatches in two sweeps; gradients meet in fp32 shard sums
+        groups, arm = 2, arm.split("-", 1)[1]
     rule = "adamw"
     if arm.startswith("lion-"):           # the unfused update path: all-reduce, then the rule
         rule, arm = "lion", arm.split("-", 1)[1]
@@ -56,14 +59,14 @@ def main():
     if expert_parallel:
         from dataclasses import replace
         cfg = replace(preset("olmoe-tiny"), d_model=256, head_dim=64, vocab_size=1024)
-    T, n_mb = 256, 2
+    T, n_mb = 256, 2 * groups
     if fused:
         # matrices large enough for several 256-row tiles and 64-multiple contraction lengths
         cfg = DecoderConfig("llama3", 2, 512, 8, 2, 64, 1024, 1024)
         T = 512
     geo = BatchGeometry(T, n_mb, slots=16, mean_seqlen=64)
     shard_world = world // replicas
-    prog, desc = build_step(cfg, geo, StepDataOrdering(), dtype=dtype, world_size=shard_world, rank=rank,
+    prog, desc = build_step(cfg, geo, StepDataOrdering(microbatch_groups=groups), dtype=dtype, world_size=shard_world, rank=rank,
                             expert_parallel=expert_parallel, replicas=replicas,
                             min_shard_bytes=min_shard, master_weights=master, fused_gather=fused)
     total = sum(o.bytes for o in prog.objects)

@@ -41,6 +41,14 @@ def test_master_copies_under_sharded_storage():
     _launch(2, "cpu", "master-small-dist", 29661)
 
 
+@pytest.mark.parametrize("arm", ["groups-dist", "groups-lion-small-dist", "groups-master-small-dist"])
+def test_microbatch_groups_accumulate_in_shard_space(arm):
+    """Four microbatches as two forward + backward sweeps: the first sweep's gradients are
+    reduce-scattered into fp32 shard sums, the update after the second sweep starts from them.
+    Matches the single-process model on the same eight microbatches."""
+    _launch(2, "cpu", arm, 29671)
+
+
 def test_whole_parameter_weights_load_into_sharded_ranks():
     """Weights of another seed given as whole tensors: every rank keeps its slice, and the
     sharded job then trains exactly like a single-process model started from those weights."""
@@ -55,7 +63,7 @@ def test_two_replicas_of_two_shards_gloo_match_resident():
 
 @pytest.mark.gpu
 @pytest.mark.multigpu
-@pytest.mark.parametrize("arm", ["peer", "dist", "small-peer", "lion-peer"])
+@pytest.mark.parametrize("arm", ["peer", "dist", "small-peer", "lion-peer", "groups-peer", "groups-small-peer"])
 def test_two_gpus_match_resident(arm):
     _launch(2, "cuda", arm, 29613 if arm == "peer" else 29615)
 
