@@ -116,7 +116,9 @@ def main() -> None:
                             "mix:8:save_attention_gu",
                     help="comma list of programs the planner sweeps: <recompute share %%>[:<saved variant>] "
                          "or mix:<K>[:<variant>] (attention saved everywhere, K layers keep <variant>, default save)")
-    ap.add_argument("--walks", default="breadth")
+    ap.add_argument("--walks", default="auto",
+                    help="comma list of breadth | depth | breadth/<G> (G sweeps over the microbatches, sharded "
+                         "runs only); auto: breadth, and with several GPUs also breadth/2 and breadth/4")
     ap.add_argument("--lora-rank", type=int, default=0, help="train rank-r adapters on a frozen base")
     ap.add_argument("--expert-parallel", action="store_true",
                     help="multi-GPU runs of routed models: split the experts over the ranks")
@@ -181,7 +183,9 @@ def main() -> None:
                           lr=1e-5, seed=1234, rank=rank, world_size=world, device_index=local,
                           collectives=args.collectives,
                           candidate_selections=tuple(c for c in args.candidates.split(",") if c),
-                          walks=tuple(args.walks.split(",")),
+                          walks=(tuple(args.walks.split(",")) if args.walks != "auto" else
+                                 ("breadth",) + tuple(f"breadth/{g}" for g in (2, 4)
+                                                      if world > 1 and (args.tokens // args.microbatch) % g == 0)),
                           trace_capacity=(1 << 16) if args.report else 0,
                           lora=({"rank": args.lora_rank, "alpha": 2.0 * args.lora_rank,
                                  "targets": ["wq", "wk", "wv", "wo", "w13", "w2"], "routed_experts": True,

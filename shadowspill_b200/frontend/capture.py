@@ -41,6 +41,8 @@ class StepDataOrdering:
     # reduce-scattered into a shard-sized fp32 accumulator, which the update of the last group
     # reads. 1 = one sweep over all microbatches.
     microbatch_groups: int = 1
+    # sharded storage, breadth walk: emit each weight gather one weight set before its first reader
+    gather_ahead: bool = True
 
     def label(self) -> str:
         return f"{self.walk}/{self.optimizer}" + (f"/groups{self.microbatch_groups}" if self.microbatch_groups > 1 else "")
@@ -185,6 +187,16 @@ def estimate_duration_ns(flops: float, nbytes: float, tflops: float = 1100.0,
     return int(max(flops / (tflops * 1e12), nbytes / (gbps * 1e9)) * 1e9) + 20_000
 
 
+def exposed_collective_ns(nbytes: float, world: int) -> int:
+    """What a collective on the communication stream costs the compute timeline. The planner's
+    timeline is one lane: a task's duration is how long the next task waits for it. The peer
+    kernels move ``(world - 1) / world`` of the bytes over NVLink (about 700 GB/s measured per
+    direction) while the compute stream keeps running; a traced two-GPU step showed the compute
+    stream idle for about a quarter of its collectives' time, which is the share charged here."""
+    remote = nbytes * (world - 1) / max(1, world)
+    return int(0.25 * remote / 700e9 * 1e9) + 20_000
+
+
 def _build(desc: TrainingDescription) -> Program:
     cfg, geo, order = desc.cfg, desc.geometry, desc.ordering
     stages = desc.stages()
@@ -281,7 +293,6 @@ def _build(desc: TrainingDescription) -> Program:
             for m in range(n_mb):
                 SAVED[(si, m)] = prog.add_object(ObjectSpec(f"{stages[si].name}.saved.{m}", sbytes,
                                                             "saved", stage=si, microbatch=m))
-    grad_created = [False] * S
     GG: dict[tuple[int, int], int] = {}       # (stage, group) -> that group's gradient object
     ACC: dict[int, int] = {}                  # stage -> fp32 shard-sized sum of the earlier groups
     acc_created: set[int] = set()
@@ -345,7 +356,7 @@ def _build(desc: TrainingDescription) -> Program:
             nbytes = full_bytes[si]
             prog.add_task(TaskSpec(f"AG.{st.name}.{tag}", "collective", si, -1,
                                    [UseSpec(W[si], "read", "shard"), UseSpec(obj, "create", "params")],
-                                   estimate_duration_ns(0.0, 2.0 * nbytes, gbps=600.0), 0,
+                                   exposed_collective_ns(nbytes, world), 0,
                                    "allgather", profile_key=f"allgather:{nbytes}:{world}"))
         return FULL[(si, tag)]
 
@@ -445,15 +456,36 @@ def _build(desc: TrainingDescription) -> Program:
         acc_created.add(si)
         prog.add_task(TaskSpec(f"RS.{st.name}.g{group_now[0]}", "collective", si, -1,
                                [UseSpec(grad_obj(si), "read", "grads"), UseSpec(ACC[si], mode, "acc")],
-                               estimate_duration_ns(0.0, 2.0 * gbytes, gbps=600.0), 0, "rs_accumulate",
+                               exposed_collective_ns(gbytes, world), 0, "rs_accumulate",
                                profile_key=f"rs_accumulate:{gbytes}:{world}"))
 
     body = list(range(S - 1))
     mbs = list(range(n_mb))
     back_mbs = list(reversed(mbs)) if order.reverse_breadth else mbs
     step = desc.mode == "step"      # from here on: does this program contain the update?
-    if order.walk == "breadth" and groups > 1:
+    if order.walk == "breadth":
         per_group = n_mb // groups
+        # the weight sets in the order the sweeps read them: a gather is emitted one set ahead of
+        # its first reader, so that it runs on the communication stream under the tasks before it
+        reads = [(si, "fwd") for si in body] + [(S - 1, "fwd")]
+        if train:
+            reads += [(si, "bwd") for si in reversed(body) if stages[si].kind != "embedding"]
+        ahead = sharded and order.gather_ahead and not desc.fused_gather
+
+        def gather_next(si: int, which: str, gi: int) -> None:
+            """Emits the gather of the weight set read after ``(si, which)`` of group ``gi``."""
+            if not ahead:
+                return
+            k = reads.index((si, which)) + 1 if (si, which) in reads else len(reads) + 1
+            if k > len(reads):
+                return
+            nxt, g_next = (reads[k], gi) if k < len(reads) else (reads[0], gi + 1)
+            if g_next >= groups:
+                return
+            keep, group_now[0] = group_now[0], g_next
+            params_of(*nxt)
+            group_now[0] = keep
+
         for gi in range(groups):
             group_now[0] = gi
             gm = mbs[gi * per_group:(gi + 1) * per_group]
@@ -462,32 +494,42 @@ def _build(desc: TrainingDescription) -> Program:
             def finish(si: int) -> None:
                 if not last:
                     accumulate(si)
-                elif order.optimizer == "stage_interleaved":
+                elif step and order.optimizer == "stage_interleaved":
                     opt(si)
             for si in body:
+                params_of(si, "fwd")
+                gather_next(si, "fwd", gi)
                 for m in gm:
                     fwd(si, m)
+            params_of(S - 1, "fwd")
+            gather_next(S - 1, "fwd", gi)
             for m in gm:
                 head(m)
-            finish(S - 1)
-            for si in reversed(body):
-                for m in (list(reversed(gm)) if order.reverse_breadth else gm):
-                    bwd(si, m)
-                finish(si)
-    elif order.walk == "breadth":
-        for si in body:
-            for m in mbs:
-                fwd(si, m)
-        for m in mbs:
-            head(m)
-        if step and order.optimizer == "stage_interleaved":
-            opt(S - 1)
-        if train:
-            for si in reversed(body):
-                for m in back_mbs:
-                    bwd(si, m)
-                if step and order.optimizer == "stage_interleaved":
-                    opt(si)
+            if train:
+                # Under sharded storage a stage's gradients are consumed on the communication
+                # stream (reduce-scatter into the sums, or the fused update), after a barrier that
+                # waits for the slowest rank. Emitted right after the stage's last backward task,
+                # the next stage's first backward task would create its gradients in the range
+                # those still occupy and wait for the collective; emitted one task later, both
+                # gradient buffers are live at once and the collective runs under the next tasks.
+                owed = None
+                if sharded:
+                    owed = S - 1
+                else:
+                    finish(S - 1)
+                for si in reversed(body):
+                    gather_next(si, "bwd", gi)
+                    for m in (list(reversed(gm)) if order.reverse_breadth else gm):
+                        bwd(si, m)
+                        if owed is not None:
+                            finish(owed)
+                            owed = None
+                    if sharded:
+                        owed = si
+                    else:
+                        finish(si)
+                if owed is not None:
+                    finish(owed)
     elif order.walk == "depth":
         for m in mbs:
             for si in body:

@@ -46,7 +46,7 @@ def test_microbatch_groups_accumulate_in_shard_space(arm):
     """Four microbatches as two forward + backward sweeps: the first sweep's gradients are
     reduce-scattered into fp32 shard sums, the update after the second sweep starts from them.
     Matches the single-process model on the same eight microbatches."""
-    _launch(2, "cpu", arm, 29671)
+    _launch(2, "cpu", arm, 29671 + 2 * ["groups-dist", "groups-lion-small-dist", "groups-master-small-dist"].index(arm))
 
 
 def test_whole_parameter_weights_load_into_sharded_ranks():
