@@ -23,6 +23,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace ss {
 
@@ -76,20 +77,36 @@ __global__ void peer_allgather_kernel(PeerPtrs shards, uint8_t* __restrict__ ful
                                       int world) {
   const long long vec_per_shard = shard_bytes >> 4;
   const long long nvec = vec_per_shard * world;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    // rotate the starting peer by rank so that the ranks do not all hit one peer at once
-    const int k0 = static_cast<int>(i / vec_per_shard);
-    const int k = (k0 + rank) % world;
-    const long long v = i - static_cast<long long>(k0) * vec_per_shard;
-    const long long off = static_cast<long long>(k) * shard_bytes + (v << 4);
-    if (off + 16 <= total_bytes) {
-      const uint4 val = reinterpret_cast<const uint4*>(shards.p[k])[v];
-      *reinterpret_cast<uint4*>(full + off) = val;
-    } else if (off < total_bytes) {
-      const uint8_t* src = reinterpret_cast<const uint8_t*>(shards.p[k]) + (v << 4);
-      for (long long b = 0; off + b < total_bytes; ++b) full[off + b] = src[b];
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  // four loads in flight per thread: the grid is kept small (it shares the SMs with the compute
+  // stream's kernels), so the bytes in flight have to come from each thread
+  for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < nvec;
+       i0 += 4 * stride) {
+    uint4 val[4];
+    long long off[4];
+    bool whole[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const long long i = i0 + q * stride;
+      whole[q] = false;
+      off[q] = -1;
+      if (i >= nvec) continue;
+      // rotate the starting peer by rank so that the ranks do not all hit one peer at once
+      const int k0 = static_cast<int>(i / vec_per_shard);
+      const int k = (k0 + rank) % world;
+      const long long v = i - static_cast<long long>(k0) * vec_per_shard;
+      off[q] = static_cast<long long>(k) * shard_bytes + (v << 4);
+      if (off[q] + 16 <= total_bytes) {
+        whole[q] = true;
+        val[q] = reinterpret_cast<const uint4*>(shards.p[k])[v];
+      } else if (off[q] < total_bytes) {
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(shards.p[k]) + (v << 4);
+        for (long long b = 0; off[q] + b < total_bytes; ++b) full[off[q] + b] = src[b];
+      }
     }
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      if (whole[q]) *reinterpret_cast<uint4*>(full + off[q]) = val[q];
   }
 }
 
@@ -123,6 +140,33 @@ __device__ __forceinline__ void up8(const uint4& u, float (&f)[8]) {
   }
 }
 
+// g[0..8) += the eight bf16 at element `elem` of every rank's tensor. Four peers' loads are in
+// flight at once, and the first peer is `rot` (a value that differs between ranks, so that the
+// ranks do not all read one peer at the same moment).
+__device__ __forceinline__ void add_peers_bf16x8(const PeerPtrs& grads, long long elem, int world,
+                                                 int rot, float (&g)[8]) {
+  for (int j0 = 0; j0 < world; j0 += 4) {
+    uint4 u[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      if (j0 + q < world) {
+        int j = j0 + q + rot;
+        if (j >= world) j -= world;
+        u[q] = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(grads.p[j]) + elem);
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      if (j0 + q < world) {
+        float f[8];
+        up8(u[q], f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) g[e] += f[e];
+      }
+    }
+  }
+}
+
 struct RsAdamArgs {
   float lr, beta1, beta2, eps, weight_decay, bias1, bias2, grad_scale;
   unsigned long long seed, offset;   // offset: global element index of the tensor's element 0
@@ -146,6 +190,7 @@ __global__ void rs_adamw_kernel(PeerPtrs grads, const __nv_bfloat16* __restrict_
                                 long long lo, long long hi, int world, RsAdamArgs a) {
   const long long n = hi - lo;
   const long long nvec = (n + 7) >> 3;
+  const int rot = n > 0 ? static_cast<int>((lo / n) % world) : 0;   // the owning rank; 0 for whole tensors
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long e0 = i << 3;
@@ -170,6 +215,8 @@ __global__ void rs_adamw_kernel(PeerPtrs grads, const __nv_bfloat16* __restrict_
       up8(u, f);
 #pragma unroll
       for (int e = 0; e < 8; ++e) g[e] += f[e];
+    } else if (!a.g_f32 && cnt == 8) {
+      add_peers_bf16x8(grads, lo + e0, world, rot, g);
     } else
     for (int j = 0; j < world; ++j) {
       if (a.g_f32) {
@@ -262,6 +309,7 @@ __global__ void rs_accumulate_kernel(PeerPtrs grads, float* __restrict__ acc, lo
     const long long e0 = i << 3;
     const int cnt = static_cast<int>(min(8LL, n - e0));
     float g[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const int rot = n > 0 ? static_cast<int>((lo / n) % world) : 0;
     if (!first) {
       if (cnt == 8) {
         const float4 x = *reinterpret_cast<const float4*>(acc + e0);
@@ -271,6 +319,9 @@ __global__ void rs_accumulate_kernel(PeerPtrs grads, float* __restrict__ acc, lo
         for (int e = 0; e < cnt; ++e) g[e] = acc[e0 + e];
       }
     }
+    if (!g_f32 && cnt == 8) {
+      add_peers_bf16x8(grads, lo + e0, world, rot, g);
+    } else
     for (int j = 0; j < world; ++j) {
       if (g_f32) {
         const float* src = reinterpret_cast<const float*>(grads.p[j]) + lo + e0;
@@ -314,6 +365,22 @@ __global__ void peer_allreduce_f32_kernel(PeerPtrs src, float* __restrict__ dst,
   }
 }
 
+// CTAs per SM that a collective kernel may take. These kernels run on the communication stream
+// beside the compute stream's GEMMs and wait on NVLink latency most of the time: a grid that
+// fills every thread slot of every SM (eight CTAs of 256 threads) keeps the compute kernels' CTAs
+// from being scheduled for as long as it runs. Two per SM leave three quarters of the slots free;
+// the bytes in flight come from four loads per thread instead. SS_COMM_CTAS_PER_SM overrides.
+static inline int comm_cap() {
+  static int cap = [] {
+    const char* e = getenv("SS_COMM_CTAS_PER_SM");
+    int v = e ? atoi(e) : 2;
+    if (v < 1) v = 1;
+    if (v > 8) v = 8;
+    return 148 * v;
+  }();
+  return cap;
+}
+
 static inline int grid_of(long long work, int threads, int cap) {
   long long g = (work + threads - 1) / threads;
   return static_cast<int>(g < 1 ? 1 : (g > cap ? cap : g));
@@ -347,7 +414,7 @@ int ss_peer_allgather(void* const* shard_ptrs, void* full, long long shard_bytes
   for (int j = 0; j < world; ++j) s.p[j] = shard_ptrs[j];
   const long long nvec = (shard_bytes >> 4) * world;
   if (nvec == 0) return 0;
-  peer_allgather_kernel<<<grid_of(nvec, 256, 148 * 8), 256, 0, (cudaStream_t)stream>>>(
+  peer_allgather_kernel<<<grid_of((nvec + 3) / 4, 256, comm_cap()), 256, 0, (cudaStream_t)stream>>>(
       s, (uint8_t*)full, shard_bytes, total_bytes, rank, world);
   return (int)cudaGetLastError();
 }
@@ -359,7 +426,7 @@ int ss_rs_accumulate(void* const* grad_ptrs, void* acc, long long lo, long long 
   PeerPtrs g;
   for (int j = 0; j < world; ++j) g.p[j] = grad_ptrs[j];
   const long long nvec = (hi - lo + 7) >> 3;
-  rs_accumulate_kernel<<<grid_of(nvec, 256, 148 * 8), 256, 0, (cudaStream_t)stream>>>(
+  rs_accumulate_kernel<<<grid_of(nvec, 256, comm_cap()), 256, 0, (cudaStream_t)stream>>>(
       g, (float*)acc, lo, hi, world, g_f32, first);
   return (int)cudaGetLastError();
 }
@@ -382,7 +449,7 @@ int ss_rs_adamw_acc(void* const* grad_ptrs, const void* acc, void* p, void* m, v
   a.seed = seed ^ (0x9E3779B97F4A7C15ull * (unsigned long long)(step + 1));
   a.offset = offset; a.sr_param = sr_param; a.sr_state = sr_state; a.g_f32 = g_f32;
   const long long nvec = (hi - lo + 7) >> 3;
-  rs_adamw_kernel<<<grid_of(nvec, 256, 148 * 8), 256, 0, (cudaStream_t)stream>>>(
+  rs_adamw_kernel<<<grid_of(nvec, 256, comm_cap()), 256, 0, (cudaStream_t)stream>>>(
       g, nullptr, (const float*)acc, (__nv_bfloat16*)p, (__nv_bfloat16*)m, (__nv_bfloat16*)v, lo, hi,
       world, a);
   return (int)cudaGetLastError();
@@ -403,7 +470,7 @@ int ss_rs_adamw(void* const* grad_ptrs, void* p, void* m, void* v, long long lo,
   a.seed = seed ^ (0x9E3779B97F4A7C15ull * (unsigned long long)(step + 1));
   a.offset = offset; a.sr_param = sr_param; a.sr_state = sr_state; a.g_f32 = g_f32;
   const long long nvec = (hi - lo + 7) >> 3;
-  rs_adamw_kernel<<<grid_of(nvec, 256, 148 * 8), 256, 0, (cudaStream_t)stream>>>(
+  rs_adamw_kernel<<<grid_of(nvec, 256, comm_cap()), 256, 0, (cudaStream_t)stream>>>(
       g, nullptr, nullptr, (__nv_bfloat16*)p, (__nv_bfloat16*)m, (__nv_bfloat16*)v, lo, hi, world, a);
   return (int)cudaGetLastError();
 }
@@ -429,7 +496,7 @@ int ss_rs_adamw_nvls(void* const* grad_ptrs, const void* mc_grad, void* p, void*
   a.seed = seed ^ (0x9E3779B97F4A7C15ull * (unsigned long long)(step + 1));
   a.offset = offset; a.sr_param = sr_param; a.sr_state = sr_state; a.g_f32 = 0;
   const long long nvec = (hi - lo + 7) >> 3;
-  rs_adamw_kernel<<<grid_of(nvec, 256, 148 * 8), 256, 0, (cudaStream_t)stream>>>(
+  rs_adamw_kernel<<<grid_of(nvec, 256, comm_cap()), 256, 0, (cudaStream_t)stream>>>(
       g, (const __nv_bfloat16*)mc_grad, nullptr, (__nv_bfloat16*)p, (__nv_bfloat16*)m, (__nv_bfloat16*)v,
       lo, hi, world, a);
   return (int)cudaGetLastError();

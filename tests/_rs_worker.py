@@ -83,12 +83,16 @@ def main():
         want = wants[0]
         for idx, (name, got, ref_full, old) in enumerate((("p", p, want[0], p_full), ("m", m, want[1], m_full),
                                                           ("v", v, want[2], v_full))):
-            ref = ref_full[lo:hi]
-            err = torch.stack([(got[:hi - lo].float() - w[idx][lo:hi]).abs() for w in wants]).min(0).values
-            # one unit in the last place of the result (twice that where the in-switch sum was rounded),
-            # plus the fp32 rounding of the terms themselves, which matters where they cancel
+            # one unit in the last place of the result, plus the fp32 rounding of the terms themselves,
+            # which matters where they cancel. With the in-switch sum the result may follow any of the
+            # candidate sums, each judged against the spacing at ITS result: where the terms cancel, a
+            # neighbouring sum gives a result orders of magnitude larger than the nearest one does
             terms = old[lo:hi].float().abs() + (g_sum[lo:hi] * hyper["grad_scale"]).abs() + 1e-3
-            tol = ulp_bf16(ref) * (2.5 if nvls else 1.01) + 4e-7 * terms
+            good = torch.zeros(hi - lo, dtype=torch.bool, device=dev)
+            for w in wants:
+                ref = w[idx][lo:hi]
+                good |= (got[:hi - lo].float() - ref).abs() <= ulp_bf16(ref) * 1.01 + 4e-7 * terms
+            err, tol = (~good).float(), 0.5
             bad = int((err > tol).sum())
             # a slice of a few elements may round back to where it was; a real slice must move
             moved = float((got[:hi - lo].float() - old[lo:hi].float()).abs().max()) if hi - lo >= 64 else 1.0
