@@ -165,7 +165,7 @@ class TrainingDescription:
             if supports(self.cfg, self.lora, ep, self.objective):
                 stages = build_graph_stages(self.cfg, self.geometry.microbatch_tokens, self.geometry.slots,
                                             self.dtype, self.grad_dtype, self.head_block_rows,
-                                            chunk_rows=self.axis_chunk_rows)
+                                            chunk_rows=self.axis_chunk_rows, lora=self.lora)
                 for st in stages:
                     st.min_shard_bytes = int(self.min_shard_bytes)
                 return stages

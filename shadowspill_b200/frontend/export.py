@@ -213,7 +213,11 @@ def partition_export(ep, policy: "str | PartitionPolicy" = "auto") -> ExportedSt
             raise ValueError(f"stage {si} reads {[b.name for b in boundary]} from earlier stages: "
                              "exactly one activation may cross a stage boundary")
         # placeholders in a canonical order: parameters (model order), boundary, batch fields
-        order = {name: i for i, name in enumerate(param_of)}
+        # (the model's registration order, not the order of first use that the export signature has:
+        # seed-only initialisation draws parameters in this order, whichever frontend built the stage)
+        registered = {target: i for i, target in enumerate(ep.state_dict)}
+        order = {name: (registered.get(target, len(registered)), i)
+                 for i, (name, target) in enumerate(param_of.items())}
         params.sort(key=lambda a: order[a.name])
         batch.sort(key=lambda a: user_inputs.index(a.name))
         name = pol.names(si) if pol.names else f"stage{si}"

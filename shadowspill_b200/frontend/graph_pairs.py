@@ -353,6 +353,8 @@ def rewrite_destinations(bwd: fx.GraphModule, param_grads: dict[int, str], dest_
     its producer has an in-place form, feed it the destination (new placeholders ``grad_<name>``
     and ``first``) and make the output the destination itself. Returns the parameters handled."""
     g = bwd.graph
+    if not param_grads:                  # a stage whose parameters are all frozen
+        return set()
     out_node = next(n for n in g.nodes if n.op == "output")
     outs = list(out_node.args[0])
     last_ph = [n for n in g.nodes if n.op == "placeholder"][-1]

@@ -372,25 +372,30 @@ def supports(cfg, lora=None, expert_parallel=None, objective=None) -> bool:
     """Catalog models the ``nn.Module`` families of :mod:`.modules` cover."""
     plain_objective = objective is None or (getattr(objective, "kind", "cross_entropy") == "cross_entropy"
                                             and not getattr(objective, "moe_balance_coef", 0))
-    return (cfg.family != "regression" and lora is None and expert_parallel is None and plain_objective
+    if lora is not None and cfg.is_moe and lora.routed_experts:
+        # ss::moe_experts_lora adapts both banks of frozen experts; other mixes stay on the stage classes
+        banks = {"w13", "w2"} & set(lora.targets)
+        if (banks and banks != {"w13", "w2"}) or (banks and lora.train_base):
+            return False
+    return (cfg.family != "regression" and expert_parallel is None and plain_objective
             and not (cfg.is_moe and cfg.router_aux_coef > 0))
 
 
 def build_graph_stages(cfg, T: int, slots: int, dtype: torch.dtype = torch.bfloat16,
                        grad_dtype: torch.dtype | None = None, head_block_rows: int = 0,
-                       module: nn.Module | None = None, chunk_rows: int = 0) -> list[Stage]:
+                       module: nn.Module | None = None, chunk_rows: int = 0, lora=None) -> list[Stage]:
     """The stage list of ``cfg`` (or of ``module``) through the graph frontend. ``chunk_rows`` > 0
     runs the token-local regions of every layer stage in row chunks of that many tokens."""
     from .modules import DecoderLM
     block = head_block_rows or 2048
     key = (cfg.to_json() if module is None else id(module), T, slots, str(dtype), str(grad_dtype), block,
-           chunk_rows)
+           chunk_rows, lora.to_json() if lora is not None else None)
     with _cache_lock:
         hit = _cache.get(str(key))
     if hit is None:
         if module is None:
             with torch.device("meta"):
-                module = DecoderLM(cfg, dtype, block)
+                module = DecoderLM(cfg, dtype, block, lora)
         hit = capture_module(module, _example_batch(T, slots), grad_dtype=grad_dtype or dtype, model_dtype=dtype)
         if 0 < chunk_rows < T:
             from .chunking import chunk_pairs, peak_intermediate_bytes

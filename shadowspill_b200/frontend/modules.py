@@ -28,9 +28,10 @@ def _param(shape, init: str = "normal", std: float = 0.02, dtype=None, trainable
 
 
 class Embedding(nn.Module):
-    def __init__(self, cfg: DecoderConfig, dtype):
+    def __init__(self, cfg: DecoderConfig, dtype, trainable: bool = True):
         super().__init__()
-        self.embed = _param((cfg.vocab_size, cfg.d_model), std=cfg.initializer_range, dtype=dtype)
+        self.embed = _param((cfg.vocab_size, cfg.d_model), std=cfg.initializer_range, dtype=dtype,
+                            trainable=trainable)
 
     def forward(self, tokens):
         return S.embedding(tokens, self.embed)
@@ -38,20 +39,59 @@ class Embedding(nn.Module):
 
 class _Norms:
     """Shared helpers of the layer modules."""
+    lora = None
+    adapted: frozenset = frozenset()
 
     def _norm(self, x, w):
         c = self.cfg
         return S.rmsnorm(x, w, c.norm_epsilon, c.zero_centered_norm)[0]
 
+    def _lin(self, x, name: str):
+        """``x W^T``, plus ``(alpha / r) (x A^T) B^T`` where ``W`` carries adapter factors."""
+        y = S.linear(x, getattr(self, name))
+        if name in self.adapted:
+            low = S.linear(S.linear(x, getattr(self, f"{name}_lora_a")), getattr(self, f"{name}_lora_b"))
+            y = y + low * self.lora.scale
+        return y
+
+    def _adapt(self, lora, dtype) -> None:
+        """Adds the low-rank factors of every targeted matrix (and expert bank) of this layer and,
+        unless the base trains too, freezes everything else: frozen parameters get no gradient
+        object, no moments and no update task (models/lora.py; the reference's ``configure_lora``,
+        packages/workloads/src/shadowspill_workloads/lora/__init__.py:16)."""
+        if lora is None:
+            return
+        self.lora = lora
+        base = dict(self.named_parameters(recurse=False))
+        adapted = set()
+        for name, p in base.items():
+            is_bank = p.dim() == 3
+            if name not in lora.targets or p.dim() < 2 or (is_bank and not lora.routed_experts):
+                continue
+            lead = tuple(p.shape[:-2])
+            setattr(self, f"{name}_lora_a", _param(lead + (lora.rank, p.shape[-1]), std=self.cfg.initializer_range,
+                                                   dtype=dtype))
+            setattr(self, f"{name}_lora_b", _param(lead + (p.shape[-2], lora.rank), "zeros", dtype=dtype))
+            adapted.add(name)
+        self.adapted = frozenset(adapted)
+        if not lora.train_base:
+            for p in base.values():
+                p.requires_grad_(False)
+
     def _mlp(self, x):
         h = self._norm(x, self.mlp_norm)
         c = self.cfg
         if not c.is_moe:
-            return x + S.linear(S.swiglu(S.linear(h, self.w13)), self.w2)
+            return x + self._lin(S.swiglu(self._lin(h, "w13")), "w2")
         logits = S.linear(h, self.router).float()
-        out = S.moe_experts(h, logits, self.w13, self.w2, c.top_k, c.router_renormalize)
+        if "w13" in self.adapted:       # both banks carry per-expert factors (see graph_stage.supports)
+            out = S.moe_experts_lora(h, logits, self.w13, self.w2, self.w13_lora_a, self.w13_lora_b,
+                                     self.w2_lora_a, self.w2_lora_b, c.top_k, c.router_renormalize,
+                                     float(self.lora.scale))
+        else:
+            out = S.moe_experts(h, logits, self.w13, self.w2, c.top_k, c.router_renormalize)
         if c.d_shared_expert:
-            shared = S.linear(S.swiglu(S.linear(h, self.sw13)), self.sw2)
+            shared = self._lin(S.swiglu(self._lin(h, "sw13")), "sw2")
             if c.gated_shared_expert:
                 shared = shared * torch.sigmoid(h.float() @ self.shared_gate.float()).to(h.dtype)[:, None]
             out = out + shared
@@ -100,7 +140,7 @@ class DenseLayer(nn.Module, _Norms):
 class HybridLayer(nn.Module, _Norms):
     """Gated DeltaNet or (gated) full attention mixer + dense SwiGLU feed-forward."""
 
-    def __init__(self, cfg: DecoderConfig, index: int, dtype):
+    def __init__(self, cfg: DecoderConfig, index: int, dtype, lora=None):
         super().__init__()
         self.cfg, self.index = cfg, index
         self.mixer = cfg.layer_kind(index)
@@ -141,14 +181,15 @@ class HybridLayer(nn.Module, _Norms):
         else:
             self.w13 = _param((2 * c.d_ff, D), std=std, dtype=dtype)
             self.w2 = _param((D, c.d_ff), std=std, dtype=dtype)
+        self._adapt(lora, dtype)
 
     def _attention(self, h, positions, cu_seqlens):
         c = self.cfg
         T = h.shape[0]
         dh, Hq, Hkv = c.head_dim, c.n_heads, c.n_kv_heads
-        qg = S.linear(h, self.wq)
+        qg = self._lin(h, "wq")
         q, gate = (qg[:, :Hq * dh], qg[:, Hq * dh:]) if c.gated_attention else (qg, None)
-        k, v = S.linear(h, self.wk), S.linear(h, self.wv)
+        k, v = self._lin(h, "wk"), self._lin(h, "wv")
         if c.qk_norm and c.qk_norm_full_width:
             q, k = self._norm(q, self.q_norm), self._norm(k, self.k_norm)
         elif c.qk_norm:
@@ -160,14 +201,14 @@ class HybridLayer(nn.Module, _Norms):
         att = att.reshape(T, Hq * dh)
         if gate is not None:
             att = att * torch.sigmoid(gate.float()).to(att.dtype)
-        return S.linear(att, self.wo)
+        return self._lin(att, "wo")
 
     def _deltanet(self, h, positions, cu_seqlens):
         c = self.cfg
         T = h.shape[0]
         Hk, Hv, dk = c.dn_qk_heads, c.dn_v_heads, c.dn_head_dim
         kw, cw = self.key_width, self.conv_width
-        qkvz = S.linear(h, self.w_qkvz)
+        qkvz = self._lin(h, "w_qkvz")
         ba = S.linear(h, self.w_ba)
         conv = S.conv_silu(qkvz[:, :cw], self.conv_w, positions, cu_seqlens)
         q = S.l2norm(conv[:, :kw].reshape(T, Hk, dk), 1e-6)
@@ -178,7 +219,7 @@ class HybridLayer(nn.Module, _Norms):
         mixed = S.gated_delta_rule(q, k, v, beta, g, cu_seqlens, c.dn_chunk)
         gate = qkvz[:, cw:].reshape(T, Hv, dk)
         normed = S.gated_rmsnorm(mixed, gate, self.lin_norm, c.norm_epsilon, c.zero_centered_norm)
-        return S.linear(normed.reshape(T, Hv * dk), self.w_out)
+        return self._lin(normed.reshape(T, Hv * dk), "w_out")
 
     def forward(self, x, positions, cu_seqlens):
         h = self._norm(x, self.attn_norm)
@@ -189,13 +230,14 @@ class HybridLayer(nn.Module, _Norms):
 class Head(nn.Module):
     """Final norm + output projection + masked weighted-sum cross entropy in row blocks."""
 
-    def __init__(self, cfg: DecoderConfig, dtype, block_rows: int = 2048):
+    def __init__(self, cfg: DecoderConfig, dtype, block_rows: int = 2048, trainable: bool = True):
         super().__init__()
         self.cfg, self.block_rows = cfg, block_rows
         ninit = "zeros" if cfg.zero_centered_norm else "ones"
-        self.final_norm = _param((cfg.d_model,), ninit, dtype=dtype)
+        self.final_norm = _param((cfg.d_model,), ninit, dtype=dtype, trainable=trainable)
         if not cfg.tied_embeddings:
-            self.head = _param((cfg.vocab_size, cfg.d_model), std=cfg.initializer_range, dtype=dtype)
+            self.head = _param((cfg.vocab_size, cfg.d_model), std=cfg.initializer_range, dtype=dtype,
+                               trainable=trainable)
 
     def forward(self, x, targets, weights, tied=None):
         c = self.cfg
@@ -207,16 +249,21 @@ class Head(nn.Module):
 class DecoderLM(nn.Module):
     """``forward(tokens, targets, weights, positions, cu_seqlens) -> loss[1]``."""
 
-    def __init__(self, cfg: DecoderConfig, dtype=torch.bfloat16, head_block_rows: int = 2048):
+    def __init__(self, cfg: DecoderConfig, dtype=torch.bfloat16, head_block_rows: int = 2048, lora=None):
+        """``lora`` (a ``models.lora.LoRAConfig``): every layer is the form with separate q / k / v
+        projections (the adapter targets), carries the factors, and the base is frozen unless
+        ``lora.train_base``."""
         super().__init__()
         self.cfg = cfg
-        self.embed = Embedding(cfg, dtype)
+        base = lora is None or lora.train_base
+        self.embed = Embedding(cfg, dtype, base)
         layers = []
         for i in range(cfg.n_layers):
-            plain = cfg.layer_kind(i) == "attention" and not cfg.gated_attention and not cfg.is_moe
-            layers.append(DenseLayer(cfg, dtype) if plain else HybridLayer(cfg, i, dtype))
+            plain = (cfg.layer_kind(i) == "attention" and not cfg.gated_attention and not cfg.is_moe
+                     and lora is None)
+            layers.append(DenseLayer(cfg, dtype) if plain else HybridLayer(cfg, i, dtype, lora))
         self.layers = nn.ModuleList(layers)
-        self.head = Head(cfg, dtype, head_block_rows)
+        self.head = Head(cfg, dtype, head_block_rows, base)
 
     def forward(self, tokens, targets, weights, positions, cu_seqlens):
         x = self.embed(tokens)

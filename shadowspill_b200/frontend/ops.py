@@ -562,6 +562,26 @@ def _(h, logits, w13, w2, gy, k, renorm):
             torch.empty_like(w13), torch.empty_like(w2))
 
 
+@custom_op("ss::moe_experts_bwd_frozen", mutates_args=())
+def moe_experts_bwd_frozen(h: Tensor, logits: Tensor, w13: Tensor, w2: Tensor, gy: Tensor, k: int,
+                           renorm: bool) -> tuple[Tensor, Tensor]:
+    """Backward of the routed experts when the banks are frozen: the gradients of the rows and of
+    the router logits only; no bank-sized gradient is computed or allocated."""
+    if h.is_cuda and F._cuda(h):
+        from ..models.autograd_ops import GradSink
+        from ..ops import moe as moe_ops
+        sink = GradSink({}, False)
+        return _autograd_elsewhere(lambda a, b: moe_ops.experts(a, b, w13, w2, k, renorm, sink),
+                                   (_c(h), _c(logits)), _c(gy))
+    return _autograd_elsewhere(lambda a, b: _moe_torch(a, b, w13, w2, k, renorm), (h, logits), gy)
+
+
+@moe_experts_bwd_frozen.register_fake
+def _(h, logits, w13, w2, gy, k, renorm):
+    return (torch.empty_like(h, memory_format=torch.contiguous_format),
+            torch.empty_like(logits, memory_format=torch.contiguous_format))
+
+
 def _moe_setup(ctx, inputs, output):
     ctx.save_for_backward(*inputs[:4])
     ctx.k, ctx.renorm = inputs[4], inputs[5]
@@ -569,6 +589,9 @@ def _moe_setup(ctx, inputs, output):
 
 def _moe_bwd(ctx, gy):
     h, logits, w13, w2 = ctx.saved_tensors
+    if not (ctx.needs_input_grad[2] or ctx.needs_input_grad[3]):
+        dh, dl = torch.ops.ss.moe_experts_bwd_frozen(h, logits, w13, w2, gy, ctx.k, ctx.renorm)
+        return dh, dl, None, None, None, None
     dh, dl, d13, d2 = torch.ops.ss.moe_experts_bwd(h, logits, w13, w2, gy, ctx.k, ctx.renorm)
     return dh, dl, d13, d2, None, None
 
@@ -576,7 +599,110 @@ def _moe_bwd(ctx, gy):
 moe_experts.register_autograd(_moe_bwd, setup_context=_moe_setup)
 
 
+# ------------------------------------------------------------------------ routed experts with adapters
+def _moe_lora_torch(h, logits, w13, w2, a13, b13, a2, b2, k: int, renorm: bool, scale: float) -> Tensor:
+    """``_moe_torch`` with per-expert low-rank factors on both banks (the definition; CPU form)."""
+    if renorm:
+        vals, ids = torch.topk(logits, k, dim=-1)
+        wts = torch.softmax(vals, dim=-1)
+    else:
+        wts, ids = torch.topk(torch.softmax(logits, dim=-1), k, dim=-1)
+    flat = ids.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=w13.shape[0]).tolist()
+    tok = order // k
+    w_sorted = wts.reshape(-1)[order].to(h.dtype)
+    out = torch.zeros_like(h)
+    pos = 0
+    for e, n in enumerate(counts):
+        if n == 0:
+            continue
+        rows = tok[pos:pos + n]
+        x = h.index_select(0, rows)
+        gu = x @ w13[e].t() + ((x @ a13[e].t()) @ b13[e].t()) * scale
+        f = gu.shape[1] // 2
+        act = (torch.nn.functional.silu(gu[:, :f].float()).to(h.dtype) * gu[:, f:])
+        y = act @ w2[e].t() + ((act @ a2[e].t()) @ b2[e].t()) * scale
+        out = out.index_add(0, rows, y * w_sorted[pos:pos + n, None])
+        pos += n
+    return out
+
+
+def _moe_lora_cuda(h, logits, w13, w2, a13, b13, a2, b2, k: int, renorm: bool, scale: float, sink):
+    """The same on the grouped tcgen05 GEMMs: gather into expert order, grouped linear per bank
+    plus the two thin grouped products of its factors, combine. ``sink`` receives the factor
+    gradients (names ``a13`` / ``b13`` / ``a2`` / ``b2``) when this runs under autograd."""
+    from ..models import autograd_ops as A
+    from ..ops import moe as moe_ops
+    ids, _, counts = moe_ops.route(logits.detach(), k, renorm)
+    wts = moe_ops._weights_from_logits(logits, ids.long(), renorm)
+    lay = moe_ops.Layout(ids, counts)
+    xs = A.expert_gather(h, lay)
+
+    def bank(x, w, a, b, an, bn):
+        low = A.grouped_linear(A.grouped_linear(x, a, lay, sink, an), b, lay, sink, bn)
+        return A.grouped_linear(x, w, lay, None, "") + low * scale
+    ys = bank(A.swiglu(bank(xs, w13, a13, b13, "a13", "b13")), w2, a2, b2, "a2", "b2")
+    return A.expert_combine(ys, wts.float().contiguous(), lay)
+
+
+@custom_op("ss::moe_experts_lora", mutates_args=())
+def moe_experts_lora(h: Tensor, logits: Tensor, w13: Tensor, w2: Tensor, a13: Tensor, b13: Tensor,
+                     a2: Tensor, b2: Tensor, k: int, renorm: bool, scale: float) -> Tensor:
+    with torch.no_grad():
+        if h.is_cuda and F._cuda(h):
+            return _moe_lora_cuda(_c(h), _c(logits), w13, w2, a13, b13, a2, b2, k, renorm, scale, None)
+        return _moe_lora_torch(h, logits, w13, w2, a13, b13, a2, b2, k, renorm, scale)
+
+
+@moe_experts_lora.register_fake
+def _(h, logits, w13, w2, a13, b13, a2, b2, k, renorm, scale):
+    return torch.empty_like(h, memory_format=torch.contiguous_format)
+
+
+@custom_op("ss::moe_experts_lora_bwd", mutates_args=())
+def moe_experts_lora_bwd(h: Tensor, logits: Tensor, w13: Tensor, w2: Tensor, a13: Tensor, b13: Tensor,
+                         a2: Tensor, b2: Tensor, gy: Tensor, k: int, renorm: bool, scale: float
+                         ) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
+    """Gradients of rows, router logits and the four factor banks; the frozen banks get none."""
+    if h.is_cuda and F._cuda(h):
+        from ..models.autograd_ops import GradSink
+        G = {"a13": torch.zeros_like(a13), "b13": torch.zeros_like(b13),
+             "a2": torch.zeros_like(a2), "b2": torch.zeros_like(b2)}     # experts without rows: zero
+        sink = GradSink(G, False)
+        dh, dl = _autograd_elsewhere(
+            lambda x, l: _moe_lora_cuda(x, l, w13, w2, a13, b13, a2, b2, k, renorm, scale, sink),
+            (_c(h), _c(logits)), _c(gy))
+        return dh, dl, G["a13"], G["b13"], G["a2"], G["b2"]
+    return _autograd_elsewhere(
+        lambda x, l, p, q, r, s: _moe_lora_torch(x, l, w13, w2, p, q, r, s, k, renorm, scale),
+        (h, logits, a13, b13, a2, b2), gy)
+
+
+@moe_experts_lora_bwd.register_fake
+def _(h, logits, w13, w2, a13, b13, a2, b2, gy, k, renorm, scale):
+    return (torch.empty_like(h, memory_format=torch.contiguous_format),
+            torch.empty_like(logits, memory_format=torch.contiguous_format),
+            torch.empty_like(a13), torch.empty_like(b13), torch.empty_like(a2), torch.empty_like(b2))
+
+
+def _moe_lora_setup(ctx, inputs, output):
+    ctx.save_for_backward(*inputs[:8])
+    ctx.k, ctx.renorm, ctx.scale = inputs[8], inputs[9], inputs[10]
+
+
+def _moe_lora_bwd(ctx, gy):
+    if ctx.needs_input_grad[2] or ctx.needs_input_grad[3]:
+        raise NotImplementedError("ss::moe_experts_lora trains the factors of frozen banks only")
+    grads = torch.ops.ss.moe_experts_lora_bwd(*ctx.saved_tensors, gy, ctx.k, ctx.renorm, ctx.scale)
+    return grads[0], grads[1], None, None, grads[2], grads[3], grads[4], grads[5], None, None, None
+
+
+moe_experts_lora.register_autograd(_moe_lora_bwd, setup_context=_moe_lora_setup)
+
+
 MEMORY_BOUND = ("ss.rmsnorm", "ss.rope", "ss.swiglu", "ss.l2norm", "ss.conv_silu", "ss.gated_rmsnorm",
                 "ss.embedding")
 # Operators dominated by tensor-core work: keeping their outputs saves real time.
-COMPUTE_BOUND = ("ss.linear", "ss.gemm", "ss.attention", "ss.gated_delta_rule", "ss.head_loss", "ss.moe_experts")
+COMPUTE_BOUND = ("ss.linear", "ss.gemm", "ss.attention", "ss.gated_delta_rule", "ss.head_loss", "ss.moe_experts",
+                 "ss.moe_experts_lora")

@@ -190,7 +190,12 @@ class TrainingSession:
         from ..models.objectives import Objective
         self.lora = LoRAConfig.from_json(setup.lora)
         self.objective = Objective.from_json(setup.objective) if setup.objective else None
-        if self.lora is not None or setup.expert_parallel:
+        graph_covers = False
+        if setup.frontend == "graph":
+            from ..frontend.graph_stage import supports
+            graph_covers = supports(self.cfg, self.lora, (world, rank) if setup.expert_parallel else None,
+                                    self.objective)
+        if (self.lora is not None or setup.expert_parallel) and not graph_covers:
             # these layers run through the autograd-derived stage, which only recomputes
             selections = [{}]
             variants = [(walk, {}) for walk in setup.walks]

@@ -111,6 +111,52 @@ def test_planned_graph_frontend_matches_the_resident_trainer(name):
     ex.close()
 
 
+@pytest.mark.parametrize("name", ["llama3-tiny", "qwen35-tiny", "qwen35moe-tiny"])
+def test_low_rank_adapters_train_through_the_graph_frontend(name):
+    """Adapters on the attention and feed-forward matrices (and on both expert banks) of a frozen
+    base: the exported stages carry the factors, frozen parameters have no gradient, moment or
+    update, the layers get save variants, and three planned updates equal the resident trainer's."""
+    from shadowspill_b200.models.lora import LoRAConfig
+    cfg = preset(name)
+    lora = LoRAConfig(rank=8, alpha=16.0, targets=("wq", "wk", "wv", "wo", "w13", "w2", "w_qkvz", "w_out"))
+    sel = {1: "save", 2: "save_attention"}
+    prog, desc = build_step(cfg, GEO, StepDataOrdering(), dtype=torch.float32, selection=sel, frontend="graph",
+                            lora=lora)
+    stages = desc.stages()
+    assert type(stages[1]).__name__ == "GraphStage"                  # not the stage-class fallback
+    assert len(stages[1].SAVE_SETS["save"]) > 0
+    assert {p.name for p in stages[1].params if p.trainable} == {p.name for p in stages[1].params
+                                                                 if "_lora_" in p.name}
+    assert not any(t.name.startswith(("O.embed", "O.head", "B.embed")) for t in prog.tasks)
+    full, _ = build_step(cfg, GEO, StepDataOrdering(), dtype=torch.float32, selection=sel, frontend="graph")
+    state = lambda p: sum(o.bytes for o in p.objects if o.kind in ("gradient", "optimizer_state"))
+    assert state(prog) < 0.25 * state(full)
+    if cfg.is_moe:
+        ops = [op_name(n) for n in stages[1].pairs.pairs["recompute"].backward.graph.nodes]
+        assert "ss.moe_experts_lora_bwd" in ops and "ss.moe_experts_bwd" not in ops
+    plan = _plan(prog)
+    ex = Executor(plan, desc, device="cpu", seed=5, hyper=Hyperparameters(lr=1e-2))
+    ex.initialize()
+    ref = ResidentTrainer(cfg, device="cpu", dtype=torch.float32, seed=5, lr=1e-2, lora=lora)
+    for step in range(3):
+        host = _batches(cfg, step)
+        res = ex.run(host)
+        want = ref.step([to_device(m, "cpu") for m in host])
+        assert abs(res.loss - want) < 1e-5 * max(1.0, abs(want)), (step, res.loss, want)
+    got = ex.state_dict()
+    moved = 0.0
+    for k, v in ref.state_dict().items():
+        if k.startswith("exp_avg"):
+            continue
+        diff = (got[k] - v).float()
+        assert float(diff.abs().max()) <= 2 * 1e-2 + 1e-6, k
+        assert float(diff.norm() / v.float().norm().clamp_min(1e-9)) < 3e-3 or float(v.float().norm()) < 1e-3, k
+        if k.endswith("_lora_b"):
+            moved = max(moved, float(got[k].abs().max()))
+    assert moved > 0                      # the zero-initialised factors were trained
+    ex.close()
+
+
 @pytest.mark.parametrize("name", ["llama3-tiny", "qwen3-tiny", "qwen35-tiny"])
 def test_axis_chunked_stage_graphs_compute_the_same_step(name):
     """Row-chunking the token-local regions of every layer graph (projections, norms, MLP; the
@@ -263,17 +309,24 @@ def test_plumbing_config_twenty_steps_match_eager_pytorch():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("name", ["llama3-small", "qwen35-numerical-small"])
+@pytest.mark.parametrize("name", ["llama3-small", "qwen35-numerical-small", "qwen35moe-lora-small"])
 def test_graph_frontend_on_the_gpu_matches_the_stage_classes(name):
     """bf16 on the GPU: the exported graphs run the same sm_100a kernels as the hand-written stages,
     so two planned updates give the same losses and weights up to bf16 rounding of reordered sums."""
     from dataclasses import replace
     from shadowspill_b200.data.synthetic import make_batch
     from shadowspill_b200.ops import _lib
+    lora = None
     if name == "qwen35-numerical-small":
         # DeltaNet heads of width 128 (the chunk kernels), two layers of each mixer kind
         cfg = replace(preset("qwen35-numerical"), n_layers=4, d_model=512, d_ff=1024, n_heads=4, n_kv_heads=2,
                       head_dim=128, dn_qk_heads=2, dn_v_heads=4, vocab_size=2048)
+    elif name == "qwen35moe-lora-small":
+        # adapters on attention, DeltaNet and both expert banks of a frozen routed hybrid
+        from shadowspill_b200.models.lora import LoRAConfig
+        cfg = replace(preset("qwen35moe-tiny"), n_layers=4, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64,
+                      dn_qk_heads=2, dn_v_heads=4, dn_head_dim=128, vocab_size=2048)
+        lora = LoRAConfig(rank=16, alpha=32.0, targets=("wq", "wk", "wv", "wo", "w13", "w2", "w_qkvz", "w_out"))
     else:
         cfg = replace(preset("llama3-tiny"), d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, d_ff=512)
     geo = BatchGeometry(microbatch_tokens=1024, n_microbatches=2, slots=33, mean_seqlen=256)
@@ -281,7 +334,9 @@ def test_graph_frontend_on_the_gpu_matches_the_stage_classes(name):
     losses, states = {}, {}
     for frontend in ("stages", "graph"):
         prog, desc = build_step(cfg, geo, StepDataOrdering(), dtype=torch.bfloat16,
-                                selection=sel if frontend == "graph" else {}, frontend=frontend)
+                                selection=sel if frontend == "graph" else {}, frontend=frontend, lora=lora)
+        if frontend == "graph":
+            assert type(desc.stages()[1]).__name__ == "GraphStage"
         plan = _plan(prog, pct_from=60, spill=1 << 30)
         ex = Executor(plan, desc, device="cuda", seed=11, hyper=Hyperparameters(lr=1e-3),
                       stochastic_rounding=False)
@@ -301,5 +356,14 @@ def test_graph_frontend_on_the_gpu_matches_the_stage_classes(name):
             continue
         w = states["graph"][k].float()
         rel = float((w - v.float()).norm() / v.float().norm().clamp_min(1e-9))
+        if k.endswith("_lora_b"):
+            # starts at zero and moves by about lr per update whatever the gradient's size: compare directions
+            cos = float(torch.dot(w.flatten(), v.float().flatten()) / (w.norm() * v.float().norm()).clamp_min(1e-12))
+            assert cos > 0.8, (k, cos)
+            continue
+        if k.endswith("_lora_a"):
+            # one update of about lr on values of size 0.02: a flipped sign is a 10 % change of that element
+            assert rel < 6e-2, (k, rel)
+            continue
         # norm vectors see the sum of many bf16-rounded terms in a different order
         assert rel < (5e-2 if v.dim() == 1 else 2.5e-2), (k, rel)
