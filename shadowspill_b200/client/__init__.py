@@ -9,11 +9,13 @@
 from .config import (BatchConfig, BuildOptions, Execution, LoRA, Memory, Model, Objective,  # noqa: F401
                      Operation, Optimizer, PlanningOptions, Policy, Preparation, ProfilingOptions,
                      Resources, Weights)
-from .display import CommandTable  # noqa: F401
-from .packing import BatchError, BatchValidator, pack_batch  # noqa: F401
+from .display import BatchStatistics, CommandTable, LengthStatistics  # noqa: F401
+from .metrics import MetricPage, MetricQueries  # noqa: F401
+from .packing import (Assignment, BatchError, BatchValidation, BatchValidator, CoverageBound,  # noqa: F401
+                      assign_bins, pack_batch)
 from .parallelism import MIN_SHARD_BYTES, data_parallel, expert_parallel  # noqa: F401
 from .schedules import Constant, WarmupCosine  # noqa: F401
 from .service import ServiceClient  # noqa: F401
 from .text import (Datum, build_candidates, policy_datum, tensor_datum, text_batch,  # noqa: F401
-                   text_datum)
+                   text_batch_statistics, text_datum)
 from .training import OperationFailed, TrainingClient, TrainingResult  # noqa: F401

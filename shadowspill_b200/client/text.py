@@ -101,3 +101,11 @@ def build_candidates(projection_chunks=(), moe_chunks=(), retention=("cost-input
                         {"id": "shadowspill/text_chunks@1", "config": {"projection": pc, "moe": mc, "rows": rows}},
                         {"id": "shadowspill/text_retention@1", "config": {"rule": r}}]})
     return {"cases": cases, "recompute_shares": list(recompute_shares)}
+
+
+def text_batch_statistics(datums):
+    """Lengths of a batch's datums and of their trained positions, for ``CommandTable.track``
+    (reference: packages/client/src/shadowspill_client/text/statistics.py)."""
+    from .display import BatchStatistics
+    return BatchStatistics.from_lengths([len(d) for d in datums],
+                                        supervised=[int((d.weights > 0).sum()) for d in datums])

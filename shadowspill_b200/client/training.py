@@ -47,9 +47,14 @@ class TrainingClient:
         self.microbatch_tokens, self.microbatches = geo["microbatch_tokens"], geo["microbatches"]
         self.slots, self.vocab, self.workers = geo["slots"], geo["vocab_size"], geo["workers"]
         self.packing = geo.get("packing", "best_fit")
+        plan = info.get("plan_summary") or {}
+        estimates = {"step": plan.get("duration_seconds")} if plan.get("duration_seconds") else {}
+        for op, summary in (info.get("operation_plans") or {}).items():
+            if summary.get("duration_seconds"):
+                estimates[op] = summary["duration_seconds"]
         self.validator = BatchValidator(self.vocab, self.microbatch_tokens,
                                         self.microbatches * self.workers, self.slots,
-                                        tuple(geo.get("extra_fields", ())))
+                                        tuple(geo.get("extra_fields", ())), estimates, self.packing)
         self.writer_id = uuid.uuid4().hex
         self.transport.request("POST", f"{self.route}/writers/{self.writer_id}", {})
         self.pool = cf.ThreadPoolExecutor(max_workers=max(2, max_pending_requests))
@@ -63,14 +68,18 @@ class TrainingClient:
         self._local_metrics: list[dict[str, Any]] = []
 
     # ------------------------------------------------------------------ batches
-    def validate_batch(self, datums: list[Datum]) -> None:
-        self.validator.validate(datums)
+    def validate_batch(self, datums: list[Datum], operation: str = "step", groups=None):
+        """Checks a batch on this machine, before anything is uploaded: field shapes and values,
+        the run's token and sequence capacities, and whether the batch packs into the run's
+        microbatches. Returns a ``BatchValidation`` (totals, the packing strategy that worked,
+        the plan's simulated time for ``operation``); raises ``BatchError`` otherwise."""
+        return self.validator.validate(datums, operation, groups)
 
-    def _pack(self, datums: list[Datum], placement: list | None = None) -> bytes:
-        self.validate_batch(datums)
+    def _pack(self, datums: list[Datum], placement: list | None = None, groups=None) -> bytes:
+        self.validator.validate(datums, check_packing=False)
         mbs = pack_batch(datums, microbatch_tokens=self.microbatch_tokens,
                          microbatches=self.microbatches * self.workers, slots=self.slots,
-                         policy=self.packing, placement=placement)
+                         policy=self.packing, placement=placement, groups=groups)
         return encode_microbatches(mbs)
 
     # ------------------------------------------------------------------ submission
@@ -125,14 +134,16 @@ class TrainingClient:
                               res.request_id, res.outputs)
 
     # ------------------------------------------------------------------ operations
-    def step(self, datums: list[Datum], *, lr: float | None = None, grad_scale: float = 1.0) -> cf.Future:
+    def step(self, datums: list[Datum], *, lr: float | None = None, grad_scale: float = 1.0,
+             groups=None) -> cf.Future:
         """Forward, backward and one optimizer update on one global batch. ``grad_scale``
-        multiplies the gradients inside the update (loss-scale compensation, caller-side clipping)."""
-        return self._submit("step", self._pack(datums), lr=lr, grad_scale=grad_scale)
+        multiplies the gradients inside the update (loss-scale compensation, caller-side clipping).
+        ``groups``: lists of datum indices that must share a microbatch."""
+        return self._submit("step", self._pack(datums, groups=groups), lr=lr, grad_scale=grad_scale)
 
-    def forward_backward(self, datums: list[Datum]) -> cf.Future:
+    def forward_backward(self, datums: list[Datum], *, groups=None) -> cf.Future:
         """Accumulates gradients; the first contribution after an update writes them fresh."""
-        return self._submit("forward_backward", self._pack(datums))
+        return self._submit("forward_backward", self._pack(datums, groups=groups))
 
     def optim_step(self, *, grad_scale: float = 1.0, lr: float | None = None) -> cf.Future:
         return self._submit("optim_step", None, grad_scale=grad_scale, lr=lr)
@@ -240,6 +251,14 @@ class TrainingClient:
         return self.pool.submit(work)
 
     # ------------------------------------------------------------------ observations
+    @property
+    def metrics(self):
+        """Reads of this run's metric journal (``client.metrics.MetricQueries``)."""
+        from .metrics import MetricQueries
+        if getattr(self, "_metrics", None) is None:
+            self._metrics = MetricQueries(self.transport, self.session, self.run, self._downloads)
+        return self._metrics
+
     def log_metrics(self, step: int, **values: float) -> None:
         self.transport.request("POST", f"{self.route}/metrics", {"step": step, "values": values})
 

@@ -283,11 +283,19 @@ def make_handler(server):
                 return self._send(200, asdict(live.controller.wait(rest[1], min(timeout, 120.0))))
             if rest == ["metrics"]:
                 if method == "POST":
-                    live.metrics.append(dict(self._json(), source="caller"))
-                    return self._send(200, {"count": len(live.metrics)})
+                    row = dict(self._json(), source="caller", position=len(live.metrics) + 1)
+                    live.metrics.append(row)
+                    return self._send(200, {"count": len(live.metrics), "record": row})
+                # journal positions count from 1; a page covers (after, through]
                 after, limit = int(q.get("after", 0)), int(q.get("limit", 1000))
-                return self._send(200, {"metrics": live.metrics[after:after + limit],
-                                        "next": min(len(live.metrics), after + limit)})
+                end = len(live.metrics)
+                through = min(end, int(q["through"])) if "through" in q else end
+                if after < 0 or limit < 1 or through < after:
+                    raise HTTPError(400, "metric cursor exceeds its snapshot")
+                stop = min(through, after + limit)
+                return self._send(200, {"metrics": live.metrics[after:stop], "next": stop,
+                                        "after": after, "through": through,
+                                        "next_cursor": stop if stop < through else None})
             if rest == ["report"] and method == "POST":
                 return self._send(200, {"run": live.info(), "metrics": live.metrics[-1000:],
                                         "receipts": live.journal.records("receipt")[-1000:]})

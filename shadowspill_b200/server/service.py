@@ -187,9 +187,11 @@ class LiveRun:
         if op == "plan_report":
             # index.html, occupancy.html, tasks.csv, transfers.csv, timeline.*: one downloadable archive
             out["outputs"] = self.server.pack_directory(Path(args["directory"]), "plan_report")
-        if op in ("step", "optim_step") and out.get("loss") is not None:
-            self.metrics.append({"update": replies[0].get("completed_updates"), "loss": out["loss"],
-                                 "execution_seconds": out["execution_seconds"]})
+        # the metric journal: one record per finished request of any operation, in completion order
+        self.metrics.append({"position": len(self.metrics) + 1, "source": "service", "operation": op,
+                             "request_id": req["request_id"], "update": replies[0].get("completed_updates"),
+                             "loss": out.get("loss"), "execution_seconds": out["execution_seconds"],
+                             "values": {k: v for k, v in out["metrics"].items() if isinstance(v, (int, float))}})
         if op == "close":
             self.state = "closed"
             self.journal.append("closed", {})
@@ -211,7 +213,7 @@ class LiveRun:
         geo = self.resolved.geometry if self.resolved else {}
         return {"session": self.session, "run": self.run, "state": self.state, "error": self.error,
                 "workers": self.resolved.workers if self.resolved else 0, "geometry": geo,
-                "plan_summary": self.plan_summary,
+                "plan_summary": self.plan_summary, "operation_plans": self.operation_plans,
                 "provenance": self.resolved.provenance if self.resolved else {},
                 "budgets": self.resolved.budgets if self.resolved else {},
                 "state_valid": (self.controller.boundary()["valid"] if self.controller else True),

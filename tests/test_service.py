@@ -4,6 +4,8 @@ A real ``Server`` listens on loopback, the run's worker is a real subprocess wit
 the mock backend, and the client is the NumPy-only package a user imports.
 """
 import numpy as np
+import time
+
 import pytest
 
 from shadowspill_b200.client import (BatchConfig, BatchError, Memory, Model, Optimizer,
@@ -95,6 +97,43 @@ def test_train_checkpoint_resume_through_the_public_api(service, tmp_path_factor
         trainer.log_metrics(6, accuracy=0.5)
         metrics = svc.get_metrics(trainer.run).result()["metrics"]
         assert any(m.get("source") == "caller" for m in metrics) and len(metrics) >= 6
+        # ---- the metric journal: one record per finished request of any operation, paged reads
+        page = trainer.metrics.query(limit=4).result()
+        assert len(page.records) == 4 and page.next_cursor == 4 and page.through >= 10
+        records = list(trainer.metrics.snapshot(limit=3))
+        assert [r["position"] for r in records] == list(range(1, len(records) + 1))
+        assert {"step", "forward", "forward_backward", "optim_step", "save"} <= {r.get("operation") for r in records}
+        xs, ys = trainer.metrics.series("loss")
+        assert len(ys) >= 6 and xs == sorted(xs)
+        assert trainer.metrics.series("accuracy")[1] == [0.5]
+        exported = trainer.metrics.export_jsonl(tmp_path_factory.mktemp("metrics") / "run.jsonl").result()
+        assert len(exported.read_text().splitlines()) == len(records)
+        with pytest.raises(FileExistsError):
+            trainer.metrics.export_jsonl(exported).result()
+        with pytest.raises(ValueError):
+            trainer.metrics.query(limit=1000)
+        # ---- local validation reports what it found; a table follows a call without touching it
+        import io
+        from shadowspill_b200.client.display import CommandTable
+        from shadowspill_b200.client.text import text_batch_statistics
+        check = trainer.validate_batch(probe, "forward")
+        assert check.packing_checked and check.strategy in ("best_fit", "balanced", "repair")
+        assert check.capacities["tokens"] == sum(len(d) for d in probe) and check.capacities["sequences"] == len(probe)
+        assert check.scheduled_capacities["tokens"] == 512
+        plan_seconds = trainer.validate_batch(probe, "step").estimated_seconds
+        assert plan_seconds and plan_seconds > 0
+        screen = io.StringIO()
+        table = CommandTable(stream=screen)
+        tracked = table.track("forward", trainer.forward(probe), batch=text_batch_statistics(probe),
+                              planned_seconds=plan_seconds)
+        assert tracked.result().loss > 0
+        for _ in range(100):
+            if " done " in screen.getvalue():
+                break
+            time.sleep(0.02)
+        lines = screen.getvalue().splitlines()
+        assert any("pending" in ln and "forward()" in ln for ln in lines) and any(" done " in ln for ln in lines)
+        assert table.error is None
         progress = svc.get_progress(trainer.run).result()["lines"]
         assert any("ready" in line for line in progress)
         trainer.close()
