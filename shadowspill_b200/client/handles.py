@@ -96,3 +96,53 @@ def download_artifact(transport: HTTPTransport, artifact: str | ArtifactHandle, 
         raise IOError(f"artifact {aid}: digest mismatch after download")
     os.replace(part, path)
     return path
+
+
+class PlansHandle:
+    """The prepared plans of a run: what ``prepare_training`` / ``plan_training`` produce and what a
+    later ``create_training_client(plans=...)`` starts from without preparing again.
+
+    ``summary(page)`` lists the planned operations with their simulated times and traffic;
+    ``save(name=)`` gives the plans a name inside the session; ``export(path)`` downloads the
+    prepared bundle as a file, and ``ServiceClient.import_plans(path)`` uploads it to this or
+    another service, whose new runs accept the returned handle as ``plans``. A bundle is reused
+    only when its identity (model, geometry, budgets, frontend, dtype, world size) matches the new
+    run's settings; otherwise the run prepares from scratch.
+    Reference: packages/client/src/shadowspill_client/plans.py:26 (``PlansHandle``: ``report``,
+    ``save``, ``summary``), preparation.py:29 (``PreparationHandle.export``)."""
+
+    def __init__(self, service, run: str | None = None, artifact: ArtifactHandle | None = None):
+        self._service, self.run, self.artifact = service, run, artifact
+
+    def _route(self) -> str:
+        if self.run is None:
+            raise ValueError("these plans were imported as an artifact: they belong to no run of this service yet")
+        return f"/v1/runs/{self._service.session}/{self.run}/plans"
+
+    def summary(self, *, page: int = 0):
+        if isinstance(page, bool) or not isinstance(page, int) or page < 0:
+            raise ValueError("page must be a nonnegative int")
+        route = self._route()
+        return self._service.pool.submit(
+            lambda: self._service.transport.request("GET", route, query={"page": page})[1])
+
+    def save(self, *, name: str, operation: str = "step"):
+        if not name or "/" in name:
+            raise ValueError("a plan name is a non-empty string without '/'")
+        route = self._route()
+        return self._service.pool.submit(
+            lambda: self._service.transport.request("POST", route, {"name": name, "plan": operation})[1])
+
+    def export(self, path, **kw):
+        """Downloads the prepared bundle into ``path`` (a new file); the future gives the path."""
+        route = self._route()
+
+        def work():
+            _, h = self._service.transport.request("POST", route + "/artifact", {})
+            handle = ArtifactHandle(h["artifact"], int(h["size"]), h["sha256"])
+            return download_artifact(self._service.transport, handle, path, **kw)
+        return self._service.pool.submit(work)
+
+    def create_arguments(self) -> dict:
+        """What ``create_training_client`` sends for these plans."""
+        return {"plans": self.run} if self.run is not None else {"plans_artifact": self.artifact.artifact}

@@ -57,6 +57,9 @@ class ServiceClient:
         body = training_setup(model, optimizer, objective, batch, memory, execution, preparation,
                               resources, parallelism, operations)
         body["plans"], body["checkpoint"] = plans, checkpoint
+        if hasattr(plans, "create_arguments"):            # a PlansHandle: a run of this session or an import
+            body["plans"] = None
+            body.update(plans.create_arguments())
 
         def work() -> TrainingClient:
             info = self._create(body, True, timeout)
@@ -75,6 +78,17 @@ class ServiceClient:
         body = training_setup(**setup)
         body["prepare_only"], body["simulation_only"] = True, True
         return self.pool.submit(lambda: self._create(body, True, 3600.0))
+
+    def plans_of(self, run: str):
+        """The ``PlansHandle`` of a prepared (or running) run of this session."""
+        from .handles import PlansHandle
+        return PlansHandle(self, run)
+
+    def import_plans(self, path, **kw) -> cf.Future:
+        """Uploads a bundle that ``PlansHandle.export`` wrote; the future gives a ``PlansHandle``
+        that new runs of this service accept as ``plans``."""
+        from .handles import PlansHandle, upload_artifact
+        return self.pool.submit(lambda: PlansHandle(self, None, upload_artifact(self.transport, path, **kw)))
 
     def get_training_client(self, run: str) -> cf.Future:
         """Attaches to a running run as its writer; any earlier writer is fenced."""

@@ -258,6 +258,11 @@ def make_handler(server):
                 rows = [{"operation": "step", **live.plan_summary}]
                 rows += [{"operation": op, **summary} for op, summary in sorted(live.operation_plans.items())]
                 return self._send(200, {"plans": rows[page * 32:(page + 1) * 32], "names": live.plan_names})
+            if rest == ["plans", "artifact"] and method == "POST":
+                try:
+                    return self._send(200, server.bundle_artifact(p[0], p[1]))
+                except FileNotFoundError as exc:
+                    raise HTTPError(404, str(exc)) from None
             if rest == ["plans", "report"] and method == "POST":
                 return self._send(200, {"summary": live.plan_summary,
                                         "note": "workers write full HTML reports with write_report"})

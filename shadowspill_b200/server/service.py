@@ -89,6 +89,12 @@ class LiveRun:
             source = self.body.get("plans")
             bundle_dir = (self.server.root / "runs" / self.session / str(source)) if source else self.dir
             r.setups[0]["bundle"] = str(bundle_dir / "training.ssp")
+            imported = self.body.get("plans_artifact")
+            if imported and not source:
+                # a bundle exported from another run or service (PlansHandle.export): unpack it here;
+                # the worker reuses it only if its identity matches these settings, else prepares anew
+                self.server.unpack_bundle(str(imported), Path(r.setups[0]["bundle"]))
+                self.log(f"prepared bundle taken from artifact {imported}")
             if (self.body.get("preparation") or {}).get("separate_processes") and not source \
                     and not Path(r.setups[0]["bundle"]).exists():
                 # build, profile, communicate and plan as four fresh processes; the worker then opens
@@ -419,6 +425,32 @@ class Server:
         uncompressed TAR with members in sorted order, so the same checkpoint always gives
         the same bytes and digest."""
         return dict(self.pack_directory(Path(self.resolve_checkpoint(session, name)), name), checkpoint=name)
+
+    def bundle_artifact(self, session: str, run: str) -> dict[str, Any]:
+        """The prepared bundle of a run (plans, profiles, calibration: ``training.ssp``) as one
+        sealed artifact that another run, or another service, can start from."""
+        import shutil
+        import tempfile
+        bundle = self.root / "runs" / session / run / "training.ssp"
+        if not bundle.exists():
+            raise FileNotFoundError(f"run {run} has no prepared bundle")
+        with tempfile.TemporaryDirectory(dir=self.root) as tmp:
+            shutil.copyfile(bundle, Path(tmp) / "training.ssp")
+            return dict(self.pack_directory(Path(tmp), "plans"), run=run)
+
+    def unpack_bundle(self, artifact: str, target: Path) -> None:
+        import tarfile
+        meta = self.artifacts.get(artifact)
+        if not meta or not meta.get("complete"):
+            raise ValueError(f"artifact {artifact} is unknown or still uploading")
+        with tarfile.open(self.root / "artifacts" / artifact) as tar:
+            member = next((m for m in tar.getmembers() if m.isfile() and Path(m.name).name == "training.ssp"), None)
+            if member is None:
+                raise ValueError(f"artifact {artifact} holds no prepared bundle")
+            target.parent.mkdir(parents=True, exist_ok=True)
+            with tar.extractfile(member) as src, open(target, "wb") as dst:
+                import shutil
+                shutil.copyfileobj(src, dst)
 
     def pack_directory(self, directory: Path, name: str) -> dict[str, Any]:
         """``directory`` as one sealed artifact (deterministic TAR under ``name/``); its handle."""

@@ -562,3 +562,37 @@ def test_a_run_prepared_in_separate_processes(service):
             tr.close()
     live = service.get_run(svc.session, tr.run)
     assert (live.dir / "preparation" / "job.json").exists()
+
+
+def test_prepared_plans_are_exported_and_start_a_run_elsewhere(service, tmp_path):
+    """``PlansHandle``: summary pages and a name for the plans of a prepared run; the bundle leaves
+    the service as a file, comes back as an artifact (as it would on another service), and a new
+    run that names it skips build, profile and plan."""
+    common = dict(batch=BatchConfig(tokens_per_step=512, microbatch_tokens=256),
+                  memory=Memory(device_gib=0.53, spill_gib=0.25), resources=Resources(gpus=1, backend="cpu"),
+                  preparation=Preparation(profiling=ProfilingOptions(enabled=False), calibrate=False,
+                                          planning=PlanningOptions(minimum_object_bytes_evict_eligible=1024,
+                                                                   workers=1)))
+    model, opt = Model("llama3-tiny", dtype="float32"), Optimizer(lr=3e-3, parameter_rounding="nearest")
+    with ServiceClient(service.url, token="secret") as svc:
+        prepared = svc.prepare_training(model=model, optimizer=opt, **common).result()
+        plans = svc.plans_of(prepared["run"])
+        page = plans.summary().result()
+        assert page["plans"][0]["operation"] == "step" and page["plans"][0]["duration_seconds"] > 0
+        assert plans.save(name="baseline").result()["plans"] == {"baseline": "step"}
+        with pytest.raises(ValueError):
+            plans.save(name="a/b")
+        bundle = plans.export(tmp_path / "plans.tar").result()
+        assert bundle.stat().st_size > 1000
+    with ServiceClient(service.url, token="secret") as other:          # another session: nothing shared but the file
+        imported = other.import_plans(bundle).result()
+        assert imported.run is None and imported.create_arguments() == {"plans_artifact": imported.artifact.artifact}
+        with pytest.raises(ValueError):
+            imported.summary()
+        tr = other.create_training_client(model, opt, plans=imported, timeout=300, **common).result()
+        try:
+            progress = " ".join(other.get_progress(tr.run).result()["lines"])
+            assert "taken from artifact" in progress and "build, profile and plan skipped" in progress
+            assert tr.step(text_batch(_sequences(0))).result().loss > 0
+        finally:
+            tr.close()
