@@ -17,6 +17,42 @@ from .training import TrainingClient
 from .transport import HTTPTransport, TransportError
 
 
+class ProgressDisplay:
+    """Shows a run's preparation log while the run comes up: a stamped heading when the run's
+    state changes, then the log lines that are new since the last poll (at most two polls a
+    second). Display trouble never reaches the creation: the first error switches it off with one
+    note. Reference: packages/client/src/shadowspill_client/_progress.py:19."""
+
+    def __init__(self, target, run: str):
+        import sys
+        self.stream = sys.stdout if target is True else (target or None)
+        self.run, self.seen, self.state, self.next_poll = run, 0, None, 0.0
+
+    def update(self, transport, session: str, info: dict[str, Any], final: bool = False) -> None:
+        if self.stream is None:
+            return
+        try:
+            changed = info.get("state") != self.state
+            if changed:
+                self.state = info.get("state")
+                stamp = time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime())
+                self.stream.write(f"\n{stamp}  Run {self.run[:12]} - {str(self.state).capitalize()}\n")
+            if not final and not changed and time.monotonic() < self.next_poll:
+                return
+            self.next_poll = time.monotonic() + 0.5
+            _, page = transport.request("GET", f"/v1/runs/{session}/{self.run}/progress", query={"after": self.seen})
+            for line in page.get("lines", ()):
+                self.stream.write(f"  {line}\n")
+            self.seen = int(page.get("next", self.seen))
+            self.stream.flush()
+        except Exception as exc:  # noqa: BLE001
+            stream, self.stream = self.stream, None
+            try:
+                stream.write(f"\n  ! live progress unavailable ({type(exc).__name__}); creation continues\n")
+            except Exception:  # noqa: BLE001
+                pass
+
+
 class ServiceClient:
     def __init__(self, url: str, token: str = "", timeout: float = 600.0, max_workers: int = 8):
         self.transport = HTTPTransport(url, token, timeout)
@@ -34,15 +70,18 @@ class ServiceClient:
         return self.pool.submit(lambda: self.transport.request("POST", "/v1/training/describe", body)[1])
 
     # ------------------------------------------------------------------ runs
-    def _create(self, body: dict[str, Any], wait: bool, timeout: float) -> dict[str, Any]:
+    def _create(self, body: dict[str, Any], wait: bool, timeout: float, progress=None) -> dict[str, Any]:
         _, info = self.transport.request("POST", f"/v1/runs/{self.session}", body)
         run = info["run"]
         deadline = time.monotonic() + timeout
+        shown = ProgressDisplay(progress, run)
         while wait and info["state"] == "preparing":
             if time.monotonic() > deadline:
                 raise TimeoutError("run did not become ready in time")
             time.sleep(0.2)
             _, info = self.transport.request("GET", f"/v1/runs/{self.session}/{run}")
+            shown.update(self.transport, self.session, info)
+        shown.update(self.transport, self.session, info, final=True)
         if info["state"] == "failed":
             raise RuntimeError(f"run creation failed: {info.get('error', '')}")
         return info
@@ -53,7 +92,9 @@ class ServiceClient:
                                preparation: Preparation = Preparation(),
                                resources: Resources = Resources(), parallelism: dict | None = None,
                                operations: tuple = ("step",), plans: str | None = None,
-                               checkpoint: str | None = None, timeout: float = 3600.0) -> cf.Future:
+                               checkpoint: str | None = None, timeout: float = 3600.0, progress=None) -> cf.Future:
+        """``progress``: ``True`` (standard output) or a text stream: the run's preparation log
+        (build, profile, calibrate, plan, worker start) is shown while the run comes up."""
         body = training_setup(model, optimizer, objective, batch, memory, execution, preparation,
                               resources, parallelism, operations)
         body["plans"], body["checkpoint"] = plans, checkpoint
@@ -62,7 +103,7 @@ class ServiceClient:
             body.update(plans.create_arguments())
 
         def work() -> TrainingClient:
-            info = self._create(body, True, timeout)
+            info = self._create(body, True, timeout, progress)
             return TrainingClient(self.transport, self.session, info["run"], info,
                                   execution.max_staging_bytes, execution.max_pending_requests)
         return self.pool.submit(work)

@@ -31,6 +31,36 @@ class TrainingResult:
     outputs: dict[str, Any] = field(default_factory=dict)
 
 
+class OperationFuture(cf.Future):
+    """The pending result of one submitted request. ``request_id`` is fixed at submission, so a
+    caller that loses its connection can look the request up again instead of submitting it twice;
+    ``accepted()`` resolves once the service has registered the request and holds its input, after
+    which the request goes on even if this client goes away (it fails with the request's own error
+    if that happens first). Reference: packages/client/src/shadowspill_client/results.py:154."""
+
+    def __init__(self, request_id: str, operation: str):
+        super().__init__()
+        self.request_id, self.operation = request_id, operation
+        self._acceptance: cf.Future = cf.Future()
+
+    def accepted(self) -> cf.Future:
+        return self._acceptance
+
+    def _accept(self, state: dict) -> None:
+        if not self._acceptance.done():
+            self._acceptance.set_result(state)
+
+    def _finish(self, source: cf.Future) -> None:
+        exc = source.exception()
+        if exc is not None:
+            if not self._acceptance.done():
+                self._acceptance.set_exception(exc)
+            self.set_exception(exc)
+        else:
+            self._accept({"request_id": self.request_id, "state": "completed"})
+            self.set_result(source.result())
+
+
 class OperationFailed(RuntimeError):
     def __init__(self, result: OperationResult):
         self.result = result
@@ -95,7 +125,8 @@ class TrainingClient:
             req = OperationRequest(operation, dependencies=deps, arguments=arguments,
                                    has_input=payload is not None, writer_id=self.writer_id)
             self._staged += size
-            fut = self.pool.submit(self._drive, req, payload)
+            fut = OperationFuture(req.request_id, operation)
+            self.pool.submit(self._drive, req, payload, fut).add_done_callback(fut._finish)
             self._pending[req.request_id] = fut
 
         def done(_f, rid=req.request_id, n=size):
@@ -106,7 +137,8 @@ class TrainingClient:
         fut.add_done_callback(done)
         return fut
 
-    def _drive(self, req: OperationRequest, payload: bytes | None) -> TrainingResult:
+    def _drive(self, req: OperationRequest, payload: bytes | None, watcher: OperationFuture | None = None
+               ) -> TrainingResult:
         body = {"operation": req.operation, "request_id": req.request_id,
                 "dependencies": req.dependencies, "arguments": req.arguments,
                 "has_input": req.has_input, "writer_id": req.writer_id, "digest": req.digest()}
@@ -122,6 +154,9 @@ class TrainingClient:
                         raise
                     time.sleep(delay)
                     delay = min(1.0, delay * 2)
+        if watcher is not None:
+            watcher._accept({"request_id": req.request_id, "state": "accepted", "operation": req.operation,
+                             "dependencies": list(req.dependencies)})
         while True:
             _, data = self.transport.request("GET", f"{self.route}/requests/{req.request_id}",
                                              query={"wait": "completed", "timeout": 30})

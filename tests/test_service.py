@@ -3,6 +3,8 @@
 A real ``Server`` listens on loopback, the run's worker is a real subprocess with
 the mock backend, and the client is the NumPy-only package a user imports.
 """
+import io
+
 import numpy as np
 import time
 
@@ -589,8 +591,15 @@ def test_prepared_plans_are_exported_and_start_a_run_elsewhere(service, tmp_path
         assert imported.run is None and imported.create_arguments() == {"plans_artifact": imported.artifact.artifact}
         with pytest.raises(ValueError):
             imported.summary()
-        tr = other.create_training_client(model, opt, plans=imported, timeout=300, **common).result()
+        screen = io.StringIO()
+        tr = other.create_training_client(model, opt, plans=imported, timeout=300, progress=screen, **common).result()
+        shown = screen.getvalue()
+        assert "- Preparing" in shown and "- Ready" in shown and "taken from artifact" in shown
         try:
+            fut = tr.step(text_batch(_sequences(1)))
+            assert fut.operation == "step" and len(fut.request_id) == 32
+            assert fut.accepted().result(60)["request_id"] == fut.request_id
+            assert fut.result(60).request_id == fut.request_id
             progress = " ".join(other.get_progress(tr.run).result()["lines"])
             assert "taken from artifact" in progress and "build, profile and plan skipped" in progress
             assert tr.step(text_batch(_sequences(0))).result().loss > 0
