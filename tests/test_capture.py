@@ -101,3 +101,36 @@ def test_stage_trace_runs_one_task_in_isolation():
     assert graph["kind"] == "forward"
     with pytest.raises(KeyError, match="B.layer0.0"):
         trace_task("llama3-tiny", "B.layer9.0", microbatch_tokens=256, device="cpu", dtype=torch.float32)
+
+
+def test_gap_report_separates_lanes_waits_and_interference(tmp_path):
+    """Two lanes built by hand: a backward task that starts exactly when a reduce-scatter ends
+    waited for it; compute tasks that ran beside a collective are slower than those that ran alone."""
+    from shadowspill_b200.qualification.gap_report import Row, build, from_directory
+    rows = [Row(0, "F.layer0.0", "forward", 0.010, 0.010, 0.000, 0.010),
+            Row(1, "B.layer1.0", "backward", 0.010, 0.010, 0.010, 0.010),            # alone, on profile
+            Row(2, "RS.layer1.g0", "collective", 0.001, 0.001, 0.020, 0.006),
+            Row(3, "B.layer0.1", "backward", 0.010, 0.010, 0.026, 0.010),            # waited for the RS
+            Row(4, "AG.layer0.fwd.g1", "collective", 0.001, 0.001, 0.036, 0.008),
+            Row(5, "F.layer0.1", "forward", 0.010, 0.010, 0.036, 0.014),             # beside the AG: slower
+            Row(6, "O.layer0", "optimizer", 0.001, 0.001, 0.050, 0.002)]
+    rep = build(rows, simulated_s=0.045)
+    assert rep.lanes["compute"]["tasks"] == 4 and rep.lanes["communication"]["tasks"] == 3
+    assert abs(rep.lanes["compute"]["gap_s"] - 0.006) < 1e-9
+    (why, gap), = rep.waits.items()
+    assert "RS task" in why and gap["count"] == 1 and abs(gap["seconds"] - 0.006) < 1e-9
+    assert rep.interference["beside"]["tasks"] == 1 and abs(rep.interference["beside"]["ratio"] - 1.4) < 1e-9
+    assert rep.interference["alone"]["tasks"] == 3 and abs(rep.interference["alone"]["ratio"] - 1.0) < 1e-9
+    assert abs(rep.makespan_s - 0.052) < 1e-9 and "measured 52.0 ms, simulated 45.0 ms" in rep.text()
+    # without collectives the update belongs to the compute lane
+    solo = build([Row(0, "B.layer0.0", "backward", 0.01, 0.01, 0.0, 0.01), Row(1, "O.layer0", "optimizer", 0.001, 0.001, 0.012, 0.001)])
+    assert "communication" not in solo.lanes and solo.waits["host (frontend late)"]["count"] == 1
+    # the files a traced step writes
+    import csv
+    with open(tmp_path / "runtime_tasks.csv", "w", newline="") as f:
+        w = csv.writer(f)
+        w.writerow(["index", "name", "kind", "stage", "microbatch", "profiled_s", "simulated_start_s", "simulated_s",
+                    "real_start_s", "real_s", "gap_before_s", "simulated_gap_s", "waited_inputs", "waited_reuse"])
+        for r in rows:
+            w.writerow([r.index, r.name, r.kind, 0, 0, r.profiled_s, 0, r.simulated_s, r.start_s, r.real_s, 0, 0, 0, 0])
+    assert from_directory(tmp_path).waits == rep.waits
