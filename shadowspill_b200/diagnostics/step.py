@@ -122,21 +122,29 @@ def diagnose_step(plan: Plan, result, task_start_seconds: list[float] | None = N
     base = t_begin or 0
     # ---- task rows
     rows: list[TaskRow] = []
-    prev_real_end = 0.0
+    # the executor runs collectives and the sharded update on a communication stream: a task's gap
+    # is measured against the previous task of ITS lane (the simulation has one lane)
+    sharded = any(t.kind == "collective" for t in prog.tasks)
+    side = [t.kind == "collective" or (sharded and t.kind == "optimizer") for t in prog.tasks]
+    prev_real_end = {False: 0.0, True: 0.0}
     prev_sim_end = 0
     for i, t in enumerate(prog.tasks):
         s_ns, e_ns = plan.task_start_ns[i], plan.task_end_ns[i]
+        lane = side[i]
         rows.append(TaskRow(i, t.name, t.kind, t.stage, t.microbatch, t.duration_ns * 1e-9,
                             s_ns * 1e-9, (e_ns - s_ns) * 1e-9, starts[i], real[i],
-                            max(0.0, starts[i] - prev_real_end), (s_ns - prev_sim_end) * 1e-9,
+                            max(0.0, starts[i] - prev_real_end[lane]), (s_ns - prev_sim_end) * 1e-9,
                             waits_in.get(i, 0), waits_reuse.get(i, 0)))
-        prev_real_end = starts[i] + real[i]
+        prev_real_end[lane] = max(prev_real_end[lane], starts[i] + real[i])
         prev_sim_end = e_ns
     # ---- idle attribution: a gap before a task that had to wait on a fetch is readiness
     # wait, on a reused range allocation wait, otherwise the frontend was late
-    w_in = sum(r.gap_before_s for r in rows[1:] if r.waited_inputs)
-    w_reuse = sum(r.gap_before_s for r in rows[1:] if not r.waited_inputs and r.waited_reuse)
-    idle_real = sum(r.gap_before_s for r in rows[1:])
+    lane_rows = [r for r in rows if not side[r.index]]          # idle = the compute lane's idle
+    first = lane_rows[0].index if lane_rows else -1
+    lane_rows = [r for r in lane_rows if r.index != first]
+    w_in = sum(r.gap_before_s for r in lane_rows if r.waited_inputs)
+    w_reuse = sum(r.gap_before_s for r in lane_rows if not r.waited_inputs and r.waited_reuse)
+    idle_real = sum(r.gap_before_s for r in lane_rows)
     frontend = idle_real - w_in - w_reuse
     # ---- phases
     phases: dict[str, dict[str, float]] = {}
