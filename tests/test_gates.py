@@ -42,3 +42,15 @@ def test_planned_bf16_training_matches_the_fp32_pytorch_twin(family, frontend):
     _lib.check_status()
     assert rec["passed"], (rec["failures"], rec["weights"], rec["losses"])
     assert rec["frontend"] == frontend and rec["fetch_bytes"] > 0
+
+
+def test_divergence_probe_agrees_on_cpu_and_names_a_flipped_bit():
+    """Two runs from one seed agree bit for bit on CPU; a single flipped bit in the second run's
+    state is found at the update where it happened, with the tensor named."""
+    from shadowspill_b200.qualification.nondeterminism import probe
+    clean = probe("llama3-tiny", "cpu", updates=2)
+    assert clean["diverged_at"] is None and clean["same_plan"] and len(clean["losses"]) == 2
+    assert all(a == b for a, b in clean["losses"])
+    dirty = probe("llama3-tiny", "cpu", updates=3, perturb_at=2)
+    assert dirty["diverged_at"] == 2 and dirty["tensors"][0]["differing"] == 1
+    assert dirty["tensors"][0]["tensor"].startswith("embed") and dirty["tensors"][0]["first_index"] == 0
