@@ -26,6 +26,7 @@ _PUBLIC = {
     "plan_program": ("shadowspill_b200.planning.plan", "plan_program"),
     "sweep_programs": ("shadowspill_b200.planning.plan", "sweep_programs"),
     "SearchOptions": ("shadowspill_b200.planning.plan", "SearchOptions"),
+    "PlanningInputs": ("shadowspill_b200.planning.offline", "PlanningInputs"),
     "simulate": ("shadowspill_b200.simulator.api", "simulate"),
     "Executor": ("shadowspill_b200.execution.executor", "Executor"),
     "ResidentTrainer": ("shadowspill_b200.execution.resident", "ResidentTrainer"),

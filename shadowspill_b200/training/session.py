@@ -130,6 +130,15 @@ class TrainingSetup:
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
 
+def _selection_label(selection: dict) -> str:
+    if not selection:
+        return "recompute"
+    kinds: dict[str, int] = {}
+    for v in selection.values():
+        kinds[v] = kinds.get(v, 0) + 1
+    return ", ".join(f"{k} x{n}" for k, n in sorted(kinds.items()))
+
+
 class TrainingSession:
     def __init__(self, setup: TrainingSetup, log=None):
         self.setup = setup
@@ -424,6 +433,8 @@ class TrainingSession:
                                 for op, (p, d) in extras.items()}
             extra_json = {op: pl.to_json() for op, (pl, _) in self.extra_plans.items()}
             self.sweep = sweep
+            self._candidates = [(p, f"{d.ordering.label()} [{_selection_label(d.selection)}]")
+                                for p, d in candidates]
             self.plan = sweep.best
             chosen = next(i for i, (p, _) in enumerate(candidates) if p is self.plan.program)
             self.desc = candidates[chosen][1]
@@ -536,6 +547,17 @@ class TrainingSession:
     def write_plan_report(self, directory: str) -> None:
         from ..reporting.write import write_report
         write_report(self.plan, directory)
+
+    def planning_inputs(self):
+        """What planning consumed, for offline sweeps over other budgets and link rates
+        (``planning.offline.PlanningInputs``): the candidate programs with their measured costs,
+        the calibrated link, the budgets and the search options. Needs a session that prepared
+        itself (one opened from a bundle never built its candidates)."""
+        from ..planning.offline import PlanningInputs
+        if not getattr(self, "_candidates", None):
+            raise ValueError("this session was opened from a prepared bundle: it holds one plan, not the candidates")
+        return PlanningInputs([p for p, _ in self._candidates], self.communication, self.budgets,
+                              [label for _, label in self._candidates], self.setup.search)
 
     def traced_step(self, batch: list[HostMicrobatch], directory: str | None = None):
         """Runs one real training step with per-task device timing and the runtime trace

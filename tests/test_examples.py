@@ -46,3 +46,25 @@ def test_policy_example():
     # iteration is -mean(advantage) over response tokens = 0 up to rounding; steps lower it
     assert abs(history[0]) < 1e-4 and abs(history[2]) < 1e-4
     assert history[1] < history[0] and history[3] < history[2]
+
+
+def test_offline_sweep_example(tmp_path):
+    """Planning inputs exported from a prepared session are planned again, elsewhere, for other
+    budgets and link rates; every feasible cell gets its plan report."""
+    mod = _load("offline_sweep")
+    exported = tmp_path / "measurements.zip"
+    mod.main(["--export", str(exported)])
+    sweep = mod.main([str(exported), "--output", str(tmp_path / "sweep.html"), "--device-gib", "0.2", "0.53", "1.0",
+                      "--transfer-scale", "0.5", "2"])
+    rows = sweep.table()
+    assert len(rows) == 6 and sum(r["feasible"] for r in rows) >= 4
+    fits = [r for r in rows if r["feasible"]]
+    # a faster link never makes the same budget slower; more memory never makes the same link slower
+    by = {(r["device_gib"], r["transfer_scale"]): r["seconds"] for r in fits}
+    for (d, x), s in by.items():
+        if (d, 2.0) in by and x == 0.5:
+            assert by[(d, 2.0)] <= s + 1e-9
+    page = (tmp_path / "sweep.html").read_text()
+    assert page.count("<tr>") == 7 and "plan</a>" in page
+    linked = next((tmp_path / "sweep").iterdir())
+    assert (linked / "index.html").exists() and (linked / "tasks.csv").exists()
