@@ -68,3 +68,13 @@ def test_offline_sweep_example(tmp_path):
     assert page.count("<tr>") == 7 and "plan</a>" in page
     linked = next((tmp_path / "sweep").iterdir())
     assert (linked / "index.html").exists() and (linked / "tasks.csv").exists()
+
+
+def test_saved_plan_example():
+    out = _load("saved_plan").main(steps=2)
+    assert out["skipped_preparation"] and len(out["losses"]) == 2 and out["prepared_seconds"] > 0
+
+
+def test_lora_long_context_example():
+    losses = _load("lora_long_context").main(["--steps", "3"])
+    assert len(losses) == 3 and losses[-1] < losses[0]
