@@ -291,7 +291,7 @@ class RecoveredRun:
 
 class Server:
     def __init__(self, service_root: str | Path, model_root: str | Path | None = None,
-                 host: str = "127.0.0.1", port: int = 0, token: str | None = None):
+                 host: str = "127.0.0.1", port: int = 0, token: str | None = None, extensions=None):
         self.root = Path(service_root)
         self.root.mkdir(parents=True, exist_ok=True)
         self.model_root = Path(model_root) if model_root else None
@@ -299,6 +299,8 @@ class Server:
         self.token = token if token is not None else os.environ.get("SHADOWSPILL_TOKEN", "")
         self.node_token = os.environ.get("SHADOWSPILL_NODE_TOKEN", self.token)
         self.registry = default_registry()
+        from ..training.extensions import load_extensions
+        self.extensions = load_extensions(self.registry, extensions)     # SHADOWSPILL_EXTENSIONS by default
         self.hardware = device_inventory()
         self.admission = NodeAdmission(self.hardware["gpus"], int(self.hardware["host_total_gib"] * GIB))
         self.membership = Membership()

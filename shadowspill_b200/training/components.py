@@ -223,6 +223,12 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
     if frontend not in ("stages", "graph"):
         raise ValueError(f"unknown build frontend {frontend!r} (stages | graph)")
     for pol in prep.get("policies", []):
+        # every policy is a registered component; one that an extension package added may be a
+        # preset of a built-in policy ("alias_of" names it, the rest is its configuration)
+        made = registry.get("policy", pol.get("id", "")).create(**(pol.get("config") or {}))
+        if isinstance(made, dict) and made.get("alias_of"):
+            prov[f"policy {pol['id']}"] = f"preset of {made['alias_of']}"
+            pol = {"id": made["alias_of"], "config": {k: v for k, v in made.items() if k != "alias_of"}}
         if pol.get("id") == "shadowspill/text_chunks@1":
             # "projection": row chunks of the output projection; "moe": expert groups a routed layer
             # is pipelined in under expert parallelism; "rows": token rows per chunk of the

@@ -605,3 +605,43 @@ def test_prepared_plans_are_exported_and_start_a_run_elsewhere(service, tmp_path
             assert tr.step(text_batch(_sequences(0))).result().loss > 0
         finally:
             tr.close()
+
+
+def test_an_extension_package_adds_components(tmp_path):
+    """A service started with an extension package lists its components under the package's name,
+    trains the model it defines, and resolves its policy preset; ids that exist are not replaced,
+    and a broken package stops the start with its name."""
+    import sys
+    from pathlib import Path
+    from shadowspill_b200.client import Policy
+    from shadowspill_b200.training.extensions import ExtensionError
+    sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+    name = "examples.extensions.custom_training"
+    with Server(tmp_path / "svc", token="secret", extensions=[name]) as srv:
+        assert srv.extensions[name] == ["model:acme/llama3-wide@1", "policy:acme/short_rows@1"]
+        with ServiceClient(srv.url, token="secret") as svc:
+            listed = {c["id"]: c for c in svc.list_components().result()}
+            assert listed["acme/llama3-wide@1"]["source"]["distribution"] == name
+            assert listed["llama3-tiny@1"]["source"]["distribution"] == "shadowspill_b200"
+            tr = svc.create_training_client(
+                Model("acme/llama3-wide@1", dtype="float32"), Optimizer(lr=3e-3, parameter_rounding="nearest"),
+                batch=BatchConfig(tokens_per_step=512, microbatch_tokens=256),
+                memory=Memory(device_gib=0.53, spill_gib=0.25), resources=Resources(gpus=1, backend="cpu"),
+                preparation=Preparation(profiling=ProfilingOptions(enabled=False), calibrate=False,
+                                        policies=(Policy("acme/short_rows@1", {"rows": 64}),),
+                                        planning=PlanningOptions(minimum_object_bytes_evict_eligible=1024, workers=1)),
+                timeout=300).result()
+            try:
+                assert tr.info["provenance"]["model"] == "catalog acme/llama3-wide@1"
+                assert tr.info["provenance"]["policy acme/short_rows@1"] == "preset of shadowspill/text_chunks@1"
+                live = srv.get_run(svc.session, tr.run)
+                from shadowspill_b200.models.config import preset
+                assert live.resolved.cfg.d_ff == 2 * preset("llama3-tiny").d_ff
+                assert live.resolved.setups[0]["axis_chunk_rows"] == 64 and live.resolved.setups[0]["frontend"] == "graph"
+                assert tr.step(text_batch(_sequences(0))).result().loss > 0
+            finally:
+                tr.close()
+    with pytest.raises(ExtensionError, match="cannot be imported"):
+        Server(tmp_path / "bad", token="secret", extensions=["no_such_extension_module"])
+    with pytest.raises(ExtensionError, match="already registered"):
+        Server(tmp_path / "twice", token="secret", extensions=[name, name])
