@@ -82,6 +82,13 @@ def classify(node: fx.Node, T: int) -> tuple[str, tuple[int, ...]]:
     if name in _ROW_ARGS_SS:
         pos = _ROW_ARGS_SS[name]
         return (ROWS, pos) if (lead(*pos) and _leading(node, T)) else none
+    if not name.startswith(("ss.", "aten.")):
+        from .operator_rules import rule_of
+        declared = rule_of(name)             # an operator of the user's own: its rule names the row arguments
+        if declared is not None and declared.row_args is not None:
+            pos = declared.row_args
+            return (ROWS, pos) if (lead(*pos) and _leading(node, T)) else none
+        return none
     if name == "ss.gemm":
         return (ROWS, (0,)) if (not a[2] and lead(0) and _leading(node, T)) else none
     if name.startswith(_POINTWISE):

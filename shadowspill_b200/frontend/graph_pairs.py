@@ -160,6 +160,10 @@ def _is_memory_bound(node: fx.Node) -> bool:
         return name in ss_ops.MEMORY_BOUND
     if node.target is operator.getitem:
         return _is_memory_bound(node.args[0])
+    from .operator_rules import rule_of
+    declared = rule_of(name)                 # an operator of the user's own, with a declared rule
+    if declared is not None:
+        return declared.cost == "memory"
     return name.startswith("aten.")          # pointwise / view / cast glue
 
 

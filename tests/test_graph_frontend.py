@@ -367,3 +367,55 @@ def test_graph_frontend_on_the_gpu_matches_the_stage_classes(name):
             continue
         # norm vectors see the sum of many bf16-rounded terms in a different order
         assert rel < (5e-2 if v.dim() == 1 else 2.5e-2), (k, rel)
+
+
+def test_an_operator_of_the_users_own_takes_part_through_its_rule():
+    """A custom operator with a declared rule (memory-bound, rows in argument 0) is exported,
+    differentiated, recomputed instead of kept by the ``save`` policy, and cut by row chunking."""
+    from torch import nn
+    from shadowspill_b200.frontend import modules as M
+    from shadowspill_b200.frontend.chunking import ROWS, classify
+    from shadowspill_b200.frontend.graph_stage import build_graph_stages
+    from shadowspill_b200.frontend.operator_rules import OperatorRule, register_operator_rule, rule_of
+
+    @torch.library.custom_op("acme::soft_gate", mutates_args=())
+    def soft_gate(x: torch.Tensor, slope: float) -> torch.Tensor:
+        return x * torch.sigmoid(slope * x.float()).to(x.dtype)
+
+    @soft_gate.register_fake
+    def _(x, slope):
+        return torch.empty_like(x)
+
+    def _bwd(ctx, gy):
+        (x,) = ctx.saved_tensors
+        s = torch.sigmoid(ctx.slope * x.float())
+        return (gy * (s + ctx.slope * x.float() * s * (1 - s)).to(gy.dtype)), None
+    soft_gate.register_autograd(_bwd, setup_context=lambda ctx, inputs, output: (ctx.save_for_backward(inputs[0]),
+                                                                                  setattr(ctx, "slope", inputs[1])))
+    if rule_of("acme.soft_gate") is None:
+        register_operator_rule(OperatorRule("acme.soft_gate", "memory", (0,)))
+    with pytest.raises(ValueError):
+        register_operator_rule(OperatorRule("acme.soft_gate", "compute"))
+
+    class GatedLayer(M.DenseLayer):
+        def forward(self, x, positions, cu_seqlens):
+            return super().forward(torch.ops.acme.soft_gate(x, 0.5), positions, cu_seqlens)
+
+    class Model(M.DecoderLM):
+        def __init__(self, cfg):
+            super().__init__(cfg, torch.float32)
+            self.layers = nn.ModuleList([GatedLayer(cfg, torch.float32) for _ in range(cfg.n_layers)])
+
+    cfg = preset("llama3-tiny")
+    with torch.device("meta"):
+        meta_model = Model(cfg)
+    stages = build_graph_stages(cfg, 256, 16, torch.float32, module=meta_model, chunk_rows=64)
+    layer = stages[1]
+    fwd_nodes = [n for n in layer.graph.gm.graph.nodes if n.op == "call_function"]
+    mine = next(n for n in fwd_nodes if "soft_gate" in op_name(n))
+    assert classify(mine, 256) == (ROWS, (0,))
+    # the save policy recomputes it (its output is not among the kept values), and the backward graph redoes it
+    save = layer.pairs.pairs["save"]
+    assert any("soft_gate" in op_name(n) for n in save.backward.graph.nodes)
+    # row chunking cut it: four copies in the chunked forward
+    assert sum("soft_gate" in op_name(n) for n in layer.pairs.pairs["recompute"].forward.graph.nodes) == 4
