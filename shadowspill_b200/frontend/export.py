@@ -279,6 +279,15 @@ def canonical_text(graph: fx.Graph) -> str:
 
 
 def _local_names(targets: list[str]) -> list[str]:
-    """Last path component of each parameter name; a clash inside one stage keeps the parents."""
+    """Last path component of each parameter name; a clash inside one stage (a stage of several
+    layers) keeps the parents below the stage's own module, so that two stages of the same structure
+    still name their parameters alike."""
     short = [t.split(".")[-1] for t in targets]
-    return [t.replace(".", "_") if short.count(s_) > 1 else s_ for t, s_ in zip(targets, short)]
+    parts = [t.split(".") for t in targets]
+    common = 0
+    while parts and all(len(p) > common + 1 for p in parts) and len({p[common] for p in parts}) == 1:
+        common += 1
+    while common > 0 and any(p[common][:1].isdigit() for p in parts):
+        common -= 1                          # a name must not start with a child's number
+    rel = ["_".join(p[common:]) for p in parts]
+    return [r if short.count(s_) > 1 else s_ for r, s_ in zip(rel, short)]

@@ -155,10 +155,12 @@ def _slice_sums(g: fx.Graph) -> int:
         inner = []
         while stack and ok:
             m = stack.pop()
-            if op_name(m) == "aten.add.Tensor" and len(m.args) == 2 and not m.kwargs and (m is root or _single_use(m)):
+            if not isinstance(m, fx.Node):           # an add with a number: not a sum of slice gradients
+                ok = False
+            elif op_name(m) == "aten.add.Tensor" and len(m.args) == 2 and not m.kwargs and (m is root or _single_use(m)):
                 inner.append(m)
                 stack += [x for x in m.args]
-            elif isinstance(m, fx.Node) and op_name(m) == "aten.slice_backward.default" and _single_use(m):
+            elif op_name(m) == "aten.slice_backward.default" and _single_use(m):
                 leaves.append(m)
             else:
                 ok = False

@@ -84,7 +84,15 @@ class _Norms:
         if not c.is_moe:
             return x + self._lin(S.swiglu(self._lin(h, "w13")), "w2")
         logits = S.linear(h, self.router).float()
-        if "w13" in self.adapted:       # both banks carry per-expert factors (see graph_stage.supports)
+        if c.router_scoring == "sigmoid":
+            # scores in (0, 1); a frozen per-expert bias takes part in the selection only; the picked
+            # scores are renormalised and scaled (GLM / DeepSeek-style routing without an auxiliary loss)
+            scores = torch.sigmoid(logits)
+            ids = torch.topk(scores + self.router_bias.float(), c.top_k, dim=-1).indices
+            picked = torch.gather(scores, 1, ids)
+            wts = picked / (picked.sum(-1, keepdim=True) + 1e-20) * c.routed_scaling_factor
+            out = S.moe_experts_routed(h, ids.to(torch.int32), wts, self.w13, self.w2)
+        elif "w13" in self.adapted:     # both banks carry per-expert factors (see graph_stage.supports)
             out = S.moe_experts_lora(h, logits, self.w13, self.w2, self.w13_lora_a, self.w13_lora_b,
                                      self.w2_lora_a, self.w2_lora_b, c.top_k, c.router_renormalize,
                                      float(self.lora.scale))
@@ -227,6 +235,125 @@ class HybridLayer(nn.Module, _Norms):
         return self._mlp(x + mix)
 
 
+def _rotate_pairs(x, positions, theta: float):
+    """Rotary embedding over interleaved (even, odd) input pairs, emitted as the real half followed
+    by the imaginary half (the layout of the published GLM checkpoints)."""
+    import math
+    width = x.shape[-1]
+    # 0, 1, ..., width/2 - 1 built from an input: a tensor created on a named device would pin the
+    # exported graph to the device it was traced on
+    one = positions[:1].to(torch.float32) * 0 + 1
+    k = torch.cumsum(one.expand(width // 2), 0) - 1
+    freq = torch.exp(k * (-2.0 * math.log(theta) / width))
+    ang = positions.to(torch.float32)[:, None] * freq
+    cos, sin = ang.cos().to(x.dtype), ang.sin().to(x.dtype)
+    if x.dim() == 3:
+        cos, sin = cos[:, None], sin[:, None]
+    re, im = x[..., 0::2], x[..., 1::2]
+    return torch.cat((re * cos - im * sin, im * cos + re * sin), -1)
+
+
+class LatentAttentionLayer(nn.Module, _Norms):
+    """Sparse multi-head latent attention + dense or routed feed-forward (GLM 5.3).
+
+    Queries go through a low-rank latent (``q_a`` -> norm -> ``q_b``); keys and values share one
+    compressed latent per token (``kv_a`` -> norm) plus one rotary key; the per-head key and value
+    projections (``kv_b``) are absorbed into the query and the output, so attention itself runs in
+    the latent space over the rows an indexer picked. A layer with ``indexer == "full"`` owns a
+    frozen indexer and returns its picks; a ``"shared"`` layer reuses the picks it is given.
+    Reference: packages/workloads/src/shadowspill_workloads/models/glm53/implementations/mlops/
+    attention.py:92-176 (``SparseMLA``), :49-89 (``Indexer``)."""
+
+    def __init__(self, cfg: DecoderConfig, index: int, dtype, lora=None):
+        super().__init__()
+        self.cfg, self.index = cfg, index
+        c, std = cfg, cfg.initializer_range
+        D, H = c.d_model, c.n_heads
+        ninit = "ones"
+        self.attn_norm = _param((D,), ninit, dtype=dtype)
+        self.q_a = _param((c.q_lora_rank, D), std=std, dtype=dtype)
+        self.q_a_norm = _param((c.q_lora_rank,), ninit, dtype=dtype)
+        self.q_b = _param((H * (c.qk_nope_head_dim + c.qk_rope_head_dim), c.q_lora_rank), std=std, dtype=dtype)
+        self.kv_a = _param((c.kv_lora_rank + c.qk_rope_head_dim, D), std=std, dtype=dtype)
+        self.kv_a_norm = _param((c.kv_lora_rank,), ninit, dtype=dtype)
+        self.kv_b = _param((H * (c.qk_nope_head_dim + c.v_head_dim), c.kv_lora_rank), std=std, dtype=dtype)
+        self.wo = _param((D, H * c.v_head_dim), std=std, dtype=dtype)
+        self.own_indexer = c.indexer_types[index] == "full"
+        if self.own_indexer:          # never trained: it only selects
+            self.ix_q = _param((c.index_n_heads * c.index_head_dim, c.q_lora_rank), std=std, dtype=dtype, trainable=False)
+            self.ix_k = _param((c.index_head_dim, D), std=std, dtype=dtype, trainable=False)
+            self.ix_k_norm = _param((c.index_head_dim,), "ones", dtype=dtype, trainable=False)
+            self.ix_k_bias = _param((c.index_head_dim,), "zeros", dtype=dtype, trainable=False)
+            self.ix_w = _param((c.index_n_heads, D), std=std, dtype=dtype, trainable=False)
+        self.mlp_norm = _param((D,), ninit, dtype=dtype)
+        self.moe = c.layer_is_moe(index)
+        if self.moe:
+            self.router = _param((c.n_experts, D), std=std, dtype=dtype)
+            self.router_bias = _param((c.n_experts,), "zeros", dtype=torch.float32, trainable=False)
+            self.w13 = _param((c.n_experts, 2 * c.d_expert, D), std=std, dtype=dtype)
+            self.w2 = _param((c.n_experts, D, c.d_expert), std=std, dtype=dtype)
+            if c.d_shared_expert:
+                self.sw13 = _param((2 * c.d_shared_expert, D), std=std, dtype=dtype)
+                self.sw2 = _param((D, c.d_shared_expert), std=std, dtype=dtype)
+        else:
+            self.w13 = _param((2 * c.d_ff, D), std=std, dtype=dtype)
+            self.w2 = _param((D, c.d_ff), std=std, dtype=dtype)
+        self._adapt(lora, dtype)
+
+    def _mlp(self, x):
+        if self.moe:
+            return _Norms._mlp(self, x)
+        h = self._norm(x, self.mlp_norm)
+        return x + self._lin(S.swiglu(self._lin(h, "w13")), "w2")
+
+    def _picks(self, h, q_res, positions, cu_seqlens):
+        c = self.cfg
+        T, r = h.shape[0], c.qk_rope_head_dim
+        q = S.linear(q_res, self.ix_q).reshape(T, c.index_n_heads, c.index_head_dim)
+        key = torch.nn.functional.layer_norm(S.linear(h, self.ix_k).float(), (c.index_head_dim,),
+                                             self.ix_k_norm.float(), self.ix_k_bias.float(), 1e-6).to(h.dtype)
+        q = torch.cat((_rotate_pairs(q[..., :r], positions, c.rope_base), q[..., r:]), -1)
+        key = torch.cat((_rotate_pairs(key[..., :r], positions, c.rope_base), key[..., r:]), -1)
+        return S.index_topk(q, key, S.linear(h, self.ix_w).float(), cu_seqlens, c.index_topk)
+
+    def forward(self, x, positions, cu_seqlens, picks=None):
+        c = self.cfg
+        T, H = x.shape[0], c.n_heads
+        n, r, dv, L = c.qk_nope_head_dim, c.qk_rope_head_dim, c.v_head_dim, c.kv_lora_rank
+        h = self._norm(x, self.attn_norm)
+        q_res = S.rmsnorm(self._lin(h, "q_a"), self.q_a_norm, 1e-6, False)[0]
+        qb = self._lin(q_res, "q_b").reshape(T, H, n + r)
+        query, q_rope = qb[..., :n], qb[..., n:]
+        kv = self._lin(h, "kv_a")
+        latent = S.rmsnorm(kv[:, :L], self.kv_a_norm, 1e-6, False)[0]
+        k_rope = _rotate_pairs(kv[:, L:], positions, c.rope_base)
+        q_rope = _rotate_pairs(q_rope, positions, c.rope_base)
+        if self.own_indexer:
+            picks = self._picks(h, q_res, positions, cu_seqlens)
+        w = self.kv_b.reshape(H, n + dv, L)
+        wk, wv = w[:, :n], w[:, n:]
+        q_latent = torch.einsum("thd,hdl->thl", query, wk)                   # key projection absorbed into the query
+        attended = S.sparse_latent_attention(q_latent, latent, picks, q_rope, k_rope, float((n + r) ** -0.5))
+        value = torch.einsum("thl,hdl->thd", attended, wv)                   # value projection applied after
+        x = x + self._lin(value.reshape(T, H * dv), "wo")
+        return self._mlp(x), picks
+
+
+class LatentAttentionGroup(nn.Module):
+    """A layer with its own indexer and the layers after it that reuse its picks: one repeated
+    child, hence one stage, so the picks never cross a stage boundary."""
+
+    def __init__(self, cfg: DecoderConfig, indices: list[int], dtype, lora=None):
+        super().__init__()
+        self.members = nn.ModuleList([LatentAttentionLayer(cfg, i, dtype, lora) for i in indices])
+
+    def forward(self, x, positions, cu_seqlens):
+        picks = None
+        for layer in self.members:
+            x, picks = layer(x, positions, cu_seqlens, picks)
+        return x
+
+
 class Head(nn.Module):
     """Final norm + output projection + masked weighted-sum cross entropy in row blocks."""
 
@@ -258,7 +385,9 @@ class DecoderLM(nn.Module):
         base = lora is None or lora.train_base
         self.embed = Embedding(cfg, dtype, base)
         layers = []
-        for i in range(cfg.n_layers):
+        if cfg.is_latent_attention:
+            layers = [LatentAttentionGroup(cfg, group, dtype, lora) for group in cfg.layer_groups()]
+        for i in range(0 if cfg.is_latent_attention else cfg.n_layers):
             plain = (cfg.layer_kind(i) == "attention" and not cfg.gated_attention and not cfg.is_moe
                      and lora is None)
             layers.append(DenseLayer(cfg, dtype) if plain else HybridLayer(cfg, i, dtype, lora))

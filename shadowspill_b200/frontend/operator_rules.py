@@ -77,6 +77,9 @@ for _r in (
     OperatorRule("ss.gated_delta_rule", "compute", None),
     OperatorRule("ss.moe_experts", "compute", None),
     OperatorRule("ss.moe_experts_lora", "compute", None),
+    OperatorRule("ss.moe_experts_routed", "compute", None),
+    OperatorRule("ss.sparse_latent_attention", "compute", None),
+    OperatorRule("ss.index_topk", "compute", None),
     OperatorRule("ss.rmsnorm", "memory", (0,)),
     OperatorRule("ss.rope", "memory", (0, 1)),
     OperatorRule("ss.swiglu", "memory", (0,)),

@@ -701,8 +701,199 @@ def _moe_lora_bwd(ctx, gy):
 moe_experts_lora.register_autograd(_moe_lora_bwd, setup_context=_moe_lora_setup)
 
 
+# ------------------------------------------------------------------------ sparse latent attention (GLM)
+def _sequence_start(cu_seqlens: Tensor, T: int) -> Tensor:
+    """For every token row, the first row of its sequence (``cu_seqlens`` may be padded with T)."""
+    rows = torch.arange(T, device=cu_seqlens.device)
+    seq = torch.searchsorted(cu_seqlens.to(torch.int64), rows, right=True) - 1
+    return cu_seqlens.to(torch.int64)[seq.clamp_min(0)]
+
+
+@custom_op("ss::index_topk", mutates_args=())
+def index_topk(q: Tensor, key: Tensor, head_weights: Tensor, cu_seqlens: Tensor, top_k: int) -> Tensor:
+    """The sparse-attention indexer's selection: for query row ``t`` the ``top_k`` rows ``s <= t``
+    of its own sequence with the largest score ``sum_h w[t, h] * relu(q[t, h] . key[s])`` (bf16
+    operands, fp32 accumulation), as global row numbers in decreasing score order; ``-1`` where a
+    query has fewer than ``top_k`` predecessors. Integer output: nothing is differentiated.
+    Reference: the indexer of packages/workloads/src/shadowspill_workloads/models/glm53/
+    implementations/mlops/attention.py:49-89 (``pooled_topk`` with pool size one).
+    Evaluated in blocks of query rows so that the score matrix stays small."""
+    T, K = q.shape[0], int(top_k)
+    start = _sequence_start(cu_seqlens, T)
+    out = torch.full((T, K), -1, dtype=torch.int32, device=q.device)
+    cols = torch.arange(T, device=q.device)
+    block = 1024
+    kf = key.float()
+    for lo in range(0, T, block):
+        hi = min(T, lo + block)
+        dots = torch.einsum("thd,sd->ths", q[lo:hi].float(), kf[:hi])
+        score = (torch.relu(dots) * head_weights[lo:hi].float()[:, :, None]).sum(1)          # [b, hi]
+        rows = torch.arange(lo, hi, device=q.device)[:, None]
+        ok = (cols[None, :hi] <= rows) & (cols[None, :hi] >= start[lo:hi, None])
+        score = score.masked_fill(~ok, float("-inf"))
+        k = min(K, hi)
+        vals, idx = torch.topk(score, k, dim=1)
+        out[lo:hi, :k] = torch.where(torch.isfinite(vals), idx, torch.full_like(idx, -1)).to(torch.int32)
+    return out
+
+
+@index_topk.register_fake
+def _(q, key, head_weights, cu_seqlens, top_k):
+    return torch.empty((q.shape[0], int(top_k)), dtype=torch.int32, device=q.device)
+
+
+def _sparse_latent_torch(q_latent: Tensor, latent: Tensor, indices: Tensor, q_rope: Tensor, k_rope: Tensor,
+                         scale: float) -> Tensor:
+    """Definition, in blocks of query rows: logits over the picked rows from the latent part and the
+    rotary part, softmax over the picks, output = the picked latents weighted (the latent is key and
+    value at once; the per-head value projection is applied by the caller)."""
+    T, H, L = q_latent.shape
+    outs = []
+    block = 512
+    safe = indices.clamp_min(0).long()
+    for lo in range(0, T, block):
+        hi = min(T, lo + block)
+        idx = safe[lo:hi]                                        # [b, K]
+        keys, rope = latent[idx], k_rope[idx]                    # [b, K, L], [b, K, R]
+        logits = (torch.einsum("bhl,bkl->bhk", q_latent[lo:hi].float(), keys.float())
+                  + torch.einsum("bhr,bkr->bhk", q_rope[lo:hi].float(), rope.float())) * scale
+        logits = logits.masked_fill((indices[lo:hi] < 0)[:, None, :], float("-inf"))
+        p = torch.softmax(logits, dim=-1)
+        outs.append(torch.einsum("bhk,bkl->bhl", p, keys.float()).to(q_latent.dtype))
+    return torch.cat(outs, 0)
+
+
+@custom_op("ss::sparse_latent_attention", mutates_args=())
+def sparse_latent_attention(q_latent: Tensor, latent: Tensor, indices: Tensor, q_rope: Tensor, k_rope: Tensor,
+                            scale: float) -> Tensor:
+    """Attention of every query over the rows its indexer picked, in the compressed latent space
+    (tensor-operation form on every device; no hand-written kernel yet). Reference:
+    ``mlops.sparse_latent_attention`` as called in .../glm53/implementations/mlops/attention.py:150."""
+    with torch.no_grad():
+        return _sparse_latent_torch(q_latent, latent, indices, q_rope, k_rope, scale)
+
+
+@sparse_latent_attention.register_fake
+def _(q_latent, latent, indices, q_rope, k_rope, scale):
+    return torch.empty_like(q_latent, memory_format=torch.contiguous_format)
+
+
+@custom_op("ss::sparse_latent_attention_bwd", mutates_args=())
+def sparse_latent_attention_bwd(q_latent: Tensor, latent: Tensor, indices: Tensor, q_rope: Tensor, k_rope: Tensor,
+                                gy: Tensor, scale: float) -> tuple[Tensor, Tensor, Tensor, Tensor]:
+    return _autograd_elsewhere(lambda a, b, c, d: _sparse_latent_torch(a, b, indices, c, d, scale),
+                               (q_latent, latent, q_rope, k_rope), gy)
+
+
+@sparse_latent_attention_bwd.register_fake
+def _(q_latent, latent, indices, q_rope, k_rope, gy, scale):
+    c = torch.contiguous_format
+    return (torch.empty_like(q_latent, memory_format=c), torch.empty_like(latent, memory_format=c),
+            torch.empty_like(q_rope, memory_format=c), torch.empty_like(k_rope, memory_format=c))
+
+
+def _sla_setup(ctx, inputs, output):
+    ctx.save_for_backward(*inputs[:5])
+    ctx.scale = inputs[5]
+
+
+def _sla_bwd(ctx, gy):
+    q_latent, latent, indices, q_rope, k_rope = ctx.saved_tensors
+    dq, dl, dqr, dkr = torch.ops.ss.sparse_latent_attention_bwd(q_latent, latent, indices, q_rope, k_rope, gy, ctx.scale)
+    return dq, dl, None, dqr, dkr, None
+
+
+sparse_latent_attention.register_autograd(_sla_bwd, setup_context=_sla_setup)
+
+
+# ------------------------------------------------------------------------ routed experts, routing given
+def _moe_routed_torch(h: Tensor, ids: Tensor, wts: Tensor, w13: Tensor, w2: Tensor) -> Tensor:
+    """Top-k SwiGLU experts with the routing decided outside (``ids`` [T, k], ``wts`` [T, k]): the
+    form for routers that are not a softmax (sigmoid scores with a selection-only bias)."""
+    k = ids.shape[1]
+    flat = ids.reshape(-1).long()
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=w13.shape[0]).tolist()
+    tok = order // k
+    w_sorted = wts.reshape(-1)[order].to(h.dtype)
+    out = torch.zeros_like(h)
+    pos = 0
+    for e, n in enumerate(counts):
+        if n == 0:
+            continue
+        rows = tok[pos:pos + n]
+        x = h.index_select(0, rows)
+        gu = x @ w13[e].t()
+        f = gu.shape[1] // 2
+        act = (torch.nn.functional.silu(gu[:, :f].float()).to(h.dtype) * gu[:, f:])
+        out = out.index_add(0, rows, (act @ w2[e].t()) * w_sorted[pos:pos + n, None])
+        pos += n
+    return out
+
+
+def _moe_routed_cuda(h, ids, wts, w13, w2, sink):
+    from ..models import autograd_ops as A
+    from ..ops import moe as moe_ops
+    counts = torch.bincount(ids.reshape(-1).long(), minlength=w13.shape[0]).to(torch.int32)
+    lay = moe_ops.Layout(ids.to(torch.int32).contiguous(), counts)
+    xs = A.expert_gather(h, lay)
+    ys = A.grouped_linear(A.swiglu(A.grouped_linear(xs, w13, lay, sink, "w13")), w2, lay, sink, "w2")
+    return A.expert_combine(ys, wts.float().contiguous(), lay)
+
+
+@custom_op("ss::moe_experts_routed", mutates_args=())
+def moe_experts_routed(h: Tensor, ids: Tensor, wts: Tensor, w13: Tensor, w2: Tensor) -> Tensor:
+    with torch.no_grad():
+        if h.is_cuda and F._cuda(h):
+            return _moe_routed_cuda(_c(h), ids, wts, w13, w2, None)
+        return _moe_routed_torch(h, ids, wts, w13, w2)
+
+
+@moe_experts_routed.register_fake
+def _(h, ids, wts, w13, w2):
+    return torch.empty_like(h, memory_format=torch.contiguous_format)
+
+
+@custom_op("ss::moe_experts_routed_bwd", mutates_args=())
+def moe_experts_routed_bwd(h: Tensor, ids: Tensor, wts: Tensor, w13: Tensor, w2: Tensor, gy: Tensor,
+                           banks: bool) -> tuple[Tensor, Tensor, Tensor, Tensor]:
+    """Gradients of rows, routing weights and (``banks``) both expert banks; without ``banks`` the
+    last two results are empty and no bank-sized tensor is touched."""
+    if h.is_cuda and F._cuda(h):
+        from ..models.autograd_ops import GradSink
+        G = {"w13": torch.zeros_like(w13), "w2": torch.zeros_like(w2)} if banks else {}
+        sink = GradSink(G, False)
+        dh, dw = _autograd_elsewhere(lambda a, b: _moe_routed_cuda(a, ids, b, w13, w2, sink), (_c(h), _c(wts)), _c(gy))
+        return dh, dw, G.get("w13", h.new_empty(0)), G.get("w2", h.new_empty(0))
+    if banks:
+        return _autograd_elsewhere(lambda a, b, c, d: _moe_routed_torch(a, ids, b, c, d), (h, wts, w13, w2), gy)
+    dh, dw = _autograd_elsewhere(lambda a, b: _moe_routed_torch(a, ids, b, w13, w2), (h, wts), gy)
+    return dh, dw, h.new_empty(0), h.new_empty(0)
+
+
+@moe_experts_routed_bwd.register_fake
+def _(h, ids, wts, w13, w2, gy, banks):
+    c = torch.contiguous_format
+    return (torch.empty_like(h, memory_format=c), torch.empty_like(wts, memory_format=c),
+            torch.empty_like(w13) if banks else h.new_empty(0), torch.empty_like(w2) if banks else h.new_empty(0))
+
+
+def _moe_routed_setup(ctx, inputs, output):
+    ctx.save_for_backward(*inputs[:5])
+
+
+def _moe_routed_bwd(ctx, gy):
+    h, ids, wts, w13, w2 = ctx.saved_tensors
+    banks = bool(ctx.needs_input_grad[3] or ctx.needs_input_grad[4])
+    dh, dw, d13, d2 = torch.ops.ss.moe_experts_routed_bwd(h, ids, wts, w13, w2, gy, banks)
+    return dh, None, dw, (d13 if banks else None), (d2 if banks else None)
+
+
+moe_experts_routed.register_autograd(_moe_routed_bwd, setup_context=_moe_routed_setup)
+
+
 MEMORY_BOUND = ("ss.rmsnorm", "ss.rope", "ss.swiglu", "ss.l2norm", "ss.conv_silu", "ss.gated_rmsnorm",
                 "ss.embedding")
 # Operators dominated by tensor-core work: keeping their outputs saves real time.
 COMPUTE_BOUND = ("ss.linear", "ss.gemm", "ss.attention", "ss.gated_delta_rule", "ss.head_loss", "ss.moe_experts",
-                 "ss.moe_experts_lora")
+                 "ss.moe_experts_lora", "ss.sparse_latent_attention", "ss.moe_experts_routed", "ss.index_topk")

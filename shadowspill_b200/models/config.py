@@ -45,10 +45,36 @@ class DecoderConfig:
     gated_shared_expert: bool = False
     router_renormalize: bool = True
     router_aux_coef: float = 0.0
+    router_scoring: str = "softmax"       # "sigmoid" (GLM): scores + a selection-only bias, top-k renormalised
+    routed_scaling_factor: float = 1.0
+    first_dense_layers: int = 0           # GLM: the first k layers have a dense feed-forward
+    # sparse multi-head latent attention (GLM 5.3): queries and keys/values through low-rank
+    # latents, a frozen indexer that picks index_topk earlier tokens per query
+    q_lora_rank: int = 0
+    kv_lora_rank: int = 0
+    qk_nope_head_dim: int = 0
+    qk_rope_head_dim: int = 0
+    v_head_dim: int = 0
+    index_n_heads: int = 0
+    index_head_dim: int = 0
+    index_topk: int = 0
+    indexer_types: tuple = ()             # per layer "full" (own indexer) or "shared" (reuses the last full one's picks)
 
     def __post_init__(self) -> None:
         if self.n_heads % self.n_kv_heads:
             raise ValueError("n_heads must be divisible by n_kv_heads")
+        if self.router_scoring not in ("softmax", "sigmoid"):
+            raise ValueError("router_scoring is 'softmax' or 'sigmoid'")
+        if self.kv_lora_rank:
+            kinds = tuple(self.indexer_types) or tuple("full" if (i < 3 or i % 4 == 2) else "shared"
+                                                       for i in range(self.n_layers))
+            if len(kinds) < self.n_layers or kinds[0] != "full" or any(k not in ("full", "shared") for k in kinds):
+                raise ValueError("indexer_types must start with 'full' and name every layer 'full' or 'shared'")
+            object.__setattr__(self, "indexer_types", tuple(kinds[:self.n_layers]))
+            if self.qk_rope_head_dim % 2 or self.index_head_dim < self.qk_rope_head_dim or self.index_topk < 1:
+                raise ValueError("sparse latent attention needs an even rope width inside the index width and index_topk >= 1")
+        elif self.indexer_types:
+            object.__setattr__(self, "indexer_types", tuple(self.indexer_types))
         if self.n_experts and not (0 < self.top_k <= self.n_experts):
             raise ValueError("top_k must be in [1, n_experts]")
         if self.full_attention_interval and not self.dn_v_heads:
@@ -57,6 +83,26 @@ class DecoderConfig:
     @property
     def is_moe(self) -> bool:
         return self.n_experts > 0
+
+    @property
+    def is_latent_attention(self) -> bool:
+        return self.kv_lora_rank > 0
+
+    def layer_is_moe(self, index: int) -> bool:
+        return self.is_moe and index >= self.first_dense_layers
+
+    def layer_groups(self) -> list[list[int]]:
+        """Layers that must share a stage: a layer whose sparse attention reuses the picks of an
+        earlier indexer stays with that indexer's layer, so the picks never cross a stage boundary."""
+        if not self.indexer_types:
+            return [[i] for i in range(self.n_layers)]
+        groups: list[list[int]] = []
+        for i, kind in enumerate(self.indexer_types):
+            if kind == "full" or not groups:
+                groups.append([i])
+            else:
+                groups[-1].append(i)
+        return groups
 
     @property
     def rotary_width(self) -> int:
@@ -75,9 +121,17 @@ class DecoderConfig:
 
     @staticmethod
     def from_json(d: dict[str, Any]) -> "DecoderConfig":
+        d = dict(d)
+        if "indexer_types" in d:
+            d["indexer_types"] = tuple(d["indexer_types"] or ())
         return DecoderConfig(**d)
 
     def parameter_count(self) -> int:
+        if self.is_latent_attention:          # defined as a module for the graph frontend only
+            import torch
+            from ..frontend.modules import DecoderLM
+            with torch.device("meta"):
+                return sum(p.numel() for p in DecoderLM(self).parameters())
         from .decoder import build_stages
         return sum(s.parameter_count() for s in build_stages(self))
 
@@ -140,6 +194,20 @@ PRESETS: dict[str, DecoderConfig] = {
     "qwen35moe-35b-a3b": replace(_qwen35(40, 2048, 16, 2, 256, 0, 16, 32), family="qwen35moe",
                                  n_experts=256, top_k=8, d_expert=512, d_shared_expert=512,
                                  gated_shared_expert=True),
+    # ---- GLM 5.3: sparse multi-head latent attention + sigmoid-scored routed experts
+    # (published shape: packages/workloads/src/shadowspill_workloads/models/glm53/config.py:10-43)
+    "glm53-tiny": DecoderConfig("glm53", 4, 128, 16, 16, 96, 128, 128, rope_base=8_000_000.0,
+                                first_dense_layers=1, n_experts=4, top_k=2, d_expert=128, d_shared_expert=128,
+                                router_scoring="sigmoid", routed_scaling_factor=2.5, q_lora_rank=32,
+                                kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=64, v_head_dim=32,
+                                index_n_heads=2, index_head_dim=64, index_topk=8,
+                                indexer_types=("full", "shared", "full", "shared")),
+    "glm53-published": DecoderConfig("glm53", 78, 6144, 64, 64, 256, 12288, 154_880, rope_base=8_000_000.0,
+                                     first_dense_layers=3, n_experts=256, top_k=8, d_expert=2048,
+                                     d_shared_expert=2048, router_scoring="sigmoid", routed_scaling_factor=2.5,
+                                     q_lora_rank=2048, kv_lora_rank=512, qk_nope_head_dim=192,
+                                     qk_rope_head_dim=64, v_head_dim=256, index_n_heads=32, index_head_dim=128,
+                                     index_topk=2048),
     # ---- the small non-text model: Linear(16, 32) -> SiLU -> Linear(32, 8), fp32
     # (d_ff = input width, d_model = hidden width, vocab_size = output width; models/regression.py)
     "regression": DecoderConfig("regression", 0, 32, 1, 1, 1, 16, 8, initializer_range=0.25),

@@ -419,3 +419,61 @@ def test_an_operator_of_the_users_own_takes_part_through_its_rule():
     assert any("soft_gate" in op_name(n) for n in save.backward.graph.nodes)
     # row chunking cut it: four copies in the chunked forward
     assert sum("soft_gate" in op_name(n) for n in layer.pairs.pairs["recompute"].forward.graph.nodes) == 4
+
+
+def test_sparse_latent_attention_family_trains_like_eager_pytorch():
+    """GLM 5.3 in small: sparse multi-head latent attention with a frozen indexer whose picks are
+    reused by the next layer, sigmoid-scored routed experts with a shared expert, a dense first
+    layer. Layers that share picks form one stage. Five planned updates (forced to spill) equal
+    eager PyTorch + AdamW on the same module."""
+    from shadowspill_b200.frontend.modules import DecoderLM, init_
+    cfg = preset("glm53-tiny")
+    assert cfg.layer_groups() == [[0, 1], [2, 3]]
+    prog, desc = build_step(cfg, GEO, StepDataOrdering(), dtype=torch.float32, selection={1: "save", 2: "save_attention"})
+    stages = desc.stages()
+    assert [type(s).__name__ for s in stages] == ["GraphEmbeddingStage", "GraphStage", "GraphStage", "GraphHeadStage"]
+    first, second = stages[1], stages[2]
+    assert any(p.name == "members_1_kv_b" for p in first.params) and not any("ix_" in p.name and p.trainable for p in first.params)
+    assert sum("ix_q" in p.name for p in first.params) == 1          # one indexer per group: the second layer shares
+    ops_of = lambda st: [op_name(n) for n in st.graph.gm.graph.nodes]
+    assert ops_of(first).count("ss.index_topk") == 1 and ops_of(first).count("ss.sparse_latent_attention") == 2
+    assert "ss.moe_experts_routed" in ops_of(first) and ops_of(second).count("ss.moe_experts_routed") == 2
+    assert first.graph.key != second.graph.key                        # the first group has the dense layer
+    assert len(first.SAVE_SETS["save"]) > len(first.SAVE_SETS["save_attention"]) >= 0
+    plan = _plan(prog)
+    assert plan.summary.fetch_bytes > 0
+    ex = Executor(plan, desc, device="cpu", seed=5, hyper=Hyperparameters(lr=3e-3))
+    ex.initialize()
+    model = DecoderLM(cfg, torch.float32)
+    state = ex.state_dict()
+    params = dict(model.named_parameters())
+    names = {}
+    for st, group in zip(stages, [["embed"], ["layers.0"], ["layers.1"], ["head"]]):
+        for p in st.params:
+            target = next(t for t in params if t.startswith(group[0] + ".") and
+                          (t.split(".")[-1] == p.name or "_".join(t.split(".")[2:]) == p.name))
+            names[f"{st.name}.{p.name}"] = target
+    with torch.no_grad():
+        for k, target in names.items():
+            params[target].copy_(state[k])
+    trainable = [p for p in model.parameters() if p.requires_grad]
+    opt = torch.optim.AdamW(trainable, lr=3e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0)
+    for step in range(5):
+        host = _batches(cfg, step)
+        got = ex.run(host).loss
+        opt.zero_grad()
+        want = 0.0
+        for mb in host:
+            m = to_device(mb, "cpu")
+            loss = model(m.tokens, m.targets, m.weights, m.positions, m.cu_seqlens)
+            loss.sum().backward()
+            want += float(loss)
+        opt.step()
+        assert abs(got - want) < 2e-5 * max(1.0, abs(want)), (step, got, want)
+    state = ex.state_dict()
+    for k, target in names.items():
+        v = params[target].detach()
+        diff = (state[k] - v).float()
+        assert float(diff.abs().max()) <= 2 * 3e-3 + 1e-6, k
+        assert float(diff.norm() / v.float().norm().clamp_min(1e-9)) < 3e-3, k
+    ex.close()
