@@ -314,7 +314,9 @@ class LatentAttentionLayer(nn.Module, _Norms):
                                              self.ix_k_norm.float(), self.ix_k_bias.float(), 1e-6).to(h.dtype)
         q = torch.cat((_rotate_pairs(q[..., :r], positions, c.rope_base), q[..., r:]), -1)
         key = torch.cat((_rotate_pairs(key[..., :r], positions, c.rope_base), key[..., r:]), -1)
-        return S.index_topk(q, key, S.linear(h, self.ix_w).float(), cu_seqlens, c.index_topk)
+        # a handful of head weights per token: a plain product (no tile or alignment constraints)
+        head_weights = h.float() @ self.ix_w.float().t()
+        return S.index_topk(q, key, head_weights, cu_seqlens, c.index_topk)
 
     def forward(self, x, positions, cu_seqlens, picks=None):
         c = self.cfg
