@@ -86,6 +86,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     if out.stride(-1) != 1 or out.dtype not in (_BF16, torch.float32):
         raise ValueError("gemm output must be bf16/fp32 with unit inner stride")
+    if N % 8 or a.stride(0) % 8 or b.stride(0) % 8 or out.stride(0) % (4 if out.dtype == torch.float32 else 8):
+        # TMA moves 16-byte pieces: say which size breaks that instead of returning the kernel's code
+        raise ValueError(f"gemm on the GPU needs N and the row strides in multiples of 8 elements "
+                         f"(N={N}, strides {a.stride(0)}, {b.stride(0)}, {out.stride(0)}); pad the operand")
     if _PAIR_GEMM and bn == 0 and M >= 256 and N >= 128:
         # CTA-pair kernel (tcgen05 cta_group::2): 256x256 tiles, half the shared-memory
         # traffic per FLOP of the single-CTA kernel

@@ -492,7 +492,7 @@ def test_sparse_latent_attention_family_on_the_gpu_follows_the_cpu_run():
     from shadowspill_b200.ops import _lib
     cfg = replace(preset("glm53-tiny"), d_model=256, d_ff=256, vocab_size=2048, q_lora_rank=64, kv_lora_rank=64,
                   qk_nope_head_dim=64, v_head_dim=64, head_dim=128, index_n_heads=8, index_topk=32, d_expert=128,
-                  d_shared_expert=128)
+                  d_shared_expert=128, n_experts=8)        # the router GEMM wants its width in multiples of 8
     geo = BatchGeometry(microbatch_tokens=1024, n_microbatches=2, slots=33, mean_seqlen=256)
     losses = {}
     for device, dtype in (("cpu", torch.float32), ("cuda", torch.bfloat16)):
