@@ -36,7 +36,7 @@ from ..models.decoder import DenseLayerStage, build_stages
 
 _ARCH = {"llama3": "LlamaForCausalLM", "qwen3": "Qwen3ForCausalLM", "olmoe": "OlmoeForCausalLM",
          "qwen3moe": "Qwen3MoeForCausalLM", "qwen35": "Qwen3_5ForConditionalGeneration",
-         "qwen35moe": "Qwen3_5MoeForConditionalGeneration"}
+         "qwen35moe": "Qwen3_5MoeForConditionalGeneration", "glm53": "GlmMoeDsaForCausalLM"}
 _IGNORED_PREFIXES = ("model.visual.", "mtp.")
 
 
@@ -151,10 +151,60 @@ def _layer_sources(cfg: DecoderConfig, i: int, stage) -> dict[str, Source]:
     return S
 
 
+def _latent_layer_sources(cfg: DecoderConfig, i: int) -> dict[str, Source]:
+    """GLM 5.3 (``glm_moe_dsa``) names of layer ``i`` (the reference's naming:
+    packages/workloads/src/shadowspill_workloads/models/glm53/weights.py:3-9)."""
+    pre = f"model.layers.{i}."
+    a, ix, m = pre + "self_attn.", pre + "self_attn.indexer.", pre + "mlp."
+    S = {"attn_norm": _tensor(pre + "input_layernorm.weight"),
+         "mlp_norm": _tensor(pre + "post_attention_layernorm.weight"),
+         "q_a": _tensor(a + "q_a_proj.weight"), "q_a_norm": _tensor(a + "q_a_layernorm.weight"),
+         "q_b": _tensor(a + "q_b_proj.weight"), "kv_a": _tensor(a + "kv_a_proj_with_mqa.weight"),
+         "kv_a_norm": _tensor(a + "kv_a_layernorm.weight"), "kv_b": _tensor(a + "kv_b_proj.weight"),
+         "wo": _tensor(a + "o_proj.weight"),
+         "ix_q": _tensor(ix + "wq_b.weight"), "ix_k": _tensor(ix + "wk.weight"),
+         "ix_k_norm": _tensor(ix + "k_norm.weight"), "ix_k_bias": _tensor(ix + "k_norm.bias"),
+         "ix_w": _tensor(ix + "weights_proj.weight")}
+    if cfg.layer_is_moe(i):
+        F, D = cfg.d_expert, cfg.d_model
+        S["router"] = _tensor(m + "gate.weight")
+        S["router_bias"] = _tensor(m + "gate.e_score_correction_bias")
+        S["w13"] = _expert_bank((m + "experts.{e}.gate_proj.weight", m + "experts.{e}.up_proj.weight"),
+                                cfg.n_experts, (F, F))
+        S["w2"] = _expert_bank((m + "experts.{e}.down_proj.weight",), cfg.n_experts, (D,))
+        if cfg.d_shared_expert:
+            Fs = cfg.d_shared_expert
+            S["sw13"] = _joined((m + "shared_experts.gate_proj.weight", m + "shared_experts.up_proj.weight"), (Fs, Fs))
+            S["sw2"] = _tensor(m + "shared_experts.down_proj.weight")
+    else:
+        S["w13"] = _joined((m + "gate_proj.weight", m + "up_proj.weight"), (cfg.d_ff, cfg.d_ff))
+        S["w2"] = _tensor(m + "down_proj.weight")
+    return S
+
+
+def _latent_sources(cfg: DecoderConfig, stages) -> dict[str, Source]:
+    """The family is exported in stages of several layers: a stage parameter is traced back to its
+    layer through the module path the export recorded for it (``layers.<group>.members.<j>.<name>``)."""
+    if stages is None:
+        from ..frontend.graph_stage import build_graph_stages
+        stages = build_graph_stages(cfg, 256, 16)
+    groups = cfg.layer_groups()
+    out = {"embed.embed": _tensor("model.embed_tokens.weight"), "head.final_norm": _tensor("model.norm.weight"),
+           "head.head": _tensor("lm_head.weight")}
+    for st in stages[1:-1]:
+        for local, target in zip(st.graph.param_names, st.graph.param_targets):
+            parts = target.split(".")                    # layers, g, members, j, name
+            layer = groups[int(parts[1])][int(parts[3])]
+            out[f"{st.name}.{local}"] = _latent_layer_sources(cfg, layer)[parts[4]]
+    return out
+
+
 def parameter_sources(cfg: DecoderConfig, stages=None) -> dict[str, Source]:
     """``{"<stage>.<param>": Source}`` for every base (non-adapter) parameter of the model."""
     if not supported(cfg):
         raise ValueError(f"no Hugging Face mapping for family {cfg.family!r}")
+    if cfg.is_latent_attention:
+        return _latent_sources(cfg, stages)
     stages = stages or build_stages(cfg)
     pre = _prefix(cfg)
     out = {"embed.embed": _tensor(pre + "embed_tokens.weight"),
@@ -184,6 +234,9 @@ def to_hf(cfg: DecoderConfig, state: dict[str, torch.Tensor], stages=None) -> di
 
 
 def from_hf(cfg: DecoderConfig, hf: dict[str, torch.Tensor], stages=None) -> dict[str, torch.Tensor]:
+    if stages is None and cfg.is_latent_attention:
+        from ..frontend.graph_stage import build_graph_stages
+        stages = build_graph_stages(cfg, 256, 16)
     stages = stages or build_stages(cfg)
     shapes = {f"{st.name}.{p.name}": tuple(p.shape) for st in stages for p in st.params}
     out: dict[str, torch.Tensor] = {}
@@ -219,6 +272,15 @@ def hf_config(cfg: DecoderConfig) -> dict:
                  moe_intermediate_size=cfg.d_expert, norm_topk_prob=cfg.router_renormalize)
         if cfg.d_shared_expert:
             d["shared_expert_intermediate_size"] = cfg.d_shared_expert
+    if cfg.is_latent_attention:
+        d.update(model_type="glm_moe_dsa", q_lora_rank=cfg.q_lora_rank, kv_lora_rank=cfg.kv_lora_rank,
+                 qk_nope_head_dim=cfg.qk_nope_head_dim, qk_rope_head_dim=cfg.qk_rope_head_dim,
+                 v_head_dim=cfg.v_head_dim, index_n_heads=cfg.index_n_heads, index_head_dim=cfg.index_head_dim,
+                 index_topk=cfg.index_topk, indexer_types=list(cfg.indexer_types),
+                 first_k_dense_replace=cfg.first_dense_layers, intermediate_size=cfg.d_ff,
+                 n_routed_experts=cfg.n_experts, n_shared_experts=1 if cfg.d_shared_expert else 0,
+                 routed_scaling_factor=cfg.routed_scaling_factor, scoring_func="sigmoid", topk_method="noaux_tc",
+                 rope_parameters={"rope_type": "default", "rope_theta": cfg.rope_base})
     if cfg.full_attention_interval:
         d.update(full_attention_interval=cfg.full_attention_interval,
                  layer_types=["full_attention" if cfg.layer_kind(i) == "attention" else "linear_attention"

@@ -288,3 +288,34 @@ def test_frozen_base_is_omitted_and_generators_resume(tmp_path):
     sa, sb = a.state_dict(), b.state_dict()
     assert all(torch.equal(sa[k], sb[k]) for k in sa)
     a.close(); b.close()
+
+
+def test_latent_attention_family_round_trips_through_hugging_face_names(tmp_path):
+    """GLM 5.3 is exported in stages of several layers: each stage parameter finds its layer's
+    checkpoint name through the module path the export recorded, and the round trip is exact."""
+    import torch
+    from shadowspill_b200.checkpoint import hf
+    from shadowspill_b200.frontend.graph_stage import build_graph_stages
+    from shadowspill_b200.models.config import preset
+    cfg = preset("glm53-tiny")
+    assert hf.supported(cfg) and hf.hf_config(cfg)["model_type"] == "glm_moe_dsa"
+    stages = build_graph_stages(cfg, 256, 16, torch.float32)
+    gen = torch.Generator().manual_seed(0)
+    state = {f"{st.name}.{p.name}": torch.randn(p.shape, generator=gen) for st in stages for p in st.params}
+    named = hf.to_hf(cfg, state, stages)
+    c = cfg
+    assert named["model.layers.1.self_attn.kv_b_proj.weight"].shape == \
+        (c.n_heads * (c.qk_nope_head_dim + c.v_head_dim), c.kv_lora_rank)
+    assert "model.layers.0.self_attn.indexer.wq_b.weight" in named          # layer 0 owns an indexer
+    assert "model.layers.1.self_attn.indexer.wq_b.weight" not in named      # layer 1 shares its picks
+    assert named["model.layers.2.self_attn.indexer.k_norm.bias"].shape == (c.index_head_dim,)
+    assert named["model.layers.0.mlp.up_proj.weight"].shape == (c.d_ff, c.d_model)             # dense first layer
+    assert named["model.layers.3.mlp.gate.e_score_correction_bias"].shape == (c.n_experts,)
+    assert named[f"model.layers.1.mlp.experts.{c.n_experts - 1}.down_proj.weight"].shape == (c.d_model, c.d_expert)
+    assert named["model.layers.2.mlp.shared_experts.gate_proj.weight"].shape == (c.d_shared_expert, c.d_model)
+    # the second layer of the first group is stored under that layer's own number
+    assert torch.equal(named["model.layers.1.self_attn.o_proj.weight"], state[f"{stages[1].name}.members_1_wo"])
+    hf.save_hf(cfg, state, tmp_path / "glm", stages)
+    back = hf.load_hf(cfg, tmp_path / "glm")
+    assert set(back) == set(state)
+    assert all(torch.equal(back[k], v) for k, v in state.items())
