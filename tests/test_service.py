@@ -645,3 +645,33 @@ def test_an_extension_package_adds_components(tmp_path):
         Server(tmp_path / "bad", token="secret", extensions=["no_such_extension_module"])
     with pytest.raises(ExtensionError, match="already registered"):
         Server(tmp_path / "twice", token="secret", extensions=[name, name])
+
+
+def test_the_latent_attention_family_trains_through_the_service(service):
+    """``glm53-tiny`` by its catalog name: the builder takes the graph frontend for it whatever the
+    build option says, layers that share picks become one stage, and steps, accumulation, a forward
+    and a checkpoint go through the public API."""
+    with ServiceClient(service.url, token="secret") as svc:
+        preview = svc.describe_training(model=Model("glm53-tiny", dtype="float32"),
+                                        batch=BatchConfig(tokens_per_step=512, microbatch_tokens=256),
+                                        memory=Memory(device_gib=0.6, spill_gib=0.25),
+                                        resources=Resources(gpus=1, backend="cpu")).result()
+        assert preview["parameters"] > 1_000_000
+        tr = svc.create_training_client(
+            Model("glm53-tiny", dtype="float32"), Optimizer(lr=3e-3, parameter_rounding="nearest"),
+            batch=BatchConfig(tokens_per_step=512, microbatch_tokens=256),
+            memory=Memory(device_gib=0.6, spill_gib=0.25), resources=Resources(gpus=1, backend="cpu"),
+            preparation=Preparation(profiling=ProfilingOptions(enabled=False), calibrate=False,
+                                    planning=PlanningOptions(minimum_object_bytes_evict_eligible=1024, workers=1)),
+            operations=("step", "forward", "forward_backward", "optim_step"), timeout=300).result()
+        try:
+            seqs = lambda s: [np.asarray(x) % 128 for x in _sequences(s)]
+            losses = [tr.step(text_batch(seqs(s % 2))).result().loss for s in range(4)]
+            assert losses[2] < losses[0] and losses[3] < losses[1]
+            tr.forward_backward(text_batch(seqs(2))).result()
+            assert tr.optim_step().result().completed_updates == 5
+            scored = tr.forward(text_batch(seqs(0))).result()
+            assert 0 < scored.loss < losses[0] and len(scored.outputs["per_datum"]) == len(seqs(0))
+            assert tr.save_checkpoint("glm").result().outputs["checkpoint"] == "glm"
+        finally:
+            tr.close()
