@@ -16,6 +16,7 @@ from .packing import (Assignment, BatchError, BatchValidation, BatchValidator, C
 from .parallelism import MIN_SHARD_BYTES, data_parallel, expert_parallel  # noqa: F401
 from .schedules import Constant, WarmupCosine  # noqa: F401
 from .service import ServiceClient  # noqa: F401
+from .transport import SSH, SSHTunnel, TransportError  # noqa: F401
 from .text import (Datum, build_candidates, policy_datum, tensor_datum, text_batch,  # noqa: F401
                    text_batch_statistics, text_datum)
 from .training import OperationFailed, TrainingClient, TrainingResult  # noqa: F401

@@ -54,9 +54,26 @@ class ProgressDisplay:
 
 
 class ServiceClient:
-    def __init__(self, url: str, token: str = "", timeout: float = 600.0, max_workers: int = 8):
+    def __init__(self, url: str | None = None, token: str = "", timeout: float = 600.0, max_workers: int = 8,
+                 ssh=None):
+        """``ssh`` (a ``client.transport.SSH``): reach the service through an OpenSSH forward that this
+        client owns and closes with itself; ``url`` is then not given."""
+        self.tunnel = None
+        if ssh is not None:
+            if url:
+                raise ValueError("give a url or ssh settings, not both")
+            from .transport import SSHTunnel
+            self.tunnel = SSHTunnel(ssh)
+            url = self.tunnel.open()
+        elif not url:
+            raise ValueError("a service url (or ssh settings) is required")
         self.transport = HTTPTransport(url, token, timeout)
-        _, self.info = self.transport.request("GET", "/v1/info")     # blocking connect
+        try:
+            _, self.info = self.transport.request("GET", "/v1/info")     # blocking connect
+        except BaseException:
+            if self.tunnel is not None:
+                self.tunnel.close()
+            raise
         self.pool = cf.ThreadPoolExecutor(max_workers=max_workers)
         self.session = uuid.uuid4().hex[:12]
 
@@ -178,6 +195,8 @@ class ServiceClient:
 
     def close(self) -> None:
         self.pool.shutdown(wait=False)
+        if self.tunnel is not None:
+            self.tunnel.close()
 
     def __enter__(self):
         return self

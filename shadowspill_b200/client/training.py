@@ -286,6 +286,21 @@ class TrainingClient:
         return self.pool.submit(work)
 
     # ------------------------------------------------------------------ observations
+    def lookup_request(self, request_id: str, wait_seconds: float = 0.0):
+        """The service's record of a request by the id fixed at submission (``OperationFuture.
+        request_id``): what to do after a lost connection instead of submitting again. Returns the
+        ``TrainingResult`` of a completed request, raises ``OperationFailed`` for a failed or rejected
+        one, and returns ``None`` while it is still pending (``wait_seconds`` > 0 waits that long)."""
+        query = {"wait": "completed", "timeout": min(float(wait_seconds), 120.0)} if wait_seconds > 0 else None
+        _, data = self.transport.request("GET", f"{self.route}/requests/{request_id}", query=query)
+        res = OperationResult(**data)
+        if not res.done:
+            return None
+        if res.state != "completed":
+            raise OperationFailed(res)
+        return TrainingResult(res.loss, res.metrics, res.completed_updates, res.execution_seconds,
+                              res.request_id, res.outputs)
+
     @property
     def metrics(self):
         """Reads of this run's metric journal (``client.metrics.MetricQueries``)."""

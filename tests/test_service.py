@@ -10,7 +10,7 @@ import time
 
 import pytest
 
-from shadowspill_b200.client import (BatchConfig, BatchError, Memory, Model, Optimizer,
+from shadowspill_b200.client import (BatchConfig, BatchError, Memory, Model, Optimizer, TransportError,
                                      OperationFailed, Preparation, ProfilingOptions, Resources,
                                      ServiceClient, text_batch)
 from shadowspill_b200.client.config import PlanningOptions
@@ -600,6 +600,10 @@ def test_prepared_plans_are_exported_and_start_a_run_elsewhere(service, tmp_path
             assert fut.operation == "step" and len(fut.request_id) == 32
             assert fut.accepted().result(60)["request_id"] == fut.request_id
             assert fut.result(60).request_id == fut.request_id
+            again = tr.lookup_request(fut.request_id)               # after a lost reply: ask, do not resubmit
+            assert again.loss == fut.result().loss and again.completed_updates == fut.result().completed_updates
+            with pytest.raises(TransportError):
+                tr.lookup_request("0" * 32)
             progress = " ".join(other.get_progress(tr.run).result()["lines"])
             assert "taken from artifact" in progress and "build, profile and plan skipped" in progress
             assert tr.step(text_batch(_sequences(0))).result().loss > 0
@@ -675,3 +679,27 @@ def test_the_latent_attention_family_trains_through_the_service(service):
             assert tr.save_checkpoint("glm").result().outputs["checkpoint"] == "glm"
         finally:
             tr.close()
+
+
+def test_a_service_is_reached_through_an_owned_ssh_forward(service, monkeypatch):
+    """``ServiceClient(ssh=SSH(...))`` starts the forward in its own process group, talks to the
+    service over it and ends it on close; an ssh that exits says why. (A stand-in plays OpenSSH.)"""
+    import urllib.parse
+    from pathlib import Path
+    from shadowspill_b200.client import SSH, SSHTunnel
+    monkeypatch.setenv("SHADOWSPILL_SSH", str(Path(__file__).with_name("_fake_ssh.py")))
+    port = urllib.parse.urlparse(service.url).port
+    with ServiceClient(token="secret", ssh=SSH("training-host", port)) as svc:
+        assert svc.tunnel.url != service.url and svc.info
+        assert isinstance(svc.list_hardware().result(), dict)
+        proc = svc.tunnel.proc
+        assert proc.poll() is None
+    assert proc.poll() is not None and svc.tunnel.closed            # the forward ended with the client
+    with pytest.raises(ConnectionError, match="No route to host"):
+        SSHTunnel(SSH("unreachable", port), timeout=10).open()
+    with pytest.raises(ValueError):
+        ServiceClient(service.url, token="secret", ssh=SSH("training-host", port))
+    with pytest.raises(ValueError):
+        SSH("-oProxyCommand=evil", port)
+    cmd = SSH("box", 8123, jump_host="bastion", ssh_port=2222, config_file="/tmp/cfg").command(4000)
+    assert cmd[-2:] == ["--", "box"] and "-J" in cmd and "127.0.0.1:4000:127.0.0.1:8123" in cmd and "-F" in cmd
