@@ -1,4 +1,6 @@
-"""Qualification gates: ``python -m shadowspill_b200.qualification.gates [numerical] [performance]``.
+"""Qualification gates: ``python -m shadowspill_b200.qualification.gates [suite] [numerical] [twin] [performance] [determinism]``.
+
+suite        the repository's tests for this machine, in child processes
 
 numerical    planned bf16 execution on the GPU (fp32 on CPU) against an independent resident
              trainer on the same data: 5 updates of 2 heterogeneous microbatches, a checkpoint
@@ -253,9 +255,29 @@ def performance_gate(model: str = "llama3-8b", device_gib: float = 24.0, spill_g
             "group_cycles": cycles, "passed": not failures, "failures": failures}
 
 
+def suite_gate(device: str = "cpu", extra: tuple[str, ...] = ()) -> dict:
+    """The repository's test suite as a gate: the CPU tests always, the GPU tests too when the
+    gates run on a GPU. One child process per marker expression; the record keeps pytest's last
+    line and the exit status. (The reference's gate launcher runs its suite before the numerical
+    and performance gates the same way: qualification/gates/.)"""
+    import subprocess
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[2]
+    runs = []
+    for marker in (["not gpu"] + (["gpu"] if device == "cuda" else [])):
+        cmd = [sys.executable, "-m", "pytest", str(root / "tests"), "-q", "-m", marker, *extra]
+        proc = subprocess.run(cmd, capture_output=True, text=True, cwd=root)
+        tail = [ln for ln in proc.stdout.splitlines() if ln.strip()][-1:] or [""]
+        runs.append({"marker": marker, "exit": proc.returncode, "summary": tail[0]})
+    return {"gate": "suite", "passed": all(r["exit"] == 0 for r in runs), "runs": runs}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m shadowspill_b200.qualification.gates")
-    ap.add_argument("gates", nargs="*", default=["numerical"], choices=["numerical", "performance", "twin"])
+    ap.add_argument("gates", nargs="*", default=["numerical"],
+                    choices=["suite", "numerical", "performance", "twin", "determinism"],
+                    help="run in the order given; suite = the test suite for this machine (CPU tests, plus the "
+                         "GPU tests where a GPU is present); determinism = the bitwise divergence probe")
     ap.add_argument("--frontend", default="stages", choices=["stages", "graph"])
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
     ap.add_argument("--model", default=None)
@@ -263,7 +285,13 @@ def main(argv=None) -> int:
     a = ap.parse_args(argv)
     ok = True
     for gate in a.gates:
-        if gate == "twin":
+        if gate == "suite":
+            rec = suite_gate(a.device)
+        elif gate == "determinism":
+            from .nondeterminism import probe
+            found = probe(a.model or "llama3-tiny", a.device, updates=3, frontend=a.frontend)
+            rec = dict(found, gate="determinism", passed=found["diverged_at"] is None)
+        elif gate == "twin":
             rec = torch_twin_gate(twin_config(a.model or "llama3"), a.device, frontend=a.frontend,
                                   tokens=256 if a.device == "cpu" else 1024)
         elif gate == "numerical":

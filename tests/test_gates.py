@@ -54,3 +54,17 @@ def test_divergence_probe_agrees_on_cpu_and_names_a_flipped_bit():
     dirty = probe("llama3-tiny", "cpu", updates=3, perturb_at=2)
     assert dirty["diverged_at"] == 2 and dirty["tensors"][0]["differing"] == 1
     assert dirty["tensors"][0]["tensor"].startswith("embed") and dirty["tensors"][0]["first_index"] == 0
+
+
+def test_gate_launcher_runs_the_suite_and_the_probe_as_gates(capsys):
+    """``gates suite`` runs pytest in child processes and records their last lines; ``gates
+    determinism`` runs the divergence probe; the exit status is the conjunction."""
+    import json
+    from shadowspill_b200.qualification import gates
+    rec = gates.suite_gate("cpu", extra=("-k", "test_blake3_known_vectors"))
+    assert rec["passed"] and rec["runs"][0]["marker"] == "not gpu" and "passed" in rec["runs"][0]["summary"]
+    bad = gates.suite_gate("cpu", extra=("-k", "no_such_test_anywhere"))
+    assert not bad["passed"]                       # pytest exits 5 when nothing was collected
+    assert gates.main(["determinism", "--device", "cpu"]) == 0
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert out["gate"] == "determinism" and out["passed"] and out["diverged_at"] is None
