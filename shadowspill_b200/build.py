@@ -137,6 +137,37 @@ def build_all(force: bool = False, verbose: bool = False) -> None:
     build_core(force=force, verbose=verbose)
 
 
+def verify() -> dict:
+    """What a fresh checkout should check after building (``python -m shadowspill_b200.build
+    --verify``): the native core loads and its structs have the sizes the Python binding expects,
+    the mock backend runs a plan, the kernel library exports its entry points, the memory daemon
+    and the allocation adapter exist, and (on a machine with a GPU) the CUDA backend opens.
+    Reference: scripts/setup.sh of the reference (build, then verify backend, ABI and adapter)."""
+    import ctypes
+    report: dict = {}
+    from . import native
+    lib = native.core()
+    native.abi_check()                                        # raises ImportError on a struct-size mismatch
+    report["core"] = {"path": str(CORE_LIB), "abi": int(lib.ss_abi_version())}
+    kernels = ctypes.CDLL(str(KERNEL_LIB))
+    wanted = ("ss_gemm_bf16", "ss_gemm2_bf16", "ss_attn_fwd", "ss_attn_bwd", "ss_rs_adamw", "ss_rs_accumulate",
+              "ss_peer_allgather", "ss_adamw_sr")
+    missing = [name for name in wanted if not hasattr(kernels, name)]
+    report["kernels"] = {"path": str(KERNEL_LIB), "missing": missing}
+    root = Path(CORE_LIB).parent
+    report["files"] = {name: (root / name).exists() for name in
+                       ("libss_backend_cuda.so", "libss_allocator.so", "ss_memory_daemon")}
+    import torch
+    report["gpu"] = torch.cuda.is_available()
+    report["ok"] = not missing and all(report["files"].values())
+    return report
+
+
 if __name__ == "__main__":
     build_all(force="--force" in sys.argv, verbose="-v" in sys.argv or "--verbose" in sys.argv)
     print("built:", KERNEL_LIB, CORE_LIB)
+    if "--verify" in sys.argv:
+        import json
+        outcome = verify()
+        print(json.dumps(outcome, indent=1))
+        sys.exit(0 if outcome["ok"] else 1)

@@ -79,3 +79,12 @@ def test_every_native_source_is_part_of_the_build():
     assert {"runtime.cpp", "planner.cpp", "simulator.cpp", "placement.cpp", "staged_lane.cpp",
             "remote_pool.cpp", "backend_mock.cpp", "backend_cuda.cpp", "blake3.cpp", "status.cpp"} <= core
     assert (build.CORE_DIR / "daemon" / "memory_daemon.cpp").exists()
+
+
+def test_build_verification_reports_every_native_artifact():
+    """``python -m shadowspill_b200.build --verify``: the core loads with matching struct sizes, the
+    kernel library exports its entry points, the backend, adapter and daemon are built."""
+    from shadowspill_b200 import build
+    report = build.verify()
+    assert report["ok"] and report["kernels"]["missing"] == [] and report["core"]["abi"] >= 1
+    assert all(report["files"].values())
