@@ -117,7 +117,9 @@ class DecoderConfig:
         return "attention"
 
     def to_json(self) -> dict[str, Any]:
-        return asdict(self)
+        d = asdict(self)
+        d["indexer_types"] = list(self.indexer_types)       # what JSON gives back, so a round trip compares equal
+        return d
 
     @staticmethod
     def from_json(d: dict[str, Any]) -> "DecoderConfig":
