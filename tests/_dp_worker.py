@@ -29,6 +29,12 @@ def main():
     master = arm.startswith("master-")    # fp32 master shards beside the model-dtype shards
     if master:
         arm = arm.split("-", 1)[1]
+    tied = arm.startswith("tied-")        # the head reads, and adds to the gradient of, the embedding
+    if tied:
+        arm = arm.split("-", 1)[1]
+    graph = arm.startswith("graph-")      # stages exported and differentiated by the graph frontend
+    if graph:
+        arm = arm.split("-", 1)[1]
     groups = 1
     if arm.startswith("groups-"):         # microbatches in two sweeps; gradients meet in fp32 shard sums
         groups, arm = 2, arm.split("-", 1)[1]
@@ -59,6 +65,9 @@ def main():
     if expert_parallel:
         from dataclasses import replace
         cfg = replace(preset("olmoe-tiny"), d_model=256, head_dim=64, vocab_size=1024)
+    if tied:
+        from dataclasses import replace
+        cfg = replace(cfg, tied_embeddings=True)
     T, n_mb = 256, 2 * groups
     if fused:
         # matrices large enough for several 256-row tiles and 64-multiple contraction lengths
@@ -68,7 +77,8 @@ def main():
     shard_world = world // replicas
     prog, desc = build_step(cfg, geo, StepDataOrdering(microbatch_groups=groups), dtype=dtype, world_size=shard_world, rank=rank,
                             expert_parallel=expert_parallel, replicas=replicas,
-                            min_shard_bytes=min_shard, master_weights=master, fused_gather=fused)
+                            min_shard_bytes=min_shard, master_weights=master, fused_gather=fused,
+                            frontend="graph" if graph else "stages")
     total = sum(o.bytes for o in prog.objects)
     plan = plan_program(prog, MemoryBudgets(total, 64 << 20, headroom_bytes=0), CommunicationInfo(),
                         SearchOptions(minimum_object_bytes_evict_eligible=1024, workers=1,

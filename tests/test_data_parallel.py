@@ -41,12 +41,16 @@ def test_master_copies_under_sharded_storage():
     _launch(2, "cpu", "master-small-dist", 29661)
 
 
-@pytest.mark.parametrize("arm", ["groups-dist", "groups-lion-small-dist", "groups-master-small-dist"])
+ARMS_WITH_GROUPS = ["groups-dist", "groups-lion-small-dist", "groups-master-small-dist", "graph-groups-dist",
+                    "tied-groups-dist", "tied-graph-groups-small-dist"]
+
+
+@pytest.mark.parametrize("arm", ARMS_WITH_GROUPS)
 def test_microbatch_groups_accumulate_in_shard_space(arm):
     """Four microbatches as two forward + backward sweeps: the first sweep's gradients are
     reduce-scattered into fp32 shard sums, the update after the second sweep starts from them.
     Matches the single-process model on the same eight microbatches."""
-    _launch(2, "cpu", arm, 29671 + 2 * ["groups-dist", "groups-lion-small-dist", "groups-master-small-dist"].index(arm))
+    _launch(2, "cpu", arm, 29671 + 2 * ARMS_WITH_GROUPS.index(arm))
 
 
 def test_whole_parameter_weights_load_into_sharded_ranks():
