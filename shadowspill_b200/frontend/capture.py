@@ -340,6 +340,8 @@ def _build(desc: TrainingDescription) -> Program:
     groups = max(1, int(order.microbatch_groups)) if (sharded and order.walk == "breadth" and step_mode) else 1
     if groups > 1 and n_mb % groups:
         raise ValueError("microbatch_groups must divide the number of microbatches")
+    if groups > 1 and desc.expert_parallel:
+        raise ValueError("microbatch groups are not combined with expert parallelism (not tested together)")
     group_now = [0]
 
     def params_of(si: int, which: str) -> int:

@@ -570,7 +570,7 @@ def moe_experts_bwd_frozen(h: Tensor, logits: Tensor, w13: Tensor, w2: Tensor, g
     if h.is_cuda and F._cuda(h):
         from ..models.autograd_ops import GradSink
         from ..ops import moe as moe_ops
-        sink = GradSink({}, False)
+        sink = GradSink(None, False)         # no buffers: the bank gradients are skipped
         return _autograd_elsewhere(lambda a, b: moe_ops.experts(a, b, w13, w2, k, renorm, sink),
                                    (_c(h), _c(logits)), _c(gy))
     return _autograd_elsewhere(lambda a, b: _moe_torch(a, b, w13, w2, k, renorm), (h, logits), gy)

@@ -149,13 +149,13 @@ class _Experts(torch.autograd.Function):
         _, dwts = lay.combine(ys, None, dots_with=dout, only_dots=True)
         del ys
         dys = lay.gather(dout, wts)                      # w * dout at every assignment
-        if sink is not None and sink.G is not None:
+        if sink is not None and sink.wants("w2"):            # a frozen bank has no gradient buffer
             grouped_wgrad(dys, hm, lay, sink.G["w2"], sink.accumulate("w2"))
         dhm = grouped_linear(dys, w2, lay, transpose=True)
         del dys, hm
         dgu = F.swiglu_bwd(gu, dhm)
         del dhm
-        if sink is not None and sink.G is not None:
+        if sink is not None and sink.wants("w13"):
             grouped_wgrad(dgu, xs, lay, sink.G["w13"], sink.accumulate("w13"))
         dxs = grouped_linear(dgu, w13, lay, transpose=True)
         dh = lay.combine(dxs, None)
