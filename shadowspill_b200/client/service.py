@@ -148,6 +148,26 @@ class ServiceClient:
         from .handles import PlansHandle, upload_artifact
         return self.pool.submit(lambda: PlansHandle(self, None, upload_artifact(self.transport, path, **kw)))
 
+    def wait_ready(self, run: str, timeout: float = 3600.0, progress=None) -> cf.Future:
+        """Waits for a run of this session that is still preparing (a client that lost its
+        connection during ``create_training_client`` or ``prepare_training`` picks the run up again
+        by its id); the future gives the run's info, or raises if the preparation failed."""
+        def work():
+            deadline = time.monotonic() + timeout
+            shown = ProgressDisplay(progress, run)
+            while True:
+                _, info = self.transport.request("GET", f"/v1/runs/{self.session}/{run}")
+                shown.update(self.transport, self.session, info, final=info["state"] != "preparing")
+                if info["state"] != "preparing":
+                    break
+                if time.monotonic() > deadline:
+                    raise TimeoutError("run did not become ready in time")
+                time.sleep(0.2)
+            if info["state"] == "failed":
+                raise RuntimeError(f"run creation failed: {info.get('error', '')}")
+            return info
+        return self.pool.submit(work)
+
     def get_training_client(self, run: str) -> cf.Future:
         """Attaches to a running run as its writer; any earlier writer is fenced."""
         def work():

@@ -265,6 +265,11 @@ class TrainingClient:
     def list_checkpoints(self) -> list[str]:
         return self.transport.request("GET", f"{self.route}/checkpoints")[1]["checkpoints"]
 
+    def checkpoint_manifest(self, name: str) -> cf.Future:
+        """What a saved checkpoint holds, without downloading it: per archive its size, metadata
+        (update count, world size, dtype, generator states) and tensor names."""
+        return self.pool.submit(lambda: self.transport.request("GET", f"{self.route}/checkpoints/{name}/manifest")[1])
+
     def download_checkpoint(self, name: str, directory, **kw) -> cf.Future:
         """Fetches a checkpoint saved by ``save_checkpoint`` (or ``export_weights``) from the
         service and unpacks it under ``directory``; the future gives the unpacked path. The

@@ -244,6 +244,11 @@ def make_handler(server):
                     return self._send(200, server.checkpoint_artifact(p[0], rest[1]))
                 except FileNotFoundError as exc:
                     raise HTTPError(404, str(exc)) from None
+            if len(rest) == 3 and rest[0] == "checkpoints" and rest[2] == "manifest" and method == "GET":
+                try:
+                    return self._send(200, server.checkpoint_manifests(p[0], rest[1]))
+                except FileNotFoundError as exc:
+                    raise HTTPError(404, str(exc)) from None
             if rest == ["checkpoints"] and method == "GET":
                 return self._send(200, {"checkpoints": sorted(live.checkpoints)})
             if rest == ["progress"]:

@@ -403,6 +403,20 @@ class Server:
             raise FileNotFoundError(f"no checkpoint {name!r} in session {session!r}")
         return str(path)
 
+    def checkpoint_manifests(self, session: str, name: str) -> dict[str, Any]:
+        """The manifests of a saved checkpoint (one archive per writing rank) without any tensor
+        bytes: what was saved, in which dtype and geometry, at which update."""
+        from ..checkpoint.archive import read_manifest
+        from ..checkpoint.load import checkpoint_files
+        files = checkpoint_files(self.resolve_checkpoint(session, name))
+        out = []
+        for f in files:
+            m = read_manifest(f)
+            out.append({"file": f.name, "bytes": f.stat().st_size, "metadata": m.get("metadata", {}),
+                        "tensors": len(m.get("tensors", m.get("entries", []))),
+                        "names": sorted(e.get("name", "") for e in m.get("tensors", m.get("entries", [])))[:2000]})
+        return {"checkpoint": name, "files": out}
+
     def unpack_artifact(self, artifact: str) -> Path:
         """Extracts an uploaded, sealed TAR artifact under the artifact store and returns the
         directory that holds its ``*.safetensors`` files."""

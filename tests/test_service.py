@@ -85,6 +85,10 @@ def test_train_checkpoint_resume_through_the_public_api(service, tmp_path_factor
         assert saved.outputs["checkpoint"] == "after5"
         # the checkpoint can be fetched: packed on the service, downloaded with ranges, unpacked
         assert trainer.list_checkpoints() == ["after5"]
+        listing = trainer.checkpoint_manifest("after5").result()
+        assert listing["checkpoint"] == "after5" and len(listing["files"]) == 1
+        assert listing["files"][0]["tensors"] > 10 and "embed.embed" in listing["files"][0]["names"]
+        assert svc.wait_ready(trainer.run).result()["state"] == "ready"
         local = trainer.download_checkpoint("after5", tmp_path_factory.mktemp("dl"), chunk_bytes=200_000).result()
         from shadowspill_b200.checkpoint.load import checkpoint_files, export_weights
         assert len(checkpoint_files(local)) == 1
