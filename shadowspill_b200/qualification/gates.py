@@ -224,9 +224,30 @@ def torch_twin_gate(cfg, device: str = "cuda", updates: int = 5, microbatches: i
             "worst_at": at, "losses": losses, "passed": not failures, "failures": failures}
 
 
+# Recorded floors, tokens/s: (device name fragment, model, device GiB, spill GiB, tokens per step).
+# Each is a few per cent under the slowest measured run of that configuration on that hardware (boxes
+# differ in the clock they sustain under the power cap), so that a pass means "no regression", not luck.
+# The reference records its floors the same way per GPU model (qualification/performance/README.md:69-100:
+# 3,423 / 3,027 / 13,907 tokens/s for these three models on one RTX 5090).
+FLOORS: dict[tuple, float] = {
+    ("B200", "llama3-8b", 24.0, 128.0, 65536): 15_800.0,          # measured 16,289 .. 16,667
+    ("B200", "qwen35-9b", 24.0, 128.0, 65536): 12_500.0,          # measured 13,127
+    ("B200", "olmoe-7b-a1b", 24.0, 128.0, 65536): 45_000.0,       # measured 46,553 .. 48,005
+}
+
+
+def recorded_floor(device_name: str, model: str, device_gib: float, spill_gib: float, tokens: int) -> float | None:
+    for (fragment, m, d, s, t), floor in FLOORS.items():
+        if fragment in device_name and (m, float(d), float(s), int(t)) == (model, float(device_gib), float(spill_gib), int(tokens)):
+            return floor
+    return None
+
+
 def performance_gate(model: str = "llama3-8b", device_gib: float = 24.0, spill_gib: float = 128.0,
                      tokens: int = 65536, microbatch: int = 8192, groups: int = 3, updates: int = 4,
                      floor: float | None = None) -> dict:
+    if floor is None and torch.cuda.is_available():
+        floor = recorded_floor(torch.cuda.get_device_name(0), model, device_gib, spill_gib, tokens)
     setup = TrainingSetup(model=model, device_gib=device_gib, spill_gib=spill_gib, tokens_per_step=tokens,
                           microbatch_tokens=microbatch, lr=1e-5, seed=1,
                           candidate_selections=("100", "0:save_attention"))

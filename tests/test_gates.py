@@ -68,3 +68,10 @@ def test_gate_launcher_runs_the_suite_and_the_probe_as_gates(capsys):
     assert gates.main(["determinism", "--device", "cpu"]) == 0
     out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert out["gate"] == "determinism" and out["passed"] and out["diverged_at"] is None
+
+
+def test_recorded_floors_are_found_by_hardware_and_configuration():
+    from shadowspill_b200.qualification.gates import recorded_floor
+    assert recorded_floor("NVIDIA B200", "llama3-8b", 24, 128, 65536) == 15_800.0
+    assert recorded_floor("NVIDIA B200", "llama3-8b", 48, 128, 65536) is None       # another budget: no floor
+    assert recorded_floor("NVIDIA H100", "llama3-8b", 24, 128, 65536) is None       # another GPU: no floor
