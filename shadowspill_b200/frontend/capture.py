@@ -164,7 +164,7 @@ class TrainingDescription:
             from .graph_stage import build_graph_stages, supports
             if self.cfg.is_latent_attention and not supports(self.cfg, self.lora, ep, self.objective):
                 raise ValueError(f"the {self.cfg.family} family is defined for the graph frontend only, which "
-                                 "does not cover adapters on latent attention, expert parallelism or the router-balance term yet")
+                                 "does not cover expert parallelism or the router-balance term yet")
             if supports(self.cfg, self.lora, ep, self.objective):
                 stages = build_graph_stages(self.cfg, self.geometry.microbatch_tokens, self.geometry.slots,
                                             self.dtype, self.grad_dtype, self.head_block_rows,

@@ -372,8 +372,6 @@ def supports(cfg, lora=None, expert_parallel=None, objective=None) -> bool:
     """Catalog models the ``nn.Module`` families of :mod:`.modules` cover."""
     plain_objective = objective is None or (getattr(objective, "kind", "cross_entropy") == "cross_entropy"
                                             and not getattr(objective, "moe_balance_coef", 0))
-    if cfg.is_latent_attention and lora is not None:
-        return False          # adapters on the absorbed key/value projection are not built
     if lora is not None and cfg.is_moe and lora.routed_experts:
         # ss::moe_experts_lora adapts both banks of frozen experts; other mixes stay on the stage classes
         banks = {"w13", "w2"} & set(lora.targets)

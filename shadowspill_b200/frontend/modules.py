@@ -91,7 +91,11 @@ class _Norms:
             ids = torch.topk(scores + self.router_bias.float(), c.top_k, dim=-1).indices
             picked = torch.gather(scores, 1, ids)
             wts = picked / (picked.sum(-1, keepdim=True) + 1e-20) * c.routed_scaling_factor
-            out = S.moe_experts_routed(h, ids.to(torch.int32), wts, self.w13, self.w2)
+            if "w13" in self.adapted:
+                out = S.moe_experts_routed_lora(h, ids.to(torch.int32), wts, self.w13, self.w2, self.w13_lora_a,
+                                                self.w13_lora_b, self.w2_lora_a, self.w2_lora_b, float(self.lora.scale))
+            else:
+                out = S.moe_experts_routed(h, ids.to(torch.int32), wts, self.w13, self.w2)
         elif "w13" in self.adapted:     # both banks carry per-expert factors (see graph_stage.supports)
             out = S.moe_experts_lora(h, logits, self.w13, self.w2, self.w13_lora_a, self.w13_lora_b,
                                      self.w2_lora_a, self.w2_lora_b, c.top_k, c.router_renormalize,
@@ -335,8 +339,18 @@ class LatentAttentionLayer(nn.Module, _Norms):
         w = self.kv_b.reshape(H, n + dv, L)
         wk, wv = w[:, :n], w[:, n:]
         q_latent = torch.einsum("thd,hdl->thl", query, wk)                   # key projection absorbed into the query
+        adapted = "kv_b" in self.adapted
+        if adapted:
+            # the adapter of the absorbed projection, absorbed the same way: W + s B A splits into the key
+            # rows and the value rows of B, and A (rank x latent) stays on the latent side
+            fa = self.kv_b_lora_a
+            fb = self.kv_b_lora_b.reshape(H, n + dv, fa.shape[0])
+            bk, bv = fb[:, :n], fb[:, n:]
+            q_latent = q_latent + (torch.einsum("thd,hdr->thr", query, bk) @ fa) * self.lora.scale
         attended = S.sparse_latent_attention(q_latent, latent, picks, q_rope, k_rope, float((n + r) ** -0.5))
         value = torch.einsum("thl,hdl->thd", attended, wv)                   # value projection applied after
+        if adapted:
+            value = value + torch.einsum("thr,hdr->thd", attended @ fa.t(), bv) * self.lora.scale
         x = x + self._lin(value.reshape(T, H * dv), "wo")
         return self._mlp(x), picks
 

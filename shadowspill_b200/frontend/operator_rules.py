@@ -78,6 +78,7 @@ for _r in (
     OperatorRule("ss.moe_experts", "compute", None),
     OperatorRule("ss.moe_experts_lora", "compute", None),
     OperatorRule("ss.moe_experts_routed", "compute", None),
+    OperatorRule("ss.moe_experts_routed_lora", "compute", None),
     OperatorRule("ss.sparse_latent_attention", "compute", None),
     OperatorRule("ss.index_topk", "compute", None),
     OperatorRule("ss.rmsnorm", "memory", (0,)),

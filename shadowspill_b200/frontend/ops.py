@@ -892,8 +892,103 @@ def _moe_routed_bwd(ctx, gy):
 moe_experts_routed.register_autograd(_moe_routed_bwd, setup_context=_moe_routed_setup)
 
 
+# ------------------------------------------------------------------------ routed experts, routing given, adapters
+def _moe_routed_lora_torch(h, ids, wts, w13, w2, a13, b13, a2, b2, scale: float) -> Tensor:
+    """``_moe_routed_torch`` with per-expert low-rank factors on both (frozen) banks."""
+    k = ids.shape[1]
+    flat = ids.reshape(-1).long()
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=w13.shape[0]).tolist()
+    tok = order // k
+    w_sorted = wts.reshape(-1)[order].to(h.dtype)
+    out = torch.zeros_like(h)
+    pos = 0
+    for e, n in enumerate(counts):
+        if n == 0:
+            continue
+        rows = tok[pos:pos + n]
+        x = h.index_select(0, rows)
+        gu = x @ w13[e].t() + ((x @ a13[e].t()) @ b13[e].t()) * scale
+        f = gu.shape[1] // 2
+        act = (torch.nn.functional.silu(gu[:, :f].float()).to(h.dtype) * gu[:, f:])
+        y = act @ w2[e].t() + ((act @ a2[e].t()) @ b2[e].t()) * scale
+        out = out.index_add(0, rows, y * w_sorted[pos:pos + n, None])
+        pos += n
+    return out
+
+
+def _moe_routed_lora_cuda(h, ids, wts, w13, w2, a13, b13, a2, b2, scale: float, sink):
+    from ..models import autograd_ops as A
+    from ..ops import moe as moe_ops
+    counts = torch.bincount(ids.reshape(-1).long(), minlength=w13.shape[0]).to(torch.int32)
+    lay = moe_ops.Layout(ids.to(torch.int32).contiguous(), counts)
+    xs = A.expert_gather(h, lay)
+
+    def bank(x, w, a, b, an, bn):
+        low = A.grouped_linear(A.grouped_linear(x, a, lay, sink, an), b, lay, sink, bn)
+        return A.grouped_linear(x, w, lay, None, "") + low * scale
+    ys = bank(A.swiglu(bank(xs, w13, a13, b13, "a13", "b13")), w2, a2, b2, "a2", "b2")
+    return A.expert_combine(ys, wts.float().contiguous(), lay)
+
+
+@custom_op("ss::moe_experts_routed_lora", mutates_args=())
+def moe_experts_routed_lora(h: Tensor, ids: Tensor, wts: Tensor, w13: Tensor, w2: Tensor, a13: Tensor,
+                            b13: Tensor, a2: Tensor, b2: Tensor, scale: float) -> Tensor:
+    with torch.no_grad():
+        if h.is_cuda and F._cuda(h):
+            return _moe_routed_lora_cuda(_c(h), ids, wts, w13, w2, a13, b13, a2, b2, scale, None)
+        return _moe_routed_lora_torch(h, ids, wts, w13, w2, a13, b13, a2, b2, scale)
+
+
+@moe_experts_routed_lora.register_fake
+def _(h, ids, wts, w13, w2, a13, b13, a2, b2, scale):
+    return torch.empty_like(h, memory_format=torch.contiguous_format)
+
+
+@custom_op("ss::moe_experts_routed_lora_bwd", mutates_args=())
+def moe_experts_routed_lora_bwd(h: Tensor, ids: Tensor, wts: Tensor, w13: Tensor, w2: Tensor, a13: Tensor,
+                                b13: Tensor, a2: Tensor, b2: Tensor, gy: Tensor, scale: float
+                                ) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
+    """Gradients of rows, routing weights and the four factor banks; the frozen banks get none."""
+    if h.is_cuda and F._cuda(h):
+        from ..models.autograd_ops import GradSink
+        G = {"a13": torch.zeros_like(a13), "b13": torch.zeros_like(b13),
+             "a2": torch.zeros_like(a2), "b2": torch.zeros_like(b2)}
+        sink = GradSink(G, False)
+        dh, dw = _autograd_elsewhere(
+            lambda x, w: _moe_routed_lora_cuda(x, ids, w, w13, w2, a13, b13, a2, b2, scale, sink),
+            (_c(h), _c(wts)), _c(gy))
+        return dh, dw, G["a13"], G["b13"], G["a2"], G["b2"]
+    return _autograd_elsewhere(
+        lambda x, w, p, q, r, s: _moe_routed_lora_torch(x, ids, w, w13, w2, p, q, r, s, scale),
+        (h, wts, a13, b13, a2, b2), gy)
+
+
+@moe_experts_routed_lora_bwd.register_fake
+def _(h, ids, wts, w13, w2, a13, b13, a2, b2, gy, scale):
+    c = torch.contiguous_format
+    return (torch.empty_like(h, memory_format=c), torch.empty_like(wts, memory_format=c),
+            torch.empty_like(a13), torch.empty_like(b13), torch.empty_like(a2), torch.empty_like(b2))
+
+
+def _moe_routed_lora_setup(ctx, inputs, output):
+    ctx.save_for_backward(*inputs[:9])
+    ctx.scale = inputs[9]
+
+
+def _moe_routed_lora_bwd(ctx, gy):
+    if ctx.needs_input_grad[3] or ctx.needs_input_grad[4]:
+        raise NotImplementedError("ss::moe_experts_routed_lora trains the factors of frozen banks only")
+    g = torch.ops.ss.moe_experts_routed_lora_bwd(*ctx.saved_tensors, gy, ctx.scale)
+    return g[0], None, g[1], None, None, g[2], g[3], g[4], g[5], None
+
+
+moe_experts_routed_lora.register_autograd(_moe_routed_lora_bwd, setup_context=_moe_routed_lora_setup)
+
+
 MEMORY_BOUND = ("ss.rmsnorm", "ss.rope", "ss.swiglu", "ss.l2norm", "ss.conv_silu", "ss.gated_rmsnorm",
                 "ss.embedding")
 # Operators dominated by tensor-core work: keeping their outputs saves real time.
 COMPUTE_BOUND = ("ss.linear", "ss.gemm", "ss.attention", "ss.gated_delta_rule", "ss.head_loss", "ss.moe_experts",
-                 "ss.moe_experts_lora", "ss.sparse_latent_attention", "ss.moe_experts_routed", "ss.index_topk")
+                 "ss.moe_experts_lora", "ss.sparse_latent_attention", "ss.moe_experts_routed", "ss.index_topk",
+                 "ss.moe_experts_routed_lora")

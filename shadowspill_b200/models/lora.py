@@ -15,7 +15,8 @@ from __future__ import annotations
 from dataclasses import asdict, dataclass
 from typing import Any
 
-DENSE_TARGETS = ("wq", "wk", "wv", "wo", "w13", "w2", "w_qkvz", "w_out", "sw13", "sw2")
+DENSE_TARGETS = ("wq", "wk", "wv", "wo", "w13", "w2", "w_qkvz", "w_out", "sw13", "sw2",
+                 "q_a", "q_b", "kv_a", "kv_b")          # the last four: latent-attention projections (GLM)
 
 
 @dataclass(frozen=True)

@@ -127,7 +127,8 @@ def _lora_record(rec: dict | None, is_moe: bool = False) -> dict | None:
     if not rec:
         return None
     from ..models.lora import DENSE_TARGETS, LoRAConfig
-    groups = {"attention": ("wq", "wk", "wv", "wo", "w_qkvz", "w_out"), "mlp": ("w13", "w2", "sw13", "sw2"),
+    groups = {"attention": ("wq", "wk", "wv", "wo", "w_qkvz", "w_out", "q_a", "q_b", "kv_a", "kv_b"),
+              "mlp": ("w13", "w2", "sw13", "sw2"),
               "experts": ("w13", "w2")}
     wanted = rec.get("targets", ("attention", "experts"))
     targets: list[str] = []

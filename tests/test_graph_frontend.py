@@ -511,3 +511,76 @@ def test_sparse_latent_attention_family_on_the_gpu_follows_the_cpu_run():
         ex.close()
     for a, b in zip(losses["cpu"], losses["cuda"]):
         assert abs(a - b) < 2e-2 * max(1.0, abs(a)), losses
+
+
+def test_adapters_on_the_latent_attention_family():
+    """Adapters on the latent projections (the absorbed key/value projection included), the dense
+    and shared feed-forward and both routed banks of the GLM-shaped model: the adapted forward
+    equals the forward with merged weights, only factors train, and three planned updates follow
+    eager PyTorch on the same module."""
+    from shadowspill_b200.frontend.modules import DecoderLM, init_
+    from shadowspill_b200.models.lora import LoRAConfig
+    cfg = preset("glm53-tiny")
+    lora = LoRAConfig(rank=8, alpha=16.0, targets=("q_a", "q_b", "kv_a", "kv_b", "wo", "w13", "w2", "sw13", "sw2"))
+    # ---- merged-weight equivalence, factors made non-trivial
+    model = DecoderLM(cfg, torch.float32, lora=lora)
+    init_(model, 0)
+    gen = torch.Generator().manual_seed(1)
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if n.endswith("_lora_b"):
+                p.copy_(torch.randn(p.shape, generator=gen) * 0.05)
+    merged = DecoderLM(cfg, torch.float32)
+    mine = dict(model.named_parameters())
+    with torch.no_grad():
+        for n, p in merged.named_parameters():
+            w = mine[n].detach().clone()
+            if n + "_lora_a" in mine:
+                w = w + lora.scale * (mine[n + "_lora_b"] @ mine[n + "_lora_a"])
+            p.copy_(w)
+    host = _batches(cfg, 0)
+    m0 = to_device(host[0], "cpu")
+    args = (m0.tokens, m0.targets, m0.weights, m0.positions, m0.cu_seqlens)
+    assert abs(float(model(*args)) - float(merged(*args))) < 1e-5
+    assert all(("_lora_" in n) == p.requires_grad for n, p in model.named_parameters())
+    # ---- planned execution against eager training of the same module
+    prog, desc = build_step(cfg, GEO, StepDataOrdering(), dtype=torch.float32, selection={1: "save"}, lora=lora)
+    stages = desc.stages()
+    ops_of = [op_name(n) for n in stages[2].graph.gm.graph.nodes]
+    assert "ss.moe_experts_routed_lora" in ops_of and "ss.moe_experts_routed" not in ops_of
+    assert not any(t.name.startswith(("O.embed", "O.head", "B.embed")) for t in prog.tasks)
+    plan = _plan(prog)
+    ex = Executor(plan, desc, device="cpu", seed=5, hyper=Hyperparameters(lr=1e-2))
+    ex.initialize()
+    state = ex.state_dict()
+    eager = DecoderLM(cfg, torch.float32, lora=lora)
+    params = dict(eager.named_parameters())
+    names = {}
+    for st, group in zip(stages, ["embed", "layers.0", "layers.1", "head"]):
+        for p in st.params:
+            names[f"{st.name}.{p.name}"] = next(t for t in params if t.startswith(group + ".") and (
+                t.split(".")[-1] == p.name or "_".join(t.split(".")[2:]) == p.name))
+    with torch.no_grad():
+        for k, target in names.items():
+            params[target].copy_(state[k])
+    opt = torch.optim.AdamW([p for p in eager.parameters() if p.requires_grad], lr=1e-2, betas=(0.9, 0.95),
+                            eps=1e-8, weight_decay=0.0)
+    for step in range(3):
+        host = _batches(cfg, step)
+        got = ex.run(host).loss
+        opt.zero_grad()
+        want = 0.0
+        for mb in host:
+            m = to_device(mb, "cpu")
+            loss = eager(m.tokens, m.targets, m.weights, m.positions, m.cu_seqlens)
+            loss.sum().backward()
+            want += float(loss.detach())
+        opt.step()
+        assert abs(got - want) < 5e-4 * max(1.0, abs(want)), (step, got, want)
+    state = ex.state_dict()
+    moved = max(float(state[k].abs().max()) for k in names if k.endswith("_lora_b"))
+    assert moved > 0
+    for k, target in names.items():
+        diff = (state[k] - params[target].detach()).float()
+        assert float(diff.abs().max()) <= 3 * 1e-2 + 1e-6, k
+    ex.close()
