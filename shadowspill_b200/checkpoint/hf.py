@@ -311,3 +311,64 @@ def load_hf(cfg: DecoderConfig, directory: str | Path, stages=None) -> dict[str,
     for f in files:
         hf.update(load_file(str(f)))
     return from_hf(cfg, hf, stages)
+
+
+def stream_hf(cfg: DecoderConfig, directory: str | Path, stages=None):
+    """Bounded loading: yields ``(stage name, {"<stage>.<param>": tensor})`` one stage at a time,
+    reading only that stage's tensors from the ``*.safetensors`` files (memory-mapped, any number
+    of shards), so that a checkpoint far larger than host memory's free part loads with one stage
+    resident. The same checks as ``from_hf``: a missing source tensor, a shape that differs and a
+    checkpoint tensor without a destination are errors (vision towers and extra prediction heads
+    are skipped). Reference: the bounded checkpoint loading of the reference's initialisation
+    (packages/workloads/src/shadowspill_workloads/initialization/: safetensors ranges, local files)."""
+    from safetensors import safe_open
+    d = Path(directory)
+    files = sorted(d.glob("*.safetensors"))
+    if not files:
+        raise FileNotFoundError(f"no .safetensors file in {d}")
+    if stages is None and cfg.is_latent_attention:
+        from ..frontend.graph_stage import build_graph_stages
+        stages = build_graph_stages(cfg, 256, 16)
+    stages = stages or build_stages(cfg)
+    where: dict[str, Path] = {}
+    for f in files:
+        with safe_open(str(f), framework="pt") as handle:
+            for key in handle.keys():
+                where[key] = f
+    sources = parameter_sources(cfg, stages)
+    used: set[str] = set()
+    shapes = {f"{st.name}.{p.name}": tuple(p.shape) for st in stages for p in st.params}
+    for st in stages:
+        part: dict[str, torch.Tensor] = {}
+        opened: dict[Path, object] = {}
+        try:
+            for p in st.params:
+                name = f"{st.name}.{p.name}"
+                src = sources.get(name)
+                if src is None:
+                    continue                            # adapters: not part of a base checkpoint
+                names = src.names
+                if name == "head.head" and "lm_head.weight" not in where:
+                    names = (_prefix(cfg) + "embed_tokens.weight",)
+                missing = [n for n in names if n not in where]
+                if missing:
+                    raise KeyError(f"{name}: checkpoint has no {missing[0]!r}")
+                tensors = []
+                for n in names:
+                    f = where[n]
+                    if f not in opened:
+                        opened[f] = safe_open(str(f), framework="pt").__enter__()
+                    tensors.append(opened[f].get_tensor(n))
+                t = src.load(tensors)
+                if tuple(t.shape) != shapes[name]:
+                    raise ValueError(f"{name}: checkpoint shape {tuple(t.shape)} != {shapes[name]}")
+                part[name] = t
+                used.update(names)
+        finally:
+            for handle in opened.values():
+                handle.__exit__(None, None, None)
+        yield st.name, part
+    extra = [k for k in where if k not in used and not k.startswith(_IGNORED_PREFIXES)
+             and not (cfg.tied_embeddings and k == "lm_head.weight")]
+    if extra:
+        raise ValueError(f"checkpoint tensors with no destination: {sorted(extra)[:4]}")

@@ -500,15 +500,17 @@ class TrainingSession:
         if not (file_spill and setup.spill_image and not setup.spill_create_image):
             self.executor.initialize()      # an opened image already holds the state
         if setup.pretrained:
-            from ..checkpoint.hf import load_hf
             # expert-parallel stages hold local banks: name the whole banks from a plain build
             from ..models.decoder import build_stages as _plain
             naming = (_plain(self.cfg, self.objective, self.lora) if setup.expert_parallel
                       else self.executor.stages)
-            state = load_hf(self.cfg, setup.pretrained, naming)
-            # adapters and anything else the checkpoint does not name keep their initial values;
-            # with several ranks each keeps its slice of every tensor
-            self.executor.load_full_state_dict(state, strict=False)
+            # one stage's tensors at a time (memory-mapped reads): the checkpoint never has to fit in
+            # host memory beside the spill pool. Adapters and anything else the checkpoint does not name
+            # keep their initial values; with several ranks each keeps its slice of every tensor
+            from ..checkpoint.hf import stream_hf
+            for _, part in stream_hf(self.cfg, setup.pretrained, naming):
+                if part:
+                    self.executor.load_full_state_dict(part, strict=False)
             self.log(f"weights from {setup.pretrained}")
         self.timings["open"] = time.perf_counter() - t0
         if cuda:

@@ -319,3 +319,38 @@ def test_latent_attention_family_round_trips_through_hugging_face_names(tmp_path
     back = hf.load_hf(cfg, tmp_path / "glm")
     assert set(back) == set(state)
     assert all(torch.equal(back[k], v) for k, v in state.items())
+
+
+def test_hugging_face_checkpoints_load_one_stage_at_a_time(tmp_path):
+    """``stream_hf`` reads a sharded checkpoint stage by stage and gives what ``load_hf`` gives;
+    a tensor without a destination is still an error, found once everything else was read."""
+    import json
+    import pytest
+    import torch
+    from safetensors.torch import save_file
+    from shadowspill_b200.checkpoint import hf
+    from shadowspill_b200.execution.resident import ResidentTrainer
+    from shadowspill_b200.models.config import preset
+    cfg = preset("qwen35moe-tiny")
+    state = ResidentTrainer(cfg, device="cpu", dtype=torch.float32, seed=3).state_dict()
+    state = {k: v for k, v in state.items() if not k.startswith("exp_avg")}
+    named = hf.to_hf(cfg, state)
+    keys = sorted(named)
+    d = tmp_path / "sharded"
+    d.mkdir()
+    for i in range(3):                                        # three shards, interleaved names
+        save_file({k: named[k].contiguous() for k in keys[i::3]}, str(d / f"model-{i:05d}-of-00003.safetensors"))
+    (d / "config.json").write_text(json.dumps(hf.hf_config(cfg)))
+    whole = hf.load_hf(cfg, d)
+    seen = {}
+    order = []
+    for stage, part in hf.stream_hf(cfg, d):
+        order.append(stage)
+        assert all(k.startswith(stage + ".") for k in part)
+        seen.update(part)
+    assert order[0] == "embed" and order[-1] == "head" and len(order) == cfg.n_layers + 2
+    assert set(seen) == set(whole) == set(state)
+    assert all(torch.equal(seen[k], whole[k]) and torch.equal(seen[k], state[k]) for k in state)
+    save_file({"model.language_model.stray": torch.zeros(2)}, str(d / "model-extra.safetensors"))
+    with pytest.raises(ValueError, match="no destination"):
+        list(hf.stream_hf(cfg, d))
