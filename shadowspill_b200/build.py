@@ -163,11 +163,17 @@ def verify() -> dict:
     return report
 
 
-if __name__ == "__main__":
-    build_all(force="--force" in sys.argv, verbose="-v" in sys.argv or "--verbose" in sys.argv)
+def main(argv=None) -> int:
+    argv = sys.argv[1:] if argv is None else list(argv)
+    build_all(force="--force" in argv, verbose="-v" in argv or "--verbose" in argv)
     print("built:", KERNEL_LIB, CORE_LIB)
-    if "--verify" in sys.argv:
+    if "--verify" in argv:
         import json
         outcome = verify()
         print(json.dumps(outcome, indent=1))
-        sys.exit(0 if outcome["ok"] else 1)
+        return 0 if outcome["ok"] else 1
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
