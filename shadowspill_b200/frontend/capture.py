@@ -466,7 +466,6 @@ def _build(desc: TrainingDescription) -> Program:
 
     body = list(range(S - 1))
     mbs = list(range(n_mb))
-    back_mbs = list(reversed(mbs)) if order.reverse_breadth else mbs
     step = desc.mode == "step"      # from here on: does this program contain the update?
     if order.walk == "breadth":
         per_group = n_mb // groups

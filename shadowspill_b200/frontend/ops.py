@@ -747,7 +747,7 @@ def _sparse_latent_torch(q_latent: Tensor, latent: Tensor, indices: Tensor, q_ro
     """Definition, in blocks of query rows: logits over the picked rows from the latent part and the
     rotary part, softmax over the picks, output = the picked latents weighted (the latent is key and
     value at once; the per-head value projection is applied by the caller)."""
-    T, H, L = q_latent.shape
+    T = q_latent.shape[0]
     outs = []
     block = 512
     safe = indices.clamp_min(0).long()
