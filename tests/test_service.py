@@ -707,3 +707,25 @@ def test_a_service_is_reached_through_an_owned_ssh_forward(service, monkeypatch)
         SSH("-oProxyCommand=evil", port)
     cmd = SSH("box", 8123, jump_host="bastion", ssh_port=2222, config_file="/tmp/cfg").command(4000)
     assert cmd[-2:] == ["--", "box"] and "-J" in cmd and "127.0.0.1:4000:127.0.0.1:8123" in cmd and "-F" in cmd
+
+
+def test_microbatch_groups_through_the_service(service):
+    """Two sharded ranks, four microbatches per rank in two sweeps (``BuildOptions(walks=("breadth/2",))``):
+    the run comes up with that walk and trains."""
+    from shadowspill_b200.client import BuildOptions, data_parallel
+    with ServiceClient(service.url, token="secret") as svc:
+        tr = svc.create_training_client(
+            Model("llama3-tiny", dtype="float32"), Optimizer(lr=3e-3, parameter_rounding="nearest"),
+            batch=BatchConfig(tokens_per_step=1024, microbatch_tokens=256),
+            memory=Memory(device_gib=0.53, spill_gib=0.25), resources=Resources(gpus=2, backend="cpu"),
+            parallelism=data_parallel(2, min_shard_bytes=0),
+            preparation=Preparation(build=BuildOptions(walks=("breadth/2",)),
+                                    profiling=ProfilingOptions(enabled=False), calibrate=False,
+                                    planning=PlanningOptions(minimum_object_bytes_evict_eligible=1024, workers=1)),
+            operations=("step", "forward"), timeout=600).result()
+        try:
+            assert tr.info["workers"] == 2 and "groups2" in tr.info["plan_summary"]["ordering"]
+            losses = [tr.step(text_batch(_sequences(0, n=48))).result().loss for _ in range(4)]
+            assert losses[-1] < losses[0]
+        finally:
+            tr.close()
