@@ -584,3 +584,27 @@ def test_adapters_on_the_latent_attention_family():
         diff = (state[k] - params[target].detach()).float()
         assert float(diff.abs().max()) <= 3 * 1e-2 + 1e-6, k
     ex.close()
+
+
+def test_row_chunks_on_the_latent_attention_family():
+    """Row chunks cut the projections, norms and the feed-forward of the GLM-shaped stages (several
+    layers each) while the indexer, the sparse latent attention and the routed experts stay whole;
+    the chunked program follows the whole one."""
+    cfg = preset("glm53-tiny")
+    whole, desc_w = build_step(cfg, GEO, StepDataOrdering(), dtype=torch.float32)
+    prog, desc = build_step(cfg, GEO, StepDataOrdering(), dtype=torch.float32, axis_chunk_rows=96)
+    for a, b in zip(desc_w.stages()[1:-1], desc.stages()[1:-1]):
+        fa, fb = a.pairs.pairs["recompute"].forward, b.pairs.pairs["recompute"].forward
+        count = lambda g, kind: sum(op_name(n) == kind for n in g.graph.nodes)
+        for kind in ("ss.index_topk", "ss.sparse_latent_attention", "ss.moe_experts_routed"):
+            assert count(fb, kind) == count(fa, kind)
+        assert count(fb, "ss.linear") > count(fa, "ss.linear") and ":rows96" in b.mixer
+
+    def run(program, description):
+        ex = Executor(_plan(program), description, device="cpu", seed=5, hyper=Hyperparameters(lr=3e-3))
+        ex.initialize()
+        losses = [ex.run(_batches(cfg, step)).loss for step in range(3)]
+        ex.close()
+        return losses
+    for a, b in zip(run(whole, desc_w), run(prog, desc)):
+        assert abs(a - b) < 5e-4 * max(1.0, abs(a))        # discrete picks: see the eager comparison above
