@@ -90,11 +90,17 @@ class Optimizer:
     master_dtype: str = "bfloat16"
     parameter_rounding: str = "stochastic"    # nearest | stochastic
     opt_state_rounding: str = "stochastic"
+    # first match wins: ({"match": ["*norm*"], "weight_decay": 0.0}, {"match": ["embed.*"], "lr_scale": 0.1})
+    parameter_groups: tuple = ()
 
     def validate(self):
         require(self.lr >= 0 and 0 <= self.beta1 < 1 and 0 <= self.beta2 < 1, "bad AdamW hyperparameters")
         require(self.parameter_rounding in ("nearest", "stochastic"), "bad parameter_rounding")
         require(self.opt_state_rounding in ("nearest", "stochastic"), "bad opt_state_rounding")
+        for g in self.parameter_groups:
+            require(isinstance(g, dict) and g.get("match") and all(isinstance(m, str) for m in g["match"]),
+                    "a parameter group needs 'match': a list of name patterns")
+            require(set(g) <= {"match", "lr_scale", "weight_decay"}, "parameter group keys: match, lr_scale, weight_decay")
 
 
 @record

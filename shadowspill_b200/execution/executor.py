@@ -43,6 +43,20 @@ class Hyperparameters:
     # reduce-scatter under data parallelism); "sgd" (momentum beta1) and "lion" run as plain
     # tensor operations with round-to-nearest stores
     rule: str = "adamw"
+    # parameter groups: ``(patterns, lr_scale, weight_decay)`` tried in order against
+    # "<stage>.<parameter>" (``fnmatch`` patterns); the first match scales the learning rate and,
+    # unless its weight_decay is None, replaces the decay. The usual use: no decay on norm vectors.
+    # (The reference binds per-group hyperparameters as ``optimizer_group.N.*``:
+    # packages/engine/src/shadowspill/build/optimizer.py:49.)
+    groups: tuple = ()
+
+    def rates(self, name: str) -> tuple[float, float]:
+        """``(learning rate, weight decay)`` of one parameter."""
+        import fnmatch
+        for patterns, lr_scale, decay in self.groups:
+            if any(fnmatch.fnmatchcase(name, pat) for pat in patterns):
+                return self.lr * float(lr_scale), (self.weight_decay if decay is None else float(decay))
+        return self.lr, self.weight_decay
 
 
 @dataclass
@@ -262,9 +276,10 @@ class TaskRunner:
         for p in st.params:
             if not p.trainable:
                 continue
+            lr, wd = h.rates(f"{st.name}.{p.name}")
             if h.rule != "adamw" or "master" in B:
                 from ..ops import reference
-                hyper = dict(lr=h.lr, beta1=h.beta1, beta2=h.beta2, eps=h.eps, weight_decay=h.weight_decay,
+                hyper = dict(lr=lr, beta1=h.beta1, beta2=h.beta2, eps=h.eps, weight_decay=wd,
                              step=self.completed_updates + 1, grad_scale=h.grad_scale)
                 # with master copies the rule runs on the fp32 shard, which is then rounded into
                 # the model-dtype shard (both laid out alike)
@@ -290,16 +305,16 @@ class TaskRunner:
                 if acc is not None:
                     own = own.float() + acc[p.name].view(-1)[:p.numel]
                 F.adamw_(B["params"][p.name][:p.numel], own,
-                         B["m"][p.name][:p.numel], B["v"][p.name][:p.numel], lr=h.lr, beta1=h.beta1,
-                         beta2=h.beta2, eps=h.eps, weight_decay=h.weight_decay,
+                         B["m"][p.name][:p.numel], B["v"][p.name][:p.numel], lr=lr, beta1=h.beta1,
+                         beta2=h.beta2, eps=h.eps, weight_decay=wd,
                          step=self.completed_updates + 1, grad_scale=h.grad_scale, seed=self.seed,
                          offset=self.param_offsets[(stage, p.name)] + p.expert_lo * (p.numel // p.shape[0]),
                          stochastic_param=self.sr, stochastic_state=self.sr)
                 continue
             coll.reduce_scatter_adamw(
                 B["grads"][p.name].view(-1), B["params"][p.name], B["m"][p.name], B["v"][p.name],
-                offset=self.param_offsets[(stage, p.name)], lr=h.lr, beta1=h.beta1, beta2=h.beta2,
-                eps=h.eps, weight_decay=h.weight_decay, step=self.completed_updates + 1,
+                offset=self.param_offsets[(stage, p.name)], lr=lr, beta1=h.beta1, beta2=h.beta2,
+                eps=h.eps, weight_decay=wd, step=self.completed_updates + 1,
                 grad_scale=h.grad_scale, seed=self.seed, stochastic_param=self.sr,
                 stochastic_state=self.sr, whole=st.kept_whole(p, self.desc.dtype),
                 **({} if acc is None else {"acc": acc[p.name]}))
@@ -310,26 +325,27 @@ class TaskRunner:
         for p in st.params:
             if not p.trainable:
                 continue
+            lr, wd = h.rates(f"{st.name}.{p.name}")
             if "master" in B:
                 # fp32 master copy: update it (unfused), then round it into the model-dtype weights
                 from ..ops import reference
                 master = B["master"][p.name].view(-1)
                 reference.update_rule_(h.rule, master, B["grads"][p.name].view(-1),
-                                       B["m"][p.name].view(-1), B["v"][p.name].view(-1), lr=h.lr,
-                                       beta1=h.beta1, beta2=h.beta2, eps=h.eps, weight_decay=h.weight_decay,
+                                       B["m"][p.name].view(-1), B["v"][p.name].view(-1), lr=lr,
+                                       beta1=h.beta1, beta2=h.beta2, eps=h.eps, weight_decay=wd,
                                        step=self.completed_updates + 1, grad_scale=h.grad_scale)
                 B["params"][p.name].view(-1).copy_(master)
                 continue
             if h.rule != "adamw":
                 from ..ops import reference
                 reference.update_rule_(h.rule, B["params"][p.name].view(-1), B["grads"][p.name].view(-1),
-                                       B["m"][p.name].view(-1), B["v"][p.name].view(-1), lr=h.lr,
-                                       beta1=h.beta1, beta2=h.beta2, eps=h.eps, weight_decay=h.weight_decay,
+                                       B["m"][p.name].view(-1), B["v"][p.name].view(-1), lr=lr,
+                                       beta1=h.beta1, beta2=h.beta2, eps=h.eps, weight_decay=wd,
                                        step=self.completed_updates + 1, grad_scale=h.grad_scale)
                 continue
             F.adamw_(B["params"][p.name].view(-1), B["grads"][p.name].view(-1),
-                     B["m"][p.name].view(-1), B["v"][p.name].view(-1), lr=h.lr, beta1=h.beta1,
-                     beta2=h.beta2, eps=h.eps, weight_decay=h.weight_decay,
+                     B["m"][p.name].view(-1), B["v"][p.name].view(-1), lr=lr, beta1=h.beta1,
+                     beta2=h.beta2, eps=h.eps, weight_decay=wd,
                      step=self.completed_updates + 1, grad_scale=h.grad_scale, seed=self.seed,
                      offset=self.param_offsets[(stage, p.name)], stochastic_param=self.sr,
                      stochastic_state=self.sr)

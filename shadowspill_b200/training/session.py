@@ -50,6 +50,9 @@ class TrainingSetup:
     beta2: float = 0.95
     eps: float = 1e-8
     weight_decay: float = 0.0
+    # parameter groups, first match wins: {"match": ["*norm*"], "lr_scale": 1.0, "weight_decay": 0.0}
+    # (patterns against "<stage>.<parameter>"; weight_decay None or absent = the run's own)
+    parameter_groups: tuple = ()
     # adamw | sgd (momentum beta1) | lion, or the captured update of any elementwise
     # torch.optim optimizer (frontend/optimizer_capture.py: capture_optimizer_update)
     optimizer_rule: object = "adamw"
@@ -488,8 +491,10 @@ class TrainingSession:
         from ..ops.reference import RULES
         if setup.optimizer_rule not in RULES and not hasattr(setup.optimizer_rule, "apply"):
             raise ValueError(f"unknown optimizer rule {setup.optimizer_rule!r}; known: {RULES}")
+        groups = tuple((tuple(g.get("match", ())), float(g.get("lr_scale", 1.0)), g.get("weight_decay"))
+                       for g in (dict(x) for x in setup.parameter_groups))
         hyper = Hyperparameters(setup.lr, setup.beta1, setup.beta2, setup.eps, setup.weight_decay,
-                                rule=setup.optimizer_rule)
+                                rule=setup.optimizer_rule, groups=groups)
         self.executor = Executor(self.plan, self.desc, device=setup.device,
                                  device_index=setup.device_index, seed=setup.seed, hyper=hyper,
                                  stochastic_rounding=setup.stochastic_rounding,

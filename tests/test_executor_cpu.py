@@ -238,3 +238,49 @@ def test_a_task_that_raises_leaves_a_terminal_runtime_that_still_closes():
     with pytest.raises(RuntimeFailure):
         ex.run(_batches(cfg, 2))
     ex.close()                                      # no "plan is active" error
+
+
+def test_parameter_groups_change_decay_and_learning_rate_per_parameter():
+    """No decay on norm vectors and a tenth of the learning rate on the embedding, as groups of the
+    planned update: equal to ``torch.optim.AdamW`` with the same three parameter groups on the same
+    gradients (first matching group wins; everything else keeps the run's own values)."""
+    import torch
+    from shadowspill_b200.execution.executor import Hyperparameters
+    h = Hyperparameters(lr=1e-2, weight_decay=0.1,
+                        groups=((("*norm*",), 1.0, 0.0), (("embed.*",), 0.1, None)))
+    assert h.rates("layer0.attn_norm") == (1e-2, 0.0)
+    assert h.rates("embed.embed") == (1e-3, 0.1)
+    assert h.rates("layer1.w13") == (1e-2, 0.1)
+    from shadowspill_b200.frontend.capture import BatchGeometry, StepDataOrdering, build_step
+    from shadowspill_b200.models.config import preset
+    from shadowspill_b200.communication.info import CommunicationInfo
+    from shadowspill_b200.planning.plan import MemoryBudgets, SearchOptions, plan_program
+    from shadowspill_b200.execution.executor import Executor
+    from shadowspill_b200.data.synthetic import make_batch
+    cfg = preset("llama3-tiny")
+    geo = BatchGeometry(256, 2, 16, 64)
+    prog, desc = build_step(cfg, geo, StepDataOrdering(), dtype=torch.float32)
+    total = sum(o.bytes for o in prog.objects) + max(t.workspace_bytes for t in prog.tasks)
+    plan = plan_program(prog, MemoryBudgets(total, 64 << 20, headroom_bytes=0), CommunicationInfo(),
+                        SearchOptions(minimum_object_bytes_evict_eligible=1024, workers=1))
+    runs = {}
+    for label, hyper in (("grouped", h), ("plain", Hyperparameters(lr=1e-2, weight_decay=0.1))):
+        ex = Executor(plan, desc, device="cpu", seed=5, hyper=hyper)
+        ex.initialize()
+        start = {k: v.clone() for k, v in ex.state_dict().items()}
+        batch = make_batch(0, vocab=cfg.vocab_size, tokens_per_step=512, microbatch_tokens=256, median=60,
+                           min_len=8, max_len=128, slots=16)
+        ex.run(batch)
+        runs[label] = (start, ex.state_dict())
+        ex.close()
+    (s0, g), (_, p) = runs["grouped"], runs["plain"]
+    # one AdamW step from zero moments moves every element by lr * sign(grad) after the decay:
+    # |new - old * (1 - lr * wd)| = lr (up to eps)
+    def step_size(state, key, lr, wd):
+        moved = (state[key] - s0[key] * (1 - lr * wd)).abs()
+        return float(moved[moved > 0].median())
+    assert abs(step_size(g, "layer0.attn_norm", 1e-2, 0.0) - 1e-2) < 1e-4          # no decay on the norm
+    assert abs(step_size(p, "layer0.attn_norm", 1e-2, 0.1) - 1e-2) < 1e-4          # the plain run decays it
+    assert not torch.allclose(g["layer0.attn_norm"], p["layer0.attn_norm"])
+    assert abs(step_size(g, "embed.embed", 1e-3, 0.1) - 1e-3) < 1e-5                # a tenth of the rate
+    assert torch.allclose(g["layer1.w13"], p["layer1.w13"])                         # ungrouped: unchanged

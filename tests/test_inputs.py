@@ -43,3 +43,23 @@ def test_objective_inputs_are_required():
     geo = dict(GEO, extra_fields=["old_logprobs"])
     with pytest.raises(InputError):
         validate_microbatches(_mbs(), geo)
+
+
+def test_parameter_groups_travel_from_the_client_record_to_the_worker_setup():
+    import pytest
+    from shadowspill_b200.client import BatchConfig, Memory, Model, Optimizer, Resources
+    from shadowspill_b200.client.config import training_setup
+    from shadowspill_b200.training.components import default_registry, resolve_training
+    groups = ({"match": ["*norm*"], "weight_decay": 0.0}, {"match": ["embed.*"], "lr_scale": 0.1})
+    body = training_setup(Model("llama3-tiny", dtype="float32"), Optimizer(lr=1e-3, weight_decay=0.1, parameter_groups=groups),
+                          batch=BatchConfig(tokens_per_step=512, microbatch_tokens=256),
+                          memory=Memory(device_gib=0.5, spill_gib=0.25), resources=Resources(gpus=1, backend="cpu"))
+    resolved = resolve_training(body, default_registry(), {"gpus": 0, "host_free_gib": 8})
+    assert resolved.setups[0]["parameter_groups"] == [dict(g) for g in groups]
+    from shadowspill_b200.training.phases import setup_from_json
+    setup = setup_from_json(resolved.setups[0])
+    assert setup.parameter_groups[1]["lr_scale"] == 0.1 and setup.weight_decay == 0.1
+    with pytest.raises(ValueError):
+        Optimizer(parameter_groups=({"weight_decay": 0.0},))
+    with pytest.raises(ValueError):
+        Optimizer(parameter_groups=({"match": ["*"], "momentum": 0.9},))
