@@ -159,6 +159,7 @@ class Execution:
     nsys: dict | None = None                  # {start_step, steps, gpu_metrics}: Nsight capture of a few
                                               # steps where the node has nsys (orchestration/capture.py)
     collectives: str = "auto"                 # peer | dist | auto
+    observe_norms: bool = False               # every update's result carries grad_norm and param_norm (one worker)
 
 
 @record

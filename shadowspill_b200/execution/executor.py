@@ -49,6 +49,9 @@ class Hyperparameters:
     # (The reference binds per-group hyperparameters as ``optimizer_group.N.*``:
     # packages/engine/src/shadowspill/build/optimizer.py:49.)
     groups: tuple = ()
+    # report the L2 norms of the final gradients and of the weights, taken just before the update
+    # (single-worker runs: under sharded storage the summed gradient never exists in memory)
+    observe_norms: bool = False
 
     def rates(self, name: str) -> tuple[float, float]:
         """``(learning rate, weight decay)`` of one parameter."""
@@ -95,6 +98,7 @@ class TaskRunner:
         self.extra_fields = tuple(desc.geometry.extra_fields)
         self.batch_layout_, _ = batch_layout(self.T, self.slots, self.extra_fields)
         self.max_seqlen = [2] * self.n_mb
+        self.norm_acc = None          # fp32[2]: sum of squares of gradients, of weights (observe_norms)
         self.uses = [program.sorted_uses(t) for t in range(len(program.tasks))]
         self.completed_updates = 0
         self.accumulated = 0
@@ -320,12 +324,32 @@ class TaskRunner:
                 **({} if acc is None else {"acc": acc[p.name]}))
         coll.barrier_end()                # peers finished reading this rank's gradients
 
+    def norm_buffers(self, device) -> None:
+        """Allocated once, outside any task: the norm observations allocate nothing while a step runs."""
+        self.norm_acc = torch.zeros(2, dtype=torch.float32, device=device)
+        self._norm_partials = torch.zeros(256, dtype=torch.float32, device=device)
+        self._norm_tmp = torch.zeros((), dtype=torch.float32, device=device)
+
+    def _observe(self, grad: torch.Tensor, param: torch.Tensor) -> None:
+        """Adds the squares of one parameter's final gradient and of its weights to the step's sums
+        (reference: packages/engine/src/shadowspill/training/observations.py:14, ``parameter_norms``)."""
+        for slot, x in ((0, grad.reshape(-1)), (1, param.reshape(-1))):
+            if x.is_cuda and x.dtype == torch.bfloat16:
+                F.sumsq(x, self._norm_partials, self.norm_acc[slot:slot + 1], accumulate=True)
+            elif x.is_cuda:                                    # the fp32 vectors: a dot product into a fixed scalar
+                torch.dot(x, x, out=self._norm_tmp)
+                self.norm_acc[slot].add_(self._norm_tmp)
+            else:
+                self.norm_acc[slot] += x.float().square().sum()
+
     def _optimizer(self, stage: int, B) -> None:
         st, h = self.stages[stage], self.hyper
         for p in st.params:
             if not p.trainable:
                 continue
             lr, wd = h.rates(f"{st.name}.{p.name}")
+            if self.norm_acc is not None:
+                self._observe(B["grads"][p.name], B["params"][p.name])
             if "master" in B:
                 # fp32 master copy: update it (unfused), then round it into the model-dtype weights
                 from ..ops import reference
@@ -379,6 +403,9 @@ class Executor:
         self.device_index = device_index
         self.torch_device = torch.device(f"cuda:{device_index}") if self.cuda else torch.device("cpu")
         self.hyper = hyper or Hyperparameters()
+        if self.hyper.observe_norms and desc.world_size > 1:
+            raise ValueError("norm observations are built for single-worker runs: under sharded storage the "
+                             "gradient sum is consumed inside the fused update and never exists as a tensor")
         self.seed = seed
         # `world` / `rank`: the shard group this rank stores state with; with replicas the job has
         # world * replicas ranks and `global_rank` is this rank's index among all of them
@@ -417,6 +444,8 @@ class Executor:
             pc.check_collective_order({"main": plan.program,
                                        **{op: p.program for op, (p, _) in extra_plans.items()}})
         self.runner = TaskRunner(plan.program, desc, self.hyper, seed, stochastic_rounding, coll)
+        if self.hyper.observe_norms:
+            self.runner.norm_buffers(self.torch_device)
         self.stages = self.runner.stages
         self.ep_group = None
         if desc.expert_parallel and self.world > 1:
@@ -494,6 +523,9 @@ class Executor:
 
     def _bind_extra(self, plan: Plan, desc: TrainingDescription, sr: bool) -> dict:
         runner = TaskRunner(plan.program, desc, self.hyper, self.seed, sr, self.collectives)
+        if self.runner.norm_acc is not None:          # one set of observation buffers for every operation's plan
+            runner.norm_acc, runner._norm_partials, runner._norm_tmp = (
+                self.runner.norm_acc, self.runner._norm_partials, self.runner._norm_tmp)
         if self.ep_group is not None:
             self._bind_expert_group(runner)
         obj = {o.name: i for i, o in enumerate(plan.program.objects)}
@@ -917,6 +949,11 @@ class Executor:
         elif self.desc.mode == "forward_backward":
             self.runner.accumulated += 1
         metrics = {}
+        if self.runner.norm_acc is not None and self.desc.mode in ("step", "optimizer"):
+            g2, p2 = (float(v) for v in self.runner.norm_acc.tolist())
+            metrics["grad_norm"] = (g2 ** 0.5) * abs(self.hyper.grad_scale)
+            metrics["param_norm"] = p2 ** 0.5
+            self.runner.norm_acc.zero_()
         aux = [st.aux_sum for st in self.stages if getattr(st, "aux_sum", None) is not None]
         if aux:
             metrics["moe_balance"] = float(sum(float(a.item()) for a in aux))

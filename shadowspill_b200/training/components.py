@@ -262,6 +262,7 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
             "lr": opt.get("lr", 1e-4), "beta1": opt.get("beta1", 0.9), "beta2": opt.get("beta2", 0.95),
             "eps": opt.get("eps", 1e-8), "weight_decay": opt.get("weight_decay", 0.0),
             "parameter_groups": [dict(g) for g in opt.get("parameter_groups", ())],
+            "observe_norms": bool(ex.get("observe_norms", False)),
             "optimizer_rule": registry.get("optimizer", opt["id"]).create()["kind"],
             "seed": int(m.get("weights", {}).get("seed", ex.get("seed", 0))),
             "dtype": m.get("dtype", "bfloat16"), "stochastic_rounding": sr, "device": device,

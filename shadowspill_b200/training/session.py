@@ -53,6 +53,7 @@ class TrainingSetup:
     # parameter groups, first match wins: {"match": ["*norm*"], "lr_scale": 1.0, "weight_decay": 0.0}
     # (patterns against "<stage>.<parameter>"; weight_decay None or absent = the run's own)
     parameter_groups: tuple = ()
+    observe_norms: bool = False          # report grad_norm / param_norm of every update (single-worker runs)
     # adamw | sgd (momentum beta1) | lion, or the captured update of any elementwise
     # torch.optim optimizer (frontend/optimizer_capture.py: capture_optimizer_update)
     optimizer_rule: object = "adamw"
@@ -494,7 +495,7 @@ class TrainingSession:
         groups = tuple((tuple(g.get("match", ())), float(g.get("lr_scale", 1.0)), g.get("weight_decay"))
                        for g in (dict(x) for x in setup.parameter_groups))
         hyper = Hyperparameters(setup.lr, setup.beta1, setup.beta2, setup.eps, setup.weight_decay,
-                                rule=setup.optimizer_rule, groups=groups)
+                                rule=setup.optimizer_rule, groups=groups, observe_norms=bool(setup.observe_norms))
         self.executor = Executor(self.plan, self.desc, device=setup.device,
                                  device_index=setup.device_index, seed=setup.seed, hyper=hyper,
                                  stochastic_rounding=setup.stochastic_rounding,

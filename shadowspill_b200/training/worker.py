@@ -141,7 +141,8 @@ def serve(chan: Channel) -> int:
                     if op == "forward" and res.outputs:
                         from ..client.protocol import encode_array
                         out["outputs"] = {"per_microbatch": [encode_array(a) for a in res.outputs]}
-                    out["metrics"] = {"tokens": res.tokens, "device_seconds": res.device_seconds}
+                    out["metrics"] = {"tokens": res.tokens, "device_seconds": res.device_seconds,
+                                      **{k: float(v) for k, v in (res.metrics or {}).items()}}
                 elif op == "discard":
                     session.executor.discard_gradients()
                 elif op == "save":

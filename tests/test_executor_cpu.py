@@ -284,3 +284,49 @@ def test_parameter_groups_change_decay_and_learning_rate_per_parameter():
     assert not torch.allclose(g["layer0.attn_norm"], p["layer0.attn_norm"])
     assert abs(step_size(g, "embed.embed", 1e-3, 0.1) - 1e-3) < 1e-5                # a tenth of the rate
     assert torch.allclose(g["layer1.w13"], p["layer1.w13"])                         # ungrouped: unchanged
+
+
+def test_norm_observations_report_the_gradient_and_weight_norms_before_the_update():
+    """``Hyperparameters(observe_norms=True)``: the step's result carries the L2 norm of the final
+    (accumulated) gradients and of the weights as they were before the update; compared with eager
+    PyTorch on the same module and batch. Sharded runs refuse the option."""
+    import pytest
+    import torch
+    from shadowspill_b200.communication.info import CommunicationInfo
+    from shadowspill_b200.data.synthetic import make_batch, to_device
+    from shadowspill_b200.execution.executor import Executor, Hyperparameters
+    from shadowspill_b200.frontend.capture import BatchGeometry, StepDataOrdering, build_step
+    from shadowspill_b200.frontend.modules import DecoderLM
+    from shadowspill_b200.models.config import preset
+    from shadowspill_b200.planning.plan import MemoryBudgets, SearchOptions, plan_program
+    cfg = preset("llama3-tiny")
+    geo = BatchGeometry(256, 2, 16, 64)
+    prog, desc = build_step(cfg, geo, StepDataOrdering(), dtype=torch.float32, frontend="graph")
+    total = sum(o.bytes for o in prog.objects) + max(t.workspace_bytes for t in prog.tasks)
+    plan = plan_program(prog, MemoryBudgets(total, 64 << 20, headroom_bytes=0), CommunicationInfo(),
+                        SearchOptions(minimum_object_bytes_evict_eligible=1024, workers=1))
+    ex = Executor(plan, desc, device="cpu", seed=5, hyper=Hyperparameters(lr=1e-3, observe_norms=True))
+    ex.initialize()
+    model = DecoderLM(cfg, torch.float32)
+    state = ex.state_dict()
+    rename = lambda k: ("layers." + k[len("layer"):] if k.startswith("layer") else k)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            p.copy_(next(v for k, v in state.items() if rename(k) == name))
+    batch = make_batch(0, vocab=cfg.vocab_size, tokens_per_step=512, microbatch_tokens=256, median=60, min_len=8,
+                       max_len=128, slots=16)
+    for mb in batch:
+        m = to_device(mb, "cpu")
+        model(m.tokens, m.targets, m.weights, m.positions, m.cu_seqlens).sum().backward()
+    want_g = float(torch.sqrt(sum(p.grad.float().square().sum() for p in model.parameters())))
+    want_p = float(torch.sqrt(sum(p.detach().float().square().sum() for p in model.parameters())))
+    first = ex.run(batch).metrics
+    assert abs(first["grad_norm"] - want_g) < 1e-4 * want_g and abs(first["param_norm"] - want_p) < 1e-5 * want_p
+    second = ex.run(batch).metrics
+    assert second["param_norm"] != first["param_norm"] and second["grad_norm"] > 0      # sums start again every step
+    ex.close()
+    sharded, sdesc = build_step(cfg, geo, StepDataOrdering(), dtype=torch.float32, world_size=2, rank=0)
+    splan = plan_program(sharded, MemoryBudgets(total, 64 << 20, headroom_bytes=0), CommunicationInfo(),
+                         SearchOptions(minimum_object_bytes_evict_eligible=1024, workers=1))
+    with pytest.raises(ValueError, match="single-worker"):
+        Executor(splan, sdesc, device="cpu", hyper=Hyperparameters(observe_norms=True), collectives="dist")

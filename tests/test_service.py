@@ -655,6 +655,27 @@ def test_an_extension_package_adds_components(tmp_path):
         Server(tmp_path / "twice", token="secret", extensions=[name, name])
 
 
+def test_norm_observations_reach_the_client_and_the_metric_journal(service):
+    """``Execution(observe_norms=True)``: every update's result and journal record carry the norms."""
+    from shadowspill_b200.client import Execution
+    with ServiceClient(service.url, token="secret") as svc:
+        tr = svc.create_training_client(
+            Model("llama3-tiny", dtype="float32"), Optimizer(lr=3e-3, parameter_rounding="nearest"),
+            batch=BatchConfig(tokens_per_step=512, microbatch_tokens=256),
+            memory=Memory(device_gib=0.53, spill_gib=0.25), resources=Resources(gpus=1, backend="cpu"),
+            execution=Execution(observe_norms=True),
+            preparation=Preparation(profiling=ProfilingOptions(enabled=False), calibrate=False,
+                                    planning=PlanningOptions(minimum_object_bytes_evict_eligible=1024, workers=1)),
+            timeout=300).result()
+        try:
+            res = tr.step(text_batch(_sequences(0))).result()
+            assert res.metrics["grad_norm"] > 0 and res.metrics["param_norm"] > 1
+            xs, ys = tr.metrics.series("grad_norm")
+            assert ys == [res.metrics["grad_norm"]]
+        finally:
+            tr.close()
+
+
 def test_the_latent_attention_family_trains_through_the_service(service):
     """``glm53-tiny`` by its catalog name: the builder takes the graph frontend for it whatever the
     build option says, layers that share picks become one stage, and steps, accumulation, a forward
