@@ -750,3 +750,37 @@ def test_microbatch_groups_through_the_service(service):
             assert losses[-1] < losses[0]
         finally:
             tr.close()
+
+
+def test_the_read_only_command_line(service, capsys, tmp_path):
+    """``python -m shadowspill_b200.client``: info, components, a run's record, its log and its metric
+    journal (printed or exported), all without touching the run."""
+    import json
+    from shadowspill_b200.client.__main__ import main
+    common = ["--url", service.url, "--token", "secret"]
+    assert main(common + ["info"]) == 0 and json.loads(capsys.readouterr().out)
+    assert main(common + ["components", "--kind", "optimizer"]) == 0
+    listed = capsys.readouterr().out
+    assert "adamw@1" in listed and "shadowspill_b200" in listed and "cross_entropy" not in listed
+    with ServiceClient(service.url, token="secret") as svc:
+        tr = svc.create_training_client(
+            Model("llama3-tiny", dtype="float32"), Optimizer(lr=3e-3, parameter_rounding="nearest"),
+            batch=BatchConfig(tokens_per_step=512, microbatch_tokens=256),
+            memory=Memory(device_gib=0.53, spill_gib=0.25), resources=Resources(gpus=1, backend="cpu"),
+            preparation=Preparation(profiling=ProfilingOptions(enabled=False), calibrate=False,
+                                    planning=PlanningOptions(minimum_object_bytes_evict_eligible=1024, workers=1)),
+            timeout=300).result()
+        try:
+            tr.step(text_batch(_sequences(0))).result()
+            where = [svc.session, tr.run]
+            assert main(common + ["run"] + where) == 0
+            assert json.loads(capsys.readouterr().out)["state"] == "ready"
+            assert main(common + ["progress"] + where) == 0 and "ready" in capsys.readouterr().out
+            assert main(common + ["metrics"] + where) == 0
+            rows = [json.loads(ln) for ln in capsys.readouterr().out.splitlines() if ln.strip()]
+            assert rows and rows[0]["operation"] == "step" and rows[0]["loss"] > 0
+            target = tmp_path / "m.jsonl"
+            assert main(common + ["metrics"] + where + ["--jsonl", str(target)]) == 0
+            assert len(target.read_text().splitlines()) == len(rows)
+        finally:
+            tr.close()
