@@ -119,6 +119,8 @@ def main() -> None:
     ap.add_argument("--walks", default="auto",
                     help="comma list of breadth | depth | breadth/<G> (G sweeps over the microbatches, sharded "
                          "runs only); auto: breadth, and with several GPUs also breadth/2 and breadth/4")
+    ap.add_argument("--collective-overhead-us", type=float, default=0.0,
+                    help="planned cost added to every communication-stream task (see qualification/gap_report.py)")
     ap.add_argument("--lora-rank", type=int, default=0, help="train rank-r adapters on a frozen base")
     ap.add_argument("--expert-parallel", action="store_true",
                     help="multi-GPU runs of routed models: split the experts over the ranks")
@@ -194,6 +196,7 @@ def main() -> None:
                           frontend=args.frontend, allocator=args.allocator, fused_gather=args.fused_gather,
                           axis_chunk_rows=args.axis_chunk_rows, profile_sequence_tokens=args.fixed_len,
                           delta_head_groups=args.delta_head_groups,
+                          collective_overhead_us=args.collective_overhead_us,
                           spill_directory=args.spill_dir if args.spill_pool == "file" else "",
                           spill_address=args.spill_address)
     log = (lambda m: print(f"[bench] {m}", file=sys.stderr, flush=True)) if rank == 0 else None

@@ -60,6 +60,7 @@ class GapReport:
     waits: dict = field(default_factory=dict)
     longest_gaps: list = field(default_factory=list)
     interference: dict = field(default_factory=dict)
+    exposure: dict = field(default_factory=dict)
 
     def to_json(self) -> dict:
         return asdict(self)
@@ -88,6 +89,11 @@ class GapReport:
                     f"{i['beside']['excess_s'] * 1e3:.1f} ms over profile",
                     f"  alone:  {i['alone']['tasks']:>5} tasks, ratio {i['alone']['ratio']:.2f}, "
                     f"{i['alone']['excess_s'] * 1e3:.1f} ms over profile"]
+        e = self.exposure
+        if e:
+            out += ["", f"communication-stream tasks cost the compute lane {e['seconds'] * 1e3:.1f} ms "
+                        f"({e['per_task_us']:.0f} us each over {e['tasks']} tasks; planned with {e['planned_per_task_us']:.0f} us each)",
+                    f"  to plan with the measured figure: collective_overhead_us = {e['suggested_overhead_us']:.0f}"]
         return "\n".join(out)
 
 
@@ -159,6 +165,17 @@ def build(rows: list[Row], simulated_s: float = 0.0) -> GapReport:
             real, prof = sum(r.real_s for r in members), sum(r.profiled_s for r in members)
             rep.interference[name] = {"tasks": len(members), "ratio": real / prof if prof else 0.0,
                                       "excess_s": real - prof}
+        # what the communication lane cost the compute lane: the gaps it caused, plus the slowdown of the
+        # compute tasks beside it relative to how the tasks that ran alone compare with their profiles
+        gaps = sum(v["seconds"] for why, v in rep.waits.items() if "communication lane" in why)
+        base = rep.interference["alone"]["ratio"] or 1.0
+        beside = groups["beside"]
+        slowed = sum(r.real_s for r in beside) - base * sum(r.profiled_s for r in beside)
+        cost = gaps + max(0.0, slowed)
+        planned = sum(s_.profiled_s for s_ in side)
+        rep.exposure = {"seconds": cost, "tasks": len(side), "per_task_us": cost / len(side) * 1e6,
+                        "planned_per_task_us": planned / len(side) * 1e6,
+                        "suggested_overhead_us": max(0.0, (cost - planned) / len(side) * 1e6)}
     return rep
 
 

@@ -35,7 +35,7 @@ def setup_identity(setup, cfg: DecoderConfig) -> str:
     keep = {k: s[k] for k in ("device_gib", "spill_gib", "tokens_per_step", "microbatch_tokens", "slots",
                               "mean_seqlen", "dtype", "world_size", "walks", "recompute_shares",
                               "saved_variant", "candidate_selections", "operations", "device",
-                              "min_shard_bytes", "head_chunks", "frontend", "axis_chunk_rows", "delta_head_groups", "master_weights", "optimizer_rule", "spill_pool", "spill_address", "spill_chunk_bytes", "spill_queue_depth")
+                              "min_shard_bytes", "head_chunks", "frontend", "axis_chunk_rows", "delta_head_groups", "collective_overhead_us", "master_weights", "optimizer_rule", "spill_pool", "spill_address", "spill_chunk_bytes", "spill_queue_depth")
             if k in s}
     keep["model"] = cfg.to_json()
     keep["search"] = s.get("search")

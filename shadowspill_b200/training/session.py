@@ -54,6 +54,10 @@ class TrainingSetup:
     # (patterns against "<stage>.<parameter>"; weight_decay None or absent = the run's own)
     parameter_groups: tuple = ()
     observe_norms: bool = False          # report grad_norm / param_norm of every update (single-worker runs)
+    # added to the planned duration of every task that runs on the communication stream (collectives,
+    # the sharded update): what such a task costs the compute lane beyond the modelled share, as a
+    # traced step shows it (qualification/gap_report.py prints the measured figure)
+    collective_overhead_us: float = 0.0
     # adamw | sgd (momentum beta1) | lion, or the captured update of any elementwise
     # torch.optim optimizer (frontend/optimizer_capture.py: capture_optimizer_update)
     optimizer_rule: object = "adamw"
@@ -225,6 +229,11 @@ class TrainingSession:
 
         def with_replicas(built):
             built[1].replicas = replicas          # programs depend on the shard count only
+            if setup.collective_overhead_us > 0:
+                extra = int(setup.collective_overhead_us * 1e3)
+                for t in built[0].tasks:
+                    if t.kind == "collective" or t.variant == "adamw_dp":
+                        t.duration_ns += extra
             if setup.optimizer_rule != "adamw":
                 # the unfused rules cost (and allocate) differently: keep their profiles apart
                 for t in built[0].tasks:

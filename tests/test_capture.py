@@ -122,6 +122,11 @@ def test_gap_report_separates_lanes_waits_and_interference(tmp_path):
     assert rep.interference["beside"]["tasks"] == 1 and abs(rep.interference["beside"]["ratio"] - 1.4) < 1e-9
     assert rep.interference["alone"]["tasks"] == 3 and abs(rep.interference["alone"]["ratio"] - 1.0) < 1e-9
     assert abs(rep.makespan_s - 0.052) < 1e-9 and "measured 52.0 ms, simulated 45.0 ms" in rep.text()
+    # the communication lane cost the compute lane the 6 ms gap and the 4 ms by which the task beside the
+    # gather ran over its profile: 10 ms over 3 tasks, planned with 1 ms each
+    assert abs(rep.exposure["seconds"] - 0.010) < 1e-9 and rep.exposure["tasks"] == 3
+    assert abs(rep.exposure["suggested_overhead_us"] - (0.010 - 0.003) / 3 * 1e6) < 1e-3
+    assert "collective_overhead_us = 2333" in rep.text()
     # without collectives the update belongs to the compute lane
     solo = build([Row(0, "B.layer0.0", "backward", 0.01, 0.01, 0.0, 0.01), Row(1, "O.layer0", "optimizer", 0.001, 0.001, 0.012, 0.001)])
     assert "communication" not in solo.lanes and solo.waits["host (frontend late)"]["count"] == 1
