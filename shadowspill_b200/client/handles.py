@@ -133,6 +133,12 @@ class PlansHandle:
         return self._service.pool.submit(
             lambda: self._service.transport.request("POST", route, {"name": name, "plan": operation})[1])
 
+    def named(self, name: str):
+        """The plan a name was given to with ``save`` (its operation and summary)."""
+        route = self._route()
+        return self._service.pool.submit(
+            lambda: self._service.transport.request("GET", route, query={"name": name})[1])
+
     def export(self, path, **kw):
         """Downloads the prepared bundle into ``path`` (a new file); the future gives the path."""
         route = self._route()

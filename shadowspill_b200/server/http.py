@@ -259,6 +259,14 @@ def make_handler(server):
                     body = self._json()
                     live.plan_names[body["name"]] = body.get("plan", "step")
                     return self._send(200, {"plans": live.plan_names})
+                if "name" in q:                       # the plan a name was given to
+                    op = live.plan_names.get(q["name"])
+                    if op is None:
+                        raise HTTPError(404, f"no plan named {q['name']!r}")
+                    summary = live.plan_summary if op == "step" else live.operation_plans.get(op)
+                    if summary is None:
+                        raise HTTPError(404, f"plan {q['name']!r} names operation {op!r}, which this run did not plan")
+                    return self._send(200, {"name": q["name"], "operation": op, "plan": summary})
                 page = int(q.get("page", 0))
                 rows = [{"operation": "step", **live.plan_summary}]
                 rows += [{"operation": op, **summary} for op, summary in sorted(live.operation_plans.items())]

@@ -586,6 +586,10 @@ def test_prepared_plans_are_exported_and_start_a_run_elsewhere(service, tmp_path
         page = plans.summary().result()
         assert page["plans"][0]["operation"] == "step" and page["plans"][0]["duration_seconds"] > 0
         assert plans.save(name="baseline").result()["plans"] == {"baseline": "step"}
+        found = plans.named("baseline").result()
+        assert found["operation"] == "step" and found["plan"]["duration_seconds"] == page["plans"][0]["duration_seconds"]
+        with pytest.raises(TransportError):
+            plans.named("never-saved").result()
         with pytest.raises(ValueError):
             plans.save(name="a/b")
         bundle = plans.export(tmp_path / "plans.tar").result()
