@@ -55,9 +55,11 @@ class ProgressDisplay:
 
 class ServiceClient:
     def __init__(self, url: str | None = None, token: str = "", timeout: float = 600.0, max_workers: int = 8,
-                 ssh=None):
+                 ssh=None, session: str | None = None):
         """``ssh`` (a ``client.transport.SSH``): reach the service through an OpenSSH forward that this
-        client owns and closes with itself; ``url`` is then not given."""
+        client owns and closes with itself; ``url`` is then not given. ``session``: the id of an earlier
+        client's session (``ServiceClient.session``), to reach its runs again from another process:
+        ``get_training_client(run)`` then attaches as the run's writer and fences the earlier one."""
         self.tunnel = None
         if ssh is not None:
             if url:
@@ -75,7 +77,9 @@ class ServiceClient:
                 self.tunnel.close()
             raise
         self.pool = cf.ThreadPoolExecutor(max_workers=max_workers)
-        self.session = uuid.uuid4().hex[:12]
+        if session is not None and (not isinstance(session, str) or not session.isalnum() or len(session) > 64):
+            raise ValueError("a session id is a short alphanumeric string")
+        self.session = session or uuid.uuid4().hex[:12]
 
     # ------------------------------------------------------------------ discovery
     def list_hardware(self) -> cf.Future:

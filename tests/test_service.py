@@ -167,7 +167,15 @@ def test_newer_writer_fences_the_older_one(service):
         with pytest.raises(TransportError) as e:
             first.step(text_batch(_sequences(2))).result()
         assert e.value.status == 409 and "fenced" in str(e.value)
-        second.close()
+        # another process: a new client that adopts the session id reaches the run and takes it over
+        with ServiceClient(service.url, token="secret", session=svc.session) as later:
+            third = later.get_training_client(first.run).result()
+            assert third.step(text_batch(_sequences(3))).result().completed_updates == 3
+            with pytest.raises(TransportError):
+                second.step(text_batch(_sequences(4))).result()
+            third.close()
+        with pytest.raises(ValueError):
+            ServiceClient(service.url, token="secret", session="../elsewhere")
 
 
 def test_lora_run_through_the_service(service):
