@@ -195,6 +195,7 @@ class PlanningOptions:
     max_repairs: int = 16
     minimum_object_bytes_evict_eligible: int = 1 << 20
     deterministic: bool = False
+    collective_overhead_us: float = 0.0       # planned cost added to every communication-stream task
 
 
 @record

@@ -200,6 +200,22 @@ def exposed_collective_ns(nbytes: float, world: int) -> int:
     return int(0.25 * remote / 700e9 * 1e9) + 20_000
 
 
+def add_collective_overhead(program: Program, microseconds: float) -> int:
+    """Adds ``microseconds`` to the planned duration of every task that runs on the communication
+    stream (collectives and the sharded update); returns how many tasks that was. The figure comes
+    from a traced step (``qualification/gap_report.py``): what such a task costs the compute lane
+    beyond the modelled share of its NVLink time."""
+    extra = int(microseconds * 1e3)
+    touched = 0
+    if extra <= 0:
+        return 0
+    for t in program.tasks:
+        if t.kind == "collective" or t.variant == "adamw_dp":
+            t.duration_ns += extra
+            touched += 1
+    return touched
+
+
 def _build(desc: TrainingDescription) -> Program:
     cfg, geo, order = desc.cfg, desc.geometry, desc.ordering
     stages = desc.stages()

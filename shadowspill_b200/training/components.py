@@ -263,6 +263,7 @@ def resolve_training(body: dict[str, Any], registry: Registry, hardware: dict[st
             "eps": opt.get("eps", 1e-8), "weight_decay": opt.get("weight_decay", 0.0),
             "parameter_groups": [dict(g) for g in opt.get("parameter_groups", ())],
             "observe_norms": bool(ex.get("observe_norms", False)),
+            "collective_overhead_us": float(planning.get("collective_overhead_us", 0.0)),
             "optimizer_rule": registry.get("optimizer", opt["id"]).create()["kind"],
             "seed": int(m.get("weights", {}).get("seed", ex.get("seed", 0))),
             "dtype": m.get("dtype", "bfloat16"), "stochastic_rounding": sr, "device": device,

@@ -230,10 +230,8 @@ class TrainingSession:
         def with_replicas(built):
             built[1].replicas = replicas          # programs depend on the shard count only
             if setup.collective_overhead_us > 0:
-                extra = int(setup.collective_overhead_us * 1e3)
-                for t in built[0].tasks:
-                    if t.kind == "collective" or t.variant == "adamw_dp":
-                        t.duration_ns += extra
+                from ..frontend.capture import add_collective_overhead
+                add_collective_overhead(built[0], setup.collective_overhead_us)
             if setup.optimizer_rule != "adamw":
                 # the unfused rules cost (and allocate) differently: keep their profiles apart
                 for t in built[0].tasks:

@@ -139,3 +139,22 @@ def test_gap_report_separates_lanes_waits_and_interference(tmp_path):
         for r in rows:
             w.writerow([r.index, r.name, r.kind, 0, 0, r.profiled_s, 0, r.simulated_s, r.start_s, r.real_s, 0, 0, 0, 0])
     assert from_directory(tmp_path).waits == rep.waits
+
+
+def test_collective_overhead_is_added_to_communication_stream_tasks_only():
+    import torch
+    from shadowspill_b200.frontend.capture import (BatchGeometry, StepDataOrdering, add_collective_overhead,
+                                                   build_step)
+    from shadowspill_b200.models.config import preset
+    geo = BatchGeometry(256, 4, 16, 64)
+    prog, _ = build_step(preset("llama3-tiny"), geo, StepDataOrdering(microbatch_groups=2), dtype=torch.float32,
+                         world_size=2, rank=0)
+    before = {t.name: t.duration_ns for t in prog.tasks}
+    side = [t for t in prog.tasks if t.kind == "collective" or t.variant == "adamw_dp"]
+    assert {t.name.split(".")[0] for t in side} == {"AG", "RS", "O"}
+    assert add_collective_overhead(prog, 250.0) == len(side)
+    for t in prog.tasks:
+        assert t.duration_ns - before[t.name] == (250_000 if t in side else 0)
+    assert add_collective_overhead(prog, 0.0) == 0
+    solo, _ = build_step(preset("llama3-tiny"), geo, StepDataOrdering(), dtype=torch.float32)
+    assert add_collective_overhead(solo, 250.0) == 0              # one worker: nothing runs on that stream
