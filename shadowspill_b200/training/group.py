@@ -30,6 +30,40 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
+class BoundedLog(threading.Thread):
+    """Copies a worker's output into its log file up to ``limit`` bytes, says once that the limit
+    was reached, and keeps draining the pipe after that so that a chatty worker never blocks on a
+    full pipe or fills the service's disk. (The reference bounds its worker logs the same way:
+    packages/engine/src/shadowspill/orchestration/launch/log_files.py.)"""
+
+    def __init__(self, stream, path, limit: int):
+        super().__init__(daemon=True, name=f"worker-log:{Path(path).name}")
+        self.stream, self.path, self.limit = stream, Path(path), max(1024, int(limit))
+        self.written = self.path.stat().st_size if self.path.exists() else 0
+        self.dropped = 0
+
+    def run(self) -> None:
+        noted = False
+        with open(self.path, "ab", buffering=0) as out:
+            while True:
+                block = self.stream.read1(65536) if hasattr(self.stream, "read1") else self.stream.read(65536)
+                if not block:
+                    break
+                room = self.limit - self.written
+                if room > 0:
+                    out.write(block[:room])
+                    self.written += min(room, len(block))
+                if len(block) > max(room, 0):
+                    self.dropped += len(block) - max(room, 0)
+                    if not noted:
+                        out.write(f"\n[log limit of {self.limit} bytes reached; later output is dropped]\n".encode())
+                        noted = True
+        try:
+            self.stream.close()
+        except OSError:
+            pass
+
+
 class WorkerGroup:
     def __init__(self, setups: list[dict], log_dir: str | Path, checkpoint: str | None = None,
                  startup_seconds: float = 1800.0, on_progress=None):
@@ -47,7 +81,7 @@ class WorkerGroup:
             to_child_r, to_child_w = os.pipe()
             from_child_r, from_child_w = os.pipe()
             env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
-            log = open(self.log_dir / f"worker{rank}.log", "ab")
+            limit = int(setup.get("max_worker_log_bytes") or os.environ.get("SHADOWSPILL_WORKER_LOG_BYTES", 64 << 20))
             command = [sys.executable, "-m", "shadowspill_b200.training.worker", "--control-fd",
                        f"{to_child_r},{from_child_w}"]
             from ..orchestration import capture
@@ -58,7 +92,8 @@ class WorkerGroup:
                 self.on_progress(f"[rank={rank}] nsys capture requested but {nsys.executable} is not "
                                  f"installed; running unprofiled")
             proc = subprocess.Popen(command, pass_fds=(to_child_r, from_child_w), env=env,
-                                    stdout=log, stderr=subprocess.STDOUT, cwd=root)
+                                    stdout=subprocess.PIPE, stderr=subprocess.STDOUT, cwd=root)
+            BoundedLog(proc.stdout, self.log_dir / f"worker{rank}.log", limit).start()
             os.close(to_child_r); os.close(from_child_w)
             chan = Channel(from_child_r, to_child_w)
             chan.send({"type": "launch", "rank": rank, "world_size": self.world, "setup": setup,

@@ -158,3 +158,28 @@ def test_collective_overhead_is_added_to_communication_stream_tasks_only():
     assert add_collective_overhead(prog, 0.0) == 0
     solo, _ = build_step(preset("llama3-tiny"), geo, StepDataOrdering(), dtype=torch.float32)
     assert add_collective_overhead(solo, 250.0) == 0              # one worker: nothing runs on that stream
+
+
+def test_worker_logs_are_bounded(tmp_path):
+    """A worker's output is copied into its log up to the limit, a note marks the cut, and the pipe
+    keeps being drained so that the writer never blocks."""
+    import subprocess
+    import sys
+    from shadowspill_b200.training.group import BoundedLog
+    chatty = ("import sys\n"
+              "for i in range(20000):\n"
+              "    sys.stdout.write('line %06d of worker output\\n' % i)\n"
+              "sys.stdout.flush()\n"
+              "print('done')\n")
+    proc = subprocess.Popen([sys.executable, "-c", chatty], stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    log = BoundedLog(proc.stdout, tmp_path / "worker0.log", 4096)
+    log.start()
+    assert proc.wait(timeout=60) == 0                     # 540 kB of output never blocked on the pipe
+    log.join(timeout=30)
+    text = (tmp_path / "worker0.log").read_bytes()
+    assert text.startswith(b"line 000000") and b"log limit of 4096 bytes reached" in text
+    assert len(text) < 4096 + 200 and log.dropped > 500_000
+    quiet = subprocess.Popen([sys.executable, "-c", "print('short')"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    small = BoundedLog(quiet.stdout, tmp_path / "worker1.log", 4096)
+    small.start(); quiet.wait(timeout=60); small.join(timeout=30)
+    assert (tmp_path / "worker1.log").read_text() == "short\n" and small.dropped == 0
